@@ -1,0 +1,385 @@
+// C-ABI window onto the UNMODIFIED reference headers (TEST INFRASTRUCTURE ONLY).
+//
+// Built by oracle/Makefile into oracle/_ref/libp3ref.so with the reference's
+// header directory on the include path; no reference source is copied here.
+// The host entry points run anywhere (they are the pins for oracle/zkh_oracle.c
+// and the source of tests/golden/); the *_gpu entry points call the
+// reference's own CUDA code paths and only work on a machine with a GPU,
+// where they serve as the "reference CUDA prover" for parity at large sizes
+// and as a timing baseline.  Nothing in the product library links to this.
+//
+// Serialised layouts are the ones documented in oracle/zkh_oracle.h.
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <vector>
+#include "p3_goldilocks.cuh"
+#include "fs_transcript.hpp"
+#include "p3_fri.cuh"
+#include "p3_basefold.cuh"
+#include "p3_scgpu.cuh"
+#include "p3_gkr.cuh"
+#include "p3_logup.cuh"
+#include "p3_hawkeye.cuh"
+#include "p3_int_gadgets.cuh"
+
+namespace {
+fs::Transcript tr_from(const uint8_t st[32]) {
+    fs::Transcript tr(std::string(""));
+    memcpy(tr.state, st, 32);
+    return tr;
+}
+void put(uint8_t*& p, const void* src, size_t n) { memcpy(p, src, n); p += n; }
+
+size_t bf_size(uint32_t v, uint32_t R, uint32_t Q) {
+    size_t s = 12 + (size_t)v * 32 + (size_t)v * 24 + ((size_t)8 << R);
+    for (uint32_t r = 0; r < v; r++) s += (size_t)Q * (16 + 2 * (size_t)(v + R - r) * 32);
+    return s + (size_t)v * 8 + 8;
+}
+size_t bf_serialize(const p3bf::EvalProof& pf, uint8_t* out, size_t cap) {
+    size_t need = bf_size(pf.logN, pf.R, pf.Q);
+    if (!out) return need;
+    if (cap < need) return 0;
+    uint8_t* p = out;
+    put(p, &pf.logN, 4); put(p, &pf.R, 4); put(p, &pf.Q, 4);
+    for (auto& h : pf.roots) put(p, h.data(), 32);
+    for (auto& m : pf.msgs) put(p, &m, 24);
+    put(p, pf.final_word.data(), pf.final_word.size() * 8);
+    for (auto& q : pf.queries)
+        for (auto& ro : q.rounds) {
+            put(p, &ro.a, 8); put(p, &ro.b, 8);
+            for (auto& h : ro.pa) put(p, h.data(), 32);
+            for (auto& h : ro.pb) put(p, h.data(), 32);
+        }
+    put(p, pf.z.data(), pf.z.size() * 8);
+    put(p, &pf.y, 8);
+    return (size_t)(p - out);
+}
+bool bf_deserialize(const uint8_t* in, size_t len, p3bf::EvalProof& pf) {
+    if (len < 12) return false;
+    const uint8_t* p = in;
+    memcpy(&pf.logN, p, 4); memcpy(&pf.R, p + 4, 4); memcpy(&pf.Q, p + 8, 4); p += 12;
+    uint32_t v = pf.logN, R = pf.R, Q = pf.Q;
+    if (v > 40 || R > 8 || len != bf_size(v, R, Q)) return false;
+    pf.roots.resize(v);
+    for (auto& h : pf.roots) { memcpy(h.data(), p, 32); p += 32; }
+    pf.msgs.resize(v);
+    for (auto& m : pf.msgs) { memcpy(&m, p, 24); p += 24; }
+    pf.final_word.resize((size_t)1 << R);
+    memcpy(pf.final_word.data(), p, pf.final_word.size() * 8); p += pf.final_word.size() * 8;
+    pf.queries.resize(Q);
+    for (auto& q : pf.queries) {
+        q.rounds.resize(v);
+        for (uint32_t r = 0; r < v; r++) {
+            auto& ro = q.rounds[r];
+            memcpy(&ro.a, p, 8); memcpy(&ro.b, p + 8, 8); p += 16;
+            uint32_t plen = v + R - r;
+            ro.pa.resize(plen); ro.pb.resize(plen);
+            for (auto& h : ro.pa) { memcpy(h.data(), p, 32); p += 32; }
+            for (auto& h : ro.pb) { memcpy(h.data(), p, 32); p += 32; }
+        }
+    }
+    pf.z.resize(v);
+    memcpy(pf.z.data(), p, (size_t)v * 8); p += (size_t)v * 8;
+    memcpy(&pf.y, p, 8);
+    return true;
+}
+size_t gkr_size(uint32_t L) {
+    size_t s = 16;
+    for (uint32_t h = L; h >= 1; h--) s += 4 + (size_t)(L - h) * 32 + 32;
+    return s;
+}
+size_t gkr_serialize(const p3gkr::Proof& pf, uint8_t* out, size_t cap) {
+    uint32_t L = (uint32_t)pf.lay.size();
+    if (cap < gkr_size(L)) return 0;
+    uint8_t* p = out;
+    put(p, &pf.P, 8); put(p, &pf.Q, 8);
+    for (auto& ly : pf.lay) {
+        uint32_t nm = (uint32_t)ly.msgs.size();
+        put(p, &nm, 4);
+        for (auto& m : ly.msgs) put(p, &m, 32);
+        gl_t t[4] = {ly.p0, ly.p1, ly.q0, ly.q1};
+        put(p, t, 32);
+    }
+    return (size_t)(p - out);
+}
+bool gkr_deserialize(const uint8_t* in, size_t len, uint32_t L, p3gkr::Proof& pf) {
+    if (len != gkr_size(L)) return false;
+    const uint8_t* p = in;
+    memcpy(&pf.P, p, 8); memcpy(&pf.Q, p + 8, 8); p += 16;
+    pf.lay.resize(L);
+    for (auto& ly : pf.lay) {
+        uint32_t nm; memcpy(&nm, p, 4); p += 4;
+        if (nm > L) return false;
+        ly.msgs.resize(nm);
+        for (auto& m : ly.msgs) { memcpy(&m, p, 32); p += 32; }
+        gl_t t[4]; memcpy(t, p, 32); p += 32;
+        ly.p0 = t[0]; ly.p1 = t[1]; ly.q0 = t[2]; ly.q1 = t[3];
+    }
+    return true;
+}
+struct FProd2 { static __device__ gl_t eval(const gl_t* c, const gl_t*) { return gl_mul(c[0], c[1]); } };
+struct M3 { gl_t s[3]; };
+struct M4 { gl_t s[4]; };
+struct M5 { gl_t s[5]; };
+}  // namespace
+
+extern "C" {
+
+// ---- field ----
+uint64_t ref_gl_add(uint64_t a, uint64_t b) { return gl_add(a, b); }
+uint64_t ref_gl_sub(uint64_t a, uint64_t b) { return gl_sub(a, b); }
+uint64_t ref_gl_mul(uint64_t a, uint64_t b) { return gl_mul(a, b); }
+uint64_t ref_gl_pow(uint64_t a, uint64_t e) { return gl_pow(a, e); }
+uint64_t ref_gl_inv(uint64_t a) { return gl_inv(a); }
+uint64_t ref_gl_root_of_unity(uint32_t logn) { return gl_root_of_unity(logn); }
+
+// ---- hashing / transcript ----
+void ref_sha256(const void* d, size_t n, uint8_t out[32]) { fs::sha256(d, n, out); }
+void ref_sha256_compress64(const uint8_t in[64], uint8_t out[32]) { p3_sha256_compress64(in, out); }
+void ref_tr_init(uint8_t st[32], const void* seed, size_t n) {
+    fs::Transcript tr(std::string((const char*)seed, n));
+    memcpy(st, tr.state, 32);
+}
+void ref_tr_absorb(uint8_t st[32], const char* label, const void* data, uint64_t len) {
+    fs::Transcript tr = tr_from(st);
+    tr.absorb(label, data, (size_t)len);
+    memcpy(st, tr.state, 32);
+}
+void ref_tr_challenge_bytes(uint8_t st[32], uint8_t out[32]) {
+    fs::Transcript tr = tr_from(st);
+    tr.challenge_bytes(out);
+    memcpy(st, tr.state, 32);
+}
+uint64_t ref_tr_chal(uint8_t st[32]) {
+    fs::Transcript tr = tr_from(st);
+    gl_t a = p3sg::chal(tr);
+    memcpy(st, tr.state, 32);
+    return a;
+}
+uint64_t ref_tr_idx(uint8_t st[32], uint64_t mod) {
+    fs::Transcript tr = tr_from(st);
+    uint64_t a = p3fri::idx_from(tr, mod);
+    memcpy(st, tr.state, 32);
+    return a;
+}
+
+// ---- multilinear helpers ----
+void ref_build_eq(const uint64_t* z, uint32_t v, uint64_t* out) {
+    std::vector<gl_t> zz(z, z + v);
+    auto w = p3bf::build_eq(zz);
+    memcpy(out, w.data(), w.size() * 8);
+}
+uint64_t ref_eval_h(const uint64_t* c, const uint64_t* eq, size_t n) {
+    return p3bf::eval_h(std::vector<gl_t>(c, c + n), std::vector<gl_t>(eq, eq + n));
+}
+uint64_t ref_quad_eval(uint64_t s0, uint64_t s1, uint64_t s2, uint64_t t) {
+    return p3bf::quad_eval(s0, s1, s2, t);
+}
+uint64_t ref_cubic_eval(uint64_t s0, uint64_t s1, uint64_t s2, uint64_t s3, uint64_t t) {
+    return p3lu::cubic_eval(s0, s1, s2, s3, t);
+}
+uint64_t ref_quartic_eval(const uint64_t s[5], uint64_t t) {
+    p3hwl::Msg5 m{s[0], s[1], s[2], s[3], s[4]};
+    return p3hwl::quartic_eval(m, t);
+}
+uint64_t ref_eq_point(const uint64_t* a, const uint64_t* z, uint32_t v) {
+    return p3bf::eq_point(std::vector<gl_t>(a, a + v), std::vector<gl_t>(z, z + v));
+}
+
+// ---- encode / merkle / fold (host paths) ----
+void ref_rs_encode_horner(const uint64_t* c, uint32_t v, uint32_t R, uint64_t* cw) {
+    auto w = p3bf::rs_encode(std::vector<gl_t>(c, c + ((size_t)1 << v)), R);
+    memcpy(cw, w.data(), w.size() * 8);
+}
+void ref_merkle_build(const uint64_t* cw, size_t M, uint8_t* tree) {
+    p3fri::g_gpu_merkle = false;
+    p3fri::Merkle mk; mk.build(std::vector<gl_t>(cw, cw + M));
+    uint8_t* p = tree;
+    for (auto& lv : mk.levels) for (auto& h : lv) put(p, h.data(), 32);
+}
+void ref_merkle_root(const uint64_t* cw, size_t M, uint8_t root[32]) {
+    p3fri::g_gpu_merkle = false;
+    p3fri::Merkle mk; mk.build(std::vector<gl_t>(cw, cw + M));
+    memcpy(root, mk.root().data(), 32);
+}
+void ref_fold(const uint64_t* f, size_t M, uint64_t wM, uint64_t beta, int mle, uint64_t* out) {
+    auto o = p3fri::fold(std::vector<gl_t>(f, f + M), wM, beta, mle != 0);
+    memcpy(out, o.data(), o.size() * 8);
+}
+
+// ---- Basefold opening (host path) + verifier ----
+size_t ref_bf_prove_eval(const uint64_t* c, const uint64_t* z, uint32_t v, uint64_t y, uint32_t R,
+                         uint32_t Q, const uint64_t* cw0, const char* seed, uint8_t* out, size_t cap) {
+    p3fri::g_gpu_merkle = false;
+    size_t N = (size_t)1 << v, M0 = (size_t)1 << (v + R);
+    auto pf = p3bf::prove_eval(std::vector<gl_t>(c, c + N), std::vector<gl_t>(z, z + v), y, R, Q,
+                               std::vector<gl_t>(cw0, cw0 + M0), seed);
+    return bf_serialize(pf, out, cap);
+}
+int ref_bf_verify_eval(const uint8_t* proof, size_t len, const char* seed) {
+    p3bf::EvalProof pf;
+    if (!bf_deserialize(proof, len, pf)) return 0;
+    return p3bf::verify_eval(pf, seed) ? 1 : 0;
+}
+
+// ---- GKR (host path) ----
+size_t ref_gkr_prove(uint8_t st[32], const char* tag, const uint64_t* p, const uint64_t* q,
+                     uint32_t L, int combine_last, uint64_t* rfin, uint64_t cpq[2], uint8_t* out,
+                     size_t cap, int gpu) {
+    fs::Transcript tr = tr_from(st);
+    size_t N = (size_t)1 << L;
+    std::vector<gl_t> rf;
+    gl_t cp = 0, cq = 0;
+    p3gkr::Proof pf;
+    try {
+        pf = p3gkr::prove(tr, tag, std::vector<gl_t>(p, p + N), std::vector<gl_t>(q, q + N),
+                          combine_last != 0, rf, &cp, &cq, gpu != 0);
+    } catch (...) { return 0; }
+    memcpy(st, tr.state, 32);
+    memcpy(rfin, rf.data(), rf.size() * 8);
+    if (cpq) { cpq[0] = cp; cpq[1] = cq; }
+    return gkr_serialize(pf, out, cap);
+}
+int ref_gkr_verify(uint8_t st[32], const char* tag, uint32_t L, const uint8_t* proof, size_t len,
+                   int combine_last, uint64_t* rfin, uint64_t out4[4]) {
+    p3gkr::Proof pf;
+    if (!gkr_deserialize(proof, len, L, pf)) return 0;
+    fs::Transcript tr = tr_from(st);
+    std::vector<gl_t> rf;
+    const char* why = nullptr;
+    bool ok = p3gkr::verify(tr, tag, L, pf, combine_last != 0, rf, out4, &why);
+    memcpy(st, tr.state, 32);
+    if (ok) memcpy(rfin, rf.data(), rf.size() * 8);
+    return ok ? 1 : 0;
+}
+
+// ---- host sumchecks: cubic logUp chain (Msg4) and generic quartic chain (Msg5) ----
+int ref_lu_sc_prove(uint8_t st[32], const char* tag, const uint64_t* H, const uint64_t* V,
+                    const uint64_t* E, const uint64_t* D, uint32_t logn, uint64_t lam, uint64_t beta,
+                    uint64_t* msgs, uint64_t* chals) {
+    fs::Transcript tr = tr_from(st);
+    size_t n = (size_t)1 << logn;
+    std::vector<p3lu::Msg4> m;
+    auto r = p3lu::sc_prove(std::vector<gl_t>(H, H + n), std::vector<gl_t>(V, V + n),
+                            std::vector<gl_t>(E, E + n), std::vector<gl_t>(D, D + n), lam, beta, tr,
+                            tag, m);
+    memcpy(st, tr.state, 32);
+    memcpy(msgs, m.data(), m.size() * 32);
+    memcpy(chals, r.data(), r.size() * 8);
+    return 0;
+}
+// functor: 0 = c0*c1, 1 = c0*c1*c2 (message always 5 points: p3_hawkeye.cuh:659-695)
+int ref_sc5_prove(uint8_t st[32], const char* tag, int functor, const uint64_t* const* cols, int nc,
+                  uint32_t logn, uint64_t* msgs, uint64_t* chals) {
+    fs::Transcript tr = tr_from(st);
+    size_t n = (size_t)1 << logn;
+    std::vector<std::vector<gl_t>> cc(nc);
+    for (int k = 0; k < nc; k++) cc[k].assign(cols[k], cols[k] + n);
+    p3hwl::CFn F;
+    if (functor == 0) F = [](const gl_t* v) { return gl_mul(v[0], v[1]); };
+    else if (functor == 1) F = [](const gl_t* v) { return gl_mul(v[0], gl_mul(v[1], v[2])); };
+    else return -1;
+    std::vector<p3hwl::Msg5> m;
+    auto r = p3hwl::sc5_prove(tr, tag, std::move(cc), F, m);
+    memcpy(st, tr.state, 32);
+    memcpy(msgs, m.data(), m.size() * 40);
+    memcpy(chals, r.data(), r.size() * 8);
+    return 0;
+}
+
+// ---- logUp primitives ----
+int ref_inv_all_add(const uint64_t* A, size_t n, uint64_t beta, uint64_t* out) {
+    try {
+        auto o = p3lu::inv_all_add(std::vector<gl_t>(A, A + n), beta);
+        memcpy(out, o.data(), n * 8);
+    } catch (...) { return -1; }
+    return 0;
+}
+void ref_combine(const uint64_t* const* cols, int c, size_t n, uint64_t g, uint64_t* out) {
+    std::vector<std::vector<gl_t>> cc(c);
+    std::vector<const std::vector<gl_t>*> pp(c);
+    for (int k = 0; k < c; k++) { cc[k].assign(cols[k], cols[k] + n); pp[k] = &cc[k]; }
+    auto o = p3lu::combine(pp, g);
+    memcpy(out, o.data(), n * 8);
+}
+
+// =====================================================================
+// GPU entry points: the reference's own CUDA paths (need a GPU).
+// =====================================================================
+int ref_gpu_available() {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
+}
+void ref_gpu_setup() { p3bf::p3_enable_mempool(); }
+// p3sg::sc_prove_gpu over host columns (uploaded here, outside any timing the
+// caller does with ref_sc_prove_gpu_dev).  functor: 0 c0*c1, 1 c0*c1*c2,
+// 2 GKR (par = lam), 3 logUp (par = lam,beta).
+static int sc_gpu_run(fs::Transcript& tr, const char* tag, int functor, int nt,
+                      std::vector<gl_t*>& d, uint32_t N, const uint64_t* par, uint32_t npar,
+                      uint64_t* msgs, uint64_t* chals) {
+    std::vector<gl_t> r;
+#define RUN(FF, MT, NT)                                                                   \
+    { std::vector<MT> m; r = p3sg::sc_prove_gpu<FF, MT, NT, 8>(tr, tag, d, N, par, npar, m); \
+      memcpy(msgs, m.data(), m.size() * sizeof(MT)); }
+    if (functor == 0 && nt == 3) RUN(FProd2, M3, 3)
+    else if (functor == 1 && nt == 4) RUN(p3imm::FImmGpu, M4, 4)
+    else if (functor == 1 && nt == 5) RUN(p3imm::FImmGpu, M5, 5)
+    else if (functor == 2 && nt == 4) RUN(p3gkr::FGkrGpu, M4, 4)
+    else if (functor == 3 && nt == 4) RUN(p3lu::FLuGpu, M4, 4)
+    else return -1;
+#undef RUN
+    memcpy(chals, r.data(), r.size() * 8);
+    return 0;
+}
+int ref_sc_prove_gpu(uint8_t st[32], const char* tag, int functor, int nt,
+                     const uint64_t* const* cols, int nc, uint32_t logn, const uint64_t* par,
+                     uint32_t npar, uint64_t* msgs, uint64_t* chals, double* ms_out) {
+    fs::Transcript tr = tr_from(st);
+    uint32_t N = 1u << logn;
+    std::vector<gl_t*> d(nc);
+    for (int k = 0; k < nc; k++) {
+        if (cudaMallocAsync(&d[k], (size_t)N * 8, 0) != cudaSuccess) return -2;
+        cudaMemcpy(d[k], cols[k], (size_t)N * 8, cudaMemcpyHostToDevice);
+    }
+    cudaDeviceSynchronize();
+    double t0 = p3bf::bf_now_ms();
+    int rc = sc_gpu_run(tr, tag, functor, nt, d, N, par, npar, msgs, chals);
+    cudaDeviceSynchronize();
+    if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+    for (auto p : d) cudaFreeAsync(p, 0);
+    cudaDeviceSynchronize();
+    memcpy(st, tr.state, 32);
+    return cudaGetLastError() == cudaSuccess ? rc : -3;
+}
+int ref_commit_gpu_rootonly(const uint64_t* c, uint32_t v, uint32_t R, uint8_t root[32], double* ms_out) {
+    try {
+        std::vector<gl_t> cc(c, c + ((size_t)1 << v));
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        auto h = p3bf::commit_gpu_rootonly(cc, R);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        memcpy(root, h.data(), 32);
+    } catch (...) { return -1; }
+    return 0;
+}
+int ref_rs_encode_gpu(const uint64_t* c, uint32_t v, uint32_t R, uint64_t* cw) {
+    auto w = p3bf::rs_encode_gpu(std::vector<gl_t>(c, c + ((size_t)1 << v)), R);
+    memcpy(cw, w.data(), w.size() * 8);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+size_t ref_bf_prove_eval_dev(const uint64_t* c, const uint64_t* z, uint32_t v, uint64_t y, uint32_t R,
+                             uint32_t Q, const uint64_t* cw0, const char* seed, uint8_t* out,
+                             size_t cap, double* ms_out) {
+    size_t N = (size_t)1 << v, M0 = (size_t)1 << (v + R);
+    std::vector<gl_t> cc(c, c + N), zz(z, z + v), cw(cw0, cw0 + M0);
+    cudaDeviceSynchronize();
+    double t0 = p3bf::bf_now_ms();
+    auto pf = p3bf::prove_eval_dev(cc, zz, y, R, Q, cw, seed);
+    cudaDeviceSynchronize();
+    if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+    return bf_serialize(pf, out, cap);
+}
+
+}  // extern "C"
