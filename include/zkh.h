@@ -1,0 +1,113 @@
+/*
+ * zkh -- C ABI of the B200 (sm_100a) prover kernels for the Goldilocks /
+ * Basefold proving path.
+ *
+ * Plain pointers and sizes only.  Every function returns ZKH_OK (0) or a
+ * negative ZKH_ERR_* code and never throws; zkh_last_error() gives the text.
+ * One context per GPU; a context is thread-compatible, not thread-safe.
+ * Pointers named *_dev are device addresses on the context's GPU, everything
+ * else is host memory.  Field elements are canonical uint64 values in [0, p),
+ * p = 2^64 - 2^32 + 1, exactly as the reference stores them.
+ *
+ * Each entry point names the reference interface it stands in for
+ * (file:line relative to the reference project root).  Results are
+ * bit-identical to that interface on the same inputs.
+ */
+#ifndef ZKH_H
+#define ZKH_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZKH_OK 0
+#define ZKH_ERR_ARG (-1)      /* bad argument (size, functor, null pointer) */
+#define ZKH_ERR_CUDA (-2)     /* a CUDA runtime call failed */
+#define ZKH_ERR_NOMEM (-3)    /* device allocation failed */
+#define ZKH_ERR_DOMAIN (-4)   /* e.g. lookup index out of table, zero denominator */
+#define ZKH_ERR_LIMIT (-5)    /* size beyond a documented maximum */
+#define ZKH_ERR_DEVICE (-6)   /* a kernel reported an internal error flag */
+
+/* Sumcheck summands.  cols = column values at one vertex, par = parameters. */
+#define ZKH_F_PROD2 0 /* c0*c1                       nc=2        zkllm-src/p3_basefold.cuh:319-330 */
+#define ZKH_F_PROD3 1 /* c0*c1*c2                    nc=3        zkllm-src/p3_int_gadgets.cuh:539-544 */
+#define ZKH_F_GKR 2   /* c0*(c1*c4+c2*c3+p0*c3*c4)   nc=5 par=1  zkllm-src/p3_gkr.cuh:48-53 */
+#define ZKH_F_LOGUP 3 /* p0*c0+c2*(c0*(c1+p1)-c3)    nc=4 par=2  zkllm-src/p3_logup.cuh:49-54 */
+
+#if defined(__GNUC__)
+#define ZKH_API __attribute__((visibility("default")))
+#else
+#define ZKH_API
+#endif
+
+typedef struct zkh_ctx zkh_ctx;
+
+/* ---- context ---- */
+/* Creates a context on `device`.  stream == NULL: the context makes its own
+ * non-blocking stream; otherwise work is queued on the given cudaStream_t. */
+ZKH_API int zkh_ctx_create(int device, void* stream, zkh_ctx** out);
+ZKH_API void zkh_ctx_destroy(zkh_ctx* ctx);
+ZKH_API int zkh_ctx_set_stream(zkh_ctx* ctx, void* stream);
+ZKH_API int zkh_ctx_sync(zkh_ctx* ctx);
+ZKH_API const char* zkh_last_error(const zkh_ctx* ctx);
+ZKH_API const char* zkh_version(void);
+
+/* Device time of the largest launch of the dominant kernel inside the most recent
+ * proving call on this context (CUDA events on the context's stream), with the
+ * algorithmic bytes that launch moved.  Measurement aid; no reference counterpart
+ * (the reference times phases on the host, zkllm-src/p3_basefold.cuh:348-349). */
+ZKH_API int zkh_profile_last(zkh_ctx* ctx, float* ms, uint64_t* bytes, const char** kernel);
+
+/* ---- device memory (stands in for p3bf::dmalloc / cudaMallocAsync use,
+ *      zkllm-src/p3_basefold.cuh:50-72) ---- */
+ZKH_API int zkh_dev_alloc(zkh_ctx* ctx, size_t bytes, void** out_dev);
+ZKH_API int zkh_dev_free(zkh_ctx* ctx, void* ptr_dev);
+ZKH_API int zkh_upload(zkh_ctx* ctx, void* dst_dev, const void* src, size_t bytes);
+ZKH_API int zkh_download(zkh_ctx* ctx, void* dst, const void* src_dev, size_t bytes);
+
+/* ---- Fiat-Shamir transcript on the host (zkllm-src/fs_transcript.hpp:115-166;
+ *      challenge mapping zkllm-src/p3_scgpu.cuh:31-35, p3_fri.cuh:422-426).
+ *      The state is the 32-byte running digest. ---- */
+ZKH_API void zkh_tr_init(uint8_t state[32], const void* seed, size_t seed_len);
+ZKH_API void zkh_tr_absorb(uint8_t state[32], const char* label, const void* data, uint64_t len);
+ZKH_API void zkh_tr_challenge_bytes(uint8_t state[32], uint8_t out[32]);
+ZKH_API uint64_t zkh_tr_chal(uint8_t state[32]);
+ZKH_API uint64_t zkh_tr_idx(uint8_t state[32], uint64_t mod);
+
+/* ---- multilinear vector kernels ---- */
+/* out_dev[b] = eq(b, z), b < 2^v.          zkllm-src/p3_basefold.cuh:247-252 (p3bf_eq_kernel) */
+ZKH_API int zkh_gl_eq_build(zkh_ctx* ctx, const uint64_t* z, uint32_t v, uint64_t* out_dev);
+/* *y = sum_b c[b]*eq(b,z).                 zkllm-src/p3_basefold.cuh:262-273 (eval_h_gpu) */
+ZKH_API int zkh_gl_mle_eval(zkh_ctx* ctx, const uint64_t* c_dev, const uint64_t* z, uint32_t v, uint64_t* y);
+/* out[i] = in[2i] + a*(in[2i+1]-in[2i]), i < n/2 (the MLE fold).
+ *                                          zkllm-src/p3_basefold.cuh:336-339 (p3bf_bind_kernel) */
+ZKH_API int zkh_gl_bind(zkh_ctx* ctx, const uint64_t* in_dev, uint64_t* out_dev, uint64_t n, uint64_t a);
+
+/* ---- sumcheck prover (zkllm-src/p3_scgpu.cuh:91-160, p3sg::sc_prove_gpu) ----
+ * Proves sum_b F(cols(b)) over 2^logn vertices, LSB-first binding.
+ * Per round: nt evaluations at t=0..nt-1 are absorbed under `tag` (nt*8 bytes),
+ * one challenge is drawn, all columns are bound.  Unlike the reference the input
+ * columns are left untouched (rounds run in the context's workspace).
+ *   cols_dev[k]  nc device columns of 2^logn elements
+ *   par          npar summand parameters (may be NULL when npar == 0)
+ *   state        in: transcript state before the first round; out: after the last
+ *   msgs         logn*nt values out;  chals: logn values out
+ *   finals       nc values out: each column bound at all challenges (may be NULL)
+ * nt: 3..5 and at least degree(F)+1. */
+ZKH_API int zkh_sumcheck(zkh_ctx* ctx, int functor, int nt, const uint64_t* const* cols_dev, int nc,
+                 uint32_t logn, const uint64_t* par, int npar, const char* tag, uint8_t state[32],
+                 uint64_t* msgs, uint64_t* chals, uint64_t* finals);
+/* Same with HOST columns: uploads, proves, returns (the path sc5_run takes for
+ * host-resident witness columns, zkllm-src/p3_hawkeye.cuh:1016-1033). */
+ZKH_API int zkh_sumcheck_host(zkh_ctx* ctx, int functor, int nt, const uint64_t* const* cols, int nc,
+                      uint32_t logn, const uint64_t* par, int npar, const char* tag,
+                      uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals);
+/* Bytes of workspace zkh_sumcheck needs for (nc, logn). */
+ZKH_API size_t zkh_sumcheck_workspace(int nc, uint32_t logn);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,15 @@
+"""B200 (sm_100a) prover kernels for the Goldilocks / Basefold proving path.
+
+The directory name carries a hyphen, so import it through ``zkh_import.load()``
+at the repository root (registers the package as ``zk_hillclimb_b200``).
+
+Layout:
+  csrc/       CUDA kernels and the C ABI (include/zkh.h) -> libzkh.so
+  build.py    nvcc recipe (sm_100a, in-tree)
+  _lib.py     ctypes binding of the C ABI; raises if the library is missing
+  p3.py       host-side mirror of the reference's in-process prover interface
+"""
+from . import _lib  # noqa: F401
+from ._lib import ZkhError, lib_path, load_library  # noqa: F401
+from . import p3  # noqa: F401
+from .p3 import (F_GKR, F_LOGUP, F_PROD2, F_PROD3, GL_P, Prover, Transcript)  # noqa: F401

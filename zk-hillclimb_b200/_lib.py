@@ -1,0 +1,67 @@
+"""ctypes binding of the C ABI declared in include/zkh.h.
+
+There is no fallback: if libzkh.so has not been built, loading raises.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+u64p = C.POINTER(C.c_uint64)
+_lib = None
+
+ERRORS = {-1: "ZKH_ERR_ARG", -2: "ZKH_ERR_CUDA", -3: "ZKH_ERR_NOMEM", -4: "ZKH_ERR_DOMAIN",
+          -5: "ZKH_ERR_LIMIT", -6: "ZKH_ERR_DEVICE"}
+
+
+class ZkhError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("%s (%d): %s" % (ERRORS.get(code, "ZKH_ERR"), code, msg))
+        self.code = code
+
+
+def lib_path():
+    return os.path.join(HERE, "libzkh.so")
+
+
+def load_library():
+    """Returns the loaded CDLL with argument types declared."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        raise FileNotFoundError(
+            "%s is missing: build it with `python zk-hillclimb_b200/build.py` "
+            "(there is no CPU fallback)" % path)
+    L = C.CDLL(path)
+    vp, sz, u32, u64, i = C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint64, C.c_int
+    sig = {
+        "zkh_ctx_create": (i, [i, vp, C.POINTER(vp)]),
+        "zkh_ctx_destroy": (None, [vp]),
+        "zkh_ctx_set_stream": (i, [vp, vp]),
+        "zkh_ctx_sync": (i, [vp]),
+        "zkh_last_error": (C.c_char_p, [vp]),
+        "zkh_version": (C.c_char_p, []),
+        "zkh_profile_last": (i, [vp, C.POINTER(C.c_float), C.POINTER(u64), C.POINTER(C.c_char_p)]),
+        "zkh_dev_alloc": (i, [vp, sz, C.POINTER(vp)]),
+        "zkh_dev_free": (i, [vp, vp]),
+        "zkh_upload": (i, [vp, vp, vp, sz]),
+        "zkh_download": (i, [vp, vp, vp, sz]),
+        "zkh_tr_init": (None, [vp, vp, sz]),
+        "zkh_tr_absorb": (None, [vp, C.c_char_p, vp, u64]),
+        "zkh_tr_challenge_bytes": (None, [vp, vp]),
+        "zkh_tr_chal": (u64, [vp]),
+        "zkh_tr_idx": (u64, [vp, u64]),
+        "zkh_gl_eq_build": (i, [vp, vp, u32, vp]),
+        "zkh_gl_mle_eval": (i, [vp, vp, vp, u32, vp]),
+        "zkh_gl_bind": (i, [vp, vp, vp, u64, u64]),
+        "zkh_sumcheck": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
+        "zkh_sumcheck_host": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
+        "zkh_sumcheck_workspace": (sz, [i, u32]),
+    }
+    for name, (res, args) in sig.items():
+        f = getattr(L, name)
+        f.restype = res
+        f.argtypes = args
+    _lib = L
+    return L

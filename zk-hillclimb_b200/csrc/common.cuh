@@ -1,0 +1,124 @@
+// Shared host-side plumbing of the library: the context object, the device
+// workspace, error reporting, and small device helpers used by several kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include "gl.cuh"
+#include "sha256.cuh"
+#include "../../include/zkh.h"
+
+#define ZKH_SM_COUNT_FALLBACK 148
+
+// Device-resident control block of one proving job.  Kernels of consecutive
+// rounds communicate through it (transcript state, round challenges), so a whole
+// sumcheck / opening runs without the host reading anything back in between.
+struct ZkhCtl {
+    uint32_t st[8];          // Fiat-Shamir state (digest words)
+    unsigned int counter;    // CTA completion counter of the running reduction
+    unsigned int err;        // sticky device-side error flag
+    gl_t par[8];             // summand parameters (lambda, beta, ...)
+    gl_t local[8];           // this GPU's round sums when the reduction is finished elsewhere
+    gl_t finals[16];         // column values after the last bind
+    gl_t chals[80];          // round challenges
+    gl_t msgs[80 * 5];       // round messages
+    gl_t aux[64];            // scratch for composite protocols
+};
+
+struct ZkhTag { char s[ZKH_TR_MAX_LABEL]; uint32_t len; };
+
+struct zkh_ctx {
+    int device = 0;
+    int sm_count = ZKH_SM_COUNT_FALLBACK;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    // workspace: one growable device allocation carved up by the running call
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    ZkhCtl* d_ctl = nullptr;     // device control block
+    ZkhCtl* h_ctl = nullptr;     // pinned host mirror (downloaded once per call)
+    gl_t* d_partials = nullptr;  // per-CTA round partial sums
+    size_t partials_cap = 0;
+    // cached twiddle tables, one set per log-size
+    struct Tw { gl_t* lo = nullptr; gl_t* hi = nullptr; gl_t* lo_inv = nullptr; gl_t* hi_inv = nullptr; uint32_t lb = 0; };
+    Tw tw[33];
+    // CUDA events around the largest launch of the dominant kernel of the last call
+    cudaEvent_t prof_ev[2] = {nullptr, nullptr};
+    bool prof_valid = false;
+    uint64_t prof_bytes = 0;     // algorithmic bytes of that launch
+    const char* prof_kernel = "";
+    std::string err;
+};
+
+static inline int zkh_fail(zkh_ctx* c, int code, const std::string& msg) {
+    if (c) c->err = msg;
+    return code;
+}
+#define ZKH_CUDA(c, expr)                                                                     \
+    do {                                                                                      \
+        cudaError_t e__ = (expr);                                                             \
+        if (e__ != cudaSuccess)                                                               \
+            return zkh_fail((c), ZKH_ERR_CUDA,                                                \
+                            std::string(#expr) + ": " + cudaGetErrorString(e__));             \
+    } while (0)
+#define ZKH_TRY(expr)                  \
+    do {                               \
+        int r__ = (expr);              \
+        if (r__ != ZKH_OK) return r__; \
+    } while (0)
+
+// make the workspace at least `bytes` large (contents are not preserved)
+int zkh_ws_reserve(zkh_ctx* c, size_t bytes);
+static inline ZkhTag zkh_make_tag(const char* s) {
+    ZkhTag t;
+    memset(&t, 0, sizeof t);
+    size_t n = strlen(s);
+    if (n > ZKH_TR_MAX_LABEL) n = ZKH_TR_MAX_LABEL;
+    memcpy(t.s, s, n);
+    t.len = (uint32_t)n;
+    return t;
+}
+static inline size_t zkh_align(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+#ifdef __CUDACC__
+// ---- device helpers ----
+__device__ __forceinline__ gl_t shfl_down_gl(gl_t v, int d) {
+    uint32_t lo = __shfl_down_sync(0xffffffffu, (uint32_t)v, d);
+    uint32_t hi = __shfl_down_sync(0xffffffffu, (uint32_t)(v >> 32), d);
+    return ((uint64_t)hi << 32) | lo;
+}
+// Sum NT per-thread values over the CTA.  Result valid in thread 0.
+// sh must hold NT*32 gl_t.  All threads must call.
+template <int NT>
+__device__ __forceinline__ void block_sum(gl_t (&v)[NT], gl_t* sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) v[t] = gl_add(v[t], shfl_down_gl(v[t], d));
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int t = 0; t < NT; t++) sh[t * 32 + warp] = v[t];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            gl_t x = lane < nwarp ? sh[t * 32 + lane] : 0;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) x = gl_add(x, shfl_down_gl(x, d));
+            v[t] = x;
+        }
+    }
+    __syncthreads();
+}
+__device__ __forceinline__ ulonglong2 ld2(const gl_t* p) {
+    return __ldg(reinterpret_cast<const ulonglong2*>(p));
+}
+__device__ __forceinline__ void st2(gl_t* p, gl_t a, gl_t b) {
+    *reinterpret_cast<ulonglong2*>(p) = make_ulonglong2(a, b);
+}
+#endif

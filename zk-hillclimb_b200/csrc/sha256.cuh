@@ -1,0 +1,181 @@
+// SHA-256 and the Fiat-Shamir transcript, usable from device and host code.
+//
+// Byte-exact with the reference's hashing:
+//   * full SHA-256 (FIPS 180-4)                      zkllm-src/fs_transcript.hpp:24-99
+//   * Merkle leaf  = SHA-256(8-byte LE value)         zkllm-src/p3_fri.cuh:33-35
+//   * Merkle node  = ONE compression of l|r from the IV, no padding block
+//                                                     zkllm-src/p3_merkle.cuh:69-104
+//   * transcript   state' = H(state|LE32(|label|)|label|LE64(len)|data)
+//                  challenge: out = H(state|"chal"), state' = H(state|"rtch")
+//                                                     zkllm-src/fs_transcript.hpp:115-166
+// A digest is kept as eight 32-bit words h[0..7]; its byte form is the big-endian
+// serialisation of those words (what the reference stores and absorbs).
+#pragma once
+#include <cstdint>
+#include "gl.cuh"
+
+namespace zkh {
+
+struct Digest { uint32_t h[8]; };
+
+GL_HD uint32_t rotr32(uint32_t x, int n) {
+#ifdef __CUDA_ARCH__
+    return __funnelshift_r(x, x, n);
+#else
+    return (x >> n) | (x << (32 - n));
+#endif
+}
+GL_HD uint32_t bswap32(uint32_t x) {
+#ifdef __CUDA_ARCH__
+    return __byte_perm(x, 0, 0x0123);
+#else
+    return (x >> 24) | ((x >> 8) & 0xff00u) | ((x << 8) & 0xff0000u) | (x << 24);
+#endif
+}
+
+#define ZKH_SHA_K_LIST                                                                           \
+    0x428a2f98u, 0x71374491u, 0xb5c0fbcfu, 0xe9b5dba5u, 0x3956c25bu, 0x59f111f1u, 0x923f82a4u,   \
+    0xab1c5ed5u, 0xd807aa98u, 0x12835b01u, 0x243185beu, 0x550c7dc3u, 0x72be5d74u, 0x80deb1feu,   \
+    0x9bdc06a7u, 0xc19bf174u, 0xe49b69c1u, 0xefbe4786u, 0x0fc19dc6u, 0x240ca1ccu, 0x2de92c6fu,   \
+    0x4a7484aau, 0x5cb0a9dcu, 0x76f988dau, 0x983e5152u, 0xa831c66du, 0xb00327c8u, 0xbf597fc7u,   \
+    0xc6e00bf3u, 0xd5a79147u, 0x06ca6351u, 0x14292967u, 0x27b70a85u, 0x2e1b2138u, 0x4d2c6dfcu,   \
+    0x53380d13u, 0x650a7354u, 0x766a0abbu, 0x81c2c92eu, 0x92722c85u, 0xa2bfe8a1u, 0xa81a664bu,   \
+    0xc24b8b70u, 0xc76c51a3u, 0xd192e819u, 0xd6990624u, 0xf40e3585u, 0x106aa070u, 0x19a4c116u,   \
+    0x1e376c08u, 0x2748774cu, 0x34b0bcb5u, 0x391c0cb3u, 0x4ed8aa4au, 0x5b9cca4fu, 0x682e6ff3u,   \
+    0x748f82eeu, 0x78a5636fu, 0x84c87814u, 0x8cc70208u, 0x90befffau, 0xa4506cebu, 0xbef9a3f7u,   \
+    0xc67178f2u
+
+// One compression: h <- h + F(h, w).  w (16 words) is consumed as a rolling schedule.
+// Fully unrolled so that round constants become immediates and w stays in registers.
+GL_HD void sha256_compress(uint32_t h[8], uint32_t w[16]) {
+    constexpr uint32_t K[64] = {ZKH_SHA_K_LIST};
+    uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
+#pragma unroll
+    for (int i = 0; i < 64; i++) {
+        uint32_t wi;
+        if (i < 16) {
+            wi = w[i];
+        } else {
+            uint32_t x = w[(i - 15) & 15], y = w[(i - 2) & 15];
+            uint32_t s0 = rotr32(x, 7) ^ rotr32(x, 18) ^ (x >> 3);
+            uint32_t s1 = rotr32(y, 17) ^ rotr32(y, 19) ^ (y >> 10);
+            wi = w[i & 15] = w[i & 15] + s0 + w[(i - 7) & 15] + s1;
+        }
+        uint32_t t1 = hh + (rotr32(e, 6) ^ rotr32(e, 11) ^ rotr32(e, 25)) + ((e & f) ^ (~e & g)) +
+                      K[i] + wi;
+        uint32_t t2 = (rotr32(a, 2) ^ rotr32(a, 13) ^ rotr32(a, 22)) + ((a & b) ^ (a & c) ^ (b & c));
+        hh = g; g = f; f = e; e = d + t1;
+        d = c; c = b; b = a; a = t1 + t2;
+    }
+    h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
+}
+GL_HD void sha256_iv(uint32_t h[8]) {
+    h[0] = 0x6a09e667u; h[1] = 0xbb67ae85u; h[2] = 0x3c6ef372u; h[3] = 0xa54ff53au;
+    h[4] = 0x510e527fu; h[5] = 0x9b05688cu; h[6] = 0x1f83d9abu; h[7] = 0x5be0cd19u;
+}
+
+// Merkle leaf: SHA-256 of the 8 little-endian bytes of v (one padded block).
+GL_HD void sha256_leaf(gl_t v, uint32_t out[8]) {
+    uint32_t w[16];
+    w[0] = bswap32((uint32_t)v);
+    w[1] = bswap32((uint32_t)(v >> 32));
+    w[2] = 0x80000000u;
+#pragma unroll
+    for (int i = 3; i < 15; i++) w[i] = 0;
+    w[15] = 64;  // message length in bits
+    sha256_iv(out);
+    sha256_compress(out, w);
+}
+// Merkle node: compression of the two child digests, IV start, no length block.
+GL_HD void sha256_node(const uint32_t l[8], const uint32_t r[8], uint32_t out[8]) {
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { w[i] = l[i]; w[8 + i] = r[i]; }
+    sha256_iv(out);
+    sha256_compress(out, w);
+}
+
+// Generic SHA-256 of a short byte string held in words-addressable scratch.
+// msg must have room for len rounded up to the next multiple of 64 (+64).
+GL_HD void sha256_bytes(uint8_t* msg, uint32_t len, uint32_t out[8]) {
+    uint32_t padded = ((len + 8) / 64 + 1) * 64;
+    msg[len] = 0x80;
+    for (uint32_t i = len + 1; i < padded - 8; i++) msg[i] = 0;
+    uint64_t bits = (uint64_t)len * 8;
+    for (int i = 0; i < 8; i++) msg[padded - 1 - i] = (uint8_t)(bits >> (8 * i));
+    sha256_iv(out);
+    for (uint32_t off = 0; off < padded; off += 64) {
+        uint32_t w[16];
+        for (int i = 0; i < 16; i++)
+            w[i] = ((uint32_t)msg[off + 4 * i] << 24) | ((uint32_t)msg[off + 4 * i + 1] << 16) |
+                   ((uint32_t)msg[off + 4 * i + 2] << 8) | (uint32_t)msg[off + 4 * i + 3];
+        sha256_compress(out, w);
+    }
+}
+
+// ---------------- transcript ----------------
+#define ZKH_TR_MAX_LABEL 48
+#define ZKH_TR_MAX_DATA 320
+
+GL_HD void digest_to_bytes(const uint32_t h[8], uint8_t* b) {
+    for (int i = 0; i < 8; i++) {
+        b[4 * i] = (uint8_t)(h[i] >> 24); b[4 * i + 1] = (uint8_t)(h[i] >> 16);
+        b[4 * i + 2] = (uint8_t)(h[i] >> 8); b[4 * i + 3] = (uint8_t)h[i];
+    }
+}
+GL_HD void digest_from_bytes(const uint8_t* b, uint32_t h[8]) {
+    for (int i = 0; i < 8; i++)
+        h[i] = ((uint32_t)b[4 * i] << 24) | ((uint32_t)b[4 * i + 1] << 16) |
+               ((uint32_t)b[4 * i + 2] << 8) | (uint32_t)b[4 * i + 3];
+}
+
+// state' = H(state | LE32(ll) | label | LE64(len) | data);  ll <= 48, len <= 320
+GL_HD void tr_absorb(uint32_t st[8], const char* label, uint32_t ll, const void* data, uint32_t len) {
+    uint8_t msg[32 + 4 + ZKH_TR_MAX_LABEL + 8 + ZKH_TR_MAX_DATA + 72];
+    digest_to_bytes(st, msg);
+    uint32_t p = 32;
+    msg[p++] = (uint8_t)ll; msg[p++] = (uint8_t)(ll >> 8); msg[p++] = 0; msg[p++] = 0;
+    for (uint32_t i = 0; i < ll; i++) msg[p++] = (uint8_t)label[i];
+    msg[p++] = (uint8_t)len; msg[p++] = (uint8_t)(len >> 8);
+    for (int i = 0; i < 6; i++) msg[p++] = 0;
+    const uint8_t* d = (const uint8_t*)data;
+    for (uint32_t i = 0; i < len; i++) msg[p++] = d[i];
+    sha256_bytes(msg, p, st);
+}
+// out = H(state|"chal"); state' = H(state|"rtch").  36-byte messages: one block each.
+GL_HD void tr_challenge(uint32_t st[8], uint32_t out[8]) {
+    uint32_t w[16], w2[16];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { w[i] = st[i]; w2[i] = st[i]; }
+    w[8] = 0x6368616cu;   // "chal"
+    w2[8] = 0x72746368u;  // "rtch"
+    w[9] = w2[9] = 0x80000000u;
+#pragma unroll
+    for (int i = 10; i < 15; i++) { w[i] = 0; w2[i] = 0; }
+    w[15] = w2[15] = 36 * 8;
+    sha256_iv(out);
+    sha256_compress(out, w);
+    uint32_t ns[8];
+    sha256_iv(ns);
+    sha256_compress(ns, w2);
+#pragma unroll
+    for (int i = 0; i < 8; i++) st[i] = ns[i];
+}
+// first 8 digest bytes as a little-endian u64
+GL_HD uint64_t digest_le64(const uint32_t out[8]) {
+    return (uint64_t)bswap32(out[0]) | ((uint64_t)bswap32(out[1]) << 32);
+}
+// field challenge: zkllm-src/p3_scgpu.cuh:31-35
+GL_HD gl_t tr_chal_gl(uint32_t st[8]) {
+    uint32_t out[8];
+    tr_challenge(st, out);
+    return digest_le64(out) % GL_P;
+}
+// query index: zkllm-src/p3_fri.cuh:422-426
+GL_HD uint64_t tr_chal_idx(uint32_t st[8], uint64_t mod) {
+    uint32_t out[8];
+    tr_challenge(st, out);
+    return digest_le64(out) % mod;
+}
+
+}  // namespace zkh

@@ -1,0 +1,485 @@
+// Sumcheck prover rounds over Goldilocks for sm_100a.
+//
+// What the reference does per round (zkllm-src/p3_scgpu.cuh:107-156): a message
+// kernel, a device-to-host copy of 256 partials per evaluation point, a host sum,
+// a host SHA-256 absorb/challenge, nc device allocations and a bind kernel.
+//
+// What happens here per round: ONE kernel.  It binds the previous round's columns
+// with the previous challenge (read from device memory), writes the halved
+// columns, and accumulates this round's message from the values it just
+// produced, all from 128-bit loads of adjacent pairs.  Partial sums are reduced
+// with warp shuffles, then across CTAs by the last CTA to finish, which also runs
+// the Fiat-Shamir absorb and derives the next challenge on the device.  The host
+// queues every round up front and reads results back once.
+//
+// Sums are exact field sums, so any partition and any order give the same
+// canonical values as the reference's accumulation.
+#include "sumcheck.cuh"
+
+namespace zkh {
+
+// ------------------------------------------------------------------ summands
+template <int F> struct Fn;
+template <> struct Fn<ZKH_F_PROD2> {
+    static constexpr int NC = 2;
+    static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t*) {
+        a.add_prod(c[0], c[1]);
+    }
+};
+template <> struct Fn<ZKH_F_PROD3> {
+    static constexpr int NC = 3;
+    static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t*) {
+        a.add_prod(c[0], gl_mul(c[1], c[2]));
+    }
+};
+template <> struct Fn<ZKH_F_GKR> {
+    static constexpr int NC = 5;
+    static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t* p) {
+        Acc192 in;
+        in.clear();
+        in.add_prod(c[1], c[4]);
+        in.add_prod(c[2], c[3]);
+        in.add_prod(p[0], gl_mul(c[3], c[4]));
+        a.add_prod(c[0], in.reduce());
+    }
+};
+template <> struct Fn<ZKH_F_LOGUP> {
+    static constexpr int NC = 4;
+    static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t* p) {
+        a.add_prod(p[0], c[0]);
+        a.add_prod(c[2], gl_sub(gl_mul(c[0], gl_add(c[1], p[1])), c[3]));
+    }
+};
+
+int functor_nc(int functor) {
+    switch (functor) {
+        case ZKH_F_PROD2: return 2;
+        case ZKH_F_PROD3: return 3;
+        case ZKH_F_GKR: return 5;
+        case ZKH_F_LOGUP: return 4;
+    }
+    return -1;
+}
+
+// ------------------------------------------------------------------ loaders
+template <int LD, int NC>
+__device__ __forceinline__ void load_pairs(const ScPtrs& P, size_t i, gl_t (&lo)[NC], gl_t (&hi)[NC]) {
+    if (LD == LD_PLAIN) {
+#pragma unroll
+        for (int k = 0; k < NC; k++) {
+            ulonglong2 v = ld2(P.in[k] + 2 * i);
+            lo[k] = v.x; hi[k] = v.y;
+        }
+    } else {
+        ulonglong2 e = ld2(P.in[0] + 2 * i);
+        lo[0] = e.x; hi[0] = e.y;
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            ulonglong2 a = ld2(P.in[1 + s] + 4 * i), b = ld2(P.in[1 + s] + 4 * i + 2);
+            lo[1 + 2 * s] = a.x; hi[1 + 2 * s] = b.x;  // even child
+            lo[2 + 2 * s] = a.y; hi[2 + 2 * s] = b.y;  // odd child
+        }
+    }
+}
+template <int LD, int NC>
+__device__ __forceinline__ void load_quads(const ScPtrs& P, size_t i, gl_t (&x)[NC][4]) {
+    if (LD == LD_PLAIN) {
+#pragma unroll
+        for (int k = 0; k < NC; k++) {
+            ulonglong2 a = ld2(P.in[k] + 4 * i), b = ld2(P.in[k] + 4 * i + 2);
+            x[k][0] = a.x; x[k][1] = a.y; x[k][2] = b.x; x[k][3] = b.y;
+        }
+    } else {
+        ulonglong2 a = ld2(P.in[0] + 4 * i), b = ld2(P.in[0] + 4 * i + 2);
+        x[0][0] = a.x; x[0][1] = a.y; x[0][2] = b.x; x[0][3] = b.y;
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            const gl_t* src = P.in[1 + s] + 8 * i;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                ulonglong2 v = ld2(src + 2 * j);
+                x[1 + 2 * s][j] = v.x;
+                x[2 + 2 * s][j] = v.y;
+            }
+        }
+    }
+}
+
+// message contribution of one pair per column: evaluations at t = 0..NT-1 of
+// F(lo + t*(hi-lo))  (zkllm-src/p3_scgpu.cuh:63-72)
+template <int F, int NT>
+__device__ __forceinline__ void msg_accum(Acc192 (&acc)[NT], const gl_t (&lo)[Fn<F>::NC],
+                                          const gl_t (&hi)[Fn<F>::NC], const gl_t* par) {
+    constexpr int NC = Fn<F>::NC;
+    gl_t cur[NC], dd[NC];
+#pragma unroll
+    for (int k = 0; k < NC; k++) cur[k] = lo[k];
+    Fn<F>::acc(acc[0], cur, par);
+#pragma unroll
+    for (int k = 0; k < NC; k++) { cur[k] = hi[k]; dd[k] = gl_sub(hi[k], lo[k]); }
+    Fn<F>::acc(acc[1], cur, par);
+#pragma unroll
+    for (int t = 2; t < NT; t++) {
+#pragma unroll
+        for (int k = 0; k < NC; k++) cur[k] = gl_add(cur[k], dd[k]);
+        Fn<F>::acc(acc[t], cur, par);
+    }
+}
+
+// ------------------------------------------------------------------ round end
+// mode 0: absorb the message under `tag` and draw the challenge on the device.
+// mode 1: leave this GPU's sums in ctl->local (another step combines the GPUs).
+template <int NT>
+__device__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t* msg_out, gl_t* chal_out,
+                             const ZkhTag& tag, int mode) {
+    if (mode == 1) {
+#pragma unroll
+        for (int t = 0; t < NT; t++) ctl->local[t] = s[t];
+        return;
+    }
+    gl_t m[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) { m[t] = s[t]; msg_out[t] = s[t]; }
+    uint32_t st[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
+    tr_absorb(st, tag.s, tag.len, m, NT * 8);
+    gl_t a = tr_chal_gl(st);
+#pragma unroll
+    for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+    *chal_out = a;
+}
+
+// CTA sums -> grid sum by the last CTA to arrive -> finish_round.
+template <int NT>
+__device__ __forceinline__ void grid_finish(gl_t (&s)[NT], gl_t* sh, ZkhCtl* ctl, gl_t* partials,
+                                            gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag,
+                                            int mode) {
+    __shared__ int is_last;
+    block_sum<NT>(s, sh);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int t = 0; t < NT; t++) __stcg(&partials[(size_t)blockIdx.x * NT + t], s[t]);
+        __threadfence();
+        unsigned prev = atomicAdd(&ctl->counter, 1u);
+        is_last = (prev == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    gl_t v[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) v[t] = 0;
+    for (unsigned b = threadIdx.x; b < gridDim.x; b += blockDim.x) {
+#pragma unroll
+        for (int t = 0; t < NT; t++) v[t] = gl_add(v[t], __ldcg(&partials[(size_t)b * NT + t]));
+    }
+    block_sum<NT>(v, sh);
+    if (threadIdx.x == 0) {
+        ctl->counter = 0;
+        finish_round<NT>(v, ctl, msg_out, chal_out, tag, mode);
+    }
+}
+
+// ------------------------------------------------------------------ kernels
+// round 0: message only
+template <int F, int NT, int LD>
+__global__ void __launch_bounds__(256)
+sc_first_kernel(ScPtrs P, size_t half, ZkhCtl* ctl, gl_t* partials, gl_t* msg_out, gl_t* chal_out,
+                ZkhTag tag, int mode) {
+    constexpr int NC = Fn<F>::NC;
+    __shared__ gl_t sh[NT * 32];
+    gl_t par[2] = {ctl->par[0], ctl->par[1]};
+    Acc192 acc[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc[t].clear();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < half; i += stride) {
+        gl_t lo[NC], hi[NC];
+        load_pairs<LD, NC>(P, i, lo, hi);
+        msg_accum<F, NT>(acc, lo, hi, par);
+    }
+    gl_t s[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) s[t] = acc[t].reduce();
+    grid_finish<NT>(s, sh, ctl, partials, msg_out, chal_out, tag, mode);
+}
+
+// round r >= 1: bind with challenge r-1, store the halved columns, message of round r
+template <int F, int NT, int LD>
+__global__ void __launch_bounds__(256)
+sc_fused_kernel(ScPtrs P, size_t quads, ZkhCtl* ctl, gl_t* partials, const gl_t* chal_prev,
+                gl_t* msg_out, gl_t* chal_out, ZkhTag tag, int mode) {
+    constexpr int NC = Fn<F>::NC;
+    __shared__ gl_t sh[NT * 32];
+    gl_t par[2] = {ctl->par[0], ctl->par[1]};
+    const gl_t a = *chal_prev;
+    Acc192 acc[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc[t].clear();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += stride) {
+        gl_t x[NC][4], lo[NC], hi[NC];
+        load_quads<LD, NC>(P, i, x);
+#pragma unroll
+        for (int k = 0; k < NC; k++) {
+            lo[k] = gl_lerp(x[k][0], x[k][1], a);
+            hi[k] = gl_lerp(x[k][2], x[k][3], a);
+            st2(P.out[k] + 2 * i, lo[k], hi[k]);
+        }
+        msg_accum<F, NT>(acc, lo, hi, par);
+    }
+    gl_t s[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) s[t] = acc[t].reduce();
+    grid_finish<NT>(s, sh, ctl, partials, msg_out, chal_out, tag, mode);
+}
+
+// all remaining rounds of a small instance in one CTA, columns in shared memory.
+// n_in: source column length; pending: bind the source with *chal_prev while loading.
+// Column length in shared memory is at most 2*blockDim.x.
+template <int F, int NT, int LD>
+__global__ void __launch_bounds__(1024)
+sc_tail_kernel(ScPtrs P, uint32_t n_in, int pending, ZkhCtl* ctl, const gl_t* chal_prev,
+               gl_t* msg_out, gl_t* chal_out, gl_t* finals_out, int nrounds, ZkhTag tag) {
+    constexpr int NC = Fn<F>::NC;
+    extern __shared__ gl_t cols[];
+    __shared__ gl_t sh[NT * 32];
+    __shared__ gl_t sh_chal;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t n0 = pending ? n_in / 2 : n_in;
+    gl_t par[2] = {ctl->par[0], ctl->par[1]};
+    if (pending) {
+        const gl_t a = *chal_prev;
+        for (uint32_t j = tid; j < n0; j += blockDim.x) {
+            gl_t lo[NC], hi[NC];
+            load_pairs<LD, NC>(P, j, lo, hi);
+#pragma unroll
+            for (int k = 0; k < NC; k++) cols[k * n0 + j] = gl_lerp(lo[k], hi[k], a);
+        }
+    } else {
+        for (uint32_t j = tid; j < n0 / 2; j += blockDim.x) {
+            gl_t lo[NC], hi[NC];
+            load_pairs<LD, NC>(P, j, lo, hi);
+#pragma unroll
+            for (int k = 0; k < NC; k++) { cols[k * n0 + 2 * j] = lo[k]; cols[k * n0 + 2 * j + 1] = hi[k]; }
+        }
+    }
+    __syncthreads();
+    uint32_t n = n0;
+    for (int r = 0; r < nrounds; r++) {
+        const uint32_t half = n / 2;
+        Acc192 acc[NT];
+#pragma unroll
+        for (int t = 0; t < NT; t++) acc[t].clear();
+        gl_t lo[NC], hi[NC];
+        const bool active = tid < half;  // half <= blockDim.x
+        if (active) {
+#pragma unroll
+            for (int k = 0; k < NC; k++) { lo[k] = cols[k * n0 + 2 * tid]; hi[k] = cols[k * n0 + 2 * tid + 1]; }
+            msg_accum<F, NT>(acc, lo, hi, par);
+        }
+        gl_t s[NT];
+#pragma unroll
+        for (int t = 0; t < NT; t++) s[t] = acc[t].reduce();
+        block_sum<NT>(s, sh);  // ends with a barrier: every pair has been read
+        if (tid == 0) {
+            finish_round<NT>(s, ctl, msg_out + (size_t)r * NT, chal_out + r, tag, 0);
+            sh_chal = chal_out[r];
+        }
+        __syncthreads();
+        const gl_t a = sh_chal;
+        if (active) {
+#pragma unroll
+            for (int k = 0; k < NC; k++) cols[k * n0 + tid] = gl_lerp(lo[k], hi[k], a);
+        }
+        __syncthreads();
+        n = half;
+    }
+    if (tid < NC) finals_out[tid] = cols[tid * n0];
+}
+
+// ------------------------------------------------------------------ host side
+size_t sc_workspace_bytes(int nc, uint32_t logn) {
+    if (logn <= SC_TAIL_LOG) return 256;
+    size_t n = (size_t)1 << logn;
+    return zkh_align((size_t)nc * (n / 2) * 8) + zkh_align((size_t)nc * (n / 4) * 8) + 256;
+}
+
+template <int F, int NT, int LD>
+static int sc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, const ZkhTag& tag,
+                        void* scratch, const ScOut& out) {
+    constexpr int NC = Fn<F>::NC;
+    const int nsrc = LD == LD_GKR ? 3 : NC;
+    cudaStream_t s = ctx->stream;
+    ZkhCtl* ctl = ctx->d_ctl;
+    const size_t n = (size_t)1 << logn;
+    ctx->prof_valid = false;
+    ScPtrs P;
+    memset(&P, 0, sizeof P);
+    for (int k = 0; k < nsrc; k++) P.in[k] = in[k];
+
+    static int occ_first = 0, occ_fused = 0, occ_fused_plain = 0;
+    if (!occ_first) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_first, sc_first_kernel<F, NT, LD>, 256, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_fused, sc_fused_kernel<F, NT, LD>, 256, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_fused_plain,
+                                                      sc_fused_kernel<F, NT, LD_PLAIN>, 256, 0);
+        cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             NC * (1 << SC_TAIL_LOG) * 8);
+        cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, NC * (1 << SC_TAIL_LOG) * 8);
+        if (occ_first < 1) occ_first = 1;
+        if (occ_fused < 1) occ_fused = 1;
+        if (occ_fused_plain < 1) occ_fused_plain = 1;
+    }
+    auto grid_for = [&](size_t items, int occ) {
+        size_t want = (items + 255) / 256, cap = (size_t)ctx->sm_count * occ;
+        if (cap > ctx->partials_cap / 5) cap = ctx->partials_cap / 5;
+        return (unsigned)(want < cap ? want : cap);
+    };
+
+    if (logn <= SC_TAIL_LOG) {
+        sc_tail_kernel<F, NT, LD><<<1, 1024, NC * n * 8, s>>>(P, (uint32_t)n, 0, ctl, nullptr, out.msgs,
+                                                              out.chals, out.finals, (int)logn, tag);
+        return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "sc_tail launch");
+    }
+    // round 0 on the caller's columns
+    sc_first_kernel<F, NT, LD><<<grid_for(n / 2, occ_first), 256, 0, s>>>(
+        P, n / 2, ctl, ctx->d_partials, out.msgs, out.chals, tag, 0);
+    // ping-pong buffers for the bound columns
+    gl_t* bufA = (gl_t*)scratch;
+    gl_t* bufB = (gl_t*)((char*)scratch + zkh_align((size_t)NC * (n / 2) * 8));
+    size_t cur_n = n;  // length of the columns the next kernel reads
+    int r = 1;
+    bool src_is_input = true;
+    const gl_t* cur_in[8];
+    for (int k = 0; k < nsrc; k++) cur_in[k] = in[k];
+    gl_t* dst = bufA;
+    while ((cur_n >> 1) > ((size_t)1 << SC_TAIL_LOG)) {
+        const size_t out_n = cur_n / 2;
+        for (int k = 0; k < 8; k++) { P.in[k] = nullptr; P.out[k] = nullptr; }
+        for (int k = 0; k < (src_is_input ? nsrc : NC); k++) P.in[k] = cur_in[k];
+        for (int k = 0; k < NC; k++) P.out[k] = dst + (size_t)k * out_n;
+        const bool prof = (r == 1) && ctx->prof_ev[0];
+        if (prof) cudaEventRecord(ctx->prof_ev[0], s);
+        if (src_is_input)
+            sc_fused_kernel<F, NT, LD><<<grid_for(cur_n / 4, occ_fused), 256, 0, s>>>(
+                P, cur_n / 4, ctl, ctx->d_partials, out.chals + (r - 1), out.msgs + (size_t)r * NT,
+                out.chals + r, tag, 0);
+        else
+            sc_fused_kernel<F, NT, LD_PLAIN><<<grid_for(cur_n / 4, occ_fused_plain), 256, 0, s>>>(
+                P, cur_n / 4, ctl, ctx->d_partials, out.chals + (r - 1), out.msgs + (size_t)r * NT,
+                out.chals + r, tag, 0);
+        if (prof) {
+            cudaEventRecord(ctx->prof_ev[1], s);
+            ctx->prof_valid = true;
+            ctx->prof_bytes = (uint64_t)12 * NC * cur_n;  // read 8, write 4 bytes per input element
+            ctx->prof_kernel = "sc_fused_kernel";
+        }
+        for (int k = 0; k < NC; k++) cur_in[k] = P.out[k];
+        src_is_input = false;
+        dst = (dst == bufA) ? bufB : bufA;
+        cur_n = out_n;
+        r++;
+    }
+    for (int k = 0; k < 8; k++) { P.in[k] = nullptr; P.out[k] = nullptr; }
+    for (int k = 0; k < (src_is_input ? nsrc : NC); k++) P.in[k] = cur_in[k];
+    const size_t tail_n = cur_n / 2;
+    if (src_is_input)
+        sc_tail_kernel<F, NT, LD><<<1, 1024, NC * tail_n * 8, s>>>(
+            P, (uint32_t)cur_n, 1, ctl, out.chals + (r - 1), out.msgs + (size_t)r * NT, out.chals + r,
+            out.finals, (int)logn - r, tag);
+    else
+        sc_tail_kernel<F, NT, LD_PLAIN><<<1, 1024, NC * tail_n * 8, s>>>(
+            P, (uint32_t)cur_n, 1, ctl, out.chals + (r - 1), out.msgs + (size_t)r * NT, out.chals + r,
+            out.finals, (int)logn - r, tag);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "sumcheck launch");
+}
+
+int sc_enqueue(zkh_ctx* ctx, int functor, int nt, int ld, const gl_t* const* in, uint32_t logn,
+               const ZkhTag& tag, void* scratch, const ScOut& out) {
+    if (logn < 1 || logn > 34) return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: logn out of range");
+#define CASE(F, NT, LD) \
+    if (functor == F && nt == NT && ld == LD) return sc_enqueue_t<F, NT, LD>(ctx, in, logn, tag, scratch, out);
+    CASE(ZKH_F_PROD2, 3, LD_PLAIN)
+    CASE(ZKH_F_PROD2, 5, LD_PLAIN)
+    CASE(ZKH_F_PROD3, 4, LD_PLAIN)
+    CASE(ZKH_F_PROD3, 5, LD_PLAIN)
+    CASE(ZKH_F_GKR, 4, LD_PLAIN)
+    CASE(ZKH_F_GKR, 4, LD_GKR)
+    CASE(ZKH_F_LOGUP, 4, LD_PLAIN)
+#undef CASE
+    return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: unsupported (functor, nt) combination");
+}
+
+}  // namespace zkh
+
+using namespace zkh;
+
+// ------------------------------------------------------------------ C ABI
+extern "C" size_t zkh_sumcheck_workspace(int nc, uint32_t logn) { return sc_workspace_bytes(nc, logn); }
+
+static int sumcheck_common(zkh_ctx* ctx, int functor, int nt, const uint64_t* const* cols_dev, int nc,
+                           uint32_t logn, const uint64_t* par, int npar, const char* tag,
+                           uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals,
+                           void* scratch) {
+    ZkhCtl* h = ctx->h_ctl;
+    digest_from_bytes(state, h->st);
+    h->counter = 0;
+    h->err = 0;
+    for (int i = 0; i < 8; i++) h->par[i] = i < npar ? par[i] : 0;
+    ZKH_CUDA(ctx, cudaMemcpyAsync(ctx->d_ctl, h, offsetof(ZkhCtl, local), cudaMemcpyHostToDevice,
+                                  ctx->stream));
+    ScOut out{ctx->d_ctl->msgs, ctx->d_ctl->chals, ctx->d_ctl->finals};
+    ZKH_TRY(sc_enqueue(ctx, functor, nt, LD_PLAIN, cols_dev, logn, zkh_make_tag(tag), scratch, out));
+    ZKH_CUDA(ctx, cudaMemcpyAsync(h, ctx->d_ctl, sizeof(ZkhCtl), cudaMemcpyDeviceToHost, ctx->stream));
+    ZKH_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (h->err) return zkh_fail(ctx, ZKH_ERR_DEVICE, "sumcheck: device error flag set");
+    memcpy(msgs, h->msgs, (size_t)logn * nt * 8);
+    memcpy(chals, h->chals, (size_t)logn * 8);
+    if (finals) memcpy(finals, h->finals, (size_t)nc * 8);
+    digest_to_bytes(h->st, state);
+    return ZKH_OK;
+}
+
+static int sumcheck_check(zkh_ctx* ctx, int functor, int nt, const void* cols, int nc, uint32_t logn,
+                          const uint64_t* par, int npar, const char* tag, const void* state,
+                          const void* msgs, const void* chals) {
+    if (!ctx) return ZKH_ERR_ARG;
+    if (!cols || !tag || !state || !msgs || !chals) return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: null pointer");
+    if (functor_nc(functor) != nc) return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: nc does not match the summand");
+    if (nt < 3 || nt > 5) return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: nt must be 3..5");
+    if (logn < 1 || logn > 34) return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: logn must be 1..34");
+    if (logn > 80) return zkh_fail(ctx, ZKH_ERR_LIMIT, "sumcheck: too many rounds");
+    if (npar < 0 || npar > 8 || (npar > 0 && !par)) return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: bad par");
+    if (strlen(tag) > ZKH_TR_MAX_LABEL) return zkh_fail(ctx, ZKH_ERR_LIMIT, "sumcheck: tag longer than 48 bytes");
+    return ZKH_OK;
+}
+
+extern "C" int zkh_sumcheck(zkh_ctx* ctx, int functor, int nt, const uint64_t* const* cols_dev, int nc,
+                            uint32_t logn, const uint64_t* par, int npar, const char* tag,
+                            uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals) {
+    ZKH_TRY(sumcheck_check(ctx, functor, nt, cols_dev, nc, logn, par, npar, tag, state, msgs, chals));
+    ZKH_CUDA(ctx, cudaSetDevice(ctx->device));
+    ZKH_TRY(zkh_ws_reserve(ctx, sc_workspace_bytes(nc, logn)));
+    return sumcheck_common(ctx, functor, nt, cols_dev, nc, logn, par, npar, tag, state, msgs, chals,
+                           finals, ctx->ws);
+}
+
+extern "C" int zkh_sumcheck_host(zkh_ctx* ctx, int functor, int nt, const uint64_t* const* cols, int nc,
+                                 uint32_t logn, const uint64_t* par, int npar, const char* tag,
+                                 uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals) {
+    ZKH_TRY(sumcheck_check(ctx, functor, nt, cols, nc, logn, par, npar, tag, state, msgs, chals));
+    ZKH_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t colb = zkh_align(((size_t)8) << logn);
+    ZKH_TRY(zkh_ws_reserve(ctx, (size_t)nc * colb + sc_workspace_bytes(nc, logn)));
+    const uint64_t* d[8];
+    for (int k = 0; k < nc; k++) {
+        d[k] = (const uint64_t*)((char*)ctx->ws + (size_t)k * colb);
+        ZKH_CUDA(ctx, cudaMemcpyAsync((void*)d[k], cols[k], ((size_t)8) << logn, cudaMemcpyHostToDevice,
+                                      ctx->stream));
+    }
+    return sumcheck_common(ctx, functor, nt, d, nc, logn, par, npar, tag, state, msgs, chals, finals,
+                           (char*)ctx->ws + (size_t)nc * colb);
+}
