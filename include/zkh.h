@@ -85,6 +85,26 @@ ZKH_API int zkh_gl_mle_eval(zkh_ctx* ctx, const uint64_t* c_dev, const uint64_t*
  *                                          zkllm-src/p3_basefold.cuh:336-339 (p3bf_bind_kernel) */
 ZKH_API int zkh_gl_bind(zkh_ctx* ctx, const uint64_t* in_dev, uint64_t* out_dev, uint64_t n, uint64_t a);
 
+/* The same evaluation for callers that cannot allocate device memory: hosts that gave the
+ * whole GPU to their own arena, code inside a stream capture (cudaMalloc is illegal there),
+ * loops that cannot afford an allocation's device-wide synchronisation.  It calls no
+ * cudaMalloc/cudaFree or any allocating routine: its scratch (two eq factor tables and the
+ * per-CTA partial sums, 278,528 bytes) is a fixed __device__ array inside the library, which
+ * every GPU that runs it holds until the process exits.  Limits and rules:
+ *   - v <= 28 variables (2^28 coefficients); larger v returns ZKH_ERR_LIMIT with a message;
+ *   - works on the CURRENT device; queues three kernels on `stream` and returns without
+ *     synchronising; *y_dev (device memory of the caller) is valid once the stream reaches it;
+ *   - the first call on each device resolves the array's device address
+ *     (cudaGetSymbolAddress), so make that first call outside of any stream capture;
+ *   - all calls on a device share the array; it keeps the previous call's contents and
+ *     needs no clearing (each call writes every word it later reads); calls that overlap on
+ *     the GPU race on it, so order them on one stream or with events.
+ * errbuf (optional, errbuf_len bytes) receives the error text.
+ * This entry point has no counterpart in the reference, whose eval_h_gpu allocates four
+ * buffers per call (zkllm-src/p3_basefold.cuh:262-273). */
+ZKH_API int zkh_gl_mle_eval_static(void* stream, const uint64_t* c_dev, const uint64_t* z, uint32_t v,
+                                   uint64_t* y_dev, char* errbuf, size_t errbuf_len);
+
 /* ---- sumcheck prover (zkllm-src/p3_scgpu.cuh:91-160, p3sg::sc_prove_gpu) ----
  * Proves sum_b F(cols(b)) over 2^logn vertices, LSB-first binding.
  * Per round: nt evaluations at t=0..nt-1 are absorbed under `tag` (nt*8 bytes),

@@ -54,6 +54,7 @@ def load_library():
         "zkh_tr_idx": (u64, [vp, u64]),
         "zkh_gl_eq_build": (i, [vp, vp, u32, vp]),
         "zkh_gl_mle_eval": (i, [vp, vp, vp, u32, vp]),
+        "zkh_gl_mle_eval_static": (i, [vp, vp, vp, u32, vp, C.c_char_p, sz]),
         "zkh_gl_bind": (i, [vp, vp, vp, u64, u64]),
         "zkh_sumcheck": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_host": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),

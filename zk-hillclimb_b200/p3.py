@@ -85,6 +85,21 @@ def _ptr(t):
     return t if isinstance(t, int) else t.data_ptr()
 
 
+def eval_h_static(c_dev, z, y_dev, stream=None):
+    """MLE evaluation without any device allocation (zkh_gl_mle_eval_static): for hosts that
+    own all of HBM through their own arena, for code inside a stream capture, and for loops
+    that must not trigger an allocation's device synchronisation.  Works on the current CUDA
+    device; c_dev and y_dev are the caller's device tensors (y_dev: one element); at most 28
+    variables.  Asynchronous on ``stream``; calls sharing a device must not overlap."""
+    L = load_library()
+    z = np.ascontiguousarray(z, dtype=np.uint64)
+    err = C.create_string_buffer(256)
+    rc = L.zkh_gl_mle_eval_static(C.c_void_p(stream or 0), _ptr(c_dev), z.ctypes.data, len(z), _ptr(y_dev),
+                                  err, len(err))
+    if rc != 0:
+        raise ZkhError(rc, err.value.decode())
+
+
 class Prover:
     """One per GPU: owns a library context (workspace, control block, stream)."""
 
