@@ -127,6 +127,49 @@ ZKH_API int zkh_sumcheck_host(zkh_ctx* ctx, int functor, int nt, const uint64_t*
 /* Bytes of workspace zkh_sumcheck needs for (nc, logn). */
 ZKH_API size_t zkh_sumcheck_workspace(int nc, uint32_t logn);
 
+/* ---- Reed-Solomon encode / NTT (zkllm-src/p3_ntt.cuh:170-230 P3Ntt::run,
+ *      p3_basefold.cuh:188-197 rs_encode_gpu_dev) ----
+ * out[k] = sum_j in[j]*w^(jk) over the 2^logn subgroup, natural order in and out; inverse
+ * divides by n.  in_dev and out_dev must differ.  Stream-ordered (no host sync). */
+ZKH_API int zkh_ntt(zkh_ctx* ctx, const uint64_t* in_dev, uint64_t* out_dev, uint32_t logn, int inverse);
+/* Codeword of the 2^v coefficients at rate 2^-R: forward NTT of the zero-padded vector.
+ * cw_dev: 2^(v+R) elements.  Stream-ordered. */
+ZKH_API int zkh_rs_encode(zkh_ctx* ctx, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t* cw_dev);
+
+/* ---- SHA-256 Merkle tree (zkllm-src/p3_fri.cuh:97-178 DeviceMerkle, p3_merkle.cuh:161-207) ----
+ * Leaf = SHA-256(8-byte LE element), node = one compression of left|right from the IV.
+ * tree_dev (optional, zkh_merkle_tree_bytes(M) bytes) receives all levels: M leaf digests,
+ * M/2, ..., root.  root (optional, host) receives the 32-byte root; when given the call
+ * synchronises.  With tree_dev == NULL only the root is computed. */
+ZKH_API size_t zkh_merkle_tree_bytes(uint64_t M);
+ZKH_API int zkh_merkle_build(zkh_ctx* ctx, const uint64_t* cw_dev, uint64_t M, uint8_t* tree_dev, uint8_t root[32]);
+/* Authentication paths (zkllm-src/p3_fri.cuh:164-178 paths_batch): for each of the n leaf
+ * indices, log2(M) sibling digests from the leaf level up; out: n*log2(M)*32 bytes (host). */
+ZKH_API int zkh_merkle_paths(zkh_ctx* ctx, const uint8_t* tree_dev, uint64_t M, const uint32_t* idx, uint32_t n,
+                             uint8_t* out);
+
+/* ---- Basefold ---- */
+/* MLE fold of a codeword of length M with challenge beta:
+ * out[c] = (1-beta)*(f[c]+f[c+M/2])/2 + beta*(f[c]-f[c+M/2])/(2*w^c), w the primitive M-th root.
+ * (zkllm-src/p3_basefold.cuh:239-245 p3bf_fold_kernel, p3_fri.cuh:396-415.)  Stream-ordered. */
+ZKH_API int zkh_gl_fold_codeword(zkh_ctx* ctx, const uint64_t* f_dev, uint64_t* out_dev, uint64_t M, uint64_t beta);
+/* Commitment root of the 2^v device coefficients at rate 2^-R (zkllm-src/p3_basefold.cuh:210-227
+ * commit_gpu_rootonly).  cw_dev (optional, 2^(v+R) elements) keeps the codeword. */
+ZKH_API int zkh_basefold_commit(zkh_ctx* ctx, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t* cw_dev,
+                                uint8_t root[32]);
+/* Same from HOST coefficients (upload inside), as the reference's entry point takes them. */
+ZKH_API int zkh_basefold_commit_host(zkh_ctx* ctx, const uint64_t* coeffs, uint32_t v, uint32_t R, uint8_t root[32]);
+/* Evaluation opening (zkllm-src/p3_basefold.cuh:355-420 prove_eval_dev): proves y = c~(z).
+ * cw0_dev: the committed codeword (2^(v+R) elements) or NULL to re-encode here.
+ * The proof is serialised little-endian as
+ *   u32 logN, R, Q | roots v*32 | messages v*24 | final word 2^R*8 |
+ *   per query, per round r: a(8) b(8) path_a((v+R-r)*32) path_b((v+R-r)*32) | z v*8 | y 8
+ * (the fields of p3bf::EvalProof in declaration order); *written = zkh_basefold_proof_size. */
+ZKH_API size_t zkh_basefold_proof_size(uint32_t v, uint32_t R, uint32_t Q);
+ZKH_API int zkh_basefold_open(zkh_ctx* ctx, const uint64_t* c_dev, const uint64_t* z, uint32_t v, uint64_t y,
+                              uint32_t R, uint32_t Q, const uint64_t* cw0_dev, const char* seed, uint8_t* out,
+                              size_t cap, size_t* written);
+
 #ifdef __cplusplus
 }
 #endif

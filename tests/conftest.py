@@ -43,6 +43,13 @@ def ref():
 
 
 @pytest.fixture(scope="session")
+def ref_or_none():
+    """Reference shim if built, else None (tests then rely on the oracle and the goldens)."""
+    from oracle import Reference
+    return Reference() if Reference.available() else None
+
+
+@pytest.fixture(scope="session")
 def zk():
     import zkh_import
     return zkh_import.load()
@@ -54,7 +61,7 @@ def prover(zk):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     torch.cuda.init()
-    p = zk.Prover(0)
+    p = zk.Prover(0, torch.cuda.current_stream().cuda_stream)   # same stream as torch: ordered with its copies
     yield p
     p.close()
 

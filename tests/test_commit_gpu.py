@@ -1,0 +1,168 @@
+"""Parity of the CUDA commitment path (NTT encode, Merkle, fold, Basefold commit/open) with the
+oracle, the golden vectors minted from the reference, the reference verifier and the
+reference's own CUDA prover."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import dig
+
+pytestmark = pytest.mark.gpu
+GL_P = 0xFFFFFFFF00000001
+
+
+@pytest.mark.parametrize("max_digit", [None, 3, 4])
+def test_ntt_matches_oracle(orc, zk, prover, max_digit, monkeypatch):
+    if max_digit:
+        monkeypatch.setenv("ZKH_NTT_MAX_DIGIT", str(max_digit))   # forces 3 and 4 pass plans at small sizes
+    sizes = [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12] + ([13, 14, 17, 18, 19, 20] if not max_digit else [])
+    for logn in sizes:
+        x, _ = orc.lcg(1 << logn, 70 + logn)
+        got = zk.p3.to_host(prover.ntt(zk.p3.to_device(x)))
+        prover.sync()
+        assert (got == orc.ntt(x)).all(), logn
+        back = zk.p3.to_host(prover.ntt(zk.p3.to_device(got), inverse=True))
+        assert (back == x).all(), logn
+
+
+def test_ntt_naive_dft_pin(orc, zk, prover):
+    # the reference's own pin: naive DFT at n = 8 (zkllm-src/p3_commit_bench.cu:20-41)
+    x, _ = orc.lcg(8, 7)
+    w = orc.gl_root_of_unity(3)
+    naive = [sum(int(x[j]) * pow(w, j * k, GL_P) for j in range(8)) % GL_P for k in range(8)]
+    assert [int(t) for t in zk.p3.to_host(prover.ntt(zk.p3.to_device(x)))] == naive
+
+
+def test_encode_merkle_fold_golden(golden, orc, zk, prover):
+    for e in golden["encode"]:
+        v, R = e["v"], e["R"]
+        cc, _ = orc.lcg(1 << v, e["seed"])
+        cw_dev = prover.rs_encode_gpu_dev(zk.p3.to_device(cc), R)
+        cw = zk.p3.to_host(cw_dev)
+        assert dig(cw) == e["cw_digest"]
+        root, tree = prover.merkle_build_dev(cw_dev)
+        assert root.hex() == e["root"]
+        assert dig(tree.cpu().numpy()) == e["tree_digest"]
+        assert prover.commit_gpu_rootonly(cc, R).hex() == e["root"]
+        assert prover.commit_gpu_rootonly(zk.p3.to_device(cc), R).hex() == e["root"]
+        out = prover.fold_gpu(cw_dev, int(cc[0]))
+        prover.sync()
+        assert dig(zk.p3.to_host(out)) == e["fold_mle_digest"]
+
+
+@pytest.mark.parametrize("logM", [1, 2, 3, 4, 5, 6, 9, 10, 11, 14, 17])
+def test_merkle_and_paths(orc, zk, prover, logM):
+    M = 1 << logM
+    cw, _ = orc.lcg(M, 300 + logM)
+    cw_dev = zk.p3.to_device(cw)
+    root, tree = prover.merkle_build_dev(cw_dev)
+    want = orc.merkle_build(cw)
+    assert (tree.cpu().numpy() == want).all()
+    assert root == want[-32:].tobytes() == orc.merkle_root(cw)
+    root2, none = prover.merkle_build_dev(cw_dev, keep_tree=False)
+    assert root2 == root and none is None
+    idxs = sorted({0, M - 1, M // 2, (M * 3) // 7})
+    paths = prover.paths_batch(tree, M, idxs)
+    for i, p in zip(idxs, paths):
+        leaf = orc.sha256(int(cw[i]).to_bytes(8, "little"))
+        h, j = leaf, i
+        for sib in p:
+            h = orc.compress64(sib + h) if j & 1 else orc.compress64(h + sib)
+            j >>= 1
+        assert h == root
+    with pytest.raises(zk.ZkhError):
+        prover.paths_batch(tree, M, [M])
+
+
+@pytest.mark.parametrize("logM", [1, 2, 5, 12, 15, 20])
+def test_fold_matches_oracle(orc, zk, prover, logM):
+    f, s = orc.lcg(1 << logM, 400 + logM)
+    beta = int(orc.lcg(1, s)[0][0])
+    out = prover.fold_gpu(zk.p3.to_device(f), beta)
+    prover.sync()
+    assert (zk.p3.to_host(out) == orc.fold(f, orc.gl_root_of_unity(logM), beta, True)).all()
+
+
+def test_basefold_open_golden(golden, orc, ref_or_none, zk, prover):
+    for b in golden["basefold"]:
+        v, R, Q = b["v"], b["R"], b["Q"]
+        cc, s2 = orc.lcg(1 << v, b["seed"])
+        zz, _ = orc.lcg(v, s2)
+        c_dev = zk.p3.to_device(cc)
+        assert prover.eval_h_gpu(c_dev, zz) == b["y"]
+        pf = prover.prove_eval_dev(c_dev, zz, b["y"], R, Q)
+        assert len(pf) == b["proof_len"] and dig(pf) == b["proof_digest"]
+        assert orc.bf_verify_eval(pf)
+        if ref_or_none:
+            assert ref_or_none.bf_verify_eval(pf)
+
+
+@pytest.mark.parametrize("v,R,Q", [(1, 1, 4), (2, 1, 8), (3, 2, 8), (5, 3, 24), (9, 1, 24), (12, 2, 24), (13, 1, 24), (16, 1, 24)])
+def test_basefold_open_matches_oracle(orc, ref_or_none, zk, prover, v, R, Q):
+    cc, s = orc.lcg(1 << v, 500 + v)
+    zz, _ = orc.lcg(v, s)
+    y = orc.mle_eval(cc, zz)
+    c_dev = zk.p3.to_device(cc)
+    want = orc.bf_prove_eval(cc, zz, y, R, Q, orc.rs_encode(cc, R), "seed-%d" % v)
+    got = prover.prove_eval_dev(c_dev, zz, y, R, Q, None, "seed-%d" % v)
+    assert got == want
+    # with the committed codeword handed in (the reference's calling convention)
+    cw_dev = prover.rs_encode_gpu_dev(c_dev, R)
+    assert prover.prove_eval_dev(c_dev, zz, y, R, Q, cw_dev, "seed-%d" % v) == want
+    assert (zk.p3.to_host(c_dev) == cc).all()
+    if ref_or_none:
+        assert ref_or_none.bf_verify_eval(got, "seed-%d" % v)
+        bad = bytearray(got)
+        bad[12 + v * 32] ^= 1
+        assert not ref_or_none.bf_verify_eval(bytes(bad), "seed-%d" % v)
+    # proving a wrong value must be rejected (the reference's tamper battery, p3_basefold_selftest.cu:55-57)
+    wrong = prover.prove_eval_dev(c_dev, zz, (y + 1) % GL_P, R, Q, None, "seed-%d" % v)
+    assert not orc.bf_verify_eval(wrong, "seed-%d" % v)
+
+
+def test_commit_and_open_at_scale(orc, ref_or_none, zk, prover):
+    """2^22 coefficients: root equals the oracle's, and the opening verifies under the reference's verifier."""
+    v, R, Q = 22, 1, 24
+    cc, s = orc.lcg(1 << v, 0xBEEF1234)
+    zz, _ = orc.lcg(v, s)
+    c_dev = zk.p3.to_device(cc)
+    cw_dev = prover.rs_encode_gpu_dev(c_dev, R)
+    root = prover.commit_gpu_rootonly(cc, R)
+    cw = orc.rs_encode(cc, R)
+    assert (zk.p3.to_host(cw_dev) == cw).all()
+    assert root == orc.merkle_root(cw)
+    y = prover.eval_h_gpu(c_dev, zz)
+    pf = prover.prove_eval_dev(c_dev, zz, y, R, Q, cw_dev)
+    assert pf[12:44] == root
+    assert orc.bf_verify_eval(pf)
+    if ref_or_none:
+        assert ref_or_none.bf_verify_eval(pf)
+
+
+def test_reference_cuda_commit_and_open_same_bytes(orc, ref, zk, prover):
+    if not ref.gpu_available():
+        pytest.skip("reference shim sees no GPU")
+    v, R, Q = 16, 1, 24
+    cc, s = orc.lcg(1 << v, 777)
+    zz, _ = orc.lcg(v, s)
+    root_ref, _ = ref.commit_gpu_rootonly(cc, R)
+    assert prover.commit_gpu_rootonly(cc, R) == root_ref
+    cw = ref.rs_encode_gpu(cc, R)
+    c_dev = zk.p3.to_device(cc)
+    assert (zk.p3.to_host(prover.rs_encode_gpu_dev(c_dev, R)) == cw).all()
+    y = orc.mle_eval(cc, zz)
+    pf_ref, _ = ref.bf_prove_eval_dev(cc, zz, y, R, Q, cw)
+    assert prover.prove_eval_dev(c_dev, zz, y, R, Q) == pf_ref
+
+
+def test_commit_argument_errors(zk, prover):
+    x = zk.p3.to_device(np.arange(8, dtype=np.uint64))
+    with pytest.raises(zk.ZkhError):
+        prover.ntt(x, out=x)
+    with pytest.raises(zk.ZkhError):
+        prover.commit_gpu_rootonly(x, 0)
+    with pytest.raises(zk.ZkhError):
+        prover.prove_eval_dev(x, np.zeros(3, np.uint64), 0, 9, 24)
+    with pytest.raises(zk.ZkhError):
+        prover.fold_gpu(x, GL_P)

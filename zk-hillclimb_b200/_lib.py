@@ -59,6 +59,16 @@ def load_library():
         "zkh_sumcheck": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_host": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_workspace": (sz, [i, u32]),
+        "zkh_ntt": (i, [vp, vp, vp, u32, i]),
+        "zkh_rs_encode": (i, [vp, vp, u32, u32, vp]),
+        "zkh_merkle_tree_bytes": (sz, [u64]),
+        "zkh_merkle_build": (i, [vp, vp, u64, vp, vp]),
+        "zkh_merkle_paths": (i, [vp, vp, u64, vp, u32, vp]),
+        "zkh_gl_fold_codeword": (i, [vp, vp, vp, u64, u64]),
+        "zkh_basefold_commit": (i, [vp, vp, u32, u32, vp, vp]),
+        "zkh_basefold_commit_host": (i, [vp, vp, u32, u32, vp]),
+        "zkh_basefold_proof_size": (sz, [u32, u32, u32]),
+        "zkh_basefold_open": (i, [vp, vp, vp, u32, u64, u32, u32, vp, C.c_char_p, vp, sz, C.POINTER(sz)]),
     }
     for name, (res, args) in sig.items():
         f = getattr(L, name)

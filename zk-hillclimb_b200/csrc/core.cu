@@ -250,44 +250,51 @@ __global__ void sum_partials_kernel(const gl_t* partials, uint32_t n, gl_t* out)
     if (threadIdx.x == 0) *out = s[0];
 }
 
-// builds the two factor tables in the workspace head; returns their device pointers
-static int eq_tables(zkh_ctx* c, const uint64_t* z, uint32_t v, gl_t** lo, gl_t** hi, uint32_t* vl_out,
-                     size_t ws_extra, void** extra) {
-    if (v > 60) return zkh_fail(c, ZKH_ERR_ARG, "eq: more than 60 variables");
+// Two factor tables of eq(.,z) in `scratch` (eq_scratch_bytes(v)); z is a host pointer.
+size_t zkh::eq_scratch_bytes(uint32_t v) {
+    uint32_t vl = v <= 1 ? v : v / 2;
+    if (vl > 14) vl = 14;
+    return zkh_align(((size_t)8) << vl) + zkh_align(((size_t)8) << (v - vl)) + zkh_align((size_t)64 * 8);
+}
+static int eq_tables(zkh_ctx* c, const uint64_t* z, uint32_t v, void* scratch, gl_t** lo, gl_t** hi, uint32_t* vl_out) {
     uint32_t vl = v <= 1 ? v : v / 2;
     if (vl > 14) vl = 14;
     uint32_t vh = v - vl;
-    if (vh > 26) return zkh_fail(c, ZKH_ERR_LIMIT, "eq: more than 40 variables");
+    if (v > 40) return zkh_fail(c, ZKH_ERR_LIMIT, "eq: more than 40 variables");
     size_t tl = zkh_align(((size_t)8) << vl), th = zkh_align(((size_t)8) << vh);
-    ZKH_TRY(zkh_ws_reserve(c, tl + th + ws_extra));
-    *lo = (gl_t*)c->ws;
-    *hi = (gl_t*)((char*)c->ws + tl);
-    if (extra) *extra = (char*)c->ws + tl + th;
+    *lo = (gl_t*)scratch;
+    *hi = (gl_t*)((char*)scratch + tl);
+    gl_t* dz = (gl_t*)((char*)scratch + tl + th);
     *vl_out = vl;
-    // the point travels through the control block's aux area
-    if (v > 64) return zkh_fail(c, ZKH_ERR_LIMIT, "eq: point too long");
-    memcpy(c->h_ctl->aux, z, (size_t)v * 8);
-    ZKH_CUDA(c, cudaMemcpyAsync(c->d_ctl->aux, c->h_ctl->aux, (size_t)v * 8, cudaMemcpyHostToDevice, c->stream));
-    eq_small_kernel<<<((1u << vl) + 255) / 256, 256, 0, c->stream>>>(c->d_ctl->aux, 0, vl, *lo);
-    eq_small_kernel<<<((1u << vh) + 255) / 256, 256, 0, c->stream>>>(c->d_ctl->aux, vl, vh, *hi);
+    // the point is staged in pageable memory by the runtime, so z may be reused by the caller at once
+    ZKH_CUDA(c, cudaMemcpyAsync(dz, z, (size_t)v * 8, cudaMemcpyHostToDevice, c->stream));
+    eq_small_kernel<<<((1u << vl) + 255) / 256, 256, 0, c->stream>>>(dz, 0, vl, *lo);
+    eq_small_kernel<<<((1u << vh) + 255) / 256, 256, 0, c->stream>>>(dz, vl, vh, *hi);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+int zkh::eq_enqueue(zkh_ctx* c, const uint64_t* z, uint32_t v, gl_t* out_dev, void* scratch) {
+    if (v == 0) {
+        static const uint64_t one = 1;
+        ZKH_CUDA(c, cudaMemcpyAsync(out_dev, &one, 8, cudaMemcpyHostToDevice, c->stream));
+        return ZKH_OK;
+    }
+    gl_t *lo, *hi;
+    uint32_t vl;
+    ZKH_TRY(eq_tables(c, z, v, scratch, &lo, &hi, &vl));
+    size_t n = (size_t)1 << v;
+    size_t blocks = (n / 2 + 255) / 256, cap = (size_t)c->sm_count * 8;
+    eq_expand_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(lo, hi, vl, out_dev, n);
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }
 
 extern "C" int zkh_gl_eq_build(zkh_ctx* c, const uint64_t* z, uint32_t v, uint64_t* out_dev) {
-    if (!c || !z || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "eq_build: null pointer");
+    if (!c || !out_dev || (v && !z)) return zkh_fail(c, ZKH_ERR_ARG, "eq_build: null pointer");
+    if (v > 40) return zkh_fail(c, ZKH_ERR_LIMIT, "eq_build: more than 40 variables");
     ZKH_CUDA(c, cudaSetDevice(c->device));
-    if (v == 0) {
-        uint64_t one = 1;
-        return zkh_upload(c, out_dev, &one, 8);
-    }
-    gl_t *lo, *hi;
-    uint32_t vl;
-    ZKH_TRY(eq_tables(c, z, v, &lo, &hi, &vl, 0, nullptr));
-    size_t n = (size_t)1 << v;
-    size_t blocks = (n / 2 + 255) / 256, cap = (size_t)c->sm_count * 8;
-    eq_expand_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(lo, hi, vl, out_dev, n);
-    ZKH_CUDA(c, cudaGetLastError());
+    ZKH_TRY(zkh_ws_reserve(c, eq_scratch_bytes(v)));
+    ZKH_TRY(eq_enqueue(c, z, v, out_dev, c->ws));
     ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
     return ZKH_OK;
 }
@@ -296,9 +303,11 @@ extern "C" int zkh_gl_mle_eval(zkh_ctx* c, const uint64_t* c_dev, const uint64_t
     if (!c || !c_dev || !z || !y) return zkh_fail(c, ZKH_ERR_ARG, "mle_eval: null pointer");
     ZKH_CUDA(c, cudaSetDevice(c->device));
     if (v == 0) return zkh_download(c, y, c_dev, 8);
+    if (v > 40) return zkh_fail(c, ZKH_ERR_LIMIT, "mle_eval: more than 40 variables");
     gl_t *lo, *hi;
     uint32_t vl;
-    ZKH_TRY(eq_tables(c, z, v, &lo, &hi, &vl, 0, nullptr));
+    ZKH_TRY(zkh_ws_reserve(c, eq_scratch_bytes(v)));
+    ZKH_TRY(eq_tables(c, z, v, c->ws, &lo, &hi, &vl));
     size_t n = (size_t)1 << v;
     size_t blocks = (n / 2 + 255) / 256, cap = (size_t)c->sm_count * 8;
     unsigned g = (unsigned)(blocks < cap ? blocks : cap);

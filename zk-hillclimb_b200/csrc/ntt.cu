@@ -1,0 +1,217 @@
+// Goldilocks NTT / Reed-Solomon encode for sm_100a.
+//
+// The reference encodes with a bit-reversal pass plus ceil(logM/2) global-memory
+// radix-4 passes (zkllm-src/p3_ntt.cuh:210-230).  Here the transform is split into
+// at most four digits of up to 9 bits (Cooley-Tukey, most significant input digit
+// first).  One pass = one kernel: a CTA pulls a (2^W x 16)-element tile into shared
+// memory with 128-byte segments, runs all W butterfly stages there, applies the
+// inter-digit twiddle and writes back; the last pass writes the digit-reversed
+// (natural-order) result.  A 2^25 codeword takes 3 passes over HBM instead of 14.
+//
+// out[k] = sum_j in[j] * w^(jk), w = the primitive 2^logM-th root the reference uses
+// (zkllm-src/p3_goldilocks.cuh:70-73).  The transform is exact field arithmetic, so the
+// codeword is bit-identical to the reference's whatever the factorisation.
+#include "ntt.cuh"
+
+namespace zkh {
+
+struct NttPass {
+    uint32_t logM, W, ls, lb, logT, last, np;
+    uint32_t ws[4];
+    uint32_t tw_lb;
+    const gl_t* tw_lo;
+    const gl_t* tw_hi;
+    uint64_t nin;  // input elements at positions >= nin are zero (only the first pass reads `in`)
+};
+
+__device__ __forceinline__ gl_t tw_pow(const NttPass& p, uint64_t e) {
+    const uint64_t lo = e & ((1ull << p.tw_lb) - 1), hi = e >> p.tw_lb;
+    gl_t a = p.tw_lo[lo];
+    return hi ? gl_mul(a, p.tw_hi[hi]) : a;
+}
+
+__global__ void pow_table_kernel(gl_t* out, gl_t base, uint32_t cnt) {
+    uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < cnt) out[k] = gl_pow(base, k);
+}
+
+__global__ void __launch_bounds__(256) ntt_pass_kernel(const gl_t* __restrict__ in, gl_t* __restrict__ out,
+                                                       NttPass p) {
+    extern __shared__ gl_t sm[];
+    const uint32_t W = p.W, nW = 1u << W, T = 1u << p.logT, TP = T + 1, tid = threadIdx.x;
+    gl_t* tile = sm;
+    gl_t* tws = sm + (size_t)nW * TP;
+    // tile origin: spread the CTA index over the index bits that are neither digit nor batch bits
+    size_t base = 0;
+    {
+        size_t c = blockIdx.x;
+        uint32_t cb = 0;
+        for (uint32_t bit = 0; bit < p.logM; bit++) {
+            if (bit >= p.ls && bit < p.ls + W) continue;
+            if (p.logT && bit >= p.lb && bit < p.lb + p.logT) continue;
+            base |= ((c >> cb) & 1) << bit;
+            cb++;
+        }
+    }
+    for (uint32_t e = tid; e < nW / 2; e += blockDim.x) tws[e] = tw_pow(p, (uint64_t)e << (p.logM - W));
+    const uint32_t nel = nW << p.logT;
+    if (p.ls == 0) {  // the digit is contiguous in memory: run along it
+        for (uint32_t x = tid; x < nel; x += blockDim.x) {
+            uint32_t d = x & (nW - 1), t = x >> W;
+            size_t pos = base | d | ((size_t)t << p.lb);
+            tile[d * TP + t] = pos < p.nin ? in[pos] : 0;
+        }
+    } else {  // batch elements are contiguous
+        for (uint32_t x = tid; x < nel; x += blockDim.x) {
+            uint32_t t = x & (T - 1), d = x >> p.logT;
+            size_t pos = base | ((size_t)d << p.ls) | ((size_t)t << p.lb);
+            tile[d * TP + t] = pos < p.nin ? in[pos] : 0;
+        }
+    }
+    __syncthreads();
+    // decimation in frequency: natural order in, bit-reversed digit out
+    for (uint32_t s = 0; s < W; s++) {
+        const uint32_t half = nW >> (s + 1);
+        for (uint32_t b = tid; b < nel / 2; b += blockDim.x) {
+            uint32_t t = b & (T - 1), q = b >> p.logT;
+            uint32_t i = q & (half - 1), d0 = ((q - i) << 1) + i, d1 = d0 + half;
+            gl_t u = tile[d0 * TP + t], v = tile[d1 * TP + t];
+            tile[d0 * TP + t] = gl_add(u, v);
+            gl_t df = gl_sub(u, v);
+            tile[d1 * TP + t] = i ? gl_mul(df, tws[i << s]) : df;
+        }
+        __syncthreads();
+    }
+    for (uint32_t x = tid; x < nel; x += blockDim.x) {
+        uint32_t t = x & (T - 1), k = x >> p.logT;
+        gl_t val = tile[(__brev(k) >> (32 - W)) * TP + t];
+        size_t pos = base | ((size_t)t << p.lb);
+        if (!p.last) {
+            uint64_t jlow = pos & (((size_t)1 << p.ls) - 1);
+            uint64_t e = (jlow * k) << (p.logM - (W + p.ls));
+            if (e) val = gl_mul(val, tw_pow(p, e));
+            out[pos | ((size_t)k << p.ls)] = val;
+        } else {
+            // digits of pos, most significant first, become the least significant digits of the output index
+            size_t outp = 0;
+            uint32_t ph = p.logM, sh = 0;
+            for (uint32_t j = 0; j + 1 < p.np; j++) {
+                ph -= p.ws[j];
+                outp |= ((pos >> ph) & (((size_t)1 << p.ws[j]) - 1)) << sh;
+                sh += p.ws[j];
+            }
+            out[outp | ((size_t)k << sh)] = val;
+        }
+    }
+}
+
+__global__ void scale_kernel(gl_t* a, gl_t c, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] = gl_mul(a[i], c);
+}
+
+static int max_digit_bits() {
+    const char* e = getenv("ZKH_NTT_MAX_DIGIT");  // test hook: force many passes at small sizes
+    int v = e ? atoi(e) : 9;
+    if (v < 2) v = 2;
+    if (v > 9) v = 9;
+    return v;
+}
+
+static int ntt_tables(zkh_ctx* c, uint32_t logM, bool inverse, const gl_t** lo, const gl_t** hi, uint32_t* lb_out) {
+    zkh_ctx::Tw& t = c->tw[logM];
+    gl_t*& tl = inverse ? t.lo_inv : t.lo;
+    gl_t*& th = inverse ? t.hi_inv : t.hi;
+    uint32_t lb = logM <= 13 ? logM : (logM + 1) / 2;
+    if (lb < 1) lb = 1;
+    if (!tl) {
+        uint32_t nlo = 1u << lb, nhi = 1u << (logM > lb ? logM - lb : 0);
+        gl_t* p = nullptr;
+        cudaError_t e = cudaMalloc(&p, (size_t)(nlo + nhi) * 8);
+        if (e != cudaSuccess) { cudaGetLastError(); return zkh_fail(c, ZKH_ERR_NOMEM, "ntt: twiddle table allocation failed"); }
+        gl_t w = gl_root_of_unity(logM);
+        if (inverse) w = gl_inv(w);
+        pow_table_kernel<<<(nlo + 255) / 256, 256, 0, c->stream>>>(p, w, nlo);
+        pow_table_kernel<<<(nhi + 255) / 256, 256, 0, c->stream>>>(p + nlo, gl_pow(w, (uint64_t)1 << lb), nhi);
+        ZKH_CUDA(c, cudaGetLastError());
+        tl = p;
+        th = p + nlo;
+        t.lb = lb;
+    }
+    *lo = tl;
+    *hi = th;
+    *lb_out = lb;
+    return ZKH_OK;
+}
+
+int ntt_inverse_tables(zkh_ctx* c, uint32_t logM, const gl_t** lo, const gl_t** hi, uint32_t* lb) {
+    return ntt_tables(c, logM, true, lo, hi, lb);
+}
+
+size_t ntt_scratch_bytes(uint32_t logM) {
+    return (logM + max_digit_bits() - 1) / max_digit_bits() > 1 ? zkh_align(((size_t)8) << logM) : 256;
+}
+
+// in: nin valid elements (the rest of the 2^logM input is implicitly zero); out: 2^logM elements.
+// in may equal out only when the transform needs more than one pass.
+int ntt_enqueue(zkh_ctx* c, const gl_t* in, uint64_t nin, gl_t* out, uint32_t logM, bool inverse, void* scratch) {
+    if (logM < 1 || logM > 32) return zkh_fail(c, ZKH_ERR_ARG, "ntt: logM must be 1..32");
+    const int maxw = max_digit_bits();
+    NttPass p;
+    memset(&p, 0, sizeof p);
+    p.logM = logM;
+    p.np = (logM + maxw - 1) / maxw;
+    if (p.np > 4) return zkh_fail(c, ZKH_ERR_LIMIT, "ntt: more than four digits");
+    for (uint32_t i = 0; i < p.np; i++) p.ws[i] = logM / p.np + (i < logM % p.np ? 1 : 0);
+    ZKH_TRY(ntt_tables(c, logM, inverse, &p.tw_lo, &p.tw_hi, &p.tw_lb));
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(ntt_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
+        attr_set = true;
+    }
+    gl_t* tmp = (gl_t*)scratch;
+    uint32_t pos_hi = logM;
+    const gl_t* src = in;
+    for (uint32_t i = 0; i < p.np; i++) {
+        p.W = p.ws[i];
+        p.ls = pos_hi - p.W;
+        p.last = (i == p.np - 1);
+        if (p.np == 1) { p.logT = 0; p.lb = 0; }
+        else if (p.last) { p.logT = p.ws[0] < 4 ? p.ws[0] : 4; p.lb = logM - p.ws[0]; }
+        else { p.logT = p.ls < 4 ? p.ls : 4; p.lb = 0; }
+        p.nin = (i == 0) ? nin : ((uint64_t)1 << logM);
+        gl_t* dst = p.last ? out : tmp;
+        size_t smem = ((size_t)(1u << p.W) * ((1u << p.logT) + 1) + (1u << p.W) / 2 + 1) * 8;
+        unsigned grid = (unsigned)(((size_t)1 << logM) >> (p.W + p.logT));
+        ntt_pass_kernel<<<grid, 256, smem, c->stream>>>(src, dst, p);
+        src = dst;
+        pos_hi = p.ls;
+    }
+    if (inverse) {
+        size_t n = (size_t)1 << logM;
+        scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(out, gl_inv((gl_t)n), n);
+    }
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+
+}  // namespace zkh
+
+using namespace zkh;
+
+extern "C" int zkh_ntt(zkh_ctx* c, const uint64_t* in_dev, uint64_t* out_dev, uint32_t logn, int inverse) {
+    if (!c || !in_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "ntt: null pointer");
+    if (in_dev == out_dev) return zkh_fail(c, ZKH_ERR_ARG, "ntt: in and out must differ");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    ZKH_TRY(zkh_ws_reserve(c, ntt_scratch_bytes(logn)));
+    return ntt_enqueue(c, in_dev, (uint64_t)1 << logn, out_dev, logn, inverse != 0, c->ws);
+}
+
+extern "C" int zkh_rs_encode(zkh_ctx* c, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t* cw_dev) {
+    if (!c || !c_dev || !cw_dev) return zkh_fail(c, ZKH_ERR_ARG, "rs_encode: null pointer");
+    if (v + R < 1 || v + R > 32 || R > 8) return zkh_fail(c, ZKH_ERR_ARG, "rs_encode: need 1 <= v+R <= 32, R <= 8");
+    if (c_dev == cw_dev) return zkh_fail(c, ZKH_ERR_ARG, "rs_encode: in and out must differ");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    ZKH_TRY(zkh_ws_reserve(c, ntt_scratch_bytes(v + R)));
+    return ntt_enqueue(c, c_dev, (uint64_t)1 << v, cw_dev, v + R, false, c->ws);
+}

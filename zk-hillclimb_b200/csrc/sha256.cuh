@@ -161,6 +161,45 @@ GL_HD void tr_challenge(uint32_t st[8], uint32_t out[8]) {
 #pragma unroll
     for (int i = 0; i < 8; i++) st[i] = ns[i];
 }
+#ifdef __CUDACC__
+// Device form of tr_absorb for one thread: the message is assembled as bytes in shared
+// memory (buf: at least 32+4+48+8+320+72 bytes, 4-byte aligned) and read back as words,
+// which avoids local-memory byte traffic in the serial part of a round.
+__device__ __forceinline__ void tr_absorb_sh(uint32_t st[8], const char* label, uint32_t ll,
+                                             const uint64_t* vals, uint32_t nvals, uint32_t* buf) {
+    uint8_t* b = reinterpret_cast<uint8_t*>(buf);
+#pragma unroll
+    for (int i = 0; i < 8; i++) buf[i] = bswap32(st[i]);
+    uint32_t p = 32;
+    b[p++] = (uint8_t)ll; b[p++] = (uint8_t)(ll >> 8); b[p++] = 0; b[p++] = 0;
+    for (uint32_t i = 0; i < ll; i++) b[p++] = (uint8_t)label[i];
+    const uint32_t len = nvals * 8;
+    b[p++] = (uint8_t)len; b[p++] = (uint8_t)(len >> 8);
+    for (int i = 0; i < 6; i++) b[p++] = 0;
+    for (uint32_t k = 0; k < nvals; k++) {
+        uint64_t v = vals[k];
+#pragma unroll
+        for (int j = 0; j < 8; j++) b[p++] = (uint8_t)(v >> (8 * j));
+    }
+    const uint32_t total = p, padded = ((total + 8) / 64 + 1) * 64;
+    b[p++] = 0x80;
+    while (p < padded - 8) b[p++] = 0;
+    const uint64_t bits = (uint64_t)total * 8;
+#pragma unroll
+    for (int i = 0; i < 8; i++) b[padded - 1 - i] = (uint8_t)(bits >> (8 * i));
+    uint32_t h[8];
+    sha256_iv(h);
+    for (uint32_t off = 0; off < padded / 4; off += 16) {
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) w[i] = bswap32(buf[off + i]);
+        sha256_compress(h, w);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) st[i] = h[i];
+}
+#endif
+
 // first 8 digest bytes as a little-endian u64
 GL_HD uint64_t digest_le64(const uint32_t out[8]) {
     return (uint64_t)bswap32(out[0]) | ((uint64_t)bswap32(out[1]) << 32);
@@ -169,7 +208,8 @@ GL_HD uint64_t digest_le64(const uint32_t out[8]) {
 GL_HD gl_t tr_chal_gl(uint32_t st[8]) {
     uint32_t out[8];
     tr_challenge(st, out);
-    return digest_le64(out) % GL_P;
+    uint64_t v = digest_le64(out);   // v < 2^64 < 2p: one conditional subtraction is the remainder
+    return v >= GL_P ? v - GL_P : v;
 }
 // query index: zkllm-src/p3_fri.cuh:422-426
 GL_HD uint64_t tr_chal_idx(uint32_t st[8], uint64_t mod) {

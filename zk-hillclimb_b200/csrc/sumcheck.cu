@@ -130,8 +130,9 @@ __device__ __forceinline__ void msg_accum(Acc192 (&acc)[NT], const gl_t (&lo)[Fn
 // mode 0: absorb the message under `tag` and draw the challenge on the device.
 // mode 1: leave this GPU's sums in ctl->local (another step combines the GPUs).
 template <int NT>
-__device__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t* msg_out, gl_t* chal_out,
-                             const ZkhTag& tag, int mode) {
+__device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t* msg_out, gl_t* chal_out,
+                                          const ZkhTag& tag, int mode) {
+    __shared__ uint32_t trbuf[(32 + 4 + ZKH_TR_MAX_LABEL + 8 + 64 + 72) / 4];
     if (mode == 1) {
 #pragma unroll
         for (int t = 0; t < NT; t++) ctl->local[t] = s[t];
@@ -143,7 +144,7 @@ __device__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t* msg_out, gl
     uint32_t st[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
-    tr_absorb(st, tag.s, tag.len, m, NT * 8);
+    tr_absorb_sh(st, tag.s, tag.len, m, NT, trbuf);
     gl_t a = tr_chal_gl(st);
 #pragma unroll
     for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
@@ -395,6 +396,50 @@ static int sc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, cons
             P, (uint32_t)cur_n, 1, ctl, out.chals + (r - 1), out.msgs + (size_t)r * NT, out.chals + r,
             out.finals, (int)logn - r, tag);
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "sumcheck launch");
+}
+
+// One round on explicit buffers (plain column layout).  first: message over `in` (n_in elements
+// per column); otherwise bind `in` with *chal_prev into `out` (n_in/2 elements) and take the
+// message of the bound columns.  n_in >= 2 (first) or >= 4 (fused).
+template <int F, int NT>
+static int sc_round_t(zkh_ctx* ctx, bool first, const gl_t* const* in, gl_t* const* out, size_t n_in,
+                      const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag) {
+    constexpr int NC = Fn<F>::NC;
+    ScPtrs P;
+    memset(&P, 0, sizeof P);
+    for (int k = 0; k < NC; k++) { P.in[k] = in[k]; P.out[k] = out ? out[k] : nullptr; }
+    const size_t items = first ? n_in / 2 : n_in / 4;
+    size_t want = (items + 255) / 256, cap = (size_t)ctx->sm_count * 4;
+    if (cap > ctx->partials_cap / 5) cap = ctx->partials_cap / 5;
+    unsigned grid = (unsigned)(want < cap ? want : cap);
+    if (first)
+        sc_first_kernel<F, NT, LD_PLAIN><<<grid, 256, 0, ctx->stream>>>(P, items, ctx->d_ctl, ctx->d_partials,
+                                                                        msg_out, chal_out, tag, 0);
+    else
+        sc_fused_kernel<F, NT, LD_PLAIN><<<grid, 256, 0, ctx->stream>>>(P, items, ctx->d_ctl, ctx->d_partials,
+                                                                        chal_prev, msg_out, chal_out, tag, 0);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "sumcheck round launch");
+}
+int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* const* in, gl_t* const* out,
+                     size_t n_in, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag) {
+    if (functor == ZKH_F_PROD2 && nt == 3)
+        return sc_round_t<ZKH_F_PROD2, 3>(ctx, first, in, out, n_in, chal_prev, msg_out, chal_out, tag);
+    return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck round: unsupported (functor, nt) combination");
+}
+
+// st = absorb(st, tag, vals[0..n)) on the device transcript (n 64-bit words of raw bytes)
+__global__ void tr_absorb_kernel(ZkhCtl* ctl, ZkhTag tag, const uint64_t* vals, uint32_t n) {
+    __shared__ uint32_t buf[(32 + 4 + ZKH_TR_MAX_LABEL + 8 + ZKH_TR_MAX_DATA + 72) / 4];
+    if (threadIdx.x != 0) return;
+    uint32_t st[8];
+    for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
+    tr_absorb_sh(st, tag.s, tag.len, vals, n, buf);
+    for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+}
+int tr_absorb_enqueue(zkh_ctx* ctx, const char* tag, const uint64_t* vals_dev, uint32_t nwords) {
+    if (nwords * 8 > ZKH_TR_MAX_DATA) return zkh_fail(ctx, ZKH_ERR_LIMIT, "device absorb: more than 320 bytes");
+    tr_absorb_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_ctl, zkh_make_tag(tag), vals_dev, nwords);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "absorb launch");
 }
 
 int sc_enqueue(zkh_ctx* ctx, int functor, int nt, int ld, const gl_t* const* in, uint32_t logn,

@@ -37,4 +37,11 @@ size_t sc_workspace_bytes(int nc, uint32_t logn);
 int sc_enqueue(zkh_ctx* ctx, int functor, int nt, int ld, const gl_t* const* in, uint32_t logn,
                const ZkhTag& tag, void* scratch, const ScOut& out);
 
+
+// One round on explicit plain-layout buffers; see sumcheck.cu.
+int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* const* in, gl_t* const* out,
+                     size_t n_in, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag);
+// Absorb nwords 64-bit words of device data under `tag` into the device transcript.
+int tr_absorb_enqueue(zkh_ctx* ctx, const char* tag, const uint64_t* vals_dev, uint32_t nwords);
+
 }  // namespace zkh

@@ -104,8 +104,13 @@ class Prover:
     """One per GPU: owns a library context (workspace, control block, stream)."""
 
     def __init__(self, device=0, stream=None):
+        """stream: None -> the context creates its own non-blocking stream; an integer
+        cudaStream_t handle -> work is queued there (0, torch's default stream, is passed as
+        cudaStreamLegacy so that it orders with torch's own kernels)."""
         self._L = load_library()
         h = C.c_void_p()
+        if stream is not None and int(stream) == 0:
+            stream = 1  # cudaStreamLegacy
         rc = self._L.zkh_ctx_create(int(device), C.c_void_p(stream or 0), C.byref(h))
         if rc != 0:
             raise ZkhError(rc, "zkh_ctx_create(device=%d) failed" % device)
@@ -128,6 +133,8 @@ class Prover:
             raise ZkhError(rc, (self._L.zkh_last_error(self._h) or b"").decode())
 
     def set_stream(self, stream):
+        if stream is not None and int(stream) == 0:
+            stream = 1  # cudaStreamLegacy
         self._ck(self._L.zkh_ctx_set_stream(self._h, C.c_void_p(stream or 0)))
 
     def sync(self):
@@ -162,6 +169,77 @@ class Prover:
             out = torch.empty(n // 2, dtype=torch.int64, device=in_dev.device)
         self._ck(self._L.zkh_gl_bind(self._h, _ptr(in_dev), _ptr(out), n, a))
         return out
+
+    # ---- Reed-Solomon / Merkle / Basefold ----
+    def ntt(self, in_dev, inverse=False, out=None):
+        """P3Ntt::run (zkllm-src/p3_ntt.cuh:210-230): natural order in and out."""
+        import torch
+        n = in_dev.numel()
+        if out is None:
+            out = torch.empty(n, dtype=torch.int64, device=in_dev.device)
+        self._ck(self._L.zkh_ntt(self._h, _ptr(in_dev), _ptr(out), n.bit_length() - 1, int(inverse)))
+        return out
+
+    def rs_encode_gpu_dev(self, c_dev, R, out=None):
+        """p3bf::rs_encode_gpu_dev (zkllm-src/p3_basefold.cuh:188-197): device codeword of device coefficients."""
+        import torch
+        n = c_dev.numel()
+        if out is None:
+            out = torch.empty(n << R, dtype=torch.int64, device=c_dev.device)
+        self._ck(self._L.zkh_rs_encode(self._h, _ptr(c_dev), n.bit_length() - 1, R, _ptr(out)))
+        return out
+
+    def merkle_build_dev(self, cw_dev, keep_tree=True):
+        """p3fri::DeviceMerkle::build_dev (zkllm-src/p3_fri.cuh:109-139).  Returns (root bytes, tree tensor or None)."""
+        import torch
+        M = cw_dev.numel()
+        tree = None
+        if keep_tree:
+            tree = torch.empty(self._L.zkh_merkle_tree_bytes(M), dtype=torch.uint8, device=cw_dev.device)
+        root = _buf32()
+        self._ck(self._L.zkh_merkle_build(self._h, _ptr(cw_dev), M, _ptr(tree) if keep_tree else 0, root))
+        return bytes(root), tree
+
+    def paths_batch(self, tree_dev, M, idxs):
+        """DeviceMerkle::paths_batch (zkllm-src/p3_fri.cuh:164-178): list of paths, each a list of 32-byte digests."""
+        idx = np.ascontiguousarray(idxs, dtype=np.uint32)
+        logM = int(M).bit_length() - 1
+        out = np.zeros(len(idx) * logM * 32, dtype=np.uint8)
+        self._ck(self._L.zkh_merkle_paths(self._h, _ptr(tree_dev), M, idx.ctypes.data, len(idx), out.ctypes.data))
+        raw = out.tobytes()
+        return [[raw[(i * logM + l) * 32:(i * logM + l + 1) * 32] for l in range(logM)] for i in range(len(idx))]
+
+    def fold_gpu(self, f_dev, beta, out=None):
+        """p3bf_fold_kernel / fold_gpu (zkllm-src/p3_basefold.cuh:239-245, :285-292), MLE form."""
+        import torch
+        M = f_dev.numel()
+        if out is None:
+            out = torch.empty(M // 2, dtype=torch.int64, device=f_dev.device)
+        self._ck(self._L.zkh_gl_fold_codeword(self._h, _ptr(f_dev), _ptr(out), M, beta))
+        return out
+
+    def commit_gpu_rootonly(self, c, R):
+        """p3bf::commit_gpu_rootonly (zkllm-src/p3_basefold.cuh:210-227).  c: host numpy array
+        (uploaded inside, like the reference) or a device tensor."""
+        root = _buf32()
+        if isinstance(c, np.ndarray):
+            c = np.ascontiguousarray(c, dtype=np.uint64)
+            self._ck(self._L.zkh_basefold_commit_host(self._h, c.ctypes.data, len(c).bit_length() - 1, R, root))
+        else:
+            self._ck(self._L.zkh_basefold_commit(self._h, _ptr(c), c.numel().bit_length() - 1, R, 0, root))
+        return bytes(root)
+
+    def prove_eval_dev(self, c_dev, z, y, R, Q, cw0_dev=None, seed="p3-bf"):
+        """p3bf::prove_eval_dev (zkllm-src/p3_basefold.cuh:355-420).  Returns the serialised EvalProof."""
+        z = np.ascontiguousarray(z, dtype=np.uint64)
+        v = len(z)
+        cap = self._L.zkh_basefold_proof_size(v, R, Q)
+        out = np.zeros(cap, dtype=np.uint8)
+        wr = C.c_size_t(0)
+        self._ck(self._L.zkh_basefold_open(self._h, _ptr(c_dev), z.ctypes.data, v, y, R, Q,
+                                           _ptr(cw0_dev) if cw0_dev is not None else 0, seed.encode(),
+                                           out.ctypes.data, cap, C.byref(wr)))
+        return out.tobytes()[:wr.value]
 
     # ---- sumcheck ----
     def sc_prove_gpu(self, tr, tag, dcols, functor, nt, par=(), logn=None):
