@@ -170,6 +170,27 @@ ZKH_API int zkh_basefold_open(zkh_ctx* ctx, const uint64_t* c_dev, const uint64_
                               uint32_t R, uint32_t Q, const uint64_t* cw0_dev, const char* seed, uint8_t* out,
                               size_t cap, size_t* written);
 
+/* ---- logUp ---- */
+/* Multiplicities: cnt_dev[j] = #{i : idx_dev[i] == j}, j < M (zkllm-src/p3_logup.cuh:149-172,
+ * host loop :1412-1475).  An index >= M returns ZKH_ERR_DOMAIN (the reference throws). */
+ZKH_API int zkh_histogram(zkh_ctx* ctx, const uint32_t* idx_dev, uint64_t n, uint32_t M, uint64_t* cnt_dev);
+/* out[i] = 1/(A[i]+beta) by batched inversion (zkllm-src/p3_logup.cuh:636-660 inv_all_add).
+ * A zero denominator returns ZKH_ERR_DOMAIN ("resample beta" in the reference). */
+ZKH_API int zkh_gl_inv_all_add(zkh_ctx* ctx, const uint64_t* A_dev, uint64_t n, uint64_t beta, uint64_t* out_dev);
+/* out[i] = sum_k g^k * cols[k][i] (zkllm-src/p3_logup.cuh:663-672 combine).  Stream-ordered. */
+ZKH_API int zkh_gl_combine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
+                           uint64_t* out_dev);
+/* GKR fractional-sum tree prover (zkllm-src/p3_gkr.cuh:200-364 p3gkr::prove / prove_dev).
+ * p_dev, q_dev: 2^L leaf numerators / denominators (left untouched, unlike prove_dev which
+ * takes ownership).  state: transcript in/out.  rfin: L values (combine_last) or L-1.
+ * cpq: (p~(rfin), q~(rfin)) when combine_last.  Proof serialised as
+ *   P(8) Q(8) | per layer h = L..1: u32 rounds, rounds*32 message bytes, p0 p1 q0 q1 (32)
+ * (p3gkr::Proof / Lay in declaration order).  A zero root denominator returns ZKH_ERR_DOMAIN. */
+ZKH_API size_t zkh_gkr_proof_size(uint32_t L);
+ZKH_API int zkh_gkr_prove(zkh_ctx* ctx, const uint64_t* p_dev, const uint64_t* q_dev, uint32_t L, int combine_last,
+                          const char* tag, uint8_t state[32], uint64_t* rfin, uint64_t cpq[2], uint8_t* out,
+                          size_t cap, size_t* written);
+
 #ifdef __cplusplus
 }
 #endif

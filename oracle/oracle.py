@@ -178,14 +178,14 @@ class _Lib:
     def gkr_proof_size(L):
         return 16 + sum(4 + (L - h) * 32 + 32 for h in range(1, L + 1))
 
-    def gkr_prove(self, st, tag, p, q, combine_last=True):
+    def gkr_prove(self, st, tag, p, q, combine_last=True, gpu=False):
         p, pp = _u64(p); q, qp = _u64(q); L = int(len(p)).bit_length() - 1
         s = _bytes32(st); cap = self.gkr_proof_size(L); out = (C.c_uint8 * cap)()
         rfin = np.zeros(L + 1, dtype=np.uint64); cpq = np.zeros(2, dtype=np.uint64)
         args = [s, tag.encode(), pp, qp, C.c_uint32(L), C.c_int(int(combine_last)),
                 rfin.ctypes.data_as(u64p), cpq.ctypes.data_as(u64p), out, C.c_size_t(cap)]
         if self.prefix == "ref_":
-            args.append(C.c_int(0))
+            args.append(C.c_int(int(gpu)))   # the reference's own CUDA path (GPU machine only)
         n = self._f("gkr_prove")(*args)
         if n == 0:
             raise ValueError("gkr_prove failed (zero denominator?)")

@@ -59,6 +59,11 @@ def load_library():
         "zkh_sumcheck": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_host": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_workspace": (sz, [i, u32]),
+        "zkh_histogram": (i, [vp, vp, u64, u32, vp]),
+        "zkh_gl_inv_all_add": (i, [vp, vp, u64, u64, vp]),
+        "zkh_gl_combine": (i, [vp, vp, i, u64, u64, vp]),
+        "zkh_gkr_proof_size": (sz, [u32]),
+        "zkh_gkr_prove": (i, [vp, vp, vp, u32, i, C.c_char_p, vp, vp, vp, vp, sz, C.POINTER(sz)]),
         "zkh_ntt": (i, [vp, vp, vp, u32, i]),
         "zkh_rs_encode": (i, [vp, vp, u32, u32, vp]),
         "zkh_merkle_tree_bytes": (sz, [u64]),

@@ -84,7 +84,7 @@ static inline size_t zkh_align(size_t x, size_t a = 256) { return (x + a - 1) / 
 namespace zkh {
 // eq(b,z) table for all b < 2^v into out_dev (queued on the context's stream; z is host memory)
 size_t eq_scratch_bytes(uint32_t v);
-int eq_enqueue(zkh_ctx* c, const uint64_t* z, uint32_t v, gl_t* out_dev, void* scratch);
+int eq_enqueue(zkh_ctx* c, const uint64_t* z, uint32_t v, gl_t* out_dev, void* scratch, bool z_on_device = false);
 }  // namespace zkh
 
 #ifdef __CUDACC__

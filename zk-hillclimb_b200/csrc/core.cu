@@ -256,7 +256,8 @@ size_t zkh::eq_scratch_bytes(uint32_t v) {
     if (vl > 14) vl = 14;
     return zkh_align(((size_t)8) << vl) + zkh_align(((size_t)8) << (v - vl)) + zkh_align((size_t)64 * 8);
 }
-static int eq_tables(zkh_ctx* c, const uint64_t* z, uint32_t v, void* scratch, gl_t** lo, gl_t** hi, uint32_t* vl_out) {
+static int eq_tables(zkh_ctx* c, const uint64_t* z, uint32_t v, void* scratch, gl_t** lo, gl_t** hi, uint32_t* vl_out,
+                     bool z_on_device = false) {
     uint32_t vl = v <= 1 ? v : v / 2;
     if (vl > 14) vl = 14;
     uint32_t vh = v - vl;
@@ -267,13 +268,14 @@ static int eq_tables(zkh_ctx* c, const uint64_t* z, uint32_t v, void* scratch, g
     gl_t* dz = (gl_t*)((char*)scratch + tl + th);
     *vl_out = vl;
     // the point is staged in pageable memory by the runtime, so z may be reused by the caller at once
-    ZKH_CUDA(c, cudaMemcpyAsync(dz, z, (size_t)v * 8, cudaMemcpyHostToDevice, c->stream));
+    if (z_on_device) dz = (gl_t*)z;
+    else ZKH_CUDA(c, cudaMemcpyAsync(dz, z, (size_t)v * 8, cudaMemcpyHostToDevice, c->stream));
     eq_small_kernel<<<((1u << vl) + 255) / 256, 256, 0, c->stream>>>(dz, 0, vl, *lo);
     eq_small_kernel<<<((1u << vh) + 255) / 256, 256, 0, c->stream>>>(dz, vl, vh, *hi);
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }
-int zkh::eq_enqueue(zkh_ctx* c, const uint64_t* z, uint32_t v, gl_t* out_dev, void* scratch) {
+int zkh::eq_enqueue(zkh_ctx* c, const uint64_t* z, uint32_t v, gl_t* out_dev, void* scratch, bool z_on_device) {
     if (v == 0) {
         static const uint64_t one = 1;
         ZKH_CUDA(c, cudaMemcpyAsync(out_dev, &one, 8, cudaMemcpyHostToDevice, c->stream));
@@ -281,7 +283,7 @@ int zkh::eq_enqueue(zkh_ctx* c, const uint64_t* z, uint32_t v, gl_t* out_dev, vo
     }
     gl_t *lo, *hi;
     uint32_t vl;
-    ZKH_TRY(eq_tables(c, z, v, scratch, &lo, &hi, &vl));
+    ZKH_TRY(eq_tables(c, z, v, scratch, &lo, &hi, &vl, z_on_device));
     size_t n = (size_t)1 << v;
     size_t blocks = (n / 2 + 255) / 256, cap = (size_t)c->sm_count * 8;
     eq_expand_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(lo, hi, vl, out_dev, n);

@@ -1,0 +1,144 @@
+// logUp primitives over Goldilocks for sm_100a: multiplicity histogram, batched inversion,
+// gamma-combination of columns, and the fraction-tree level combine.
+//   histogram    zkllm-src/p3_logup.cuh:149-172 (p3lu_cntg/cnts_kernel), host loop :1412-1475
+//   inversion    zkllm-src/p3_logup.cuh:636-660 (inv_all_add, host OpenMP Montgomery trick)
+//   combine      zkllm-src/p3_logup.cuh:663-672 (combine), :93-107 (device Am build)
+#include "common.cuh"
+
+namespace zkh {
+
+// Counting is order-free integer accumulation, so the bins equal the host loop's exactly.
+// Tables of up to 2^15 rows are counted in shared memory (32-bit sub-histograms flushed with
+// 64-bit atomics); larger tables go straight to 64-bit global atomics in L2.
+__global__ void __launch_bounds__(512)
+hist_shared_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsigned long long* bins,
+                   unsigned int* oob) {
+    extern __shared__ uint32_t shc[];
+    for (uint32_t t = threadIdx.x; t < M; t += blockDim.x) shc[t] = 0;
+    __syncthreads();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        uint32_t r = idx[i];
+        if (r >= M) atomicAdd(oob, 1u);
+        else atomicAdd(&shc[r], 1u);
+    }
+    __syncthreads();
+    for (uint32_t t = threadIdx.x; t < M; t += blockDim.x)
+        if (shc[t]) atomicAdd(&bins[t], (unsigned long long)shc[t]);
+}
+__global__ void __launch_bounds__(256)
+hist_global_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsigned long long* bins,
+                   unsigned int* oob) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        uint32_t r = idx[i];
+        if (r >= M) atomicAdd(oob, 1u);
+        else atomicAdd(&bins[r], 1ULL);
+    }
+}
+
+// out[i] = 1/(A[i]+beta).  Each thread inverts INV_K strided elements with one Fermat
+// inversion: prefix products, invert the total, peel off backwards (3 multiplies per element).
+#define INV_K 16
+__global__ void __launch_bounds__(256)
+inv_add_kernel(const gl_t* __restrict__ A, gl_t* __restrict__ out, size_t n, gl_t beta, unsigned int* zero) {
+    const size_t nthreads = (size_t)gridDim.x * blockDim.x, t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    gl_t d[INV_K], pre[INV_K];
+    gl_t acc = 1;
+#pragma unroll
+    for (int k = 0; k < INV_K; k++) {
+        size_t i = t + (size_t)k * nthreads;
+        gl_t v = 1;
+        if (i < n) {
+            v = gl_add(A[i], beta);
+            if (v == 0) { atomicAdd(zero, 1u); v = 1; }
+        }
+        d[k] = v;
+        pre[k] = acc;
+        acc = gl_mul(acc, v);
+    }
+    gl_t inv = gl_inv(acc);
+#pragma unroll
+    for (int k = INV_K - 1; k >= 0; k--) {
+        size_t i = t + (size_t)k * nthreads;
+        if (i < n) out[i] = gl_mul(pre[k], inv);
+        inv = gl_mul(inv, d[k]);
+    }
+}
+
+struct CombCols { const gl_t* col[8]; gl_t gk[8]; int c; };
+__global__ void __launch_bounds__(256) combine_kernel(CombCols cc, gl_t* __restrict__ out, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        Acc192 acc;
+        acc.clear();
+        for (int k = 0; k < cc.c; k++) acc.add_prod(cc.gk[k], cc.col[k][i]);
+        out[i] = acc.reduce();
+    }
+}
+
+}  // namespace zkh
+
+using namespace zkh;
+
+extern "C" int zkh_histogram(zkh_ctx* c, const uint32_t* idx_dev, uint64_t n, uint32_t M, uint64_t* cnt_dev) {
+    if (!c || !idx_dev || !cnt_dev) return zkh_fail(c, ZKH_ERR_ARG, "histogram: null pointer");
+    if (M == 0) return zkh_fail(c, ZKH_ERR_ARG, "histogram: empty table");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    unsigned int* oob = (unsigned int*)&c->d_ctl->err;
+    ZKH_CUDA(c, cudaMemsetAsync(cnt_dev, 0, (size_t)M * 8, c->stream));
+    ZKH_CUDA(c, cudaMemsetAsync(oob, 0, 4, c->stream));
+    if (n) {
+        if (M <= (1u << 15)) {
+            static bool attr = false;
+            if (!attr) { cudaFuncSetAttribute(hist_shared_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024); attr = true; }
+            size_t blocks = (n + 512 * 64 - 1) / (512 * 64), cap = (size_t)c->sm_count;
+            if (blocks < 1) blocks = 1;
+            hist_shared_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 512, (size_t)M * 4, c->stream>>>(
+                idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
+        } else {
+            size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 8;
+            hist_global_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(
+                idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
+        }
+        ZKH_CUDA(c, cudaGetLastError());
+    }
+    ZKH_CUDA(c, cudaMemcpyAsync(&c->h_ctl->err, oob, 4, cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (c->h_ctl->err) return zkh_fail(c, ZKH_ERR_DOMAIN, "histogram: lookup index outside the table");
+    return ZKH_OK;
+}
+
+extern "C" int zkh_gl_inv_all_add(zkh_ctx* c, const uint64_t* A_dev, uint64_t n, uint64_t beta, uint64_t* out_dev) {
+    if (!c || (n && (!A_dev || !out_dev))) return zkh_fail(c, ZKH_ERR_ARG, "inv_all_add: null pointer");
+    if (beta >= GL_P) return zkh_fail(c, ZKH_ERR_ARG, "inv_all_add: beta not canonical");
+    if (!n) return ZKH_OK;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    unsigned int* zero = (unsigned int*)&c->d_ctl->err;
+    ZKH_CUDA(c, cudaMemsetAsync(zero, 0, 4, c->stream));
+    size_t threads = (n + INV_K - 1) / INV_K, blocks = (threads + 255) / 256;
+    inv_add_kernel<<<(unsigned)blocks, 256, 0, c->stream>>>(A_dev, out_dev, (size_t)n, beta, zero);
+    ZKH_CUDA(c, cudaGetLastError());
+    ZKH_CUDA(c, cudaMemcpyAsync(&c->h_ctl->err, zero, 4, cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (c->h_ctl->err) return zkh_fail(c, ZKH_ERR_DOMAIN, "inv_all_add: zero denominator (resample beta)");
+    return ZKH_OK;
+}
+
+extern "C" int zkh_gl_combine(zkh_ctx* c, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
+                              uint64_t* out_dev) {
+    if (!c || !cols_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "combine: null pointer");
+    if (ncols < 1 || ncols > 8) return zkh_fail(c, ZKH_ERR_LIMIT, "combine: 1..8 columns");
+    if (g >= GL_P) return zkh_fail(c, ZKH_ERR_ARG, "combine: gamma not canonical");
+    if (!n) return ZKH_OK;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    CombCols cc;
+    memset(&cc, 0, sizeof cc);
+    cc.c = ncols;
+    gl_t gk = 1;
+    for (int k = 0; k < ncols; k++) { cc.col[k] = cols_dev[k]; cc.gk[k] = gk; gk = gl_mul(gk, g); }
+    size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 8;
+    combine_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(cc, out_dev, (size_t)n);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}

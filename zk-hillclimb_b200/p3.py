@@ -241,6 +241,47 @@ class Prover:
                                            out.ctypes.data, cap, C.byref(wr)))
         return out.tobytes()[:wr.value]
 
+    # ---- logUp / GKR ----
+    def histogram(self, idx_dev, M):
+        """p3lu_cnts/cntg_kernel (zkllm-src/p3_logup.cuh:149-172): 64-bit multiplicities of uint32 indices
+        (idx_dev: torch int32 tensor holding the uint32 bit patterns)."""
+        import torch
+        cnt = torch.empty(M, dtype=torch.int64, device=idx_dev.device)
+        self._ck(self._L.zkh_histogram(self._h, _ptr(idx_dev), idx_dev.numel(), M, _ptr(cnt)))
+        return cnt
+
+    def inv_all_add(self, A_dev, beta):
+        """p3lu::inv_all_add (zkllm-src/p3_logup.cuh:636-660)."""
+        import torch
+        out = torch.empty_like(A_dev)
+        self._ck(self._L.zkh_gl_inv_all_add(self._h, _ptr(A_dev), A_dev.numel(), beta, _ptr(out)))
+        return out
+
+    def combine(self, cols_dev, g):
+        """p3lu::combine (zkllm-src/p3_logup.cuh:663-672)."""
+        import torch
+        nc = len(cols_dev)
+        ptrs = (C.c_uint64 * nc)(*[_ptr(t) for t in cols_dev])
+        out = torch.empty_like(cols_dev[0])
+        self._ck(self._L.zkh_gl_combine(self._h, ptrs, nc, cols_dev[0].numel(), g, _ptr(out)))
+        return out
+
+    def gkr_prove(self, tr, tag, p_dev, q_dev, combine_last=True):
+        """p3gkr::prove_dev (zkllm-src/p3_gkr.cuh:423-429).  Returns (proof bytes, rfin, (cp, cq));
+        ``tr`` advances exactly as the reference's transcript."""
+        L = p_dev.numel().bit_length() - 1
+        cap = self._L.zkh_gkr_proof_size(L)
+        out = np.zeros(cap, dtype=np.uint8)
+        rfin = np.zeros(L + 1, dtype=np.uint64)
+        cpq = np.zeros(2, dtype=np.uint64)
+        wr = C.c_size_t(0)
+        st = _buf32(tr.state)
+        self._ck(self._L.zkh_gkr_prove(self._h, _ptr(p_dev), _ptr(q_dev), L, int(combine_last), tag.encode(), st,
+                                       rfin.ctypes.data, cpq.ctypes.data, out.ctypes.data, cap, C.byref(wr)))
+        tr.state = bytes(st)
+        nr = L if combine_last else L - 1
+        return out.tobytes()[:wr.value], rfin[:nr].copy(), (int(cpq[0]), int(cpq[1]))
+
     # ---- sumcheck ----
     def sc_prove_gpu(self, tr, tag, dcols, functor, nt, par=(), logn=None):
         """p3sg::sc_prove_gpu: appends nothing to the caller's lists; returns
