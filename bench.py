@@ -275,7 +275,8 @@ def main():
             "roofline": {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": UNIT,
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                          "launch_ms": k_ms, "alg_bytes_per_launch": k_bytes},
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(args.steps * (1 + (logn - 12) + 1)),
+            "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": int(args.steps * ((1 + (logn - 12) + 1) if world == 1 else (2 * logn + 3))),
             "clocks": clocks,
         }
         print(json.dumps(out))

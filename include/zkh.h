@@ -127,6 +127,29 @@ ZKH_API int zkh_sumcheck_host(zkh_ctx* ctx, int functor, int nt, const uint64_t*
 /* Bytes of workspace zkh_sumcheck needs for (nc, logn). */
 ZKH_API size_t zkh_sumcheck_workspace(int nc, uint32_t logn);
 
+/* ---- sumcheck sharded over several GPUs of one node ----
+ * The reference has no multi-GPU code; this is the sharded form of p3sg::sc_prove_gpu
+ * (zkllm-src/p3_scgpu.cuh:91-160) with an identical transcript.  The hypercube is split on
+ * its top log2(G) variables: GPU g (one context, one process) holds elements
+ * [g*2^logn_local, (g+1)*2^logn_local) of every column.  Per local round r = 0..logn_local-1:
+ *   zkh_shard_round_local(r, sums_dev)     this GPU's nt round sums -> sums_dev (device)
+ *   <caller all-gathers the G*nt values, rank-major, into gathered_dev on every GPU>
+ *   zkh_shard_round_combine(r, gathered_dev, G)   mod-p sum, absorb, challenge (same on every GPU)
+ * then zkh_shard_finals(finals_dev) gives this GPU's nc bound values; the caller all-gathers
+ * them (rank-major [G][nc]) and zkh_shard_residual runs the last log2(G) rounds on every GPU.
+ * zkh_shard_end returns the transcript state, (logn_local+log2 G)*nt message values, the
+ * challenges and the nc final values -- the same on every GPU and equal to an unsharded proof.
+ * Everything between begin and end is stream-ordered; nothing waits on another GPU inside a
+ * kernel. */
+ZKH_API int zkh_shard_begin(zkh_ctx* ctx, int functor, int nt, const uint64_t* const* cols_dev, int nc,
+                            uint32_t logn_local, const uint64_t* par, int npar, const char* tag,
+                            const uint8_t state[32]);
+ZKH_API int zkh_shard_round_local(zkh_ctx* ctx, uint32_t r, uint64_t* sums_dev);
+ZKH_API int zkh_shard_round_combine(zkh_ctx* ctx, uint32_t r, const uint64_t* gathered_dev, uint32_t G);
+ZKH_API int zkh_shard_finals(zkh_ctx* ctx, uint64_t* finals_dev);
+ZKH_API int zkh_shard_residual(zkh_ctx* ctx, const uint64_t* gathered_finals_dev, uint32_t G);
+ZKH_API int zkh_shard_end(zkh_ctx* ctx, uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals);
+
 /* ---- Reed-Solomon encode / NTT (zkllm-src/p3_ntt.cuh:170-230 P3Ntt::run,
  *      p3_basefold.cuh:188-197 rs_encode_gpu_dev) ----
  * out[k] = sum_j in[j]*w^(jk) over the 2^logn subgroup, natural order in and out; inverse

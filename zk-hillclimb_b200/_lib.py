@@ -59,6 +59,12 @@ def load_library():
         "zkh_sumcheck": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_host": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_workspace": (sz, [i, u32]),
+        "zkh_shard_begin": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp]),
+        "zkh_shard_round_local": (i, [vp, u32, vp]),
+        "zkh_shard_round_combine": (i, [vp, u32, vp, u32]),
+        "zkh_shard_finals": (i, [vp, vp]),
+        "zkh_shard_residual": (i, [vp, vp, u32]),
+        "zkh_shard_end": (i, [vp, vp, vp, vp, vp]),
         "zkh_histogram": (i, [vp, vp, u64, u32, vp]),
         "zkh_gl_inv_all_add": (i, [vp, vp, u64, u64, vp]),
         "zkh_gl_combine": (i, [vp, vp, i, u64, u64, vp]),

@@ -49,6 +49,18 @@ struct zkh_ctx {
     bool prof_valid = false;
     uint64_t prof_bytes = 0;     // algorithmic bytes of that launch
     const char* prof_kernel = "";
+    // running sharded sumcheck (zkh_shard_*)
+    struct Shard {
+        bool active = false;
+        int functor = 0, nt = 0, nc = 0;
+        uint32_t logn = 0, next_round = 0;
+        ZkhTag tag;
+        const gl_t* cur_in[8];
+        gl_t* bufA = nullptr;
+        gl_t* bufB = nullptr;
+        gl_t* dst = nullptr;
+        gl_t* res = nullptr;  // transposed residual columns
+    } shard;
     std::string err;
 };
 

@@ -128,14 +128,14 @@ __device__ __forceinline__ void msg_accum(Acc192 (&acc)[NT], const gl_t (&lo)[Fn
 
 // ------------------------------------------------------------------ round end
 // mode 0: absorb the message under `tag` and draw the challenge on the device.
-// mode 1: leave this GPU's sums in ctl->local (another step combines the GPUs).
+// mode 1: write this GPU's sums to msg_out and stop (another step combines the GPUs).
 template <int NT>
 __device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t* msg_out, gl_t* chal_out,
                                           const ZkhTag& tag, int mode) {
     __shared__ uint32_t trbuf[(32 + 4 + ZKH_TR_MAX_LABEL + 8 + 64 + 72) / 4];
     if (mode == 1) {
 #pragma unroll
-        for (int t = 0; t < NT; t++) ctl->local[t] = s[t];
+        for (int t = 0; t < NT; t++) msg_out[t] = s[t];
         return;
     }
     gl_t m[NT];
@@ -403,7 +403,7 @@ static int sc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, cons
 // message of the bound columns.  n_in >= 2 (first) or >= 4 (fused).
 template <int F, int NT>
 static int sc_round_t(zkh_ctx* ctx, bool first, const gl_t* const* in, gl_t* const* out, size_t n_in,
-                      const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag) {
+                      const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag, int mode) {
     constexpr int NC = Fn<F>::NC;
     ScPtrs P;
     memset(&P, 0, sizeof P);
@@ -414,17 +414,82 @@ static int sc_round_t(zkh_ctx* ctx, bool first, const gl_t* const* in, gl_t* con
     unsigned grid = (unsigned)(want < cap ? want : cap);
     if (first)
         sc_first_kernel<F, NT, LD_PLAIN><<<grid, 256, 0, ctx->stream>>>(P, items, ctx->d_ctl, ctx->d_partials,
-                                                                        msg_out, chal_out, tag, 0);
+                                                                        msg_out, chal_out, tag, mode);
     else
         sc_fused_kernel<F, NT, LD_PLAIN><<<grid, 256, 0, ctx->stream>>>(P, items, ctx->d_ctl, ctx->d_partials,
-                                                                        chal_prev, msg_out, chal_out, tag, 0);
+                                                                        chal_prev, msg_out, chal_out, tag, mode);
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "sumcheck round launch");
 }
 int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* const* in, gl_t* const* out,
-                     size_t n_in, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag) {
-    if (functor == ZKH_F_PROD2 && nt == 3)
-        return sc_round_t<ZKH_F_PROD2, 3>(ctx, first, in, out, n_in, chal_prev, msg_out, chal_out, tag);
+                     size_t n_in, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag, int mode) {
+#define CASE(F, NT) \
+    if (functor == F && nt == NT) return sc_round_t<F, NT>(ctx, first, in, out, n_in, chal_prev, msg_out, chal_out, tag, mode);
+    CASE(ZKH_F_PROD2, 3)
+    CASE(ZKH_F_PROD2, 5)
+    CASE(ZKH_F_PROD3, 4)
+    CASE(ZKH_F_PROD3, 5)
+    CASE(ZKH_F_GKR, 4)
+    CASE(ZKH_F_LOGUP, 4)
+#undef CASE
     return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck round: unsupported (functor, nt) combination");
+}
+
+// tail on explicit plain columns of length n (<= 2^11): nrounds rounds, no pending bind
+template <int F, int NT>
+static int sc_tail_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out, gl_t* chal_out,
+                     gl_t* finals_out, const ZkhTag& tag) {
+    constexpr int NC = Fn<F>::NC;
+    ScPtrs P;
+    memset(&P, 0, sizeof P);
+    for (int k = 0; k < NC; k++) P.in[k] = in[k];
+    cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         NC * (1 << SC_TAIL_LOG) * 8);
+    sc_tail_kernel<F, NT, LD_PLAIN><<<1, 1024, (size_t)NC * n * 8, ctx->stream>>>(P, n, 0, ctx->d_ctl, nullptr, msg_out,
+                                                                             chal_out, finals_out, nrounds, tag);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "sumcheck tail launch");
+}
+int sc_enqueue_tail(zkh_ctx* ctx, int functor, int nt, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out,
+                    gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag) {
+#define CASE(F, NT) \
+    if (functor == F && nt == NT) return sc_tail_t<F, NT>(ctx, in, n, nrounds, msg_out, chal_out, finals_out, tag);
+    CASE(ZKH_F_PROD2, 3)
+    CASE(ZKH_F_PROD2, 5)
+    CASE(ZKH_F_PROD3, 4)
+    CASE(ZKH_F_PROD3, 5)
+    CASE(ZKH_F_GKR, 4)
+    CASE(ZKH_F_LOGUP, 4)
+#undef CASE
+    return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck tail: unsupported (functor, nt) combination");
+}
+
+// sum the G ranks' round sums (rank-major [G][nt]), absorb, draw the challenge: the step every
+// rank of a sharded sumcheck runs identically after the all-gather
+__global__ void sc_combine_kernel(ZkhCtl* ctl, const gl_t* gathered, uint32_t G, int nt, ZkhTag tag, gl_t* msg_out,
+                                  gl_t* chal_out) {
+    __shared__ uint32_t buf[(32 + 4 + ZKH_TR_MAX_LABEL + 8 + 64 + 72) / 4];
+    if (threadIdx.x != 0) return;
+    gl_t m[5];
+    for (int t = 0; t < nt; t++) {
+        gl_t a = 0;
+        for (uint32_t g = 0; g < G; g++) a = gl_add(a, gathered[(size_t)g * nt + t]);
+        m[t] = a;
+        msg_out[t] = a;
+    }
+    uint32_t st[8];
+    for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
+    tr_absorb_sh(st, tag.s, tag.len, m, nt, buf);
+    *chal_out = tr_chal_gl(st);
+    for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+}
+// out[k] = in[k][0] + a*(in[k][1]-in[k][0]): the last local bind of a sharded sumcheck
+__global__ void sc_finals_kernel(ScPtrs P, int nc, const gl_t* chal, gl_t* out) {
+    int k = threadIdx.x;
+    if (k < nc) out[k] = gl_lerp(P.in[k][0], P.in[k][1], *chal);
+}
+// rank-major [G][nc] -> column-major [nc][G]
+__global__ void sc_transpose_kernel(const gl_t* in, gl_t* out, uint32_t G, int nc) {
+    uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < G * nc) { uint32_t g = t / nc, k = t % nc; out[(size_t)k * G + g] = in[t]; }
 }
 
 // st = absorb(st, tag, vals[0..n)) on the device transcript (n 64-bit words of raw bytes)
@@ -527,4 +592,120 @@ extern "C" int zkh_sumcheck_host(zkh_ctx* ctx, int functor, int nt, const uint64
     }
     return sumcheck_common(ctx, functor, nt, d, nc, logn, par, npar, tag, state, msgs, chals, finals,
                            (char*)ctx->ws + (size_t)nc * colb);
+}
+
+// ------------------------------------------------------------------ sharded sumcheck (multi-GPU)
+// The hypercube is split on its top log2(G) variables: GPU g holds the slice [g*n, (g+1)*n) of
+// every column.  LSB-first pairs never cross a slice, so rounds 0..log2(n)-1 are local apart from
+// summing the nt round values of all GPUs (the caller all-gathers them between
+// zkh_shard_round_local and zkh_shard_round_combine; every GPU runs the same transcript).
+// After log2(n) rounds each GPU holds one value per column; the caller all-gathers those and
+// every GPU finishes the last log2(G) rounds on the G-element residual.
+extern "C" int zkh_shard_begin(zkh_ctx* c, int functor, int nt, const uint64_t* const* cols_dev, int nc,
+                               uint32_t logn_local, const uint64_t* par, int npar, const char* tag,
+                               const uint8_t state[32]) {
+    static const uint64_t dummy = 0;
+    ZKH_TRY(sumcheck_check(c, functor, nt, cols_dev, nc, logn_local, par, npar, tag, state, &dummy, &dummy));
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    const size_t n = (size_t)1 << logn_local;
+    const size_t a = zkh_align((size_t)nc * (n / 2 + 1) * 8), b = zkh_align((size_t)nc * (n / 4 + 1) * 8);
+    ZKH_TRY(zkh_ws_reserve(c, a + b + zkh_align((size_t)nc * 2048 * 8)));
+    zkh_ctx::Shard& sh = c->shard;
+    sh.active = true;
+    sh.functor = functor; sh.nt = nt; sh.nc = nc; sh.logn = logn_local; sh.next_round = 0;
+    sh.tag = zkh_make_tag(tag);
+    for (int k = 0; k < nc; k++) sh.cur_in[k] = cols_dev[k];
+    sh.bufA = (gl_t*)c->ws;
+    sh.bufB = (gl_t*)((char*)c->ws + a);
+    sh.res = (gl_t*)((char*)c->ws + a + b);
+    sh.dst = sh.bufA;
+    ZkhCtl* h = c->h_ctl;
+    digest_from_bytes(state, h->st);
+    h->counter = 0;
+    h->err = 0;
+    for (int i = 0; i < 8; i++) h->par[i] = i < npar ? par[i] : 0;
+    ZKH_CUDA(c, cudaMemcpyAsync(c->d_ctl, h, offsetof(ZkhCtl, local), cudaMemcpyHostToDevice, c->stream));
+    return ZKH_OK;
+}
+extern "C" int zkh_shard_round_local(zkh_ctx* c, uint32_t r, uint64_t* sums_dev) {
+    if (!c || !sums_dev) return zkh_fail(c, ZKH_ERR_ARG, "shard_round_local: null pointer");
+    zkh_ctx::Shard& sh = c->shard;
+    if (!sh.active || r != sh.next_round || r >= sh.logn)
+        return zkh_fail(c, ZKH_ERR_ARG, "shard_round_local: rounds must run in order 0..logn_local-1");
+    if (r == 0)
+        return sc_enqueue_round(c, sh.functor, sh.nt, true, sh.cur_in, nullptr, (size_t)1 << sh.logn, nullptr,
+                                sums_dev, nullptr, sh.tag, 1);
+    const size_t n_in = (size_t)1 << (sh.logn - r + 1), n_out = n_in / 2;
+    gl_t* outp[8];
+    for (int k = 0; k < sh.nc; k++) outp[k] = sh.dst + (size_t)k * n_out;
+    const bool prof = (r == 1) && c->prof_ev[0];
+    if (prof) cudaEventRecord(c->prof_ev[0], c->stream);
+    ZKH_TRY(sc_enqueue_round(c, sh.functor, sh.nt, false, sh.cur_in, outp, n_in, c->d_ctl->chals + (r - 1), sums_dev,
+                             nullptr, sh.tag, 1));
+    if (prof) {
+        cudaEventRecord(c->prof_ev[1], c->stream);
+        c->prof_valid = true;
+        c->prof_bytes = (uint64_t)12 * sh.nc * n_in;
+        c->prof_kernel = "sc_fused_kernel";
+    }
+    for (int k = 0; k < sh.nc; k++) sh.cur_in[k] = outp[k];
+    sh.dst = (sh.dst == sh.bufA) ? sh.bufB : sh.bufA;
+    return ZKH_OK;
+}
+extern "C" int zkh_shard_round_combine(zkh_ctx* c, uint32_t r, const uint64_t* gathered_dev, uint32_t G) {
+    if (!c || !gathered_dev) return zkh_fail(c, ZKH_ERR_ARG, "shard_round_combine: null pointer");
+    zkh_ctx::Shard& sh = c->shard;
+    if (!sh.active || r != sh.next_round || G < 1 || G > 1024)
+        return zkh_fail(c, ZKH_ERR_ARG, "shard_round_combine: out of order, or G outside 1..1024");
+    sc_combine_kernel<<<1, 32, 0, c->stream>>>(c->d_ctl, gathered_dev, G, sh.nt, sh.tag,
+                                              c->d_ctl->msgs + (size_t)r * sh.nt, c->d_ctl->chals + r);
+    ZKH_CUDA(c, cudaGetLastError());
+    sh.next_round = r + 1;
+    return ZKH_OK;
+}
+extern "C" int zkh_shard_finals(zkh_ctx* c, uint64_t* finals_dev) {
+    if (!c || !finals_dev) return zkh_fail(c, ZKH_ERR_ARG, "shard_finals: null pointer");
+    zkh_ctx::Shard& sh = c->shard;
+    if (!sh.active || sh.next_round != sh.logn) return zkh_fail(c, ZKH_ERR_ARG, "shard_finals: local rounds not finished");
+    ScPtrs P;
+    memset(&P, 0, sizeof P);
+    for (int k = 0; k < sh.nc; k++) P.in[k] = sh.cur_in[k];
+    sc_finals_kernel<<<1, 32, 0, c->stream>>>(P, sh.nc, c->d_ctl->chals + (sh.logn - 1), finals_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+extern "C" int zkh_shard_residual(zkh_ctx* c, const uint64_t* gathered_finals_dev, uint32_t G) {
+    if (!c || !gathered_finals_dev) return zkh_fail(c, ZKH_ERR_ARG, "shard_residual: null pointer");
+    zkh_ctx::Shard& sh = c->shard;
+    if (!sh.active || sh.next_round != sh.logn) return zkh_fail(c, ZKH_ERR_ARG, "shard_residual: local rounds not finished");
+    if (G < 1 || G > 2048 || (G & (G - 1))) return zkh_fail(c, ZKH_ERR_ARG, "shard_residual: G must be a power of two <= 2048");
+    uint32_t k2 = 0;
+    while ((1u << k2) < G) k2++;
+    if (G == 1) {
+        ZKH_CUDA(c, cudaMemcpyAsync(c->d_ctl->finals, gathered_finals_dev, (size_t)sh.nc * 8, cudaMemcpyDeviceToDevice,
+                                    c->stream));
+    } else {
+        sc_transpose_kernel<<<(G * sh.nc + 255) / 256, 256, 0, c->stream>>>(gathered_finals_dev, sh.res, G, sh.nc);
+        const gl_t* in[8];
+        for (int k = 0; k < sh.nc; k++) in[k] = sh.res + (size_t)k * G;
+        ZKH_TRY(sc_enqueue_tail(c, sh.functor, sh.nt, in, G, (int)k2, c->d_ctl->msgs + (size_t)sh.logn * sh.nt,
+                                c->d_ctl->chals + sh.logn, c->d_ctl->finals, sh.tag));
+    }
+    sh.next_round = sh.logn + k2;
+    return ZKH_OK;
+}
+extern "C" int zkh_shard_end(zkh_ctx* c, uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals) {
+    if (!c || !state || !msgs || !chals) return zkh_fail(c, ZKH_ERR_ARG, "shard_end: null pointer");
+    zkh_ctx::Shard& sh = c->shard;
+    if (!sh.active) return zkh_fail(c, ZKH_ERR_ARG, "shard_end: no sharded sumcheck is running");
+    ZkhCtl* h = c->h_ctl;
+    ZKH_CUDA(c, cudaMemcpyAsync(h, c->d_ctl, sizeof(ZkhCtl), cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    sh.active = false;
+    if (h->err) return zkh_fail(c, ZKH_ERR_DEVICE, "shard_end: device error flag set");
+    memcpy(msgs, h->msgs, (size_t)sh.next_round * sh.nt * 8);
+    memcpy(chals, h->chals, (size_t)sh.next_round * 8);
+    if (finals) memcpy(finals, h->finals, (size_t)sh.nc * 8);
+    digest_to_bytes(h->st, state);
+    return ZKH_OK;
 }

@@ -40,7 +40,10 @@ int sc_enqueue(zkh_ctx* ctx, int functor, int nt, int ld, const gl_t* const* in,
 
 // One round on explicit plain-layout buffers; see sumcheck.cu.
 int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* const* in, gl_t* const* out,
-                     size_t n_in, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag);
+                     size_t n_in, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag,
+                     int mode = 0);
+int sc_enqueue_tail(zkh_ctx* ctx, int functor, int nt, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out,
+                    gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag);
 // Absorb nwords 64-bit words of device data under `tag` into the device transcript.
 int tr_absorb_enqueue(zkh_ctx* ctx, const char* tag, const uint64_t* vals_dev, uint32_t nwords);
 

@@ -282,6 +282,40 @@ class Prover:
         nr = L if combine_last else L - 1
         return out.tobytes()[:wr.value], rfin[:nr].copy(), (int(cpq[0]), int(cpq[1]))
 
+    # ---- sharded sumcheck: the per-GPU engine interface used by sc_prove_sharded ----
+    def new_buffer(self, n):
+        import torch
+        return torch.zeros(n, dtype=torch.int64, device="cuda:%d" % self.device)
+
+    def shard_begin(self, functor, nt, dcols, logn, par, tag, state):
+        nc = len(dcols)
+        ptrs = (C.c_uint64 * nc)(*[_ptr(t) for t in dcols])
+        par_a = np.ascontiguousarray(list(par) if len(par) else [0], dtype=np.uint64)
+        self._shard_shape = (nt, nc)
+        self._ck(self._L.zkh_shard_begin(self._h, functor, nt, ptrs, nc, logn, par_a.ctypes.data, len(par),
+                                         tag.encode(), _buf32(state)))
+
+    def shard_round_local(self, r, sums):
+        self._ck(self._L.zkh_shard_round_local(self._h, r, _ptr(sums)))
+
+    def shard_round_combine(self, r, gathered, G):
+        self._ck(self._L.zkh_shard_round_combine(self._h, r, _ptr(gathered), G))
+
+    def shard_finals(self, fin):
+        self._ck(self._L.zkh_shard_finals(self._h, _ptr(fin)))
+
+    def shard_residual(self, gathered_fin, G):
+        self._ck(self._L.zkh_shard_residual(self._h, _ptr(gathered_fin), G))
+
+    def shard_end(self, rounds):
+        nt, nc = self._shard_shape
+        msgs = np.zeros((rounds, nt), dtype=np.uint64)
+        chals = np.zeros(rounds, dtype=np.uint64)
+        fin = np.zeros(nc, dtype=np.uint64)
+        st = _buf32()
+        self._ck(self._L.zkh_shard_end(self._h, st, msgs.ctypes.data, chals.ctypes.data, fin.ctypes.data))
+        return bytes(st), msgs, chals, fin
+
     # ---- sumcheck ----
     def sc_prove_gpu(self, tr, tag, dcols, functor, nt, par=(), logn=None):
         """p3sg::sc_prove_gpu: appends nothing to the caller's lists; returns
@@ -319,3 +353,44 @@ class Prover:
                                            chals.ctypes.data, fin.ctypes.data))
         tr.state = bytes(st)
         return chals, msgs, fin
+
+
+def sc_prove_sharded(engine, tr, tag, dcols, functor, nt, dist=None, par=(), group=None):
+    """p3sg::sc_prove_gpu over several GPUs of one node: the hypercube is split on its top
+    log2(G) variables, rank g holding slice g of every column (``dcols``: this rank's slices).
+    Per round the ranks all-gather their nt partial sums (nt*8 bytes each); every rank adds
+    them mod p, runs the same transcript step and binds its own slice.  After the local
+    rounds the G per-rank values of each column are all-gathered and every rank finishes the
+    last log2(G) rounds.  Returns (r, msgs, finals) exactly as sc_prove_gpu would on the
+    concatenated columns; ``tr`` advances identically on every rank.
+
+    ``engine``: a Prover (CUDA) -- or, in the CPU tests of this host logic, an object with the
+    same shard_* methods.  ``dist``: torch.distributed (initialised) or None for one rank."""
+    G = dist.get_world_size(group) if (dist is not None and dist.is_initialized()) else 1
+    if G & (G - 1):
+        raise ValueError("the number of ranks must be a power of two")
+    nc = len(dcols)
+    logn = int(dcols[0].numel()).bit_length() - 1
+    if logn < 1:
+        raise ValueError("each rank needs at least two elements per column")
+    k = G.bit_length() - 1
+
+    def all_gather(out, inp):
+        if G == 1:
+            out.copy_(inp)
+        else:
+            dist.all_gather_into_tensor(out, inp, group=group)
+
+    engine.shard_begin(functor, nt, dcols, logn, par, tag, tr.state)
+    sums, gathered = engine.new_buffer(nt), engine.new_buffer(G * nt)
+    for r in range(logn):
+        engine.shard_round_local(r, sums)
+        all_gather(gathered, sums)
+        engine.shard_round_combine(r, gathered, G)
+    fin, gfin = engine.new_buffer(nc), engine.new_buffer(G * nc)
+    engine.shard_finals(fin)
+    all_gather(gfin, fin)
+    engine.shard_residual(gfin, G)
+    state, msgs, chals, finals = engine.shard_end(logn + k)
+    tr.state = state
+    return chals, msgs, finals
