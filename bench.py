@@ -39,52 +39,47 @@ def alg_bytes(nc, logn):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons sampled (NVML, read-only) every few ms while the timed region runs."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, index=0):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, torch_index=0, period=0.003):
+        self.period, self.samples, self.mask, self.stop_flag, self.thread, self.h = period, [], 0, False, None, None
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            pr = torch.cuda.get_device_properties(torch_index)
+            bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            self.max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # no NVML: report that instead of numbers
+            self.err = repr(e)
+
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.mask |= nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True)
-            self.t.start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+        if self.h is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for nm, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(nm)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if self.h is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + getattr(self, "err", "?")]}
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        if not self.samples:  # region shorter than one period: take one reading now
+            self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": float(self.max), "samples": len(self.samples),
+                "reasons": sorted(n for bit, n in self.REASONS.items() if self.mask & bit)}
 
 
 def lcg_cols(orc, n, count, seed):
@@ -116,7 +111,7 @@ def cpu_baseline(logn_sample, nthreads, use_reference):
         Reference().sc5_prove(st0, "sc", 0, cols)
         kind = "reference"
     else:
-        orc.sumcheck(st0, "sc", F_PROD2, 3, cols, (), nthreads)
+        orc.sumcheck(st0, "sc", F_PROD2, 3, cols, (), nthreads, inplace=True)
     dt = time.perf_counter() - t0
     return {"value": alg_bytes(2, logn_sample) / dt / 1e9, "unit": UNIT, "cores": nthreads, "kind": kind,
             "sample": "one degree-2 sumcheck over 2^%d elements per column (%.1f s)" % (logn_sample, dt)}
@@ -152,6 +147,116 @@ def run_reference(args):
     }))
 
 
+def run_suite(args):
+    """--suite: the other BASELINE.json microbench shapes (configs[1] and configs[2]) on one GPU, one
+    JSON line each: degree-2/3 sumchecks at 2^20/2^24/2^28, Basefold commit and opening of 2^24
+    coefficients at rate 1/2, the 2^24-into-2^16 lookup pieces.  Device-resident inputs, CUDA
+    events, best of `steps` after `warmup`."""
+    import torch
+    import zkh_import
+    zk = zkh_import.load()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle import Oracle, Reference
+    orc = Oracle()
+    torch.cuda.set_device(0)
+    prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+    ref = Reference() if (Reference.available() and not args.no_ref_cuda) else None
+    if ref is not None and not ref.gpu_available():
+        ref = None
+    if ref is not None:
+        ref.lib.ref_gpu_setup()
+    peak, _ = measured_peak()
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        best = 1e30
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return best
+
+    def emit(name, ms, alg, extra=None):
+        d = {"suite": name, "ms": ms, "alg_bytes": alg, "GB/s": alg / ms / 1e6 if alg else None,
+             "frac_of_measured_hbm": (alg / ms / 1e6) / peak if alg else None}
+        d.update(extra or {})
+        print(json.dumps(d), flush=True)
+
+    for functor, nt, nc, name in [(zk.F_PROD2, 3, 2, "sumcheck deg2"), (zk.F_PROD3, 4, 3, "sumcheck deg3")]:
+        for logn in (20, 24, 28):
+            host = lcg_cols(orc, 1 << logn, nc, SEED)
+            dcols = [zk.p3.to_device(c) for c in host]
+            ms = timed(lambda: prover.sc_prove_gpu(zk.Transcript("bench"), "sc", dcols, functor, nt))
+            extra = {}
+            if ref is not None:
+                st0 = orc.tr_init("bench")
+                extra["reference_cuda_ms"] = min(ref.sc_prove_gpu(st0, "sc", functor, nt, host)[3] for _ in range(3))
+                extra["speedup_vs_reference_cuda"] = extra["reference_cuda_ms"] / ms
+            emit("%s 2^%d" % (name, logn), ms, 24 * nc * (1 << logn), extra)
+            del dcols, host
+            torch.cuda.empty_cache()
+    # Basefold commitment of 2^24 coefficients at rate 1/2 (1 element per leaf, the reference's layout)
+    v, R, Q = 24, 1, 24
+    cc, s2 = orc.lcg(1 << v, SEED)
+    zz, _ = orc.lcg(v, s2)
+    c_dev = zk.p3.to_device(cc)
+    cw_dev = torch.empty(1 << (v + R), dtype=torch.int64, device="cuda")
+    M = 1 << (v + R)
+    ms = timed(lambda: (prover.rs_encode_gpu_dev(c_dev, R, cw_dev), prover.sync()))
+    emit("rs_encode 2^24 -> 2^25 (3 NTT passes)", ms, 3 * 16 * M - 8 * M // 2)
+    ms = timed(lambda: prover.merkle_build_dev(cw_dev, keep_tree=False))
+    emit("merkle root 2^25 leaves", ms, 8 * M, {"sha256_compressions_per_s": (2 * M - 1) / ms * 1e3})
+    ms = timed(lambda: prover.commit_gpu_rootonly(c_dev, R))
+    extra = {}
+    if ref is not None:
+        extra["reference_cuda_ms"] = min(ref.commit_gpu_rootonly(cc, R)[1] for _ in range(3))
+        extra["note"] = "the reference's timer includes its H2D upload of the coefficients (134 MB)"
+    emit("basefold commit 2^24 (encode + root), device coefficients", ms, None, extra)
+    ms = timed(lambda: prover.commit_gpu_rootonly(cc, R))
+    emit("basefold commit 2^24 from host coefficients", ms, None)
+    y = prover.eval_h_gpu(c_dev, zz)
+    ms = timed(lambda: prover.prove_eval_dev(c_dev, zz, y, R, Q, cw_dev))
+    extra = {}
+    if ref is not None:
+        cw_host = zk.p3.to_host(cw_dev)
+        extra["reference_cuda_ms"] = min(ref.bf_prove_eval_dev(cc, zz, y, R, Q, cw_host)[1] for _ in range(2))
+        extra["note"] = "the reference's timer includes its H2D upload of coefficients and codeword (403 MB)"
+        del cw_host
+    emit("basefold opening 2^24, Q=24", ms, None, extra)
+    del cw_dev, c_dev
+    torch.cuda.empty_cache()
+    # lookup pieces: 2^24 queries into a 2^16-row table
+    rng = np.random.default_rng(0)
+    idx = np.clip(np.rint(rng.normal(0, 1 << 10, 1 << 24)), -32768, 32767).astype(np.int64) + 32768
+    idx_dev = torch.from_numpy(idx.astype(np.uint32).view(np.int32)).cuda()
+    ms = timed(lambda: prover.histogram(idx_dev, 1 << 16))
+    emit("histogram 2^24 -> 2^16", ms, 4 << 24)
+    A, s3 = orc.lcg(1 << 24, SEED + 7)
+    A_dev = zk.p3.to_device(A)
+    beta = int(orc.lcg(1, s3)[0][0])
+    ms = timed(lambda: prover.inv_all_add(A_dev, beta))
+    emit("batched inversion 2^24", ms, 16 << 24)
+    q_dev = zk.p3.to_device(((A.astype(object) + beta) % 0xFFFFFFFF00000001).astype(np.uint64))
+    p_dev = zk.p3.to_device(np.ones(1 << 24, dtype=np.uint64))
+    ms = timed(lambda: prover.gkr_prove(zk.Transcript("bench"), "lug-gA", p_dev, q_dev, True))
+    extra = {}
+    if ref is not None:
+        import time as _t
+        pq = (zk.p3.to_host(p_dev), zk.p3.to_host(q_dev))
+        ts = []
+        for _ in range(2):
+            t0 = _t.perf_counter()
+            ref.gkr_prove(orc.tr_init("bench"), "lug-gA", pq[0], pq[1], True, gpu=True)
+            ts.append((_t.perf_counter() - t0) * 1e3)
+        extra["reference_cuda_ms"] = min(ts)
+        extra["note"] = "reference wall time including its upload of the leaves (268 MB)"
+    emit("GKR fractional-sum proof 2^24 leaves (A side)", ms, 48 << 24, extra)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -160,12 +265,16 @@ def main():
     ap.add_argument("--impl", default="zkh", choices=["zkh", "reference"])
     ap.add_argument("--logn", type=int, default=28, help="log2 elements per column per GPU")
     ap.add_argument("--ref-logn", type=int, default=22, help="sample size of the CPU reference arm")
-    ap.add_argument("--cpu-logn", type=int, default=24, help="sample size of the cpu_baseline leg")
+    ap.add_argument("--cpu-logn", type=int, default=26, help="sample size of the cpu_baseline leg")
+    ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's CUDA prover")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.suite:
+        return run_suite(args)
 
     import torch
     import torch.distributed as dist
@@ -262,6 +371,27 @@ def main():
         ncores = os.cpu_count() or 1
         cpu = cpu_baseline(args.cpu_logn, ncores, False)
 
+    # the reference's own CUDA prover (p3sg::sc_prove_gpu, compiled unchanged for sm_100a) on the
+    # same inputs and GPU: device-resident columns, its own timer around the proof only
+    ref_cuda = None
+    if rank == 0 and world == 1 and not args.no_ref_cuda:
+        try:
+            from oracle import Reference
+            if Reference.available():
+                ref = Reference()
+                if ref.gpu_available():
+                    ref.lib.ref_gpu_setup()
+                    st0 = orc.tr_init("bench-sc2")
+                    ms = [ref.sc_prove_gpu(st0, "sc", 0, nt, host_cols)[3] for _ in range(3)]
+                    tr_chk = zk.Transcript("bench-sc2")
+                    mine = prover.sc_prove_gpu(tr_chk, "sc", dcols, zk.F_PROD2, nt)
+                    same = ref.sc_prove_gpu(st0, "sc", 0, nt, host_cols)
+                    ref_cuda = {"ms_per_step": min(ms[1:]), "value": alg_bytes(nc, logn) / (min(ms[1:]) / 1e3) / 1e9,
+                                "unit": UNIT, "what": "p3sg::sc_prove_gpu built for sm_100a, columns resident on the device",
+                                "same_transcript": bool(same[0] == tr_chk.state and (same[1] == mine[1]).all())}
+        except Exception as e:  # the comparison is informative; never fail the bench on it
+            ref_cuda = {"error": repr(e)}
+
     if rank == 0:
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -277,7 +407,7 @@ def main():
                          "launch_ms": k_ms, "alg_bytes_per_launch": k_bytes},
             "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(args.steps * ((1 + (logn - 12) + 1) if world == 1 else (2 * logn + 3))),
-            "clocks": clocks,
+            "clocks": clocks, "reference_cuda": ref_cuda,
         }
         print(json.dumps(out))
     if world > 1:

@@ -232,9 +232,11 @@ class Oracle(_Lib):
         L.orc_lcg_fill.argtypes = [u64p, C.c_size_t, u64p]
         L.orc_bind_lsb.argtypes = [u64p, C.c_size_t, C.c_uint64]
 
-    def sumcheck(self, st, tag, functor, nt, cols, par=(), nthreads=1):
-        """Returns (state, msgs[v,nt], chals[v], finals[nc]); cols are copied."""
-        arrs = [np.array(c, dtype=np.uint64, copy=True) for c in cols]
+    def sumcheck(self, st, tag, functor, nt, cols, par=(), nthreads=1, inplace=False):
+        """Returns (state, msgs[v,nt], chals[v], finals[nc]); cols are copied unless inplace
+        (then they are consumed: bound in place)."""
+        arrs = [np.ascontiguousarray(c, dtype=np.uint64) if inplace else np.array(c, dtype=np.uint64, copy=True)
+                for c in cols]
         nc = len(arrs); logn = int(len(arrs[0])).bit_length() - 1
         ptrs = (u64p * nc)(*[a.ctypes.data_as(u64p) for a in arrs])
         par, pp = _u64(list(par) if len(par) else [0])

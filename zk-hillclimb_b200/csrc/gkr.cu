@@ -42,11 +42,14 @@ __global__ void gkr_top_kernel(const gl_t* cp, const gl_t* cq, gl_t* term) {
 }
 // draw one field challenge from the device transcript into *dst
 __global__ void tr_chal_kernel(ZkhCtl* ctl, gl_t* dst) {
-    if (threadIdx.x != 0) return;
     uint32_t st[8];
     for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
-    *dst = tr_chal_gl(st);
-    for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+    gl_t a = tr_warp_chal_gl(st);
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        *dst = a;
+        for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+    }
 }
 
 }  // namespace zkh

@@ -24,6 +24,81 @@
 
 typedef uint64_t gl_t;
 
+#ifdef __CUDA_ARCH__
+// ---- carry-chain forms for the device: the canonical add / sub / reduce are the bulk of the
+// integer-ALU work of every kernel, and the compiler's compare+select sequences for the
+// 64-bit carries are about twice as long as these.
+__device__ __forceinline__ void gl_split(uint64_t x, uint32_t& lo, uint32_t& hi) {
+    asm("mov.b64 {%0,%1}, %2;" : "=r"(lo), "=r"(hi) : "l"(x));
+}
+__device__ __forceinline__ uint64_t gl_join(uint32_t lo, uint32_t hi) {
+    uint64_t x;
+    asm("mov.b64 %0, {%1,%2};" : "=l"(x) : "r"(lo), "r"(hi));
+    return x;
+}
+// a, b canonical -> canonical a+b.  s = a+b (65 bits); s >= p  <=>  s + (2^32-1) >= 2^64.
+__device__ __forceinline__ gl_t gl_add(gl_t a, gl_t b) {
+    uint32_t al, ah, bl, bh, tl, th, ul, uh, c;
+    gl_split(a, al, ah);
+    gl_split(b, bl, bh);
+    asm("{\n\t"
+        "add.cc.u32 %0, %5, %7;\n\t"
+        "addc.cc.u32 %1, %6, %8;\n\t"
+        "addc.u32 %4, 0, 0;\n\t"
+        "add.cc.u32 %2, %0, 0xffffffff;\n\t"
+        "addc.cc.u32 %3, %1, 0;\n\t"
+        "addc.u32 %4, %4, 0;\n\t"
+        "}"
+        : "=&r"(tl), "=&r"(th), "=&r"(ul), "=&r"(uh), "=&r"(c)
+        : "r"(al), "r"(ah), "r"(bl), "r"(bh));
+    return c ? gl_join(ul, uh) : gl_join(tl, th);
+}
+// a, b canonical -> canonical a-b: on borrow add p, i.e. subtract 2^32-1 from the wrapped value
+__device__ __forceinline__ gl_t gl_sub(gl_t a, gl_t b) {
+    uint32_t al, ah, bl, bh, dl, dh;
+    gl_split(a, al, ah);
+    gl_split(b, bl, bh);
+    asm("{\n\t"
+        ".reg .u32 m;\n\t"
+        "sub.cc.u32 %0, %2, %4;\n\t"
+        "subc.cc.u32 %1, %3, %5;\n\t"
+        "subc.u32 m, 0, 0;\n\t"
+        "sub.cc.u32 %0, %0, m;\n\t"
+        "subc.u32 %1, %1, 0;\n\t"
+        "}"
+        : "=&r"(dl), "=&r"(dh)
+        : "r"(al), "r"(ah), "r"(bl), "r"(bh));
+    return gl_join(dl, dh);
+}
+// hi:lo (any 128-bit value) -> canonical.  hi = hh*2^32 + hl:  lo - hh + hl*(2^32-1)
+__device__ __forceinline__ gl_t gl_reduce128(uint64_t lo, uint64_t hi) {
+    uint32_t ll, lh, hl, hh, rl, rh, ul, uh, c;
+    gl_split(lo, ll, lh);
+    gl_split(hi, hl, hh);
+    asm("{\n\t"
+        ".reg .u32 m, t1l, t1h, k;\n\t"
+        "sub.cc.u32 %0, %5, %8;\n\t"      // t0 = lo - hh
+        "subc.cc.u32 %1, %6, 0;\n\t"
+        "subc.u32 m, 0, 0;\n\t"
+        "sub.cc.u32 %0, %0, m;\n\t"       // borrow: -(2^32-1)
+        "subc.u32 %1, %1, 0;\n\t"
+        "sub.cc.u32 t1l, 0, %7;\n\t"      // t1 = (hl<<32) - hl
+        "subc.u32 t1h, %7, 0;\n\t"
+        "add.cc.u32 %0, %0, t1l;\n\t"     // t2 = t0 + t1
+        "addc.cc.u32 %1, %1, t1h;\n\t"
+        "addc.u32 k, 0, 0;\n\t"
+        "sub.u32 k, 0, k;\n\t"            // carry: +(2^32-1)
+        "add.cc.u32 %0, %0, k;\n\t"
+        "addc.u32 %1, %1, 0;\n\t"
+        "add.cc.u32 %2, %0, 0xffffffff;\n\t"  // >= p  <=>  + (2^32-1) carries
+        "addc.cc.u32 %3, %1, 0;\n\t"
+        "addc.u32 %4, 0, 0;\n\t"
+        "}"
+        : "=&r"(rl), "=&r"(rh), "=&r"(ul), "=&r"(uh), "=&r"(c)
+        : "r"(ll), "r"(lh), "r"(hl), "r"(hh));
+    return c ? gl_join(ul, uh) : gl_join(rl, rh);
+}
+#else
 GL_HD gl_t gl_add(gl_t a, gl_t b) {
     uint64_t s = a + b;
     if (s < a) s += GL_EPS;  // wrapped past 2^64 == EPS (mod p); cannot wrap twice
@@ -35,9 +110,11 @@ GL_HD gl_t gl_sub(gl_t a, gl_t b) {
     if (a < b) d -= GL_EPS;  // borrow of 2^64 == EPS
     return d;
 }
+#endif
 GL_HD gl_t gl_neg(gl_t a) { return a ? GL_P - a : 0; }
 GL_HD gl_t gl_dbl(gl_t a) { return gl_add(a, a); }
 
+#ifndef __CUDA_ARCH__
 // hi:lo (< 2^128) -> canonical.  hi = hh*2^32 + hl:  lo - hh + hl*(2^32-1)
 GL_HD gl_t gl_reduce128(uint64_t lo, uint64_t hi) {
     uint32_t hh = (uint32_t)(hi >> 32), hl = (uint32_t)hi;
@@ -49,6 +126,7 @@ GL_HD gl_t gl_reduce128(uint64_t lo, uint64_t hi) {
     if (t2 >= GL_P) t2 -= GL_P;
     return t2;
 }
+#endif
 GL_HD void gl_mul_wide(gl_t a, gl_t b, uint64_t& lo, uint64_t& hi) {
 #ifdef __CUDA_ARCH__
     lo = a * b;
@@ -78,8 +156,15 @@ GL_HD gl_t gl_inv(gl_t a) { return gl_pow(a, GL_P - 2); }
 GL_HD gl_t gl_root_of_unity(uint32_t logn) {
     return gl_pow(gl_pow(7ULL, GL_EPS), 1ULL << (32 - logn));
 }
-// a + t*(b-a): the multilinear bind of one pair
-GL_HD gl_t gl_lerp(gl_t a, gl_t b, gl_t t) { return gl_add(a, gl_mul(t, gl_sub(b, a))); }
+// a + t*(b-a): the multilinear bind of one pair.  The addend joins the 128-bit product before the
+// single reduction ((p-1)^2 + p-1 < 2^128).
+GL_HD gl_t gl_lerp(gl_t a, gl_t b, gl_t t) {
+    uint64_t lo, hi;
+    gl_mul_wide(t, gl_sub(b, a), lo, hi);
+    lo += a;
+    hi += (lo < a);
+    return gl_reduce128(lo, hi);
+}
 
 // Lazy sum of 128-bit products.  Holds up to 2^32 products without overflow.
 struct Acc192 {
@@ -89,6 +174,25 @@ struct Acc192 {
     GL_HD void add_prod(gl_t a, gl_t b) {
         uint64_t pl, ph;
         gl_mul_wide(a, b, pl, ph);
+#ifdef __CUDA_ARCH__
+        asm("{\n\t"
+            ".reg .u32 a0, a1, a2, a3, b0, b1, b2, b3;\n\t"
+            "mov.b64 {a0,a1}, %0;\n\t"
+            "mov.b64 {a2,a3}, %1;\n\t"
+            "mov.b64 {b0,b1}, %3;\n\t"
+            "mov.b64 {b2,b3}, %4;\n\t"
+            "add.cc.u32 a0, a0, b0;\n\t"
+            "addc.cc.u32 a1, a1, b1;\n\t"
+            "addc.cc.u32 a2, a2, b2;\n\t"
+            "addc.cc.u32 a3, a3, b3;\n\t"
+            "addc.u32 %2, %2, 0;\n\t"
+            "mov.b64 %0, {a0,a1};\n\t"
+            "mov.b64 %1, {a2,a3};\n\t"
+            "}"
+            : "+l"(lo), "+l"(mid), "+r"(top)
+            : "l"(pl), "l"(ph));
+        return;
+#endif
         lo += pl;
         uint64_t c = lo < pl;
         uint64_t m = mid + ph;

@@ -162,42 +162,102 @@ GL_HD void tr_challenge(uint32_t st[8], uint32_t out[8]) {
     for (int i = 0; i < 8; i++) st[i] = ns[i];
 }
 #ifdef __CUDACC__
-// Device form of tr_absorb for one thread: the message is assembled as bytes in shared
-// memory (buf: at least 32+4+48+8+320+72 bytes, 4-byte aligned) and read back as words,
-// which avoids local-memory byte traffic in the serial part of a round.
-__device__ __forceinline__ void tr_absorb_sh(uint32_t st[8], const char* label, uint32_t ll,
-                                             const uint64_t* vals, uint32_t nvals, uint32_t* buf) {
-    uint8_t* b = reinterpret_cast<uint8_t*>(buf);
+// ---- warp-level transcript steps for the serial end of a round ----
+// The fully unrolled compression above is ~30 KB of straight-line code per instance; run once
+// by one thread at the end of a kernel it is an instruction-cache miss from start to end.  The
+// transcript path therefore uses ONE shared, compact copy (16 rounds unrolled, looped 4 times,
+// round constants from constant memory), and runs the two independent hashes of a challenge
+// ("chal" and "rtch") on two lanes of the same warp.
+static __constant__ uint32_t zkh_sha_k[64] = {ZKH_SHA_K_LIST};
+
+static __device__ __noinline__ void sha256_compress_compact(uint32_t* h, uint32_t* wp) {
+    uint32_t w[16];
 #pragma unroll
-    for (int i = 0; i < 8; i++) buf[i] = bswap32(st[i]);
-    uint32_t p = 32;
-    b[p++] = (uint8_t)ll; b[p++] = (uint8_t)(ll >> 8); b[p++] = 0; b[p++] = 0;
-    for (uint32_t i = 0; i < ll; i++) b[p++] = (uint8_t)label[i];
-    const uint32_t len = nvals * 8;
-    b[p++] = (uint8_t)len; b[p++] = (uint8_t)(len >> 8);
-    for (int i = 0; i < 6; i++) b[p++] = 0;
-    for (uint32_t k = 0; k < nvals; k++) {
-        uint64_t v = vals[k];
+    for (int i = 0; i < 16; i++) w[i] = wp[i];
+    uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
+#pragma unroll 1
+    for (int r = 0; r < 4; r++) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) b[p++] = (uint8_t)(v >> (8 * j));
+        for (int j = 0; j < 16; j++) {
+            if (r) {
+                uint32_t x = w[(j + 1) & 15], y = w[(j + 14) & 15];
+                w[j] += (rotr32(x, 7) ^ rotr32(x, 18) ^ (x >> 3)) + w[(j + 9) & 15] +
+                        (rotr32(y, 17) ^ rotr32(y, 19) ^ (y >> 10));
+            }
+            uint32_t t1 = hh + (rotr32(e, 6) ^ rotr32(e, 11) ^ rotr32(e, 25)) + ((e & f) ^ (~e & g)) +
+                          zkh_sha_k[16 * r + j] + w[j];
+            uint32_t t2 = (rotr32(a, 2) ^ rotr32(a, 13) ^ rotr32(a, 22)) + ((a & b) ^ (a & c) ^ (b & c));
+            hh = g; g = f; f = e; e = d + t1;
+            d = c; c = b; b = a; a = t1 + t2;
+        }
     }
-    const uint32_t total = p, padded = ((total + 8) / 64 + 1) * 64;
-    b[p++] = 0x80;
-    while (p < padded - 8) b[p++] = 0;
-    const uint64_t bits = (uint64_t)total * 8;
-#pragma unroll
-    for (int i = 0; i < 8; i++) b[padded - 1 - i] = (uint8_t)(bits >> (8 * i));
+    h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
+}
+
+// state' = H(state|LE32(ll)|label|LE64(8*nvals)|vals).  Called by all 32 lanes of one warp with
+// identical arguments (vals: nvals 64-bit words readable by every lane); buf is shared memory of
+// at least 32+4+48+8+320+72 bytes.  Every lane ends with the same new state.
+__device__ __forceinline__ void tr_warp_absorb(uint32_t st[8], const char* label, uint32_t ll,
+                                               const uint64_t* vals, uint32_t nvals, uint32_t* buf) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t total = 32 + 4 + ll + 8 + nvals * 8, padded = ((total + 8) / 64 + 1) * 64;
+    __syncwarp();
+    if (lane == 0) {
+        uint8_t* b = reinterpret_cast<uint8_t*>(buf);
+        for (int i = 0; i < 8; i++) buf[i] = bswap32(st[i]);
+        uint32_t p = 32;
+        b[p++] = (uint8_t)ll; b[p++] = (uint8_t)(ll >> 8); b[p++] = 0; b[p++] = 0;
+        for (uint32_t i = 0; i < ll; i++) b[p++] = (uint8_t)label[i];
+        const uint32_t len = nvals * 8;
+        b[p++] = (uint8_t)len; b[p++] = (uint8_t)(len >> 8);
+        for (int i = 0; i < 6; i++) b[p++] = 0;
+        for (uint32_t k = 0; k < nvals; k++) {
+            uint64_t v = vals[k];
+            for (int j = 0; j < 8; j++) b[p++] = (uint8_t)(v >> (8 * j));
+        }
+        b[p++] = 0x80;
+        while (p < padded - 8) b[p++] = 0;
+        const uint64_t bits = (uint64_t)total * 8;
+        for (int i = 0; i < 8; i++) b[padded - 1 - i] = (uint8_t)(bits >> (8 * i));
+    }
+    __syncwarp();
     uint32_t h[8];
     sha256_iv(h);
     for (uint32_t off = 0; off < padded / 4; off += 16) {
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) w[i] = bswap32(buf[off + i]);
-        sha256_compress(h, w);
+        sha256_compress_compact(h, w);
     }
 #pragma unroll
     for (int i = 0; i < 8; i++) st[i] = h[i];
+    __syncwarp();
 }
+// Challenge by a full warp holding the same state on every lane: lane 0 hashes state|"chal",
+// lane 1 hashes state|"rtch" in the same instruction stream.  Returns the first 8 digest bytes
+// as a little-endian integer on every lane; st becomes the ratcheted state on every lane.
+__device__ __forceinline__ uint64_t tr_warp_challenge(uint32_t st[8]) {
+    const uint32_t lane = threadIdx.x & 31;
+    uint32_t w[16], o[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) w[i] = st[i];
+    w[8] = (lane == 1) ? 0x72746368u : 0x6368616cu;  // "rtch" : "chal"
+    w[9] = 0x80000000u;
+#pragma unroll
+    for (int i = 10; i < 15; i++) w[i] = 0;
+    w[15] = 36 * 8;
+    sha256_iv(o);
+    sha256_compress_compact(o, w);
+#pragma unroll
+    for (int i = 0; i < 8; i++) st[i] = __shfl_sync(0xffffffffu, o[i], 1);
+    uint32_t c0 = __shfl_sync(0xffffffffu, o[0], 0), c1 = __shfl_sync(0xffffffffu, o[1], 0);
+    return (uint64_t)bswap32(c0) | ((uint64_t)bswap32(c1) << 32);
+}
+__device__ __forceinline__ gl_t tr_warp_chal_gl(uint32_t st[8]) {
+    uint64_t v = tr_warp_challenge(st);
+    return v >= GL_P ? v - GL_P : v;
+}
+#define ZKH_TRBUF_WORDS ((32 + 4 + ZKH_TR_MAX_LABEL + 8 + ZKH_TR_MAX_DATA + 72) / 4)
 #endif
 
 // first 8 digest bytes as a little-endian u64

@@ -19,21 +19,32 @@
 namespace zkh {
 
 // ------------------------------------------------------------------ summands
+// Each summand F has degree DEG (2 or 3) in the round variable.  Its round polynomial is fixed
+// by DEG+1 numbers; the kernels accumulate F at t = 0 .. DEG-1 and the leading coefficient
+// (F's top-degree part applied to the pair differences), which needs no stepped operands, and
+// derive the evaluations at t = DEG .. NT-1 by finite differences afterwards.  All of it is
+// exact field arithmetic, so the message equals the reference's t = 0..NT-1 sums.
 template <int F> struct Fn;
 template <> struct Fn<ZKH_F_PROD2> {
-    static constexpr int NC = 2;
+    static constexpr int NC = 2, DEG = 2;
     static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t*) {
         a.add_prod(c[0], c[1]);
     }
+    static __device__ __forceinline__ void lead(Acc192& a, const gl_t* d, const gl_t*) {
+        a.add_prod(d[0], d[1]);
+    }
 };
 template <> struct Fn<ZKH_F_PROD3> {
-    static constexpr int NC = 3;
+    static constexpr int NC = 3, DEG = 3;
     static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t*) {
         a.add_prod(c[0], gl_mul(c[1], c[2]));
     }
+    static __device__ __forceinline__ void lead(Acc192& a, const gl_t* d, const gl_t*) {
+        a.add_prod(d[0], gl_mul(d[1], d[2]));
+    }
 };
 template <> struct Fn<ZKH_F_GKR> {
-    static constexpr int NC = 5;
+    static constexpr int NC = 5, DEG = 3;
     static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t* p) {
         Acc192 in;
         in.clear();
@@ -42,12 +53,17 @@ template <> struct Fn<ZKH_F_GKR> {
         in.add_prod(p[0], gl_mul(c[3], c[4]));
         a.add_prod(c[0], in.reduce());
     }
+    static __device__ __forceinline__ void lead(Acc192& a, const gl_t* d, const gl_t* p) { acc(a, d, p); }
 };
 template <> struct Fn<ZKH_F_LOGUP> {
-    static constexpr int NC = 4;
+    static constexpr int NC = 4, DEG = 3;
     static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t* p) {
         a.add_prod(p[0], c[0]);
         a.add_prod(c[2], gl_sub(gl_mul(c[0], gl_add(c[1], p[1])), c[3]));
+    }
+    // the only cubic term of  p0*H + E*(H*(V+p1) - D)  is E*H*V
+    static __device__ __forceinline__ void lead(Acc192& a, const gl_t* d, const gl_t*) {
+        a.add_prod(d[2], gl_mul(d[0], d[1]));
     }
 };
 
@@ -105,50 +121,76 @@ __device__ __forceinline__ void load_quads(const ScPtrs& P, size_t i, gl_t (&x)[
     }
 }
 
-// message contribution of one pair per column: evaluations at t = 0..NT-1 of
-// F(lo + t*(hi-lo))  (zkllm-src/p3_scgpu.cuh:63-72)
+// message contribution of one pair per column (zkllm-src/p3_scgpu.cuh:63-72 computes
+// F(lo + t*(hi-lo)) for every t; see the note above Fn for what is accumulated instead).
+// acc[t], t < DEG: F at t;  acc[DEG]: leading coefficient;  acc[t > DEG]: unused.
 template <int F, int NT>
 __device__ __forceinline__ void msg_accum(Acc192 (&acc)[NT], const gl_t (&lo)[Fn<F>::NC],
                                           const gl_t (&hi)[Fn<F>::NC], const gl_t* par) {
-    constexpr int NC = Fn<F>::NC;
-    gl_t cur[NC], dd[NC];
+    constexpr int NC = Fn<F>::NC, DEG = Fn<F>::DEG;
+    static_assert(NT > DEG, "message must carry at least DEG+1 evaluations");
+    gl_t dd[NC];
+    Fn<F>::acc(acc[0], lo, par);
+    Fn<F>::acc(acc[1], hi, par);
 #pragma unroll
-    for (int k = 0; k < NC; k++) cur[k] = lo[k];
-    Fn<F>::acc(acc[0], cur, par);
+    for (int k = 0; k < NC; k++) dd[k] = gl_sub(hi[k], lo[k]);
+    Fn<F>::lead(acc[DEG], dd, par);
+    if (DEG == 3) {
+        gl_t cur[NC];
 #pragma unroll
-    for (int k = 0; k < NC; k++) { cur[k] = hi[k]; dd[k] = gl_sub(hi[k], lo[k]); }
-    Fn<F>::acc(acc[1], cur, par);
+        for (int k = 0; k < NC; k++) cur[k] = gl_add(hi[k], dd[k]);
+        Fn<F>::acc(acc[2], cur, par);
+    }
+}
+// per-thread: reduce the lazy sums and turn (F(0..DEG-1), lead) into evaluations at t = 0..NT-1.
+// Linear in the accumulated quantities, so it commutes with the later summation over threads.
+template <int F, int NT>
+__device__ __forceinline__ void msg_reduce(const Acc192 (&acc)[NT], gl_t (&s)[NT]) {
+    constexpr int DEG = Fn<F>::DEG;
 #pragma unroll
-    for (int t = 2; t < NT; t++) {
+    for (int t = 0; t <= DEG; t++) s[t] = acc[t].reduce();
+    if (DEG == 2) {
+        // g(2) = 2 g(1) - g(0) + 2 c2 ; third difference vanishes afterwards
+        gl_t c2 = s[2];
+        s[2] = gl_add(gl_sub(gl_dbl(s[1]), s[0]), gl_dbl(c2));
 #pragma unroll
-        for (int k = 0; k < NC; k++) cur[k] = gl_add(cur[k], dd[k]);
-        Fn<F>::acc(acc[t], cur, par);
+        for (int t = 3; t < NT; t++)
+            s[t] = gl_add(gl_mul(3, gl_sub(s[t - 1], s[t - 2])), s[t - 3]);
+    } else {
+        // g(3) = 3 g(2) - 3 g(1) + g(0) + 6 c3 ; fourth difference vanishes afterwards
+        gl_t c3 = s[3];
+        s[3] = gl_add(gl_add(gl_mul(3, gl_sub(s[2], s[1])), s[0]), gl_mul(6, c3));
+#pragma unroll
+        for (int t = 4; t < NT; t++)
+            s[t] = gl_sub(gl_add(gl_mul(4, gl_add(s[t - 1], s[t - 3])), 0), gl_add(gl_mul(6, s[t - 2]), s[t - 4]));
     }
 }
 
 // ------------------------------------------------------------------ round end
 // mode 0: absorb the message under `tag` and draw the challenge on the device.
 // mode 1: write this GPU's sums to msg_out and stop (another step combines the GPUs).
+// Called by all 32 lanes of warp 0; the sums s are valid on lane 0.
 template <int NT>
 __device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t* msg_out, gl_t* chal_out,
                                           const ZkhTag& tag, int mode) {
-    __shared__ uint32_t trbuf[(32 + 4 + ZKH_TR_MAX_LABEL + 8 + 64 + 72) / 4];
-    if (mode == 1) {
+    __shared__ uint32_t trbuf[ZKH_TRBUF_WORDS];
+    __shared__ gl_t mvals[NT];
+    const uint32_t lane = threadIdx.x & 31;
+    if (lane == 0) {
 #pragma unroll
-        for (int t = 0; t < NT; t++) msg_out[t] = s[t];
-        return;
+        for (int t = 0; t < NT; t++) { msg_out[t] = s[t]; mvals[t] = s[t]; }
     }
-    gl_t m[NT];
-#pragma unroll
-    for (int t = 0; t < NT; t++) { m[t] = s[t]; msg_out[t] = s[t]; }
+    if (mode == 1) return;
     uint32_t st[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
-    tr_absorb_sh(st, tag.s, tag.len, m, NT, trbuf);
-    gl_t a = tr_chal_gl(st);
+    tr_warp_absorb(st, tag.s, tag.len, mvals, NT, trbuf);
+    gl_t a = tr_warp_chal_gl(st);
+    if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
-    *chal_out = a;
+        for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+        *chal_out = a;
+    }
 }
 
 // CTA sums -> grid sum by the last CTA to arrive -> finish_round.
@@ -176,8 +218,8 @@ __device__ __forceinline__ void grid_finish(gl_t (&s)[NT], gl_t* sh, ZkhCtl* ctl
         for (int t = 0; t < NT; t++) v[t] = gl_add(v[t], __ldcg(&partials[(size_t)b * NT + t]));
     }
     block_sum<NT>(v, sh);
-    if (threadIdx.x == 0) {
-        ctl->counter = 0;
+    if (threadIdx.x < 32) {
+        if (threadIdx.x == 0) ctl->counter = 0;
         finish_round<NT>(v, ctl, msg_out, chal_out, tag, mode);
     }
 }
@@ -201,8 +243,7 @@ sc_first_kernel(ScPtrs P, size_t half, ZkhCtl* ctl, gl_t* partials, gl_t* msg_ou
         msg_accum<F, NT>(acc, lo, hi, par);
     }
     gl_t s[NT];
-#pragma unroll
-    for (int t = 0; t < NT; t++) s[t] = acc[t].reduce();
+    msg_reduce<F, NT>(acc, s);
     grid_finish<NT>(s, sh, ctl, partials, msg_out, chal_out, tag, mode);
 }
 
@@ -231,8 +272,7 @@ sc_fused_kernel(ScPtrs P, size_t quads, ZkhCtl* ctl, gl_t* partials, const gl_t*
         msg_accum<F, NT>(acc, lo, hi, par);
     }
     gl_t s[NT];
-#pragma unroll
-    for (int t = 0; t < NT; t++) s[t] = acc[t].reduce();
+    msg_reduce<F, NT>(acc, s);
     grid_finish<NT>(s, sh, ctl, partials, msg_out, chal_out, tag, mode);
 }
 
@@ -281,12 +321,11 @@ sc_tail_kernel(ScPtrs P, uint32_t n_in, int pending, ZkhCtl* ctl, const gl_t* ch
             msg_accum<F, NT>(acc, lo, hi, par);
         }
         gl_t s[NT];
-#pragma unroll
-        for (int t = 0; t < NT; t++) s[t] = acc[t].reduce();
+        msg_reduce<F, NT>(acc, s);
         block_sum<NT>(s, sh);  // ends with a barrier: every pair has been read
-        if (tid == 0) {
+        if (tid < 32) {
             finish_round<NT>(s, ctl, msg_out + (size_t)r * NT, chal_out + r, tag, 0);
-            sh_chal = chal_out[r];
+            if (tid == 0) sh_chal = chal_out[r];
         }
         __syncthreads();
         const gl_t a = sh_chal;
@@ -466,20 +505,22 @@ int sc_enqueue_tail(zkh_ctx* ctx, int functor, int nt, const gl_t* const* in, ui
 // rank of a sharded sumcheck runs identically after the all-gather
 __global__ void sc_combine_kernel(ZkhCtl* ctl, const gl_t* gathered, uint32_t G, int nt, ZkhTag tag, gl_t* msg_out,
                                   gl_t* chal_out) {
-    __shared__ uint32_t buf[(32 + 4 + ZKH_TR_MAX_LABEL + 8 + 64 + 72) / 4];
-    if (threadIdx.x != 0) return;
-    gl_t m[5];
-    for (int t = 0; t < nt; t++) {
+    __shared__ uint32_t buf[ZKH_TRBUF_WORDS];
+    __shared__ gl_t m[5];
+    if (threadIdx.x < (unsigned)nt) {
         gl_t a = 0;
-        for (uint32_t g = 0; g < G; g++) a = gl_add(a, gathered[(size_t)g * nt + t]);
-        m[t] = a;
-        msg_out[t] = a;
+        for (uint32_t g = 0; g < G; g++) a = gl_add(a, gathered[(size_t)g * nt + threadIdx.x]);
+        m[threadIdx.x] = a;
+        msg_out[threadIdx.x] = a;
     }
     uint32_t st[8];
     for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
-    tr_absorb_sh(st, tag.s, tag.len, m, nt, buf);
-    *chal_out = tr_chal_gl(st);
-    for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+    tr_warp_absorb(st, tag.s, tag.len, m, nt, buf);
+    gl_t a = tr_warp_chal_gl(st);
+    if (threadIdx.x == 0) {
+        *chal_out = a;
+        for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+    }
 }
 // out[k] = in[k][0] + a*(in[k][1]-in[k][0]): the last local bind of a sharded sumcheck
 __global__ void sc_finals_kernel(ScPtrs P, int nc, const gl_t* chal, gl_t* out) {
@@ -494,12 +535,12 @@ __global__ void sc_transpose_kernel(const gl_t* in, gl_t* out, uint32_t G, int n
 
 // st = absorb(st, tag, vals[0..n)) on the device transcript (n 64-bit words of raw bytes)
 __global__ void tr_absorb_kernel(ZkhCtl* ctl, ZkhTag tag, const uint64_t* vals, uint32_t n) {
-    __shared__ uint32_t buf[(32 + 4 + ZKH_TR_MAX_LABEL + 8 + ZKH_TR_MAX_DATA + 72) / 4];
-    if (threadIdx.x != 0) return;
+    __shared__ uint32_t buf[ZKH_TRBUF_WORDS];
     uint32_t st[8];
     for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
-    tr_absorb_sh(st, tag.s, tag.len, vals, n, buf);
-    for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
+    tr_warp_absorb(st, tag.s, tag.len, vals, n, buf);
+    if (threadIdx.x == 0)
+        for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
 }
 int tr_absorb_enqueue(zkh_ctx* ctx, const char* tag, const uint64_t* vals_dev, uint32_t nwords) {
     if (nwords * 8 > ZKH_TR_MAX_DATA) return zkh_fail(ctx, ZKH_ERR_LIMIT, "device absorb: more than 320 bytes");
