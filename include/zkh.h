@@ -193,6 +193,23 @@ ZKH_API int zkh_basefold_open(zkh_ctx* ctx, const uint64_t* c_dev, const uint64_
                               uint32_t R, uint32_t Q, const uint64_t* cw0_dev, const char* seed, uint8_t* out,
                               size_t cap, size_t* written);
 
+/* Batched opening of one size class, non-zk (zkllm-src/p3_batchopen.cuh:307-1147 p3bo::prove_class).
+ * Ledger of k claims over columns of 2^v rows: entry j = (cols_dev[j], roots + 32*j, zid[j]) claims the
+ * column committed under that root at point pts[zid[j]] (T points of v coordinates, host).  Entries
+ * with equal roots are one column (deduplicated by first appearance, like the reference).
+ * state: the MAIN transcript, in/out (mu, "bo-rm" rounds, "bo-ys", rho are drawn/absorbed on it); the
+ * opening itself runs on a fresh transcript seeded with `label`, as in the reference.
+ * The proof is the fields of p3bo::BatchProof in declaration order (zk fields omitted):
+ *   u32 v, R, Q, nc | ystar nc*8 | rmsgs v*24 | roots (v-1)*32 | omsgs v*24 | final 2^R*8 |
+ *   per query, per round r = 1..v-1: a(8) b(8) path_a((v+R-r)*32) path_b((v+R-r)*32) |
+ *   per distinct column: u32 nvals, vals nvals*8, u32 nnodes, nodes nnodes*32
+ * cap must be at least zkh_batchopen_proof_bound(v, R, Q, number of distinct columns <= k). */
+ZKH_API size_t zkh_batchopen_proof_bound(uint32_t v, uint32_t R, uint32_t Q, uint32_t ncols);
+ZKH_API int zkh_batchopen_prove_class(zkh_ctx* ctx, uint32_t v, const uint64_t* pts, uint32_t T,
+                                      const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
+                                      uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
+                                      uint8_t* out, size_t cap, size_t* written);
+
 /* ---- logUp ---- */
 /* Multiplicities: cnt_dev[j] = #{i : idx_dev[i] == j}, j < M (zkllm-src/p3_logup.cuh:149-172,
  * host loop :1412-1475).  An index >= M returns ZKH_ERR_DOMAIN (the reference throws). */

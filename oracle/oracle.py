@@ -200,6 +200,49 @@ class _Lib:
         nr = L if combine_last else L - 1
         return bool(ok), bytes(s), rfin[:nr].copy(), out4
 
+    # ---- batched opening of one size class ----
+    @staticmethod
+    def _bo_args(pts, roots, zid):
+        pts = np.ascontiguousarray(pts, dtype=np.uint64)
+        T, v = pts.shape
+        rb = b"".join(bytes(r) for r in roots)
+        zid = np.ascontiguousarray(zid, dtype=np.uint32)
+        return pts, T, v, rb, zid
+
+    def bo_verify_class(self, st, pts, roots, zid, y, R, Q, label, proof):
+        """p3bo::verify_class on the serialised BatchProof.  Returns (ok, new transcript state)."""
+        pts, T, v, rb, zid = self._bo_args(pts, roots, zid)
+        y = np.ascontiguousarray(y, dtype=np.uint64)
+        s = _bytes32(st)
+        ok = self._f("bo_verify_class")(s, C.c_uint32(v), pts.ctypes.data_as(u64p), C.c_uint32(T), rb,
+                                        zid.ctypes.data_as(C.c_void_p), y.ctypes.data_as(u64p),
+                                        C.c_uint32(len(zid)), C.c_uint32(R), C.c_uint32(Q), label.encode(),
+                                        bytes(proof), C.c_size_t(len(proof)))
+        return bool(ok), bytes(s)
+
+    def bo_prove_class(self, st, pts, cols, roots, zid, R, Q, label):
+        """p3bo::prove_class; cols[j] = values of entry j.  Returns (proof bytes, new state[, ms])."""
+        pts, T, v, rb, zid = self._bo_args(pts, roots, zid)
+        arrs = [np.ascontiguousarray(c, dtype=np.uint64) for c in cols]
+        ptrs = (u64p * len(arrs))(*[a.ctypes.data_as(u64p) for a in arrs])
+        nc = len(set(bytes(r) for r in roots))
+        cap = 16 + nc * 8 + v * 48 + max(v - 1, 0) * 32 + (8 << R) + \
+            sum(Q * (16 + 2 * (v + R - r) * 32) for r in range(1, v)) + nc * (8 + 2 * Q * 8 + 2 * Q * (v + R) * 32)
+        out = (C.c_uint8 * cap)()
+        s = _bytes32(st)
+        f = self._f("bo_prove_class")
+        f.restype = C.c_size_t
+        args = [s, C.c_uint32(v), pts.ctypes.data_as(u64p), C.c_uint32(T), ptrs, rb,
+                zid.ctypes.data_as(C.c_void_p), C.c_uint32(len(zid)), C.c_uint32(R), C.c_uint32(Q),
+                label.encode(), out, C.c_size_t(cap)]
+        ms = C.c_double(0)
+        if self.prefix == "ref_":
+            args.append(C.byref(ms))
+        n = f(*args)
+        if n == 0:
+            raise RuntimeError("bo_prove_class failed")
+        return (bytes(out)[:n], bytes(s)) + ((ms.value,) if self.prefix == "ref_" else ())
+
     # ---- logUp primitives ----
     def inv_all_add(self, A, beta):
         A, ap = _u64(A); out = np.empty(len(A), dtype=np.uint64)

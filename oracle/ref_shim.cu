@@ -118,6 +118,76 @@ bool gkr_deserialize(const uint8_t* in, size_t len, uint32_t L, p3gkr::Proof& pf
     }
     return true;
 }
+// BatchProof <-> the byte layout documented in oracle/zkh_oracle.c (non-zk fields)
+size_t bo_serialize(const p3bo::BatchProof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&pf.v, 4); app(&pf.R, 4); app(&pf.Q, 4); app(&pf.nc, 4);
+    app(pf.ystar.data(), pf.ystar.size() * 8);
+    for (auto& m : pf.rmsgs) app(&m, 24);
+    for (auto& h : pf.roots) app(h.data(), 32);
+    for (auto& m : pf.omsgs) app(&m, 24);
+    app(pf.final_word.data(), pf.final_word.size() * 8);
+    for (auto& q : pf.queries)
+        for (auto& ro : q.rounds) {
+            app(&ro.a, 8); app(&ro.b, 8);
+            for (auto& h : ro.pa) app(h.data(), 32);
+            for (auto& h : ro.pb) app(h.data(), 32);
+        }
+    for (auto& oc : pf.q0c) {
+        uint32_t nv = (uint32_t)oc.vals.size(), nn = (uint32_t)oc.nodes.size();
+        app(&nv, 4); app(oc.vals.data(), (size_t)nv * 8);
+        app(&nn, 4);
+        for (auto& h : oc.nodes) app(h.data(), 32);
+    }
+    if (b.size() > cap) return 0;
+    memcpy(out, b.data(), b.size());
+    return b.size();
+}
+bool bo_deserialize(const uint8_t* in, size_t len, p3bo::BatchProof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
+    if (!need(16)) return false;
+    memcpy(&pf.v, p, 4); memcpy(&pf.R, p + 4, 4); memcpy(&pf.Q, p + 8, 4); memcpy(&pf.nc, p + 12, 4); p += 16;
+    uint32_t v = pf.v, R = pf.R, Q = pf.Q, nc = pf.nc;
+    if (v > 40 || R > 8 || Q > 4096 || nc > (1u << 20)) return false;
+    if (!need((size_t)nc * 8)) return false;
+    pf.ystar.resize(nc); memcpy(pf.ystar.data(), p, (size_t)nc * 8); p += (size_t)nc * 8;
+    if (!need((size_t)v * 24)) return false;
+    pf.rmsgs.resize(v); for (auto& m : pf.rmsgs) { memcpy(&m, p, 24); p += 24; }
+    uint32_t nr = v ? v - 1 : 0;
+    if (!need((size_t)nr * 32)) return false;
+    pf.roots.resize(nr); for (auto& h : pf.roots) { memcpy(h.data(), p, 32); p += 32; }
+    if (!need((size_t)v * 24)) return false;
+    pf.omsgs.resize(v); for (auto& m : pf.omsgs) { memcpy(&m, p, 24); p += 24; }
+    if (!need((size_t)8 << R)) return false;
+    pf.final_word.resize((size_t)1 << R); memcpy(pf.final_word.data(), p, (size_t)8 << R); p += (size_t)8 << R;
+    pf.queries.resize(Q);
+    for (auto& q : pf.queries) {
+        q.rounds.resize(nr);
+        for (uint32_t r = 1; r < v; r++) {
+            auto& ro = q.rounds[r - 1];
+            uint32_t plen = v + R - r;
+            if (!need(16 + (size_t)2 * plen * 32)) return false;
+            memcpy(&ro.a, p, 8); memcpy(&ro.b, p + 8, 8); p += 16;
+            ro.pa.resize(plen); ro.pb.resize(plen);
+            for (auto& h : ro.pa) { memcpy(h.data(), p, 32); p += 32; }
+            for (auto& h : ro.pb) { memcpy(h.data(), p, 32); p += 32; }
+        }
+    }
+    pf.q0c.resize(nc);
+    for (auto& oc : pf.q0c) {
+        uint32_t nv, nn;
+        if (!need(4)) return false;
+        memcpy(&nv, p, 4); p += 4;
+        if (!need((size_t)nv * 8 + 4)) return false;
+        oc.vals.resize(nv); memcpy(oc.vals.data(), p, (size_t)nv * 8); p += (size_t)nv * 8;
+        memcpy(&nn, p, 4); p += 4;
+        if (!need((size_t)nn * 32)) return false;
+        oc.nodes.resize(nn); for (auto& h : oc.nodes) { memcpy(h.data(), p, 32); p += 32; }
+    }
+    return p == end;
+}
 struct FProd2 { static __device__ gl_t eval(const gl_t* c, const gl_t*) { return gl_mul(c[0], c[1]); } };
 struct M3 { gl_t s[3]; };
 struct M4 { gl_t s[4]; };
@@ -304,6 +374,26 @@ void ref_combine(const uint64_t* const* cols, int c, size_t n, uint64_t g, uint6
     memcpy(out, o.data(), n * 8);
 }
 
+// ---- batched opening: the reference's host-only verifier (p3_batchopen.cuh:1149-1302) ----
+int ref_bo_verify_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T, const uint8_t* roots,
+                        const uint32_t* zid, const uint64_t* y, uint32_t k, uint32_t R, uint32_t Q,
+                        const char* label, const uint8_t* proof, size_t len) {
+    p3bo::BatchProof pf;
+    if (!bo_deserialize(proof, len, pf)) return 0;
+    p3bo::VLedger::Cls C;
+    C.v = v;
+    for (uint32_t t = 0; t < T; t++) C.pts.push_back(std::vector<gl_t>(pts + (size_t)t * v, pts + (size_t)(t + 1) * v));
+    for (uint32_t j = 0; j < k; j++) {
+        p3fri::Hash h; memcpy(h.data(), roots + (size_t)j * 32, 32);
+        C.ents.push_back({h, zid[j], y[j]});
+    }
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3bo::verify_class(tr, C, pf, Q, R, label, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+
 // =====================================================================
 // GPU entry points: the reference's own CUDA paths (need a GPU).
 // =====================================================================
@@ -380,6 +470,36 @@ size_t ref_bf_prove_eval_dev(const uint64_t* c, const uint64_t* z, uint32_t v, u
     cudaDeviceSynchronize();
     if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
     return bf_serialize(pf, out, cap);
+}
+
+// p3bo::prove_class (GPU): cols[j] = host values of entry j (entries with equal roots share values)
+size_t ref_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
+                          const uint64_t* const* cols, const uint8_t* roots, const uint32_t* zid, uint32_t k,
+                          uint32_t R, uint32_t Q, const char* label, uint8_t* out, size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    size_t N = (size_t)1 << v;
+    std::vector<std::vector<gl_t>> vals(k);
+    p3bo::PLedger::Cls C;
+    C.v = v;
+    for (uint32_t t = 0; t < T; t++) C.pts.push_back(std::vector<gl_t>(pts + (size_t)t * v, pts + (size_t)(t + 1) * v));
+    for (uint32_t j = 0; j < k; j++) {
+        vals[j].assign(cols[j], cols[j] + N);
+        p3fri::Hash h; memcpy(h.data(), roots + (size_t)j * 32, 32);
+        C.ents.push_back({&vals[j], h, zid[j], 0, 0, {}, {}});
+    }
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        auto pf = p3bo::prove_class(tr, C, R, Q, label);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = bo_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
 }
 
 }  // extern "C"

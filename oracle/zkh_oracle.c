@@ -846,3 +846,381 @@ void orc_lcg_fill(uint64_t* out, size_t n, uint64_t* state) {
     }
     *state = s;
 }
+
+/* ======================= batched opening (one size class, non-zk) ======================= */
+/* Serialized BatchProof (fields of p3bo::BatchProof in declaration order, zk fields omitted):
+ *   u32 v, R, Q, nc | ystar nc*8 | rmsgs v*24 | roots (v-1)*32 | omsgs v*24 | final 2^R*8 |
+ *   per query q, per round r = 1..v-1: a(8) b(8) pa((v+R-r)*32) pb((v+R-r)*32) |
+ *   per distinct column: u32 nvals, vals nvals*8, u32 nnodes, nodes nnodes*32 */
+static int cmp_u32(const void* a, const void* b) {
+    uint32_t x = *(const uint32_t*)a, y = *(const uint32_t*)b;
+    return x < y ? -1 : x > y;
+}
+size_t orc_bo_proof_bound(uint32_t v, uint32_t R, uint32_t Q, uint32_t nc) {
+    size_t s = 16 + (size_t)nc * 8 + (size_t)v * 48 + (size_t)(v ? v - 1 : 0) * 32 + ((size_t)8 << R);
+    for (uint32_t r = 1; r < v; r++) s += (size_t)Q * (16 + 2 * (size_t)(v + R - r) * 32);
+    s += (size_t)nc * (8 + (size_t)2 * Q * 8 + (size_t)2 * Q * (v + R) * 32);
+    return s;
+}
+/* distinct columns by root, first appearance: zkllm-src/p3_batchopen.cuh:393-403 */
+static uint32_t dedupe_roots(const uint8_t* roots, uint32_t k, uint32_t* colidx, uint32_t* first) {
+    uint32_t nc = 0;
+    for (uint32_t j = 0; j < k; j++) {
+        uint32_t c = 0;
+        while (c < nc && memcmp(roots + (size_t)first[c] * 32, roots + (size_t)j * 32, 32)) c++;
+        if (c == nc) first[nc++] = j;
+        colidx[j] = c;
+    }
+    return nc;
+}
+/* pruned multi-path node stream: zkllm-src/p3_batchopen.cuh:75-106 (subset_prove).  The emitted
+ * siblings do not depend on the recomputed hashes, so only the index walk is needed. */
+static size_t subset_nodes(uint32_t logM, const uint32_t* upos, uint32_t nu, const uint8_t* tree, size_t M,
+                           uint8_t* out) {
+    uint32_t* fr = (uint32_t*)malloc((size_t)nu * 4);
+    memcpy(fr, upos, (size_t)nu * 4);
+    uint32_t nf = nu;
+    size_t nn = 0;
+    const uint8_t* lvl = tree;
+    size_t cnt = M;
+    for (uint32_t l = 0; l < logM; l++) {
+        uint32_t w = 0, i = 0;
+        while (i < nf) {
+            uint32_t idx = fr[i];
+            if (!(idx & 1) && i + 1 < nf && fr[i + 1] == (idx | 1)) i += 2;
+            else { memcpy(out + nn * 32, lvl + (size_t)(idx ^ 1) * 32, 32); nn++; i += 1; }
+            fr[w++] = idx >> 1;
+        }
+        nf = w;
+        lvl += cnt * 32;
+        cnt /= 2;
+    }
+    free(fr);
+    return nn;
+}
+/* zkllm-src/p3_batchopen.cuh:307-1147 (prove_class), non-zk, A.8 schedule */
+size_t orc_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
+                          const uint64_t* const* cols, const uint8_t* roots, const uint32_t* zid, uint32_t k,
+                          uint32_t R, uint32_t Q, const char* label, uint8_t* out, size_t cap) {
+    const size_t N = (size_t)1 << v;
+    const uint32_t logM0 = v + R;
+    const size_t M0 = (size_t)1 << logM0;
+    uint32_t* colidx = (uint32_t*)malloc((size_t)k * 4);
+    uint32_t* first = (uint32_t*)malloc((size_t)k * 4);
+    const uint32_t nc = dedupe_roots(roots, k, colidx, first);
+    if (cap < orc_bo_proof_bound(v, R, Q, nc)) { free(colidx); free(first); return 0; }
+    uint8_t* p = out;
+    put32(&p, v); put32(&p, R); put32(&p, Q); put32(&p, nc);
+    uint8_t* p_ystar = p;            p += (size_t)nc * 8;
+    uint8_t* p_rmsgs = p;            p += (size_t)v * 24;
+    uint8_t* p_roots = p;            p += (size_t)(v ? v - 1 : 0) * 32;
+    uint8_t* p_omsgs = p;            p += (size_t)v * 24;
+    uint8_t* p_final = p;            p += (size_t)8 << R;
+
+    uint64_t mu = orc_tr_chal(st);
+    /* G_t = sum_{j at point t} mu^j col_j ; E_t = eq(z_t, .) */
+    uint64_t* G = (uint64_t*)calloc((size_t)T * N, 8);
+    uint64_t* E = (uint64_t*)malloc((size_t)T * N * 8);
+    uint64_t wj = 1;
+    for (uint32_t j = 0; j < k; j++) {
+        uint64_t* g = G + (size_t)zid[j] * N;
+        for (size_t i = 0; i < N; i++) g[i] = orc_gl_add(g[i], orc_gl_mul(wj, cols[j][i]));
+        wj = orc_gl_mul(wj, mu);
+    }
+    for (uint32_t t = 0; t < T; t++) orc_build_eq(pts + (size_t)t * v, v, E + (size_t)t * N);
+    /* reduction sumcheck over all points at once */
+    uint64_t* rstar = (uint64_t*)malloc(((size_t)v + 1) * 8);
+    for (uint32_t rd = 0; rd < v; rd++) {
+        size_t L = N >> rd, half = L / 2;
+        uint64_t s0 = 0, s1 = 0, s2 = 0;
+        for (uint32_t t = 0; t < T; t++) {
+            const uint64_t* c = G + (size_t)t * L;   /* bound arrays stay packed per point */
+            const uint64_t* w = E + (size_t)t * L;
+            for (size_t i = 0; i < half; i++) {
+                uint64_t cl = c[2 * i], ch = c[2 * i + 1], wl = w[2 * i], wh = w[2 * i + 1];
+                s0 = orc_gl_add(s0, orc_gl_mul(cl, wl));
+                s1 = orc_gl_add(s1, orc_gl_mul(ch, wh));
+                s2 = orc_gl_add(s2, orc_gl_mul(orc_gl_sub(orc_gl_add(ch, ch), cl),
+                                               orc_gl_sub(orc_gl_add(wh, wh), wl)));
+            }
+        }
+        uint64_t m[3] = {s0, s1, s2};
+        memcpy(p_rmsgs + (size_t)rd * 24, m, 24);
+        orc_tr_absorb(st, "bo-rm", m, 24);
+        uint64_t a = orc_tr_chal(st);
+        rstar[rd] = a;
+        /* the stacked arrays bind as one array: pairs never cross a point (L is even) */
+        orc_bind_lsb(G, (size_t)T * L, a);
+        orc_bind_lsb(E, (size_t)T * L, a);
+    }
+    free(G); free(E);
+    /* per-column terminal evaluations */
+    uint64_t* eqr = (uint64_t*)malloc(N * 8);
+    orc_build_eq(rstar, v, eqr);
+    uint64_t* ystar = (uint64_t*)malloc(((size_t)nc + 1) * 8);
+    for (uint32_t c = 0; c < nc; c++) ystar[c] = orc_eval_h(cols[first[c]], eqr, N);
+    memcpy(p_ystar, ystar, (size_t)nc * 8);
+    orc_tr_absorb(st, "bo-ys", ystar, (uint64_t)nc * 8);
+    uint64_t rho = orc_tr_chal(st);
+    uint64_t* U = (uint64_t*)calloc(N, 8);
+    uint64_t yU = 0, w = 1;
+    for (uint32_t c = 0; c < nc; c++) {
+        const uint64_t* col = cols[first[c]];
+        for (size_t i = 0; i < N; i++) U[i] = orc_gl_add(U[i], orc_gl_mul(w, col[i]));
+        yU = orc_gl_add(yU, orc_gl_mul(w, ystar[c]));
+        w = orc_gl_mul(w, rho);
+    }
+    /* opening of U at r* on its own transcript; round 0 carries no root */
+    uint8_t ot[32];
+    orc_tr_init(ot, label, strlen(label));
+    orc_tr_absorb(ot, "z", rstar, (uint64_t)v * 8);
+    orc_tr_absorb(ot, "y", &yU, 8);
+    uint64_t** words = (uint64_t**)calloc(v + 1, sizeof(uint64_t*));
+    uint8_t** trees = (uint8_t**)calloc(v + 1, sizeof(uint8_t*));
+    words[0] = (uint64_t*)malloc(M0 * 8);
+    orc_rs_encode(U, v, R, words[0]);
+    for (uint32_t r = 0; r < v; r++) {
+        size_t Mr = M0 >> r, n = N >> r, half = n / 2;
+        if (r > 0) {
+            trees[r] = (uint8_t*)malloc((2 * Mr - 1) * 32);
+            orc_merkle_build(words[r], Mr, trees[r]);
+            const uint8_t* root = trees[r] + (2 * Mr - 2) * 32;
+            memcpy(p_roots + (size_t)(r - 1) * 32, root, 32);
+            orc_tr_absorb(ot, "root", root, 32);
+        }
+        uint64_t s0 = 0, s1 = 0, s2 = 0;
+        for (size_t b = 0; b < half; b++) {
+            uint64_t cl = U[2 * b], ch = U[2 * b + 1], wl = eqr[2 * b], wh = eqr[2 * b + 1];
+            s0 = orc_gl_add(s0, orc_gl_mul(cl, wl));
+            s1 = orc_gl_add(s1, orc_gl_mul(ch, wh));
+            s2 = orc_gl_add(s2, orc_gl_mul(orc_gl_sub(orc_gl_add(ch, ch), cl), orc_gl_sub(orc_gl_add(wh, wh), wl)));
+        }
+        uint64_t m[3] = {s0, s1, s2};
+        memcpy(p_omsgs + (size_t)r * 24, m, 24);
+        orc_tr_absorb(ot, "sc", m, 24);
+        uint64_t a = orc_tr_chal(ot);
+        orc_bind_lsb(U, n, a);
+        orc_bind_lsb(eqr, n, a);
+        words[r + 1] = (uint64_t*)malloc((Mr / 2) * 8);
+        orc_fold(words[r], Mr, orc_gl_root_of_unity(logM0 - r), a, 1, words[r + 1]);
+    }
+    size_t fin = (size_t)1 << R;
+    memcpy(p_final, words[v], fin * 8);
+    orc_tr_absorb(ot, "final", words[v], fin * 8);
+    uint32_t* pos0 = (uint32_t*)malloc(((size_t)Q + 1) * 4);
+    for (uint32_t q = 0; q < Q; q++) {
+        size_t pos = (size_t)orc_tr_idx(ot, M0 / 2);
+        for (uint32_t r = 0; r < v; r++) {
+            size_t Mr = M0 >> r, h = Mr / 2, ci = pos % h;
+            if (r == 0) pos0[q] = (uint32_t)ci;
+            else {
+                uint32_t plen = logM0 - r;
+                put64(&p, words[r][ci]);
+                put64(&p, words[r][ci + h]);
+                orc_merkle_path(trees[r], Mr, ci, p); p += (size_t)plen * 32;
+                orc_merkle_path(trees[r], Mr, ci + h, p); p += (size_t)plen * 32;
+            }
+            pos = ci;
+        }
+    }
+    /* round-0 openings per distinct column against its own commitment */
+    uint32_t* upos = (uint32_t*)malloc(((size_t)2 * Q + 1) * 4);
+    uint32_t nu = 0;
+    for (uint32_t q = 0; q < Q; q++) { upos[nu++] = pos0[q]; upos[nu++] = pos0[q] + (uint32_t)(M0 / 2); }
+    qsort(upos, nu, 4, cmp_u32);
+    { uint32_t w2 = 0; for (uint32_t i = 0; i < nu; i++) if (!i || upos[i] != upos[i - 1]) upos[w2++] = upos[i]; nu = w2; }
+    uint64_t* cwc = (uint64_t*)malloc(M0 * 8);
+    uint8_t* treec = (uint8_t*)malloc((2 * M0 - 1) * 32);
+    for (uint32_t c = 0; c < nc; c++) {
+        orc_rs_encode(cols[first[c]], v, R, cwc);
+        orc_merkle_build(cwc, M0, treec);
+        put32(&p, nu);
+        for (uint32_t i = 0; i < nu; i++) put64(&p, cwc[upos[i]]);
+        uint8_t* p_cnt = p; p += 4;
+        uint32_t nn = (uint32_t)subset_nodes(logM0, upos, nu, treec, M0, p);
+        memcpy(p_cnt, &nn, 4);
+        p += (size_t)nn * 32;
+    }
+    free(cwc); free(treec); free(upos); free(pos0);
+    for (uint32_t r = 0; r <= v; r++) { free(words[r]); free(trees[r]); }
+    free(words); free(trees); free(U); free(eqr); free(ystar); free(rstar); free(colidx); free(first);
+    return (size_t)(p - out);
+}
+
+/* subset_verify: zkllm-src/p3_batchopen.cuh:108-135 */
+static int subset_verify(uint32_t logM, const uint32_t* upos, uint32_t nu, const uint8_t* leaves,
+                         const uint8_t* nodes, uint32_t nnodes, const uint8_t root[32]) {
+    uint32_t* fi = (uint32_t*)malloc((size_t)nu * 4);
+    uint8_t* fh = (uint8_t*)malloc((size_t)nu * 32);
+    memcpy(fi, upos, (size_t)nu * 4);
+    memcpy(fh, leaves, (size_t)nu * 32);
+    uint32_t nf = nu, ni = 0;
+    int ok = 1;
+    for (uint32_t l = 0; l < logM && ok; l++) {
+        uint32_t w = 0, i = 0;
+        while (i < nf) {
+            uint32_t idx = fi[i];
+            uint8_t h[32];
+            if (!(idx & 1) && i + 1 < nf && fi[i + 1] == (idx | 1)) {
+                orc_node_hash(fh + (size_t)i * 32, fh + (size_t)(i + 1) * 32, h);
+                i += 2;
+            } else {
+                if (ni >= nnodes) { ok = 0; break; }
+                const uint8_t* sib = nodes + (size_t)ni++ * 32;
+                if (idx & 1) orc_node_hash(sib, fh + (size_t)i * 32, h);
+                else orc_node_hash(fh + (size_t)i * 32, sib, h);
+                i += 1;
+            }
+            fi[w] = idx >> 1;
+            memcpy(fh + (size_t)w * 32, h, 32);
+            w++;
+        }
+        nf = w;
+    }
+    ok = ok && ni == nnodes && nf == 1 && !memcmp(fh, root, 32);
+    free(fi); free(fh);
+    return ok;
+}
+/* zkllm-src/p3_batchopen.cuh:1149-1302 (verify_class), non-zk.  1 = accept */
+int orc_bo_verify_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T, const uint8_t* roots,
+                        const uint32_t* zid, const uint64_t* y, uint32_t k, uint32_t R, uint32_t Q,
+                        const char* label, const uint8_t* proof, size_t len) {
+    const uint32_t logM0 = v + R;
+    const size_t M0 = (size_t)1 << logM0, fin = (size_t)1 << R;
+    if (len < 16) return 0;
+    uint32_t hv, hR, hQ, hnc;
+    memcpy(&hv, proof, 4); memcpy(&hR, proof + 4, 4); memcpy(&hQ, proof + 8, 4); memcpy(&hnc, proof + 12, 4);
+    if (hv != v || hR != R || hQ != Q) return 0;
+    uint32_t* colidx = (uint32_t*)malloc((size_t)k * 4);
+    uint32_t* first = (uint32_t*)malloc((size_t)k * 4);
+    const uint32_t nc = dedupe_roots(roots, k, colidx, first);
+    int ok = hnc == nc;
+    size_t fixed = 16 + (size_t)nc * 8 + (size_t)v * 48 + (size_t)(v ? v - 1 : 0) * 32 + fin * 8;
+    for (uint32_t r = 1; r < v; r++) fixed += (size_t)Q * (16 + 2 * (size_t)(logM0 - r) * 32);
+    if (!ok || len < fixed) { free(colidx); free(first); return 0; }
+    const uint8_t* p = proof + 16;
+    const uint64_t* ystar = (const uint64_t*)(const void*)p;  p += (size_t)nc * 8;
+    const uint8_t* rmsgs = p;  p += (size_t)v * 24;
+    const uint8_t* proots = p; p += (size_t)(v ? v - 1 : 0) * 32;
+    const uint8_t* omsgs = p;  p += (size_t)v * 24;
+    const uint8_t* fw = p;     p += fin * 8;
+    const uint8_t* qsec = p;
+    uint64_t* ys = (uint64_t*)malloc(((size_t)nc + 1) * 8);
+    memcpy(ys, ystar, (size_t)nc * 8);
+    uint64_t* final_word = (uint64_t*)malloc(fin * 8);
+    memcpy(final_word, fw, fin * 8);
+
+    uint64_t mu = orc_tr_chal(st);
+    uint64_t claim = 0, wj = 1;
+    for (uint32_t j = 0; j < k; j++) { claim = orc_gl_add(claim, orc_gl_mul(wj, y[j])); wj = orc_gl_mul(wj, mu); }
+    uint64_t* rstar = (uint64_t*)malloc(((size_t)v + 1) * 8);
+    uint64_t* al = (uint64_t*)malloc(((size_t)v + 1) * 8);
+    for (uint32_t rd = 0; rd < v; rd++) {
+        uint64_t m[3]; memcpy(m, rmsgs + (size_t)rd * 24, 24);
+        if (orc_gl_add(m[0], m[1]) != claim) ok = 0;
+        orc_tr_absorb(st, "bo-rm", m, 24);
+        rstar[rd] = orc_tr_chal(st);
+        claim = orc_quad_eval(m[0], m[1], m[2], rstar[rd]);
+    }
+    orc_tr_absorb(st, "bo-ys", ys, (uint64_t)nc * 8);
+    {
+        uint64_t* gt = (uint64_t*)calloc(T, 8);
+        wj = 1;
+        for (uint32_t j = 0; j < k; j++) {
+            gt[zid[j]] = orc_gl_add(gt[zid[j]], orc_gl_mul(wj, ys[colidx[j]]));
+            wj = orc_gl_mul(wj, mu);
+        }
+        uint64_t end = 0;
+        for (uint32_t t = 0; t < T; t++)
+            end = orc_gl_add(end, orc_gl_mul(orc_eq_point(rstar, pts + (size_t)t * v, v), gt[t]));
+        if (end != claim) ok = 0;
+        free(gt);
+    }
+    uint64_t rho = orc_tr_chal(st);
+    uint64_t* rhop = (uint64_t*)malloc(((size_t)nc + 1) * 8);
+    uint64_t yU = 0, wc = 1;
+    for (uint32_t c = 0; c < nc; c++) { rhop[c] = wc; yU = orc_gl_add(yU, orc_gl_mul(wc, ys[c])); wc = orc_gl_mul(wc, rho); }
+    uint8_t ot[32];
+    orc_tr_init(ot, label, strlen(label));
+    orc_tr_absorb(ot, "z", rstar, (uint64_t)v * 8);
+    orc_tr_absorb(ot, "y", &yU, 8);
+    uint64_t oclaim = yU;
+    for (uint32_t r = 0; r < v; r++) {
+        if (r > 0) orc_tr_absorb(ot, "root", proots + (size_t)(r - 1) * 32, 32);
+        uint64_t m[3]; memcpy(m, omsgs + (size_t)r * 24, 24);
+        if (orc_gl_add(m[0], m[1]) != oclaim) ok = 0;
+        orc_tr_absorb(ot, "sc", m, 24);
+        al[r] = orc_tr_chal(ot);
+        oclaim = orc_quad_eval(m[0], m[1], m[2], al[r]);
+    }
+    orc_tr_absorb(ot, "final", final_word, fin * 8);
+    for (size_t i = 1; i < fin; i++) if (final_word[i] != final_word[0]) ok = 0;
+    if (oclaim != orc_gl_mul(final_word[0], orc_eq_point(al, rstar, v))) ok = 0;
+    uint32_t* c0q = (uint32_t*)malloc(((size_t)Q + 1) * 4);
+    uint32_t* upos = (uint32_t*)malloc(((size_t)2 * Q + 1) * 4);
+    uint32_t nu = 0;
+    for (uint32_t q = 0; q < Q; q++) {
+        c0q[q] = (uint32_t)orc_tr_idx(ot, M0 / 2);
+        upos[nu++] = c0q[q]; upos[nu++] = c0q[q] + (uint32_t)(M0 / 2);
+    }
+    qsort(upos, nu, 4, cmp_u32);
+    { uint32_t w2 = 0; for (uint32_t i = 0; i < nu; i++) if (!i || upos[i] != upos[i - 1]) upos[w2++] = upos[i]; nu = w2; }
+    /* locate the per-column sections */
+    const uint8_t* q0 = qsec;
+    for (uint32_t r = 1; r < v; r++) q0 += (size_t)Q * (16 + 2 * (size_t)(logM0 - r) * 32);
+    const uint8_t** cvals = (const uint8_t**)calloc(nc + 1, sizeof(uint8_t*));
+    const uint8_t* cp = q0;
+    uint8_t* leaves = (uint8_t*)malloc(((size_t)nu + 1) * 32);
+    for (uint32_t c = 0; c < nc && ok; c++) {
+        if ((size_t)(cp - proof) + 4 > len) { ok = 0; break; }
+        uint32_t nv; memcpy(&nv, cp, 4); cp += 4;
+        if (nv != nu || (size_t)(cp - proof) + (size_t)nv * 8 + 4 > len) { ok = 0; break; }
+        cvals[c] = cp; cp += (size_t)nv * 8;
+        uint32_t nn; memcpy(&nn, cp, 4); cp += 4;
+        if ((size_t)(cp - proof) + (size_t)nn * 32 > len) { ok = 0; break; }
+        for (uint32_t i = 0; i < nu; i++) { uint64_t x; memcpy(&x, cvals[c] + (size_t)i * 8, 8); orc_leaf_hash(x, leaves + (size_t)i * 32); }
+        if (!subset_verify(logM0, upos, nu, leaves, cp, nn, roots + (size_t)first[c] * 32)) ok = 0;
+        cp += (size_t)nn * 32;
+    }
+    if (ok && (size_t)(cp - proof) != len) ok = 0;
+    const uint8_t* qp = qsec;
+    for (uint32_t q = 0; q < Q && ok; q++) {
+        size_t pos = c0q[q];
+        uint64_t prev = 0;
+        for (uint32_t r = 0; r < v; r++) {
+            size_t Mr = M0 >> r, h = Mr / 2, ci = pos % h;
+            uint32_t plen = logM0 - r;
+            uint64_t a = 0, b = 0;
+            if (r == 0) {
+                uint32_t key = (uint32_t)ci, sa, sb;
+                sa = (uint32_t)((uint32_t*)bsearch(&key, upos, nu, 4, cmp_u32) - upos);
+                key = (uint32_t)(ci + h);
+                sb = (uint32_t)((uint32_t*)bsearch(&key, upos, nu, 4, cmp_u32) - upos);
+                for (uint32_t c = 0; c < nc; c++) {
+                    uint64_t va, vb;
+                    memcpy(&va, cvals[c] + (size_t)sa * 8, 8); memcpy(&vb, cvals[c] + (size_t)sb * 8, 8);
+                    a = orc_gl_add(a, orc_gl_mul(rhop[c], va));
+                    b = orc_gl_add(b, orc_gl_mul(rhop[c], vb));
+                }
+            } else {
+                memcpy(&a, qp, 8); memcpy(&b, qp + 8, 8); qp += 16;
+                const uint8_t* pa = qp; qp += (size_t)plen * 32;
+                const uint8_t* pb = qp; qp += (size_t)plen * 32;
+                uint8_t lh[32];
+                orc_leaf_hash(a, lh);
+                if (!orc_merkle_verify_path(lh, ci, pa, plen, proots + (size_t)(r - 1) * 32)) ok = 0;
+                orc_leaf_hash(b, lh);
+                if (!orc_merkle_verify_path(lh, ci + h, pb, plen, proots + (size_t)(r - 1) * 32)) ok = 0;
+                uint64_t val = pos < h ? a : b;
+                if (val != prev) ok = 0;
+            }
+            uint64_t x = orc_gl_pow(orc_gl_root_of_unity(plen), ci);
+            prev = orc_fold_pair(a, b, orc_gl_inv(x), al[r], 1);
+            if (r + 1 == v && final_word[ci] != prev) ok = 0;
+            pos = ci;
+        }
+    }
+    free(colidx); free(first); free(ys); free(final_word); free(rstar); free(al); free(rhop); free(c0q); free(upos);
+    free(cvals); free(leaves);
+    return ok;
+}

@@ -117,6 +117,18 @@ size_t orc_gkr_prove(uint8_t st[32], const char* tag, const uint64_t* p, const u
 int orc_gkr_verify(uint8_t st[32], const char* tag, uint32_t L, const uint8_t* proof,
                    size_t len, int combine_last, uint64_t* rfin, uint64_t out4[4]);
 
+/* ---- batched opening of one size class, non-zk: zkllm-src/p3_batchopen.cuh:307-1302 ----
+ * Ledger: k entries (column values, commitment root, point index zid, claimed value y), T points
+ * of v coordinates.  Entries with equal roots are the same column.  st = main transcript.
+ * Serialized BatchProof: see zkh_oracle.c. */
+size_t orc_bo_proof_bound(uint32_t v, uint32_t R, uint32_t Q, uint32_t nc);
+size_t orc_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
+                          const uint64_t* const* cols, const uint8_t* roots, const uint32_t* zid, uint32_t k,
+                          uint32_t R, uint32_t Q, const char* label, uint8_t* out, size_t cap);
+int orc_bo_verify_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T, const uint8_t* roots,
+                        const uint32_t* zid, const uint64_t* y, uint32_t k, uint32_t R, uint32_t Q,
+                        const char* label, const uint8_t* proof, size_t len);
+
 /* ---- logUp primitives: zkllm-src/p3_logup.cuh:149-172, 636-672 ---- */
 int  orc_histogram(const uint32_t* idx, size_t n, uint32_t M, uint64_t* cnt); /* -1 on oob */
 int  orc_inv_all_add(const uint64_t* A, size_t n, uint64_t beta, uint64_t* out); /* -1 on zero */

@@ -147,6 +147,34 @@ def main():
     g["logup"] = {"seed": seed + 400, "n": 70000, "beta": beta, "inv_digest": dig(ref.inv_all_add(A, beta)),
                   "combine_digest": dig(ref.combine([A, A[::-1].copy()], beta))}
 
+    # ---- batched opening: the reference's prover needs a GPU, its verifier does not.  The vectors
+    # are the restatement's proofs, recorded only after the REFERENCE verifier accepted them and
+    # rejected a tampered copy (the accepted transcript state is recorded too).
+    bo = []
+    for v, R, Q, ncols, T, k in [(3, 1, 24, 2, 2, 3), (6, 2, 24, 5, 3, 9), (8, 1, 32, 4, 4, 7)]:
+        s = seed + 500 + v
+        cols = []
+        for _ in range(ncols):
+            a, s = lcg(1 << v, s)
+            cols.append(a)
+        pts, s = lcg(T * v, s)
+        pts = pts.reshape(T, v)
+        ent_col = [(3 * j + 1) % ncols for j in range(k)]
+        zid = [(5 * j + 2) % T for j in range(k)]
+        roots_c = [ref.merkle_root(ref.rs_encode_horner(c, R)) for c in cols]
+        roots = [roots_c[c] for c in ent_col]
+        y = [ref.eval_h(cols[c], ref.build_eq(pts[t])) for c, t in zip(ent_col, zid)]
+        st0 = ref.tr_init("bo-golden")
+        pf, st1 = orc.bo_prove_class(st0, pts, [cols[c] for c in ent_col], roots, zid, R, Q, "tf-bo0")
+        ok, st2 = ref.bo_verify_class(st0, pts, roots, zid, y, R, Q, "tf-bo0", pf)
+        assert ok and st2 == st1
+        bad = bytearray(pf); bad[20] ^= 1
+        assert not ref.bo_verify_class(st0, pts, roots, zid, y, R, Q, "tf-bo0", bytes(bad))[0]
+        bo.append({"seed": seed + 500 + v, "v": v, "R": R, "Q": Q, "ncols": ncols, "T": T, "k": k,
+                   "ent_col": ent_col, "zid": zid, "y": y, "state": st1.hex(), "proof_digest": dig(pf),
+                   "proof_len": len(pf), "accepted_by": "p3bo::verify_class (reference, host)"})
+    g["batchopen"] = bo
+
     with open(OUT, "w") as f:
         json.dump(g, f, indent=1)
     print("wrote", OUT, os.path.getsize(OUT), "bytes")

@@ -148,6 +148,34 @@ def test_logup_primitives(golden, orc):
         orc.inv_all_add(np.array([5, 7], dtype=np.uint64), GL_P - 7)
 
 
+def _bo_inputs(orc, b):
+    s, cols = b["seed"], []
+    for _ in range(b["ncols"]):
+        a, s = orc.lcg(1 << b["v"], s)
+        cols.append(a)
+    pts, s = orc.lcg(b["T"] * b["v"], s)
+    return cols, pts.reshape(b["T"], b["v"])
+
+
+def test_batchopen(golden, orc, ref_or_none):
+    for b in golden["batchopen"]:
+        v, R, Q = b["v"], b["R"], b["Q"]
+        cols, pts = _bo_inputs(orc, b)
+        roots_c = [orc.merkle_root(orc.rs_encode(c, R)) for c in cols]
+        roots = [roots_c[c] for c in b["ent_col"]]
+        st0 = orc.tr_init("bo-golden")
+        pf, st1 = orc.bo_prove_class(st0, pts, [cols[c] for c in b["ent_col"]], roots, b["zid"], R, Q, "tf-bo0")
+        assert dig(pf) == b["proof_digest"] and len(pf) == b["proof_len"] and st1.hex() == b["state"]
+        assert b["y"] == [orc.mle_eval(cols[c], pts[t]) for c, t in zip(b["ent_col"], b["zid"])]
+        for verifier in [orc] + ([ref_or_none] if ref_or_none else []):
+            ok, st2 = verifier.bo_verify_class(st0, pts, roots, b["zid"], b["y"], R, Q, "tf-bo0", pf)
+            assert ok and st2 == st1
+            for off in (16, len(pf) // 3, len(pf) - 7):
+                bad = bytearray(pf)
+                bad[off] ^= 1
+                assert not verifier.bo_verify_class(st0, pts, roots, b["zid"], b["y"], R, Q, "tf-bo0", bytes(bad))[0]
+
+
 def test_oracle_equals_reference_live(orc, ref):
     """Where the reference shim is built (it needs the reference tree), compare directly on fresh inputs."""
     rng = np.random.default_rng(5)

@@ -241,6 +241,25 @@ class Prover:
                                            out.ctypes.data, cap, C.byref(wr)))
         return out.tobytes()[:wr.value]
 
+    def prove_class(self, tr, pts, ents, R, Q, label):
+        """p3bo::prove_class (zkllm-src/p3_batchopen.cuh:307-1147), non-zk.  pts: T x v points;
+        ents: ledger entries (device column, 32-byte root, point index) in insertion order.
+        ``tr`` (the main transcript) advances as in the reference.  Returns the serialised BatchProof."""
+        pts = np.ascontiguousarray(pts, dtype=np.uint64)
+        T, v = pts.shape
+        k = len(ents)
+        ptrs = (C.c_uint64 * k)(*[_ptr(e[0]) for e in ents])
+        roots = b"".join(bytes(e[1]) for e in ents)
+        zid = np.ascontiguousarray([e[2] for e in ents], dtype=np.uint32)
+        cap = self._L.zkh_batchopen_proof_bound(v, R, Q, k)
+        out = np.zeros(cap, dtype=np.uint8)
+        wr = C.c_size_t(0)
+        st = _buf32(tr.state)
+        self._ck(self._L.zkh_batchopen_prove_class(self._h, v, pts.ctypes.data, T, ptrs, roots, zid.ctypes.data, k,
+                                                   R, Q, label.encode(), st, out.ctypes.data, cap, C.byref(wr)))
+        tr.state = bytes(st)
+        return out.tobytes()[:wr.value]
+
     # ---- logUp / GKR ----
     def histogram(self, idx_dev, M):
         """p3lu_cnts/cntg_kernel (zkllm-src/p3_logup.cuh:149-172): 64-bit multiplicities of uint32 indices
