@@ -220,6 +220,10 @@ ZKH_API int zkh_gl_inv_all_add(zkh_ctx* ctx, const uint64_t* A_dev, uint64_t n, 
 /* out[i] = sum_k g^k * cols[k][i] (zkllm-src/p3_logup.cuh:663-672 combine).  Stream-ordered. */
 ZKH_API int zkh_gl_combine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
                            uint64_t* out_dev);
+/* out[i] = addend + sum_k g^k * cols[k][i]: the gamma-combination with the logUp shift folded in
+ * (leaf denominators A_i + beta of zkllm-src/p3_logup.cuh:1645-1647, :1788-1789).  Stream-ordered. */
+ZKH_API int zkh_gl_affine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
+                          uint64_t addend, uint64_t* out_dev);
 /* GKR fractional-sum tree prover (zkllm-src/p3_gkr.cuh:200-364 p3gkr::prove / prove_dev).
  * p_dev, q_dev: 2^L leaf numerators / denominators (left untouched, unlike prove_dev which
  * takes ownership).  state: transcript in/out.  rfin: L values (combine_last) or L-1.

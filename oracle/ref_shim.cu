@@ -188,6 +188,65 @@ bool bo_deserialize(const uint8_t* in, size_t len, p3bo::BatchProof& pf) {
     }
     return p == end;
 }
+// GroupProof (merged lookup, non-zk) <-> bytes:
+//   u32 m, c, ns | root_cnt 32 | gkT | per subgroup: u32 n, k | gk | per member: u32 nW, yW.., u32 nV, yv.., u32 nX, extra..
+size_t lu_serialize(const p3lu::GroupProof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    auto appg = [&](const p3gkr::Proof& g) {
+        std::vector<uint8_t> t(gkr_size((uint32_t)g.lay.size()));
+        gkr_serialize(g, t.data(), t.size());
+        app(t.data(), t.size());
+    };
+    uint32_t ns = (uint32_t)pf.sub.size();
+    app(&pf.m, 4); app(&pf.c, 4); app(&ns, 4); app(pf.root_cnt.data(), 32);
+    appg(pf.gkT);
+    for (auto& sb : pf.sub) {
+        app(&sb.n, 4); app(&sb.k, 4);
+        appg(sb.gk);
+        for (auto& mm : sb.mem) {
+            uint32_t a = (uint32_t)mm.yW.size(), v = (uint32_t)mm.y_virt.size(), x = (uint32_t)mm.extra.size();
+            app(&a, 4); app(mm.yW.data(), (size_t)a * 8);
+            app(&v, 4); app(mm.y_virt.data(), (size_t)v * 8);
+            app(&x, 4); app(mm.extra.data(), (size_t)x * 8);
+        }
+    }
+    if (b.size() > cap) return 0;
+    memcpy(out, b.data(), b.size());
+    return b.size();
+}
+bool lu_deserialize(const uint8_t* in, size_t len, p3lu::GroupProof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
+    uint32_t ns;
+    if (!need(44)) return false;
+    memcpy(&pf.m, p, 4); memcpy(&pf.c, p + 4, 4); memcpy(&ns, p + 8, 4); memcpy(pf.root_cnt.data(), p + 12, 32); p += 44;
+    if (pf.m > 40 || ns > 4096) return false;
+    if (!need(gkr_size(pf.m)) || !gkr_deserialize(p, gkr_size(pf.m), pf.m, pf.gkT)) return false;
+    p += gkr_size(pf.m);
+    pf.sub.resize(ns);
+    for (auto& sb : pf.sub) {
+        if (!need(8)) return false;
+        memcpy(&sb.n, p, 4); memcpy(&sb.k, p + 4, 4); p += 8;
+        if (sb.n > 40 || sb.k == 0 || sb.k > 4096) return false;
+        uint32_t g = 0; while ((1u << g) < sb.k) g++;
+        uint32_t L = sb.n + g;
+        if (!need(gkr_size(L)) || !gkr_deserialize(p, gkr_size(L), L, sb.gk)) return false;
+        p += gkr_size(L);
+        sb.mem.resize(sb.k);
+        for (auto& mm : sb.mem) {
+            std::vector<gl_t>* vs[3] = {&mm.yW, &mm.y_virt, &mm.extra};
+            for (auto* v : vs) {
+                uint32_t a;
+                if (!need(4)) return false;
+                memcpy(&a, p, 4); p += 4;
+                if (a > 4096 || !need((size_t)a * 8)) return false;
+                v->resize(a); memcpy(v->data(), p, (size_t)a * 8); p += (size_t)a * 8;
+            }
+        }
+    }
+    return p == end;
+}
 struct FProd2 { static __device__ gl_t eval(const gl_t* c, const gl_t*) { return gl_mul(c[0], c[1]); } };
 struct M3 { gl_t s[3]; };
 struct M4 { gl_t s[4]; };
@@ -394,6 +453,58 @@ int ref_bo_verify_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_
     return ok ? 1 : 0;
 }
 
+// ---- merged lookup: the reference's host-only verifier (p3_logup.cuh:1958-2086 verify_super) ----
+// Members are listed in flush order, subgroup after subgroup (K = sum of sub_k); wit_committed[j*c+t]
+// tells whether column t of member j is a committed column (its root at wit_roots) or virtual.
+// The verifier's opening-ledger additions come back in insertion order.
+int ref_lu_verify_super(uint8_t st[32], const uint64_t* const* tcols, uint32_t m, uint32_t c, uint32_t ns,
+                        const uint32_t* sub_n, const uint32_t* sub_k, const uint8_t* wit_roots,
+                        const uint8_t* wit_committed, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len,
+                        uint32_t* n_claims, uint8_t* claim_roots, uint32_t* claim_vlen, uint64_t* claim_pts,
+                        uint64_t* claim_y, uint32_t max_claims) {
+    p3lu::GroupProof pf;
+    if (!lu_deserialize(proof, len, pf)) return 0;
+    std::vector<std::vector<gl_t>> cols(c);
+    for (uint32_t t = 0; t < c; t++) cols[t].assign(tcols[t], tcols[t] + ((size_t)1 << m));
+    p3lu::Table T = p3lu::make_table(cols);
+    uint32_t K = 0;
+    for (uint32_t s = 0; s < ns; s++) K += sub_k[s];
+    std::vector<p3fri::Hash> roots((size_t)K * c);
+    for (size_t i = 0; i < roots.size(); i++) memcpy(roots[i].data(), wit_roots + i * 32, 32);
+    p3lu::VCtx V;
+    std::vector<std::vector<size_t>> smi(ns);
+    std::vector<uint32_t> sns(sub_n, sub_n + ns);
+    size_t j = 0;
+    for (uint32_t s = 0; s < ns; s++)
+        for (uint32_t i = 0; i < sub_k[s]; i++, j++) {
+            std::vector<const p3fri::Hash*> rp(c);
+            for (uint32_t t = 0; t < c; t++) rp[t] = wit_committed[j * c + t] ? &roots[j * c + t] : nullptr;
+            p3lu::vdefer_v(V, rp, T, sub_n[s], "m");
+            smi[s].push_back(j);
+        }
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3lu::verify_super(tr, V, smi, sns, pf, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    if (!ok) return 0;
+    uint32_t nc = 0;
+    for (auto& cl : V.vlg.cls)
+        for (auto& e : cl.ents) (void)e, nc++;
+    // ledger classes are keyed by size; return entries class by class, in class creation order
+    uint32_t w = 0;
+    for (auto& cl : V.vlg.cls)
+        for (auto& e : cl.ents) {
+            if (w >= max_claims) return 0;
+            memcpy(claim_roots + (size_t)w * 32, e.root.data(), 32);
+            claim_vlen[w] = cl.v;
+            memcpy(claim_pts + (size_t)w * 64, cl.pts[e.zid].data(), (size_t)cl.v * 8);
+            claim_y[w] = e.y;
+            w++;
+        }
+    *n_claims = w;
+    return 1;
+}
+
 // =====================================================================
 // GPU entry points: the reference's own CUDA paths (need a GPU).
 // =====================================================================
@@ -496,6 +607,53 @@ size_t ref_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint3
         cudaDeviceSynchronize();
         if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
         n = bo_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+// p3lu::prove_super (GPU): all columns committed (roots given), host values; idx per member
+size_t ref_lu_prove_super(uint8_t st[32], const uint64_t* const* tcols, uint32_t m, uint32_t c, uint32_t ns,
+                          const uint32_t* sub_n, const uint32_t* sub_k, const uint64_t* const* wit_cols,
+                          const uint8_t* wit_roots, const uint32_t* const* idx, uint32_t R, uint32_t Q,
+                          uint8_t* out, size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    std::vector<std::vector<gl_t>> cols(c);
+    for (uint32_t t = 0; t < c; t++) cols[t].assign(tcols[t], tcols[t] + ((size_t)1 << m));
+    p3lu::Table T = p3lu::make_table(cols);
+    uint32_t K = 0;
+    for (uint32_t s = 0; s < ns; s++) K += sub_k[s];
+    std::vector<p3lu::Col> wc((size_t)K * c);
+    std::vector<std::vector<uint32_t>> ix(K);
+    p3lu::XCtx xc;
+    std::vector<std::vector<size_t>> smi(ns);
+    std::vector<uint32_t> sns(sub_n, sub_n + ns);
+    size_t j = 0;
+    for (uint32_t s = 0; s < ns; s++)
+        for (uint32_t i = 0; i < sub_k[s]; i++, j++) {
+            size_t N = (size_t)1 << sub_n[s];
+            std::vector<p3lu::LuColSpec> W;
+            for (uint32_t t = 0; t < c; t++) {
+                p3lu::Col& col = wc[j * c + t];
+                col.v.assign(wit_cols[j * c + t], wit_cols[j * c + t] + N);
+                memcpy(col.root.data(), wit_roots + (j * c + t) * 32, 32);
+                col.vreal = sub_n[s];
+                W.push_back(p3lu::LC(&col));
+            }
+            ix[j].assign(idx[j], idx[j] + N);
+            p3lu::defer_v(xc, W, ix[j], T, "m");
+            smi[s].push_back(j);
+        }
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        auto pf = p3lu::prove_super(tr, xc, smi, sns, R, Q, true, true);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = lu_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);

@@ -66,12 +66,13 @@ inv_add_kernel(const gl_t* __restrict__ A, gl_t* __restrict__ out, size_t n, gl_
     }
 }
 
-struct CombCols { const gl_t* col[8]; gl_t gk[8]; int c; };
+struct CombCols { const gl_t* col[8]; gl_t gk[8]; int c; gl_t addend; };
 __global__ void __launch_bounds__(256) combine_kernel(CombCols cc, gl_t* __restrict__ out, size_t n) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         Acc192 acc;
         acc.clear();
+        acc.add_val(cc.addend);
         for (int k = 0; k < cc.c; k++) acc.add_prod(cc.gk[k], cc.col[k][i]);
         out[i] = acc.reduce();
     }
@@ -125,16 +126,23 @@ extern "C" int zkh_gl_inv_all_add(zkh_ctx* c, const uint64_t* A_dev, uint64_t n,
     return ZKH_OK;
 }
 
+extern "C" int zkh_gl_affine(zkh_ctx* c, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
+                             uint64_t addend, uint64_t* out_dev);
 extern "C" int zkh_gl_combine(zkh_ctx* c, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
                               uint64_t* out_dev) {
+    return zkh_gl_affine(c, cols_dev, ncols, n, g, 0, out_dev);
+}
+extern "C" int zkh_gl_affine(zkh_ctx* c, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
+                             uint64_t addend, uint64_t* out_dev) {
     if (!c || !cols_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "combine: null pointer");
     if (ncols < 1 || ncols > 8) return zkh_fail(c, ZKH_ERR_LIMIT, "combine: 1..8 columns");
-    if (g >= GL_P) return zkh_fail(c, ZKH_ERR_ARG, "combine: gamma not canonical");
+    if (g >= GL_P || addend >= GL_P) return zkh_fail(c, ZKH_ERR_ARG, "combine: gamma / addend not canonical");
     if (!n) return ZKH_OK;
     ZKH_CUDA(c, cudaSetDevice(c->device));
     CombCols cc;
     memset(&cc, 0, sizeof cc);
     cc.c = ncols;
+    cc.addend = addend;
     gl_t gk = 1;
     for (int k = 0; k < ncols; k++) { cc.col[k] = cols_dev[k]; cc.gk[k] = gk; gk = gl_mul(gk, g); }
     size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 8;

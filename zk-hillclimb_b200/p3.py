@@ -162,6 +162,9 @@ class Prover:
         self._ck(self._L.zkh_gl_mle_eval(self._h, _ptr(c_dev), z.ctypes.data, len(z), C.byref(y)))
         return int(y.value)
 
+    def element(self, col_dev, i):
+        return int(to_host(col_dev[i:i + 1])[0])
+
     def bind(self, in_dev, a, out=None, n=None):
         import torch
         n = n if n is not None else in_dev.numel()
@@ -259,6 +262,45 @@ class Prover:
                                                    R, Q, label.encode(), st, out.ctypes.data, cap, C.byref(wr)))
         tr.state = bytes(st)
         return out.tobytes()[:wr.value]
+
+    # ---- engine interface used by prove_super ----
+    def lu_counts(self, idx_list, M, pad_rows):
+        """Multiplicity column of a merged lookup: histogram of all members' indices plus the
+        padding rows (which hold table row 0)."""
+        cnt = None
+        for idx in idx_list:
+            h = self.histogram(idx, M)
+            cnt = h if cnt is None else cnt + h
+        cnt[0] += pad_rows
+        return cnt
+
+    def lu_leaf_denominators(self, members, kp, n, gamma, shift, pad_value):
+        """LQ over the merged domain u = i | (j << n): member j < k holds shift + sum_t gamma^t W_jt[i],
+        pad members hold pad_value."""
+        import torch
+        N = 1 << n
+        out = torch.empty(kp << n, dtype=torch.int64, device="cuda:%d" % self.device)
+        for j in range(kp):
+            sl = out[j * N:(j + 1) * N]
+            if j < len(members):
+                nc = len(members[j])
+                ptrs = (C.c_uint64 * nc)(*[_ptr(t) for t in members[j]])
+                self._ck(self._L.zkh_gl_affine(self._h, ptrs, nc, N, gamma, shift, _ptr(sl)))
+            else:
+                sl.fill_(pad_value - (1 << 64) if pad_value >= (1 << 63) else pad_value)
+        return out
+
+    def lu_ones(self, n):
+        import torch
+        return torch.ones(n, dtype=torch.int64, device="cuda:%d" % self.device)
+
+    def affine(self, cols_dev, g, addend):
+        import torch
+        nc = len(cols_dev)
+        ptrs = (C.c_uint64 * nc)(*[_ptr(t) for t in cols_dev])
+        out = torch.empty_like(cols_dev[0])
+        self._ck(self._L.zkh_gl_affine(self._h, ptrs, nc, cols_dev[0].numel(), g, addend, _ptr(out)))
+        return out
 
     # ---- logUp / GKR ----
     def histogram(self, idx_dev, M):
@@ -413,3 +455,89 @@ def sc_prove_sharded(engine, tr, tag, dcols, functor, nt, dist=None, par=(), gro
     state, msgs, chals, finals = engine.shard_end(logn + k)
     tr.state = state
     return chals, msgs, finals
+
+
+def _ser_gkr_group(m, c, root_cnt, gkT, subs):
+    import struct
+    b = struct.pack("<III", m, c, len(subs)) + root_cnt + gkT
+    for n, k, gk, mem in subs:
+        b += struct.pack("<II", n, k) + gk
+        for yW, yv in mem:
+            b += struct.pack("<I", len(yW)) + np.array(yW, dtype=np.uint64).tobytes()
+            b += struct.pack("<I", len(yv)) + np.array(yv, dtype=np.uint64).tobytes()
+            b += struct.pack("<I", 0)
+    return b
+
+
+def prove_super(engine, tr, table_cols, table_id, subgroups, R, strict=True):
+    """p3lu::prove_super (zkllm-src/p3_logup.cuh:1357-1881), non-zk: ONE merged logUp instance for all
+    lookups into one table.
+
+    table_cols: c columns of 2^m rows (engine buffers); table_id: its 32-byte binding hash
+    (p3lu::make_table).  subgroups: list, in flush order, of (n, members); a member is
+    (cols, roots, idx) with c witness columns of 2^n rows, their commitment roots (None for a
+    virtual column) and the uint32 row indices into the table.
+    Returns (proof bytes, claims, cnt column).  claims = the opening-ledger additions in the
+    reference's order: (column, root, point, value) for every committed member column at the
+    subgroup's shared point, then the multiplicity column at the table-side point.
+    ``tr`` advances exactly as the reference's transcript."""
+    import struct
+    c = len(table_cols)
+    M = int(table_cols[0].numel())
+    m = M.bit_length() - 1
+    tr.absorb("lug-tab", table_id)
+    tr.absorb("lug-sdims", struct.pack("<III", len(subgroups), m, c))
+    pad_rows, idx_all = 0, []
+    for n, members in subgroups:
+        k = len(members)
+        g = (k - 1).bit_length()
+        tr.absorb("lug-dims", struct.pack("<IIII", n, g, k, c))
+        for cols, roots, idx in members:
+            if len(cols) != c or any(int(t.numel()) != (1 << n) for t in cols) or int(idx.numel()) != (1 << n):
+                raise ValueError("p3lu: group member size")
+            for r in roots:
+                if r is not None:
+                    tr.absorb("lug-W", r)
+                else:
+                    tr.absorb("lug-Wv", b"virt")
+            idx_all.append(idx)
+        pad_rows += ((1 << g) - k) << n
+    cnt = engine.lu_counts(idx_all, M, pad_rows)           # raises on an index outside the table
+    root_cnt = engine.commit_gpu_rootonly(cnt, R)
+    tr.absorb("lug-cnt", root_cnt)
+    gamma, beta = tr.chal(), tr.chal()
+    gp = [pow(gamma, t, GL_P) for t in range(c)]
+    row0 = [int(engine.element(col, 0)) for col in table_cols]
+    a0 = sum(g_ * r for g_, r in zip(gp, row0)) % GL_P
+    accP, accQ = 0, 1
+    subs, claims = [], []
+    for n, members in subgroups:
+        k = len(members)
+        g = (k - 1).bit_length()
+        LQ = engine.lu_leaf_denominators([mb[0] for mb in members], 1 << g, n, gamma, beta, (a0 + beta) % GL_P)
+        LP = engine.lu_ones(1 << (n + g))
+        gk, rA, _ = engine.gkr_prove(tr, "lug-gA", LP, LQ, True)
+        P, Q = (int(x) for x in np.frombuffer(gk[:16], dtype=np.uint64))
+        accP, accQ = (accP * Q + P * accQ) % GL_P, accQ * Q % GL_P
+        pm = np.array(rA[:n], dtype=np.uint64)
+        mem = []
+        for cols, roots, idx in members:
+            yW, yv = [], []
+            for col, r in zip(cols, roots):
+                y = engine.eval_h_gpu(col, pm)
+                if r is not None:
+                    yW.append(y)
+                    tr.absorb("lug-yW", struct.pack("<Q", y))
+                    claims.append((col, r, pm, y))
+                else:
+                    yv.append(y)
+                    tr.absorb("lug-yv", struct.pack("<Q", y))
+            mem.append((yW, yv))
+        subs.append((n, k, gk, mem))
+    LQT = engine.affine(table_cols, gamma, beta)
+    gkT, rT, (cpT, _cq) = engine.gkr_prove(tr, "lug-gT", cnt, LQT, True)
+    PT, QT = (int(x) for x in np.frombuffer(gkT[:16], dtype=np.uint64))
+    if strict and accP * QT % GL_P != PT * accQ % GL_P:
+        raise ValueError("p3lu: witness not in table")
+    claims.append((cnt, root_cnt, np.array(rT, dtype=np.uint64), cpT))
+    return _ser_gkr_group(m, c, root_cnt, gkT, subs), claims, cnt
