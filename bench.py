@@ -257,6 +257,119 @@ def run_suite(args):
     emit("GKR fractional-sum proof 2^24 leaves (A side)", ms, 48 << 24, extra)
 
 
+def run_suite_gadgets(args):
+    """--suite-gadgets: BASELINE configs[0] (int8 matmul proof, padded to powers of two) and configs[2]
+    (2^24 lookups into a 2^16-row table, c = 2) through the gadget-level provers, beside the
+    reference's own CUDA provers on the same inputs."""
+    import ctypes as C
+    import torch
+    import zkh_import
+    zk = zkh_import.load()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import Oracle, Reference
+    orc = Oracle()
+    torch.cuda.set_device(0)
+    prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+    ref = Reference() if (Reference.available() and not args.no_ref_cuda) else None
+    if ref is not None and not ref.gpu_available():
+        ref = None
+    if ref is not None:
+        ref.lib.ref_gpu_setup()
+    u64p, u32p = C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)
+    P = 0xFFFFFFFF00000001
+    R, Q = 1, 24
+
+    def wall(fn, reps):
+        best = 1e30
+        for _ in range(reps):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize()
+            best = min(best, (time.perf_counter() - t0) * 1e3)
+        return best
+
+    # ---- configs[0]: X 128x768, W 768x768 int8 in [-127,127], seed 0; IN/OUT padded 768 -> 1024 ----
+    lj, lk, li = 10, 10, 7
+    rng = np.random.default_rng(0)
+    Xi = np.zeros((128, 1024), dtype=np.int64)
+    Wi = np.zeros((1024, 1024), dtype=np.int64)
+    Xi[:, :768] = rng.integers(-127, 128, (128, 768))
+    Wi[:768, :768] = rng.integers(-127, 128, (768, 768))
+    Yi = Xi @ Wi
+    lift = lambda a: np.where(a.reshape(-1) < 0, a.reshape(-1).astype(object) + P, a.reshape(-1).astype(object)).astype(np.uint64)
+    X, W, Y = lift(Xi), lift(Wi), lift(Yi)
+    d = [zk.p3.to_device(c) for c in (X, W, Y)]
+    t_commit = wall(lambda: [prover.commit_gpu_rootonly(x, R) for x in d], 3)
+    roots = [prover.commit_gpu_rootonly(x, R) for x in d]
+    pf_holder = {}
+
+    def mine():
+        tr = zk.Transcript("imm")
+        pf_holder["pf"] = zk.p3.imm_prove(prover, tr, (d[0], roots[0]), (d[1], roots[1]), (d[2], roots[2]), lj, lk, li, R, Q)
+        pf_holder["st"] = tr.state
+    mine()
+    t_mine = wall(mine, 3)
+    line = {"suite": "configs[0] int matmul proof 128x1024 . 1024x1024 (imm_prove incl. batched openings)", "ms": t_mine,
+            "commit_3_columns_ms": t_commit, "proof_bytes": len(pf_holder["pf"])}
+    if ref is not None:
+        st = (C.c_uint8 * 32)(*zk.Transcript("imm").state)
+        out = (C.c_uint8 * (16 << 20))()
+        ms = C.c_double(0)
+        f = ref.lib.ref_imm_prove
+        f.restype = C.c_size_t
+        n = f(st, X.ctypes.data_as(u64p), W.ctypes.data_as(u64p), Y.ctypes.data_as(u64p), roots[0], roots[1], roots[2],
+              C.c_uint32(lj), C.c_uint32(lk), C.c_uint32(li), C.c_uint32(R), C.c_uint32(Q), out, C.c_size_t(16 << 20),
+              C.byref(ms))
+        line.update({"reference_cuda_ms": ms.value, "speedup_vs_reference_cuda": ms.value / t_mine,
+                     "same_proof_bytes": bool(n and bytes(out)[:n] == pf_holder["pf"])})
+    print(json.dumps(line), flush=True)
+    del d
+    torch.cuda.empty_cache()
+
+    # ---- configs[2]: 2^24 int16 inputs ~ N(0, 2^10) clipped, table (x, round(2^16 silu(x/2^16))) of 2^16 rows ----
+    from lu_helpers import table_id
+    m, n = 16, 24
+    xs = np.arange(-32768, 32768, dtype=np.int64)
+    silu = np.rint(65536.0 * (xs / 65536.0) / (1.0 + np.exp(-xs / 65536.0))).astype(np.int64)
+    tl = lambda a: np.where(a < 0, a.astype(object) + P, a.astype(object)).astype(np.uint64)
+    tcols = [tl(xs), tl(silu)]
+    idx = (np.clip(np.rint(np.random.default_rng(0).normal(0, 1 << 10, 1 << n)), -32768, 32767).astype(np.int64) + 32768).astype(np.uint32)
+    wcols = [tc[idx] for tc in tcols]
+    dT = [zk.p3.to_device(t) for t in tcols]
+    dWc = [zk.p3.to_device(w) for w in wcols]
+    didx = torch.from_numpy(idx.view(np.int32)).cuda()
+    wroots = [prover.commit_gpu_rootonly(x, R) for x in dWc]
+    tid = table_id(tcols)
+    holder = {}
+
+    def lookup():
+        tr = zk.Transcript("lu")
+        holder["pf"], holder["claims"], _ = zk.p3.prove_super(prover, tr, dT, tid, [(n, [(dWc, wroots, didx)])], R)
+        holder["st"] = tr.state
+    lookup()
+    t_lu = wall(lookup, 3)
+    line = {"suite": "configs[2] lookup proof: 2^24 queries, 2^16-row table, c=2 (prove_super: histogram, cnt commit, 2 GKR trees, claims)",
+            "ms": t_lu, "proof_bytes": len(holder["pf"])}
+    if ref is not None:
+        tp = (u64p * 2)(*[a.ctypes.data_as(u64p) for a in tcols])
+        wp = (u64p * 2)(*[a.ctypes.data_as(u64p) for a in wcols])
+        ip = (u32p * 1)(idx.ctypes.data_as(u32p))
+        sub_n, sub_k = np.array([n], dtype=np.uint32), np.array([1], dtype=np.uint32)
+        st = (C.c_uint8 * 32)(*zk.Transcript("lu").state)
+        out = (C.c_uint8 * (1 << 20))()
+        ms = C.c_double(0)
+        f = ref.lib.ref_lu_prove_super
+        f.restype = C.c_size_t
+        nb = f(st, tp, C.c_uint32(m), C.c_uint32(2), C.c_uint32(1), sub_n.ctypes.data_as(C.c_void_p),
+               sub_k.ctypes.data_as(C.c_void_p), wp, b"".join(wroots), ip, C.c_uint32(R), C.c_uint32(Q), out,
+               C.c_size_t(1 << 20), C.byref(ms))
+        line.update({"reference_cuda_ms": ms.value, "speedup_vs_reference_cuda": ms.value / t_lu,
+                     "same_proof_bytes": bool(nb and bytes(out)[:nb] == holder["pf"])})
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -270,11 +383,14 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
+    ap.add_argument("--suite-gadgets", action="store_true", help="configs[0]/[2] through the gadget-level provers")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
     if args.suite:
         return run_suite(args)
+    if args.suite_gadgets:
+        return run_suite_gadgets(args)
 
     import torch
     import torch.distributed as dist

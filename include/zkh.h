@@ -224,6 +224,15 @@ ZKH_API int zkh_gl_combine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc
  * (leaf denominators A_i + beta of zkllm-src/p3_logup.cuh:1645-1647, :1788-1789).  Stream-ordered. */
 ZKH_API int zkh_gl_affine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
                           uint64_t addend, uint64_t* out_dev);
+/* Dense field helpers for binding one index group of a committed matrix M (rows x cols, row-major):
+ * along_rows != 0: out[r] = sum_c M[r][c]*w[c] (rows values); else out[c] = sum_r w[r]*M[r][c] (cols values).
+ * They replace the 2^(lj+lk+li) broadcast columns that p3imm::prove materialises on the host
+ * (zkllm-src/p3_int_gadgets.cuh:574-593): the matmul summand EQ*X*W factors over the index groups,
+ * so its round messages come from these partial evaluations (see p3.imm_prove).  Stream-ordered. */
+ZKH_API int zkh_gl_matvec(zkh_ctx* ctx, const uint64_t* M_dev, uint64_t rows, uint64_t cols, const uint64_t* w_dev,
+                          int along_rows, uint64_t* out_dev);
+/* out[i] = s*in[i].  Stream-ordered. */
+ZKH_API int zkh_gl_scale(zkh_ctx* ctx, const uint64_t* in_dev, uint64_t n, uint64_t s, uint64_t* out_dev);
 /* GKR fractional-sum tree prover (zkllm-src/p3_gkr.cuh:200-364 p3gkr::prove / prove_dev).
  * p_dev, q_dev: 2^L leaf numerators / denominators (left untouched, unlike prove_dev which
  * takes ownership).  state: transcript in/out.  rfin: L values (combine_last) or L-1.

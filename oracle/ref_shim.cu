@@ -247,6 +247,46 @@ bool lu_deserialize(const uint8_t* in, size_t len, p3lu::GroupProof& pf) {
     }
     return p == end;
 }
+// p3imm::Proof (non-zk) <-> bytes: u32 lj, lk, li | messages (lj+lk+li)*40 | yY yX yW | u32 nb | nb x (u32 len, BatchProof)
+size_t imm_serialize(const p3imm::Proof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&pf.lj, 4); app(&pf.lk, 4); app(&pf.li, 4);
+    for (auto& m : pf.m) app(&m, 40);
+    app(&pf.yY, 8); app(&pf.yX, 8); app(&pf.yW, 8);
+    uint32_t nb = (uint32_t)pf.tail.batches.size();
+    app(&nb, 4);
+    for (auto& bp : pf.tail.batches) {
+        std::vector<uint8_t> t((size_t)64 << 20);
+        uint32_t n = (uint32_t)bo_serialize(bp, t.data(), t.size());
+        app(&n, 4); app(t.data(), n);
+    }
+    if (b.size() > cap) return 0;
+    memcpy(out, b.data(), b.size());
+    return b.size();
+}
+bool imm_deserialize(const uint8_t* in, size_t len, p3imm::Proof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
+    if (!need(12)) return false;
+    memcpy(&pf.lj, p, 4); memcpy(&pf.lk, p + 4, 4); memcpy(&pf.li, p + 8, 4); p += 12;
+    uint32_t lt = pf.lj + pf.lk + pf.li;
+    if (lt > 64 || !need((size_t)lt * 40 + 28)) return false;
+    pf.m.resize(lt);
+    for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
+    memcpy(&pf.yY, p, 8); memcpy(&pf.yX, p + 8, 8); memcpy(&pf.yW, p + 16, 8); p += 24;
+    uint32_t nb; memcpy(&nb, p, 4); p += 4;
+    if (nb > 64) return false;
+    pf.tail.batches.resize(nb);
+    for (auto& bp : pf.tail.batches) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (!need(n) || !bo_deserialize(p, n, bp)) return false;
+        p += n;
+    }
+    return p == end;
+}
 struct FProd2 { static __device__ gl_t eval(const gl_t* c, const gl_t*) { return gl_mul(c[0], c[1]); } };
 struct M3 { gl_t s[3]; };
 struct M4 { gl_t s[4]; };
@@ -505,6 +545,21 @@ int ref_lu_verify_super(uint8_t st[32], const uint64_t* const* tcols, uint32_t m
     return 1;
 }
 
+// ---- integer matmul gadget: the reference's host-only verifier (p3_int_gadgets.cuh:608-655) ----
+int ref_imm_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootW[32], const uint8_t rootY[32],
+                   uint32_t lj, uint32_t lk, uint32_t li, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
+    p3imm::Proof pf;
+    if (!imm_deserialize(proof, len, pf)) return 0;
+    p3imm::OpView xv = p3imm::direct_x(nullptr, lj, li), wv = p3imm::direct_w(nullptr, lj, lk),
+                  yv = p3imm::direct_y(nullptr, lk, li);
+    memcpy(xv.root.data(), rootX, 32); memcpy(wv.root.data(), rootW, 32); memcpy(yv.root.data(), rootY, 32);
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3imm::verify(tr, pf, xv, wv, yv, lj, lk, li, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+
 // =====================================================================
 // GPU entry points: the reference's own CUDA paths (need a GPU).
 // =====================================================================
@@ -654,6 +709,31 @@ size_t ref_lu_prove_super(uint8_t st[32], const uint64_t* const* tcols, uint32_t
         cudaDeviceSynchronize();
         if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
         n = lu_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+// p3imm::prove (GPU): host values + given commitment roots of X [j | i<<lj], W [k | j<<lk], Y [k | i<<lk]
+size_t ref_imm_prove(uint8_t st[32], const uint64_t* X, const uint64_t* W, const uint64_t* Y, const uint8_t rootX[32],
+                     const uint8_t rootW[32], const uint8_t rootY[32], uint32_t lj, uint32_t lk, uint32_t li,
+                     uint32_t R, uint32_t Q, uint8_t* out, size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    p3lu::Col cx, cw, cy;
+    cx.v.assign(X, X + ((size_t)1 << (lj + li))); memcpy(cx.root.data(), rootX, 32); cx.vreal = lj + li;
+    cw.v.assign(W, W + ((size_t)1 << (lj + lk))); memcpy(cw.root.data(), rootW, 32); cw.vreal = lj + lk;
+    cy.v.assign(Y, Y + ((size_t)1 << (lk + li))); memcpy(cy.root.data(), rootY, 32); cy.vreal = lk + li;
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        auto pf = p3imm::prove(tr, p3imm::direct_x(&cx, lj, li), p3imm::direct_w(&cw, lj, lk),
+                               p3imm::direct_y(&cy, lk, li), lj, lk, li, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = imm_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);

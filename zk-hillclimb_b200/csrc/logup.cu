@@ -150,3 +150,57 @@ extern "C" int zkh_gl_affine(zkh_ctx* c, const uint64_t* const* cols_dev, int nc
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }
+
+// ---------------------------------------------------------------- small dense helpers
+// Matrix-vector products over the field, used to bind one index group of a committed matrix
+// (partial multilinear evaluation): rows: out[r] = sum_c M[r*C+c]*w[c]; cols: out[c] = sum_r w[r]*M[r*C+c].
+namespace zkh {
+__global__ void __launch_bounds__(256)
+matvec_rows_kernel(const gl_t* __restrict__ M, const gl_t* __restrict__ w, size_t C, gl_t* out) {
+    __shared__ gl_t sh[32];
+    const gl_t* row = M + (size_t)blockIdx.x * C;
+    Acc192 acc;
+    acc.clear();
+    for (size_t c = threadIdx.x; c < C; c += blockDim.x) acc.add_prod(row[c], w[c]);
+    gl_t s[1] = {acc.reduce()};
+    block_sum<1>(s, sh);
+    if (threadIdx.x == 0) out[blockIdx.x] = s[0];
+}
+__global__ void __launch_bounds__(256)
+matvec_cols_kernel(const gl_t* __restrict__ M, const gl_t* __restrict__ w, size_t R, size_t C, gl_t* out) {
+    size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    Acc192 acc;
+    acc.clear();
+    for (size_t r = 0; r < R; r++) acc.add_prod(w[r], M[r * C + c]);
+    out[c] = acc.reduce();
+}
+__global__ void __launch_bounds__(256) scale_vec_kernel(const gl_t* __restrict__ in, gl_t s, size_t n, gl_t* out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = gl_mul(in[i], s);
+}
+}  // namespace zkh
+
+extern "C" int zkh_gl_matvec(zkh_ctx* c, const uint64_t* M_dev, uint64_t rows, uint64_t cols, const uint64_t* w_dev,
+                             int along_rows, uint64_t* out_dev) {
+    if (!c || !M_dev || !w_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "matvec: null pointer");
+    if (!rows || !cols || rows > ((uint64_t)1 << 31) || cols > ((uint64_t)1 << 40))
+        return zkh_fail(c, ZKH_ERR_ARG, "matvec: bad shape");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    if (along_rows)
+        matvec_rows_kernel<<<(unsigned)rows, cols >= 256 ? 256 : 32, 0, c->stream>>>(M_dev, w_dev, (size_t)cols, out_dev);
+    else
+        matvec_cols_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, c->stream>>>(M_dev, w_dev, (size_t)rows, (size_t)cols,
+                                                                                 out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+extern "C" int zkh_gl_scale(zkh_ctx* c, const uint64_t* in_dev, uint64_t n, uint64_t s, uint64_t* out_dev) {
+    if (!c || !in_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "scale: null pointer");
+    if (s >= GL_P) return zkh_fail(c, ZKH_ERR_ARG, "scale: factor not canonical");
+    if (!n) return ZKH_OK;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    scale_vec_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(in_dev, s, (size_t)n, out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}

@@ -263,6 +263,20 @@ class Prover:
         tr.state = bytes(st)
         return out.tobytes()[:wr.value]
 
+    def matvec(self, M_dev, rows, cols, w_dev, along_rows):
+        """Row-major rows x cols field matrix times vector: along_rows -> out[r] = sum_c M[r][c] w[c],
+        else out[c] = sum_r w[r] M[r][c]."""
+        import torch
+        out = torch.empty(rows if along_rows else cols, dtype=torch.int64, device=M_dev.device)
+        self._ck(self._L.zkh_gl_matvec(self._h, _ptr(M_dev), rows, cols, _ptr(w_dev), int(along_rows), _ptr(out)))
+        return out
+
+    def scale(self, col_dev, s):
+        import torch
+        out = torch.empty_like(col_dev)
+        self._ck(self._L.zkh_gl_scale(self._h, _ptr(col_dev), col_dev.numel(), s, _ptr(out)))
+        return out
+
     # ---- engine interface used by prove_super ----
     def lu_counts(self, idx_list, M, pad_rows):
         """Multiplicity column of a merged lookup: histogram of all members' indices plus the
@@ -541,3 +555,104 @@ def prove_super(engine, tr, table_cols, table_id, subgroups, R, strict=True):
         raise ValueError("p3lu: witness not in table")
     claims.append((cnt, root_cnt, np.array(rT, dtype=np.uint64), cpT))
     return _ser_gkr_group(m, c, root_cnt, gkT, subs), claims, cnt
+
+
+class Ledger:
+    """p3bo::PLedger (zkllm-src/p3_batchopen.cuh:144-178): opening claims grouped by size class in
+    order of first appearance; points deduplicated per class in order."""
+
+    def __init__(self):
+        self.cls = []          # [v, pts(list of np arrays), ents(list of (col, root, zid)), ys]
+
+    def add(self, col, root, z, y):
+        z = np.ascontiguousarray(z, dtype=np.uint64)
+        for c in self.cls:
+            if c[0] == len(z):
+                keys = [p.tobytes() for p in c[1]]
+                if z.tobytes() not in keys:
+                    c[1].append(z)
+                    keys.append(z.tobytes())
+                c[2].append((col, root, keys.index(z.tobytes())))
+                c[3].append(y)
+                return
+        self.cls.append([len(z), [z], [(col, root, 0)], [y]])
+
+
+def claimc(engine, tr, ledger, col, root, z):
+    """p3hwl::claimc (zkllm-src/p3_hawkeye.cuh:800-838): evaluate, absorb under "hwl-y", defer the opening."""
+    import struct
+    y = engine.eval_h_gpu(col, np.ascontiguousarray(z, dtype=np.uint64))
+    tr.absorb("hwl-y", struct.pack("<Q", y))
+    ledger.add(col, root, z, y)
+    return y
+
+
+def tail_prove(engine, tr, ledger, R, Q, tag):
+    """p3ig::tail_prove (zkllm-src/p3_int_gadgets.cuh:190-197) without deferred lookups: one batched
+    opening per size class, labelled tag + index."""
+    return [engine.prove_class(tr, np.stack(c[1]), c[2], R, Q, "%s%d" % (tag, i)) for i, c in enumerate(ledger.cls)]
+
+
+def imm_prove(engine, tr, X, W, Y, lj, lk, li, R, Q, ledger=None):
+    """p3imm::prove (zkllm-src/p3_int_gadgets.cuh:546-605), non-zk, direct layouts: proves
+    Y(i,k) = sum_j X(i,j) W(j,k) for committed columns X = [j | i<<lj], W = [k | j<<lk], Y = [k | i<<lk].
+    X, W, Y: (device column, 32-byte root).
+
+    The reference materialises three broadcast columns of 2^(lj+lk+li) elements and runs a cubic
+    sumcheck over them.  The summand eq(z;k,i) X(j,i) W(j,k) factors over the index groups, so the
+    identical round messages are produced from three short product sumchecks: over j on the vectors
+    X(j,zi) and W(j,zk), then over k, then over i, each after a partial evaluation of X / W (matrix-
+    vector products).  Work is O(|X| + |W|) instead of O(2^(lj+lk+li)); the proof bytes are the same.
+    Returns the serialised p3imm::Proof (u32 lj, lk, li | messages (lj+lk+li)*40 | yY yX yW |
+    u32 batches, each u32 length + BatchProof) -- the tail is present when no shared ledger is given."""
+    import struct
+    own = ledger is None
+    if own:
+        ledger = Ledger()
+    tr.absorb("imm-dims", struct.pack("<III", lj, lk, li))
+    tr.absorb("imm-X", X[1])
+    tr.absorb("imm-W", W[1])
+    tr.absorb("imm-Y", Y[1])
+    z = [tr.chal() for _ in range(lk + li)]
+    zk_, zi_ = z[:lk], z[lk:]
+    yY = claimc(engine, tr, ledger, Y[0], Y[1], z)
+    J, K, I = 1 << lj, 1 << lk, 1 << li
+    eq_i, eq_k = engine.build_eq_gpu(np.array(zi_, dtype=np.uint64)), engine.build_eq_gpu(np.array(zk_, dtype=np.uint64))
+    msgs, r = [], []
+    # rounds over j: sum_j X(j, zi) * W(j, zk)
+    Xz = engine.matvec(X[0], I, J, eq_i, False)
+    Wz = engine.matvec(W[0], J, K, eq_k, True)
+    if lj:
+        rj, m, _ = engine.sc_prove_gpu(tr, "imm-sc", [Xz, Wz], F_PROD2, 5)
+        msgs.append(m)
+        rj = [int(x) for x in rj]
+    else:
+        rj = []
+    eq_rj = engine.build_eq_gpu(np.array(rj, dtype=np.uint64))
+    X1 = engine.matvec(X[0], I, J, eq_rj, True)       # X(rj, i)
+    W1 = engine.matvec(W[0], J, K, eq_rj, False)      # W(rj, k)
+    # rounds over k: [sum_i eq(zi,i) X(rj,i)] * sum_k eq(zk,k) W(rj,k)
+    SX = engine.eval_h_gpu(X1, np.array(zi_, dtype=np.uint64))
+    if lk:
+        rk, m, fin = engine.sc_prove_gpu(tr, "imm-sc", [engine.scale(eq_k, SX), W1], F_PROD2, 5)
+        msgs.append(m)
+        rk, Wrr = [int(x) for x in rk], int(fin[1])
+    else:
+        rk, Wrr = [], engine.element(W1, 0)
+    eqk_r = 1
+    for a, b in zip(rk, zk_):
+        eqk_r = eqk_r * ((a * b + (1 - a) * (1 - b)) % GL_P) % GL_P
+    # rounds over i: eq(zk,rk) W(rj,rk) * sum_i eq(zi,i) X(rj,i)
+    if li:
+        ri, m, _ = engine.sc_prove_gpu(tr, "imm-sc", [engine.scale(eq_i, eqk_r * Wrr % GL_P), X1], F_PROD2, 5)
+        msgs.append(m)
+        ri = [int(x) for x in ri]
+    else:
+        ri = []
+    yX = claimc(engine, tr, ledger, X[0], X[1], rj + ri)
+    yW = claimc(engine, tr, ledger, W[0], W[1], rk + rj)
+    out = struct.pack("<III", lj, lk, li) + b"".join(np.ascontiguousarray(m, dtype=np.uint64).tobytes() for m in msgs)
+    out += struct.pack("<QQQ", yY, yX, yW)
+    batches = tail_prove(engine, tr, ledger, R, Q, "imm-bo") if own else []
+    out += struct.pack("<I", len(batches)) + b"".join(struct.pack("<I", len(b)) + b for b in batches)
+    return out
