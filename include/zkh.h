@@ -36,6 +36,9 @@ extern "C" {
 #define ZKH_F_GKR 2   /* c0*(c1*c4+c2*c3+p0*c3*c4)   nc=5 par=1  zkllm-src/p3_gkr.cuh:48-53 */
 #define ZKH_F_LOGUP 3 /* p0*c0+c2*(c0*(c1+p1)-c3)    nc=4 par=2  zkllm-src/p3_logup.cuh:49-54 */
 
+#define ZKH_F_IRS1 4  /* c0*(c1+p0-c2*p1-c3)           nc=4 par=2  zkllm-src/p3_int_gadgets.cuh:316-325 (one limb) */
+#define ZKH_F_IRS2 5  /* c0*(c1+p0-c2*p1-c3-65536*c4)  nc=5 par=2  same, two limbs */
+
 #if defined(__GNUC__)
 #define ZKH_API __attribute__((visibility("default")))
 #else
@@ -233,6 +236,13 @@ ZKH_API int zkh_gl_matvec(zkh_ctx* ctx, const uint64_t* M_dev, uint64_t rows, ui
                           int along_rows, uint64_t* out_dev);
 /* out[i] = s*in[i].  Stream-ordered. */
 ZKH_API int zkh_gl_scale(zkh_ctx* ctx, const uint64_t* in_dev, uint64_t n, uint64_t s, uint64_t* out_dev);
+/* Rescale witness (zkllm-src/p3_int_gadgets.cuh:230-275 p3irs::gen_witness): for each signed acc value
+ * y = floor((acc + 2^(sf-1)) / 2^sf), remainder limbs L0 (16 bits), L1 (sf > 16 only), and the lookup row
+ * indices of the limbs and of y in its window (rng 1: [-2^19,2^19), rng 2: [-2^15,2^15), rng 0: none).
+ * y outside the window returns ZKH_ERR_DOMAIN ("y out of range" in the reference). */
+ZKH_API int zkh_irs_witness(zkh_ctx* ctx, const uint64_t* acc_dev, uint64_t n, uint32_t sf, int rng, uint64_t* y_dev,
+                            uint64_t* L0_dev, uint64_t* L1_dev, uint32_t* idxL0_dev, uint32_t* idxL1_dev,
+                            uint32_t* idxY_dev);
 /* GKR fractional-sum tree prover (zkllm-src/p3_gkr.cuh:200-364 p3gkr::prove / prove_dev).
  * p_dev, q_dev: 2^L leaf numerators / denominators (left untouched, unlike prove_dev which
  * takes ownership).  state: transcript in/out.  rfin: L values (combine_last) or L-1.

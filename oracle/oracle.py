@@ -19,8 +19,8 @@ GL_P = 0xFFFFFFFF00000001
 u64p = C.POINTER(C.c_uint64)
 u8p = C.POINTER(C.c_uint8)
 
-F_PROD2, F_PROD3, F_GKR, F_LOGUP = 0, 1, 2, 3
-FUNCTOR_NC = {F_PROD2: 2, F_PROD3: 3, F_GKR: 5, F_LOGUP: 4}
+F_PROD2, F_PROD3, F_GKR, F_LOGUP, F_IRS1, F_IRS2 = 0, 1, 2, 3, 4, 5
+FUNCTOR_NC = {F_PROD2: 2, F_PROD3: 3, F_GKR: 5, F_LOGUP: 4, F_IRS1: 4, F_IRS2: 5}
 
 
 def build(ref=True):

@@ -287,6 +287,79 @@ bool imm_deserialize(const uint8_t* in, size_t len, p3imm::Proof& pf) {
     }
     return p == end;
 }
+// p3irs::Proof (non-zk) <-> bytes: u32 le, sf, nl, rng | limb roots nl*32 | messages le*40 | yX yY yL[nl] |
+//   u32 groups, each u32 len + GroupProof | u32 batches, each u32 len + BatchProof
+size_t irs_serialize(const p3irs::Proof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&pf.le, 4); app(&pf.sf, 4); app(&pf.nl, 4); app(&pf.rng, 4);
+    for (uint32_t l = 0; l < pf.nl; l++) app(pf.rL[l].data(), 32);
+    for (auto& m : pf.m) app(&m, 40);
+    app(&pf.yX, 8); app(&pf.yY, 8);
+    for (uint32_t l = 0; l < pf.nl; l++) app(&pf.yL[l], 8);
+    std::vector<uint8_t> t((size_t)64 << 20);
+    uint32_t ng = (uint32_t)pf.tail.lug.size();
+    app(&ng, 4);
+    for (auto& g : pf.tail.lug) {
+        uint32_t n = (uint32_t)lu_serialize(g, t.data(), t.size());
+        app(&n, 4); app(t.data(), n);
+    }
+    uint32_t nb = (uint32_t)pf.tail.batches.size();
+    app(&nb, 4);
+    for (auto& bp : pf.tail.batches) {
+        uint32_t n = (uint32_t)bo_serialize(bp, t.data(), t.size());
+        app(&n, 4); app(t.data(), n);
+    }
+    if (b.size() > cap) return 0;
+    memcpy(out, b.data(), b.size());
+    return b.size();
+}
+bool irs_deserialize(const uint8_t* in, size_t len, p3irs::Proof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
+    if (!need(16)) return false;
+    memcpy(&pf.le, p, 4); memcpy(&pf.sf, p + 4, 4); memcpy(&pf.nl, p + 8, 4); memcpy(&pf.rng, p + 12, 4); p += 16;
+    if (pf.le > 40 || pf.nl < 1 || pf.nl > 2) return false;
+    if (!need((size_t)pf.nl * 40 + (size_t)pf.le * 40 + 16 + 4)) return false;
+    for (uint32_t l = 0; l < pf.nl; l++) { memcpy(pf.rL[l].data(), p, 32); p += 32; }
+    pf.m.resize(pf.le);
+    for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
+    memcpy(&pf.yX, p, 8); memcpy(&pf.yY, p + 8, 8); p += 16;
+    for (uint32_t l = 0; l < pf.nl; l++) { memcpy(&pf.yL[l], p, 8); p += 8; }
+    uint32_t ng; memcpy(&ng, p, 4); p += 4;
+    if (ng > 64) return false;
+    pf.tail.lug.resize(ng);
+    for (auto& g : pf.tail.lug) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (!need(n) || !lu_deserialize(p, n, g)) return false;
+        p += n;
+    }
+    if (!need(4)) return false;
+    uint32_t nb; memcpy(&nb, p, 4); p += 4;
+    if (nb > 64) return false;
+    pf.tail.batches.resize(nb);
+    for (auto& bp : pf.tail.batches) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (!need(n) || !bo_deserialize(p, n, bp)) return false;
+        p += n;
+    }
+    return p == end;
+}
+// the five range tables the rescale gadget looks up into (p3_int_gadgets.cuh:60-75)
+p3ig::Tables irs_tables(uint32_t sf) {
+    p3ig::Tables T;
+    T.btop = sf > 16 && sf < 32 ? sf - 16 : 1;
+    T.R16 = p3ig::range_table(16, 0);
+    T.R14 = p3ig::range_table(14, 0);
+    T.RTOP = p3ig::range_table(T.btop, 0);
+    T.RS16 = p3ig::range_table(16, -(1LL << 15));
+    T.RS20 = p3ig::range_table(20, -(1LL << 19));
+    return T;
+}
 struct FProd2 { static __device__ gl_t eval(const gl_t* c, const gl_t*) { return gl_mul(c[0], c[1]); } };
 struct M3 { gl_t s[3]; };
 struct M4 { gl_t s[4]; };
@@ -560,6 +633,34 @@ int ref_imm_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootW[
     return ok ? 1 : 0;
 }
 
+// ---- rescale gadget: the reference's host-only verifier (p3_int_gadgets.cuh:342-388) ----
+int ref_irs_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootY[32], uint32_t le, uint32_t sf,
+                   int rng, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
+    p3irs::Proof pf;
+    if (!irs_deserialize(proof, len, pf)) return 0;
+    p3ig::Tables T = irs_tables(sf);
+    p3fri::Hash rX, rY;
+    memcpy(rX.data(), rootX, 32); memcpy(rY.data(), rootY, 32);
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3irs::verify(tr, T, pf, rX, rY, le, sf, rng, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+// p3irs::gen_witness (p3_int_gadgets.cuh:234-281): y, limbs and lookup indices from the accumulator
+int ref_irs_witness(const uint64_t* acc, uint32_t le, uint32_t sf, int rng, uint64_t* y, uint64_t* L0, uint64_t* L1,
+                    uint32_t* iL0, uint32_t* iL1, uint32_t* iY) {
+    try {
+        std::vector<gl_t> a(acc, acc + ((size_t)1 << le));
+        p3irs::Wit w = p3irs::gen_witness(le, sf, rng, a);
+        size_t N = (size_t)1 << le;
+        memcpy(y, w.y.data(), N * 8); memcpy(L0, w.L[0].data(), N * 8); memcpy(iL0, w.idxL[0].data(), N * 4);
+        if (w.nl == 2) { memcpy(L1, w.L[1].data(), N * 8); memcpy(iL1, w.idxL[1].data(), N * 4); }
+        memcpy(iY, w.idxY.data(), N * 4);
+        return (int)w.nl;
+    } catch (...) { return 0; }
+}
+
 // =====================================================================
 // GPU entry points: the reference's own CUDA paths (need a GPU).
 // =====================================================================
@@ -734,6 +835,34 @@ size_t ref_imm_prove(uint8_t st[32], const uint64_t* X, const uint64_t* W, const
         cudaDeviceSynchronize();
         if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
         n = imm_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+// p3irs::prove (commitments, lookup flush and batched openings on the GPU): host accumulator values and
+// the commitment roots of X (= acc) and Y (= the rescaled output, as gen_witness computes it)
+size_t ref_irs_prove(uint8_t st[32], const uint64_t* acc, const uint8_t rootX[32], const uint8_t rootY[32],
+                     uint32_t le, uint32_t sf, int rng, uint32_t R, uint32_t Q, uint8_t* out, size_t cap,
+                     double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        std::vector<gl_t> a(acc, acc + ((size_t)1 << le));
+        p3ig::Tables T = irs_tables(sf);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3irs::Wit w = p3irs::gen_witness(le, sf, rng, a);
+        p3lu::Col cx, cy;
+        cx.v = w.acc; memcpy(cx.root.data(), rootX, 32); cx.vreal = le;
+        cy.v = w.y;   memcpy(cy.root.data(), rootY, 32); cy.vreal = le;
+        p3irs::Operands ops{&cx, &cy};
+        auto pf = p3irs::prove(tr, w, T, ops, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = irs_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);

@@ -264,6 +264,13 @@ static inline uint64_t summand(int functor, const uint64_t* c, const uint64_t* p
     case ORC_F_GKR:   /* zkllm-src/p3_gkr.cuh:48-53 */
         return orc_gl_mul(c[0], orc_gl_add(orc_gl_add(orc_gl_mul(c[1], c[4]), orc_gl_mul(c[2], c[3])),
                                            orc_gl_mul(p[0], orc_gl_mul(c[3], c[4]))));
+    case ORC_F_IRS1: /* zkllm-src/p3_int_gadgets.cuh:316-325, one limb */
+    case ORC_F_IRS2: {
+        uint64_t t = orc_gl_sub(orc_gl_add(c[1], p[0]), orc_gl_mul(c[2], p[1]));
+        t = orc_gl_sub(t, c[3]);
+        if (functor == ORC_F_IRS2) t = orc_gl_sub(t, orc_gl_mul(c[4], 65536ULL));
+        return orc_gl_mul(c[0], t);
+    }
     case ORC_F_LOGUP: /* zkllm-src/p3_logup.cuh:49-54 */
         return orc_gl_add(orc_gl_mul(p[0], c[0]),
                           orc_gl_mul(c[2], orc_gl_sub(orc_gl_mul(c[0], orc_gl_add(c[1], p[1])), c[3])));
@@ -276,6 +283,8 @@ static int functor_nc(int functor) {
     case ORC_F_PROD3: return 3;
     case ORC_F_GKR: return 5;
     case ORC_F_LOGUP: return 4;
+    case ORC_F_IRS1: return 4;
+    case ORC_F_IRS2: return 5;
     }
     return -1;
 }

@@ -31,7 +31,9 @@ enum {
     ORC_F_PROD2 = 0, /* c0*c1                        nc=2 */
     ORC_F_PROD3 = 1, /* c0*c1*c2                     nc=3 */
     ORC_F_GKR   = 2, /* c0*(c1*c4+c2*c3+p0*c3*c4)    nc=5 par=1 */
-    ORC_F_LOGUP = 3  /* p0*c0+c2*(c0*(c1+p1)-c3)     nc=4 par=2 */
+    ORC_F_LOGUP = 3, /* p0*c0+c2*(c0*(c1+p1)-c3)     nc=4 par=2 */
+    ORC_F_IRS1  = 4, /* c0*(c1+p0-c2*p1-c3)          nc=4 par=2 */
+    ORC_F_IRS2  = 5  /* c0*(c1+p0-c2*p1-c3-65536*c4) nc=5 par=2 */
 };
 
 /* ---- field: zkllm-src/p3_goldilocks.cuh:16-73 ---- */

@@ -204,3 +204,48 @@ extern "C" int zkh_gl_scale(zkh_ctx* c, const uint64_t* in_dev, uint64_t n, uint
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }
+
+// ---------------------------------------------------------------- rescale witness
+// y = floor((acc + 2^(sf-1)) / 2^sf) on the signed value of acc, rem = acc + 2^(sf-1) - y*2^sf split into
+// 16-bit limbs, plus the lookup row indices of the limbs and of y in its signed window
+// (zkllm-src/p3_int_gadgets.cuh:230-275 gen_witness).  window = 2^19 (rng 1), 2^15 (rng 2), none (rng 0).
+namespace zkh {
+__global__ void __launch_bounds__(256)
+irs_witness_kernel(const gl_t* __restrict__ acc, size_t n, uint32_t sf, int rng, gl_t* y, gl_t* L0, gl_t* L1,
+                   uint32_t* iL0, uint32_t* iL1, uint32_t* iY, unsigned int* bad) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const gl_t v = acc[i];
+    const long long a = v > (GL_P >> 1) ? (long long)v - (long long)GL_P : (long long)v;
+    const long long H = 1LL << (sf - 1), win = rng == 1 ? (1LL << 19) : (1LL << 15);
+    const long long yv = (a + H) >> sf, rem = (a + H) - (yv << sf);
+    if (rng != 0 && (yv < -win || yv >= win)) { atomicAdd(bad, 1u); }
+    y[i] = yv >= 0 ? (gl_t)yv : GL_P - (gl_t)(-yv);
+    const long long r0 = rem & 0xFFFF, r1 = rem >> 16;   // rem >= 0 for an honest witness
+    L0[i] = (gl_t)r0;
+    iL0[i] = (uint32_t)r0;
+    if (L1) { L1[i] = (gl_t)r1; iL1[i] = (uint32_t)r1; }
+    if (iY) iY[i] = (uint32_t)(yv + win);
+}
+}  // namespace zkh
+
+extern "C" int zkh_irs_witness(zkh_ctx* c, const uint64_t* acc_dev, uint64_t n, uint32_t sf, int rng, uint64_t* y_dev,
+                               uint64_t* L0_dev, uint64_t* L1_dev, uint32_t* idxL0_dev, uint32_t* idxL1_dev,
+                               uint32_t* idxY_dev) {
+    if (!c || !acc_dev || !y_dev || !L0_dev || !idxL0_dev) return zkh_fail(c, ZKH_ERR_ARG, "irs_witness: null pointer");
+    if (sf < 1 || sf > 32 || rng < 0 || rng > 2) return zkh_fail(c, ZKH_ERR_ARG, "irs_witness: sf must be 1..32, rng 0..2");
+    if ((sf > 16) != (L1_dev != nullptr) || (sf > 16) != (idxL1_dev != nullptr))
+        return zkh_fail(c, ZKH_ERR_ARG, "irs_witness: the second limb is present exactly when sf > 16");
+    if ((rng != 0) != (idxY_dev != nullptr)) return zkh_fail(c, ZKH_ERR_ARG, "irs_witness: idxY is present exactly when rng != 0");
+    if (!n) return ZKH_OK;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    unsigned int* bad = (unsigned int*)&c->d_ctl->err;
+    ZKH_CUDA(c, cudaMemsetAsync(bad, 0, 4, c->stream));
+    irs_witness_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(acc_dev, (size_t)n, sf, rng, y_dev, L0_dev, L1_dev,
+                                                                         idxL0_dev, idxL1_dev, idxY_dev, bad);
+    ZKH_CUDA(c, cudaGetLastError());
+    ZKH_CUDA(c, cudaMemcpyAsync(&c->h_ctl->err, bad, 4, cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (c->h_ctl->err) return zkh_fail(c, ZKH_ERR_DOMAIN, "irs_witness: y out of range (data too large)");
+    return ZKH_OK;
+}

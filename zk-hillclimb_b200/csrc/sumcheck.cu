@@ -67,8 +67,30 @@ template <> struct Fn<ZKH_F_LOGUP> {
     }
 };
 
+// rescale zero-check (zkllm-src/p3_int_gadgets.cuh:316-325):
+//   E * (X + H - Y*2^sf - L0 [- 2^16*L1]),  par = [H, 2^sf]
+template <int NL> struct FnIrs {
+    static constexpr int NC = 3 + NL, DEG = 2;
+    static __device__ __forceinline__ gl_t inner(const gl_t* c, const gl_t* p, gl_t h) {
+        gl_t t = gl_sub(gl_add(c[1], h), gl_mul(c[2], p[1]));
+        t = gl_sub(t, c[3]);
+        if (NL == 2) t = gl_sub(t, gl_mul(c[4], 65536ULL));
+        return t;
+    }
+    static __device__ __forceinline__ void acc(Acc192& a, const gl_t* c, const gl_t* p) {
+        a.add_prod(c[0], inner(c, p, p[0]));
+    }
+    static __device__ __forceinline__ void lead(Acc192& a, const gl_t* d, const gl_t* p) {
+        a.add_prod(d[0], inner(d, p, 0));   // the constant H has no part in the top coefficient
+    }
+};
+template <> struct Fn<ZKH_F_IRS1> : FnIrs<1> {};
+template <> struct Fn<ZKH_F_IRS2> : FnIrs<2> {};
+
 int functor_nc(int functor) {
     switch (functor) {
+        case ZKH_F_IRS1: return 4;
+        case ZKH_F_IRS2: return 5;
         case ZKH_F_PROD2: return 2;
         case ZKH_F_PROD3: return 3;
         case ZKH_F_GKR: return 5;
@@ -469,6 +491,8 @@ int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* 
     CASE(ZKH_F_PROD3, 5)
     CASE(ZKH_F_GKR, 4)
     CASE(ZKH_F_LOGUP, 4)
+    CASE(ZKH_F_IRS1, 5)
+    CASE(ZKH_F_IRS2, 5)
 #undef CASE
     return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck round: unsupported (functor, nt) combination");
 }
@@ -497,6 +521,8 @@ int sc_enqueue_tail(zkh_ctx* ctx, int functor, int nt, const gl_t* const* in, ui
     CASE(ZKH_F_PROD3, 5)
     CASE(ZKH_F_GKR, 4)
     CASE(ZKH_F_LOGUP, 4)
+    CASE(ZKH_F_IRS1, 5)
+    CASE(ZKH_F_IRS2, 5)
 #undef CASE
     return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck tail: unsupported (functor, nt) combination");
 }
@@ -560,6 +586,8 @@ int sc_enqueue(zkh_ctx* ctx, int functor, int nt, int ld, const gl_t* const* in,
     CASE(ZKH_F_GKR, 4, LD_PLAIN)
     CASE(ZKH_F_GKR, 4, LD_GKR)
     CASE(ZKH_F_LOGUP, 4, LD_PLAIN)
+    CASE(ZKH_F_IRS1, 5, LD_PLAIN)
+    CASE(ZKH_F_IRS2, 5, LD_PLAIN)
 #undef CASE
     return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: unsupported (functor, nt) combination");
 }

@@ -21,8 +21,8 @@ import numpy as np
 from ._lib import ZkhError, load_library, u64p
 
 GL_P = 0xFFFFFFFF00000001
-F_PROD2, F_PROD3, F_GKR, F_LOGUP = 0, 1, 2, 3
-FUNCTOR_NC = {F_PROD2: 2, F_PROD3: 3, F_GKR: 5, F_LOGUP: 4}
+F_PROD2, F_PROD3, F_GKR, F_LOGUP, F_IRS1, F_IRS2 = 0, 1, 2, 3, 4, 5
+FUNCTOR_NC = {F_PROD2: 2, F_PROD3: 3, F_GKR: 5, F_LOGUP: 4, F_IRS1: 4, F_IRS2: 5}
 
 
 def _buf32(b=None):
@@ -276,6 +276,23 @@ class Prover:
         out = torch.empty_like(col_dev)
         self._ck(self._L.zkh_gl_scale(self._h, _ptr(col_dev), col_dev.numel(), s, _ptr(out)))
         return out
+
+    def irs_witness(self, acc_dev, sf, rng):
+        """p3irs::gen_witness on the device: returns (y, [L0(, L1)], [idxL0(, idxL1)], idxY or None)."""
+        import torch
+        n, dev = acc_dev.numel(), acc_dev.device
+        nl = 1 if sf <= 16 else 2
+        y = torch.empty(n, dtype=torch.int64, device=dev)
+        L = [torch.empty(n, dtype=torch.int64, device=dev) for _ in range(nl)]
+        iL = [torch.empty(n, dtype=torch.int32, device=dev) for _ in range(nl)]
+        iY = torch.empty(n, dtype=torch.int32, device=dev) if rng else None
+        self._ck(self._L.zkh_irs_witness(self._h, _ptr(acc_dev), n, sf, rng, _ptr(y), _ptr(L[0]),
+                                         _ptr(L[1]) if nl == 2 else 0, _ptr(iL[0]), _ptr(iL[1]) if nl == 2 else 0,
+                                         _ptr(iY) if rng else 0))
+        return y, L, iL, iY
+
+    def upload(self, arr):
+        return to_device(arr, "cuda:%d" % self.device)
 
     # ---- engine interface used by prove_super ----
     def lu_counts(self, idx_list, M, pad_rows):
@@ -654,5 +671,109 @@ def imm_prove(engine, tr, X, W, Y, lj, lk, li, R, Q, ledger=None):
     out = struct.pack("<III", lj, lk, li) + b"".join(np.ascontiguousarray(m, dtype=np.uint64).tobytes() for m in msgs)
     out += struct.pack("<QQQ", yY, yX, yW)
     batches = tail_prove(engine, tr, ledger, R, Q, "imm-bo") if own else []
+    out += struct.pack("<I", len(batches)) + b"".join(struct.pack("<I", len(b)) + b for b in batches)
+    return out
+
+
+LU_GCAP = 25   # zkllm-src/p3_logup.cuh:1891
+
+
+def make_table(cols):
+    """p3lu::make_table (zkllm-src/p3_logup.cuh:413-421): host columns + the binding hash of a public table."""
+    import hashlib
+    cols = [np.ascontiguousarray(c, dtype=np.uint64) for c in cols]
+    h = hashlib.sha256(np.uint64(len(cols)).tobytes() + np.uint64(len(cols[0])).tobytes())
+    for c in cols:
+        h.update(c.tobytes())
+    return {"cols": cols, "id": h.digest(), "dev": None}
+
+
+def range_table(b, off):
+    """p3ig::range_table (zkllm-src/p3_int_gadgets.cuh:60-64): rows j + off as field elements, j < 2^b."""
+    v = np.arange(1 << b, dtype=np.int64) + off
+    return make_table([np.where(v < 0, v.astype(object) + GL_P, v.astype(object)).astype(np.uint64)])
+
+
+def lu_flush(engine, tr, luq, ledger, R, strict=True):
+    """p3lu::lu_flush (zkllm-src/p3_logup.cuh:1940-1956): group the deferred lookups by (table, log-rows)
+    in first-appearance order (groups capped at 2^LU_GCAP stacked rows), bundle the groups by table,
+    prove one merged instance per table.  luq entries: {"W": [(col, root or None), ...], "idx": indices,
+    "tab": make_table(...)}.  Opening claims go to ``ledger``.  Returns the list of GroupProof bytes."""
+    groups = []                                    # lu_groups
+    for i, o in enumerate(luq):
+        n = int(o["idx"].numel()).bit_length() - 1
+        for g in groups:
+            if g[0] == o["tab"]["id"] and g[1] == n:
+                g[2].append(i)
+                break
+        else:
+            groups.append([o["tab"]["id"], n, [i]])
+    split = []
+    for tid, n, mem in groups:
+        cap = 1 if n >= LU_GCAP else 1 << (LU_GCAP - n)
+        for off in range(0, len(mem), cap):
+            split.append((tid, n, mem[off:off + cap]))
+    supers = []                                    # lu_supers
+    for tid, n, mem in split:
+        for sp in supers:
+            if sp[0] == tid:
+                sp[1].append((n, mem))
+                break
+        else:
+            supers.append([tid, [(n, mem)]])
+    out = []
+    for tid, subs in supers:
+        tab = luq[subs[0][1][0]]["tab"]
+        if tab["dev"] is None:
+            tab["dev"] = [engine.upload(c) for c in tab["cols"]]
+        sg = [(n, [([w[0] for w in luq[j]["W"]], [w[1] for w in luq[j]["W"]], luq[j]["idx"]) for j in mem]) for n, mem in subs]
+        pf, claims, _cnt = prove_super(engine, tr, tab["dev"], tid, sg, R, strict)
+        for col, root, pt, y in claims:
+            ledger.add(col, root, pt, y)
+        out.append(pf)
+    del luq[:]
+    return out
+
+
+def irs_prove(engine, tr, tables, X, Y, wit, le, sf, rng, R, Q, ledger=None, luq=None, tag="irs"):
+    """p3irs::prove (zkllm-src/p3_int_gadgets.cuh:291-340), non-zk: Y = round-half-up(X / 2^sf) with the
+    remainder limbs and Y range-checked by lookups.  X, Y: (column, root) committed operands of 2^le rows;
+    wit = (limb columns, limb indices, y indices) from engine.irs_witness; tables: {"R16","R14","RTOP",
+    "RS16","RS20"} as make_table objects.  With ledger/luq given the gadget only records its claims and
+    lookups; otherwise it runs the tail itself (lookup flush + batched openings, tags tag-bo<i>).
+    Proof: u32 le, sf, nl, rng | limb roots nl*32 | messages le*40 | yX yY yL[nl] |
+    u32 groups, each u32 len + GroupProof | u32 batches, each u32 len + BatchProof."""
+    import struct
+    own = ledger is None
+    if own:
+        ledger, luq = Ledger(), []
+    L, iL, iY = wit
+    nl = 1 if sf <= 16 else 2
+    tr.absorb("irs-dims", struct.pack("<IIII", le, sf, nl, rng))
+    tr.absorb("irs-X", X[1])
+    tr.absorb("irs-Y", Y[1])
+    rL = [engine.commit_gpu_rootonly(L[l], R) for l in range(nl)]
+    for l in range(nl):
+        tr.absorb("irs-L", rL[l])
+    for l in range(nl):
+        tab = (tables["R14"] if sf == 14 else tables["R16"]) if l == 0 else (tables["R16"] if sf == 32 else tables["RTOP"])
+        luq.append({"W": [(L[l], rL[l])], "idx": iL[l], "tab": tab})
+    if rng:
+        luq.append({"W": [(Y[0], Y[1])], "idx": iY, "tab": tables["RS20"] if rng == 1 else tables["RS16"]})
+    zE = np.array([tr.chal() for _ in range(le)], dtype=np.uint64)
+    E = engine.build_eq_gpu(zE)
+    rE, m, _ = engine.sc_prove_gpu(tr, "irs-sc", [E, X[0], Y[0]] + list(L[:nl]), F_IRS1 if nl == 1 else F_IRS2, 5,
+                                   [1 << (sf - 1), 1 << sf])
+    rE = [int(x) for x in rE]
+    yX = claimc(engine, tr, ledger, X[0], X[1], rE)
+    yY = claimc(engine, tr, ledger, Y[0], Y[1], rE)
+    yL = [claimc(engine, tr, ledger, L[l], rL[l], rE) for l in range(nl)]
+    out = struct.pack("<IIII", le, sf, nl, rng) + b"".join(rL) + np.ascontiguousarray(m, dtype=np.uint64).tobytes()
+    out += struct.pack("<QQ", yX, yY) + b"".join(struct.pack("<Q", v) for v in yL)
+    lug, batches = [], []
+    if own:
+        lug = lu_flush(engine, tr, luq, ledger, R)
+        batches = tail_prove(engine, tr, ledger, R, Q, tag + "-bo")
+    out += struct.pack("<I", len(lug)) + b"".join(struct.pack("<I", len(b)) + b for b in lug)
     out += struct.pack("<I", len(batches)) + b"".join(struct.pack("<I", len(b)) + b for b in batches)
     return out
