@@ -38,6 +38,15 @@ extern "C" {
 
 #define ZKH_F_IRS1 4  /* c0*(c1+p0-c2*p1-c3)           nc=4 par=2  zkllm-src/p3_int_gadgets.cuh:316-325 (one limb) */
 #define ZKH_F_IRS2 5  /* c0*(c1+p0-c2*p1-c3-65536*c4)  nc=5 par=2  same, two limbs */
+/* Quartic constraint summands of the fp8 matmul gadget (zkh_sumcheck_wide only; nt = 5).  Column and
+ * constraint order as in zkllm-src/p3_hawkeye.cuh:87-101 and :850-1010; lam = the random coefficients. */
+#define ZKH_F_HW_DP 6  /* per-product alignment      nc=12 nlam=6   F_dp  p3_hawkeye.cuh:850-864 */
+#define ZKH_F_HW_DG 7  /* per-group accumulate       nc=30 nlam=18  F_dg  p3_hawkeye.cuh:866-895 */
+#define ZKH_F_HW_CH 8  /* group state chain          nc=11 nlam=6   F_ch  p3_hawkeye.cuh:897-905 */
+#define ZKH_F_HW_GS 9  /* group sum + attainment     nc=3  nlam=2   F_gs  p3_hawkeye.cuh:907-909 */
+#define ZKH_F_HW_DS 10 /* per-row scale decomposition nc=8 nlam=6   F_ds  p3_hawkeye.cuh:915-927 */
+#define ZKH_F_HW_DO 11 /* per-output float pipeline  nc=57 nlam=49  F_do  p3_hawkeye.cuh:929-1010 */
+/* (the reference's F_y, p3_hawkeye.cuh:911-913, is ZKH_F_PROD3) */
 
 #if defined(__GNUC__)
 #define ZKH_API __attribute__((visibility("default")))
@@ -129,6 +138,17 @@ ZKH_API int zkh_sumcheck_host(zkh_ctx* ctx, int functor, int nt, const uint64_t*
                       uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals);
 /* Bytes of workspace zkh_sumcheck needs for (nc, logn). */
 ZKH_API size_t zkh_sumcheck_workspace(int nc, uint32_t logn);
+
+/* Quartic zero-check sumcheck over many device columns: replaces p3hwl::sc5_run<FF> /
+ * sc5_prove (zkllm-src/p3_hawkeye.cuh:1016-1033, :641-700; non-zk) for the ZKH_F_HW_* summands.
+ * Five evaluations per round (Msg5), messages absorbed under `tag`, columns bound LSB-first; the
+ * caller's columns are left untouched.  lam: nlam canonical coefficients (host).  msgs: logn*5 out,
+ * chals: logn out, finals: nc out (may be NULL).  nc and nlam must equal the summand's shape. */
+ZKH_API int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* const* cols_dev, int nc, uint32_t logn,
+                      const uint64_t* lam, int nlam, const char* tag, uint8_t state[32], uint64_t* msgs,
+                      uint64_t* chals, uint64_t* finals);
+/* Column and coefficient counts of a ZKH_F_HW_* summand (ZKH_ERR_ARG for any other id). */
+ZKH_API int zkh_sumcheck_wide_shape(int functor, int* nc, int* nlam);
 
 /* ---- sumcheck sharded over several GPUs of one node ----
  * The reference has no multi-GPU code; this is the sharded form of p3sg::sc_prove_gpu

@@ -21,6 +21,8 @@ u8p = C.POINTER(C.c_uint8)
 
 F_PROD2, F_PROD3, F_GKR, F_LOGUP, F_IRS1, F_IRS2 = 0, 1, 2, 3, 4, 5
 FUNCTOR_NC = {F_PROD2: 2, F_PROD3: 3, F_GKR: 5, F_LOGUP: 4, F_IRS1: 4, F_IRS2: 5}
+F_HW_DP, F_HW_DG, F_HW_CH, F_HW_GS, F_HW_DS, F_HW_DO = 6, 7, 8, 9, 10, 11
+HW_SHAPE = {6: (12, 6), 7: (30, 18), 8: (11, 6), 9: (3, 2), 10: (8, 6), 11: (57, 49)}   # functor -> (columns, coefficients)
 
 
 def build(ref=True):
@@ -352,6 +354,19 @@ class Reference(_Lib):
         s = _bytes32(st)
         rc = self.lib.ref_sc5_prove(s, tag.encode(), functor, ptrs, nc, C.c_uint32(logn),
                                     msgs.ctypes.data_as(u64p), chals.ctypes.data_as(u64p))
+        assert rc == 0
+        return bytes(s), msgs, chals
+
+    def sc5_prove_lam(self, st, tag, functor, cols, lam):
+        """p3hwl::sc5_prove with the reference's fp8-gadget constraint function `functor` (6..11)."""
+        arrs = [np.ascontiguousarray(c, dtype=np.uint64) for c in cols]
+        nc = len(arrs); logn = int(len(arrs[0])).bit_length() - 1
+        ptrs = (u64p * nc)(*[a.ctypes.data_as(u64p) for a in arrs])
+        la, lp = _u64(lam)
+        msgs = np.zeros((logn, 5), dtype=np.uint64); chals = np.zeros(logn, dtype=np.uint64)
+        s = _bytes32(st)
+        rc = self.lib.ref_sc5_prove_lam(s, tag.encode(), functor, ptrs, nc, C.c_uint32(logn), lp, len(la),
+                                        msgs.ctypes.data_as(u64p), chals.ctypes.data_as(u64p))
         assert rc == 0
         return bytes(s), msgs, chals
 

@@ -530,6 +530,32 @@ int ref_sc5_prove(uint8_t st[32], const char* tag, int functor, const uint64_t* 
     return 0;
 }
 
+// quartic zero-checks of the fp8 gadget on host cores: p3hwl::sc5_prove with the reference's own
+// constraint functions (p3_hawkeye.cuh:850-1010).  functor 6..11 = F_dp, F_dg, F_ch, F_gs, F_ds, F_do.
+int ref_sc5_prove_lam(uint8_t st[32], const char* tag, int functor, const uint64_t* const* cols, int nc,
+                      uint32_t logn, const uint64_t* lam, int nlam, uint64_t* msgs, uint64_t* chals) {
+    fs::Transcript tr = tr_from(st);
+    size_t n = (size_t)1 << logn;
+    std::vector<std::vector<gl_t>> cc(nc);
+    for (int k = 0; k < nc; k++) cc[k].assign(cols[k], cols[k] + n);
+    std::vector<gl_t> L(lam, lam + nlam);
+    L.resize(64, 0);
+    p3hwl::CFn F;
+    if (functor == 6) F = [L](const gl_t* v) { return p3hwl::F_dp(v, L.data()); };
+    else if (functor == 7) F = [L](const gl_t* v) { return p3hwl::F_dg(v, L.data()); };
+    else if (functor == 8) F = [L](const gl_t* v) { return p3hwl::F_ch(v, L.data()); };
+    else if (functor == 9) F = [L](const gl_t* v) { return p3hwl::F_gs(v, L.data()); };
+    else if (functor == 10) F = [L](const gl_t* v) { return p3hwl::F_ds(v, L.data()); };
+    else if (functor == 11) F = [L](const gl_t* v) { return p3hwl::F_do(v, L.data()); };
+    else return -1;
+    std::vector<p3hwl::Msg5> m;
+    auto r = p3hwl::sc5_prove(tr, tag, std::move(cc), F, m);
+    memcpy(st, tr.state, 32);
+    memcpy(msgs, m.data(), m.size() * 40);
+    memcpy(chals, r.data(), r.size() * 8);
+    return 0;
+}
+
 // ---- logUp primitives ----
 int ref_inv_all_add(const uint64_t* A, size_t n, uint64_t beta, uint64_t* out) {
     try {
@@ -684,6 +710,14 @@ static int sc_gpu_run(fs::Transcript& tr, const char* tag, int functor, int nt,
     else if (functor == 1 && nt == 5) RUN(p3imm::FImmGpu, M5, 5)
     else if (functor == 2 && nt == 4) RUN(p3gkr::FGkrGpu, M4, 4)
     else if (functor == 3 && nt == 4) RUN(p3lu::FLuGpu, M4, 4)
+    else if (functor >= 6 && functor <= 9 && nt == 5) {
+        std::vector<M5> m;
+        if (functor == 6) r = p3sg::sc_prove_gpu<p3hwl::FFdp, M5, 5, 40>(tr, tag, d, N, par, npar, m);
+        else if (functor == 7) r = p3sg::sc_prove_gpu<p3hwl::FFdg, M5, 5, 40>(tr, tag, d, N, par, npar, m);
+        else if (functor == 8) r = p3sg::sc_prove_gpu<p3hwl::FFch, M5, 5, 40>(tr, tag, d, N, par, npar, m);
+        else r = p3sg::sc_prove_gpu<p3hwl::FFgs, M5, 5, 40>(tr, tag, d, N, par, npar, m);
+        memcpy(msgs, m.data(), m.size() * sizeof(M5));
+    }
     else return -1;
 #undef RUN
     memcpy(chals, r.data(), r.size() * 8);

@@ -175,6 +175,24 @@ def main():
                    "proof_len": len(pf), "accepted_by": "p3bo::verify_class (reference, host)"})
     g["batchopen"] = bo
 
+    # ---- quartic zero-checks of the fp8 gadget: p3hwl::sc5_prove over the reference's own constraint
+    # functions F_dp .. F_do (ids 6..11), random columns and coefficients
+    from oracle import HW_SHAPE
+    hw = []
+    for f, (nc, nlam) in sorted(HW_SHAPE.items()):
+        for logn in (1, 7):
+            s = seed + 600 + 10 * f + logn
+            cols = []
+            for _ in range(nc):
+                a, s = lcg(1 << logn, s)
+                cols.append(a)
+            lam, s = lcg(nlam, s)
+            st0 = ref.tr_init("hw-golden")
+            st1, m, r = ref.sc5_prove_lam(st0, "hwl-sc", f, cols, lam)
+            hw.append({"functor": f, "nc": nc, "nlam": nlam, "seed": seed + 600 + 10 * f + logn, "logn": logn,
+                       "tag": "hwl-sc", "state": st1.hex(), "msgs_digest": dig(m), "chals": [int(x) for x in r]})
+    g["hawkeye_sumcheck"] = hw
+
     with open(OUT, "w") as f:
         json.dump(g, f, indent=1)
     print("wrote", OUT, os.path.getsize(OUT), "bytes")

@@ -191,3 +191,19 @@ def test_oracle_equals_reference_live(orc, ref):
     pf = orc.bf_prove_eval(c, z, y, 2, 24, cw, "seed-live")
     assert pf == ref.bf_prove_eval(c, z, y, 2, 24, cw, "seed-live")
     assert ref.bf_verify_eval(pf, "seed-live") and not ref.bf_verify_eval(pf, "other-seed")
+
+
+def test_hawkeye_constraint_sumchecks_reference_live(golden, orc, ref):
+    """The fp8 gadget's quartic zero-checks have the reference's host loop itself as their oracle
+    (p3hwl::sc5_prove over F_dp .. F_do through oracle/_ref): it must reproduce the committed vectors."""
+    from oracle import HW_SHAPE
+    for gv in golden["hawkeye_sumcheck"]:
+        nc, nlam = HW_SHAPE[gv["functor"]]
+        assert (nc, nlam) == (gv["nc"], gv["nlam"])
+        s, cols = gv["seed"], []
+        for _ in range(nc):
+            a, s = orc.lcg(1 << gv["logn"], s)
+            cols.append(a)
+        lam, s = orc.lcg(nlam, s)
+        st, m, r = ref.sc5_prove_lam(ref.tr_init("hw-golden"), gv["tag"], gv["functor"], cols, lam)
+        assert st.hex() == gv["state"] and dig(m) == gv["msgs_digest"] and [int(x) for x in r] == gv["chals"]

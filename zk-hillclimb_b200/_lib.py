@@ -59,6 +59,8 @@ def load_library():
         "zkh_sumcheck": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_host": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_workspace": (sz, [i, u32]),
+        "zkh_sumcheck_wide": (i, [vp, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
+        "zkh_sumcheck_wide_shape": (i, [i, vp, vp]),
         "zkh_shard_begin": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp]),
         "zkh_shard_round_local": (i, [vp, u32, vp]),
         "zkh_shard_round_combine": (i, [vp, u32, vp, u32]),

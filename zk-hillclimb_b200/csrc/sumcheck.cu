@@ -188,64 +188,6 @@ __device__ __forceinline__ void msg_reduce(const Acc192 (&acc)[NT], gl_t (&s)[NT
     }
 }
 
-// ------------------------------------------------------------------ round end
-// mode 0: absorb the message under `tag` and draw the challenge on the device.
-// mode 1: write this GPU's sums to msg_out and stop (another step combines the GPUs).
-// Called by all 32 lanes of warp 0; the sums s are valid on lane 0.
-template <int NT>
-__device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t* msg_out, gl_t* chal_out,
-                                          const ZkhTag& tag, int mode) {
-    __shared__ uint32_t trbuf[ZKH_TRBUF_WORDS];
-    __shared__ gl_t mvals[NT];
-    const uint32_t lane = threadIdx.x & 31;
-    if (lane == 0) {
-#pragma unroll
-        for (int t = 0; t < NT; t++) { msg_out[t] = s[t]; mvals[t] = s[t]; }
-    }
-    if (mode == 1) return;
-    uint32_t st[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
-    tr_warp_absorb(st, tag.s, tag.len, mvals, NT, trbuf);
-    gl_t a = tr_warp_chal_gl(st);
-    if (lane == 0) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
-        *chal_out = a;
-    }
-}
-
-// CTA sums -> grid sum by the last CTA to arrive -> finish_round.
-template <int NT>
-__device__ __forceinline__ void grid_finish(gl_t (&s)[NT], gl_t* sh, ZkhCtl* ctl, gl_t* partials,
-                                            gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag,
-                                            int mode) {
-    __shared__ int is_last;
-    block_sum<NT>(s, sh);
-    if (threadIdx.x == 0) {
-#pragma unroll
-        for (int t = 0; t < NT; t++) __stcg(&partials[(size_t)blockIdx.x * NT + t], s[t]);
-        __threadfence();
-        unsigned prev = atomicAdd(&ctl->counter, 1u);
-        is_last = (prev == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    gl_t v[NT];
-#pragma unroll
-    for (int t = 0; t < NT; t++) v[t] = 0;
-    for (unsigned b = threadIdx.x; b < gridDim.x; b += blockDim.x) {
-#pragma unroll
-        for (int t = 0; t < NT; t++) v[t] = gl_add(v[t], __ldcg(&partials[(size_t)b * NT + t]));
-    }
-    block_sum<NT>(v, sh);
-    if (threadIdx.x < 32) {
-        if (threadIdx.x == 0) ctl->counter = 0;
-        finish_round<NT>(v, ctl, msg_out, chal_out, tag, mode);
-    }
-}
-
 // ------------------------------------------------------------------ kernels
 // round 0: message only
 template <int F, int NT, int LD>

@@ -1,0 +1,184 @@
+// Quartic zero-check sumchecks over many columns (up to 64) for sm_100a: the round engine behind the
+// fp8 gadget's constraint summands (hawkeye_fn.cuh).
+//
+// The reference runs these through sc_prove_gpu<FF, Msg5, 5, 40> when the domain is large
+// (zkllm-src/p3_hawkeye.cuh:1016-1033: every column uploaded per call, two launches, a copy back and
+// nc allocations per round) and through a host loop (sc5_prove, :641-700) otherwise, which is also the
+// only path for the 57-column output constraint.  Here every size and every summand takes the same
+// device path: one kernel per round that binds with the previous challenge, stores the halved columns,
+// evaluates the summand at t = 0..4 on the pair it just produced, reduces across the grid through the
+// last CTA to finish, and advances the Fiat-Shamir transcript on the device.
+//
+// A thread keeps one pair of every column (value and difference) in registers; at 57 columns the
+// compiler spills part of that to local memory, which stays in L1.  These kernels are bound by the
+// integer pipe (tens of field multiplications per row and evaluation point), not by HBM.
+#include "sumcheck.cuh"
+#include "hawkeye_fn.cuh"
+
+namespace zkh {
+
+constexpr int SCW_MAXC = 64;
+constexpr int SCW_NT = 5;
+constexpr int SCW_THREADS = 128;
+
+struct WidePtrs {
+    const gl_t* in[SCW_MAXC];
+    gl_t* out[SCW_MAXC];
+};
+
+// first != 0: message over the caller's columns (items = pairs).
+// first == 0: bind with *chal_prev, store, message over the bound columns (items = quads).
+template <int F>
+__global__ void __launch_bounds__(SCW_THREADS)
+scw_round_kernel(WidePtrs P, size_t items, int first, ZkhCtl* ctl, gl_t* partials, const gl_t* chal_prev,
+                 gl_t* msg_out, gl_t* chal_out, ZkhTag tag) {
+    constexpr int NC = WFn<F>::NC, NLAM = WFn<F>::NLAM;
+    __shared__ gl_t lam[NLAM];
+    __shared__ gl_t sh[SCW_NT * 32];
+    for (int j = threadIdx.x; j < NLAM; j += blockDim.x) lam[j] = ctl->aux[j];
+    __syncthreads();
+    const gl_t a = first ? 0 : *chal_prev;
+    gl_t s[SCW_NT];
+#pragma unroll
+    for (int t = 0; t < SCW_NT; t++) s[t] = 0;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < items; i += stride) {
+        gl_t cur[NC], dif[NC];
+        if (first) {
+#pragma unroll
+            for (int k = 0; k < NC; k++) {
+                ulonglong2 v = ld2(P.in[k] + 2 * i);
+                cur[k] = v.x;
+                dif[k] = gl_sub(v.y, v.x);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < NC; k++) {
+                ulonglong2 u = ld2(P.in[k] + 4 * i), w = ld2(P.in[k] + 4 * i + 2);
+                gl_t lo = gl_lerp(u.x, u.y, a), hi = gl_lerp(w.x, w.y, a);
+                st2(P.out[k] + 2 * i, lo, hi);
+                cur[k] = lo;
+                dif[k] = gl_sub(hi, lo);
+            }
+        }
+        s[0] = gl_add(s[0], WFn<F>::eval(cur, lam));
+#pragma unroll
+        for (int t = 1; t < SCW_NT; t++) {
+#pragma unroll
+            for (int k = 0; k < NC; k++) cur[k] = gl_add(cur[k], dif[k]);
+            s[t] = gl_add(s[t], WFn<F>::eval(cur, lam));
+        }
+    }
+    grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, 0);
+}
+
+// out[k] = in[k][0] + a*(in[k][1] - in[k][0]) after the last round
+__global__ void scw_finals_kernel(WidePtrs P, int nc, const gl_t* chal, gl_t* out) {
+    int k = threadIdx.x;
+    if (k < nc) out[k] = gl_lerp(P.in[k][0], P.in[k][1], *chal);
+}
+
+static size_t scw_workspace_bytes(int nc, uint32_t logn) {
+    const size_t n = (size_t)1 << logn;
+    return zkh_align((size_t)nc * (n / 2 + 1) * 8) + zkh_align((size_t)nc * (n / 4 + 1) * 8) + zkh_align((size_t)nc * 8);
+}
+
+template <int F>
+static int scw_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, const ZkhTag& tag, gl_t* finals_dev) {
+    constexpr int NC = WFn<F>::NC;
+    cudaStream_t s = ctx->stream;
+    ZkhCtl* ctl = ctx->d_ctl;
+    const size_t n = (size_t)1 << logn;
+    static int occ = 0;
+    if (!occ) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, scw_round_kernel<F>, SCW_THREADS, 0);
+        if (occ < 1) occ = 1;
+    }
+    auto grid_for = [&](size_t items) {
+        size_t want = (items + SCW_THREADS - 1) / SCW_THREADS, cap = (size_t)ctx->sm_count * occ;
+        if (cap > ctx->partials_cap / SCW_NT) cap = ctx->partials_cap / SCW_NT;
+        return (unsigned)(want < cap ? want : cap);
+    };
+    WidePtrs P;
+    memset(&P, 0, sizeof P);
+    for (int k = 0; k < NC; k++) P.in[k] = in[k];
+    scw_round_kernel<F><<<grid_for(n / 2), SCW_THREADS, 0, s>>>(P, n / 2, 1, ctl, ctx->d_partials, nullptr, ctl->msgs,
+                                                               ctl->chals, tag);
+    gl_t* bufA = (gl_t*)ctx->ws;
+    gl_t* bufB = (gl_t*)((char*)ctx->ws + zkh_align((size_t)NC * (n / 2 + 1) * 8));
+    gl_t* dst = bufA;
+    size_t cur_n = n;
+    for (uint32_t r = 1; r < logn; r++) {
+        const size_t out_n = cur_n / 2;
+        for (int k = 0; k < NC; k++) P.out[k] = dst + (size_t)k * out_n;
+        scw_round_kernel<F><<<grid_for(cur_n / 4), SCW_THREADS, 0, s>>>(
+            P, cur_n / 4, 0, ctl, ctx->d_partials, ctl->chals + (r - 1), ctl->msgs + (size_t)r * SCW_NT,
+            ctl->chals + r, tag);
+        for (int k = 0; k < NC; k++) P.in[k] = P.out[k];
+        dst = (dst == bufA) ? bufB : bufA;
+        cur_n = out_n;
+    }
+    scw_finals_kernel<<<1, SCW_MAXC, 0, s>>>(P, NC, ctl->chals + (logn - 1), finals_dev);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "wide sumcheck launch");
+}
+
+static int scw_shape(int functor, int* nc, int* nlam) {
+#define CASE(F) if (functor == F) { *nc = WFn<F>::NC; *nlam = WFn<F>::NLAM; return 1; }
+    CASE(ZKH_F_HW_DP) CASE(ZKH_F_HW_DG) CASE(ZKH_F_HW_CH) CASE(ZKH_F_HW_GS) CASE(ZKH_F_HW_DS) CASE(ZKH_F_HW_DO)
+#undef CASE
+    return 0;
+}
+
+}  // namespace zkh
+
+using namespace zkh;
+
+extern "C" int zkh_sumcheck_wide_shape(int functor, int* nc, int* nlam) {
+    int a = 0, b = 0;
+    if (!scw_shape(functor, &a, &b)) return ZKH_ERR_ARG;
+    if (nc) *nc = a;
+    if (nlam) *nlam = b;
+    return ZKH_OK;
+}
+
+extern "C" int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* const* cols_dev, int nc, uint32_t logn,
+                                 const uint64_t* lam, int nlam, const char* tag, uint8_t state[32], uint64_t* msgs,
+                                 uint64_t* chals, uint64_t* finals) {
+    if (!ctx) return ZKH_ERR_ARG;
+    if (!cols_dev || !lam || !tag || !state || !msgs || !chals) return zkh_fail(ctx, ZKH_ERR_ARG, "wide sumcheck: null pointer");
+    int want_nc = 0, want_nlam = 0;
+    if (!scw_shape(functor, &want_nc, &want_nlam)) return zkh_fail(ctx, ZKH_ERR_ARG, "wide sumcheck: unknown summand");
+    if (nc != want_nc || nlam != want_nlam)
+        return zkh_fail(ctx, ZKH_ERR_ARG, "wide sumcheck: column or coefficient count does not match the summand");
+    if (logn < 1 || logn > 34) return zkh_fail(ctx, ZKH_ERR_ARG, "wide sumcheck: logn must be 1..34");
+    if (strlen(tag) > ZKH_TR_MAX_LABEL) return zkh_fail(ctx, ZKH_ERR_LIMIT, "wide sumcheck: tag longer than 48 bytes");
+    for (int j = 0; j < nlam; j++)
+        if (lam[j] >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "wide sumcheck: coefficient not canonical");
+    ZKH_CUDA(ctx, cudaSetDevice(ctx->device));
+    ZKH_TRY(zkh_ws_reserve(ctx, scw_workspace_bytes(nc, logn)));
+    ZkhCtl* h = ctx->h_ctl;
+    digest_from_bytes(state, h->st);
+    h->counter = 0;
+    h->err = 0;
+    for (int i = 0; i < 8; i++) h->par[i] = 0;
+    for (int j = 0; j < 64; j++) h->aux[j] = j < nlam ? lam[j] : 0;
+    ZKH_CUDA(ctx, cudaMemcpyAsync(ctx->d_ctl, h, offsetof(ZkhCtl, local), cudaMemcpyHostToDevice, ctx->stream));
+    ZKH_CUDA(ctx, cudaMemcpyAsync(ctx->d_ctl->aux, h->aux, sizeof h->aux, cudaMemcpyHostToDevice, ctx->stream));
+    const size_t n = (size_t)1 << logn;
+    gl_t* finals_dev = (gl_t*)((char*)ctx->ws + zkh_align((size_t)nc * (n / 2 + 1) * 8) + zkh_align((size_t)nc * (n / 4 + 1) * 8));
+    const ZkhTag t = zkh_make_tag(tag);
+    int rc = ZKH_ERR_ARG;
+#define CASE(F) if (functor == F) rc = scw_enqueue_t<F>(ctx, cols_dev, logn, t, finals_dev);
+    CASE(ZKH_F_HW_DP) CASE(ZKH_F_HW_DG) CASE(ZKH_F_HW_CH) CASE(ZKH_F_HW_GS) CASE(ZKH_F_HW_DS) CASE(ZKH_F_HW_DO)
+#undef CASE
+    ZKH_TRY(rc);
+    ZKH_CUDA(ctx, cudaMemcpyAsync(h, ctx->d_ctl, sizeof(ZkhCtl), cudaMemcpyDeviceToHost, ctx->stream));
+    if (finals)
+        ZKH_CUDA(ctx, cudaMemcpyAsync(finals, finals_dev, (size_t)nc * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    ZKH_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (h->err) return zkh_fail(ctx, ZKH_ERR_DEVICE, "wide sumcheck: device error flag set");
+    memcpy(msgs, h->msgs, (size_t)logn * SCW_NT * 8);
+    memcpy(chals, h->chals, (size_t)logn * 8);
+    digest_to_bytes(h->st, state);
+    return ZKH_OK;
+}

@@ -23,6 +23,7 @@ from ._lib import ZkhError, load_library, u64p
 GL_P = 0xFFFFFFFF00000001
 F_PROD2, F_PROD3, F_GKR, F_LOGUP, F_IRS1, F_IRS2 = 0, 1, 2, 3, 4, 5
 FUNCTOR_NC = {F_PROD2: 2, F_PROD3: 3, F_GKR: 5, F_LOGUP: 4, F_IRS1: 4, F_IRS2: 5}
+F_HW_DP, F_HW_DG, F_HW_CH, F_HW_GS, F_HW_DS, F_HW_DO = 6, 7, 8, 9, 10, 11   # wide quartic summands (sc5_run)
 
 
 def _buf32(b=None):
@@ -426,6 +427,23 @@ class Prover:
         self._ck(self._L.zkh_sumcheck(self._h, functor, nt, ptrs, nc, logn, par_a.ctypes.data, len(par),
                                       tag.encode(), st, msgs.ctypes.data, chals.ctypes.data,
                                       fin.ctypes.data))
+        tr.state = bytes(st)
+        return chals, msgs, fin
+
+    def sc5_run(self, tr, tag, dcols, functor, lam):
+        """p3hwl::sc5_run / sc5_prove (zkllm-src/p3_hawkeye.cuh:1016-1033, :641-700), non-zk, for the fp8
+        gadget's constraint summands F_HW_*: quartic zero-check over device columns with the random
+        coefficients ``lam``.  Returns (r, msgs[v, 5], finals); ``tr`` advances as the reference's does."""
+        nc = len(dcols)
+        logn = int(dcols[0].numel()).bit_length() - 1
+        ptrs = (C.c_uint64 * nc)(*[_ptr(t) for t in dcols])
+        lam_a = np.ascontiguousarray(lam, dtype=np.uint64)
+        msgs = np.zeros((logn, 5), dtype=np.uint64)
+        chals = np.zeros(logn, dtype=np.uint64)
+        fin = np.zeros(nc, dtype=np.uint64)
+        st = _buf32(tr.state)
+        self._ck(self._L.zkh_sumcheck_wide(self._h, functor, ptrs, nc, logn, lam_a.ctypes.data, len(lam_a),
+                                           tag.encode(), st, msgs.ctypes.data, chals.ctypes.data, fin.ctypes.data))
         tr.state = bytes(st)
         return chals, msgs, fin
 
