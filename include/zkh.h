@@ -274,6 +274,40 @@ ZKH_API int zkh_gkr_prove(zkh_ctx* ctx, const uint64_t* p_dev, const uint64_t* q
                           const char* tag, uint8_t state[32], uint64_t* rfin, uint64_t cpq[2], uint8_t* out,
                           size_t cap, size_t* written);
 
+/* ======================================================================================
+ * BLS12-381 scalar field (Fr) back-end: the reference's first proof stack.
+ * An element is the reference's Fr_t (zkllm-src/bls12-381.cuh:116-120): eight 32-bit limbs, little
+ * endian, 32 bytes, holding a PLAIN canonical integer below
+ *   p = 0x73eda753299d7d483339d80809a1d80553bda402fffe5bfeffffffff00000001
+ * (the reference keeps tensors plain and converts around each Montgomery product).  Device arrays
+ * must be 16-byte aligned.  Points and challenges are host arrays of 32-byte elements.
+ * ====================================================================================== */
+
+/* E[b] = prod_i (bit_i(b) ? u[i] : 1 - u[i]), 2^v entries: build_eq_tensor / k_eq_expand
+ * (zkllm-src/zkob_lookup.cuh:202-212, :247-268). */
+ZKH_API int zkh_fr_eq_build(zkh_ctx* ctx, const void* u, uint32_t v, void* out_dev);
+/* out[i] = in[i] + w*(in[i+h] - in[i]), i < h: k_fr_fold (zkllm-src/zkob_lookup.cuh:285-293 call sites). */
+ZKH_API int zkh_fr_fold(zkh_ctx* ctx, const void* in_dev, uint64_t h, const void* w, void* out_dev);
+/* FrTensor::partial_me (zkllm-src/fr-tensor.cu:542-561, :601-632) for a power-of-two dimension:
+ * t viewed as [other][2^logd][window]; out[o][w] = sum_d eq(u, d) * t[o][d][w], u[0] bound first.
+ * One pass over t instead of logd passes with intermediates. */
+ZKH_API int zkh_fr_partial_me(zkh_ctx* ctx, const void* t_dev, uint64_t other, uint32_t logd, uint64_t window,
+                      const void* u, void* out_dev);
+/* FrTensor::operator()(u) / Fr_me (zkllm-src/fr-tensor.cu:578-600): the multilinear extension of the
+ * 2^v-element t at u (u[0] pairs adjacent elements).  out32: 32 bytes, host. */
+ZKH_API int zkh_fr_mle_eval(zkh_ctx* ctx, const void* t_dev, const void* u, uint32_t v, void* out32);
+/* Product sumcheck over nc (2..4) device columns of 2^logn elements, binding the TOP variable first
+ * (pairs (i, i+h)), nt = nc+1 evaluations per round at t = 0..nc:
+ *   nc=2  the inner-product rounds of zkob_fc   (zkllm-src/zkob_fc.cu:290-332; labels "p0","p1","p2")
+ *   nc=3  fs_hadamard                            (zkllm-src/zkob_lookup.cuh:297-318; "hp0".."hp3")
+ *   nc=4  the bracket sumcheck fs_quartic        (zkllm-src/zkob_lookup.cuh:321-425)
+ * Per round: each evaluation is absorbed as 32 bytes under labels[t], then the challenge is drawn as
+ * fs_challenge_fr does (zkllm-src/vrf_common.cuh:233-244).  The columns are left untouched.
+ *   state   transcript in/out;  evals: logn*nt*32 bytes out;  chals: logn*32 bytes out (round order);
+ *   finals  nc*32 bytes out: every column bound at all challenges (may be NULL). */
+ZKH_API int zkh_fr_sumcheck(zkh_ctx* ctx, const void* const* cols_dev, int nc, uint32_t logn,
+                    const char* const* labels, uint8_t state[32], void* evals, void* chals, void* finals);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,139 @@
+"""CPU restatement of the reference's BLS12-381 Fr sumcheck path with Python integers.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/ and by __graft_entry__.smoke(); never by the package.
+
+The reference's first proof stack keeps every tensor as plain integers below
+    p = 0x73eda753299d7d483339d80809a1d80553bda402fffe5bfeffffffff00000001
+(limb constant at zkllm-src/bls12-381.cu:4) and reaches the transcript only with plain values, so exact
+integer arithmetic mod p restates it.  Functions follow:
+    fs transcript / challenge      zkllm-src/fs_transcript.hpp:115-166, vrf_common.cuh:219-244
+    eq tensor                      zkllm-src/zkob_lookup.cuh:202-212, :247-268
+    FrTensor folds                 zkllm-src/fr-tensor.cu:542-652
+    inner-product rounds           zkllm-src/zkfc.cu:94-127, zkob_fc.cu:290-332
+    Hadamard / bracket rounds      zkllm-src/zkob_lookup.cuh:214-318, :321-425
+    lagrange3 / lagrange4          zkllm-src/vrf_common.cuh:130-140
+
+Pin status: the reference's own implementation of this stack needs a GPU even for scalar arithmetic
+(h_scalar launches a one-thread kernel, vrf_common.cuh:100-104), so it cannot run where there is no
+GPU.  The transcript half is pinned by the shared fs::Transcript golden vectors; the field half is
+exact integer arithmetic on the published modulus.  PARITY UNPINNED against the reference's CUDA code.
+"""
+import hashlib
+import struct
+
+P = 0x73eda753299d7d483339d80809a1d80553bda402fffe5bfeffffffff00000001
+TOP = 0x73eda753     # top limb of p (vrf_common.cuh:241)
+
+
+def to_bytes(x):
+    return int(x).to_bytes(32, "little")
+
+
+def from_bytes(b):
+    return int.from_bytes(b, "little")
+
+
+class Transcript:
+    """fs::Transcript (zkllm-src/fs_transcript.hpp:115-166)."""
+
+    def __init__(self, seed):
+        self.state = hashlib.sha256(seed.encode() if isinstance(seed, str) else seed).digest()
+
+    def absorb(self, label, data):
+        lb = label.encode()
+        self.state = hashlib.sha256(self.state + struct.pack("<I", len(lb)) + lb + struct.pack("<Q", len(data)) + data).digest()
+
+    def challenge_bytes(self):
+        out = hashlib.sha256(self.state + b"chal").digest()
+        self.state = hashlib.sha256(self.state + b"rtch").digest()
+        return out
+
+    def absorb_fr(self, label, x):
+        self.absorb(label, to_bytes(x))
+
+    def challenge_fr(self):
+        """fs_challenge_fr: eight LE limbs of the challenge bytes, top limb mod TOP, redraw on zero."""
+        while True:
+            b = self.challenge_bytes()
+            limbs = list(struct.unpack("<8I", b))
+            limbs[7] %= TOP
+            x = sum(l << (32 * i) for i, l in enumerate(limbs))
+            if x:
+                return x
+
+
+def eq_build(u):
+    E = [1]
+    for c in u:                       # bit i is the new top bit
+        E = [(1 - c) * e % P for e in E] + [c * e % P for e in E]
+    return E
+
+
+def mle_eval(t, u):
+    """Fr_me: pairs (2i, 2i+1) with u[0] first."""
+    t = list(t)
+    for x in u:
+        t = [(t[2 * i] + x * (t[2 * i + 1] - t[2 * i])) % P for i in range(len(t) // 2)]
+    return t[0]
+
+
+def partial_me(t, other, logd, window, u):
+    """FrTensor::partial_me on [other][2^logd][window], u[0] pairs adjacent windows."""
+    D = 1 << logd
+    t = list(t)
+    for x in u[:logd]:
+        Dn = D // 2
+        out = [0] * (other * Dn * window)
+        for o in range(other):
+            for d in range(Dn):
+                for w in range(window):
+                    a = t[(o * D + 2 * d) * window + w]
+                    b = t[(o * D + 2 * d + 1) * window + w]
+                    out[(o * Dn + d) * window + w] = (a + x * (b - a)) % P
+        t, D = out, Dn
+    return t
+
+
+def fold(t, w):
+    h = len(t) // 2
+    return [(t[i] + w * (t[i + h] - t[i])) % P for i in range(h)]
+
+
+def lagrange(evals, x):
+    """Value at x of the polynomial with the given evaluations at 0..len-1 (lagrange3 / lagrange4)."""
+    n, acc = len(evals), 0
+    for i, y in enumerate(evals):
+        num, den = 1, 1
+        for j in range(n):
+            if j != i:
+                num = num * (x - j) % P
+                den = den * (i - j) % P
+        acc = (acc + y * num * pow(den, -1, P)) % P
+    return acc
+
+
+def product_sumcheck(tr, cols, labels):
+    """Round loop shared by zkob_fc (2 columns), fs_hadamard (3) and fs_quartic (4): top variable first,
+    evaluations at t = 0..nc absorbed one by one under `labels`, challenge by fs_challenge_fr.
+    Returns (evals per round, challenges, final column values)."""
+    cols = [list(c) for c in cols]
+    nc, nt = len(cols), len(cols) + 1
+    evals, chals = [], []
+    while len(cols[0]) > 1:
+        h = len(cols[0]) // 2
+        ev = []
+        for t in range(nt):
+            s = 0
+            for i in range(h):
+                prod = 1
+                for c in cols:
+                    prod = prod * (c[i] + t * (c[i + h] - c[i])) % P
+                s += prod
+            ev.append(s % P)
+        for lb, e in zip(labels, ev):
+            tr.absorb_fr(lb, e)
+        x = tr.challenge_fr()
+        evals.append(ev)
+        chals.append(x)
+        cols = [fold(c, x) for c in cols]
+    return evals, chals, [c[0] for c in cols]

@@ -1,0 +1,119 @@
+"""Host-side mirror of the reference's BLS12-381 Fr prover pieces (its first proof stack) over the C ABI.
+
+Elements are the reference's Fr_t: eight little-endian 32-bit limbs holding a plain integer below P.
+Device arrays are torch int32 tensors of shape [n, 8]; points, challenges and results are Python ints.
+Names follow the reference: build_eq_tensor, k_fr_fold, FrTensor.partial_me / operator()(u),
+fs_hadamard, fs_quartic, the zkob_fc inner-product rounds (zkllm-src/zkob_lookup.cuh, fr-tensor.cu,
+zkob_fc.cu).  There is no CPU path: every function calls the CUDA library.
+"""
+import ctypes as C
+
+import numpy as np
+
+from ._lib import ZkhError  # noqa: F401
+
+P = 0x73eda753299d7d483339d80809a1d80553bda402fffe5bfeffffffff00000001
+
+
+def pack(vals):
+    """ints -> numpy uint32 [n, 8] limb array."""
+    out = np.empty((len(vals), 8), dtype=np.uint32)
+    for i, x in enumerate(vals):
+        out[i] = np.frombuffer(int(x).to_bytes(32, "little"), dtype=np.uint32)
+    return out
+
+
+def unpack(arr):
+    a = np.ascontiguousarray(arr, dtype=np.uint32).reshape(-1, 8)
+    return [int.from_bytes(row.tobytes(), "little") for row in a]
+
+
+def to_device(vals, device="cuda:0"):
+    import torch
+    a = vals if isinstance(vals, np.ndarray) else pack(vals)
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.uint32).view(np.int32)).to(device)
+
+
+def to_host(t):
+    return unpack(t.detach().cpu().numpy().view(np.uint32))
+
+
+def _pt(u):
+    return np.ascontiguousarray(pack(u)) if len(u) else np.zeros((1, 8), dtype=np.uint32)
+
+
+def _new(prover, n):
+    import torch
+    return torch.empty((n, 8), dtype=torch.int32, device="cuda:%d" % prover.device)
+
+
+def build_eq_tensor(prover, u):
+    """E[b] = prod_i (bit_i(b) ? u[i] : 1-u[i])  (zkllm-src/zkob_lookup.cuh:247-268)."""
+    out = _new(prover, 1 << len(u))
+    a = _pt(u)
+    prover._ck(prover._L.zkh_fr_eq_build(prover._h, a.ctypes.data, len(u), out.data_ptr()))
+    return out
+
+
+def fr_fold(prover, t, w):
+    """k_fr_fold: out[i] = t[i] + w*(t[i+h]-t[i])."""
+    h = t.shape[0] // 2
+    out = _new(prover, h)
+    a = _pt([w])
+    prover._ck(prover._L.zkh_fr_fold(prover._h, t.data_ptr(), h, a.ctypes.data, out.data_ptr()))
+    return out
+
+
+def partial_me(prover, t, u, cur_dim, window_size):
+    """FrTensor::partial_me(u, cur_dim, window_size) for cur_dim == 2^len(u)."""
+    if cur_dim != 1 << len(u):
+        raise ValueError("partial_me: cur_dim must equal 2^len(u)")
+    n = t.shape[0]
+    if n % (cur_dim * window_size):
+        raise ValueError("partial_me: size not divisible by cur_dim*window_size")
+    other = n // (cur_dim * window_size)
+    out = _new(prover, other * window_size)
+    a = _pt(u)
+    prover._ck(prover._L.zkh_fr_partial_me(prover._h, t.data_ptr(), other, len(u), window_size, a.ctypes.data,
+                                           out.data_ptr()))
+    return out
+
+
+def mle_eval(prover, t, u):
+    """FrTensor::operator()(u): multilinear extension of t at u, u[0] pairing adjacent elements."""
+    if t.shape[0] != 1 << len(u):
+        raise ValueError("mle_eval: size must equal 2^len(u)")
+    a = _pt(u)
+    out = (C.c_uint8 * 32)()
+    prover._ck(prover._L.zkh_fr_mle_eval(prover._h, t.data_ptr(), a.ctypes.data, len(u), out))
+    return int.from_bytes(bytes(out), "little")
+
+
+def multi_dim_me(prover, t, us, shape):
+    """FrTensor::multi_dim_me (zkllm-src/fr-tensor.cu:634-643): fold the last dimension first."""
+    if len(us) != len(shape):
+        raise ValueError("Incompatible dimensions")
+    for u, d in zip(reversed(us[1:]), reversed(shape[1:])):
+        t = partial_me(prover, t, u, d, 1)
+    return mle_eval(prover, t, us[0]) if us else to_host(t[:1])[0]
+
+
+def product_sumcheck(prover, tr, cols, labels):
+    """The round loop of zkob_fc's inner product (2 columns; labels p0 p1 p2), fs_hadamard (3; hp0..hp3)
+    and fs_quartic (4; tag+p0..p4): returns (evals[rounds][nt], challenges, finals) as ints and
+    advances ``tr`` exactly as the reference's transcript advances."""
+    nc = len(cols)
+    n = cols[0].shape[0]
+    logn = n.bit_length() - 1
+    if n != 1 << logn or len(labels) != nc + 1:
+        raise ValueError("product_sumcheck: power-of-two columns and nc+1 labels")
+    ptrs = (C.c_void_p * nc)(*[c.data_ptr() for c in cols])
+    labs = (C.c_char_p * (nc + 1))(*[l.encode() for l in labels])
+    ev = np.zeros((logn, nc + 1, 8), dtype=np.uint32)
+    ch = np.zeros((logn, 8), dtype=np.uint32)
+    fin = np.zeros((nc, 8), dtype=np.uint32)
+    st = (C.c_uint8 * 32)(*tr.state)
+    prover._ck(prover._L.zkh_fr_sumcheck(prover._h, ptrs, nc, logn, labs, st, ev.ctypes.data, ch.ctypes.data,
+                                         fin.ctypes.data))
+    tr.state = bytes(st)
+    return [unpack(e) for e in ev], unpack(ch), unpack(fin)
