@@ -137,3 +137,87 @@ def product_sumcheck(tr, cols, labels):
         chals.append(x)
         cols = [fold(c, x) for c in cols]
     return evals, chals, [c[0] for c in cols]
+
+
+class ReferenceFr:
+    """ctypes window on oracle/_ref/libfrref.so: the unmodified reference's Fr stack (GPU machine only)."""
+
+    PATH = __import__("os").path.join(__import__("os").path.dirname(__import__("os").path.abspath(__file__)), "_ref", "libfrref.so")
+
+    @classmethod
+    def available(cls):
+        import os
+        return os.path.exists(cls.PATH)
+
+    def __init__(self):
+        import ctypes
+        self.C = ctypes
+        self.lib = ctypes.CDLL(self.PATH)
+
+    def gpu_available(self):
+        return bool(self.lib.refA_gpu_available())
+
+    @staticmethod
+    def _pack(vals):
+        return b"".join(to_bytes(v) for v in vals)
+
+    @staticmethod
+    def _unpack(buf, n):
+        b = bytes(buf)
+        return [from_bytes(b[32 * i:32 * i + 32]) for i in range(n)]
+
+    def _out(self, n):
+        return (self.C.c_uint8 * (32 * max(n, 1)))()
+
+    def fold(self, t, w):
+        out = self._out(len(t) // 2)
+        assert self.lib.refA_fold(self._pack(t), len(t), to_bytes(w), out) == 0
+        return self._unpack(out, len(t) // 2)
+
+    def eq_build(self, u):
+        out = self._out(1 << len(u))
+        assert self.lib.refA_eq(self._pack(u), len(u), out) == 0
+        return self._unpack(out, 1 << len(u))
+
+    def partial_me(self, t, u, cur_dim, window):
+        out = self._out(len(t))
+        n = self.lib.refA_partial_me(self._pack(t), len(t), self._pack(u), len(u), cur_dim, window, out)
+        assert n >= 0
+        return self._unpack(out, n)
+
+    def mle_eval(self, t, u):
+        out = self._out(1)
+        assert self.lib.refA_me(self._pack(t), len(t), self._pack(u), len(u), out) == 0
+        return self._unpack(out, 1)[0]
+
+    def _rounds(self, fn, st, cols, nt, *pre):
+        n = len(cols[0])
+        logn = n.bit_length() - 1
+        s = (self.C.c_uint8 * 32)(*st)
+        ev, ws, fin = self._out(logn * nt), self._out(logn), self._out(len(cols))
+        assert fn(s, *pre, *[self._pack(c) for c in cols], n, ev, ws, fin) == 0
+        e = self._unpack(ev, logn * nt)
+        return bytes(s), [e[i * nt:(i + 1) * nt] for i in range(logn)], self._unpack(ws, logn), self._unpack(fin, len(cols))
+
+    def ip_rounds(self, st, a, b):
+        return self._rounds(self.lib.refA_ip_rounds, st, [a, b], 3)
+
+    def hadamard(self, st, E, S, U):
+        """fs_hadamard: terminals are S and U only (E's is verifier-computed)."""
+        n = len(E)
+        logn = n.bit_length() - 1
+        s = (self.C.c_uint8 * 32)(*st)
+        ev, ws, fin = self._out(logn * 4), self._out(logn), self._out(2)
+        assert self.lib.refA_hadamard(s, self._pack(E), self._pack(S), self._pack(U), n, ev, ws, fin) == 0
+        e = self._unpack(ev, logn * 4)
+        return bytes(s), [e[i * 4:(i + 1) * 4] for i in range(logn)], self._unpack(ws, logn), self._unpack(fin, 2)
+
+    def quartic(self, st, tag, E, A, B, Cc):
+        n = len(E)
+        logn = n.bit_length() - 1
+        s = (self.C.c_uint8 * 32)(*st)
+        ev, ws, fin = self._out(logn * 5), self._out(logn), self._out(3)
+        assert self.lib.refA_quartic(s, tag.encode(), self._pack(E), self._pack(A), self._pack(B), self._pack(Cc), n,
+                                     ev, ws, fin) == 0
+        e = self._unpack(ev, logn * 5)
+        return bytes(s), [e[i * 5:(i + 1) * 5] for i in range(logn)], self._unpack(ws, logn), self._unpack(fin, 3)

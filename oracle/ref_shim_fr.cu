@@ -1,0 +1,143 @@
+// C window on the UNMODIFIED reference's BLS12-381 Fr stack (test infrastructure; needs a GPU to run,
+// because that stack does even scalar arithmetic in one-thread kernels).  Built by `make -C oracle ref_fr`
+// into oracle/_ref/libfrref.so from the reference sources where they lie; nothing is copied.
+//
+// Exposes the reference's own: k_fr_fold, build_eq_tensor, FrTensor::partial_me / operator()(u),
+// fs_hadamard, fs_quartic, and the zkob_fc inner-product rounds driven with the reference's
+// zkip_poly_kernel / zkip_reduce_kernel, FrTensor::sum and lagrange-free host glue
+// (zkllm-src/zkob_fc.cu:290-332 is inside that program's main flow, so the loop is restated here
+// around the reference kernels).
+#include "zkob_lookup.cuh"
+#include "zkfc.cuh"
+
+// defined in the reference's zkfc.cu (zkob_fc.cu declares them the same way before use)
+KERNEL void zkip_poly_kernel(GLOBAL Fr_t* a, GLOBAL Fr_t* b, GLOBAL Fr_t* out0, GLOBAL Fr_t* out1, GLOBAL Fr_t* out2,
+                             uint N_in, uint N_out);
+KERNEL void zkip_reduce_kernel(GLOBAL Fr_t* a, GLOBAL Fr_t* b, GLOBAL Fr_t* new_a, GLOBAL Fr_t* new_b, Fr_t v, uint N_in,
+                               uint N_out);
+
+namespace {
+std::vector<Fr_t> vec_from(const uint32_t* p, uint32_t n) {
+    std::vector<Fr_t> v(n);
+    memcpy(v.data(), p, (size_t)n * 32);
+    return v;
+}
+fs::Transcript tr_from(const uint8_t st[32]) {
+    fs::Transcript tr("x");
+    memcpy(tr.state, st, 32);
+    return tr;
+}
+void to_host(const FrTensor& t, uint32_t* out) {
+    cudaMemcpy(out, t.gpu_data, (size_t)t.size * 32, cudaMemcpyDeviceToHost);
+}
+}  // namespace
+
+extern "C" {
+
+int refA_gpu_available() {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
+}
+int refA_fold(const uint32_t* in, uint32_t n, const uint32_t* w, uint32_t* out) {
+    FrTensor t(n, (const Fr_t*)in), o(n / 2);
+    Fr_t wv; memcpy(&wv, w, 32);
+    k_fr_fold<<<(n / 2 + 255) / 256, 256>>>(t.gpu_data, wv, o.gpu_data, n / 2);
+    cudaDeviceSynchronize();
+    to_host(o, out);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int refA_eq(const uint32_t* u, uint32_t v, uint32_t* out) {
+    FrTensor E = build_eq_tensor(vec_from(u, v));
+    to_host(E, out);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int refA_partial_me(const uint32_t* t, uint32_t n, const uint32_t* u, uint32_t nu, uint32_t cur_dim, uint32_t window,
+                    uint32_t* out) {
+    try {
+        FrTensor T(n, (const Fr_t*)t);
+        FrTensor R = T.partial_me(vec_from(u, nu), cur_dim, window);
+        to_host(R, out);
+        return (int)R.size;
+    } catch (...) { return -1; }
+}
+int refA_me(const uint32_t* t, uint32_t n, const uint32_t* u, uint32_t nu, uint32_t* out) {
+    try {
+        FrTensor T(n, (const Fr_t*)t);
+        Fr_t y = T(vec_from(u, nu));
+        memcpy(out, &y, 32);
+        return 0;
+    } catch (...) { return -1; }
+}
+// fs_hadamard (zkob_lookup.cuh:297-318): evals 4 per round, ws the challenges, terminals S, U
+int refA_hadamard(uint8_t st[32], const uint32_t* E, const uint32_t* S, const uint32_t* U, uint32_t n, uint32_t* evals,
+                  uint32_t* ws, uint32_t* fin) {
+    try {
+        FrTensor e(n, (const Fr_t*)E), s(n, (const Fr_t*)S), u(n, (const Fr_t*)U);
+        fs::Transcript tr = tr_from(st);
+        std::vector<Fr_t> w;
+        HadamardProof hp;
+        fs_hadamard(F_ZERO, e, s, u, tr, w, hp, false);
+        memcpy(evals, hp.ev.data(), hp.ev.size() * 32);
+        memcpy(ws, w.data(), w.size() * 32);
+        memcpy(fin, &hp.S_f2, 32); memcpy(fin + 8, &hp.U_f2, 32);
+        memcpy(st, tr.state, 32);
+        return 0;
+    } catch (...) { return -1; }
+}
+// fs_quartic (zkob_lookup.cuh:402-425)
+int refA_quartic(uint8_t st[32], const char* tag, const uint32_t* E, const uint32_t* A, const uint32_t* B,
+                 const uint32_t* Cc, uint32_t n, uint32_t* evals, uint32_t* ws, uint32_t* fin) {
+    try {
+        FrTensor e(n, (const Fr_t*)E), a(n, (const Fr_t*)A), b(n, (const Fr_t*)B), c(n, (const Fr_t*)Cc);
+        fs::Transcript tr = tr_from(st);
+        std::vector<Fr_t> w;
+        QuarticProof qp;
+        fs_quartic(F_ZERO, e, a, b, c, tr, tag, w, qp, false);
+        memcpy(evals, qp.ev.data(), qp.ev.size() * 32);
+        memcpy(ws, w.data(), w.size() * 32);
+        memcpy(fin, &qp.A_f, 32); memcpy(fin + 8, &qp.B_f, 32); memcpy(fin + 16, &qp.C_f, 32);
+        memcpy(st, tr.state, 32);
+        return 0;
+    } catch (...) { return -1; }
+}
+// inner-product rounds with the reference kernels (zkfc.cu:94-127) and the transcript schedule of
+// zkob_fc.cu:290-332 (non-private mode): absorb p0, p1, p2; challenge; reduce.
+int refA_ip_rounds(uint8_t st[32], const uint32_t* a, const uint32_t* b, uint32_t n, uint32_t* evals, uint32_t* xs,
+                   uint32_t* fin) {
+    try {
+        FrTensor A(n, (const Fr_t*)a), B(n, (const Fr_t*)b);
+        fs::Transcript tr = tr_from(st);
+        Fr_t *da = nullptr, *db = nullptr, *da2 = nullptr, *db2 = nullptr;
+        cudaMalloc(&da, (size_t)n * 32); cudaMalloc(&db, (size_t)n * 32);
+        cudaMalloc(&da2, (size_t)n * 32); cudaMalloc(&db2, (size_t)n * 32);
+        cudaMemcpy(da, A.gpu_data, (size_t)n * 32, cudaMemcpyDeviceToDevice);
+        cudaMemcpy(db, B.gpu_data, (size_t)n * 32, cudaMemcpyDeviceToDevice);
+        uint32_t sz = n, r = 0;
+        while (sz > 1) {
+            uint32_t N_out = sz / 2;
+            FrTensor o0(N_out), o1(N_out), o2(N_out);
+            zkip_poly_kernel<<<(N_out + 63) / 64, 64>>>(da, db, o0.gpu_data, o1.gpu_data, o2.gpu_data, sz, N_out);
+            cudaDeviceSynchronize();
+            Fr_t c0 = o0.sum(), c1 = o1.sum(), c2 = o2.sum();
+            Fr_t p0 = c0;
+            Fr_t p1 = h_scalar(h_scalar(c0, c1, 0), c2, 0);
+            Fr_t p2 = h_scalar(h_scalar(c0, h_scalar(F_TWO, c1, 2), 0), h_scalar(h_scalar(F_TWO, F_TWO, 2), c2, 2), 0);
+            absorb_fr(tr, "p0", p0); absorb_fr(tr, "p1", p1); absorb_fr(tr, "p2", p2);
+            Fr_t x = fs_challenge_fr(tr);
+            memcpy(evals + (size_t)r * 24, &p0, 32); memcpy(evals + (size_t)r * 24 + 8, &p1, 32);
+            memcpy(evals + (size_t)r * 24 + 16, &p2, 32);
+            memcpy(xs + (size_t)r * 8, &x, 32);
+            zkip_reduce_kernel<<<(N_out + 63) / 64, 64>>>(da, db, da2, db2, x, sz, N_out);
+            cudaDeviceSynchronize();
+            std::swap(da, da2); std::swap(db, db2);
+            sz = N_out; r++;
+        }
+        cudaMemcpy(fin, da, 32, cudaMemcpyDeviceToHost);
+        cudaMemcpy(fin + 8, db, 32, cudaMemcpyDeviceToHost);
+        cudaFree(da); cudaFree(db); cudaFree(da2); cudaFree(db2);
+        memcpy(st, tr.state, 32);
+        return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    } catch (...) { return -1; }
+}
+
+}  // extern "C"
