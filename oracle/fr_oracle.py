@@ -15,8 +15,11 @@ integer arithmetic mod p restates it.  Functions follow:
 
 Pin status: the reference's own implementation of this stack needs a GPU even for scalar arithmetic
 (h_scalar launches a one-thread kernel, vrf_common.cuh:100-104), so it cannot run where there is no
-GPU.  The transcript half is pinned by the shared fs::Transcript golden vectors; the field half is
-exact integer arithmetic on the published modulus.  PARITY UNPINNED against the reference's CUDA code.
+GPU.  On a GPU machine this restatement is pinned against the UNMODIFIED reference compiled into
+oracle/_ref/libfrref.so (ReferenceFr below; tests/test_fr_reference_gpu.py compares fold, eq tensor,
+partial_me, operator()(u), the inner-product rounds, fs_hadamard and fs_quartic value for value,
+transcript state included).  Without a GPU only the transcript half is pinned (shared fs::Transcript
+golden vectors); the field half is exact integer arithmetic on the published modulus.
 """
 import hashlib
 import struct
