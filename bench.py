@@ -398,6 +398,186 @@ def run_suite_gadgets(args):
     print(json.dumps(line), flush=True)
 
 
+def run_suite_fr(args):
+    """--suite-fr: the BLS12-381 Fr kernels at the reference's layer sizes (SURVEY-style sizes: Hadamard /
+    bracket sumchecks over D = 2^22, the fully connected layer's partial evaluations and inner-product
+    rounds for 128 x 1024 . 1024 x 1024), beside the reference's own CUDA code on the same inputs."""
+    import torch
+    import zkh_import
+    zk = zkh_import.load()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import fr_oracle as fo
+    torch.cuda.set_device(0)
+    prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+    fr = zk.fr
+    refA = fo.ReferenceFr() if (fo.ReferenceFr.available() and not args.no_ref_cuda) else None
+    if refA is not None and not refA.gpu_available():
+        refA = None
+    rng = np.random.default_rng(0)
+
+    def rand_fr(n, small=False):
+        a = rng.integers(0, 1 << 32, (n, 8), dtype=np.uint64).astype(np.uint32)
+        if small:
+            a[:, 1:] = 0
+            a[:, 0] &= 0xFFFFF
+        a[:, 7] %= 0x73EDA753
+        return a
+
+    def wall(fn, reps=3):
+        best = 1e30
+        for _ in range(reps):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize()
+            best = min(best, (time.perf_counter() - t0) * 1e3)
+        return best
+
+    gm = fr.mul_throughput(prover, 4096)
+    print(json.dumps({"suite": "Fr Montgomery products, 4 chains per thread", "gmul_per_s": gm}), flush=True)
+
+    logD = args.fr_logd
+    cols_h = [rand_fr(1 << logD, small=(k > 0)) for k in range(4)]
+    cols = [fr.to_device(c) for c in cols_h]
+    for nc, labels, name in [(3, ["hp0", "hp1", "hp2", "hp3"], "fs_hadamard"), (4, ["qp%d" % i for i in range(5)], "fs_quartic")]:
+        out = {}
+
+        def run():
+            tr = zk.Transcript("fr-bench")
+            out["r"] = fr.product_sumcheck(prover, tr, cols[:nc], labels)
+            out["st"] = tr.state
+        run()
+        ms = wall(run)
+        n = 1 << logD
+        # products per sumcheck: (nc+1) evaluation points x (nc-1) products per pair, plus nc products per pair for
+        # the bind; pairs summed over the rounds = n
+        muls = n * ((nc + 1) * (nc - 1) + nc)
+        line = {"suite": "%s over D=2^%d (%d columns, %d rounds)" % (name, logD, nc, logD), "ms": ms,
+                "algorithmic_GBps": 96.0 * nc * n / ms / 1e6, "gmul_per_s": muls / ms / 1e6,
+                "fraction_of_probe_rate": muls / ms / 1e6 / gm}
+        if refA is not None:
+            st0 = zk.Transcript("fr-bench").state
+            if nc == 3:
+                st, ev, ws, fin = refA.hadamard(st0, *cols_h[:3])
+            else:
+                st, ev, ws, fin = refA.quartic(st0, "q", *cols_h)
+            line.update({"reference_cuda_ms": refA.ms.value, "speedup_vs_reference_cuda": refA.ms.value / ms,
+                         "same_transcript": bool(st == out["st"] and ev == out["r"][0] and ws == out["r"][1])})
+        print(json.dumps(line), flush=True)
+    del cols
+    torch.cuda.empty_cache()
+
+    # fully connected layer (BASELINE configs[0] shape, padded): X 128 x 1024, W 1024 x 1024
+    B, IN, OUT = 128, 1024, 1024
+    Xh, Wh = rand_fr(B * IN, small=True), rand_fr(IN * OUT, small=True)
+    X, W = fr.to_device(Xh), fr.to_device(Wh)
+    ub = fo.ReferenceFr._unpack(rand_fr(7).tobytes(), 7)
+    uo = fo.ReferenceFr._unpack(rand_fr(10).tobytes(), 10)
+    hold = {}
+
+    def fc():
+        hold["xr"] = fr.partial_me(prover, X, ub, B, IN)
+        hold["wr"] = fr.partial_me(prover, W, uo, OUT, 1)
+        tr = zk.Transcript("fc-bench")
+        hold["sc"] = fr.product_sumcheck(prover, tr, [hold["xr"], hold["wr"]], ["p0", "p1", "p2"])
+        u_in = list(reversed(hold["sc"][1]))
+        hold["cx"] = fr.multi_dim_me(prover, X, [ub, u_in], [B, IN])
+        hold["cw"] = fr.multi_dim_me(prover, W, [u_in, uo], [IN, OUT])
+        hold["st"] = tr.state
+    fc()
+    ms = wall(fc)
+    line = {"suite": "fully connected layer 128x1024 . 1024x1024 over Fr: two partial evaluations, %d inner-product rounds, two multi_dim_me claims" % 10,
+            "ms": ms, "terminal_claims_consistent": bool(hold["sc"][2] == [hold["cx"], hold["cw"]])}
+    if refA is not None:
+        t = 0.0
+        xr = refA.partial_me(Xh, ub, B, IN); t += refA.ms.value
+        wr = refA.partial_me(Wh, uo, OUT, 1); t += refA.ms.value
+        st, ev, xs, fin = refA.ip_rounds(zk.Transcript("fc-bench").state, xr, wr); t += refA.ms.value
+        u_in = list(reversed(xs))
+        # the two terminal claims: fold the last dimension, then evaluate (multi_dim_me)
+        r1 = refA.partial_me(Xh, u_in, IN, 1); t += refA.ms.value
+        r2 = refA.partial_me(Wh, uo, OUT, 1); t += refA.ms.value
+        line.update({"reference_cuda_ms": t, "speedup_vs_reference_cuda": t / ms,
+                     "same_transcript": bool(st == hold["st"] and ev == hold["sc"][0] and fin == hold["sc"][2])})
+    print(json.dumps(line), flush=True)
+
+
+def run_profile_case(args):
+    """--profile-case NAME: one small, self-terminating invocation of one kernel family (a few hundred MB on
+    the device, inputs larger than L2, two launches) - the command the ncu summaries under profiles/ are
+    captured from.  Prints the CUDA-event time of the second invocation."""
+    import torch
+    import zkh_import
+    zk = zkh_import.load()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle import Oracle
+    orc = Oracle()
+    torch.cuda.set_device(0)
+    prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+    name = args.profile_case
+    rng = np.random.default_rng(1)
+
+    def gl_rand(n):
+        return zk.p3.to_device(rng.integers(0, 0xFFFFFFFF00000001, n, dtype=np.uint64))
+
+    if name in ("ntt", "merkle", "commit"):
+        c = gl_rand(1 << 23)
+        cw = torch.empty(1 << 24, dtype=torch.int64, device="cuda")
+        if name == "ntt":
+            fn = lambda: prover.rs_encode_gpu_dev(c, 1, cw)
+        elif name == "merkle":
+            prover.rs_encode_gpu_dev(c, 1, cw)
+            fn = lambda: prover.merkle_build_dev(cw, keep_tree=False)
+        else:
+            fn = lambda: prover.commit_gpu_rootonly(c, 1)
+    elif name == "open":
+        c = gl_rand(1 << 22)
+        z = rng.integers(0, 0xFFFFFFFF00000001, 22, dtype=np.uint64)
+        y = prover.eval_h_gpu(c, z)
+        fn = lambda: prover.prove_eval_dev(c, z, y, 1, 24)
+    elif name == "gkr":
+        p, q = gl_rand(1 << 23), gl_rand(1 << 23)
+        fn = lambda: prover.gkr_prove(zk.Transcript("prof"), "lug-gA", p, q, True)
+    elif name == "hist":
+        idx = torch.from_numpy(np.clip(np.rint(rng.normal(32768, 1024, 1 << 25)), 0, 65535).astype(np.int32)).cuda()
+        fn = lambda: prover.histogram(idx, 1 << 16)
+    elif name == "inv":
+        a = gl_rand(1 << 24)
+        fn = lambda: prover.inv_all_add(a, 12345)
+    elif name == "sumcheck3":
+        cols = [gl_rand(1 << 24) for _ in range(3)]
+        fn = lambda: prover.sc_prove_gpu(zk.Transcript("prof"), "sc", cols, zk.F_PROD3, 4)
+    elif name in ("wide_dg", "wide_do", "wide_dp"):
+        f = {"wide_dp": 6, "wide_dg": 7, "wide_do": 11}[name]
+        nc, nlam = {6: (12, 6), 7: (30, 18), 11: (57, 49)}[f]
+        cols = [gl_rand(1 << 20) for _ in range(nc)]
+        lam = rng.integers(0, 0xFFFFFFFF00000001, nlam, dtype=np.uint64)
+        fn = lambda: prover.sc5_run(zk.Transcript("prof"), "hwl", cols, f, lam)
+    elif name in ("fr_hp3", "fr_ip", "fr_pme"):
+        def rand_fr(n):
+            a = rng.integers(0, 1 << 32, (n, 8), dtype=np.uint64).astype(np.uint32)
+            a[:, 7] %= 0x73EDA753
+            return zk.fr.to_device(a)
+        if name == "fr_pme":
+            W = rand_fr(1 << 22)
+            u = [int(x) for x in rng.integers(1, 1 << 62, 11)]
+            fn = lambda: zk.fr.partial_me(prover, W, u, 1 << 11, 1)
+        else:
+            nc = 3 if name == "fr_hp3" else 2
+            cols = [rand_fr(1 << 21) for _ in range(nc)]
+            fn = lambda: zk.fr.product_sumcheck(prover, zk.Transcript("prof"), cols, ["l%d" % t for t in range(nc + 1)])
+    else:
+        raise SystemExit("unknown profile case " + name)
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": name, "ms": e0.elapsed_time(e1)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -411,12 +591,19 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
+    ap.add_argument("--profile-case", default=None, help="one small kernel-family invocation (for ncu captures)")
+    ap.add_argument("--suite-fr", action="store_true", help="BLS12-381 Fr kernels beside the reference's CUDA code")
+    ap.add_argument("--fr-logd", type=int, default=22)
     ap.add_argument("--suite-gadgets", action="store_true", help="configs[0]/[2] through the gadget-level provers")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.profile_case:
+        return run_profile_case(args)
     if args.suite:
         return run_suite(args)
+    if args.suite_fr:
+        return run_suite_fr(args)
     if args.suite_gadgets:
         return run_suite_gadgets(args)
 

@@ -305,6 +305,10 @@ ZKH_API int zkh_fr_mle_eval(zkh_ctx* ctx, const void* t_dev, const void* u, uint
  * fs_challenge_fr does (zkllm-src/vrf_common.cuh:233-244).  The columns are left untouched.
  *   state   transcript in/out;  evals: logn*nt*32 bytes out;  chals: logn*32 bytes out (round order);
  *   finals  nc*32 bytes out: every column bound at all challenges (may be NULL). */
+/* Measured rate of Montgomery products on this GPU in 10^9 per second (four independent chains per
+ * thread, grid = 8 CTAs per SM): the integer-pipe ceiling the Fr kernels are read against, as
+ * zkllm-src/p3_field_bench.cu does for its two fields. */
+ZKH_API int zkh_fr_mul_throughput(zkh_ctx* ctx, uint32_t iters, double* gmul_per_s);
 ZKH_API int zkh_fr_sumcheck(zkh_ctx* ctx, const void* const* cols_dev, int nc, uint32_t logn,
                     const char* const* labels, uint8_t state[32], void* evals, void* chals, void* finals);
 

@@ -156,12 +156,15 @@ class ReferenceFr:
         import ctypes
         self.C = ctypes
         self.lib = ctypes.CDLL(self.PATH)
+        self.ms = ctypes.c_double(0)      # duration of the last timed reference call, milliseconds
 
     def gpu_available(self):
         return bool(self.lib.refA_gpu_available())
 
     @staticmethod
     def _pack(vals):
+        if hasattr(vals, "tobytes"):            # numpy limb array [n, 8] uint32
+            return vals.tobytes()
         return b"".join(to_bytes(v) for v in vals)
 
     @staticmethod
@@ -184,7 +187,7 @@ class ReferenceFr:
 
     def partial_me(self, t, u, cur_dim, window):
         out = self._out(len(t))
-        n = self.lib.refA_partial_me(self._pack(t), len(t), self._pack(u), len(u), cur_dim, window, out)
+        n = self.lib.refA_partial_me(self._pack(t), len(t), self._pack(u), len(u), cur_dim, window, out, self.C.byref(self.ms))
         assert n >= 0
         return self._unpack(out, n)
 
@@ -198,7 +201,7 @@ class ReferenceFr:
         logn = n.bit_length() - 1
         s = (self.C.c_uint8 * 32)(*st)
         ev, ws, fin = self._out(logn * nt), self._out(logn), self._out(len(cols))
-        assert fn(s, *pre, *[self._pack(c) for c in cols], n, ev, ws, fin) == 0
+        assert fn(s, *pre, *[self._pack(c) for c in cols], n, ev, ws, fin, self.C.byref(self.ms)) == 0
         e = self._unpack(ev, logn * nt)
         return bytes(s), [e[i * nt:(i + 1) * nt] for i in range(logn)], self._unpack(ws, logn), self._unpack(fin, len(cols))
 
@@ -211,7 +214,7 @@ class ReferenceFr:
         logn = n.bit_length() - 1
         s = (self.C.c_uint8 * 32)(*st)
         ev, ws, fin = self._out(logn * 4), self._out(logn), self._out(2)
-        assert self.lib.refA_hadamard(s, self._pack(E), self._pack(S), self._pack(U), n, ev, ws, fin) == 0
+        assert self.lib.refA_hadamard(s, self._pack(E), self._pack(S), self._pack(U), n, ev, ws, fin, self.C.byref(self.ms)) == 0
         e = self._unpack(ev, logn * 4)
         return bytes(s), [e[i * 4:(i + 1) * 4] for i in range(logn)], self._unpack(ws, logn), self._unpack(fin, 2)
 
@@ -221,6 +224,6 @@ class ReferenceFr:
         s = (self.C.c_uint8 * 32)(*st)
         ev, ws, fin = self._out(logn * 5), self._out(logn), self._out(3)
         assert self.lib.refA_quartic(s, tag.encode(), self._pack(E), self._pack(A), self._pack(B), self._pack(Cc), n,
-                                     ev, ws, fin) == 0
+                                     ev, ws, fin, self.C.byref(self.ms)) == 0
         e = self._unpack(ev, logn * 5)
         return bytes(s), [e[i * 5:(i + 1) * 5] for i in range(logn)], self._unpack(ws, logn), self._unpack(fin, 3)

@@ -9,6 +9,7 @@
 // around the reference kernels).
 #include "zkob_lookup.cuh"
 #include "zkfc.cuh"
+#include <chrono>
 
 // defined in the reference's zkfc.cu (zkob_fc.cu declares them the same way before use)
 KERNEL void zkip_poly_kernel(GLOBAL Fr_t* a, GLOBAL Fr_t* b, GLOBAL Fr_t* out0, GLOBAL Fr_t* out1, GLOBAL Fr_t* out2,
@@ -26,6 +27,9 @@ fs::Transcript tr_from(const uint8_t st[32]) {
     fs::Transcript tr("x");
     memcpy(tr.state, st, 32);
     return tr;
+}
+double now_ms() {
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 void to_host(const FrTensor& t, uint32_t* out) {
     cudaMemcpy(out, t.gpu_data, (size_t)t.size * 32, cudaMemcpyDeviceToHost);
@@ -52,10 +56,14 @@ int refA_eq(const uint32_t* u, uint32_t v, uint32_t* out) {
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 int refA_partial_me(const uint32_t* t, uint32_t n, const uint32_t* u, uint32_t nu, uint32_t cur_dim, uint32_t window,
-                    uint32_t* out) {
+                    uint32_t* out, double* ms_out) {
     try {
         FrTensor T(n, (const Fr_t*)t);
+        cudaDeviceSynchronize();
+        double t0 = now_ms();
         FrTensor R = T.partial_me(vec_from(u, nu), cur_dim, window);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = now_ms() - t0;
         to_host(R, out);
         return (int)R.size;
     } catch (...) { return -1; }
@@ -70,13 +78,17 @@ int refA_me(const uint32_t* t, uint32_t n, const uint32_t* u, uint32_t nu, uint3
 }
 // fs_hadamard (zkob_lookup.cuh:297-318): evals 4 per round, ws the challenges, terminals S, U
 int refA_hadamard(uint8_t st[32], const uint32_t* E, const uint32_t* S, const uint32_t* U, uint32_t n, uint32_t* evals,
-                  uint32_t* ws, uint32_t* fin) {
+                  uint32_t* ws, uint32_t* fin, double* ms_out) {
     try {
         FrTensor e(n, (const Fr_t*)E), s(n, (const Fr_t*)S), u(n, (const Fr_t*)U);
         fs::Transcript tr = tr_from(st);
         std::vector<Fr_t> w;
         HadamardProof hp;
+        cudaDeviceSynchronize();
+        double t0 = now_ms();
         fs_hadamard(F_ZERO, e, s, u, tr, w, hp, false);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = now_ms() - t0;
         memcpy(evals, hp.ev.data(), hp.ev.size() * 32);
         memcpy(ws, w.data(), w.size() * 32);
         memcpy(fin, &hp.S_f2, 32); memcpy(fin + 8, &hp.U_f2, 32);
@@ -86,13 +98,17 @@ int refA_hadamard(uint8_t st[32], const uint32_t* E, const uint32_t* S, const ui
 }
 // fs_quartic (zkob_lookup.cuh:402-425)
 int refA_quartic(uint8_t st[32], const char* tag, const uint32_t* E, const uint32_t* A, const uint32_t* B,
-                 const uint32_t* Cc, uint32_t n, uint32_t* evals, uint32_t* ws, uint32_t* fin) {
+                 const uint32_t* Cc, uint32_t n, uint32_t* evals, uint32_t* ws, uint32_t* fin, double* ms_out) {
     try {
         FrTensor e(n, (const Fr_t*)E), a(n, (const Fr_t*)A), b(n, (const Fr_t*)B), c(n, (const Fr_t*)Cc);
         fs::Transcript tr = tr_from(st);
         std::vector<Fr_t> w;
         QuarticProof qp;
+        cudaDeviceSynchronize();
+        double t0 = now_ms();
         fs_quartic(F_ZERO, e, a, b, c, tr, tag, w, qp, false);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = now_ms() - t0;
         memcpy(evals, qp.ev.data(), qp.ev.size() * 32);
         memcpy(ws, w.data(), w.size() * 32);
         memcpy(fin, &qp.A_f, 32); memcpy(fin + 8, &qp.B_f, 32); memcpy(fin + 16, &qp.C_f, 32);
@@ -103,7 +119,7 @@ int refA_quartic(uint8_t st[32], const char* tag, const uint32_t* E, const uint3
 // inner-product rounds with the reference kernels (zkfc.cu:94-127) and the transcript schedule of
 // zkob_fc.cu:290-332 (non-private mode): absorb p0, p1, p2; challenge; reduce.
 int refA_ip_rounds(uint8_t st[32], const uint32_t* a, const uint32_t* b, uint32_t n, uint32_t* evals, uint32_t* xs,
-                   uint32_t* fin) {
+                   uint32_t* fin, double* ms_out) {
     try {
         FrTensor A(n, (const Fr_t*)a), B(n, (const Fr_t*)b);
         fs::Transcript tr = tr_from(st);
@@ -113,6 +129,8 @@ int refA_ip_rounds(uint8_t st[32], const uint32_t* a, const uint32_t* b, uint32_
         cudaMemcpy(da, A.gpu_data, (size_t)n * 32, cudaMemcpyDeviceToDevice);
         cudaMemcpy(db, B.gpu_data, (size_t)n * 32, cudaMemcpyDeviceToDevice);
         uint32_t sz = n, r = 0;
+        cudaDeviceSynchronize();
+        double t0 = now_ms();
         while (sz > 1) {
             uint32_t N_out = sz / 2;
             FrTensor o0(N_out), o1(N_out), o2(N_out);
@@ -132,6 +150,8 @@ int refA_ip_rounds(uint8_t st[32], const uint32_t* a, const uint32_t* b, uint32_
             std::swap(da, da2); std::swap(db, db2);
             sz = N_out; r++;
         }
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = now_ms() - t0;
         cudaMemcpy(fin, da, 32, cudaMemcpyDeviceToHost);
         cudaMemcpy(fin + 8, db, 32, cudaMemcpyDeviceToHost);
         cudaFree(da); cudaFree(db); cudaFree(da2); cudaFree(db2);

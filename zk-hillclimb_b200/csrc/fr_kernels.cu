@@ -276,6 +276,16 @@ fr_pme_rows_kernel(const Fr* t, const Fr* eq, size_t other, uint32_t D, Fr* out)
     }
 }
 
+// integer-pipe probe: four independent chains of Montgomery products per thread
+__global__ void __launch_bounds__(256) fr_mul_probe_kernel(Fr seed, uint32_t iters, Fr* out) {
+    Fr a = seed, b = seed, c = seed, d = seed;
+    a.v[0] ^= threadIdx.x; b.v[1] ^= blockIdx.x; c.v[2] ^= threadIdx.x * 7u; d.v[3] ^= blockIdx.x * 5u;
+    for (uint32_t i = 0; i < iters; i++) {
+        a = fr_mmul(a, b); b = fr_mmul(b, c); c = fr_mmul(c, d); d = fr_mmul(d, a);
+    }
+    if (fr_is_zero(fr_add(fr_add(a, b), fr_add(c, d)))) out[0] = a;   // keeps the chains alive
+}
+
 static bool fr_canonical(const uint32_t* x) {
     static const uint32_t P[8] = {0x00000001u, 0xffffffffu, 0xfffe5bfeu, 0x53bda402u, 0x09a1d805u, 0x3339d808u, 0x299d7d48u, 0x73eda753u};
     for (int i = 7; i >= 0; i--) {
@@ -453,5 +463,30 @@ extern "C" int zkh_fr_sumcheck(zkh_ctx* c, const void* const* cols_dev, int nc, 
     ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
     if (h->err) return zkh_fail(c, ZKH_ERR_DEVICE, "fr_sumcheck: device error flag set");
     digest_to_bytes(h->st, state);
+    return ZKH_OK;
+}
+
+extern "C" int zkh_fr_mul_throughput(zkh_ctx* c, uint32_t iters, double* gmul_per_s) {
+    if (!c || !gmul_per_s || iters == 0 || iters > (1u << 20)) return zkh_fail(c, ZKH_ERR_ARG, "fr_mul_throughput: bad arguments");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    ZKH_TRY(zkh_ws_reserve(c, 64));
+    cudaEvent_t e0, e1;
+    ZKH_CUDA(c, cudaEventCreate(&e0));
+    ZKH_CUDA(c, cudaEventCreate(&e1));
+    Fr seed;
+    for (int i = 0; i < 8; i++) seed.v[i] = 0x01234567u + 0x11111111u * i;
+    seed.v[7] &= 0x3fffffffu;
+    const unsigned grid = (unsigned)c->sm_count * 8;
+    fr_mul_probe_kernel<<<grid, 256, 0, c->stream>>>(seed, 16, (Fr*)c->ws);   // warm-up
+    cudaEventRecord(e0, c->stream);
+    fr_mul_probe_kernel<<<grid, 256, 0, c->stream>>>(seed, iters, (Fr*)c->ws);
+    cudaEventRecord(e1, c->stream);
+    cudaError_t err = cudaEventSynchronize(e1);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (err != cudaSuccess) return zkh_fail(c, ZKH_ERR_CUDA, "fr_mul_throughput: launch failed");
+    *gmul_per_s = 4.0 * iters * grid * 256 / (ms * 1e6);
     return ZKH_OK;
 }

@@ -117,3 +117,10 @@ def product_sumcheck(prover, tr, cols, labels):
                                          fin.ctypes.data))
     tr.state = bytes(st)
     return [unpack(e) for e in ev], unpack(ch), unpack(fin)
+
+
+def mul_throughput(prover, iters=4096):
+    """Montgomery products per second (in 10^9) measured on the prover's GPU."""
+    out = C.c_double(0)
+    prover._ck(prover._L.zkh_fr_mul_throughput(prover._h, iters, C.byref(out)))
+    return out.value
