@@ -254,6 +254,9 @@ ZKH_API int zkh_gl_affine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nco
  * so its round messages come from these partial evaluations (see p3.imm_prove).  Stream-ordered. */
 ZKH_API int zkh_gl_matvec(zkh_ctx* ctx, const uint64_t* M_dev, uint64_t rows, uint64_t cols, const uint64_t* w_dev,
                           int along_rows, uint64_t* out_dev);
+/* out[i] = a[i]*b[i]: the helper column hT = cnt * 1/(Tc+beta) of the standalone lookup
+ * (zkllm-src/p3_logup.cuh:984).  Stream-ordered. */
+ZKH_API int zkh_gl_mul(zkh_ctx* ctx, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev);
 /* out[i] = s*in[i].  Stream-ordered. */
 ZKH_API int zkh_gl_scale(zkh_ctx* ctx, const uint64_t* in_dev, uint64_t n, uint64_t s, uint64_t* out_dev);
 /* Rescale witness (zkllm-src/p3_int_gadgets.cuh:230-275 p3irs::gen_witness): for each signed acc value

@@ -287,6 +287,66 @@ bool imm_deserialize(const uint8_t* in, size_t len, p3imm::Proof& pf) {
     }
     return p == end;
 }
+// LookupProof (standalone logUp, non-zk, per-instance openings) <-> bytes:
+//   u32 n, m, c | root_cnt root_hA root_hT | S | msgsA n*32 | msgsT m*32 | u32 len, open_hA |
+//   u32 count, (u32 len, open_W)* | u32 count, y_virt* | u32 len, open_hT | u32 len, open_cnt
+size_t lup_serialize(const p3lu::LookupProof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    auto appe = [&](const p3bf::EvalProof& e) {
+        std::vector<uint8_t> t(bf_size(e.logN, e.R, e.Q));
+        uint32_t n = (uint32_t)bf_serialize(e, t.data(), t.size());
+        app(&n, 4); app(t.data(), n);
+    };
+    app(&pf.n, 4); app(&pf.m, 4); app(&pf.c, 4);
+    app(pf.root_cnt.data(), 32); app(pf.root_hA.data(), 32); app(pf.root_hT.data(), 32);
+    app(&pf.S, 8);
+    for (auto& m : pf.msgsA) app(&m, 32);
+    for (auto& m : pf.msgsT) app(&m, 32);
+    appe(pf.open_hA);
+    uint32_t nw = (uint32_t)pf.open_W.size(); app(&nw, 4);
+    for (auto& e : pf.open_W) appe(e);
+    uint32_t nv = (uint32_t)pf.y_virt.size(); app(&nv, 4);
+    app(pf.y_virt.data(), (size_t)nv * 8);
+    appe(pf.open_hT); appe(pf.open_cnt);
+    if (b.size() > cap) return 0;
+    memcpy(out, b.data(), b.size());
+    return b.size();
+}
+bool lup_deserialize(const uint8_t* in, size_t len, p3lu::LookupProof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
+    auto gete = [&](p3bf::EvalProof& e) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (!need(n) || !bf_deserialize(p, n, e)) return false;
+        p += n;
+        return true;
+    };
+    if (!need(12 + 96 + 8)) return false;
+    memcpy(&pf.n, p, 4); memcpy(&pf.m, p + 4, 4); memcpy(&pf.c, p + 8, 4); p += 12;
+    memcpy(pf.root_cnt.data(), p, 32); memcpy(pf.root_hA.data(), p + 32, 32); memcpy(pf.root_hT.data(), p + 64, 32); p += 96;
+    memcpy(&pf.S, p, 8); p += 8;
+    if (pf.n > 40 || pf.m > 40 || pf.c > 64 || !need(((size_t)pf.n + pf.m) * 32)) return false;
+    pf.msgsA.resize(pf.n); pf.msgsT.resize(pf.m);
+    for (auto& m : pf.msgsA) { memcpy(&m, p, 32); p += 32; }
+    for (auto& m : pf.msgsT) { memcpy(&m, p, 32); p += 32; }
+    if (!gete(pf.open_hA)) return false;
+    uint32_t nw;
+    if (!need(4)) return false;
+    memcpy(&nw, p, 4); p += 4;
+    if (nw > 64) return false;
+    pf.open_W.resize(nw);
+    for (auto& e : pf.open_W) if (!gete(e)) return false;
+    uint32_t nv;
+    if (!need(4)) return false;
+    memcpy(&nv, p, 4); p += 4;
+    if (nv > 64 || !need((size_t)nv * 8)) return false;
+    pf.y_virt.resize(nv); memcpy(pf.y_virt.data(), p, (size_t)nv * 8); p += (size_t)nv * 8;
+    if (!gete(pf.open_hT) || !gete(pf.open_cnt)) return false;
+    return p == end;
+}
 // p3irs::Proof (non-zk) <-> bytes: u32 le, sf, nl, rng | limb roots nl*32 | messages le*40 | yX yY yL[nl] |
 //   u32 groups, each u32 len + GroupProof | u32 batches, each u32 len + BatchProof
 size_t irs_serialize(const p3irs::Proof& pf, uint8_t* out, size_t cap) {
@@ -642,6 +702,67 @@ int ref_lu_verify_super(uint8_t st[32], const uint64_t* const* tcols, uint32_t m
         }
     *n_claims = w;
     return 1;
+}
+
+// ---- standalone logUp (p3_logup.cuh:932-1163 prove_v, :1170-1350 verify_v), non-zk, per-instance openings.
+// committed[k] != 0: column k is committed (root given / produced); else virtual.  gpu = 0 runs everything on
+// host cores (Horner encode: small instances only).
+size_t ref_lu_prove_v(uint8_t st[32], const uint64_t* const* tcols, uint32_t m, uint32_t c, const uint64_t* const* wcols,
+                      const uint8_t* committed, const uint32_t* idx, uint32_t n, uint32_t R, uint32_t Q, const char* label,
+                      int gpu, uint8_t* wroots_out, uint64_t* rA_out, uint8_t* out, size_t cap) {
+    try {
+        p3fri::g_gpu_merkle = gpu != 0;
+        std::vector<std::vector<gl_t>> tc(c);
+        for (uint32_t t = 0; t < c; t++) tc[t].assign(tcols[t], tcols[t] + ((size_t)1 << m));
+        p3lu::Table T = p3lu::make_table(tc);
+        std::vector<p3lu::Col> cols(c);
+        std::vector<std::vector<gl_t>> virt(c);
+        std::vector<p3lu::LuColSpec> W;
+        for (uint32_t k = 0; k < c; k++) {
+            std::vector<gl_t> v(wcols[k], wcols[k] + ((size_t)1 << n));
+            if (committed[k]) {
+                cols[k] = p3lu::commit_col(v, R, gpu != 0);
+                memcpy(wroots_out + (size_t)k * 32, cols[k].root.data(), 32);
+                W.push_back(p3lu::LC(&cols[k]));
+            } else {
+                virt[k] = v;
+                W.push_back(p3lu::LV(&virt[k]));
+            }
+        }
+        std::vector<uint32_t> ix(idx, idx + ((size_t)1 << n));
+        fs::Transcript tr = tr_from(st);
+        std::vector<gl_t> rA;
+        auto pf = p3lu::prove_v(tr, W, ix, T, R, Q, label, gpu != 0, true, &rA);
+        p3fri::g_gpu_merkle = false;
+        memcpy(st, tr.state, 32);
+        memcpy(rA_out, rA.data(), rA.size() * 8);
+        return lup_serialize(pf, out, cap);
+    } catch (...) { p3fri::g_gpu_merkle = false; return 0; }
+}
+int ref_lu_verify_v(uint8_t st[32], const uint64_t* const* tcols, uint32_t m, uint32_t c, const uint8_t* wroots,
+                    const uint8_t* committed, uint32_t R, uint32_t Q, const char* label, const uint8_t* proof, size_t len,
+                    uint64_t* rA_out, uint64_t* yvirt_out) {
+    p3lu::LookupProof pf;
+    if (!lup_deserialize(proof, len, pf)) return 0;
+    std::vector<std::vector<gl_t>> tc(c);
+    for (uint32_t t = 0; t < c; t++) tc[t].assign(tcols[t], tcols[t] + ((size_t)1 << m));
+    p3lu::Table T = p3lu::make_table(tc);
+    std::vector<p3fri::Hash> roots(c);
+    std::vector<const p3fri::Hash*> rp(c);
+    for (uint32_t k = 0; k < c; k++) {
+        memcpy(roots[k].data(), wroots + (size_t)k * 32, 32);
+        rp[k] = committed[k] ? &roots[k] : nullptr;
+    }
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    std::vector<gl_t> rA, yv;
+    bool ok = p3lu::verify_v(tr, rp, T, pf, Q, R, label, &why, &rA, &yv);
+    memcpy(st, tr.state, 32);
+    if (ok) {
+        memcpy(rA_out, rA.data(), rA.size() * 8);
+        memcpy(yvirt_out, yv.data(), yv.size() * 8);
+    }
+    return ok ? 1 : 0;
 }
 
 // ---- integer matmul gadget: the reference's host-only verifier (p3_int_gadgets.cuh:608-655) ----

@@ -67,3 +67,57 @@ def ref_irs_witness(ref, acc, le, sf, rng):
     nl = ref.lib.ref_irs_witness(vp(np.ascontiguousarray(acc)), C.c_uint32(le), C.c_uint32(sf), C.c_int(rng),
                                  vp(y), vp(L0), vp(L1), vp(i0), vp(i1), vp(iY))
     return nl, y, [L0, L1][:nl], [i0, i1][:nl], iY
+
+
+class OracleStandaloneLuEngine(OracleIrsEngine):
+    """Adds what the standalone lookup (p3.lu_prove) needs on top of the gadget engine."""
+
+    def combine(self, cols, g):
+        return _Arr(self.orc.combine([c.a for c in cols], g))
+
+    def inv_all_add(self, A, beta):
+        return _Arr(self.orc.inv_all_add(A.a, beta))
+
+    def mul(self, a, b):
+        return _Arr(np.array([int(x) * int(y) % GL_P for x, y in zip(a.a, b.a)], dtype=np.uint64))
+
+    def prove_eval_dev(self, col, z, y, R, Q, cw0, seed):
+        return self.orc.bf_prove_eval(col.a, np.ascontiguousarray(z, dtype=np.uint64), y, R, Q,
+                                      self.orc.rs_encode(col.a, R), seed)
+
+
+def ref_lu_prove_v(ref, st, tcols, wcols, committed, idx, R, Q, label, gpu):
+    u64p, u32p = C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)
+    c = len(tcols)
+    m = len(tcols[0]).bit_length() - 1
+    n = len(idx).bit_length() - 1
+    ta = [np.ascontiguousarray(t, dtype=np.uint64) for t in tcols]
+    wa = [np.ascontiguousarray(w, dtype=np.uint64) for w in wcols]
+    tp = (u64p * c)(*[a.ctypes.data_as(u64p) for a in ta])
+    wp = (u64p * c)(*[a.ctypes.data_as(u64p) for a in wa])
+    ix = np.ascontiguousarray(idx, dtype=np.uint32)
+    s = (C.c_uint8 * 32)(*st)
+    roots = (C.c_uint8 * (32 * c))()
+    rA = np.zeros(n, dtype=np.uint64)
+    cap = 64 << 20
+    out = (C.c_uint8 * cap)()
+    f = ref.lib.ref_lu_prove_v
+    f.restype = C.c_size_t
+    k = f(s, tp, C.c_uint32(m), C.c_uint32(c), wp, bytes(committed), ix.ctypes.data_as(u32p), C.c_uint32(n), C.c_uint32(R),
+          C.c_uint32(Q), label.encode(), C.c_int(gpu), roots, rA.ctypes.data_as(u64p), out, C.c_size_t(cap))
+    return bytes(out)[:k], bytes(s), [bytes(roots)[32 * i:32 * i + 32] for i in range(c)], rA
+
+
+def ref_lu_verify_v(ref, st, tcols, wroots, committed, R, Q, label, proof):
+    u64p = C.POINTER(C.c_uint64)
+    c = len(tcols)
+    m = len(tcols[0]).bit_length() - 1
+    ta = [np.ascontiguousarray(t, dtype=np.uint64) for t in tcols]
+    tp = (u64p * c)(*[a.ctypes.data_as(u64p) for a in ta])
+    s = (C.c_uint8 * 32)(*st)
+    rA = np.zeros(64, dtype=np.uint64)
+    yv = np.zeros(64, dtype=np.uint64)
+    ok = ref.lib.ref_lu_verify_v(s, tp, C.c_uint32(m), C.c_uint32(c), b"".join(wroots), bytes(committed), C.c_uint32(R),
+                                 C.c_uint32(Q), label.encode(), bytes(proof), C.c_size_t(len(proof)),
+                                 rA.ctypes.data_as(u64p), yv.ctypes.data_as(u64p))
+    return bool(ok), bytes(s), rA, yv

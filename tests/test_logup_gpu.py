@@ -35,7 +35,8 @@ def test_inv_all_add_zero_denominator(zk, prover):
     assert ei.value.code == -4
 
 
-@pytest.mark.parametrize("M,n", [(1, 10), (16, 1000), (1 << 10, 1 << 16), (1 << 15, 1 << 18), (1 << 16, 1 << 20), (1 << 20, 1 << 18)])
+@pytest.mark.parametrize("M,n", [(1, 10), (16, 1000), (1 << 10, 1 << 16), (1 << 15, 1 << 18), (1 << 16, 1 << 20), (1 << 20, 1 << 18),
+                                 (1 << 16, (1 << 20) + 3), (1 << 17, 1 << 19), (3 * (1 << 15) + 5, 1 << 18), (1 << 18, 1 << 18)])
 def test_histogram(orc, zk, prover, M, n):
     import torch
     rng = np.random.default_rng(M + n)

@@ -9,7 +9,11 @@ namespace zkh {
 
 // Counting is order-free integer accumulation, so the bins equal the host loop's exactly.
 // Tables of up to 2^15 rows are counted in shared memory (32-bit sub-histograms flushed with
-// 64-bit atomics); larger tables go straight to 64-bit global atomics in L2.
+// 64-bit atomics).  Tables of up to 2^18 rows are cut into windows of 2^15 bins: blockIdx.y picks the
+// window, every CTA scans its slice of the indices and counts only those inside its window, so the
+// indices are read once per window but every increment is a shared-memory atomic (skewed lookups
+// such as range checks of Gaussian activations serialise in L2 otherwise).  Larger tables go
+// straight to 64-bit global atomics.
 __global__ void __launch_bounds__(512)
 hist_shared_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsigned long long* bins,
                    unsigned int* oob) {
@@ -25,6 +29,37 @@ hist_shared_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsig
     __syncthreads();
     for (uint32_t t = threadIdx.x; t < M; t += blockDim.x)
         if (shc[t]) atomicAdd(&bins[t], (unsigned long long)shc[t]);
+}
+__global__ void __launch_bounds__(512)
+hist_window_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsigned long long* bins,
+                   unsigned int* oob) {
+    extern __shared__ uint32_t shc[];
+    constexpr uint32_t W = 1u << 15;
+    const uint32_t base = blockIdx.y * W;
+    for (uint32_t t = threadIdx.x; t < W; t += blockDim.x) shc[t] = 0;
+    __syncthreads();
+    const size_t n4 = n / 4, stride = (size_t)gridDim.x * blockDim.x;
+    const uint4* idx4 = reinterpret_cast<const uint4*>(idx);
+    unsigned bad = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const uint4 v = __ldg(idx4 + i);
+        const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t d = r[j] - base;
+            if (d < W) atomicAdd(&shc[d], 1u);
+            bad += r[j] >= M;
+        }
+    }
+    for (size_t i = 4 * n4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const uint32_t d = idx[i] - base;
+        if (d < W) atomicAdd(&shc[d], 1u);
+        bad += idx[i] >= M;
+    }
+    if (bad && blockIdx.y == 0) atomicAdd(oob, bad);
+    __syncthreads();
+    for (uint32_t t = threadIdx.x; t < W && base + t < M; t += blockDim.x)
+        if (shc[t]) atomicAdd(&bins[base + t], (unsigned long long)shc[t]);
 }
 __global__ void __launch_bounds__(256)
 hist_global_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsigned long long* bins,
@@ -96,6 +131,15 @@ extern "C" int zkh_histogram(zkh_ctx* c, const uint32_t* idx_dev, uint64_t n, ui
             size_t blocks = (n + 512 * 64 - 1) / (512 * 64), cap = (size_t)c->sm_count;
             if (blocks < 1) blocks = 1;
             hist_shared_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 512, (size_t)M * 4, c->stream>>>(
+                idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
+        } else if (M <= (1u << 18) && ((uintptr_t)idx_dev & 15) == 0) {
+            static bool attr = false;
+            if (!attr) { cudaFuncSetAttribute(hist_window_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024); attr = true; }
+            const unsigned windows = (M + (1u << 15) - 1) >> 15;
+            size_t blocks = (n + 512 * 64 - 1) / (512 * 64), cap = (size_t)c->sm_count / windows;
+            if (cap < 1) cap = 1;
+            if (blocks < 1) blocks = 1;
+            hist_window_kernel<<<dim3((unsigned)(blocks < cap ? blocks : cap), windows), 512, 128 * 1024, c->stream>>>(
                 idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
         } else {
             size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 8;
@@ -192,6 +236,21 @@ extern "C" int zkh_gl_matvec(zkh_ctx* c, const uint64_t* M_dev, uint64_t rows, u
     else
         matvec_cols_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, c->stream>>>(M_dev, w_dev, (size_t)rows, (size_t)cols,
                                                                                  out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+namespace zkh {
+__global__ void __launch_bounds__(256) mul_vec_kernel(const gl_t* __restrict__ a, const gl_t* __restrict__ b, size_t n, gl_t* out) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = gl_mul(a[i], b[i]);
+}
+}  // namespace zkh
+extern "C" int zkh_gl_mul(zkh_ctx* c, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev) {
+    if (!c || !a_dev || !b_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "mul: null pointer");
+    if (!n) return ZKH_OK;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 16;
+    mul_vec_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(a_dev, b_dev, (size_t)n, out_dev);
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }

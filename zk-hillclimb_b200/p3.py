@@ -278,6 +278,12 @@ class Prover:
         self._ck(self._L.zkh_gl_scale(self._h, _ptr(col_dev), col_dev.numel(), s, _ptr(out)))
         return out
 
+    def mul(self, a_dev, b_dev):
+        import torch
+        out = torch.empty_like(a_dev)
+        self._ck(self._L.zkh_gl_mul(self._h, _ptr(a_dev), _ptr(b_dev), a_dev.numel(), _ptr(out)))
+        return out
+
     def irs_witness(self, acc_dev, sf, rng):
         """p3irs::gen_witness on the device: returns (y, [L0(, L1)], [idxL0(, idxL1)], idxY or None)."""
         import torch
@@ -795,3 +801,79 @@ def irs_prove(engine, tr, tables, X, Y, wit, le, sf, rng, R, Q, ledger=None, luq
     out += struct.pack("<I", len(lug)) + b"".join(struct.pack("<I", len(b)) + b for b in lug)
     out += struct.pack("<I", len(batches)) + b"".join(struct.pack("<I", len(b)) + b for b in batches)
     return out
+
+
+def col_sum(engine, col):
+    """Sum of a power-of-two column through its multilinear extension: sum = 2^v * c~(1/2, ..., 1/2)."""
+    v = int(col.numel()).bit_length() - 1
+    half = (GL_P + 1) // 2
+    return engine.eval_h_gpu(col, np.full(v, half, dtype=np.uint64)) * pow(2, v, GL_P) % GL_P
+
+
+def lu_prove(engine, tr, W, idx, tab, R, Q, label, strict=True):
+    """p3lu::prove / prove_v (zkllm-src/p3_logup.cuh:754-765, :932-1163), non-zk, standalone openings: the
+    classic logUp with committed helper columns hA = 1/(A+beta), hT = cnt/(Tc+beta), two cubic sumchecks
+    ("lu-scA", "lu-scT") and one Basefold opening per committed column.
+    W: [(column, root) or (column, None) for a virtual column]; idx: row indices; tab: make_table(...).
+    Returns (proof bytes, rA).  Serialised LookupProof: u32 n, m, c | root_cnt root_hA root_hT | S |
+    msgsA n*32 | msgsT m*32 | u32 len, open_hA | u32 count, (u32 len, open_W)* | u32 count, y_virt* |
+    u32 len, open_hT | u32 len, open_cnt."""
+    import struct
+    N, M = int(idx.numel()), len(tab["cols"][0])
+    n, m, c = N.bit_length() - 1, M.bit_length() - 1, len(W)
+    if (1 << n) != N or (1 << m) != M:
+        raise ValueError("p3lu: pow2")
+    if len(tab["cols"]) != c:
+        raise ValueError("p3lu: col count")
+    if tab["dev"] is None:
+        tab["dev"] = [engine.upload(t) for t in tab["cols"]]
+    tr.absorb("lu-tab", tab["id"])
+    for col, root in W:
+        if root is not None:
+            tr.absorb("lu-W", root)
+        else:
+            tr.absorb("lu-Wv", b"virt")
+    cnt = engine.lu_counts([idx], M, 0)
+    root_cnt = engine.commit_gpu_rootonly(cnt, R)
+    tr.absorb("lu-cnt", root_cnt)
+    gamma, beta = tr.chal(), tr.chal()
+    A = engine.combine([w[0] for w in W], gamma)
+    Tc = engine.combine(tab["dev"], gamma)
+    hA = engine.inv_all_add(A, beta)
+    hT = engine.mul(cnt, engine.inv_all_add(Tc, beta))
+    SA, ST = col_sum(engine, hA), col_sum(engine, hT)
+    if strict and SA != ST:
+        raise ValueError("p3lu: witness not in table: " + label)
+    root_hA, root_hT = engine.commit_gpu_rootonly(hA, R), engine.commit_gpu_rootonly(hT, R)
+    tr.absorb("lu-hA", root_hA)
+    tr.absorb("lu-hT", root_hT)
+    tr.absorb("lu-S", struct.pack("<Q", SA))
+    zA = np.array([tr.chal() for _ in range(n)], dtype=np.uint64)
+    lamA = tr.chal()
+    rA, msgsA, _ = engine.sc_prove_gpu(tr, "lu-scA", [hA, A, engine.build_eq_gpu(zA), engine.lu_ones(N)], F_LOGUP, 4,
+                                       [lamA, beta])
+    y_hA = engine.eval_h_gpu(hA, rA)
+    open_hA = engine.prove_eval_dev(hA, rA, y_hA, R, Q, None, label + "-hA")
+    open_W, y_virt = [], []
+    for k, (col, root) in enumerate(W):
+        y = engine.eval_h_gpu(col, rA)
+        if root is not None:
+            open_W.append(engine.prove_eval_dev(col, rA, y, R, Q, None, label + "-W%d" % k))
+        else:
+            y_virt.append(y)
+            tr.absorb("lu-yv", struct.pack("<Q", y))
+    zT = np.array([tr.chal() for _ in range(m)], dtype=np.uint64)
+    lamT = tr.chal()
+    rT, msgsT, _ = engine.sc_prove_gpu(tr, "lu-scT", [hT, Tc, engine.build_eq_gpu(zT), cnt], F_LOGUP, 4, [lamT, beta])
+    y_hT, y_cnt = engine.eval_h_gpu(hT, rT), engine.eval_h_gpu(cnt, rT)
+    open_hT = engine.prove_eval_dev(hT, rT, y_hT, R, Q, None, label + "-hT")
+    open_cnt = engine.prove_eval_dev(cnt, rT, y_cnt, R, Q, None, label + "-cnt")
+    for y in (y_hA, y_hT, y_cnt):
+        tr.absorb("lu-ends", struct.pack("<Q", y))
+    blob = lambda b: struct.pack("<I", len(b)) + b
+    out = struct.pack("<III", n, m, c) + root_cnt + root_hA + root_hT + struct.pack("<Q", SA)
+    out += np.ascontiguousarray(msgsA, dtype=np.uint64).tobytes() + np.ascontiguousarray(msgsT, dtype=np.uint64).tobytes()
+    out += blob(open_hA) + struct.pack("<I", len(open_W)) + b"".join(blob(b) for b in open_W)
+    out += struct.pack("<I", len(y_virt)) + b"".join(struct.pack("<Q", y) for y in y_virt)
+    out += blob(open_hT) + blob(open_cnt)
+    return out, rA
