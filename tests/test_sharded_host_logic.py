@@ -143,3 +143,53 @@ def test_single_rank_path_is_the_plain_proof(orc, zk):
                                        [torch.from_numpy(c.view(np.int64)) for c in cols], 0, 3, None)
     st1, m0, r0, f0 = orc.sumcheck(orc.tr_init("one"), "sc", 0, 3, cols)
     assert (m == m0).all() and (r == r0).all() and (fin == f0).all() and tr.state == st1
+
+
+def _commit_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch.distributed as dist
+    import zkh_import
+    from lu_helpers import OracleLookupEngine, _Arr
+    from oracle import Oracle
+    zk = zkh_import.load()
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    orc = Oracle()
+    eng = OracleLookupEngine(orc)
+    K, s = 5, 17
+    cols = []
+    for j in range(K):
+        a, s = orc.lcg(1 << (3 + j % 3), s)
+        cols.append(a)
+    mine = [_Arr(c) if j % world == rank else None for j, c in enumerate(cols)]      # only owned columns are resident
+    roots = zk.p3.commit_columns_sharded(eng, mine, 1, dist)
+    want = [orc.merkle_root(orc.rs_encode(c, 1)) for c in cols]
+    sizes = zk.p3.run_independent(list(range(7)), lambda i: (i, rank, i * i), dist)
+    ok = roots == want and [x[0] for x in sizes] == list(range(7)) and all(x[1] == x[0] % world for x in sizes)
+    q.put((rank, bool(ok)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_column_sharded_commitments_and_independent_proofs():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_commit_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(res) == [(0, True), (1, True)]
+
+
+def test_column_sharded_commitments_single_rank(orc, zk):
+    from lu_helpers import OracleLookupEngine, _Arr
+    cols = [orc.lcg(8, 5 + j)[0] for j in range(3)]
+    roots = zk.p3.commit_columns_sharded(OracleLookupEngine(orc), [_Arr(c) for c in cols], 1)
+    assert roots == [orc.merkle_root(orc.rs_encode(c, 1)) for c in cols]
+    assert zk.p3.run_independent([3, 4], lambda x: x + 1) == [4, 5]

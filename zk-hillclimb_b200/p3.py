@@ -512,6 +512,51 @@ def sc_prove_sharded(engine, tr, tag, dcols, functor, nt, dist=None, par=(), gro
     return chals, msgs, finals
 
 
+def commit_columns_sharded(engine, cols, R, dist=None, group=None, device=None):
+    """Commitments of K independent columns over the GPUs of one node: column j belongs to rank j mod G,
+    which encodes and hashes it (p3bf::commit_gpu_rootonly); the 32-byte roots are all-gathered so every
+    rank (in particular the transcript owner) ends with all K roots in column order.  The reference commits
+    its thousands of per-layer columns one after another on one GPU; columns are independent, so no data
+    moves between GPUs except the roots.  ``cols[j]`` is this rank's buffer for column j when it owns it and
+    may be None otherwise."""
+    import torch
+    G = dist.get_world_size(group) if (dist is not None and dist.is_initialized()) else 1
+    rank = dist.get_rank(group) if G > 1 else 0
+    K = len(cols)
+    per = (K + G - 1) // G
+    mine = torch.zeros((per, 32), dtype=torch.uint8)
+    for slot, j in enumerate(range(rank, K, G)):
+        if cols[j] is None:
+            raise ValueError("rank %d owns column %d but holds no data for it" % (rank, j))
+        mine[slot] = torch.frombuffer(bytearray(engine.commit_gpu_rootonly(cols[j], R)), dtype=torch.uint8)
+    if G == 1:
+        allr = mine.unsqueeze(0)
+    else:
+        if device is not None:
+            mine = mine.to(device)
+        allr = torch.zeros((G, per, 32), dtype=torch.uint8, device=mine.device)
+        dist.all_gather_into_tensor(allr.view(-1), mine.view(-1), group=group)
+        allr = allr.cpu()
+    return [bytes(allr[j % G, j // G].numpy().tobytes()) for j in range(K)]
+
+
+def run_independent(items, fn, dist=None, group=None):
+    """Independent proofs (e.g. one layer proof per transcript) placed on separate GPUs: rank g runs
+    fn(item) for items g, g+G, g+2G, ... and every rank receives all results in item order."""
+    G = dist.get_world_size(group) if (dist is not None and dist.is_initialized()) else 1
+    rank = dist.get_rank(group) if G > 1 else 0
+    local = [(i, fn(items[i])) for i in range(rank, len(items), G)]
+    if G == 1:
+        return [r for _, r in local]
+    gathered = [None] * G
+    dist.all_gather_object(gathered, local, group=group)
+    out = [None] * len(items)
+    for part in gathered:
+        for i, r in part:
+            out[i] = r
+    return out
+
+
 def _ser_gkr_group(m, c, root_cnt, gkT, subs):
     import struct
     b = struct.pack("<III", m, c, len(subs)) + root_cnt + gkT
