@@ -697,6 +697,33 @@ def main():
                "h2d_bytes_per_step": nc * n * 8, "d2h_bytes_per_step": int(m.nbytes + r.nbytes + fin.nbytes + 32),
                "ms_per_step": e_ms, "call": "zkh_sumcheck_host (pinned host columns in, proof out)"}
 
+    if world > 1 and args.e2e_steps > 0:
+        # every rank: its slice from pinned host memory to the device, then the sharded proof, then the
+        # proof (messages, challenges, finals) back on the host
+        pinned = [torch.from_numpy(c.view(np.int64)).pin_memory() for c in host_cols]
+        stage = [torch.empty_like(t) for t in dcols]
+
+        def e2e_step():
+            for dst, src in zip(stage, pinned):
+                dst.copy_(src, non_blocking=True)
+            return zk.p3.sc_prove_sharded(prover, zk.Transcript("bench-sc2"), "sc", stage, zk.F_PROD2, nt, dist)
+        e2e_step()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            r, m, fin = e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.e2e_steps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e_ms = float(t.item())
+        e2e = {"value": alg_bytes(nc, logn) * world / (e_ms / 1e3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": nc * n * 8 * world, "d2h_bytes_per_step": int(m.nbytes + r.nbytes + fin.nbytes + 32) * world,
+               "ms_per_step": e_ms, "call": "p3.sc_prove_sharded after each rank uploads its slice from pinned host memory"}
+        del stage, pinned
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         ncores = os.cpu_count() or 1
