@@ -589,6 +589,7 @@ def main():
     ap.add_argument("--cpu-logn", type=int, default=26, help="sample size of the cpu_baseline leg")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's CUDA prover")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--nccl-rounds", action="store_true", help="N>1: exchange the round sums with NCCL instead of peer stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
     ap.add_argument("--profile-case", default=None, help="one small kernel-family invocation (for ncu captures)")
@@ -630,6 +631,10 @@ def main():
     n = 1 << logn
     stream = torch.cuda.current_stream()
     prover = zk.Prover(local, stream.cuda_stream)
+    exchange = "single GPU"
+    if world > 1:
+        exchange = ("one kernel per round, round sums exchanged by NVLink peer stores into mapped mailboxes"
+                    if (not args.nccl_rounds and prover.p2p_connect(dist)) else "NCCL all-gather per round")
 
     # inputs: seeded, resident in HBM before the timed region (8 GB > L2, no flush needed)
     host_cols = lcg_cols(orc, n, nc, SEED + 1000 * rank)
@@ -759,16 +764,22 @@ def main():
                                    "instance 2^%d" % (logn, total_logn),
                        "nc": nc, "nt": nt, "rounds": total_logn, "l2": "inputs (%.1f GB per GPU) exceed the 126 MB L2; "
                        "no flush between steps" % (nc * n * 8 / 1e9),
-                       "parallelism": "hypercube split on the top %d variables" % (world.bit_length() - 1)},
+                       "parallelism": "hypercube split on the top %d variables" % (world.bit_length() - 1),
+                       "round_exchange": exchange},
             "roofline": {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": UNIT,
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                          "launch_ms": k_ms, "alg_bytes_per_launch": k_bytes},
             "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": int(args.steps * ((1 + (logn - 12) + 1) if world == 1 else (2 * logn + 3))),
+            "gpu_launches": int(args.steps * ((1 + (logn - 12) + 1) if world == 1 else
+                                             ((logn + 3) if exchange.startswith("one kernel") else (2 * logn + 3)))),
             "clocks": clocks, "reference_cuda": ref_cuda,
         }
         print(json.dumps(out))
     if world > 1:
+        dist.barrier()
+        if getattr(prover, "p2p_ready", False):
+            prover.p2p_disconnect()
+        dist.barrier()
         dist.destroy_process_group()
 
 

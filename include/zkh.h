@@ -167,6 +167,21 @@ ZKH_API int zkh_sumcheck_wide_shape(int functor, int* nc, int* nlam);
 ZKH_API int zkh_shard_begin(zkh_ctx* ctx, int functor, int nt, const uint64_t* const* cols_dev, int nc,
                             uint32_t logn_local, const uint64_t* par, int npar, const char* tag,
                             const uint8_t state[32]);
+/* Peer-to-peer exchange of the round sums (one process per GPU, NVLink peer stores, no NCCL call per round).
+ * zkh_p2p_create: allocate this GPU's mailbox, return its 64-byte CUDA IPC handle.  The caller exchanges the
+ * handles between ranks and passes all G of them, in rank order, to zkh_p2p_connect on every rank (collective:
+ * all ranks must connect before any of them runs a fused round).  zkh_shard_round_fused(r) then runs round r of
+ * the running sharded sumcheck as ONE kernel (bind, local sums, peer stores, bounded wait of about a second per
+ * round for the other ranks, sum in rank order, absorb, challenge).  A rank that never arrives makes the others
+ * return ZKH_ERR_DEVICE from zkh_shard_end; after such an error disconnect and connect again on all ranks. */
+ZKH_API int zkh_p2p_create(zkh_ctx* ctx, uint8_t handle_out[64]);
+ZKH_API int zkh_p2p_connect(zkh_ctx* ctx, uint32_t rank, uint32_t G, const uint8_t* handles);
+ZKH_API int zkh_p2p_disconnect(zkh_ctx* ctx);
+ZKH_API int zkh_shard_round_fused(zkh_ctx* ctx, uint32_t r);
+/* All local rounds after zkh_shard_begin with the peer exchange; the rounds on columns of at most 2^12 elements
+ * run inside one single-CTA kernel per GPU.  finals_dev receives this rank's nc bound column values (what
+ * zkh_shard_finals would return); continue with the all-gather of those and zkh_shard_residual. */
+ZKH_API int zkh_shard_local_fused(zkh_ctx* ctx, uint64_t* finals_dev);
 ZKH_API int zkh_shard_round_local(zkh_ctx* ctx, uint32_t r, uint64_t* sums_dev);
 ZKH_API int zkh_shard_round_combine(zkh_ctx* ctx, uint32_t r, const uint64_t* gathered_dev, uint32_t G);
 ZKH_API int zkh_shard_finals(zkh_ctx* ctx, uint64_t* finals_dev);

@@ -73,7 +73,7 @@ def _worker(rank, world, port, logn_total, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     orc = Oracle()
     ok = True
-    for functor, nt, par in [(0, 3, []), (1, 4, [])]:
+    for functor, nt, par, logn_total in [(0, 3, [], logn_total), (1, 4, [], logn_total), (3, 4, [5, 9], 8), (1, 4, [], 13)]:
         nc = zk.p3.FUNCTOR_NC[functor]
         cols, s = [], 97531
         for _ in range(nc):
@@ -86,6 +86,35 @@ def _worker(rank, world, port, logn_total, q):
         r, m, fin = zk.p3.sc_prove_sharded(prover, tr, "sc", mine, functor, nt, dist, par)
         st1, m0, r0, f0 = orc.sumcheck(orc.tr_init("nccl"), "sc", functor, nt, cols, par, nthreads=4)
         ok &= bool((m == m0).all() and (r == r0).all() and (fin == f0).all() and tr.state == st1)
+        # the same proof with every round as one kernel: sums cross NVLink as peer stores, no NCCL per round
+        if prover.p2p_connect(dist):
+            for rep in range(2):               # two proofs back to back: the exchange sequence carries over
+                tr = zk.Transcript("nccl")
+                r, m, fin = zk.p3.sc_prove_sharded(prover, tr, "sc", mine, functor, nt, dist, par)
+                ok &= bool((m == m0).all() and (r == r0).all() and (fin == f0).all() and tr.state == st1)
+            if functor == 0 and logn_total > 13:
+                # a rank that never arrives: the wait of the others runs out (about a second) and the call
+                # reports a device error instead of hanging; after reconnecting, proofs work again
+                dist.barrier()
+                if rank == 0:
+                    prover.shard_begin(functor, nt, mine, logn_total - (world.bit_length() - 1), par, "sc",
+                                       zk.Transcript("nccl").state)
+                    prover.shard_round_fused(0)
+                    try:
+                        prover.shard_end(1)
+                        ok = False
+                    except zk.ZkhError as e:
+                        ok &= e.code == -6
+                dist.barrier()
+                prover.p2p_disconnect()
+                dist.barrier()
+                ok &= bool(prover.p2p_connect(dist))
+                tr = zk.Transcript("nccl")
+                r, m, fin = zk.p3.sc_prove_sharded(prover, tr, "sc", mine, functor, nt, dist, par)
+                ok &= bool((m == m0).all() and (r == r0).all() and (fin == f0).all() and tr.state == st1)
+            dist.barrier()
+            prover.p2p_disconnect()
+        dist.barrier()
         prover.close()
     q.put((rank, ok))
     dist.barrier()

@@ -69,6 +69,11 @@ def load_library():
         "zkh_fr_sumcheck": (i, [vp, vp, i, u32, vp, vp, vp, vp, vp]),
         "zkh_shard_begin": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp]),
         "zkh_shard_round_local": (i, [vp, u32, vp]),
+        "zkh_p2p_create": (i, [vp, vp]),
+        "zkh_p2p_connect": (i, [vp, u32, u32, vp]),
+        "zkh_p2p_disconnect": (i, [vp]),
+        "zkh_shard_round_fused": (i, [vp, u32]),
+        "zkh_shard_local_fused": (i, [vp, vp]),
         "zkh_shard_round_combine": (i, [vp, u32, vp, u32]),
         "zkh_shard_finals": (i, [vp, vp]),
         "zkh_shard_residual": (i, [vp, vp, u32]),

@@ -25,6 +25,22 @@ struct ZkhCtl {
     gl_t chals[80];          // round challenges
     gl_t msgs[80 * 5];       // round messages
     gl_t aux[64];            // scratch for composite protocols
+    void* xchg;              // ZkhXchg* of this GPU when the peer-to-peer round exchange is connected
+};
+
+// Peer-to-peer exchange of the per-round sums of a sharded sumcheck (one process per GPU, mailboxes
+// mapped into every peer through CUDA IPC).  Each GPU owns one mailbox; rank g writes its values and
+// then its flag into slot [seq & 1][g] of EVERY mailbox with plain peer stores over NVLink and waits,
+// with a bounded number of polls, until its own mailbox holds the flags of all ranks for this seq.
+#define ZKH_XCHG_MAXG 16
+struct ZkhMailbox {
+    unsigned long long flag[2][ZKH_XCHG_MAXG];
+    gl_t data[2][ZKH_XCHG_MAXG][8];
+};
+struct ZkhXchg {
+    ZkhMailbox* mbox[ZKH_XCHG_MAXG];  // mbox[rank] is this GPU's own
+    uint32_t rank, G;
+    unsigned long long seq;           // exchanges completed so far (same on every rank)
 };
 
 struct ZkhTag { char s[ZKH_TR_MAX_LABEL]; uint32_t len; };
@@ -61,6 +77,13 @@ struct zkh_ctx {
         gl_t* dst = nullptr;
         gl_t* res = nullptr;  // transposed residual columns
     } shard;
+    // peer-to-peer round exchange (zkh_p2p_*)
+    struct P2P {
+        ZkhMailbox* mine = nullptr;
+        ZkhXchg* d_xchg = nullptr;
+        void* opened[ZKH_XCHG_MAXG] = {};
+        int rank = 0, G = 0;
+    } p2p;
     std::string err;
 };
 
@@ -83,6 +106,7 @@ static inline int zkh_fail(zkh_ctx* c, int code, const std::string& msg) {
 
 // make the workspace at least `bytes` large (contents are not preserved)
 int zkh_ws_reserve(zkh_ctx* c, size_t bytes);
+extern "C" int zkh_p2p_disconnect(zkh_ctx* c);
 static inline ZkhTag zkh_make_tag(const char* s) {
     ZkhTag t;
     memset(&t, 0, sizeof t);

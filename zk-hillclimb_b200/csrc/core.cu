@@ -58,6 +58,8 @@ extern "C" void zkh_ctx_destroy(zkh_ctx* c) {
     if (!c) return;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    zkh_p2p_disconnect(c);
+    if (c->p2p.mine) cudaFree(c->p2p.mine);
     if (c->ws) cudaFree(c->ws);
     if (c->d_ctl) cudaFree(c->d_ctl);
     if (c->d_partials) cudaFree(c->d_partials);

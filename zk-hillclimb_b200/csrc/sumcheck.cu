@@ -246,7 +246,7 @@ sc_fused_kernel(ScPtrs P, size_t quads, ZkhCtl* ctl, gl_t* partials, const gl_t*
 template <int F, int NT, int LD>
 __global__ void __launch_bounds__(1024)
 sc_tail_kernel(ScPtrs P, uint32_t n_in, int pending, ZkhCtl* ctl, const gl_t* chal_prev,
-               gl_t* msg_out, gl_t* chal_out, gl_t* finals_out, int nrounds, ZkhTag tag) {
+               gl_t* msg_out, gl_t* chal_out, gl_t* finals_out, int nrounds, ZkhTag tag, int mode = 0) {
     constexpr int NC = Fn<F>::NC;
     extern __shared__ gl_t cols[];
     __shared__ gl_t sh[NT * 32];
@@ -288,7 +288,7 @@ sc_tail_kernel(ScPtrs P, uint32_t n_in, int pending, ZkhCtl* ctl, const gl_t* ch
         msg_reduce<F, NT>(acc, s);
         block_sum<NT>(s, sh);  // ends with a barrier: every pair has been read
         if (tid < 32) {
-            finish_round<NT>(s, ctl, msg_out + (size_t)r * NT, chal_out + r, tag, 0);
+            finish_round<NT>(s, ctl, msg_out + (size_t)r * NT, chal_out + r, tag, mode);
             if (tid == 0) sh_chal = chal_out[r];
         }
         __syncthreads();
@@ -439,24 +439,28 @@ int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* 
     return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck round: unsupported (functor, nt) combination");
 }
 
-// tail on explicit plain columns of length n (<= 2^11): nrounds rounds, no pending bind
+// tail on explicit plain columns: nrounds rounds in one CTA.  pending == 0: columns of length n (<= 2^11);
+// pending == 1: columns of length n (<= 2^12) still to be bound with *chal_prev first.
 template <int F, int NT>
 static int sc_tail_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out, gl_t* chal_out,
-                     gl_t* finals_out, const ZkhTag& tag) {
+                     gl_t* finals_out, const ZkhTag& tag, int pending, const gl_t* chal_prev, int mode) {
     constexpr int NC = Fn<F>::NC;
     ScPtrs P;
     memset(&P, 0, sizeof P);
     for (int k = 0; k < NC; k++) P.in[k] = in[k];
     cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          NC * (1 << SC_TAIL_LOG) * 8);
-    sc_tail_kernel<F, NT, LD_PLAIN><<<1, 1024, (size_t)NC * n * 8, ctx->stream>>>(P, n, 0, ctx->d_ctl, nullptr, msg_out,
-                                                                             chal_out, finals_out, nrounds, tag);
+    const size_t held = pending ? n / 2 : n;
+    sc_tail_kernel<F, NT, LD_PLAIN><<<1, 1024, (size_t)NC * held * 8, ctx->stream>>>(P, n, pending, ctx->d_ctl, chal_prev,
+                                                                                msg_out, chal_out, finals_out, nrounds, tag,
+                                                                                mode);
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "sumcheck tail launch");
 }
 int sc_enqueue_tail(zkh_ctx* ctx, int functor, int nt, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out,
-                    gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag) {
+                    gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag, int pending, const gl_t* chal_prev, int mode) {
 #define CASE(F, NT) \
-    if (functor == F && nt == NT) return sc_tail_t<F, NT>(ctx, in, n, nrounds, msg_out, chal_out, finals_out, tag);
+    if (functor == F && nt == NT) \
+        return sc_tail_t<F, NT>(ctx, in, n, nrounds, msg_out, chal_out, finals_out, tag, pending, chal_prev, mode);
     CASE(ZKH_F_PROD2, 3)
     CASE(ZKH_F_PROD2, 5)
     CASE(ZKH_F_PROD3, 4)
@@ -638,6 +642,122 @@ extern "C" int zkh_shard_begin(zkh_ctx* c, int functor, int nt, const uint64_t* 
     ZKH_CUDA(c, cudaMemcpyAsync(c->d_ctl, h, offsetof(ZkhCtl, local), cudaMemcpyHostToDevice, c->stream));
     return ZKH_OK;
 }
+// ------------------------------------------------------------------ peer-to-peer round exchange
+// One process per GPU.  zkh_p2p_create allocates this GPU's mailbox and returns its CUDA IPC handle; the
+// caller exchanges the handles between the ranks (any host channel) and calls zkh_p2p_connect with all of
+// them in rank order.  After that zkh_shard_round_fused runs a whole sharded round as ONE kernel: local
+// bind + sums, peer stores of the sums, bounded wait for the other ranks, combine, transcript step.
+extern "C" int zkh_p2p_create(zkh_ctx* c, uint8_t handle_out[64]) {
+    if (!c || !handle_out) return zkh_fail(c, ZKH_ERR_ARG, "p2p_create: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    if (!c->p2p.mine) {
+        ZKH_CUDA(c, cudaMalloc(&c->p2p.mine, sizeof(ZkhMailbox)));
+        ZKH_CUDA(c, cudaMemset(c->p2p.mine, 0, sizeof(ZkhMailbox)));
+    }
+    cudaIpcMemHandle_t h;
+    ZKH_CUDA(c, cudaIpcGetMemHandle(&h, c->p2p.mine));
+    memcpy(handle_out, &h, 64);
+    return ZKH_OK;
+}
+extern "C" int zkh_p2p_disconnect(zkh_ctx* c) {
+    if (!c) return ZKH_ERR_ARG;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    for (int g = 0; g < ZKH_XCHG_MAXG; g++)
+        if (c->p2p.opened[g]) { cudaIpcCloseMemHandle(c->p2p.opened[g]); c->p2p.opened[g] = nullptr; }
+    if (c->p2p.d_xchg) { cudaFree(c->p2p.d_xchg); c->p2p.d_xchg = nullptr; }
+    if (c->d_ctl) cudaMemset(&c->d_ctl->xchg, 0, sizeof(void*));
+    c->p2p.G = 0;
+    return ZKH_OK;
+}
+extern "C" int zkh_p2p_connect(zkh_ctx* c, uint32_t rank, uint32_t G, const uint8_t* handles) {
+    if (!c || !handles) return zkh_fail(c, ZKH_ERR_ARG, "p2p_connect: null pointer");
+    if (G < 2 || G > ZKH_XCHG_MAXG || rank >= G) return zkh_fail(c, ZKH_ERR_ARG, "p2p_connect: 2..16 ranks");
+    if (!c->p2p.mine) return zkh_fail(c, ZKH_ERR_ARG, "p2p_connect: call zkh_p2p_create first");
+    zkh_p2p_disconnect(c);
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    ZkhXchg hx;
+    memset(&hx, 0, sizeof hx);
+    hx.rank = rank;
+    hx.G = G;
+    hx.seq = 0;
+    for (uint32_t g = 0; g < G; g++) {
+        if (g == rank) { hx.mbox[g] = c->p2p.mine; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)g * 64, 64);
+        void* ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            zkh_p2p_disconnect(c);
+            return zkh_fail(c, ZKH_ERR_CUDA, "p2p_connect: cannot map a peer mailbox (no peer access between these GPUs?)");
+        }
+        c->p2p.opened[g] = ptr;
+        hx.mbox[g] = (ZkhMailbox*)ptr;
+    }
+    ZKH_CUDA(c, cudaMemset(c->p2p.mine, 0, sizeof(ZkhMailbox)));
+    ZKH_CUDA(c, cudaMalloc(&c->p2p.d_xchg, sizeof(ZkhXchg)));
+    ZKH_CUDA(c, cudaMemcpy(c->p2p.d_xchg, &hx, sizeof hx, cudaMemcpyHostToDevice));
+    void* xp = c->p2p.d_xchg;
+    ZKH_CUDA(c, cudaMemcpy(&c->d_ctl->xchg, &xp, sizeof xp, cudaMemcpyHostToDevice));
+    c->p2p.rank = (int)rank;
+    c->p2p.G = (int)G;
+    return ZKH_OK;
+}
+extern "C" int zkh_shard_round_fused(zkh_ctx* c, uint32_t r) {
+    if (!c) return ZKH_ERR_ARG;
+    zkh_ctx::Shard& sh = c->shard;
+    if (c->p2p.G < 2) return zkh_fail(c, ZKH_ERR_ARG, "shard_round_fused: peer exchange not connected");
+    if (!sh.active || r != sh.next_round || r >= sh.logn)
+        return zkh_fail(c, ZKH_ERR_ARG, "shard_round_fused: rounds must run in order 0..logn_local-1");
+    gl_t* msg = c->d_ctl->msgs + (size_t)r * sh.nt;
+    if (r == 0) {
+        ZKH_TRY(sc_enqueue_round(c, sh.functor, sh.nt, true, sh.cur_in, nullptr, (size_t)1 << sh.logn, nullptr, msg,
+                                 c->d_ctl->chals + r, sh.tag, 2));
+    } else {
+        const size_t n_in = (size_t)1 << (sh.logn - r + 1), n_out = n_in / 2;
+        gl_t* outp[8];
+        for (int k = 0; k < sh.nc; k++) outp[k] = sh.dst + (size_t)k * n_out;
+        const bool prof = (r == 1) && c->prof_ev[0];
+        if (prof) cudaEventRecord(c->prof_ev[0], c->stream);
+        ZKH_TRY(sc_enqueue_round(c, sh.functor, sh.nt, false, sh.cur_in, outp, n_in, c->d_ctl->chals + (r - 1), msg,
+                                 c->d_ctl->chals + r, sh.tag, 2));
+        if (prof) {
+            cudaEventRecord(c->prof_ev[1], c->stream);
+            c->prof_valid = true;
+            c->prof_bytes = (uint64_t)12 * sh.nc * n_in;
+            c->prof_kernel = "sc_fused_kernel";
+        }
+        for (int k = 0; k < sh.nc; k++) sh.cur_in[k] = outp[k];
+        sh.dst = (sh.dst == sh.bufA) ? sh.bufB : sh.bufA;
+    }
+    sh.next_round = r + 1;
+    return ZKH_OK;
+}
+
+// all local rounds of the running sharded sumcheck with the peer exchange, the last ones (columns of at most
+// 2^12 elements) inside one single-CTA kernel per GPU; this rank's bound column values go to finals_dev
+extern "C" int zkh_shard_local_fused(zkh_ctx* c, uint64_t* finals_dev) {
+    if (!c || !finals_dev) return zkh_fail(c, ZKH_ERR_ARG, "shard_local_fused: null pointer");
+    zkh_ctx::Shard& sh = c->shard;
+    if (c->p2p.G < 2) return zkh_fail(c, ZKH_ERR_ARG, "shard_local_fused: peer exchange not connected");
+    if (!sh.active || sh.next_round != 0) return zkh_fail(c, ZKH_ERR_ARG, "shard_local_fused: must follow shard_begin");
+    uint32_t r = 0;
+    if (sh.logn <= SC_TAIL_LOG) {
+        ZKH_TRY(sc_enqueue_tail(c, sh.functor, sh.nt, sh.cur_in, 1u << sh.logn, (int)sh.logn, c->d_ctl->msgs, c->d_ctl->chals,
+                                finals_dev, sh.tag, 0, nullptr, 2));
+    } else {
+        ZKH_TRY(zkh_shard_round_fused(c, 0));
+        for (r = 1; sh.logn - r + 1 > SC_TAIL_LOG + 1; r++) ZKH_TRY(zkh_shard_round_fused(c, r));
+        // columns of 2^(logn-r+1) <= 2^12 elements, still to be bound with challenge r-1
+        ZKH_TRY(sc_enqueue_tail(c, sh.functor, sh.nt, sh.cur_in, 1u << (sh.logn - r + 1), (int)(sh.logn - r),
+                                c->d_ctl->msgs + (size_t)r * sh.nt, c->d_ctl->chals + r, finals_dev, sh.tag, 1,
+                                c->d_ctl->chals + (r - 1), 2));
+    }
+    sh.next_round = sh.logn;
+    return ZKH_OK;
+}
+
 extern "C" int zkh_shard_round_local(zkh_ctx* c, uint32_t r, uint64_t* sums_dev) {
     if (!c || !sums_dev) return zkh_fail(c, ZKH_ERR_ARG, "shard_round_local: null pointer");
     zkh_ctx::Shard& sh = c->shard;

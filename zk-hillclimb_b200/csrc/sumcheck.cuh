@@ -43,13 +43,16 @@ int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* 
                      size_t n_in, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, const ZkhTag& tag,
                      int mode = 0);
 int sc_enqueue_tail(zkh_ctx* ctx, int functor, int nt, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out,
-                    gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag);
+                    gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag, int pending = 0, const gl_t* chal_prev = nullptr,
+                    int mode = 0);
 // Absorb nwords 64-bit words of device data under `tag` into the device transcript.
 int tr_absorb_enqueue(zkh_ctx* ctx, const char* tag, const uint64_t* vals_dev, uint32_t nwords);
 
 // ------------------------------------------------------------------ round end
 // mode 0: absorb the message under `tag` and draw the challenge on the device.
 // mode 1: write this GPU's sums to msg_out and stop (another step combines the GPUs).
+// mode 2: exchange the sums with the other GPUs through the peer mailboxes (ctl->xchg), add them in
+//         rank order, then absorb and draw the challenge as in mode 0: the whole round is one kernel.
 // Called by all 32 lanes of warp 0; the sums s are valid on lane 0.
 template <int NT>
 __device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t* msg_out, gl_t* chal_out,
@@ -62,6 +65,42 @@ __device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t
         for (int t = 0; t < NT; t++) { msg_out[t] = s[t]; mvals[t] = s[t]; }
     }
     if (mode == 1) return;
+    if (mode == 2) {
+        // sum over the GPUs through the peer mailboxes: publish, fence, flag, bounded wait, add in rank order
+        ZkhXchg* x = static_cast<ZkhXchg*>(ctl->xchg);
+        const uint32_t G = x->G, me = x->rank;
+        const unsigned long long seq = x->seq + 1;
+        const int slot = (int)(seq & 1);
+        __syncwarp();
+        if (lane < NT)
+            for (uint32_t p = 0; p < G; p++)
+                *reinterpret_cast<volatile gl_t*>(&x->mbox[p]->data[slot][me][lane]) = mvals[lane];
+        __threadfence_system();
+        __syncwarp();
+        if (lane < G) *reinterpret_cast<volatile unsigned long long*>(&x->mbox[lane]->flag[slot][me]) = seq;
+        bool arrived = true;
+        if (lane < G) {
+            volatile unsigned long long* f = &x->mbox[me]->flag[slot][lane];
+            const uint32_t limit = ctl->err ? 0u : (1u << 21);   // about a second, then give up with an error flag
+            uint32_t it = 0;
+            while (*f != seq && it < limit) { __nanosleep(128); it++; }
+            arrived = (*f == seq);
+        }
+        arrived = __all_sync(0xffffffffu, arrived);
+        __threadfence_system();
+        if (lane < NT) {
+            gl_t a = 0;
+            for (uint32_t g = 0; g < G; g++)
+                a = gl_add(a, *reinterpret_cast<volatile gl_t*>(&x->mbox[me]->data[slot][g][lane]));
+            mvals[lane] = a;
+            msg_out[lane] = a;
+        }
+        if (lane == 0) {
+            x->seq = seq;
+            if (!arrived) atomicOr(&ctl->err, 4u);
+        }
+        __syncwarp();
+    }
     uint32_t st[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) st[i] = ctl->st[i];

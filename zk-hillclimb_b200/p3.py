@@ -394,6 +394,36 @@ class Prover:
         self._ck(self._L.zkh_shard_begin(self._h, functor, nt, ptrs, nc, logn, par_a.ctypes.data, len(par),
                                          tag.encode(), _buf32(state)))
 
+    def p2p_connect(self, dist, group=None):
+        """Map every rank's round-exchange mailbox into this process (CUDA IPC, one process per GPU) so that
+        sc_prove_sharded runs each round as one kernel with NVLink peer stores instead of an NCCL all-gather.
+        Collective over ``group``.  Returns False (and leaves the NCCL path in use) when the GPUs have no
+        peer access."""
+        G, rank = dist.get_world_size(group), dist.get_rank(group)
+        if G < 2 or G > 16:
+            return False
+        h = (C.c_uint8 * 64)()
+        self._ck(self._L.zkh_p2p_create(self._h, h))
+        handles = [None] * G
+        dist.all_gather_object(handles, bytes(h), group=group)
+        rc = self._L.zkh_p2p_connect(self._h, rank, G, b"".join(handles))
+        oks = [None] * G
+        dist.all_gather_object(oks, rc == 0, group=group)
+        self.p2p_ready = all(oks)
+        if not self.p2p_ready:
+            self._L.zkh_p2p_disconnect(self._h)
+        return self.p2p_ready
+
+    def p2p_disconnect(self):
+        self.p2p_ready = False
+        self._ck(self._L.zkh_p2p_disconnect(self._h))
+
+    def shard_round_fused(self, r):
+        self._ck(self._L.zkh_shard_round_fused(self._h, r))
+
+    def shard_local_fused(self, fin):
+        self._ck(self._L.zkh_shard_local_fused(self._h, _ptr(fin)))
+
     def shard_round_local(self, r, sums):
         self._ck(self._L.zkh_shard_round_local(self._h, r, _ptr(sums)))
 
@@ -498,13 +528,16 @@ def sc_prove_sharded(engine, tr, tag, dcols, functor, nt, dist=None, par=(), gro
             dist.all_gather_into_tensor(out, inp, group=group)
 
     engine.shard_begin(functor, nt, dcols, logn, par, tag, tr.state)
-    sums, gathered = engine.new_buffer(nt), engine.new_buffer(G * nt)
-    for r in range(logn):
-        engine.shard_round_local(r, sums)
-        all_gather(gathered, sums)
-        engine.shard_round_combine(r, gathered, G)
     fin, gfin = engine.new_buffer(nc), engine.new_buffer(G * nc)
-    engine.shard_finals(fin)
+    if G > 1 and getattr(engine, "p2p_ready", False):
+        engine.shard_local_fused(fin)              # one kernel per round, sums cross NVLink as peer stores
+    else:
+        sums, gathered = engine.new_buffer(nt), engine.new_buffer(G * nt)
+        for r in range(logn):
+            engine.shard_round_local(r, sums)
+            all_gather(gathered, sums)
+            engine.shard_round_combine(r, gathered, G)
+        engine.shard_finals(fin)
     all_gather(gfin, fin)
     engine.shard_residual(gfin, G)
     state, msgs, chals, finals = engine.shard_end(logn + k)
