@@ -467,6 +467,39 @@ def run_suite_fr(args):
     del cols
     torch.cuda.empty_cache()
 
+    # rescale lookup of BASELINE configs[0] on the first stack: D = 128 x 1024 remainders into a 2^16-row range table
+    logDl, logNl = 17, 16
+    T_l = np.zeros((1 << logNl, 8), dtype=np.uint32)
+    T_l[:, 0] = np.arange(1 << logNl, dtype=np.uint32)
+    idx = rng.integers(0, 1 << logNl, 1 << logDl)
+    S_l = T_l[idx]
+    m_l = np.zeros((1 << logNl, 8), dtype=np.uint32)
+    m_l[:, 0] = np.bincount(idx, minlength=1 << logNl).astype(np.uint32)
+    un = fo.ReferenceFr._unpack
+    alpha, beta = un(rand_fr(2).tobytes(), 2)
+    u_l = un(rand_fr(logDl).tobytes(), logDl)
+    dS, dT, dm = fr.to_device(S_l), fr.to_device(T_l), fr.to_device(m_l)
+    hold = {}
+
+    def lookup():
+        dA, dB = fr.inv_add(prover, dS, beta), fr.inv_add(prover, dT, beta)
+        bm = fr.dot(prover, dB, dm)
+        Cc = (alpha * alpha - bm) % fo.P
+        tr = zk.Transcript("tl-bench")
+        hold["r"] = fr.lookup_sumcheck(prover, tr, dA, dS, dB, dT, dm, alpha, beta, Cc, u_l)
+        hold["st"] = tr.state
+    lookup()
+    ms = wall(lookup)
+    line = {"suite": "tLookup over Fr: D=2^%d lookups into a 2^%d-row table (two batched inversions, %d sumcheck rounds)" % (logDl, logNl, logDl),
+            "ms": ms}
+    if refA is not None:
+        st, rA, rev, rws, rterm = refA.lookup(zk.Transcript("tl-bench").state, S_l, T_l, m_l, alpha, beta, u_l)
+        line.update({"reference_cuda_ms": refA.ms.value, "speedup_vs_reference_cuda": refA.ms.value / ms,
+                     "same_transcript": bool(st == hold["st"] and rev == hold["r"][0] and rws == hold["r"][1] and rterm == hold["r"][2])})
+    print(json.dumps(line), flush=True)
+    del dS, dT, dm
+    torch.cuda.empty_cache()
+
     # fully connected layer (BASELINE configs[0] shape, padded): X 128 x 1024, W 1024 x 1024
     B, IN, OUT = 128, 1024, 1024
     Xh, Wh = rand_fr(B * IN, small=True), rand_fr(IN * OUT, small=True)

@@ -323,6 +323,20 @@ ZKH_API int zkh_fr_mle_eval(zkh_ctx* ctx, const void* t_dev, const void* u, uint
  * fs_challenge_fr does (zkllm-src/vrf_common.cuh:233-244).  The columns are left untouched.
  *   state   transcript in/out;  evals: logn*nt*32 bytes out;  chals: logn*32 bytes out (round order);
  *   finals  nc*32 bytes out: every column bound at all challenges (may be NULL). */
+/* sum_i a[i]*b[i]: (B * m).sum() of the lookup set-up (zkllm-src/zkob_rescale.cu:137).  out32: 32 bytes, host. */
+ZKH_API int zkh_fr_dot(zkh_ctx* ctx, const void* a_dev, const void* b_dev, uint64_t n, void* out32);
+/* out[i] = 1/(in[i] + beta), 0 where in[i] + beta = 0: tlookup_inv_kernel (zkllm-src/tlookup.cu:50-62), with one
+ * Fermat inversion per eight elements instead of one per element. */
+ZKH_API int zkh_fr_inv_add(zkh_ctx* ctx, const void* in_dev, uint64_t n, const void* beta, void* out_dev);
+/* The logUp sumcheck of the reference's first stack: fs_phase1 + fs_phase2 (zkllm-src/zkob_lookup.cuh:143-198) over
+ * tLookup_phase1/2_step_poly (zkllm-src/tlookup.cu:184-296).  A, S: 2^logD entries (A = 1/(S+beta)); B, T, m: 2^logN
+ * entries (B = 1/(T+beta), table, multiplicities); logN <= logD.  alpha, beta, Cc (= alpha^2 - sum B*m) and the
+ * point u (logD entries) are host values.  Per round the four evaluations p(0..3) are absorbed under "p0".."p3"
+ * and the challenge is drawn as fs_challenge_fr does.  Out (host): evals logD*4*32 bytes, ws logD*32 bytes (round
+ * order), terminals 5*32 bytes (A_f, S_f, B_f, T_f, m_f).  The columns are left untouched. */
+ZKH_API int zkh_fr_lookup_sumcheck(zkh_ctx* ctx, const void* A_dev, const void* S_dev, const void* B_dev, const void* T_dev,
+                           const void* m_dev, uint32_t logD, uint32_t logN, const void* alpha, const void* beta,
+                           const void* Cc, const void* u, uint8_t state[32], void* evals, void* ws, void* terminals);
 /* Measured rate of Montgomery products on this GPU in 10^9 per second (four independent chains per
  * thread, grid = 8 CTAs per SM): the integer-pipe ceiling the Fr kernels are read against, as
  * zkllm-src/p3_field_bench.cu does for its two fields. */

@@ -218,6 +218,18 @@ class ReferenceFr:
         e = self._unpack(ev, logn * 4)
         return bytes(s), [e[i * 4:(i + 1) * 4] for i in range(logn)], self._unpack(ws, logn), self._unpack(fin, 2)
 
+    def lookup(self, st, S, T, m, alpha, beta, u):
+        """tlookup_inv_kernel + fs_phase1/fs_phase2: returns (state, A, evals, ws, terminals)."""
+        D, N = len(S), len(m)
+        logD = D.bit_length() - 1
+        s = (self.C.c_uint8 * 32)(*st)
+        Ao, ev, ws, term = self._out(D), self._out(logD * 4), self._out(logD), self._out(5)
+        assert self.lib.refA_lookup(s, self._pack(S), self._pack(T), self._pack(m), D, N, to_bytes(alpha), to_bytes(beta),
+                                    self._pack(u), Ao, ev, ws, term, self.C.byref(self.ms)) == 0
+        e = self._unpack(ev, logD * 4)
+        return (bytes(s), self._unpack(Ao, D), [e[i * 4:(i + 1) * 4] for i in range(logD)], self._unpack(ws, logD),
+                tuple(self._unpack(term, 5)))
+
     def quartic(self, st, tag, E, A, B, Cc):
         n = len(E)
         logn = n.bit_length() - 1
@@ -227,3 +239,85 @@ class ReferenceFr:
                                      ev, ws, fin, self.C.byref(self.ms)) == 0
         e = self._unpack(ev, logn * 5)
         return bytes(s), [e[i * 5:(i + 1) * 5] for i in range(logn)], self._unpack(ws, logn), self._unpack(fin, 3)
+
+
+# ---- tLookup: logUp over Fr (zkllm-src/tlookup.cu:184-296, zkob_lookup.cuh:143-198) ----
+def inv_add(vals, beta):
+    """tlookup_inv_kernel: 1/(x+beta), Fermat's inverse of 0 being 0."""
+    return [pow((x + beta) % P, P - 2, P) for x in vals]
+
+
+def _poly_eval(coef, x):
+    acc = 0
+    for c in reversed(coef):
+        acc = (acc * x + c) % P
+    return acc
+
+
+def _poly_mul(a, b):
+    out = [0] * (len(a) + len(b) - 1)
+    for i, x in enumerate(a):
+        for j, y in enumerate(b):
+            out[i + j] = (out[i + j] + x * y) % P
+    return out
+
+
+def _poly_add(a, b):
+    n = max(len(a), len(b))
+    return [((a[i] if i < len(a) else 0) + (b[i] if i < len(b) else 0)) % P for i in range(n)]
+
+
+def _eq_poly(u):
+    return [(1 - u) % P, (2 * u - 1) % P]            # Polynomial::eq(u): (1-u) + (2u-1) t
+
+
+def _eval_coeffs(X, Y, scale, beta, u_):
+    """tLookup_phase*_poly_eval_kernel + MLE evaluation at u_: coefficients in t of
+    sum_i eq(u_, i) * scale * X_i(t) * (Y_i(t) + beta), pairs (i, i+h)."""
+    h = len(X) // 2
+    t0 = [scale * X[i] * (Y[i] + beta) % P for i in range(h)]
+    t1 = [scale * ((X[i + h] - X[i]) * (Y[i] + beta) + X[i] * (Y[i + h] - Y[i])) % P for i in range(h)]
+    t2 = [scale * (X[i + h] - X[i]) * (Y[i + h] - Y[i]) % P for i in range(h)]
+    return [mle_eval(t0, u_), mle_eval(t1, u_), mle_eval(t2, u_)]
+
+
+def lookup_sumcheck(tr, A, S, B, T, m, alpha, beta, C, u):
+    """fs_phase1 followed by fs_phase2 (non-strict): returns (evals per round [p(0..3)], challenges,
+    terminals (A_f, S_f, B_f, T_f, m_f)).  D = len(A) = len(S), N = len(B) = len(T) = len(m)."""
+    A, S, B, T, m = list(A), list(S), list(B), list(T), list(m)
+    D, N = len(A), len(m)
+    inv_ratio = N * pow(D, -1, P) % P
+    alpha_run, alpha_sq = alpha, alpha * alpha % P
+    inv2 = pow(2, -1, P)
+    u = list(u)
+    evals, ws = [], []
+    while u:
+        u_, ul = u[:-1], u[-1]
+        h = len(A) // 2
+        if len(A) != len(m):                          # phase 1
+            p0 = _eval_coeffs(A, S, alpha_run, beta, u_)
+            p1 = [sum(A[:h]) % P, (sum(A[h:]) - sum(A[:h])) % P]
+            poly = _poly_add(_poly_add(_poly_mul(p0, _eq_poly(ul)), p1), [C * inv2 % P])
+        else:                                         # phase 2
+            p0 = _poly_add(_eval_coeffs(A, S, alpha_run, beta, u_), _eval_coeffs(B, T, inv_ratio * alpha_sq % P, beta, u_))
+            p1 = [sum(A[:h]) % P, (sum(A[h:]) - sum(A[:h])) % P]
+            p2 = [sum(m[i] * B[i] for i in range(h)) % P,
+                  sum((m[i + h] - m[i]) * B[i] + m[i] * (B[i + h] - B[i]) for i in range(h)) % P,
+                  sum((m[i + h] - m[i]) * (B[i + h] - B[i]) for i in range(h)) % P]
+            poly = _poly_add(_poly_add(_poly_mul(p0, _eq_poly(ul)), p1), [(-inv_ratio * c) % P for c in p2])
+        e = [_poly_eval(poly, t) for t in range(4)]
+        for lb, x in zip(("p0", "p1", "p2", "p3"), e):
+            tr.absorb_fr(lb, x)
+        v = tr.challenge_fr()
+        evals.append(e)
+        ws.append(v)
+        eqv = (ul * v + (1 - ul) * (1 - v)) % P
+        if len(A) != len(m):
+            C = C * inv2 % P
+        else:
+            B, T, m = fold(B, v), fold(T, v), fold(m, v)
+            alpha_sq = alpha_sq * eqv % P
+        A, S = fold(A, v), fold(S, v)
+        alpha_run = alpha_run * eqv % P
+        u = u_
+    return evals, ws, (A[0], S[0], B[0], T[0], m[0])

@@ -17,6 +17,8 @@ KERNEL void zkip_poly_kernel(GLOBAL Fr_t* a, GLOBAL Fr_t* b, GLOBAL Fr_t* out0, 
 KERNEL void zkip_reduce_kernel(GLOBAL Fr_t* a, GLOBAL Fr_t* b, GLOBAL Fr_t* new_a, GLOBAL Fr_t* new_b, Fr_t v, uint N_in,
                                uint N_out);
 
+KERNEL void tlookup_inv_kernel(Fr_t* in_data, Fr_t beta, Fr_t* out_data, uint N);   // reference's tlookup.cu
+
 namespace {
 std::vector<Fr_t> vec_from(const uint32_t* p, uint32_t n) {
     std::vector<Fr_t> v(n);
@@ -157,6 +159,43 @@ int refA_ip_rounds(uint8_t st[32], const uint32_t* a, const uint32_t* b, uint32_
         cudaFree(da); cudaFree(db); cudaFree(da2); cudaFree(db2);
         memcpy(st, tr.state, 32);
         return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    } catch (...) { return -1; }
+}
+
+// tLookup over Fr: tlookup_inv_kernel for A and B, then fs_phase1 / fs_phase2 (zkob_lookup.cuh:143-198) with
+// the scalars set up as zkob_rescale.cu:119-142 does.  terms: A_f, S_f, B_f, T_f, m_f.
+int refA_lookup(uint8_t st[32], const uint32_t* S, const uint32_t* T, const uint32_t* m, uint32_t D, uint32_t N,
+                const uint32_t* alpha_, const uint32_t* beta_, const uint32_t* u, uint32_t* A_out, uint32_t* evals,
+                uint32_t* ws_out, uint32_t* terms, double* ms_out) {
+    try {
+        FrTensor Sx(D, (const Fr_t*)S), Tx(N, (const Fr_t*)T), mx(N, (const Fr_t*)m);
+        Fr_t alpha, beta;
+        memcpy(&alpha, alpha_, 32); memcpy(&beta, beta_, 32);
+        uint32_t logD = 0; while ((1u << logD) < D) logD++;
+        std::vector<Fr_t> uu = vec_from(u, logD);
+        fs::Transcript tr = tr_from(st);
+        cudaDeviceSynchronize();
+        double t0 = now_ms();
+        FrTensor A(D), Bv(N);
+        tlookup_inv_kernel<<<(D + FrNumThread - 1) / FrNumThread, FrNumThread>>>(Sx.gpu_data, beta, A.gpu_data, D);
+        tlookup_inv_kernel<<<(N + FrNumThread - 1) / FrNumThread, FrNumThread>>>(Tx.gpu_data, beta, Bv.gpu_data, N);
+        cudaDeviceSynchronize();
+        Fr_t alpha_sq = alpha * alpha;
+        Fr_t Cc = alpha_sq - (Bv * mx).sum();
+        Fr_t claim = alpha + alpha_sq;
+        Fr_t inv_ratio = Fr_t{N, 0, 0, 0, 0, 0, 0, 0} / Fr_t{D, 0, 0, 0, 0, 0, 0, 0};
+        LookupProof pf;
+        std::vector<Fr_t> ws;
+        fs_phase1(claim, A, Sx, Bv, Tx, mx, alpha, beta, Cc, inv_ratio, alpha_sq, uu, tr, ws, pf, false);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = now_ms() - t0;
+        to_host(A, A_out);
+        memcpy(evals, pf.ev.data(), pf.ev.size() * 32);
+        memcpy(ws_out, ws.data(), ws.size() * 32);
+        memcpy(terms, &pf.A_f, 32); memcpy(terms + 8, &pf.S_f, 32); memcpy(terms + 16, &pf.B_f, 32);
+        memcpy(terms + 24, &pf.T_f, 32); memcpy(terms + 32, &pf.m_f, 32);
+        memcpy(st, tr.state, 32);
+        return 0;
     } catch (...) { return -1; }
 }
 

@@ -123,3 +123,55 @@ def test_argument_checks(zk, prover):
         fr.product_sumcheck(prover, zk.Transcript("x"), [t], ["a", "b"])   # one column
     with pytest.raises(ValueError):
         fr.partial_me(prover, t, [1], 4, 1)
+
+
+def lookup_instance(rng, logD, logN):
+    D, N = 1 << logD, 1 << logN
+    T = [rng.randrange(-(1 << 15), 1 << 15) % fo.P for _ in range(N)]
+    idx = [min(N - 1, max(0, int(rng.gauss(N / 2, N / 8)))) for _ in range(D)]
+    S = [T[i] for i in idx]
+    m = [0] * N
+    for i in idx:
+        m[i] += 1
+    return S, T, m
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 1000, 4097])
+def test_inv_add(zk, prover, n):
+    rng = random.Random(n)
+    fr = zk.fr
+    beta = rng.randrange(fo.P)
+    vals = rnd(rng, n)
+    vals[0] = (fo.P - beta) % fo.P                      # zero denominator: Fermat's inverse is 0
+    if n > 8:
+        vals[n // 2] = (fo.P - beta) % fo.P
+    got = fr.to_host(fr.inv_add(prover, fr.to_device(vals), beta))
+    assert got == fo.inv_add(vals, beta)
+
+
+@pytest.mark.parametrize("logD,logN", [(1, 1), (3, 3), (5, 2), (9, 6), (12, 12), (13, 8)])
+def test_lookup_sumcheck(zk, prover, logD, logN):
+    rng = random.Random(logD * 31 + logN)
+    fr = zk.fr
+    S, T, m = lookup_instance(rng, logD, logN)
+    alpha, beta = rng.randrange(fo.P), rng.randrange(fo.P)
+    u = rnd(rng, logD)
+    dS, dT, dm = fr.to_device(S), fr.to_device(T), fr.to_device(m)
+    dA, dB = fr.inv_add(prover, dS, beta), fr.inv_add(prover, dT, beta)
+    A, B = fo.inv_add(S, beta), fo.inv_add(T, beta)
+    assert fr.to_host(dA) == A and fr.to_host(dB) == B
+    Cc = (alpha * alpha - sum(b * mm for b, mm in zip(B, m))) % fo.P
+    assert fr.dot(prover, dB, dm) == sum(b * mm for b, mm in zip(B, m)) % fo.P
+    tr = zk.Transcript("tlookup")
+    ev, ws, term = fr.lookup_sumcheck(prover, tr, dA, dS, dB, dT, dm, alpha, beta, Cc, u)
+    otr = fo.Transcript("tlookup")
+    oev, ows, oterm = fo.lookup_sumcheck(otr, A, S, B, T, m, alpha, beta, Cc, u)
+    assert ev == oev and ws == ows and term == oterm and tr.state == otr.state
+    claim = (alpha + alpha * alpha) % fo.P               # the honest instance satisfies every round check
+    for e, v in zip(ev, ws):
+        assert (e[0] + e[1]) % fo.P == claim
+        claim = fo.lagrange(e, v)
+    # terminals are the columns' multilinear extensions at the reversed challenges
+    pt = list(reversed(ws))
+    assert term[0] == fo.mle_eval(A, pt) and term[1] == fo.mle_eval(S, pt)
+    assert term[4] == fo.mle_eval(m, pt[:logN]) and term[3] == fo.mle_eval(T, pt[:logN])

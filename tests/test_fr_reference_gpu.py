@@ -80,3 +80,22 @@ def test_hadamard_and_quartic(refA, zk, prover, logn):
     ev, ws, fin = fr.product_sumcheck(prover, tr, d, ["smx" + "p%d" % i for i in range(5)])
     st, rev, rws, rfin = refA.quartic(zk.Transcript("qp").state, "smx", *cols)
     assert st == tr.state and rev == ev and rws == ws and rfin == fin[1:]
+
+
+@pytest.mark.parametrize("logD,logN", [(4, 4), (7, 5), (11, 8)])
+def test_lookup_sumcheck(refA, zk, prover, logD, logN):
+    from test_fr_gpu import lookup_instance
+    rng = random.Random(logD * 31 + logN)
+    fr = zk.fr
+    S, T, m = lookup_instance(rng, logD, logN)
+    alpha, beta = rng.randrange(fo.P), rng.randrange(fo.P)
+    u = rnd(rng, logD)
+    st, rA, rev, rws, rterm = refA.lookup(zk.Transcript("tlookup").state, S, T, m, alpha, beta, u)
+    dS, dT, dm = fr.to_device(S), fr.to_device(T), fr.to_device(m)
+    dA, dB = fr.inv_add(prover, dS, beta), fr.inv_add(prover, dT, beta)
+    assert fr.to_host(dA) == rA == fo.inv_add(S, beta)
+    B = fo.inv_add(T, beta)
+    Cc = (alpha * alpha - sum(b * mm for b, mm in zip(B, m))) % fo.P
+    tr = zk.Transcript("tlookup")
+    ev, ws, term = fr.lookup_sumcheck(prover, tr, dA, dS, dB, dT, dm, alpha, beta, Cc, u)
+    assert tr.state == st and ev == rev and ws == rws and term == rterm

@@ -66,6 +66,9 @@ def load_library():
         "zkh_fr_partial_me": (i, [vp, vp, u64, u32, u64, vp, vp]),
         "zkh_fr_mle_eval": (i, [vp, vp, vp, u32, vp]),
         "zkh_fr_mul_throughput": (i, [vp, u32, vp]),
+        "zkh_fr_inv_add": (i, [vp, vp, u64, vp, vp]),
+        "zkh_fr_dot": (i, [vp, vp, vp, u64, vp]),
+        "zkh_fr_lookup_sumcheck": (i, [vp, vp, vp, vp, vp, vp, u32, u32, vp, vp, vp, vp, vp, vp, vp, vp]),
         "zkh_fr_sumcheck": (i, [vp, vp, i, u32, vp, vp, vp, vp, vp]),
         "zkh_shard_begin": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp]),
         "zkh_shard_round_local": (i, [vp, u32, vp]),

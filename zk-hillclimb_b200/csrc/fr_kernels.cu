@@ -13,64 +13,9 @@
 // the values it just produced, reduces over the grid through the last CTA to finish, and runs the
 // Fiat-Shamir step (nt labelled 32-byte absorbs, challenge with the reference's limb mapping) on the
 // device.  The host queues all rounds and reads the results back once.
-#include "common.cuh"
-#include "fr.cuh"
+#include "fr_dev.cuh"
 
 namespace zkh {
-
-constexpr int FR_THREADS = 128;
-constexpr int FR_MAXC = 4;
-constexpr int FR_MAXNT = 5;
-
-struct FrPtrs {
-    const Fr* in[FR_MAXC];
-    Fr* out[FR_MAXC];
-};
-struct FrLabels { ZkhTag t[FR_MAXNT]; };
-
-// ------------------------------------------------------------------ reductions
-template <int NT>
-__device__ __forceinline__ void fr_block_sum(Fr (&v)[NT], Fr* sh) {  // sh: NT*32 elements
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
-#pragma unroll
-    for (int t = 0; t < NT; t++)
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) v[t] = fr_add(v[t], fr_shfl_down(v[t], d));
-    if (lane == 0)
-#pragma unroll
-        for (int t = 0; t < NT; t++) sh[t * 32 + warp] = v[t];
-    __syncthreads();
-    if (warp == 0) {
-#pragma unroll
-        for (int t = 0; t < NT; t++) {
-            Fr x = lane < nwarp ? sh[t * 32 + lane] : fr_zero();
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) x = fr_add(x, fr_shfl_down(x, d));
-            v[t] = x;
-        }
-    }
-    __syncthreads();
-}
-
-// full 32 challenge bytes as eight little-endian limbs; st is ratcheted (fs::Transcript::challenge_bytes)
-__device__ __forceinline__ void tr_warp_challenge_limbs(uint32_t st[8], uint32_t out[8]) {
-    const uint32_t lane = threadIdx.x & 31;
-    uint32_t w[16], o[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) w[i] = st[i];
-    w[8] = (lane == 1) ? 0x72746368u : 0x6368616cu;  // "rtch" : "chal"
-    w[9] = 0x80000000u;
-#pragma unroll
-    for (int i = 10; i < 15; i++) w[i] = 0;
-    w[15] = 36 * 8;
-    sha256_iv(o);
-    sha256_compress_compact(o, w);
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        st[i] = __shfl_sync(0xffffffffu, o[i], 1);
-        out[i] = bswap32(__shfl_sync(0xffffffffu, o[i], 0));
-    }
-}
 
 // Round end on warp 0: make the sums plain, publish them, absorb each under its label, draw the
 // challenge (zkllm-src/vrf_common.cuh:233-244: limbs from the challenge bytes, top limb reduced
@@ -286,21 +231,8 @@ __global__ void __launch_bounds__(256) fr_mul_probe_kernel(Fr seed, uint32_t ite
     if (fr_is_zero(fr_add(fr_add(a, b), fr_add(c, d)))) out[0] = a;   // keeps the chains alive
 }
 
-static bool fr_canonical(const uint32_t* x) {
-    static const uint32_t P[8] = {0x00000001u, 0xffffffffu, 0xfffe5bfeu, 0x53bda402u, 0x09a1d805u, 0x3339d808u, 0x299d7d48u, 0x73eda753u};
-    for (int i = 7; i >= 0; i--) {
-        if (x[i] < P[i]) return true;
-        if (x[i] > P[i]) return false;
-    }
-    return false;
-}
-static unsigned fr_grid(zkh_ctx* c, size_t items, int per_sm) {
-    size_t want = (items + FR_THREADS - 1) / FR_THREADS, cap = (size_t)c->sm_count * per_sm;
-    if (want < 1) want = 1;
-    return (unsigned)(want < cap ? want : cap);
-}
 // E (2^v entries) from the point u (device, v entries)
-static int fr_eq_enqueue(zkh_ctx* c, const Fr* u_dev, const Fr* u_host, uint32_t v, Fr* E) {
+int fr_eq_enqueue(zkh_ctx* c, const Fr* u_dev, const Fr* u_host, uint32_t v, Fr* E) {
     const int head = v < 10 ? (int)v : 10;
     fr_eq_head_kernel<<<1, 512, 0, c->stream>>>(E, u_dev, head);
     for (uint32_t l = head; l < v; l++) {
@@ -379,6 +311,21 @@ extern "C" int zkh_fr_mle_eval(zkh_ctx* c, const void* t_dev, const void* u, uin
     ZKH_CUDA(c, cudaMemcpyAsync(u_dev, u, (size_t)v * 32, cudaMemcpyHostToDevice, c->stream));
     ZKH_TRY(fr_eq_enqueue(c, u_dev, (const Fr*)u, v, eq));
     fr_dot_kernel<<<g, FR_THREADS, 0, c->stream>>>((const Fr*)t_dev, eq, n, part);
+    fr_sum_fix_kernel<<<1, FR_THREADS, 0, c->stream>>>(part, g, res);
+    ZKH_CUDA(c, cudaMemcpyAsync(out32, res, 32, cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    return ZKH_OK;
+}
+
+extern "C" int zkh_fr_dot(zkh_ctx* c, const void* a_dev, const void* b_dev, uint64_t n, void* out32) {
+    if (!c) return ZKH_ERR_ARG;
+    if (!a_dev || !b_dev || !out32 || !n) return zkh_fail(c, ZKH_ERR_ARG, "fr_dot: bad arguments");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    const unsigned g = fr_grid(c, n, 8);
+    ZKH_TRY(zkh_ws_reserve(c, (size_t)g * 32 + 32));
+    Fr* part = (Fr*)c->ws;
+    Fr* res = part + g;
+    fr_dot_kernel<<<g, FR_THREADS, 0, c->stream>>>((const Fr*)a_dev, (const Fr*)b_dev, (size_t)n, part);
     fr_sum_fix_kernel<<<1, FR_THREADS, 0, c->stream>>>(part, g, res);
     ZKH_CUDA(c, cudaMemcpyAsync(out32, res, 32, cudaMemcpyDeviceToHost, c->stream));
     ZKH_CUDA(c, cudaStreamSynchronize(c->stream));

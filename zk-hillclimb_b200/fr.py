@@ -119,6 +119,43 @@ def product_sumcheck(prover, tr, cols, labels):
     return [unpack(e) for e in ev], unpack(ch), unpack(fin)
 
 
+def inv_add(prover, t, beta):
+    """tlookup_inv_kernel (zkllm-src/tlookup.cu:50-62): 1/(t[i] + beta), 0 for a zero denominator."""
+    out = _new(prover, t.shape[0])
+    b = _pt([beta])                       # keep the host arrays alive across the call
+    prover._ck(prover._L.zkh_fr_inv_add(prover._h, t.data_ptr(), t.shape[0], b.ctypes.data, out.data_ptr()))
+    return out
+
+
+def dot(prover, a, b):
+    """(a * b).sum() over Fr."""
+    out = (C.c_uint8 * 32)()
+    prover._ck(prover._L.zkh_fr_dot(prover._h, a.data_ptr(), b.data_ptr(), a.shape[0], out))
+    return int.from_bytes(bytes(out), "little")
+
+
+def lookup_sumcheck(prover, tr, A, S, Bv, T, m, alpha, beta, Cc, u):
+    """fs_phase1 + fs_phase2 (zkllm-src/zkob_lookup.cuh:143-198): the logUp sumcheck over A = 1/(S+beta) (D entries),
+    Bv = 1/(T+beta), the table T and the multiplicities m (N entries), u the logD-entry point.  Claim alpha + alpha^2,
+    Cc = alpha^2 - sum(Bv*m).  Returns (evals[rounds][4], challenges, (A_f, S_f, B_f, T_f, m_f)); ``tr`` advances as
+    the reference's transcript (labels p0..p3 per round)."""
+    D, N = A.shape[0], m.shape[0]
+    logD, logN = D.bit_length() - 1, N.bit_length() - 1
+    if D != 1 << logD or N != 1 << logN or len(u) != logD or S.shape[0] != D or Bv.shape[0] != N or T.shape[0] != N:
+        raise ValueError("lookup_sumcheck: power-of-two sizes, len(u) == log2(D)")
+    ev = np.zeros((logD, 4, 8), dtype=np.uint32)
+    ws = np.zeros((logD, 8), dtype=np.uint32)
+    term = np.zeros((5, 8), dtype=np.uint32)
+    st = (C.c_uint8 * 32)(*tr.state)
+    a_, b_, c_, u_ = _pt([alpha]), _pt([beta]), _pt([Cc]), _pt(u)      # keep the host arrays alive across the call
+    prover._ck(prover._L.zkh_fr_lookup_sumcheck(prover._h, A.data_ptr(), S.data_ptr(), Bv.data_ptr(), T.data_ptr(),
+                                                m.data_ptr(), logD, logN, a_.ctypes.data, b_.ctypes.data,
+                                                c_.ctypes.data, u_.ctypes.data, st, ev.ctypes.data,
+                                                ws.ctypes.data, term.ctypes.data))
+    tr.state = bytes(st)
+    return [unpack(e) for e in ev], unpack(ws), tuple(unpack(term))
+
+
 def mul_throughput(prover, iters=4096):
     """Montgomery products per second (in 10^9) measured on the prover's GPU."""
     out = C.c_double(0)
