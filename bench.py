@@ -457,10 +457,14 @@ def run_suite_fr(args):
                 "fraction_of_probe_rate": muls / ms / 1e6 / gm}
         if refA is not None:
             st0 = zk.Transcript("fr-bench").state
-            if nc == 3:
-                st, ev, ws, fin = refA.hadamard(st0, *cols_h[:3])
-            else:
-                st, ev, ws, fin = refA.quartic(st0, "q", *cols_h)
+            best = 1e30
+            for _ in range(2):                                   # first call warms the reference's allocations
+                if nc == 3:
+                    st, ev, ws, fin = refA.hadamard(st0, *cols_h[:3])
+                else:
+                    st, ev, ws, fin = refA.quartic(st0, "q", *cols_h)
+                best = min(best, refA.ms.value)
+            refA.ms.value = best
             line.update({"reference_cuda_ms": refA.ms.value, "speedup_vs_reference_cuda": refA.ms.value / ms,
                          "same_transcript": bool(st == out["st"] and ev == out["r"][0] and ws == out["r"][1])})
         print(json.dumps(line), flush=True)
@@ -493,7 +497,11 @@ def run_suite_fr(args):
     line = {"suite": "tLookup over Fr: D=2^%d lookups into a 2^%d-row table (two batched inversions, %d sumcheck rounds)" % (logDl, logNl, logDl),
             "ms": ms}
     if refA is not None:
-        st, rA, rev, rws, rterm = refA.lookup(zk.Transcript("tl-bench").state, S_l, T_l, m_l, alpha, beta, u_l)
+        best = 1e30
+        for _ in range(2):
+            st, rA, rev, rws, rterm = refA.lookup(zk.Transcript("tl-bench").state, S_l, T_l, m_l, alpha, beta, u_l)
+            best = min(best, refA.ms.value)
+        refA.ms.value = best
         line.update({"reference_cuda_ms": refA.ms.value, "speedup_vs_reference_cuda": refA.ms.value / ms,
                      "same_transcript": bool(st == hold["st"] and rev == hold["r"][0] and rws == hold["r"][1] and rterm == hold["r"][2])})
     print(json.dumps(line), flush=True)
