@@ -147,6 +147,16 @@ ZKH_API size_t zkh_sumcheck_workspace(int nc, uint32_t logn);
 ZKH_API int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* const* cols_dev, int nc, uint32_t logn,
                       const uint64_t* lam, int nlam, const char* tag, uint8_t state[32], uint64_t* msgs,
                       uint64_t* chals, uint64_t* finals);
+/* Programmable eq-weighted zero-check: the summand is
+ *   col0 * (konst + sum_j coef_j * prod_{k < deg_j} col[idx_jk]),   deg_j in 1..3,
+ * the shape of the integer-layer gadgets' constraint polynomials (zkllm-src/p3_int_gadgets.cuh:326, :726,
+ * :977-1035, :1307, :1563-1640, :1818), which the reference proves with its host loop p3hwl::sc5_prove
+ * (non-zk path of sc5z).  Five evaluations per round (Msg5), absorbed under `tag`.
+ * prog: word 0 = number of terms (<= 120), word 1 = konst, then per term two words: coefficient,
+ * degree | idx0 << 8 | idx1 << 16 | idx2 << 24.  nwords = 2 + 2*terms.  1 <= nc <= 32. */
+ZKH_API int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
+                           const uint64_t* prog, int nwords, const char* tag, uint8_t state[32], uint64_t* msgs,
+                           uint64_t* chals, uint64_t* finals);
 /* Column and coefficient counts of a ZKH_F_HW_* summand (ZKH_ERR_ARG for any other id). */
 ZKH_API int zkh_sumcheck_wide_shape(int functor, int* nc, int* nlam);
 
@@ -291,6 +301,11 @@ ZKH_API size_t zkh_gkr_proof_size(uint32_t L);
 ZKH_API int zkh_gkr_prove(zkh_ctx* ctx, const uint64_t* p_dev, const uint64_t* q_dev, uint32_t L, int combine_last,
                           const char* tag, uint8_t state[32], uint64_t* rfin, uint64_t cpq[2], uint8_t* out,
                           size_t cap, size_t* written);
+
+/* Host-side construction of the integer layer's function tables (p3ig::build_tables,
+ * zkllm-src/p3_int_gadgets.cuh:99-118): kind 0 EXPT (2^17 rows), 1 SILU (2^20 rows), 2 ISQ (2^16 rows, uses d).
+ * col0 / col1: host arrays of that many field elements.  No GPU involved. */
+ZKH_API int zkh_ig_table(int kind, uint32_t d, uint64_t* col0, uint64_t* col1);
 
 /* ======================================================================================
  * BLS12-381 scalar field (Fr) back-end: the reference's first proof stack.

@@ -12,6 +12,7 @@
 #include <cstdint>
 #include <cstring>
 #include <string>
+#include <map>
 #include <vector>
 #include "p3_goldilocks.cuh"
 #include "fs_transcript.hpp"
@@ -346,6 +347,106 @@ bool lup_deserialize(const uint8_t* in, size_t len, p3lu::LookupProof& pf) {
     pf.y_virt.resize(nv); memcpy(pf.y_virt.data(), p, (size_t)nv * 8); p += (size_t)nv * 8;
     if (!gete(pf.open_hT) || !gete(pf.open_cnt)) return false;
     return p == end;
+}
+// gadget tail (p3ig::Tail) <-> bytes: u32 groups, each u32 len + GroupProof | u32 batches, each u32 len + BatchProof
+void tail_append(const p3ig::Tail& t, std::vector<uint8_t>& b) {
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    std::vector<uint8_t> tmp((size_t)64 << 20);
+    uint32_t ng = (uint32_t)t.lug.size();
+    app(&ng, 4);
+    for (auto& g : t.lug) { uint32_t n = (uint32_t)lu_serialize(g, tmp.data(), tmp.size()); app(&n, 4); app(tmp.data(), n); }
+    uint32_t nb = (uint32_t)t.batches.size();
+    app(&nb, 4);
+    for (auto& bp : t.batches) { uint32_t n = (uint32_t)bo_serialize(bp, tmp.data(), tmp.size()); app(&n, 4); app(tmp.data(), n); }
+}
+bool tail_parse(const uint8_t*& p, const uint8_t* end, p3ig::Tail& t) {
+    auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
+    uint32_t ng;
+    if (!need(4)) return false;
+    memcpy(&ng, p, 4); p += 4;
+    if (ng > 64) return false;
+    t.lug.resize(ng);
+    for (auto& g : t.lug) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (!need(n) || !lu_deserialize(p, n, g)) return false;
+        p += n;
+    }
+    uint32_t nb;
+    if (!need(4)) return false;
+    memcpy(&nb, p, 4); p += 4;
+    if (nb > 64) return false;
+    t.batches.resize(nb);
+    for (auto& bp : t.batches) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (!need(n) || !bo_deserialize(p, n, bp)) return false;
+        p += n;
+    }
+    return true;
+}
+size_t emit(const std::vector<uint8_t>& b, uint8_t* out, size_t cap) {
+    if (b.size() > cap) return 0;
+    memcpy(out, b.data(), b.size());
+    return b.size();
+}
+// p3iadd::Proof <-> bytes: u32 le | messages le*40 | yA yB yO | tail
+size_t iadd_serialize(const p3iadd::Proof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&pf.le, 4);
+    for (auto& m : pf.m) app(&m, 40);
+    app(&pf.yA, 8); app(&pf.yB, 8); app(&pf.yO, 8);
+    tail_append(pf.tail, b);
+    return emit(b, out, cap);
+}
+bool iadd_deserialize(const uint8_t* in, size_t len, p3iadd::Proof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    if (len < 4) return false;
+    memcpy(&pf.le, p, 4); p += 4;
+    if (pf.le > 40 || (size_t)(end - p) < (size_t)pf.le * 40 + 24) return false;
+    pf.m.resize(pf.le);
+    for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
+    memcpy(&pf.yA, p, 8); memcpy(&pf.yB, p + 8, 8); memcpy(&pf.yO, p + 16, 8); p += 24;
+    return tail_parse(p, end, pf.tail) && p == end;
+}
+// p3iswg::Proof <-> bytes: u32 le | rSIL rREM | messages le*40 | ySIL yU yM yR | tail
+size_t iswg_serialize(const p3iswg::Proof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&pf.le, 4); app(pf.rSIL.data(), 32); app(pf.rREM.data(), 32);
+    for (auto& m : pf.m) app(&m, 40);
+    app(&pf.ySIL, 8); app(&pf.yU, 8); app(&pf.yM, 8); app(&pf.yR, 8);
+    tail_append(pf.tail, b);
+    return emit(b, out, cap);
+}
+bool iswg_deserialize(const uint8_t* in, size_t len, p3iswg::Proof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    if (len < 68) return false;
+    memcpy(&pf.le, p, 4); memcpy(pf.rSIL.data(), p + 4, 32); memcpy(pf.rREM.data(), p + 36, 32); p += 68;
+    if (pf.le > 40 || (size_t)(end - p) < (size_t)pf.le * 40 + 32) return false;
+    pf.m.resize(pf.le);
+    for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
+    memcpy(&pf.ySIL, p, 8); memcpy(&pf.yU, p + 8, 8); memcpy(&pf.yM, p + 16, 8); memcpy(&pf.yR, p + 24, 8); p += 32;
+    return tail_parse(p, end, pf.tail) && p == end;
+}
+// the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
+const p3ig::Tables& ig_tables(uint32_t d, uint32_t btop) {
+    static std::map<std::pair<uint32_t, uint32_t>, p3ig::Tables> cache;
+    auto key = std::make_pair(d, btop);
+    auto it = cache.find(key);
+    if (it == cache.end()) it = cache.emplace(key, p3ig::build_tables(d, btop)).first;
+    return it->second;
+}
+p3fri::Hash hash_from(const uint8_t* p) { p3fri::Hash h; memcpy(h.data(), p, 32); return h; }
+p3lu::Col col_from(const uint64_t* v, size_t n, const uint8_t* root, uint32_t vreal) {
+    p3lu::Col c;
+    c.v.assign(v, v + n);
+    if (root) memcpy(c.root.data(), root, 32);
+    c.vreal = vreal;
+    return c;
 }
 // p3irs::Proof (non-zk) <-> bytes: u32 le, sf, nl, rng | limb roots nl*32 | messages le*40 | yX yY yL[nl] |
 //   u32 groups, each u32 len + GroupProof | u32 batches, each u32 len + BatchProof
@@ -765,6 +866,37 @@ int ref_lu_verify_v(uint8_t st[32], const uint64_t* const* tcols, uint32_t m, ui
     return ok ? 1 : 0;
 }
 
+// ---- integer-layer tables: columns of the reference's build_tables (which: 0 EXPT, 1 SILU, 2 ISQ, 3 EXP4) ----
+int ref_ig_table(uint32_t d, uint32_t btop, int which, uint64_t* const* cols_out, uint8_t id_out[32]) {
+    const p3ig::Tables& T = ig_tables(d, btop);
+    const p3lu::Table* t = which == 0 ? &T.EXPT : which == 1 ? &T.SILU : which == 2 ? &T.ISQ : which == 3 ? &T.EXP4 : nullptr;
+    if (!t) return -1;
+    for (size_t c = 0; c < t->cols.size(); c++) memcpy(cols_out[c], t->cols[c].data(), t->cols[c].size() * 8);
+    memcpy(id_out, t->id.data(), 32);
+    return (int)t->cols.size();
+}
+// ---- residual add / SwiGLU gadgets: host-only verifiers (p3_int_gadgets.cuh:739-773, :1834-1872) ----
+int ref_iadd_verify(uint8_t st[32], const uint8_t* rA, const uint8_t* rB, const uint8_t* rO, uint32_t le, uint32_t R, uint32_t Q,
+                    const uint8_t* proof, size_t len) {
+    p3iadd::Proof pf;
+    if (!iadd_deserialize(proof, len, pf)) return 0;
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3iadd::verify(tr, ig_tables(64, 12), pf, hash_from(rA), hash_from(rB), hash_from(rO), le, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+int ref_iswg_verify(uint8_t st[32], const uint8_t* rG, const uint8_t* rU, const uint8_t* rM, uint32_t le, uint32_t R, uint32_t Q,
+                    const uint8_t* proof, size_t len) {
+    p3iswg::Proof pf;
+    if (!iswg_deserialize(proof, len, pf)) return 0;
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3iswg::verify(tr, ig_tables(64, 12), pf, hash_from(rG), hash_from(rU), hash_from(rM), le, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+
 // ---- integer matmul gadget: the reference's host-only verifier (p3_int_gadgets.cuh:608-655) ----
 int ref_imm_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootW[32], const uint8_t rootY[32],
                    uint32_t lj, uint32_t lk, uint32_t li, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
@@ -1018,6 +1150,54 @@ size_t ref_irs_prove(uint8_t st[32], const uint64_t* acc, const uint8_t rootX[32
         cudaDeviceSynchronize();
         if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
         n = irs_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+// p3iadd::prove / p3iswg::prove with the reference's own witness replay; commitments, lookups and openings on the GPU
+size_t ref_iadd_prove(uint8_t st[32], const uint64_t* a, const uint64_t* b, const uint8_t* rA, const uint8_t* rB,
+                      const uint8_t* rO, uint32_t le, uint32_t R, uint32_t Q, uint8_t* out, size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        const size_t N = (size_t)1 << le;
+        std::vector<gl_t> av(a, a + N), bv(b, b + N);
+        const p3ig::Tables& T = ig_tables(64, 12);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3iadd::Wit w = p3iadd::gen_witness(le, av, bv);
+        p3lu::Col ca = col_from(a, N, rA, le), cb = col_from(b, N, rB, le), co = col_from(w.out.data(), N, rO, le);
+        p3iadd::Operands ops{&ca, &cb, &co};
+        auto pf = p3iadd::prove(tr, w, T, ops, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = iadd_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+size_t ref_iswg_prove(uint8_t st[32], const uint64_t* g, const uint64_t* u, const uint8_t* rG, const uint8_t* rU,
+                      const uint8_t* rM, uint32_t le, uint32_t R, uint32_t Q, uint8_t* out, size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        const size_t N = (size_t)1 << le;
+        std::vector<gl_t> gv(g, g + N), uv(u, u + N);
+        const p3ig::Tables& T = ig_tables(64, 12);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3iswg::Wit w = p3iswg::gen_witness(le, gv, uv, T);
+        p3lu::Col cg = col_from(g, N, rG, le), cu = col_from(u, N, rU, le), cm = col_from(w.mo.data(), N, rM, le);
+        p3iswg::Operands ops{&cg, &cu, &cm};
+        auto pf = p3iswg::prove(tr, w, T, ops, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = iswg_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);

@@ -1,0 +1,59 @@
+"""CPU stand-in engine and reference windows for the integer-layer gadgets (test infrastructure)."""
+import ctypes as C
+
+import numpy as np
+
+from irs_helpers import OracleStandaloneLuEngine
+from lu_helpers import _Arr
+from zc_helpers import zc_sumcheck
+
+GL_P = 0xFFFFFFFF00000001
+
+
+class OracleGadgetEngine(OracleStandaloneLuEngine):
+    """Everything the gadget host logic asks of an engine, on the CPU oracle."""
+
+    def sc_prove_zc(self, tr, tag, cols, terms, konst=0):
+        st, m, r, fin = zc_sumcheck(self.orc, tr.state, tag, [c.a for c in cols], terms, konst)
+        tr.state = st
+        return r, m, fin
+
+
+def arr(engine, a):
+    return _Arr(np.ascontiguousarray(a))
+
+
+def commit(engine, col, R):
+    return (col, engine.commit_gpu_rootonly(col, R))
+
+
+def ref_table(ref, which, d=64, btop=12):
+    rows, nc = {0: (1 << 17, 2), 1: (1 << 20, 2), 2: (1 << 16, 2), 3: (32, 3)}[which]
+    cols = [np.zeros(rows, dtype=np.uint64) for _ in range(nc)]
+    u64p = C.POINTER(C.c_uint64)
+    ptrs = (u64p * nc)(*[c.ctypes.data_as(u64p) for c in cols])
+    tid = (C.c_uint8 * 32)()
+    assert ref.lib.ref_ig_table(C.c_uint32(d), C.c_uint32(btop), which, ptrs, tid) == nc
+    return cols, bytes(tid)
+
+
+def ref_verify3(ref, name, st, roots, le, R, Q, proof):
+    """ref_iadd_verify / ref_iswg_verify: three operand roots, (le, R, Q)."""
+    s = (C.c_uint8 * 32)(*st)
+    ok = getattr(ref.lib, name)(s, roots[0], roots[1], roots[2], C.c_uint32(le), C.c_uint32(R), C.c_uint32(Q), bytes(proof),
+                                C.c_size_t(len(proof)))
+    return bool(ok), bytes(s)
+
+
+def ref_prove2(ref, name, st, a, b, roots, le, R, Q):
+    """ref_iadd_prove / ref_iswg_prove (GPU): two input columns, three operand roots."""
+    s = (C.c_uint8 * 32)(*st)
+    cap = 64 << 20
+    out = (C.c_uint8 * cap)()
+    ms = C.c_double(0)
+    f = getattr(ref.lib, name)
+    f.restype = C.c_size_t
+    a, b = np.ascontiguousarray(a, dtype=np.uint64), np.ascontiguousarray(b, dtype=np.uint64)
+    n = f(s, a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), roots[0], roots[1], roots[2], C.c_uint32(le),
+          C.c_uint32(R), C.c_uint32(Q), out, C.c_size_t(cap), C.byref(ms))
+    return bytes(out)[:n], bytes(s), ms.value

@@ -1,0 +1,65 @@
+"""Integer-layer gadgets (zk_hillclimb_b200.ig) on CPU: the host logic over an oracle-backed engine produces
+proofs the reference's own host-only verifiers accept, ending on the same transcript state; tampered proofs
+are rejected; the function tables equal the reference's build_tables."""
+import numpy as np
+import pytest
+
+from ig_helpers import OracleGadgetEngine, arr, commit, ref_table, ref_verify3
+
+
+@pytest.fixture(scope="module")
+def tables(zk):
+    return zk.ig.build_tables(zk.load_library(), 64, 12)
+
+
+def test_function_tables_equal_reference(ref, zk, tables):
+    for which, name in ((0, "EXPT"), (1, "SILU"), (2, "ISQ"), (3, "EXP4")):
+        cols, tid = ref_table(ref, which)
+        assert tables[name]["id"] == tid, name
+        for a, b in zip(tables[name]["cols"], cols):
+            assert (a == b).all()
+
+
+def tamper_rejected(ref, name, st0, roots, le, R, Q, pf):
+    for off in (5, 4 + 7 * 8, len(pf) // 2, len(pf) - 11):
+        bad = bytearray(pf)
+        bad[off] ^= 1
+        assert not ref_verify3(ref, name, st0, roots, le, R, Q, bytes(bad))[0]
+
+
+@pytest.mark.parametrize("le", [5, 8])
+def test_iadd(orc, ref, zk, tables, le):
+    R, Q = 1, 24
+    ig = zk.ig
+    eng = OracleGadgetEngine(orc)
+    g = np.random.default_rng(le)
+    a, b = g.integers(-(1 << 18), 1 << 18, 1 << le), g.integers(-(1 << 18), 1 << 18, 1 << le)
+    a[0], b[0] = (1 << 18) - 1, 1 << 18                    # top of the window
+    out, idxO = ig.iadd_witness(ig.lift(a), ig.lift(b))
+    A, B, O = (commit(eng, arr(eng, x), R) for x in (ig.lift(a), ig.lift(b), out))
+    tr = zk.Transcript("iadd")
+    pf = ig.iadd_prove(eng, tr, tables, A, B, O, arr(eng, idxO), le, R, Q)
+    st0 = zk.Transcript("iadd").state
+    ok, st = ref_verify3(ref, "ref_iadd_verify", st0, [A[1], B[1], O[1]], le, R, Q, pf)
+    assert ok and st == tr.state
+    tamper_rejected(ref, "ref_iadd_verify", st0, [A[1], B[1], O[1]], le, R, Q, pf)
+    with pytest.raises(ValueError):
+        ig.iadd_witness(ig.lift(np.array([1 << 18])), ig.lift(np.array([1 << 18])))
+
+
+@pytest.mark.parametrize("le", [5, 7])
+def test_iswg(orc, ref, zk, tables, le):
+    R, Q = 1, 24
+    ig = zk.ig
+    eng = OracleGadgetEngine(orc)
+    g = np.random.default_rng(100 + le)
+    gv, uv = g.integers(-(1 << 19), 1 << 19, 1 << le), g.integers(-(1 << 15), 1 << 15, 1 << le)
+    gv[:2] = (-(1 << 19), (1 << 19) - 1)
+    sil, rem, mo, iG, iR, iM = ig.iswg_witness(ig.lift(gv), ig.lift(uv), tables)
+    G, U, MO = (commit(eng, arr(eng, x), R) for x in (ig.lift(gv), ig.lift(uv), mo))
+    tr = zk.Transcript("iswg")
+    pf = ig.iswg_prove(eng, tr, tables, G, U, MO, (arr(eng, sil), arr(eng, rem), arr(eng, iG), arr(eng, iR), arr(eng, iM)), le, R, Q)
+    st0 = zk.Transcript("iswg").state
+    ok, st = ref_verify3(ref, "ref_iswg_verify", st0, [G[1], U[1], MO[1]], le, R, Q, pf)
+    assert ok and st == tr.state
+    tamper_rejected(ref, "ref_iswg_verify", st0, [G[1], U[1], MO[1]], le, R, Q, pf)

@@ -1,0 +1,53 @@
+"""The programmable zero-check engine on CUDA against the Python-integer evaluation and, for the two summands
+the library also has as compiled functors (rescale), against those."""
+import numpy as np
+import pytest
+
+from conftest import lcg_cols
+from zc_helpers import zc_sumcheck
+
+pytestmark = pytest.mark.gpu
+GL_P = 0xFFFFFFFF00000001
+
+PROGRAMS = {
+    "add": (4, [(1, (1,)), (1, (2,)), (GL_P - 1, (3,))], 0),                                   # E*(A+B-O)
+    "swiglu": (5, [(1, (1, 2)), (GL_P - 65536, (3,)), (GL_P - 1, (4,))], 32768),              # E*(SIL*U+2^15-MO*2^16-REM)
+    "rope": (7, [(1, (1, 5)), (1, (2, 6)), (GL_P - 16384, (3,)), (GL_P - 1, (4,))], 8192),
+    "cubic": (9, [(3, (1, 2, 3)), (5, (4, 4)), (7, (8,)), (11, (5, 6, 7))], 99),
+    "wide": (20, [(k + 1, (k, 19 - k)) for k in range(1, 10)] + [(2, (10, 11, 12))], 1),
+}
+
+
+@pytest.mark.parametrize("name", sorted(PROGRAMS))
+@pytest.mark.parametrize("logn", [1, 2, 7, 12])
+def test_matches_python_evaluation(orc, zk, prover, name, logn):
+    nc, terms, konst = PROGRAMS[name]
+    if logn == 12 and nc > 9:
+        pytest.skip("python evaluation too slow")
+    cols = lcg_cols(orc, 1 << logn, nc, 31 * logn + nc)
+    tr = zk.Transcript("zc")
+    r, m, fin = prover.sc_prove_zc(tr, "isw-sc", [zk.p3.to_device(c) for c in cols], terms, konst)
+    st, m0, r0, f0 = zc_sumcheck(orc, orc.tr_init("zc"), "isw-sc", cols, terms, konst)
+    assert st == tr.state and (m == m0).all() and (r == r0).all() and (fin == f0).all()
+
+
+@pytest.mark.parametrize("nl", [1, 2])
+def test_matches_compiled_rescale_summand(orc, zk, prover, nl):
+    logn = 15
+    cols = lcg_cols(orc, 1 << logn, 3 + nl, 5 + nl)
+    H, P2 = 1 << 15, 1 << 16
+    d = [zk.p3.to_device(c) for c in cols]
+    tr1 = zk.Transcript("zc")
+    r1, m1, f1 = prover.sc_prove_gpu(tr1, "irs-sc", d, zk.p3.F_IRS1 if nl == 1 else zk.p3.F_IRS2, 5, [H, P2])
+    terms = [(1, (1,)), (GL_P - P2, (2,)), (GL_P - 1, (3,))] + ([(GL_P - 65536, (4,))] if nl == 2 else [])
+    tr2 = zk.Transcript("zc")
+    r2, m2, f2 = prover.sc_prove_zc(tr2, "irs-sc", d, terms, H)
+    assert tr1.state == tr2.state and (m1 == m2).all() and (r1 == r2).all() and (f1 == f2).all()
+
+
+def test_argument_checks(zk, prover):
+    d = [zk.p3.to_device(np.zeros(4, dtype=np.uint64)) for _ in range(3)]
+    with pytest.raises(Exception):
+        prover.sc_prove_zc(zk.Transcript("x"), "t", d, [(1, (3,))])            # column index out of range
+    with pytest.raises(Exception):
+        prover.sc_prove_zc(zk.Transcript("x"), "t", d, [(1, (1, 1, 1, 1))])    # degree 4 term

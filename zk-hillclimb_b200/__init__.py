@@ -8,10 +8,12 @@ Layout:
   build.py    nvcc recipe (sm_100a, in-tree)
   _lib.py     ctypes binding of the C ABI; raises if the library is missing
   p3.py       host-side mirror of the reference's in-process prover interface
+  ig.py       integer-layer gadgets (residual add, SwiGLU, ...) as host logic over the engine
   fr.py       host-side mirror of the BLS12-381 Fr pieces (eq tensors, folds, product sumchecks)
 """
 from . import _lib  # noqa: F401
 from ._lib import ZkhError, lib_path, load_library  # noqa: F401
 from . import p3  # noqa: F401
 from . import fr  # noqa: F401
+from . import ig  # noqa: F401
 from .p3 import (F_GKR, F_LOGUP, F_PROD2, F_PROD3, GL_P, Prover, Transcript)  # noqa: F401

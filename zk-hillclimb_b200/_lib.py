@@ -61,6 +61,8 @@ def load_library():
         "zkh_sumcheck_workspace": (sz, [i, u32]),
         "zkh_sumcheck_wide": (i, [vp, i, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_wide_shape": (i, [i, vp, vp]),
+        "zkh_sumcheck_zerocheck": (i, [vp, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
+        "zkh_ig_table": (i, [i, u32, vp, vp]),
         "zkh_fr_eq_build": (i, [vp, vp, u32, vp]),
         "zkh_fr_fold": (i, [vp, vp, u64, vp, vp]),
         "zkh_fr_partial_me": (i, [vp, vp, u64, u32, u64, vp, vp]),

@@ -353,3 +353,36 @@ extern "C" int zkh_gl_bind(zkh_ctx* c, const uint64_t* in_dev, uint64_t* out_dev
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }
+
+// Public lookup tables of the integer layer whose entries come from double-precision functions
+// (zkllm-src/p3_int_gadgets.cuh:99-118).  They are part of the proof statement (the table hash is absorbed),
+// so they are computed here on the host with the same libm calls and roundings:
+//   kind 0  EXPT  2^17 rows  (t, round(2^16 exp(-t/2^8)) for t < 2^16, else 0)
+//   kind 1  SILU  2^20 rows  (x, round(2^16 silu(x/2^16))) for x = j - 2^19, both as field elements
+//   kind 2  ISQ   2^16 rows  (m, round(2^32 sqrt(d/m)), 0 for m = 0)
+#include <cmath>
+extern "C" int zkh_ig_table(int kind, uint32_t d, uint64_t* col0, uint64_t* col1) {
+    if (!col0 || !col1) return ZKH_ERR_ARG;
+    auto lift = [](long long x) { return x >= 0 ? (uint64_t)x : GL_P - (uint64_t)(-x); };
+    if (kind == 0) {
+        for (size_t j = 0; j < ((size_t)1 << 17); j++) {
+            col0[j] = j;
+            col1[j] = j < 65536 ? (uint64_t)llround(65536.0 * exp(-(double)j / 256.0)) : 0;
+        }
+    } else if (kind == 1) {
+        for (size_t j = 0; j < ((size_t)1 << 20); j++) {
+            const long long xi = (long long)j - (1LL << 19);
+            const double xr = (double)xi / 65536.0;
+            col0[j] = lift(xi);
+            col1[j] = lift(llround(65536.0 * xr / (1.0 + exp(-xr))));
+        }
+    } else if (kind == 2) {
+        for (size_t j = 0; j < 65536; j++) {
+            col0[j] = j;
+            col1[j] = j ? (uint64_t)llround(4294967296.0 * sqrt((double)d / (double)j)) : 0;
+        }
+    } else {
+        return ZKH_ERR_ARG;
+    }
+    return ZKH_OK;
+}

@@ -122,6 +122,119 @@ static int scw_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, con
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "wide sumcheck launch");
 }
 
+
+// ------------------------------------------------------------------ programmable zero-check
+// Summand  col0 * (konst + sum_j coef_j * prod_{k < deg_j} col[idx_jk]),  deg_j in 1..3: the shape of every
+// eq-weighted constraint of the integer-layer gadgets (residual add, rescale, SwiGLU, RoPE, RMSNorm,
+// softmax: zkllm-src/p3_int_gadgets.cuh:326, :726, :977-1035, :1307, :1563-1640, :1818).  The reference runs
+// each of them through its host loop sc5_prove with a std::function per row; here the term list is data
+// (ZkhZcProg, read from device memory into shared memory), so one kernel serves all gadgets.
+// A thread stages the current value of every column in its own shared-memory column (no bank conflicts,
+// no synchronisation) so that terms can index columns at run time.
+constexpr int ZC_MAXTERMS = 120;
+struct ZkhZcProg {
+    uint32_t nterms, nc;
+    gl_t konst;
+    gl_t coef[ZC_MAXTERMS];
+    uint32_t packed[ZC_MAXTERMS];   // deg | idx0 << 8 | idx1 << 16 | idx2 << 24
+};
+
+template <int NCMAX>
+__global__ void __launch_bounds__(SCW_THREADS)
+zc_round_kernel(WidePtrs P, size_t items, int first, const ZkhZcProg* prog_g, ZkhCtl* ctl, gl_t* partials,
+                const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, ZkhTag tag) {
+    __shared__ ZkhZcProg prog;
+    __shared__ gl_t vals[NCMAX][SCW_THREADS];
+    __shared__ gl_t sh[SCW_NT * 32];
+    for (uint32_t j = threadIdx.x; j < sizeof(ZkhZcProg) / 4; j += blockDim.x)
+        reinterpret_cast<uint32_t*>(&prog)[j] = reinterpret_cast<const uint32_t*>(prog_g)[j];
+    __syncthreads();
+    const int nc = (int)prog.nc;
+    const uint32_t nterms = prog.nterms;
+    const gl_t konst = prog.konst;
+    const gl_t a = first ? 0 : *chal_prev;
+    const uint32_t tid = threadIdx.x;
+    gl_t s[SCW_NT];
+#pragma unroll
+    for (int t = 0; t < SCW_NT; t++) s[t] = 0;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < items; i += stride) {
+        gl_t cur[NCMAX], dif[NCMAX];
+#pragma unroll
+        for (int k = 0; k < NCMAX; k++) {
+            if (k < nc) {
+                if (first) {
+                    ulonglong2 v = ld2(P.in[k] + 2 * i);
+                    cur[k] = v.x;
+                    dif[k] = gl_sub(v.y, v.x);
+                } else {
+                    ulonglong2 u = ld2(P.in[k] + 4 * i), w = ld2(P.in[k] + 4 * i + 2);
+                    gl_t lo = gl_lerp(u.x, u.y, a), hi = gl_lerp(w.x, w.y, a);
+                    st2(P.out[k] + 2 * i, lo, hi);
+                    cur[k] = lo;
+                    dif[k] = gl_sub(hi, lo);
+                }
+            }
+        }
+#pragma unroll 1
+        for (int t = 0; t < SCW_NT; t++) {
+#pragma unroll
+            for (int k = 0; k < NCMAX; k++)
+                if (k < nc) { vals[k][tid] = cur[k]; cur[k] = gl_add(cur[k], dif[k]); }
+            Acc192 acc;
+            acc.clear();
+            for (uint32_t j = 0; j < nterms; j++) {
+                const uint32_t pk = prog.packed[j];
+                gl_t x = vals[(pk >> 8) & 0xff][tid];
+                if ((pk & 0xff) >= 2) x = gl_mul(x, vals[(pk >> 16) & 0xff][tid]);
+                if ((pk & 0xff) >= 3) x = gl_mul(x, vals[(pk >> 24) & 0xff][tid]);
+                acc.add_prod(prog.coef[j], x);
+            }
+            s[t] = gl_add(s[t], gl_mul(vals[0][tid], gl_add(acc.reduce(), konst)));
+        }
+    }
+    grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, 0);
+}
+
+template <int NCMAX>
+static int zc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t logn, const ZkhZcProg* prog_dev,
+                        const ZkhTag& tag, gl_t* finals_dev) {
+    cudaStream_t s = ctx->stream;
+    ZkhCtl* ctl = ctx->d_ctl;
+    const size_t n = (size_t)1 << logn;
+    static int occ = 0;
+    if (!occ) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, zc_round_kernel<NCMAX>, SCW_THREADS, 0);
+        if (occ < 1) occ = 1;
+    }
+    auto grid_for = [&](size_t items) {
+        size_t want = (items + SCW_THREADS - 1) / SCW_THREADS, cap = (size_t)ctx->sm_count * occ;
+        if (cap > ctx->partials_cap / SCW_NT) cap = ctx->partials_cap / SCW_NT;
+        return (unsigned)(want < cap ? want : cap);
+    };
+    WidePtrs P;
+    memset(&P, 0, sizeof P);
+    for (int k = 0; k < nc; k++) P.in[k] = in[k];
+    zc_round_kernel<NCMAX><<<grid_for(n / 2), SCW_THREADS, 0, s>>>(P, n / 2, 1, prog_dev, ctl, ctx->d_partials, nullptr,
+                                                                  ctl->msgs, ctl->chals, tag);
+    gl_t* bufA = (gl_t*)ctx->ws;
+    gl_t* bufB = (gl_t*)((char*)ctx->ws + zkh_align((size_t)nc * (n / 2 + 1) * 8));
+    gl_t* dst = bufA;
+    size_t cur_n = n;
+    for (uint32_t r = 1; r < logn; r++) {
+        const size_t out_n = cur_n / 2;
+        for (int k = 0; k < nc; k++) P.out[k] = dst + (size_t)k * out_n;
+        zc_round_kernel<NCMAX><<<grid_for(cur_n / 4), SCW_THREADS, 0, s>>>(
+            P, cur_n / 4, 0, prog_dev, ctl, ctx->d_partials, ctl->chals + (r - 1), ctl->msgs + (size_t)r * SCW_NT,
+            ctl->chals + r, tag);
+        for (int k = 0; k < nc; k++) P.in[k] = P.out[k];
+        dst = (dst == bufA) ? bufB : bufA;
+        cur_n = out_n;
+    }
+    scw_finals_kernel<<<1, SCW_MAXC, 0, s>>>(P, nc, ctl->chals + (logn - 1), finals_dev);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "zero-check sumcheck launch");
+}
+
 static int scw_shape(int functor, int* nc, int* nlam) {
 #define CASE(F) if (functor == F) { *nc = WFn<F>::NC; *nlam = WFn<F>::NLAM; return 1; }
     CASE(ZKH_F_HW_DP) CASE(ZKH_F_HW_DG) CASE(ZKH_F_HW_CH) CASE(ZKH_F_HW_GS) CASE(ZKH_F_HW_DS) CASE(ZKH_F_HW_DO)
@@ -177,6 +290,64 @@ extern "C" int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* cons
         ZKH_CUDA(ctx, cudaMemcpyAsync(finals, finals_dev, (size_t)nc * 8, cudaMemcpyDeviceToHost, ctx->stream));
     ZKH_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (h->err) return zkh_fail(ctx, ZKH_ERR_DEVICE, "wide sumcheck: device error flag set");
+    memcpy(msgs, h->msgs, (size_t)logn * SCW_NT * 8);
+    memcpy(chals, h->chals, (size_t)logn * 8);
+    digest_to_bytes(h->st, state);
+    return ZKH_OK;
+}
+
+// prog: [0] = number of terms, [1] = constant inside the bracket, then per term (coefficient, packed) with
+// packed = degree | idx0 << 8 | idx1 << 16 | idx2 << 24
+extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
+                                      const uint64_t* prog, int nwords, const char* tag, uint8_t state[32], uint64_t* msgs,
+                                      uint64_t* chals, uint64_t* finals) {
+    if (!ctx) return ZKH_ERR_ARG;
+    if (!cols_dev || !prog || !tag || !state || !msgs || !chals) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: null pointer");
+    if (nc < 1 || nc > 32) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: 1..32 columns");
+    if (logn < 1 || logn > 34) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: logn must be 1..34");
+    if (strlen(tag) > ZKH_TR_MAX_LABEL) return zkh_fail(ctx, ZKH_ERR_LIMIT, "zero-check: tag longer than 48 bytes");
+    if (nwords < 2 || prog[0] > ZC_MAXTERMS || (uint64_t)nwords != 2 + 2 * prog[0])
+        return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: malformed program (at most 120 terms)");
+    static ZkhZcProg hp;   // staging copy; calls on one context are serial
+    memset(&hp, 0, sizeof hp);
+    hp.nterms = (uint32_t)prog[0];
+    hp.nc = (uint32_t)nc;
+    hp.konst = prog[1];
+    if (hp.konst >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: constant not canonical");
+    for (uint32_t j = 0; j < hp.nterms; j++) {
+        const uint64_t coef = prog[2 + 2 * j], pk = prog[3 + 2 * j];
+        const uint32_t deg = pk & 0xff;
+        if (coef >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: coefficient not canonical");
+        if (deg < 1 || deg > 3 || (pk >> 32)) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: term degree must be 1..3");
+        for (uint32_t k = 0; k < deg; k++)
+            if (((pk >> (8 + 8 * k)) & 0xff) >= (uint64_t)nc) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: column index out of range");
+        hp.coef[j] = coef;
+        hp.packed[j] = (uint32_t)pk;
+    }
+    ZKH_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t n = (size_t)1 << logn;
+    const size_t szA = zkh_align((size_t)nc * (n / 2 + 1) * 8), szB = zkh_align((size_t)nc * (n / 4 + 1) * 8);
+    const size_t szF = zkh_align((size_t)nc * 8);
+    ZKH_TRY(zkh_ws_reserve(ctx, szA + szB + szF + zkh_align(sizeof(ZkhZcProg))));
+    gl_t* finals_dev = (gl_t*)((char*)ctx->ws + szA + szB);
+    ZkhZcProg* prog_dev = (ZkhZcProg*)((char*)ctx->ws + szA + szB + szF);
+    ZkhCtl* h = ctx->h_ctl;
+    digest_from_bytes(state, h->st);
+    h->counter = 0;
+    h->err = 0;
+    for (int i = 0; i < 8; i++) h->par[i] = 0;
+    ZKH_CUDA(ctx, cudaMemcpyAsync(ctx->d_ctl, h, offsetof(ZkhCtl, local), cudaMemcpyHostToDevice, ctx->stream));
+    ZKH_CUDA(ctx, cudaMemcpyAsync(prog_dev, &hp, sizeof hp, cudaMemcpyHostToDevice, ctx->stream));
+    const ZkhTag t = zkh_make_tag(tag);
+    int rc = nc <= 8 ? zc_enqueue_t<8>(ctx, cols_dev, nc, logn, prog_dev, t, finals_dev)
+           : nc <= 16 ? zc_enqueue_t<16>(ctx, cols_dev, nc, logn, prog_dev, t, finals_dev)
+                      : zc_enqueue_t<32>(ctx, cols_dev, nc, logn, prog_dev, t, finals_dev);
+    ZKH_TRY(rc);
+    ZKH_CUDA(ctx, cudaMemcpyAsync(h, ctx->d_ctl, sizeof(ZkhCtl), cudaMemcpyDeviceToHost, ctx->stream));
+    if (finals)
+        ZKH_CUDA(ctx, cudaMemcpyAsync(finals, finals_dev, (size_t)nc * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    ZKH_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (h->err) return zkh_fail(ctx, ZKH_ERR_DEVICE, "zero-check: device error flag set");
     memcpy(msgs, h->msgs, (size_t)logn * SCW_NT * 8);
     memcpy(chals, h->chals, (size_t)logn * 8);
     digest_to_bytes(h->st, state);

@@ -70,6 +70,19 @@ class Transcript:
         return int(self._L.zkh_tr_idx(self._st, mod))
 
 
+def zc_program(terms, konst=0):
+    """Pack [(coef, (idx, ...)), ...] and the constant into the word list zkh_sumcheck_zerocheck reads."""
+    words = [len(terms), int(konst) % GL_P]
+    for coef, idx in terms:
+        if not 1 <= len(idx) <= 3:
+            raise ValueError("zero-check term: one to three columns")
+        pk = len(idx)
+        for k, i in enumerate(idx):
+            pk |= int(i) << (8 + 8 * k)
+        words += [int(coef) % GL_P, pk]
+    return np.array(words, dtype=np.uint64)
+
+
 def to_device(arr, device="cuda:0"):
     """numpy uint64 array -> torch int64 CUDA tensor with the same bits."""
     import torch
@@ -480,6 +493,25 @@ class Prover:
         st = _buf32(tr.state)
         self._ck(self._L.zkh_sumcheck_wide(self._h, functor, ptrs, nc, logn, lam_a.ctypes.data, len(lam_a),
                                            tag.encode(), st, msgs.ctypes.data, chals.ctypes.data, fin.ctypes.data))
+        tr.state = bytes(st)
+        return chals, msgs, fin
+
+    def sc_prove_zc(self, tr, tag, dcols, terms, konst=0):
+        """Eq-weighted zero-check with a programmable summand (the non-zk path of p3hwl::sc5z / sc5_prove,
+        zkllm-src/p3_hawkeye.cuh:641-700, for the integer-layer gadgets): proves the sumcheck of
+            dcols[0] * (konst + sum_j coef_j * prod_k dcols[idx_jk])
+        with ``terms`` = [(coef, (idx, ...)), ...], one to three column indices per term.  Five evaluations per
+        round.  Returns (r, msgs[v, 5], finals)."""
+        nc = len(dcols)
+        logn = int(dcols[0].numel()).bit_length() - 1
+        ptrs = (C.c_uint64 * nc)(*[_ptr(t) for t in dcols])
+        prog = zc_program(terms, konst)
+        msgs = np.zeros((logn, 5), dtype=np.uint64)
+        chals = np.zeros(logn, dtype=np.uint64)
+        fin = np.zeros(nc, dtype=np.uint64)
+        st = _buf32(tr.state)
+        self._ck(self._L.zkh_sumcheck_zerocheck(self._h, ptrs, nc, logn, prog.ctypes.data, len(prog), tag.encode(), st,
+                                                msgs.ctypes.data, chals.ctypes.data, fin.ctypes.data))
         tr.state = bytes(st)
         return chals, msgs, fin
 
