@@ -432,6 +432,34 @@ bool iswg_deserialize(const uint8_t* in, size_t len, p3iswg::Proof& pf) {
     memcpy(&pf.ySIL, p, 8); memcpy(&pf.yU, p + 8, 8); memcpy(&pf.yM, p + 16, 8); memcpy(&pf.yR, p + 24, 8); p += 32;
     return tail_parse(p, end, pf.tail) && p == end;
 }
+// p3irope::Proof <-> bytes: u32 lT, ld, fb | rREM | messages (lT+ld)*40 | yQ yQx yY yR | tail
+size_t irope_serialize(const p3irope::Proof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&pf.lT, 4); app(&pf.ld, 4); app(&pf.fb, 4); app(pf.rREM.data(), 32);
+    for (auto& m : pf.m) app(&m, 40);
+    app(&pf.yQ, 8); app(&pf.yQx, 8); app(&pf.yY, 8); app(&pf.yR, 8);
+    tail_append(pf.tail, b);
+    return emit(b, out, cap);
+}
+bool irope_deserialize(const uint8_t* in, size_t len, p3irope::Proof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    if (len < 44) return false;
+    memcpy(&pf.lT, p, 4); memcpy(&pf.ld, p + 4, 4); memcpy(&pf.fb, p + 8, 4); memcpy(pf.rREM.data(), p + 12, 32); p += 44;
+    const size_t le = (size_t)pf.lT + pf.ld;
+    if (le > 40 || (size_t)(end - p) < le * 40 + 32) return false;
+    pf.m.resize(le);
+    for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
+    memcpy(&pf.yQ, p, 8); memcpy(&pf.yQx, p + 8, 8); memcpy(&pf.yY, p + 16, 8); memcpy(&pf.yR, p + 24, 8); p += 32;
+    return tail_parse(p, end, pf.tail) && p == end;
+}
+p3irope::Pub rope_pub(const int32_t* ct, const int32_t* st, uint32_t lseq, uint32_t ldh) {
+    p3irope::Pub P;
+    P.lseq = lseq; P.ldh = ldh;
+    const size_t n = ((size_t)1 << lseq) << (ldh - 1);
+    P.ct.assign(ct, ct + n); P.st.assign(st, st + n);
+    return P;
+}
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
 const p3ig::Tables& ig_tables(uint32_t d, uint32_t btop) {
     static std::map<std::pair<uint32_t, uint32_t>, p3ig::Tables> cache;
@@ -897,6 +925,17 @@ int ref_iswg_verify(uint8_t st[32], const uint8_t* rG, const uint8_t* rU, const 
     return ok ? 1 : 0;
 }
 
+int ref_irope_verify(uint8_t st[32], const int32_t* ct, const int32_t* sn, uint32_t lseq, uint32_t ldh, const uint8_t* rQ,
+                     const uint8_t* rY, uint32_t lT, uint32_t ld, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
+    p3irope::Proof pf;
+    if (!irope_deserialize(proof, len, pf)) return 0;
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3irope::verify(tr, ig_tables(64, 12), rope_pub(ct, sn, lseq, ldh), pf, hash_from(rQ), hash_from(rY), lT, ld, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+
 // ---- integer matmul gadget: the reference's host-only verifier (p3_int_gadgets.cuh:608-655) ----
 int ref_imm_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootW[32], const uint8_t rootY[32],
                    uint32_t lj, uint32_t lk, uint32_t li, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
@@ -1198,6 +1237,32 @@ size_t ref_iswg_prove(uint8_t st[32], const uint64_t* g, const uint64_t* u, cons
         cudaDeviceSynchronize();
         if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
         n = iswg_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+size_t ref_irope_prove(uint8_t st[32], const uint64_t* q, const int32_t* ct, const int32_t* sn, uint32_t lseq, uint32_t ldh,
+                       const uint8_t* rQ, const uint8_t* rY, uint32_t lT, uint32_t ld, uint32_t R, uint32_t Q, uint8_t* out,
+                       size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        const size_t N = (size_t)1 << (lT + ld);
+        std::vector<gl_t> qv(q, q + N);
+        const p3ig::Tables& T = ig_tables(64, 12);
+        p3irope::Pub P = rope_pub(ct, sn, lseq, ldh);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3irope::Wit w = p3irope::gen_witness(lT, ld, P, qv);
+        p3lu::Col cq = col_from(q, N, rQ, lT + ld), cy = col_from(w.y.data(), N, rY, lT + ld);
+        p3irope::Operands ops{&cq, &cy};
+        auto pf = p3irope::prove(tr, w, T, P, ops, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = irope_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);

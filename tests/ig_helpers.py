@@ -13,6 +13,9 @@ GL_P = 0xFFFFFFFF00000001
 class OracleGadgetEngine(OracleStandaloneLuEngine):
     """Everything the gadget host logic asks of an engine, on the CPU oracle."""
 
+    def flip_bit(self, col, b):
+        return _Arr(col.a.reshape(-1, 2, 1 << b)[:, ::-1, :].reshape(-1).copy())
+
     def sc_prove_zc(self, tr, tag, cols, terms, konst=0):
         st, m, r, fin = zc_sumcheck(self.orc, tr.state, tag, [c.a for c in cols], terms, konst)
         tr.state = st

@@ -63,3 +63,35 @@ def test_iswg(orc, ref, zk, tables, le):
     ok, st = ref_verify3(ref, "ref_iswg_verify", st0, [G[1], U[1], MO[1]], le, R, Q, pf)
     assert ok and st == tr.state
     tamper_rejected(ref, "ref_iswg_verify", st0, [G[1], U[1], MO[1]], le, R, Q, pf)
+
+
+@pytest.mark.parametrize("lseq,ldh,lnh", [(2, 2, 1), (3, 3, 1)])
+def test_irope(orc, ref, zk, tables, lseq, ldh, lnh):
+    import ctypes as C
+    R, Q = 1, 24
+    ig = zk.ig
+    eng = OracleGadgetEngine(orc)
+    g = np.random.default_rng(7 + lseq)
+    ld, lT = ldh + lnh, lseq
+    le = lT + ld
+    ct = g.integers(-(1 << 14), (1 << 14) + 1, (1 << lseq, 1 << (ldh - 1))).astype(np.int32)
+    sn = g.integers(-(1 << 14), (1 << 14) + 1, (1 << lseq, 1 << (ldh - 1))).astype(np.int32)
+    q = ig.lift(g.integers(-(1 << 17), 1 << 17, 1 << le))
+    y, rem, iR, iY, Cc, S2 = ig.irope_witness(q, ct, sn, lseq, ldh, lT, ld)
+    Qc, Y = commit(eng, arr(eng, q), R), commit(eng, arr(eng, y), R)
+    pub = (arr(eng, ig.lift(Cc)), arr(eng, ig.lift(S2)), ldh)
+    tr = zk.Transcript("irope")
+    pf = ig.irope_prove(eng, tr, tables, pub, Qc, Y, (arr(eng, rem), arr(eng, iR), arr(eng, iY)), lT, ld, R, Q)
+
+    def verify(proof):
+        s = (C.c_uint8 * 32)(*zk.Transcript("irope").state)
+        ok = ref.lib.ref_irope_verify(s, ct.ctypes.data_as(C.c_void_p), sn.ctypes.data_as(C.c_void_p), C.c_uint32(lseq),
+                                      C.c_uint32(ldh), Qc[1], Y[1], C.c_uint32(lT), C.c_uint32(ld), C.c_uint32(R), C.c_uint32(Q),
+                                      bytes(proof), C.c_size_t(len(proof)))
+        return bool(ok), bytes(s)
+    ok, st = verify(pf)
+    assert ok and st == tr.state
+    for off in (3, 50, len(pf) // 2, len(pf) - 11):
+        bad = bytearray(pf)
+        bad[off] ^= 1
+        assert not verify(bad)[0]

@@ -138,3 +138,60 @@ def iswg_prove(engine, tr, T, G, U, MO, wit, le, R, Q, ctx=None):
     ys = [claimc(engine, tr, ctx.ledger, c, r, rE) for c, r in ((sil, rS), U, MO, (rem, rR))]
     out = struct.pack("<I", le) + rS + rR + msgs + struct.pack("<QQQQ", *ys)
     return out + (_tail(engine, tr, ctx, R, Q, "isw-bo") if own else _EMPTY_TAIL)
+
+
+# ---------------------------------------------------------------------------------- RoPE (p3irope)
+def rope_pub_cols(ct, st, lseq, ldh, ld, le):
+    """p3irope::cs_at / pub_col (p3_int_gadgets.cuh:1199-1222): the public cos / signed-sin broadcasts over the
+    element domain u = j | (t << ld); ct, st: int arrays [2^lseq][2^(ldh-1)] at scale 2^14."""
+    u = np.arange(1 << le, dtype=np.int64)
+    j, t = u & ((1 << ld) - 1), u >> ld
+    s = t & ((1 << lseq) - 1)
+    jj = j & ((1 << ldh) - 1)
+    hb = (jj >> (ldh - 1)) & 1
+    ti = s * (1 << (ldh - 1)) + (jj & ((1 << (ldh - 1)) - 1))
+    ct, st = np.asarray(ct, dtype=np.int64).reshape(-1), np.asarray(st, dtype=np.int64).reshape(-1)
+    return ct[ti], np.where(hb == 1, st[ti], -st[ti])
+
+
+def irope_witness(q, ct, st, lseq, ldh, lT, ld):
+    """p3irope::gen_witness (p3_int_gadgets.cuh:1241-1267): y = round((q*C + q_rot*S2) / 2^14) with remainder;
+    returns (y, rem, idxR, idxY, C, S2) with C, S2 the public columns as signed ints."""
+    le, fb = lT + ld, ldh - 1
+    C_, S2 = rope_pub_cols(ct, st, lseq, ldh, ld, le)
+    qv = sig(q)
+    qf = qv[np.arange(1 << le) ^ (1 << fb)]
+    y64 = qv * C_ + qf * S2
+    Y = (y64 + (1 << 13)) >> 14
+    rem = (y64 + (1 << 13)) - (Y << 14)
+    if ((Y < -ABND) | (Y >= ABND)).any():
+        raise ValueError("irope: y out of range")
+    return lift(Y), rem.astype(np.uint64), (rem & 0x3FFF).astype(np.uint32), (Y + ABND).astype(np.uint32), C_, S2
+
+
+def irope_prove(engine, tr, T, pub, Qc, Y, wit, lT, ld, R, Q, ctx=None):
+    """p3irope::prove (p3_int_gadgets.cuh:1279-1322).  pub = (C, S2) engine columns of the public broadcasts and
+    ldh; Qc, Y: (column, root); wit = (rem, idxR, idxY).  Proof: u32 lT, ld, fb | rREM | messages | yQ yQx yY yR | tail."""
+    own = ctx is None
+    ctx = ctx or Ctx()
+    Ccol, Scol, ldh = pub
+    rem, idxR, idxY = wit
+    le, fb = lT + ld, ldh - 1
+    tr.absorb("irp-dims", struct.pack("<III", lT, ld, fb))
+    tr.absorb("irp-Q", Qc[1])
+    tr.absorb("irp-Y", Y[1])
+    rR = engine.commit_gpu_rootonly(rem, R)
+    tr.absorb("irp-r", rR)
+    ctx.defer([(rem, rR)], idxR, T["R14"])
+    ctx.defer([Y], idxY, T["RS20"])
+    Qx = engine.flip_bit(Qc[0], fb)
+    rE, msgs = _zerocheck(engine, tr, "irp-sc", le, [Qc[0], Qx, Y[0], rem, Ccol, Scol],
+                          [(1, (1, 5)), (1, (2, 6)), (NEG(16384), (3,)), (NEG(1), (4,))], 8192)
+    rf = list(rE)
+    rf[fb] = (1 - rf[fb]) % GL_P
+    yQ = claimc(engine, tr, ctx.ledger, Qc[0], Qc[1], rE)
+    yQx = claimc(engine, tr, ctx.ledger, Qc[0], Qc[1], rf)
+    yY = claimc(engine, tr, ctx.ledger, Y[0], Y[1], rE)
+    yR = claimc(engine, tr, ctx.ledger, rem, rR, rE)
+    out = struct.pack("<III", lT, ld, fb) + rR + msgs + struct.pack("<QQQQ", yQ, yQx, yY, yR)
+    return out + (_tail(engine, tr, ctx, R, Q, "irp-bo") if own else _EMPTY_TAIL)

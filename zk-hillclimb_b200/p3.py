@@ -314,6 +314,10 @@ class Prover:
     def upload(self, arr):
         return to_device(arr, "cuda:%d" % self.device)
 
+    def flip_bit(self, col, b):
+        """out[u] = col[u ^ (1 << b)]: the rotate-half permutation of RoPE (zkllm-src/p3_int_gadgets.cuh:1297-1298)."""
+        return col.view(-1, 2, 1 << b).flip(1).reshape(-1).contiguous()
+
     # ---- engine interface used by prove_super ----
     def lu_counts(self, idx_list, M, pad_rows):
         """Multiplicity column of a merged lookup: histogram of all members' indices plus the
