@@ -460,6 +460,44 @@ p3irope::Pub rope_pub(const int32_t* ct, const int32_t* st, uint32_t lseq, uint3
     P.ct.assign(ct, ct + n); P.st.assign(st, st + n);
     return P;
 }
+// p3irms::Proof <-> bytes: u32 lT, ld | 18 row roots | 3 element roots | yM yMX | mS (lT+ld)*40 | mB lT*40 | yB[18] |
+//   mE (lT+ld)*40 | yE[3] | yEX yEY yER yEG | tail
+size_t irms_serialize(const p3irms::Proof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&pf.lT, 4); app(&pf.ld, 4);
+    for (int c = 0; c < p3irms::NDB; c++) app(pf.rdb[c].data(), 32);
+    for (int c = 0; c < p3irms::NDE; c++) app(pf.rde[c].data(), 32);
+    app(&pf.yM, 8); app(&pf.yMX, 8);
+    for (auto& m : pf.mS) app(&m, 40);
+    for (auto& m : pf.mB) app(&m, 40);
+    app(pf.yB, 8 * p3irms::NDB);
+    for (auto& m : pf.mE) app(&m, 40);
+    app(pf.yE, 8 * p3irms::NDE);
+    app(&pf.yEX, 8); app(&pf.yEY, 8); app(&pf.yER, 8); app(&pf.yEG, 8);
+    tail_append(pf.tail, b);
+    return emit(b, out, cap);
+}
+bool irms_deserialize(const uint8_t* in, size_t len, p3irms::Proof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    if (len < 8) return false;
+    memcpy(&pf.lT, p, 4); memcpy(&pf.ld, p + 4, 4); p += 8;
+    const size_t le = (size_t)pf.lT + pf.ld;
+    if (le > 40) return false;
+    const size_t fixed = 32 * (p3irms::NDB + p3irms::NDE) + 16 + 40 * (2 * le + pf.lT) + 8 * (p3irms::NDB + p3irms::NDE) + 32;
+    if ((size_t)(end - p) < fixed) return false;
+    for (int c = 0; c < p3irms::NDB; c++) { memcpy(pf.rdb[c].data(), p, 32); p += 32; }
+    for (int c = 0; c < p3irms::NDE; c++) { memcpy(pf.rde[c].data(), p, 32); p += 32; }
+    memcpy(&pf.yM, p, 8); memcpy(&pf.yMX, p + 8, 8); p += 16;
+    pf.mS.resize(le); pf.mB.resize(pf.lT); pf.mE.resize(le);
+    for (auto& m : pf.mS) { memcpy(&m, p, 40); p += 40; }
+    for (auto& m : pf.mB) { memcpy(&m, p, 40); p += 40; }
+    memcpy(pf.yB, p, 8 * p3irms::NDB); p += 8 * p3irms::NDB;
+    for (auto& m : pf.mE) { memcpy(&m, p, 40); p += 40; }
+    memcpy(pf.yE, p, 8 * p3irms::NDE); p += 8 * p3irms::NDE;
+    memcpy(&pf.yEX, p, 8); memcpy(&pf.yEY, p + 8, 8); memcpy(&pf.yER, p + 16, 8); memcpy(&pf.yEG, p + 24, 8); p += 32;
+    return tail_parse(p, end, pf.tail) && p == end;
+}
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
 const p3ig::Tables& ig_tables(uint32_t d, uint32_t btop) {
     static std::map<std::pair<uint32_t, uint32_t>, p3ig::Tables> cache;
@@ -936,6 +974,17 @@ int ref_irope_verify(uint8_t st[32], const int32_t* ct, const int32_t* sn, uint3
     return ok ? 1 : 0;
 }
 
+int ref_irms_verify(uint8_t st[32], const uint8_t* rX, const uint8_t* rG, const uint8_t* rY, uint32_t lT, uint32_t ld, uint32_t R,
+                    uint32_t Q, const uint8_t* proof, size_t len) {
+    p3irms::Proof pf;
+    if (!irms_deserialize(proof, len, pf)) return 0;
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3irms::verify(tr, ig_tables(1u << ld, 12), pf, hash_from(rX), hash_from(rG), hash_from(rY), lT, ld, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+
 // ---- integer matmul gadget: the reference's host-only verifier (p3_int_gadgets.cuh:608-655) ----
 int ref_imm_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootW[32], const uint8_t rootY[32],
                    uint32_t lj, uint32_t lk, uint32_t li, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
@@ -1263,6 +1312,30 @@ size_t ref_irope_prove(uint8_t st[32], const uint64_t* q, const int32_t* ct, con
         cudaDeviceSynchronize();
         if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
         n = irope_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+size_t ref_irms_prove(uint8_t st[32], const uint64_t* x, const uint64_t* g, const uint8_t* rX, const uint8_t* rG, const uint8_t* rY,
+                      uint32_t lT, uint32_t ld, uint32_t R, uint32_t Q, uint8_t* out, size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        const size_t N = (size_t)1 << (lT + ld), D = (size_t)1 << ld;
+        std::vector<gl_t> xv(x, x + N), gv(g, g + D);
+        const p3ig::Tables& T = ig_tables(1u << ld, 12);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3irms::Wit w = p3irms::gen_witness(lT, ld, xv, gv, T);
+        p3lu::Col cx = col_from(x, N, rX, lT + ld), cg = col_from(g, D, rG, ld), cy = col_from(w.y.data(), N, rY, lT + ld);
+        p3irms::Operands ops{&cx, &cg, &cy};
+        auto pf = p3irms::prove(tr, w, T, ops, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = irms_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);

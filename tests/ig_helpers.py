@@ -13,6 +13,12 @@ GL_P = 0xFFFFFFFF00000001
 class OracleGadgetEngine(OracleStandaloneLuEngine):
     """Everything the gadget host logic asks of an engine, on the CPU oracle."""
 
+    def bcast_rows(self, col, ld):
+        return _Arr(np.repeat(col.a, 1 << ld))
+
+    def bcast_cols(self, col, lT):
+        return _Arr(np.tile(col.a, 1 << lT))
+
     def flip_bit(self, col, b):
         return _Arr(col.a.reshape(-1, 2, 1 << b)[:, ::-1, :].reshape(-1).copy())
 

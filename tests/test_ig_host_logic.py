@@ -95,3 +95,38 @@ def test_irope(orc, ref, zk, tables, lseq, ldh, lnh):
         bad = bytearray(pf)
         bad[off] ^= 1
         assert not verify(bad)[0]
+
+
+@pytest.mark.parametrize("lT,ld", [(2, 3), (3, 4)])
+def test_irms(orc, ref, zk, lT, ld):
+    R, Q = 1, 24
+    ig = zk.ig
+    T = ig.build_tables(zk.load_library(), 1 << ld, 12)          # ISQ depends on the row width d
+    eng = OracleGadgetEngine(orc)
+    g = np.random.default_rng(lT * 10 + ld)
+    le = lT + ld
+    x = ig.lift(g.integers(-(1 << 17), 1 << 17, 1 << le))
+    gains = ig.lift(g.integers(1 << 15, 1 << 17, 1 << ld))
+    w = ig.irms_witness(x, gains, T, lT, ld)
+    X, G, Y = commit(eng, arr(eng, x), R), commit(eng, arr(eng, gains), R), commit(eng, arr(eng, w["y"]), R)
+    wit = dict(w)
+    wit["db"] = [arr(eng, c) for c in w["db"]]
+    wit["de"] = [arr(eng, c) for c in w["de"]]
+    for k in ("idxE4", "idxM16", "idxMS", "idxISQ", "idxLR1", "idxRW", "idxW", "idxRY", "idxY"):
+        wit[k] = arr(eng, w[k])
+    wit["idxL"] = [arr(eng, i) for i in w["idxL"]]
+    tr = zk.Transcript("irms")
+    pf = ig.irms_prove(eng, tr, T, X, G, Y, wit, lT, ld, R, Q)
+    import ctypes as C
+
+    def verify(proof):
+        s = (C.c_uint8 * 32)(*zk.Transcript("irms").state)
+        ok = ref.lib.ref_irms_verify(s, X[1], G[1], Y[1], C.c_uint32(lT), C.c_uint32(ld), C.c_uint32(R), C.c_uint32(Q),
+                                     bytes(proof), C.c_size_t(len(proof)))
+        return bool(ok), bytes(s)
+    ok, st = verify(pf)
+    assert ok and st == tr.state
+    for off in (9, 8 + 32 * 21 + 3, len(pf) // 3, len(pf) - 11):
+        bad = bytearray(pf)
+        bad[off] ^= 1
+        assert not verify(bad)[0]

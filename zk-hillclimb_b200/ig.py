@@ -195,3 +195,151 @@ def irope_prove(engine, tr, T, pub, Qc, Y, wit, lT, ld, R, Q, ctx=None):
     yR = claimc(engine, tr, ctx.ledger, rem, rR, rE)
     out = struct.pack("<III", lT, ld, fb) + rR + msgs + struct.pack("<QQQQ", yQ, yQx, yY, yR)
     return out + (_tail(engine, tr, ctx, R, Q, "irp-bo") if own else _EMPTY_TAIL)
+
+
+# ---------------------------------------------------------------------------------- RMSNorm (p3irms)
+CEPS = 1 << 14
+(B_M, B_MM, B_MS, B_P4, B_P2, B_H2, B_RP, B_L40, B_L41, B_L42, B_D40, B_D41, B_D42, B_R, B_L20, B_D20, B_LR0, B_LR1) = range(18)
+NDB, NDE = 18, 3          # per-row columns; per-element witness columns W, remW, remY
+
+
+def rshu(x, sf):
+    return (x + (1 << (sf - 1))) >> sf
+
+
+def irms_witness(x, g, T, lT, ld):
+    """p3irms::gen_witness (p3_int_gadgets.cuh:823-903).  x: 2^(lT+ld) activations, g: 2^ld gains (field elements).
+    Returns dict with db (18 row columns), de (W, remW, remY), y and the lookup indices."""
+    B, d = 1 << lT, 1 << ld
+    xv = sig(x).reshape(B, d)
+    gv = sig(g)
+    M = CEPS + (xv * xv).sum(axis=1)
+    e = np.zeros(B, dtype=np.int64)
+    while True:
+        big = (M >> (2 * e)) >= (1 << 16)
+        if not big.any():
+            break
+        e += big
+    m = M >> (2 * e)
+    p4, p2 = np.int64(1) << (2 * e), np.int64(1) << e
+    h2 = np.where(e > 0, np.int64(1) << np.maximum(e - 1, 0), 0)
+    r4 = M - m * p4
+    d4 = p4 - 1 - r4
+    RP = T["ISQ"]["cols"][1][m].astype(np.int64)
+    Rr = (RP + h2) >> e
+    r2 = RP + h2 - (Rr << e)
+    d2 = p2 - 1 - r2
+    db = [None] * NDB
+    db[B_M], db[B_MM], db[B_MS] = M, m, m - (1 << 14)
+    db[B_P4], db[B_P2], db[B_H2], db[B_RP] = p4, p2, h2, RP
+    db[B_L40], db[B_L41], db[B_L42] = r4 & 0xFFFF, (r4 >> 16) & 0xFFFF, r4 >> 32
+    db[B_D40], db[B_D41], db[B_D42] = d4 & 0xFFFF, (d4 >> 16) & 0xFFFF, d4 >> 32
+    db[B_R], db[B_L20], db[B_D20] = Rr, r2, d2
+    db[B_LR0], db[B_LR1] = Rr & 0xFFFF, Rr >> 16
+    w64 = Rr[:, None] * gv[None, :]
+    Wv = rshu(w64, 16)
+    remW = (w64 + (1 << 15)) - (Wv << 16)
+    if ((Wv < -ABND) | (Wv >= ABND)).any():
+        raise ValueError("irms: W out of range")
+    y64 = Wv * xv
+    Yv = rshu(y64, 16)
+    remY = (y64 + (1 << 15)) - (Yv << 16)
+    if ((Yv < -ABND) | (Yv >= ABND)).any():
+        raise ValueError("irms: Y out of range")
+    u32 = lambda a: np.asarray(a).reshape(-1).astype(np.uint32)
+    idxL = [u32(db[c] & 0xFFFF) if c in (B_L20, B_D20) else u32(db[c]) for c in
+            (B_L40, B_L41, B_L42, B_D40, B_D41, B_D42, B_L20, B_D20, B_LR0)]
+    return {"db": [lift(c) for c in db], "de": [lift(Wv.reshape(-1)), lift(remW.reshape(-1)), lift(remY.reshape(-1))],
+            "y": lift(Yv.reshape(-1)), "idxE4": u32(e), "idxM16": u32(m), "idxMS": u32(m - (1 << 14)), "idxISQ": u32(m),
+            "idxL": idxL, "idxLR1": u32(Rr >> 16), "idxRW": u32(remW), "idxW": u32(Wv + ABND), "idxRY": u32(remY),
+            "idxY": u32(Yv + ABND)}
+
+
+def _sumcheck(engine, tr, tag, cols, terms, konst):
+    r, m, _ = engine.sc_prove_zc(tr, tag, cols, terms, konst)
+    return [int(x) for x in r], np.ascontiguousarray(m, dtype=np.uint64).tobytes()
+
+
+def irms_prove(engine, tr, T, X, G, Y, wit, lT, ld, R, Q, ctx=None):
+    """p3irms::prove (p3_int_gadgets.cuh:922-1047).  X, Y: (column, root) over 2^(lT+ld) elements, G: gains over 2^ld;
+    wit: irms_witness output with db/de as engine columns and index arrays.
+    Proof: u32 lT, ld | 18 row roots | 3 element roots | yM yMX | mS | mB yB[18] | mE yE[3] yEX yEY yER yEG | tail."""
+    own = ctx is None
+    ctx = ctx or Ctx()
+    le = lT + ld
+    tr.absorb("irm-dims", struct.pack("<II", lT, ld))
+    tr.absorb("irm-X", X[1])
+    tr.absorb("irm-G", G[1])
+    tr.absorb("irm-Y", Y[1])
+    CB, CE = [], []
+    for c in wit["db"]:
+        root = engine.commit_gpu_rootonly(c, R)
+        CB.append((c, root))
+        tr.absorb("irm-cb", root)
+    for c in wit["de"]:
+        root = engine.commit_gpu_rootonly(c, R)
+        CE.append((c, root))
+        tr.absorb("irm-ce", root)
+    ctx.defer([CB[B_P4], CB[B_P2], CB[B_H2]], wit["idxE4"], T["EXP4"])
+    ctx.defer([CB[B_MM]], wit["idxM16"], T["R16"])
+    ctx.defer([CB[B_MS]], wit["idxMS"], T["R16"])
+    ctx.defer([CB[B_MM], CB[B_RP]], wit["idxISQ"], T["ISQ"])
+    for l, c in enumerate((B_L40, B_L41, B_L42, B_D40, B_D41, B_D42, B_L20, B_D20, B_LR0)):
+        ctx.defer([CB[c]], wit["idxL"][l], T["R16"])
+    ctx.defer([CB[B_LR1]], wit["idxLR1"], T["R16"])
+    ctx.defer([CE[1]], wit["idxRW"], T["R16"])
+    ctx.defer([CE[0]], wit["idxW"], T["RS20"])
+    ctx.defer([CE[2]], wit["idxRY"], T["R16"])
+    ctx.defer([Y], wit["idxY"], T["RS20"])
+    # M row-sum binding: sum_j X^2 = M - CEPS, weighted by eq(zb, row)
+    zb = [tr.chal() for _ in range(lT)]
+    yM = claimc(engine, tr, ctx.ledger, CB[B_M][0], CB[B_M][1], zb)
+    EQb = engine.bcast_rows(engine.build_eq_gpu(np.array(zb, dtype=np.uint64)), ld)
+    rS, mS = _sumcheck(engine, tr, "irm-scS", [EQb, X[0]], [(1, (1, 1))], 0)
+    yMX = claimc(engine, tr, ctx.ledger, X[0], X[1], rS)
+    # per-row zero-check
+    zB = np.array([tr.chal() for _ in range(lT)], dtype=np.uint64)
+    lamB = tr.chal()
+    lam = [pow(lamB, j, GL_P) for j in range(6)]
+    c = lambda k: 1 + k                        # column index of row column k (column 0 is the eq weight)
+    n = lambda x: NEG(x)
+    terms = [
+        # r0 = M - (MM*P4 + r4),  r4 = L40 + 2^16 L41 + 2^32 L42
+        (lam[0], (c(B_M),)), (n(lam[0]), (c(B_MM), c(B_P4))), (n(lam[0]), (c(B_L40),)), (n(lam[0] << 16), (c(B_L41),)),
+        (n(lam[0] << 32), (c(B_L42),)),
+        # r1 = P4 - 1 - r4 - d4
+        (lam[1], (c(B_P4),)), (n(lam[1]), (c(B_L40),)), (n(lam[1] << 16), (c(B_L41),)), (n(lam[1] << 32), (c(B_L42),)),
+        (n(lam[1]), (c(B_D40),)), (n(lam[1] << 16), (c(B_D41),)), (n(lam[1] << 32), (c(B_D42),)),
+        # r2 = R*P2 + L20 - RP - H2
+        (lam[2], (c(B_R), c(B_P2))), (lam[2], (c(B_L20),)), (n(lam[2]), (c(B_RP),)), (n(lam[2]), (c(B_H2),)),
+        # r3 = P2 - 1 - L20 - D20
+        (lam[3], (c(B_P2),)), (n(lam[3]), (c(B_L20),)), (n(lam[3]), (c(B_D20),)),
+        # r4' = R - LR0 - 2^16 LR1
+        (lam[4], (c(B_R),)), (n(lam[4]), (c(B_LR0),)), (n(lam[4] << 16), (c(B_LR1),)),
+        # r5 = MS + 2^14 - MM
+        (lam[5], (c(B_MS),)), (n(lam[5]), (c(B_MM),)),
+    ]
+    konstB = (-lam[1] - lam[3] + lam[5] * 16384) % GL_P
+    EB = engine.build_eq_gpu(zB)
+    rB, mB = _sumcheck(engine, tr, "irm-scB", [EB] + [cb[0] for cb in CB], terms, konstB)
+    yB = [claimc(engine, tr, ctx.ledger, cb[0], cb[1], rB) for cb in CB]
+    # per-element zero-check: W = round(R*g / 2^16), Y = round(W*x / 2^16)
+    zE = np.array([tr.chal() for _ in range(le)], dtype=np.uint64)
+    lamE = tr.chal()
+    Rb = engine.bcast_rows(CB[B_R][0], ld)
+    Gb = engine.bcast_cols(G[0], lT)
+    # columns: 0 E, 1 X, 2 Y, 3 W, 4 RW, 5 RY, 6 Rb, 7 Gb
+    termsE = [(1, (6, 7)), (n(65536), (3,)), (n(1), (4,)),
+              (lamE, (3, 1)), (n(lamE * 65536), (2,)), (n(lamE), (5,))]
+    konstE = (32768 + lamE * 32768) % GL_P
+    rE, mE = _sumcheck(engine, tr, "irm-scE", [engine.build_eq_gpu(zE), X[0], Y[0], CE[0][0], CE[1][0], CE[2][0], Rb, Gb],
+                       termsE, konstE)
+    yEX = claimc(engine, tr, ctx.ledger, X[0], X[1], rE)
+    yEY = claimc(engine, tr, ctx.ledger, Y[0], Y[1], rE)
+    yE = [claimc(engine, tr, ctx.ledger, ce[0], ce[1], rE) for ce in CE]
+    yER = claimc(engine, tr, ctx.ledger, CB[B_R][0], CB[B_R][1], rE[ld:le])
+    yEG = claimc(engine, tr, ctx.ledger, G[0], G[1], rE[:ld])
+    out = struct.pack("<II", lT, ld) + b"".join(cb[1] for cb in CB) + b"".join(ce[1] for ce in CE)
+    out += struct.pack("<QQ", yM, yMX) + mS + mB + struct.pack("<18Q", *yB) + mE + struct.pack("<3Q", *yE)
+    out += struct.pack("<QQQQ", yEX, yEY, yER, yEG)
+    return out + (_tail(engine, tr, ctx, R, Q, "irm-bo") if own else _EMPTY_TAIL)

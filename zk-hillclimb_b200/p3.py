@@ -314,6 +314,14 @@ class Prover:
     def upload(self, arr):
         return to_device(arr, "cuda:%d" % self.device)
 
+    def bcast_rows(self, col, ld):
+        """out[e] = col[e >> ld]: a per-row value repeated along the row (p3ig::eqb_col / bc_aug)."""
+        return col.repeat_interleave(1 << ld).contiguous()
+
+    def bcast_cols(self, col, lT):
+        """out[e] = col[e mod len(col)]: a per-column value repeated over 2^lT rows."""
+        return col.repeat(1 << lT).contiguous()
+
     def flip_bit(self, col, b):
         """out[u] = col[u ^ (1 << b)]: the rotate-half permutation of RoPE (zkllm-src/p3_int_gadgets.cuh:1297-1298)."""
         return col.view(-1, 2, 1 << b).flip(1).reshape(-1).contiguous()
