@@ -498,6 +498,44 @@ bool irms_deserialize(const uint8_t* in, size_t len, p3irms::Proof& pf) {
     memcpy(&pf.yEX, p, 8); memcpy(&pf.yEY, p + 8, 8); memcpy(&pf.yER, p + 16, 8); memcpy(&pf.yEG, p + 24, 8); p += 32;
     return tail_parse(p, end, pf.tail) && p == end;
 }
+// p3ismx::Proof <-> bytes: u32 la, lseq | 7 element roots | 2 row roots | mSel le*40 | ySel | ySrow | mS le*40 | ySE |
+//   mE le*40 | yEZ | yE[7] | yEP yEMX yES | tail        (le = la + 2*lseq)
+size_t ismx_serialize(const p3ismx::Proof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&pf.la, 4); app(&pf.lseq, 4);
+    for (int c = 0; c < p3ismx::NXE; c++) app(pf.rxe[c].data(), 32);
+    for (int c = 0; c < p3ismx::NXB; c++) app(pf.rxb[c].data(), 32);
+    for (auto& m : pf.mSel) app(&m, 40);
+    app(&pf.ySel, 8); app(&pf.ySrow, 8);
+    for (auto& m : pf.mS) app(&m, 40);
+    app(&pf.ySE, 8);
+    for (auto& m : pf.mE) app(&m, 40);
+    app(&pf.yEZ, 8); app(pf.yE, 8 * p3ismx::NXE); app(&pf.yEP, 8); app(&pf.yEMX, 8); app(&pf.yES, 8);
+    tail_append(pf.tail, b);
+    return emit(b, out, cap);
+}
+bool ismx_deserialize(const uint8_t* in, size_t len, p3ismx::Proof& pf) {
+    const uint8_t* p = in; const uint8_t* end = in + len;
+    if (len < 8) return false;
+    memcpy(&pf.la, p, 4); memcpy(&pf.lseq, p + 4, 4); p += 8;
+    const size_t le = (size_t)pf.la + 2 * (size_t)pf.lseq;
+    if (le > 40) return false;
+    const size_t fixed = 32 * (p3ismx::NXE + p3ismx::NXB) + 120 * le + 8 * (3 + 1 + p3ismx::NXE + 3);
+    if ((size_t)(end - p) < fixed) return false;
+    for (int c = 0; c < p3ismx::NXE; c++) { memcpy(pf.rxe[c].data(), p, 32); p += 32; }
+    for (int c = 0; c < p3ismx::NXB; c++) { memcpy(pf.rxb[c].data(), p, 32); p += 32; }
+    pf.mSel.resize(le); pf.mS.resize(le); pf.mE.resize(le);
+    for (auto& m : pf.mSel) { memcpy(&m, p, 40); p += 40; }
+    memcpy(&pf.ySel, p, 8); memcpy(&pf.ySrow, p + 8, 8); p += 16;
+    for (auto& m : pf.mS) { memcpy(&m, p, 40); p += 40; }
+    memcpy(&pf.ySE, p, 8); p += 8;
+    for (auto& m : pf.mE) { memcpy(&m, p, 40); p += 40; }
+    memcpy(&pf.yEZ, p, 8); p += 8;
+    memcpy(pf.yE, p, 8 * p3ismx::NXE); p += 8 * p3ismx::NXE;
+    memcpy(&pf.yEP, p, 8); memcpy(&pf.yEMX, p + 8, 8); memcpy(&pf.yES, p + 16, 8); p += 24;
+    return tail_parse(p, end, pf.tail) && p == end;
+}
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
 const p3ig::Tables& ig_tables(uint32_t d, uint32_t btop) {
     static std::map<std::pair<uint32_t, uint32_t>, p3ig::Tables> cache;
@@ -985,6 +1023,17 @@ int ref_irms_verify(uint8_t st[32], const uint8_t* rX, const uint8_t* rG, const 
     return ok ? 1 : 0;
 }
 
+int ref_ismx_verify(uint8_t st[32], const uint8_t* rZ, const uint8_t* rP, uint32_t la, uint32_t lseq, uint32_t R, uint32_t Q,
+                    const uint8_t* proof, size_t len) {
+    p3ismx::Proof pf;
+    if (!ismx_deserialize(proof, len, pf)) return 0;
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3ismx::verify(tr, ig_tables(64, 12), pf, hash_from(rZ), hash_from(rP), la, lseq, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+
 // ---- integer matmul gadget: the reference's host-only verifier (p3_int_gadgets.cuh:608-655) ----
 int ref_imm_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootW[32], const uint8_t rootY[32],
                    uint32_t lj, uint32_t lk, uint32_t li, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
@@ -1336,6 +1385,31 @@ size_t ref_irms_prove(uint8_t st[32], const uint64_t* x, const uint64_t* g, cons
         cudaDeviceSynchronize();
         if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
         n = irms_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+size_t ref_ismx_prove(uint8_t st[32], const uint64_t* z, const uint8_t* rZ, const uint8_t* rP, uint32_t la, uint32_t lseq,
+                      uint32_t R, uint32_t Q, uint8_t* out, size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        const uint32_t le = la + 2 * lseq;
+        const size_t N = (size_t)1 << le;
+        std::vector<gl_t> zv(z, z + N);
+        const p3ig::Tables& T = ig_tables(64, 12);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3ismx::Wit w = p3ismx::gen_witness(la, lseq, zv, T);
+        p3lu::Col cz = col_from(z, N, rZ, le), cp = col_from(w.p.data(), N, rP, le);
+        p3ismx::Operands ops{&cz, &cp};
+        auto pf = p3ismx::prove(tr, w, T, ops, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = ismx_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);

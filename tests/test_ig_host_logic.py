@@ -130,3 +130,32 @@ def test_irms(orc, ref, zk, lT, ld):
         bad = bytearray(pf)
         bad[off] ^= 1
         assert not verify(bad)[0]
+
+
+@pytest.mark.parametrize("la,lseq", [(1, 2), (0, 3)])
+def test_ismx(orc, ref, zk, tables, la, lseq):
+    import ctypes as C
+    R, Q = 1, 24
+    ig = zk.ig
+    eng = OracleGadgetEngine(orc)
+    g = np.random.default_rng(la * 10 + lseq)
+    le = la + 2 * lseq
+    z = ig.lift(g.integers(-2000, 2000, 1 << le))
+    w = ig.ismx_witness(z, tables, la, lseq)
+    Z, P = commit(eng, arr(eng, z), R), commit(eng, arr(eng, w["p"]), R)
+    wit = {"xe": [arr(eng, c) for c in w["xe"]], "xb": [arr(eng, c) for c in w["xb"]], "idxDM": arr(eng, w["idxDM"]),
+           "idxL": [arr(eng, i) for i in w["idxL"]], "idxMX": arr(eng, w["idxMX"])}
+    tr = zk.Transcript("ismx")
+    pf = ig.ismx_prove(eng, tr, tables, Z, P, wit, la, lseq, R, Q)
+
+    def verify(proof):
+        s = (C.c_uint8 * 32)(*zk.Transcript("ismx").state)
+        ok = ref.lib.ref_ismx_verify(s, Z[1], P[1], C.c_uint32(la), C.c_uint32(lseq), C.c_uint32(R), C.c_uint32(Q), bytes(proof),
+                                     C.c_size_t(len(proof)))
+        return bool(ok), bytes(s)
+    ok, st = verify(pf)
+    assert ok and st == tr.state
+    for off in (9, 8 + 32 * 9 + 3, len(pf) // 3, len(pf) - 11):
+        bad = bytearray(pf)
+        bad[off] ^= 1
+        assert not verify(bad)[0]

@@ -343,3 +343,106 @@ def irms_prove(engine, tr, T, X, G, Y, wit, lT, ld, R, Q, ctx=None):
     out += struct.pack("<QQ", yM, yMX) + mS + mB + struct.pack("<18Q", *yB) + mE + struct.pack("<3Q", *yE)
     out += struct.pack("<QQQQ", yEX, yEY, yER, yEG)
     return out + (_tail(engine, tr, ctx, R, Q, "irm-bo") if own else _EMPTY_TAIL)
+
+
+# ---------------------------------------------------------------------------------- causal softmax (p3ismx)
+X_SEL, X_DM, X_EE, X_L0, X_L1, X_L2, X_L3 = range(7)
+NXE, NXB = 7, 2           # per-element witness columns; per-row columns MX, S
+
+
+def ismx_witness(z, T, la, lseq):
+    """p3ismx::gen_witness (p3_int_gadgets.cuh:1410-1477): causal row max, EXPT lookups, row sum S,
+    P = round(E/S * 2^16) with the bracket remainders in 16-bit limbs.  z: 2^(la+2*lseq) scores."""
+    seq, NR = 1 << lseq, 1 << (la + lseq)
+    zv = sig(z).reshape(NR, seq)
+    i = (np.arange(NR) & (seq - 1))[:, None]
+    j = np.arange(seq)[None, :]
+    causal = j <= i
+    mx = np.where(causal, zv, np.iinfo(np.int64).min).max(axis=1)
+    dm = np.where(causal, mx[:, None] - zv, 1 << 16)
+    if ((dm < 0) | (dm >= (1 << 17))).any():
+        raise ValueError("ismx: DM range")
+    E = T["EXPT"]["cols"][1][dm].astype(np.int64)
+    S = E.sum(axis=1)
+    hit = causal & (dm == 0)
+    first = hit & (np.cumsum(hit, axis=1) == 1)
+    P = ((1 << 17) * E + S[:, None]) // (2 * S[:, None])
+    r1 = (1 << 17) * E + S[:, None] - 2 * P * S[:, None]
+    r2 = 2 * S[:, None] - 1 - r1
+    flat = lambda a: np.ascontiguousarray(a).reshape(-1)
+    xe = [first.astype(np.int64), dm, E, r1 & 0xFFFF, r1 >> 16, r2 & 0xFFFF, r2 >> 16]
+    u32 = lambda a: flat(a).astype(np.uint32)
+    return {"xe": [lift(flat(c)) for c in xe], "xb": [lift(mx), lift(S)], "p": lift(flat(P)), "idxDM": u32(dm),
+            "idxL": [u32(r1 & 0xFFFF), u32(r1 >> 16), u32(r2 & 0xFFFF), u32(r2 >> 16)], "idxMX": (mx + (1 << 15)).astype(np.uint32)}
+
+
+def causal_mask(la, lseq):
+    """p3ismx::mask_col: 1 where key index j <= query index i, over u = j | (i << lseq) | (a << 2 lseq)."""
+    u = np.arange(1 << (la + 2 * lseq), dtype=np.int64)
+    seq = 1 << lseq
+    return ((u & (seq - 1)) <= ((u >> lseq) & (seq - 1))).astype(np.uint64)
+
+
+def ismx_prove(engine, tr, T, Z, P, wit, la, lseq, R, Q, ctx=None):
+    """p3ismx::prove (p3_int_gadgets.cuh:1518-1643).  Z, P: (column, root) over 2^(la + 2 lseq); wit: ismx_witness
+    output with xe/xb as engine columns and index arrays.
+    Proof: u32 la, lseq | 7 element roots | 2 row roots | mSel ySel | ySrow mS ySE | mE yEZ yE[7] yEP yEMX yES | tail."""
+    own = ctx is None
+    ctx = ctx or Ctx()
+    lr, le = la + lseq, la + 2 * lseq
+    tr.absorb("ism-dims", struct.pack("<II", la, lseq))
+    tr.absorb("ism-Z", Z[1])
+    tr.absorb("ism-P", P[1])
+    CE, CB = [], []
+    for c in wit["xe"]:
+        root = engine.commit_gpu_rootonly(c, R)
+        CE.append((c, root))
+        tr.absorb("ism-ce", root)
+    for c in wit["xb"]:
+        CB.append((c, engine.commit_gpu_rootonly(c, R)))
+    for cb in CB:
+        tr.absorb("ism-cb", cb[1])
+    ctx.defer([CE[X_DM], CE[X_EE]], wit["idxDM"], T["EXPT"])
+    for l in range(4):
+        ctx.defer([CE[X_L0 + l]], wit["idxL"][l], T["R16"])
+    ctx.defer([CB[0]], wit["idxMX"], T["RS16"])
+    # SEL row sum: sum_j SEL = 1, weighted by eq(zb, row)
+    zb = np.array([tr.chal() for _ in range(lr)], dtype=np.uint64)
+    rS, mSel = _sumcheck(engine, tr, "ism-scsel", [engine.bcast_rows(engine.build_eq_gpu(zb), lseq), CE[X_SEL][0]], [(1, (1,))], 0)
+    ySel = claimc(engine, tr, ctx.ledger, CE[X_SEL][0], CE[X_SEL][1], rS)
+    # S row sum: sum_j EE = S
+    zb = [tr.chal() for _ in range(lr)]
+    ySrow = claimc(engine, tr, ctx.ledger, CB[1][0], CB[1][1], zb)
+    rS2, mS = _sumcheck(engine, tr, "ism-scs", [engine.bcast_rows(engine.build_eq_gpu(np.array(zb, dtype=np.uint64)), lseq), CE[X_EE][0]],
+                        [(1, (1,))], 0)
+    ySE = claimc(engine, tr, ctx.ledger, CE[X_EE][0], CE[X_EE][1], rS2)
+    # per-element zero-check
+    zE = np.array([tr.chal() for _ in range(le)], dtype=np.uint64)
+    lamE = tr.chal()
+    lam = [pow(lamE, k, GL_P) for k in range(5)]
+    n = NEG
+    ce = lambda k: 2 + k
+    Zc, Pc, MXb, Sb, MK = 1, 2 + NXE, 3 + NXE, 4 + NXE, 5 + NXE
+    terms = [
+        (lam[0], (ce(X_SEL), ce(X_SEL))), (n(lam[0]), (ce(X_SEL),)),                                   # SEL^2 - SEL
+        (lam[1], (ce(X_SEL), ce(X_DM))),                                                               # SEL * DM
+        (lam[2], (ce(X_DM),)), (n(lam[2]), (MK, MXb)), (lam[2], (MK, Zc)), (lam[2] * 65536, (MK,)),    # DM - MK(MX - Z) - (1-MK) 2^16
+        (lam[3] * 131072, (ce(X_EE),)), (lam[3], (Sb,)), (n(2 * lam[3]), (Pc, Sb)), (n(lam[3]), (ce(X_L0),)),
+        (n(lam[3] * 65536), (ce(X_L1),)),                                                              # 2^17 EE + S - 2 P S - r1
+        (lam[4], (ce(X_L2),)), (lam[4] * 65536, (ce(X_L3),)), (lam[4], (ce(X_L0),)), (lam[4] * 65536, (ce(X_L1),)),
+        (n(2 * lam[4]), (Sb,)),                                                                        # r2 + r1 + 1 - 2 S
+    ]
+    konst = (-lam[2] * 65536 + lam[4]) % GL_P
+    cols = [engine.build_eq_gpu(zE), Z[0]] + [c[0] for c in CE] + [P[0], engine.bcast_rows(CB[0][0], lseq),
+                                                                   engine.bcast_rows(CB[1][0], lseq), engine.upload(causal_mask(la, lseq))]
+    rE, mE = _sumcheck(engine, tr, "ism-sce", cols, terms, konst)
+    yEZ = claimc(engine, tr, ctx.ledger, Z[0], Z[1], rE)
+    yE = [claimc(engine, tr, ctx.ledger, c[0], c[1], rE) for c in CE]
+    yEP = claimc(engine, tr, ctx.ledger, P[0], P[1], rE)
+    rb = rE[lseq:le]
+    yEMX = claimc(engine, tr, ctx.ledger, CB[0][0], CB[0][1], rb)
+    yES = claimc(engine, tr, ctx.ledger, CB[1][0], CB[1][1], rb)
+    out = struct.pack("<II", la, lseq) + b"".join(c[1] for c in CE) + b"".join(c[1] for c in CB)
+    out += mSel + struct.pack("<Q", ySel) + struct.pack("<Q", ySrow) + mS + struct.pack("<Q", ySE)
+    out += mE + struct.pack("<Q", yEZ) + struct.pack("<7Q", *yE) + struct.pack("<QQQ", yEP, yEMX, yES)
+    return out + (_tail(engine, tr, ctx, R, Q, "ism-bo") if own else _EMPTY_TAIL)
