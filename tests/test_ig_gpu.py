@@ -1,0 +1,159 @@
+"""Integer-layer gadgets on CUDA: the proof bytes of the Prover-backed run equal the oracle-backed run of the same
+host logic and the reference's own provers (witness replay on the host, commitments / lookups / openings on the
+GPU) on the same inputs."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from ig_helpers import OracleGadgetEngine, arr, commit, ref_prove2
+
+pytestmark = pytest.mark.gpu
+R, Q = 1, 24
+
+
+@pytest.fixture(scope="module")
+def tables(zk):
+    return zk.ig.build_tables(zk.load_library(), 64, 12)
+
+
+class Dev:
+    """Upload helpers for the CUDA engine mirroring ig_helpers.arr / commit."""
+
+    def __init__(self, zk, prover):
+        self.zk, self.p = zk, prover
+
+    def col(self, a):
+        import torch
+        a = np.ascontiguousarray(a)
+        if a.dtype == np.uint32:
+            return torch.from_numpy(a.view(np.int32)).cuda()
+        return self.zk.p3.to_device(a)
+
+    def commit(self, a):
+        c = self.col(a)
+        return (c, self.p.commit_gpu_rootonly(c, R))
+
+
+def both(zk, prover, orc, fn):
+    """fn(engine, col, commit) -> proof bytes on a fresh transcript; run on CUDA and on the oracle engine."""
+    d = Dev(zk, prover)
+    tr1 = zk.Transcript("ig")
+    pf1 = fn(prover, tr1, d.col, d.commit)
+    eng = OracleGadgetEngine(orc)
+    tr2 = zk.Transcript("ig")
+    pf2 = fn(eng, tr2, lambda a: arr(eng, a), lambda a: commit(eng, arr(eng, a), R))
+    assert pf1 == pf2 and tr1.state == tr2.state
+    return pf1, tr1.state
+
+
+def test_iadd(orc, ref_or_none, zk, prover, tables):
+    ig, le = zk.ig, 11
+    g = np.random.default_rng(1)
+    a, b = ig.lift(g.integers(-(1 << 18), 1 << 18, 1 << le)), ig.lift(g.integers(-(1 << 18), 1 << 18, 1 << le))
+    out, idxO = ig.iadd_witness(a, b)
+    roots = {}
+
+    def run(eng, tr, col, com):
+        A, B, O = com(a), com(b), com(out)
+        roots["r"] = [A[1], B[1], O[1]]
+        return ig.iadd_prove(eng, tr, tables, A, B, O, col(idxO), le, R, Q)
+    pf, st = both(zk, prover, orc, run)
+    if ref_or_none is not None and ref_or_none.gpu_available():
+        rpf, rst, _ = ref_prove2(ref_or_none, "ref_iadd_prove", zk.Transcript("ig").state, a, b, roots["r"], le, R, Q)
+        assert rpf == pf and rst == st
+
+
+def test_iswg(orc, ref_or_none, zk, prover, tables):
+    ig, le = zk.ig, 10
+    g = np.random.default_rng(2)
+    gv, uv = ig.lift(g.integers(-(1 << 19), 1 << 19, 1 << le)), ig.lift(g.integers(-(1 << 15), 1 << 15, 1 << le))
+    sil, rem, mo, iG, iR, iM = ig.iswg_witness(gv, uv, tables)
+    roots = {}
+
+    def run(eng, tr, col, com):
+        G, U, MO = com(gv), com(uv), com(mo)
+        roots["r"] = [G[1], U[1], MO[1]]
+        return ig.iswg_prove(eng, tr, tables, G, U, MO, (col(sil), col(rem), col(iG), col(iR), col(iM)), le, R, Q)
+    pf, st = both(zk, prover, orc, run)
+    if ref_or_none is not None and ref_or_none.gpu_available():
+        rpf, rst, _ = ref_prove2(ref_or_none, "ref_iswg_prove", zk.Transcript("ig").state, gv, uv, roots["r"], le, R, Q)
+        assert rpf == pf and rst == st
+
+
+def test_irope(orc, ref_or_none, zk, prover, tables):
+    ig = zk.ig
+    lseq, ldh, lnh = 4, 3, 1
+    ld, lT = ldh + lnh, lseq
+    le = lT + ld
+    g = np.random.default_rng(3)
+    ct = g.integers(-(1 << 14), (1 << 14) + 1, (1 << lseq, 1 << (ldh - 1))).astype(np.int32)
+    sn = g.integers(-(1 << 14), (1 << 14) + 1, (1 << lseq, 1 << (ldh - 1))).astype(np.int32)
+    q = ig.lift(g.integers(-(1 << 17), 1 << 17, 1 << le))
+    y, rem, iR, iY, Cc, S2 = ig.irope_witness(q, ct, sn, lseq, ldh, lT, ld)
+    roots = {}
+
+    def run(eng, tr, col, com):
+        Qc, Y = com(q), com(y)
+        roots["r"] = [Qc[1], Y[1]]
+        return ig.irope_prove(eng, tr, tables, (col(ig.lift(Cc)), col(ig.lift(S2)), ldh), Qc, Y, (col(rem), col(iR), col(iY)), lT, ld, R, Q)
+    pf, st = both(zk, prover, orc, run)
+    if ref_or_none is not None and ref_or_none.gpu_available():
+        s = (C.c_uint8 * 32)(*zk.Transcript("ig").state)
+        out = (C.c_uint8 * (32 << 20))()
+        f = ref_or_none.lib.ref_irope_prove
+        f.restype = C.c_size_t
+        n = f(s, q.ctypes.data_as(C.c_void_p), ct.ctypes.data_as(C.c_void_p), sn.ctypes.data_as(C.c_void_p), C.c_uint32(lseq),
+              C.c_uint32(ldh), roots["r"][0], roots["r"][1], C.c_uint32(lT), C.c_uint32(ld), C.c_uint32(R), C.c_uint32(Q), out,
+              C.c_size_t(32 << 20), None)
+        assert bytes(out)[:n] == pf and bytes(s) == st
+
+
+def test_irms(orc, ref_or_none, zk, prover):
+    ig = zk.ig
+    lT, ld = 4, 5
+    T = ig.build_tables(zk.load_library(), 1 << ld, 12)
+    g = np.random.default_rng(4)
+    x = ig.lift(g.integers(-(1 << 17), 1 << 17, 1 << (lT + ld)))
+    gains = ig.lift(g.integers(1 << 15, 1 << 17, 1 << ld))
+    w = ig.irms_witness(x, gains, T, lT, ld)
+    roots = {}
+
+    def run(eng, tr, col, com):
+        X, G, Y = com(x), com(gains), com(w["y"])
+        roots["r"] = [X[1], G[1], Y[1]]
+        wit = {k: (col(v) if isinstance(v, np.ndarray) else [col(c) for c in v]) for k, v in w.items()}
+        return ig.irms_prove(eng, tr, T, X, G, Y, wit, lT, ld, R, Q)
+    pf, st = both(zk, prover, orc, run)
+    if ref_or_none is not None and ref_or_none.gpu_available():
+        s = (C.c_uint8 * 32)(*zk.Transcript("ig").state)
+        out = (C.c_uint8 * (32 << 20))()
+        f = ref_or_none.lib.ref_irms_prove
+        f.restype = C.c_size_t
+        n = f(s, x.ctypes.data_as(C.c_void_p), gains.ctypes.data_as(C.c_void_p), roots["r"][0], roots["r"][1], roots["r"][2],
+              C.c_uint32(lT), C.c_uint32(ld), C.c_uint32(R), C.c_uint32(Q), out, C.c_size_t(32 << 20), None)
+        assert bytes(out)[:n] == pf and bytes(s) == st
+
+
+def test_ismx(orc, ref_or_none, zk, prover, tables):
+    ig = zk.ig
+    la, lseq = 1, 4
+    g = np.random.default_rng(5)
+    z = ig.lift(g.integers(-3000, 3000, 1 << (la + 2 * lseq)))
+    w = ig.ismx_witness(z, tables, la, lseq)
+    roots = {}
+
+    def run(eng, tr, col, com):
+        Z, P = com(z), com(w["p"])
+        roots["r"] = [Z[1], P[1]]
+        wit = {k: (col(v) if isinstance(v, np.ndarray) else [col(c) for c in v]) for k, v in w.items() if k != "p"}
+        return ig.ismx_prove(eng, tr, tables, Z, P, wit, la, lseq, R, Q)
+    pf, st = both(zk, prover, orc, run)
+    if ref_or_none is not None and ref_or_none.gpu_available():
+        s = (C.c_uint8 * 32)(*zk.Transcript("ig").state)
+        out = (C.c_uint8 * (32 << 20))()
+        f = ref_or_none.lib.ref_ismx_prove
+        f.restype = C.c_size_t
+        n = f(s, z.ctypes.data_as(C.c_void_p), roots["r"][0], roots["r"][1], C.c_uint32(la), C.c_uint32(lseq), C.c_uint32(R),
+              C.c_uint32(Q), out, C.c_size_t(32 << 20), None)
+        assert bytes(out)[:n] == pf and bytes(s) == st

@@ -831,7 +831,15 @@ def make_table(cols):
     h = hashlib.sha256(np.uint64(len(cols)).tobytes() + np.uint64(len(cols[0])).tobytes())
     for c in cols:
         h.update(c.tobytes())
-    return {"cols": cols, "id": h.digest(), "dev": None}
+    return {"cols": cols, "id": h.digest(), "dev": {}}
+
+
+def table_columns(engine, tab):
+    """The table's columns as buffers of ``engine`` (uploaded once per engine and cached in the table object)."""
+    key = id(engine)
+    if key not in tab["dev"]:
+        tab["dev"][key] = [engine.upload(c) for c in tab["cols"]]
+    return tab["dev"][key]
 
 
 def range_table(b, off):
@@ -870,10 +878,8 @@ def lu_flush(engine, tr, luq, ledger, R, strict=True):
     out = []
     for tid, subs in supers:
         tab = luq[subs[0][1][0]]["tab"]
-        if tab["dev"] is None:
-            tab["dev"] = [engine.upload(c) for c in tab["cols"]]
         sg = [(n, [([w[0] for w in luq[j]["W"]], [w[1] for w in luq[j]["W"]], luq[j]["idx"]) for j in mem]) for n, mem in subs]
-        pf, claims, _cnt = prove_super(engine, tr, tab["dev"], tid, sg, R, strict)
+        pf, claims, _cnt = prove_super(engine, tr, table_columns(engine, tab), tid, sg, R, strict)
         for col, root, pt, y in claims:
             ledger.add(col, root, pt, y)
         out.append(pf)
@@ -947,8 +953,7 @@ def lu_prove(engine, tr, W, idx, tab, R, Q, label, strict=True):
         raise ValueError("p3lu: pow2")
     if len(tab["cols"]) != c:
         raise ValueError("p3lu: col count")
-    if tab["dev"] is None:
-        tab["dev"] = [engine.upload(t) for t in tab["cols"]]
+    tcols = table_columns(engine, tab)
     tr.absorb("lu-tab", tab["id"])
     for col, root in W:
         if root is not None:
@@ -960,7 +965,7 @@ def lu_prove(engine, tr, W, idx, tab, R, Q, label, strict=True):
     tr.absorb("lu-cnt", root_cnt)
     gamma, beta = tr.chal(), tr.chal()
     A = engine.combine([w[0] for w in W], gamma)
-    Tc = engine.combine(tab["dev"], gamma)
+    Tc = engine.combine(tcols, gamma)
     hA = engine.inv_all_add(A, beta)
     hT = engine.mul(cnt, engine.inv_all_add(Tc, beta))
     SA, ST = col_sum(engine, hA), col_sum(engine, hT)
