@@ -23,6 +23,7 @@
 #include "p3_logup.cuh"
 #include "p3_hawkeye.cuh"
 #include "p3_int_gadgets.cuh"
+#include "p3_int_layer.cuh"
 
 namespace {
 fs::Transcript tr_from(const uint8_t st[32]) {
@@ -536,6 +537,134 @@ bool ismx_deserialize(const uint8_t* in, size_t len, p3ismx::Proof& pf) {
     memcpy(&pf.yEP, p, 8); memcpy(&pf.yEMX, p + 8, 8); memcpy(&pf.yES, p + 16, 8); p += 24;
     return tail_parse(p, end, pf.tail) && p == end;
 }
+size_t irs_serialize(const p3irs::Proof& pf, uint8_t* out, size_t cap);
+bool irs_deserialize(const uint8_t* in, size_t len, p3irs::Proof& pf);
+// p3itf::TfProof <-> bytes: 6 x u32 dims | length-prefixed sub-proofs in proving order (rms1, mm Q K V, rsq rsk rsv,
+// rpq rpk, mmqk[A], rsz, smx, mmpv[A], rsat, mm O, rso, add1, rms2, mm G U, rsg rsu, swg, mm D, rsd, add2) | 28 roots |
+// u32 groups (len, GroupProof)* | ioin ioout | u32 batches (len, BatchProof)*
+struct SubIO {
+    std::vector<uint8_t>* b = nullptr;          // writing
+    const uint8_t* p = nullptr; const uint8_t* end = nullptr; bool ok = true;   // reading
+    std::vector<uint8_t> tmp = std::vector<uint8_t>((size_t)64 << 20);
+    template <typename PF, typename SER> void put(const PF& pf, SER ser) {
+        uint32_t n = (uint32_t)ser(pf, tmp.data(), tmp.size());
+        const uint8_t* q = (const uint8_t*)&n;
+        b->insert(b->end(), q, q + 4);
+        b->insert(b->end(), tmp.data(), tmp.data() + n);
+    }
+    template <typename PF, typename DES> void get(PF& pf, DES des) {
+        if (!ok || (size_t)(end - p) < 4) { ok = false; return; }
+        uint32_t n; memcpy(&n, p, 4); p += 4;
+        if ((size_t)(end - p) < n || !des(p, n, pf)) { ok = false; return; }
+        p += n;
+    }
+};
+template <typename IO, typename PFT>
+void itf_walk(IO& io, PFT& pf, bool writing) {
+    using namespace p3itf;
+    auto RMS = [&](auto& x) { if (writing) io.put(x, irms_serialize); else io.get(const_cast<p3irms::Proof&>(x), irms_deserialize); };
+    auto MM = [&](auto& x) { if (writing) io.put(x, imm_serialize); else io.get(const_cast<p3imm::Proof&>(x), imm_deserialize); };
+    auto RS = [&](auto& x) { if (writing) io.put(x, irs_serialize); else io.get(const_cast<p3irs::Proof&>(x), irs_deserialize); };
+    auto RP = [&](auto& x) { if (writing) io.put(x, irope_serialize); else io.get(const_cast<p3irope::Proof&>(x), irope_deserialize); };
+    auto SMX = [&](auto& x) { if (writing) io.put(x, ismx_serialize); else io.get(const_cast<p3ismx::Proof&>(x), ismx_deserialize); };
+    auto SWG = [&](auto& x) { if (writing) io.put(x, iswg_serialize); else io.get(const_cast<p3iswg::Proof&>(x), iswg_deserialize); };
+    auto ADD = [&](auto& x) { if (writing) io.put(x, iadd_serialize); else io.get(const_cast<p3iadd::Proof&>(x), iadd_deserialize); };
+    const uint32_t A = pf.batch * pf.nh;
+    auto& P = const_cast<TfProof&>(pf);
+    if (!writing) { P.mmqk.resize(A); P.mmpv.resize(A); }
+    RMS(pf.rms1);
+    MM(pf.mm[W_Q]); MM(pf.mm[W_K]); MM(pf.mm[W_V]);
+    RS(pf.rsq); RS(pf.rsk); RS(pf.rsv);
+    RP(pf.rpq); RP(pf.rpk);
+    for (uint32_t a = 0; a < A; a++) MM(pf.mmqk[a]);
+    RS(pf.rsz);
+    SMX(pf.smx);
+    for (uint32_t a = 0; a < A; a++) MM(pf.mmpv[a]);
+    RS(pf.rsat);
+    MM(pf.mm[W_O]);
+    RS(pf.rso);
+    ADD(pf.add1);
+    RMS(pf.rms2);
+    MM(pf.mm[W_G]); MM(pf.mm[W_U]);
+    RS(pf.rsg); RS(pf.rsu);
+    SWG(pf.swg);
+    MM(pf.mm[W_D]);
+    RS(pf.rsd);
+    ADD(pf.add2);
+}
+std::vector<p3fri::Hash*> itf_roots(p3itf::TfProof& pf) {
+    std::vector<p3fri::Hash*> r = {&pf.rX0, &pf.rH1};
+    for (int i = 0; i < p3itf::NW; i++) r.push_back(&pf.rACC[i]);
+    for (auto* h : {&pf.rYQ, &pf.rYK, &pf.rYV, &pf.rRQ, &pf.rRK, &pf.rSC, &pf.rZ, &pf.rP, &pf.rPVA, &pf.rAT, &pf.rYO, &pf.rRES1,
+                    &pf.rH2, &pf.rGG, &pf.rUU, &pf.rMO, &pf.rYD, &pf.rOUT}) r.push_back(h);
+    return r;
+}
+size_t itf_serialize(const p3itf::TfProof& pf, uint8_t* out, size_t cap) {
+    std::vector<uint8_t> b;
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    uint32_t hdr[6] = {pf.seq, pf.d, pf.nh, pf.dh, pf.dff, pf.batch};
+    app(hdr, 24);
+    SubIO io; io.b = &b;
+    itf_walk(io, pf, true);
+    for (auto* h : itf_roots(const_cast<p3itf::TfProof&>(pf))) app(h->data(), 32);
+    p3ig::Tail t; t.lug = pf.lug;
+    uint32_t ng = (uint32_t)pf.lug.size();
+    app(&ng, 4);
+    for (auto& g : pf.lug) { uint32_t n = (uint32_t)lu_serialize(g, io.tmp.data(), io.tmp.size()); app(&n, 4); app(io.tmp.data(), n); }
+    app(&pf.ioin, 8); app(&pf.ioout, 8);
+    uint32_t nb = (uint32_t)pf.batches.size();
+    app(&nb, 4);
+    for (auto& bp : pf.batches) { uint32_t n = (uint32_t)bo_serialize(bp, io.tmp.data(), io.tmp.size()); app(&n, 4); app(io.tmp.data(), n); }
+    return emit(b, out, cap);
+}
+bool itf_deserialize(const uint8_t* in, size_t len, p3itf::TfProof& pf) {
+    if (len < 24) return false;
+    uint32_t hdr[6]; memcpy(hdr, in, 24);
+    pf.seq = hdr[0]; pf.d = hdr[1]; pf.nh = hdr[2]; pf.dh = hdr[3]; pf.dff = hdr[4]; pf.batch = hdr[5];
+    if (pf.nh == 0 || pf.batch == 0 || (uint64_t)pf.nh * pf.batch > 4096) return false;
+    SubIO io; io.p = in + 24; io.end = in + len;
+    itf_walk(io, pf, false);
+    if (!io.ok) return false;
+    const uint8_t* p = io.p; const uint8_t* end = io.end;
+    auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
+    for (auto* h : itf_roots(pf)) { if (!need(32)) return false; memcpy(h->data(), p, 32); p += 32; }
+    uint32_t ng;
+    if (!need(4)) return false;
+    memcpy(&ng, p, 4); p += 4;
+    if (ng > 64) return false;
+    pf.lug.resize(ng);
+    for (auto& g : pf.lug) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (!need(n) || !lu_deserialize(p, n, g)) return false;
+        p += n;
+    }
+    if (!need(20)) return false;
+    memcpy(&pf.ioin, p, 8); memcpy(&pf.ioout, p + 8, 8); p += 16;
+    uint32_t nb; memcpy(&nb, p, 4); p += 4;
+    if (nb > 64) return false;
+    pf.batches.resize(nb);
+    for (auto& bp : pf.batches) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (!need(n) || !bo_deserialize(p, n, bp)) return false;
+        p += n;
+    }
+    return p == end;
+}
+p3itf::Weights itf_weights(const p3itf::Config& cfg, const uint64_t* const* w7, const uint64_t* g1, const uint64_t* g2,
+                           const int32_t* ct, const int32_t* sn) {
+    p3itf::Weights W; W.cfg = cfg;
+    for (int i = 0; i < p3itf::NW; i++) {
+        uint32_t K, N; p3itf::wshape(cfg, i, K, N);
+        W.w[i].assign(w7[i], w7[i] + (size_t)K * N);
+    }
+    W.g1.assign(g1, g1 + cfg.d); W.g2.assign(g2, g2 + cfg.d);
+    W.rp = rope_pub(ct, sn, cfg.lseq(), cfg.ldh());
+    return W;
+}
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
 const p3ig::Tables& ig_tables(uint32_t d, uint32_t btop) {
     static std::map<std::pair<uint32_t, uint32_t>, p3ig::Tables> cache;
@@ -1034,6 +1163,29 @@ int ref_ismx_verify(uint8_t st[32], const uint8_t* rZ, const uint8_t* rP, uint32
     return ok ? 1 : 0;
 }
 
+// ---- decoder layer: the reference's host-only verifier (p3_int_layer.cuh:584-737) ----
+// wroots: the 7 weight roots then g1, g2 (9 x 32 bytes); x0 / outp: the public input and output grids
+int ref_itf_verify(uint8_t st[32], const uint32_t dims[6], const uint64_t* x0, const uint8_t* rX0, const uint8_t* wroots,
+                   const int32_t* ct, const int32_t* sn, const uint64_t* outp, uint32_t R, uint32_t Q, const uint8_t* proof,
+                   size_t len) {
+    p3itf::TfProof pf;
+    if (!itf_deserialize(proof, len, pf)) return 0;
+    p3itf::Config cfg;
+    cfg.seq = dims[0]; cfg.d = dims[1]; cfg.nh = dims[2]; cfg.dh = dims[3]; cfg.dff = dims[4]; cfg.batch = dims[5];
+    if (!cfg.pow2()) return 0;
+    const size_t Ne = (size_t)cfg.T() * cfg.d;
+    std::vector<gl_t> x0v(x0, x0 + Ne), outv(outp, outp + Ne);
+    p3itf::WeightRoots wr;
+    for (int i = 0; i < p3itf::NW; i++) wr.Wc[i] = hash_from(wroots + 32 * i);
+    wr.G1 = hash_from(wroots + 32 * 7); wr.G2 = hash_from(wroots + 32 * 8);
+    fs::Transcript tr = tr_from(st);
+    const char* why = nullptr;
+    bool ok = p3itf::verify(tr, pf, ig_tables(cfg.d, cfg.btop()), cfg, x0v, hash_from(rX0), wr,
+                            rope_pub(ct, sn, cfg.lseq(), cfg.ldh()), outv, Q, R, &why);
+    memcpy(st, tr.state, 32);
+    return ok ? 1 : 0;
+}
+
 // ---- integer matmul gadget: the reference's host-only verifier (p3_int_gadgets.cuh:608-655) ----
 int ref_imm_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootW[32], const uint8_t rootY[32],
                    uint32_t lj, uint32_t lk, uint32_t li, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
@@ -1410,6 +1562,40 @@ size_t ref_ismx_prove(uint8_t st[32], const uint64_t* z, const uint8_t* rZ, cons
         cudaDeviceSynchronize();
         if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
         n = ismx_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+// p3itf: build_witness (host) + commit_all + prove (GPU) of one decoder layer; ms_out[0] witness, [1] commit, [2] prove
+size_t ref_itf_prove(uint8_t st[32], const uint32_t dims[6], const uint64_t* x0, const uint64_t* const* w7, const uint64_t* g1,
+                     const uint64_t* g2, const int32_t* ct, const int32_t* sn, uint32_t R, uint32_t Q, uint8_t* out, size_t cap,
+                     uint64_t* out_grid, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    p3bf::p3_enable_mempool();
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        p3itf::Config cfg;
+        cfg.seq = dims[0]; cfg.d = dims[1]; cfg.nh = dims[2]; cfg.dh = dims[3]; cfg.dff = dims[4]; cfg.batch = dims[5];
+        const size_t Ne = (size_t)cfg.T() * cfg.d;
+        p3itf::Weights W = itf_weights(cfg, w7, g1, g2, ct, sn);
+        const p3ig::Tables& T = ig_tables(cfg.d, cfg.btop());
+        std::vector<gl_t> x0v(x0, x0 + Ne);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3itf::TfWit w = p3itf::build_witness(cfg, x0v, W, T);
+        double t1 = p3bf::bf_now_ms();
+        p3itf::TfOps o = p3itf::commit_all(w, W, R);
+        cudaDeviceSynchronize();
+        double t2 = p3bf::bf_now_ms();
+        auto pf = p3itf::prove(tr, w, o, W, T, R, Q);
+        cudaDeviceSynchronize();
+        double t3 = p3bf::bf_now_ms();
+        if (ms_out) { ms_out[0] = t1 - t0; ms_out[1] = t2 - t1; ms_out[2] = t3 - t2; }
+        if (out_grid) memcpy(out_grid, w.out.data(), Ne * 8);
+        n = itf_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);

@@ -19,6 +19,9 @@ class OracleGadgetEngine(OracleStandaloneLuEngine):
     def bcast_cols(self, col, lT):
         return _Arr(np.tile(col.a, 1 << lT))
 
+    def gather(self, col, idx):
+        return _Arr(col.a[np.asarray(idx, dtype=np.int64)])
+
     def flip_bit(self, col, b):
         return _Arr(col.a.reshape(-1, 2, 1 << b)[:, ::-1, :].reshape(-1).copy())
 
@@ -66,3 +69,53 @@ def ref_prove2(ref, name, st, a, b, roots, le, R, Q):
     n = f(s, a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), roots[0], roots[1], roots[2], C.c_uint32(le),
           C.c_uint32(R), C.c_uint32(Q), out, C.c_size_t(cap), C.byref(ms))
     return bytes(out)[:n], bytes(s), ms.value
+
+
+def layer_inputs(ig, c, seed, wscale=0.9):
+    """Random in-range layer inputs in the style of zkllm-src/p3_int_layer_bench.cu:49-72 (numpy generator)."""
+    g = np.random.default_rng(seed)
+    wb = max(2, int(round(65536.0 * wscale / np.sqrt(c.d))))
+    wbd = max(2, int(round(65536.0 * wscale / np.sqrt(c.dff))))
+    Wt = {"w": []}
+    for i in range(7):
+        K, N = c.wshape(i)
+        b = wbd if i == ig.W_D else wb
+        Wt["w"].append(ig.lift(g.integers(-(b - 1), b, K * N)))
+    Wt["g1"] = ig.lift(49152 + g.integers(-16383, 16384, c.d))
+    Wt["g2"] = ig.lift(49152 + g.integers(-16383, 16384, c.d))
+    dh2 = c.dh // 2
+    s = np.arange(c.seq)[:, None]
+    j = np.arange(dh2)[None, :]
+    ang = s * np.power(10000.0, -2.0 * j / c.dh)
+    Wt["ct"] = np.rint(np.cos(ang) * 16384.0).astype(np.int32)
+    Wt["st"] = np.rint(np.sin(ang) * 16384.0).astype(np.int32)
+    x0 = ig.lift(g.integers(-(1 << 16) + 1, 1 << 16, c.seq * c.batch * c.d))
+    return x0, Wt
+
+
+def ref_itf_verify(ref, st, c, x0, rX0, wroots, Wt, out, R, Q, proof):
+    s = (C.c_uint8 * 32)(*st)
+    dims = (C.c_uint32 * 6)(c.seq, c.d, c.nh, c.dh, c.dff, c.batch)
+    vp = lambda a: np.ascontiguousarray(a).ctypes.data_as(C.c_void_p)
+    x0c, outc, ct, sn = (np.ascontiguousarray(a) for a in (x0, out, Wt["ct"], Wt["st"]))
+    ok = ref.lib.ref_itf_verify(s, dims, vp(x0c), rX0, b"".join(wroots), vp(ct), vp(sn), vp(outc), C.c_uint32(R), C.c_uint32(Q),
+                                bytes(proof), C.c_size_t(len(proof)))
+    return bool(ok), bytes(s)
+
+
+def ref_itf_prove(ref, st, c, x0, Wt, R, Q):
+    s = (C.c_uint8 * 32)(*st)
+    dims = (C.c_uint32 * 6)(c.seq, c.d, c.nh, c.dh, c.dff, c.batch)
+    u64p = C.POINTER(C.c_uint64)
+    ws = [np.ascontiguousarray(w, dtype=np.uint64) for w in Wt["w"]]
+    wp = (u64p * 7)(*[w.ctypes.data_as(u64p) for w in ws])
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)
+    x0c, g1, g2, ct, sn = (np.ascontiguousarray(a) for a in (x0, Wt["g1"], Wt["g2"], Wt["ct"], Wt["st"]))
+    cap = 256 << 20
+    out = (C.c_uint8 * cap)()
+    grid = np.zeros(len(x0c), dtype=np.uint64)
+    ms = (C.c_double * 3)()
+    f = ref.lib.ref_itf_prove
+    f.restype = C.c_size_t
+    n = f(s, dims, vp(x0c), wp, vp(g1), vp(g2), vp(ct), vp(sn), C.c_uint32(R), C.c_uint32(Q), out, C.c_size_t(cap), vp(grid), ms)
+    return bytes(out[:n]), bytes(s), grid, list(ms)

@@ -1,0 +1,35 @@
+"""One decoder layer (p3itf::prove, non-zk) through the host logic in zk_hillclimb_b200.ig on CPU: witness chain,
+commitments, 26 + 2A sub-proofs, merged lookups, public I/O bindings and batched openings; the proof must be
+accepted by the reference's own host-only layer verifier on the same transcript."""
+import numpy as np
+import pytest
+
+from ig_helpers import OracleGadgetEngine, arr, layer_inputs, ref_itf_verify
+
+
+@pytest.mark.parametrize("dims", [(4, 8, 2, 4, 16, 1), (4, 8, 2, 4, 8, 2)])
+def test_layer_accepted_by_reference_verifier(orc, ref, zk, dims):
+    R, Q = 1, 24
+    ig = zk.ig
+    c = ig.Config(*dims)
+    T = ig.build_tables(zk.load_library(), c.d, c.btop)
+    x0, Wt = layer_inputs(ig, c, 11)
+    w = ig.itf_build_witness(c, x0, Wt, T)
+    eng = OracleGadgetEngine(orc)
+    col = lambda a: arr(eng, a)
+    o = ig.itf_commit_all(eng, w, Wt, R, col)
+    tr = zk.Transcript("itf-layer")
+    pf = ig.itf_prove(eng, tr, c, w, o, Wt, T, R, Q, col)
+    wroots = [x[1] for x in o["w"]] + [o["g1"][1], o["g2"][1]]
+    st0 = zk.Transcript("itf-layer").state
+    ok, st = ref_itf_verify(ref, st0, c, x0, o["x0"][1], wroots, Wt, w["out"], R, Q, pf)
+    assert ok and st == tr.state
+    # a wrong public output, a wrong weight root and a flipped proof byte are rejected
+    bad_out = w["out"].copy()
+    bad_out[3] = (int(bad_out[3]) + 1) % 0xFFFFFFFF00000001
+    assert not ref_itf_verify(ref, st0, c, x0, o["x0"][1], wroots, Wt, bad_out, R, Q, pf)[0]
+    assert not ref_itf_verify(ref, st0, c, x0, o["x0"][1], wroots[1:] + wroots[:1], Wt, w["out"], R, Q, pf)[0]
+    for off in (30, len(pf) // 2, len(pf) - 9):
+        bad = bytearray(pf)
+        bad[off] ^= 1
+        assert not ref_itf_verify(ref, st0, c, x0, o["x0"][1], wroots, Wt, w["out"], R, Q, bytes(bad))[0]

@@ -446,3 +446,236 @@ def ismx_prove(engine, tr, T, Z, P, wit, la, lseq, R, Q, ctx=None):
     out += mSel + struct.pack("<Q", ySel) + struct.pack("<Q", ySrow) + mS + struct.pack("<Q", ySE)
     out += mE + struct.pack("<Q", yEZ) + struct.pack("<7Q", *yE) + struct.pack("<QQQ", yEP, yEMX, yES)
     return out + (_tail(engine, tr, ctx, R, Q, "ism-bo") if own else _EMPTY_TAIL)
+
+
+# ---------------------------------------------------------------------------------- decoder layer (p3itf)
+from .p3 import S_A, S_C, S_I, S_J, imm_prove, irs_prove  # noqa: E402
+
+W_Q, W_K, W_V, W_O, W_G, W_U, W_D = range(7)
+
+
+class Config:
+    """p3itf::Config (zkllm-src/p3_int_layer.cuh:41-62): all dimensions powers of two, nh*dh == d."""
+
+    def __init__(self, seq, d, nh, dh, dff, batch=1):
+        self.seq, self.d, self.nh, self.dh, self.dff, self.batch = seq, d, nh, dh, dff, batch
+        lg = lambda x: int(x).bit_length() - 1
+        self.lseq, self.ld, self.lnh, self.ldh, self.ldff, self.lbb = lg(seq), lg(d), lg(nh), lg(dh), lg(dff), lg(batch)
+        if any((1 << l) != v for l, v in ((self.lseq, seq), (self.ld, d), (self.lnh, nh), (self.ldh, dh), (self.ldff, dff),
+                                          (self.lbb, batch))) or nh * dh != d:
+            raise ValueError("itf: config must be pow2 with nh*dh == d")
+        self.lT, self.la = self.lseq + self.lbb, self.lnh + self.lbb
+        self.A = batch * nh
+        self.tsh = (self.ldh + 1) // 2              # power-of-two softmax temperature
+        self.sfz = 24 + self.tsh                    # scores rescale shift
+        self.btop = self.sfz - 16                   # width of the top-limb table
+
+    def wshape(self, i):
+        return (self.dff if i == W_D else self.d), (self.dff if i in (W_G, W_U) else self.d)
+
+
+def _consts(bits, val):
+    return [(S_C, (val >> t) & 1) for t in range(bits)]
+
+
+def views_qk(c, h, b):
+    """xview_qk / wview_qk / yview_qk (p3_int_layer.cuh:96-122): scores of head h, batch b, Y = RQ_h . RK_h^T."""
+    a = b * c.nh + h
+    xv = [(S_J, t) for t in range(c.ldh)] + _consts(c.lnh, h) + [(S_A, t) for t in range(c.lseq)] + _consts(c.lbb, b)
+    yv = [(S_A, t) for t in range(c.lseq)] + [(S_I, t) for t in range(c.lseq)] + _consts(c.la, a)
+    return xv, list(xv), yv
+
+
+def views_pv(c, h, b):
+    """xview_pv / wview_pv / yview_pv (p3_int_layer.cuh:124-148): attention output of head h, batch b."""
+    a = b * c.nh + h
+    xv = [(S_J, t) for t in range(c.lseq)] + [(S_A, t) for t in range(c.lseq)] + _consts(c.la, a)
+    wv = [(S_A, t) for t in range(c.ldh)] + _consts(c.lnh, h) + [(S_J, t) for t in range(c.lseq)] + _consts(c.lbb, b)
+    yv = [(S_A, t) for t in range(c.ldh)] + _consts(c.lnh, h) + [(S_I, t) for t in range(c.lseq)] + _consts(c.lbb, b)
+    return xv, wv, yv
+
+
+def _view_idx(view, n_first, n_second, first, second):
+    """Element indices of a Y-style or operand-style view for all (second, first) index pairs."""
+    f = np.arange(1 << n_first, dtype=np.int64)[None, :]
+    s = np.arange(1 << n_second, dtype=np.int64)[:, None]
+    idx = np.zeros((1 << n_second, 1 << n_first), dtype=np.int64)
+    for t, (src, bit) in enumerate(view):
+        b = ((f >> bit) & 1) if src == first else ((s >> bit) & 1) if src == second else (bit if src == S_C else 0)
+        idx |= b << t
+    return idx
+
+
+def rs20_idx(v):
+    s = sig(v)
+    if ((s < -ABND) | (s >= ABND)).any():
+        raise ValueError("itf: value out of RS20")
+    return (s + ABND).astype(np.uint32)
+
+
+def irs_witness_host(acc, sf, rng):
+    """p3irs::gen_witness in numpy (the layer's witness chain runs on the host): returns (y, limbs, limb indices, y indices)."""
+    a = sig(acc)
+    H = 1 << (sf - 1)
+    y = (a + H) >> sf
+    rem = (a + H) - (y << sf)
+    win = (1 << 19) if rng == 1 else (1 << 15)
+    if rng and ((y < -win) | (y >= win)).any():
+        raise ValueError("irs: y out of range (data too large)")
+    L = [(rem & 0xFFFF).astype(np.uint64)] + ([(rem >> 16).astype(np.uint64)] if sf > 16 else [])
+    return lift(y), L, [l.astype(np.uint32) for l in L], ((y + win).astype(np.uint32) if rng else None)
+
+
+def itf_build_witness(c, x0, Wt, T):
+    """p3itf::build_witness (p3_int_layer.cuh:182-318): the layer computed by the gadget replays themselves.
+    Wt = {"w": [7 weight grids K x N row-major], "g1", "g2", "ct", "st"} as field elements / int tables."""
+    ld, lT, ldff, lseq, ldh, la = c.ld, c.lT, c.ldff, c.lseq, c.ldh, c.la
+    le, lef, lez = ld + lT, ldff + lT, la + 2 * lseq
+    w = {"x0": x0, "idxW": [rs20_idx(x) for x in Wt["w"]], "idxG1": rs20_idx(Wt["g1"]), "idxG2": rs20_idx(Wt["g2"]),
+         "idxX0": rs20_idx(x0)}
+    mat = lambda X, Wm, K, N: lift((sig(X).reshape(-1, K) @ sig(Wm).reshape(K, N)).reshape(-1))      # Y[k | i << lk]
+    w["rms1"] = irms_witness(x0, Wt["g1"], T, lT, ld)
+    w["h1"] = w["rms1"]["y"]
+    w["acc"] = [None] * 7
+    for i in (W_Q, W_K, W_V):
+        w["acc"][i] = mat(w["h1"], Wt["w"][i], c.d, c.d)
+    w["rsq"], w["rsk"], w["rsv"] = (irs_witness_host(w["acc"][i], 16, 1) for i in (W_Q, W_K, W_V))
+    w["yq"], w["yk"], w["yv"] = w["rsq"][0], w["rsk"][0], w["rsv"][0]
+    w["rpq"] = irope_witness(w["yq"], Wt["ct"], Wt["st"], lseq, ldh, lT, ld)
+    w["rpk"] = irope_witness(w["yk"], Wt["ct"], Wt["st"], lseq, ldh, lT, ld)
+    w["rq"], w["rk"] = w["rpq"][0], w["rpk"][0]
+    sc = np.zeros(1 << lez, dtype=np.int64)
+    rq, rk = sig(w["rq"]), sig(w["rk"])
+    for b in range(c.batch):
+        for h in range(c.nh):
+            xv, wv, yv = views_qk(c, h, b)
+            Xd = rq[_view_idx(xv, ldh, lseq, S_J, S_A)]                    # [i][j]
+            Wd = rk[_view_idx(wv, ldh, lseq, S_J, S_A)]                    # [k][j]
+            sc[_view_idx(yv, lseq, lseq, S_A, S_I)] = Xd @ Wd.T            # [i][k]
+    w["sc"] = lift(sc)
+    w["rsz"] = irs_witness_host(w["sc"], c.sfz, 2)
+    w["z"] = w["rsz"][0]
+    w["smx"] = ismx_witness(w["z"], T, la, lseq)
+    w["p"] = w["smx"]["p"]
+    pva = np.zeros(1 << le, dtype=np.int64)
+    pp, yv_ = sig(w["p"]), sig(w["yv"])
+    for b in range(c.batch):
+        for h in range(c.nh):
+            xv, wv, yv = views_pv(c, h, b)
+            Xd = pp[_view_idx(xv, lseq, lseq, S_J, S_A)]                   # [i][j]
+            Wd = yv_[_view_idx(wv, lseq, ldh, S_J, S_A)]                   # [k][j]
+            pva[_view_idx(yv, ldh, lseq, S_A, S_I)] = Xd @ Wd.T            # [i][k]
+    w["pva"] = lift(pva)
+    w["rsat"] = irs_witness_host(w["pva"], 16, 1)
+    w["at"] = w["rsat"][0]
+    w["acc"][W_O] = mat(w["at"], Wt["w"][W_O], c.d, c.d)
+    w["rso"] = irs_witness_host(w["acc"][W_O], 16, 1)
+    w["yo"] = w["rso"][0]
+    w["res1"], w["idxRes1"] = iadd_witness(x0, w["yo"])
+    w["rms2"] = irms_witness(w["res1"], Wt["g2"], T, lT, ld)
+    w["h2"] = w["rms2"]["y"]
+    for i in (W_G, W_U):
+        w["acc"][i] = mat(w["h2"], Wt["w"][i], c.d, c.dff)
+    w["rsg"], w["rsu"] = irs_witness_host(w["acc"][W_G], 16, 1), irs_witness_host(w["acc"][W_U], 16, 1)
+    w["gg"], w["uu"] = w["rsg"][0], w["rsu"][0]
+    w["swg"] = iswg_witness(w["gg"], w["uu"], T)
+    w["mo"] = w["swg"][2]
+    w["acc"][W_D] = mat(w["mo"], Wt["w"][W_D], c.dff, c.d)
+    w["rsd"] = irs_witness_host(w["acc"][W_D], 16, 1)
+    w["yd"] = w["rsd"][0]
+    w["out"], w["idxOut"] = iadd_witness(w["res1"], w["yd"])
+    return w
+
+
+_CHAIN = ("x0", "h1", "yq", "yk", "yv", "rq", "rk", "sc", "z", "p", "pva", "at", "yo", "res1", "h2", "gg", "uu", "mo", "yd", "out")
+
+
+def itf_commit_all(engine, w, Wt, R, col):
+    """p3itf::commit_all (p3_int_layer.cuh:343-419), non-zk: every chain grid, weight and gain committed once.
+    ``col`` uploads a host array into an engine column.  Returns {name: (column, root)}."""
+    o = {}
+    com = lambda a: (lambda c_: (c_, engine.commit_gpu_rootonly(c_, R)))(col(a))
+    for k in _CHAIN:
+        o[k] = com(w[k])
+    o["g1"], o["g2"] = com(Wt["g1"]), com(Wt["g2"])
+    o["w"] = [com(x) for x in Wt["w"]]
+    o["acc"] = [com(x) for x in w["acc"]]
+    return o
+
+
+def itf_prove(engine, tr, c, w, o, Wt, T, R, Q, col):
+    """p3itf::prove (p3_int_layer.cuh:452-581), non-zk: all sub-proofs in fixed order on one transcript with one
+    ledger and one lookup queue, one merged-lookup flush, the public input/output bindings, one batched opening per
+    size class.  Returns the serialised TfProof: 6 x u32 dims | 26 + 2A length-prefixed sub-proofs in proving order |
+    28 roots | u32 groups (len, GroupProof)* | ioin ioout | u32 batches (len, BatchProof)*."""
+    ld, lT, ldff, lseq, ldh, la = c.ld, c.lT, c.ldff, c.lseq, c.ldh, c.la
+    le, lef, lez = ld + lT, ldff + lT, la + 2 * lseq
+    ctx = Ctx()
+    tr.absorb("itf-dims", struct.pack("<6I", c.seq, c.d, c.nh, c.dh, c.dff, c.batch))
+    for i in range(7):
+        ctx.defer([o["w"][i]], col(w["idxW"][i]), T["RS20"])
+    ctx.defer([o["g1"]], col(w["idxG1"]), T["RS20"])
+    ctx.defer([o["g2"]], col(w["idxG2"]), T["RS20"])
+    ctx.defer([o["x0"]], col(w["idxX0"]), T["RS20"])
+    subs = []
+
+    def up(wit):
+        return {k: (col(v) if isinstance(v, np.ndarray) else [col(x) for x in v]) for k, v in wit.items() if k not in ("y", "p")}
+
+    def rms(name, X, G, Y):
+        subs.append(irms_prove(engine, tr, T, X, G, Y, up(w[name]), lT, ld, R, Q, ctx))
+
+    def mm(X, Wc, Y, lj, lk, li, views=None):
+        subs.append(imm_prove(engine, tr, X, Wc, Y, lj, lk, li, R, Q, ctx.ledger, views))
+
+    def irs(name, X, Y, lev, sf, rng):
+        y, L, iL, iY = w[name]
+        subs.append(irs_prove(engine, tr, T, X, Y, ([col(l) for l in L], [col(i) for i in iL], col(iY) if iY is not None else None),
+                              lev, sf, rng, R, Q, ctx.ledger, ctx.luq))
+
+    def rope(name, Qc, Y):
+        y, rem, iR, iY, Cc, S2 = w[name]
+        subs.append(irope_prove(engine, tr, T, (col(lift(Cc)), col(lift(S2)), ldh), Qc, Y, (col(rem), col(iR), col(iY)), lT, ld, R, Q, ctx))
+
+    rms("rms1", o["x0"], o["g1"], o["h1"])
+    for i in (W_Q, W_K, W_V):
+        mm(o["h1"], o["w"][i], o["acc"][i], ld, ld, lT)
+    irs("rsq", o["acc"][W_Q], o["yq"], le, 16, 1)
+    irs("rsk", o["acc"][W_K], o["yk"], le, 16, 1)
+    irs("rsv", o["acc"][W_V], o["yv"], le, 16, 1)
+    rope("rpq", o["yq"], o["rq"])
+    rope("rpk", o["yk"], o["rk"])
+    for b in range(c.batch):
+        for h in range(c.nh):
+            mm(o["rq"], o["rk"], o["sc"], ldh, lseq, lseq, views_qk(c, h, b))
+    irs("rsz", o["sc"], o["z"], lez, c.sfz, 2)
+    subs.append(ismx_prove(engine, tr, T, o["z"], o["p"], up(w["smx"]), la, lseq, R, Q, ctx))
+    for b in range(c.batch):
+        for h in range(c.nh):
+            mm(o["p"], o["yv"], o["pva"], lseq, ldh, lseq, views_pv(c, h, b))
+    irs("rsat", o["pva"], o["at"], le, 16, 1)
+    mm(o["at"], o["w"][W_O], o["acc"][W_O], ld, ld, lT)
+    irs("rso", o["acc"][W_O], o["yo"], le, 16, 1)
+    subs.append(iadd_prove(engine, tr, T, o["x0"], o["yo"], o["res1"], col(w["idxRes1"]), le, R, Q, ctx))
+    rms("rms2", o["res1"], o["g2"], o["h2"])
+    for i in (W_G, W_U):
+        mm(o["h2"], o["w"][i], o["acc"][i], ld, ldff, lT)
+    irs("rsg", o["acc"][W_G], o["gg"], lef, 16, 1)
+    irs("rsu", o["acc"][W_U], o["uu"], lef, 16, 1)
+    sil, rem, mo, iG, iR, iM = w["swg"]
+    subs.append(iswg_prove(engine, tr, T, o["gg"], o["uu"], o["mo"], (col(sil), col(rem), col(iG), col(iR), col(iM)), lef, R, Q, ctx))
+    mm(o["mo"], o["w"][W_D], o["acc"][W_D], ldff, ld, lT)
+    irs("rsd", o["acc"][W_D], o["yd"], le, 16, 1)
+    subs.append(iadd_prove(engine, tr, T, o["res1"], o["yd"], o["out"], col(w["idxOut"]), le, R, Q, ctx))
+    lug = lu_flush(engine, tr, ctx.luq, ctx.ledger, R)
+    z1 = [tr.chal() for _ in range(le)]
+    ioin = claimc(engine, tr, ctx.ledger, o["x0"][0], o["x0"][1], z1)
+    z2 = [tr.chal() for _ in range(le)]
+    ioout = claimc(engine, tr, ctx.ledger, o["out"][0], o["out"][1], z2)
+    batches = tail_prove(engine, tr, ctx.ledger, R, Q, "itf-bo")
+    blob = lambda b: struct.pack("<I", len(b)) + b
+    roots = [o["x0"][1], o["h1"][1]] + [a[1] for a in o["acc"]] + [o[k][1] for k in
+             ("yq", "yk", "yv", "rq", "rk", "sc", "z", "p", "pva", "at", "yo", "res1", "h2", "gg", "uu", "mo", "yd", "out")]
+    out = struct.pack("<6I", c.seq, c.d, c.nh, c.dh, c.dff, c.batch) + b"".join(blob(s) for s in subs) + b"".join(roots)
+    out += struct.pack("<I", len(lug)) + b"".join(blob(b) for b in lug) + struct.pack("<QQ", ioin, ioout)
+    return out + struct.pack("<I", len(batches)) + b"".join(blob(b) for b in batches)

@@ -322,6 +322,11 @@ class Prover:
         """out[e] = col[e mod len(col)]: a per-column value repeated over 2^lT rows."""
         return col.repeat(1 << lT).contiguous()
 
+    def gather(self, col, idx):
+        """out[t] = col[idx[t]] (idx: host int64 array): the dense operand behind a p3imm operand view."""
+        import torch
+        return col[torch.from_numpy(np.ascontiguousarray(idx, dtype=np.int64)).to(col.device)].contiguous()
+
     def flip_bit(self, col, b):
         """out[u] = col[u ^ (1 << b)]: the rotate-half permutation of RoPE (zkllm-src/p3_int_gadgets.cuh:1297-1298)."""
         return col.view(-1, 2, 1 << b).flip(1).reshape(-1).contiguous()
@@ -756,7 +761,28 @@ def tail_prove(engine, tr, ledger, R, Q, tag):
     return [engine.prove_class(tr, np.stack(c[1]), c[2], R, Q, "%s%d" % (tag, i)) for i, c in enumerate(ledger.cls)]
 
 
-def imm_prove(engine, tr, X, W, Y, lj, lk, li, R, Q, ledger=None):
+S_J, S_A, S_I, S_C = 0, 1, 2, 3      # p3imm bit sources: contraction index, free index, Y's i index, constant
+
+
+def view_offsets(view, lj, la):
+    """p3imm::op_off (zkllm-src/p3_int_gadgets.cuh:448-459) for all (a, j): element index inside the committed
+    column of entry (j, a) of the operand view; result shape [2^la][2^lj]."""
+    j = np.arange(1 << lj, dtype=np.int64)[None, :]
+    a = np.arange(1 << la, dtype=np.int64)[:, None]
+    idx = np.zeros((1 << la, 1 << lj), dtype=np.int64)
+    for t, (src, bit) in enumerate(view):
+        b = ((j >> bit) & 1) if src == S_J else ((a >> bit) & 1) if src == S_A else (bit if src == S_C else 0)
+        idx |= b << t
+    return idx
+
+
+def view_point(view, r_first, r_second, first=S_J, second=S_A):
+    """p3imm::op_pt / y_pt (zkllm-src/p3_int_gadgets.cuh:473-497): the claim point on the committed column."""
+    return [r_first[bit] if src == first else r_second[bit] if src == second else (bit if src == S_C else 0)
+            for src, bit in view]
+
+
+def imm_prove(engine, tr, X, W, Y, lj, lk, li, R, Q, ledger=None, views=None):
     """p3imm::prove (zkllm-src/p3_int_gadgets.cuh:546-605), non-zk, direct layouts: proves
     Y(i,k) = sum_j X(i,j) W(j,k) for committed columns X = [j | i<<lj], W = [k | j<<lk], Y = [k | i<<lk].
     X, W, Y: (device column, 32-byte root).
@@ -778,7 +804,16 @@ def imm_prove(engine, tr, X, W, Y, lj, lk, li, R, Q, ledger=None):
     tr.absorb("imm-Y", Y[1])
     z = [tr.chal() for _ in range(lk + li)]
     zk_, zi_ = z[:lk], z[lk:]
-    yY = claimc(engine, tr, ledger, Y[0], Y[1], z)
+    Xfull, Wfull = X, W
+    if views is None:
+        yY = claimc(engine, tr, ledger, Y[0], Y[1], z)
+    else:
+        # operand views into larger committed columns (per-head attention matmuls): gather the dense operands,
+        # prove on them, and place every claim on the committed column at the view's point
+        xv, wv, yv = views
+        yY = claimc(engine, tr, ledger, Y[0], Y[1], view_point(yv, zk_, zi_, S_A, S_I))
+        X = (engine.gather(X[0], view_offsets(xv, lj, li).reshape(-1)), None)          # [i][j]
+        W = (engine.gather(W[0], view_offsets(wv, lj, lk).T.reshape(-1)), None)        # [j][k]
     J, K, I = 1 << lj, 1 << lk, 1 << li
     eq_i, eq_k = engine.build_eq_gpu(np.array(zi_, dtype=np.uint64)), engine.build_eq_gpu(np.array(zk_, dtype=np.uint64))
     msgs, r = [], []
@@ -812,8 +847,12 @@ def imm_prove(engine, tr, X, W, Y, lj, lk, li, R, Q, ledger=None):
         ri = [int(x) for x in ri]
     else:
         ri = []
-    yX = claimc(engine, tr, ledger, X[0], X[1], rj + ri)
-    yW = claimc(engine, tr, ledger, W[0], W[1], rk + rj)
+    if views is None:
+        yX = claimc(engine, tr, ledger, X[0], X[1], rj + ri)
+        yW = claimc(engine, tr, ledger, W[0], W[1], rk + rj)
+    else:
+        yX = claimc(engine, tr, ledger, Xfull[0], Xfull[1], view_point(views[0], rj, ri))
+        yW = claimc(engine, tr, ledger, Wfull[0], Wfull[1], view_point(views[1], rj, rk))
     out = struct.pack("<III", lj, lk, li) + b"".join(np.ascontiguousarray(m, dtype=np.uint64).tobytes() for m in msgs)
     out += struct.pack("<QQQ", yY, yX, yW)
     batches = tail_prove(engine, tr, ledger, R, Q, "imm-bo") if own else []
