@@ -619,6 +619,80 @@ def run_profile_case(args):
     print(json.dumps({"profile_case": name, "ms": e0.elapsed_time(e1)}), flush=True)
 
 
+def run_suite_layer(args):
+    """--suite-layer: one integer decoder layer (the reference's p3itf stack, non-zk) at the padded shapes of
+    BASELINE configs[3] (Llama-68M-shaped, seq 128) and configs[4] (TinyLlama-shaped, seq 512): witness chain on the
+    host, commitments, proof; beside the reference's own layer prover on the same inputs."""
+    import torch
+    import zkh_import
+    zk = zkh_import.load()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import Reference
+    torch.cuda.set_device(0)
+    prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+    ig = zk.ig
+    ref = Reference() if (Reference.available() and not args.no_ref_cuda) else None
+    if ref is not None and not ref.gpu_available():
+        ref = None
+    R, Q = 2, 24
+
+    def col(a):
+        a = np.ascontiguousarray(a)
+        return torch.from_numpy(a.view(np.int32)).cuda() if a.dtype == np.uint32 else zk.p3.to_device(a)
+
+    shapes = {"c3": ("BASELINE configs[3]: Llama-68M-shaped layer, seq 128 (hidden 768 -> 1024, 12 -> 16 heads of 64, MLP 3072 -> 4096)",
+                     (128, 1024, 16, 64, 4096, 1)),
+              "c4": ("BASELINE configs[4]: TinyLlama-1.1B-shaped layer, seq 512 (hidden 2048, 32 heads of 64 with each KV head "
+                     "replicated 8x, MLP 5632 -> 8192)", (512, 2048, 32, 64, 8192, 1)),
+              "tiny": ("smoke shape", (16, 32, 2, 16, 64, 1))}
+    for key in args.layer_shapes.split(","):
+        name, dims = shapes[key]
+        c = ig.Config(*dims)
+        T = ig.build_tables(zk.load_library(), c.d, c.btop)
+        x0 = Wt = w = None
+        for tries in range(6):                      # in-range witness: retry seeds, shrink weights (as the reference's bench)
+            try:
+                x0, Wt = ig.random_layer_inputs(c, 42 + tries, 0.9 * (0.7 ** (tries // 2)))
+                t0 = time.perf_counter()
+                w = ig.itf_build_witness(c, x0, Wt, T)
+                t_wit = time.perf_counter() - t0
+                break
+            except ValueError:
+                continue
+        if w is None:
+            raise SystemExit("no in-range witness")
+        best = None
+        for rep in range(args.layer_reps):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            o = ig.itf_commit_all(prover, w, Wt, R, col)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            tr = zk.Transcript("itf-layer")
+            pf = ig.itf_prove(prover, tr, c, w, o, Wt, T, R, Q, col)
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+            if best is None or t2 - t1 < best[1]:
+                best = (t1 - t0, t2 - t1)
+        line = {"suite": name, "dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), dims)), "R": R, "Q": Q,
+                "witness_host_s": t_wit, "commit_s": best[0], "prove_s": best[1], "prove_s_per_layer": best[1],
+                "proof_MB": len(pf) / 1048576.0}
+        if ref is not None:
+            from ig_helpers import ref_itf_prove, ref_itf_verify
+            rpf, rst, grid, ms = ref_itf_prove(ref, zk.Transcript("itf-layer").state, c, x0, Wt, R, Q)
+            wroots = [x[1] for x in o["w"]] + [o["g1"][1], o["g2"][1]]
+            ok, st = ref_itf_verify(ref, zk.Transcript("itf-layer").state, c, x0, o["x0"][1], wroots, Wt, w["out"], R, Q, pf)
+            line.update({"reference_witness_s": ms[0] / 1e3, "reference_commit_s": ms[1] / 1e3, "reference_prove_s": ms[2] / 1e3,
+                         "speedup_prove_vs_reference": ms[2] / 1e3 / best[1],
+                         "speedup_commit_plus_prove_vs_reference": (ms[1] + ms[2]) / 1e3 / (best[0] + best[1]),
+                         "same_proof_bytes": bool(rpf == pf and rst == tr.state),
+                         "accepted_by_reference_verifier": bool(ok and st == tr.state)})
+        print(json.dumps(line), flush=True)
+        del o, w
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -634,6 +708,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
     ap.add_argument("--profile-case", default=None, help="one small kernel-family invocation (for ncu captures)")
+    ap.add_argument("--suite-layer", action="store_true", help="one integer decoder layer beside the reference's layer prover")
+    ap.add_argument("--layer-shapes", default="c3")
+    ap.add_argument("--layer-reps", type=int, default=2)
     ap.add_argument("--suite-fr", action="store_true", help="BLS12-381 Fr kernels beside the reference's CUDA code")
     ap.add_argument("--fr-logd", type=int, default=22)
     ap.add_argument("--suite-gadgets", action="store_true", help="configs[0]/[2] through the gadget-level provers")
@@ -646,6 +723,8 @@ def main():
         return run_suite(args)
     if args.suite_fr:
         return run_suite_fr(args)
+    if args.suite_layer:
+        return run_suite_layer(args)
     if args.suite_gadgets:
         return run_suite_gadgets(args)
 

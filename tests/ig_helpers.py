@@ -72,25 +72,7 @@ def ref_prove2(ref, name, st, a, b, roots, le, R, Q):
 
 
 def layer_inputs(ig, c, seed, wscale=0.9):
-    """Random in-range layer inputs in the style of zkllm-src/p3_int_layer_bench.cu:49-72 (numpy generator)."""
-    g = np.random.default_rng(seed)
-    wb = max(2, int(round(65536.0 * wscale / np.sqrt(c.d))))
-    wbd = max(2, int(round(65536.0 * wscale / np.sqrt(c.dff))))
-    Wt = {"w": []}
-    for i in range(7):
-        K, N = c.wshape(i)
-        b = wbd if i == ig.W_D else wb
-        Wt["w"].append(ig.lift(g.integers(-(b - 1), b, K * N)))
-    Wt["g1"] = ig.lift(49152 + g.integers(-16383, 16384, c.d))
-    Wt["g2"] = ig.lift(49152 + g.integers(-16383, 16384, c.d))
-    dh2 = c.dh // 2
-    s = np.arange(c.seq)[:, None]
-    j = np.arange(dh2)[None, :]
-    ang = s * np.power(10000.0, -2.0 * j / c.dh)
-    Wt["ct"] = np.rint(np.cos(ang) * 16384.0).astype(np.int32)
-    Wt["st"] = np.rint(np.sin(ang) * 16384.0).astype(np.int32)
-    x0 = ig.lift(g.integers(-(1 << 16) + 1, 1 << 16, c.seq * c.batch * c.d))
-    return x0, Wt
+    return ig.random_layer_inputs(c, seed, wscale)
 
 
 def ref_itf_verify(ref, st, c, x0, rX0, wroots, Wt, out, R, Q, proof):

@@ -506,6 +506,29 @@ def _view_idx(view, n_first, n_second, first, second):
     return idx
 
 
+def random_layer_inputs(c, seed, wscale=0.9):
+    """Synthetic in-range layer inputs in the style of the reference's layer bench (zkllm-src/p3_int_layer_bench.cu:49-72):
+    weights uniform within +-2^16*wscale/sqrt(fan-in), gains around 0.75*2^16, RoPE tables for theta = 10000 at scale
+    2^14, activations uniform in +-2^16.  Returns (x0, weights dict)."""
+    g = np.random.default_rng(seed)
+    wb = max(2, int(round(65536.0 * wscale / np.sqrt(c.d))))
+    wbd = max(2, int(round(65536.0 * wscale / np.sqrt(c.dff))))
+    Wt = {"w": []}
+    for i in range(7):
+        K, N = c.wshape(i)
+        b = wbd if i == W_D else wb
+        Wt["w"].append(lift(g.integers(-(b - 1), b, K * N)))
+    Wt["g1"] = lift(49152 + g.integers(-16383, 16384, c.d))
+    Wt["g2"] = lift(49152 + g.integers(-16383, 16384, c.d))
+    s_ = np.arange(c.seq)[:, None]
+    j_ = np.arange(c.dh // 2)[None, :]
+    ang = s_ * np.power(10000.0, -2.0 * j_ / c.dh)
+    Wt["ct"] = np.rint(np.cos(ang) * 16384.0).astype(np.int32)
+    Wt["st"] = np.rint(np.sin(ang) * 16384.0).astype(np.int32)
+    x0 = lift(g.integers(-(1 << 16) + 1, 1 << 16, c.seq * c.batch * c.d))
+    return x0, Wt
+
+
 def rs20_idx(v):
     s = sig(v)
     if ((s < -ABND) | (s >= ABND)).any():
@@ -533,7 +556,10 @@ def itf_build_witness(c, x0, Wt, T):
     le, lef, lez = ld + lT, ldff + lT, la + 2 * lseq
     w = {"x0": x0, "idxW": [rs20_idx(x) for x in Wt["w"]], "idxG1": rs20_idx(Wt["g1"]), "idxG2": rs20_idx(Wt["g2"]),
          "idxX0": rs20_idx(x0)}
-    mat = lambda X, Wm, K, N: lift((sig(X).reshape(-1, K) @ sig(Wm).reshape(K, N)).reshape(-1))      # Y[k | i << lk]
+    def mat(X, Wm, K, N):
+        # Y[k | i << lk]; |x|, |w| < 2^19 and K <= 2^13 keep every partial sum below 2^53, so the float64 product is exact
+        y = sig(X).reshape(-1, K).astype(np.float64) @ sig(Wm).reshape(K, N).astype(np.float64)
+        return lift(np.rint(y).astype(np.int64).reshape(-1))
     w["rms1"] = irms_witness(x0, Wt["g1"], T, lT, ld)
     w["h1"] = w["rms1"]["y"]
     w["acc"] = [None] * 7
