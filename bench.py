@@ -693,6 +693,64 @@ def run_suite_layer(args):
         torch.cuda.empty_cache()
 
 
+def run_suite_model(args):
+    """--suite-model [--gpus N under torch.distributed.run]: the 22 independent layer proofs of the TinyLlama-shaped
+    model (BASELINE configs[4]; one transcript per layer, as the reference's transformer bench proves them) placed
+    round-robin on N GPUs with no collective on the data path.  Every layer uses the same synthetic witness (built
+    once per rank on the host, outside the timed region); commitments and proof are timed.  Device time is taken
+    per rank and the maximum over ranks is reported."""
+    import torch
+    import torch.distributed as dist
+    import zkh_import
+    zk = zkh_import.load()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run" % (args.gpus, world))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    prover = zk.Prover(local, torch.cuda.current_stream().cuda_stream)
+    ig = zk.ig
+    R, Q = 2, 24
+    dims = (512, 2048, 32, 64, 8192, 1) if args.layer_shapes != "tiny" else (16, 32, 2, 16, 64, 1)
+    nlayers = args.model_layers
+    c = ig.Config(*dims)
+    T = ig.build_tables(zk.load_library(), c.d, c.btop)
+    x0, Wt = ig.random_layer_inputs(c, 42, 0.9)
+    w = ig.itf_build_witness(c, x0, Wt, T)
+
+    def col(a):
+        a = np.ascontiguousarray(a)
+        return torch.from_numpy(a.view(np.int32)).cuda() if a.dtype == np.uint32 else zk.p3.to_device(a, "cuda:%d" % local)
+
+    def prove_layer(layer):
+        o = ig.itf_commit_all(prover, w, Wt, R, col)
+        tr = zk.Transcript("itf-layer-%d" % layer)
+        return len(ig.itf_prove(prover, tr, c, w, o, Wt, T, R, Q, col))
+    prove_layer(0)                                   # warm-up (table uploads, workspace growth)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    sizes = zk.p3.run_independent(list(range(nlayers)), prove_layer, dist if world > 1 else None)
+    torch.cuda.synchronize()
+    secs = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([secs], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t.item())
+    if rank == 0:
+        print(json.dumps({"suite": "model: %d independent layer proofs, dims %s, placed round-robin on %d GPU(s)" % (nlayers, dims, world),
+                          "n_gpus": world, "total_s": secs, "s_per_layer": secs / nlayers, "layers_per_s": nlayers / secs,
+                          "proof_MB_per_layer": sizes[0] / 1048576.0, "R": R, "Q": Q,
+                          "timed": "commitments + proof per layer (witness built once on the host beforehand)"}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -708,6 +766,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
     ap.add_argument("--profile-case", default=None, help="one small kernel-family invocation (for ncu captures)")
+    ap.add_argument("--suite-model", action="store_true", help="22 independent TinyLlama-shaped layer proofs over --gpus N")
+    ap.add_argument("--model-layers", type=int, default=22)
     ap.add_argument("--suite-layer", action="store_true", help="one integer decoder layer beside the reference's layer prover")
     ap.add_argument("--layer-shapes", default="c3")
     ap.add_argument("--layer-reps", type=int, default=2)
@@ -725,6 +785,8 @@ def main():
         return run_suite_fr(args)
     if args.suite_layer:
         return run_suite_layer(args)
+    if args.suite_model:
+        return run_suite_model(args)
     if args.suite_gadgets:
         return run_suite_gadgets(args)
 
