@@ -663,7 +663,9 @@ def run_suite_layer(args):
         if w is None:
             raise SystemExit("no in-range witness")
         best = None
+        prover.keep_trees = not args.no_keep_trees     # codewords and Merkle trees of the layer stay in HBM for the openings
         for rep in range(args.layer_reps):
+            prover.release_kept()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             o = ig.itf_commit_all(prover, w, Wt, R, col)
@@ -688,7 +690,9 @@ def run_suite_layer(args):
                          "speedup_commit_plus_prove_vs_reference": (ms[1] + ms[2]) / 1e3 / (best[0] + best[1]),
                          "same_proof_bytes": bool(rpf == pf and rst == tr.state),
                          "accepted_by_reference_verifier": bool(ok and st == tr.state)})
+        line["trees_kept_resident"] = bool(prover.keep_trees)
         print(json.dumps(line), flush=True)
+        prover.release_kept()
         del o, w
         torch.cuda.empty_cache()
 
@@ -725,10 +729,14 @@ def run_suite_model(args):
         a = np.ascontiguousarray(a)
         return torch.from_numpy(a.view(np.int32)).cuda() if a.dtype == np.uint32 else zk.p3.to_device(a, "cuda:%d" % local)
 
+    prover.keep_trees = not args.no_keep_trees
+
     def prove_layer(layer):
         o = ig.itf_commit_all(prover, w, Wt, R, col)
         tr = zk.Transcript("itf-layer-%d" % layer)
-        return len(ig.itf_prove(prover, tr, c, w, o, Wt, T, R, Q, col))
+        n = len(ig.itf_prove(prover, tr, c, w, o, Wt, T, R, Q, col))
+        prover.release_kept()
+        return n
     prove_layer(0)                                   # warm-up (table uploads, workspace growth)
     if world > 1:
         dist.barrier()
@@ -766,6 +774,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
     ap.add_argument("--profile-case", default=None, help="one small kernel-family invocation (for ncu captures)")
+    ap.add_argument("--no-keep-trees", action="store_true", help="layer suites: recompute codewords and trees in the openings")
     ap.add_argument("--suite-model", action="store_true", help="22 independent TinyLlama-shaped layer proofs over --gpus N")
     ap.add_argument("--model-layers", type=int, default=22)
     ap.add_argument("--suite-layer", action="store_true", help="one integer decoder layer beside the reference's layer prover")

@@ -257,6 +257,18 @@ ZKH_API int zkh_batchopen_prove_class(zkh_ctx* ctx, uint32_t v, const uint64_t* 
                                       const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
                                       uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
                                       uint8_t* out, size_t cap, size_t* written);
+/* Commitment that keeps its codeword (2^(v+R) elements) and Merkle tree (zkh_merkle_tree_bytes(2^(v+R)) bytes) in
+ * caller-owned device buffers, and the batched opening that reads them: with 180 GB of HBM a prover can keep the
+ * trees of a whole layer resident, so prove_class no longer re-encodes and re-hashes every opened column as the
+ * reference does (zkllm-src/p3_batchopen.cuh:393-445 resolves and rebuilds them).  Proof bytes are unchanged.
+ * kept_cw[j] / kept_tree[j]: buffers of entry j's column, or NULL to recompute that column. */
+ZKH_API int zkh_basefold_commit_keep(zkh_ctx* ctx, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t* cw_dev,
+                             uint8_t* tree_dev, uint8_t root[32]);
+ZKH_API int zkh_batchopen_prove_class_kept(zkh_ctx* ctx, uint32_t v, const uint64_t* pts, uint32_t T,
+                                   const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
+                                   uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
+                                   uint8_t* out, size_t cap, size_t* written, const uint64_t* const* kept_cw,
+                                   const uint8_t* const* kept_tree);
 
 /* ---- logUp ---- */
 /* Multiplicities: cnt_dev[j] = #{i : idx_dev[i] == j}, j < M (zkllm-src/p3_logup.cuh:149-172,

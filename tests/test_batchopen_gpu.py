@@ -92,3 +92,27 @@ def test_prove_class_argument_errors(orc, zk, prover):
         prover.prove_class(tr, pts, [(col, b"\\0" * 32, 1)], 1, 24, "x")   # point index out of range
     with pytest.raises(zk.ZkhError):
         prover.prove_class(tr, pts, [(col, b"\\0" * 32, 0)], 0, 24, "x")   # rate
+
+
+@pytest.mark.parametrize("v,R,ncols,T,k", [(2, 1, 2, 2, 3), (9, 2, 4, 3, 8), (14, 1, 5, 4, 11)])
+def test_kept_commitments_give_the_same_proof(orc, zk, prover, v, R, ncols, T, k):
+    """Columns committed with their codeword and tree kept resident open to the same bytes as recomputed ones;
+    a class may mix kept and recomputed columns."""
+    Q = 24
+    cols, pts, ent_col, zid = make_ledger(orc, v, ncols, T, k, 300 + v)
+    dcols = [zk.p3.to_device(c) for c in cols]
+    plain_roots = [prover.commit_gpu_rootonly(d, R) for d in dcols]
+    tr0 = zk.Transcript("main")
+    want = prover.prove_class(tr0, pts, [(dcols[c], plain_roots[c], t) for c, t in zip(ent_col, zid)], R, Q, "tf-bo1")
+    prover.keep_trees = True
+    try:
+        kept_roots = [prover.commit_gpu_rootonly(d, R) if i % 2 == 0 or ncols < 3 else plain_roots[i] for i, d in enumerate(dcols)]
+        assert kept_roots == plain_roots
+        tr1 = zk.Transcript("main")
+        got = prover.prove_class(tr1, pts, [(dcols[c], kept_roots[c], t) for c, t in zip(ent_col, zid)], R, Q, "tf-bo1")
+        assert got == want and tr1.state == tr0.state
+    finally:
+        prover.keep_trees = False
+        prover.release_kept()
+    tr2 = zk.Transcript("main")
+    assert prover.prove_class(tr2, pts, [(dcols[c], plain_roots[c], t) for c, t in zip(ent_col, zid)], R, Q, "tf-bo1") == want

@@ -132,6 +132,25 @@ extern "C" int zkh_basefold_commit(zkh_ctx* c, const uint64_t* c_dev, uint32_t v
     return ZKH_OK;
 }
 
+// Commit and KEEP: the codeword and the whole Merkle tree stay in caller-owned device buffers, so that later
+// openings of this column read authentication paths instead of encoding and hashing the column again.
+extern "C" int zkh_basefold_commit_keep(zkh_ctx* c, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t* cw_dev,
+                                        uint8_t* tree_dev, uint8_t root[32]) {
+    if (!c || !c_dev || !root || !cw_dev || !tree_dev) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_keep: null pointer");
+    if (v + R < 1 || v + R > 32 || R < 1 || R > 8) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_keep: need R in 1..8, v+R <= 32");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    const uint32_t logM = v + R;
+    const size_t M = (size_t)1 << logM;
+    ZKH_TRY(zkh_ws_reserve(c, ntt_scratch_bytes(logM)));
+    ZKH_TRY(ntt_enqueue(c, c_dev, (uint64_t)1 << v, cw_dev, logM, false, c->ws));
+    uint8_t* root_dev = (uint8_t*)c->d_ctl->aux;
+    ZKH_TRY(merkle_enqueue(c, cw_dev, M, tree_dev, nullptr, root_dev));
+    ZKH_CUDA(c, cudaMemcpyAsync(c->h_ctl->aux, root_dev, 32, cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    memcpy(root, c->h_ctl->aux, 32);
+    return ZKH_OK;
+}
+
 extern "C" int zkh_basefold_commit_host(zkh_ctx* c, const uint64_t* coeffs, uint32_t v, uint32_t R, uint8_t root[32]) {
     if (!c || !coeffs || !root) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_host: null pointer");
     if (v + R < 1 || v + R > 32 || R < 1 || R > 8) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_host: need R in 1..8, v+R <= 32");

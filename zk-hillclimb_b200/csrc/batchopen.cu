@@ -139,10 +139,11 @@ extern "C" size_t zkh_batchopen_proof_bound(uint32_t v, uint32_t R, uint32_t Q, 
     return bo_bound(v, R, Q, ncols);
 }
 
-extern "C" int zkh_batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, uint32_t T,
-                                         const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
-                                         uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
-                                         uint8_t* out, size_t cap, size_t* written) {
+static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, uint32_t T,
+                                 const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
+                                 uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
+                                 uint8_t* out, size_t cap, size_t* written, const uint64_t* const* kept_cw,
+                                 const uint8_t* const* kept_tree) {
     if (!c || !pts || !cols_dev || !roots || !zid || !label || !state || !out || !written)
         return zkh_fail(c, ZKH_ERR_ARG, "batchopen: null pointer");
     if (v < 1 || R < 1 || R > 3 || v + R > 30) return zkh_fail(c, ZKH_ERR_ARG, "batchopen: need v >= 1, R in 1..3, v+R <= 30");
@@ -376,10 +377,17 @@ extern "C" int zkh_batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t*
     // round-0 openings: re-encode each distinct column, hash its tree, gather values and paths
     const size_t q0_used = (size_t)nu * 8 + (size_t)nu * logM0 * 32;
     for (uint32_t cc = 0; cc < nc; cc++) {
-        ZKH_TRY(ntt_enqueue(c, cols_dev[first[cc]], N, cwc, logM0, false, ws + o_misc));
-        ZKH_TRY(merkle_enqueue(c, cwc, M0, treec, nullptr, nullptr));
+        const gl_t* cw_use = cwc;
+        const uint8_t* tree_use = treec;
+        if (kept_cw && kept_tree && kept_cw[first[cc]] && kept_tree[first[cc]]) {
+            cw_use = kept_cw[first[cc]];          // committed with zkh_basefold_commit_keep: nothing to recompute
+            tree_use = kept_tree[first[cc]];
+        } else {
+            ZKH_TRY(ntt_enqueue(c, cols_dev[first[cc]], N, cwc, logM0, false, ws + o_misc));
+            ZKH_TRY(merkle_enqueue(c, cwc, M0, treec, nullptr, nullptr));
+        }
         const uint32_t nth = nu * (logM0 + 1);
-        bo_q0_kernel<<<(nth + 127) / 128, 128, 0, s>>>(cwc, treec, logM0, d_upos, nu, d_q0 + (size_t)cc * q0_per_col);
+        bo_q0_kernel<<<(nth + 127) / 128, 128, 0, s>>>(cw_use, tree_use, logM0, d_upos, nu, d_q0 + (size_t)cc * q0_per_col);
     }
     ZKH_CUDA(c, cudaGetLastError());
     std::vector<uint8_t> hq0((size_t)nc * q0_per_col);
@@ -417,4 +425,20 @@ extern "C" int zkh_batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t*
     }
     *written = (size_t)(p - out);
     return ZKH_OK;
+}
+
+extern "C" int zkh_batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, uint32_t T,
+                                         const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
+                                         uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
+                                         uint8_t* out, size_t cap, size_t* written) {
+    return batchopen_prove_class(c, v, pts, T, cols_dev, roots, zid, k, R, Q, label, state, out, cap, written, nullptr, nullptr);
+}
+// Same, with kept_cw[j] / kept_tree[j] (either may be NULL per entry) the codeword and Merkle tree that
+// zkh_basefold_commit_keep left for entry j's column under the same R.
+extern "C" int zkh_batchopen_prove_class_kept(zkh_ctx* c, uint32_t v, const uint64_t* pts, uint32_t T,
+                                              const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
+                                              uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
+                                              uint8_t* out, size_t cap, size_t* written, const uint64_t* const* kept_cw,
+                                              const uint8_t* const* kept_tree) {
+    return batchopen_prove_class(c, v, pts, T, cols_dev, roots, zid, k, R, Q, label, state, out, cap, written, kept_cw, kept_tree);
 }

@@ -242,9 +242,22 @@ class Prover:
         if isinstance(c, np.ndarray):
             c = np.ascontiguousarray(c, dtype=np.uint64)
             self._ck(self._L.zkh_basefold_commit_host(self._h, c.ctypes.data, len(c).bit_length() - 1, R, root))
+        elif getattr(self, "keep_trees", False) and c.numel() >= 2:
+            # keep the codeword and the tree resident for the batched openings (released by release_kept())
+            import torch
+            v = c.numel().bit_length() - 1
+            M = 1 << (v + R)
+            cw = torch.empty(M, dtype=torch.int64, device=c.device)
+            tree = torch.empty(self._L.zkh_merkle_tree_bytes(M), dtype=torch.uint8, device=c.device)
+            self._ck(self._L.zkh_basefold_commit_keep(self._h, _ptr(c), v, R, _ptr(cw), _ptr(tree), root))
+            self.__dict__.setdefault("_kept", {})[(c.data_ptr(), R)] = (c, cw, tree)
         else:
             self._ck(self._L.zkh_basefold_commit(self._h, _ptr(c), c.numel().bit_length() - 1, R, 0, root))
         return bytes(root)
+
+    def release_kept(self):
+        """Drop the codewords and trees kept by commit_gpu_rootonly under ``keep_trees``."""
+        self.__dict__.pop("_kept", None)
 
     def prove_eval_dev(self, c_dev, z, y, R, Q, cw0_dev=None, seed="p3-bf"):
         """p3bf::prove_eval_dev (zkllm-src/p3_basefold.cuh:355-420).  Returns the serialised EvalProof."""
@@ -272,8 +285,17 @@ class Prover:
         out = np.zeros(cap, dtype=np.uint8)
         wr = C.c_size_t(0)
         st = _buf32(tr.state)
-        self._ck(self._L.zkh_batchopen_prove_class(self._h, v, pts.ctypes.data, T, ptrs, roots, zid.ctypes.data, k,
-                                                   R, Q, label.encode(), st, out.ctypes.data, cap, C.byref(wr)))
+        kept = self.__dict__.get("_kept")
+        if kept:
+            hit = [kept.get((_ptr(e[0]), R)) for e in ents]
+            hit = [h if (h is not None and h[0] is e[0]) else None for h, e in zip(hit, ents)]
+            kcw = (C.c_uint64 * k)(*[(_ptr(h[1]) if h else 0) for h in hit])
+            ktr = (C.c_uint64 * k)(*[(_ptr(h[2]) if h else 0) for h in hit])
+            self._ck(self._L.zkh_batchopen_prove_class_kept(self._h, v, pts.ctypes.data, T, ptrs, roots, zid.ctypes.data, k,
+                                                            R, Q, label.encode(), st, out.ctypes.data, cap, C.byref(wr), kcw, ktr))
+        else:
+            self._ck(self._L.zkh_batchopen_prove_class(self._h, v, pts.ctypes.data, T, ptrs, roots, zid.ctypes.data, k,
+                                                       R, Q, label.encode(), st, out.ctypes.data, cap, C.byref(wr)))
         tr.state = bytes(st)
         return out.tobytes()[:wr.value]
 
@@ -359,8 +381,14 @@ class Prover:
         return out
 
     def lu_ones(self, n):
+        """All-ones numerator column of a lookup's witness side (read-only; cached per size)."""
         import torch
-        return torch.ones(n, dtype=torch.int64, device="cuda:%d" % self.device)
+        cache = self.__dict__.setdefault("_ones", {})
+        if n not in cache:
+            if sum(cache) + n > (1 << 27):        # at most 1 GiB of cached ones
+                cache.clear()
+            cache[n] = torch.ones(n, dtype=torch.int64, device="cuda:%d" % self.device)
+        return cache[n]
 
     def affine(self, cols_dev, g, addend):
         import torch
