@@ -7,9 +7,9 @@
 // the same convention at their boundaries and track the power of R = 2^256 a product chain carries
 // internally, correcting once per reduced sum instead of once per element.
 //
-// Montgomery multiplication is operand scanning with two carry chains per row: the low halves of
-// a[j]*b[i] ripple into limbs j, the high halves into limbs j+1 (mad.lo.cc / madc.hi.cc), then the
-// same pair of chains for m*p with m = t[0] * (-1/p mod 2^32) = -t[0] (p = 1 mod 2^32).
+// Montgomery multiplication is operand scanning with two carry chains per row (even and odd limbs of
+// the multiplicand, each product's low half directly followed by its high half: mad.lo.cc / madc.hi.cc),
+// then the same pair of chains for m*p with m = t[0] * (-1/p mod 2^32) = -t[0] (p = 1 mod 2^32).
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -125,25 +125,27 @@ __device__ __forceinline__ Fr fr_sub(const Fr& a, const Fr& b) {
     return r;
 }
 
-// t[0..9] += x[0..7] * y   (two carry chains; t[9] collects the final carries)
+// t[0..9] += x[0..7] * y.  Two carry-propagating additions: the products of the even limbs occupy limb pairs
+// (0,1) (2,3) (4,5) (6,7), those of the odd limbs (1,2) (3,4) (5,6) (7,8); inside a chain every low half is
+// followed by the high half of the same product, the shape that maps to one wide multiply-add with carry.
 __device__ __forceinline__ void fr_row_mad(uint32_t (&t)[10], const uint32_t (&x)[8], uint32_t y) {
     asm("mad.lo.cc.u32 %0, %10, %18, %0;\n\t"
-        "madc.lo.cc.u32 %1, %11, %18, %1;\n\t"
+        "madc.hi.cc.u32 %1, %10, %18, %1;\n\t"
         "madc.lo.cc.u32 %2, %12, %18, %2;\n\t"
-        "madc.lo.cc.u32 %3, %13, %18, %3;\n\t"
+        "madc.hi.cc.u32 %3, %12, %18, %3;\n\t"
         "madc.lo.cc.u32 %4, %14, %18, %4;\n\t"
-        "madc.lo.cc.u32 %5, %15, %18, %5;\n\t"
+        "madc.hi.cc.u32 %5, %14, %18, %5;\n\t"
         "madc.lo.cc.u32 %6, %16, %18, %6;\n\t"
-        "madc.lo.cc.u32 %7, %17, %18, %7;\n\t"
+        "madc.hi.cc.u32 %7, %16, %18, %7;\n\t"
         "addc.cc.u32 %8, %8, 0;\n\t"
         "addc.u32 %9, %9, 0;\n\t"
-        "mad.hi.cc.u32 %1, %10, %18, %1;\n\t"
+        "mad.lo.cc.u32 %1, %11, %18, %1;\n\t"
         "madc.hi.cc.u32 %2, %11, %18, %2;\n\t"
-        "madc.hi.cc.u32 %3, %12, %18, %3;\n\t"
+        "madc.lo.cc.u32 %3, %13, %18, %3;\n\t"
         "madc.hi.cc.u32 %4, %13, %18, %4;\n\t"
-        "madc.hi.cc.u32 %5, %14, %18, %5;\n\t"
+        "madc.lo.cc.u32 %5, %15, %18, %5;\n\t"
         "madc.hi.cc.u32 %6, %15, %18, %6;\n\t"
-        "madc.hi.cc.u32 %7, %16, %18, %7;\n\t"
+        "madc.lo.cc.u32 %7, %17, %18, %7;\n\t"
         "madc.hi.cc.u32 %8, %17, %18, %8;\n\t"
         "addc.u32 %9, %9, 0;"
         : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]), "+r"(t[4]), "+r"(t[5]), "+r"(t[6]), "+r"(t[7]),
