@@ -399,7 +399,7 @@ def run_suite_gadgets(args):
 
 
 def run_suite_fr(args):
-    """--suite-fr: the BLS12-381 Fr kernels at the reference's layer sizes (SURVEY-style sizes: Hadamard /
+    """--suite-fr: the BLS12-381 Fr kernels at the sizes the reference.s layer drivers use (Hadamard /
     bracket sumchecks over D = 2^22, the fully connected layer's partial evaluations and inner-product
     rounds for 128 x 1024 . 1024 x 1024), beside the reference's own CUDA code on the same inputs."""
     import torch
