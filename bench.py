@@ -651,40 +651,54 @@ def run_suite_layer(args):
         c = ig.Config(*dims)
         T = ig.build_tables(zk.load_library(), c.d, c.btop)
         x0 = Wt = w = None
+        on_dev = not args.host_witness
+        if on_dev:
+            from zk_hillclimb_b200 import ig_dev
         for tries in range(6):                      # in-range witness: retry seeds, shrink weights (as the reference's bench)
             try:
                 x0, Wt = ig.random_layer_inputs(c, 42 + tries, 0.9 * (0.7 ** (tries // 2)))
+                torch.cuda.synchronize()
                 t0 = time.perf_counter()
-                w = ig.itf_build_witness(c, x0, Wt, T)
+                w = ig_dev.itf_build_witness(c, x0, Wt, T) if on_dev else ig.itf_build_witness(c, x0, Wt, T)
+                torch.cuda.synchronize()
                 t_wit = time.perf_counter() - t0
                 break
             except ValueError:
                 continue
         if w is None:
             raise SystemExit("no in-range witness")
+        if on_dev:                                  # second run: kernels and allocator warm
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            w = ig_dev.itf_build_witness(c, x0, Wt, T)
+            torch.cuda.synchronize()
+            t_wit = time.perf_counter() - t0
+        wcol = (lambda a: a) if on_dev else col
+        Wc = w["dev_W"] if on_dev else Wt
         best = None
         prover.keep_trees = not args.no_keep_trees     # codewords and Merkle trees of the layer stay in HBM for the openings
         for rep in range(args.layer_reps):
             prover.release_kept()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            o = ig.itf_commit_all(prover, w, Wt, R, col)
+            o = ig.itf_commit_all(prover, w, Wc, R, wcol)
             torch.cuda.synchronize()
             t1 = time.perf_counter()
             tr = zk.Transcript("itf-layer")
-            pf = ig.itf_prove(prover, tr, c, w, o, Wt, T, R, Q, col)
+            pf = ig.itf_prove(prover, tr, c, w, o, Wt, T, R, Q, wcol)
             torch.cuda.synchronize()
             t2 = time.perf_counter()
             if best is None or t2 - t1 < best[1]:
                 best = (t1 - t0, t2 - t1)
+        out_host = zk.p3.to_host(w["out"]) if on_dev else w["out"]
         line = {"suite": name, "dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), dims)), "R": R, "Q": Q,
-                "witness_host_s": t_wit, "commit_s": best[0], "prove_s": best[1], "prove_s_per_layer": best[1],
-                "proof_MB": len(pf) / 1048576.0}
+                ("witness_device_s" if on_dev else "witness_host_s"): t_wit, "commit_s": best[0], "prove_s": best[1],
+                "prove_s_per_layer": best[1], "proof_MB": len(pf) / 1048576.0}
         if ref is not None:
             from ig_helpers import ref_itf_prove, ref_itf_verify
             rpf, rst, grid, ms = ref_itf_prove(ref, zk.Transcript("itf-layer").state, c, x0, Wt, R, Q)
             wroots = [x[1] for x in o["w"]] + [o["g1"][1], o["g2"][1]]
-            ok, st = ref_itf_verify(ref, zk.Transcript("itf-layer").state, c, x0, o["x0"][1], wroots, Wt, w["out"], R, Q, pf)
+            ok, st = ref_itf_verify(ref, zk.Transcript("itf-layer").state, c, x0, o["x0"][1], wroots, Wt, out_host, R, Q, pf)
             line.update({"reference_witness_s": ms[0] / 1e3, "reference_commit_s": ms[1] / 1e3, "reference_prove_s": ms[2] / 1e3,
                          "speedup_prove_vs_reference": ms[2] / 1e3 / best[1],
                          "speedup_commit_plus_prove_vs_reference": (ms[1] + ms[2]) / 1e3 / (best[0] + best[1]),
@@ -775,6 +789,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
     ap.add_argument("--profile-case", default=None, help="one small kernel-family invocation (for ncu captures)")
+    ap.add_argument("--host-witness", action="store_true", help="layer suites: build the witness chain with numpy on the host")
     ap.add_argument("--no-keep-trees", action="store_true", help="layer suites: recompute codewords and trees in the openings")
     ap.add_argument("--suite-model", action="store_true", help="22 independent TinyLlama-shaped layer proofs over --gpus N")
     ap.add_argument("--model-layers", type=int, default=22)
@@ -948,7 +963,7 @@ def main():
             ref_cuda = {"error": repr(e)}
 
     # BASELINE.json's first metric on the same GPU: prove seconds per TinyLlama-shaped decoder layer, seq 512
-    # (integer layer, non-zk; witness chain on the host and outside the timed region, as in the reference's bench)
+    # (integer layer, non-zk; the witness chain runs on the device and, as in the reference's bench, outside the timed region)
     layer = None
     if rank == 0 and world == 1 and not args.no_layer:
         try:
@@ -958,20 +973,22 @@ def main():
             cfg = ig.Config(512, 2048, 32, 64, 8192, 1)
             tabs = ig.build_tables(zk.load_library(), cfg.d, cfg.btop)
             lx0, lW = ig.random_layer_inputs(cfg, 42, 0.9)
+            from zk_hillclimb_b200 import ig_dev
+            dvc = "cuda:%d" % local
+            lw = ig_dev.itf_build_witness(cfg, lx0, lW, tabs, dvc)            # warm-up of the witness kernels
+            torch.cuda.synchronize()
             t0 = time.perf_counter()
-            lw = ig.itf_build_witness(cfg, lx0, lW, tabs)
+            lw = ig_dev.itf_build_witness(cfg, lx0, lW, tabs, dvc)
+            torch.cuda.synchronize()
             t_wit = time.perf_counter() - t0
-
-            def lcol(a):
-                a = np.ascontiguousarray(a)
-                return torch.from_numpy(a.view(np.int32)).cuda() if a.dtype == np.uint32 else zk.p3.to_device(a, "cuda:%d" % local)
+            lcol = lambda a: a
             prover.keep_trees = True
             times = []
             for _ in range(2):
                 prover.release_kept()
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
-                lo = ig.itf_commit_all(prover, lw, lW, 2, lcol)
+                lo = ig.itf_commit_all(prover, lw, lw["dev_W"], 2, lcol)
                 torch.cuda.synchronize()
                 t1 = time.perf_counter()
                 lpf = ig.itf_prove(prover, zk.Transcript("itf-layer"), cfg, lw, lo, lW, tabs, 2, 24, lcol)
@@ -982,7 +999,7 @@ def main():
             prover.keep_trees = False
             layer = {"metric": "prove s/layer (TinyLlama-1.1B-shaped integer decoder layer, seq 512, non-zk, R=2, Q=24)",
                      "prove_s_per_layer": min(t[1] for t in times), "commit_s_per_layer": min(t[0] for t in times),
-                     "witness_host_s": t_wit, "proof_MB": len(lpf) / 1048576.0,
+                     "witness_device_s": t_wit, "proof_MB": len(lpf) / 1048576.0,
                      "dims": {"seq": 512, "d": 2048, "nh": 32, "dh": 64, "dff": 8192},
                      "note": "hidden 2048, 32 heads of 64 (each KV head replicated 8x), MLP 5632 padded to 8192; the reference's "
                              "prover cannot run this shape (2^33-element host columns per matmul); at the Llama-68M shape it "

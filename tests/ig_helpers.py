@@ -19,6 +19,11 @@ class OracleGadgetEngine(OracleStandaloneLuEngine):
     def bcast_cols(self, col, lT):
         return _Arr(np.tile(col.a, 1 << lT))
 
+    def causal_mask(self, la, lseq):
+        u = np.arange(1 << (la + 2 * lseq), dtype=np.int64)
+        seq = 1 << lseq
+        return _Arr(((u & (seq - 1)) <= ((u >> lseq) & (seq - 1))).astype(np.uint64))
+
     def gather(self, col, idx):
         return _Arr(col.a[np.asarray(idx, dtype=np.int64)])
 

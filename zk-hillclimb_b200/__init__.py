@@ -9,6 +9,7 @@ Layout:
   _lib.py     ctypes binding of the C ABI; raises if the library is missing
   p3.py       host-side mirror of the reference's in-process prover interface
   ig.py       integer-layer gadgets (residual add, SwiGLU, ...) as host logic over the engine
+  ig_dev.py   the layer's witness chain on the GPU (imported on demand; needs torch)
   fr.py       host-side mirror of the BLS12-381 Fr pieces (eq tensors, folds, product sumchecks)
 """
 from . import _lib  # noqa: F401

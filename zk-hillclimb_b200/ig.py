@@ -434,7 +434,7 @@ def ismx_prove(engine, tr, T, Z, P, wit, la, lseq, R, Q, ctx=None):
     ]
     konst = (-lam[2] * 65536 + lam[4]) % GL_P
     cols = [engine.build_eq_gpu(zE), Z[0]] + [c[0] for c in CE] + [P[0], engine.bcast_rows(CB[0][0], lseq),
-                                                                   engine.bcast_rows(CB[1][0], lseq), engine.upload(causal_mask(la, lseq))]
+                                                                   engine.bcast_rows(CB[1][0], lseq), engine.causal_mask(la, lseq)]
     rE, mE = _sumcheck(engine, tr, "ism-sce", cols, terms, konst)
     yEZ = claimc(engine, tr, ctx.ledger, Z[0], Z[1], rE)
     yE = [claimc(engine, tr, ctx.ledger, c[0], c[1], rE) for c in CE]
@@ -646,7 +646,13 @@ def itf_prove(engine, tr, c, w, o, Wt, T, R, Q, col):
     subs = []
 
     def up(wit):
-        return {k: (col(v) if isinstance(v, np.ndarray) else [col(x) for x in v]) for k, v in wit.items() if k not in ("y", "p")}
+        return {k: ([col(x) for x in v] if isinstance(v, (list, tuple)) else col(v)) for k, v in wit.items() if k not in ("y", "p")}
+
+    def lift_any(a):                     # host witness: numpy; device witness (ig_dev): torch
+        if isinstance(a, np.ndarray):
+            return lift(a)
+        from . import ig_dev
+        return ig_dev.lift(a)
 
     def rms(name, X, G, Y):
         subs.append(irms_prove(engine, tr, T, X, G, Y, up(w[name]), lT, ld, R, Q, ctx))
@@ -661,7 +667,7 @@ def itf_prove(engine, tr, c, w, o, Wt, T, R, Q, col):
 
     def rope(name, Qc, Y):
         y, rem, iR, iY, Cc, S2 = w[name]
-        subs.append(irope_prove(engine, tr, T, (col(lift(Cc)), col(lift(S2)), ldh), Qc, Y, (col(rem), col(iR), col(iY)), lT, ld, R, Q, ctx))
+        subs.append(irope_prove(engine, tr, T, (col(lift_any(Cc)), col(lift_any(S2)), ldh), Qc, Y, (col(rem), col(iR), col(iY)), lT, ld, R, Q, ctx))
 
     rms("rms1", o["x0"], o["g1"], o["h1"])
     for i in (W_Q, W_K, W_V):

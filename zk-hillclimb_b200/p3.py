@@ -344,6 +344,13 @@ class Prover:
         """out[e] = col[e mod len(col)]: a per-column value repeated over 2^lT rows."""
         return col.repeat(1 << lT).contiguous()
 
+    def causal_mask(self, la, lseq):
+        """p3ismx::mask_col: 1 where key index j <= query index i over u = j | (i << lseq) | (a << 2 lseq)."""
+        import torch
+        u = torch.arange(1 << (la + 2 * lseq), dtype=torch.int64, device="cuda:%d" % self.device)
+        seq = 1 << lseq
+        return ((u & (seq - 1)) <= ((u >> lseq) & (seq - 1))).to(torch.int64)
+
     def gather(self, col, idx):
         """out[t] = col[idx[t]] (idx: host int64 array): the dense operand behind a p3imm operand view."""
         import torch
