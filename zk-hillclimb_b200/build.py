@@ -4,6 +4,8 @@
 
 Produces zk-hillclimb_b200/libzkh.so from csrc/*.cu with nvcc.  The library has
 no Python or torch dependency; it is what the C ABI in include/zkh.h names.
+Also builds zk-hillclimb_b200/zkh_p3_selftest from host/p3_selftest.cpp with g++: the
+C++ host side (include/zkh_p3.hpp) linked against the library.
 """
 import glob
 import os
@@ -13,6 +15,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libzkh.so")
+SELFTEST = os.path.join(HERE, "zkh_p3_selftest")
+INCLUDE = os.path.abspath(os.path.join(HERE, "..", "include"))
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -32,7 +36,24 @@ def stale():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def build_selftest(force=False):
+    """The C++ host program over the C ABI; linked with an rpath beside the library."""
+    src = os.path.join(HERE, "host", "p3_selftest.cpp")
+    deps = [src, os.path.join(INCLUDE, "zkh.h"), os.path.join(INCLUDE, "zkh_p3.hpp"), LIB]
+    if not force and os.path.exists(SELFTEST) and all(os.path.getmtime(d) <= os.path.getmtime(SELFTEST) for d in deps):
+        return SELFTEST
+    subprocess.check_call([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", "-I", INCLUDE, src, "-o", SELFTEST,
+                           "-L", HERE, "-lzkh", "-Wl,-rpath,$ORIGIN"])
+    return SELFTEST
+
+
 def build(force=False, verbose=False):
+    build_lib(force, verbose)
+    build_selftest(force)
+    return LIB
+
+
+def build_lib(force=False, verbose=False):
     if not force and not stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
