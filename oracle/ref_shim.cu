@@ -665,6 +665,100 @@ p3itf::Weights itf_weights(const p3itf::Config& cfg, const uint64_t* const* w7, 
     W.rp = rope_pub(ct, sn, cfg.lseq(), cfg.ldh());
     return W;
 }
+// p3hwl::LayerProof <-> bytes (non-zk fields, declaration order):
+//   u32 B K N | roots rdp[10] rdg[29] rdo[46] rdb[6] rdn[6] | u32 groups (len, GroupProof)* |
+//   mDp yDp[10] yDpG | mDg yDg[29] | mCh yCh[8] | yGSc yGSa | mGS yGSal yGSsel | mDo yDo[46] | yDbBC[5] yDnBC[5] |
+//   mDb yDb[6] yXsb | mDn yDn[6] yWsb | ySlA ySlE ySlS ySlF ySlBE ySlSG | mY yY | u32 batches (len, BatchProof)*
+// every message list is u32 rounds + rounds*40 bytes
+template <typename IO>
+void hwl_walk(IO& io, p3hwl::LayerProof& pf) {
+    using namespace p3hwl;
+    io.u32(pf.B); io.u32(pf.K); io.u32(pf.N);
+    for (int c = 0; c < NDP; c++) io.raw(pf.rdp[c].data(), 32);
+    for (int c = 0; c < NDG; c++) io.raw(pf.rdg[c].data(), 32);
+    for (int c = 0; c < NDO; c++) io.raw(pf.rdo[c].data(), 32);
+    for (int c = 0; c < NDS; c++) io.raw(pf.rdb[c].data(), 32);
+    for (int c = 0; c < NDS; c++) io.raw(pf.rdn[c].data(), 32);
+    io.groups(pf.lug);
+    io.msgs(pf.mDp); io.raw(pf.yDp, sizeof pf.yDp); io.raw(&pf.yDpG, 8);
+    io.msgs(pf.mDg); io.raw(pf.yDg, sizeof pf.yDg);
+    io.msgs(pf.mCh); io.raw(pf.yCh, sizeof pf.yCh);
+    io.raw(&pf.yGSc, 8); io.raw(&pf.yGSa, 8);
+    io.msgs(pf.mGS); io.raw(&pf.yGSal, 8); io.raw(&pf.yGSsel, 8);
+    io.msgs(pf.mDo); io.raw(pf.yDo, sizeof pf.yDo);
+    io.raw(pf.yDbBC, sizeof pf.yDbBC); io.raw(pf.yDnBC, sizeof pf.yDnBC);
+    io.msgs(pf.mDb); io.raw(pf.yDb, sizeof pf.yDb); io.raw(&pf.yXsb, 8);
+    io.msgs(pf.mDn); io.raw(pf.yDn, sizeof pf.yDn); io.raw(&pf.yWsb, 8);
+    io.raw(&pf.ySlA, 8); io.raw(&pf.ySlE, 8); io.raw(&pf.ySlS, 8); io.raw(&pf.ySlF, 8); io.raw(&pf.ySlBE, 8); io.raw(&pf.ySlSG, 8);
+    io.msgs(pf.mY); io.raw(&pf.yY, 8);
+    io.batches(pf.batches);
+}
+struct HwlWriter {
+    std::vector<uint8_t> b;
+    std::vector<uint8_t> tmp = std::vector<uint8_t>((size_t)256 << 20);
+    void raw(const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); }
+    void u32(uint32_t& v) { raw(&v, 4); }
+    void msgs(std::vector<p3hwl::Msg5>& m) { uint32_t n = (uint32_t)m.size(); raw(&n, 4); raw(m.data(), (size_t)n * 40); }
+    void groups(std::vector<p3lu::GroupProof>& g) {
+        uint32_t ng = (uint32_t)g.size(); raw(&ng, 4);
+        for (auto& x : g) { uint32_t n = (uint32_t)lu_serialize(x, tmp.data(), tmp.size()); raw(&n, 4); raw(tmp.data(), n); }
+    }
+    void batches(std::vector<p3bo::BatchProof>& v) {
+        uint32_t nb = (uint32_t)v.size(); raw(&nb, 4);
+        for (auto& x : v) { uint32_t n = (uint32_t)bo_serialize(x, tmp.data(), tmp.size()); raw(&n, 4); raw(tmp.data(), n); }
+    }
+};
+struct HwlReader {
+    const uint8_t* p; const uint8_t* end; bool ok = true;
+    bool need(size_t n) { if (!ok || (size_t)(end - p) < n) ok = false; return ok; }
+    void raw(void* d, size_t n) { if (need(n)) { memcpy(d, p, n); p += n; } }
+    void u32(uint32_t& v) { raw(&v, 4); }
+    void msgs(std::vector<p3hwl::Msg5>& m) {
+        uint32_t n = 0; u32(n);
+        if (!ok || n > 64 || !need((size_t)n * 40)) { ok = false; return; }
+        m.resize(n); raw(m.data(), (size_t)n * 40);
+    }
+    void groups(std::vector<p3lu::GroupProof>& g) {
+        uint32_t ng = 0; u32(ng);
+        if (!ok || ng > 256) { ok = false; return; }
+        g.resize(ng);
+        for (auto& x : g) { uint32_t n = 0; u32(n); if (!need(n) || !lu_deserialize(p, n, x)) { ok = false; return; } p += n; }
+    }
+    void batches(std::vector<p3bo::BatchProof>& v) {
+        uint32_t nb = 0; u32(nb);
+        if (!ok || nb > 64) { ok = false; return; }
+        v.resize(nb);
+        for (auto& x : v) { uint32_t n = 0; u32(n); if (!need(n) || !bo_deserialize(p, n, x)) { ok = false; return; } p += n; }
+    }
+};
+size_t hwl_serialize(const p3hwl::LayerProof& pf, uint8_t* out, size_t cap) {
+    HwlWriter w;
+    hwl_walk(w, const_cast<p3hwl::LayerProof&>(pf));
+    return emit(w.b, out, cap);
+}
+bool hwl_deserialize(const uint8_t* in, size_t len, p3hwl::LayerProof& pf) {
+    HwlReader r{in, in + len};
+    hwl_walk(r, pf);
+    return r.ok && r.p == r.end;
+}
+const p3hwl::Tables& hwl_tables() {
+    static p3hwl::Tables T = p3hwl::build_tables();
+    return T;
+}
+const p3lu::Table* hwl_table_at(int which) {
+    const p3hwl::Tables& T = hwl_tables();
+    const p3lu::Table* tabs[16] = {&T.DM, &T.SH, &T.RM, &T.R15, &T.ASH, &T.WIDTH, &T.R10, &T.R11,
+                                   &T.R12, &T.R16, &T.FH, &T.REXP, &T.SE, &T.CREM13, &T.CREM12, &T.CTH};
+    return (which >= 0 && which < 16) ? tabs[which] : nullptr;
+}
+p3hwl::Golden hwl_golden(uint32_t B, uint32_t K, uint32_t N, const uint8_t* x, const uint8_t* w, const uint32_t* xs,
+                         const uint32_t* ws) {
+    p3hwl::Golden L; L.B = B; L.K = K; L.N = N;
+    L.x.assign(x, x + (size_t)B * K); L.w.assign(w, w + (size_t)N * K);
+    L.xs.assign(xs, xs + B); L.ws.assign(ws, ws + N);
+    L.y.assign((size_t)B * N, 0);
+    return L;
+}
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
 const p3ig::Tables& ig_tables(uint32_t d, uint32_t btop) {
     static std::map<std::pair<uint32_t, uint32_t>, p3ig::Tables> cache;
@@ -1600,6 +1694,88 @@ size_t ref_itf_prove(uint8_t st[32], const uint32_t dims[6], const uint64_t* x0,
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);
     return n;
+}
+
+// ---- p3hwl: the fp8 (Hawkeye) matmul gadget ----
+// public table `which` (0..15 in the order the prover absorbs them): rows and column count, columns copied when given
+int ref_hwl_table(int which, uint64_t* const* cols_out, uint32_t* rows_out, uint8_t id_out[32]) {
+    const p3lu::Table* t = hwl_table_at(which);
+    if (!t) return 0;
+    if (rows_out) *rows_out = (uint32_t)t->cols[0].size();
+    if (cols_out) for (size_t c = 0; c < t->cols.size(); c++) memcpy(cols_out[c], t->cols[c].data(), t->cols[c].size() * 8);
+    if (id_out) memcpy(id_out, t->id.data(), 32);
+    return (int)t->cols.size();
+}
+// p3hwl::gen_witness on the host.  dom: 0 dp, 1 dg, 2 dob, 3 db, 4 dn (column `col` copied to out64), 5 lookup indices of
+// instance `col` (copied to out32), 6 the bf16 output (B*N uint16 to out32's memory).  Returns elements written, 0 on throw.
+size_t ref_hwl_witness(uint32_t B, uint32_t K, uint32_t N, const uint8_t* x, const uint8_t* w, const uint32_t* xs, const uint32_t* ws,
+                       int dom, int col, uint64_t* out64, uint32_t* out32) {
+    try {
+        static p3hwl::LayerWit wt; static std::vector<uint8_t> key;
+        std::vector<uint8_t> k2;
+        auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; k2.insert(k2.end(), q, q + n); };
+        uint32_t d3[3] = {B, K, N}; app(d3, 12); app(x, (size_t)B * K); app(w, (size_t)N * K); app(xs, 4 * B); app(ws, 4 * N);
+        if (k2 != key) { wt = p3hwl::gen_witness(hwl_golden(B, K, N, x, w, xs, ws), true); key = k2; }
+        const std::vector<gl_t>* v = nullptr;
+        if (dom == 0 && col < p3hwl::NDP) v = &wt.dp[col];
+        else if (dom == 1 && col < p3hwl::NDG) v = &wt.dg[col];
+        else if (dom == 2 && col < p3hwl::NDO) v = &wt.dob[col];
+        else if (dom == 3 && col < p3hwl::NDS) v = &wt.db[col];
+        else if (dom == 4 && col < p3hwl::NDS) v = &wt.dn[col];
+        if (v) { memcpy(out64, v->data(), v->size() * 8); return v->size(); }
+        if (dom == 5 && col < p3hwl::NLU) { memcpy(out32, wt.lidx[col].data(), wt.lidx[col].size() * 4); return wt.lidx[col].size(); }
+        if (dom == 6) { memcpy(out32, wt.Y.data(), wt.Y.size() * 2); return wt.Y.size(); }
+    } catch (...) {}
+    return 0;
+}
+// gen_witness + commit_operands + prove; roots4_out: X W XS WS roots; Y_out: B*N bf16 patterns; ms_out[0] witness,
+// [1] operand commits, [2] prove
+size_t ref_hwl_prove(uint8_t st[32], uint32_t B, uint32_t K, uint32_t N, const uint8_t* x, const uint8_t* w, const uint32_t* xs,
+                     const uint32_t* ws, uint32_t R, uint32_t Q, int gpu, uint8_t* roots4_out, uint16_t* Y_out, uint8_t* out,
+                     size_t cap, double* ms_out) {
+    p3fri::g_gpu_merkle = gpu != 0;
+    if (gpu) p3bf::p3_enable_mempool();
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        const p3hwl::Tables& T = hwl_tables();
+        double t0 = p3bf::bf_now_ms();
+        p3hwl::LayerWit wt = p3hwl::gen_witness(hwl_golden(B, K, N, x, w, xs, ws), false);
+        double t1 = p3bf::bf_now_ms();
+        p3hwl::Operands ops = p3hwl::commit_operands(wt, R, gpu != 0);
+        if (gpu) cudaDeviceSynchronize();
+        double t2 = p3bf::bf_now_ms();
+        auto pf = p3hwl::prove(tr, wt, T, ops, R, Q, gpu != 0);
+        if (gpu) cudaDeviceSynchronize();
+        double t3 = p3bf::bf_now_ms();
+        if (ms_out) { ms_out[0] = t1 - t0; ms_out[1] = t2 - t1; ms_out[2] = t3 - t2; }
+        if (roots4_out) {
+            memcpy(roots4_out, ops.X.root.data(), 32); memcpy(roots4_out + 32, ops.W.root.data(), 32);
+            memcpy(roots4_out + 64, ops.XS.root.data(), 32); memcpy(roots4_out + 96, ops.WS.root.data(), 32);
+        }
+        if (Y_out) memcpy(Y_out, wt.Y.data(), wt.Y.size() * 2);
+        n = hwl_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+// p3hwl::verify (host only) on the serialised proof
+int ref_hwl_verify(uint8_t st[32], uint32_t B, uint32_t K, uint32_t N, const uint8_t* roots4, const uint16_t* Y, uint32_t R,
+                   uint32_t Q, const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3hwl::LayerProof pf;
+        if (hwl_deserialize(proof, len, pf)) {
+            p3fri::Hash r[4];
+            for (int i = 0; i < 4; i++) memcpy(r[i].data(), roots4 + 32 * i, 32);
+            std::vector<uint16_t> Yv(Y, Y + (size_t)B * N);
+            ok = p3hwl::verify(tr, hwl_tables(), pf, r[0], r[1], r[2], r[3], Yv, B, K, N, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
 }
 
 }  // extern "C"

@@ -10,6 +10,7 @@ Layout:
   p3.py       host-side mirror of the reference's in-process prover interface
   ig.py       integer-layer gadgets (residual add, SwiGLU, ...) as host logic over the engine
   ig_dev.py   the layer's witness chain on the GPU (imported on demand; needs torch)
+  hwl.py      the fp8 (Hawkeye) matmul gadget: tables, witness replay as tensor arithmetic, prover (on demand; needs torch)
   fr.py       host-side mirror of the BLS12-381 Fr pieces (eq tensors, folds, product sumchecks)
 """
 from . import _lib  # noqa: F401
@@ -18,3 +19,11 @@ from . import p3  # noqa: F401
 from . import fr  # noqa: F401
 from . import ig  # noqa: F401
 from .p3 import (F_GKR, F_LOGUP, F_PROD2, F_PROD3, GL_P, Prover, Transcript)  # noqa: F401
+
+
+def __getattr__(name):
+    """The torch-based modules load on first use."""
+    if name in ("hwl", "ig_dev"):
+        import importlib
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError(name)

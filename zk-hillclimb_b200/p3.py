@@ -693,7 +693,9 @@ def prove_super(engine, tr, table_cols, table_id, subgroups, R, strict=True):
     table_cols: c columns of 2^m rows (engine buffers); table_id: its 32-byte binding hash
     (p3lu::make_table).  subgroups: list, in flush order, of (n, members); a member is
     (cols, roots, idx) with c witness columns of 2^n rows, their commitment roots (None for a
-    virtual column) and the uint32 row indices into the table.
+    virtual column) and the uint32 row indices into the table; an optional fourth element is the member's bind
+    callback (p3lu::PBind, p3_logup.cuh:451-456): called as bind(pm, y_virt) after the member's own claims, it returns
+    further opening claims (column, root, point, value) that tie the virtual columns to commitments.
     Returns (proof bytes, claims, cnt column).  claims = the opening-ledger additions in the
     reference's order: (column, root, point, value) for every committed member column at the
     subgroup's shared point, then the multiplicity column at the table-side point.
@@ -709,7 +711,7 @@ def prove_super(engine, tr, table_cols, table_id, subgroups, R, strict=True):
         k = len(members)
         g = (k - 1).bit_length()
         tr.absorb("lug-dims", struct.pack("<IIII", n, g, k, c))
-        for cols, roots, idx in members:
+        for cols, roots, idx, *_ in members:
             if len(cols) != c or any(int(t.numel()) != (1 << n) for t in cols) or int(idx.numel()) != (1 << n):
                 raise ValueError("p3lu: group member size")
             for r in roots:
@@ -738,7 +740,7 @@ def prove_super(engine, tr, table_cols, table_id, subgroups, R, strict=True):
         accP, accQ = (accP * Q + P * accQ) % GL_P, accQ * Q % GL_P
         pm = np.array(rA[:n], dtype=np.uint64)
         mem = []
-        for cols, roots, idx in members:
+        for cols, roots, idx, *bind in members:
             yW, yv = [], []
             for col, r in zip(cols, roots):
                 y = engine.eval_h_gpu(col, pm)
@@ -749,6 +751,8 @@ def prove_super(engine, tr, table_cols, table_id, subgroups, R, strict=True):
                 else:
                     yv.append(y)
                     tr.absorb("lug-yv", struct.pack("<Q", y))
+            if bind and bind[0] is not None:
+                claims.extend(bind[0](pm, yv))
             mem.append((yW, yv))
         subs.append((n, k, gk, mem))
     LQT = engine.affine(table_cols, gamma, beta)
@@ -926,7 +930,7 @@ def lu_flush(engine, tr, luq, ledger, R, strict=True):
     """p3lu::lu_flush (zkllm-src/p3_logup.cuh:1940-1956): group the deferred lookups by (table, log-rows)
     in first-appearance order (groups capped at 2^LU_GCAP stacked rows), bundle the groups by table,
     prove one merged instance per table.  luq entries: {"W": [(col, root or None), ...], "idx": indices,
-    "tab": make_table(...)}.  Opening claims go to ``ledger``.  Returns the list of GroupProof bytes."""
+    "tab": make_table(...)} plus an optional "bind" callback (see prove_super).  Opening claims go to ``ledger``.  Returns the list of GroupProof bytes."""
     groups = []                                    # lu_groups
     for i, o in enumerate(luq):
         n = int(o["idx"].numel()).bit_length() - 1
@@ -952,7 +956,7 @@ def lu_flush(engine, tr, luq, ledger, R, strict=True):
     out = []
     for tid, subs in supers:
         tab = luq[subs[0][1][0]]["tab"]
-        sg = [(n, [([w[0] for w in luq[j]["W"]], [w[1] for w in luq[j]["W"]], luq[j]["idx"]) for j in mem]) for n, mem in subs]
+        sg = [(n, [([w[0] for w in luq[j]["W"]], [w[1] for w in luq[j]["W"]], luq[j]["idx"], luq[j].get("bind")) for j in mem]) for n, mem in subs]
         pf, claims, _cnt = prove_super(engine, tr, table_columns(engine, tab), tid, sg, R, strict)
         for col, root, pt, y in claims:
             ledger.add(col, root, pt, y)
