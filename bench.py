@@ -711,6 +711,75 @@ def run_suite_layer(args):
         torch.cuda.empty_cache()
 
 
+def run_suite_hwl(args):
+    """--suite-hwl: the fp8 (Hawkeye) matmul gadget (the reference's p3hwl stack, non-zk): witness replay on the GPU,
+    commitments and proof of one fp8-e4m3 matmul with per-row fp32 scales and bf16 output; beside the reference's own
+    gen_witness (host) + prove (CUDA) on the same inputs at the shapes the host can hold."""
+    import torch
+    import zkh_import
+    zk = zkh_import.load()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import Reference
+    from hwl_helpers import layer_inputs, ref_hwl_prove, ref_hwl_verify
+    torch.cuda.set_device(0)
+    prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+    hwl = zk.hwl
+    ref = Reference() if (Reference.available() and not args.no_ref_cuda) else None
+    if ref is not None and not ref.gpu_available():
+        ref = None
+    R, Q = 1, 24
+    T = hwl.build_tables()
+    shapes = {"small": ("fp8 matmul 32x256 . 256x256", (32, 256, 256), True),
+              "mid": ("fp8 matmul 128x256 . 256x256", (128, 256, 256), True),
+              "c1": ("BASELINE configs[0] shape as an fp8 matmul: 128x768 . 768x768", (128, 768, 768), False)}
+    inverse = lambda t: prover.inv_all_add(t.contiguous(), 0)
+    col = lambda t: t
+    for key in args.hwl_shapes.split(","):
+        name, dims, with_ref = shapes[key]
+        inp = layer_inputs(*dims, seed=42)
+        t_wit = None
+        for _ in range(2):                                  # second run: kernels and allocator warm
+            wt = None
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            wt = hwl.gen_witness(*dims, *inp, device="cuda:0", inverse=inverse) if args.hwl_tensor_witness else \
+                hwl.gen_witness_dev(prover, *dims, *inp)
+            torch.cuda.synchronize()
+            t_wit = time.perf_counter() - t0
+        best = None
+        prover.keep_trees = bool(args.hwl_keep_trees)
+        for rep in range(args.layer_reps):
+            prover.release_kept()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            ops = hwl.commit_operands(prover, wt, R, col)
+            tr = zk.Transcript("hwl-layer")
+            pf = hwl.prove(prover, tr, wt, T, ops, R, Q, col)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            best = t1 - t0 if best is None else min(best, t1 - t0)
+        d = wt["d"]
+        line = {"suite": name, "dims": dict(zip(("B", "K", "N"), dims)), "log2_products_padded": d.lp, "R": R, "Q": Q,
+                "witness_device_s": t_wit, "prove_s": best, "proof_MB": len(pf) / 1048576.0,
+                "trees_kept_resident": bool(prover.keep_trees)}
+        roots4 = [ops[k][1] for k in ("X", "W", "XS", "WS")]
+        st0 = zk.Transcript("hwl-layer").state
+        if ref is not None:
+            ok, st = ref_hwl_verify(ref, st0, dims, roots4, wt["Y"], R, Q, pf)
+            line["accepted_by_reference_verifier"] = bool(ok and st == tr.state)
+            if with_ref:
+                rpf, rst, rroots, rY, ms = ref_hwl_prove(ref, st0, dims, inp, R, Q)
+                line.update({"reference_witness_host_s": ms[0] / 1e3, "reference_prove_s": (ms[1] + ms[2]) / 1e3,
+                             "speedup_prove_vs_reference": (ms[1] + ms[2]) / 1e3 / best,
+                             "speedup_witness_vs_reference": ms[0] / 1e3 / t_wit,
+                             "same_proof_bytes": bool(rpf == pf and rst == tr.state)})
+        print(json.dumps(line), flush=True)
+        prover.release_kept()
+        del wt, ops
+        torch.cuda.empty_cache()
+
+
 def run_suite_model(args):
     """--suite-model [--gpus N under torch.distributed.run]: the 22 independent layer proofs of the TinyLlama-shaped
     model (BASELINE configs[4]; one transcript per layer, as the reference's transformer bench proves them) placed
@@ -796,6 +865,10 @@ def main():
     ap.add_argument("--suite-layer", action="store_true", help="one integer decoder layer beside the reference's layer prover")
     ap.add_argument("--layer-shapes", default="c3")
     ap.add_argument("--layer-reps", type=int, default=2)
+    ap.add_argument("--suite-hwl", action="store_true", help="the fp8 (Hawkeye) matmul gadget beside the reference's prover")
+    ap.add_argument("--hwl-shapes", default="small,mid")
+    ap.add_argument("--hwl-keep-trees", action="store_true")
+    ap.add_argument("--hwl-tensor-witness", action="store_true", help="fp8 witness by tensor arithmetic instead of the replay kernel")
     ap.add_argument("--suite-fr", action="store_true", help="BLS12-381 Fr kernels beside the reference's CUDA code")
     ap.add_argument("--fr-logd", type=int, default=22)
     ap.add_argument("--suite-gadgets", action="store_true", help="configs[0]/[2] through the gadget-level provers")
@@ -810,6 +883,8 @@ def main():
         return run_suite_fr(args)
     if args.suite_layer:
         return run_suite_layer(args)
+    if args.suite_hwl:
+        return run_suite_hwl(args)
     if args.suite_model:
         return run_suite_model(args)
     if args.suite_gadgets:

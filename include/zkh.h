@@ -314,6 +314,20 @@ ZKH_API int zkh_gkr_prove(zkh_ctx* ctx, const uint64_t* p_dev, const uint64_t* q
                           const char* tag, uint8_t state[32], uint64_t* rfin, uint64_t cpq[2], uint8_t* out,
                           size_t cap, size_t* written);
 
+/* Witness of the fp8 (Hawkeye) matmul gadget: the exact replay of the fp8 forward pass that p3hwl::gen_witness runs as a host
+ * loop (zkllm-src/p3_hawkeye.cuh:342-637), as one kernel with a warp per output.  Padded grids: 2^lb rows of X, 2^ln rows of
+ * W, 2^lg groups of 32 products (lg covers one phantom group after the last real one), K padded to 32*2^lg.
+ *   xcodes_dev  2^lb * 32*2^lg fp8-e4m3 codes of X as field elements, row-major (zero beyond the real grid)
+ *   wcodes_dev  2^ln * 32*2^lg codes of W;  xsb_dev / wsb_dev: 2^lb / 2^ln fp32 bit patterns of the per-row scales
+ *   cols_dev    99 output columns in the order dp[10] (2^(lb+ln+lg+5) elements each, index ((g*2^(lb+ln) + b*2^ln + n)*32 + kk),
+ *               dg[29] (2^(lb+ln+lg)), dob[46] (2^(lb+ln)), db[6] (2^lb), dn[6] (2^ln), va, vb (product domain): the columns of
+ *               LayerWit in the reference's enum order (p3_hawkeye.cuh:86-101)
+ *   lidx_dev    38 uint32 lookup-index columns in the order of the reference's LU_* enum (p3_hawkeye.cuh:104-112)
+ * A layer outside the gadget's supported domain returns ZKH_ERR_DOMAIN with the message the reference throws. */
+ZKH_API int zkh_hwl_witness(zkh_ctx* ctx, uint32_t lb, uint32_t ln, uint32_t lg, const uint64_t* xcodes_dev,
+                            const uint64_t* wcodes_dev, const uint64_t* xsb_dev, const uint64_t* wsb_dev,
+                            uint64_t* const* cols_dev, uint32_t* const* lidx_dev);
+
 /* Host-side construction of the integer layer's function tables (p3ig::build_tables,
  * zkllm-src/p3_int_gadgets.cuh:99-118): kind 0 EXPT (2^17 rows), 1 SILU (2^20 rows), 2 ISQ (2^16 rows, uses d).
  * col0 / col1: host arrays of that many field elements.  No GPU involved. */

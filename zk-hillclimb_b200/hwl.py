@@ -342,6 +342,36 @@ def gen_witness(B, K, N, x, w, xs, ws, device="cpu", inverse=host_inverse):
             "lidx": [t.reshape(-1).contiguous() for t in lidx], "Y": Y}
 
 
+
+def gen_witness_dev(engine, B, K, N, x, w, xs, ws):
+    """The same witness from the CUDA replay kernel (zkh_hwl_witness: one warp per output, lane = product of the group):
+    columns are allocated on the engine's GPU and filled in one pass.  Same result dict as gen_witness."""
+    d = Dims(B, K, N)
+    dev = torch.device("cuda:%d" % engine.device)
+    I = torch.int64
+    xc, wc = torch.zeros(d.Bpad, d.Kpad, dtype=I, device=dev), torch.zeros(d.Npad, d.Kpad, dtype=I, device=dev)
+    xc[:B, :K] = torch.as_tensor(np.asarray(x, dtype=np.uint8).reshape(B, K).astype(np.int64), device=dev)
+    wc[:N, :K] = torch.as_tensor(np.asarray(w, dtype=np.uint8).reshape(N, K).astype(np.int64), device=dev)
+    xsb, wsb = torch.zeros(d.Bpad, dtype=I, device=dev), torch.zeros(d.Npad, dtype=I, device=dev)
+    xsb[:B] = torch.as_tensor(np.asarray(xs, dtype=np.uint32).astype(np.int64), device=dev)
+    wsb[:N] = torch.as_tensor(np.asarray(ws, dtype=np.uint32).astype(np.int64), device=dev)
+    new = lambda n, dt=I: torch.empty(n, dtype=dt, device=dev)
+    dp, dg, dob = [new(d.P) for _ in range(NDP)], [new(d.G) for _ in range(NDG)], [new(d.Opad) for _ in range(NDO)]
+    db, dn = [new(d.Bpad) for _ in range(NDS)], [new(d.Npad) for _ in range(NDS)]
+    va, vb = new(d.P), new(d.P)
+    sizes = [d.P] * 4 + [d.G] * 12 + [d.Opad] * 16 + [d.Bpad] * 3 + [d.Npad] * 3
+    lidx = [new(n, torch.int32) for n in sizes]
+    try:
+        engine.hwl_witness(d.lb, d.ln, d.lg, xc, wc, xsb, wsb, dp + dg + dob + db + dn + [va, vb], lidx)
+    except Exception as e:
+        if "hwl:" in str(e):
+            raise WitnessError(str(e)[str(e).index("hwl:"):]) from None
+        raise
+    Y = dob[O_YB].view(d.Bpad, d.Npad)[:B, :N].to(torch.int32).cpu().numpy().astype(np.uint16).reshape(-1)
+    return {"d": d, "xcodes": xc.reshape(-1), "wcodes": wc.reshape(-1), "xsb": xsb, "wsb": wsb, "dp": dp, "dg": dg, "dob": dob,
+            "db": db, "dn": dn, "va": va, "vb": vb, "lidx": lidx, "Y": Y}
+
+
 def zx_point(d, rA):
     """p3hwl::zx_point (p3_hawkeye.cuh:1856-1862): product-domain point [kk | n | b | g] -> X's point [kk | g | b]."""
     rA = [int(v) for v in rA]

@@ -333,6 +333,13 @@ class Prover:
                                          _ptr(iY) if rng else 0))
         return y, L, iL, iY
 
+    def hwl_witness(self, lb, ln, lg, xcodes, wcodes, xsb, wsb, cols, lidx):
+        """p3hwl::gen_witness (zkllm-src/p3_hawkeye.cuh:342-637) as one kernel: fills the 99 field columns and the 38
+        lookup-index columns (preallocated tensors, reference enum order) from the padded operand columns."""
+        pc = (C.c_uint64 * len(cols))(*[_ptr(t) for t in cols])
+        pl = (C.c_uint64 * len(lidx))(*[_ptr(t) for t in lidx])
+        self._ck(self._L.zkh_hwl_witness(self._h, lb, ln, lg, _ptr(xcodes), _ptr(wcodes), _ptr(xsb), _ptr(wsb), pc, pl))
+
     def upload(self, arr):
         return to_device(arr, "cuda:%d" % self.device)
 
