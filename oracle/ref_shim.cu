@@ -24,6 +24,7 @@
 #include "p3_hawkeye.cuh"
 #include "p3_int_gadgets.cuh"
 #include "p3_int_layer.cuh"
+#include "p3_swiglu.cuh"
 
 namespace {
 fs::Transcript tr_from(const uint8_t st[32]) {
@@ -758,6 +759,21 @@ p3hwl::Golden hwl_golden(uint32_t B, uint32_t K, uint32_t N, const uint8_t* x, c
     L.xs.assign(xs, xs + B); L.ws.assign(ws, ws + N);
     L.y.assign((size_t)B * N, 0);
     return L;
+}
+// ---- bf16 gadgets of the fp8 transformer layer: the pinned table artefact and per-gadget proof walks ----
+p3rms::Art& tf_art() { static p3rms::Art a; return a; }
+// p3swg::SwgProof <-> bytes: u32 n | rws[14] | u32 groups (len, GroupProof)* | mE | yE[14] yUP yM | u32 batches (len, BatchProof)*
+template <typename IO>
+void swg_walk(IO& io, p3swg::SwgProof& pf) {
+    io.u32(pf.n);
+    for (int c = 0; c < p3swg::NDS; c++) io.raw(pf.rws[c].data(), 32);
+    io.groups(pf.lug);
+    io.msgs(pf.mE); io.raw(pf.yE, sizeof pf.yE); io.raw(&pf.yUP, 8); io.raw(&pf.yM, 8);
+    io.batches(pf.batches);
+}
+const p3swg::Tables& swg_tables() {
+    static p3swg::Tables T = p3swg::build_tables(tf_art());
+    return T;
 }
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
 const p3ig::Tables& ig_tables(uint32_t d, uint32_t btop) {
@@ -1776,6 +1792,53 @@ int ref_hwl_verify(uint8_t st[32], uint32_t B, uint32_t K, uint32_t N, const uin
     } catch (...) { ok = 0; }
     memcpy(st, tr.state, 32);
     return ok;
+}
+
+// ---- bf16 gadgets of the fp8 transformer layer ----
+// load the pinned table artefact (the file p3rms::load_art reads); call once before any gadget entry point below
+int ref_tf_load_art(const char* path) { return p3rms::load_art(path, tf_art()) ? 1 : 0; }
+// p3swg::verify (host only)
+int ref_swg_verify(uint8_t st[32], const uint8_t* rG, const uint8_t* rU, const uint8_t* rM, uint32_t n, uint32_t R, uint32_t Q,
+                   const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3swg::SwgProof pf;
+        HwlReader rd{proof, proof + len};
+        swg_walk(rd, pf);
+        if (rd.ok && rd.p == rd.end) {
+            p3fri::Hash h[3];
+            memcpy(h[0].data(), rG, 32); memcpy(h[1].data(), rU, 32); memcpy(h[2].data(), rM, 32);
+            ok = p3swg::verify(tr, swg_tables(), pf, h[0], h[1], h[2], n, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
+}
+// p3swg: gen_witness + commit_operands + prove; roots3_out: GATE UP M roots; M_out: n bf16 patterns
+size_t ref_swg_prove(uint8_t st[32], const uint16_t* gate, const uint16_t* up, uint32_t n, uint32_t R, uint32_t Q, int gpu,
+                     uint8_t* roots3_out, uint16_t* M_out, uint8_t* out, size_t cap) {
+    p3fri::g_gpu_merkle = gpu != 0;
+    if (gpu) p3bf::p3_enable_mempool();
+    fs::Transcript tr = tr_from(st);
+    size_t w = 0;
+    try {
+        p3swg::Golden L; L.n = n; L.gate.assign(gate, gate + n); L.up.assign(up, up + n); L.m.assign(n, 0);
+        p3swg::Wit wt = p3swg::gen_witness(L, tf_art());
+        p3swg::Operands ops = p3swg::commit_operands(wt, R);
+        auto pf = p3swg::prove(tr, wt, swg_tables(), ops, R, Q);
+        if (roots3_out) {
+            memcpy(roots3_out, ops.GATE.root.data(), 32); memcpy(roots3_out + 32, ops.UP.root.data(), 32);
+            memcpy(roots3_out + 64, ops.M.root.data(), 32);
+        }
+        if (M_out) memcpy(M_out, wt.M.data(), (size_t)n * 2);
+        HwlWriter wr;
+        swg_walk(wr, pf);
+        w = emit(wr.b, out, cap);
+    } catch (...) { w = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return w;
 }
 
 }  // extern "C"

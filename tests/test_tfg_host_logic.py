@@ -1,0 +1,66 @@
+"""bf16 gadgets of the fp8 transformer layer through the host logic in zk_hillclimb_b200.tfg on CPU: the pinned table
+artefact equals the reference generator's, and every gadget's proof is accepted by the reference's host-only verifier."""
+import hashlib
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from hwl_helpers import host_col
+from ig_helpers import OracleGadgetEngine
+from tfg_helpers import bf16_patterns, load_art, ref_swg_verify
+
+ART_LD6_SHA256 = "72ca8b6045cf1ff65d2386e6026884b3d9e2759c7c69cd5298f8e61ae8583223"
+
+
+def test_artefact_digest(zk):
+    """The ld = 6 artefact file (the bytes the reference's loader reads) is pinned by its digest."""
+    assert hashlib.sha256(zk.tfart.art_bytes(zk.tfart.build_art(6))).hexdigest() == ART_LD6_SHA256
+
+
+def test_artefact_equals_reference_generator(zk):
+    """Where the reference tree is present, its own Python generator gives the same tables."""
+    src = "/root/reference/zkllm-src"
+    if not os.path.exists(os.path.join(src, "transformer_ref.py")):
+        pytest.skip("reference tree not present")
+    sys.path.insert(0, src)
+    try:
+        import contextlib
+        import io
+        with contextlib.redirect_stdout(io.StringIO()):
+            import transformer_ref as R
+    finally:
+        sys.path.remove(src)
+    art = zk.tfart.build_art(6)
+    for k, ref in (("mul_mo", R.MUL_MO), ("mul_einc", R.MUL_EINC), ("rsq_mr", R.RSQ_MR), ("rsq_hb", R.RSQ_HB), ("rcp_mr", R.RCP_MR),
+                   ("rcp_hb", R.RCP_HB), ("exp_tab", R.EXP_TAB), ("silu_tab", R.SILU_TAB), ("qe4m3", R.QE4M3)):
+        assert (np.asarray(art[k]).astype(np.int64) == np.asarray(ref).astype(np.int64)).all(), k
+    for ld in (4, 7, 11):
+        emin, epsa = R.epsa_table(ld)
+        a = zk.tfart.build_art(ld)
+        assert emin == a["EMIN"] and (epsa == a["epsa"]).all()
+
+
+@pytest.mark.parametrize("ln", [1, 5])
+def test_swiglu_accepted_by_reference_verifier(orc, ref, zk, ln):
+    R, Q = 1, 24
+    tfg = zk.tfg
+    art = load_art(ref, zk)
+    T = tfg.swg_tables(art)
+    rng = np.random.default_rng(ln)
+    gate, up = bf16_patterns(rng, 1 << ln, 2.0), bf16_patterns(rng, 1 << ln, 1.0)
+    wt = tfg.swg_witness(gate, up, art)
+    eng = OracleGadgetEngine(orc)
+    ops = tfg.swg_commit_operands(eng, wt, R, host_col)
+    tr = zk.Transcript("swg")
+    pf = tfg.swg_prove(eng, tr, wt, T, ops, R, Q, host_col)
+    roots3 = [ops[k][1] for k in ("GATE", "UP", "M")]
+    st0 = zk.Transcript("swg").state
+    ok, st = ref_swg_verify(ref, st0, roots3, 1 << ln, R, Q, pf)
+    assert ok and st == tr.state
+    assert not ref_swg_verify(ref, st0, roots3[1:] + roots3[:1], 1 << ln, R, Q, pf)[0]
+    for off in (40, len(pf) // 2, len(pf) - 9):
+        bad = bytearray(pf)
+        bad[off] ^= 1
+        assert not ref_swg_verify(ref, st0, roots3, 1 << ln, R, Q, bytes(bad))[0]

@@ -686,10 +686,10 @@ def _ser_gkr_group(m, c, root_cnt, gkT, subs):
     b = struct.pack("<III", m, c, len(subs)) + root_cnt + gkT
     for n, k, gk, mem in subs:
         b += struct.pack("<II", n, k) + gk
-        for yW, yv in mem:
+        for yW, yv, extra in mem:
             b += struct.pack("<I", len(yW)) + np.array(yW, dtype=np.uint64).tobytes()
             b += struct.pack("<I", len(yv)) + np.array(yv, dtype=np.uint64).tobytes()
-            b += struct.pack("<I", 0)
+            b += struct.pack("<I", len(extra)) + np.array(extra, dtype=np.uint64).tobytes()
     return b
 
 
@@ -702,7 +702,8 @@ def prove_super(engine, tr, table_cols, table_id, subgroups, R, strict=True):
     (cols, roots, idx) with c witness columns of 2^n rows, their commitment roots (None for a
     virtual column) and the uint32 row indices into the table; an optional fourth element is the member's bind
     callback (p3lu::PBind, p3_logup.cuh:451-456): called as bind(pm, y_virt) after the member's own claims, it returns
-    further opening claims (column, root, point, value) that tie the virtual columns to commitments.
+    further opening claims (column, root, point, value) that tie the virtual columns to commitments, or a pair
+    (claims, extra) when values ride in the proof (LuMember::extra).
     Returns (proof bytes, claims, cnt column).  claims = the opening-ledger additions in the
     reference's order: (column, root, point, value) for every committed member column at the
     subgroup's shared point, then the multiplicity column at the table-side point.
@@ -758,9 +759,13 @@ def prove_super(engine, tr, table_cols, table_id, subgroups, R, strict=True):
                 else:
                     yv.append(y)
                     tr.absorb("lug-yv", struct.pack("<Q", y))
+            extra = []
             if bind and bind[0] is not None:
-                claims.extend(bind[0](pm, yv))
-            mem.append((yW, yv))
+                more = bind[0](pm, yv)
+                if isinstance(more, tuple):       # (claims, values that ride in the proof as LuMember::extra)
+                    more, extra = more
+                claims.extend(more)
+            mem.append((yW, yv, extra))
         subs.append((n, k, gk, mem))
     LQT = engine.affine(table_cols, gamma, beta)
     gkT, rT, (cpT, _cq) = engine.gkr_prove(tr, "lug-gT", cnt, LQT, True)
