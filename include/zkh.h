@@ -152,8 +152,10 @@ ZKH_API int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* const* 
  * the shape of the integer-layer gadgets' constraint polynomials (zkllm-src/p3_int_gadgets.cuh:326, :726,
  * :977-1035, :1307, :1563-1640, :1818), which the reference proves with its host loop p3hwl::sc5_prove
  * (non-zk path of sc5z).  Five evaluations per round (Msg5), absorbed under `tag`.
- * prog: word 0 = number of terms (<= 120), word 1 = konst, then per term two words: coefficient,
- * degree | idx0 << 8 | idx1 << 16 | idx2 << 24.  nwords = 2 + 2*terms.  1 <= nc <= 32. */
+ * prog: word 0 = number of terms (<= 2048), word 1 = konst, then per term two words: coefficient,
+ * degree | idx0 << 8 | idx1 << 16 | idx2 << 24.  nwords = 2 + 2*terms.  1 <= nc <= 224.
+ * Programs of more than 32 columns or 120 terms (the bf16 gadgets of the fp8 transformer layer, zkllm-src/p3_bfadd.cuh:
+ * 214-330, p3_swiglu.cuh:172-207 and siblings) run on a variant that keeps the column values in shared memory. */
 ZKH_API int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
                            const uint64_t* prog, int nwords, const char* tag, uint8_t state[32], uint64_t* msgs,
                            uint64_t* chals, uint64_t* finals);

@@ -25,6 +25,7 @@
 #include "p3_int_gadgets.cuh"
 #include "p3_int_layer.cuh"
 #include "p3_swiglu.cuh"
+#include "p3_bfadd.cuh"
 
 namespace {
 fs::Transcript tr_from(const uint8_t st[32]) {
@@ -773,6 +774,19 @@ void swg_walk(IO& io, p3swg::SwgProof& pf) {
 }
 const p3swg::Tables& swg_tables() {
     static p3swg::Tables T = p3swg::build_tables(tf_art());
+    return T;
+}
+// p3bfa::BfaProof <-> bytes: u32 n | rws[55] | groups | mE | yE[55] yX1 yX2 yOUT | batches
+template <typename IO>
+void bfa_walk(IO& io, p3bfa::BfaProof& pf) {
+    io.u32(pf.n);
+    for (int c = 0; c < p3bfa::NBA; c++) io.raw(pf.rws[c].data(), 32);
+    io.groups(pf.lug);
+    io.msgs(pf.mE); io.raw(pf.yE, sizeof pf.yE); io.raw(&pf.yX1, 8); io.raw(&pf.yX2, 8); io.raw(&pf.yOUT, 8);
+    io.batches(pf.batches);
+}
+const p3bfa::Tables& bfa_tables() {
+    static p3bfa::Tables T = p3bfa::build_tables();
     return T;
 }
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
@@ -1834,6 +1848,50 @@ size_t ref_swg_prove(uint8_t st[32], const uint16_t* gate, const uint16_t* up, u
         if (M_out) memcpy(M_out, wt.M.data(), (size_t)n * 2);
         HwlWriter wr;
         swg_walk(wr, pf);
+        w = emit(wr.b, out, cap);
+    } catch (...) { w = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return w;
+}
+
+// p3bfa::verify (host only)
+int ref_bfa_verify(uint8_t st[32], const uint8_t* r1, const uint8_t* r2, const uint8_t* ro, uint32_t n, uint32_t R, uint32_t Q,
+                   const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3bfa::BfaProof pf;
+        HwlReader rd{proof, proof + len};
+        bfa_walk(rd, pf);
+        if (rd.ok && rd.p == rd.end) {
+            p3fri::Hash h[3];
+            memcpy(h[0].data(), r1, 32); memcpy(h[1].data(), r2, 32); memcpy(h[2].data(), ro, 32);
+            ok = p3bfa::verify(tr, bfa_tables(), pf, h[0], h[1], h[2], n, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
+}
+// p3bfa: gen_witness + commit_operands + prove; roots3_out: X1 X2 OUT roots; O_out: n bf16 patterns
+size_t ref_bfa_prove(uint8_t st[32], const uint16_t* a, const uint16_t* b, uint32_t n, uint32_t R, uint32_t Q, int gpu,
+                     uint8_t* roots3_out, uint16_t* O_out, uint8_t* out, size_t cap) {
+    p3fri::g_gpu_merkle = gpu != 0;
+    if (gpu) p3bf::p3_enable_mempool();
+    fs::Transcript tr = tr_from(st);
+    size_t w = 0;
+    try {
+        p3bfa::Golden L; L.n = n; L.a.assign(a, a + n); L.b.assign(b, b + n); L.o.assign(n, 0);
+        p3bfa::Wit wt = p3bfa::gen_witness(L);
+        p3bfa::Operands ops = p3bfa::commit_operands(wt, R);
+        auto pf = p3bfa::prove(tr, wt, bfa_tables(), ops, R, Q);
+        if (roots3_out) {
+            memcpy(roots3_out, ops.X1.root.data(), 32); memcpy(roots3_out + 32, ops.X2.root.data(), 32);
+            memcpy(roots3_out + 64, ops.OUT.root.data(), 32);
+        }
+        if (O_out) memcpy(O_out, wt.O.data(), (size_t)n * 2);
+        HwlWriter wr;
+        bfa_walk(wr, pf);
         w = emit(wr.b, out, cap);
     } catch (...) { w = 0; }
     p3fri::g_gpu_merkle = false;

@@ -9,7 +9,7 @@ import pytest
 
 from hwl_helpers import host_col
 from ig_helpers import OracleGadgetEngine
-from tfg_helpers import bf16_patterns, load_art, ref_swg_verify
+from tfg_helpers import bf16_add_cases, bf16_patterns, load_art, ref_swg_verify, ref_verify3
 
 ART_LD6_SHA256 = "72ca8b6045cf1ff65d2386e6026884b3d9e2759c7c69cd5298f8e61ae8583223"
 
@@ -64,3 +64,34 @@ def test_swiglu_accepted_by_reference_verifier(orc, ref, zk, ln):
         bad = bytearray(pf)
         bad[off] ^= 1
         assert not ref_swg_verify(ref, st0, roots3, 1 << ln, R, Q, bytes(bad))[0]
+
+
+def _bf16_add_numpy(a, b):
+    """float32 addition of bf16 values rounded back to bf16 (RNE): an independent check of the replay on in-domain rows"""
+    fa = (a.astype(np.uint32) << 16).view(np.float32)
+    fb = (b.astype(np.uint32) << 16).view(np.float32)
+    s = (fa + fb).view(np.uint32).astype(np.uint64)
+    return ((s + 0x7FFF + ((s >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+@pytest.mark.parametrize("ln", [1, 6])
+def test_bf16_add_accepted_by_reference_verifier(orc, ref, zk, ln):
+    R, Q = 1, 24
+    tfg = zk.tfg
+    T = tfg.bfa_tables()
+    a, b = bf16_add_cases(np.random.default_rng(10 + ln), 1 << ln)
+    wt = tfg.bfa_witness(a, b)
+    both = ((a & 0x7F80) != 0) & ((b & 0x7F80) != 0) & ((wt["O"] & 0x7F80) != 0)      # no flushed operands / results
+    assert (wt["O"][both] == _bf16_add_numpy(a, b)[both]).all()
+    eng = OracleGadgetEngine(orc)
+    ops = tfg.bfa_commit_operands(eng, wt, R, host_col)
+    tr = zk.Transcript("bfa")
+    pf = tfg.bfa_prove(eng, tr, wt, T, ops, R, Q, host_col)
+    roots3 = [ops[k][1] for k in ("X1", "X2", "OUT")]
+    st0 = zk.Transcript("bfa").state
+    ok, st = ref_verify3(ref, "ref_bfa_verify", st0, roots3, 1 << ln, R, Q, pf)
+    assert ok and st == tr.state
+    assert not ref_verify3(ref, "ref_bfa_verify", st0, roots3[::-1], 1 << ln, R, Q, pf)[0]
+    bad = bytearray(pf)
+    bad[len(pf) // 2] ^= 1
+    assert not ref_verify3(ref, "ref_bfa_verify", st0, roots3, 1 << ln, R, Q, bytes(bad))[0]

@@ -31,6 +31,37 @@ def test_matches_python_evaluation(orc, zk, prover, name, logn):
     assert st == tr.state and (m == m0).all() and (r == r0).all() and (fin == f0).all()
 
 
+def _large_program(nc, nterms, seed):
+    rng = np.random.default_rng(seed)
+    terms = []
+    for _ in range(nterms):
+        deg = int(rng.integers(1, 4))
+        terms.append((int(rng.integers(1, GL_P)), tuple(int(x) for x in rng.integers(0, nc, size=deg))))
+    return terms
+
+
+@pytest.mark.parametrize("nc,nterms,logn", [(40, 100, 1), (59, 400, 6), (33, 10, 9), (130, 900, 5), (224, 2048, 3), (20, 300, 7)])
+def test_large_programs_match_python_evaluation(orc, zk, prover, nc, nterms, logn):
+    """More than 32 columns or 120 terms: the shared-memory variant (the bf16 gadgets' constraint systems)."""
+    terms = _large_program(nc, nterms, nc + nterms)
+    cols = lcg_cols(orc, 1 << logn, nc, 7 * nc + logn)
+    tr = zk.Transcript("zc")
+    r, m, fin = prover.sc_prove_zc(tr, "bfa-scE", [zk.p3.to_device(c) for c in cols], terms, 12345)
+    st, m0, r0, f0 = zc_sumcheck(orc, orc.tr_init("zc"), "bfa-scE", cols, terms, 12345)
+    assert st == tr.state and (m == m0).all() and (r == r0).all() and (fin == f0).all()
+
+
+def test_large_program_equals_small_engine(orc, zk, prover):
+    """The same 30-column program through both variants (the second padded with a zero-coefficient term count > 120)."""
+    nc, logn = 30, 13
+    terms = _large_program(nc, 100, 5)
+    cols = [zk.p3.to_device(c) for c in lcg_cols(orc, 1 << logn, nc, 77)]
+    tr1, tr2 = zk.Transcript("zc"), zk.Transcript("zc")
+    a = prover.sc_prove_zc(tr1, "t", cols, terms, 9)
+    b = prover.sc_prove_zc(tr2, "t", cols, terms + [(0, (1,))] * 30, 9)
+    assert tr1.state == tr2.state and all((x == y).all() for x, y in zip(a, b))
+
+
 @pytest.mark.parametrize("nl", [1, 2])
 def test_matches_compiled_rescale_summand(orc, zk, prover, nl):
     logn = 15

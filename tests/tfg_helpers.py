@@ -51,3 +51,38 @@ def ref_swg_prove(ref, st, gate, up, R, Q, gpu=True):
     w = f(s, _vp(g), _vp(u), C.c_uint32(n), C.c_uint32(R), C.c_uint32(Q), int(gpu), roots, _vp(M), out, C.c_size_t(cap))
     rb = bytes(roots)
     return bytes(out[:w]), bytes(s), [rb[i * 32:(i + 1) * 32] for i in range(3)], M
+
+
+def ref_verify3(ref, fn, st, roots3, n, R, Q, proof):
+    """ref_swg_verify / ref_bfa_verify: three operand roots and the element count."""
+    s = (C.c_uint8 * 32)(*st)
+    ok = getattr(ref.lib, fn)(s, roots3[0], roots3[1], roots3[2], C.c_uint32(n), C.c_uint32(R), C.c_uint32(Q), bytes(proof),
+                              C.c_size_t(len(proof)))
+    return bool(ok), bytes(s)
+
+
+def ref_prove2(ref, fn, st, a, b, R, Q, gpu=True):
+    """ref_swg_prove / ref_bfa_prove: two bf16 input arrays -> (proof, state, three roots, output patterns)."""
+    s = (C.c_uint8 * 32)(*st)
+    n = len(a)
+    cap = 128 << 20
+    out, roots, O = (C.c_uint8 * cap)(), (C.c_uint8 * 96)(), np.zeros(n, dtype=np.uint16)
+    f = getattr(ref.lib, fn)
+    f.restype = C.c_size_t
+    a, b = np.ascontiguousarray(a, dtype=np.uint16), np.ascontiguousarray(b, dtype=np.uint16)
+    w = f(s, _vp(a), _vp(b), C.c_uint32(n), C.c_uint32(R), C.c_uint32(Q), int(gpu), roots, _vp(O), out, C.c_size_t(cap))
+    rb = bytes(roots)
+    return bytes(out[:w]), bytes(s), [rb[i * 32:(i + 1) * 32] for i in range(3)], O
+
+
+def bf16_add_cases(rng, n):
+    """bf16 pairs covering the add gadget's branches: near/far exponent gaps, cancellation, zeros, equal exponents."""
+    a = bf16_patterns(rng, n, 1.0)
+    b = bf16_patterns(rng, n, 1.0)
+    k = n // 8
+    if k:
+        b[:k] = a[:k] ^ 0x8000                                   # exact cancellation
+        b[k:2 * k] = a[k:2 * k]                                   # doubling
+        b[2 * k:3 * k] = bf16_patterns(rng, k, 1e-4)              # far addend
+        b[3 * k:4 * k] = (a[3 * k:4 * k] & 0xFF80) | rng.integers(0, 128, size=k).astype(np.uint16)   # same binade
+    return a, b

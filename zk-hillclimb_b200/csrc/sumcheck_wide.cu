@@ -12,6 +12,7 @@
 // A thread keeps one pair of every column (value and difference) in registers; at 57 columns the
 // compiler spills part of that to local memory, which stays in L1.  These kernels are bound by the
 // integer pipe (tens of field multiplications per row and evaluation point), not by HBM.
+#include <vector>
 #include "sumcheck.cuh"
 #include "hawkeye_fn.cuh"
 
@@ -235,6 +236,125 @@ static int zc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t lo
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "zero-check sumcheck launch");
 }
 
+// Large programs (more than 32 columns or 120 terms: the bf16 gadgets of the fp8 transformer layer, whose constraint
+// systems span 60..200 columns and several hundred monomials; the reference runs them through its host loop sc5_prove,
+// zkllm-src/p3_bfadd.cuh:214-330 and siblings).  Same summand shape; the program, the current value and the difference of
+// every column live in dynamic shared memory ([column][thread], conflict-free), the column pointers of the round in
+// global memory.  Block size shrinks as the column count grows so that one block always fits an SM.
+constexpr int ZCX_MAXTERMS = 2048;
+constexpr int ZCX_MAXC = 224;
+struct ZcxHdr { uint32_t nterms, nc; gl_t konst; };
+
+__global__ void zcx_round_kernel(const uint8_t* prog_g, const gl_t* const* in, gl_t* const* out, size_t items, int first,
+                                 ZkhCtl* ctl, gl_t* partials, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, ZkhTag tag) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const ZcxHdr hdr = *reinterpret_cast<const ZcxHdr*>(prog_g);
+    const uint32_t nc = hdr.nc, nterms = hdr.nterms, T = blockDim.x, tid = threadIdx.x;
+    gl_t* coef = reinterpret_cast<gl_t*>(smem);
+    gl_t* cur = coef + nterms;                 // [nc][T]
+    gl_t* dif = cur + (size_t)nc * T;          // [nc][T]
+    gl_t* sh = dif + (size_t)nc * T;           // SCW_NT * 32
+    uint32_t* packed = reinterpret_cast<uint32_t*>(sh + SCW_NT * 32);
+    const gl_t* coef_g = reinterpret_cast<const gl_t*>(prog_g + sizeof(ZcxHdr));
+    const uint32_t* packed_g = reinterpret_cast<const uint32_t*>(coef_g + nterms);
+    for (uint32_t j = tid; j < nterms; j += T) { coef[j] = coef_g[j]; packed[j] = packed_g[j]; }
+    __syncthreads();
+    const gl_t a = first ? 0 : *chal_prev;
+    gl_t s[SCW_NT];
+#pragma unroll
+    for (int t = 0; t < SCW_NT; t++) s[t] = 0;
+    const size_t stride = (size_t)gridDim.x * T;
+    for (size_t i = (size_t)blockIdx.x * T + tid; i < items; i += stride) {
+        for (uint32_t k = 0; k < nc; k++) {
+            const gl_t* src = in[k];
+            gl_t lo, hi;
+            if (first) {
+                ulonglong2 v = ld2(src + 2 * i);
+                lo = v.x; hi = v.y;
+            } else {
+                ulonglong2 u = ld2(src + 4 * i), w = ld2(src + 4 * i + 2);
+                lo = gl_lerp(u.x, u.y, a); hi = gl_lerp(w.x, w.y, a);
+                st2(out[k] + 2 * i, lo, hi);
+            }
+            cur[(size_t)k * T + tid] = lo;
+            dif[(size_t)k * T + tid] = gl_sub(hi, lo);
+        }
+#pragma unroll 1
+        for (int t = 0; t < SCW_NT; t++) {
+            Acc192 acc;
+            acc.clear();
+            for (uint32_t j = 0; j < nterms; j++) {
+                const uint32_t pk = packed[j];
+                gl_t x = cur[(size_t)((pk >> 8) & 0xff) * T + tid];
+                if ((pk & 0xff) >= 2) x = gl_mul(x, cur[(size_t)((pk >> 16) & 0xff) * T + tid]);
+                if ((pk & 0xff) >= 3) x = gl_mul(x, cur[(size_t)((pk >> 24) & 0xff) * T + tid]);
+                acc.add_prod(coef[j], x);
+            }
+            s[t] = gl_add(s[t], gl_mul(cur[tid], gl_add(acc.reduce(), hdr.konst)));
+            if (t + 1 < SCW_NT)
+                for (uint32_t k = 0; k < nc; k++) cur[(size_t)k * T + tid] = gl_add(cur[(size_t)k * T + tid], dif[(size_t)k * T + tid]);
+        }
+    }
+    grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, 0);
+}
+
+__global__ void zcx_finals_kernel(const gl_t* const* in, int nc, const gl_t* chal, gl_t* out) {
+    for (int k = threadIdx.x; k < nc; k += blockDim.x) out[k] = gl_lerp(in[k][0], in[k][1], *chal);
+}
+
+static size_t zcx_smem_bytes(int nc, uint32_t nterms, int T) {
+    return (size_t)nterms * 8 + (size_t)2 * nc * T * 8 + SCW_NT * 32 * 8 + (size_t)nterms * 4 + 16;
+}
+
+// prog_dev: ZcxHdr | coef | packed (already uploaded); ptr_dev: room for logn * 2 * nc pointers
+static int zcx_enqueue(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t nterms, uint32_t logn, const uint8_t* prog_dev,
+                       const gl_t** ptr_dev, const ZkhTag& tag, gl_t* finals_dev) {
+    cudaStream_t s = ctx->stream;
+    ZkhCtl* ctl = ctx->d_ctl;
+    const size_t n = (size_t)1 << logn;
+    int T = 128;
+    while (T > 32 && zcx_smem_bytes(nc, nterms, T) > 200 * 1024) T >>= 1;
+    const size_t smem = zcx_smem_bytes(nc, nterms, T);
+    if (smem > 220 * 1024) return zkh_fail(ctx, ZKH_ERR_LIMIT, "zero-check: program does not fit shared memory");
+    if (cudaFuncSetAttribute(zcx_round_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return zkh_fail(ctx, ZKH_ERR_CUDA, "zero-check: shared memory attribute");
+    auto grid_for = [&](size_t items) {
+        size_t want = (items + T - 1) / T, cap = (size_t)ctx->sm_count;
+        if (cap > ctx->partials_cap / SCW_NT) cap = ctx->partials_cap / SCW_NT;
+        return (unsigned)(want < cap ? want : cap);
+    };
+    // pointer tables of every round: round r reads table 2r, writes table 2r+1
+    std::vector<const gl_t*> tab((size_t)logn * 2 * nc, nullptr);
+    gl_t* bufA = (gl_t*)ctx->ws;
+    gl_t* bufB = (gl_t*)((char*)ctx->ws + zkh_align((size_t)nc * (n / 2 + 1) * 8));
+    gl_t* dst = bufA;
+    size_t cur_n = n;
+    for (int k = 0; k < nc; k++) tab[k] = in[k];
+    for (uint32_t r = 1; r < logn; r++) {
+        const size_t out_n = cur_n / 2;
+        for (int k = 0; k < nc; k++) {
+            tab[((size_t)2 * r + 1) * nc + k] = dst + (size_t)k * out_n;
+            tab[((size_t)2 * r) * nc + k] = r == 1 ? in[k] : tab[((size_t)2 * (r - 1) + 1) * nc + k];
+        }
+        dst = (dst == bufA) ? bufB : bufA;
+        cur_n = out_n;
+    }
+    ZKH_CUDA(ctx, cudaMemcpyAsync(ptr_dev, tab.data(), tab.size() * sizeof(void*), cudaMemcpyHostToDevice, s));
+    ZKH_CUDA(ctx, cudaStreamSynchronize(s));      // tab is a host temporary
+    zcx_round_kernel<<<grid_for(n / 2), T, smem, s>>>(prog_dev, ptr_dev, nullptr, n / 2, 1, ctl, ctx->d_partials, nullptr,
+                                                     ctl->msgs, ctl->chals, tag);
+    cur_n = n;
+    for (uint32_t r = 1; r < logn; r++) {
+        zcx_round_kernel<<<grid_for(cur_n / 4), T, smem, s>>>(
+            prog_dev, ptr_dev + ((size_t)2 * r) * nc, (gl_t* const*)(ptr_dev + ((size_t)2 * r + 1) * nc), cur_n / 4, 0, ctl,
+            ctx->d_partials, ctl->chals + (r - 1), ctl->msgs + (size_t)r * SCW_NT, ctl->chals + r, tag);
+        cur_n /= 2;
+    }
+    const gl_t** last = logn == 1 ? ptr_dev : ptr_dev + ((size_t)2 * (logn - 1) + 1) * nc;
+    zcx_finals_kernel<<<1, 256, 0, s>>>(last, nc, ctl->chals + (logn - 1), finals_dev);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "zero-check sumcheck launch");
+}
+
 static int scw_shape(int functor, int* nc, int* nlam) {
 #define CASE(F) if (functor == F) { *nc = WFn<F>::NC; *nlam = WFn<F>::NLAM; return 1; }
     CASE(ZKH_F_HW_DP) CASE(ZKH_F_HW_DG) CASE(ZKH_F_HW_CH) CASE(ZKH_F_HW_GS) CASE(ZKH_F_HW_DS) CASE(ZKH_F_HW_DO)
@@ -303,45 +423,64 @@ extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_
                                       uint64_t* chals, uint64_t* finals) {
     if (!ctx) return ZKH_ERR_ARG;
     if (!cols_dev || !prog || !tag || !state || !msgs || !chals) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: null pointer");
-    if (nc < 1 || nc > 32) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: 1..32 columns");
+    if (nc < 1 || nc > ZCX_MAXC) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: 1..224 columns");
     if (logn < 1 || logn > 34) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: logn must be 1..34");
     if (strlen(tag) > ZKH_TR_MAX_LABEL) return zkh_fail(ctx, ZKH_ERR_LIMIT, "zero-check: tag longer than 48 bytes");
-    if (nwords < 2 || prog[0] > ZC_MAXTERMS || (uint64_t)nwords != 2 + 2 * prog[0])
-        return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: malformed program (at most 120 terms)");
-    static ZkhZcProg hp;   // staging copy; calls on one context are serial
-    memset(&hp, 0, sizeof hp);
-    hp.nterms = (uint32_t)prog[0];
-    hp.nc = (uint32_t)nc;
-    hp.konst = prog[1];
-    if (hp.konst >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: constant not canonical");
-    for (uint32_t j = 0; j < hp.nterms; j++) {
+    if (nwords < 2 || prog[0] > ZCX_MAXTERMS || (uint64_t)nwords != 2 + 2 * prog[0])
+        return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: malformed program (at most 2048 terms)");
+    const uint32_t nterms = (uint32_t)prog[0];
+    const bool large = nc > 32 || nterms > ZC_MAXTERMS;
+    if (prog[1] >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: constant not canonical");
+    static ZkhZcProg hp;   // staging copies; calls on one context are serial
+    static std::vector<uint8_t> hx;
+    if (!large) {
+        memset(&hp, 0, sizeof hp);
+        hp.nterms = nterms;
+        hp.nc = (uint32_t)nc;
+        hp.konst = prog[1];
+    } else {
+        hx.assign(sizeof(ZcxHdr) + (size_t)nterms * 12, 0);
+        ZcxHdr hd{nterms, (uint32_t)nc, prog[1]};
+        memcpy(hx.data(), &hd, sizeof hd);
+    }
+    for (uint32_t j = 0; j < nterms; j++) {
         const uint64_t coef = prog[2 + 2 * j], pk = prog[3 + 2 * j];
         const uint32_t deg = pk & 0xff;
         if (coef >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: coefficient not canonical");
         if (deg < 1 || deg > 3 || (pk >> 32)) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: term degree must be 1..3");
         for (uint32_t k = 0; k < deg; k++)
             if (((pk >> (8 + 8 * k)) & 0xff) >= (uint64_t)nc) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: column index out of range");
-        hp.coef[j] = coef;
-        hp.packed[j] = (uint32_t)pk;
+        if (!large) {
+            hp.coef[j] = coef;
+            hp.packed[j] = (uint32_t)pk;
+        } else {
+            memcpy(hx.data() + sizeof(ZcxHdr) + (size_t)j * 8, &coef, 8);
+            const uint32_t pk32 = (uint32_t)pk;
+            memcpy(hx.data() + sizeof(ZcxHdr) + (size_t)nterms * 8 + (size_t)j * 4, &pk32, 4);
+        }
     }
     ZKH_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t n = (size_t)1 << logn;
     const size_t szA = zkh_align((size_t)nc * (n / 2 + 1) * 8), szB = zkh_align((size_t)nc * (n / 4 + 1) * 8);
     const size_t szF = zkh_align((size_t)nc * 8);
-    ZKH_TRY(zkh_ws_reserve(ctx, szA + szB + szF + zkh_align(sizeof(ZkhZcProg))));
+    const size_t szP = zkh_align(large ? hx.size() : sizeof(ZkhZcProg)), szT = zkh_align((size_t)logn * 2 * nc * sizeof(void*));
+    ZKH_TRY(zkh_ws_reserve(ctx, szA + szB + szF + szP + szT));
     gl_t* finals_dev = (gl_t*)((char*)ctx->ws + szA + szB);
-    ZkhZcProg* prog_dev = (ZkhZcProg*)((char*)ctx->ws + szA + szB + szF);
+    uint8_t* prog_dev = (uint8_t*)ctx->ws + szA + szB + szF;
+    const gl_t** ptr_dev = (const gl_t**)((char*)ctx->ws + szA + szB + szF + szP);
     ZkhCtl* h = ctx->h_ctl;
     digest_from_bytes(state, h->st);
     h->counter = 0;
     h->err = 0;
     for (int i = 0; i < 8; i++) h->par[i] = 0;
     ZKH_CUDA(ctx, cudaMemcpyAsync(ctx->d_ctl, h, offsetof(ZkhCtl, local), cudaMemcpyHostToDevice, ctx->stream));
-    ZKH_CUDA(ctx, cudaMemcpyAsync(prog_dev, &hp, sizeof hp, cudaMemcpyHostToDevice, ctx->stream));
+    ZKH_CUDA(ctx, cudaMemcpyAsync(prog_dev, large ? (const void*)hx.data() : (const void*)&hp, large ? hx.size() : sizeof hp,
+                                  cudaMemcpyHostToDevice, ctx->stream));
     const ZkhTag t = zkh_make_tag(tag);
-    int rc = nc <= 8 ? zc_enqueue_t<8>(ctx, cols_dev, nc, logn, prog_dev, t, finals_dev)
-           : nc <= 16 ? zc_enqueue_t<16>(ctx, cols_dev, nc, logn, prog_dev, t, finals_dev)
-                      : zc_enqueue_t<32>(ctx, cols_dev, nc, logn, prog_dev, t, finals_dev);
+    int rc = large ? zcx_enqueue(ctx, cols_dev, nc, nterms, logn, prog_dev, ptr_dev, t, finals_dev)
+           : nc <= 8 ? zc_enqueue_t<8>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev)
+           : nc <= 16 ? zc_enqueue_t<16>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev)
+                      : zc_enqueue_t<32>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev);
     ZKH_TRY(rc);
     ZKH_CUDA(ctx, cudaMemcpyAsync(h, ctx->d_ctl, sizeof(ZkhCtl), cudaMemcpyDeviceToHost, ctx->stream));
     if (finals)

@@ -241,3 +241,327 @@ def swg_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
     lug, batches = _tail(engine, tr, ctx, R, Q, "swg-bo", strict) if own else ([], [])
     sl, sb = _ser_tail(lug, batches)
     return struct.pack("<I", wt["n"]) + b"".join(root for _, root in C) + sl + _msgs(mE) + _u64(yE) + _u64([yUP, yM]) + sb
+
+
+# ---------------------------------------------------------------------------------- bf16 add block and gadget (p3bfa)
+BA_COLS = ("S1 E1 M1 Z1 I1 S2 E2 M2 Z2 I2 SG EH EL MH ML SHS SLS OP KD PWD DR DZ DI DM FAR ZB NZ NNF NN AV CZ AI AN "
+           "W PLO PHI PDN PDH PUP U1H U1L U2H U2L QM RR RB RT RTI ZRT L0 QH RUP C CI EO").split()
+BA = {name: i for i, name in enumerate(BA_COLS)}
+NBA = len(BA_COLS)                       # 55
+BT_NAMES = ("R128", "R256", "R512", "D16", "WDA", "RM17", "RMH", "REXP")
+# block lookups in flush order: (table, block columns)
+BA_LU = [("R256", ("E1",)), ("R256", ("E2",)), ("R128", ("M1",)), ("R128", ("M2",)), ("D16", ("KD", "PWD")), ("R256", ("DR",)),
+         ("R128", ("DM",)), ("WDA", ("W", "PLO", "PHI", "PDN", "PDH", "PUP")), ("R512", ("U1H",)), ("R512", ("U1L",)),
+         ("R512", ("U2H",)), ("R512", ("U2L",)), ("RM17", ("PDN", "RR")), ("R128", ("QM",)), ("RMH", ("PDH", "RB", "RT")),
+         ("REXP", ("EO",))]
+N_BA_C = 52
+
+
+def rm_table(tmax):
+    """(2^t, r) for r < 2^t, t = 0..tmax, padded with (1, 0) to a power of two."""
+    rows = 2 << tmax
+    p, r = np.ones(rows, dtype=np.int64), np.zeros(rows, dtype=np.int64)
+    row = 0
+    for t in range(tmax + 1):
+        p[row:row + (1 << t)] = 1 << t
+        r[row:row + (1 << t)] = np.arange(1 << t)
+        row += 1 << t
+    return make_table([p, r])
+
+
+def bfa_tables():
+    """p3bfa::build_tables (p3_bfadd.cuh:86-124)."""
+    T = {"R128": range_tab(128), "R256": range_tab(256), "R512": range_tab(512), "REXP": rexp_tab(), "RM17": rm_table(16)}
+    kd = np.where(np.arange(16) < 10, np.arange(16), 0)
+    T["D16"] = make_table([kd, 1 << kd])
+    w = np.where((np.arange(32) >= 1) & (np.arange(32) <= 18), np.arange(32), 1)
+    pdn = 1 << np.maximum(w - 8, 0)
+    T["WDA"] = make_table([w, 1 << (w - 1), 1 << w, pdn, pdn >> 1, 1 << np.maximum(8 - w, 0)])
+    h, b, x = np.zeros(2048, dtype=np.int64), np.zeros(2048, dtype=np.int64), np.zeros(2048, dtype=np.int64)
+    row = 1
+    for t in range(10):
+        for rb in (0, 1):
+            h[row:row + (1 << t)], b[row:row + (1 << t)], x[row:row + (1 << t)] = 1 << t, rb, np.arange(1 << t)
+            row += 1 << t
+    T["RMH"] = make_table([h, b, x])
+    return T
+
+
+def ba_fill(p1, p2, inverse):
+    """p3bfa::ba_fill (p3_bfadd.cuh:167-283) on int64 tensors of bf16 patterns: the canonical bf16 addition replayed with all
+    intermediate values.  Returns (55 columns in BA_COLS order, 16 lookup-index columns, output patterns); raises on rows outside
+    the gadget's domain (flush / saturate)."""
+    from .hwl import enc
+    I = torch.int64
+    b2i = lambda t: t.to(I)
+    one, zero = torch.ones_like(p1), torch.zeros_like(p1)
+    shl = torch.bitwise_left_shift
+    s1, e1, m1 = (p1 >> 15) & 1, (p1 >> 7) & 255, p1 & 127
+    s2, e2, m2 = (p2 >> 15) & 1, (p2 >> 7) & 255, p2 & 127
+    z1, z2 = e1 == 0, e2 == 0
+    sg = (e2 > e1) | ((e2 == e1) & (m2 > m1))
+    pick = lambda a, b: torch.where(sg, b, a)             # hi operand's field
+    eh, el = pick(e1, e2), pick(e2, e1)
+    mh, ml = 128 + pick(m1, m2), 128 + pick(m2, m1)
+    shs, sls = pick(s1, s2), pick(s2, s1)
+    op = shs ^ sls
+    d = eh - el
+    far = d >= 10
+    kd = torch.where(far, zero, d)
+    pwd = shl(one, kd)
+    dr = torch.where(far, d - 10, zero)
+    dz = d == 0
+    nz = ~z1 & ~z2
+    dm = torch.where(nz & dz, mh - ml, zero)
+    zb = z1 & z2
+    nnf = nz & ~far
+    av = torch.where(nnf, mh * pwd + torch.where(op != 0, -ml, ml), zero + 128)
+    cz = nnf & (av == 0)
+    nn = nnf & ~cz
+    an = torch.where((av > 0) & ~cz, av, zero + 128)
+    w = zero.clone()
+    for j in range(20):
+        w += b2i(an >= (1 << j))
+    if bool(((w < 1) | (w > 18)).any()):
+        raise ValueError("bfa: bitlen window")
+    plo, phi = shl(one, w - 1), shl(one, w)
+    dn_s, up_s = (w - 8).clamp(min=0), (8 - w).clamp(min=0)
+    pdn, pup = shl(one, dn_s), shl(one, up_s)
+    pdh = pdn >> 1
+    u1, u2 = an - plo, phi - 1 - an
+    q = torch.where(w > 8, an >> dn_s, shl(an, up_s))
+    rr = an * pup - q * pdn
+    rb = b2i((pdh > 0) & (rr >= pdh))
+    rt = rr - rb * pdh
+    zrt, l0, qh = rt == 0, q & 1, q >> 1
+    rup = b2i((rb != 0) & (~zrt | (l0 != 0)))
+    qr = q + rup
+    c = b2i(qr == 256)
+    eo_near = el + w - 8 + c
+    if bool((nn & ((eo_near < 1) | (eo_near > 254))).any()):
+        raise ValueError("bfa: add exp domain")
+    if bool((nz & far & (eh > 254)).any()):
+        raise ValueError("bfa: far exp domain")
+    eo = torch.where(nn, eo_near, torch.where(nz & far, eh, one))
+    out = torch.where(zb, (s1 & s2) << 15,
+          torch.where(z1, p2, torch.where(z2, p1, torch.where(far, (shs << 15) | (eh << 7) | (mh - 128),
+          torch.where(cz, zero, (shs << 15) | (eo << 7) | (qr - 128 * c - 128))))))
+    inv0 = lambda t: _inv_or0(t, inverse)
+    v = {"S1": s1, "E1": e1, "M1": m1, "Z1": b2i(z1), "I1": inv0(e1), "S2": s2, "E2": e2, "M2": m2, "Z2": b2i(z2), "I2": inv0(e2),
+         "SG": b2i(sg), "EH": eh, "EL": el, "MH": mh, "ML": ml, "SHS": shs, "SLS": sls, "OP": op, "KD": kd, "PWD": pwd, "DR": dr,
+         "DZ": b2i(dz), "DI": inv0(d), "DM": dm, "FAR": b2i(far), "ZB": b2i(zb), "NZ": b2i(nz), "NNF": b2i(nnf), "NN": b2i(nn),
+         "AV": enc(av), "CZ": b2i(cz), "AI": inv0(enc(av)), "AN": an, "W": w, "PLO": plo, "PHI": phi, "PDN": pdn, "PDH": pdh,
+         "PUP": pup, "U1H": u1 >> 9, "U1L": u1 & 511, "U2H": u2 >> 9, "U2L": u2 & 511, "QM": q - 128, "RR": rr, "RB": rb, "RT": rt,
+         "RTI": inv0(rt), "ZRT": b2i(zrt), "L0": l0, "QH": qh, "RUP": rup, "C": c, "CI": inv0(enc(qr - 256)), "EO": eo}
+    cols = [v[name] for name in BA_COLS]
+    rmh = torch.where(pdh == 0, zero, 2 * pdh - 1 + rb * pdh + rt)
+    lu = [e1, e2, m1, m2, kd, dr, dm, w, u1 >> 9, u1 & 511, u2 >> 9, u2 & 511, pdn - 1 + rr, q - 128, rmh, eo]
+    return cols, [t.to(torch.int32) for t in lu], out
+
+
+def ba_constraints(c, x1, x2, out):
+    """p3bfa::ba_constraints (p3_bfadd.cuh:289-392): the 52 residuals of one add block; c maps a block column name to its
+    polynomial variable, x1 / x2 / out are the operand and output pattern variables."""
+    nz1, nz2, nfar = 1 - c["Z1"], 1 - c["Z2"], 1 - c["FAR"]
+    D = c["EH"] - c["EL"]
+    qr256 = c["QM"] + c["RUP"] - 128
+    hipat = 32768 * c["SHS"] + 128 * c["EH"] + c["MH"] - 128
+    nrpat = 32768 * c["SHS"] + 128 * c["EO"] + c["QM"] + c["RUP"] - 128 * c["C"]
+    mux = lambda a, b: a + c["SG"] * (b - a)
+    return [
+        x1 - (32768 * c["S1"] + 128 * c["E1"] + c["M1"]), boolc(c["S1"]), boolc(c["Z1"]), c["Z1"] * c["E1"], c["E1"] * c["I1"] - nz1,
+        x2 - (32768 * c["S2"] + 128 * c["E2"] + c["M2"]), boolc(c["S2"]), boolc(c["Z2"]), c["Z2"] * c["E2"], c["E2"] * c["I2"] - nz2,
+        boolc(c["SG"]), c["EH"] - mux(c["E1"], c["E2"]), c["EL"] - mux(c["E2"], c["E1"]),
+        c["MH"] - (128 + mux(c["M1"], c["M2"])), c["ML"] - (128 + mux(c["M2"], c["M1"])),
+        c["SHS"] - mux(c["S1"], c["S2"]), c["SLS"] - mux(c["S2"], c["S1"]),
+        c["OP"] + 2 * c["SHS"] * c["SLS"] - (c["SHS"] + c["SLS"]),
+        boolc(c["FAR"]), nfar * (c["KD"] - D), c["FAR"] * c["KD"], c["FAR"] * (D - (c["DR"] + 10)),
+        boolc(c["DZ"]), c["DZ"] * D, D * c["DI"] - (1 - c["DZ"]), c["NZ"] * c["DZ"] * (c["MH"] - c["ML"] - c["DM"]),
+        c["ZB"] - c["Z1"] * c["Z2"], c["NZ"] - nz1 * nz2, c["NNF"] - c["NZ"] * nfar, c["FAR"] * c["CZ"],
+        c["NN"] - c["NNF"] + c["NZ"] * c["CZ"],
+        c["NNF"] * (c["AV"] - c["MH"] * c["PWD"] - c["ML"] + 2 * c["OP"] * c["ML"]),
+        boolc(c["CZ"]), c["CZ"] * c["AV"], c["AV"] * c["AI"] - (1 - c["CZ"]),
+        c["AN"] + c["AV"] * c["CZ"] - (c["AV"] + 128 * c["CZ"]),
+        c["AN"] - c["PLO"] - (512 * c["U1H"] + c["U1L"]), c["PHI"] - 1 - c["AN"] - (512 * c["U2H"] + c["U2L"]),
+        (c["QM"] + 128) * c["PDN"] + c["RR"] - c["AN"] * c["PUP"], c["RR"] - (c["RB"] * c["PDH"] + c["RT"]),
+        c["RT"] * c["RTI"] - (1 - c["ZRT"]), c["ZRT"] * c["RT"], boolc(c["ZRT"]), boolc(c["L0"]),
+        c["QM"] + 128 - (2 * c["QH"] + c["L0"]), c["RUP"] + c["RB"] * c["ZRT"] * (1 - c["L0"]) - c["RB"],
+        boolc(c["C"]), c["C"] * qr256, qr256 * c["CI"] - (1 - c["C"]),
+        c["NN"] * (c["EO"] + 8 - (c["EL"] + c["W"] + c["C"])),
+        out - (32768 * c["ZB"] * c["S1"] * c["S2"] + c["Z1"] * nz2 * x2 + nz1 * c["Z2"] * x1 + c["NZ"] * c["FAR"] * hipat
+               + c["NN"] * nrpat),
+        c["NZ"] * c["FAR"] * (c["EO"] - c["EH"]),
+    ]
+
+
+def bfa_witness(a, b, device="cpu", inverse=None):
+    """p3bfa::gen_witness (p3_bfadd.cuh:421-438): out = bf16_add(a, b) elementwise on 2^ln bf16 patterns."""
+    from .hwl import host_inverse
+    dev = torch.device(device)
+    t64 = lambda x: torch.as_tensor(np.asarray(x).astype(np.int64), device=dev)
+    x1, x2 = t64(a), t64(b)
+    n = x1.numel()
+    if n & (n - 1):
+        raise ValueError("bfa: n must be pow2")
+    ws, lidx, out = ba_fill(x1, x2, inverse or host_inverse)
+    return {"n": n, "ln": n.bit_length() - 1, "x1": x1, "x2": x2, "opat": out, "ws": ws, "lidx": lidx,
+            "O": out.cpu().numpy().astype(np.uint16)}
+
+
+def bfa_commit_operands(engine, wt, R, col):
+    out = {}
+    for name, key in (("X1", "x1"), ("X2", "x2"), ("OUT", "opat")):
+        c = col(wt[key])
+        out[name] = (c, engine.commit_gpu_rootonly(c, R))
+    return out
+
+
+def bfa_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
+    """p3bfa::prove (p3_bfadd.cuh:447-499), non-zk.  Serialised BfaProof:
+    u32 n | rws[55] | u32 groups (len, GroupProof)* | mE | yE[55] yX1 yX2 yOUT | u32 batches (len, BatchProof)*."""
+    from .ig import Ctx
+    own = ctx is None
+    ctx = ctx or Ctx()
+    tr.absorb("bfa-dims", struct.pack("<I", wt["n"]))
+    for name in BT_NAMES:
+        tr.absorb("bfa-tab", T[name]["id"])
+    tr.absorb("bfa-X1", ops["X1"][1])
+    tr.absorb("bfa-X2", ops["X2"][1])
+    tr.absorb("bfa-O", ops["OUT"][1])
+    C = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["ws"])]
+    for _, root in C:
+        tr.absorb("bfa-cw", root)
+    for i, (tab, names) in enumerate(BA_LU):
+        ctx.luq.append({"W": [C[BA[nm]] for nm in names], "idx": col(wt["lidx"][i]), "tab": T[tab]})
+    zE = [tr.chal() for _ in range(wt["ln"])]
+    lam = _powers(tr.chal(), N_BA_C)
+    cv = {name: Poly.var(4 + i) for i, name in enumerate(BA_COLS)}
+    terms, konst = zc_terms(ba_constraints(cv, Poly.var(1), Poly.var(2), Poly.var(3)), lam)
+    E = engine.build_eq_gpu(np.array(zE, dtype=np.uint64))
+    rE, mE, _ = engine.sc_prove_zc(tr, "bfa-scE", [E, ops["X1"][0], ops["X2"][0], ops["OUT"][0]] + [c for c, _ in C], terms, konst)
+    rE = [int(x) for x in rE]
+    yX = [claimc(engine, tr, ctx.ledger, ops[k][0], ops[k][1], rE) for k in ("X1", "X2", "OUT")]
+    yE = [claimc(engine, tr, ctx.ledger, c, root, rE) for c, root in C]
+    lug, batches = _tail(engine, tr, ctx, R, Q, "bfa-bo", strict) if own else ([], [])
+    sl, sb = _ser_tail(lug, batches)
+    return struct.pack("<I", wt["n"]) + b"".join(root for _, root in C) + sl + _msgs(mE) + _u64(yE) + _u64(yX) + sb
+
+
+# ---------------------------------------------------------------------------------- activation quantisation (p3qnt)
+(QD_XS, QD_XEB, QD_XMB, QD_XZ, QD_XEI, QD_SH, QD_SEL, QD_MAG) = range(8)
+(QR_E, QR_EDIF, QR_FSEL) = range(3)
+Q_EFLOOR = 9
+
+
+def qnt_tables(art):
+    """p3qnt::build_tables (p3_quant.cuh:60-76): R256 and the quantisation table extended with zero rows to dexp < 256."""
+    j = np.arange(32768, dtype=np.int64)
+    mag = np.zeros(32768, dtype=np.int64)
+    mag[:4096] = art["qe4m3"].astype(np.int64)
+    return {"R256": range_tab(256), "QEXT": make_table([j >> 7, j & 127, mag])}
+
+
+def qnt_witness(x, B, ld, art, device="cpu", inverse=None):
+    """p3qnt::gen_witness (p3_quant.cuh:143-213): per row of d = 2^ld bf16 patterns, the shared exponent E = max(9, largest
+    exponent present), the power-of-two fp32 scale (E - 8) << 23 and the e4m3 code of every element.  x: B*d uint16 patterns.
+    Rows are padded to a power of two (at least 2)."""
+    from .hwl import host_inverse
+    inverse = inverse or host_inverse
+    dev = torch.device(device)
+    I = torch.int64
+    d = 1 << ld
+    Bpad = 1 << max(max(B, 2) - 1, 0).bit_length()
+    lb = Bpad.bit_length() - 1
+    xp = torch.zeros(Bpad, d, dtype=I, device=dev)
+    xp[:B] = torch.as_tensor(np.asarray(x).astype(np.int64).reshape(B, d), device=dev)
+    xs, xeb, xmb = (xp >> 15) & 1, (xp >> 7) & 255, xp & 127
+    xz = xeb == 0
+    E = torch.where(xz, torch.zeros_like(xeb), xeb).amax(dim=1).clamp(min=Q_EFLOOR)
+    att = ~xz & (xeb == E[:, None])
+    sel = att & (att.cumsum(dim=1) == 1)
+    fsel = (~att.any(dim=1)).to(I)
+    sh = torch.where(xz, torch.zeros_like(xeb), E[:, None] - xeb)
+    qe = torch.as_tensor(np.asarray(art["qe4m3"]).astype(np.int64), device=dev)
+    mag = torch.where(sh < 32, qe[((sh.clamp(max=31)) << 7) | xmb], torch.zeros_like(sh))
+    code = xs * 128 + torch.where(xz, torch.zeros_like(mag), mag)
+    scale = (E - 8) << 23
+    flat = lambda t: t.reshape(-1).contiguous()
+    de = [flat(t) for t in (xs, xeb, xmb, xz.to(I), _inv_or0(xeb, inverse), sh, sel.to(I), mag)]
+    db = [E, E - Q_EFLOOR, fsel]
+    i32 = lambda t: flat(t).to(torch.int32)
+    return {"B": B, "ld": ld, "d": d, "Bpad": Bpad, "lb": lb, "le": lb + ld, "xpat": flat(xp), "cpat": flat(code), "spat": scale,
+            "de": de, "db": db, "lidx": [i32(xeb), i32((sh << 7) | xmb), i32(E - Q_EFLOOR)],
+            "C": code[:B].cpu().numpy().astype(np.uint8).reshape(-1), "S": scale[:B].cpu().numpy().astype(np.uint32)}
+
+
+def qnt_commit_operands(engine, wt, R, col):
+    out = {}
+    for name, key in (("X", "xpat"), ("CODES", "cpat"), ("SCALES", "spat")):
+        c = col(wt[key])
+        out[name] = (c, engine.commit_gpu_rootonly(c, R))
+    return out
+
+
+def qnt_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
+    """p3qnt::prove (p3_quant.cuh:291-416), non-zk.  Serialised QntProof: u32 B ld | rde[8] rdb[3] | groups |
+    mDe yDe[8] yDeX yDeC yDeE | mDb yDb[3] yDbS | yBF | mBind yBSEL | batches."""
+    from .ig import Ctx
+    from .p3 import F_PROD2
+    own = ctx is None
+    ctx = ctx or Ctx()
+    lg = ctx.ledger
+    ld, lb, le = wt["ld"], wt["lb"], wt["le"]
+    tr.absorb("qnt-dims", struct.pack("<II", wt["B"], ld))
+    tr.absorb("qnt-tab", T["R256"]["id"])
+    tr.absorb("qnt-tab", T["QEXT"]["id"])
+    tr.absorb("qnt-X", ops["X"][1])
+    tr.absorb("qnt-C", ops["CODES"][1])
+    tr.absorb("qnt-S", ops["SCALES"][1])
+    CDe = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["de"])]
+    CDb = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["db"])]
+    for _, root in CDe:
+        tr.absorb("qnt-ce", root)
+    for _, root in CDb:
+        tr.absorb("qnt-cb", root)
+    ctx.luq.append({"W": [CDe[QD_XEB]], "idx": col(wt["lidx"][0]), "tab": T["R256"]})
+    ctx.luq.append({"W": [CDe[QD_SH], CDe[QD_XMB], CDe[QD_MAG]], "idx": col(wt["lidx"][1]), "tab": T["QEXT"]})
+    ctx.luq.append({"W": [CDb[QR_EDIF]], "idx": col(wt["lidx"][2]), "tab": T["R256"]})
+    chal_vec = lambda n: [tr.chal() for _ in range(n)]
+    eq = lambda z: engine.build_eq_gpu(np.array(z, dtype=np.uint64))
+    claim = lambda c, z: claimc(engine, tr, lg, c[0], c[1], z)
+    v = Poly.var
+    # element domain: columns [E, X, CODES, de[8], E of the row broadcast]
+    zE = chal_vec(le)
+    lam = _powers(tr.chal(), 11)
+    c = lambda k: v(3 + k)
+    Ebc, nz = v(11), 1 - c(QD_XZ)
+    cons = [v(1) - (32768 * c(QD_XS) + 128 * c(QD_XEB) + c(QD_XMB)), boolc(c(QD_XS)), boolc(c(QD_XZ)), c(QD_XZ) * c(QD_XEB),
+            c(QD_XEB) * c(QD_XEI) - nz, nz * (c(QD_SH) + c(QD_XEB) - Ebc), c(QD_XZ) * c(QD_SH), boolc(c(QD_SEL)),
+            c(QD_SEL) * c(QD_SH), c(QD_SEL) * c(QD_XZ), v(2) - (128 * c(QD_XS) + nz * c(QD_MAG))]
+    terms, konst = zc_terms(cons, lam)
+    cols = [eq(zE), ops["X"][0], ops["CODES"][0]] + [t for t, _ in CDe] + [engine.bcast_rows(CDb[QR_E][0], ld)]
+    rE, mDe, _ = engine.sc_prove_zc(tr, "qnt-scE", cols, terms, konst)
+    rE = [int(x) for x in rE]
+    yDeX, yDeC = claim(ops["X"], rE), claim(ops["CODES"], rE)
+    yDe = [claim(cd, rE) for cd in CDe]
+    yDeE = claim(CDb[QR_E], rE[ld:le])
+    # row domain: columns [E, SCALES, db[3]]
+    zB = chal_vec(lb)
+    lamB = _powers(tr.chal(), 4)
+    r_ = lambda k: v(2 + k)
+    consB = [boolc(r_(QR_FSEL)), r_(QR_FSEL) * r_(QR_EDIF), r_(QR_E) - (Q_EFLOOR + r_(QR_EDIF)), v(1) - (r_(QR_E) - 8) * (1 << 23)]
+    terms, konst = zc_terms(consB, lamB)
+    rB, mDb, _ = engine.sc_prove_zc(tr, "qnt-scB", [eq(zB), ops["SCALES"][0]] + [t for t, _ in CDb], terms, konst)
+    rB = [int(x) for x in rB]
+    yDbS = claim(ops["SCALES"], rB)
+    yDb = [claim(cd, rB) for cd in CDb]
+    # row binding: sum_i SEL = 1 - FSEL
+    z2 = chal_vec(lb)
+    yBF = claim(CDb[QR_FSEL], z2)
+    rS, mBind, _ = engine.sc_prove_gpu(tr, "qnt-scS", [engine.bcast_rows(eq(z2), ld), CDe[QD_SEL][0]], F_PROD2, 5)
+    yBSEL = claim(CDe[QD_SEL], [int(x) for x in rS])
+    lug, batches = _tail(engine, tr, ctx, R, Q, "qnt-bo", strict) if own else ([], [])
+    sl, sb = _ser_tail(lug, batches)
+    out = struct.pack("<II", wt["B"], ld) + b"".join(r for _, r in CDe) + b"".join(r for _, r in CDb) + sl
+    out += _msgs(mDe) + _u64(yDe) + _u64([yDeX, yDeC, yDeE]) + _msgs(mDb) + _u64(yDb) + _u64([yDbS, yBF]) + _msgs(mBind) + _u64([yBSEL])
+    return out + sb
