@@ -26,6 +26,9 @@
 #include "p3_int_layer.cuh"
 #include "p3_swiglu.cuh"
 #include "p3_bfadd.cuh"
+#include "p3_quant.cuh"
+#include "p3_rope.cuh"
+#include "p3_softmax.cuh"
 
 namespace {
 fs::Transcript tr_from(const uint8_t st[32]) {
@@ -701,6 +704,7 @@ struct HwlWriter {
     void raw(const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); }
     void u32(uint32_t& v) { raw(&v, 4); }
     void msgs(std::vector<p3hwl::Msg5>& m) { uint32_t n = (uint32_t)m.size(); raw(&n, 4); raw(m.data(), (size_t)n * 40); }
+    void vec(std::vector<gl_t>& v) { uint32_t n = (uint32_t)v.size(); raw(&n, 4); raw(v.data(), (size_t)n * 8); }
     void groups(std::vector<p3lu::GroupProof>& g) {
         uint32_t ng = (uint32_t)g.size(); raw(&ng, 4);
         for (auto& x : g) { uint32_t n = (uint32_t)lu_serialize(x, tmp.data(), tmp.size()); raw(&n, 4); raw(tmp.data(), n); }
@@ -719,6 +723,11 @@ struct HwlReader {
         uint32_t n = 0; u32(n);
         if (!ok || n > 64 || !need((size_t)n * 40)) { ok = false; return; }
         m.resize(n); raw(m.data(), (size_t)n * 40);
+    }
+    void vec(std::vector<gl_t>& v) {
+        uint32_t n = 0; u32(n);
+        if (!ok || n > 4096 || !need((size_t)n * 8)) { ok = false; return; }
+        v.resize(n); raw(v.data(), (size_t)n * 8);
     }
     void groups(std::vector<p3lu::GroupProof>& g) {
         uint32_t ng = 0; u32(ng);
@@ -788,6 +797,64 @@ void bfa_walk(IO& io, p3bfa::BfaProof& pf) {
 const p3bfa::Tables& bfa_tables() {
     static p3bfa::Tables T = p3bfa::build_tables();
     return T;
+}
+// p3qnt::QntProof <-> bytes: u32 B ld | rde[8] rdb[3] | groups | mDe yDe[8] yDeX yDeC yDeE | mDb yDb[3] yDbS | yBF | mBind yBSEL | batches
+template <typename IO>
+void qnt_walk(IO& io, p3qnt::QntProof& pf) {
+    io.u32(pf.B); io.u32(pf.ld);
+    for (int c = 0; c < p3qnt::NDE; c++) io.raw(pf.rde[c].data(), 32);
+    for (int c = 0; c < p3qnt::NDB; c++) io.raw(pf.rdb[c].data(), 32);
+    io.groups(pf.lug);
+    io.msgs(pf.mDe); io.raw(pf.yDe, sizeof pf.yDe); io.raw(&pf.yDeX, 8); io.raw(&pf.yDeC, 8); io.raw(&pf.yDeE, 8);
+    io.msgs(pf.mDb); io.raw(pf.yDb, sizeof pf.yDb); io.raw(&pf.yDbS, 8);
+    io.raw(&pf.yBF, 8);
+    io.msgs(pf.mBind); io.raw(&pf.yBSEL, 8);
+    io.batches(pf.batches);
+}
+const p3qnt::Tables& qnt_tables() { static p3qnt::Tables T = p3qnt::build_tables(tf_art()); return T; }
+// p3rope::RopeProof <-> bytes: u32 lp lh | rws[NDR] | groups | mE | u32 count, yE.. | yQA yQB yOA yOB | batches
+template <typename IO>
+void rope_walk(IO& io, p3rope::RopeProof& pf) {
+    io.u32(pf.lp); io.u32(pf.lh);
+    for (int c = 0; c < p3rope::NDR; c++) io.raw(pf.rws[c].data(), 32);
+    io.groups(pf.lug);
+    io.msgs(pf.mE); io.vec(pf.yE);
+    io.raw(&pf.yQA, 8); io.raw(&pf.yQB, 8); io.raw(&pf.yOA, 8); io.raw(&pf.yOB, 8);
+    io.batches(pf.batches);
+}
+const p3rope::Tables& rope_tables() { static p3rope::Tables T = p3rope::build_tables(tf_art()); return T; }
+// p3rms::RmsProof <-> bytes: u32 B ld | rde rdb rdw | groups | mDe yDe yDeX yDeY yDeE yDeTEB yDeGS yDeGEB yDeGZ | mDb yDb |
+//   mDw yDw yDwG | yBS yBF | mBind yBXZ yBQ yBSEL | batches
+template <typename IO>
+void rms_walk(IO& io, p3rms::RmsProof& pf) {
+    io.u32(pf.B); io.u32(pf.ld);
+    for (int c = 0; c < p3rms::NDE; c++) io.raw(pf.rde[c].data(), 32);
+    for (int c = 0; c < p3rms::NDB; c++) io.raw(pf.rdb[c].data(), 32);
+    for (int c = 0; c < p3rms::NDW; c++) io.raw(pf.rdw[c].data(), 32);
+    io.groups(pf.lug);
+    io.msgs(pf.mDe); io.raw(pf.yDe, sizeof pf.yDe);
+    io.raw(&pf.yDeX, 8); io.raw(&pf.yDeY, 8); io.raw(&pf.yDeE, 8); io.raw(&pf.yDeTEB, 8); io.raw(&pf.yDeGS, 8);
+    io.raw(&pf.yDeGEB, 8); io.raw(&pf.yDeGZ, 8);
+    io.msgs(pf.mDb); io.raw(pf.yDb, sizeof pf.yDb);
+    io.msgs(pf.mDw); io.raw(pf.yDw, sizeof pf.yDw); io.raw(&pf.yDwG, 8);
+    io.raw(&pf.yBS, 8); io.raw(&pf.yBF, 8);
+    io.msgs(pf.mBind); io.raw(&pf.yBXZ, 8); io.raw(&pf.yBQ, 8); io.raw(&pf.yBSEL, 8);
+    io.batches(pf.batches);
+}
+// p3smx::SmxProof <-> bytes: u32 B ln | rde[NDE2] rdb[NDB2] | groups | mDe | u32 count, yDe.. | yDeS yDeP yDeKM yDeMX yDeE yDeRB |
+//   mDb yDb | yBF yBS | mBind yBSEL1 yBSEL2 yBQ2 | batches
+template <typename IO>
+void smx_walk(IO& io, p3smx::SmxProof& pf) {
+    io.u32(pf.B); io.u32(pf.ln);
+    for (int c = 0; c < p3smx::NDE2; c++) io.raw(pf.rde[c].data(), 32);
+    for (int c = 0; c < p3smx::NDB2; c++) io.raw(pf.rdb[c].data(), 32);
+    io.groups(pf.lug);
+    io.msgs(pf.mDe); io.vec(pf.yDe);
+    io.raw(&pf.yDeS, 8); io.raw(&pf.yDeP, 8); io.raw(&pf.yDeKM, 8); io.raw(&pf.yDeMX, 8); io.raw(&pf.yDeE, 8); io.raw(&pf.yDeRB, 8);
+    io.msgs(pf.mDb); io.raw(pf.yDb, sizeof pf.yDb);
+    io.raw(&pf.yBF, 8); io.raw(&pf.yBS, 8);
+    io.msgs(pf.mBind); io.raw(&pf.yBSEL1, 8); io.raw(&pf.yBSEL2, 8); io.raw(&pf.yBQ2, 8);
+    io.batches(pf.batches);
 }
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
 const p3ig::Tables& ig_tables(uint32_t d, uint32_t btop) {
@@ -1897,6 +1964,112 @@ size_t ref_bfa_prove(uint8_t st[32], const uint16_t* a, const uint16_t* b, uint3
     p3fri::g_gpu_merkle = false;
     memcpy(st, tr.state, 32);
     return w;
+}
+
+// p3qnt::verify (host only): roots X CODES SCALES
+int ref_qnt_verify(uint8_t st[32], const uint8_t* roots3, uint32_t B, uint32_t ld, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3qnt::QntProof pf;
+        HwlReader rd{proof, proof + len};
+        qnt_walk(rd, pf);
+        if (rd.ok && rd.p == rd.end) {
+            p3fri::Hash h[3];
+            for (int i = 0; i < 3; i++) memcpy(h[i].data(), roots3 + 32 * i, 32);
+            ok = p3qnt::verify(tr, qnt_tables(), pf, h[0], h[1], h[2], B, ld, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
+}
+// p3qnt: gen_witness + commit_operands + prove; codes_out: B*d codes, scales_out: B fp32 bit patterns
+size_t ref_qnt_prove(uint8_t st[32], const uint16_t* x, uint32_t B, uint32_t ld, uint32_t R, uint32_t Q, int gpu, uint8_t* roots3_out,
+                     uint8_t* codes_out, uint32_t* scales_out, uint8_t* out, size_t cap) {
+    p3fri::g_gpu_merkle = gpu != 0;
+    if (gpu) p3bf::p3_enable_mempool();
+    fs::Transcript tr = tr_from(st);
+    size_t w = 0;
+    try {
+        p3qnt::Golden L; L.B = B; L.d = 1u << ld;
+        const size_t n = (size_t)B << ld;
+        L.x.assign(x, x + n); L.codes.assign(n, 0); L.scales.assign(B, 0);
+        p3qnt::Wit wt = p3qnt::gen_witness(L, tf_art());
+        p3qnt::Operands ops = p3qnt::commit_operands(wt, R);
+        auto pf = p3qnt::prove(tr, wt, qnt_tables(), ops, R, Q);
+        if (roots3_out) {
+            memcpy(roots3_out, ops.X.root.data(), 32); memcpy(roots3_out + 32, ops.CODES.root.data(), 32);
+            memcpy(roots3_out + 64, ops.SCALES.root.data(), 32);
+        }
+        if (codes_out) memcpy(codes_out, wt.C.data(), n);
+        if (scales_out) memcpy(scales_out, wt.S.data(), (size_t)B * 4);
+        HwlWriter wr;
+        qnt_walk(wr, pf);
+        w = emit(wr.b, out, cap);
+    } catch (...) { w = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return w;
+}
+// p3rope::verify (host only): cos / sin bf16 tables of seq * dh/2 patterns, roots Q OUT
+int ref_rope_verify(uint8_t st[32], const uint16_t* cosp, const uint16_t* sinp, const uint8_t* roots2, uint32_t seq, uint32_t dh,
+                    uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3rope::RopeProof pf;
+        HwlReader rd{proof, proof + len};
+        rope_walk(rd, pf);
+        if (rd.ok && rd.p == rd.end) {
+            p3fri::Hash h[2];
+            for (int i = 0; i < 2; i++) memcpy(h[i].data(), roots2 + 32 * i, 32);
+            const size_t nh = (size_t)seq * (dh / 2);
+            std::vector<uint16_t> c(cosp, cosp + nh), s2(sinp, sinp + nh);
+            ok = p3rope::verify(tr, rope_tables(), pf, c, s2, h[0], h[1], seq, dh, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
+}
+// p3rms::verify (host only): roots X G Y
+int ref_rms_verify(uint8_t st[32], const uint8_t* roots3, uint32_t B, uint32_t ld, uint32_t R, uint32_t Q, const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3rms::RmsProof pf;
+        HwlReader rd{proof, proof + len};
+        rms_walk(rd, pf);
+        if (rd.ok && rd.p == rd.end) {
+            static p3rms::Tables T; static int64_t t_ld = -1;
+            if (t_ld != tf_art().ld) { T = p3rms::build_tables(tf_art()); t_ld = tf_art().ld; }
+            p3fri::Hash h[3];
+            for (int i = 0; i < 3; i++) memcpy(h[i].data(), roots3 + 32 * i, 32);
+            ok = p3rms::verify(tr, T, tf_art(), pf, h[0], h[1], h[2], B, ld, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
+}
+// p3smx::verify (host only): mask of B*n bytes, roots S P
+int ref_smx_verify(uint8_t st[32], const uint8_t* mask, const uint8_t* roots2, uint32_t B, uint32_t n, uint32_t wmax, uint32_t R,
+                   uint32_t Q, const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3smx::SmxProof pf;
+        HwlReader rd{proof, proof + len};
+        smx_walk(rd, pf);
+        if (rd.ok && rd.p == rd.end) {
+            static p3smx::Tables T; static uint32_t t_w = 0;
+            if (t_w != wmax) { T = p3smx::build_tables(tf_art(), wmax); t_w = wmax; }
+            p3fri::Hash h[2];
+            for (int i = 0; i < 2; i++) memcpy(h[i].data(), roots2 + 32 * i, 32);
+            std::vector<uint8_t> m(mask, mask + (size_t)B * n);
+            ok = p3smx::verify(tr, T, tf_art(), pf, m, h[0], h[1], B, n, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
 }
 
 }  // extern "C"

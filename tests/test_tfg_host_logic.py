@@ -9,7 +9,7 @@ import pytest
 
 from hwl_helpers import host_col
 from ig_helpers import OracleGadgetEngine
-from tfg_helpers import bf16_add_cases, bf16_patterns, load_art, ref_swg_verify, ref_verify3
+from tfg_helpers import bf16_add_cases, bf16_patterns, load_art, ref_swg_verify, ref_verify3, ref_verify_roots
 
 ART_LD6_SHA256 = "72ca8b6045cf1ff65d2386e6026884b3d9e2759c7c69cd5298f8e61ae8583223"
 
@@ -95,3 +95,64 @@ def test_bf16_add_accepted_by_reference_verifier(orc, ref, zk, ln):
     bad = bytearray(pf)
     bad[len(pf) // 2] ^= 1
     assert not ref_verify3(ref, "ref_bfa_verify", st0, roots3, 1 << ln, R, Q, bytes(bad))[0]
+
+
+@pytest.mark.parametrize("B,ld", [(1, 3), (3, 4), (4, 6)])
+def test_quantize_accepted_by_reference_verifier(orc, ref, zk, B, ld):
+    R, Q = 1, 24
+    tfg = zk.tfg
+    art = load_art(ref, zk)
+    T = tfg.qnt_tables(art)
+    rng = np.random.default_rng(B * 10 + ld)
+    x = bf16_patterns(rng, B << ld, 3.0).reshape(B, 1 << ld)
+    x[0] = (x[0] & 0x8000)                                   # an all-zero row: the phantom floor is the row maximum
+    if B > 2:
+        x[2] = bf16_patterns(rng, 1 << ld, 1e-12)            # tiny row
+    wt = tfg.qnt_witness(x.reshape(-1), B, ld, art)
+    # scale = 2^(E-8-127), codes decode to x / scale on the e4m3 grid for a sample of elements
+    assert wt["S"][0] == (1 << 23)
+    eng = OracleGadgetEngine(orc)
+    ops = tfg.qnt_commit_operands(eng, wt, R, host_col)
+    tr = zk.Transcript("qnt")
+    pf = tfg.qnt_prove(eng, tr, wt, T, ops, R, Q, host_col)
+    roots3 = [ops[k][1] for k in ("X", "CODES", "SCALES")]
+    st0 = zk.Transcript("qnt").state
+    ok, st = ref_verify_roots(ref, "ref_qnt_verify", st0, roots3, (B, ld), R, Q, pf)
+    assert ok and st == tr.state
+    assert not ref_verify_roots(ref, "ref_qnt_verify", st0, roots3[::-1], (B, ld), R, Q, pf)[0]
+    bad = bytearray(pf)
+    bad[len(pf) // 3] ^= 1
+    assert not ref_verify_roots(ref, "ref_qnt_verify", st0, roots3, (B, ld), R, Q, bytes(bad))[0]
+
+
+def _rope_tables(zk, seq, dh):
+    """bf16 cos / sin tables of the llama rotation, theta = 10000 (seq x dh/2 patterns)."""
+    half = dh // 2
+    ang = np.arange(seq, dtype=np.float64)[:, None] * (10000.0 ** (-np.arange(half, dtype=np.float64) / half))[None, :]
+    to_bf = np.vectorize(zk.tfart.bf_from_f64, otypes=[np.uint16])
+    return to_bf(np.cos(ang)).reshape(-1), to_bf(np.sin(ang)).reshape(-1)
+
+
+@pytest.mark.parametrize("seq,dh", [(2, 4), (4, 8)])
+def test_rope_accepted_by_reference_verifier(orc, ref, zk, seq, dh):
+    R, Q = 1, 24
+    tfg = zk.tfg
+    art = load_art(ref, zk)
+    T = tfg.rope_tables(art)
+    cos, sin = _rope_tables(zk, seq, dh)
+    q = bf16_patterns(np.random.default_rng(seq + dh), seq * dh, 1.0)
+    wt = tfg.rope_witness(q, cos, sin, seq, dh, art)
+    nzq = (q[:dh] & 0x7F80) != 0
+    assert (wt["OUT"][:dh][nzq] == q[:dh][nzq]).all()             # position 0: cos = 1, sin = +0
+    eng = OracleGadgetEngine(orc)
+    ops = tfg.rope_commit_operands(eng, wt, R, host_col)
+    tr = zk.Transcript("rope")
+    pf = tfg.rope_prove(eng, tr, wt, T, ops, R, Q, host_col)
+    roots2 = [ops["Q"][1], ops["OUT"][1]]
+    st0 = zk.Transcript("rope").state
+    ok, st = ref_verify_roots(ref, "ref_rope_verify", st0, roots2, (seq, dh), R, Q, pf, pre=(cos, sin))
+    assert ok and st == tr.state
+    assert not ref_verify_roots(ref, "ref_rope_verify", st0, roots2, (seq, dh), R, Q, pf, pre=(sin, cos))[0]
+    bad = bytearray(pf)
+    bad[len(pf) // 3] ^= 1
+    assert not ref_verify_roots(ref, "ref_rope_verify", st0, roots2, (seq, dh), R, Q, bytes(bad), pre=(cos, sin))[0]

@@ -86,3 +86,12 @@ def bf16_add_cases(rng, n):
         b[2 * k:3 * k] = bf16_patterns(rng, k, 1e-4)              # far addend
         b[3 * k:4 * k] = (a[3 * k:4 * k] & 0xFF80) | rng.integers(0, 128, size=k).astype(np.uint16)   # same binade
     return a, b
+
+
+def ref_verify_roots(ref, fn, st, roots, dims, R, Q, proof, pre=()):
+    """ref_qnt_verify / ref_rms_verify (roots concatenated, two dims) and, with leading array arguments, the rope / softmax forms."""
+    s = (C.c_uint8 * 32)(*st)
+    args = [s] + [_vp(np.ascontiguousarray(a)) for a in pre] + [b"".join(roots)] + [C.c_uint32(v) for v in dims] + \
+        [C.c_uint32(R), C.c_uint32(Q), bytes(proof), C.c_size_t(len(proof))]
+    ok = getattr(ref.lib, fn)(*args)
+    return bool(ok), bytes(s)

@@ -565,3 +565,150 @@ def qnt_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
     out = struct.pack("<II", wt["B"], ld) + b"".join(r for _, r in CDe) + b"".join(r for _, r in CDb) + sl
     out += _msgs(mDe) + _u64(yDe) + _u64([yDeX, yDeC, yDeE]) + _msgs(mDb) + _u64(yDb) + _u64([yDbS, yBF]) + _msgs(mBind) + _u64([yBSEL])
     return out + sb
+
+
+# ---------------------------------------------------------------------------------- RoPE (p3rope)
+RP_FIXED = ("AS AEB AMB AZ AEI BS BEB BMB BZ BEI MOAC EIAC EOAC PAC MOSB EISB EOSB PSB MOCB EICB EOCB PCB MOSA EISA EOSA PSA "
+            "NSB").split()
+RP = {name: i for i, name in enumerate(RP_FIXED)}
+RP_A1, RP_A2 = len(RP_FIXED), len(RP_FIXED) + NBA
+NDR = len(RP_FIXED) + 2 * NBA            # 137
+N_RP_C = 23 + 2 * N_BA_C
+
+
+def rope_tables(art):
+    """p3rope::build_tables (p3_rope.cuh:88-98): the add block's tables plus MUL7."""
+    T = bfa_tables()
+    T["MUL7"] = mul7_tab(art)
+    return T
+
+
+def _bf_fields(p):
+    eb = (p >> 7) & 255
+    return (p >> 15) & 1, eb, p & 127, (eb == 0).to(torch.int64)
+
+
+def _bf_mul(x, t, art_mo, art_ei, what):
+    """canonical bf16 product of decomposed operands (sign, exponent, mantissa, zero flag): (mo, ei, eo, pattern, MUL7 row)"""
+    mj = (x[2] << 7) | t[2]
+    mo, ei = 128 + art_mo[mj], art_ei[mj]
+    z2 = (x[3] | t[3]) != 0
+    eo = torch.where(z2, torch.ones_like(mj), x[1] + t[1] - 127 + ei)
+    if bool(((eo < 1) | (eo > 254)).any()):
+        raise ValueError("%s: mul exp domain" % what)
+    pat = ((x[0] ^ t[0]) << 15) | torch.where(z2, torch.zeros_like(eo), (eo << 7) | (mo - 128))
+    return mo, ei, eo, pat, mj
+
+
+def rope_witness(q, cos, sin, seq, dh, art, device="cpu", inverse=None):
+    """p3rope::gen_witness (p3_rope.cuh:146-243): llama rotate-half RoPE on bf16 patterns with public bf16 cos / sin tables
+    (seq * dh/2 patterns each): four canonical products and two canonical adds per (position, pair)."""
+    from .hwl import host_inverse
+    inverse = inverse or host_inverse
+    dev = torch.device(device)
+    t64 = lambda a: torch.as_tensor(np.asarray(a).astype(np.int64), device=dev)
+    half = dh // 2
+    lp, lh = seq.bit_length() - 1, half.bit_length() - 1
+    if (1 << lp) != seq or (1 << lh) != half:
+        raise ValueError("rope: dims must be pow2")
+    Q = t64(q).reshape(seq, dh)
+    ap, bp = Q[:, :half].reshape(-1).contiguous(), Q[:, half:].reshape(-1).contiguous()
+    da, db, dc, ds = _bf_fields(ap), _bf_fields(bp), _bf_fields(t64(cos).reshape(-1)), _bf_fields(t64(sin).reshape(-1))
+    mo_t, ei_t = t64(art["mul_mo"]), t64(art["mul_einc"])
+    pac, psb, pcb, psa = (_bf_mul(x, t, mo_t, ei_t, "rope") for x, t in ((da, dc), (db, ds), (db, dc), (da, ds)))
+    nsb = psb[3] ^ 0x8000
+    a1, lu1, oa = ba_fill(pac[3], nsb, inverse)
+    a2, lu2, ob = ba_fill(pcb[3], psa[3], inverse)
+    inv0 = lambda t: _inv_or0(t, inverse)
+    ws = [da[0], da[1], da[2], da[3], inv0(da[1]), db[0], db[1], db[2], db[3], inv0(db[1])]
+    for m in (pac, psb, pcb, psa):
+        ws += [m[0], m[1], m[2], m[3]]
+    ws += [nsb] + a1 + a2
+    i32 = lambda t: t.to(torch.int32)
+    lidx = [i32(da[1]), i32(da[2]), i32(db[1]), i32(db[2]), i32(pac[4]), i32(psb[4]), i32(pcb[4]), i32(psa[4]),
+            i32(pac[2]), i32(psb[2]), i32(pcb[2]), i32(psa[2])] + lu1 + lu2
+    out = torch.cat([oa.reshape(seq, half), ob.reshape(seq, half)], dim=1).reshape(-1).contiguous()
+    return {"seq": seq, "dh": dh, "lp": lp, "lh": lh, "ln": lp + lh, "qpat": Q.reshape(-1).contiguous(), "opat": out, "qa": ap, "qb": bp,
+            "oa": oa, "ob": ob, "cf": list(dc), "sf": list(ds), "ws": ws, "lidx": lidx, "amf": 128 + da[2], "bmf": 128 + db[2],
+            "cmf": 128 + dc[2], "smf": 128 + ds[2], "OUT": out.cpu().numpy().astype(np.uint16)}
+
+
+def rope_commit_operands(engine, wt, R, col):
+    out = {}
+    for name, key in (("Q", "qpat"), ("OUT", "opat")):
+        c = col(wt[key])
+        out[name] = (c, engine.commit_gpu_rootonly(c, R))
+    return out
+
+
+def rope_constraints():
+    """F_rp (p3_rope.cuh:262-318) over [Eq, QA, QB, OA, OB, cos fields s eb mb z, sin fields s eb mb z, ws[137]]."""
+    v = Poly.var
+    c = lambda name: v(13 + RP[name])
+    cons = []
+    for x, src in (("A", 1), ("B", 2)):
+        cons += [v(src) - (32768 * c(x + "S") + 128 * c(x + "EB") + c(x + "MB")), boolc(c(x + "S")), boolc(c(x + "Z")),
+                 c(x + "Z") * c(x + "EB"), c(x + "EB") * c(x + "EI") - (1 - c(x + "Z"))]
+    for x, tv, suf in (("A", 5, "AC"), ("B", 9, "SB"), ("B", 5, "CB"), ("A", 9, "SA")):
+        TS, TEB, TZ = v(tv), v(tv + 1), v(tv + 3)
+        z2 = c(x + "Z") + TZ - c(x + "Z") * TZ
+        sg = c(x + "S") + TS - 2 * c(x + "S") * TS
+        cons += [z2 * (c("EO" + suf) - 1), (1 - z2) * (c("EO" + suf) - (c(x + "EB") + TEB + c("EI" + suf) - 127)),
+                 c("P" + suf) - (32768 * sg + (1 - z2) * (128 * c("EO" + suf) + c("MO" + suf) - 128))]
+    sgsb = c("BS") + v(9) - 2 * c("BS") * v(9)
+    cons.append(c("NSB") + 65536 * sgsb - (c("PSB") + 32768))
+    blk = lambda base: {name: v(13 + base + i) for i, name in enumerate(BA_COLS)}
+    cons += ba_constraints(blk(RP_A1), c("PAC"), c("NSB"), v(3))
+    cons += ba_constraints(blk(RP_A2), c("PCB"), c("PSA"), v(4))
+    return cons
+
+
+def rope_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
+    """p3rope::prove (p3_rope.cuh:345-459), non-zk.  Serialised RopeProof: u32 lp lh | rws[137] | groups | mE |
+    u32 137, yE | yQA yQB yOA yOB | batches."""
+    from .ig import Ctx
+    own = ctx is None
+    ctx = ctx or Ctx()
+    lg = ctx.ledger
+    lh, ln = wt["lh"], wt["ln"]
+    field_bytes = lambda t: t.cpu().numpy().astype(np.uint64).tobytes()
+    tr.absorb("rop-dims", struct.pack("<II", wt["lp"], lh))
+    for name in BT_NAMES:
+        tr.absorb("rop-tab", T[name]["id"])
+    tr.absorb("rop-tab", T["MUL7"]["id"])
+    for k in range(4):
+        tr.absorb("rop-cos", field_bytes(wt["cf"][k]))
+        tr.absorb("rop-sin", field_bytes(wt["sf"][k]))
+    tr.absorb("rop-Q", ops["Q"][1])
+    tr.absorb("rop-O", ops["OUT"][1])
+    C = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["ws"])]
+    for _, root in C:
+        tr.absorb("rop-cw", root)
+    virt = {k: (col(wt[k]), None) for k in ("amf", "bmf", "cmf", "smf")}
+    cc = lambda name: C[RP[name]]
+    specs = [("R256", [cc("AEB")], None), ("R128", [cc("AMB")], None), ("R256", [cc("BEB")], None), ("R128", [cc("BMB")], None),
+             ("MUL7", [virt["amf"], virt["cmf"], cc("MOAC"), cc("EIAC")], "AMB"), ("MUL7", [virt["bmf"], virt["smf"], cc("MOSB"), cc("EISB")], "BMB"),
+             ("MUL7", [virt["bmf"], virt["cmf"], cc("MOCB"), cc("EICB")], "BMB"), ("MUL7", [virt["amf"], virt["smf"], cc("MOSA"), cc("EISA")], "AMB"),
+             ("REXP", [cc("EOAC")], None), ("REXP", [cc("EOSB")], None), ("REXP", [cc("EOCB")], None), ("REXP", [cc("EOSA")], None)]
+    for base in (RP_A1, RP_A2):
+        specs += [(tab, [C[base + BA[nm]] for nm in names], None) for tab, names in BA_LU]
+    for i, (tab, W, bindcol) in enumerate(specs):
+        ent = {"W": W, "idx": col(wt["lidx"][i]), "tab": T[tab]}
+        if bindcol:
+            ent["bind"] = claim_bind(engine, tr, lg, [cc(bindcol)])
+        ctx.luq.append(ent)
+    zE = [tr.chal() for _ in range(ln)]
+    lam = _powers(tr.chal(), N_RP_C)
+    terms, konst = zc_terms(rope_constraints(), lam)
+    cols = [engine.build_eq_gpu(np.array(zE, dtype=np.uint64))] + [col(wt[k]) for k in ("qa", "qb", "oa", "ob")] + \
+        [col(t) for t in wt["cf"]] + [col(t) for t in wt["sf"]] + [c for c, _ in C]
+    rE, mE, _ = engine.sc_prove_zc(tr, "rop-scE", cols, terms, konst)
+    rE = [int(x) for x in rE]
+    ins = lambda bit: rE[:lh] + [bit] + rE[lh:]
+    claim = lambda c, z: claimc(engine, tr, lg, c[0], c[1], z)
+    yQ = [claim(ops["Q"], ins(0)), claim(ops["Q"], ins(1)), claim(ops["OUT"], ins(0)), claim(ops["OUT"], ins(1))]
+    yE = [claim(cd, rE) for cd in C]
+    lug, batches = _tail(engine, tr, ctx, R, Q, "rop-bo", strict) if own else ([], [])
+    sl, sb = _ser_tail(lug, batches)
+    return struct.pack("<II", wt["lp"], lh) + b"".join(r for _, r in C) + sl + _msgs(mE) + struct.pack("<I", len(yE)) + _u64(yE) + \
+        _u64(yQ) + sb
