@@ -33,3 +33,34 @@ def test_layer_accepted_by_reference_verifier(orc, ref, zk, dims):
         bad = bytearray(pf)
         bad[off] ^= 1
         assert not ref_itf_verify(ref, st0, c, x0, o["x0"][1], wroots, Wt, w["out"], R, Q, bytes(bad))[0]
+
+
+def _flat(v):
+    import torch
+    if isinstance(v, dict):
+        return [x for k in sorted(v) for x in _flat(v[k])]
+    if isinstance(v, (list, tuple)):
+        return [x for e in v for x in _flat(e)]
+    if v is None:
+        return [None]
+    if isinstance(v, torch.Tensor):
+        v = v.cpu().numpy()
+    v = np.asarray(v)
+    return [v.view(np.uint64) if v.dtype == np.int64 else v.astype(np.uint64)]
+
+
+@pytest.mark.parametrize("dims", [(4, 8, 2, 4, 16, 2), (8, 16, 2, 8, 32, 1)])
+def test_tensor_witness_chain_equals_numpy_chain(zk, dims):
+    """The tensor-arithmetic witness chain (ig_dev, here on the CPU) gives every column and index array of the numpy chain."""
+    from zk_hillclimb_b200 import ig_dev
+    ig = zk.ig
+    c = ig.Config(*dims)
+    T = ig.build_tables(zk.load_library(), c.d, c.btop)
+    x0, Wt = layer_inputs(ig, c, 9)
+    w = ig.itf_build_witness(c, x0, Wt, T)
+    wd = ig_dev.itf_build_witness(c, x0, Wt, T, device="cpu")
+    for k, v in w.items():
+        a, b = _flat(v), _flat(wd[k])
+        assert len(a) == len(b), k
+        for x, y in zip(a, b):
+            assert (x is None and y is None) or (x.shape == y.shape and (x == y).all()), k

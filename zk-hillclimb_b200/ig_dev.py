@@ -59,7 +59,7 @@ def iswg_witness(g, u, silu_col):
     gv, uv = sig(g), sig(u)
     if bool(((gv < -ABND) | (gv >= ABND)).any()):
         raise ValueError("iswg: G out of range")
-    sil = sig(silu_col[gv + ABND])
+    sil = silu_col[gv + ABND]                    # the table column is passed already signed
     m64 = sil * uv
     mo = (m64 + (1 << 15)) >> 16
     rem = (m64 + (1 << 15)) - (mo << 16)
