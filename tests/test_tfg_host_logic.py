@@ -156,3 +156,36 @@ def test_rope_accepted_by_reference_verifier(orc, ref, zk, seq, dh):
     bad = bytearray(pf)
     bad[len(pf) // 3] ^= 1
     assert not ref_verify_roots(ref, "ref_rope_verify", st0, roots2, (seq, dh), R, Q, bytes(bad), pre=(cos, sin))[0]
+
+
+@pytest.mark.parametrize("B,ld", [(1, 4), (3, 6)])
+def test_rmsnorm_accepted_by_reference_verifier(orc, ref, zk, B, ld):
+    R, Q = 1, 24
+    tfg = zk.tfg
+    art = load_art(ref, zk, ld)
+    T = tfg.rms_tables(art)
+    rng = np.random.default_rng(B + ld)
+    x = bf16_patterns(rng, B << ld, 1.5).reshape(B, 1 << ld)
+    if B > 1:
+        x[1] = x[1] & 0x8000                                  # zero row: eps dominates
+    g = bf16_patterns(rng, 1 << ld, 0.1, zeros=0.0)
+    g = ((g.astype(np.uint32) << 16).view(np.float32) + np.float32(1.0)).view(np.uint32) >> 16
+    wt = tfg.rms_witness(x.reshape(-1), g.astype(np.uint16), B, art)
+    # float check on an ordinary row: y ~ x * g / rms(x) within bf16 rounding of three steps
+    xf = (x[0].astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    gf = (g.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    yf = (wt["Y"][:1 << ld].astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    want = xf * gf / np.sqrt((xf * xf).mean() + 1e-6)
+    assert np.allclose(yf, want, rtol=0.03, atol=1e-30)
+    eng = OracleGadgetEngine(orc)
+    ops = tfg.rms_commit_operands(eng, wt, R, host_col)
+    tr = zk.Transcript("rms")
+    pf = tfg.rms_prove(eng, tr, wt, T, art, ops, R, Q, host_col)
+    roots3 = [ops[k][1] for k in ("X", "G", "Y")]
+    st0 = zk.Transcript("rms").state
+    ok, st = ref_verify_roots(ref, "ref_rms_verify", st0, roots3, (B, ld), R, Q, pf)
+    assert ok and st == tr.state
+    assert not ref_verify_roots(ref, "ref_rms_verify", st0, roots3[::-1], (B, ld), R, Q, pf)[0]
+    bad = bytearray(pf)
+    bad[len(pf) // 3] ^= 1
+    assert not ref_verify_roots(ref, "ref_rms_verify", st0, roots3, (B, ld), R, Q, bytes(bad))[0]

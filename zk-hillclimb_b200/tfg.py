@@ -111,14 +111,18 @@ def _ser_tail(lug, batches):
 
 
 def claim_bind(engine, tr, ledger, cols):
-    """Bind callback of a lookup whose virtual key columns are affine in committed columns: claim those columns at the
-    lookup point (absorbed like any claim); the values ride in the proof as the member's extra slots."""
+    """Bind callback of a lookup whose virtual key columns are affine in (or broadcasts of) committed columns: claim those
+    columns at the lookup point (absorbed like any claim); the values ride in the proof as the member's extra slots.
+    cols: (column, root) or (column, root, f) with f mapping the lookup point to the column's point (a sub-range of its
+    coordinates for a broadcast column)."""
     def bind(pm, _yv):
         claims, extra = [], []
-        for c, root in cols:
-            y = engine.eval_h_gpu(c, np.ascontiguousarray(pm, dtype=np.uint64))
+        for ent in cols:
+            c, root = ent[0], ent[1]
+            pt = np.ascontiguousarray(ent[2](list(pm)) if len(ent) > 2 else pm, dtype=np.uint64)
+            y = engine.eval_h_gpu(c, pt)
             tr.absorb("hwl-y", struct.pack("<Q", y))
-            claims.append((c, root, np.ascontiguousarray(pm, dtype=np.uint64), y))
+            claims.append((c, root, pt, y))
             extra.append(y)
         return claims, extra
     return bind
@@ -712,3 +716,222 @@ def rope_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
     sl, sb = _ser_tail(lug, batches)
     return struct.pack("<II", wt["lp"], lh) + b"".join(r for _, r in C) + sl + _msgs(mE) + struct.pack("<I", len(yE)) + _u64(yE) + \
         _u64(yQ) + sb
+
+
+# ---------------------------------------------------------------------------------- RMSNorm (p3rms)
+RMS_DE = "XS XEB XMB XZ XEI SH PW Q RR SEL MO1 EI1 EO1 MO2 EI2 EO2".split()
+RMS_DB = "E FSEL EDIF S EPSA WD PLO PHI PDN PUP U1H U1L U2H U2L NR U16 QB PP MR HB TEB".split()
+RMS_DW = "GS GEB GMB GZ GEI".split()
+RD, RB_, RW = ({n: i for i, n in enumerate(names)} for names in (RMS_DE, RMS_DB, RMS_DW))
+RMS_TABS = ("R128", "R256", "R512", "R11", "R12", "R16", "SH512", "RM17", "RM8", "WD24", "EPSAT", "RSQT", "MUL7", "REXP")
+
+
+def rms_tables(art):
+    """p3rms::build_tables (p3_rmsnorm.cuh:95-146); the window of the row sum depends on the row length 2^ld."""
+    wmax = 17 + art["ld"]
+    if wmax > 30:
+        raise ValueError("rms: ld too large (WMAX > 30)")
+    j = np.arange(512, dtype=np.int64)
+    wd = np.where(np.arange(32) <= wmax, np.arange(32), 0).astype(np.int64)
+    j16 = np.arange(65536, dtype=np.int64)
+    return {"R128": range_tab(128), "R256": range_tab(256), "R512": range_tab(512), "R11": range_tab(1 << (wmax - 12)),
+            "R12": range_tab(4096), "R16": range_tab(65536), "SH512": make_table([j, 1 << np.minimum(j, 16)]),
+            "RM17": rm_table(16), "RM8": rm_table(wmax - 16),
+            "WD24": make_table([wd, np.where(wd > 0, 1 << np.maximum(wd - 1, 0), 0), 1 << wd, 1 << np.maximum(wd - 16, 0),
+                                1 << np.maximum(16 - wd, 0)]),
+            "EPSAT": make_table([j, art["epsa"].astype(np.int64)]),
+            "RSQT": make_table([32768 + (j16 & 32767), j16 >> 15, 128 + art["rsq_mr"].astype(np.int64), art["rsq_hb"].astype(np.int64)]),
+            "MUL7": mul7_tab(art), "REXP": rexp_tab()}
+
+
+def _bitlen(t, maxbits):
+    w = torch.zeros_like(t)
+    for j in range(maxbits):
+        w += (t >= (1 << j)).to(torch.int64)
+    return w
+
+
+def rms_witness(x, g, B, art, device="cpu", inverse=None):
+    """p3rms::gen_witness (p3_rmsnorm.cuh:225-377): canonical RMSNorm of B rows of d = 2^ld bf16 patterns with bf16 gains:
+    block-float sum of squares, eps, top-16-bit normalisation, table reciprocal square root, two table multiplies."""
+    from .hwl import enc, host_inverse
+    inverse = inverse or host_inverse
+    dev = torch.device(device)
+    I = torch.int64
+    t64 = lambda a: torch.as_tensor(np.asarray(a).astype(np.int64), device=dev)
+    ld, EMIN = art["ld"], art["EMIN"]
+    d = 1 << ld
+    Bpad = 1 << max(max(B, 2) - 1, 0).bit_length()
+    lb = Bpad.bit_length() - 1
+    shl = torch.bitwise_left_shift
+    xp = torch.zeros(Bpad, d, dtype=I, device=dev)
+    xp[:B] = t64(x).reshape(B, d)
+    gp = t64(g)
+    gs, geb, gmb, gz = _bf_fields(gp)
+    xs, xeb, xmb, xz = _bf_fields(xp)
+    pres = xz == 0
+    E = torch.where(pres, 2 * xeb, torch.zeros_like(xeb)).amax(dim=1).clamp(min=EMIN)
+    att = pres & (2 * xeb == E[:, None])
+    sel = att & (att.cumsum(dim=1) == 1)
+    fsel = (~att.any(dim=1)).to(I)
+    zero, one = torch.zeros_like(xeb), torch.ones_like(xeb)
+    sh = torch.where(pres, E[:, None] - 2 * xeb, zero)
+    shc = sh.clamp(max=16)
+    pw = torch.where(pres, shl(one, shc), one)
+    sq = (128 + xmb) * (128 + xmb)
+    q = torch.where(pres, sq >> shc, zero)
+    rr = torch.where(pres, sq - shl(q, shc), zero)
+    S = q.sum(dim=1)
+    epsa = t64(art["epsa"])[E.clamp(max=511)]
+    Sp = S + epsa
+    if bool(((Sp < 1) | (Sp >= (1 << (17 + ld)))).any()):
+        raise ValueError("rms: S' window")
+    wd = _bitlen(Sp, 40)
+    o1 = torch.ones_like(wd)
+    plo, phi = shl(o1, wd - 1), shl(o1, wd)
+    dn_s, up_s = (wd - 16).clamp(min=0), (16 - wd).clamp(min=0)
+    pdn, pup = shl(o1, dn_s), shl(o1, up_s)
+    u1, u2 = Sp - plo, phi - 1 - Sp
+    nr = torch.where(wd > 16, Sp & (pdn - 1), torch.zeros_like(Sp))
+    u16 = torch.where(wd > 16, Sp >> dn_s, shl(Sp, up_s))
+    Xexp = E + wd - (284 + ld)
+    qb = (Xexp + 400) >> 1
+    pp = Xexp + 400 - 2 * qb
+    rsj = (pp << 15) | (u16 - 32768)
+    mrfull, hb = 128 + t64(art["rsq_mr"])[rsj], t64(art["rsq_hb"])[rsj]
+    teb = 318 + hb - qb
+    if bool(((teb < 1) | (teb > 254)).any()):
+        raise ValueError("rms: rsqrt exp domain")
+    mo_t, ei_t = t64(art["mul_mo"]), t64(art["mul_einc"])
+    j1 = (xmb << 7) | (mrfull[:, None] - 128)
+    mo1, ei1 = 128 + mo_t[j1], ei_t[j1]
+    eo1 = torch.where(pres, xeb + teb[:, None] - 127 + ei1, one)
+    if bool(((eo1 < 1) | (eo1 > 254)).any()):
+        raise ValueError("rms: mul1 exp domain")
+    j2 = ((mo1 - 128) << 7) | gmb[None, :]
+    mo2, ei2 = 128 + mo_t[j2], ei_t[j2]
+    z2 = (xz | gz[None, :]) != 0
+    eo2 = torch.where(z2, one, eo1 + geb[None, :] - 127 + ei2)
+    if bool(((eo2 < 1) | (eo2 > 254)).any()):
+        raise ValueError("rms: mul2 exp domain")
+    y = ((xs ^ gs[None, :]) << 15) | torch.where(z2, zero, (eo2 << 7) | (mo2 - 128))
+    inv0 = lambda t: _inv_or0(t, inverse)
+    flat = lambda t: t.reshape(-1).contiguous()
+    de = [flat(t) for t in (xs, xeb, xmb, xz, inv0(xeb), sh, pw, q, enc(rr), sel.to(I), mo1, ei1, eo1, mo2, ei2, eo2)]
+    db = [E, fsel, E - EMIN, S, epsa, wd, plo, phi, pdn, pup, u1 >> 12, u1 & 4095, u2 >> 12, u2 & 4095, nr, u16, qb, pp, mrfull, hb, teb]
+    dw = [gs, geb, gmb, gz, inv0(geb)]
+    i32 = lambda t: flat(t).to(torch.int32)
+    lidx = [i32(xeb), i32(xmb), i32(sh), i32(pw - 1 + rr), i32(q), i32(j1), i32(j2), i32(eo1), i32(eo2), i32(geb), i32(gmb),
+            i32(E.clamp(max=511)), i32(wd), i32(u1 >> 12), i32(u1 & 4095), i32(u2 >> 12), i32(u2 & 4095), i32(pdn - 1 + nr), i32(rsj),
+            i32(E - EMIN), i32(qb), i32(teb)]
+    return {"B": B, "ld": ld, "d": d, "Bpad": Bpad, "lb": lb, "le": lb + ld, "xpat": flat(xp), "gpat": gp, "ypat": flat(y), "de": de,
+            "db": db, "dw": dw, "xmf": flat(128 + xmb), "mrf": flat(mrfull[:, None].expand(Bpad, d)), "gmf": flat((128 + gmb)[None, :].expand(Bpad, d)),
+            "lidx": lidx, "Y": y[:B].cpu().numpy().astype(np.uint16).reshape(-1)}
+
+
+def rms_commit_operands(engine, wt, R, col):
+    out = {}
+    for name, key in (("X", "xpat"), ("G", "gpat"), ("Y", "ypat")):
+        c = col(wt[key])
+        out[name] = (c, engine.commit_gpu_rootonly(c, R))
+    return out
+
+
+def rms_prove(engine, tr, wt, T, art, ops, R, Q, col, ctx=None, strict=True):
+    """p3rms::prove (p3_rmsnorm.cuh:527-735), non-zk.  Serialised RmsProof: u32 B ld | rde[16] rdb[21] rdw[5] | groups |
+    mDe yDe[16] yDeX yDeY yDeE yDeTEB yDeGS yDeGEB yDeGZ | mDb yDb[21] | mDw yDw[5] yDwG | yBS yBF | mBind yBXZ yBQ yBSEL | batches."""
+    from .ig import Ctx
+    own = ctx is None
+    ctx = ctx or Ctx()
+    lg = ctx.ledger
+    ld, lb, le = wt["ld"], wt["lb"], wt["le"]
+    tr.absorb("rms-dims", struct.pack("<IIII", wt["B"], ld, art["EMIN"], art["eps_bits"]))
+    for name in RMS_TABS:
+        tr.absorb("rms-tab", T[name]["id"])
+    tr.absorb("rms-X", ops["X"][1])
+    tr.absorb("rms-G", ops["G"][1])
+    tr.absorb("rms-Y", ops["Y"][1])
+    commit = lambda cols: [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in cols)]
+    CDe, CDb, CDw = commit(wt["de"]), commit(wt["db"]), commit(wt["dw"])
+    for label, cd in (("rms-ce", CDe), ("rms-cb", CDb), ("rms-cw", CDw)):
+        for _, root in cd:
+            tr.absorb(label, root)
+    e_, b_, w_ = (lambda n: CDe[RD[n]]), (lambda n: CDb[RB_[n]]), (lambda n: CDw[RW[n]])
+    xmf, mrf, gmf = ((col(wt[k]), None) for k in ("xmf", "mrf", "gmf"))
+    specs = [("R256", [e_("XEB")]), ("R128", [e_("XMB")]), ("SH512", [e_("SH"), e_("PW")]), ("RM17", [e_("PW"), e_("RR")]),
+             ("R16", [e_("Q")]), ("MUL7", [xmf, mrf, e_("MO1"), e_("EI1")]), ("MUL7", [e_("MO1"), gmf, e_("MO2"), e_("EI2")]),
+             ("REXP", [e_("EO1")]), ("REXP", [e_("EO2")]), ("R256", [w_("GEB")]), ("R128", [w_("GMB")]),
+             ("EPSAT", [b_("E"), b_("EPSA")]), ("WD24", [b_(n) for n in ("WD", "PLO", "PHI", "PDN", "PUP")]), ("R11", [b_("U1H")]),
+             ("R12", [b_("U1L")]), ("R11", [b_("U2H")]), ("R12", [b_("U2L")]), ("RM8", [b_("PDN"), b_("NR")]),
+             ("RSQT", [b_(n) for n in ("U16", "PP", "MR", "HB")]), ("R512", [b_("EDIF")]), ("R512", [b_("QB")]), ("REXP", [b_("TEB")])]
+    for i, (tab, W) in enumerate(specs):
+        ent = {"W": W, "idx": col(wt["lidx"][i]), "tab": T[tab]}
+        if i == 5:
+            ent["bind"] = claim_bind(engine, tr, lg, [e_("XMB"), b_("MR") + (lambda pm: pm[ld:le],)])
+        elif i == 6:
+            ent["bind"] = claim_bind(engine, tr, lg, [w_("GMB") + (lambda pm: pm[:ld],)])
+        ctx.luq.append(ent)
+    chal_vec = lambda n: [tr.chal() for _ in range(n)]
+    eq = lambda z: engine.build_eq_gpu(np.array(z, dtype=np.uint64))
+    claim = lambda c, z: claimc(engine, tr, lg, c[0], c[1], z)
+    v = Poly.var
+    # element domain: [E, X, Y, de[16], E row, TEB row, GS col, GEB col, GZ col]
+    zE = chal_vec(le)
+    lam = _powers(tr.chal(), 16)
+    c = lambda n: v(3 + RD[n])
+    Ebc, TEB, GS, GEB, GZ = (v(19 + k) for k in range(5))
+    nz = 1 - c("XZ")
+    z2 = c("XZ") + GZ - c("XZ") * GZ
+    xmfp = 128 + c("XMB")
+    sy = c("XS") + GS - 2 * c("XS") * GS
+    cons = [v(1) - (32768 * c("XS") + 128 * c("XEB") + c("XMB")), boolc(c("XS")), boolc(c("XZ")), c("XZ") * c("XEB"),
+            c("XEB") * c("XEI") - nz, c("Q") * c("PW") + c("RR") - nz * xmfp * xmfp, nz * (c("SH") + 2 * c("XEB") - Ebc),
+            c("XZ") * c("SH"), boolc(c("SEL")), c("SEL") * c("SH"), c("SEL") * c("XZ"),
+            nz * (c("EO1") - (c("XEB") + TEB + c("EI1") - 127)), c("XZ") * (c("EO1") - 1), z2 * (c("EO2") - 1),
+            (1 - z2) * (c("EO2") - (c("EO1") + GEB + c("EI2") - 127)),
+            v(2) - (32768 * sy + (1 - z2) * (128 * c("EO2") + c("MO2") - 128))]
+    terms, konst = zc_terms(cons, lam)
+    cols = [eq(zE), ops["X"][0], ops["Y"][0]] + [t for t, _ in CDe] + [engine.bcast_rows(b_("E")[0], ld), engine.bcast_rows(b_("TEB")[0], ld),
+            engine.bcast_cols(w_("GS")[0], lb), engine.bcast_cols(w_("GEB")[0], lb), engine.bcast_cols(w_("GZ")[0], lb)]
+    rE, mDe, _ = engine.sc_prove_zc(tr, "rms-scE", cols, terms, konst)
+    rE = [int(x) for x in rE]
+    yDeX, yDeY = claim(ops["X"], rE), claim(ops["Y"], rE)
+    yDe = [claim(cd, rE) for cd in CDe]
+    rb, ri = rE[ld:le], rE[:ld]
+    yDeT = [claim(b_("E"), rb), claim(b_("TEB"), rb), claim(w_("GS"), ri), claim(w_("GEB"), ri), claim(w_("GZ"), ri)]
+    # row domain: [E, db[21]]
+    zB = chal_vec(lb)
+    lamB = _powers(tr.chal(), 10)
+    r_ = lambda n: v(1 + RB_[n])
+    Sp = r_("S") + r_("EPSA")
+    consB = [boolc(r_("FSEL")), r_("FSEL") * r_("EDIF"), r_("E") - (art["EMIN"] + r_("EDIF")), boolc(r_("PP")), boolc(r_("HB")),
+             r_("E") + r_("WD") + 400 - (2 * r_("QB") + r_("PP") + (284 + ld)), r_("TEB") + r_("QB") - (318 + r_("HB")),
+             Sp - r_("PLO") - (4096 * r_("U1H") + r_("U1L")), r_("PHI") - 1 - Sp - (4096 * r_("U2H") + r_("U2L")),
+             r_("U16") * r_("PDN") + r_("NR") - Sp * r_("PUP")]
+    terms, konst = zc_terms(consB, lamB)
+    rB, mDb, _ = engine.sc_prove_zc(tr, "rms-scB", [eq(zB)] + [t for t, _ in CDb], terms, konst)
+    rB = [int(x) for x in rB]
+    yDb = [claim(cd, rB) for cd in CDb]
+    # gain domain: [E, G, dw[5]]
+    zW = chal_vec(ld)
+    lamW = _powers(tr.chal(), 5)
+    consW = [v(1) - (32768 * v(2) + 128 * v(3) + v(4)), boolc(v(2)), boolc(v(5)), v(5) * v(3), v(3) * v(6) - (1 - v(5))]
+    terms, konst = zc_terms(consW, lamW)
+    rW, mDw, _ = engine.sc_prove_zc(tr, "rms-scW", [eq(zW), ops["G"][0]] + [t for t, _ in CDw], terms, konst)
+    rW = [int(x) for x in rW]
+    yDwG = claim(ops["G"], rW)
+    yDw = [claim(cd, rW) for cd in CDw]
+    # row binding: sum_i (1 - XZ) Q = S and sum_i SEL = 1 - FSEL
+    z2r = chal_vec(lb)
+    yBS, yBF = claim(b_("S"), z2r), claim(b_("FSEL"), z2r)
+    lam1, lam2 = tr.chal(), tr.chal()
+    terms, konst = zc_terms([(1 - v(1)) * v(2), v(3)], [lam1, lam2])
+    rS, mBind, _ = engine.sc_prove_zc(tr, "rms-scS", [engine.bcast_rows(eq(z2r), ld), e_("XZ")[0], e_("Q")[0], e_("SEL")[0]], terms, konst)
+    rS = [int(x) for x in rS]
+    yB = [claim(e_("XZ"), rS), claim(e_("Q"), rS), claim(e_("SEL"), rS)]
+    lug, batches = _tail(engine, tr, ctx, R, Q, "rms-bo", strict) if own else ([], [])
+    sl, sb = _ser_tail(lug, batches)
+    out = struct.pack("<II", wt["B"], ld) + b"".join(r for cd in (CDe, CDb, CDw) for _, r in cd) + sl
+    out += _msgs(mDe) + _u64(yDe) + _u64([yDeX, yDeY] + yDeT) + _msgs(mDb) + _u64(yDb) + _msgs(mDw) + _u64(yDw) + _u64([yDwG])
+    out += _u64([yBS, yBF]) + _msgs(mBind) + _u64(yB)
+    return out + sb
