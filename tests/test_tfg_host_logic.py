@@ -189,3 +189,40 @@ def test_rmsnorm_accepted_by_reference_verifier(orc, ref, zk, B, ld):
     bad = bytearray(pf)
     bad[len(pf) // 3] ^= 1
     assert not ref_verify_roots(ref, "ref_rms_verify", st0, roots3, (B, ld), R, Q, bytes(bad))[0]
+
+
+@pytest.mark.parametrize("B,ln", [(2, 2), (4, 3)])
+def test_softmax_accepted_by_reference_verifier(orc, ref, zk, B, ln):
+    R, Q = 1, 24
+    tfg = zk.tfg
+    art = load_art(ref, zk)
+    T = tfg.smx_tables(art)
+    n = 1 << ln
+    rng = np.random.default_rng(B + ln)
+    s = bf16_patterns(rng, B * n, 2.0).reshape(B, n)
+    msk = (np.arange(n)[None, :] <= (np.arange(B)[:, None] % n)).astype(np.uint8)        # causal rows
+    if B > 2:
+        msk[B - 1] = 0                                                                      # a row with every lane masked
+    wt = tfg.smx_witness(s.reshape(-1), msk.reshape(-1), B, ln, art)
+    pf32 = (wt["P"].astype(np.uint32) << 16).view(np.float32).reshape(B, n)
+    sf = (s.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    for b in range(B):
+        if msk[b].any():
+            e = np.where(msk[b] != 0, np.exp(sf[b] - sf[b][msk[b] != 0].max()), 0.0)
+            assert np.allclose(pf32[b], e / e.sum(), rtol=0.04, atol=1e-3)
+        else:
+            assert (wt["P"].reshape(B, n)[b] == 0).all()
+    eng = OracleGadgetEngine(orc)
+    ops = tfg.smx_commit_operands(eng, wt, R, host_col)
+    tr = zk.Transcript("smx")
+    pf = tfg.smx_prove(eng, tr, wt, T, art, ops, R, Q, host_col)
+    roots2 = [ops["S"][1], ops["P"][1]]
+    st0 = zk.Transcript("smx").state
+    ok, st = ref_verify_roots(ref, "ref_smx_verify", st0, roots2, (B, n, 23), R, Q, pf, pre=(msk.reshape(-1),))
+    assert ok and st == tr.state
+    bad_mask = msk.copy()
+    bad_mask[0, n - 1] ^= 1
+    assert not ref_verify_roots(ref, "ref_smx_verify", st0, roots2, (B, n, 23), R, Q, pf, pre=(bad_mask.reshape(-1),))[0]
+    bad = bytearray(pf)
+    bad[len(pf) // 3] ^= 1
+    assert not ref_verify_roots(ref, "ref_smx_verify", st0, roots2, (B, n, 23), R, Q, bytes(bad), pre=(msk.reshape(-1),))[0]

@@ -935,3 +935,228 @@ def rms_prove(engine, tr, wt, T, art, ops, R, Q, col, ctx=None, strict=True):
     out += _msgs(mDe) + _u64(yDe) + _u64([yDeX, yDeY] + yDeT) + _msgs(mDb) + _u64(yDb) + _msgs(mDw) + _u64(yDw) + _u64([yDwG])
     out += _u64([yBS, yBF]) + _msgs(mBind) + _u64(yB)
     return out + sb
+
+
+# ---------------------------------------------------------------------------------- masked softmax (p3smx)
+SMX_FIXED = "XM X2M DP DK SEL1 EXV EEB EMB EZ EZI SH2 PW2 Q2 RR2 SEL2 MO3 EI3 EO3".split()
+SM = {n: i for i, n in enumerate(SMX_FIXED)}
+SM_A = len(SMX_FIXED)
+NDE2 = SM_A + NBA                          # 73
+SMX_DB = "KMAX MXP E EDIF FSEL S WD PLO PHI PDN PUP U1H U1L U2H U2L NR U16 MRC HBC REB".split()
+SB = {n: i for i, n in enumerate(SMX_DB)}
+SMX_XT = ("R11", "R12", "R16", "SH512", "WD24", "RM8", "MUL7", "EXPT", "RCPT")
+N_SM_DE = 22 + N_BA_C
+
+
+def smx_tables(art, wmax=23):
+    """p3smx::build_tables (p3_softmax.cuh:95-138): the add block's tables plus the denominator / exp / reciprocal tables;
+    rows of 2^ln lanes need wmax >= 16 + ln."""
+    if not 23 <= wmax <= 30:
+        raise ValueError("smx: wmax out of [23,30]")
+    T = bfa_tables()
+    j = np.arange(512, dtype=np.int64)
+    wd = np.where(np.arange(32) <= wmax, np.arange(32), 0).astype(np.int64)
+    j16, j15 = np.arange(65536, dtype=np.int64), np.arange(32768, dtype=np.int64)
+    T.update({"wmax": wmax, "R11": range_tab(1 << (wmax - 12)), "R12": range_tab(4096), "R16": range_tab(65536),
+              "SH512": make_table([j, 1 << np.minimum(j, 16)]),
+              "WD24": make_table([wd, np.where(wd > 0, 1 << np.maximum(wd - 1, 0), 0), 1 << wd, 1 << np.maximum(wd - 16, 0),
+                                  1 << np.maximum(16 - wd, 0)]),
+              "RM8": rm_table(wmax - 16), "MUL7": mul7_tab(art), "EXPT": make_table([j16, art["exp_tab"].astype(np.int64)]),
+              "RCPT": make_table([32768 + j15, 128 + art["rcp_mr"].astype(np.int64), art["rcp_hb"].astype(np.int64)])})
+    return T
+
+
+def smx_witness(s, msk, B, ln, art, device="cpu", inverse=None):
+    """p3smx::gen_witness (p3_softmax.cuh:213-398): canonical masked softmax of B rows of n = 2^ln bf16 scores (masked lanes
+    output +0 and take no part in the maximum or the sum): key-order maximum, one bf16 subtract block, table exp, block-float
+    denominator, table reciprocal, table multiply."""
+    from .hwl import host_inverse
+    inverse = inverse or host_inverse
+    dev = torch.device(device)
+    I = torch.int64
+    t64 = lambda a: torch.as_tensor(np.asarray(a).astype(np.int64), device=dev)
+    n = 1 << ln
+    Bpad = 1 << max(max(B, 2) - 1, 0).bit_length()
+    lb = Bpad.bit_length() - 1
+    EMIN = art["sm_emin"]
+    shl = torch.bitwise_left_shift
+    sp = torch.zeros(Bpad, n, dtype=I, device=dev)
+    mk = torch.zeros(Bpad, n, dtype=I, device=dev)
+    sp[:B] = t64(s).reshape(B, n)
+    mk[:B] = (t64(msk).reshape(B, n) != 0).to(I)
+    M = mk != 0
+    sgn, eb, mb, _ = _bf_fields(sp)
+    key = 32768 - sgn + (1 - 2 * sgn) * (128 * eb + mb)
+    kq = torch.where(M, key, torch.full_like(key, -1))
+    kmax_all = kq.amax(dim=1)
+    emp = kmax_all < 0
+    attk = M & (key == kmax_all[:, None])
+    sel1 = attk & (attk.cumsum(dim=1) == 1)
+    mxp = (sel1.to(I) * sp).sum(dim=1)
+    kmax = torch.where(emp, torch.zeros_like(kmax_all), kmax_all)
+    zero, one = torch.zeros_like(sp), torch.ones_like(sp)
+    xm = torch.where(M, sp, zero)
+    x2m = torch.where(M, (mxp ^ 0x8000)[:, None].expand(Bpad, n), zero)
+    blk, blu, dp = ba_fill(xm.reshape(-1), x2m.reshape(-1), inverse)
+    dp = dp.reshape(Bpad, n)
+    dk = torch.where(M, kmax[:, None] - key, zero)
+    xv = t64(art["exp_tab"])[dp]
+    if bool((((xv >> 15) & 1) != 0).any()):
+        raise ValueError("smx: negative exp")
+    eeb, emb = (xv >> 7) & 255, xv & 127
+    ez = eeb == 0
+    pres = M & ~ez
+    E = torch.where(pres, eeb + 8, zero).amax(dim=1).clamp(min=EMIN)
+    att2 = pres & (eeb + 8 == E[:, None])
+    sel2 = att2 & (att2.cumsum(dim=1) == 1)
+    fsel = (~att2.any(dim=1)).to(I)
+    sh = torch.where(pres, E[:, None] - (eeb + 8), zero)
+    shc = sh.clamp(max=16)
+    pw = torch.where(pres, shl(one, shc), one)
+    sq = (128 + emb) << 8
+    q = torch.where(pres, sq >> shc, zero)
+    rr = torch.where(pres, sq - shl(q, shc), zero)
+    S = q.sum(dim=1)
+    wcap = min(max(16 + ln, 23), 30)
+    if bool((~emp & ((S < 1) | (S >= (1 << wcap)))).any()):
+        raise ValueError("smx: S window")
+    Ssafe = torch.where(emp, torch.ones_like(S), S)
+    wd = _bitlen(Ssafe, 40)
+    o1 = torch.ones_like(wd)
+    dn_s, up_s = (wd - 16).clamp(min=0), (16 - wd).clamp(min=0)
+    plo, phi, pdn, pup = shl(o1, wd - 1), shl(o1, wd), shl(o1, dn_s), shl(o1, up_s)
+    u1, u2 = Ssafe - plo, phi - 1 - Ssafe
+    nr = torch.where(wd > 16, Ssafe & (pdn - 1), torch.zeros_like(S))
+    u16 = torch.where(wd > 16, Ssafe >> dn_s, shl(Ssafe, up_s))
+    ri = u16 - 32768
+    mrc, hbc = 128 + t64(art["rcp_mr"])[ri], t64(art["rcp_hb"])[ri]
+    reb = 277 + hbc - E - wd
+    if bool((~emp & ((reb < 1) | (reb > 254))).any()):
+        raise ValueError("smx: recip exp domain")
+    # rows without any participating lane: the benign constants of the reference (normalisation gated off)
+    gate = lambda t, dflt: torch.where(emp, torch.full_like(t, dflt), t)
+    wd, plo, phi, pdn, pup = gate(wd, 1), gate(plo, 1), gate(phi, 2), gate(pdn, 1), gate(pup, 1 << 15)
+    u1, u2, nr, u16, mrc, hbc, reb = gate(u1, 0), gate(u2, 0), gate(nr, 0), gate(u16, 32768), gate(mrc, 128), gate(hbc, 1), gate(reb, 1)
+    mj = (emb << 7) | (mrc[:, None] - 128)
+    mo, ei = 128 + t64(art["mul_mo"])[mj], t64(art["mul_einc"])[mj]
+    eo = torch.where(pres, eeb + reb[:, None] - 127 + ei, one)
+    if bool(((eo < 1) | (eo > 254)).any()):
+        raise ValueError("smx: out exp domain")
+    p = torch.where(pres, (eo << 7) | (mo - 128), zero)
+    flat = lambda t: t.reshape(-1).contiguous()
+    de = [flat(t) for t in (xm, x2m, dp, dk, sel1.to(I), xv, eeb, emb, ez.to(I), _inv_or0(eeb, inverse), sh, pw, q, rr, sel2.to(I), mo, ei, eo)] + blk
+    db = [kmax, mxp, E, E - EMIN, fsel, S, wd, plo, phi, pdn, pup, u1 >> 12, u1 & 4095, u2 >> 12, u2 & 4095, nr, u16, mrc, hbc, reb]
+    i32 = lambda t: flat(t).to(torch.int32)
+    lidx = [i32(dk), i32(dp), i32(eeb), i32(emb), i32(sh), i32(pw - 1 + rr), i32(q), i32(mj), i32(eo),
+            i32(E - EMIN), i32(wd), i32(u1 >> 12), i32(u1 & 4095), i32(u2 >> 12), i32(u2 & 4095), i32(pdn - 1 + nr), i32(u16 - 32768),
+            i32(reb)] + blu
+    return {"B": B, "ln": ln, "n": n, "Bpad": Bpad, "lb": lb, "le": lb + ln, "spat": flat(sp), "ppat": flat(p), "mskc": flat(mk),
+            "empc": emp.to(I), "de": de, "db": db, "lidx": lidx, "emf": flat(128 + emb), "mrcf": flat(mrc[:, None].expand(Bpad, n)),
+            "P": p[:B].cpu().numpy().astype(np.uint16).reshape(-1)}
+
+
+def smx_commit_operands(engine, wt, R, col):
+    out = {}
+    for name, key in (("S", "spat"), ("P", "ppat")):
+        c = col(wt[key])
+        out[name] = (c, engine.commit_gpu_rootonly(c, R))
+    return out
+
+
+def smx_prove(engine, tr, wt, T, art, ops, R, Q, col, ctx=None, strict=True):
+    """p3smx::prove (p3_softmax.cuh:529-713), non-zk.  Serialised SmxProof: u32 B ln | rde[73] rdb[20] | groups | mDe |
+    u32 73, yDe | yDeS yDeP yDeKM yDeMX yDeE yDeRB | mDb yDb[20] | yBF yBS | mBind yBSEL1 yBSEL2 yBQ2 | batches."""
+    from .ig import Ctx
+    own = ctx is None
+    ctx = ctx or Ctx()
+    lg = ctx.ledger
+    ln, lb, le = wt["ln"], wt["lb"], wt["le"]
+    if 16 + ln > T["wmax"]:
+        raise ValueError("smx: tables too small (need wmax >= 16+ln)")
+    tr.absorb("smx-dims", struct.pack("<III", wt["B"], ln, art["sm_emin"]))
+    for name in BT_NAMES + SMX_XT:
+        tr.absorb("smx-tab", T[name]["id"])
+    tr.absorb("smx-msk", wt["mskc"].cpu().numpy().astype(np.uint64).tobytes())
+    tr.absorb("smx-S", ops["S"][1])
+    tr.absorb("smx-P", ops["P"][1])
+    commit = lambda cols: [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in cols)]
+    CDe, CDb = commit(wt["de"]), commit(wt["db"])
+    for _, root in CDe:
+        tr.absorb("smx-ce", root)
+    for _, root in CDb:
+        tr.absorb("smx-cb", root)
+    e_, b_ = (lambda nm: CDe[SM[nm]]), (lambda nm: CDb[SB[nm]])
+    emf, mrcf = (col(wt["emf"]), None), (col(wt["mrcf"]), None)
+    specs = [("R16", [e_("DK")]), ("EXPT", [e_("DP"), e_("EXV")]), ("R256", [e_("EEB")]), ("R128", [e_("EMB")]),
+             ("SH512", [e_("SH2"), e_("PW2")]), ("RM17", [e_("PW2"), e_("RR2")]), ("R16", [e_("Q2")]),
+             ("MUL7", [emf, mrcf, e_("MO3"), e_("EI3")]), ("REXP", [e_("EO3")]), ("R512", [b_("EDIF")]),
+             ("WD24", [b_(nm) for nm in ("WD", "PLO", "PHI", "PDN", "PUP")]), ("R11", [b_("U1H")]), ("R12", [b_("U1L")]),
+             ("R11", [b_("U2H")]), ("R12", [b_("U2L")]), ("RM8", [b_("PDN"), b_("NR")]), ("RCPT", [b_("U16"), b_("MRC"), b_("HBC")]),
+             ("REXP", [b_("REB")])]
+    specs += [(tab, [CDe[SM_A + BA[nm]] for nm in names]) for tab, names in BA_LU]
+    for i, (tab, W) in enumerate(specs):
+        ent = {"W": W, "idx": col(wt["lidx"][i]), "tab": T[tab]}
+        if i == 7:
+            ent["bind"] = claim_bind(engine, tr, lg, [e_("EMB"), b_("MRC") + (lambda pm: pm[ln:le],)])
+        ctx.luq.append(ent)
+    chal_vec = lambda k: [tr.chal() for _ in range(k)]
+    eq = lambda z: engine.build_eq_gpu(np.array(z, dtype=np.uint64))
+    claim = lambda c, z: claimc(engine, tr, lg, c[0], c[1], z)
+    v = Poly.var
+    # element domain: [E, S, P, MSK, de[73], KMAX row, MXP row, E row, REB row]
+    zE = chal_vec(le)
+    lam = _powers(tr.chal(), N_SM_DE)
+    c = lambda nm: v(4 + SM[nm])
+    cA = {nm: v(4 + SM_A + i) for i, nm in enumerate(BA_COLS)}
+    Mv = v(3)
+    KM, MX, Eb, RBv = (v(4 + NDE2 + k) for k in range(4))
+    nM, MEZ = 1 - Mv, Mv * c("EZ")
+    absent = 1 - Mv + MEZ
+    mag = 128 * cA["E1"] + cA["M1"]
+    key = 32768 - cA["S1"] + mag - 2 * cA["S1"] * mag
+    shrel = c("SH2") + c("EEB") + 8 - Eb
+    sqv = 256 * (128 + c("EMB"))
+    eo3rel = c("EO3") + 127 - (c("EEB") + RBv + c("EI3"))
+    pat = 128 * c("EO3") + c("MO3") - 128
+    cons = [c("XM") - Mv * v(1), nM * c("X2M"), Mv * (MX - (32768 - 32768 * cA["S2"] + 128 * cA["E2"] + cA["M2"])),
+            Mv * (KM - (key + c("DK"))), nM * c("DK"), boolc(c("SEL1")), c("SEL1") * nM, c("SEL1") * c("DK"),
+            c("SEL1") * (c("XM") - MX), c("EXV") - (128 * c("EEB") + c("EMB")), boolc(c("EZ")), c("EZ") * c("EEB"),
+            c("EEB") * c("EZI") - (1 - c("EZ")), c("SH2") * absent, Mv * shrel - MEZ * shrel,
+            c("Q2") * c("PW2") + c("RR2") - (Mv * sqv - MEZ * sqv), boolc(c("SEL2")), c("SEL2") * c("SH2"), c("SEL2") * absent,
+            Mv * eo3rel - MEZ * eo3rel, absent * (c("EO3") - 1), v(2) - (Mv * pat - MEZ * pat)]
+    cons += ba_constraints(cA, c("XM"), c("X2M"), c("DP"))
+    terms, konst = zc_terms(cons, lam)
+    cols = [eq(zE), ops["S"][0], ops["P"][0], col(wt["mskc"])] + [t for t, _ in CDe] + \
+        [engine.bcast_rows(b_(nm)[0], ln) for nm in ("KMAX", "MXP", "E", "REB")]
+    rE, mDe, _ = engine.sc_prove_zc(tr, "smx-scE", cols, terms, konst)
+    rE = [int(x) for x in rE]
+    yDeS, yDeP = claim(ops["S"], rE), claim(ops["P"], rE)
+    yDe = [claim(cd, rE) for cd in CDe]
+    rb = rE[ln:le]
+    yDeR = [claim(b_(nm), rb) for nm in ("KMAX", "MXP", "E", "REB")]
+    # row domain: [E, EMP, db[20]]
+    zB = chal_vec(lb)
+    lamB = _powers(tr.chal(), 7)
+    r_ = lambda nm: v(2 + SB[nm])
+    nE = 1 - v(1)
+    consB = [boolc(r_("FSEL")), r_("FSEL") * r_("EDIF"), r_("E") - (art["sm_emin"] + r_("EDIF")),
+             nE * (r_("S") - r_("PLO") - (4096 * r_("U1H") + r_("U1L"))), nE * (r_("PHI") - 1 - r_("S") - (4096 * r_("U2H") + r_("U2L"))),
+             nE * (r_("U16") * r_("PDN") + r_("NR") - r_("S") * r_("PUP")), nE * (r_("REB") + r_("E") + r_("WD") - (277 + r_("HBC")))]
+    terms, konst = zc_terms(consB, lamB)
+    rB, mDb, _ = engine.sc_prove_zc(tr, "smx-scB", [eq(zB), col(wt["empc"])] + [t for t, _ in CDb], terms, konst)
+    rB = [int(x) for x in rB]
+    yDb = [claim(cd, rB) for cd in CDb]
+    # row binding: sum_j SEL1 = 1 - EMP, sum_j SEL2 = 1 - FSEL, sum_j Q2 = S
+    z2 = chal_vec(lb)
+    yBF, yBS = claim(b_("FSEL"), z2), claim(b_("S"), z2)
+    lam3 = [tr.chal(), tr.chal(), tr.chal()]
+    terms, konst = zc_terms([v(1), v(2), v(3)], lam3)
+    rS, mBind, _ = engine.sc_prove_zc(tr, "smx-scS", [engine.bcast_rows(eq(z2), ln), e_("SEL1")[0], e_("SEL2")[0], e_("Q2")[0]], terms, konst)
+    rS = [int(x) for x in rS]
+    yB = [claim(e_("SEL1"), rS), claim(e_("SEL2"), rS), claim(e_("Q2"), rS)]
+    lug, batches = _tail(engine, tr, ctx, R, Q, "smx-bo", strict) if own else ([], [])
+    sl, sb = _ser_tail(lug, batches)
+    out = struct.pack("<II", wt["B"], ln) + b"".join(r for cd in (CDe, CDb) for _, r in cd) + sl
+    out += _msgs(mDe) + struct.pack("<I", len(yDe)) + _u64(yDe) + _u64([yDeS, yDeP] + yDeR) + _msgs(mDb) + _u64(yDb)
+    out += _u64([yBF, yBS]) + _msgs(mBind) + _u64(yB)
+    return out + sb
