@@ -29,6 +29,7 @@
 #include "p3_quant.cuh"
 #include "p3_rope.cuh"
 #include "p3_softmax.cuh"
+#include "p3_transformer.cuh"
 
 namespace {
 fs::Transcript tr_from(const uint8_t st[32]) {
@@ -702,9 +703,16 @@ struct HwlWriter {
     std::vector<uint8_t> b;
     std::vector<uint8_t> tmp = std::vector<uint8_t>((size_t)256 << 20);
     void raw(const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); }
+    void fail() {}
     void u32(uint32_t& v) { raw(&v, 4); }
     void msgs(std::vector<p3hwl::Msg5>& m) { uint32_t n = (uint32_t)m.size(); raw(&n, 4); raw(m.data(), (size_t)n * 40); }
     void vec(std::vector<gl_t>& v) { uint32_t n = (uint32_t)v.size(); raw(&n, 4); raw(v.data(), (size_t)n * 8); }
+    void vec16(std::vector<uint16_t>& v) { uint32_t n = (uint32_t)v.size(); raw(&n, 4); raw(v.data(), (size_t)n * 2); }
+    template <typename PF, typename WALK> void sub(PF& pf, WALK walk) {      // length-prefixed nested proof
+        HwlWriter w2;
+        walk(w2, pf);
+        uint32_t n = (uint32_t)w2.b.size(); raw(&n, 4); raw(w2.b.data(), n);
+    }
     void groups(std::vector<p3lu::GroupProof>& g) {
         uint32_t ng = (uint32_t)g.size(); raw(&ng, 4);
         for (auto& x : g) { uint32_t n = (uint32_t)lu_serialize(x, tmp.data(), tmp.size()); raw(&n, 4); raw(tmp.data(), n); }
@@ -717,6 +725,7 @@ struct HwlWriter {
 struct HwlReader {
     const uint8_t* p; const uint8_t* end; bool ok = true;
     bool need(size_t n) { if (!ok || (size_t)(end - p) < n) ok = false; return ok; }
+    void fail() { ok = false; }
     void raw(void* d, size_t n) { if (need(n)) { memcpy(d, p, n); p += n; } }
     void u32(uint32_t& v) { raw(&v, 4); }
     void msgs(std::vector<p3hwl::Msg5>& m) {
@@ -726,8 +735,21 @@ struct HwlReader {
     }
     void vec(std::vector<gl_t>& v) {
         uint32_t n = 0; u32(n);
-        if (!ok || n > 4096 || !need((size_t)n * 8)) { ok = false; return; }
+        if (!ok || n > (1u << 20) || !need((size_t)n * 8)) { ok = false; return; }
         v.resize(n); raw(v.data(), (size_t)n * 8);
+    }
+    void vec16(std::vector<uint16_t>& v) {
+        uint32_t n = 0; u32(n);
+        if (!ok || !need((size_t)n * 2)) { ok = false; return; }
+        v.resize(n); raw(v.data(), (size_t)n * 2);
+    }
+    template <typename PF, typename WALK> void sub(PF& pf, WALK walk) {
+        uint32_t n = 0; u32(n);
+        if (!need(n)) return;
+        HwlReader r2{p, p + n};
+        walk(r2, pf);
+        if (!r2.ok || r2.p != r2.end) { ok = false; return; }
+        p += n;
     }
     void groups(std::vector<p3lu::GroupProof>& g) {
         uint32_t ng = 0; u32(ng);
@@ -854,6 +876,53 @@ void smx_walk(IO& io, p3smx::SmxProof& pf) {
     io.msgs(pf.mDb); io.raw(pf.yDb, sizeof pf.yDb);
     io.raw(&pf.yBF, 8); io.raw(&pf.yBS, 8);
     io.msgs(pf.mBind); io.raw(&pf.yBSEL1, 8); io.raw(&pf.yBSEL2, 8); io.raw(&pf.yBQ2, 8);
+    io.batches(pf.batches);
+}
+// p3tf::TfProof <-> bytes: 6 x u32 dims | length-prefixed sub-proofs in proving order | roots rX0 rRmsY[2] rCodes[] rScales[]
+//   rMX[] rMW[] rRopeQ[] rRopeO[] rSmP[] rVtX[] rAtX rRes1 rSwM rOut | per matmul u32 count + bf16 outputs | groups |
+//   u32 count + seam values | batches
+template <typename IO>
+void tf_walk(IO& io, p3tf::TfProof& pf, bool reading) {
+    io.u32(pf.seq); io.u32(pf.d); io.u32(pf.nh); io.u32(pf.dh); io.u32(pf.dff); io.u32(pf.batch);
+    p3tf::Config c; c.seq = pf.seq; c.d = pf.d; c.nh = pf.nh; c.dh = pf.dh; c.dff = pf.dff; c.batch = pf.batch;
+    if (reading) {
+        if (!c.pow2() || c.A() > 4096) { io.fail(); return; }
+        pf.qn.resize(c.nqn()); pf.mm.resize(c.nmm()); pf.rp.resize(2 * c.A()); pf.sm.resize(c.A());
+        pf.rCodes.resize(c.nqn()); pf.rScales.resize(c.nqn()); pf.rMX.resize(c.nmm()); pf.rMW.resize(c.nmm());
+        pf.rRopeQ.resize(2 * c.A()); pf.rRopeO.resize(2 * c.A()); pf.rSmP.resize(c.A()); pf.rVtX.resize(c.A());
+        pf.mmY.resize(c.nmm());
+    }
+    auto RMS = [&](p3rms::RmsProof& x) { io.sub(x, [](auto& i2, p3rms::RmsProof& y) { rms_walk(i2, y); }); };
+    auto QN = [&](p3qnt::QntProof& x) { io.sub(x, [](auto& i2, p3qnt::QntProof& y) { qnt_walk(i2, y); }); };
+    auto MM = [&](p3hwl::LayerProof& x) { io.sub(x, [](auto& i2, p3hwl::LayerProof& y) { hwl_walk(i2, y); }); };
+    auto RP = [&](p3rope::RopeProof& x) { io.sub(x, [](auto& i2, p3rope::RopeProof& y) { rope_walk(i2, y); }); };
+    auto SMX = [&](p3smx::SmxProof& x) { io.sub(x, [](auto& i2, p3smx::SmxProof& y) { smx_walk(i2, y); }); };
+    auto BFA = [&](p3bfa::BfaProof& x) { io.sub(x, [](auto& i2, p3bfa::BfaProof& y) { bfa_walk(i2, y); }); };
+    auto SWG = [&](p3swg::SwgProof& x) { io.sub(x, [](auto& i2, p3swg::SwgProof& y) { swg_walk(i2, y); }); };
+    RMS(pf.rms[0]); QN(pf.qn[p3tf::QN_H1]);
+    MM(pf.mm[p3tf::MM_WQ]); MM(pf.mm[p3tf::MM_WK]); MM(pf.mm[p3tf::MM_WV]);
+    for (uint32_t a = 0; a < c.A(); a++) {
+        RP(pf.rp[2 * a]); RP(pf.rp[2 * a + 1]);
+        QN(pf.qn[c.qnRQ(a)]); QN(pf.qn[c.qnRK(a)]); MM(pf.mm[c.mmQK(a)]);
+        SMX(pf.sm[a]);
+        QN(pf.qn[c.qnPB(a)]); QN(pf.qn[c.qnVT(a)]); MM(pf.mm[c.mmPV(a)]);
+    }
+    QN(pf.qn[c.qnAT()]); MM(pf.mm[c.mmWO()]); BFA(pf.res[0]); RMS(pf.rms[1]); QN(pf.qn[c.qnH2()]);
+    MM(pf.mm[c.mmWG()]); MM(pf.mm[c.mmWU()]); SWG(pf.sw); QN(pf.qn[c.qnSW()]); MM(pf.mm[c.mmWD()]); BFA(pf.res[1]);
+    auto H = [&](p3fri::Hash& h) { io.raw(h.data(), 32); };
+    H(pf.rX0); H(pf.rRmsY[0]); H(pf.rRmsY[1]);
+    for (auto& h : pf.rCodes) H(h);
+    for (auto& h : pf.rScales) H(h);
+    for (auto& h : pf.rMX) H(h);
+    for (auto& h : pf.rMW) H(h);
+    for (auto& h : pf.rRopeQ) H(h);
+    for (auto& h : pf.rRopeO) H(h);
+    for (auto& h : pf.rSmP) H(h);
+    for (auto& h : pf.rVtX) H(h);
+    H(pf.rAtX); H(pf.rRes1); H(pf.rSwM); H(pf.rOut);
+    for (auto& y : pf.mmY) io.vec16(y);
+    io.groups(pf.lug);
+    io.vec(pf.seam);
     io.batches(pf.batches);
 }
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
@@ -2066,6 +2135,37 @@ int ref_smx_verify(uint8_t st[32], const uint8_t* mask, const uint8_t* roots2, u
             for (int i = 0; i < 2; i++) memcpy(h[i].data(), roots2 + 32 * i, 32);
             std::vector<uint8_t> m(mask, mask + (size_t)B * n);
             ok = p3smx::verify(tr, T, tf_art(), pf, m, h[0], h[1], B, n, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
+}
+
+// p3tf::verify (host only) of one composed fp8 transformer layer.  dims: seq d nh dh dff batch; x0 / out: T*d bf16 patterns;
+// rX0: root of the committed input; wroots: 16 roots (7 weight codes, 7 weight scales, g1, g2); cos / sin: seq*dh/2 patterns
+int ref_tf_verify(uint8_t st[32], const uint32_t dims[6], const uint16_t* x0, const uint8_t* rX0, const uint8_t* wroots,
+                  const uint16_t* cosp, const uint16_t* sinp, const uint16_t* outp, uint32_t smx_wmax, uint32_t R, uint32_t Q,
+                  const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3tf::TfProof pf;
+        HwlReader rd{proof, proof + len};
+        tf_walk(rd, pf, true);
+        if (rd.ok && rd.p == rd.end) {
+            p3tf::Config c; c.seq = dims[0]; c.d = dims[1]; c.nh = dims[2]; c.dh = dims[3]; c.dff = dims[4]; c.batch = dims[5];
+            static p3tf::TfTables T; static int64_t t_ld = -1; static uint32_t t_w = 0;
+            if (t_ld != tf_art().ld || t_w != smx_wmax) { T = p3tf::build_tables(tf_art(), smx_wmax); t_ld = tf_art().ld; t_w = smx_wmax; }
+            p3tf::WeightRoots wr;
+            for (int i = 0; i < p3tf::NW; i++) {
+                memcpy(wr.Wc[i].data(), wroots + 32 * i, 32);
+                memcpy(wr.Ws[i].data(), wroots + 32 * (p3tf::NW + i), 32);
+            }
+            memcpy(wr.G1.data(), wroots + 32 * 14, 32); memcpy(wr.G2.data(), wroots + 32 * 15, 32);
+            p3fri::Hash hx; memcpy(hx.data(), rX0, 32);
+            const size_t n = (size_t)c.T() * c.d, nh2 = (size_t)c.seq * (c.dh / 2);
+            std::vector<uint16_t> xv(x0, x0 + n), ov(outp, outp + n), cv(cosp, cosp + nh2), sv(sinp, sinp + nh2);
+            ok = p3tf::verify(tr, pf, T, tf_art(), c, xv, hx, wr, cv, sv, ov, Q, R) ? 1 : 0;
         }
     } catch (...) { ok = 0; }
     memcpy(st, tr.state, 32);

@@ -1160,3 +1160,266 @@ def smx_prove(engine, tr, wt, T, art, ops, R, Q, col, ctx=None, strict=True):
     out += _msgs(mDe) + struct.pack("<I", len(yDe)) + _u64(yDe) + _u64([yDeS, yDeP] + yDeR) + _msgs(mDb) + _u64(yDb)
     out += _u64([yBF, yBS]) + _msgs(mBind) + _u64(yB)
     return out + sb
+
+
+# ---------------------------------------------------------------------------------- composed fp8 transformer layer (p3tf)
+class TfConfig:
+    """p3tf::Config (p3_transformer.cuh:93-127): power-of-two shapes; attention instances a = b * nh + h."""
+
+    def __init__(self, seq, d, nh, dh, dff, batch=1):
+        self.seq, self.d, self.nh, self.dh, self.dff, self.batch = seq, d, nh, dh, dff, batch
+        lg = lambda x: x.bit_length() - 1
+        self.lseq, self.ld, self.ldh, self.ldff, self.lnh, self.lbb = lg(seq), lg(d), lg(dh), lg(dff), lg(nh), lg(batch)
+        if any((1 << l) != x for l, x in ((self.lseq, seq), (self.ld, d), (self.ldh, dh), (self.ldff, dff), (self.lnh, nh),
+                                          (self.lbb, batch))) or nh * dh != d:
+            raise ValueError("tf: config must be pow2")
+        self.T, self.lT, self.A = seq * batch, self.lseq + self.lbb, batch * nh
+        A = self.A
+        self.nmm, self.nqn = 7 + 2 * A, 4 + 4 * A
+        self.mmWQ, self.mmWK, self.mmWV = 0, 1, 2
+        self.mmQK, self.mmPV = (lambda a: 3 + a), (lambda a: 3 + A + a)
+        self.mmWO, self.mmWG, self.mmWU, self.mmWD = 3 + 2 * A, 4 + 2 * A, 5 + 2 * A, 6 + 2 * A
+        self.qnH1 = 0
+        self.qnRQ, self.qnRK = (lambda a: 1 + 2 * a), (lambda a: 2 + 2 * a)
+        self.qnPB, self.qnVT = (lambda a: 1 + 2 * A + a), (lambda a: 1 + 3 * A + a)
+        self.qnAT, self.qnH2, self.qnSW = 1 + 4 * A, 2 + 4 * A, 3 + 4 * A
+
+    def dims(self):
+        return (self.seq, self.d, self.nh, self.dh, self.dff, self.batch)
+
+
+W_Q, W_K, W_V, W_O, W_G, W_U, W_D = range(7)
+
+
+def tf_tables(art, smx_wmax=23):
+    """p3tf::build_tables (p3_transformer.cuh:506-520)."""
+    from . import hwl
+    return {"hw": hwl.build_tables(), "rms": rms_tables(art), "qnt": qnt_tables(art), "rope": rope_tables(art),
+            "smx": smx_tables(art, smx_wmax), "bfa": bfa_tables(), "swg": swg_tables(art)}
+
+
+def tf_build_witness(c, x0, W, art, device="cpu", engine=None):
+    """p3tf::build_witness (p3_transformer.cuh:238-499): the layer is computed by the gadget replays themselves, each output
+    feeding the next input.  x0: T*d bf16 patterns; W: {"w": [(codes N*K uint8, scales N uint32)] * 7, "g1", "g2" (d bf16),
+    "cos", "sin" (seq * dh/2 bf16)}.  With ``engine`` (the CUDA prover) the matmul replays run in its witness kernel."""
+    from . import hwl
+    inverse = None if engine is None else (lambda t: engine.inv_all_add(t.contiguous(), 0))
+    kw = {"device": device, "inverse": inverse}
+    u16 = lambda a: np.ascontiguousarray(a, dtype=np.uint16)
+    seq, d, dh, dff, T, A, nh = c.seq, c.d, c.dh, c.dff, c.T, c.A, c.nh
+    w = {"cfg": c, "qn": [None] * c.nqn, "mm": [None] * c.nmm, "rp": [None] * (2 * A), "sm": [None] * A, "mmY": [None] * c.nmm}
+
+    def matmul(i, B, K, N, xq, wcodes, wscales):
+        args = (B, K, N, xq["C"], wcodes, xq["S"], wscales)
+        w["mm"][i] = hwl.gen_witness_dev(engine, *args) if engine is not None else hwl.gen_witness(*args, device=device)
+        w["mmY"][i] = w["mm"][i]["Y"]
+        return w["mmY"][i]
+
+    w["rms"] = [rms_witness(u16(x0), W["g1"], T, art, **kw), None]
+    w["qn"][c.qnH1] = qnt_witness(w["rms"][0]["Y"], T, c.ld, art, **kw)
+    yq, yk, yv = (matmul(i, T, d, d, w["qn"][c.qnH1], *W["w"][wi]) for i, wi in ((c.mmWQ, W_Q), (c.mmWK, W_K), (c.mmWV, W_V)))
+    mask = np.tril(np.ones((seq, seq), dtype=np.uint8)).reshape(-1)
+    w["smmask"] = mask
+    attn = np.zeros((T, d), dtype=np.uint16)
+    head = lambda Y, b, h: Y.reshape(T, d)[b * seq:(b + 1) * seq, h * dh:(h + 1) * dh]
+    for b in range(c.batch):
+        for h in range(nh):
+            a = b * nh + h
+            w["rp"][2 * a] = rope_witness(head(yq, b, h).reshape(-1), W["cos"], W["sin"], seq, dh, art, **kw)
+            w["rp"][2 * a + 1] = rope_witness(head(yk, b, h).reshape(-1), W["cos"], W["sin"], seq, dh, art, **kw)
+            w["qn"][c.qnRQ(a)] = qnt_witness(w["rp"][2 * a]["OUT"], seq, c.ldh, art, **kw)
+            w["qn"][c.qnRK(a)] = qnt_witness(w["rp"][2 * a + 1]["OUT"], seq, c.ldh, art, **kw)
+            sc = matmul(c.mmQK(a), seq, dh, seq, w["qn"][c.qnRQ(a)], w["qn"][c.qnRK(a)]["C"], w["qn"][c.qnRK(a)]["S"])
+            w["sm"][a] = smx_witness(sc, mask, seq, c.lseq, art, **kw)
+            w["qn"][c.qnPB(a)] = qnt_witness(w["sm"][a]["P"], seq, c.lseq, art, **kw)
+            vt = np.ascontiguousarray(head(yv, b, h).T).reshape(-1)
+            w["qn"][c.qnVT(a)] = qnt_witness(vt, dh, c.lseq, art, **kw)
+            pv = matmul(c.mmPV(a), seq, seq, dh, w["qn"][c.qnPB(a)], w["qn"][c.qnVT(a)]["C"], w["qn"][c.qnVT(a)]["S"])
+            attn[b * seq:(b + 1) * seq, h * dh:(h + 1) * dh] = pv.reshape(seq, dh)
+    w["qn"][c.qnAT] = qnt_witness(attn.reshape(-1), T, c.ld, art, **kw)
+    yo = matmul(c.mmWO, T, d, d, w["qn"][c.qnAT], *W["w"][W_O])
+    w["res"] = [bfa_witness(u16(x0), yo, **kw), None]
+    w["rms"][1] = rms_witness(w["res"][0]["O"], W["g2"], T, art, **kw)
+    w["qn"][c.qnH2] = qnt_witness(w["rms"][1]["Y"], T, c.ld, art, **kw)
+    yg = matmul(c.mmWG, T, d, dff, w["qn"][c.qnH2], *W["w"][W_G])
+    yu = matmul(c.mmWU, T, d, dff, w["qn"][c.qnH2], *W["w"][W_U])
+    w["sw"] = swg_witness(yg, yu, art, **kw)
+    w["qn"][c.qnSW] = qnt_witness(w["sw"]["M"], T, c.ldff, art, **kw)
+    yd = matmul(c.mmWD, T, dff, d, w["qn"][c.qnSW], *W["w"][W_D])
+    w["res"][1] = bfa_witness(w["res"][0]["O"], yd, **kw)
+    w["x0"], w["out"] = u16(x0), w["res"][1]["O"]
+    return w
+
+
+def tf_commit_all(engine, w, R, col):
+    """p3tf::commit_all (p3_transformer.cuh:565-727): every chained column is committed once; producer and consumer share
+    the (column, root) pair wherever they hold the same values on the same domain."""
+    from . import hwl
+    c = w["cfg"]
+    A, nh = c.A, c.nh
+    com = lambda t: (lambda cc: (cc, engine.commit_gpu_rootonly(cc, R)))(col(t))
+    o = {"rms": [None, None], "qn": [None] * c.nqn, "mm": [None] * c.nmm, "rp": [None] * (2 * A), "sm": [None] * A, "res": [None, None],
+         "Ymm": [None] * c.nmm}
+
+    def quant(i, X):
+        o["qn"][i] = {"X": X, "CODES": com(w["qn"][i]["cpat"]), "SCALES": com(w["qn"][i]["spat"])}
+
+    def matmul(i, X, Wc, XS, WS):
+        m = w["mm"][i]
+        o["mm"][i] = {"X": X if X is not None else com(m["xcodes"]), "W": Wc if Wc is not None else com(m["wcodes"]), "XS": XS,
+                      "WS": WS if WS is not None else com(m["wsb"])}
+        o["Ymm"][i] = com(m["dob"][hwl.O_YB])
+
+    o["rms"][0] = rms_commit_operands(engine, w["rms"][0], R, col)
+    quant(c.qnH1, o["rms"][0]["Y"])
+    X1 = com(w["mm"][c.mmWQ]["xcodes"])
+    for i in (c.mmWQ, c.mmWK, c.mmWV):
+        matmul(i, X1, None, o["qn"][c.qnH1]["SCALES"], None)
+    for a in range(A):
+        for k in (0, 1):
+            o["rp"][2 * a + k] = rope_commit_operands(engine, w["rp"][2 * a + k], R, col)
+        quant(c.qnRQ(a), o["rp"][2 * a]["OUT"])
+        quant(c.qnRK(a), o["rp"][2 * a + 1]["OUT"])
+        matmul(c.mmQK(a), None, None, o["qn"][c.qnRQ(a)]["SCALES"], o["qn"][c.qnRK(a)]["SCALES"])
+        o["sm"][a] = {"S": o["Ymm"][c.mmQK(a)], "P": com(w["sm"][a]["ppat"])}
+        quant(c.qnPB(a), o["sm"][a]["P"])
+        quant(c.qnVT(a), com(w["qn"][c.qnVT(a)]["xpat"]))
+        matmul(c.mmPV(a), None, None, o["qn"][c.qnPB(a)]["SCALES"], o["qn"][c.qnVT(a)]["SCALES"])
+    quant(c.qnAT, com(w["qn"][c.qnAT]["xpat"]))
+    matmul(c.mmWO, None, None, o["qn"][c.qnAT]["SCALES"], None)
+    o["res"][0] = {"X1": o["rms"][0]["X"], "X2": o["Ymm"][c.mmWO], "OUT": com(w["res"][0]["opat"])}
+    o["rms"][1] = {"X": o["res"][0]["OUT"], "G": com(w["rms"][1]["gpat"]), "Y": com(w["rms"][1]["ypat"])}
+    quant(c.qnH2, o["rms"][1]["Y"])
+    X2 = com(w["mm"][c.mmWG]["xcodes"])
+    for i in (c.mmWG, c.mmWU):
+        matmul(i, X2, None, o["qn"][c.qnH2]["SCALES"], None)
+    o["sw"] = {"GATE": o["Ymm"][c.mmWG], "UP": o["Ymm"][c.mmWU], "M": com(w["sw"]["mpat"])}
+    quant(c.qnSW, o["sw"]["M"])
+    matmul(c.mmWD, None, None, o["qn"][c.qnSW]["SCALES"], None)
+    o["res"][1] = {"X1": o["res"][0]["OUT"], "X2": o["Ymm"][c.mmWD], "OUT": com(w["res"][1]["opat"])}
+    return o
+
+
+def tf_weight_roots(engine, c, W, R, col):
+    """p3tf::weight_roots (p3_transformer.cuh:732-752): the public weight-side commitments, from the weights and the canonical
+    padding alone: 7 code roots, 7 scale roots, g1, g2."""
+    from . import hwl
+    roots_c, roots_s = [], []
+    for codes, scales in W["w"]:
+        N = len(scales)
+        K = len(codes) // N
+        dd = hwl.Dims(c.T, K, N)
+        wc = np.zeros((dd.Npad, dd.Kpad), dtype=np.uint64)
+        wc[:N, :K] = np.asarray(codes, dtype=np.uint64).reshape(N, K)
+        ws = np.zeros(dd.Npad, dtype=np.uint64)
+        ws[:N] = np.asarray(scales, dtype=np.uint64)
+        roots_c.append(engine.commit_gpu_rootonly(engine.upload(wc.reshape(-1)), R))
+        roots_s.append(engine.commit_gpu_rootonly(engine.upload(ws), R))
+    g = [engine.commit_gpu_rootonly(engine.upload(np.asarray(W[k], dtype=np.uint64)), R) for k in ("g1", "g2")]
+    return roots_c + roots_s + g
+
+
+def tf_prove(engine, tr, w, o, T, art, R, Q, col, strict=True):
+    """p3tf::prove (p3_transformer.cuh:1011-1037), non-zk: all sub-proofs in fixed order on one transcript with one ledger,
+    one merged-lookup flush, the composition seams with both public I/O bindings, one batched opening per size class.
+    Serialised TfProof: 6 x u32 dims | length-prefixed sub-proofs in proving order | roots rX0 rRmsY[2] rCodes[] rScales[]
+    rMX[] rMW[] rRopeQ[] rRopeO[] rSmP[] rVtX[] rAtX rRes1 rSwM rOut | per matmul u32 count + bf16 outputs | groups |
+    u32 count + seam values | batches."""
+    from . import hwl
+    from .ig import Ctx
+    c = w["cfg"]
+    A, nh = c.A, c.nh
+    ctx = Ctx()
+    lg = ctx.ledger
+    tr.absorb("tf-dims", struct.pack("<6I", *c.dims()))
+    subs = []
+    rms = lambda i: subs.append(rms_prove(engine, tr, w["rms"][i], T["rms"], art, o["rms"][i], R, Q, col, ctx, strict))
+    qn = lambda i: subs.append(qnt_prove(engine, tr, w["qn"][i], T["qnt"], o["qn"][i], R, Q, col, ctx, strict))
+    mm = lambda i: subs.append(hwl.prove(engine, tr, w["mm"][i], T["hw"], o["mm"][i], R, Q, col, w["mmY"][i], ctx, strict))
+    rms(0)
+    qn(c.qnH1)
+    for i in (c.mmWQ, c.mmWK, c.mmWV):
+        mm(i)
+    for a in range(A):
+        for k in (0, 1):
+            subs.append(rope_prove(engine, tr, w["rp"][2 * a + k], T["rope"], o["rp"][2 * a + k], R, Q, col, ctx, strict))
+        qn(c.qnRQ(a))
+        qn(c.qnRK(a))
+        mm(c.mmQK(a))
+        subs.append(smx_prove(engine, tr, w["sm"][a], T["smx"], art, o["sm"][a], R, Q, col, ctx, strict))
+        qn(c.qnPB(a))
+        qn(c.qnVT(a))
+        mm(c.mmPV(a))
+    qn(c.qnAT)
+    mm(c.mmWO)
+    subs.append(bfa_prove(engine, tr, w["res"][0], T["bfa"], o["res"][0], R, Q, col, ctx, strict))
+    rms(1)
+    qn(c.qnH2)
+    mm(c.mmWG)
+    mm(c.mmWU)
+    subs.append(swg_prove(engine, tr, w["sw"], T["swg"], o["sw"], R, Q, col, ctx, strict))
+    qn(c.qnSW)
+    mm(c.mmWD)
+    subs.append(bfa_prove(engine, tr, w["res"][1], T["bfa"], o["res"][1], R, Q, col, ctx, strict))
+    lug = lu_flush(engine, tr, ctx.luq, lg, R, strict)
+    # ---- composition seams ----
+    seam = []
+    chal_vec = lambda n: [tr.chal() for _ in range(n)]
+
+    def cl(cr, z):
+        y = claimc(engine, tr, lg, cr[0], cr[1], z)
+        seam.append(y)
+        return y
+
+    def seam_pair(Ac, zA, Bc, zB, what):
+        if cl(Ac, zA) != cl(Bc, zB) and strict:
+            raise ValueError("tf: seam mismatch: " + what)
+
+    def seam_codes(Cc, Xc, ldr, lk, lb, what):
+        z = chal_vec(ldr + lb)
+        seam_pair(Cc, z, Xc, z[:ldr] + [0] * (lk - ldr) + z[ldr:], what)
+        for t in range(ldr, lk):
+            zt = chal_vec(t + lb)
+            if cl(Xc, zt[:t] + [1] + [0] * (lk - t - 1) + zt[t:]) != 0 and strict:
+                raise ValueError("tf: padding not zero: " + what)
+
+    bits = lambda v, n: [(v >> i) & 1 for i in range(n)]
+    slice_pt = lambda z, li, h, b: z[:li] + bits(h, c.lnh) + z[li:] + bits(b, c.lbb)
+    lk_of = lambda i: w["mm"][i]["d"].Kpad.bit_length() - 1
+    lkH1, lkQK, lkPV, lkSW = lk_of(c.mmWQ), lk_of(c.mmQK(0)), lk_of(c.mmPV(0)), lk_of(c.mmWD)
+    cl(o["rms"][0]["X"], chal_vec(c.ld + c.lT))
+    seam_codes(o["qn"][c.qnH1]["CODES"], o["mm"][c.mmWQ]["X"], c.ld, lkH1, c.lT, "h1 codes")
+    for b in range(c.batch):
+        for h in range(nh):
+            a = b * nh + h
+            z = chal_vec(c.ldh + c.lseq)
+            seam_pair(o["rp"][2 * a]["Q"], z, o["Ymm"][c.mmWQ], slice_pt(z, c.ldh, h, b), "rope-q slice")
+            z = chal_vec(c.ldh + c.lseq)
+            seam_pair(o["rp"][2 * a + 1]["Q"], z, o["Ymm"][c.mmWK], slice_pt(z, c.ldh, h, b), "rope-k slice")
+            seam_codes(o["qn"][c.qnRQ(a)]["CODES"], o["mm"][c.mmQK(a)]["X"], c.ldh, lkQK, c.lseq, "qk x codes")
+            seam_codes(o["qn"][c.qnRK(a)]["CODES"], o["mm"][c.mmQK(a)]["W"], c.ldh, lkQK, c.lseq, "qk w codes")
+            z = chal_vec(c.lseq + c.ldh)
+            zt = z[c.lseq:] + bits(h, c.lnh) + z[:c.lseq] + bits(b, c.lbb)
+            seam_pair(o["qn"][c.qnVT(a)]["X"], z, o["Ymm"][c.mmWV], zt, "v^T transpose")
+            seam_codes(o["qn"][c.qnPB(a)]["CODES"], o["mm"][c.mmPV(a)]["X"], c.lseq, lkPV, c.lseq, "pv x codes")
+            seam_codes(o["qn"][c.qnVT(a)]["CODES"], o["mm"][c.mmPV(a)]["W"], c.lseq, lkPV, c.ldh, "pv w codes")
+            z = chal_vec(c.ldh + c.lseq)
+            seam_pair(o["qn"][c.qnAT]["X"], slice_pt(z, c.ldh, h, b), o["Ymm"][c.mmPV(a)], z, "concat half")
+    seam_codes(o["qn"][c.qnAT]["CODES"], o["mm"][c.mmWO]["X"], c.ld, lkH1, c.lT, "attn codes")
+    seam_codes(o["qn"][c.qnH2]["CODES"], o["mm"][c.mmWG]["X"], c.ld, lkH1, c.lT, "h2 codes")
+    seam_codes(o["qn"][c.qnSW]["CODES"], o["mm"][c.mmWD]["X"], c.ldff, lkSW, c.lT, "swiglu codes")
+    cl(o["res"][1]["OUT"], chal_vec(c.ld + c.lT))
+    batches = [engine.prove_class(tr, np.stack(k[1]), k[2], R, Q, "tf-bo%d" % i) for i, k in enumerate(lg.cls)]
+    # ---- serialise ----
+    root = lambda cr: cr[1]
+    out = struct.pack("<6I", *c.dims()) + b"".join(_blob(s) for s in subs)
+    out += root(o["rms"][0]["X"]) + root(o["rms"][0]["Y"]) + root(o["rms"][1]["Y"])
+    out += b"".join(root(q["CODES"]) for q in o["qn"]) + b"".join(root(q["SCALES"]) for q in o["qn"])
+    out += b"".join(root(m["X"]) for m in o["mm"]) + b"".join(root(m["W"]) for m in o["mm"])
+    out += b"".join(root(r["Q"]) for r in o["rp"]) + b"".join(root(r["OUT"]) for r in o["rp"])
+    out += b"".join(root(s["P"]) for s in o["sm"]) + b"".join(root(o["qn"][c.qnVT(a)]["X"]) for a in range(A))
+    out += root(o["qn"][c.qnAT]["X"]) + root(o["res"][0]["OUT"]) + root(o["sw"]["M"]) + root(o["res"][1]["OUT"])
+    for y in w["mmY"]:
+        out += struct.pack("<I", len(y)) + np.ascontiguousarray(y, dtype=np.uint16).tobytes()
+    sl, sb = _ser_tail(lug, batches)
+    return out + sl + struct.pack("<I", len(seam)) + _u64(seam) + sb
