@@ -780,6 +780,66 @@ def run_suite_hwl(args):
         torch.cuda.empty_cache()
 
 
+def run_suite_tf(args):
+    """--suite-tf: one composed fp8 transformer layer (the reference's p3tf stack, non-zk: RMSNorm, quantise, fp8 matmuls,
+    RoPE, masked softmax, SwiGLU, bf16 residual adds, seams) with the witness chain on the GPU; accepted by the reference's
+    layer verifier.  Shapes are bounded by the witness of the largest matmul (10 columns per padded product)."""
+    import torch
+    import zkh_import
+    zk = zkh_import.load()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import Reference
+    from test_tf_layer_host_logic import ref_tf_verify, small_layer
+    from tfg_helpers import load_art
+    torch.cuda.set_device(0)
+    prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+    tfg = zk.tfg
+    ref = Reference() if Reference.available() else None
+    R, Q = 1, 24
+    shapes = {"tiny": (4, 64, 2, 32, 128, 1), "d256s64": (64, 256, 4, 64, 512, 1), "d256s128": (128, 256, 4, 64, 1024, 1),
+              "d512s128": (128, 512, 8, 64, 1024, 1)}
+    ident = lambda t: t
+    for key in args.tf_shapes.split(","):
+        c = tfg.TfConfig(*shapes[key])
+        art = load_art(ref, zk, c.ld) if ref is not None else zk.tfart.build_art(c.ld)
+        wmax = max(23, 16 + c.lseq)
+        T = tfg.tf_tables(art, wmax)
+        x0, W = small_layer(zk, c, 42)
+        t_wit = None
+        for _ in range(2):
+            w = None
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            w = tfg.tf_build_witness(c, x0, W, art, device="cuda:0", engine=prover)
+            torch.cuda.synchronize()
+            t_wit = time.perf_counter() - t0
+        best = None
+        for rep in range(args.layer_reps):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            o = tfg.tf_commit_all(prover, w, R, ident)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            tr = zk.Transcript("tf-layer")
+            pf = tfg.tf_prove(prover, tr, w, o, T, art, R, Q, ident)
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+            if best is None or t2 - t1 < best[1]:
+                best = (t1 - t0, t2 - t1)
+        line = {"suite": "fp8 transformer layer " + key, "dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), c.dims())),
+                "R": R, "Q": Q, "witness_device_s": t_wit, "commit_s": best[0], "prove_s": best[1], "proof_MB": len(pf) / 1048576.0,
+                "sub_proofs": 12 + 13 * c.A}
+        if ref is not None:
+            wroots = tfg.tf_weight_roots(prover, c, W, R, ident)
+            t0 = time.perf_counter()
+            ok, st = ref_tf_verify(ref, zk.Transcript("tf-layer").state, c, x0, o["rms"][0]["X"][1], wroots, W, w["out"], R, Q, pf, wmax)
+            line.update({"accepted_by_reference_verifier": bool(ok and st == tr.state), "reference_verify_host_s": time.perf_counter() - t0})
+        print(json.dumps(line), flush=True)
+        del w, o
+        torch.cuda.empty_cache()
+
+
 def run_suite_model(args):
     """--suite-model [--gpus N under torch.distributed.run]: the 22 independent layer proofs of the TinyLlama-shaped
     model (BASELINE configs[4]; one transcript per layer, as the reference's transformer bench proves them) placed
@@ -865,6 +925,8 @@ def main():
     ap.add_argument("--suite-layer", action="store_true", help="one integer decoder layer beside the reference's layer prover")
     ap.add_argument("--layer-shapes", default="c3")
     ap.add_argument("--layer-reps", type=int, default=2)
+    ap.add_argument("--suite-tf", action="store_true", help="one composed fp8 transformer layer (RMSNorm .. residual) on the GPU")
+    ap.add_argument("--tf-shapes", default="tiny,d256s64")
     ap.add_argument("--suite-hwl", action="store_true", help="the fp8 (Hawkeye) matmul gadget beside the reference's prover")
     ap.add_argument("--hwl-shapes", default="small,mid")
     ap.add_argument("--hwl-keep-trees", action="store_true")
@@ -885,6 +947,8 @@ def main():
         return run_suite_layer(args)
     if args.suite_hwl:
         return run_suite_hwl(args)
+    if args.suite_tf:
+        return run_suite_tf(args)
     if args.suite_model:
         return run_suite_model(args)
     if args.suite_gadgets:
