@@ -30,6 +30,7 @@
 #include "p3_rope.cuh"
 #include "p3_softmax.cuh"
 #include "p3_transformer.cuh"
+#include "p3_model.cuh"
 
 namespace {
 fs::Transcript tr_from(const uint8_t st[32]) {
@@ -923,6 +924,26 @@ void tf_walk(IO& io, p3tf::TfProof& pf, bool reading) {
     for (auto& y : pf.mmY) io.vec16(y);
     io.groups(pf.lug);
     io.vec(pf.seam);
+    io.batches(pf.batches);
+}
+// p3mdl::MdlProof <-> bytes: u32 nlayers vocab seq d batch | per layer u32 len + TfProof | rEmb | u32 len + rmsF, qnF, mmH |
+//   rRmsFY rCodesF rScalesF rMXH rMWH | u32 count + logits | u32 count + seam values | groups | batches
+template <typename IO>
+void mdl_walk(IO& io, p3mdl::MdlProof& pf, bool reading) {
+    io.u32(pf.nlayers); io.u32(pf.vocab); io.u32(pf.seq); io.u32(pf.d); io.u32(pf.batch);
+    if (reading) {
+        if (pf.nlayers < 1 || pf.nlayers > 256) { io.fail(); return; }
+        pf.lay.resize(pf.nlayers);
+    }
+    for (auto& l : pf.lay) io.sub(l, [reading](auto& i2, p3tf::TfProof& y) { tf_walk(i2, y, reading); });
+    io.raw(pf.rEmb.data(), 32);
+    io.sub(pf.rmsF, [](auto& i2, p3rms::RmsProof& y) { rms_walk(i2, y); });
+    io.sub(pf.qnF, [](auto& i2, p3qnt::QntProof& y) { qnt_walk(i2, y); });
+    io.sub(pf.mmH, [](auto& i2, p3hwl::LayerProof& y) { hwl_walk(i2, y); });
+    for (auto* h : {&pf.rRmsFY, &pf.rCodesF, &pf.rScalesF, &pf.rMXH, &pf.rMWH}) io.raw(h->data(), 32);
+    io.vec16(pf.mmYH);
+    io.vec(pf.seam);
+    io.groups(pf.lug);
     io.batches(pf.batches);
 }
 // the integer layer's public tables, built once per (d, btop) by the reference's own build_tables
@@ -2166,6 +2187,40 @@ int ref_tf_verify(uint8_t st[32], const uint32_t dims[6], const uint16_t* x0, co
             const size_t n = (size_t)c.T() * c.d, nh2 = (size_t)c.seq * (c.dh / 2);
             std::vector<uint16_t> xv(x0, x0 + n), ov(outp, outp + n), cv(cosp, cosp + nh2), sv(sinp, sinp + nh2);
             ok = p3tf::verify(tr, pf, T, tf_art(), c, xv, hx, wr, cv, sv, ov, Q, R) ? 1 : 0;
+        }
+    } catch (...) { ok = 0; }
+    memcpy(st, tr.state, 32);
+    return ok;
+}
+
+// p3mdl::verify_model (host only).  roots: E, GF, WHc, WHs, then 16 per layer (7 weight codes, 7 weight scales, g1, g2);
+// ids: T token ids; logits: T*vocab bf16 patterns
+int ref_mdl_verify(uint8_t st[32], const uint32_t dims[6], uint32_t nlayers, uint32_t vocab, const uint32_t* ids, const uint8_t* roots,
+                   const uint16_t* cosp, const uint16_t* sinp, const uint16_t* logits, uint32_t smx_wmax, uint32_t R, uint32_t Q,
+                   const uint8_t* proof, size_t len) {
+    fs::Transcript tr = tr_from(st);
+    int ok = 0;
+    try {
+        p3mdl::MdlProof pf;
+        HwlReader rd{proof, proof + len};
+        mdl_walk(rd, pf, true);
+        if (rd.ok && rd.p == rd.end) {
+            p3tf::Config c; c.seq = dims[0]; c.d = dims[1]; c.nh = dims[2]; c.dh = dims[3]; c.dff = dims[4]; c.batch = dims[5];
+            static p3tf::TfTables T; static int64_t t_ld = -1; static uint32_t t_w = 0;
+            if (t_ld != tf_art().ld || t_w != smx_wmax) { T = p3tf::build_tables(tf_art(), smx_wmax); t_ld = tf_art().ld; t_w = smx_wmax; }
+            p3mdl::MdlRoots mr;
+            auto H = [&](p3fri::Hash& h, size_t i) { memcpy(h.data(), roots + 32 * i, 32); };
+            H(mr.E, 0); H(mr.GF, 1); H(mr.WHc, 2); H(mr.WHs, 3);
+            mr.lw.resize(nlayers);
+            for (uint32_t li = 0; li < nlayers; li++) {
+                const size_t b = 4 + (size_t)16 * li;
+                for (int i = 0; i < p3tf::NW; i++) { H(mr.lw[li].Wc[i], b + i); H(mr.lw[li].Ws[i], b + p3tf::NW + i); }
+                H(mr.lw[li].G1, b + 14); H(mr.lw[li].G2, b + 15);
+            }
+            const size_t nh2 = (size_t)c.seq * (c.dh / 2);
+            std::vector<uint32_t> idv(ids, ids + c.T());
+            std::vector<uint16_t> cv(cosp, cosp + nh2), sv(sinp, sinp + nh2), lv(logits, logits + (size_t)c.T() * vocab);
+            ok = p3mdl::verify_model(tr, pf, T, tf_art(), c, nlayers, vocab, idv, mr, cv, sv, lv, Q, R) ? 1 : 0;
         }
     } catch (...) { ok = 0; }
     memcpy(st, tr.state, 32);

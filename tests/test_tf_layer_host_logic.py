@@ -94,3 +94,55 @@ def test_layer_accepted_by_reference_verifier(orc, ref, zk, dims):
         bad = bytearray(pf)
         bad[off] ^= 1
         assert not ref_tf_verify(ref, st0, c, x0, rX0, wroots, W, w["out"], R, Q, bytes(bad))[0]
+
+
+def ref_mdl_verify(ref, st, c, nlayers, vocab, ids, roots, W, logits, R, Q, proof, wmax=23):
+    s = (C.c_uint8 * 32)(*st)
+    dims = (C.c_uint32 * 6)(*c.dims())
+    keep = [np.ascontiguousarray(ids, dtype=np.uint32)] + [np.ascontiguousarray(a, dtype=np.uint16) for a in (W["cos"], W["sin"], logits)]
+    p = [a.ctypes.data_as(C.c_void_p) for a in keep]
+    ok = ref.lib.ref_mdl_verify(s, dims, C.c_uint32(nlayers), C.c_uint32(vocab), p[0], b"".join(roots), p[1], p[2], p[3], C.c_uint32(wmax),
+                                C.c_uint32(R), C.c_uint32(Q), bytes(proof), C.c_size_t(len(proof)))
+    return bool(ok), bytes(s)
+
+
+def small_model(zk, c, nlayers, vocab, seed):
+    rng = np.random.default_rng(seed)
+    to_bf = np.vectorize(zk.tfart.bf_from_f64, otypes=[np.uint16])
+    layers = []
+    for li in range(nlayers):
+        _x, W = small_layer(zk, c, seed + 10 * li)
+        layers.append(W)
+    MW = {"vocab": vocab, "emb": to_bf(rng.normal(0, 1.0, vocab * c.d)), "layers": layers, "gF": to_bf(1.0 + rng.normal(0, 0.1, c.d)),
+          "wh": (rng.integers(0, 256, vocab * c.d).astype(np.uint8), (np.exp(rng.normal(0, 0.3, vocab)) * 0.02).astype(np.float32).view(np.uint32))}
+    ids = rng.integers(0, vocab, c.T)
+    return MW, ids
+
+
+def test_two_layer_model_accepted_by_reference_verifier(orc, ref, zk):
+    """Embedding gather, two chained layers (shared commitments, no public activations), final RMSNorm, LM head, public logits."""
+    R, Q = 1, 24
+    tfg = zk.tfg
+    c = tfg.TfConfig(2, 16, 2, 8, 16, 1)
+    nlayers, vocab = 2, 8
+    art = load_art(ref, zk, c.ld)
+    T = tfg.tf_tables(art)
+    MW, ids = small_model(zk, c, nlayers, vocab, 21)
+    w = tfg.mdl_build_witness(c, ids, MW, art)
+    eng = OracleHwlEngine(orc, ref)
+    o = tfg.mdl_commit(eng, w, MW, R, host_col)
+    assert o["lay"][1]["rms"][0]["X"][1] == o["lay"][0]["res"][1]["OUT"][1]
+    roots = tfg.mdl_roots(eng, c, MW, R, host_col)
+    tr = zk.Transcript("mdl")
+    pf = tfg.mdl_prove(eng, tr, w, o, T, art, R, Q, host_col)
+    st0 = zk.Transcript("mdl").state
+    W0 = MW["layers"][0]
+    ok, st = ref_mdl_verify(ref, st0, c, nlayers, vocab, ids, roots, W0, w["logits"], R, Q, pf)
+    assert ok and st == tr.state
+    bad_logits = w["logits"].copy()
+    bad_logits[2] ^= 1
+    assert not ref_mdl_verify(ref, st0, c, nlayers, vocab, ids, roots, W0, bad_logits, R, Q, pf)[0]
+    bad_ids = np.array(ids).copy()
+    bad_ids[0] = (bad_ids[0] + 1) % vocab
+    assert not ref_mdl_verify(ref, st0, c, nlayers, vocab, bad_ids, roots, W0, w["logits"], R, Q, pf)[0]
+    assert not ref_mdl_verify(ref, st0, c, nlayers, vocab, ids, roots[:4] + roots[20:] + roots[4:20], W0, w["logits"], R, Q, pf)[0]

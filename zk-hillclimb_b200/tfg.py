@@ -1251,9 +1251,10 @@ def tf_build_witness(c, x0, W, art, device="cpu", engine=None):
     return w
 
 
-def tf_commit_all(engine, w, R, col):
+def tf_commit_all(engine, w, R, col, x0ext=None):
     """p3tf::commit_all (p3_transformer.cuh:565-727): every chained column is committed once; producer and consumer share
-    the (column, root) pair wherever they hold the same values on the same domain."""
+    the (column, root) pair wherever they hold the same values on the same domain.  x0ext: an already committed input
+    column (the previous layer's output, or the embedded input of a model)."""
     from . import hwl
     c = w["cfg"]
     A, nh = c.A, c.nh
@@ -1270,7 +1271,8 @@ def tf_commit_all(engine, w, R, col):
                       "WS": WS if WS is not None else com(m["wsb"])}
         o["Ymm"][i] = com(m["dob"][hwl.O_YB])
 
-    o["rms"][0] = rms_commit_operands(engine, w["rms"][0], R, col)
+    o["rms"][0] = rms_commit_operands(engine, w["rms"][0], R, col) if x0ext is None else \
+        {"X": x0ext, "G": com(w["rms"][0]["gpat"]), "Y": com(w["rms"][0]["ypat"])}
     quant(c.qnH1, o["rms"][0]["Y"])
     X1 = com(w["mm"][c.mmWQ]["xcodes"])
     for i in (c.mmWQ, c.mmWK, c.mmWV):
@@ -1319,18 +1321,12 @@ def tf_weight_roots(engine, c, W, R, col):
     return roots_c + roots_s + g
 
 
-def tf_prove(engine, tr, w, o, T, art, R, Q, col, strict=True):
-    """p3tf::prove (p3_transformer.cuh:1011-1037), non-zk: all sub-proofs in fixed order on one transcript with one ledger,
-    one merged-lookup flush, the composition seams with both public I/O bindings, one batched opening per size class.
-    Serialised TfProof: 6 x u32 dims | length-prefixed sub-proofs in proving order | roots rX0 rRmsY[2] rCodes[] rScales[]
-    rMX[] rMW[] rRopeQ[] rRopeO[] rSmP[] rVtX[] rAtX rRes1 rSwM rOut | per matmul u32 count + bf16 outputs | groups |
-    u32 count + seam values | batches."""
+def tf_prove_subs(engine, tr, w, o, T, art, R, Q, col, ctx, strict=True):
+    """p3tf::prove_subs (p3_transformer.cuh:826-925): the layer header and every gadget sub-proof in fixed order on the shared
+    transcript, ledger and lookup queue.  Returns the serialised sub-proofs in proving order."""
     from . import hwl
-    from .ig import Ctx
     c = w["cfg"]
-    A, nh = c.A, c.nh
-    ctx = Ctx()
-    lg = ctx.ledger
+    A = c.A
     tr.absorb("tf-dims", struct.pack("<6I", *c.dims()))
     subs = []
     rms = lambda i: subs.append(rms_prove(engine, tr, w["rms"][i], T["rms"], art, o["rms"][i], R, Q, col, ctx, strict))
@@ -1361,65 +1357,202 @@ def tf_prove(engine, tr, w, o, T, art, R, Q, col, strict=True):
     qn(c.qnSW)
     mm(c.mmWD)
     subs.append(bfa_prove(engine, tr, w["res"][1], T["bfa"], o["res"][1], R, Q, col, ctx, strict))
-    lug = lu_flush(engine, tr, ctx.luq, lg, R, strict)
-    # ---- composition seams ----
-    seam = []
-    chal_vec = lambda n: [tr.chal() for _ in range(n)]
+    return subs
 
-    def cl(cr, z):
-        y = claimc(engine, tr, lg, cr[0], cr[1], z)
-        seam.append(y)
+
+class Seams:
+    """Seam claims on the shared ledger: every claimed value is absorbed like any opening claim and recorded in order."""
+
+    def __init__(self, engine, tr, ledger, strict, who):
+        self.engine, self.tr, self.lg, self.strict, self.who, self.vals = engine, tr, ledger, strict, who, []
+
+    def chal_vec(self, n):
+        return [self.tr.chal() for _ in range(n)]
+
+    def cl(self, cr, z):
+        y = claimc(self.engine, self.tr, self.lg, cr[0], cr[1], z)
+        self.vals.append(y)
         return y
 
-    def seam_pair(Ac, zA, Bc, zB, what):
-        if cl(Ac, zA) != cl(Bc, zB) and strict:
-            raise ValueError("tf: seam mismatch: " + what)
+    def pair(self, Ac, zA, Bc, zB, what):
+        if self.cl(Ac, zA) != self.cl(Bc, zB) and self.strict:
+            raise ValueError("%s: seam mismatch: %s" % (self.who, what))
 
-    def seam_codes(Cc, Xc, ldr, lk, lb, what):
-        z = chal_vec(ldr + lb)
-        seam_pair(Cc, z, Xc, z[:ldr] + [0] * (lk - ldr) + z[ldr:], what)
+    def codes(self, Cc, Xc, ldr, lk, lb, what):
+        """quantiser codes against the padded matmul operand: restriction, then one zero claim per padding subcube"""
+        z = self.chal_vec(ldr + lb)
+        self.pair(Cc, z, Xc, z[:ldr] + [0] * (lk - ldr) + z[ldr:], what)
         for t in range(ldr, lk):
-            zt = chal_vec(t + lb)
-            if cl(Xc, zt[:t] + [1] + [0] * (lk - t - 1) + zt[t:]) != 0 and strict:
-                raise ValueError("tf: padding not zero: " + what)
+            zt = self.chal_vec(t + lb)
+            if self.cl(Xc, zt[:t] + [1] + [0] * (lk - t - 1) + zt[t:]) != 0 and self.strict:
+                raise ValueError("%s: padding not zero: %s" % (self.who, what))
 
+
+def tf_prove_seams(engine, tr, w, o, ctx, strict=True, bind_in=True, bind_out=True):
+    """p3tf::prove_seams (p3_transformer.cuh:931-1006): restriction / zero-padding seams between quantiser codes and matmul
+    operands, head slice / transpose / concat seams, and (single layer) the public input / output bindings.  Returns the
+    seam values in order."""
+    c = w["cfg"]
+    nh = c.nh
+    S = Seams(engine, tr, ctx.ledger, strict, "tf")
     bits = lambda v, n: [(v >> i) & 1 for i in range(n)]
     slice_pt = lambda z, li, h, b: z[:li] + bits(h, c.lnh) + z[li:] + bits(b, c.lbb)
     lk_of = lambda i: w["mm"][i]["d"].Kpad.bit_length() - 1
     lkH1, lkQK, lkPV, lkSW = lk_of(c.mmWQ), lk_of(c.mmQK(0)), lk_of(c.mmPV(0)), lk_of(c.mmWD)
-    cl(o["rms"][0]["X"], chal_vec(c.ld + c.lT))
-    seam_codes(o["qn"][c.qnH1]["CODES"], o["mm"][c.mmWQ]["X"], c.ld, lkH1, c.lT, "h1 codes")
+    if bind_in:
+        S.cl(o["rms"][0]["X"], S.chal_vec(c.ld + c.lT))
+    S.codes(o["qn"][c.qnH1]["CODES"], o["mm"][c.mmWQ]["X"], c.ld, lkH1, c.lT, "h1 codes")
     for b in range(c.batch):
         for h in range(nh):
             a = b * nh + h
-            z = chal_vec(c.ldh + c.lseq)
-            seam_pair(o["rp"][2 * a]["Q"], z, o["Ymm"][c.mmWQ], slice_pt(z, c.ldh, h, b), "rope-q slice")
-            z = chal_vec(c.ldh + c.lseq)
-            seam_pair(o["rp"][2 * a + 1]["Q"], z, o["Ymm"][c.mmWK], slice_pt(z, c.ldh, h, b), "rope-k slice")
-            seam_codes(o["qn"][c.qnRQ(a)]["CODES"], o["mm"][c.mmQK(a)]["X"], c.ldh, lkQK, c.lseq, "qk x codes")
-            seam_codes(o["qn"][c.qnRK(a)]["CODES"], o["mm"][c.mmQK(a)]["W"], c.ldh, lkQK, c.lseq, "qk w codes")
-            z = chal_vec(c.lseq + c.ldh)
+            z = S.chal_vec(c.ldh + c.lseq)
+            S.pair(o["rp"][2 * a]["Q"], z, o["Ymm"][c.mmWQ], slice_pt(z, c.ldh, h, b), "rope-q slice")
+            z = S.chal_vec(c.ldh + c.lseq)
+            S.pair(o["rp"][2 * a + 1]["Q"], z, o["Ymm"][c.mmWK], slice_pt(z, c.ldh, h, b), "rope-k slice")
+            S.codes(o["qn"][c.qnRQ(a)]["CODES"], o["mm"][c.mmQK(a)]["X"], c.ldh, lkQK, c.lseq, "qk x codes")
+            S.codes(o["qn"][c.qnRK(a)]["CODES"], o["mm"][c.mmQK(a)]["W"], c.ldh, lkQK, c.lseq, "qk w codes")
+            z = S.chal_vec(c.lseq + c.ldh)
             zt = z[c.lseq:] + bits(h, c.lnh) + z[:c.lseq] + bits(b, c.lbb)
-            seam_pair(o["qn"][c.qnVT(a)]["X"], z, o["Ymm"][c.mmWV], zt, "v^T transpose")
-            seam_codes(o["qn"][c.qnPB(a)]["CODES"], o["mm"][c.mmPV(a)]["X"], c.lseq, lkPV, c.lseq, "pv x codes")
-            seam_codes(o["qn"][c.qnVT(a)]["CODES"], o["mm"][c.mmPV(a)]["W"], c.lseq, lkPV, c.ldh, "pv w codes")
-            z = chal_vec(c.ldh + c.lseq)
-            seam_pair(o["qn"][c.qnAT]["X"], slice_pt(z, c.ldh, h, b), o["Ymm"][c.mmPV(a)], z, "concat half")
-    seam_codes(o["qn"][c.qnAT]["CODES"], o["mm"][c.mmWO]["X"], c.ld, lkH1, c.lT, "attn codes")
-    seam_codes(o["qn"][c.qnH2]["CODES"], o["mm"][c.mmWG]["X"], c.ld, lkH1, c.lT, "h2 codes")
-    seam_codes(o["qn"][c.qnSW]["CODES"], o["mm"][c.mmWD]["X"], c.ldff, lkSW, c.lT, "swiglu codes")
-    cl(o["res"][1]["OUT"], chal_vec(c.ld + c.lT))
-    batches = [engine.prove_class(tr, np.stack(k[1]), k[2], R, Q, "tf-bo%d" % i) for i, k in enumerate(lg.cls)]
-    # ---- serialise ----
+            S.pair(o["qn"][c.qnVT(a)]["X"], z, o["Ymm"][c.mmWV], zt, "v^T transpose")
+            S.codes(o["qn"][c.qnPB(a)]["CODES"], o["mm"][c.mmPV(a)]["X"], c.lseq, lkPV, c.lseq, "pv x codes")
+            S.codes(o["qn"][c.qnVT(a)]["CODES"], o["mm"][c.mmPV(a)]["W"], c.lseq, lkPV, c.ldh, "pv w codes")
+            z = S.chal_vec(c.ldh + c.lseq)
+            S.pair(o["qn"][c.qnAT]["X"], slice_pt(z, c.ldh, h, b), o["Ymm"][c.mmPV(a)], z, "concat half")
+    S.codes(o["qn"][c.qnAT]["CODES"], o["mm"][c.mmWO]["X"], c.ld, lkH1, c.lT, "attn codes")
+    S.codes(o["qn"][c.qnH2]["CODES"], o["mm"][c.mmWG]["X"], c.ld, lkH1, c.lT, "h2 codes")
+    S.codes(o["qn"][c.qnSW]["CODES"], o["mm"][c.mmWD]["X"], c.ldff, lkSW, c.lT, "swiglu codes")
+    if bind_out:
+        S.cl(o["res"][1]["OUT"], S.chal_vec(c.ld + c.lT))
+    return S.vals
+
+
+def tf_serialize(w, o, subs, lug, seam, batches):
+    """Serialised TfProof: 6 x u32 dims | length-prefixed sub-proofs in proving order | roots rX0 rRmsY[2] rCodes[] rScales[]
+    rMX[] rMW[] rRopeQ[] rRopeO[] rSmP[] rVtX[] rAtX rRes1 rSwM rOut | per matmul u32 count + bf16 outputs | groups |
+    u32 count + seam values | batches."""
+    c = w["cfg"]
     root = lambda cr: cr[1]
     out = struct.pack("<6I", *c.dims()) + b"".join(_blob(s) for s in subs)
     out += root(o["rms"][0]["X"]) + root(o["rms"][0]["Y"]) + root(o["rms"][1]["Y"])
     out += b"".join(root(q["CODES"]) for q in o["qn"]) + b"".join(root(q["SCALES"]) for q in o["qn"])
     out += b"".join(root(m["X"]) for m in o["mm"]) + b"".join(root(m["W"]) for m in o["mm"])
     out += b"".join(root(r["Q"]) for r in o["rp"]) + b"".join(root(r["OUT"]) for r in o["rp"])
-    out += b"".join(root(s["P"]) for s in o["sm"]) + b"".join(root(o["qn"][c.qnVT(a)]["X"]) for a in range(A))
+    out += b"".join(root(s["P"]) for s in o["sm"]) + b"".join(root(o["qn"][c.qnVT(a)]["X"]) for a in range(c.A))
     out += root(o["qn"][c.qnAT]["X"]) + root(o["res"][0]["OUT"]) + root(o["sw"]["M"]) + root(o["res"][1]["OUT"])
     for y in w["mmY"]:
         out += struct.pack("<I", len(y)) + np.ascontiguousarray(y, dtype=np.uint16).tobytes()
     sl, sb = _ser_tail(lug, batches)
     return out + sl + struct.pack("<I", len(seam)) + _u64(seam) + sb
+
+
+def tf_prove(engine, tr, w, o, T, art, R, Q, col, strict=True):
+    """p3tf::prove (p3_transformer.cuh:1011-1037), non-zk: all sub-proofs in fixed order on one transcript with one ledger,
+    one merged-lookup flush, the composition seams with both public I/O bindings, one batched opening per size class."""
+    from .ig import Ctx
+    ctx = Ctx()
+    subs = tf_prove_subs(engine, tr, w, o, T, art, R, Q, col, ctx, strict)
+    lug = lu_flush(engine, tr, ctx.luq, ctx.ledger, R, strict)
+    seam = tf_prove_seams(engine, tr, w, o, ctx, strict, True, True)
+    batches = [engine.prove_class(tr, np.stack(k[1]), k[2], R, Q, "tf-bo%d" % i) for i, k in enumerate(ctx.ledger.cls)]
+    return tf_serialize(w, o, subs, lug, seam, batches)
+
+
+# ---------------------------------------------------------------------------------- multi-layer model (p3mdl)
+def mdl_build_witness(c, ids, MW, art, device="cpu", engine=None):
+    """p3mdl::build_model_witness (p3_model.cuh:169-229): embedding gather at the public token ids, the chained layers, final
+    RMSNorm, quantise, LM-head fp8 matmul -> logits.  MW: {"vocab", "emb" (vocab*d bf16), "layers": [layer weights as for
+    tf_build_witness], "gF" (d bf16), "wh": (codes vocab*d uint8, scales vocab uint32)}."""
+    from . import hwl
+    V, d, T = MW["vocab"], c.d, c.T
+    if V & (V - 1):
+        raise ValueError("mdl: vocab must be pow2")
+    ids = np.asarray(ids, dtype=np.int64)
+    if len(ids) != T or (ids >= V).any():
+        raise ValueError("mdl: token ids")
+    inverse = None if engine is None else (lambda t: engine.inv_all_add(t.contiguous(), 0))
+    kw = {"device": device, "inverse": inverse}
+    x0 = np.asarray(MW["emb"], dtype=np.uint16).reshape(V, d)[ids].reshape(-1)
+    w = {"cfg": c, "vocab": V, "ids": ids.astype(np.uint32), "x0": x0, "lay": []}
+    xi = x0
+    for LW in MW["layers"]:
+        w["lay"].append(tf_build_witness(c, xi, LW, art, device, engine))
+        xi = w["lay"][-1]["out"]
+    w["rmsF"] = rms_witness(xi, MW["gF"], T, art, **kw)
+    w["qnF"] = qnt_witness(w["rmsF"]["Y"], T, c.ld, art, **kw)
+    args = (T, d, V, w["qnF"]["C"], MW["wh"][0], w["qnF"]["S"], MW["wh"][1])
+    w["mmH"] = hwl.gen_witness_dev(engine, *args) if engine is not None else hwl.gen_witness(*args, device=device)
+    w["logits"] = w["mmH"]["Y"]
+    return w
+
+
+def mdl_commit(engine, w, MW, R, col):
+    """p3mdl::commit_model (p3_model.cuh:240-296): embedding table, embedded input, the layers chained through shared
+    commitments (layer i + 1's input column is layer i's output column), the head."""
+    from . import hwl
+    c = w["cfg"]
+    com = lambda t: (lambda cc: (cc, engine.commit_gpu_rootonly(cc, R)))(col(t))
+    up = lambda a: com(torch.as_tensor(np.asarray(a).astype(np.int64)))
+    o = {"E": up(MW["emb"]), "X0": up(w["x0"]), "lay": []}
+    for li, wl in enumerate(w["lay"]):
+        o["lay"].append(tf_commit_all(engine, wl, R, col, o["X0"] if li == 0 else o["lay"][li - 1]["res"][1]["OUT"]))
+    o["rmsF"] = {"X": o["lay"][-1]["res"][1]["OUT"], "G": com(w["rmsF"]["gpat"]), "Y": com(w["rmsF"]["ypat"])}
+    o["qnF"] = {"X": o["rmsF"]["Y"], "CODES": com(w["qnF"]["cpat"]), "SCALES": com(w["qnF"]["spat"])}
+    o["mmH"] = {"X": com(w["mmH"]["xcodes"]), "W": com(w["mmH"]["wcodes"]), "XS": o["qnF"]["SCALES"], "WS": com(w["mmH"]["wsb"])}
+    o["YH"] = com(w["mmH"]["dob"][hwl.O_YB])
+    return o
+
+
+def mdl_roots(engine, c, MW, R, col):
+    """p3mdl::model_roots (p3_model.cuh:306-327): embedding, final gain, head codes / scales, then 16 roots per layer."""
+    from . import hwl
+    up = lambda a: engine.commit_gpu_rootonly(engine.upload(np.asarray(a, dtype=np.uint64)), R)
+    V = MW["vocab"]
+    dd = hwl.Dims(c.T, c.d, V)
+    wc = np.zeros((dd.Npad, dd.Kpad), dtype=np.uint64)
+    wc[:V, :c.d] = np.asarray(MW["wh"][0], dtype=np.uint64).reshape(V, c.d)
+    ws = np.zeros(dd.Npad, dtype=np.uint64)
+    ws[:V] = np.asarray(MW["wh"][1], dtype=np.uint64)
+    roots = [up(MW["emb"]), up(MW["gF"]), up(wc.reshape(-1)), up(ws)]
+    for LW in MW["layers"]:
+        roots += tf_weight_roots(engine, c, LW, R, col)
+    return roots
+
+
+def mdl_prove(engine, tr, w, o, T, art, R, Q, col, strict=True):
+    """p3mdl::prove_model (p3_model.cuh:346-448), non-zk: every layer's sub-proofs and the head's on one transcript, ONE
+    merged-lookup flush, per-layer seams without public bindings, the embedding gather seams, the head seams and the public
+    logits binding, ONE batched opening per size class.  Serialised MdlProof: u32 nlayers vocab seq d batch | per layer
+    u32 len + TfProof | rEmb | u32 len + rmsF, qnF, mmH | rRmsFY rCodesF rScalesF rMXH rMWH | u32 count + logits |
+    u32 count + seam values | groups | batches."""
+    from . import hwl
+    from .ig import Ctx
+    c = w["cfg"]
+    V = w["vocab"]
+    lv = V.bit_length() - 1
+    ctx = Ctx()
+    tr.absorb("mdl-dims", struct.pack("<8I", len(w["lay"]), V, *c.dims()))
+    tr.absorb("mdl-ids", np.ascontiguousarray(w["ids"], dtype=np.uint32).tobytes())
+    tr.absorb("mdl-emb", o["E"][1])
+    lay_subs = [tf_prove_subs(engine, tr, wl, ol, T, art, R, Q, col, ctx, strict) for wl, ol in zip(w["lay"], o["lay"])]
+    head = [rms_prove(engine, tr, w["rmsF"], T["rms"], art, o["rmsF"], R, Q, col, ctx, strict),
+            qnt_prove(engine, tr, w["qnF"], T["qnt"], o["qnF"], R, Q, col, ctx, strict),
+            hwl.prove(engine, tr, w["mmH"], T["hw"], o["mmH"], R, Q, col, w["logits"], ctx, strict)]
+    lug = lu_flush(engine, tr, ctx.luq, ctx.ledger, R, strict)
+    lay_seams = [tf_prove_seams(engine, tr, wl, ol, ctx, strict, False, False) for wl, ol in zip(w["lay"], o["lay"])]
+    S = Seams(engine, tr, ctx.ledger, strict, "mdl")
+    bits = lambda v, n: [(int(v) >> i) & 1 for i in range(n)]
+    for t in range(c.T):
+        z = S.chal_vec(c.ld)
+        S.pair(o["X0"], z + bits(t, c.lT), o["E"], z + bits(w["ids"][t], lv), "embedding gather")
+    lkH = w["mmH"]["d"].Kpad.bit_length() - 1
+    S.codes(o["qnF"]["CODES"], o["mmH"]["X"], c.ld, lkH, c.lT, "head codes")
+    S.cl(o["YH"], S.chal_vec(lv + c.lT))
+    batches = [engine.prove_class(tr, np.stack(k[1]), k[2], R, Q, "tf-bo%d" % i) for i, k in enumerate(ctx.ledger.cls)]
+    out = struct.pack("<5I", len(w["lay"]), V, c.seq, c.d, c.batch)
+    for wl, ol, subs, seam in zip(w["lay"], o["lay"], lay_subs, lay_seams):
+        out += _blob(tf_serialize(wl, ol, subs, [], seam, []))
+    out += o["E"][1] + b"".join(_blob(h) for h in head)
+    out += o["rmsF"]["Y"][1] + o["qnF"]["CODES"][1] + o["qnF"]["SCALES"][1] + o["mmH"]["X"][1] + o["mmH"]["W"][1]
+    out += struct.pack("<I", len(w["logits"])) + np.ascontiguousarray(w["logits"], dtype=np.uint16).tobytes()
+    sl, sb = _ser_tail(lug, batches)
+    return out + struct.pack("<I", len(S.vals)) + _u64(S.vals) + sl + sb
