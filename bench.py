@@ -607,6 +607,24 @@ def run_profile_case(args):
             nc = 3 if name == "fr_hp3" else 2
             cols = [rand_fr(1 << 21) for _ in range(nc)]
             fn = lambda: zk.fr.product_sumcheck(prover, zk.Transcript("prof"), cols, ["l%d" % t for t in range(nc + 1)])
+    elif name == "hwl_witness":
+        # fp8 witness replay, 64 x 512 . 512 x 256: 2^24 padded products, 1.9 GB of columns written
+        dims = (64, 512, 256)
+        x = rng.integers(0, 256, dims[0] * dims[1]).astype(np.uint8)
+        w = rng.integers(0, 256, dims[2] * dims[1]).astype(np.uint8)
+        x[(x & 0x7F) == 0x7F] = 0x38
+        w[(w & 0x7F) == 0x7F] = 0x38
+        xs = np.full(dims[0], np.float32(1.0)).view(np.uint32)
+        ws = np.full(dims[2], np.float32(0.02)).view(np.uint32)
+        fn = lambda: zk.hwl.gen_witness_dev(prover, *dims, x, w, xs, ws)
+    elif name == "zc_bfadd":
+        # zero-check of the bf16 add gadget's constraint system (59 columns, 116 monomials) over 2^19 rows: 247 MB of columns
+        tfg = zk.tfg
+        cv = {nm: tfg.Poly.var(4 + i) for i, nm in enumerate(tfg.BA_COLS)}
+        lam = [int(v) for v in rng.integers(1, 0xFFFFFFFF00000001, tfg.N_BA_C, dtype=np.uint64)]
+        terms, konst = tfg.zc_terms(tfg.ba_constraints(cv, tfg.Poly.var(1), tfg.Poly.var(2), tfg.Poly.var(3)), lam)
+        cols = [gl_rand(1 << 19) for _ in range(4 + tfg.NBA)]
+        fn = lambda: prover.sc_prove_zc(zk.Transcript("prof"), "bfa-scE", cols, terms, konst)
     else:
         raise SystemExit("unknown profile case " + name)
     fn()
