@@ -272,6 +272,13 @@ ZKH_API int zkh_batchopen_prove_class_kept(zkh_ctx* ctx, uint32_t v, const uint6
                                    uint8_t* out, size_t cap, size_t* written, const uint64_t* const* kept_cw,
                                    const uint8_t* const* kept_tree);
 
+/* Hiding commitment: salted Merkle leaves (zkllm-src/p3_zkc.cuh:230-292 salt_of / salted_leaf / p3zkc_salted_leaf_kernel,
+ * :320-397 salted_commit_root, salted_commit_root_dev).  Leaf i = SHA-256(value_le8 | SHA-256(sseed_le8 | i_le8)); internal
+ * nodes as in the plain tree, so authentication paths verify unchanged.  cw_dev (2^(v+R) elements) and tree_dev
+ * (zkh_merkle_tree_bytes(2^(v+R)) bytes) are optional; a kept tree needs the kept codeword. */
+ZKH_API int zkh_basefold_commit_salted(zkh_ctx* ctx, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t sseed,
+                               uint64_t* cw_dev, uint8_t* tree_dev, uint8_t root[32]);
+
 /* ---- logUp ---- */
 /* Multiplicities: cnt_dev[j] = #{i : idx_dev[i] == j}, j < M (zkllm-src/p3_logup.cuh:149-172,
  * host loop :1412-1475).  An index >= M returns ZKH_ERR_DOMAIN (the reference throws). */

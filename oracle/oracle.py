@@ -152,6 +152,15 @@ class _Lib:
         cw, p = _u64(cw); out = np.empty((2 * len(cw) - 1) * 32, dtype=np.uint8)
         self._f("merkle_build")(p, len(cw), out.ctypes.data_as(C.c_void_p)); return out
 
+    def salted_leaf(self, v, sseed, idx):
+        """hiding-commitment leaf SHA-256(value | SHA-256(seed | index)) (reference: p3zkc::salted_leaf o salt_of)"""
+        out = _bytes32()
+        if self.prefix == "ref_":
+            self.lib.ref_salted_leaf(C.c_uint64(v), C.c_uint64(sseed), C.c_uint64(idx), out)
+        else:
+            self.lib.orc_salted_leaf_hash(C.c_uint64(v), C.c_uint64(sseed), C.c_uint64(idx), out)
+        return bytes(out)
+
     def fold(self, f, wM, beta, mle=True):
         f, p = _u64(f); out = np.empty(len(f) // 2, dtype=np.uint64)
         self._f("fold")(p, len(f), wM, beta, int(mle), out.ctypes.data_as(u64p)); return out
@@ -293,6 +302,10 @@ class Oracle(_Lib):
         assert rc == 0
         return bytes(s), msgs, chals, fin
 
+    def merkle_build_salted(self, cw, sseed):
+        cw, p = _u64(cw); out = np.empty((2 * len(cw) - 1) * 32, dtype=np.uint8)
+        self.lib.orc_merkle_build_salted(p, C.c_size_t(len(cw)), C.c_uint64(sseed), out.ctypes.data_as(C.c_void_p)); return out
+
     def mle_eval(self, c, z):
         c, cp = _u64(c); z, zp = _u64(z); return self.lib.orc_mle_eval(cp, zp, len(z))
 
@@ -392,6 +405,15 @@ class Reference(_Lib):
         if rc != 0:
             raise RuntimeError("ref_commit_gpu_rootonly failed")
         return bytes(out), ms.value
+
+    def salted_commit_root(self, c, R, sseed):
+        """p3zkc::salted_commit_root_dev on the GPU (salting on)"""
+        c, cp = _u64(c); v = int(len(c)).bit_length() - 1
+        out = _bytes32()
+        rc = self.lib.ref_salted_commit_root(cp, C.c_uint32(v), C.c_uint32(R), C.c_uint64(sseed), out)
+        if rc != 0:
+            raise RuntimeError("ref_salted_commit_root rc=%d" % rc)
+        return bytes(out)
 
     def rs_encode_gpu(self, c, R):
         c, cp = _u64(c); v = int(len(c)).bit_length() - 1

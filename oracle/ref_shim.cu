@@ -2227,4 +2227,30 @@ int ref_mdl_verify(uint8_t st[32], const uint32_t dims[6], uint32_t nlayers, uin
     return ok;
 }
 
+// ---- hiding commitment (p3_zkc.cuh) ----
+// host: p3zkc::salted_leaf(v, p3zkc::salt_of(sseed, i))
+void ref_salted_leaf(uint64_t v, uint64_t sseed, uint64_t i, uint8_t out[32]) {
+    p3fri::Hash h = p3zkc::salted_leaf(v, p3zkc::salt_of(sseed, i));
+    memcpy(out, h.data(), 32);
+}
+// GPU: p3zkc::salted_commit_root_dev of 2^v values with salting on
+int ref_salted_commit_root(const uint64_t* c, uint32_t v, uint32_t R, uint64_t sseed, uint8_t root[32]) {
+    int rc = 0;
+    const bool was = p3zkc::G.salt_on;
+    try {
+        p3fri::g_gpu_merkle = true;
+        p3zkc::G.salt_on = true;
+        const size_t n = (size_t)1 << v;
+        gl_t* d = p3bf::dmalloc(n, "shim:salt");
+        cudaMemcpy(d, c, n * 8, cudaMemcpyHostToDevice);
+        p3fri::Hash h = p3zkc::salted_commit_root_dev(d, n, R, sseed);
+        cudaFreeAsync(d, 0);
+        cudaDeviceSynchronize();
+        memcpy(root, h.data(), 32);
+    } catch (...) { rc = -1; }
+    p3zkc::G.salt_on = was;
+    p3fri::g_gpu_merkle = false;
+    return rc;
+}
+
 }  // extern "C"

@@ -423,6 +423,15 @@ void orc_leaf_hash(uint64_t v, uint8_t out[32]) {
     orc_sha256(b, 8, out);
 }
 /* zkllm-src/p3_fri.cuh:36-39 -- single compression of l|r from the IV */
+/* salted leaf of the hiding commitment (zkllm-src/p3_zkc.cuh:235-249 salt_of, salted_leaf):
+ * salt = SHA-256(seed_le8 | index_le8), leaf = SHA-256(value_le8 | salt) */
+void orc_salted_leaf_hash(uint64_t v, uint64_t sseed, uint64_t idx, uint8_t out[32]) {
+    uint8_t b[40], sb[16];
+    for (int k = 0; k < 8; k++) { sb[k] = (uint8_t)(sseed >> (8 * k)); sb[8 + k] = (uint8_t)(idx >> (8 * k)); }
+    orc_sha256(sb, 16, b + 8);
+    for (int k = 0; k < 8; k++) b[k] = (uint8_t)(v >> (8 * k));
+    orc_sha256(b, 40, out);
+}
 void orc_node_hash(const uint8_t l[32], const uint8_t r[32], uint8_t out[32]) {
     uint8_t b[64];
     memcpy(b, l, 32);
@@ -443,6 +452,16 @@ void orc_merkle_build(const uint64_t* cw, size_t M, uint8_t* tree) {
 #endif
         for (size_t i = 0; i < cnt / 2; i++)
             orc_node_hash(cur + 2 * i * 32, cur + (2 * i + 1) * 32, nxt + i * 32);
+        cur = nxt;
+    }
+}
+/* tree with salted leaves; internal nodes as orc_merkle_build (zkllm-src/p3_zkc.cuh:294-318 SaltedDevMerkle) */
+void orc_merkle_build_salted(const uint64_t* cw, size_t M, uint64_t sseed, uint8_t* tree) {
+    for (size_t i = 0; i < M; i++) orc_salted_leaf_hash(cw[i], sseed, (uint64_t)i, tree + i * 32);
+    uint8_t* cur = tree;
+    for (size_t cnt = M; cnt > 1; cnt >>= 1) {
+        uint8_t* nxt = cur + cnt * 32;
+        for (size_t i = 0; i < cnt / 2; i++) orc_node_hash(cur + 2 * i * 32, cur + (2 * i + 1) * 32, nxt + i * 32);
         cur = nxt;
     }
 }

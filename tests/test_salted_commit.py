@@ -1,0 +1,51 @@
+"""Hiding (salted-leaf) commitments: the oracle restatement against hashlib and the reference's host functions; the CUDA
+kernels against the oracle and, on a GPU machine, against the reference's own salted commitment."""
+import hashlib
+import struct
+
+import numpy as np
+import pytest
+
+from conftest import lcg_cols
+
+
+def test_salted_leaf_oracle_matches_hashlib_and_reference(orc, ref_or_none):
+    for v, seed, i in [(0, 0, 0), (1, 2, 3), (0xFFFFFFFF00000000, 0xDEADBEEFCAFEF00D, 1 << 40), (12345, 99, 7)]:
+        salt = hashlib.sha256(struct.pack("<QQ", seed, i)).digest()
+        want = hashlib.sha256(struct.pack("<Q", v) + salt).digest()
+        assert orc.salted_leaf(v, seed, i) == want
+        if ref_or_none:
+            assert ref_or_none.salted_leaf(v, seed, i) == want
+
+
+def test_salted_tree_oracle_structure(orc):
+    cw = lcg_cols(orc, 8, 1, 5)[0]
+    tree = orc.merkle_build_salted(cw, 77).tobytes()
+    leaves = [orc.salted_leaf(int(x), 77, i) for i, x in enumerate(cw)]
+    assert tree[:8 * 32] == b"".join(leaves)
+    plain = orc.merkle_build(cw).tobytes()
+    assert tree[:32] != plain[:32] and len(tree) == len(plain)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("v,R", [(1, 1), (3, 2), (10, 1), (16, 1)])
+def test_salted_commit_kernel_matches_oracle(orc, zk, prover, v, R):
+    c = lcg_cols(orc, 1 << v, 1, 40 + v)[0]
+    sseed = 0x1234567890ABCDEF + v
+    cw = orc.rs_encode(c, R)
+    want_tree = orc.merkle_build_salted(cw, sseed).tobytes()
+    d = zk.p3.to_device(c)
+    assert prover.commit_salted(d, R, sseed) == want_tree[-32:]
+    root, cw_dev, tree_dev = prover.commit_salted(d, R, sseed, keep=True)
+    assert root == want_tree[-32:] and (zk.p3.to_host(cw_dev) == cw).all()
+    assert tree_dev.cpu().numpy().tobytes() == want_tree
+    assert prover.commit_salted(d, R, sseed + 1) != root and prover.commit_gpu_rootonly(d, R) != root
+
+
+@pytest.mark.gpu
+def test_salted_commit_equals_reference_cuda(orc, ref, zk, prover):
+    if not ref.gpu_available():
+        pytest.skip("reference shim sees no GPU")
+    for v, R in [(12, 1), (18, 2)]:
+        c = lcg_cols(orc, 1 << v, 1, 3 + v)[0]
+        assert prover.commit_salted(zk.p3.to_device(c), R, 424242) == ref.salted_commit_root(c, R, 424242)

@@ -151,6 +151,28 @@ extern "C" int zkh_basefold_commit_keep(zkh_ctx* c, const uint64_t* c_dev, uint3
     return ZKH_OK;
 }
 
+// Hiding commitment (zkllm-src/p3_zkc.cuh:320-397 salted_commit_root / salted_commit_root_dev): the same codeword, leaves
+// salted with SHA-256(seed | leaf index).  cw_dev / tree_dev optional (both or none keep codeword and tree resident).
+extern "C" int zkh_basefold_commit_salted(zkh_ctx* c, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t sseed,
+                                          uint64_t* cw_dev, uint8_t* tree_dev, uint8_t root[32]) {
+    if (!c || !c_dev || !root) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_salted: null pointer");
+    if (v + R < 1 || v + R > 32 || R < 1 || R > 8) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_salted: need R in 1..8, v+R <= 32");
+    if (tree_dev && !cw_dev) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_salted: a kept tree needs the kept codeword");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    const uint32_t logM = v + R;
+    const size_t M = (size_t)1 << logM;
+    const size_t cwb = cw_dev ? 0 : zkh_align(M * 8), nttb = ntt_scratch_bytes(logM), mkb = tree_dev ? 0 : merkle_scratch_bytes(M);
+    ZKH_TRY(zkh_ws_reserve(c, cwb + nttb + mkb));
+    gl_t* cw = cw_dev ? cw_dev : (gl_t*)c->ws;
+    ZKH_TRY(ntt_enqueue(c, c_dev, (uint64_t)1 << v, cw, logM, false, (char*)c->ws + cwb));
+    uint8_t* root_dev = (uint8_t*)c->d_ctl->aux;
+    ZKH_TRY(merkle_enqueue(c, cw, M, tree_dev, tree_dev ? nullptr : (char*)c->ws + cwb + nttb, root_dev, &sseed));
+    ZKH_CUDA(c, cudaMemcpyAsync(c->h_ctl->aux, root_dev, 32, cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    memcpy(root, c->h_ctl->aux, 32);
+    return ZKH_OK;
+}
+
 extern "C" int zkh_basefold_commit_host(zkh_ctx* c, const uint64_t* coeffs, uint32_t v, uint32_t R, uint8_t root[32]) {
     if (!c || !coeffs || !root) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_host: null pointer");
     if (v + R < 1 || v + R > 32 || R < 1 || R > 8) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_host: need R in 1..8, v+R <= 32");

@@ -22,19 +22,26 @@ __device__ __forceinline__ void load_digest(const uint32_t* src, uint32_t h[8]) 
     h[4] = bswap32(b.x); h[5] = bswap32(b.y); h[6] = bswap32(b.z); h[7] = bswap32(b.w);
 }
 
+// leaf digest: plain, or salted with (seed, leaf index) for hiding commitments (zkllm-src/p3_zkc.cuh:272-279)
+template <bool SALT>
+__device__ __forceinline__ void leaf_digest(gl_t v, uint64_t sseed, size_t idx, uint32_t h[8]) {
+    if (SALT) sha256_salted_leaf(v, sseed, (uint64_t)idx, h);
+    else sha256_leaf(v, h);
+}
 // thread i: leaves 4i..4i+3 -> level-1 nodes 2i, 2i+1 -> level-2 node i
+template <bool SALT>
 __global__ void __launch_bounds__(256)
-merkle_leaf4_kernel(const gl_t* __restrict__ cw, uint32_t* lv0, uint32_t* lv1, uint32_t* lv2, size_t quads) {
+merkle_leaf4_kernel(const gl_t* __restrict__ cw, uint32_t* lv0, uint32_t* lv1, uint32_t* lv2, size_t quads, uint64_t sseed) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= quads) return;
     ulonglong2 a = ld2(cw + 4 * i), b = ld2(cw + 4 * i + 2);
     uint32_t h0[8], h1[8], n0[8], n1[8], top[8];
-    sha256_leaf(a.x, h0);
-    sha256_leaf(a.y, h1);
+    leaf_digest<SALT>(a.x, sseed, 4 * i, h0);
+    leaf_digest<SALT>(a.y, sseed, 4 * i + 1, h1);
     if (lv0) { store_digest(lv0 + (4 * i) * 8, h0); store_digest(lv0 + (4 * i + 1) * 8, h1); }
     sha256_node(h0, h1, n0);
-    sha256_leaf(b.x, h0);
-    sha256_leaf(b.y, h1);
+    leaf_digest<SALT>(b.x, sseed, 4 * i + 2, h0);
+    leaf_digest<SALT>(b.y, sseed, 4 * i + 3, h1);
     if (lv0) { store_digest(lv0 + (4 * i + 2) * 8, h0); store_digest(lv0 + (4 * i + 3) * 8, h1); }
     sha256_node(h0, h1, n1);
     if (lv1) { store_digest(lv1 + (2 * i) * 8, n0); store_digest(lv1 + (2 * i + 1) * 8, n1); }
@@ -67,18 +74,19 @@ __global__ void merkle_node2_kernel(const uint32_t* __restrict__ in, uint32_t* u
     sha256_node(a, b, n);
     store_digest(up + i * 8, n);
 }
-__global__ void merkle_leaf1_kernel(const gl_t* __restrict__ cw, uint32_t* lv0, size_t M) {
+template <bool SALT>
+__global__ void merkle_leaf1_kernel(const gl_t* __restrict__ cw, uint32_t* lv0, size_t M, uint64_t sseed) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= M) return;
     uint32_t h[8];
-    sha256_leaf(cw[i], h);
+    leaf_digest<SALT>(cw[i], sseed, i, h);
     store_digest(lv0 + i * 8, h);
 }
 __global__ void copy32_kernel(const uint32_t* src, uint32_t* dst) {
     if (threadIdx.x < 8) dst[threadIdx.x] = src[threadIdx.x];
 }
 
-int merkle_enqueue(zkh_ctx* c, const gl_t* cw, size_t M, uint8_t* tree, void* scratch, uint8_t* root_dev) {
+int merkle_enqueue(zkh_ctx* c, const gl_t* cw, size_t M, uint8_t* tree, void* scratch, uint8_t* root_dev, const uint64_t* sseed) {
     if (M < 2 || (M & (M - 1))) return zkh_fail(c, ZKH_ERR_ARG, "merkle: leaf count must be a power of two >= 2");
     cudaStream_t s = c->stream;
     auto level_ptr = [&](size_t cnt_at_level) -> uint32_t* {  // start of the level that has cnt nodes
@@ -91,13 +99,17 @@ int merkle_enqueue(zkh_ctx* c, const gl_t* cw, size_t M, uint8_t* tree, void* sc
     size_t cnt;
     if (M >= 4) {
         uint32_t* l2 = tree ? level_ptr(M / 4) : sA;
-        merkle_leaf4_kernel<<<(unsigned)((M / 4 + 255) / 256), 256, 0, s>>>(
-            cw, tree ? level_ptr(M) : nullptr, tree ? level_ptr(M / 2) : nullptr, l2, M / 4);
+        uint32_t* l0 = tree ? level_ptr(M) : nullptr;
+        uint32_t* l1 = tree ? level_ptr(M / 2) : nullptr;
+        const unsigned grid = (unsigned)((M / 4 + 255) / 256);
+        if (sseed) merkle_leaf4_kernel<true><<<grid, 256, 0, s>>>(cw, l0, l1, l2, M / 4, *sseed);
+        else merkle_leaf4_kernel<false><<<grid, 256, 0, s>>>(cw, l0, l1, l2, M / 4, 0);
         cur = l2;
         cnt = M / 4;
     } else {
         uint32_t* l0 = tree ? level_ptr(M) : sA;
-        merkle_leaf1_kernel<<<1, 32, 0, s>>>(cw, l0, M);
+        if (sseed) merkle_leaf1_kernel<true><<<1, 32, 0, s>>>(cw, l0, M, *sseed);
+        else merkle_leaf1_kernel<false><<<1, 32, 0, s>>>(cw, l0, M, 0);
         cur = l0;
         cnt = M;
     }

@@ -10,5 +10,7 @@ inline size_t merkle_scratch_bytes(size_t M) { return merkle_scratch_a(M) + zkh_
 // Queue the tree build.  tree != nullptr: every level is stored there and the root is the
 // last 32 bytes.  tree == nullptr: only the root is produced, levels live in `scratch`
 // (merkle_scratch_bytes).  root_dev (optional) receives a copy of the root digest bytes.
-int merkle_enqueue(zkh_ctx* c, const gl_t* cw, size_t M, uint8_t* tree, void* scratch, uint8_t* root_dev);
+// sseed != nullptr: salted leaves SHA-256(value | SHA-256(seed | index)) for hiding commitments.
+int merkle_enqueue(zkh_ctx* c, const gl_t* cw, size_t M, uint8_t* tree, void* scratch, uint8_t* root_dev,
+                   const uint64_t* sseed = nullptr);
 }  // namespace zkh

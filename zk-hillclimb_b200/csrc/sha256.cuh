@@ -86,6 +86,28 @@ GL_HD void sha256_leaf(gl_t v, uint32_t out[8]) {
     sha256_iv(out);
     sha256_compress(out, w);
 }
+// Salted (hiding) Merkle leaf (zkllm-src/p3_zkc.cuh:230-270): salt = SHA-256(seed_le8 | index_le8), leaf =
+// SHA-256(value_le8 | salt); both are single padded blocks, the salt's digest words feed the leaf block directly.
+GL_HD void sha256_salted_leaf(gl_t v, uint64_t sseed, uint64_t idx, uint32_t out[8]) {
+    uint32_t w[16], hs[8];
+    w[0] = bswap32((uint32_t)sseed); w[1] = bswap32((uint32_t)(sseed >> 32));
+    w[2] = bswap32((uint32_t)idx); w[3] = bswap32((uint32_t)(idx >> 32));
+    w[4] = 0x80000000u;
+#pragma unroll
+    for (int i = 5; i < 15; i++) w[i] = 0;
+    w[15] = 128;  // 16-byte message
+    sha256_iv(hs);
+    sha256_compress(hs, w);
+    w[0] = bswap32((uint32_t)v); w[1] = bswap32((uint32_t)(v >> 32));
+#pragma unroll
+    for (int i = 0; i < 8; i++) w[2 + i] = hs[i];
+    w[10] = 0x80000000u;
+#pragma unroll
+    for (int i = 11; i < 15; i++) w[i] = 0;
+    w[15] = 320;  // 40-byte message
+    sha256_iv(out);
+    sha256_compress(out, w);
+}
 // Merkle node: compression of the two child digests, IV start, no length block.
 GL_HD void sha256_node(const uint32_t l[8], const uint32_t r[8], uint32_t out[8]) {
     uint32_t w[16];

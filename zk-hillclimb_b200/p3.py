@@ -255,6 +255,20 @@ class Prover:
             self._ck(self._L.zkh_basefold_commit(self._h, _ptr(c), c.numel().bit_length() - 1, R, 0, root))
         return bytes(root)
 
+    def commit_salted(self, c, R, sseed, keep=False):
+        """p3zkc::salted_commit_root_dev (zkllm-src/p3_zkc.cuh:362-397): hiding commitment root of a device column, leaves
+        salted with SHA-256(seed | index).  keep: also return the codeword and the tree (device tensors)."""
+        import torch
+        v = int(c.numel()).bit_length() - 1
+        root = _buf32()
+        cw = tree = None
+        if keep:
+            M = 1 << (v + R)
+            cw = torch.empty(M, dtype=torch.int64, device=c.device)
+            tree = torch.empty(self._L.zkh_merkle_tree_bytes(M), dtype=torch.uint8, device=c.device)
+        self._ck(self._L.zkh_basefold_commit_salted(self._h, _ptr(c), v, R, sseed, _ptr(cw) if keep else 0, _ptr(tree) if keep else 0, root))
+        return (bytes(root), cw, tree) if keep else bytes(root)
+
     def release_kept(self):
         """Drop the codewords and trees kept by commit_gpu_rootonly under ``keep_trees``."""
         self.__dict__.pop("_kept", None)
