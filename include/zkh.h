@@ -279,6 +279,16 @@ ZKH_API int zkh_batchopen_prove_class_kept(zkh_ctx* ctx, uint32_t v, const uint6
 ZKH_API int zkh_basefold_commit_salted(zkh_ctx* ctx, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t sseed,
                                uint64_t* cw_dev, uint8_t* tree_dev, uint8_t root[32]);
 
+/* Randomness of the hiding mode (zkllm-src/p3_zkc.cuh:100-123 zprng / zprng_at, :471-534 zprng_fill / zprng_fill_at /
+ * blind_col_aug_dev, :158-185 fresh_mask_into / augment).  Stream-ordered.
+ *   zkh_zk_fill_at     out[i] = zprng_at(seed, i0 + i): the random-access stream of blind columns
+ *   zkh_zk_fill_chain  out[i] = element k0 + i of the zprng chain started at state s0 (element 0 = first output)
+ *   zkh_zk_augment     out = [col (2^v) | mask slices ((2^e - 1) * 2^v chain elements from mask_seed)]; mask_seed 0
+ *                      gives zero slices (the reference's masks-off control) */
+ZKH_API int zkh_zk_fill_at(zkh_ctx* ctx, uint64_t seed, uint64_t i0, uint64_t n, uint64_t* out_dev);
+ZKH_API int zkh_zk_fill_chain(zkh_ctx* ctx, uint64_t s0, uint64_t k0, uint64_t n, uint64_t* out_dev);
+ZKH_API int zkh_zk_augment(zkh_ctx* ctx, const uint64_t* col_dev, uint32_t v, uint32_t e, uint64_t mask_seed, uint64_t* out_dev);
+
 /* ---- logUp ---- */
 /* Multiplicities: cnt_dev[j] = #{i : idx_dev[i] == j}, j < M (zkllm-src/p3_logup.cuh:149-172,
  * host loop :1412-1475).  An index >= M returns ZKH_ERR_DOMAIN (the reference throws). */

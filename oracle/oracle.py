@@ -152,6 +152,18 @@ class _Lib:
         cw, p = _u64(cw); out = np.empty((2 * len(cw) - 1) * 32, dtype=np.uint8)
         self._f("merkle_build")(p, len(cw), out.ctypes.data_as(C.c_void_p)); return out
 
+    def zprng_fill(self, s, n):
+        """n elements of the hiding mode's mask chain from state s (reference: p3zkc::zprng_fill)"""
+        out = np.empty(n, dtype=np.uint64)
+        f = self.lib.ref_zprng_fill if self.prefix == "ref_" else self.lib.orc_zprng_fill
+        f(C.c_uint64(s), out.ctypes.data_as(u64p), C.c_size_t(n))
+        return out
+
+    def zprng_at(self, seed, i):
+        f = self.lib.ref_zprng_at if self.prefix == "ref_" else self.lib.orc_zprng_at
+        f.restype = C.c_uint64
+        return int(f(C.c_uint64(seed), C.c_uint64(i)))
+
     def salted_leaf(self, v, sseed, idx):
         """hiding-commitment leaf SHA-256(value | SHA-256(seed | index)) (reference: p3zkc::salted_leaf o salt_of)"""
         out = _bytes32()

@@ -2253,4 +2253,8 @@ int ref_salted_commit_root(const uint64_t* c, uint32_t v, uint32_t R, uint64_t s
     return rc;
 }
 
+// host: p3zkc::zprng_fill (the mask chain) and p3zkc::zprng_at (the random-access stream)
+void ref_zprng_fill(uint64_t s, uint64_t* out, size_t n) { p3zkc::zprng_fill(s, out, n); }
+uint64_t ref_zprng_at(uint64_t seed, uint64_t i) { return p3zkc::zprng_at(seed, i); }
+
 }  // extern "C"

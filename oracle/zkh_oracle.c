@@ -875,6 +875,22 @@ void orc_lcg_fill(uint64_t* out, size_t n, uint64_t* state) {
     *state = s;
 }
 
+/* randomness of the hiding mode (zkllm-src/p3_zkc.cuh:100-118): the sequential chain and the random-access stream */
+void orc_zprng_fill(uint64_t s, uint64_t* out, size_t n) {
+    for (size_t i = 0; i < n; i++) {
+        s = s * 6364136223846793005ULL + 1442695040888963407ULL;
+        uint64_t z = s ^ (s >> 31);
+        out[i] = z % P;
+    }
+}
+uint64_t orc_zprng_at(uint64_t seed, uint64_t i) {
+    uint64_t z = seed + 0x9E3779B97F4A7C15ULL * (i + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+    z ^= z >> 31;
+    return z % P;
+}
+
 /* ======================= batched opening (one size class, non-zk) ======================= */
 /* Serialized BatchProof (fields of p3bo::BatchProof in declaration order, zk fields omitted):
  *   u32 v, R, Q, nc | ystar nc*8 | rmsgs v*24 | roots (v-1)*32 | omsgs v*24 | final 2^R*8 |

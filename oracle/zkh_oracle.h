@@ -84,6 +84,8 @@ void orc_ntt(uint64_t* a, uint32_t logn, int inverse); /* in place, natural orde
  * tree holds all levels back to back: level 0 (M leaf hashes), level 1 (M/2) ...
  * total (2M-1)*32 bytes. */
 void orc_leaf_hash(uint64_t v, uint8_t out[32]);
+void orc_zprng_fill(uint64_t s, uint64_t* out, size_t n);
+uint64_t orc_zprng_at(uint64_t seed, uint64_t i);
 void orc_salted_leaf_hash(uint64_t v, uint64_t sseed, uint64_t idx, uint8_t out[32]);
 void orc_merkle_build_salted(const uint64_t* cw, size_t M, uint64_t sseed, uint8_t* tree);
 void orc_node_hash(const uint8_t l[32], const uint8_t r[32], uint8_t out[32]);

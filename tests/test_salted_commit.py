@@ -49,3 +49,29 @@ def test_salted_commit_equals_reference_cuda(orc, ref, zk, prover):
     for v, R in [(12, 1), (18, 2)]:
         c = lcg_cols(orc, 1 << v, 1, 3 + v)[0]
         assert prover.commit_salted(zk.p3.to_device(c), R, 424242) == ref.salted_commit_root(c, R, 424242)
+
+
+def test_zk_randomness_oracle_matches_reference(orc, ref_or_none):
+    a = orc.zprng_fill(0xABCDEF, 1000)
+    assert int(a[0]) == ((lambda s: (s ^ (s >> 31)) % 0xFFFFFFFF00000001)((0xABCDEF * 6364136223846793005 + 1442695040888963407) % (1 << 64)))
+    assert orc.zprng_at(5, 0) == orc.zprng_at(5, 0) and orc.zprng_at(5, 0) != orc.zprng_at(5, 1)
+    if ref_or_none:
+        assert (ref_or_none.zprng_fill(0xABCDEF, 1000) == a).all()
+        big = 1 << 20                                      # the reference's parallel (jump-ahead) path
+        assert (ref_or_none.zprng_fill(77, big) == orc.zprng_fill(77, big)).all()
+        for seed, i in [(1, 0), (0xFFFFFFFFFFFFFFFF, 12345), (99, 1 << 40)]:
+            assert ref_or_none.zprng_at(seed, i) == orc.zprng_at(seed, i)
+
+
+@pytest.mark.gpu
+def test_zk_fill_kernels_match_oracle(orc, zk, prover):
+    for n in (1, 7, 2048, 2049, (1 << 18) + 3):
+        want = orc.zprng_fill(424242, n + 100)
+        assert (zk.p3.to_host(prover.zk_fill_chain(424242, n)) == want[:n]).all()
+        assert (zk.p3.to_host(prover.zk_fill_chain(424242, n, k0=100)) == want[100:100 + n]).all()
+    got = zk.p3.to_host(prover.zk_fill_at(31337, 5000, i0=10))
+    assert all(int(got[i]) == orc.zprng_at(31337, 10 + i) for i in (0, 1, 17, 4999))
+    col = lcg_cols(orc, 1 << 10, 1, 8)[0]
+    aug = zk.p3.to_host(prover.zk_augment(zk.p3.to_device(col), 2, 555))
+    assert (aug[:1 << 10] == col).all() and (aug[1 << 10:] == orc.zprng_fill(555, 3 << 10)).all()
+    assert (zk.p3.to_host(prover.zk_augment(zk.p3.to_device(col), 1, 0))[1 << 10:] == 0).all()

@@ -98,6 +98,9 @@ def load_library():
         "zkh_gl_mul": (i, [vp, vp, vp, u64, vp]),
         "zkh_irs_witness": (i, [vp, vp, u64, u32, i, vp, vp, vp, vp, vp, vp]),
         "zkh_basefold_commit_salted": (i, [vp, vp, u32, u32, u64, vp, vp, vp]),
+        "zkh_zk_fill_at": (i, [vp, u64, u64, u64, vp]),
+        "zkh_zk_fill_chain": (i, [vp, u64, u64, u64, vp]),
+        "zkh_zk_augment": (i, [vp, vp, u32, u32, u64, vp]),
         "zkh_hwl_witness": (i, [vp, u32, u32, u32, vp, vp, vp, vp, vp, vp]),
         "zkh_gkr_proof_size": (sz, [u32]),
         "zkh_gkr_prove": (i, [vp, vp, vp, u32, i, C.c_char_p, vp, vp, vp, vp, sz, C.POINTER(sz)]),

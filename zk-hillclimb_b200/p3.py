@@ -269,6 +269,28 @@ class Prover:
         self._ck(self._L.zkh_basefold_commit_salted(self._h, _ptr(c), v, R, sseed, _ptr(cw) if keep else 0, _ptr(tree) if keep else 0, root))
         return (bytes(root), cw, tree) if keep else bytes(root)
 
+    def zk_fill_at(self, seed, n, i0=0):
+        """p3zkc::zprng_at stream (zkllm-src/p3_zkc.cuh:108-118): out[i] = zprng_at(seed, i0 + i)."""
+        import torch
+        out = torch.empty(n, dtype=torch.int64, device="cuda:%d" % self.device)
+        self._ck(self._L.zkh_zk_fill_at(self._h, seed, i0, n, _ptr(out)))
+        return out
+
+    def zk_fill_chain(self, s0, n, k0=0):
+        """p3zkc::zprng_fill / zprng_fill_at (zkllm-src/p3_zkc.cuh:498-534): n elements of the chain from state s0, offset k0."""
+        import torch
+        out = torch.empty(n, dtype=torch.int64, device="cuda:%d" % self.device)
+        self._ck(self._L.zkh_zk_fill_chain(self._h, s0, k0, n, _ptr(out)))
+        return out
+
+    def zk_augment(self, col, e, mask_seed):
+        """p3zkc::augment(vals, fresh mask from mask_seed) (zkllm-src/p3_zkc.cuh:158-185): [real | mask slices]."""
+        import torch
+        v = int(col.numel()).bit_length() - 1
+        out = torch.empty(1 << (v + e), dtype=torch.int64, device=col.device)
+        self._ck(self._L.zkh_zk_augment(self._h, _ptr(col), v, e, mask_seed, _ptr(out)))
+        return out
+
     def release_kept(self):
         """Drop the codewords and trees kept by commit_gpu_rootonly under ``keep_trees``."""
         self.__dict__.pop("_kept", None)
