@@ -167,7 +167,20 @@ def _commit_worker(rank, world, port, q):
     roots = zk.p3.commit_columns_sharded(eng, mine, 1, dist)
     want = [orc.merkle_root(orc.rs_encode(c, 1)) for c in cols]
     sizes = zk.p3.run_independent(list(range(7)), lambda i: (i, rank, i * i), dist)
-    ok = roots == want and [x[0] for x in sizes] == list(range(7)) and all(x[1] == x[0] % world for x in sizes)
+    # lookup multiplicities from index arrays split over the ranks
+    import numpy as np
+    import torch
+
+    class _TorchHist:
+        def histogram(self, idx, M):
+            return torch.bincount(idx.to(torch.int64), minlength=M)
+    allidx = np.random.default_rng(3).integers(0, 64, 1000).astype(np.int32)
+    part = torch.from_numpy(allidx[rank::world].copy())
+    cnt = zk.p3.lu_counts_sharded(_TorchHist(), [part], 64, 5, dist)
+    wantc = np.bincount(allidx, minlength=64)
+    wantc[0] += 5
+    roots_ok = (cnt.numpy() == wantc).all()
+    ok = roots_ok and roots == want and [x[0] for x in sizes] == list(range(7)) and all(x[1] == x[0] % world for x in sizes)
     q.put((rank, bool(ok)))
     dist.barrier()
     dist.destroy_process_group()

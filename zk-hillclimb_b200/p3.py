@@ -700,6 +700,25 @@ def commit_columns_sharded(engine, cols, R, dist=None, group=None, device=None):
     return [bytes(allr[j % G, j // G].numpy().tobytes()) for j in range(K)]
 
 
+def lu_counts_sharded(engine, idx_local, M, pad_rows, dist=None, group=None):
+    """Multiplicity column of a lookup whose index arrays are split over the GPUs of one node: every rank histograms the
+    index arrays it holds (p3lu_cnts/cntg_kernel, zkllm-src/p3_logup.cuh:149-172) and the 64-bit partial counts are summed
+    with one all-reduce (plain integer sum: counts stay far below 2^63), so every rank ends with the full column; the
+    padding rows (table row 0) are added once.  idx_local: this rank's index arrays (possibly empty)."""
+    import torch
+    cnt = None
+    for idx in idx_local:
+        h = engine.histogram(idx, M)
+        cnt = h if cnt is None else cnt + h
+    G = dist.get_world_size(group) if (dist is not None and dist.is_initialized()) else 1
+    if cnt is None:
+        raise ValueError("lu_counts_sharded: every rank needs at least one (possibly empty) index array")
+    if G > 1:
+        dist.all_reduce(cnt, group=group)
+    cnt[0] += pad_rows
+    return cnt
+
+
 def run_independent(items, fn, dist=None, group=None):
     """Independent proofs (e.g. one layer proof per transcript) placed on separate GPUs: rank g runs
     fn(item) for items g, g+G, g+2G, ... and every rank receives all results in item order."""
