@@ -36,7 +36,7 @@ def _large_program(nc, nterms, seed):
     terms = []
     for _ in range(nterms):
         deg = int(rng.integers(1, 4))
-        terms.append((int(rng.integers(1, GL_P)), tuple(int(x) for x in rng.integers(0, nc, size=deg))))
+        terms.append((int(rng.integers(1, GL_P, dtype=np.uint64)), tuple(int(x) for x in rng.integers(0, nc, size=deg))))
     return terms
 
 
