@@ -300,7 +300,8 @@ ZKH_API int zkh_gl_inv_all_add(zkh_ctx* ctx, const uint64_t* A_dev, uint64_t n, 
 ZKH_API int zkh_gl_combine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
                            uint64_t* out_dev);
 /* out[i] = addend + sum_k g^k * cols[k][i]: the gamma-combination with the logUp shift folded in
- * (leaf denominators A_i + beta of zkllm-src/p3_logup.cuh:1645-1647, :1788-1789).  Stream-ordered. */
+ * (leaf denominators A_i + beta of zkllm-src/p3_logup.cuh:1645-1647, :1788-1789).  ncols = 0 fills out with the
+ * constant addend (padding members of a merged lookup, all-ones numerators).  Stream-ordered. */
 ZKH_API int zkh_gl_affine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
                           uint64_t addend, uint64_t* out_dev);
 /* Dense field helpers for binding one index group of a committed matrix M (rows x cols, row-major):

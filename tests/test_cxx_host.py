@@ -21,7 +21,7 @@ def test_cxx_header_compiles_and_program_fails_loudly_without_a_gpu(zk, tmp_path
     subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(tu), "-o", str(out),
                            "-L", PKG, "-lzkh", "-Wl,-rpath," + PKG])
     assert subprocess.run([str(out)]).returncode == 0
-    assert os.path.exists(EXE), "build() makes the selftest program"
+    assert os.path.exists(EXE) and os.path.exists(os.path.join(PKG, "zkh_p3_gadgets_selftest")), "build() makes the selftest programs"
     import torch
     if not torch.cuda.is_available():
         r = subprocess.run([EXE], capture_output=True, text=True)
@@ -73,3 +73,51 @@ def test_cxx_flow_matches_checker(orc, ref_or_none, v, R, Q):
         ok, st2 = ref_or_none.bo_verify_class(st0, pts, [ra, rb, ra], [0, 1, 1], y, R, Q, "cxx-bo",
                                               bytes.fromhex(got["batch_proof"]))
         assert ok and st2 == st
+
+
+GEXE = os.path.join(PKG, "zkh_p3_gadgets_selftest")
+
+
+def _i8_stream(n, s):
+    out = np.empty(n, dtype=np.int64)
+    for i in range(n):
+        s = (s * 6364136223846793005 + 1442695040888963407) % (1 << 64)
+        out[i] = ((s >> 33) % 255) - 127
+    return out, s
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("li,lj,lk,sf", [(4, 6, 5, 16), (3, 5, 7, 14), (5, 7, 6, 20)])
+def test_cxx_gadgets_match_python_host_logic(zk, prover, li, lj, lk, sf):
+    """Quantised matmul proof + rescale with range lookups, standalone and composed, driven from C++: the same bytes as the
+    Python host logic (which is pinned to the reference's provers and verifiers in the imm / irs tests)."""
+    from irs_helpers import irs_tables, lift
+    R, Q = 1, 24
+    r = subprocess.run([GEXE] + [str(v) for v in (li, lj, lk, sf, R, Q)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    got = dict(line.split(" ", 1) for line in r.stdout.splitlines())
+    I, J, K = 1 << li, 1 << lj, 1 << lk
+    x, s = _i8_stream(I * J, 0x5EED)
+    w, s = _i8_stream(J * K, s)
+    y = (x.reshape(I, J) @ w.reshape(J, K)).reshape(-1)
+    p3 = zk.p3
+    com = lambda a: (lambda d: (d, prover.commit_gpu_rootonly(d, R)))(p3.to_device(lift(a)))
+    X, W, Y = com(x), com(w), com(y)
+    assert got["root_Y"] == Y[1].hex()
+    tr = zk.Transcript("cxx-imm")
+    assert got["imm_proof"] == p3.imm_prove(prover, tr, X, W, Y, lj, lk, li, R, Q).hex() and got["imm_state"] == tr.state.hex()
+    T = irs_tables(zk, sf)
+    yo, L, iL, iY = prover.irs_witness(Y[0], sf, 1)
+    Yo = (yo, prover.commit_gpu_rootonly(yo, R))
+    tr = zk.Transcript("cxx-irs")
+    assert got["irs_proof"] == p3.irs_prove(prover, tr, T, Y, Yo, (L, iL, iY), li + lk, sf, 1, R, Q).hex()
+    assert got["irs_state"] == tr.state.hex() and got["irs_rootY"] == Yo[1].hex()
+    tr = zk.Transcript("cxx-c0")
+    ledger, luq = p3.Ledger(), []
+    p1 = p3.imm_prove(prover, tr, X, W, Y, lj, lk, li, R, Q, ledger)
+    p2 = p3.irs_prove(prover, tr, T, Y, Yo, (L, iL, iY), li + lk, sf, 1, R, Q, ledger, luq)
+    lug = p3.lu_flush(prover, tr, luq, ledger, R)
+    bo = p3.tail_prove(prover, tr, ledger, R, Q, "c0-bo")
+    blob = lambda bs: b"".join(len(b).to_bytes(4, "little") + b for b in bs)
+    assert got["c0_imm"] == p1.hex() and got["c0_irs"] == p2.hex() and got["c0_lug"] == blob(lug).hex()
+    assert got["c0_batches"] == blob(bo).hex() and got["c0_state"] == tr.state.hex()

@@ -178,8 +178,8 @@ extern "C" int zkh_gl_combine(zkh_ctx* c, const uint64_t* const* cols_dev, int n
 }
 extern "C" int zkh_gl_affine(zkh_ctx* c, const uint64_t* const* cols_dev, int ncols, uint64_t n, uint64_t g,
                              uint64_t addend, uint64_t* out_dev) {
-    if (!c || !cols_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "combine: null pointer");
-    if (ncols < 1 || ncols > 8) return zkh_fail(c, ZKH_ERR_LIMIT, "combine: 1..8 columns");
+    if (!c || (ncols > 0 && !cols_dev) || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "combine: null pointer");
+    if (ncols < 0 || ncols > 8) return zkh_fail(c, ZKH_ERR_LIMIT, "combine: 0..8 columns");
     if (g >= GL_P || addend >= GL_P) return zkh_fail(c, ZKH_ERR_ARG, "combine: gamma / addend not canonical");
     if (!n) return ZKH_OK;
     ZKH_CUDA(c, cudaSetDevice(c->device));
