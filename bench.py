@@ -808,7 +808,7 @@ def run_suite_tf(args):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from oracle import Reference
-    from test_tf_layer_host_logic import ref_tf_verify, small_layer
+    from test_tf_layer_host_logic import ref_tf_prove, ref_tf_verify, small_layer
     from tfg_helpers import load_art
     torch.cuda.set_device(0)
     prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
@@ -853,6 +853,10 @@ def run_suite_tf(args):
             t0 = time.perf_counter()
             ok, st = ref_tf_verify(ref, zk.Transcript("tf-layer").state, c, x0, o["rms"][0]["X"][1], wroots, W, w["out"], R, Q, pf, wmax)
             line.update({"accepted_by_reference_verifier": bool(ok and st == tr.state), "reference_verify_host_s": time.perf_counter() - t0})
+            if ref.gpu_available() and not args.no_ref_cuda and key in ("tiny", "d256s64"):
+                rpf, rst, _act, ms = ref_tf_prove(ref, zk.Transcript("tf-layer").state, c, x0, W, R, Q, wmax)
+                line.update({"reference_witness_host_s": ms[0] / 1e3, "reference_commit_s": ms[1] / 1e3, "reference_prove_s": ms[2] / 1e3,
+                             "speedup_prove_vs_reference": ms[2] / 1e3 / best[1], "same_proof_bytes": bool(rpf == pf and rst == tr.state)})
         print(json.dumps(line), flush=True)
         del w, o
         torch.cuda.empty_cache()

@@ -2257,4 +2257,49 @@ int ref_salted_commit_root(const uint64_t* c, uint32_t v, uint32_t R, uint64_t s
 void ref_zprng_fill(uint64_t s, uint64_t* out, size_t n) { p3zkc::zprng_fill(s, out, n); }
 uint64_t ref_zprng_at(uint64_t seed, uint64_t i) { return p3zkc::zprng_at(seed, i); }
 
+// p3tf: build_witness (host) + commit_all + prove (GPU) of one fp8 transformer layer.  wcodes[i] / wscales[i]: the 7 weight
+// matrices (N*K codes, N fp32 bit patterns) in the order q k v o g u d; ms_out[0] witness, [1] commit, [2] prove
+size_t ref_tf_prove(uint8_t st[32], const uint32_t dims[6], const uint16_t* x0, const uint8_t* const* wcodes, const uint32_t* const* wscales,
+                    const uint16_t* g1, const uint16_t* g2, const uint16_t* cosp, const uint16_t* sinp, uint32_t smx_wmax, uint32_t R,
+                    uint32_t Q, uint8_t* out, size_t cap, uint16_t* out_act, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    p3bf::p3_enable_mempool();
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        p3tf::Config c; c.seq = dims[0]; c.d = dims[1]; c.nh = dims[2]; c.dh = dims[3]; c.dff = dims[4]; c.batch = dims[5];
+        p3tf::Weights W; W.cfg = c;
+        const uint32_t NK[7][2] = {{c.d, c.d}, {c.d, c.d}, {c.d, c.d}, {c.d, c.d}, {c.dff, c.d}, {c.dff, c.d}, {c.d, c.dff}};
+        for (int i = 0; i < p3tf::NW; i++) {
+            W.w[i].N = NK[i][0]; W.w[i].K = NK[i][1];
+            W.w[i].codes.assign(wcodes[i], wcodes[i] + (size_t)NK[i][0] * NK[i][1]);
+            W.w[i].scales.assign(wscales[i], wscales[i] + NK[i][0]);
+        }
+        const size_t nh2 = (size_t)c.seq * (c.dh / 2), ne = (size_t)c.T() * c.d;
+        W.g1.assign(g1, g1 + c.d); W.g2.assign(g2, g2 + c.d);
+        W.cos.assign(cosp, cosp + nh2); W.sin.assign(sinp, sinp + nh2);
+        static p3tf::TfTables T; static int64_t t_ld = -1; static uint32_t t_w = 0;
+        if (t_ld != tf_art().ld || t_w != smx_wmax) { T = p3tf::build_tables(tf_art(), smx_wmax); t_ld = tf_art().ld; t_w = smx_wmax; }
+        std::vector<uint16_t> xv(x0, x0 + ne);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3tf::TfWit w = p3tf::build_witness(c, xv, W, tf_art());
+        double t1 = p3bf::bf_now_ms();
+        p3tf::TfOps o = p3tf::commit_all(w, R);
+        cudaDeviceSynchronize();
+        double t2 = p3bf::bf_now_ms();
+        auto pf = p3tf::prove(tr, w, o, T, tf_art(), R, Q);
+        cudaDeviceSynchronize();
+        double t3 = p3bf::bf_now_ms();
+        if (ms_out) { ms_out[0] = t1 - t0; ms_out[1] = t2 - t1; ms_out[2] = t3 - t2; }
+        if (out_act) memcpy(out_act, w.outp.data(), ne * 2);
+        HwlWriter wr;
+        tf_walk(wr, pf, false);
+        n = emit(wr.b, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
 }  // extern "C"

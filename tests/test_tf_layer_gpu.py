@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from hwl_helpers import OracleHwlEngine, host_col
-from test_tf_layer_host_logic import golden_layer, ref_tf_verify, small_layer
+from test_tf_layer_host_logic import golden_layer, ref_tf_prove, ref_tf_verify, small_layer
 from tfg_helpers import bf16_add_cases, bf16_patterns, load_art, ref_verify3, ref_verify_roots
 
 pytestmark = pytest.mark.gpu
@@ -110,6 +110,9 @@ def test_layer_proof_same_bytes_as_cpu_engine_and_verifies(orc, ref, zk, prover,
     st0 = zk.Transcript("tf-layer").state
     ok, st = ref_tf_verify(ref, st0, c, x0, o["rms"][0]["X"][1], wroots, W, w["out"], R, Q, pf)
     assert ok and st == tr.state
+    if ref.gpu_available():                           # the reference's own CUDA layer prover: identical bytes
+        rpf, rst, ract, _ms = ref_tf_prove(ref, st0, c, x0, W, R, Q)
+        assert (ract == w["out"]).all() and rpf == pf and rst == tr.state
     if dims[0] == 2:                                  # the CPU stand-in engine on the CPU witness: identical bytes
         wh = tfg.tf_build_witness(c, x0, W, art)
         eng = OracleHwlEngine(orc, ref)

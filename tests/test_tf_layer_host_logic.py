@@ -50,6 +50,26 @@ def ref_tf_verify(ref, st, c, x0, rX0, wroots, W, out, R, Q, proof, wmax=23):
     return bool(ok), bytes(s)
 
 
+def ref_tf_prove(ref, st, c, x0, W, R, Q, wmax=23):
+    """The reference's own build_witness (host) + commit_all + prove (CUDA): (proof bytes, state, output patterns, [ms])."""
+    s = (C.c_uint8 * 32)(*st)
+    dims = (C.c_uint32 * 6)(*c.dims())
+    codes = [np.ascontiguousarray(w[0], dtype=np.uint8) for w in W["w"]]
+    scales = [np.ascontiguousarray(w[1], dtype=np.uint32) for w in W["w"]]
+    pc = (C.c_void_p * 7)(*[a.ctypes.data for a in codes])
+    ps = (C.c_void_p * 7)(*[a.ctypes.data for a in scales])
+    keep = [np.ascontiguousarray(a, dtype=np.uint16) for a in (x0, W["g1"], W["g2"], W["cos"], W["sin"])]
+    cap = 1 << 30
+    out = (C.c_uint8 * cap)()
+    act = np.zeros(c.T * c.d, dtype=np.uint16)
+    ms = (C.c_double * 3)()
+    f = ref.lib.ref_tf_prove
+    f.restype = C.c_size_t
+    n = f(s, dims, *[a.ctypes.data_as(C.c_void_p) for a in keep[:1]], pc, ps, *[a.ctypes.data_as(C.c_void_p) for a in keep[1:]],
+          C.c_uint32(wmax), C.c_uint32(R), C.c_uint32(Q), out, C.c_size_t(cap), act.ctypes.data_as(C.c_void_p), ms)
+    return bytes(out[:n]), bytes(s), act, list(ms)
+
+
 def small_layer(zk, c, seed):
     """Seeded weights as the reference's tiny layer draws them: random e4m3 codes, log-normal fp32 row scales around 0.02."""
     rng = np.random.default_rng(seed)

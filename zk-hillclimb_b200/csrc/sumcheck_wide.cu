@@ -431,8 +431,8 @@ extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_
     const uint32_t nterms = (uint32_t)prog[0];
     const bool large = nc > 32 || nterms > ZC_MAXTERMS;
     if (prog[1] >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: constant not canonical");
-    static ZkhZcProg hp;   // staging copies; calls on one context are serial
-    static std::vector<uint8_t> hx;
+    ZkhZcProg hp;          // staging copies (pageable memory: the asynchronous copies below return after staging them)
+    std::vector<uint8_t> hx;
     if (!large) {
         memset(&hp, 0, sizeof hp);
         hp.nterms = nterms;
