@@ -272,6 +272,10 @@ ZKH_API int zkh_batchopen_prove_class_kept(zkh_ctx* ctx, uint32_t v, const uint6
                                    uint8_t* out, size_t cap, size_t* written, const uint64_t* const* kept_cw,
                                    const uint8_t* const* kept_tree);
 
+/* Roots of k independent columns (2^vs[j] elements each) with one host synchronisation; roots: k*32 bytes (host).  The bytes
+ * equal k calls of zkh_basefold_commit (zkllm-src/p3_basefold.cuh:210-227 commit_gpu_rootonly). */
+ZKH_API int zkh_basefold_commit_many(zkh_ctx* ctx, const uint64_t* const* cols_dev, const uint32_t* vs, uint32_t k, uint32_t R,
+                             uint8_t* roots);
 /* Hiding commitment: salted Merkle leaves (zkllm-src/p3_zkc.cuh:230-292 salt_of / salted_leaf / p3zkc_salted_leaf_kernel,
  * :320-397 salted_commit_root, salted_commit_root_dev).  Leaf i = SHA-256(value_le8 | SHA-256(sseed_le8 | i_le8)); internal
  * nodes as in the plain tree, so authentication paths verify unchanged.  cw_dev (2^(v+R) elements) and tree_dev

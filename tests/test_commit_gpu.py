@@ -166,3 +166,13 @@ def test_commit_argument_errors(zk, prover):
         prover.prove_eval_dev(x, np.zeros(3, np.uint64), 0, 9, 24)
     with pytest.raises(zk.ZkhError):
         prover.fold_gpu(x, GL_P)
+
+
+@pytest.mark.gpu
+def test_commit_many_equals_single_commits(orc, zk, prover):
+    """Roots of many columns of mixed sizes queued with one synchronisation equal the one-by-one commitments."""
+    from conftest import lcg_cols
+    cols = [zk.p3.to_device(lcg_cols(orc, 1 << v, 1, 100 + v)[0]) for v in (1, 3, 10, 2, 16, 7, 12, 1)]
+    for R in (1, 2):
+        assert prover.commit_many(cols, R) == [prover.commit_gpu_rootonly(c, R) for c in cols]
+    assert prover.commit_many([], 1) == []

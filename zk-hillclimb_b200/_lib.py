@@ -97,6 +97,7 @@ def load_library():
         "zkh_gl_scale": (i, [vp, vp, u64, u64, vp]),
         "zkh_gl_mul": (i, [vp, vp, vp, u64, vp]),
         "zkh_irs_witness": (i, [vp, vp, u64, u32, i, vp, vp, vp, vp, vp, vp]),
+        "zkh_basefold_commit_many": (i, [vp, vp, vp, u32, u32, vp]),
         "zkh_basefold_commit_salted": (i, [vp, vp, u32, u32, u64, vp, vp, vp]),
         "zkh_zk_fill_at": (i, [vp, u64, u64, u64, vp]),
         "zkh_zk_fill_chain": (i, [vp, u64, u64, u64, vp]),

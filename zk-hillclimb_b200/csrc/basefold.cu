@@ -151,6 +151,38 @@ extern "C" int zkh_basefold_commit_keep(zkh_ctx* c, const uint64_t* c_dev, uint3
     return ZKH_OK;
 }
 
+// Commitment roots of k independent columns with ONE host synchronisation: a layer proof commits hundreds of small witness
+// columns (the reference commits them one after another, each with its own device round trip, zkllm-src/p3_logup.cuh
+// commit_col_nc -> p3_basefold.cuh:210-227); here every encode + tree build is queued on the stream and the k roots come
+// back in one copy.
+extern "C" int zkh_basefold_commit_many(zkh_ctx* c, const uint64_t* const* cols_dev, const uint32_t* vs, uint32_t k, uint32_t R,
+                                        uint8_t* roots) {
+    if (!c || !cols_dev || !vs || !roots) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_many: null pointer");
+    if (R < 1 || R > 8) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_many: need R in 1..8");
+    if (!k) return ZKH_OK;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    size_t need = 0;
+    for (uint32_t j = 0; j < k; j++) {
+        if (!cols_dev[j] || vs[j] + R < 1 || vs[j] + R > 32) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_many: bad column");
+        const uint32_t logM = vs[j] + R;
+        const size_t M = (size_t)1 << logM, b = zkh_align(M * 8) + ntt_scratch_bytes(logM) + merkle_scratch_bytes(M);
+        if (b > need) need = b;
+    }
+    const size_t rootb = zkh_align((size_t)k * 32);
+    ZKH_TRY(zkh_ws_reserve(c, need + rootb));            // one reservation: the workspace must not move while work is queued
+    uint8_t* roots_dev = (uint8_t*)c->ws + need;
+    for (uint32_t j = 0; j < k; j++) {
+        const uint32_t logM = vs[j] + R;
+        const size_t M = (size_t)1 << logM, cwb = zkh_align(M * 8), nttb = ntt_scratch_bytes(logM);
+        gl_t* cw = (gl_t*)c->ws;
+        ZKH_TRY(ntt_enqueue(c, cols_dev[j], (uint64_t)1 << vs[j], cw, logM, false, (char*)c->ws + cwb));
+        ZKH_TRY(merkle_enqueue(c, cw, M, nullptr, (char*)c->ws + cwb + nttb, roots_dev + (size_t)j * 32));
+    }
+    ZKH_CUDA(c, cudaMemcpyAsync(roots, roots_dev, (size_t)k * 32, cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    return ZKH_OK;
+}
+
 // Hiding commitment (zkllm-src/p3_zkc.cuh:320-397 salted_commit_root / salted_commit_root_dev): the same codeword, leaves
 // salted with SHA-256(seed | leaf index).  cw_dev / tree_dev optional (both or none keep codeword and tree resident).
 extern "C" int zkh_basefold_commit_salted(zkh_ctx* c, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t sseed,

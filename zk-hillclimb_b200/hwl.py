@@ -16,7 +16,7 @@ import struct
 import numpy as np
 import torch
 
-from .p3 import (F_HW_CH, F_HW_DG, F_HW_DO, F_HW_DP, F_HW_DS, F_HW_GS, F_PROD3, GL_P, Ledger, claimc, lu_flush,
+from .p3 import (F_HW_CH, F_HW_DG, F_HW_DO, F_HW_DP, F_HW_DS, F_HW_GS, F_PROD3, GL_P, Ledger, claimc, commit_cols, lu_flush,
                  make_table)
 
 # ---- column ids (p3_hawkeye.cuh:86-112) ----
@@ -430,8 +430,7 @@ def prove(engine, tr, wt, T, ops, R, Q, col, Ypub=None, ctx=None, strict=True):
 
     # -- witness commitments --
     def commit_all(cols):
-        cs = [col(t) for t in cols]
-        return [(c, engine.commit_gpu_rootonly(c, R)) for c in cs]
+        return commit_cols(engine, [col(t) for t in cols], R)
     CDp, CDg, CDo, CDb, CDn = (commit_all(wt[k]) for k in ("dp", "dg", "dob", "db", "dn"))
     for label, cd in (("hwl-cp", CDp), ("hwl-cg", CDg), ("hwl-co", CDo), ("hwl-cb", CDb), ("hwl-cn", CDn)):
         for _, root in cd:

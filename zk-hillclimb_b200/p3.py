@@ -255,6 +255,19 @@ class Prover:
             self._ck(self._L.zkh_basefold_commit(self._h, _ptr(c), c.numel().bit_length() - 1, R, 0, root))
         return bytes(root)
 
+    def commit_many(self, cols, R):
+        """Commitment roots of several device columns with one host synchronisation (same roots as commit_gpu_rootonly on
+        each).  With kept trees enabled the columns are committed one by one so that their codewords and trees stay."""
+        if getattr(self, "keep_trees", False) or not cols:
+            return [self.commit_gpu_rootonly(c, R) for c in cols]
+        k = len(cols)
+        ptrs = (C.c_uint64 * k)(*[_ptr(c) for c in cols])
+        vs = (C.c_uint32 * k)(*[int(c.numel()).bit_length() - 1 for c in cols])
+        roots = (C.c_uint8 * (32 * k))()
+        self._ck(self._L.zkh_basefold_commit_many(self._h, ptrs, vs, k, R, roots))
+        rb = bytes(roots)
+        return [rb[32 * j:32 * j + 32] for j in range(k)]
+
     def commit_salted(self, c, R, sseed, keep=False):
         """p3zkc::salted_commit_root_dev (zkllm-src/p3_zkc.cuh:362-397): hiding commitment root of a device column, leaves
         salted with SHA-256(seed | index).  keep: also return the codeword and the tree (device tensors)."""
@@ -850,6 +863,13 @@ class Ledger:
                 c[3].append(y)
                 return
         self.cls.append([len(z), [z], [(col, root, 0)], [y]])
+
+
+def commit_cols(engine, cols, R):
+    """(column, root) pairs of several columns; engines that can queue many commitments before synchronising do so."""
+    if hasattr(engine, "commit_many"):
+        return list(zip(cols, engine.commit_many(cols, R)))
+    return [(c, engine.commit_gpu_rootonly(c, R)) for c in cols]
 
 
 def claimc(engine, tr, ledger, col, root, z):

@@ -10,7 +10,7 @@ import struct
 import numpy as np
 import torch
 
-from .p3 import GL_P, claimc, lu_flush, make_table
+from .p3 import GL_P, claimc, commit_cols, lu_flush, make_table
 
 
 # ---------------------------------------------------------------------------------- constraint polynomials
@@ -222,7 +222,7 @@ def swg_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
     tr.absorb("swg-G", ops["GATE"][1])
     tr.absorb("swg-U", ops["UP"][1])
     tr.absorb("swg-M", ops["M"][1])
-    C = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["ws"])]
+    C = commit_cols(engine, [col(t) for t in wt["ws"]], R)
     for _, root in C:
         tr.absorb("swg-cw", root)
     sgmf, umf = col(wt["sgmf"]), col(wt["umf"])
@@ -432,7 +432,7 @@ def bfa_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
     tr.absorb("bfa-X1", ops["X1"][1])
     tr.absorb("bfa-X2", ops["X2"][1])
     tr.absorb("bfa-O", ops["OUT"][1])
-    C = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["ws"])]
+    C = commit_cols(engine, [col(t) for t in wt["ws"]], R)
     for _, root in C:
         tr.absorb("bfa-cw", root)
     for i, (tab, names) in enumerate(BA_LU):
@@ -521,8 +521,8 @@ def qnt_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
     tr.absorb("qnt-X", ops["X"][1])
     tr.absorb("qnt-C", ops["CODES"][1])
     tr.absorb("qnt-S", ops["SCALES"][1])
-    CDe = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["de"])]
-    CDb = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["db"])]
+    CDe = commit_cols(engine, [col(t) for t in wt["de"]], R)
+    CDb = commit_cols(engine, [col(t) for t in wt["db"]], R)
     for _, root in CDe:
         tr.absorb("qnt-ce", root)
     for _, root in CDb:
@@ -685,7 +685,7 @@ def rope_prove(engine, tr, wt, T, ops, R, Q, col, ctx=None, strict=True):
         tr.absorb("rop-sin", field_bytes(wt["sf"][k]))
     tr.absorb("rop-Q", ops["Q"][1])
     tr.absorb("rop-O", ops["OUT"][1])
-    C = [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in wt["ws"])]
+    C = commit_cols(engine, [col(t) for t in wt["ws"]], R)
     for _, root in C:
         tr.absorb("rop-cw", root)
     virt = {k: (col(wt[k]), None) for k in ("amf", "bmf", "cmf", "smf")}
@@ -851,7 +851,7 @@ def rms_prove(engine, tr, wt, T, art, ops, R, Q, col, ctx=None, strict=True):
     tr.absorb("rms-X", ops["X"][1])
     tr.absorb("rms-G", ops["G"][1])
     tr.absorb("rms-Y", ops["Y"][1])
-    commit = lambda cols: [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in cols)]
+    commit = lambda cols: commit_cols(engine, [col(t) for t in cols], R)
     CDe, CDb, CDw = commit(wt["de"]), commit(wt["db"]), commit(wt["dw"])
     for label, cd in (("rms-ce", CDe), ("rms-cb", CDb), ("rms-cw", CDw)):
         for _, root in cd:
@@ -1079,7 +1079,7 @@ def smx_prove(engine, tr, wt, T, art, ops, R, Q, col, ctx=None, strict=True):
     tr.absorb("smx-msk", wt["mskc"].cpu().numpy().astype(np.uint64).tobytes())
     tr.absorb("smx-S", ops["S"][1])
     tr.absorb("smx-P", ops["P"][1])
-    commit = lambda cols: [(c, engine.commit_gpu_rootonly(c, R)) for c in (col(t) for t in cols)]
+    commit = lambda cols: commit_cols(engine, [col(t) for t in cols], R)
     CDe, CDb = commit(wt["de"]), commit(wt["db"])
     for _, root in CDe:
         tr.absorb("smx-ce", root)
