@@ -154,6 +154,9 @@ ZKH_API int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* const* 
  * (non-zk path of sc5z).  Five evaluations per round (Msg5), absorbed under `tag`.
  * prog: word 0 = number of terms (<= 2048), word 1 = konst, then per term two words: coefficient,
  * degree | idx0 << 8 | idx1 << 16 | idx2 << 24.  nwords = 2 + 2*terms.  1 <= nc <= 224.
+ * A term whose degree byte has bit 7 set (degree | 0x80) is added OUTSIDE the col0 factor: with it the summand of a
+ * blinded chain, F + rho*(B1 + E*B2 + E^2*B3 + E^3*B4) with E = col0 (zkllm-src/p3_hawkeye.cuh:1035-1053, :1333-1341),
+ * is one program.
  * Programs of more than 32 columns or 120 terms (the bf16 gadgets of the fp8 transformer layer, zkllm-src/p3_bfadd.cuh:
  * 214-330, p3_swiglu.cuh:172-207 and siblings) run on a variant that keeps the column values in shared memory. */
 ZKH_API int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
@@ -271,6 +274,19 @@ ZKH_API int zkh_batchopen_prove_class_kept(zkh_ctx* ctx, uint32_t v, const uint6
                                    uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
                                    uint8_t* out, size_t cap, size_t* written, const uint64_t* const* kept_cw,
                                    const uint8_t* const* kept_tree);
+
+/* Batched opening of the hiding mode (zkllm-src/p3_batchopen.cuh:969-1131, the zk_salted branches of p3bo::prove_class):
+ * every column of the class was committed with zkh_basefold_commit_salted under sseeds[j] (equal roots carry equal seeds).
+ * The protocol is the one above; each distinct column's round-0 section becomes
+ *   u32 nvals, vals nvals*8, salts nvals*32, u32 nnodes, nodes nnodes*32
+ * (BQ0C vals / salts / nodes).  The class blinder (one fresh uniform salted column claimed at a fresh point, its root and
+ * claim absorbed under "bo-blr" / "bo-bly", :315-384) is an ordinary ledger entry the caller appends before the call.
+ * cap: zkh_batchopen_proof_bound(...) + distinct columns * 2*Q*32.  kept_cw / kept_tree as above (arrays or NULL). */
+ZKH_API int zkh_batchopen_prove_class_salted(zkh_ctx* ctx, uint32_t v, const uint64_t* pts, uint32_t T,
+                                     const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
+                                     const uint64_t* sseeds, uint32_t k, uint32_t R, uint32_t Q, const char* label,
+                                     uint8_t state[32], uint8_t* out, size_t cap, size_t* written,
+                                     const uint64_t* const* kept_cw, const uint8_t* const* kept_tree);
 
 /* Roots of k independent columns (2^vs[j] elements each) with one host synchronisation; roots: k*32 bytes (host).  The bytes
  * equal k calls of zkh_basefold_commit (zkllm-src/p3_basefold.cuh:210-227 commit_gpu_rootonly). */

@@ -266,6 +266,25 @@ class _Lib:
             raise RuntimeError("bo_prove_class failed")
         return (bytes(out)[:n], bytes(s)) + ((ms.value,) if self.prefix == "ref_" else ())
 
+    def bo_prove_class_salted(self, st, pts, cols, roots, zid, sseeds, R, Q, label):
+        """The hiding mode's prove_class after the blinder was appended (oracle restatement only): salted round-0 openings."""
+        pts, T, v, rb, zid = self._bo_args(pts, roots, zid)
+        arrs = [np.ascontiguousarray(c, dtype=np.uint64) for c in cols]
+        ptrs = (u64p * len(arrs))(*[a.ctypes.data_as(u64p) for a in arrs])
+        ss = np.ascontiguousarray(sseeds, dtype=np.uint64)
+        nc = len(set(bytes(r) for r in roots))
+        cap = 16 + nc * 8 + v * 48 + max(v - 1, 0) * 32 + (8 << R) + \
+            sum(Q * (16 + 2 * (v + R - r) * 32) for r in range(1, v)) + nc * (8 + 2 * Q * 40 + 2 * Q * (v + R) * 32)
+        out = (C.c_uint8 * cap)()
+        s = _bytes32(st)
+        f = self.lib.orc_bo_prove_class_salted
+        f.restype = C.c_size_t
+        n = f(s, C.c_uint32(v), pts.ctypes.data_as(u64p), C.c_uint32(T), ptrs, rb, zid.ctypes.data_as(C.c_void_p),
+              ss.ctypes.data_as(u64p), C.c_uint32(len(zid)), C.c_uint32(R), C.c_uint32(Q), label.encode(), out, C.c_size_t(cap))
+        if n == 0:
+            raise RuntimeError("bo_prove_class_salted failed")
+        return bytes(out)[:n], bytes(s)
+
     # ---- logUp primitives ----
     def inv_all_add(self, A, beta):
         A, ap = _u64(A); out = np.empty(len(A), dtype=np.uint64)

@@ -425,10 +425,14 @@ void orc_leaf_hash(uint64_t v, uint8_t out[32]) {
 /* zkllm-src/p3_fri.cuh:36-39 -- single compression of l|r from the IV */
 /* salted leaf of the hiding commitment (zkllm-src/p3_zkc.cuh:235-249 salt_of, salted_leaf):
  * salt = SHA-256(seed_le8 | index_le8), leaf = SHA-256(value_le8 | salt) */
-void orc_salted_leaf_hash(uint64_t v, uint64_t sseed, uint64_t idx, uint8_t out[32]) {
-    uint8_t b[40], sb[16];
+void orc_salt_of(uint64_t sseed, uint64_t idx, uint8_t out[32]) {
+    uint8_t sb[16];
     for (int k = 0; k < 8; k++) { sb[k] = (uint8_t)(sseed >> (8 * k)); sb[8 + k] = (uint8_t)(idx >> (8 * k)); }
-    orc_sha256(sb, 16, b + 8);
+    orc_sha256(sb, 16, out);
+}
+void orc_salted_leaf_hash(uint64_t v, uint64_t sseed, uint64_t idx, uint8_t out[32]) {
+    uint8_t b[40];
+    orc_salt_of(sseed, idx, b + 8);
     for (int k = 0; k < 8; k++) b[k] = (uint8_t)(v >> (8 * k));
     orc_sha256(b, 40, out);
 }
@@ -942,17 +946,18 @@ static size_t subset_nodes(uint32_t logM, const uint32_t* upos, uint32_t nu, con
     free(fr);
     return nn;
 }
-/* zkllm-src/p3_batchopen.cuh:307-1147 (prove_class), non-zk, A.8 schedule */
-size_t orc_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
+/* zkllm-src/p3_batchopen.cuh:307-1147 (prove_class), A.8 schedule; sseeds != NULL: the hiding mode's salted
+ * round-0 openings (:1028-1131), the class blinder having been appended to the ledger by the caller */
+static size_t bo_prove_class_impl(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
                           const uint64_t* const* cols, const uint8_t* roots, const uint32_t* zid, uint32_t k,
-                          uint32_t R, uint32_t Q, const char* label, uint8_t* out, size_t cap) {
+                          uint32_t R, uint32_t Q, const char* label, uint8_t* out, size_t cap, const uint64_t* sseeds) {
     const size_t N = (size_t)1 << v;
     const uint32_t logM0 = v + R;
     const size_t M0 = (size_t)1 << logM0;
     uint32_t* colidx = (uint32_t*)malloc((size_t)k * 4);
     uint32_t* first = (uint32_t*)malloc((size_t)k * 4);
     const uint32_t nc = dedupe_roots(roots, k, colidx, first);
-    if (cap < orc_bo_proof_bound(v, R, Q, nc)) { free(colidx); free(first); return 0; }
+    if (cap < orc_bo_proof_bound(v, R, Q, nc) + (sseeds ? (size_t)nc * 2 * Q * 32 : 0)) { free(colidx); free(first); return 0; }
     uint8_t* p = out;
     put32(&p, v); put32(&p, R); put32(&p, Q); put32(&p, nc);
     uint8_t* p_ystar = p;            p += (size_t)nc * 8;
@@ -1077,9 +1082,12 @@ size_t orc_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint3
     uint8_t* treec = (uint8_t*)malloc((2 * M0 - 1) * 32);
     for (uint32_t c = 0; c < nc; c++) {
         orc_rs_encode(cols[first[c]], v, R, cwc);
-        orc_merkle_build(cwc, M0, treec);
+        if (sseeds) orc_merkle_build_salted(cwc, M0, sseeds[first[c]], treec);
+        else orc_merkle_build(cwc, M0, treec);
         put32(&p, nu);
         for (uint32_t i = 0; i < nu; i++) put64(&p, cwc[upos[i]]);
+        if (sseeds)
+            for (uint32_t i = 0; i < nu; i++) { orc_salt_of(sseeds[first[c]], upos[i], p); p += 32; }
         uint8_t* p_cnt = p; p += 4;
         uint32_t nn = (uint32_t)subset_nodes(logM0, upos, nu, treec, M0, p);
         memcpy(p_cnt, &nn, 4);
@@ -1089,6 +1097,17 @@ size_t orc_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint3
     for (uint32_t r = 0; r <= v; r++) { free(words[r]); free(trees[r]); }
     free(words); free(trees); free(U); free(eqr); free(ystar); free(rstar); free(colidx); free(first);
     return (size_t)(p - out);
+}
+size_t orc_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
+                          const uint64_t* const* cols, const uint8_t* roots, const uint32_t* zid, uint32_t k,
+                          uint32_t R, uint32_t Q, const char* label, uint8_t* out, size_t cap) {
+    return bo_prove_class_impl(st, v, pts, T, cols, roots, zid, k, R, Q, label, out, cap, NULL);
+}
+size_t orc_bo_prove_class_salted(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
+                                 const uint64_t* const* cols, const uint8_t* roots, const uint32_t* zid,
+                                 const uint64_t* sseeds, uint32_t k, uint32_t R, uint32_t Q, const char* label,
+                                 uint8_t* out, size_t cap) {
+    return bo_prove_class_impl(st, v, pts, T, cols, roots, zid, k, R, Q, label, out, cap, sseeds);
 }
 
 /* subset_verify: zkllm-src/p3_batchopen.cuh:108-135 */

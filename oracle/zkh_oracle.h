@@ -131,6 +131,13 @@ size_t orc_bo_proof_bound(uint32_t v, uint32_t R, uint32_t Q, uint32_t nc);
 size_t orc_bo_prove_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
                           const uint64_t* const* cols, const uint8_t* roots, const uint32_t* zid, uint32_t k,
                           uint32_t R, uint32_t Q, const char* label, uint8_t* out, size_t cap);
+/* hiding mode: columns committed with salted leaves under sseeds[j]; round-0 sections carry the salts after the values
+ * (zkllm-src/p3_batchopen.cuh:1028-1131); cap: orc_bo_proof_bound + nc*2*Q*32 */
+size_t orc_bo_prove_class_salted(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T,
+                                 const uint64_t* const* cols, const uint8_t* roots, const uint32_t* zid,
+                                 const uint64_t* sseeds, uint32_t k, uint32_t R, uint32_t Q, const char* label,
+                                 uint8_t* out, size_t cap);
+void orc_salt_of(uint64_t sseed, uint64_t idx, uint8_t out[32]);
 int orc_bo_verify_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T, const uint8_t* roots,
                         const uint32_t* zid, const uint64_t* y, uint32_t k, uint32_t R, uint32_t Q,
                         const char* label, const uint8_t* proof, size_t len);

@@ -3,7 +3,6 @@ kernels against the oracle and, on a GPU machine, against the reference's own sa
 import hashlib
 import struct
 
-import numpy as np
 import pytest
 
 from conftest import lcg_cols

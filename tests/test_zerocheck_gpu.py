@@ -15,6 +15,9 @@ PROGRAMS = {
     "rope": (7, [(1, (1, 5)), (1, (2, 6)), (GL_P - 16384, (3,)), (GL_P - 1, (4,))], 8192),
     "cubic": (9, [(3, (1, 2, 3)), (5, (4, 4)), (7, (8,)), (11, (5, 6, 7))], 99),
     "wide": (20, [(k + 1, (k, 19 - k)) for k in range(1, 10)] + [(2, (10, 11, 12))], 1),
+    # a blinded chain: E*X*W + rho*(B1 + E*B2 + E^2*B3 + E^3*B4), the B1 term outside the E factor
+    "blinded": (7, [(1, (1, 2)), (77, (4,)), (77, (0, 5)), (77, (0, 0, 6)), (77, (3,), True)], 0),
+    "free-mix": (6, [(3, (1, 2, 3)), (5, (4, 5), True), (9, (0, 0, 0), True), (2, (1,), True)], 4),
 }
 
 
@@ -31,12 +34,13 @@ def test_matches_python_evaluation(orc, zk, prover, name, logn):
     assert st == tr.state and (m == m0).all() and (r == r0).all() and (fin == f0).all()
 
 
-def _large_program(nc, nterms, seed):
+def _large_program(nc, nterms, seed, free_every=0):
     rng = np.random.default_rng(seed)
     terms = []
-    for _ in range(nterms):
+    for j in range(nterms):
         deg = int(rng.integers(1, 4))
-        terms.append((int(rng.integers(1, GL_P, dtype=np.uint64)), tuple(int(x) for x in rng.integers(0, nc, size=deg))))
+        t = (int(rng.integers(1, GL_P, dtype=np.uint64)), tuple(int(x) for x in rng.integers(0, nc, size=deg)))
+        terms.append(t + (True,) if free_every and j % free_every == 0 else t)
     return terms
 
 
@@ -48,6 +52,15 @@ def test_large_programs_match_python_evaluation(orc, zk, prover, nc, nterms, log
     tr = zk.Transcript("zc")
     r, m, fin = prover.sc_prove_zc(tr, "bfa-scE", [zk.p3.to_device(c) for c in cols], terms, 12345)
     st, m0, r0, f0 = zc_sumcheck(orc, orc.tr_init("zc"), "bfa-scE", cols, terms, 12345)
+    assert st == tr.state and (m == m0).all() and (r == r0).all() and (fin == f0).all()
+
+
+def test_large_program_with_terms_outside_the_factor(orc, zk, prover):
+    terms = _large_program(45, 200, 3, free_every=7)
+    cols = lcg_cols(orc, 1 << 5, 45, 11)
+    tr = zk.Transcript("zc")
+    r, m, fin = prover.sc_prove_zc(tr, "z", [zk.p3.to_device(c) for c in cols], terms, 5)
+    st, m0, r0, f0 = zc_sumcheck(orc, orc.tr_init("zc"), "z", cols, terms, 5)
     assert st == tr.state and (m == m0).all() and (r == r0).all() and (fin == f0).all()
 
 

@@ -6,10 +6,10 @@ GL_P = 0xFFFFFFFF00000001
 
 
 def zc_sumcheck(orc, st, tag, cols, terms, konst):
-    """Sumcheck of cols[0] * (konst + sum coef * prod cols[idx]) with 5 evaluations per round, LSB-first binding,
+    """Sumcheck of cols[0] * (konst + sum coef * prod cols[idx]) + (terms flagged as outside the factor) with 5 evaluations per round, LSB-first binding,
     messages absorbed under `tag` (p3hwl::sc5_prove's schedule, zkllm-src/p3_hawkeye.cuh:641-700)."""
     cols = [[int(x) for x in c] for c in cols]
-    terms = [(int(c) % GL_P, tuple(i)) for c, i in terms]
+    terms = [(int(t[0]) % GL_P, tuple(t[1]), bool(len(t) > 2 and t[2])) for t in terms]
     konst = int(konst) % GL_P
     msgs, chals = [], []
     while len(cols[0]) > 1:
@@ -20,13 +20,16 @@ def zc_sumcheck(orc, st, tag, cols, terms, konst):
             df = [c[2 * i + 1] - c[2 * i] for c in cols]
             for t in range(5):
                 v = [(l + t * d) % GL_P for l, d in zip(lo, df)]
-                acc = konst
-                for coef, idx in terms:
+                acc, free = konst, 0
+                for coef, idx, outside in terms:
                     p = coef
                     for k in idx:
                         p = p * v[k] % GL_P
-                    acc += p
-                s[t] = (s[t] + v[0] * (acc % GL_P)) % GL_P
+                    if outside:
+                        free += p
+                    else:
+                        acc += p
+                s[t] = (s[t] + v[0] * (acc % GL_P) + free) % GL_P
         m = np.array(s, dtype=np.uint64)
         st = orc.tr_absorb(st, tag, m.tobytes())
         st, a = orc.tr_chal(st)

@@ -88,6 +88,8 @@ def load_library():
                                           C.POINTER(sz)]),
         "zkh_batchopen_prove_class_kept": (i, [vp, u32, vp, u32, vp, vp, vp, u32, u32, u32, C.c_char_p, vp, vp, sz,
                                                C.POINTER(sz), vp, vp]),
+        "zkh_batchopen_prove_class_salted": (i, [vp, u32, vp, u32, vp, vp, vp, vp, u32, u32, u32, C.c_char_p, vp, vp, sz,
+                                                 C.POINTER(sz), vp, vp]),
         "zkh_basefold_commit_keep": (i, [vp, vp, u32, u32, vp, vp, vp]),
         "zkh_histogram": (i, [vp, vp, u64, u32, vp]),
         "zkh_gl_inv_all_add": (i, [vp, vp, u64, u64, vp]),

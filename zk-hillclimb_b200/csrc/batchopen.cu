@@ -1,4 +1,5 @@
-// Batched Basefold openings of one size class (non-zk) for sm_100a.
+// Batched Basefold openings of one size class for sm_100a (plain and, with per-column salt seeds, the hiding mode's
+// salted round-0 openings: zkllm-src/p3_batchopen.cuh:969-1131).
 //
 // Protocol and transcript: zkllm-src/p3_batchopen.cuh:307-1147 (p3bo::prove_class).
 //   mu -> G_t = sum_{claims j at point t} mu^j col_j -> reduction sumcheck of
@@ -143,7 +144,7 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
                                  const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
                                  uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
                                  uint8_t* out, size_t cap, size_t* written, const uint64_t* const* kept_cw,
-                                 const uint8_t* const* kept_tree) {
+                                 const uint8_t* const* kept_tree, const uint64_t* sseeds = nullptr) {
     if (!c || !pts || !cols_dev || !roots || !zid || !label || !state || !out || !written)
         return zkh_fail(c, ZKH_ERR_ARG, "batchopen: null pointer");
     if (v < 1 || R < 1 || R > 3 || v + R > 30) return zkh_fail(c, ZKH_ERR_ARG, "batchopen: need v >= 1, R in 1..3, v+R <= 30");
@@ -166,7 +167,7 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
         colidx[j] = cc;
     }
     const uint32_t nc = (uint32_t)first.size();
-    if (cap < bo_bound(v, R, Q, nc)) return zkh_fail(c, ZKH_ERR_ARG, "batchopen: output buffer smaller than zkh_batchopen_proof_bound");
+    if (cap < bo_bound(v, R, Q, nc) + (sseeds ? (size_t)nc * 2 * Q * 32 : 0)) return zkh_fail(c, ZKH_ERR_ARG, "batchopen: output buffer smaller than zkh_batchopen_proof_bound");
     if ((size_t)T * N > ((size_t)1 << 33)) return zkh_fail(c, ZKH_ERR_LIMIT, "batchopen: T*2^v beyond 2^33");
 
     // ---- main transcript: mu and its powers (host; nothing on the device precedes it) ----
@@ -384,7 +385,7 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
             tree_use = kept_tree[first[cc]];
         } else {
             ZKH_TRY(ntt_enqueue(c, cols_dev[first[cc]], N, cwc, logM0, false, ws + o_misc));
-            ZKH_TRY(merkle_enqueue(c, cwc, M0, treec, nullptr, nullptr));
+            ZKH_TRY(merkle_enqueue(c, cwc, M0, treec, nullptr, nullptr, sseeds ? sseeds + first[cc] : nullptr));
         }
         const uint32_t nth = nu * (logM0 + 1);
         bo_q0_kernel<<<(nth + 127) / 128, 128, 0, s>>>(cw_use, tree_use, logM0, d_upos, nu, d_q0 + (size_t)cc * q0_per_col);
@@ -404,6 +405,13 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
         const uint8_t* paths = colq + (size_t)nu * 8;
         memcpy(p, &nu, 4); p += 4;
         memcpy(p, colq, (size_t)nu * 8); p += (size_t)nu * 8;
+        if (sseeds)   // the salts of the opened leaves (p3_batchopen.cuh:1047-1051, :1103-1104)
+            for (uint32_t i = 0; i < nu; i++) {
+                uint32_t hs[8];
+                sha256_salt(sseeds[first[cc]], upos[i], hs);
+                digest_to_bytes(hs, p);
+                p += 32;
+            }
         uint8_t* p_cnt = p; p += 4;
         uint32_t nn = 0, nf = nu;
         for (uint32_t i = 0; i < nu; i++) { fr_idx[i] = upos[i]; fr_slot[i] = i; }
@@ -432,6 +440,18 @@ extern "C" int zkh_batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t*
                                          uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
                                          uint8_t* out, size_t cap, size_t* written) {
     return batchopen_prove_class(c, v, pts, T, cols_dev, roots, zid, k, R, Q, label, state, out, cap, written, nullptr, nullptr);
+}
+// Hiding mode: every column was committed with zkh_basefold_commit_salted under sseeds[j]; the round-0 openings rebuild (or
+// reuse) the salted trees and carry the 32-byte salt of every opened leaf after the values.  The class blinder column
+// (p3_batchopen.cuh:315-384) is an ordinary entry the caller appends before the call.
+extern "C" int zkh_batchopen_prove_class_salted(zkh_ctx* c, uint32_t v, const uint64_t* pts, uint32_t T,
+                                                const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
+                                                const uint64_t* sseeds, uint32_t k, uint32_t R, uint32_t Q, const char* label,
+                                                uint8_t state[32], uint8_t* out, size_t cap, size_t* written,
+                                                const uint64_t* const* kept_cw, const uint8_t* const* kept_tree) {
+    if (!sseeds) return zkh_fail(c, ZKH_ERR_ARG, "batchopen: salted openings need the salt seeds");
+    return batchopen_prove_class(c, v, pts, T, cols_dev, roots, zid, k, R, Q, label, state, out, cap, written, kept_cw, kept_tree,
+                                 sseeds);
 }
 // Same, with kept_cw[j] / kept_tree[j] (either may be NULL per entry) the codeword and Merkle tree that
 // zkh_basefold_commit_keep left for entry j's column under the same R.

@@ -88,8 +88,8 @@ GL_HD void sha256_leaf(gl_t v, uint32_t out[8]) {
 }
 // Salted (hiding) Merkle leaf (zkllm-src/p3_zkc.cuh:230-270): salt = SHA-256(seed_le8 | index_le8), leaf =
 // SHA-256(value_le8 | salt); both are single padded blocks, the salt's digest words feed the leaf block directly.
-GL_HD void sha256_salted_leaf(gl_t v, uint64_t sseed, uint64_t idx, uint32_t out[8]) {
-    uint32_t w[16], hs[8];
+GL_HD void sha256_salt(uint64_t sseed, uint64_t idx, uint32_t hs[8]) {
+    uint32_t w[16];
     w[0] = bswap32((uint32_t)sseed); w[1] = bswap32((uint32_t)(sseed >> 32));
     w[2] = bswap32((uint32_t)idx); w[3] = bswap32((uint32_t)(idx >> 32));
     w[4] = 0x80000000u;
@@ -98,6 +98,10 @@ GL_HD void sha256_salted_leaf(gl_t v, uint64_t sseed, uint64_t idx, uint32_t out
     w[15] = 128;  // 16-byte message
     sha256_iv(hs);
     sha256_compress(hs, w);
+}
+GL_HD void sha256_salted_leaf(gl_t v, uint64_t sseed, uint64_t idx, uint32_t out[8]) {
+    uint32_t w[16], hs[8];
+    sha256_salt(sseed, idx, hs);
     w[0] = bswap32((uint32_t)v); w[1] = bswap32((uint32_t)(v >> 32));
 #pragma unroll
     for (int i = 0; i < 8; i++) w[2 + i] = hs[i];

@@ -125,7 +125,8 @@ static int scw_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, con
 
 
 // ------------------------------------------------------------------ programmable zero-check
-// Summand  col0 * (konst + sum_j coef_j * prod_{k < deg_j} col[idx_jk]),  deg_j in 1..3: the shape of every
+// Summand  col0 * (konst + sum_j coef_j * prod_{k < deg_j} col[idx_jk]) + sum_f coef_f * prod col[idx_fk],  degrees 1..3
+// (the second sum: terms flagged "free", the Libra blind of the hiding mode, zkllm-src/p3_hawkeye.cuh:1035-1053): the shape of every
 // eq-weighted constraint of the integer-layer gadgets (residual add, rescale, SwiGLU, RoPE, RMSNorm,
 // softmax: zkllm-src/p3_int_gadgets.cuh:326, :726, :977-1035, :1307, :1563-1640, :1818).  The reference runs
 // each of them through its host loop sc5_prove with a std::function per row; here the term list is data
@@ -182,16 +183,18 @@ zc_round_kernel(WidePtrs P, size_t items, int first, const ZkhZcProg* prog_g, Zk
 #pragma unroll
             for (int k = 0; k < NCMAX; k++)
                 if (k < nc) { vals[k][tid] = cur[k]; cur[k] = gl_add(cur[k], dif[k]); }
-            Acc192 acc;
+            Acc192 acc, accf;
             acc.clear();
+            accf.clear();
             for (uint32_t j = 0; j < nterms; j++) {
                 const uint32_t pk = prog.packed[j];
                 gl_t x = vals[(pk >> 8) & 0xff][tid];
-                if ((pk & 0xff) >= 2) x = gl_mul(x, vals[(pk >> 16) & 0xff][tid]);
-                if ((pk & 0xff) >= 3) x = gl_mul(x, vals[(pk >> 24) & 0xff][tid]);
-                acc.add_prod(prog.coef[j], x);
+                if ((pk & 0x7f) >= 2) x = gl_mul(x, vals[(pk >> 16) & 0xff][tid]);
+                if ((pk & 0x7f) >= 3) x = gl_mul(x, vals[(pk >> 24) & 0xff][tid]);
+                if (pk & 0x80) accf.add_prod(prog.coef[j], x);
+                else acc.add_prod(prog.coef[j], x);
             }
-            s[t] = gl_add(s[t], gl_mul(vals[0][tid], gl_add(acc.reduce(), konst)));
+            s[t] = gl_add(s[t], gl_add(gl_mul(vals[0][tid], gl_add(acc.reduce(), konst)), accf.reduce()));
         }
     }
     grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, 0);
@@ -281,16 +284,18 @@ __global__ void zcx_round_kernel(const uint8_t* prog_g, const gl_t* const* in, g
         }
 #pragma unroll 1
         for (int t = 0; t < SCW_NT; t++) {
-            Acc192 acc;
+            Acc192 acc, accf;
             acc.clear();
+            accf.clear();
             for (uint32_t j = 0; j < nterms; j++) {
                 const uint32_t pk = packed[j];
                 gl_t x = cur[(size_t)((pk >> 8) & 0xff) * T + tid];
-                if ((pk & 0xff) >= 2) x = gl_mul(x, cur[(size_t)((pk >> 16) & 0xff) * T + tid]);
-                if ((pk & 0xff) >= 3) x = gl_mul(x, cur[(size_t)((pk >> 24) & 0xff) * T + tid]);
-                acc.add_prod(coef[j], x);
+                if ((pk & 0x7f) >= 2) x = gl_mul(x, cur[(size_t)((pk >> 16) & 0xff) * T + tid]);
+                if ((pk & 0x7f) >= 3) x = gl_mul(x, cur[(size_t)((pk >> 24) & 0xff) * T + tid]);
+                if (pk & 0x80) accf.add_prod(coef[j], x);
+                else acc.add_prod(coef[j], x);
             }
-            s[t] = gl_add(s[t], gl_mul(cur[tid], gl_add(acc.reduce(), hdr.konst)));
+            s[t] = gl_add(s[t], gl_add(gl_mul(cur[tid], gl_add(acc.reduce(), hdr.konst)), accf.reduce()));
             if (t + 1 < SCW_NT)
                 for (uint32_t k = 0; k < nc; k++) cur[(size_t)k * T + tid] = gl_add(cur[(size_t)k * T + tid], dif[(size_t)k * T + tid]);
         }
@@ -445,7 +450,7 @@ extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_
     }
     for (uint32_t j = 0; j < nterms; j++) {
         const uint64_t coef = prog[2 + 2 * j], pk = prog[3 + 2 * j];
-        const uint32_t deg = pk & 0xff;
+        const uint32_t deg = pk & 0x7f;      // bit 7: the term stands outside the col0 factor
         if (coef >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: coefficient not canonical");
         if (deg < 1 || deg > 3 || (pk >> 32)) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: term degree must be 1..3");
         for (uint32_t k = 0; k < deg; k++)

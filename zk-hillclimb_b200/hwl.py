@@ -16,7 +16,7 @@ import struct
 import numpy as np
 import torch
 
-from .p3 import (F_HW_CH, F_HW_DG, F_HW_DO, F_HW_DP, F_HW_DS, F_HW_GS, F_PROD3, GL_P, Ledger, claimc, commit_cols, lu_flush,
+from .p3 import (F_HW_CH, F_HW_DG, F_HW_DO, F_HW_DP, F_HW_DS, F_HW_GS, F_PROD3, GL_P, claimc, commit_cols, lu_flush,
                  make_table)
 
 # ---- column ids (p3_hawkeye.cuh:86-112) ----

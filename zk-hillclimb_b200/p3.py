@@ -71,12 +71,14 @@ class Transcript:
 
 
 def zc_program(terms, konst=0):
-    """Pack [(coef, (idx, ...)), ...] and the constant into the word list zkh_sumcheck_zerocheck reads."""
+    """Pack [(coef, (idx, ...)), ...] and the constant into the word list zkh_sumcheck_zerocheck reads.  A term with a
+    third element that is true stands outside the col0 factor (the blind of a hiding chain)."""
     words = [len(terms), int(konst) % GL_P]
-    for coef, idx in terms:
+    for term in terms:
+        coef, idx = term[0], term[1]
         if not 1 <= len(idx) <= 3:
             raise ValueError("zero-check term: one to three columns")
-        pk = len(idx)
+        pk = len(idx) | (0x80 if len(term) > 2 and term[2] else 0)
         for k, i in enumerate(idx):
             pk |= int(i) << (8 + 8 * k)
         words += [int(coef) % GL_P, pk]
@@ -345,6 +347,28 @@ class Prover:
         else:
             self._ck(self._L.zkh_batchopen_prove_class(self._h, v, pts.ctypes.data, T, ptrs, roots, zid.ctypes.data, k,
                                                        R, Q, label.encode(), st, out.ctypes.data, cap, C.byref(wr)))
+        tr.state = bytes(st)
+        return out.tobytes()[:wr.value]
+
+    def prove_class_salted(self, tr, pts, ents, R, Q, label):
+        """The hiding mode's p3bo::prove_class after its blinder was appended (zkllm-src/p3_batchopen.cuh:385-1147 with
+        zk_salted): ents = (device column, root, point index, salt seed, kept codeword or None, kept tree or None)."""
+        pts = np.ascontiguousarray(pts, dtype=np.uint64)
+        T, v = pts.shape
+        k = len(ents)
+        ptrs = (C.c_uint64 * k)(*[_ptr(e[0]) for e in ents])
+        roots = b"".join(bytes(e[1]) for e in ents)
+        zid = np.ascontiguousarray([e[2] for e in ents], dtype=np.uint32)
+        ss = np.ascontiguousarray([e[3] for e in ents], dtype=np.uint64)
+        kcw = (C.c_uint64 * k)(*[(_ptr(e[4]) if len(e) > 5 and e[4] is not None and e[5] is not None else 0) for e in ents])
+        ktr = (C.c_uint64 * k)(*[(_ptr(e[5]) if len(e) > 5 and e[4] is not None and e[5] is not None else 0) for e in ents])
+        cap = self._L.zkh_batchopen_proof_bound(v, R, Q, k) + k * 2 * Q * 32
+        out = np.zeros(cap, dtype=np.uint8)
+        wr = C.c_size_t(0)
+        st = _buf32(tr.state)
+        self._ck(self._L.zkh_batchopen_prove_class_salted(self._h, v, pts.ctypes.data, T, ptrs, roots, zid.ctypes.data,
+                                                          ss.ctypes.data, k, R, Q, label.encode(), st, out.ctypes.data, cap,
+                                                          C.byref(wr), kcw, ktr))
         tr.state = bytes(st)
         return out.tobytes()[:wr.value]
 
