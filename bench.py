@@ -808,7 +808,7 @@ def run_suite_tf(args):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from oracle import Reference
-    from test_tf_layer_host_logic import ref_tf_prove, ref_tf_verify, small_layer
+    from test_tf_layer_host_logic import ref_tf_prove, ref_tf_verify
     from tfg_helpers import load_art
     torch.cuda.set_device(0)
     prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
@@ -818,12 +818,35 @@ def run_suite_tf(args):
     shapes = {"tiny": (4, 64, 2, 32, 128, 1), "d256s64": (64, 256, 4, 64, 512, 1), "d256s128": (128, 256, 4, 64, 1024, 1),
               "d512s128": (128, 512, 8, 64, 1024, 1)}
     ident = lambda t: t
+
+    def bench_layer(c, seed):
+        """Seeded synthetic layer shaped like the inputs of the reference's own layer bench (zkllm-src/p3_transformer_bench.cu:
+        56-90): moderate-range e4m3 weight codes, unit row scales, norm gains in [0.5, 1.5), bf16 inputs with exponent
+        field 125..127, canonical RoPE tables (theta 10000).  The code exponent field is 2..6 here (4..8 there): with 256
+        and more inputs per row the wider range drives some SwiGLU gates below -88, where silu(gate) * up underflows bf16
+        and the gadget's exponent domain ends (both witness builders refuse: p3_swiglu.cuh:137)."""
+        rng = np.random.default_rng(seed)
+        to_bf = np.vectorize(zk.tfart.bf_from_f64, otypes=[np.uint16])
+
+        def wmat(n, k):
+            codes = (rng.integers(0, 2, n * k) << 7) | (rng.integers(2, 7, n * k) << 3) | rng.integers(0, 8, n * k)
+            return codes.astype(np.uint8), np.full(n, 0x3F800000, dtype=np.uint32)
+        d, dff, dh, seq = c.d, c.dff, c.dh, c.seq
+        half = dh // 2
+        ang = np.arange(seq, dtype=np.float64)[:, None] * (10000.0 ** (-np.arange(half, dtype=np.float64) / half))[None, :]
+        W = {"w": [wmat(d, d), wmat(d, d), wmat(d, d), wmat(d, d), wmat(dff, d), wmat(dff, d), wmat(d, dff)],
+             "g1": to_bf(0.5 + rng.integers(0, 1000, d) / 1000.0), "g2": to_bf(0.5 + rng.integers(0, 1000, d) / 1000.0),
+             "cos": to_bf(np.cos(ang)).reshape(-1), "sin": to_bf(np.sin(ang)).reshape(-1)}
+        n0 = c.T * d
+        x0 = ((rng.integers(0, 2, n0) << 15) | (rng.integers(125, 128, n0) << 7) | rng.integers(0, 128, n0)).astype(np.uint16)
+        return x0, W
+
     for key in args.tf_shapes.split(","):
         c = tfg.TfConfig(*shapes[key])
         art = load_art(ref, zk, c.ld) if ref is not None else zk.tfart.build_art(c.ld)
         wmax = max(23, 16 + c.lseq)
         T = tfg.tf_tables(art, wmax)
-        x0, W = small_layer(zk, c, 42)
+        x0, W = bench_layer(c, 42)
         t_wit = None
         for _ in range(2):
             w = None

@@ -162,6 +162,13 @@ ZKH_API int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* const* 
 ZKH_API int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
                            const uint64_t* prog, int nwords, const char* tag, uint8_t state[32], uint64_t* msgs,
                            uint64_t* chals, uint64_t* finals);
+/* The same chain under a structured Libra blind g(x) = sum_j g_j(x_j), g_j of degree 4 (zkllm-src/p3_hawkeye.cuh:1065-1110 sb_fix,
+ * :1329-1331): the message of round rd gains A_rd * (pref + g_rd(t)) + B_rd, pref = sum_{i < rd} g_i(a_i), applied on the device
+ * before the message is absorbed.  fix: 7 words per round (host): the five coefficients of g_rd, A_rd = rho * 2^(v-1-rd),
+ * B_rd = rho * 2^(v-2-rd) * suf[rd+1].  pref_out: g(r) after the last round. */
+ZKH_API int zkh_sumcheck_zerocheck_blind(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
+                                 const uint64_t* prog, int nwords, const uint64_t* fix, const char* tag, uint8_t state[32],
+                                 uint64_t* msgs, uint64_t* chals, uint64_t* finals, uint64_t* pref_out);
 /* Column and coefficient counts of a ZKH_F_HW_* summand (ZKH_ERR_ARG for any other id). */
 ZKH_API int zkh_sumcheck_wide_shape(int functor, int* nc, int* nlam);
 

@@ -146,9 +146,11 @@ size_t bo_serialize(const p3bo::BatchProof& pf, uint8_t* out, size_t cap) {
     for (auto& oc : pf.q0c) {
         uint32_t nv = (uint32_t)oc.vals.size(), nn = (uint32_t)oc.nodes.size();
         app(&nv, 4); app(oc.vals.data(), (size_t)nv * 8);
+        if (p3zkc::G.on) for (auto& sl : oc.salts) app(sl.data(), 32);
         app(&nn, 4);
         for (auto& h : oc.nodes) app(h.data(), 32);
     }
+    if (p3zkc::G.on) { app(pf.bl_root.data(), 32); app(&pf.bl_y, 8); }
     if (b.size() > cap) return 0;
     memcpy(out, b.data(), b.size());
     return b.size();
@@ -191,11 +193,56 @@ bool bo_deserialize(const uint8_t* in, size_t len, p3bo::BatchProof& pf) {
         memcpy(&nv, p, 4); p += 4;
         if (!need((size_t)nv * 8 + 4)) return false;
         oc.vals.resize(nv); memcpy(oc.vals.data(), p, (size_t)nv * 8); p += (size_t)nv * 8;
+        if (p3zkc::G.on) {
+            if (!need((size_t)nv * 32 + 4)) return false;
+            oc.salts.resize(nv);
+            for (auto& sl : oc.salts) { memcpy(sl.data(), p, 32); p += 32; }
+        }
         memcpy(&nn, p, 4); p += 4;
         if (!need((size_t)nn * 32)) return false;
         oc.nodes.resize(nn); for (auto& h : oc.nodes) { memcpy(h.data(), p, 32); p += 32; }
     }
+    if (p3zkc::G.on) {
+        if (!need(40)) return false;
+        memcpy(pf.bl_root.data(), p, 32); memcpy(&pf.bl_y, p + 32, 8); p += 40;
+    }
     return p == end;
+}
+// p3zkc::Blind <-> bytes: u32 nb | nb == 5: four roots, else one | H | nb == 6: ystar, else yB[4] |
+//                         nb == 6: u32 rounds, rounds x 24 bytes, yw
+void blind_serialize(const p3zkc::Blind& bl, std::vector<uint8_t>& b) {
+    auto app = [&](const void* s, size_t n) { const uint8_t* q = (const uint8_t*)s; b.insert(b.end(), q, q + n); };
+    app(&bl.nb, 4);
+    for (uint32_t j = 0; j < (bl.nb == 5 ? 4u : 1u); j++) app(bl.rt[j].data(), 32);
+    app(&bl.H, 8);
+    app(bl.yB, bl.nb == 6 ? 8 : 32);
+    if (bl.nb == 6) {
+        uint32_t n = (uint32_t)bl.ip.size();
+        app(&n, 4);
+        for (auto& m : bl.ip) app(m.data(), 24);
+        app(&bl.yw, 8);
+    }
+}
+bool blind_deserialize(const uint8_t*& p, const uint8_t* end, p3zkc::Blind& bl) {
+    auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
+    if (!need(4)) return false;
+    memcpy(&bl.nb, p, 4); p += 4;
+    if (bl.nb < 4 || bl.nb > 6) return false;
+    const uint32_t nr = bl.nb == 5 ? 4 : 1, ny = bl.nb == 6 ? 1 : 4;
+    if (!need((size_t)nr * 32 + 8 + (size_t)ny * 8)) return false;
+    for (uint32_t j = 0; j < nr; j++) { memcpy(bl.rt[j].data(), p, 32); p += 32; }
+    memcpy(&bl.H, p, 8); p += 8;
+    memcpy(bl.yB, p, (size_t)ny * 8); p += (size_t)ny * 8;
+    if (bl.nb == 6) {
+        uint32_t n;
+        if (!need(4)) return false;
+        memcpy(&n, p, 4); p += 4;
+        if (n > 64 || !need((size_t)n * 24 + 8)) return false;
+        bl.ip.resize(n);
+        for (auto& m : bl.ip) { memcpy(m.data(), p, 24); p += 24; }
+        memcpy(&bl.yw, p, 8); p += 8;
+    }
+    return true;
 }
 // GroupProof (merged lookup, non-zk) <-> bytes:
 //   u32 m, c, ns | root_cnt 32 | gkT | per subgroup: u32 n, k | gk | per member: u32 nW, yW.., u32 nV, yv.., u32 nX, extra..
@@ -263,6 +310,7 @@ size_t imm_serialize(const p3imm::Proof& pf, uint8_t* out, size_t cap) {
     app(&pf.lj, 4); app(&pf.lk, 4); app(&pf.li, 4);
     for (auto& m : pf.m) app(&m, 40);
     app(&pf.yY, 8); app(&pf.yX, 8); app(&pf.yW, 8);
+    if (p3zkc::G.on) blind_serialize(pf.bl, b);
     uint32_t nb = (uint32_t)pf.tail.batches.size();
     app(&nb, 4);
     for (auto& bp : pf.tail.batches) {
@@ -279,11 +327,14 @@ bool imm_deserialize(const uint8_t* in, size_t len, p3imm::Proof& pf) {
     auto need = [&](size_t n) { return (size_t)(end - p) >= n; };
     if (!need(12)) return false;
     memcpy(&pf.lj, p, 4); memcpy(&pf.lk, p + 4, 4); memcpy(&pf.li, p + 8, 4); p += 12;
-    uint32_t lt = pf.lj + pf.lk + pf.li;
+    if (pf.lj + pf.lk + pf.li > 60) return false;
+    uint32_t lt = p3zkc::vfull(pf.lj + pf.lk + pf.li);      // the chain runs over the augmented domain when zk is on
     if (lt > 64 || !need((size_t)lt * 40 + 28)) return false;
     pf.m.resize(lt);
     for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
     memcpy(&pf.yY, p, 8); memcpy(&pf.yX, p + 8, 8); memcpy(&pf.yW, p + 16, 8); p += 24;
+    if (p3zkc::G.on && !blind_deserialize(p, end, pf.bl)) return false;
+    if (!need(4)) return false;
     uint32_t nb; memcpy(&nb, p, 4); p += 4;
     if (nb > 64) return false;
     pf.tail.batches.resize(nb);
@@ -1247,6 +1298,19 @@ void ref_combine(const uint64_t* const* cols, int c, size_t n, uint64_t g, uint6
     memcpy(out, o.data(), n * 8);
 }
 
+// ---- the zk switch of the reference (p3zkc::G, p3_zkc.cuh:83-97): on/off, query budget, master seed, structured-blind
+// threshold; the draw counter restarts.  While it is on, the (de)serialisers above read and write the zk fields. ----
+void ref_zk_set(int on, uint32_t Q, uint64_t seed, uint32_t sblind_min) {
+    p3zkc::G = p3zkc::Ctx();
+    p3zkc::G.on = on != 0;
+    p3zkc::G.Q = Q;
+    p3zkc::G.seed = seed;
+    p3zkc::G.ctr = 0;
+    p3zkc::G.sblind_min = sblind_min;
+}
+uint64_t ref_zk_next_seed() { return p3zkc::next_seed(); }
+uint32_t ref_zk_e_of(uint32_t v) { return p3zkc::e_of(v); }
+
 // ---- batched opening: the reference's host-only verifier (p3_batchopen.cuh:1149-1302) ----
 int ref_bo_verify_class(uint8_t st[32], uint32_t v, const uint64_t* pts, uint32_t T, const uint8_t* roots,
                         const uint32_t* zid, const uint64_t* y, uint32_t k, uint32_t R, uint32_t Q,
@@ -1694,6 +1758,41 @@ size_t ref_imm_prove(uint8_t st[32], const uint64_t* X, const uint64_t* W, const
         n = imm_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+// p3imm::prove with the zk switch on (GPU): operands committed by the reference (fresh masks, salted leaves), Y with the
+// mask linkage of its selftest (p3_int_selftest.cu:89-100); roots_out: X, W, Y.  The switch is off again on return.
+size_t ref_imm_prove_zk(uint8_t st[32], const uint64_t* X, const uint64_t* W, uint32_t lj, uint32_t lk, uint32_t li,
+                        uint32_t R, uint32_t Q, uint64_t seed, uint32_t sblind_min, uint8_t* out, size_t cap,
+                        uint8_t* roots_out, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    ref_zk_set(1, Q, seed, sblind_min);
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        std::vector<gl_t> xv_((size_t)1 << (lj + li)), wv_((size_t)1 << (lj + lk));
+        memcpy(xv_.data(), X, xv_.size() * 8); memcpy(wv_.data(), W, wv_.size() * 8);
+        p3lu::Col cx = p3lu::commit_col_nc(xv_, R), cw = p3lu::commit_col_nc(wv_, R);
+        p3imm::OpView xv = p3imm::direct_x(&cx, lj, li), wv = p3imm::direct_w(&cw, lj, lk);
+        std::vector<gl_t> Y = p3imm::compute_y(xv_, xv, wv_, wv, lj, lk, li);
+        p3imm::OpView yv = p3imm::direct_y(nullptr, lk, li);
+        std::vector<gl_t> m1((size_t)1 << (lk + li), 0);
+        p3imm::accum_mask1(m1, xv, wv, yv, lj, lk, li);
+        std::vector<gl_t> mask = p3zkc::mk_linked(lk + li, m1);
+        p3lu::Col cy = p3lu::commit_col_nc(Y, R, &mask);
+        yv.c = &cy; yv.root = cy.root;
+        memcpy(roots_out, cx.root.data(), 32); memcpy(roots_out + 32, cw.root.data(), 32); memcpy(roots_out + 64, cy.root.data(), 32);
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        auto pf = p3imm::prove(tr, xv, wv, yv, lj, lk, li, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = imm_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    ref_zk_set(0, 24, 1, 22);
     memcpy(st, tr.state, 32);
     return n;
 }

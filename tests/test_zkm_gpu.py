@@ -1,0 +1,70 @@
+"""Hiding mode on CUDA: the zk matmul proof equals the CPU engine's bytes, is accepted by the reference's verifier with its zk
+switch on, and equals the reference's own zk prover byte for byte (same master seed, same draw order)."""
+import numpy as np
+import pytest
+
+from imm_helpers import matmul_instance
+from lu_helpers import _Arr
+from zkm_helpers import OracleZkEngine, ref_imm_prove_zk, ref_imm_verify_zk
+
+pytestmark = pytest.mark.gpu
+GL_P = 0xFFFFFFFF00000001
+
+
+def commit3(zk, eng, zc, x, w, y, dims, R, wrap):
+    zkm = zk.zkm
+    lj, lk, li = dims
+    X = zkm.commit_col(eng, zc, wrap(x), R)
+    W = zkm.commit_col(eng, zc, wrap(w), R)
+    Y = zkm.commit_col(eng, zc, wrap(y), R, mask=zkm.linked_y_mask(eng, zc, X, W, lj, lk, li))
+    return X, W, Y
+
+
+@pytest.mark.parametrize("dims,sblind_min", [((3, 2, 3), 22), ((4, 3, 3), 22), ((3, 2, 3), 5), ((4, 4, 2), 8)])
+def test_zk_matmul_equals_cpu_engine(orc, ref_or_none, zk, prover, dims, sblind_min):
+    R, Q, seed = 1, 24, 31
+    lj, lk, li = dims
+    x, w, y = matmul_instance(orc, lj, lk, li, seed)
+    out = []
+    for eng, wrap in ((OracleZkEngine(orc), _Arr), (prover, zk.p3.to_device)):
+        zc = zk.zkm.ZkCtx(seed=seed, Q=Q, sblind_min=sblind_min)
+        X, W, Y = commit3(zk, eng, zc, x, w, y, dims, R, wrap)
+        tr = zk.Transcript("imm-t")
+        pf = zk.zkm.imm_prove(eng, zc, tr, X, W, Y, lj, lk, li, R, Q)
+        out.append((pf, tr.state, [X.root, W.root, Y.root]))
+    assert out[0][2] == out[1][2] and out[0][1] == out[1][1] and out[0][0] == out[1][0]
+    if ref_or_none:
+        ok, st = ref_imm_verify_zk(ref_or_none, zk.Transcript("imm-t").state, out[1][2], lj, lk, li, R, Q, out[1][0], sblind_min)
+        assert ok and st == out[1][1]
+
+
+@pytest.mark.parametrize("dims,sblind_min", [((4, 3, 5), 22), ((6, 6, 5), 22), ((6, 6, 5), 12), ((8, 7, 6), 22)])
+def test_zk_matmul_equals_reference_prover(orc, ref, zk, prover, dims, sblind_min):
+    """Merged blinds below the structured threshold, structured blinds above: same bytes as p3imm::prove with zk on."""
+    R, Q, seed = 1, 24, 0xC0FFEE
+    lj, lk, li = dims
+    x, w, y = matmul_instance(orc, lj, lk, li, 3)
+    st0 = zk.Transcript("imm-t").state
+    want, st_ref, roots_ref, _ = ref_imm_prove_zk(ref, st0, x, w, lj, lk, li, R, Q, seed, sblind_min)
+    assert len(want) > 0
+    zc = zk.zkm.ZkCtx(seed=seed, Q=Q, sblind_min=sblind_min)
+    X, W, Y = commit3(zk, prover, zc, x, w, y, dims, R, zk.p3.to_device)
+    assert [X.root, W.root, Y.root] == roots_ref
+    tr = zk.Transcript("imm-t")
+    pf = zk.zkm.imm_prove(prover, zc, tr, X, W, Y, lj, lk, li, R, Q)
+    assert tr.state == st_ref and pf == want
+    ok, st = ref_imm_verify_zk(ref, st0, roots_ref, lj, lk, li, R, Q, pf, sblind_min)
+    assert ok and st == tr.state
+
+
+def test_blinded_zero_check_matches_python_evaluation(orc, zk, prover):
+    from conftest import lcg_cols
+    logn, nc = 6, 5
+    cols = lcg_cols(orc, 1 << logn, nc, 99)
+    terms = [(3, (1, 2)), (7, (3, 4, 4)), (5, (2,), True)]
+    rng = np.random.default_rng(1)
+    table = [[int(v) for v in rng.integers(1, GL_P, 7, dtype=np.uint64)] for _ in range(logn)]
+    tr1, tr2 = zk.Transcript("zb"), zk.Transcript("zb")
+    a = prover.sc_prove_zc_blind(tr1, "t", [zk.p3.to_device(c) for c in cols], terms, 17, table)
+    b = OracleZkEngine(orc).sc_prove_zc_blind(tr2, "t", [_Arr(c) for c in cols], terms, 17, table)
+    assert tr1.state == tr2.state and a[3] == b[3] and all((np.asarray(u) == np.asarray(v)).all() for u, v in zip(a[:3], b[:3]))

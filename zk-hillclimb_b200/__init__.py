@@ -13,6 +13,7 @@ Layout:
   hwl.py      the fp8 (Hawkeye) matmul gadget: tables, witness replay as tensor arithmetic, prover (on demand; needs torch)
   tfart.py    pinned table artefact of the fp8 transformer layer's bf16 gadgets (exact integer rounding; numpy)
   tfg.py      bf16 gadgets of the fp8 transformer layer (SwiGLU, ...) as host logic over the engine (on demand; needs torch)
+  zkm.py      hiding mode: masks, salted commitments, blinded sumcheck, blinded batched openings, the zk matmul proof
   fr.py       host-side mirror of the BLS12-381 Fr pieces (eq tensors, folds, product sumchecks)
 """
 from . import _lib  # noqa: F401
@@ -25,7 +26,7 @@ from .p3 import (F_GKR, F_LOGUP, F_PROD2, F_PROD3, GL_P, Prover, Transcript)  # 
 
 def __getattr__(name):
     """The torch-based modules load on first use."""
-    if name in ("hwl", "ig_dev", "tfg", "tfart"):
+    if name in ("hwl", "ig_dev", "tfg", "tfart", "zkm"):
         import importlib
         return importlib.import_module("." + name, __name__)
     raise AttributeError(name)

@@ -101,6 +101,25 @@ __device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t
         }
         __syncwarp();
     }
+    // mode 3: structured Libra blind g(x) = sum_j g_j(x_j) of the hiding mode (zkllm-src/p3_hawkeye.cuh:1092-1110 sb_fix): the
+    // message of round rd gains A_rd * (pref + g_rd(t)) + B_rd, and pref gains g_rd(a) once the challenge a is known.
+    // Table at par[6]: word 0 = pref, then 8 words per round: the five coefficients of g_rd, A_rd, B_rd, unused.
+    gl_t* fx = nullptr;
+    const gl_t* fe = nullptr;
+    if (mode == 3) {
+        fx = reinterpret_cast<gl_t*>(ctl->par[6]);
+        fe = fx + 8 + 8 * (size_t)((msg_out - ctl->msgs) / NT);
+        if (lane < NT) {
+            const gl_t t = (gl_t)lane;
+            gl_t g = fe[4];
+#pragma unroll
+            for (int k = 3; k >= 0; k--) g = gl_add(gl_mul(g, t), fe[k]);
+            const gl_t add = gl_add(gl_mul(fe[5], gl_add(fx[0], g)), fe[6]);
+            mvals[lane] = gl_add(mvals[lane], add);
+            msg_out[lane] = mvals[lane];
+        }
+        __syncwarp();
+    }
     uint32_t st[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) st[i] = ctl->st[i];
@@ -110,6 +129,12 @@ __device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t
 #pragma unroll
         for (int i = 0; i < 8; i++) ctl->st[i] = st[i];
         *chal_out = a;
+        if (mode == 3) {
+            gl_t g = fe[4];
+#pragma unroll
+            for (int k = 3; k >= 0; k--) g = gl_add(gl_mul(g, a), fe[k]);
+            fx[0] = gl_add(fx[0], g);
+        }
     }
 }
 

@@ -197,7 +197,7 @@ zc_round_kernel(WidePtrs P, size_t items, int first, const ZkhZcProg* prog_g, Zk
             s[t] = gl_add(s[t], gl_add(gl_mul(vals[0][tid], gl_add(acc.reduce(), konst)), accf.reduce()));
         }
     }
-    grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, 0);
+    grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, ctl->par[6] ? 3 : 0);
 }
 
 template <int NCMAX>
@@ -300,7 +300,7 @@ __global__ void zcx_round_kernel(const uint8_t* prog_g, const gl_t* const* in, g
                 for (uint32_t k = 0; k < nc; k++) cur[(size_t)k * T + tid] = gl_add(cur[(size_t)k * T + tid], dif[(size_t)k * T + tid]);
         }
     }
-    grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, 0);
+    grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, ctl->par[6] ? 3 : 0);
 }
 
 __global__ void zcx_finals_kernel(const gl_t* const* in, int nc, const gl_t* chal, gl_t* out) {
@@ -423,9 +423,9 @@ extern "C" int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* cons
 
 // prog: [0] = number of terms, [1] = constant inside the bracket, then per term (coefficient, packed) with
 // packed = degree | idx0 << 8 | idx1 << 16 | idx2 << 24
-extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
-                                      const uint64_t* prog, int nwords, const char* tag, uint8_t state[32], uint64_t* msgs,
-                                      uint64_t* chals, uint64_t* finals) {
+static int zerocheck_impl(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
+                          const uint64_t* prog, int nwords, const char* tag, uint8_t state[32], uint64_t* msgs,
+                          uint64_t* chals, uint64_t* finals, const uint64_t* fix, uint64_t* pref_out) {
     if (!ctx) return ZKH_ERR_ARG;
     if (!cols_dev || !prog || !tag || !state || !msgs || !chals) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: null pointer");
     if (nc < 1 || nc > ZCX_MAXC) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: 1..224 columns");
@@ -469,7 +469,18 @@ extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_
     const size_t szA = zkh_align((size_t)nc * (n / 2 + 1) * 8), szB = zkh_align((size_t)nc * (n / 4 + 1) * 8);
     const size_t szF = zkh_align((size_t)nc * 8);
     const size_t szP = zkh_align(large ? hx.size() : sizeof(ZkhZcProg)), szT = zkh_align((size_t)logn * 2 * nc * sizeof(void*));
-    ZKH_TRY(zkh_ws_reserve(ctx, szA + szB + szF + szP + szT));
+    const size_t szX = zkh_align((8 + 8 * (size_t)logn) * 8);
+    ZKH_TRY(zkh_ws_reserve(ctx, szA + szB + szF + szP + szT + szX));
+    gl_t* fix_dev = (gl_t*)((char*)ctx->ws + szA + szB + szF + szP + szT);
+    std::vector<gl_t> hfix;
+    if (fix) {
+        hfix.assign(8 + 8 * (size_t)logn, 0);
+        for (uint32_t r = 0; r < logn; r++)
+            for (int k = 0; k < 7; k++) {
+                if (fix[7 * (size_t)r + k] >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: blind coefficient not canonical");
+                hfix[8 + 8 * (size_t)r + k] = fix[7 * (size_t)r + k];
+            }
+    }
     gl_t* finals_dev = (gl_t*)((char*)ctx->ws + szA + szB);
     uint8_t* prog_dev = (uint8_t*)ctx->ws + szA + szB + szF;
     const gl_t** ptr_dev = (const gl_t**)((char*)ctx->ws + szA + szB + szF + szP);
@@ -478,6 +489,10 @@ extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_
     h->counter = 0;
     h->err = 0;
     for (int i = 0; i < 8; i++) h->par[i] = 0;
+    if (fix) {
+        h->par[6] = (gl_t)(uintptr_t)fix_dev;
+        ZKH_CUDA(ctx, cudaMemcpyAsync(fix_dev, hfix.data(), hfix.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
+    }
     ZKH_CUDA(ctx, cudaMemcpyAsync(ctx->d_ctl, h, offsetof(ZkhCtl, local), cudaMemcpyHostToDevice, ctx->stream));
     ZKH_CUDA(ctx, cudaMemcpyAsync(prog_dev, large ? (const void*)hx.data() : (const void*)&hp, large ? hx.size() : sizeof hp,
                                   cudaMemcpyHostToDevice, ctx->stream));
@@ -490,10 +505,28 @@ extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_
     ZKH_CUDA(ctx, cudaMemcpyAsync(h, ctx->d_ctl, sizeof(ZkhCtl), cudaMemcpyDeviceToHost, ctx->stream));
     if (finals)
         ZKH_CUDA(ctx, cudaMemcpyAsync(finals, finals_dev, (size_t)nc * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    if (fix && pref_out) ZKH_CUDA(ctx, cudaMemcpyAsync(pref_out, fix_dev, 8, cudaMemcpyDeviceToHost, ctx->stream));
     ZKH_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (h->err) return zkh_fail(ctx, ZKH_ERR_DEVICE, "zero-check: device error flag set");
     memcpy(msgs, h->msgs, (size_t)logn * SCW_NT * 8);
     memcpy(chals, h->chals, (size_t)logn * 8);
     digest_to_bytes(h->st, state);
     return ZKH_OK;
+}
+
+extern "C" int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
+                                      const uint64_t* prog, int nwords, const char* tag, uint8_t state[32], uint64_t* msgs,
+                                      uint64_t* chals, uint64_t* finals) {
+    return zerocheck_impl(ctx, cols_dev, nc, logn, prog, nwords, tag, state, msgs, chals, finals, nullptr, nullptr);
+}
+// The same chain under a structured Libra blind (zkllm-src/p3_hawkeye.cuh:1065-1110, :1329-1331): fix holds, per round, the five
+// coefficients of g_rd, A_rd = rho * 2^(v-1-rd) and B_rd = rho * 2^(v-2-rd) * suf[rd+1]; the message of round rd gains
+// A_rd * (pref + g_rd(t)) + B_rd with pref = sum_{i < rd} g_i(a_i), all on the device.  pref_out: g(r) after the last round.
+extern "C" int zkh_sumcheck_zerocheck_blind(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
+                                            const uint64_t* prog, int nwords, const uint64_t* fix, const char* tag,
+                                            uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals,
+                                            uint64_t* pref_out) {
+    if (!ctx) return ZKH_ERR_ARG;
+    if (!fix || !pref_out) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: the blinded chain needs its table and pref_out");
+    return zerocheck_impl(ctx, cols_dev, nc, logn, prog, nwords, tag, state, msgs, chals, finals, fix, pref_out);
 }

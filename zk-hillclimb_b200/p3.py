@@ -436,6 +436,23 @@ class Prover:
         import torch
         return col[torch.from_numpy(np.ascontiguousarray(idx, dtype=np.int64)).to(col.device)].contiguous()
 
+    def gather_fn(self, col, n, fn):
+        """out[u] = col[fn(u)] for u < n, the index map written with integer operators (&, |, <<, >>) and evaluated on the
+        device: broadcast columns of the hiding mode's product domains."""
+        import torch
+        u = torch.arange(n, dtype=torch.int64, device=col.device)
+        return col[fn(u)].contiguous()
+
+    def slice(self, col, lo, n):
+        return col[lo:lo + n]
+
+    def concat(self, cols):
+        import torch
+        return torch.cat(list(cols)).contiguous()
+
+    def download(self, col):
+        return to_host(col)
+
     def flip_bit(self, col, b):
         """out[u] = col[u ^ (1 << b)]: the rotate-half permutation of RoPE (zkllm-src/p3_int_gadgets.cuh:1297-1298)."""
         return col.view(-1, 2, 1 << b).flip(1).reshape(-1).contiguous()
@@ -646,6 +663,26 @@ class Prover:
                                                 msgs.ctypes.data, chals.ctypes.data, fin.ctypes.data))
         tr.state = bytes(st)
         return chals, msgs, fin
+
+    def sc_prove_zc_blind(self, tr, tag, dcols, terms, konst, table):
+        """The zero-check chain under a structured Libra blind (the structured branch of p3hwl::sc5z, zkllm-src/p3_hawkeye.cuh:
+        1329-1331 with sb_fix :1092-1110).  table: per round [c0..c4 of g_rd, A_rd, B_rd]; the message of round rd gains
+        A_rd * (pref + g_rd(t)) + B_rd on the device.  Returns (r, msgs, finals, g(r))."""
+        nc = len(dcols)
+        logn = int(dcols[0].numel()).bit_length() - 1
+        ptrs = (C.c_uint64 * nc)(*[_ptr(t) for t in dcols])
+        prog = zc_program(terms, konst)
+        fix = np.ascontiguousarray(table, dtype=np.uint64).reshape(logn, 7)
+        msgs = np.zeros((logn, 5), dtype=np.uint64)
+        chals = np.zeros(logn, dtype=np.uint64)
+        fin = np.zeros(nc, dtype=np.uint64)
+        pref = C.c_uint64(0)
+        st = _buf32(tr.state)
+        self._ck(self._L.zkh_sumcheck_zerocheck_blind(self._h, ptrs, nc, logn, prog.ctypes.data, len(prog), fix.ctypes.data,
+                                                      tag.encode(), st, msgs.ctypes.data, chals.ctypes.data, fin.ctypes.data,
+                                                      C.byref(pref)))
+        tr.state = bytes(st)
+        return chals, msgs, fin, int(pref.value)
 
     def sc_prove_host(self, tr, tag, cols, functor, nt, par=()):
         """Same through host columns (numpy uint64): upload + prove + download in one call."""
