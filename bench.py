@@ -798,6 +798,67 @@ def run_suite_hwl(args):
         torch.cuda.empty_cache()
 
 
+def run_suite_zk(args):
+    """--suite-zk: the quantised matmul proof in hiding mode (masked salted commitments, Libra-blinded chain, blinded batched
+    openings; the reference's p3imm::prove with its zk switch on) beside the reference's own zk prover on the same inputs and
+    master seed.  Shapes (lj, lk, li): small = 64x64.64x32, mid = 256x256.256x64 (structured blinds), c1 = BASELINE configs[0]
+    padded, 1024x1024.1024x128 (2^28-point chain; the reference is not run there: its host columns need tens of GB)."""
+    import torch
+    import zkh_import
+    zk = zkh_import.load()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import Reference
+    from zkm_helpers import ref_imm_prove_zk, ref_imm_verify_zk
+    torch.cuda.set_device(0)
+    prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+    zkm = zk.zkm
+    ref = Reference() if Reference.available() else None
+    R, Q, seed = 1, 24, 0xC0FFEE
+    shapes = {"small": (6, 5, 6), "mid": (8, 6, 8), "c1": (10, 10, 7)}
+    for key in args.zk_shapes.split(","):
+        lj, lk, li = shapes[key]
+        rng = np.random.default_rng(7)
+        xi = rng.integers(-127, 128, (1 << li, 1 << lj))
+        wi = rng.integers(-127, 128, (1 << lj, 1 << lk))
+        lift = lambda a: np.where(a < 0, a.astype(np.int64).astype(np.uint64) + np.uint64(0xFFFFFFFF00000001), a.astype(np.uint64)).reshape(-1)
+        x, w, y = lift(xi), lift(wi), lift(xi @ wi)
+        dx, dw, dy = (zk.p3.to_device(a) for a in (x, w, y))
+        best = None
+        for rep in range(args.layer_reps):
+            zc = zkm.ZkCtx(seed=seed, Q=Q)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            X = zkm.commit_col(prover, zc, dx, R)
+            W = zkm.commit_col(prover, zc, dw, R)
+            Y = zkm.commit_col(prover, zc, dy, R, mask=zkm.linked_y_mask(prover, zc, X, W, lj, lk, li))
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            tr = zk.Transcript("imm-t")
+            pf = zkm.imm_prove(prover, zc, tr, X, W, Y, lj, lk, li, R, Q)
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+            if best is None or t2 - t1 < best[1]:
+                best = (t1 - t0, t2 - t1)
+        line = {"suite": "zk matmul " + key, "lj_lk_li": [lj, lk, li], "chain_points_log2": zkm.ZkCtx(Q=Q).vfull(lj + lk + li), "R": R, "Q": Q,
+                "commit_s": best[0], "prove_s": best[1], "proof_MB": len(pf) / 1048576.0}
+        st0 = zk.Transcript("imm-t").state
+        if ref is not None:
+            t0 = time.perf_counter()
+            ok, st = ref_imm_verify_zk(ref, st0, [X.root, W.root, Y.root], lj, lk, li, R, Q, pf)
+            line["accepted_by_reference_verifier"] = bool(ok and st == tr.state)
+            line["reference_verify_host_s"] = time.perf_counter() - t0
+            if key != "c1" and not args.no_ref_cuda:
+                want, st_ref, roots_ref, ms = ref_imm_prove_zk(ref, st0, x, w, lj, lk, li, R, Q, seed)
+                line["reference_prove_s"] = ms / 1e3
+                line["speedup_prove_vs_reference"] = ms / 1e3 / best[1]
+                line["same_proof_bytes"] = bool(want == pf and roots_ref == [X.root, W.root, Y.root])
+        print(json.dumps(line), flush=True)
+        del X, W, Y, dx, dw, dy
+        torch.cuda.empty_cache()
+    return 0
+
+
 def run_suite_tf(args):
     """--suite-tf: one composed fp8 transformer layer (the reference's p3tf stack, non-zk: RMSNorm, quantise, fp8 matmuls,
     RoPE, masked softmax, SwiGLU, bf16 residual adds, seams) with the witness chain on the GPU; accepted by the reference's
@@ -863,14 +924,15 @@ def run_suite_tf(args):
             torch.cuda.synchronize()
             t1 = time.perf_counter()
             tr = zk.Transcript("tf-layer")
-            pf = tfg.tf_prove(prover, tr, w, o, T, art, R, Q, ident)
+            stages = {}
+            pf = tfg.tf_prove(prover, tr, w, o, T, art, R, Q, ident, stages=stages)
             torch.cuda.synchronize()
             t2 = time.perf_counter()
             if best is None or t2 - t1 < best[1]:
-                best = (t1 - t0, t2 - t1)
+                best = (t1 - t0, t2 - t1, stages)
         line = {"suite": "fp8 transformer layer " + key, "dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), c.dims())),
                 "R": R, "Q": Q, "witness_device_s": t_wit, "commit_s": best[0], "prove_s": best[1], "proof_MB": len(pf) / 1048576.0,
-                "sub_proofs": 12 + 13 * c.A}
+                "sub_proofs": 12 + 13 * c.A, "stages": {k: (round(v, 4) if isinstance(v, float) else v) for k, v in best[2].items()}}
         if ref is not None:
             wroots = tfg.tf_weight_roots(prover, c, W, R, ident)
             t0 = time.perf_counter()
@@ -972,6 +1034,8 @@ def main():
     ap.add_argument("--layer-reps", type=int, default=2)
     ap.add_argument("--suite-tf", action="store_true", help="one composed fp8 transformer layer (RMSNorm .. residual) on the GPU")
     ap.add_argument("--tf-shapes", default="tiny,d256s64")
+    ap.add_argument("--suite-zk", action="store_true", help="the quantised matmul proof in hiding mode beside the reference's zk prover")
+    ap.add_argument("--zk-shapes", default="small,mid")
     ap.add_argument("--suite-hwl", action="store_true", help="the fp8 (Hawkeye) matmul gadget beside the reference's prover")
     ap.add_argument("--hwl-shapes", default="small,mid")
     ap.add_argument("--hwl-keep-trees", action="store_true")
@@ -994,6 +1058,8 @@ def main():
         return run_suite_hwl(args)
     if args.suite_tf:
         return run_suite_tf(args)
+    if args.suite_zk:
+        return run_suite_zk(args)
     if args.suite_model:
         return run_suite_model(args)
     if args.suite_gadgets:

@@ -1445,15 +1445,24 @@ def tf_serialize(w, o, subs, lug, seam, batches):
     return out + sl + struct.pack("<I", len(seam)) + _u64(seam) + sb
 
 
-def tf_prove(engine, tr, w, o, T, art, R, Q, col, strict=True):
+def tf_prove(engine, tr, w, o, T, art, R, Q, col, strict=True, stages=None):
     """p3tf::prove (p3_transformer.cuh:1011-1037), non-zk: all sub-proofs in fixed order on one transcript with one ledger,
-    one merged-lookup flush, the composition seams with both public I/O bindings, one batched opening per size class."""
+    one merged-lookup flush, the composition seams with both public I/O bindings, one batched opening per size class.
+    stages: optional dict that receives the wall-clock seconds of the four stages (the engine calls synchronise)."""
+    import time
     from .ig import Ctx
     ctx = Ctx()
+    t0 = time.perf_counter()
     subs = tf_prove_subs(engine, tr, w, o, T, art, R, Q, col, ctx, strict)
+    t1 = time.perf_counter()
     lug = lu_flush(engine, tr, ctx.luq, ctx.ledger, R, strict)
+    t2 = time.perf_counter()
     seam = tf_prove_seams(engine, tr, w, o, ctx, strict, True, True)
+    t3 = time.perf_counter()
     batches = [engine.prove_class(tr, np.stack(k[1]), k[2], R, Q, "tf-bo%d" % i) for i, k in enumerate(ctx.ledger.cls)]
+    if stages is not None:
+        stages.update(subs_s=t1 - t0, lookups_s=t2 - t1, seams_s=t3 - t2, openings_s=time.perf_counter() - t3,
+                      lookup_groups=len(lug), opening_classes=len(batches))
     return tf_serialize(w, o, subs, lug, seam, batches)
 
 
