@@ -256,9 +256,11 @@ size_t lu_serialize(const p3lu::GroupProof& pf, uint8_t* out, size_t cap) {
     };
     uint32_t ns = (uint32_t)pf.sub.size();
     app(&pf.m, 4); app(&pf.c, 4); app(&ns, 4); app(pf.root_cnt.data(), 32);
+    if (p3zkc::G.on) { app(pf.rt_pmT.data(), 32); app(pf.rt_qmT.data(), 32); }
     appg(pf.gkT);
     for (auto& sb : pf.sub) {
         app(&sb.n, 4); app(&sb.k, 4);
+        if (p3zkc::G.on) { app(sb.rt_pm.data(), 32); app(sb.rt_qm.data(), 32); }
         appg(sb.gk);
         for (auto& mm : sb.mem) {
             uint32_t a = (uint32_t)mm.yW.size(), v = (uint32_t)mm.y_virt.size(), x = (uint32_t)mm.extra.size();
@@ -278,15 +280,25 @@ bool lu_deserialize(const uint8_t* in, size_t len, p3lu::GroupProof& pf) {
     if (!need(44)) return false;
     memcpy(&pf.m, p, 4); memcpy(&pf.c, p + 4, 4); memcpy(&ns, p + 8, 4); memcpy(pf.root_cnt.data(), p + 12, 32); p += 44;
     if (pf.m > 40 || ns > 4096) return false;
-    if (!need(gkr_size(pf.m)) || !gkr_deserialize(p, gkr_size(pf.m), pf.m, pf.gkT)) return false;
-    p += gkr_size(pf.m);
+    const bool zk = p3zkc::G.on;        // zk: mask-leaf roots ride along and the trees run over the interleaved augmented domains
+    if (zk) {
+        if (!need(64)) return false;
+        memcpy(pf.rt_pmT.data(), p, 32); memcpy(pf.rt_qmT.data(), p + 32, 32); p += 64;
+    }
+    const uint32_t LT = zk ? p3zkc::vfull(pf.m) + 1 : pf.m;
+    if (!need(gkr_size(LT)) || !gkr_deserialize(p, gkr_size(LT), LT, pf.gkT)) return false;
+    p += gkr_size(LT);
     pf.sub.resize(ns);
     for (auto& sb : pf.sub) {
         if (!need(8)) return false;
         memcpy(&sb.n, p, 4); memcpy(&sb.k, p + 4, 4); p += 8;
         if (sb.n > 40 || sb.k == 0 || sb.k > 4096) return false;
+        if (zk) {
+            if (!need(64)) return false;
+            memcpy(sb.rt_pm.data(), p, 32); memcpy(sb.rt_qm.data(), p + 32, 32); p += 64;
+        }
         uint32_t g = 0; while ((1u << g) < sb.k) g++;
-        uint32_t L = sb.n + g;
+        uint32_t L = zk ? p3zkc::vfull(sb.n) + g + 1 : sb.n + g;
         if (!need(gkr_size(L)) || !gkr_deserialize(p, gkr_size(L), L, sb.gk)) return false;
         p += gkr_size(L);
         sb.mem.resize(sb.k);
@@ -1023,6 +1035,7 @@ size_t irs_serialize(const p3irs::Proof& pf, uint8_t* out, size_t cap) {
     for (auto& m : pf.m) app(&m, 40);
     app(&pf.yX, 8); app(&pf.yY, 8);
     for (uint32_t l = 0; l < pf.nl; l++) app(&pf.yL[l], 8);
+    if (p3zkc::G.on) blind_serialize(pf.bl, b);
     std::vector<uint8_t> t((size_t)64 << 20);
     uint32_t ng = (uint32_t)pf.tail.lug.size();
     app(&ng, 4);
@@ -1046,12 +1059,15 @@ bool irs_deserialize(const uint8_t* in, size_t len, p3irs::Proof& pf) {
     if (!need(16)) return false;
     memcpy(&pf.le, p, 4); memcpy(&pf.sf, p + 4, 4); memcpy(&pf.nl, p + 8, 4); memcpy(&pf.rng, p + 12, 4); p += 16;
     if (pf.le > 40 || pf.nl < 1 || pf.nl > 2) return false;
-    if (!need((size_t)pf.nl * 40 + (size_t)pf.le * 40 + 16 + 4)) return false;
+    const uint32_t lch = p3zkc::vfull(pf.le);
+    if (!need((size_t)pf.nl * 40 + (size_t)lch * 40 + 16 + 4)) return false;
     for (uint32_t l = 0; l < pf.nl; l++) { memcpy(pf.rL[l].data(), p, 32); p += 32; }
-    pf.m.resize(pf.le);
+    pf.m.resize(lch);
     for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
     memcpy(&pf.yX, p, 8); memcpy(&pf.yY, p + 8, 8); p += 16;
     for (uint32_t l = 0; l < pf.nl; l++) { memcpy(&pf.yL[l], p, 8); p += 8; }
+    if (p3zkc::G.on && !blind_deserialize(p, end, pf.bl)) return false;
+    if (!need(4)) return false;
     uint32_t ng; memcpy(&ng, p, 4); p += 4;
     if (ng > 64) return false;
     pf.tail.lug.resize(ng);
@@ -1758,6 +1774,34 @@ size_t ref_imm_prove(uint8_t st[32], const uint64_t* X, const uint64_t* W, const
         n = imm_serialize(pf, out, cap);
     } catch (...) { n = 0; }
     p3fri::g_gpu_merkle = false;
+    memcpy(st, tr.state, 32);
+    return n;
+}
+
+// p3irs::prove with the zk switch on (GPU): X = acc and Y = the rescaled output committed by the reference (fresh masks),
+// limb commitments, deferred range lookups, blinded zero-check, flush and blinded batched openings.  roots_out: X, Y.
+size_t ref_irs_prove_zk(uint8_t st[32], const uint64_t* acc, uint32_t le, uint32_t sf, int rng, uint32_t R, uint32_t Q,
+                        uint64_t seed, uint32_t sblind_min, uint8_t* out, size_t cap, uint8_t* roots_out, double* ms_out) {
+    p3fri::g_gpu_merkle = true;
+    ref_zk_set(1, Q, seed, sblind_min);
+    fs::Transcript tr = tr_from(st);
+    size_t n = 0;
+    try {
+        std::vector<gl_t> a(acc, acc + ((size_t)1 << le));
+        p3irs::Wit w = p3irs::gen_witness(le, sf, rng, a);
+        p3ig::Tables T = irs_tables(sf);
+        p3lu::Col CX = p3lu::commit_col_nc(w.acc, R), CY = p3lu::commit_col_nc(w.y, R);
+        memcpy(roots_out, CX.root.data(), 32); memcpy(roots_out + 32, CY.root.data(), 32);
+        p3irs::Operands o{&CX, &CY};
+        cudaDeviceSynchronize();
+        double t0 = p3bf::bf_now_ms();
+        p3irs::Proof pf = p3irs::prove(tr, w, T, o, R, Q);
+        cudaDeviceSynchronize();
+        if (ms_out) *ms_out = p3bf::bf_now_ms() - t0;
+        n = irs_serialize(pf, out, cap);
+    } catch (...) { n = 0; }
+    p3fri::g_gpu_merkle = false;
+    ref_zk_set(0, 24, 1, 22);
     memcpy(st, tr.state, 32);
     return n;
 }

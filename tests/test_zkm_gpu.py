@@ -5,7 +5,7 @@ import pytest
 
 from imm_helpers import matmul_instance
 from lu_helpers import _Arr
-from zkm_helpers import OracleZkEngine, ref_imm_prove_zk, ref_imm_verify_zk
+from zkm_helpers import OracleZkEngine, ref_imm_prove_zk, ref_imm_verify_zk, ref_irs_prove_zk, ref_irs_verify_zk
 
 pytestmark = pytest.mark.gpu
 GL_P = 0xFFFFFFFF00000001
@@ -68,3 +68,51 @@ def test_blinded_zero_check_matches_python_evaluation(orc, zk, prover):
     a = prover.sc_prove_zc_blind(tr1, "t", [zk.p3.to_device(c) for c in cols], terms, 17, table)
     b = OracleZkEngine(orc).sc_prove_zc_blind(tr2, "t", [_Arr(c) for c in cols], terms, 17, table)
     assert tr1.state == tr2.state and a[3] == b[3] and all((np.asarray(u) == np.asarray(v)).all() for u, v in zip(a[:3], b[:3]))
+
+
+def _acc(le, sf, rng, seed):
+    from irs_helpers import lift
+    r = np.random.default_rng(seed)
+    win = (1 << 19) if rng == 1 else (1 << 15)
+    return lift(r.integers(-(win - 2) << sf, (win - 2) << sf, 1 << le))
+
+
+@pytest.mark.parametrize("le,sf,rng,sblind_min", [(4, 16, 2, 22), (5, 20, 2, 22), (5, 16, 2, 6)])
+def test_zk_rescale_equals_cpu_engine(orc, zk, prover, le, sf, rng, sblind_min):
+    from irs_helpers import irs_tables
+    R, Q = 1, 24
+    acc = _acc(le, sf, rng, le + sf)
+    out = []
+    for eng, wrap in ((OracleZkEngine(orc), _Arr), (prover, zk.p3.to_device)):
+        zc = zk.zkm.ZkCtx(seed=9, Q=Q, sblind_min=sblind_min)
+        T = irs_tables(zk, sf)
+        X = zk.zkm.commit_col(eng, zc, wrap(acc), R)
+        yo, L, iL, iY = eng.irs_witness(X.dev[:1 << le] if eng is prover else _Arr(acc), sf, rng)
+        Y = zk.zkm.commit_col(eng, zc, yo, R)
+        tr = zk.Transcript("irs-t")
+        pf = zk.zkm.irs_prove(eng, zc, tr, T, X, Y, (L, iL, iY), le, sf, rng, R, Q)
+        out.append((pf, tr.state, X.root, Y.root))
+    assert out[0][2:] == out[1][2:] and out[0][1] == out[1][1] and out[0][0] == out[1][0]
+
+
+@pytest.mark.parametrize("le,sf,rng,sblind_min", [(6, 16, 1, 22), (10, 16, 1, 22), (12, 20, 2, 22), (12, 16, 1, 10), (16, 16, 1, 22)])
+def test_zk_rescale_equals_reference_prover(orc, ref, zk, prover, le, sf, rng, sblind_min):
+    """Same bytes as p3irs::prove with the zk switch on: limb commitments, the merged range lookups with their mask-leaf
+    streams, the blinded zero-check, the flush and the blinded batched openings."""
+    from irs_helpers import irs_tables
+    R, Q, seed = 1, 24, 0xFEED
+    acc = _acc(le, sf, rng, 5)
+    st0 = zk.Transcript("irs-t").state
+    want, st_ref, roots_ref, _ = ref_irs_prove_zk(ref, st0, acc, le, sf, rng, R, Q, seed, sblind_min)
+    assert len(want) > 0
+    zc = zk.zkm.ZkCtx(seed=seed, Q=Q, sblind_min=sblind_min)
+    T = irs_tables(zk, sf)
+    X = zk.zkm.commit_col(prover, zc, zk.p3.to_device(acc), R)
+    yo, L, iL, iY = prover.irs_witness(X.dev[:1 << le], sf, rng)
+    Y = zk.zkm.commit_col(prover, zc, yo, R)
+    assert [X.root, Y.root] == roots_ref
+    tr = zk.Transcript("irs-t")
+    pf = zk.zkm.irs_prove(prover, zc, tr, T, X, Y, (L, iL, iY), le, sf, rng, R, Q)
+    assert tr.state == st_ref and pf == want
+    ok, st = ref_irs_verify_zk(ref, st0, X.root, Y.root, le, sf, rng, R, Q, pf, sblind_min)
+    assert ok and st == tr.state

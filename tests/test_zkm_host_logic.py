@@ -5,7 +5,7 @@ import pytest
 
 from imm_helpers import matmul_instance
 from lu_helpers import _Arr
-from zkm_helpers import OracleZkEngine, ref_imm_verify_zk, ref_zk
+from zkm_helpers import OracleZkEngine, ref_imm_verify_zk, ref_irs_verify_zk, ref_zk
 
 GL_P = 0xFFFFFFFF00000001
 
@@ -60,3 +60,37 @@ def test_unlinked_y_mask_is_refused(orc, ref, zk):
     tr = zk.Transcript("imm-t")
     pf = zk.zkm.imm_prove(eng, zc, tr, X, W, Y, lj, lk, li, R, Q)
     assert not ref_imm_verify_zk(ref, zk.Transcript("imm-t").state, [X.root, W.root, Y.root], lj, lk, li, R, Q, pf)[0]
+
+
+def test_zprng_at_vectorised_matches_restatement(orc):
+    eng = OracleZkEngine(orc)
+    got = eng.zk_fill_at(0x1234567, 50, 7).a
+    assert [int(x) for x in got] == [orc.zprng_at(0x1234567, 7 + i) for i in range(50)]
+
+
+@pytest.mark.parametrize("le,sf,rng,sblind_min", [(4, 16, 2, 22), (5, 20, 2, 22), (3, 14, 2, 22), (4, 16, 0, 22), (5, 16, 2, 6)])
+def test_zk_rescale_accepted_by_reference_verifier(orc, ref, zk, le, sf, rng, sblind_min):
+    """Rescale in hiding mode: masked limb commitments, merged range lookups over mask-interleaved fraction trees, blinded
+    zero-check, blinded openings.  (The 2^20-row window table runs in the GPU suite; it takes a minute per case here.)"""
+    from irs_helpers import irs_tables, lift
+    R, Q = 1, 24
+    zkm = zk.zkm
+    eng = OracleZkEngine(orc)
+    zc = zkm.ZkCtx(seed=9, Q=Q, sblind_min=sblind_min)
+    r = np.random.default_rng(le + sf)
+    win = (1 << 19) if rng == 1 else (1 << 15)
+    acc = lift(r.integers(-(win - 2) << sf, (win - 2) << sf, 1 << le))
+    T = irs_tables(zk, sf)
+    X = zkm.commit_col(eng, zc, _Arr(acc), R)
+    yo, L, iL, iY = eng.irs_witness(_Arr(acc), sf, rng)
+    Y = zkm.commit_col(eng, zc, yo, R)
+    tr = zk.Transcript("irs-t")
+    pf = zkm.irs_prove(eng, zc, tr, T, X, Y, (L, iL, iY), le, sf, rng, R, Q)
+    st0 = zk.Transcript("irs-t").state
+    ok, st = ref_irs_verify_zk(ref, st0, X.root, Y.root, le, sf, rng, R, Q, pf, sblind_min)
+    assert ok and st == tr.state
+    assert not ref_irs_verify_zk(ref, st0, Y.root, X.root, le, sf, rng, R, Q, pf, sblind_min)[0]
+    for off in (40, len(pf) // 2, len(pf) - 60):
+        bad = bytearray(pf)
+        bad[off] ^= 1
+        assert not ref_irs_verify_zk(ref, st0, X.root, Y.root, le, sf, rng, R, Q, bytes(bad), sblind_min)[0]

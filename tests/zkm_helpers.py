@@ -32,6 +32,24 @@ class OracleZkEngine(OracleGadgetEngine):
     def download(self, col):
         return col.a
 
+    def zk_fill_at(self, seed, n, i0=0):
+        """p3zkc::zprng_at stream, vectorised (checked against the C restatement in the tests)."""
+        with np.errstate(over="ignore"):
+            z = np.uint64(seed) + np.uint64(0x9E3779B97F4A7C15) * (np.arange(i0, i0 + n, dtype=np.uint64) + np.uint64(1))
+            z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+            z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+            z ^= z >> np.uint64(31)
+        return _Arr(z % np.uint64(GL_P))
+
+    def interleave(self, a, b):
+        return _Arr(np.stack([a.a, b.a], axis=1).reshape(-1))
+
+    def zeros(self, n):
+        return _Arr(np.zeros(n, dtype=np.uint64))
+
+    def set_element(self, col, i, value):
+        col.a[i] = np.uint64(int(value) % GL_P)
+
     def gather_fn(self, col, n, fn):
         return _Arr(col.a[fn(np.arange(n, dtype=np.int64))])
 
@@ -113,3 +131,31 @@ def ref_imm_prove_zk(ref, st, X, W, lj, lk, li, R, Q, seed, sblind_min=22):
           C.c_uint32(R), C.c_uint32(Q), C.c_uint64(seed), C.c_uint32(sblind_min), out, C.c_size_t(cap), roots, C.byref(ms))
     rb = bytes(roots)
     return bytes(out[:n]), bytes(s), [rb[0:32], rb[32:64], rb[64:96]], ms.value
+
+
+def ref_irs_verify_zk(ref, st, rootX, rootY, le, sf, rng, R, Q, proof, sblind_min=22):
+    """p3irs::verify with the reference's zk switch on."""
+    ref_zk(ref, True, Q, 1, sblind_min)
+    try:
+        s = (C.c_uint8 * 32)(*st)
+        ok = ref.lib.ref_irs_verify(s, rootX, rootY, C.c_uint32(le), C.c_uint32(sf), C.c_int(rng), C.c_uint32(R),
+                                    C.c_uint32(Q), bytes(proof), C.c_size_t(len(proof)))
+    finally:
+        ref_zk(ref, False)
+    return bool(ok), bytes(s)
+
+
+def ref_irs_prove_zk(ref, st, acc, le, sf, rng, R, Q, seed, sblind_min=22):
+    """The reference's zk rescale prover (GPU): returns (proof bytes, state, roots X Y, ms)."""
+    s = (C.c_uint8 * 32)(*st)
+    cap = 256 << 20
+    out = (C.c_uint8 * cap)()
+    roots = (C.c_uint8 * 64)()
+    ms = C.c_double(0)
+    f = ref.lib.ref_irs_prove_zk
+    f.restype = C.c_size_t
+    a = np.ascontiguousarray(acc, dtype=np.uint64)
+    n = f(s, a.ctypes.data_as(C.c_void_p), C.c_uint32(le), C.c_uint32(sf), C.c_int(rng), C.c_uint32(R), C.c_uint32(Q),
+          C.c_uint64(seed), C.c_uint32(sblind_min), out, C.c_size_t(cap), roots, C.byref(ms))
+    rb = bytes(roots)
+    return bytes(out[:n]), bytes(s), [rb[0:32], rb[32:64]], ms.value

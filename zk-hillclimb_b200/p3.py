@@ -453,6 +453,19 @@ class Prover:
     def download(self, col):
         return to_host(col)
 
+    def interleave(self, a, b):
+        """out[2x] = a[x], out[2x+1] = b[x]: sibling-interleaved leaves of the hiding mode's fraction trees."""
+        import torch
+        return torch.stack([a, b], dim=1).reshape(-1).contiguous()
+
+    def zeros(self, n):
+        import torch
+        return torch.zeros(n, dtype=torch.int64, device="cuda:%d" % self.device)
+
+    def set_element(self, col, i, value):
+        value = int(value) % GL_P
+        col[i] = value - (1 << 64) if value >= (1 << 63) else value
+
     def flip_bit(self, col, b):
         """out[u] = col[u ^ (1 << b)]: the rotate-half permutation of RoPE (zkllm-src/p3_int_gadgets.cuh:1297-1298)."""
         return col.view(-1, 2, 1 << b).flip(1).reshape(-1).contiguous()

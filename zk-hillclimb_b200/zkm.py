@@ -305,3 +305,210 @@ def imm_prove(engine, zc, tr, X, W, Y, lj, lk, li, R, Q, ledger=None):
     batches = tail_prove(engine, zc, tr, ledger, R, Q, "imm-bo") if own else []
     out += struct.pack("<I", len(batches)) + b"".join(struct.pack("<I", len(b)) + b for b in batches)
     return out
+
+
+# ---------------------------------------------------------------------------------- merged lookups in hiding mode
+def _virt(col):
+    return not isinstance(col, ZCol)
+
+
+def _dev(col):
+    return col if _virt(col) else col.dev
+
+
+def prove_super(engine, zc, tr, table_cols, table_id, subgroups, R, ledger, strict=True):
+    """p3lu::prove_super with the zk switch on (zkllm-src/p3_logup.cuh:1357-1881): one merged logUp instance per table over
+    GKR fraction trees whose leaves are sibling-interleaved with committed uniform mask leaves.
+
+    subgroups: [(n, members)] in flush order; a member is (cols, idx[, bind]) with c AUGMENTED columns of 2^(n + e_of(n))
+    entries (ZCol when committed, a plain engine column when virtual) and 2^n row indices; bind(tr, ledger, pm, y_virt)
+    returns the values that ride in the proof.  Per subgroup two mask streams pm = sm * qm and qm are committed (salted, not
+    augmented) before gamma / beta; the table side's last mask fraction is fixed so that the junk cancels.  The claims go to
+    ``ledger`` in the reference's order.  Returns (proof bytes, committed multiplicity column).
+    Serialised GroupProof: u32 m, c, ns | root_cnt | rt_pmT rt_qmT | gkT | per subgroup: u32 n, k | rt_pm rt_qm | gk |
+    per member: u32 nW, yW.., u32 nV, y_virt.., u32 nX, extra.."""
+    from .p3 import col_sum
+    c = len(table_cols)
+    M = int(table_cols[0].numel())
+    m = M.bit_length() - 1
+    tr.absorb("lug-tab", table_id)
+    tr.absorb("lug-sdims", struct.pack("<III", len(subgroups), m, c))
+    pad_rows, idx_all = 0, []
+    for n, members in subgroups:
+        k = len(members)
+        g = (k - 1).bit_length()
+        NA = 1 << zc.vfull(n)
+        tr.absorb("lug-dims", struct.pack("<IIII", n, g, k, c))
+        for cols, idx, *_ in members:
+            if len(cols) != c or any(int(_dev(t).numel()) != NA for t in cols) or int(idx.numel()) != (1 << n):
+                raise ValueError("p3lu: group member size")
+            for t in cols:
+                if _virt(t):
+                    tr.absorb("lug-Wv", b"virt")
+                else:
+                    tr.absorb("lug-W", t.root)
+            idx_all.append(idx)
+        pad_rows += ((1 << g) - k) << n
+    cnt = engine.lu_counts(idx_all, M, pad_rows)
+    Ccnt = commit_col(engine, zc, cnt, R)
+    tr.absorb("lug-cnt", Ccnt.root)
+    # mask-leaf streams of every subgroup, then of the table side, all committed before gamma / beta
+    masks, SmA = [], 0
+    for n, members in subgroups:
+        g = (len(members) - 1).bit_length()
+        NM = 1 << (n + g + zc.e_of(n))
+        pseed, qseed = zc.next_seed(), zc.next_seed()
+        sm, qm = engine.zk_fill_at(pseed, NM), engine.zk_fill_at(qseed, NM)
+        SmA = (SmA + col_sum(engine, sm)) % GL_P
+        sP = zc.next_seed()
+        pm_ = engine.mul(sm, qm)
+        PM = ZCol(pm_, engine.commit_salted(pm_, R, sP), n + g + zc.e_of(n), sP)
+        sQ = zc.next_seed()
+        QM = ZCol(qm, engine.commit_salted(qm, R, sQ), n + g + zc.e_of(n), sQ)
+        tr.absorb("lug-pm", PM.root)
+        tr.absorb("lug-qm", QM.root)
+        masks.append((PM, QM))
+    MT = 1 << zc.vfull(m)
+    pseedT, qseedT = zc.next_seed(), zc.next_seed()
+    smT, qmT = engine.zk_fill_at(pseedT, MT), engine.zk_fill_at(qseedT, MT)
+    Smcnt = (col_sum(engine, Ccnt.dev) - col_sum(engine, cnt)) % GL_P
+    part = (col_sum(engine, smT) - engine.element(smT, MT - 1)) % GL_P
+    pmT = engine.mul(smT, qmT)
+    engine.set_element(pmT, MT - 1, (SmA - Smcnt - part) % GL_P * engine.element(qmT, MT - 1) % GL_P)
+    sP = zc.next_seed()
+    PMT = ZCol(pmT, engine.commit_salted(pmT, R, sP), m + zc.e_of(m), sP)
+    sQ = zc.next_seed()
+    QMT = ZCol(qmT, engine.commit_salted(qmT, R, sQ), m + zc.e_of(m), sQ)
+    tr.absorb("lug-pmT", PMT.root)
+    tr.absorb("lug-qmT", QMT.root)
+    gamma, beta = tr.chal(), tr.chal()
+    gp = [pow(gamma, t, GL_P) for t in range(c)]
+    a0 = sum(g_ * int(engine.element(col, 0)) for g_, col in zip(gp, table_cols)) % GL_P
+    accP, accQ = 0, 1
+    subs = []
+    for (n, members), (PM, QM) in zip(subgroups, masks):
+        k = len(members)
+        g = (k - 1).bit_length()
+        E = zc.e_of(n)
+        NR, NM, N = 1 << (n + g), 1 << (n + g + E), 1 << n
+        # even leaves: numerator 1 on the real rows, 0 on the witness-mask rows; denominator A + beta on every slice
+        evenQ = engine.concat([engine.lu_leaf_denominators([[engine.slice(_dev(t), ex << n, N) for t in mb[0]] for mb in members],
+                                                           1 << g, n, gamma, beta, (a0 + beta) % GL_P) for ex in range(1 << E)])
+        evenP = engine.concat([engine.lu_ones(NR), engine.zeros(NM - NR)])
+        gk, rA, _ = engine.gkr_prove(tr, "lug-gA", engine.interleave(evenP, PM.dev), engine.interleave(evenQ, QM.dev), False)
+        P, Q = (int(x) for x in np.frombuffer(gk[:16], dtype=np.uint64))
+        accP, accQ = (accP * Q + P * accQ) % GL_P, accQ * Q % GL_P
+        _p0, p1, _q0, q1 = (int(x) for x in np.frombuffer(gk[-32:], dtype=np.uint64))
+        rA = [int(x) for x in rA]
+        ledger.add(PM, rA, p1)
+        ledger.add(QM, rA, q1)
+        pm = rA[:n] + rA[n + g:]
+        pma = np.array(pm, dtype=np.uint64)
+        mem = []
+        for cols, idx, *bind in members:
+            yW, yv = [], []
+            for t in cols:
+                y = engine.eval_h_gpu(_dev(t), pma)
+                if _virt(t):
+                    yv.append(y)
+                    tr.absorb("lug-yv", struct.pack("<Q", y))
+                else:
+                    yW.append(y)
+                    tr.absorb("lug-yW", struct.pack("<Q", y))
+                    ledger.add(t, pm, y)
+            extra = bind[0](tr, ledger, pm, yv) if bind and bind[0] is not None else []
+            mem.append((yW, yv, extra))
+        subs.append((n, k, PM.root + QM.root, gk, mem))
+    evenQ = engine.concat([engine.affine(table_cols, gamma, beta), engine.lu_ones(MT - M)]) if MT > M else engine.affine(table_cols, gamma, beta)
+    gkT, rT, _ = engine.gkr_prove(tr, "lug-gT", engine.interleave(Ccnt.dev, PMT.dev), engine.interleave(evenQ, QMT.dev), False)
+    PT, QT = (int(x) for x in np.frombuffer(gkT[:16], dtype=np.uint64))
+    if strict and accP * QT % GL_P != PT * accQ % GL_P:
+        raise ValueError("p3lu: witness not in table")
+    p0, p1, _q0, q1 = (int(x) for x in np.frombuffer(gkT[-32:], dtype=np.uint64))
+    rT = [int(x) for x in rT]
+    ledger.add(Ccnt, rT, p0)
+    ledger.add(PMT, rT, p1)
+    ledger.add(QMT, rT, q1)
+    out = struct.pack("<III", m, c, len(subs)) + Ccnt.root + PMT.root + QMT.root + gkT
+    for n, k, rts, gk, mem in subs:
+        out += struct.pack("<II", n, k) + rts + gk
+        for yW, yv, extra in mem:
+            for vals in (yW, yv, extra):
+                out += struct.pack("<I", len(vals)) + np.array(vals, dtype=np.uint64).tobytes()
+    return out, Ccnt
+
+
+def lu_flush(engine, zc, tr, luq, ledger, R, strict=True):
+    """p3lu::lu_flush (zkllm-src/p3_logup.cuh:1883-1956) over queued obligations {"W": augmented columns, "idx", "tab", "bind"}:
+    groups by (table, log-rows) in first-appearance order, chunks of 2^(25 - n) members, bundles by table, one prove_super
+    per table.  The table columns are uploaded once per flush."""
+    from .p3 import LU_GCAP, table_columns
+    groups = []                                       # [table id, n, [queue index]]
+    for i, o in enumerate(luq):
+        n = int(o["idx"].numel()).bit_length() - 1
+        for grp in groups:
+            if grp[0] == o["tab"]["id"] and grp[1] == n:
+                grp[2].append(i)
+                break
+        else:
+            groups.append([o["tab"]["id"], n, [i]])
+    chunks = []
+    for tid, n, mem in groups:
+        cap = 1 if n >= LU_GCAP else 1 << (LU_GCAP - n)
+        for off in range(0, len(mem), cap):
+            chunks.append((tid, n, mem[off:off + cap]))
+    supers = []
+    for tid, n, mem in chunks:
+        for sp in supers:
+            if sp[0] == tid:
+                sp[1].append((n, mem))
+                break
+        else:
+            supers.append((tid, [(n, mem)]))
+    out = []
+    for tid, sgs in supers:
+        tab = luq[sgs[0][1][0]]["tab"]
+        subgroups = [(n, [(luq[j]["W"], luq[j]["idx"], luq[j].get("bind")) for j in mem]) for n, mem in sgs]
+        pf, _ = prove_super(engine, zc, tr, table_columns(engine, tab), tab["id"], subgroups, R, ledger, strict)
+        out.append(pf)
+    del luq[:]
+    return out
+
+
+def irs_prove(engine, zc, tr, tables, X, Y, wit, le, sf, rng, R, Q, ledger=None, luq=None, tag="irs"):
+    """p3irs::prove with the zk switch on (zkllm-src/p3_int_gadgets.cuh:282-340): y = round(x / 2^sf) through committed limb
+    columns, range lookups on the limbs and on y, and the blinded zero-check of x + 2^(sf-1) - y 2^sf - L0 - 2^16 L1.
+    X, Y: ZCol; wit: (limb columns, limb index columns, index column of y or None) as Prover.irs_witness returns them.
+    Serialised: u32 le, sf, nl, rng | limb roots | messages vfull(le) * 40 | yX yY yL.. | Blind | standalone: u32 groups
+    (u32 length + GroupProof)*, u32 batches (u32 length + BatchProof)*."""
+    own = ledger is None
+    if own:
+        ledger, luq = ZLedger(), []
+    L, iL, iY = wit
+    nl = len(L)
+    tr.absorb("irs-dims", struct.pack("<IIII", le, sf, nl, rng))
+    tr.absorb("irs-X", X.root)
+    tr.absorb("irs-Y", Y.root)
+    CL = []
+    for l in range(nl):
+        CL.append(commit_col(engine, zc, L[l], R))
+        tr.absorb("irs-L", CL[l].root)
+    limb_tab = lambda l: (tables["R14"] if sf == 14 else tables["R16"]) if l == 0 else (tables["R16"] if sf == 32 else tables["RTOP"])
+    for l in range(nl):
+        luq.append({"W": [CL[l]], "idx": iL[l], "tab": limb_tab(l)})
+    if rng:
+        luq.append({"W": [Y], "idx": iY, "tab": tables["RS20"] if rng == 1 else tables["RS16"]})
+    zE = [tr.chal() for _ in range(le)]
+    H, P2 = 1 << (sf - 1), 1 << sf
+    cols = [engine.build_eq_gpu(np.array(zpt(zc, zE), dtype=np.uint64)), X.dev, Y.dev] + [c.dev for c in CL]
+    terms = [(1, (1,)), (GL_P - P2, (2,)), (GL_P - 1, (3,))] + ([(GL_P - 65536, (4,))] if nl == 2 else [])
+    r, msgs, _, blind = sc5z(engine, zc, tr, "irs-sc", le, cols, terms, H, R, ledger)
+    ys = [claimc(engine, tr, ledger, col, r) for col in [X, Y] + CL]
+    out = struct.pack("<IIII", le, sf, nl, rng) + b"".join(c.root for c in CL)
+    out += np.ascontiguousarray(msgs, dtype=np.uint64).tobytes() + struct.pack("<%dQ" % len(ys), *ys) + blind
+    if own:
+        lug = lu_flush(engine, zc, tr, luq, ledger, R)
+        batches = tail_prove(engine, zc, tr, ledger, R, Q, "irs-bo")
+        blob = lambda bs: struct.pack("<I", len(bs)) + b"".join(struct.pack("<I", len(b)) + b for b in bs)
+        out += blob(lug) + blob(batches)
+    return out
