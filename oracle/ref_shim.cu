@@ -470,6 +470,7 @@ size_t iadd_serialize(const p3iadd::Proof& pf, uint8_t* out, size_t cap) {
     app(&pf.le, 4);
     for (auto& m : pf.m) app(&m, 40);
     app(&pf.yA, 8); app(&pf.yB, 8); app(&pf.yO, 8);
+    if (p3zkc::G.on) blind_serialize(pf.bl, b);
     tail_append(pf.tail, b);
     return emit(b, out, cap);
 }
@@ -477,10 +478,11 @@ bool iadd_deserialize(const uint8_t* in, size_t len, p3iadd::Proof& pf) {
     const uint8_t* p = in; const uint8_t* end = in + len;
     if (len < 4) return false;
     memcpy(&pf.le, p, 4); p += 4;
-    if (pf.le > 40 || (size_t)(end - p) < (size_t)pf.le * 40 + 24) return false;
-    pf.m.resize(pf.le);
+    if (pf.le > 40 || (size_t)(end - p) < (size_t)p3zkc::vfull(pf.le) * 40 + 24) return false;
+    pf.m.resize(p3zkc::vfull(pf.le));
     for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
     memcpy(&pf.yA, p, 8); memcpy(&pf.yB, p + 8, 8); memcpy(&pf.yO, p + 16, 8); p += 24;
+    if (p3zkc::G.on && !blind_deserialize(p, end, pf.bl)) return false;
     return tail_parse(p, end, pf.tail) && p == end;
 }
 // p3iswg::Proof <-> bytes: u32 le | rSIL rREM | messages le*40 | ySIL yU yM yR | tail
@@ -490,6 +492,7 @@ size_t iswg_serialize(const p3iswg::Proof& pf, uint8_t* out, size_t cap) {
     app(&pf.le, 4); app(pf.rSIL.data(), 32); app(pf.rREM.data(), 32);
     for (auto& m : pf.m) app(&m, 40);
     app(&pf.ySIL, 8); app(&pf.yU, 8); app(&pf.yM, 8); app(&pf.yR, 8);
+    if (p3zkc::G.on) blind_serialize(pf.bl, b);
     tail_append(pf.tail, b);
     return emit(b, out, cap);
 }
@@ -497,10 +500,11 @@ bool iswg_deserialize(const uint8_t* in, size_t len, p3iswg::Proof& pf) {
     const uint8_t* p = in; const uint8_t* end = in + len;
     if (len < 68) return false;
     memcpy(&pf.le, p, 4); memcpy(pf.rSIL.data(), p + 4, 32); memcpy(pf.rREM.data(), p + 36, 32); p += 68;
-    if (pf.le > 40 || (size_t)(end - p) < (size_t)pf.le * 40 + 32) return false;
-    pf.m.resize(pf.le);
+    if (pf.le > 40 || (size_t)(end - p) < (size_t)p3zkc::vfull(pf.le) * 40 + 32) return false;
+    pf.m.resize(p3zkc::vfull(pf.le));
     for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
     memcpy(&pf.ySIL, p, 8); memcpy(&pf.yU, p + 8, 8); memcpy(&pf.yM, p + 16, 8); memcpy(&pf.yR, p + 24, 8); p += 32;
+    if (p3zkc::G.on && !blind_deserialize(p, end, pf.bl)) return false;
     return tail_parse(p, end, pf.tail) && p == end;
 }
 // p3irope::Proof <-> bytes: u32 lT, ld, fb | rREM | messages (lT+ld)*40 | yQ yQx yY yR | tail

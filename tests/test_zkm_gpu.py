@@ -5,7 +5,7 @@ import pytest
 
 from imm_helpers import matmul_instance
 from lu_helpers import _Arr
-from zkm_helpers import OracleZkEngine, ref_imm_prove_zk, ref_imm_verify_zk, ref_irs_prove_zk, ref_irs_verify_zk
+from zkm_helpers import ref_zk, OracleZkEngine, ref_imm_prove_zk, ref_imm_verify_zk, ref_irs_prove_zk, ref_irs_verify_zk
 
 pytestmark = pytest.mark.gpu
 GL_P = 0xFFFFFFFF00000001
@@ -116,3 +116,49 @@ def test_zk_rescale_equals_reference_prover(orc, ref, zk, prover, le, sf, rng, s
     assert tr.state == st_ref and pf == want
     ok, st = ref_irs_verify_zk(ref, st0, X.root, Y.root, le, sf, rng, R, Q, pf, sblind_min)
     assert ok and st == tr.state
+
+
+def _ref_verify3_zk(ref, name, st, roots, le, R, Q, proof):
+    from ig_helpers import ref_verify3
+    ref_zk(ref, True, Q, 1, 22)
+    try:
+        return ref_verify3(ref, name, st, roots, le, R, Q, proof)
+    finally:
+        ref_zk(ref, False)
+
+
+def test_zk_residual_add_and_swiglu_accepted_by_reference_verifier(orc, ref, zk, prover):
+    """p3iadd and p3iswg in hiding mode (blinded zero-check + merged lookups into the 2^20-row window and SILU tables); the
+    same host logic runs on the CPU engine in minutes, so it lives in the GPU suite."""
+    from ig_helpers import ref_table
+    from irs_helpers import lift
+    import torch
+    R, Q, le = 1, 24, 6
+    _dev32 = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int32)).cuda()
+    zkm, ig = zk.zkm, zk.ig
+    eng, _Arr = prover, zk.p3.to_device
+    T = ig.build_tables(zk.load_library(), 64, 12)
+    r = np.random.default_rng(3)
+    a, b = r.integers(-(1 << 17), 1 << 17, 1 << le), r.integers(-(1 << 17), 1 << 17, 1 << le)
+    zc = zkm.ZkCtx(seed=21, Q=Q)
+    A, B = zkm.commit_col(eng, zc, _Arr(lift(a)), R), zkm.commit_col(eng, zc, _Arr(lift(b)), R)
+    OUT = zkm.commit_col(eng, zc, _Arr(lift(a + b)), R)
+    tr = zk.Transcript("iad-t")
+    pf = zkm.iadd_prove(eng, zc, tr, T, A, B, OUT, _dev32((a + b + ig.ABND).astype(np.uint32)), le, R, Q)
+    st0 = zk.Transcript("iad-t").state
+    ok, st = _ref_verify3_zk(ref, "ref_iadd_verify", st0, [A.root, B.root, OUT.root], le, R, Q, pf)
+    assert ok and st == tr.state
+    assert not _ref_verify3_zk(ref, "ref_iadd_verify", st0, [B.root, A.root, OUT.root], le, R, Q, pf)[0]
+    # SwiGLU product
+    g, u = lift(r.integers(-(1 << 18), 1 << 18, 1 << le)), lift(r.integers(-(1 << 17), 1 << 17, 1 << le))
+    sil, rem, mo, idxG, idxR, idxM = ig.iswg_witness(g, u, T)
+    zc = zkm.ZkCtx(seed=22, Q=Q)
+    G, U, MO = (zkm.commit_col(eng, zc, _Arr(x), R) for x in (g, u, mo))
+    tr = zk.Transcript("isw-t")
+    pf = zkm.iswg_prove(eng, zc, tr, T, G, U, MO, (_Arr(sil), _Arr(rem), _dev32(idxG), _dev32(idxR), _dev32(idxM)), le, R, Q)
+    st0 = zk.Transcript("isw-t").state
+    ok, st = _ref_verify3_zk(ref, "ref_iswg_verify", st0, [G.root, U.root, MO.root], le, R, Q, pf)
+    assert ok and st == tr.state
+    bad = bytearray(pf)
+    bad[len(pf) // 2] ^= 1
+    assert not _ref_verify3_zk(ref, "ref_iswg_verify", st0, [G.root, U.root, MO.root], le, R, Q, bytes(bad))[0]

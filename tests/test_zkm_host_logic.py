@@ -94,3 +94,4 @@ def test_zk_rescale_accepted_by_reference_verifier(orc, ref, zk, le, sf, rng, sb
         bad = bytearray(pf)
         bad[off] ^= 1
         assert not ref_irs_verify_zk(ref, st0, X.root, Y.root, le, sf, rng, R, Q, bytes(bad), sblind_min)[0]
+

@@ -8,6 +8,8 @@
   sc5z                   Libra-blinded quartic sumcheck             zkllm-src/p3_hawkeye.cuh:1035-1351
   prove_class / tail_prove   class blinder + salted openings        zkllm-src/p3_batchopen.cuh:315-384, :969-1131
   imm_prove              p3imm::prove with the zk switch on         zkllm-src/p3_int_gadgets.cuh:510-605
+  prove_super / lu_flush p3lu::prove_super / lu_flush, zk branches  zkllm-src/p3_logup.cuh:1357-1956
+  irs_prove / iadd_prove / iswg_prove   p3irs / p3iadd / p3iswg::prove with the zk switch on   p3_int_gadgets.cuh:282-340, :712-737, :1790-1832
 
 Every random draw follows the reference's order (one counter-mode seed per draw, zkllm-src/p3_zkc.cuh:118-123), so with
 the same master seed the proofs are the reference prover's bytes.  The device work is the library's: mask and blind
@@ -507,8 +509,66 @@ def irs_prove(engine, zc, tr, tables, X, Y, wit, le, sf, rng, R, Q, ledger=None,
     out = struct.pack("<IIII", le, sf, nl, rng) + b"".join(c.root for c in CL)
     out += np.ascontiguousarray(msgs, dtype=np.uint64).tobytes() + struct.pack("<%dQ" % len(ys), *ys) + blind
     if own:
-        lug = lu_flush(engine, zc, tr, luq, ledger, R)
-        batches = tail_prove(engine, zc, tr, ledger, R, Q, "irs-bo")
-        blob = lambda bs: struct.pack("<I", len(bs)) + b"".join(struct.pack("<I", len(b)) + b for b in bs)
-        out += blob(lug) + blob(batches)
+        out += _tail(engine, zc, tr, luq, ledger, R, Q, "irs-bo")
     return out
+
+
+def _tail(engine, zc, tr, luq, ledger, R, Q, tag):
+    """p3ig::tail_prove: the lookup flush, then one blinded batched opening per size class; serialised as u32 groups (u32 length
+    + GroupProof)*, u32 batches (u32 length + BatchProof)*."""
+    lug = lu_flush(engine, zc, tr, luq, ledger, R)
+    batches = tail_prove(engine, zc, tr, ledger, R, Q, tag)
+    blob = lambda bs: struct.pack("<I", len(bs)) + b"".join(struct.pack("<I", len(b)) + b for b in bs)
+    return blob(lug) + blob(batches)
+
+
+_EMPTY_TAIL = struct.pack("<II", 0, 0)
+
+
+def iadd_prove(engine, zc, tr, tables, A, B, OUT, idxO, le, R, Q, ledger=None, luq=None):
+    """p3iadd::prove with the zk switch on (zkllm-src/p3_int_gadgets.cuh:712-737): OUT = A + B through one blinded zero-check
+    and the signed range lookup on OUT.  A, B, OUT: ZCol.  Serialised: u32 le | messages vfull(le)*40 | yA yB yO | Blind | tail."""
+    own = ledger is None
+    if own:
+        ledger, luq = ZLedger(), []
+    tr.absorb("iad-dims", struct.pack("<I", le))
+    tr.absorb("iad-A", A.root)
+    tr.absorb("iad-B", B.root)
+    tr.absorb("iad-O", OUT.root)
+    luq.append({"W": [OUT], "idx": idxO, "tab": tables["RS20"]})
+    zE = [tr.chal() for _ in range(le)]
+    cols = [engine.build_eq_gpu(np.array(zpt(zc, zE), dtype=np.uint64)), A.dev, B.dev, OUT.dev]
+    r, msgs, _, blind = sc5z(engine, zc, tr, "iad-sc", le, cols, [(1, (1,)), (1, (2,)), (GL_P - 1, (3,))], 0, R, ledger)
+    ys = [claimc(engine, tr, ledger, col, r) for col in (A, B, OUT)]
+    out = struct.pack("<I", le) + np.ascontiguousarray(msgs, dtype=np.uint64).tobytes() + struct.pack("<QQQ", *ys) + blind
+    return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "iad-bo") if own else _EMPTY_TAIL)
+
+
+def iswg_prove(engine, zc, tr, tables, G, U, MO, wit, le, R, Q, ledger=None, luq=None):
+    """p3iswg::prove with the zk switch on (zkllm-src/p3_int_gadgets.cuh:1790-1832): MO = round(SILU[G] * U / 2^16) through the
+    committed SILU values and remainders, the two-column SILU lookup, two range lookups and one blinded zero-check.
+    G, U, MO: ZCol; wit = (sil, rem, idxG, idxR, idxM).  Serialised: u32 le | rSIL rREM | messages vfull(le)*40 |
+    ySIL yU yM yR | Blind | tail."""
+    own = ledger is None
+    if own:
+        ledger, luq = ZLedger(), []
+    sil, rem, idxG, idxR, idxM = wit
+    tr.absorb("isw-dims", struct.pack("<I", le))
+    tr.absorb("isw-G", G.root)
+    tr.absorb("isw-U", U.root)
+    tr.absorb("isw-M", MO.root)
+    SIL = commit_col(engine, zc, sil, R)
+    REM = commit_col(engine, zc, rem, R)
+    tr.absorb("isw-s", SIL.root)
+    tr.absorb("isw-r", REM.root)
+    luq.append({"W": [G, SIL], "idx": idxG, "tab": tables["SILU"]})
+    luq.append({"W": [REM], "idx": idxR, "tab": tables["R16"]})
+    luq.append({"W": [MO], "idx": idxM, "tab": tables["RS20"]})
+    zE = [tr.chal() for _ in range(le)]
+    cols = [engine.build_eq_gpu(np.array(zpt(zc, zE), dtype=np.uint64)), SIL.dev, U.dev, MO.dev, REM.dev]
+    terms = [(1, (1, 2)), (GL_P - 65536, (3,)), (GL_P - 1, (4,))]
+    r, msgs, _, blind = sc5z(engine, zc, tr, "isw-sc", le, cols, terms, 32768, R, ledger)
+    ys = [claimc(engine, tr, ledger, col, r) for col in (SIL, U, MO, REM)]
+    out = struct.pack("<I", le) + SIL.root + REM.root + np.ascontiguousarray(msgs, dtype=np.uint64).tobytes()
+    out += struct.pack("<QQQQ", *ys) + blind
+    return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "isw-bo") if own else _EMPTY_TAIL)
