@@ -182,6 +182,83 @@ class Prover {
         return out;
     }
 
+    // ---- hiding mode (the reference's zk switch): engine calls under p3zkc / sc5z / the zk branches of prove_class ----
+    // p3zkc::salted_commit_root_dev (zkllm-src/p3_zkc.cuh:357-397)
+    Hash commit_salted(const DevCol& c, uint32_t R, uint64_t sseed) {
+        uint32_t v = 0;
+        while (((size_t)1 << v) < c.size()) v++;
+        Hash h;
+        ck(zkh_basefold_commit_salted(ctx_, c.data(), v, R, sseed, nullptr, nullptr, h.data()));
+        return h;
+    }
+    // p3zkc::zprng_fill chain / zprng_at stream on the device (zkllm-src/p3_zkc.cuh:100-117, :464-534)
+    DevCol zk_fill_chain(uint64_t s0, size_t n, uint64_t k0 = 0) {
+        DevCol out(*this, n);
+        ck(zkh_zk_fill_chain(ctx_, s0, k0, n, out.data()));
+        return out;
+    }
+    DevCol zk_fill_at(uint64_t seed, size_t n, uint64_t i0 = 0) {
+        DevCol out(*this, n);
+        ck(zkh_zk_fill_at(ctx_, seed, i0, n, out.data()));
+        return out;
+    }
+    // [real | mask slices from the chain of mask_seed]: p3zkc::augment over a fresh mask (zkllm-src/p3_zkc.cuh:158-177)
+    DevCol zk_augment(const DevCol& c, uint32_t e, uint64_t mask_seed) {
+        uint32_t v = 0;
+        while (((size_t)1 << v) < c.size()) v++;
+        DevCol out(*this, (size_t)1 << (v + e));
+        ck(zkh_zk_augment(ctx_, c.data(), v, e, mask_seed, out.data()));
+        return out;
+    }
+    // the blinded chain of p3hwl::sc5z, structured layout (zkllm-src/p3_hawkeye.cuh:1092-1110, :1329-1331): terms may carry a
+    // third field "outside the col0 factor"; fix = 7 words per round (g_rd coefficients, A_rd, B_rd); returns r, g(r) in pref
+    struct ZTerm { gl_t coef; std::vector<uint8_t> idx; bool outside = false; };
+    std::vector<gl_t> sc_prove_zc_blind(Transcript& tr, const char* tag, const std::vector<const gl_t*>& d_cols, uint32_t N,
+                                        const std::vector<ZTerm>& terms, gl_t konst, const std::vector<gl_t>& fix,
+                                        std::vector<gl_t>& msgs, std::vector<gl_t>& finals, gl_t& pref) {
+        uint32_t logn = 0;
+        while ((1u << logn) < N) logn++;
+        std::vector<uint64_t> prog = {terms.size(), konst};
+        for (auto& t : terms) {
+            uint64_t pk = t.idx.size() | (t.outside ? 0x80u : 0u);
+            for (size_t k = 0; k < t.idx.size(); k++) pk |= (uint64_t)t.idx[k] << (8 + 8 * k);
+            prog.push_back(t.coef);
+            prog.push_back(pk);
+        }
+        std::vector<gl_t> r(logn), m((size_t)logn * 5);
+        finals.assign(d_cols.size(), 0);
+        if (fix.empty())
+            ck(zkh_sumcheck_zerocheck(ctx_, d_cols.data(), (int)d_cols.size(), logn, prog.data(), (int)prog.size(), tag, tr.state,
+                                      m.data(), r.data(), finals.data()));
+        else
+            ck(zkh_sumcheck_zerocheck_blind(ctx_, d_cols.data(), (int)d_cols.size(), logn, prog.data(), (int)prog.size(), fix.data(),
+                                            tag, tr.state, m.data(), r.data(), finals.data(), &pref));
+        msgs.insert(msgs.end(), m.begin(), m.end());
+        return r;
+    }
+    // p3bo::prove_class after the class blinder was appended, salted round-0 openings (zkllm-src/p3_batchopen.cuh:969-1131)
+    std::vector<uint8_t> prove_class_salted(Transcript& tr, const std::vector<std::vector<gl_t>>& pts, const std::vector<Entry>& ents,
+                                            const std::vector<uint64_t>& sseeds, uint32_t R, uint32_t Q, const std::string& label) {
+        const uint32_t T = (uint32_t)pts.size(), v = (uint32_t)pts[0].size(), k = (uint32_t)ents.size();
+        if (sseeds.size() != k) throw std::runtime_error("zkh: one salt seed per ledger entry");
+        std::vector<gl_t> flat;
+        for (auto& p : pts) flat.insert(flat.end(), p.begin(), p.end());
+        std::vector<const gl_t*> cols(k);
+        std::vector<uint8_t> roots((size_t)k * 32);
+        std::vector<uint32_t> zid(k);
+        for (uint32_t j = 0; j < k; j++) {
+            cols[j] = ents[j].col->data();
+            memcpy(&roots[(size_t)j * 32], ents[j].root.data(), 32);
+            zid[j] = ents[j].zid;
+        }
+        std::vector<uint8_t> out(zkh_batchopen_proof_bound(v, R, Q, k) + (size_t)k * 2 * Q * 32);
+        size_t wr = 0;
+        ck(zkh_batchopen_prove_class_salted(ctx_, v, flat.data(), T, cols.data(), roots.data(), zid.data(), sseeds.data(), k, R, Q,
+                                            label.c_str(), tr.state, out.data(), out.size(), &wr, nullptr, nullptr));
+        out.resize(wr);
+        return out;
+    }
+
   private:
     zkh_ctx* ctx_ = nullptr;
 };
