@@ -744,6 +744,10 @@ def sc_prove_sharded(engine, tr, tag, dcols, functor, nt, dist=None, par=(), gro
     engine.shard_begin(functor, nt, dcols, logn, par, tag, tr.state)
     fin, gfin = engine.new_buffer(nc), engine.new_buffer(G * nc)
     if G > 1 and getattr(engine, "p2p_ready", False):
+        # the waits inside the fused rounds are bounded (about a second): meet on the host first, inputs complete, so that they
+        # only have to cover kernel skew and not whatever each rank did before (staging copies, page pinning, allocation)
+        engine.sync()
+        dist.barrier(group=group)
         engine.shard_local_fused(fin)              # one kernel per round, sums cross NVLink as peer stores
     else:
         sums, gathered = engine.new_buffer(nt), engine.new_buffer(G * nt)
