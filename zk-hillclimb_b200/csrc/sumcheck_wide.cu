@@ -241,9 +241,10 @@ static int zc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t lo
 
 // Large programs (more than 32 columns or 120 terms: the bf16 gadgets of the fp8 transformer layer, whose constraint
 // systems span 60..200 columns and several hundred monomials; the reference runs them through its host loop sc5_prove,
-// zkllm-src/p3_bfadd.cuh:214-330 and siblings).  Same summand shape; the program, the current value and the difference of
-// every column live in dynamic shared memory ([column][thread], conflict-free), the column pointers of the round in
-// global memory.  Block size shrinks as the column count grows so that one block always fits an SM.
+// zkllm-src/p3_bfadd.cuh:214-330 and siblings).  Same summand shape; the program and the current value of every column
+// live in dynamic shared memory ([column][thread], conflict-free), the column pointers of the round in global memory.
+// The kernel is bound by the field multiplications of the monomials, not by memory: what matters is how many warps an SM
+// holds, so a thread keeps one word per column and re-reads the pair behind it (from cache) for each evaluation point.
 constexpr int ZCX_MAXTERMS = 2048;
 constexpr int ZCX_MAXC = 224;
 struct ZcxHdr { uint32_t nterms, nc; gl_t konst; };
@@ -254,9 +255,8 @@ __global__ void zcx_round_kernel(const uint8_t* prog_g, const gl_t* const* in, g
     const ZcxHdr hdr = *reinterpret_cast<const ZcxHdr*>(prog_g);
     const uint32_t nc = hdr.nc, nterms = hdr.nterms, T = blockDim.x, tid = threadIdx.x;
     gl_t* coef = reinterpret_cast<gl_t*>(smem);
-    gl_t* cur = coef + nterms;                 // [nc][T]
-    gl_t* dif = cur + (size_t)nc * T;          // [nc][T]
-    gl_t* sh = dif + (size_t)nc * T;           // SCW_NT * 32
+    gl_t* cur = coef + nterms;                 // [nc][T]: the columns' values at the current evaluation point
+    gl_t* sh = cur + (size_t)nc * T;           // SCW_NT * 32
     uint32_t* packed = reinterpret_cast<uint32_t*>(sh + SCW_NT * 32);
     const gl_t* coef_g = reinterpret_cast<const gl_t*>(prog_g + sizeof(ZcxHdr));
     const uint32_t* packed_g = reinterpret_cast<const uint32_t*>(coef_g + nterms);
@@ -268,19 +268,20 @@ __global__ void zcx_round_kernel(const uint8_t* prog_g, const gl_t* const* in, g
     for (int t = 0; t < SCW_NT; t++) s[t] = 0;
     const size_t stride = (size_t)gridDim.x * T;
     for (size_t i = (size_t)blockIdx.x * T + tid; i < items; i += stride) {
+        // Only the current values live in shared memory (one word per column and thread, so that several blocks fit an SM);
+        // the pair (lo, hi) of a column is read again for every evaluation point: from the input in the first round, from
+        // the bound pair this thread has just written otherwise.  The reads hit L1 / L2: DRAM traffic stays one pass.
         for (uint32_t k = 0; k < nc; k++) {
-            const gl_t* src = in[k];
-            gl_t lo, hi;
+            gl_t lo;
             if (first) {
-                ulonglong2 v = ld2(src + 2 * i);
-                lo = v.x; hi = v.y;
+                lo = in[k][2 * i];
             } else {
+                const gl_t* src = in[k];
                 ulonglong2 u = ld2(src + 4 * i), w = ld2(src + 4 * i + 2);
-                lo = gl_lerp(u.x, u.y, a); hi = gl_lerp(w.x, w.y, a);
-                st2(out[k] + 2 * i, lo, hi);
+                lo = gl_lerp(u.x, u.y, a);
+                st2(out[k] + 2 * i, lo, gl_lerp(w.x, w.y, a));
             }
             cur[(size_t)k * T + tid] = lo;
-            dif[(size_t)k * T + tid] = gl_sub(hi, lo);
         }
 #pragma unroll 1
         for (int t = 0; t < SCW_NT; t++) {
@@ -297,7 +298,11 @@ __global__ void zcx_round_kernel(const uint8_t* prog_g, const gl_t* const* in, g
             }
             s[t] = gl_add(s[t], gl_add(gl_mul(cur[tid], gl_add(acc.reduce(), hdr.konst)), accf.reduce()));
             if (t + 1 < SCW_NT)
-                for (uint32_t k = 0; k < nc; k++) cur[(size_t)k * T + tid] = gl_add(cur[(size_t)k * T + tid], dif[(size_t)k * T + tid]);
+                for (uint32_t k = 0; k < nc; k++) {
+                    const gl_t* pr = first ? in[k] : out[k];
+                    ulonglong2 v = ld2(pr + 2 * i);
+                    cur[(size_t)k * T + tid] = gl_add(cur[(size_t)k * T + tid], gl_sub(v.y, v.x));
+                }
         }
     }
     grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, ctl->par[6] ? 3 : 0);
@@ -308,7 +313,7 @@ __global__ void zcx_finals_kernel(const gl_t* const* in, int nc, const gl_t* cha
 }
 
 static size_t zcx_smem_bytes(int nc, uint32_t nterms, int T) {
-    return (size_t)nterms * 8 + (size_t)2 * nc * T * 8 + SCW_NT * 32 * 8 + (size_t)nterms * 4 + 16;
+    return (size_t)nterms * 8 + (size_t)nc * T * 8 + SCW_NT * 32 * 8 + (size_t)nterms * 4 + 16;
 }
 
 // prog_dev: ZcxHdr | coef | packed (already uploaded); ptr_dev: room for logn * 2 * nc pointers
@@ -317,14 +322,17 @@ static int zcx_enqueue(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t nte
     cudaStream_t s = ctx->stream;
     ZkhCtl* ctl = ctx->d_ctl;
     const size_t n = (size_t)1 << logn;
+    // 128 threads per block; fewer only when one block would not fit.  Several blocks share an SM (occupancy query below).
     int T = 128;
     while (T > 32 && zcx_smem_bytes(nc, nterms, T) > 200 * 1024) T >>= 1;
     const size_t smem = zcx_smem_bytes(nc, nterms, T);
     if (smem > 220 * 1024) return zkh_fail(ctx, ZKH_ERR_LIMIT, "zero-check: program does not fit shared memory");
     if (cudaFuncSetAttribute(zcx_round_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return zkh_fail(ctx, ZKH_ERR_CUDA, "zero-check: shared memory attribute");
+    int occ = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, zcx_round_kernel, T, smem) != cudaSuccess || occ < 1) occ = 1;
     auto grid_for = [&](size_t items) {
-        size_t want = (items + T - 1) / T, cap = (size_t)ctx->sm_count;
+        size_t want = (items + T - 1) / T, cap = (size_t)ctx->sm_count * occ;
         if (cap > ctx->partials_cap / SCW_NT) cap = ctx->partials_cap / SCW_NT;
         return (unsigned)(want < cap ? want : cap);
     };

@@ -260,6 +260,39 @@ def _sumcheck(engine, tr, tag, cols, terms, konst):
     return [int(x) for x in r], np.ascontiguousarray(m, dtype=np.uint64).tobytes()
 
 
+def irms_terms_rows(lamB):
+    """The six per-row constraints of p3irms (p3_int_gadgets.cuh:984-1003) as zero-check terms over [E, 18 row columns],
+    batched with powers of lamB.  Returns (terms, constant)."""
+    lam = [pow(lamB, j, GL_P) for j in range(6)]
+    c = lambda k: 1 + k                        # column index of row column k (column 0 is the eq weight)
+    n = lambda x: NEG(x)
+    terms = [
+        # r0 = M - (MM*P4 + r4),  r4 = L40 + 2^16 L41 + 2^32 L42
+        (lam[0], (c(B_M),)), (n(lam[0]), (c(B_MM), c(B_P4))), (n(lam[0]), (c(B_L40),)), (n(lam[0] << 16), (c(B_L41),)),
+        (n(lam[0] << 32), (c(B_L42),)),
+        # r1 = P4 - 1 - r4 - d4
+        (lam[1], (c(B_P4),)), (n(lam[1]), (c(B_L40),)), (n(lam[1] << 16), (c(B_L41),)), (n(lam[1] << 32), (c(B_L42),)),
+        (n(lam[1]), (c(B_D40),)), (n(lam[1] << 16), (c(B_D41),)), (n(lam[1] << 32), (c(B_D42),)),
+        # r2 = R*P2 + L20 - RP - H2
+        (lam[2], (c(B_R), c(B_P2))), (lam[2], (c(B_L20),)), (n(lam[2]), (c(B_RP),)), (n(lam[2]), (c(B_H2),)),
+        # r3 = P2 - 1 - L20 - D20
+        (lam[3], (c(B_P2),)), (n(lam[3]), (c(B_L20),)), (n(lam[3]), (c(B_D20),)),
+        # r4' = R - LR0 - 2^16 LR1
+        (lam[4], (c(B_R),)), (n(lam[4]), (c(B_LR0),)), (n(lam[4] << 16), (c(B_LR1),)),
+        # r5 = MS + 2^14 - MM
+        (lam[5], (c(B_MS),)), (n(lam[5]), (c(B_MM),)),
+    ]
+    konstB = (-lam[1] - lam[3] + lam[5] * 16384) % GL_P
+    return terms, konstB
+
+
+def irms_terms_elements(lamE):
+    """The two per-element constraints (p3_int_gadgets.cuh:1028-1035) over columns 0 E, 1 X, 2 Y, 3 W, 4 RW, 5 RY, 6 Rb, 7 Gb."""
+    n = lambda x: NEG(x)
+    terms = [(1, (6, 7)), (n(65536), (3,)), (n(1), (4,)), (lamE, (3, 1)), (n(lamE * 65536), (2,)), (n(lamE), (5,))]
+    return terms, (32768 + lamE * 32768) % GL_P
+
+
 def irms_prove(engine, tr, T, X, G, Y, wit, lT, ld, R, Q, ctx=None):
     """p3irms::prove (p3_int_gadgets.cuh:922-1047).  X, Y: (column, root) over 2^(lT+ld) elements, G: gains over 2^ld;
     wit: irms_witness output with db/de as engine columns and index arrays.
@@ -300,26 +333,7 @@ def irms_prove(engine, tr, T, X, G, Y, wit, lT, ld, R, Q, ctx=None):
     # per-row zero-check
     zB = np.array([tr.chal() for _ in range(lT)], dtype=np.uint64)
     lamB = tr.chal()
-    lam = [pow(lamB, j, GL_P) for j in range(6)]
-    c = lambda k: 1 + k                        # column index of row column k (column 0 is the eq weight)
-    n = lambda x: NEG(x)
-    terms = [
-        # r0 = M - (MM*P4 + r4),  r4 = L40 + 2^16 L41 + 2^32 L42
-        (lam[0], (c(B_M),)), (n(lam[0]), (c(B_MM), c(B_P4))), (n(lam[0]), (c(B_L40),)), (n(lam[0] << 16), (c(B_L41),)),
-        (n(lam[0] << 32), (c(B_L42),)),
-        # r1 = P4 - 1 - r4 - d4
-        (lam[1], (c(B_P4),)), (n(lam[1]), (c(B_L40),)), (n(lam[1] << 16), (c(B_L41),)), (n(lam[1] << 32), (c(B_L42),)),
-        (n(lam[1]), (c(B_D40),)), (n(lam[1] << 16), (c(B_D41),)), (n(lam[1] << 32), (c(B_D42),)),
-        # r2 = R*P2 + L20 - RP - H2
-        (lam[2], (c(B_R), c(B_P2))), (lam[2], (c(B_L20),)), (n(lam[2]), (c(B_RP),)), (n(lam[2]), (c(B_H2),)),
-        # r3 = P2 - 1 - L20 - D20
-        (lam[3], (c(B_P2),)), (n(lam[3]), (c(B_L20),)), (n(lam[3]), (c(B_D20),)),
-        # r4' = R - LR0 - 2^16 LR1
-        (lam[4], (c(B_R),)), (n(lam[4]), (c(B_LR0),)), (n(lam[4] << 16), (c(B_LR1),)),
-        # r5 = MS + 2^14 - MM
-        (lam[5], (c(B_MS),)), (n(lam[5]), (c(B_MM),)),
-    ]
-    konstB = (-lam[1] - lam[3] + lam[5] * 16384) % GL_P
+    terms, konstB = irms_terms_rows(lamB)
     EB = engine.build_eq_gpu(zB)
     rB, mB = _sumcheck(engine, tr, "irm-scB", [EB] + [cb[0] for cb in CB], terms, konstB)
     yB = [claimc(engine, tr, ctx.ledger, cb[0], cb[1], rB) for cb in CB]
@@ -328,10 +342,7 @@ def irms_prove(engine, tr, T, X, G, Y, wit, lT, ld, R, Q, ctx=None):
     lamE = tr.chal()
     Rb = engine.bcast_rows(CB[B_R][0], ld)
     Gb = engine.bcast_cols(G[0], lT)
-    # columns: 0 E, 1 X, 2 Y, 3 W, 4 RW, 5 RY, 6 Rb, 7 Gb
-    termsE = [(1, (6, 7)), (n(65536), (3,)), (n(1), (4,)),
-              (lamE, (3, 1)), (n(lamE * 65536), (2,)), (n(lamE), (5,))]
-    konstE = (32768 + lamE * 32768) % GL_P
+    termsE, konstE = irms_terms_elements(lamE)
     rE, mE = _sumcheck(engine, tr, "irm-scE", [engine.build_eq_gpu(zE), X[0], Y[0], CE[0][0], CE[1][0], CE[2][0], Rb, Gb],
                        termsE, konstE)
     yEX = claimc(engine, tr, ctx.ledger, X[0], X[1], rE)
