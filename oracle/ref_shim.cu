@@ -514,6 +514,7 @@ size_t irope_serialize(const p3irope::Proof& pf, uint8_t* out, size_t cap) {
     app(&pf.lT, 4); app(&pf.ld, 4); app(&pf.fb, 4); app(pf.rREM.data(), 32);
     for (auto& m : pf.m) app(&m, 40);
     app(&pf.yQ, 8); app(&pf.yQx, 8); app(&pf.yY, 8); app(&pf.yR, 8);
+    if (p3zkc::G.on) blind_serialize(pf.bl, b);
     tail_append(pf.tail, b);
     return emit(b, out, cap);
 }
@@ -521,11 +522,13 @@ bool irope_deserialize(const uint8_t* in, size_t len, p3irope::Proof& pf) {
     const uint8_t* p = in; const uint8_t* end = in + len;
     if (len < 44) return false;
     memcpy(&pf.lT, p, 4); memcpy(&pf.ld, p + 4, 4); memcpy(&pf.fb, p + 8, 4); memcpy(pf.rREM.data(), p + 12, 32); p += 44;
-    const size_t le = (size_t)pf.lT + pf.ld;
-    if (le > 40 || (size_t)(end - p) < le * 40 + 32) return false;
+    if ((size_t)pf.lT + pf.ld > 40) return false;
+    const size_t le = p3zkc::vfull(pf.lT + pf.ld);
+    if ((size_t)(end - p) < le * 40 + 32) return false;
     pf.m.resize(le);
     for (auto& m : pf.m) { memcpy(&m, p, 40); p += 40; }
     memcpy(&pf.yQ, p, 8); memcpy(&pf.yQx, p + 8, 8); memcpy(&pf.yY, p + 16, 8); memcpy(&pf.yR, p + 24, 8); p += 32;
+    if (p3zkc::G.on && !blind_deserialize(p, end, pf.bl)) return false;
     return tail_parse(p, end, pf.tail) && p == end;
 }
 p3irope::Pub rope_pub(const int32_t* ct, const int32_t* st, uint32_t lseq, uint32_t ldh) {
@@ -550,6 +553,7 @@ size_t irms_serialize(const p3irms::Proof& pf, uint8_t* out, size_t cap) {
     for (auto& m : pf.mE) app(&m, 40);
     app(pf.yE, 8 * p3irms::NDE);
     app(&pf.yEX, 8); app(&pf.yEY, 8); app(&pf.yER, 8); app(&pf.yEG, 8);
+    if (p3zkc::G.on) for (int j = 0; j < 3; j++) blind_serialize(pf.bl[j], b);
     tail_append(pf.tail, b);
     return emit(b, out, cap);
 }
@@ -557,20 +561,21 @@ bool irms_deserialize(const uint8_t* in, size_t len, p3irms::Proof& pf) {
     const uint8_t* p = in; const uint8_t* end = in + len;
     if (len < 8) return false;
     memcpy(&pf.lT, p, 4); memcpy(&pf.ld, p + 4, 4); p += 8;
-    const size_t le = (size_t)pf.lT + pf.ld;
-    if (le > 40) return false;
-    const size_t fixed = 32 * (p3irms::NDB + p3irms::NDE) + 16 + 40 * (2 * le + pf.lT) + 8 * (p3irms::NDB + p3irms::NDE) + 32;
+    if ((size_t)pf.lT + pf.ld > 40) return false;
+    const size_t le = p3zkc::vfull(pf.lT + pf.ld), lTf = p3zkc::vfull(pf.lT);   // chains run over the augmented domains when zk is on
+    const size_t fixed = 32 * (p3irms::NDB + p3irms::NDE) + 16 + 40 * (2 * le + lTf) + 8 * (p3irms::NDB + p3irms::NDE) + 32;
     if ((size_t)(end - p) < fixed) return false;
     for (int c = 0; c < p3irms::NDB; c++) { memcpy(pf.rdb[c].data(), p, 32); p += 32; }
     for (int c = 0; c < p3irms::NDE; c++) { memcpy(pf.rde[c].data(), p, 32); p += 32; }
     memcpy(&pf.yM, p, 8); memcpy(&pf.yMX, p + 8, 8); p += 16;
-    pf.mS.resize(le); pf.mB.resize(pf.lT); pf.mE.resize(le);
+    pf.mS.resize(le); pf.mB.resize(lTf); pf.mE.resize(le);
     for (auto& m : pf.mS) { memcpy(&m, p, 40); p += 40; }
     for (auto& m : pf.mB) { memcpy(&m, p, 40); p += 40; }
     memcpy(pf.yB, p, 8 * p3irms::NDB); p += 8 * p3irms::NDB;
     for (auto& m : pf.mE) { memcpy(&m, p, 40); p += 40; }
     memcpy(pf.yE, p, 8 * p3irms::NDE); p += 8 * p3irms::NDE;
     memcpy(&pf.yEX, p, 8); memcpy(&pf.yEY, p + 8, 8); memcpy(&pf.yER, p + 16, 8); memcpy(&pf.yEG, p + 24, 8); p += 32;
+    if (p3zkc::G.on) for (int j = 0; j < 3; j++) if (!blind_deserialize(p, end, pf.bl[j])) return false;
     return tail_parse(p, end, pf.tail) && p == end;
 }
 // p3ismx::Proof <-> bytes: u32 la, lseq | 7 element roots | 2 row roots | mSel le*40 | ySel | ySrow | mS le*40 | ySE |

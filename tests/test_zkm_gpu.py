@@ -162,3 +162,80 @@ def test_zk_residual_add_and_swiglu_accepted_by_reference_verifier(orc, ref, zk,
     bad = bytearray(pf)
     bad[len(pf) // 2] ^= 1
     assert not _ref_verify3_zk(ref, "ref_iswg_verify", st0, [G.root, U.root, MO.root], le, R, Q, bytes(bad))[0]
+
+
+def _with_zk(ref, fn):
+    ref_zk(ref, True, 24, 1, 22)
+    try:
+        return fn()
+    finally:
+        ref_zk(ref, False)
+
+
+def test_zk_rope_accepted_by_reference_verifier(orc, ref, zk, prover):
+    import ctypes as C
+    import torch
+    R, Q, (lseq, ldh, lnh) = 1, 24, (3, 3, 1)
+    zkm, ig = zk.zkm, zk.ig
+    T = ig.build_tables(zk.load_library(), 64, 12)
+    dev, d32 = zk.p3.to_device, lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int32)).cuda()
+    g = np.random.default_rng(11)
+    ld, lT = ldh + lnh, lseq
+    le = lT + ld
+    ct = g.integers(-(1 << 14), (1 << 14) + 1, (1 << lseq, 1 << (ldh - 1))).astype(np.int32)
+    sn = g.integers(-(1 << 14), (1 << 14) + 1, (1 << lseq, 1 << (ldh - 1))).astype(np.int32)
+    q = ig.lift(g.integers(-(1 << 17), 1 << 17, 1 << le))
+    y, rem, iR, iY, Cc, S2 = ig.irope_witness(q, ct, sn, lseq, ldh, lT, ld)
+    zc = zkm.ZkCtx(seed=41, Q=Q)
+    Qc, Y = zkm.commit_col(prover, zc, dev(q), R), zkm.commit_col(prover, zc, dev(y), R)
+    tr = zk.Transcript("irope")
+    pf = zkm.irope_prove(prover, zc, tr, T, (dev(ig.lift(Cc)), dev(ig.lift(S2)), ldh), Qc, Y, (dev(rem), d32(iR), d32(iY)), lT, ld, R, Q)
+
+    def verify(proof):
+        s = (C.c_uint8 * 32)(*zk.Transcript("irope").state)
+        ok = ref.lib.ref_irope_verify(s, ct.ctypes.data_as(C.c_void_p), sn.ctypes.data_as(C.c_void_p), C.c_uint32(lseq),
+                                      C.c_uint32(ldh), Qc.root, Y.root, C.c_uint32(lT), C.c_uint32(ld), C.c_uint32(R), C.c_uint32(Q),
+                                      bytes(proof), C.c_size_t(len(proof)))
+        return bool(ok), bytes(s)
+    ok, st = _with_zk(ref, lambda: verify(pf))
+    assert ok and st == tr.state
+    bad = bytearray(pf)
+    bad[len(pf) // 2] ^= 1
+    assert not _with_zk(ref, lambda: verify(bad))[0]
+
+
+def test_zk_rmsnorm_accepted_by_reference_verifier(orc, ref, zk, prover):
+    """The row column M carries a LINKED mask (CEPS + row sums of squares of X's first mask slice): with a fresh mask instead,
+    the hiding row-sum binding fails and the reference refuses the proof."""
+    import ctypes as C
+    import torch
+    R, Q, (lT, ld) = 1, 24, (3, 4)
+    zkm, ig = zk.zkm, zk.ig
+    T = ig.build_tables(zk.load_library(), 1 << ld, 12)
+    dev, d32 = zk.p3.to_device, lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int32)).cuda()
+    g = np.random.default_rng(34)
+    le = lT + ld
+    x = ig.lift(g.integers(-(1 << 17), 1 << 17, 1 << le))
+    gains = ig.lift(g.integers(1 << 15, 1 << 17, 1 << ld))
+    w = ig.irms_witness(x, gains, T, lT, ld)
+    wit = dict(w)
+    wit["db"] = [dev(c) for c in w["db"]]
+    wit["de"] = [dev(c) for c in w["de"]]
+    for k in ("idxE4", "idxM16", "idxMS", "idxISQ", "idxLR1", "idxRW", "idxW", "idxRY", "idxY"):
+        wit[k] = d32(w[k])
+    wit["idxL"] = [d32(i) for i in w["idxL"]]
+    zc = zkm.ZkCtx(seed=43, Q=Q)
+    X, G, Y = (zkm.commit_col(prover, zc, dev(a), R) for a in (x, gains, w["y"]))
+    tr = zk.Transcript("irms")
+    pf = zkm.irms_prove(prover, zc, tr, T, X, G, Y, wit, lT, ld, R, Q)
+
+    def verify(proof):
+        s = (C.c_uint8 * 32)(*zk.Transcript("irms").state)
+        ok = ref.lib.ref_irms_verify(s, X.root, G.root, Y.root, C.c_uint32(lT), C.c_uint32(ld), C.c_uint32(R), C.c_uint32(Q),
+                                     bytes(proof), C.c_size_t(len(proof)))
+        return bool(ok), bytes(s)
+    ok, st = _with_zk(ref, lambda: verify(pf))
+    assert ok and st == tr.state
+    bad = bytearray(pf)
+    bad[len(pf) // 3] ^= 1
+    assert not _with_zk(ref, lambda: verify(bad))[0]

@@ -572,3 +572,110 @@ def iswg_prove(engine, zc, tr, tables, G, U, MO, wit, le, R, Q, ledger=None, luq
     out = struct.pack("<I", le) + SIL.root + REM.root + np.ascontiguousarray(msgs, dtype=np.uint64).tobytes()
     out += struct.pack("<QQQQ", *ys) + blind
     return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "isw-bo") if own else _EMPTY_TAIL)
+
+
+def irope_prove(engine, zc, tr, tables, pub, Qc, Y, wit, lT, ld, R, Q, ledger=None, luq=None):
+    """p3irope::prove with the zk switch on (zkllm-src/p3_int_gadgets.cuh:1275-1322).  pub = (C, S2, ldh): the public
+    broadcasts over the 2^(lT+ld) real entries (zero on the mask slices, as the reference's pub_col); Qc, Y: ZCol;
+    wit = (rem, idxR, idxY).  The rotate-half partner is the bit flip of the whole augmented array, so its claim sits at
+    the flipped point.  Serialised: u32 lT, ld, fb | rREM | messages vfull(le)*40 | yQ yQx yY yR | Blind | tail."""
+    own = ledger is None
+    if own:
+        ledger, luq = ZLedger(), []
+    Ccol, Scol, ldh = pub
+    rem, idxR, idxY = wit
+    le, fb = lT + ld, ldh - 1
+    tr.absorb("irp-dims", struct.pack("<III", lT, ld, fb))
+    tr.absorb("irp-Q", Qc.root)
+    tr.absorb("irp-Y", Y.root)
+    REM = commit_col(engine, zc, rem, R)
+    tr.absorb("irp-r", REM.root)
+    luq.append({"W": [REM], "idx": idxR, "tab": tables["R14"]})
+    luq.append({"W": [Y], "idx": idxY, "tab": tables["RS20"]})
+    zE = [tr.chal() for _ in range(le)]
+    pad = (1 << zc.vfull(le)) - (1 << le)
+    cols = [engine.build_eq_gpu(np.array(zpt(zc, zE), dtype=np.uint64)), Qc.dev, engine.flip_bit(Qc.dev, fb), Y.dev, REM.dev,
+            engine.concat([Ccol, engine.zeros(pad)]), engine.concat([Scol, engine.zeros(pad)])]
+    terms = [(1, (1, 5)), (1, (2, 6)), (GL_P - 16384, (3,)), (GL_P - 1, (4,))]
+    r, msgs, _, blind = sc5z(engine, zc, tr, "irp-sc", le, cols, terms, 8192, R, ledger)
+    rf = list(r)
+    rf[fb] = (1 - rf[fb]) % GL_P
+    ys = [claimc(engine, tr, ledger, Qc, r), claimc(engine, tr, ledger, Qc, rf), claimc(engine, tr, ledger, Y, r),
+          claimc(engine, tr, ledger, REM, r)]
+    out = struct.pack("<III", lT, ld, fb) + REM.root + np.ascontiguousarray(msgs, dtype=np.uint64).tobytes()
+    out += struct.pack("<QQQQ", *ys) + blind
+    return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "irp-bo") if own else _EMPTY_TAIL)
+
+
+def irms_prove(engine, zc, tr, tables, X, G, Y, wit, lT, ld, R, Q, ledger=None, luq=None):
+    """p3irms::prove with the zk switch on (zkllm-src/p3_int_gadgets.cuh:918-1047).  X, Y: ZCol over 2^(lT+ld) entries, G over
+    2^ld; wit: ig.irms_witness output with db / de as engine columns.  The first mask slice of the row column M is LINKED:
+    CEPS plus the row sums of squares of X's first mask slice, so that the row-sum binding holds slice by slice at the
+    hiding point (z | zex | 0..).  Three blinded chains.  Serialised: u32 lT, ld | 18 row roots | 3 element roots | yM yMX |
+    mS | mB yB[18] | mE yE[3] yEX yEY yER yEG | three Blinds | tail."""
+    from . import ig
+    own = ledger is None
+    if own:
+        ledger, luq = ZLedger(), []
+    le = lT + ld
+    tr.absorb("irm-dims", struct.pack("<II", lT, ld))
+    tr.absorb("irm-X", X.root)
+    tr.absorb("irm-G", G.root)
+    tr.absorb("irm-Y", Y.root)
+    x1 = slice1(engine, X)
+    rows = engine.matvec(engine.mul(x1, x1), 1 << lT, 1 << ld, engine.lu_ones(1 << ld), True)
+    mM = mk_linked(engine, zc, lT, engine.affine([rows], 1, ig.CEPS))
+    CB, CE = [], []
+    for k, c in enumerate(wit["db"]):
+        CB.append(commit_col(engine, zc, c, R, mask=mM if k == ig.B_M else None))
+        tr.absorb("irm-cb", CB[k].root)
+    for k, c in enumerate(wit["de"]):
+        CE.append(commit_col(engine, zc, c, R))
+        tr.absorb("irm-ce", CE[k].root)
+    defer = lambda cols, idx, tab: luq.append({"W": cols, "idx": idx, "tab": tables[tab]})
+    defer([CB[ig.B_P4], CB[ig.B_P2], CB[ig.B_H2]], wit["idxE4"], "EXP4")
+    defer([CB[ig.B_MM]], wit["idxM16"], "R16")
+    defer([CB[ig.B_MS]], wit["idxMS"], "R16")
+    defer([CB[ig.B_MM], CB[ig.B_RP]], wit["idxISQ"], "ISQ")
+    for l, c in enumerate((ig.B_L40, ig.B_L41, ig.B_L42, ig.B_D40, ig.B_D41, ig.B_D42, ig.B_L20, ig.B_D20, ig.B_LR0)):
+        defer([CB[c]], wit["idxL"][l], "R16")
+    defer([CB[ig.B_LR1]], wit["idxLR1"], "R16")
+    defer([CE[1]], wit["idxRW"], "R16")
+    defer([CE[0]], wit["idxW"], "RS20")
+    defer([CE[2]], wit["idxRY"], "R16")
+    defer([Y], wit["idxY"], "RS20")
+    eX = zc.e_of(le)
+    NeA = 1 << (le + eX)
+    # M row-sum binding at the hiding point: sum_j X^2 = M - CEPS on the real slice and on mask slice 1
+    zb = [tr.chal() for _ in range(lT)]
+    zex = tr.chal()
+    yM = claimc(engine, tr, ledger, CB[ig.B_M], xpt(zc, zb, zex))
+    eqb = engine.build_eq_gpu(np.array(zb + [zex] + [0] * (eX - 1), dtype=np.uint64))
+    EQb = engine.gather_fn(eqb, NeA, lambda q: ((q >> le) << lT) | ((q & ((1 << le) - 1)) >> ld))
+    rS, mS, _, bl0 = sc5z(engine, zc, tr, "irm-scS", le, [EQb, X.dev], [(1, (1, 1))], 0, R, ledger)
+    yMX = claimc(engine, tr, ledger, X, rS)
+    # per-row zero-check
+    zB = [tr.chal() for _ in range(lT)]
+    termsB, konstB = ig.irms_terms_rows(tr.chal())
+    colsB = [engine.build_eq_gpu(np.array(zpt(zc, zB), dtype=np.uint64))] + [c.dev for c in CB]
+    rB, mB, _, bl1 = sc5z(engine, zc, tr, "irm-scB", lT, colsB, termsB, konstB, R, ledger)
+    yB = [claimc(engine, tr, ledger, c, rB) for c in CB]
+    # per-element zero-check; the row value R and the gains are broadcast over the augmented element domain
+    zE = [tr.chal() for _ in range(le)]
+    termsE, konstE = ig.irms_terms_elements(tr.chal())
+    eR, eG = zc.e_of(lT), zc.e_of(ld)
+    mR, mG = (1 << min(eR, eX)) - 1, (1 << min(eG, eX)) - 1
+    Rb = engine.gather_fn(CB[ig.B_R].dev, NeA, lambda q: ((q & ((1 << le) - 1)) >> ld) | (((q >> le) & mR) << lT))
+    Gb = engine.gather_fn(G.dev, NeA, lambda q: (q & ((1 << ld) - 1)) | (((q >> le) & mG) << ld))
+    colsE = [engine.build_eq_gpu(np.array(zpt(zc, zE), dtype=np.uint64)), X.dev, Y.dev, CE[0].dev, CE[1].dev, CE[2].dev, Rb, Gb]
+    rE, mE, _, bl2 = sc5z(engine, zc, tr, "irm-scE", le, colsE, termsE, konstE, R, ledger)
+    yEX = claimc(engine, tr, ledger, X, rE)
+    yEY = claimc(engine, tr, ledger, Y, rE)
+    yE = [claimc(engine, tr, ledger, c, rE) for c in CE]
+    yER = claimc(engine, tr, ledger, CB[ig.B_R], expt(zc, rE[ld:le], rE, le))
+    yEG = claimc(engine, tr, ledger, G, expt(zc, rE[:ld], rE, le))
+    u64 = lambda m: np.ascontiguousarray(m, dtype=np.uint64).tobytes()
+    out = struct.pack("<II", lT, ld) + b"".join(c.root for c in CB) + b"".join(c.root for c in CE)
+    out += struct.pack("<QQ", yM, yMX) + u64(mS) + u64(mB) + struct.pack("<18Q", *yB) + u64(mE) + struct.pack("<3Q", *yE)
+    out += struct.pack("<QQQQ", yEX, yEY, yER, yEG) + bl0 + bl1 + bl2
+    return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "irm-bo") if own else _EMPTY_TAIL)
