@@ -592,6 +592,7 @@ size_t ismx_serialize(const p3ismx::Proof& pf, uint8_t* out, size_t cap) {
     app(&pf.ySE, 8);
     for (auto& m : pf.mE) app(&m, 40);
     app(&pf.yEZ, 8); app(pf.yE, 8 * p3ismx::NXE); app(&pf.yEP, 8); app(&pf.yEMX, 8); app(&pf.yES, 8);
+    if (p3zkc::G.on) for (int j = 0; j < 3; j++) blind_serialize(pf.bl[j], b);
     tail_append(pf.tail, b);
     return emit(b, out, cap);
 }
@@ -599,8 +600,8 @@ bool ismx_deserialize(const uint8_t* in, size_t len, p3ismx::Proof& pf) {
     const uint8_t* p = in; const uint8_t* end = in + len;
     if (len < 8) return false;
     memcpy(&pf.la, p, 4); memcpy(&pf.lseq, p + 4, 4); p += 8;
-    const size_t le = (size_t)pf.la + 2 * (size_t)pf.lseq;
-    if (le > 40) return false;
+    if ((size_t)pf.la + 2 * (size_t)pf.lseq > 40) return false;
+    const size_t le = p3zkc::vfull(pf.la + 2 * pf.lseq);      // the chains run over the augmented domain when zk is on
     const size_t fixed = 32 * (p3ismx::NXE + p3ismx::NXB) + 120 * le + 8 * (3 + 1 + p3ismx::NXE + 3);
     if ((size_t)(end - p) < fixed) return false;
     for (int c = 0; c < p3ismx::NXE; c++) { memcpy(pf.rxe[c].data(), p, 32); p += 32; }
@@ -614,6 +615,7 @@ bool ismx_deserialize(const uint8_t* in, size_t len, p3ismx::Proof& pf) {
     memcpy(&pf.yEZ, p, 8); p += 8;
     memcpy(pf.yE, p, 8 * p3ismx::NXE); p += 8 * p3ismx::NXE;
     memcpy(&pf.yEP, p, 8); memcpy(&pf.yEMX, p + 8, 8); memcpy(&pf.yES, p + 16, 8); p += 24;
+    if (p3zkc::G.on) for (int j = 0; j < 3; j++) if (!blind_deserialize(p, end, pf.bl[j])) return false;
     return tail_parse(p, end, pf.tail) && p == end;
 }
 size_t irs_serialize(const p3irs::Proof& pf, uint8_t* out, size_t cap);

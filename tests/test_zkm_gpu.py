@@ -239,3 +239,34 @@ def test_zk_rmsnorm_accepted_by_reference_verifier(orc, ref, zk, prover):
     bad = bytearray(pf)
     bad[len(pf) // 3] ^= 1
     assert not _with_zk(ref, lambda: verify(bad))[0]
+
+
+def test_zk_softmax_accepted_by_reference_verifier(orc, ref, zk, prover):
+    """Causal softmax rows in hiding mode: the first mask slice of the row sums S is linked to the row sums of EE's."""
+    import ctypes as C
+    import torch
+    R, Q, (la, lseq) = 1, 24, (1, 3)
+    zkm, ig = zk.zkm, zk.ig
+    T = ig.build_tables(zk.load_library(), 64, 12)
+    dev, d32 = zk.p3.to_device, lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int32)).cuda()
+    g = np.random.default_rng(17)
+    le = la + 2 * lseq
+    z = ig.lift(g.integers(-2000, 2000, 1 << le))
+    w = ig.ismx_witness(z, T, la, lseq)
+    wit = {"xe": [dev(c) for c in w["xe"]], "xb": [dev(c) for c in w["xb"]], "idxDM": d32(w["idxDM"]),
+           "idxL": [d32(i) for i in w["idxL"]], "idxMX": d32(w["idxMX"])}
+    zc = zkm.ZkCtx(seed=47, Q=Q)
+    Z, P = zkm.commit_col(prover, zc, dev(z), R), zkm.commit_col(prover, zc, dev(w["p"]), R)
+    tr = zk.Transcript("ismx")
+    pf = zkm.ismx_prove(prover, zc, tr, T, Z, P, wit, la, lseq, R, Q)
+
+    def verify(proof):
+        s = (C.c_uint8 * 32)(*zk.Transcript("ismx").state)
+        ok = ref.lib.ref_ismx_verify(s, Z.root, P.root, C.c_uint32(la), C.c_uint32(lseq), C.c_uint32(R), C.c_uint32(Q), bytes(proof),
+                                     C.c_size_t(len(proof)))
+        return bool(ok), bytes(s)
+    ok, st = _with_zk(ref, lambda: verify(pf))
+    assert ok and st == tr.state
+    bad = bytearray(pf)
+    bad[len(pf) // 3] ^= 1
+    assert not _with_zk(ref, lambda: verify(bad))[0]

@@ -394,6 +394,26 @@ def causal_mask(la, lseq):
     return ((u & (seq - 1)) <= ((u >> lseq) & (seq - 1))).astype(np.uint64)
 
 
+def ismx_terms(lamE):
+    """The five per-element constraints of p3ismx (p3_int_gadgets.cuh:1604-1622) over columns 0 E, 1 Z, 2.. the seven element
+    columns, then P, MX broadcast, S broadcast, causal mask; batched with powers of lamE.  Returns (terms, constant)."""
+    lam = [pow(lamE, k, GL_P) for k in range(5)]
+    n = NEG
+    ce = lambda k: 2 + k
+    Zc, Pc, MXb, Sb, MK = 1, 2 + NXE, 3 + NXE, 4 + NXE, 5 + NXE
+    terms = [
+        (lam[0], (ce(X_SEL), ce(X_SEL))), (n(lam[0]), (ce(X_SEL),)),                                   # SEL^2 - SEL
+        (lam[1], (ce(X_SEL), ce(X_DM))),                                                               # SEL * DM
+        (lam[2], (ce(X_DM),)), (n(lam[2]), (MK, MXb)), (lam[2], (MK, Zc)), (lam[2] * 65536, (MK,)),    # DM - MK(MX - Z) - (1-MK) 2^16
+        (lam[3] * 131072, (ce(X_EE),)), (lam[3], (Sb,)), (n(2 * lam[3]), (Pc, Sb)), (n(lam[3]), (ce(X_L0),)),
+        (n(lam[3] * 65536), (ce(X_L1),)),                                                              # 2^17 EE + S - 2 P S - r1
+        (lam[4], (ce(X_L2),)), (lam[4] * 65536, (ce(X_L3),)), (lam[4], (ce(X_L0),)), (lam[4] * 65536, (ce(X_L1),)),
+        (n(2 * lam[4]), (Sb,)),                                                                        # r2 + r1 + 1 - 2 S
+    ]
+    konst = (-lam[2] * 65536 + lam[4]) % GL_P
+    return terms, konst
+
+
 def ismx_prove(engine, tr, T, Z, P, wit, la, lseq, R, Q, ctx=None):
     """p3ismx::prove (p3_int_gadgets.cuh:1518-1643).  Z, P: (column, root) over 2^(la + 2 lseq); wit: ismx_witness
     output with xe/xb as engine columns and index arrays.
@@ -430,20 +450,7 @@ def ismx_prove(engine, tr, T, Z, P, wit, la, lseq, R, Q, ctx=None):
     # per-element zero-check
     zE = np.array([tr.chal() for _ in range(le)], dtype=np.uint64)
     lamE = tr.chal()
-    lam = [pow(lamE, k, GL_P) for k in range(5)]
-    n = NEG
-    ce = lambda k: 2 + k
-    Zc, Pc, MXb, Sb, MK = 1, 2 + NXE, 3 + NXE, 4 + NXE, 5 + NXE
-    terms = [
-        (lam[0], (ce(X_SEL), ce(X_SEL))), (n(lam[0]), (ce(X_SEL),)),                                   # SEL^2 - SEL
-        (lam[1], (ce(X_SEL), ce(X_DM))),                                                               # SEL * DM
-        (lam[2], (ce(X_DM),)), (n(lam[2]), (MK, MXb)), (lam[2], (MK, Zc)), (lam[2] * 65536, (MK,)),    # DM - MK(MX - Z) - (1-MK) 2^16
-        (lam[3] * 131072, (ce(X_EE),)), (lam[3], (Sb,)), (n(2 * lam[3]), (Pc, Sb)), (n(lam[3]), (ce(X_L0),)),
-        (n(lam[3] * 65536), (ce(X_L1),)),                                                              # 2^17 EE + S - 2 P S - r1
-        (lam[4], (ce(X_L2),)), (lam[4] * 65536, (ce(X_L3),)), (lam[4], (ce(X_L0),)), (lam[4] * 65536, (ce(X_L1),)),
-        (n(2 * lam[4]), (Sb,)),                                                                        # r2 + r1 + 1 - 2 S
-    ]
-    konst = (-lam[2] * 65536 + lam[4]) % GL_P
+    terms, konst = ismx_terms(lamE)
     cols = [engine.build_eq_gpu(zE), Z[0]] + [c[0] for c in CE] + [P[0], engine.bcast_rows(CB[0][0], lseq),
                                                                    engine.bcast_rows(CB[1][0], lseq), engine.causal_mask(la, lseq)]
     rE, mE = _sumcheck(engine, tr, "ism-sce", cols, terms, konst)

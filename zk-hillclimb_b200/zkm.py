@@ -10,6 +10,7 @@
   imm_prove              p3imm::prove with the zk switch on         zkllm-src/p3_int_gadgets.cuh:510-605
   prove_super / lu_flush p3lu::prove_super / lu_flush, zk branches  zkllm-src/p3_logup.cuh:1357-1956
   irs_prove / iadd_prove / iswg_prove   p3irs / p3iadd / p3iswg::prove with the zk switch on   p3_int_gadgets.cuh:282-340, :712-737, :1790-1832
+  irope_prove / irms_prove / ismx_prove p3irope / p3irms / p3ismx::prove with the zk switch on p3_int_gadgets.cuh:1275-1322, :918-1047, :1514-1643
 
 Every random draw follows the reference's order (one counter-mode seed per draw, zkllm-src/p3_zkc.cuh:118-123), so with
 the same master seed the proofs are the reference prover's bytes.  The device work is the library's: mask and blind
@@ -679,3 +680,71 @@ def irms_prove(engine, zc, tr, tables, X, G, Y, wit, lT, ld, R, Q, ledger=None, 
     out += struct.pack("<QQ", yM, yMX) + u64(mS) + u64(mB) + struct.pack("<18Q", *yB) + u64(mE) + struct.pack("<3Q", *yE)
     out += struct.pack("<QQQQ", yEX, yEY, yER, yEG) + bl0 + bl1 + bl2
     return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "irm-bo") if own else _EMPTY_TAIL)
+
+
+def _eqb_col(engine, ptb, lb, lcols, le, NeA):
+    """p3ig::eqb_col (zkllm-src/p3_int_gadgets.cuh:150-162): the row weight over the augmented element domain,
+    EQb[e | ex << le] = eq(ptb)[(ex << lb) | row(e)]."""
+    eqb = engine.build_eq_gpu(np.array(ptb, dtype=np.uint64))
+    return engine.gather_fn(eqb, NeA, lambda q: ((q >> le) << lb) | ((q & ((1 << le) - 1)) >> lcols))
+
+
+def ismx_prove(engine, zc, tr, tables, Z, P, wit, la, lseq, R, Q, ledger=None, luq=None):
+    """p3ismx::prove with the zk switch on (zkllm-src/p3_int_gadgets.cuh:1514-1643): causal softmax rows.  Z, P: ZCol over
+    2^(la + 2 lseq) entries; wit: ig.ismx_witness output with xe / xb as engine columns.  The first mask slice of the row sums
+    S is LINKED to the row sums of EE's first mask slice.  The SEL row sums are bound at the zero-extended point (public
+    base 1), the S row sums at the hiding point.  Serialised: u32 la, lseq | 7 element roots | 2 row roots | mSel ySel |
+    ySrow mS ySE | mE yEZ yE[7] yEP yEMX yES | three Blinds | tail."""
+    from . import ig
+    own = ledger is None
+    if own:
+        ledger, luq = ZLedger(), []
+    lr, le = la + lseq, la + 2 * lseq
+    tr.absorb("ism-dims", struct.pack("<II", la, lseq))
+    tr.absorb("ism-Z", Z.root)
+    tr.absorb("ism-P", P.root)
+    CE = []
+    for c in wit["xe"]:
+        CE.append(commit_col(engine, zc, c, R))
+        tr.absorb("ism-ce", CE[-1].root)
+    e1 = slice1(engine, CE[ig.X_EE])
+    mS_ = mk_linked(engine, zc, lr, engine.matvec(e1, 1 << lr, 1 << lseq, engine.lu_ones(1 << lseq), True))
+    CB = [commit_col(engine, zc, wit["xb"][0], R), commit_col(engine, zc, wit["xb"][1], R, mask=mS_)]
+    for c in CB:
+        tr.absorb("ism-cb", c.root)
+    luq.append({"W": [CE[ig.X_DM], CE[ig.X_EE]], "idx": wit["idxDM"], "tab": tables["EXPT"]})
+    for l in range(4):
+        luq.append({"W": [CE[ig.X_L0 + l]], "idx": wit["idxL"][l], "tab": tables["R16"]})
+    luq.append({"W": [CB[0]], "idx": wit["idxMX"], "tab": tables["RS16"]})
+    eX = zc.e_of(le)
+    NeA = 1 << (le + eX)
+    # SEL row sums = 1: zero-extended row point
+    zb = [tr.chal() for _ in range(lr)]
+    rS, mSel, _, bl0 = sc5z(engine, zc, tr, "ism-scsel", le, [_eqb_col(engine, zb + [0] * eX, lr, lseq, le, NeA), CE[ig.X_SEL].dev],
+                            [(1, (1,))], 0, R, ledger)
+    ySel = claimc(engine, tr, ledger, CE[ig.X_SEL], rS)
+    # S row sums: hiding claim on S, linked masks
+    zb = [tr.chal() for _ in range(lr)]
+    zex = tr.chal()
+    ySrow = claimc(engine, tr, ledger, CB[1], xpt(zc, zb, zex))
+    rS2, mS, _, bl1 = sc5z(engine, zc, tr, "ism-scs", le,
+                           [_eqb_col(engine, zb + [zex] + [0] * (eX - 1), lr, lseq, le, NeA), CE[ig.X_EE].dev], [(1, (1,))], 0, R, ledger)
+    ySE = claimc(engine, tr, ledger, CE[ig.X_EE], rS2)
+    # per-element zero-check
+    zE = [tr.chal() for _ in range(le)]
+    terms, konst = ig.ismx_terms(tr.chal())
+    mB = (1 << min(zc.e_of(lr), eX)) - 1
+    bc = lambda col: engine.gather_fn(col.dev, NeA, lambda q: ((q & ((1 << le) - 1)) >> lseq) | (((q >> le) & mB) << lr))
+    mask = engine.concat([engine.causal_mask(la, lseq), engine.zeros(NeA - (1 << le))])
+    cols = [engine.build_eq_gpu(np.array(zpt(zc, zE), dtype=np.uint64)), Z.dev] + [c.dev for c in CE] + [P.dev, bc(CB[0]), bc(CB[1]), mask]
+    rE, mE, _, bl2 = sc5z(engine, zc, tr, "ism-sce", le, cols, terms, konst, R, ledger)
+    yEZ = claimc(engine, tr, ledger, Z, rE)
+    yE = [claimc(engine, tr, ledger, c, rE) for c in CE]
+    yEP = claimc(engine, tr, ledger, P, rE)
+    yEMX = claimc(engine, tr, ledger, CB[0], expt(zc, rE[lseq:le], rE, le))
+    yES = claimc(engine, tr, ledger, CB[1], expt(zc, rE[lseq:le], rE, le))
+    u64 = lambda m: np.ascontiguousarray(m, dtype=np.uint64).tobytes()
+    out = struct.pack("<II", la, lseq) + b"".join(c.root for c in CE) + b"".join(c.root for c in CB)
+    out += u64(mSel) + struct.pack("<QQ", ySel, ySrow) + u64(mS) + struct.pack("<Q", ySE)
+    out += u64(mE) + struct.pack("<Q", yEZ) + struct.pack("<7Q", *yE) + struct.pack("<QQQ", yEP, yEMX, yES) + bl0 + bl1 + bl2
+    return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "ism-bo") if own else _EMPTY_TAIL)
