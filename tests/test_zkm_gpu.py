@@ -270,3 +270,37 @@ def test_zk_softmax_accepted_by_reference_verifier(orc, ref, zk, prover):
     bad = bytearray(pf)
     bad[len(pf) // 3] ^= 1
     assert not _with_zk(ref, lambda: verify(bad))[0]
+
+
+@pytest.mark.parametrize("dims", [(4, 8, 2, 4, 16, 1), (8, 16, 2, 8, 32, 2)])
+def test_zk_integer_layer_equals_reference_prover(orc, ref, zk, prover, dims):
+    """The whole decoder layer in hiding mode (p3itf with the zk switch on): 26 + 2A blinded sub-proofs, linked accumulator
+    masks, merged lookups over mask-interleaved trees, blinded openings.  Accepted by the reference's layer verifier and, with
+    the same master seed, the bytes of the reference's own zk layer prover."""
+    from ig_helpers import layer_inputs, ref_itf_prove, ref_itf_verify
+    from test_itf_gpu import device_col
+    R, Q, seed = 1, 24, 0xABCDEF
+    ig, zkm = zk.ig, zk.zkm
+    c = ig.Config(*dims)
+    T = ig.build_tables(zk.load_library(), c.d, c.btop)
+    x0, Wt = layer_inputs(ig, c, 5)
+    w = ig.itf_build_witness(c, x0, Wt, T)
+    col = device_col(zk)
+    zc = zkm.ZkCtx(seed=seed, Q=Q)
+    o = zkm.itf_commit_all(prover, zc, c, w, Wt, R, col)
+    tr = zk.Transcript("itf-layer")
+    pf = zkm.itf_prove(prover, zc, tr, c, w, o, Wt, T, R, Q, col)
+    wroots = [x.root for x in o["w"]] + [o["g1"].root, o["g2"].root]
+    st0 = zk.Transcript("itf-layer").state
+    ok, st = _with_zk(ref, lambda: ref_itf_verify(ref, st0, c, x0, o["x0"].root, wroots, Wt, w["out"], R, Q, pf))
+    assert ok and st == tr.state
+    bad = bytearray(pf)
+    bad[len(pf) // 2] ^= 1
+    assert not _with_zk(ref, lambda: ref_itf_verify(ref, st0, c, x0, o["x0"].root, wroots, Wt, w["out"], R, Q, bytes(bad)))[0]
+    ref_zk(ref, True, Q, seed, 22)
+    try:
+        rpf, rst, grid, ms = ref_itf_prove(ref, st0, c, x0, Wt, R, Q)
+    finally:
+        ref_zk(ref, False)
+    assert (grid == w["out"]).all()
+    assert rst == tr.state and rpf == pf

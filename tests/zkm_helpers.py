@@ -50,6 +50,10 @@ class OracleZkEngine(OracleGadgetEngine):
     def set_element(self, col, i, value):
         col.a[i] = np.uint64(int(value) % GL_P)
 
+    def scatter_fn(self, col, n, fn, vals):
+        col.a[fn(np.arange(n, dtype=np.int64))] = vals.a
+        return col
+
     def gather_fn(self, col, n, fn):
         return _Arr(col.a[fn(np.arange(n, dtype=np.int64))])
 

@@ -446,6 +446,13 @@ class Prover:
     def slice(self, col, lo, n):
         return col[lo:lo + n]
 
+    def scatter_fn(self, col, n, fn, vals):
+        """col[fn(u)] = vals[u] for u < n (distinct targets), the index map evaluated on the device; returns col."""
+        import torch
+        u = torch.arange(n, dtype=torch.int64, device=col.device)
+        col[fn(u)] = vals
+        return col
+
     def concat(self, cols):
         import torch
         return torch.cat(list(cols)).contiguous()

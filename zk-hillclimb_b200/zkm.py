@@ -748,3 +748,191 @@ def ismx_prove(engine, zc, tr, tables, Z, P, wit, la, lseq, R, Q, ledger=None, l
     out += u64(mSel) + struct.pack("<QQ", ySel, ySrow) + u64(mS) + struct.pack("<Q", ySE)
     out += u64(mE) + struct.pack("<Q", yEZ) + struct.pack("<7Q", *yE) + struct.pack("<QQQ", yEP, yEMX, yES) + bl0 + bl1 + bl2
     return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "ism-bo") if own else _EMPTY_TAIL)
+
+
+# ---------------------------------------------------------------------------------- operand views and the integer layer
+def _view_index(view, vals):
+    """p3imm::op_off / y_off (zkllm-src/p3_int_gadgets.cuh:448-470) on index arrays: bit t of the element index comes from bit
+    `bit` of vals[src] (S_J, S_A, S_I) or is the constant `bit` (S_C)."""
+    from .p3 import S_C
+    idx = 0
+    for t, (src, bit) in enumerate(view):
+        if src == S_C:
+            idx = idx | (bit << t)
+        elif src in vals:
+            idx = idx | (((vals[src] >> bit) & 1) << t)
+    return idx
+
+
+def direct_views(lj, lk, li):
+    """p3imm::direct_x / direct_w / direct_y: X = [j | i<<lj], W = [k | j<<lk], Y = [k | i<<lk]."""
+    from .p3 import S_A, S_I, S_J
+    xv = [(S_J, t) for t in range(lj)] + [(S_A, t) for t in range(li)]
+    wv = [(S_A, t) for t in range(lk)] + [(S_J, t) for t in range(lj)]
+    yv = [(S_A, t) for t in range(lk)] + [(S_I, t) for t in range(li)]
+    return xv, wv, yv
+
+
+def linked_acc_mask(engine, zc, vY, insts):
+    """p3itf::commit_acc (zkllm-src/p3_int_layer.cuh:331-340): the mask of a matmul accumulator grid whose first slice is, per
+    instance (X, W, views, lj, lk, li), the product of the operands' first mask slices placed at the instance's Y view."""
+    from .p3 import S_A, S_I, S_J
+    m1 = engine.zeros(1 << vY)
+    for X, W, (xv, wv, yv), lj, lk, li in insts:
+        J, K, I = 1 << lj, 1 << lk, 1 << li
+        xd = engine.gather_fn(slice1(engine, X), I * J, lambda u: _view_index(xv, {S_J: u & (J - 1), S_A: u >> lj}))
+        wd = engine.gather_fn(slice1(engine, W), J * K, lambda u: _view_index(wv, {S_J: u >> lk, S_A: u & (K - 1)}))
+        rows = engine.concat([engine.matvec(wd, J, K, engine.slice(xd, i * J, J), False) for i in range(I)])
+        m1 = engine.scatter_fn(m1, K * I, lambda u: _view_index(yv, {S_A: u & (K - 1), S_I: u >> lk}), rows)
+    return mk_linked(engine, zc, vY, m1)
+
+
+def imm_prove_views(engine, zc, tr, X, W, Y, lj, lk, li, R, Q, ledger, views=None):
+    """p3imm::prove with the zk switch on for operand views into larger committed grids (per-head attention matmuls): the
+    broadcast columns read the augmented grids through the views, every claim sits at the view's point extended by the
+    chain's extra coordinates (expt).  Composed mode only (shared ledger; no tail)."""
+    from .p3 import S_A, S_I, S_J, view_point
+    xv, wv, yv = views or direct_views(lj, lk, li)
+    tr.absorb("imm-dims", struct.pack("<III", lj, lk, li))
+    tr.absorb("imm-X", X.root)
+    tr.absorb("imm-W", W.root)
+    tr.absorb("imm-Y", Y.root)
+    z = [tr.chal() for _ in range(lk + li)]
+    zex = tr.chal()
+    yY = claimc(engine, tr, ledger, Y, xpt(zc, view_point(yv, z[:lk], z[lk:], S_A, S_I), zex))
+    lt = lj + lk + li
+    e_p, eX, eW = zc.e_of(lt), zc.e_of(X.vreal), zc.e_of(W.vreal)
+    N = 1 << (lt + e_p)
+    J, K, I = 1 << lj, 1 << lk, 1 << li
+    mX, mW = (1 << min(eX, e_p)) - 1, (1 << min(eW, e_p)) - 1
+    eqv = engine.build_eq_gpu(np.array(z + [zex] + [0] * (e_p - 1), dtype=np.uint64))
+    cols = [engine.bcast_rows(eqv, lj),
+            engine.gather_fn(X.dev, N, lambda u: _view_index(xv, {S_J: u & (J - 1), S_A: (u >> (lj + lk)) & (I - 1)})
+                             | (((u >> lt) & mX) << X.vreal)),
+            engine.gather_fn(W.dev, N, lambda u: _view_index(wv, {S_J: u & (J - 1), S_A: (u >> lj) & (K - 1)})
+                             | (((u >> lt) & mW) << W.vreal))]
+    r, msgs, _, blind = sc5z(engine, zc, tr, "imm-sc", lt, cols, [(1, (1, 2))], 0, R, ledger)
+    rj, rk, ri = r[:lj], r[lj:lj + lk], r[lj + lk:lt]
+    yX = claimc(engine, tr, ledger, X, expt(zc, view_point(xv, rj, ri), r, lt))
+    yW = claimc(engine, tr, ledger, W, expt(zc, view_point(wv, rj, rk), r, lt))
+    out = struct.pack("<III", lj, lk, li) + np.ascontiguousarray(msgs, dtype=np.uint64).tobytes()
+    return out + struct.pack("<QQQ", yY, yX, yW) + blind + struct.pack("<I", 0)
+
+
+def itf_commit_all(engine, zc, c, w, Wt, R, col):
+    """p3itf::commit_all with the zk switch on (zkllm-src/p3_int_layer.cuh:343-415), in the reference's commitment order:
+    every chain grid, weight and gain with a fresh mask, the matmul accumulator grids with linked masks.  Returns {name: ZCol}
+    (weights under "w", accumulators under "acc")."""
+    from . import ig
+    ld, lT, ldff, lseq, ldh, la = c.ld, c.lT, c.ldff, c.lseq, c.ldh, c.la
+    le, lef, lez = ld + lT, ldff + lT, la + 2 * lseq
+    o = {"acc": [None] * 7}
+    com = lambda a: commit_col(engine, zc, col(a), R)
+    heads = [(h, b) for b in range(c.batch) for h in range(c.nh)]
+
+    def acc(i, vY, insts):
+        o["acc"][i] = commit_col(engine, zc, col(w["acc"][i]), R, mask=linked_acc_mask(engine, zc, vY, insts))
+
+    o["x0"] = com(w["x0"])
+    o["g1"], o["g2"] = com(Wt["g1"]), com(Wt["g2"])
+    o["w"] = [com(x) for x in Wt["w"]]
+    o["h1"] = com(w["h1"])
+    for i in (ig.W_Q, ig.W_K, ig.W_V):
+        acc(i, le, [(o["h1"], o["w"][i], direct_views(ld, ld, lT), ld, ld, lT)])
+    for k in ("yq", "yk", "yv", "rq", "rk"):
+        o[k] = com(w[k])
+    o["sc"] = commit_col(engine, zc, col(w["sc"]), R, mask=linked_acc_mask(
+        engine, zc, lez, [(o["rq"], o["rk"], ig.views_qk(c, h, b), ldh, lseq, lseq) for h, b in heads]))
+    o["z"], o["p"] = com(w["z"]), com(w["p"])
+    o["pva"] = commit_col(engine, zc, col(w["pva"]), R, mask=linked_acc_mask(
+        engine, zc, le, [(o["p"], o["yv"], ig.views_pv(c, h, b), lseq, ldh, lseq) for h, b in heads]))
+    o["at"] = com(w["at"])
+    acc(ig.W_O, le, [(o["at"], o["w"][ig.W_O], direct_views(ld, ld, lT), ld, ld, lT)])
+    for k in ("yo", "res1", "h2"):
+        o[k] = com(w[k])
+    for i in (ig.W_G, ig.W_U):
+        acc(i, lef, [(o["h2"], o["w"][i], direct_views(ld, ldff, lT), ld, ldff, lT)])
+    for k in ("gg", "uu", "mo"):
+        o[k] = com(w[k])
+    acc(ig.W_D, le, [(o["mo"], o["w"][ig.W_D], direct_views(ldff, ld, lT), ldff, ld, lT)])
+    o["yd"], o["out"] = com(w["yd"]), com(w["out"])
+    return o
+
+
+def itf_prove(engine, zc, tr, c, w, o, Wt, T, R, Q, col):
+    """p3itf::prove with the zk switch on (zkllm-src/p3_int_layer.cuh:452-581): the decoder layer's 26 + 2A sub-proofs in fixed
+    order on one transcript with one ledger and one lookup queue, one merged-lookup flush, the public input / output
+    bindings at zero-extended points, one blinded batched opening per size class.  Same serialised layout as the plain
+    layer proof, every part in its hiding form."""
+    from . import ig
+    ld, lT, ldff, lseq, ldh, la = c.ld, c.lT, c.ldff, c.lseq, c.ldh, c.la
+    le, lef, lez = ld + lT, ldff + lT, la + 2 * lseq
+    ledger, luq = ZLedger(), []
+    tr.absorb("itf-dims", struct.pack("<6I", c.seq, c.d, c.nh, c.dh, c.dff, c.batch))
+    for i in range(7):
+        luq.append({"W": [o["w"][i]], "idx": col(w["idxW"][i]), "tab": T["RS20"]})
+    luq.append({"W": [o["g1"]], "idx": col(w["idxG1"]), "tab": T["RS20"]})
+    luq.append({"W": [o["g2"]], "idx": col(w["idxG2"]), "tab": T["RS20"]})
+    luq.append({"W": [o["x0"]], "idx": col(w["idxX0"]), "tab": T["RS20"]})
+    subs = []
+    up = lambda wit: {k: ([col(x) for x in v] if isinstance(v, (list, tuple)) else col(v)) for k, v in wit.items() if k not in ("y", "p")}
+
+    def lift_any(a):
+        if isinstance(a, np.ndarray):
+            return ig.lift(a)
+        from . import ig_dev
+        return ig_dev.lift(a)
+
+    rms = lambda name, X, G, Y: subs.append(irms_prove(engine, zc, tr, T, X, G, Y, up(w[name]), lT, ld, R, Q, ledger, luq))
+    mm = lambda X, Wc, Y, lj, lk, li, views=None: subs.append(imm_prove_views(engine, zc, tr, X, Wc, Y, lj, lk, li, R, Q, ledger, views))
+
+    def irs(name, X, Y, lev, sf, rng):
+        y, L, iL, iY = w[name]
+        subs.append(irs_prove(engine, zc, tr, T, X, Y, ([col(l) for l in L], [col(i) for i in iL], col(iY) if iY is not None else None),
+                              lev, sf, rng, R, Q, ledger, luq))
+
+    def rope(name, Qc, Y):
+        y, rem, iR, iY, Cc, S2 = w[name]
+        subs.append(irope_prove(engine, zc, tr, T, (col(lift_any(Cc)), col(lift_any(S2)), ldh), Qc, Y, (col(rem), col(iR), col(iY)),
+                                lT, ld, R, Q, ledger, luq))
+
+    heads = [(h, b) for b in range(c.batch) for h in range(c.nh)]
+    rms("rms1", o["x0"], o["g1"], o["h1"])
+    for i in (ig.W_Q, ig.W_K, ig.W_V):
+        mm(o["h1"], o["w"][i], o["acc"][i], ld, ld, lT)
+    irs("rsq", o["acc"][ig.W_Q], o["yq"], le, 16, 1)
+    irs("rsk", o["acc"][ig.W_K], o["yk"], le, 16, 1)
+    irs("rsv", o["acc"][ig.W_V], o["yv"], le, 16, 1)
+    rope("rpq", o["yq"], o["rq"])
+    rope("rpk", o["yk"], o["rk"])
+    for h, b in heads:
+        mm(o["rq"], o["rk"], o["sc"], ldh, lseq, lseq, ig.views_qk(c, h, b))
+    irs("rsz", o["sc"], o["z"], lez, c.sfz, 2)
+    subs.append(ismx_prove(engine, zc, tr, T, o["z"], o["p"], up(w["smx"]), la, lseq, R, Q, ledger, luq))
+    for h, b in heads:
+        mm(o["p"], o["yv"], o["pva"], lseq, ldh, lseq, ig.views_pv(c, h, b))
+    irs("rsat", o["pva"], o["at"], le, 16, 1)
+    mm(o["at"], o["w"][ig.W_O], o["acc"][ig.W_O], ld, ld, lT)
+    irs("rso", o["acc"][ig.W_O], o["yo"], le, 16, 1)
+    subs.append(iadd_prove(engine, zc, tr, T, o["x0"], o["yo"], o["res1"], col(w["idxRes1"]), le, R, Q, ledger, luq))
+    rms("rms2", o["res1"], o["g2"], o["h2"])
+    for i in (ig.W_G, ig.W_U):
+        mm(o["h2"], o["w"][i], o["acc"][i], ld, ldff, lT)
+    irs("rsg", o["acc"][ig.W_G], o["gg"], lef, 16, 1)
+    irs("rsu", o["acc"][ig.W_U], o["uu"], lef, 16, 1)
+    sil, rem, mo, iG, iR, iM = w["swg"]
+    subs.append(iswg_prove(engine, zc, tr, T, o["gg"], o["uu"], o["mo"], (col(sil), col(rem), col(iG), col(iR), col(iM)), lef, R, Q,
+                           ledger, luq))
+    mm(o["mo"], o["w"][ig.W_D], o["acc"][ig.W_D], ldff, ld, lT)
+    irs("rsd", o["acc"][ig.W_D], o["yd"], le, 16, 1)
+    subs.append(iadd_prove(engine, zc, tr, T, o["res1"], o["yd"], o["out"], col(w["idxOut"]), le, R, Q, ledger, luq))
+    lug = lu_flush(engine, zc, tr, luq, ledger, R)
+    ioin = claimc(engine, tr, ledger, o["x0"], zpt(zc, [tr.chal() for _ in range(le)]))
+    ioout = claimc(engine, tr, ledger, o["out"], zpt(zc, [tr.chal() for _ in range(le)]))
+    batches = tail_prove(engine, zc, tr, ledger, R, Q, "itf-bo")
+    blob = lambda b: struct.pack("<I", len(b)) + b
+    roots = [o["x0"].root, o["h1"].root] + [a.root for a in o["acc"]] + [o[k].root for k in
+             ("yq", "yk", "yv", "rq", "rk", "sc", "z", "p", "pva", "at", "yo", "res1", "h2", "gg", "uu", "mo", "yd", "out")]
+    out = struct.pack("<6I", c.seq, c.d, c.nh, c.dh, c.dff, c.batch) + b"".join(blob(s) for s in subs) + b"".join(roots)
+    out += struct.pack("<I", len(lug)) + b"".join(blob(b) for b in lug) + struct.pack("<QQ", ioin, ioout)
+    return out + struct.pack("<I", len(batches)) + b"".join(blob(b) for b in batches)
