@@ -663,7 +663,12 @@ def run_suite_layer(args):
                      (128, 1024, 16, 64, 4096, 1)),
               "c4": ("BASELINE configs[4]: TinyLlama-1.1B-shaped layer, seq 512 (hidden 2048, 32 heads of 64 with each KV head "
                      "replicated 8x, MLP 5632 -> 8192)", (512, 2048, 32, 64, 8192, 1)),
+              "m": ("mid shape: seq 64, hidden 256, 4 heads of 64, MLP 1024", (64, 256, 4, 64, 1024, 1)),
               "tiny": ("smoke shape", (16, 32, 2, 16, 64, 1))}
+    zkm = zk.zkm if args.zk else None
+    zseed = 0xC0FFEE
+    if args.zk:
+        from zkm_helpers import ref_zk
     for key in args.layer_shapes.split(","):
         name, dims = shapes[key]
         c = ig.Config(*dims)
@@ -694,29 +699,40 @@ def run_suite_layer(args):
         wcol = (lambda a: a) if on_dev else col
         Wc = w["dev_W"] if on_dev else Wt
         best = None
-        prover.keep_trees = not args.no_keep_trees     # codewords and Merkle trees of the layer stay in HBM for the openings
+        prover.keep_trees = not args.no_keep_trees and not args.zk    # codewords and Merkle trees of the layer stay in HBM for the openings
         for rep in range(args.layer_reps):
             prover.release_kept()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            o = ig.itf_commit_all(prover, w, Wc, R, wcol)
+            if args.zk:      # hiding mode: masked salted commitments, blinded chains, blinded openings (the reference's zk switch)
+                zc = zkm.ZkCtx(seed=zseed, Q=Q)
+                o = zkm.itf_commit_all(prover, zc, c, w, Wc, R, wcol)
+            else:
+                o = ig.itf_commit_all(prover, w, Wc, R, wcol)
             torch.cuda.synchronize()
             t1 = time.perf_counter()
             tr = zk.Transcript("itf-layer")
-            pf = ig.itf_prove(prover, tr, c, w, o, Wt, T, R, Q, wcol)
+            pf = zkm.itf_prove(prover, zc, tr, c, w, o, Wt, T, R, Q, wcol) if args.zk else ig.itf_prove(prover, tr, c, w, o, Wt, T, R, Q, wcol)
             torch.cuda.synchronize()
             t2 = time.perf_counter()
             if best is None or t2 - t1 < best[1]:
                 best = (t1 - t0, t2 - t1)
         out_host = zk.p3.to_host(w["out"]) if on_dev else w["out"]
-        line = {"suite": name, "dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), dims)), "R": R, "Q": Q,
-                ("witness_device_s" if on_dev else "witness_host_s"): t_wit, "commit_s": best[0], "prove_s": best[1],
+        line = {"suite": name + (" [hiding mode]" if args.zk else ""), "dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), dims)),
+                "R": R, "Q": Q, ("witness_device_s" if on_dev else "witness_host_s"): t_wit, "commit_s": best[0], "prove_s": best[1],
                 "prove_s_per_layer": best[1], "proof_MB": len(pf) / 1048576.0}
         if ref is not None:
             from ig_helpers import ref_itf_prove, ref_itf_verify
-            rpf, rst, grid, ms = ref_itf_prove(ref, zk.Transcript("itf-layer").state, c, x0, Wt, R, Q)
-            wroots = [x[1] for x in o["w"]] + [o["g1"][1], o["g2"][1]]
-            ok, st = ref_itf_verify(ref, zk.Transcript("itf-layer").state, c, x0, o["x0"][1], wroots, Wt, out_host, R, Q, pf)
+            root_of = (lambda x: x.root) if args.zk else (lambda x: x[1])
+            wroots = [root_of(x) for x in o["w"]] + [root_of(o["g1"]), root_of(o["g2"])]
+            if args.zk:
+                ref_zk(ref, True, Q, zseed, 22)
+            try:
+                rpf, rst, grid, ms = ref_itf_prove(ref, zk.Transcript("itf-layer").state, c, x0, Wt, R, Q)
+                ok, st = ref_itf_verify(ref, zk.Transcript("itf-layer").state, c, x0, root_of(o["x0"]), wroots, Wt, out_host, R, Q, pf)
+            finally:
+                if args.zk:
+                    ref_zk(ref, False)
             line.update({"reference_witness_s": ms[0] / 1e3, "reference_commit_s": ms[1] / 1e3, "reference_prove_s": ms[2] / 1e3,
                          "speedup_prove_vs_reference": ms[2] / 1e3 / best[1],
                          "speedup_commit_plus_prove_vs_reference": (ms[1] + ms[2]) / 1e3 / (best[0] + best[1]),
@@ -1058,6 +1074,7 @@ def main():
     ap.add_argument("--suite", action="store_true", help="extra single-GPU microbench lines (not the driver line)")
     ap.add_argument("--profile-case", default=None, help="one small kernel-family invocation (for ncu captures)")
     ap.add_argument("--host-witness", action="store_true", help="layer suites: build the witness chain with numpy on the host")
+    ap.add_argument("--zk", action="store_true", help="layer suite: prove in hiding mode (the reference's zk switch) beside its zk prover")
     ap.add_argument("--no-keep-trees", action="store_true", help="layer suites: recompute codewords and trees in the openings")
     ap.add_argument("--suite-model", action="store_true", help="22 independent TinyLlama-shaped layer proofs over --gpus N")
     ap.add_argument("--model-layers", type=int, default=22)

@@ -1119,6 +1119,8 @@ struct M4 { gl_t s[4]; };
 struct M5 { gl_t s[5]; };
 }  // namespace
 
+static const char* g_last_why = "";
+
 extern "C" {
 
 // ---- field ----
@@ -1541,6 +1543,7 @@ int ref_itf_verify(uint8_t st[32], const uint32_t dims[6], const uint64_t* x0, c
                    const int32_t* ct, const int32_t* sn, const uint64_t* outp, uint32_t R, uint32_t Q, const uint8_t* proof,
                    size_t len) {
     p3itf::TfProof pf;
+    g_last_why = "proof bytes do not parse";
     if (!itf_deserialize(proof, len, pf)) return 0;
     p3itf::Config cfg;
     cfg.seq = dims[0]; cfg.d = dims[1]; cfg.nh = dims[2]; cfg.dh = dims[3]; cfg.dff = dims[4]; cfg.batch = dims[5];
@@ -1554,9 +1557,12 @@ int ref_itf_verify(uint8_t st[32], const uint32_t dims[6], const uint64_t* x0, c
     const char* why = nullptr;
     bool ok = p3itf::verify(tr, pf, ig_tables(cfg.d, cfg.btop()), cfg, x0v, hash_from(rX0), wr,
                             rope_pub(ct, sn, cfg.lseq(), cfg.ldh()), outv, Q, R, &why);
+    g_last_why = why ? why : "";
     memcpy(st, tr.state, 32);
     return ok ? 1 : 0;
 }
+// the reason string of the last ref_itf_verify call (the reference's `why`), for test diagnostics
+const char* ref_last_why() { return g_last_why; }
 
 // ---- integer matmul gadget: the reference's host-only verifier (p3_int_gadgets.cuh:608-655) ----
 int ref_imm_verify(uint8_t st[32], const uint8_t rootX[32], const uint8_t rootW[32], const uint8_t rootY[32],

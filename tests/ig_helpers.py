@@ -87,6 +87,9 @@ def ref_itf_verify(ref, st, c, x0, rX0, wroots, Wt, out, R, Q, proof):
     x0c, outc, ct, sn = (np.ascontiguousarray(a) for a in (x0, out, Wt["ct"], Wt["st"]))
     ok = ref.lib.ref_itf_verify(s, dims, vp(x0c), rX0, b"".join(wroots), vp(ct), vp(sn), vp(outc), C.c_uint32(R), C.c_uint32(Q),
                                 bytes(proof), C.c_size_t(len(proof)))
+    if not ok and hasattr(ref.lib, "ref_last_why"):
+        ref.lib.ref_last_why.restype = C.c_char_p
+        ref.last_why = (ref.lib.ref_last_why() or b"").decode()
     return bool(ok), bytes(s)
 
 

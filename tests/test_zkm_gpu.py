@@ -293,7 +293,7 @@ def test_zk_integer_layer_equals_reference_prover(orc, ref, zk, prover, dims):
     wroots = [x.root for x in o["w"]] + [o["g1"].root, o["g2"].root]
     st0 = zk.Transcript("itf-layer").state
     ok, st = _with_zk(ref, lambda: ref_itf_verify(ref, st0, c, x0, o["x0"].root, wroots, Wt, w["out"], R, Q, pf))
-    assert ok and st == tr.state
+    assert ok and st == tr.state, getattr(ref, "last_why", "")
     bad = bytearray(pf)
     bad[len(pf) // 2] ^= 1
     assert not _with_zk(ref, lambda: ref_itf_verify(ref, st0, c, x0, o["x0"].root, wroots, Wt, w["out"], R, Q, bytes(bad)))[0]

@@ -509,9 +509,7 @@ def irs_prove(engine, zc, tr, tables, X, Y, wit, le, sf, rng, R, Q, ledger=None,
     ys = [claimc(engine, tr, ledger, col, r) for col in [X, Y] + CL]
     out = struct.pack("<IIII", le, sf, nl, rng) + b"".join(c.root for c in CL)
     out += np.ascontiguousarray(msgs, dtype=np.uint64).tobytes() + struct.pack("<%dQ" % len(ys), *ys) + blind
-    if own:
-        out += _tail(engine, zc, tr, luq, ledger, R, Q, "irs-bo")
-    return out
+    return out + (_tail(engine, zc, tr, luq, ledger, R, Q, "irs-bo") if own else _EMPTY_TAIL)
 
 
 def _tail(engine, zc, tr, luq, ledger, R, Q, tag):
