@@ -11,6 +11,7 @@
   prove_super / lu_flush p3lu::prove_super / lu_flush, zk branches  zkllm-src/p3_logup.cuh:1357-1956
   irs_prove / iadd_prove / iswg_prove   p3irs / p3iadd / p3iswg::prove with the zk switch on   p3_int_gadgets.cuh:282-340, :712-737, :1790-1832
   irope_prove / irms_prove / ismx_prove p3irope / p3irms / p3ismx::prove with the zk switch on p3_int_gadgets.cuh:1275-1322, :918-1047, :1514-1643
+  linked_acc_mask / itf_commit_all / imm_prove_views / itf_prove   p3itf::commit_acc, commit_all, prove with the zk switch on   zkllm-src/p3_int_layer.cuh:331-415, :452-581
 
 Every random draw follows the reference's order (one counter-mode seed per draw, zkllm-src/p3_zkc.cuh:118-123), so with
 the same master seed the proofs are the reference prover's bytes.  The device work is the library's: mask and blind
