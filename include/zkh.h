@@ -169,6 +169,14 @@ ZKH_API int zkh_sumcheck_zerocheck(zkh_ctx* ctx, const uint64_t* const* cols_dev
 ZKH_API int zkh_sumcheck_zerocheck_blind(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
                                  const uint64_t* prog, int nwords, const uint64_t* fix, const char* tag, uint8_t state[32],
                                  uint64_t* msgs, uint64_t* chals, uint64_t* finals, uint64_t* pref_out);
+/* The first `rounds` rounds of such a chain when its later variables belong to other columns (the factored matmul chain of
+ * p3imm, whose summand eq * X * W splits over the index groups): messages, challenges and the transcript advance as in the
+ * full chain; left receives, column after column, the 2^(logn - rounds) values that remain after the last bind.  fix: NULL or
+ * the structured blind's rows of THESE rounds; pref_in / pref_out carry its running prefix from one partial chain to the next.
+ * Programs of the small engine only (<= 32 columns, <= 120 terms). */
+ZKH_API int zkh_sumcheck_zerocheck_partial(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn, uint32_t rounds,
+                                   const uint64_t* prog, int nwords, const uint64_t* fix, uint64_t pref_in, const char* tag,
+                                   uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* left, uint64_t* pref_out);
 /* Column and coefficient counts of a ZKH_F_HW_* summand (ZKH_ERR_ARG for any other id). */
 ZKH_API int zkh_sumcheck_wide_shape(int functor, int* nc, int* nlam);
 

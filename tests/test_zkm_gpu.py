@@ -304,3 +304,34 @@ def test_zk_integer_layer_equals_reference_prover(orc, ref, zk, prover, dims):
         ref_zk(ref, False)
     assert (grid == w["out"]).all()
     assert rst == tr.state and rpf == pf
+
+
+@pytest.mark.parametrize("logn,rounds,with_table", [(6, 3, True), (5, 5, True), (7, 1, False), (4, 3, False), (9, 8, True)])
+def test_partial_zero_check_matches_python_evaluation(orc, zk, prover, logn, rounds, with_table):
+    """A chain stopped before its last variables: messages, challenges, what every column still holds, the blind's prefix."""
+    from conftest import lcg_cols
+    nc = 4
+    cols = lcg_cols(orc, 1 << logn, nc, 5 * logn + rounds)
+    terms = [(3, (1, 2)), (7, (3,)), (5, (2,), True)]
+    rng = np.random.default_rng(rounds)
+    table = [[int(v) for v in rng.integers(1, GL_P, 7, dtype=np.uint64)] for _ in range(rounds)] if with_table else None
+    tr1, tr2 = zk.Transcript("zp"), zk.Transcript("zp")
+    a = prover.sc_prove_zc_partial(tr1, "t", [zk.p3.to_device(c) for c in cols], terms, 17, rounds, table, 12345)
+    b = OracleZkEngine(orc).sc_prove_zc_partial(tr2, "t", [_Arr(c) for c in cols], terms, 17, rounds, table, 12345)
+    assert tr1.state == tr2.state and a[3] == b[3]
+    assert all((np.asarray(u) == np.asarray(v)).all() for u, v in zip(a[:3], b[:3]))
+
+
+@pytest.mark.parametrize("dims,sblind_min", [((3, 2, 3), 5), ((5, 4, 4), 9), ((0, 4, 4), 6)])
+def test_factored_matmul_chain_equals_materialised_chain_on_cuda(orc, zk, prover, dims, sblind_min):
+    R, Q, seed = 1, 24, 77
+    lj, lk, li = dims
+    x, w, y = matmul_instance(orc, lj, lk, li, seed)
+    out = []
+    for materialise in (True, False):
+        zc = zk.zkm.ZkCtx(seed=seed, Q=Q, sblind_min=sblind_min)
+        zc.materialise = materialise
+        X, W, Y = commit3(zk, prover, zc, x, w, y, dims, R, zk.p3.to_device)
+        tr = zk.Transcript("imm-t")
+        out.append((zk.zkm.imm_prove(prover, zc, tr, X, W, Y, lj, lk, li, R, Q), tr.state))
+    assert out[0] == out[1]

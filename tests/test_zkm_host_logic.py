@@ -95,3 +95,19 @@ def test_zk_rescale_accepted_by_reference_verifier(orc, ref, zk, le, sf, rng, sb
         bad[off] ^= 1
         assert not ref_irs_verify_zk(ref, st0, X.root, Y.root, le, sf, rng, R, Q, bytes(bad), sblind_min)[0]
 
+
+
+@pytest.mark.parametrize("lj,lk,li,sblind_min", [(3, 2, 3, 5), (4, 4, 2, 8), (2, 3, 4, 4), (0, 3, 3, 4), (3, 0, 3, 4)])
+def test_factored_matmul_chain_equals_materialised_chain(orc, ref, zk, lj, lk, li, sblind_min):
+    """Structured blinds: the chain split over the index groups (three short product chains on partially evaluated operands
+    and the slice rounds) gives the proof bytes of the chain over the materialised product domain."""
+    R, Q = 1, 24
+    out = []
+    for materialise in (True, False):
+        eng, zc, X, W, Y = zk_matmul(orc, zk, lj, lk, li, 11 + lj, R, sblind_min)
+        zc.materialise = materialise
+        tr = zk.Transcript("imm-t")
+        out.append((zk.zkm.imm_prove(eng, zc, tr, X, W, Y, lj, lk, li, R, Q), tr.state, [X.root, W.root, Y.root]))
+    assert out[0] == out[1]
+    ok, st = ref_imm_verify_zk(ref, zk.Transcript("imm-t").state, out[1][2], lj, lk, li, R, Q, out[1][0], sblind_min)
+    assert ok and st == out[1][1]

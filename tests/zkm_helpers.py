@@ -63,6 +63,10 @@ class OracleZkEngine(OracleGadgetEngine):
         tr.state = st
         return pf
 
+    def sc_prove_zc_partial(self, tr, tag, cols, terms, konst, rounds, table=None, pref=0):
+        """The first rounds of a zero-check chain, optionally under the structured blind's table rows of these rounds."""
+        return _partial(self, tr, tag, cols, terms, konst, rounds, table, pref)
+
     def sc_prove_zc_blind(self, tr, tag, cols, terms, konst, table):
         """The zero-check whose round messages gain A * (pref + g(t)) + B from the table rows [c0..c4, A, B]."""
         geval = lambda c, t: sum(int(c[k]) * pow(t, k, GL_P) for k in range(5)) % GL_P
@@ -81,6 +85,26 @@ class OracleZkEngine(OracleGadgetEngine):
                             dtype=np.uint64) for c in cur]
         return (np.array(chals, dtype=np.uint64), np.array(msgs, dtype=np.uint64), np.array([c[0] for c in cur], dtype=np.uint64),
                 pref)
+
+
+def _partial(engine, tr, tag, cols, terms, konst, rounds, table, pref):
+    geval = lambda c, t: sum(int(c[k]) * pow(t, k, GL_P) for k in range(5)) % GL_P
+    cur = [c.a for c in cols]
+    msgs, chals = [], []
+    for rd in range(rounds):
+        s = _round_message(cur, terms, konst)
+        if table is not None:
+            row = table[rd]
+            s = [(m + int(row[5]) * ((pref + geval(row, t)) % GL_P) + int(row[6])) % GL_P for t, m in enumerate(s)]
+        tr.absorb(tag, np.array(s, dtype=np.uint64).tobytes())
+        a = tr.chal()
+        if table is not None:
+            pref = (pref + geval(table[rd], a)) % GL_P
+        msgs.append(s)
+        chals.append(a)
+        cur = [np.array([(int(c[2 * i]) + a * (int(c[2 * i + 1]) - int(c[2 * i]))) % GL_P for i in range(len(c) // 2)], dtype=np.uint64)
+               for c in cur]
+    return np.array(chals, dtype=np.uint64), np.array(msgs, dtype=np.uint64), np.stack(cur), pref
 
 
 def _round_message(cols, terms, konst):

@@ -63,6 +63,7 @@ def load_library():
         "zkh_sumcheck_wide_shape": (i, [i, vp, vp]),
         "zkh_sumcheck_zerocheck": (i, [vp, vp, i, u32, vp, i, C.c_char_p, vp, vp, vp, vp]),
         "zkh_sumcheck_zerocheck_blind": (i, [vp, vp, i, u32, vp, i, vp, C.c_char_p, vp, vp, vp, vp, vp]),
+        "zkh_sumcheck_zerocheck_partial": (i, [vp, vp, i, u32, u32, vp, i, vp, u64, C.c_char_p, vp, vp, vp, vp, vp]),
         "zkh_ig_table": (i, [i, u32, vp, vp]),
         "zkh_fr_eq_build": (i, [vp, vp, u32, vp]),
         "zkh_fr_fold": (i, [vp, vp, u64, vp, vp]),

@@ -12,6 +12,7 @@
 // A thread keeps one pair of every column (value and difference) in registers; at 57 columns the
 // compiler spills part of that to local memory, which stays in L1.  These kernels are bound by the
 // integer pipe (tens of field multiplications per row and evaluation point), not by HBM.
+#include <algorithm>
 #include <vector>
 #include "sumcheck.cuh"
 #include "hawkeye_fn.cuh"
@@ -77,6 +78,15 @@ scw_round_kernel(WidePtrs P, size_t items, int first, ZkhCtl* ctl, gl_t* partial
 __global__ void scw_finals_kernel(WidePtrs P, int nc, const gl_t* chal, gl_t* out) {
     int k = threadIdx.x;
     if (k < nc) out[k] = gl_lerp(P.in[k][0], P.in[k][1], *chal);
+}
+
+// after a chain stopped early: out[k][p] = lerp(in[k][2p], in[k][2p+1], a) for the nleft pairs every column still holds
+__global__ void zc_left_kernel(WidePtrs P, int nc, size_t nleft, const gl_t* chal, gl_t* out) {
+    const gl_t a = *chal;
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < (size_t)nc * nleft; t += (size_t)gridDim.x * blockDim.x) {
+        const size_t k = t / nleft, p = t - k * nleft;
+        out[t] = gl_lerp(P.in[k][2 * p], P.in[k][2 * p + 1], a);
+    }
 }
 
 static size_t scw_workspace_bytes(int nc, uint32_t logn) {
@@ -202,7 +212,7 @@ zc_round_kernel(WidePtrs P, size_t items, int first, const ZkhZcProg* prog_g, Zk
 
 template <int NCMAX>
 static int zc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t logn, const ZkhZcProg* prog_dev,
-                        const ZkhTag& tag, gl_t* finals_dev) {
+                        const ZkhTag& tag, gl_t* finals_dev, uint32_t rounds) {
     cudaStream_t s = ctx->stream;
     ZkhCtl* ctl = ctx->d_ctl;
     const size_t n = (size_t)1 << logn;
@@ -225,7 +235,7 @@ static int zc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t lo
     gl_t* bufB = (gl_t*)((char*)ctx->ws + zkh_align((size_t)nc * (n / 2 + 1) * 8));
     gl_t* dst = bufA;
     size_t cur_n = n;
-    for (uint32_t r = 1; r < logn; r++) {
+    for (uint32_t r = 1; r < rounds; r++) {
         const size_t out_n = cur_n / 2;
         for (int k = 0; k < nc; k++) P.out[k] = dst + (size_t)k * out_n;
         zc_round_kernel<NCMAX><<<grid_for(cur_n / 4), SCW_THREADS, 0, s>>>(
@@ -235,7 +245,9 @@ static int zc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t lo
         dst = (dst == bufA) ? bufB : bufA;
         cur_n = out_n;
     }
-    scw_finals_kernel<<<1, SCW_MAXC, 0, s>>>(P, nc, ctl->chals + (logn - 1), finals_dev);
+    const size_t nleft = n >> rounds;       // 1 after a full chain; more when the caller continues on other columns
+    zc_left_kernel<<<(unsigned)std::min<size_t>(((size_t)nc * nleft + 255) / 256, 1024), 256, 0, s>>>(P, nc, nleft, ctl->chals + (rounds - 1),
+                                                                                                 finals_dev);
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "zero-check sumcheck launch");
 }
 
@@ -433,8 +445,10 @@ extern "C" int zkh_sumcheck_wide(zkh_ctx* ctx, int functor, const uint64_t* cons
 // packed = degree | idx0 << 8 | idx1 << 16 | idx2 << 24
 static int zerocheck_impl(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn,
                           const uint64_t* prog, int nwords, const char* tag, uint8_t state[32], uint64_t* msgs,
-                          uint64_t* chals, uint64_t* finals, const uint64_t* fix, uint64_t* pref_out) {
+                          uint64_t* chals, uint64_t* finals, const uint64_t* fix, uint64_t* pref_out, uint32_t rounds = 0,
+                          uint64_t pref_in = 0) {
     if (!ctx) return ZKH_ERR_ARG;
+    if (rounds == 0) rounds = logn;
     if (!cols_dev || !prog || !tag || !state || !msgs || !chals) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: null pointer");
     if (nc < 1 || nc > ZCX_MAXC) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: 1..224 columns");
     if (logn < 1 || logn > 34) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: logn must be 1..34");
@@ -443,6 +457,9 @@ static int zerocheck_impl(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc,
         return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: malformed program (at most 2048 terms)");
     const uint32_t nterms = (uint32_t)prog[0];
     const bool large = nc > 32 || nterms > ZC_MAXTERMS;
+    if (rounds > logn || pref_in >= GL_P) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: rounds beyond the chain or pref not canonical");
+    if (rounds < logn && large) return zkh_fail(ctx, ZKH_ERR_LIMIT, "zero-check: partial chains run on the small engine (<= 32 columns, 120 terms)");
+    const size_t nleft = ((size_t)1 << logn) >> rounds;
     if (prog[1] >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: constant not canonical");
     ZkhZcProg hp;          // staging copies (pageable memory: the asynchronous copies below return after staging them)
     std::vector<uint8_t> hx;
@@ -475,7 +492,7 @@ static int zerocheck_impl(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc,
     ZKH_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t n = (size_t)1 << logn;
     const size_t szA = zkh_align((size_t)nc * (n / 2 + 1) * 8), szB = zkh_align((size_t)nc * (n / 4 + 1) * 8);
-    const size_t szF = zkh_align((size_t)nc * 8);
+    const size_t szF = zkh_align((size_t)nc * nleft * 8);
     const size_t szP = zkh_align(large ? hx.size() : sizeof(ZkhZcProg)), szT = zkh_align((size_t)logn * 2 * nc * sizeof(void*));
     const size_t szX = zkh_align((8 + 8 * (size_t)logn) * 8);
     ZKH_TRY(zkh_ws_reserve(ctx, szA + szB + szF + szP + szT + szX));
@@ -483,7 +500,8 @@ static int zerocheck_impl(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc,
     std::vector<gl_t> hfix;
     if (fix) {
         hfix.assign(8 + 8 * (size_t)logn, 0);
-        for (uint32_t r = 0; r < logn; r++)
+        hfix[0] = pref_in;
+        for (uint32_t r = 0; r < rounds; r++)
             for (int k = 0; k < 7; k++) {
                 if (fix[7 * (size_t)r + k] >= GL_P) return zkh_fail(ctx, ZKH_ERR_DOMAIN, "zero-check: blind coefficient not canonical");
                 hfix[8 + 8 * (size_t)r + k] = fix[7 * (size_t)r + k];
@@ -506,18 +524,18 @@ static int zerocheck_impl(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc,
                                   cudaMemcpyHostToDevice, ctx->stream));
     const ZkhTag t = zkh_make_tag(tag);
     int rc = large ? zcx_enqueue(ctx, cols_dev, nc, nterms, logn, prog_dev, ptr_dev, t, finals_dev)
-           : nc <= 8 ? zc_enqueue_t<8>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev)
-           : nc <= 16 ? zc_enqueue_t<16>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev)
-                      : zc_enqueue_t<32>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev);
+           : nc <= 8 ? zc_enqueue_t<8>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev, rounds)
+           : nc <= 16 ? zc_enqueue_t<16>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev, rounds)
+                      : zc_enqueue_t<32>(ctx, cols_dev, nc, logn, (const ZkhZcProg*)prog_dev, t, finals_dev, rounds);
     ZKH_TRY(rc);
     ZKH_CUDA(ctx, cudaMemcpyAsync(h, ctx->d_ctl, sizeof(ZkhCtl), cudaMemcpyDeviceToHost, ctx->stream));
     if (finals)
-        ZKH_CUDA(ctx, cudaMemcpyAsync(finals, finals_dev, (size_t)nc * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        ZKH_CUDA(ctx, cudaMemcpyAsync(finals, finals_dev, (size_t)nc * nleft * 8, cudaMemcpyDeviceToHost, ctx->stream));
     if (fix && pref_out) ZKH_CUDA(ctx, cudaMemcpyAsync(pref_out, fix_dev, 8, cudaMemcpyDeviceToHost, ctx->stream));
     ZKH_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (h->err) return zkh_fail(ctx, ZKH_ERR_DEVICE, "zero-check: device error flag set");
-    memcpy(msgs, h->msgs, (size_t)logn * SCW_NT * 8);
-    memcpy(chals, h->chals, (size_t)logn * 8);
+    memcpy(msgs, h->msgs, (size_t)rounds * SCW_NT * 8);
+    memcpy(chals, h->chals, (size_t)rounds * 8);
     digest_to_bytes(h->st, state);
     return ZKH_OK;
 }
@@ -537,4 +555,18 @@ extern "C" int zkh_sumcheck_zerocheck_blind(zkh_ctx* ctx, const uint64_t* const*
     if (!ctx) return ZKH_ERR_ARG;
     if (!fix || !pref_out) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: the blinded chain needs its table and pref_out");
     return zerocheck_impl(ctx, cols_dev, nc, logn, prog, nwords, tag, state, msgs, chals, finals, fix, pref_out);
+}
+
+// The first `rounds` rounds of a chain whose later variables belong to other columns (a factored product domain): messages,
+// challenges and transcript advance as in the full chain; `left` receives, per column, the 2^(logn - rounds) values that remain
+// after the last bind.  fix (optional): the structured blind's table rows of THESE rounds (7 words each), pref_in / pref_out
+// its running prefix, carried from one partial chain to the next.
+extern "C" int zkh_sumcheck_zerocheck_partial(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nc, uint32_t logn, uint32_t rounds,
+                                              const uint64_t* prog, int nwords, const uint64_t* fix, uint64_t pref_in,
+                                              const char* tag, uint8_t state[32], uint64_t* msgs, uint64_t* chals,
+                                              uint64_t* left, uint64_t* pref_out) {
+    if (!ctx) return ZKH_ERR_ARG;
+    if (rounds < 1 || !left) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: a partial chain needs 1..logn rounds and the buffer for what is left");
+    if (fix && !pref_out) return zkh_fail(ctx, ZKH_ERR_ARG, "zero-check: the blinded chain needs pref_out");
+    return zerocheck_impl(ctx, cols_dev, nc, logn, prog, nwords, tag, state, msgs, chals, left, fix, pref_out, rounds, pref_in);
 }

@@ -704,6 +704,25 @@ class Prover:
         tr.state = bytes(st)
         return chals, msgs, fin, int(pref.value)
 
+    def sc_prove_zc_partial(self, tr, tag, dcols, terms, konst, rounds, table=None, pref=0):
+        """The first ``rounds`` rounds of a zero-check chain (zkh_sumcheck_zerocheck_partial): returns (r, msgs, left, pref) with
+        left[k] the values column k still holds after the last bind.  table: the structured blind's rows of these rounds."""
+        nc = len(dcols)
+        logn = int(dcols[0].numel()).bit_length() - 1
+        ptrs = (C.c_uint64 * nc)(*[_ptr(t) for t in dcols])
+        prog = zc_program(terms, konst)
+        fix = np.ascontiguousarray(table, dtype=np.uint64).reshape(rounds, 7) if table is not None else None
+        msgs = np.zeros((rounds, 5), dtype=np.uint64)
+        chals = np.zeros(rounds, dtype=np.uint64)
+        left = np.zeros((nc, (1 << logn) >> rounds), dtype=np.uint64)
+        pout = C.c_uint64(0)
+        st = _buf32(tr.state)
+        self._ck(self._L.zkh_sumcheck_zerocheck_partial(self._h, ptrs, nc, logn, rounds, prog.ctypes.data, len(prog),
+                                                        fix.ctypes.data if fix is not None else 0, int(pref), tag.encode(), st,
+                                                        msgs.ctypes.data, chals.ctypes.data, left.ctypes.data, C.byref(pout)))
+        tr.state = bytes(st)
+        return chals, msgs, left, int(pout.value) if fix is not None else int(pref)
+
     def sc_prove_host(self, tr, tag, cols, functor, nt, par=()):
         """Same through host columns (numpy uint64): upload + prove + download in one call."""
         arrs = [np.ascontiguousarray(c, dtype=np.uint64) for c in cols]

@@ -224,10 +224,10 @@ def _geval(c, t):
     return acc
 
 
-def _sc5z_structured(engine, zc, tr, tag, v, cols, terms, konst, R, ledger):
-    """Structured blind g(x) = sum_j g_j(x_j), g_j uniform of degree 4 (zkllm-src/p3_hawkeye.cuh:1065-1139, :1172-1216): one
-    small committed coefficient column, a per-round additive term on the messages, and an inner-product sumcheck that
-    binds g(r) to the commitment."""
+def _sblind_begin(engine, zc, tr, v, R):
+    """Structured blind g(x) = sum_j g_j(x_j), g_j uniform of degree 4, for a chain of v rounds (zkllm-src/p3_hawkeye.cuh:
+    1065-1139): commits the coefficient column, absorbs its root and H, draws rho.  Returns the state the chain and the closing
+    step need; "table" holds per round the coefficients of g_rd, A_rd = rho 2^(v-1-rd), B_rd = rho 2^(v-2-rd) suf[rd+1]."""
     u = 8
     while (1 << u) < 5 * v + 64:
         u += 1
@@ -245,25 +245,109 @@ def _sc5z_structured(engine, zc, tr, tag, v, cols, terms, konst, R, ledger):
     rho = tr.chal()
     table = [sc[rd] + [rho * pow(2, v - 1 - rd, GL_P) % GL_P,
                        rho * pow(2, v - 2 - rd, GL_P) % GL_P * suf[rd + 1] % GL_P if rd + 1 < v else 0] for rd in range(v)]
-    r, msgs, fin, ystar = engine.sc_prove_zc_blind(tr, tag, list(cols), list(terms), konst, table)
-    r = [int(x) for x in r]
+    return {"v": v, "u": u, "W": W, "H": H, "table": table}
+
+
+def _sblind_end(engine, zc, tr, sb, r, ystar, ledger):
+    """Closing step of a structured-blind chain (zkllm-src/p3_hawkeye.cuh:1172-1216): g(r) is absorbed and bound to the committed
+    coefficient column by the inner-product sumcheck with Phi[5j + k] = r_j^k.  Returns the serialised Blind."""
+    from .p3 import F_PROD2
+    v, W = sb["v"], sb["W"]
     tr.absorb("sc5-yB", struct.pack("<Q", ystar))
-    # inner product of the augmented coefficient column with Phi[5j + k] = r_j^k
-    uf = zc.vfull(u)
+    uf = zc.vfull(sb["u"])
     phi = np.zeros(1 << uf, dtype=np.uint64)
     for j in range(v):
         p = 1
         for k in range(5):
             phi[5 * j + k] = p
             p = p * r[j] % GL_P
-    from .p3 import F_PROD2
     rip, ipm, ipf = engine.sc_prove_gpu(tr, "sc5-ip", [W.dev, engine.upload(phi)], F_PROD2, 3)
     yw = int(ipf[0])
     tr.absorb("sc5-yw", struct.pack("<Q", yw))
     ledger.add(W, [int(x) for x in rip], yw)
-    blind = struct.pack("<I", 6) + W.root + struct.pack("<QQ", H, ystar) + struct.pack("<I", uf) + \
+    return struct.pack("<I", 6) + W.root + struct.pack("<QQ", sb["H"], ystar) + struct.pack("<I", uf) + \
         np.ascontiguousarray(ipm, dtype=np.uint64).tobytes() + struct.pack("<Q", yw)
-    return r, msgs, fin, blind
+
+
+def _sc5z_structured(engine, zc, tr, tag, v, cols, terms, konst, R, ledger):
+    """The whole chain under a structured blind: the per-round term is added to the messages on the device."""
+    sb = _sblind_begin(engine, zc, tr, v, R)
+    r, msgs, fin, ystar = engine.sc_prove_zc_blind(tr, tag, list(cols), list(terms), konst, sb["table"])
+    r = [int(x) for x in r]
+    return r, msgs, fin, _sblind_end(engine, zc, tr, sb, r, ystar, ledger)
+
+
+def imm_chain_factored(engine, zc, tr, X, W, views, lj, lk, li, z, zex, R, ledger):
+    """The matmul chain of p3imm under a structured blind WITHOUT the 2^(lj+lk+li+e) product domain.  The summand
+    eq(z, zex; k, i, ex) X(j, i, ex) W(j, k, ex) splits over the index groups, and a structured blind only adds a public
+    per-round term to the messages, so the rounds over j, over k and over i are three short product chains on partially
+    evaluated operands (the two slices ex = 0, 1 the weight touches, stacked and pre-weighted), stopped before the slice
+    variable, and the last e rounds run over the slice variable alone.  Messages, challenges and transcript equal the chain
+    over the materialised domain (zkllm-src/p3_int_gadgets.cuh:567-597 with p3_hawkeye.cuh:1329-1331).
+    Returns (r, msgs as bytes, serialised Blind)."""
+    from .p3 import S_A, S_J, view_point
+    xv, wv, _ = views
+    lt = lj + lk + li
+    e_p, eX, eW = zc.e_of(lt), zc.e_of(X.vreal), zc.e_of(W.vreal)
+    J, K, I = 1 << lj, 1 << lk, 1 << li
+    mX, mW = (1 << min(eX, e_p)) - 1, (1 << min(eW, e_p)) - 1
+    sb = _sblind_begin(engine, zc, tr, lt + e_p, R)
+    table, pref = sb["table"], 0
+    zk_, zi_ = z[:lk], z[lk:]
+    ws = [(1 - zex) % GL_P, zex % GL_P]
+    u64 = lambda a: np.array(a, dtype=np.uint64)
+    Xd = [engine.gather_fn(X.dev, I * J, lambda t, s=s: _view_index(xv, {S_J: t & (J - 1), S_A: t >> lj}) | ((s & mX) << X.vreal))
+          for s in (0, 1)]                                                  # [i][j]
+    Wd = [engine.gather_fn(W.dev, J * K, lambda t, s=s: _view_index(wv, {S_J: t >> lk, S_A: t & (K - 1)}) | ((s & mW) << W.vreal))
+          for s in (0, 1)]                                                  # [j][k]
+    eq_i, eq_k = engine.build_eq_gpu(u64(zi_)), engine.build_eq_gpu(u64(zk_))
+    msgs, r = [], []
+
+    def phase(A, B, rounds, rd0):
+        nonlocal pref
+        ch, m, left, pref = engine.sc_prove_zc_partial(tr, "imm-sc", [A, B], [(1, (1,))], 0, rounds, table[rd0:rd0 + rounds], pref)
+        msgs.append(np.ascontiguousarray(m, dtype=np.uint64).tobytes())
+        return [int(x) for x in ch], left
+
+    # rounds over j: sum_s w_s sum_j X_s(j, zi) W_s(j, zk)
+    rj = []
+    if lj:
+        A = engine.concat([engine.scale(engine.matvec(Xd[s], I, J, eq_i, False), ws[s]) for s in (0, 1)])
+        B = engine.concat([engine.matvec(Wd[s], J, K, eq_k, True) for s in (0, 1)])
+        rj, _ = phase(A, B, lj, 0)
+    eq_rj = engine.build_eq_gpu(u64(rj))
+    X1 = [engine.matvec(Xd[s], I, J, eq_rj, True) for s in (0, 1)]          # X_s(rj, i)
+    W1 = [engine.matvec(Wd[s], J, K, eq_rj, False) for s in (0, 1)]         # W_s(rj, k)
+    # rounds over k: sum_s w_s [sum_i eq(zi, i) X_s(rj, i)] sum_k eq(zk, k) W_s(rj, k)
+    SX = [engine.eval_h_gpu(X1[s], u64(zi_)) for s in (0, 1)]
+    rk, Wrr = [], [engine.element(W1[s], 0) for s in (0, 1)]
+    if lk:
+        A = engine.concat([engine.scale(eq_k, ws[s] * SX[s] % GL_P) for s in (0, 1)])
+        rk, left = phase(A, engine.concat(W1), lk, lj)
+        Wrr = [int(left[1][s]) for s in (0, 1)]
+    eqk_r = 1
+    for a, b in zip(rk, zk_):
+        eqk_r = eqk_r * ((a * b + (1 - a) * (1 - b)) % GL_P) % GL_P
+    # rounds over i: sum_s w_s eq(zk, rk) W_s(rj, rk) sum_i eq(zi, i) X_s(rj, i)
+    ri = []
+    if li:
+        A = engine.concat([engine.scale(eq_i, ws[s] * eqk_r % GL_P * Wrr[s] % GL_P) for s in (0, 1)])
+        ri, _ = phase(A, engine.concat(X1), li, lj + lk)
+    eqi_r = 1
+    for a, b in zip(ri, zi_):
+        eqi_r = eqi_r * ((a * b + (1 - a) * (1 - b)) % GL_P) % GL_P
+    # rounds over the slice variables: eq((zex, 0..); ex) * eq(zk, rk) eq(zi, ri) * X(rj, ri, ex) * W(rj, rk, ex)
+    px, pw = u64(view_point(xv, rj, ri)), u64(view_point(wv, rj, rk))
+    NX, NW = 1 << X.vreal, 1 << W.vreal
+    xs = [engine.eval_h_gpu(engine.slice(X.dev, (s & mX) * NX, NX), px) for s in range(1 << e_p)]
+    wsl = [engine.eval_h_gpu(engine.slice(W.dev, (s & mW) * NW, NW), pw) for s in range(1 << e_p)]
+    c0 = eqk_r * eqi_r % GL_P
+    ecol = [c0 * ws[s] % GL_P if s < 2 else 0 for s in range(1 << e_p)]
+    ch, m, _, pref = engine.sc_prove_zc_partial(tr, "imm-sc", [engine.upload(u64(ecol)), engine.upload(u64(xs)), engine.upload(u64(wsl))],
+                                                [(1, (1, 2))], 0, e_p, table[lt:lt + e_p], pref)
+    msgs.append(np.ascontiguousarray(m, dtype=np.uint64).tobytes())
+    r = rj + rk + ri + [int(x) for x in ch]
+    return r, b"".join(msgs), _sblind_end(engine, zc, tr, sb, r, pref, ledger)
 
 
 def linked_y_mask(engine, zc, X, W, lj, lk, li):
@@ -277,38 +361,15 @@ def linked_y_mask(engine, zc, X, W, lj, lk, li):
 
 def imm_prove(engine, zc, tr, X, W, Y, lj, lk, li, R, Q, ledger=None):
     """p3imm::prove with the zk switch on, direct layouts X = [j | i<<lj], W = [k | j<<lk], Y = [k | i<<lk] (ZCol each; Y
-    committed with linked_y_mask).  The summand eq * X * W runs over the (j, k, i, ex) domain of 2^vfull(lj+lk+li) points
-    as one blinded chain."""
-    own = ledger is None
-    if own:
-        ledger = ZLedger()
-    tr.absorb("imm-dims", struct.pack("<III", lj, lk, li))
-    tr.absorb("imm-X", X.root)
-    tr.absorb("imm-W", W.root)
-    tr.absorb("imm-Y", Y.root)
-    z = [tr.chal() for _ in range(lk + li)]
-    zex = tr.chal()
-    yY = claimc(engine, tr, ledger, Y, xpt(zc, z, zex))
-    lt = lj + lk + li
-    e_p, eX, eW = zc.e_of(lt), zc.e_of(lj + li), zc.e_of(lj + lk)
-    N = 1 << (lt + e_p)
-    ptE = z + [zex] + [0] * (e_p - 1)
-    eqv = engine.build_eq_gpu(np.array(ptE, dtype=np.uint64))
-    J, K, I = 1 << lj, 1 << lk, 1 << li
-    mX = (1 << min(eX, e_p)) - 1
-    mW = (1 << min(eW, e_p)) - 1
-    cols = [engine.bcast_rows(eqv, lj),
-            engine.gather_fn(X.dev, N, lambda u: (u & (J - 1)) | (((u >> (lj + lk)) & (I - 1)) << lj) | (((u >> lt) & mX) << (lj + li))),
-            engine.gather_fn(W.dev, N, lambda u: ((u >> lj) & (K - 1)) | ((u & (J - 1)) << lk) | (((u >> lt) & mW) << (lj + lk)))]
-    r, msgs, _, blind = sc5z(engine, zc, tr, "imm-sc", lt, cols, [(1, (1, 2))], 0, R, ledger)
-    rj, rk, ri = r[:lj], r[lj:lj + lk], r[lj + lk:lt]
-    yX = claimc(engine, tr, ledger, X, expt(zc, rj + ri, r, lt))
-    yW = claimc(engine, tr, ledger, W, expt(zc, rk + rj, r, lt))
-    out = struct.pack("<III", lj, lk, li) + np.ascontiguousarray(msgs, dtype=np.uint64).tobytes()
-    out += struct.pack("<QQQ", yY, yX, yW) + blind
-    batches = tail_prove(engine, zc, tr, ledger, R, Q, "imm-bo") if own else []
-    out += struct.pack("<I", len(batches)) + b"".join(struct.pack("<I", len(b)) + b for b in batches)
-    return out
+    committed with linked_y_mask).  Chains below the structured-blind threshold run over the materialised (j, k, i, ex)
+    domain with four committed blind columns, chains above it in the factored form (imm_chain_factored).  Standalone (no
+    shared ledger): the blinded batched openings follow."""
+    if ledger is not None:
+        return imm_prove_views(engine, zc, tr, X, W, Y, lj, lk, li, R, Q, ledger)
+    ledger = ZLedger()
+    body = imm_prove_views(engine, zc, tr, X, W, Y, lj, lk, li, R, Q, ledger)[:-4]
+    batches = tail_prove(engine, zc, tr, ledger, R, Q, "imm-bo")
+    return body + struct.pack("<I", len(batches)) + b"".join(struct.pack("<I", len(b)) + b for b in batches)
 
 
 # ---------------------------------------------------------------------------------- merged lookups in hiding mode
@@ -804,17 +865,21 @@ def imm_prove_views(engine, zc, tr, X, W, Y, lj, lk, li, R, Q, ledger, views=Non
     N = 1 << (lt + e_p)
     J, K, I = 1 << lj, 1 << lk, 1 << li
     mX, mW = (1 << min(eX, e_p)) - 1, (1 << min(eW, e_p)) - 1
-    eqv = engine.build_eq_gpu(np.array(z + [zex] + [0] * (e_p - 1), dtype=np.uint64))
-    cols = [engine.bcast_rows(eqv, lj),
-            engine.gather_fn(X.dev, N, lambda u: _view_index(xv, {S_J: u & (J - 1), S_A: (u >> (lj + lk)) & (I - 1)})
-                             | (((u >> lt) & mX) << X.vreal)),
-            engine.gather_fn(W.dev, N, lambda u: _view_index(wv, {S_J: u & (J - 1), S_A: (u >> lj) & (K - 1)})
-                             | (((u >> lt) & mW) << W.vreal))]
-    r, msgs, _, blind = sc5z(engine, zc, tr, "imm-sc", lt, cols, [(1, (1, 2))], 0, R, ledger)
+    if lt + e_p >= zc.sblind_min and not getattr(zc, "materialise", False):
+        r, msgs, blind = imm_chain_factored(engine, zc, tr, X, W, (xv, wv, yv), lj, lk, li, z, zex, R, ledger)
+    else:
+        eqv = engine.build_eq_gpu(np.array(z + [zex] + [0] * (e_p - 1), dtype=np.uint64))
+        cols = [engine.bcast_rows(eqv, lj),
+                engine.gather_fn(X.dev, N, lambda u: _view_index(xv, {S_J: u & (J - 1), S_A: (u >> (lj + lk)) & (I - 1)})
+                                 | (((u >> lt) & mX) << X.vreal)),
+                engine.gather_fn(W.dev, N, lambda u: _view_index(wv, {S_J: u & (J - 1), S_A: (u >> lj) & (K - 1)})
+                                 | (((u >> lt) & mW) << W.vreal))]
+        r, msgs, _, blind = sc5z(engine, zc, tr, "imm-sc", lt, cols, [(1, (1, 2))], 0, R, ledger)
+        msgs = np.ascontiguousarray(msgs, dtype=np.uint64).tobytes()
     rj, rk, ri = r[:lj], r[lj:lj + lk], r[lj + lk:lt]
     yX = claimc(engine, tr, ledger, X, expt(zc, view_point(xv, rj, ri), r, lt))
     yW = claimc(engine, tr, ledger, W, expt(zc, view_point(wv, rj, rk), r, lt))
-    out = struct.pack("<III", lj, lk, li) + np.ascontiguousarray(msgs, dtype=np.uint64).tobytes()
+    out = struct.pack("<III", lj, lk, li) + msgs
     return out + struct.pack("<QQQ", yY, yX, yW) + blind + struct.pack("<I", 0)
 
 
