@@ -236,6 +236,28 @@ class Prover {
         msgs.insert(msgs.end(), m.begin(), m.end());
         return r;
     }
+    // the first `rounds` rounds of such a chain (factored matmul chain): left = what every column still holds, column after column
+    std::vector<gl_t> sc_prove_zc_partial(Transcript& tr, const char* tag, const std::vector<const gl_t*>& d_cols, uint32_t N,
+                                          const std::vector<ZTerm>& terms, gl_t konst, uint32_t rounds, const std::vector<gl_t>& fix,
+                                          std::vector<gl_t>& msgs, std::vector<gl_t>& left, gl_t& pref) {
+        uint32_t logn = 0;
+        while ((1u << logn) < N) logn++;
+        std::vector<uint64_t> prog = {terms.size(), konst};
+        for (auto& t : terms) {
+            uint64_t pk = t.idx.size() | (t.outside ? 0x80u : 0u);
+            for (size_t k = 0; k < t.idx.size(); k++) pk |= (uint64_t)t.idx[k] << (8 + 8 * k);
+            prog.push_back(t.coef);
+            prog.push_back(pk);
+        }
+        std::vector<gl_t> r(rounds), m((size_t)rounds * 5);
+        left.assign(d_cols.size() * ((size_t)N >> rounds), 0);
+        gl_t pout = pref;
+        ck(zkh_sumcheck_zerocheck_partial(ctx_, d_cols.data(), (int)d_cols.size(), logn, rounds, prog.data(), (int)prog.size(),
+                                          fix.empty() ? nullptr : fix.data(), pref, tag, tr.state, m.data(), r.data(), left.data(), &pout));
+        if (!fix.empty()) pref = pout;
+        msgs.insert(msgs.end(), m.begin(), m.end());
+        return r;
+    }
     // p3bo::prove_class after the class blinder was appended, salted round-0 openings (zkllm-src/p3_batchopen.cuh:969-1131)
     std::vector<uint8_t> prove_class_salted(Transcript& tr, const std::vector<std::vector<gl_t>>& pts, const std::vector<Entry>& ents,
                                             const std::vector<uint64_t>& sseeds, uint32_t R, uint32_t Q, const std::string& label) {
