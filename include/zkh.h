@@ -346,6 +346,11 @@ ZKH_API int zkh_gl_affine(zkh_ctx* ctx, const uint64_t* const* cols_dev, int nco
  * so its round messages come from these partial evaluations (see p3.imm_prove).  Stream-ordered. */
 ZKH_API int zkh_gl_matvec(zkh_ctx* ctx, const uint64_t* M_dev, uint64_t rows, uint64_t cols, const uint64_t* w_dev,
                           int along_rows, uint64_t* out_dev);
+/* C = A * B over the field, row-major, A: I x J, B: J x K (device): the product of the operands' first mask slices that links the
+ * mask of a matmul accumulator in hiding mode (zkllm-src/p3_int_gadgets.cuh:510-527 accum_mask1, a host triple loop there).
+ * Stream-ordered. */
+ZKH_API int zkh_gl_matmul(zkh_ctx* ctx, const uint64_t* A_dev, const uint64_t* B_dev, uint64_t I, uint64_t J, uint64_t K,
+                          uint64_t* C_dev);
 /* out[i] = a[i]*b[i]: the helper column hT = cnt * 1/(Tc+beta) of the standalone lookup
  * (zkllm-src/p3_logup.cuh:984).  Stream-ordered. */
 ZKH_API int zkh_gl_mul(zkh_ctx* ctx, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev);

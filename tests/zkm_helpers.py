@@ -50,6 +50,10 @@ class OracleZkEngine(OracleGadgetEngine):
     def set_element(self, col, i, value):
         col.a[i] = np.uint64(int(value) % GL_P)
 
+    def matmul(self, A, B, I, J, K):
+        a, b = A.a.astype(object).reshape(I, J), B.a.astype(object).reshape(J, K)
+        return _Arr(np.array([int(x) % GL_P for x in a.dot(b).reshape(-1)], dtype=np.uint64))
+
     def scatter_fn(self, col, n, fn, vals):
         col.a[fn(np.arange(n, dtype=np.int64))] = vals.a
         return col

@@ -98,6 +98,7 @@ def load_library():
         "zkh_gl_combine": (i, [vp, vp, i, u64, u64, vp]),
         "zkh_gl_affine": (i, [vp, vp, i, u64, u64, u64, vp]),
         "zkh_gl_matvec": (i, [vp, vp, u64, u64, vp, i, vp]),
+        "zkh_gl_matmul": (i, [vp, vp, vp, u64, u64, u64, vp]),
         "zkh_gl_scale": (i, [vp, vp, u64, u64, vp]),
         "zkh_gl_mul": (i, [vp, vp, vp, u64, vp]),
         "zkh_irs_witness": (i, [vp, vp, u64, u32, i, vp, vp, vp, vp, vp, vp]),

@@ -240,11 +240,45 @@ extern "C" int zkh_gl_matvec(zkh_ctx* c, const uint64_t* M_dev, uint64_t rows, u
     return ZKH_OK;
 }
 namespace zkh {
+// C[i][k] = sum_j A[i][j] * B[j][k] mod p (row-major).  One thread owns four rows of one output column: a B element is
+// loaded once per four products (coalesced over k), the A elements are warp-wide broadcasts; products accumulate in 192 bits
+// and reduce once.  Used for the linked first mask slices of matmul accumulators (zkllm-src/p3_int_gadgets.cuh:512-527).
+constexpr int MM_ROWS = 4;
+__global__ void __launch_bounds__(256) matmul_kernel(const gl_t* __restrict__ A, const gl_t* __restrict__ B, size_t I, size_t J,
+                                                     size_t K, gl_t* __restrict__ C) {
+    const size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i0 = (size_t)blockIdx.y * MM_ROWS;
+    if (k >= K) return;
+    Acc192 acc[MM_ROWS];
+#pragma unroll
+    for (int r = 0; r < MM_ROWS; r++) acc[r].clear();
+    for (size_t j = 0; j < J; j++) {
+        const gl_t b = B[j * K + k];
+#pragma unroll
+        for (int r = 0; r < MM_ROWS; r++)
+            if (i0 + r < I) acc[r].add_prod(A[(i0 + r) * J + j], b);
+    }
+#pragma unroll
+    for (int r = 0; r < MM_ROWS; r++)
+        if (i0 + r < I) C[(i0 + r) * K + k] = acc[r].reduce();
+}
 __global__ void __launch_bounds__(256) mul_vec_kernel(const gl_t* __restrict__ a, const gl_t* __restrict__ b, size_t n, gl_t* out) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = gl_mul(a[i], b[i]);
 }
 }  // namespace zkh
+extern "C" int zkh_gl_matmul(zkh_ctx* c, const uint64_t* A_dev, const uint64_t* B_dev, uint64_t I, uint64_t J, uint64_t K,
+                             uint64_t* C_dev) {
+    if (!c || !A_dev || !B_dev || !C_dev) return zkh_fail(c, ZKH_ERR_ARG, "matmul: null pointer");
+    if (!I || !J || !K || I > ((uint64_t)1 << 24) || J > ((uint64_t)1 << 30) || K > ((uint64_t)1 << 30))
+        return zkh_fail(c, ZKH_ERR_ARG, "matmul: bad shape");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    const unsigned gy = (unsigned)((I + MM_ROWS - 1) / MM_ROWS);
+    if (gy > 65535) return zkh_fail(c, ZKH_ERR_LIMIT, "matmul: more than 262140 rows");
+    matmul_kernel<<<dim3((unsigned)((K + 255) / 256), gy), 256, 0, c->stream>>>(A_dev, B_dev, (size_t)I, (size_t)J, (size_t)K, C_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
 extern "C" int zkh_gl_mul(zkh_ctx* c, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev) {
     if (!c || !a_dev || !b_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "mul: null pointer");
     if (!n) return ZKH_OK;

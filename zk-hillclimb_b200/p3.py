@@ -380,6 +380,13 @@ class Prover:
         self._ck(self._L.zkh_gl_matvec(self._h, _ptr(M_dev), rows, cols, _ptr(w_dev), int(along_rows), _ptr(out)))
         return out
 
+    def matmul(self, A_dev, B_dev, I, J, K):
+        """C = A * B over the field, row-major (A: I x J, B: J x K): zkh_gl_matmul."""
+        import torch
+        out = torch.empty(I * K, dtype=torch.int64, device=A_dev.device)
+        self._ck(self._L.zkh_gl_matmul(self._h, _ptr(A_dev), _ptr(B_dev), I, J, K, _ptr(out)))
+        return out
+
     def scale(self, col_dev, s):
         import torch
         out = torch.empty_like(col_dev)

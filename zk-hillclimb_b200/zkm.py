@@ -355,8 +355,7 @@ def linked_y_mask(engine, zc, X, W, lj, lk, li):
     slices (zkllm-src/p3_int_gadgets.cuh:510-527), the higher slices are fresh."""
     J, K, I = 1 << lj, 1 << lk, 1 << li
     xm, wm = slice1(engine, X), slice1(engine, W)
-    rows = [engine.matvec(wm, J, K, engine.slice(xm, i * J, J), False) for i in range(I)]
-    return mk_linked(engine, zc, lk + li, engine.concat(rows))
+    return mk_linked(engine, zc, lk + li, engine.matmul(xm, wm, I, J, K))
 
 
 def imm_prove(engine, zc, tr, X, W, Y, lj, lk, li, R, Q, ledger=None):
@@ -842,7 +841,7 @@ def linked_acc_mask(engine, zc, vY, insts):
         J, K, I = 1 << lj, 1 << lk, 1 << li
         xd = engine.gather_fn(slice1(engine, X), I * J, lambda u: _view_index(xv, {S_J: u & (J - 1), S_A: u >> lj}))
         wd = engine.gather_fn(slice1(engine, W), J * K, lambda u: _view_index(wv, {S_J: u >> lk, S_A: u & (K - 1)}))
-        rows = engine.concat([engine.matvec(wd, J, K, engine.slice(xd, i * J, J), False) for i in range(I)])
+        rows = engine.matmul(xd, wd, I, J, K)
         m1 = engine.scatter_fn(m1, K * I, lambda u: _view_index(yv, {S_A: u & (K - 1), S_I: u >> lk}), rows)
     return mk_linked(engine, zc, vY, m1)
 
