@@ -304,6 +304,12 @@ def test_zk_integer_layer_equals_reference_prover(orc, ref, zk, prover, dims):
         ref_zk(ref, False)
     assert (grid == w["out"]).all()
     assert rst == tr.state and rpf == pf
+    # codewords and salted trees kept in HBM for the openings (within a byte budget): the same proof
+    zc = zkm.ZkCtx(seed=seed, Q=Q, keep_bytes=1 << 28)
+    o2 = zkm.itf_commit_all(prover, zc, c, w, Wt, R, col)
+    assert o2["x0"].tree is not None
+    tr2 = zk.Transcript("itf-layer")
+    assert zkm.itf_prove(prover, zc, tr2, c, w, o2, Wt, T, R, Q, col) == pf and tr2.state == tr.state
 
 
 @pytest.mark.parametrize("logn,rounds,with_table", [(6, 3, True), (5, 5, True), (7, 1, False), (4, 3, False), (9, 8, True)])

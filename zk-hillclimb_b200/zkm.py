@@ -40,8 +40,17 @@ GOLD = 0x9E3779B97F4A7C15
 class ZkCtx:
     """p3zkc::Ctx with the switch on: master seed, draw counter, query budget, structured-blind threshold."""
 
-    def __init__(self, seed=1, Q=24, sblind_min=22):
+    def __init__(self, seed=1, Q=24, sblind_min=22, keep_bytes=0):
         self.seed, self.ctr, self.Q, self.sblind_min = seed & M64, 0, Q, sblind_min
+        self.keep_bytes = keep_bytes          # HBM the prover may spend on codewords and salted trees kept for the openings
+
+    def take(self, v, R):
+        """Reserve room for the codeword and the tree of a column of 2^v entries; False when the budget is spent."""
+        need = (8 + 64) << (v + R)
+        if need > self.keep_bytes:
+            return False
+        self.keep_bytes -= need
+        return True
 
     def next_seed(self):
         """zkllm-src/p3_zkc.cuh:118-123."""
@@ -104,7 +113,7 @@ def commit_col(engine, zc, vals, R, mask=None, keep=False):
     else:
         aug = engine.concat([vals, mask])
     sseed = zc.next_seed()
-    root, cw, tree = _salted(engine, aug, R, sseed, keep)
+    root, cw, tree = _salted(engine, aug, R, sseed, keep or zc.take(int(aug.numel()).bit_length() - 1, R))
     return ZCol(aug, root, v, sseed, cw, tree)
 
 
@@ -426,9 +435,12 @@ def prove_super(engine, zc, tr, table_cols, table_id, subgroups, R, ledger, stri
         SmA = (SmA + col_sum(engine, sm)) % GL_P
         sP = zc.next_seed()
         pm_ = engine.mul(sm, qm)
-        PM = ZCol(pm_, engine.commit_salted(pm_, R, sP), n + g + zc.e_of(n), sP)
+        vm = n + g + zc.e_of(n)
+        PM = ZCol(pm_, None, vm, sP)
+        PM.root, PM.cw, PM.tree = _salted(engine, pm_, R, sP, zc.take(vm, R))
         sQ = zc.next_seed()
-        QM = ZCol(qm, engine.commit_salted(qm, R, sQ), n + g + zc.e_of(n), sQ)
+        QM = ZCol(qm, None, vm, sQ)
+        QM.root, QM.cw, QM.tree = _salted(engine, qm, R, sQ, zc.take(vm, R))
         tr.absorb("lug-pm", PM.root)
         tr.absorb("lug-qm", QM.root)
         masks.append((PM, QM))
@@ -440,9 +452,11 @@ def prove_super(engine, zc, tr, table_cols, table_id, subgroups, R, ledger, stri
     pmT = engine.mul(smT, qmT)
     engine.set_element(pmT, MT - 1, (SmA - Smcnt - part) % GL_P * engine.element(qmT, MT - 1) % GL_P)
     sP = zc.next_seed()
-    PMT = ZCol(pmT, engine.commit_salted(pmT, R, sP), m + zc.e_of(m), sP)
+    PMT = ZCol(pmT, None, m + zc.e_of(m), sP)
+    PMT.root, PMT.cw, PMT.tree = _salted(engine, pmT, R, sP, zc.take(m + zc.e_of(m), R))
     sQ = zc.next_seed()
-    QMT = ZCol(qmT, engine.commit_salted(qmT, R, sQ), m + zc.e_of(m), sQ)
+    QMT = ZCol(qmT, None, m + zc.e_of(m), sQ)
+    QMT.root, QMT.cw, QMT.tree = _salted(engine, qmT, R, sQ, zc.take(m + zc.e_of(m), R))
     tr.absorb("lug-pmT", PMT.root)
     tr.absorb("lug-qmT", QMT.root)
     gamma, beta = tr.chal(), tr.chal()
@@ -922,7 +936,7 @@ def itf_commit_all(engine, zc, c, w, Wt, R, col):
     return o
 
 
-def itf_prove(engine, zc, tr, c, w, o, Wt, T, R, Q, col):
+def itf_prove(engine, zc, tr, c, w, o, Wt, T, R, Q, col, stages=None):
     """p3itf::prove with the zk switch on (zkllm-src/p3_int_layer.cuh:452-581): the decoder layer's 26 + 2A sub-proofs in fixed
     order on one transcript with one ledger and one lookup queue, one merged-lookup flush, the public input / output
     bindings at zero-extended points, one blinded batched opening per size class.  Same serialised layout as the plain
@@ -930,6 +944,8 @@ def itf_prove(engine, zc, tr, c, w, o, Wt, T, R, Q, col):
     from . import ig
     ld, lT, ldff, lseq, ldh, la = c.ld, c.lT, c.ldff, c.lseq, c.ldh, c.la
     le, lef, lez = ld + lT, ldff + lT, la + 2 * lseq
+    import time
+    t0 = time.perf_counter()
     ledger, luq = ZLedger(), []
     tr.absorb("itf-dims", struct.pack("<6I", c.seq, c.d, c.nh, c.dh, c.dff, c.batch))
     for i in range(7):
@@ -989,10 +1005,15 @@ def itf_prove(engine, zc, tr, c, w, o, Wt, T, R, Q, col):
     mm(o["mo"], o["w"][ig.W_D], o["acc"][ig.W_D], ldff, ld, lT)
     irs("rsd", o["acc"][ig.W_D], o["yd"], le, 16, 1)
     subs.append(iadd_prove(engine, zc, tr, T, o["res1"], o["yd"], o["out"], col(w["idxOut"]), le, R, Q, ledger, luq))
+    t1 = time.perf_counter()
     lug = lu_flush(engine, zc, tr, luq, ledger, R)
+    t2 = time.perf_counter()
     ioin = claimc(engine, tr, ledger, o["x0"], zpt(zc, [tr.chal() for _ in range(le)]))
     ioout = claimc(engine, tr, ledger, o["out"], zpt(zc, [tr.chal() for _ in range(le)]))
     batches = tail_prove(engine, zc, tr, ledger, R, Q, "itf-bo")
+    if stages is not None:
+        stages.update(subs_s=t1 - t0, lookups_s=t2 - t1, openings_s=time.perf_counter() - t2, lookup_groups=len(lug),
+                      opening_classes=len(batches))
     blob = lambda b: struct.pack("<I", len(b)) + b
     roots = [o["x0"].root, o["h1"].root] + [a.root for a in o["acc"]] + [o[k].root for k in
              ("yq", "yk", "yv", "rq", "rk", "sc", "z", "p", "pva", "at", "yo", "res1", "h2", "gg", "uu", "mo", "yd", "out")]
