@@ -98,50 +98,63 @@ def measured_peak():
     return 6650.0, "fallback (6.65 TB/s, no MEASURED_PEAKS.json)"
 
 
-def cpu_baseline(logn_sample, nthreads, use_reference):
-    """The same degree-2 sumcheck on the host cores, bounded sample."""
+def cpu_baseline(logn_sample, nthreads, use_reference, reps=1):
+    """The same degree-2 sumcheck on the host cores, bounded sample.  Only the prover call is timed (inputs are built
+    before); returns the dictionary and the list of per-call seconds."""
     from oracle import F_PROD2, Oracle, Reference
     orc = Oracle()
     cols = lcg_cols(orc, 1 << logn_sample, 2, SEED)
     st0 = orc.tr_init("bench-sc2")
     kind = "port"
-    t0 = time.perf_counter()
-    if use_reference and Reference.available():
-        # the reference's host sumcheck loop (p3hwl::sc5_prove, OpenMP over all host threads)
-        Reference().sc5_prove(st0, "sc", 0, cols)
-        kind = "reference"
-    else:
-        orc.sumcheck(st0, "sc", F_PROD2, 3, cols, (), nthreads, inplace=True)
-    dt = time.perf_counter() - t0
+    refobj = Reference() if (use_reference and Reference.available()) else None
+    secs = []
+    for _ in range(reps):
+        work = None if refobj is not None else [c.copy() for c in cols]     # the port folds in place
+        t0 = time.perf_counter()
+        if refobj is not None:
+            # the reference's host sumcheck loop (p3hwl::sc5_prove, OpenMP over all host threads)
+            refobj.sc5_prove(st0, "sc", 0, cols)
+            kind = "reference"
+        else:
+            orc.sumcheck(st0, "sc", F_PROD2, 3, work, (), nthreads, inplace=True)
+        secs.append(time.perf_counter() - t0)
+    dt = min(secs)
     return {"value": alg_bytes(2, logn_sample) / dt / 1e9, "unit": UNIT, "cores": nthreads, "kind": kind,
-            "sample": "one degree-2 sumcheck over 2^%d elements per column (%.1f s)" % (logn_sample, dt)}
+            "sample": "one degree-2 sumcheck over 2^%d elements per column (%.2f s)" % (logn_sample, dt)}, secs
 
 
 def run_reference(args):
-    """--impl reference: the reference's own CPU implementation of the path, rank 0 only."""
+    """--impl reference: the reference's own CPU implementation of the path (p3hwl::sc5_prove, OpenMP), rank 0 only,
+    all host threads.  The sample size is the largest power of two up to the full 2^28 whose (warmup + steps) calls fit
+    a time budget on this host, estimated from one 2^22 call."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     ncores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(ncores))
+    os.environ["OMP_NUM_THREADS"] = str(ncores)      # a launcher may have exported 1; the reference loop is OpenMP
+    os.environ.pop("OMP_THREAD_LIMIT", None)
+    calls = args.warmup + args.steps
     logn = args.ref_logn
-    times = []
-    base = None
-    for i in range(args.warmup + args.steps):
-        t0 = time.perf_counter()
-        base = cpu_baseline(logn, ncores, True)
-        if i >= args.warmup:
-            times.append(time.perf_counter() - t0)
+    if logn <= 0:
+        _, probe = cpu_baseline(22, ncores, True, reps=2)
+        per_elem = min(probe) / (1 << 22)
+        logn = 22
+        while logn < args.logn and per_elem * (1 << (logn + 1)) * calls <= args.ref_budget_s:
+            logn += 1
+    base, secs = cpu_baseline(logn, ncores, True, reps=calls)
+    times = secs[args.warmup:]
     ms = 1e3 * sum(times) / max(len(times), 1)
     val = alg_bytes(2, logn) / (ms / 1e3) / 1e9
     base["value"] = val
+    base["omp_threads"] = ncores
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u64 (Goldilocks field)", "data": "synthetic",
-        "config": {"workload": "degree-2 sumcheck, bounded sample 2^%d elements per column on the host "
-                               "cores (full workload 2^28)" % logn, "nc": 2, "nt": 3},
+        "config": {"workload": "degree-2 sumcheck, %s 2^%d elements per column on the host cores (full workload 2^%d)"
+                               % ("the full" if logn == args.logn else "bounded sample", logn, args.logn),
+                   "nc": 2, "nt": 3, "same_size_as_gpu_arm": logn == args.logn},
         "cpu_baseline": base,
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -545,8 +558,7 @@ def run_suite_fr(args):
 
 def run_profile_case(args):
     """--profile-case NAME: one small, self-terminating invocation of one kernel family (a few hundred MB on
-    the device, inputs larger than L2, two launches) - the command the ncu summaries under profiles/ are
-    captured from.  Prints the CUDA-event time of the second invocation."""
+    the device, inputs larger than L2, two launches) - a command small enough to capture under a profiler.  Prints the CUDA-event time of the second invocation."""
     import torch
     import zkh_import
     zk = zkh_import.load()
@@ -585,6 +597,9 @@ def run_profile_case(args):
     elif name == "inv":
         a = gl_rand(1 << 24)
         fn = lambda: prover.inv_all_add(a, 12345)
+    elif name == "sumcheck2":
+        cols = [gl_rand(1 << 24) for _ in range(2)]
+        fn = lambda: prover.sc_prove_gpu(zk.Transcript("prof"), "sc", cols, zk.F_PROD2, 3)
     elif name == "sumcheck3":
         cols = [gl_rand(1 << 24) for _ in range(3)]
         fn = lambda: prover.sc_prove_gpu(zk.Transcript("prof"), "sc", cols, zk.F_PROD3, 4)
@@ -1068,6 +1083,180 @@ def run_suite_model(args):
         dist.destroy_process_group()
 
 
+TINYLLAMA_DIMS = (512, 2048, 32, 64, 8192, 1)      # seq, hidden, heads, head dim, MLP (5632 padded to 8192), batch
+MODEL_LAYERS = 22
+
+
+def layer_figure(args, zk, prover, world, rank, local, dist):
+    """BASELINE.json's first metric at N GPUs: the 22 decoder layers of the TinyLlama-1.1B-shaped model (seq 512) proved as
+    22 independent integer-layer proofs (p3itf; one transcript per layer, as the reference's layer bench proves them),
+    layer l on GPU l mod N, no collective on the data path.  Timed per rank on the device (CUDA events around everything
+    the rank does: witness chain, commitments, proof of each of its layers), maximum over ranks.  Two passes: plain, and
+    hiding mode (the reference's zk switch, which every published reference layer number uses)."""
+    import torch
+    ig, zkm = zk.ig, zk.zkm
+    from zk_hillclimb_b200 import ig_dev
+    dims = TINYLLAMA_DIMS if args.layer_shapes != "tiny" else (16, 32, 2, 16, 64, 1)
+    nlayers = args.model_layers
+    R, Q, zseed = 2, 24, 0xC0FFEE
+    dvc = "cuda:%d" % local
+    ident = lambda a: a
+    out = {"metric": "prove s/layer (TinyLlama-1.1B-shaped integer decoder layer, seq 512, R=2, Q=24)",
+           "layers": nlayers, "n_gpus": world, "placement": "layer l on GPU l mod N; no collective on the data path",
+           "timed": "witness chain + commitments + proof of every layer (CUDA events per rank, max over ranks)",
+           "dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), dims)),
+           "shape_note": "hidden 2048, 32 heads of 64 (each KV head replicated 8x), MLP 5632 padded to 8192"}
+    err = None
+    try:
+        cfg = ig.Config(*dims)
+        tabs = ig.build_tables(zk.load_library(), cfg.d, cfg.btop)
+        lx0, lW = ig.random_layer_inputs(cfg, 42, 0.9)
+    except Exception as e:
+        err = repr(e)
+
+    def one_layer(layer, hiding, acc):
+        t = [time.perf_counter()]
+        lw = ig_dev.itf_build_witness(cfg, lx0, lW, tabs, dvc)
+        torch.cuda.synchronize()
+        t.append(time.perf_counter())
+        if hiding:
+            zc = zkm.ZkCtx(seed=zseed + layer, Q=Q, keep_bytes=80 << 30)
+            lo = zkm.itf_commit_all(prover, zc, cfg, lw, lw["dev_W"], R, ident)
+        else:
+            lo = ig.itf_commit_all(prover, lw, lw["dev_W"], R, ident)
+        torch.cuda.synchronize()
+        t.append(time.perf_counter())
+        tr = zk.Transcript("itf-layer-%d" % layer)
+        if hiding:
+            pf = zkm.itf_prove(prover, zc, tr, cfg, lw, lo, lW, tabs, R, Q, ident, {})
+        else:
+            pf = ig.itf_prove(prover, tr, cfg, lw, lo, lW, tabs, R, Q, ident)
+        torch.cuda.synchronize()
+        t.append(time.perf_counter())
+        prover.release_kept()
+        del lo, lw
+        if hiding:
+            torch.cuda.empty_cache()
+        for k, name in enumerate(("witness_s", "commit_s", "prove_s")):
+            acc[name] = acc.get(name, 0.0) + t[k + 1] - t[k]
+        acc["n"] = acc.get("n", 0) + 1
+        return len(pf)
+
+    for mode in (("plain",) if args.no_zk_layer else ("plain", "zk")):
+        hiding = mode == "zk"
+        res = {}
+        ms, nbytes, acc = 0.0, 0, {}
+        if err is None:
+            try:
+                prover.keep_trees = not hiding          # plain mode: codewords and trees stay in HBM for the openings
+                nbytes = one_layer(rank, hiding, {})     # warm-up (table uploads, workspace growth)
+            except Exception as e:
+                err = "%s pass, warm-up: %r" % (mode, e)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        if err is None:
+            try:
+                for layer in range(rank, nlayers, world):
+                    nbytes = one_layer(layer, hiding, acc)
+            except Exception as e:
+                err = "%s pass: %r" % (mode, e)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        prover.keep_trees = False
+        prover.release_kept()
+        bad = 1.0 if err is not None else 0.0
+        if world > 1:
+            t = torch.tensor([ms, bad], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms, bad = float(t[0].item()), float(t[1].item())
+        if bad:
+            out[mode] = {"error": err or "another rank failed"}
+            break
+        n = max(acc.get("n", 1), 1)
+        out[mode] = {"total_s": ms / 1e3, "s_per_layer": ms / 1e3 / nlayers, "layers_per_s": nlayers / (ms / 1e3),
+                     "rank0_mean_per_layer": {k: acc.get(k, 0.0) / n for k in ("witness_s", "commit_s", "prove_s")},
+                     "proof_MB": nbytes / 1048576.0}
+    if "plain" in out and "s_per_layer" in out["plain"]:
+        out["s_per_layer"] = out["plain"]["s_per_layer"]
+        out["layers_per_s"] = out["plain"]["layers_per_s"]
+    return out
+
+
+def reference_layer_figure(args, zk, prover):
+    """N = 1: the reference's own layer prover (p3itf, compiled unchanged for sm_100a) timed live on this GPU beside this
+    library on the same inputs, at the shapes its host-side matmul columns allow: the Llama-68M-shaped layer of BASELINE
+    configs[3] in plain mode and the 64 x 256 layer in hiding mode.  Proof bytes are compared."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import Reference
+    if not Reference.available():
+        return {"unavailable": "the reference build used as the checker is not present"}
+    ref = Reference()
+    if not ref.gpu_available():
+        return {"unavailable": "the reference's CUDA paths need a GPU build of the checker"}
+    from ig_helpers import ref_itf_prove
+    from zkm_helpers import ref_zk
+    from zk_hillclimb_b200 import ig_dev
+    ig, zkm = zk.ig, zk.zkm
+    R, Q, zseed = 2, 24, 0xC0FFEE
+    ident = lambda a: a
+    res = {}
+    cases = [("plain, BASELINE configs[3] Llama-68M-shaped layer (seq 128, hidden 1024, 16 heads of 64, MLP 4096)", (128, 1024, 16, 64, 4096, 1), False),
+             ("hiding mode, seq 64, hidden 256, 4 heads of 64, MLP 1024", (64, 256, 4, 64, 1024, 1), True)]
+    if args.layer_shapes == "tiny":
+        cases = [("plain, smoke shape", (16, 32, 2, 16, 64, 1), False), ("hiding mode, smoke shape", (16, 32, 2, 16, 64, 1), True)]
+    for name, dims, hiding in cases:
+        cfg = ig.Config(*dims)
+        tabs = ig.build_tables(zk.load_library(), cfg.d, cfg.btop)
+        x0, Wt = ig.random_layer_inputs(cfg, 42, 0.9)
+        best = None
+        prover.keep_trees = not hiding
+        for rep in range(2):
+            prover.release_kept()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            w = ig_dev.itf_build_witness(cfg, x0, Wt, tabs)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            if hiding:
+                zc = zkm.ZkCtx(seed=zseed, Q=Q, keep_bytes=80 << 30)
+                o = zkm.itf_commit_all(prover, zc, cfg, w, w["dev_W"], R, ident)
+            else:
+                o = ig.itf_commit_all(prover, w, w["dev_W"], R, ident)
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+            tr = zk.Transcript("itf-layer")
+            pf = (zkm.itf_prove(prover, zc, tr, cfg, w, o, Wt, tabs, R, Q, ident, {}) if hiding
+                  else ig.itf_prove(prover, tr, cfg, w, o, Wt, tabs, R, Q, ident))
+            torch.cuda.synchronize()
+            t3 = time.perf_counter()
+            if best is None or t3 - t0 < sum(best):
+                best = (t1 - t0, t2 - t1, t3 - t2)
+            del o, w
+        prover.keep_trees = False
+        prover.release_kept()
+        torch.cuda.empty_cache()
+        if hiding:
+            ref_zk(ref, True, Q, zseed, 22)
+        try:
+            rpf, rst, _grid, ms = ref_itf_prove(ref, zk.Transcript("itf-layer").state, cfg, x0, Wt, R, Q)
+        finally:
+            if hiding:
+                ref_zk(ref, False)
+        res[name] = {"dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), dims)),
+                     "zkh_s": {"witness": best[0], "commit": best[1], "prove": best[2], "total": sum(best)},
+                     "reference_s": {"witness": ms[0] / 1e3, "commit": ms[1] / 1e3, "prove": ms[2] / 1e3, "total": sum(ms) / 1e3},
+                     "speedup_prove": ms[2] / 1e3 / best[2], "speedup_total": sum(ms) / 1e3 / sum(best),
+                     "same_proof_bytes": bool(rpf == pf and rst == tr.state), "proof_MB": len(pf) / 1048576.0}
+    res["what"] = ("p3itf::build_witness / commit_all / prove of the unmodified reference, compiled for sm_100a, on this GPU; "
+                   "the TinyLlama shape does not fit it (2^33-element host columns per MLP matmul)")
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1075,7 +1264,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="zkh", choices=["zkh", "reference"])
     ap.add_argument("--logn", type=int, default=28, help="log2 elements per column per GPU")
-    ap.add_argument("--ref-logn", type=int, default=22, help="sample size of the CPU reference arm")
+    ap.add_argument("--ref-logn", type=int, default=0, help="sample size of the CPU reference arm (0: the largest that fits --ref-budget-s)")
+    ap.add_argument("--ref-budget-s", type=float, default=150.0, help="time budget of the CPU reference arm's calls")
+    ap.add_argument("--parity-logn", type=int, default=18, help="N>1: per-rank size of the sharded proof checked against the CPU checker")
+    ap.add_argument("--no-zk-layer", action="store_true", help="skip the hiding-mode pass of the 22-layer figure")
+    ap.add_argument("--no-ref-layer", action="store_true", help="skip timing the reference's own layer prover at N=1")
     ap.add_argument("--cpu-logn", type=int, default=26, help="sample size of the cpu_baseline leg")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's CUDA prover")
     ap.add_argument("--e2e-steps", type=int, default=2)
@@ -1158,14 +1351,42 @@ def main():
     dcols = [zk.p3.to_device(c, "cuda:%d" % local) for c in host_cols]
     torch.cuda.synchronize()
 
-    def step():
+    def step(rendezvous=False):
         tr = zk.Transcript("bench-sc2")
         if world == 1:
             return prover.sc_prove_gpu(tr, "sc", dcols, zk.F_PROD2, nt)
-        return zk.p3.sc_prove_sharded(prover, tr, "sc", dcols, zk.F_PROD2, nt, dist)
+        return zk.p3.sc_prove_sharded(prover, tr, "sc", dcols, zk.F_PROD2, nt, dist, rendezvous=rendezvous)
 
-    for _ in range(args.warmup):
-        step()
+    # N > 1: one smaller sharded proof through the same exchange path, compared on rank 0 with the CPU checker's
+    # sumcheck of the concatenated columns (messages, challenges, bound values, transcript state)
+    parity_ok = None
+    if world > 1:
+        pl = args.parity_logn
+        slices = [lcg_cols(orc, 1 << pl, nc, SEED + 77 + 1000 * g) for g in range(world)]
+        mine = [zk.p3.to_device(c, "cuda:%d" % local) for c in slices[rank]]
+        good = True
+        for rep in range(2):                       # the second without the host rendezvous, as in the timed loop
+            ptr = zk.Transcript("bench-parity")
+            pr, pm, pf = zk.p3.sc_prove_sharded(prover, ptr, "sc", mine, zk.F_PROD2, nt, dist, rendezvous=(rep == 0))
+            if rank == 0:
+                from oracle import F_PROD2
+                full = [np.concatenate([slices[g][k] for g in range(world)]) for k in range(nc)]
+                st1, m0, r0, f0 = orc.sumcheck(orc.tr_init("bench-parity"), "sc", F_PROD2, nt, full, (), os.cpu_count() or 1)
+                good &= bool((pm == m0).all() and (pr == r0).all() and (pf == f0).all() and ptr.state == st1)
+        flag = torch.tensor([1 if good else 0], device="cuda")
+        dist.broadcast(flag, 0)
+        parity_ok = bool(flag.item())
+        if not parity_ok:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "n_gpus": world, "parity_ok": False,
+                                  "error": "sharded proof differs from the CPU checker's proof of the concatenated columns"}))
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(3)
+        del mine, slices
+
+    for i in range(args.warmup):
+        step(rendezvous=(i == 0))
     sampler = ClockSampler(local)
     if world > 1:
         dist.barrier()
@@ -1196,8 +1417,8 @@ def main():
     k_bytes = kern_ms[0][2]
     peak, peak_src = measured_peak()
     achieved = k_bytes / (k_ms / 1e3) / 1e9
-    # DRAM bytes per algorithmic byte from the ncu capture of a smaller launch of the same kernel
-    # (profiles/sc_fused_kernel_deg2_sumcheck.md), scaled linearly to this launch
+    # DRAM bytes per algorithmic byte from a profiler capture of a smaller launch of the same kernel
+    # (2^24 elements per column), scaled linearly to this launch
     traffic = DRAM_PER_ALG_BYTE.get(kname)
     traffic = traffic * k_bytes if traffic else None
 
@@ -1249,7 +1470,8 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         ncores = os.cpu_count() or 1
-        cpu = cpu_baseline(args.cpu_logn, ncores, False)
+        os.environ["OMP_NUM_THREADS"] = str(ncores)
+        cpu, _ = cpu_baseline(args.cpu_logn, ncores, False)
 
     # the reference's own CUDA prover (p3sg::sc_prove_gpu, compiled unchanged for sm_100a) on the
     # same inputs and GPU: device-resident columns, its own timer around the proof only
@@ -1272,50 +1494,19 @@ def main():
         except Exception as e:  # the comparison is informative; never fail the bench on it
             ref_cuda = {"error": repr(e)}
 
-    # BASELINE.json's first metric on the same GPU: prove seconds per TinyLlama-shaped decoder layer, seq 512
-    # (integer layer, non-zk; the witness chain runs on the device and, as in the reference's bench, outside the timed region)
+    # BASELINE.json's first metric: prove seconds per TinyLlama-shaped decoder layer, seq 512, over the 22 layers of
+    # the model placed round-robin on the N GPUs (one transcript per layer, no collective on the data path)
+    del dcols, host_cols
+    torch.cuda.empty_cache()
     layer = None
-    if rank == 0 and world == 1 and not args.no_layer:
+    if not args.no_layer:
+        layer = layer_figure(args, zk, prover, world, rank, local, dist)
+    ref_layer = None
+    if rank == 0 and world == 1 and not args.no_layer and not args.no_ref_layer and not args.no_ref_cuda:
         try:
-            del dcols
-            torch.cuda.empty_cache()
-            ig = zk.ig
-            cfg = ig.Config(512, 2048, 32, 64, 8192, 1)
-            tabs = ig.build_tables(zk.load_library(), cfg.d, cfg.btop)
-            lx0, lW = ig.random_layer_inputs(cfg, 42, 0.9)
-            from zk_hillclimb_b200 import ig_dev
-            dvc = "cuda:%d" % local
-            lw = ig_dev.itf_build_witness(cfg, lx0, lW, tabs, dvc)            # warm-up of the witness kernels
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            lw = ig_dev.itf_build_witness(cfg, lx0, lW, tabs, dvc)
-            torch.cuda.synchronize()
-            t_wit = time.perf_counter() - t0
-            lcol = lambda a: a
-            prover.keep_trees = True
-            times = []
-            for _ in range(2):
-                prover.release_kept()
-                torch.cuda.synchronize()
-                t0 = time.perf_counter()
-                lo = ig.itf_commit_all(prover, lw, lw["dev_W"], 2, lcol)
-                torch.cuda.synchronize()
-                t1 = time.perf_counter()
-                lpf = ig.itf_prove(prover, zk.Transcript("itf-layer"), cfg, lw, lo, lW, tabs, 2, 24, lcol)
-                torch.cuda.synchronize()
-                times.append((t1 - t0, time.perf_counter() - t1))
-                del lo
-            prover.release_kept()
-            prover.keep_trees = False
-            layer = {"metric": "prove s/layer (TinyLlama-1.1B-shaped integer decoder layer, seq 512, non-zk, R=2, Q=24)",
-                     "prove_s_per_layer": min(t[1] for t in times), "commit_s_per_layer": min(t[0] for t in times),
-                     "witness_device_s": t_wit, "proof_MB": len(lpf) / 1048576.0,
-                     "dims": {"seq": 512, "d": 2048, "nh": 32, "dh": 64, "dff": 8192},
-                     "note": "hidden 2048, 32 heads of 64 (each KV head replicated 8x), MLP 5632 padded to 8192; the reference's "
-                             "prover cannot run this shape (2^33-element host columns per matmul); at the Llama-68M shape it "
-                             "takes 34.7 s per layer against 0.20 s here with identical proof bytes (profiles/layer_suite_c3_c4.md)"}
-        except Exception as e:          # the layer figure is additional; never lose the main line over it
-            layer = {"error": repr(e)}
+            ref_layer = reference_layer_figure(args, zk, prover)
+        except Exception as e:
+            ref_layer = {"error": repr(e)}
 
     if rank == 0:
         out = {
@@ -1327,15 +1518,20 @@ def main():
                        "nc": nc, "nt": nt, "rounds": total_logn, "l2": "inputs (%.1f GB per GPU) exceed the 126 MB L2; "
                        "no flush between steps" % (nc * n * 8 / 1e9),
                        "parallelism": "hypercube split on the top %d variables" % (world.bit_length() - 1),
-                       "round_exchange": exchange},
+                       "round_exchange": exchange,
+                       "host_rendezvous": "once before the warm-up steps; none inside the timed steps" if world > 1 else None},
             "roofline": {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": UNIT,
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                          "launch_ms": k_ms, "alg_bytes_per_launch": k_bytes},
             "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(args.steps * ((1 + (logn - 12) + 1) if world == 1 else
-                                             ((logn + 3) if exchange.startswith("one kernel") else (2 * logn + 3)))),
-            "clocks": clocks, "reference_cuda": ref_cuda, "layer": layer,
+                                             ((1 + (logn - 12) + 1) if exchange.startswith("one kernel") else (2 * logn + 3)))),
+            "clocks": clocks, "reference_cuda": ref_cuda, "layer": layer, "reference_cuda_layer": ref_layer,
         }
+        if parity_ok is not None:
+            out["parity_ok"] = parity_ok
+            out["parity_check"] = ("2^%d-per-rank sharded proofs through the same exchange path (with and without the host "
+                                   "rendezvous) equal the CPU checker's proof of the concatenated columns" % args.parity_logn)
         print(json.dumps(out))
     if world > 1:
         dist.barrier()

@@ -203,7 +203,9 @@ ZKH_API int zkh_shard_begin(zkh_ctx* ctx, int functor, int nt, const uint64_t* c
  * all ranks must connect before any of them runs a fused round).  zkh_shard_round_fused(r) then runs round r of
  * the running sharded sumcheck as ONE kernel (bind, local sums, peer stores, bounded wait of about a second per
  * round for the other ranks, sum in rank order, absorb, challenge).  A rank that never arrives makes the others
- * return ZKH_ERR_DEVICE from zkh_shard_end; after such an error disconnect and connect again on all ranks. */
+ * return ZKH_ERR_DEVICE from zkh_shard_end; a rank that arrives after another rank's wait ran out is told so by that
+ * rank's next flag (a poison bit) and returns ZKH_ERR_DEVICE as well.  After such an error disconnect and connect
+ * again on all ranks. */
 ZKH_API int zkh_p2p_create(zkh_ctx* ctx, uint8_t handle_out[64]);
 ZKH_API int zkh_p2p_connect(zkh_ctx* ctx, uint32_t rank, uint32_t G, const uint8_t* handles);
 ZKH_API int zkh_p2p_disconnect(zkh_ctx* ctx);
@@ -212,6 +214,14 @@ ZKH_API int zkh_shard_round_fused(zkh_ctx* ctx, uint32_t r);
  * run inside one single-CTA kernel per GPU.  finals_dev receives this rank's nc bound column values (what
  * zkh_shard_finals would return); continue with the all-gather of those and zkh_shard_residual. */
 ZKH_API int zkh_shard_local_fused(zkh_ctx* ctx, uint64_t* finals_dev);
+/* The whole sharded proof after zkh_shard_begin with the peer exchange: the local rounds as above, then -- inside the
+ * same single-CTA kernel -- one more mailbox exchange that all-gathers every GPU's nc bound values, and the log2(G)
+ * residual rounds, which every GPU runs identically.  No collective library call and no host round trip between
+ * zkh_shard_begin and zkh_shard_end.  The device waits are bounded (about a second each), so the caller must see that
+ * the ranks start within that time of one another (a host rendezvous before the first proof of a series; proofs that
+ * follow back to back only have kernel skew between them).  A GPU whose wait ran out marks every later exchange, so
+ * the proof ends with ZKH_ERR_DEVICE from zkh_shard_end on every GPU that took part after that point. */
+ZKH_API int zkh_shard_prove_fused(zkh_ctx* ctx);
 ZKH_API int zkh_shard_round_local(zkh_ctx* ctx, uint32_t r, uint64_t* sums_dev);
 ZKH_API int zkh_shard_round_combine(zkh_ctx* ctx, uint32_t r, const uint64_t* gathered_dev, uint32_t G);
 ZKH_API int zkh_shard_finals(zkh_ctx* ctx, uint64_t* finals_dev);

@@ -32,4 +32,6 @@ def main(src):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference/zkllm-src")
+    _repo = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    main(sys.argv[1] if len(sys.argv) > 1 else
+         os.path.join(os.environ.get("ZKH_REFERENCE") or os.path.join(os.path.dirname(_repo), "reference"), "zkllm-src"))

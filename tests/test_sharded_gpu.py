@@ -112,6 +112,26 @@ def _worker(rank, world, port, logn_total, q):
                 tr = zk.Transcript("nccl")
                 r, m, fin = zk.p3.sc_prove_sharded(prover, tr, "sc", mine, functor, nt, dist, par)
                 ok &= bool((m == m0).all() and (r == r0).all() and (fin == f0).all() and tr.state == st1)
+                # a rank that arrives after the others' waits ran out: the others flag their later exchanges, so the
+                # late rank learns of it and EVERY rank reports the device error (no rank returns a proof built
+                # from sums the others never used)
+                dist.barrier()
+                if rank == world - 1:
+                    import time
+                    time.sleep(6.0)
+                try:
+                    zk.p3.sc_prove_sharded(prover, zk.Transcript("nccl"), "sc", mine, functor, nt, dist, par, rendezvous=False)
+                    ok = False
+                except zk.ZkhError as e:
+                    ok &= e.code == -6
+                dist.barrier()
+                prover.p2p_disconnect()
+                dist.barrier()
+                ok &= bool(prover.p2p_connect(dist))
+                for rep in range(3):           # back to back without the host rendezvous: only kernel skew between ranks
+                    tr = zk.Transcript("nccl")
+                    r, m, fin = zk.p3.sc_prove_sharded(prover, tr, "sc", mine, functor, nt, dist, par, rendezvous=(rep == 0))
+                    ok &= bool((m == m0).all() and (r == r0).all() and (fin == f0).all() and tr.state == st1)
             dist.barrier()
             prover.p2p_disconnect()
         dist.barrier()

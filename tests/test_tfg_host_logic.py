@@ -21,7 +21,8 @@ def test_artefact_digest(zk):
 
 def test_artefact_equals_reference_generator(zk):
     """Where the reference tree is present, its own Python generator gives the same tables."""
-    src = "/root/reference/zkllm-src"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(os.environ.get("ZKH_REFERENCE") or os.path.join(os.path.dirname(root), "reference"), "zkllm-src")
     if not os.path.exists(os.path.join(src, "transformer_ref.py")):
         pytest.skip("reference tree not present")
     sys.path.insert(0, src)

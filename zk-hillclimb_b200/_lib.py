@@ -81,6 +81,7 @@ def load_library():
         "zkh_p2p_disconnect": (i, [vp]),
         "zkh_shard_round_fused": (i, [vp, u32]),
         "zkh_shard_local_fused": (i, [vp, vp]),
+        "zkh_shard_prove_fused": (i, [vp]),
         "zkh_shard_round_combine": (i, [vp, u32, vp, u32]),
         "zkh_shard_finals": (i, [vp, vp]),
         "zkh_shard_residual": (i, [vp, vp, u32]),

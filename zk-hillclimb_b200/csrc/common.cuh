@@ -5,6 +5,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <string>
 #include "gl.cuh"
 #include "sha256.cuh"
@@ -103,6 +104,13 @@ static inline int zkh_fail(zkh_ctx* c, int code, const std::string& msg) {
         int r__ = (expr);              \
         if (r__ != ZKH_OK) return r__; \
     } while (0)
+
+// Function attributes (the dynamic shared-memory limit) belong to a device, not to the process: one bit per device
+// ordinal records where a kernel's one-time set-up has run.  True exactly once per (guard, device).
+static inline bool zkh_first_on_device(std::atomic<uint64_t>& done, int device) {
+    const uint64_t bit = 1ull << (device & 63);
+    return !(done.fetch_or(bit) & bit);
+}
 
 // make the workspace at least `bytes` large (contents are not preserved)
 int zkh_ws_reserve(zkh_ctx* c, size_t bytes);

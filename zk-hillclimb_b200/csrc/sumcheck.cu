@@ -243,16 +243,19 @@ sc_fused_kernel(ScPtrs P, size_t quads, ZkhCtl* ctl, gl_t* partials, const gl_t*
 // all remaining rounds of a small instance in one CTA, columns in shared memory.
 // n_in: source column length; pending: bind the source with *chal_prev while loading.
 // Column length in shared memory is at most 2*blockDim.x.
+// resid > 0 (sharded proofs, mode 2): after the nrounds local rounds the GPUs all-gather their nc bound values through
+// the peer mailboxes (one more exchange) and every GPU runs the last `resid` = log2(G) rounds on the G-element columns
+// here, without further exchanges: the proof ends in this launch.
 template <int F, int NT, int LD>
 __global__ void __launch_bounds__(1024)
 sc_tail_kernel(ScPtrs P, uint32_t n_in, int pending, ZkhCtl* ctl, const gl_t* chal_prev,
-               gl_t* msg_out, gl_t* chal_out, gl_t* finals_out, int nrounds, ZkhTag tag, int mode = 0) {
+               gl_t* msg_out, gl_t* chal_out, gl_t* finals_out, int nrounds, ZkhTag tag, int mode = 0, int resid = 0) {
     constexpr int NC = Fn<F>::NC;
     extern __shared__ gl_t cols[];
     __shared__ gl_t sh[NT * 32];
     __shared__ gl_t sh_chal;
     const uint32_t tid = threadIdx.x;
-    const uint32_t n0 = pending ? n_in / 2 : n_in;
+    uint32_t n0 = pending ? n_in / 2 : n_in;
     gl_t par[2] = {ctl->par[0], ctl->par[1]};
     if (pending) {
         const gl_t a = *chal_prev;
@@ -271,36 +274,59 @@ sc_tail_kernel(ScPtrs P, uint32_t n_in, int pending, ZkhCtl* ctl, const gl_t* ch
         }
     }
     __syncthreads();
-    uint32_t n = n0;
-    for (int r = 0; r < nrounds; r++) {
-        const uint32_t half = n / 2;
-        Acc192 acc[NT];
+    for (int phase = 0; phase < 2; phase++) {
+        uint32_t n = n0;
+        for (int r = 0; r < nrounds; r++) {
+            const uint32_t half = n / 2;
+            Acc192 acc[NT];
 #pragma unroll
-        for (int t = 0; t < NT; t++) acc[t].clear();
-        gl_t lo[NC], hi[NC];
-        const bool active = tid < half;  // half <= blockDim.x
-        if (active) {
+            for (int t = 0; t < NT; t++) acc[t].clear();
+            gl_t lo[NC], hi[NC];
+            const bool active = tid < half;  // half <= blockDim.x
+            if (active) {
 #pragma unroll
-            for (int k = 0; k < NC; k++) { lo[k] = cols[k * n0 + 2 * tid]; hi[k] = cols[k * n0 + 2 * tid + 1]; }
-            msg_accum<F, NT>(acc, lo, hi, par);
+                for (int k = 0; k < NC; k++) { lo[k] = cols[k * n0 + 2 * tid]; hi[k] = cols[k * n0 + 2 * tid + 1]; }
+                msg_accum<F, NT>(acc, lo, hi, par);
+            }
+            gl_t s[NT];
+            msg_reduce<F, NT>(acc, s);
+            block_sum<NT>(s, sh);  // ends with a barrier: every pair has been read
+            if (tid < 32) {
+                finish_round<NT>(s, ctl, msg_out + (size_t)r * NT, chal_out + r, tag, mode);
+                if (tid == 0) sh_chal = chal_out[r];
+            }
+            __syncthreads();
+            const gl_t a = sh_chal;
+            if (active) {
+#pragma unroll
+                for (int k = 0; k < NC; k++) cols[k * n0 + tid] = gl_lerp(lo[k], hi[k], a);
+            }
+            __syncthreads();
+            n = half;
         }
-        gl_t s[NT];
-        msg_reduce<F, NT>(acc, s);
-        block_sum<NT>(s, sh);  // ends with a barrier: every pair has been read
+        if (phase == 1 || resid == 0) break;
+        // every GPU's bound values -> G-element columns, column k at cols[k * G ..]; the remaining rounds are local
+        __shared__ gl_t xmine[8];
+        __shared__ gl_t xall[ZKH_XCHG_MAXG * 8];
+        __shared__ uint32_t xG;
+        if (tid < NC) { xmine[tid] = cols[tid * n0]; if (finals_out) finals_out[tid] = xmine[tid]; }
+        __syncthreads();
         if (tid < 32) {
-            finish_round<NT>(s, ctl, msg_out + (size_t)r * NT, chal_out + r, tag, mode);
-            if (tid == 0) sh_chal = chal_out[r];
+            const uint32_t G = xchg_allgather(ctl, xmine, NC, xall);
+            if (tid == 0) xG = G;
         }
         __syncthreads();
-        const gl_t a = sh_chal;
-        if (active) {
-#pragma unroll
-            for (int k = 0; k < NC; k++) cols[k * n0 + tid] = gl_lerp(lo[k], hi[k], a);
-        }
+        const uint32_t G = xG;
+        if (tid < NC * G) cols[(tid / G) * G + (tid % G)] = xall[(tid % G) * 8 + tid / G];
         __syncthreads();
-        n = half;
+        msg_out += (size_t)nrounds * NT;
+        chal_out += nrounds;
+        n0 = G;
+        nrounds = resid;
+        mode = 0;
+        finals_out = ctl->finals;
     }
-    if (tid < NC) finals_out[tid] = cols[tid * n0];
+    if (tid < NC && finals_out) finals_out[tid] = cols[tid * n0];
 }
 
 // ------------------------------------------------------------------ host side
@@ -329,13 +355,16 @@ static int sc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, cons
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_fused, sc_fused_kernel<F, NT, LD>, 256, 0);
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_fused_plain,
                                                       sc_fused_kernel<F, NT, LD_PLAIN>, 256, 0);
+        if (occ_first < 1) occ_first = 1;
+        if (occ_fused < 1) occ_fused = 1;
+        if (occ_fused_plain < 1) occ_fused_plain = 1;
+    }
+    static std::atomic<uint64_t> attr_set{0};
+    if (zkh_first_on_device(attr_set, ctx->device)) {   // per device: the limit is a property of the device's function
         cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              NC * (1 << SC_TAIL_LOG) * 8);
         cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, NC * (1 << SC_TAIL_LOG) * 8);
-        if (occ_first < 1) occ_first = 1;
-        if (occ_fused < 1) occ_fused = 1;
-        if (occ_fused_plain < 1) occ_fused_plain = 1;
     }
     auto grid_for = [&](size_t items, int occ) {
         size_t want = (items + 255) / 256, cap = (size_t)ctx->sm_count * occ;
@@ -443,24 +472,26 @@ int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* 
 // pending == 1: columns of length n (<= 2^12) still to be bound with *chal_prev first.
 template <int F, int NT>
 static int sc_tail_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out, gl_t* chal_out,
-                     gl_t* finals_out, const ZkhTag& tag, int pending, const gl_t* chal_prev, int mode) {
+                     gl_t* finals_out, const ZkhTag& tag, int pending, const gl_t* chal_prev, int mode, int resid) {
     constexpr int NC = Fn<F>::NC;
     ScPtrs P;
     memset(&P, 0, sizeof P);
     for (int k = 0; k < NC; k++) P.in[k] = in[k];
     cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          NC * (1 << SC_TAIL_LOG) * 8);
-    const size_t held = pending ? n / 2 : n;
+    size_t held = pending ? n / 2 : n;
+    if (resid > 0 && held < ((size_t)1 << resid)) held = (size_t)1 << resid;   // room for the G-element residual columns
     sc_tail_kernel<F, NT, LD_PLAIN><<<1, 1024, (size_t)NC * held * 8, ctx->stream>>>(P, n, pending, ctx->d_ctl, chal_prev,
                                                                                 msg_out, chal_out, finals_out, nrounds, tag,
-                                                                                mode);
+                                                                                mode, resid);
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(ctx, ZKH_ERR_CUDA, "sumcheck tail launch");
 }
 int sc_enqueue_tail(zkh_ctx* ctx, int functor, int nt, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out,
-                    gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag, int pending, const gl_t* chal_prev, int mode) {
+                    gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag, int pending, const gl_t* chal_prev, int mode,
+                    int resid) {
 #define CASE(F, NT) \
     if (functor == F && nt == NT) \
-        return sc_tail_t<F, NT>(ctx, in, n, nrounds, msg_out, chal_out, finals_out, tag, pending, chal_prev, mode);
+        return sc_tail_t<F, NT>(ctx, in, n, nrounds, msg_out, chal_out, finals_out, tag, pending, chal_prev, mode, resid);
     CASE(ZKH_F_PROD2, 3)
     CASE(ZKH_F_PROD2, 5)
     CASE(ZKH_F_PROD3, 4)
@@ -736,26 +767,39 @@ extern "C" int zkh_shard_round_fused(zkh_ctx* c, uint32_t r) {
 }
 
 // all local rounds of the running sharded sumcheck with the peer exchange, the last ones (columns of at most
-// 2^12 elements) inside one single-CTA kernel per GPU; this rank's bound column values go to finals_dev
-extern "C" int zkh_shard_local_fused(zkh_ctx* c, uint64_t* finals_dev) {
-    if (!c || !finals_dev) return zkh_fail(c, ZKH_ERR_ARG, "shard_local_fused: null pointer");
+// 2^12 elements) inside one single-CTA kernel per GPU; this rank's bound column values go to finals_dev.
+// whole: that last kernel also all-gathers the bound values through the mailboxes and runs the log2(G) residual rounds,
+// so the proof is complete when it ends (no collective and no further launch).
+static int shard_fused(zkh_ctx* c, uint64_t* finals_dev, bool whole) {
     zkh_ctx::Shard& sh = c->shard;
-    if (c->p2p.G < 2) return zkh_fail(c, ZKH_ERR_ARG, "shard_local_fused: peer exchange not connected");
-    if (!sh.active || sh.next_round != 0) return zkh_fail(c, ZKH_ERR_ARG, "shard_local_fused: must follow shard_begin");
+    if (c->p2p.G < 2) return zkh_fail(c, ZKH_ERR_ARG, "shard fused: peer exchange not connected");
+    if (!sh.active || sh.next_round != 0) return zkh_fail(c, ZKH_ERR_ARG, "shard fused: must follow shard_begin");
+    uint32_t k2 = 0;
+    while ((1u << k2) < (uint32_t)c->p2p.G) k2++;
+    if (whole && sh.logn + k2 > 80) return zkh_fail(c, ZKH_ERR_LIMIT, "shard fused: too many rounds");
+    const int resid = whole ? (int)k2 : 0;
     uint32_t r = 0;
     if (sh.logn <= SC_TAIL_LOG) {
         ZKH_TRY(sc_enqueue_tail(c, sh.functor, sh.nt, sh.cur_in, 1u << sh.logn, (int)sh.logn, c->d_ctl->msgs, c->d_ctl->chals,
-                                finals_dev, sh.tag, 0, nullptr, 2));
+                                finals_dev, sh.tag, 0, nullptr, 2, resid));
     } else {
         ZKH_TRY(zkh_shard_round_fused(c, 0));
         for (r = 1; sh.logn - r + 1 > SC_TAIL_LOG + 1; r++) ZKH_TRY(zkh_shard_round_fused(c, r));
         // columns of 2^(logn-r+1) <= 2^12 elements, still to be bound with challenge r-1
         ZKH_TRY(sc_enqueue_tail(c, sh.functor, sh.nt, sh.cur_in, 1u << (sh.logn - r + 1), (int)(sh.logn - r),
                                 c->d_ctl->msgs + (size_t)r * sh.nt, c->d_ctl->chals + r, finals_dev, sh.tag, 1,
-                                c->d_ctl->chals + (r - 1), 2));
+                                c->d_ctl->chals + (r - 1), 2, resid));
     }
-    sh.next_round = sh.logn;
+    sh.next_round = sh.logn + (whole ? k2 : 0);
     return ZKH_OK;
+}
+extern "C" int zkh_shard_local_fused(zkh_ctx* c, uint64_t* finals_dev) {
+    if (!c || !finals_dev) return zkh_fail(c, ZKH_ERR_ARG, "shard_local_fused: null pointer");
+    return shard_fused(c, finals_dev, false);
+}
+extern "C" int zkh_shard_prove_fused(zkh_ctx* c) {
+    if (!c) return ZKH_ERR_ARG;
+    return shard_fused(c, nullptr, true);
 }
 
 extern "C" int zkh_shard_round_local(zkh_ctx* c, uint32_t r, uint64_t* sums_dev) {

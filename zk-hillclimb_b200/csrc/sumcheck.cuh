@@ -44,9 +44,56 @@ int sc_enqueue_round(zkh_ctx* ctx, int functor, int nt, bool first, const gl_t* 
                      int mode = 0);
 int sc_enqueue_tail(zkh_ctx* ctx, int functor, int nt, const gl_t* const* in, uint32_t n, int nrounds, gl_t* msg_out,
                     gl_t* chal_out, gl_t* finals_out, const ZkhTag& tag, int pending = 0, const gl_t* chal_prev = nullptr,
-                    int mode = 0);
+                    int mode = 0, int resid = 0);
 // Absorb nwords 64-bit words of device data under `tag` into the device transcript.
 int tr_absorb_enqueue(zkh_ctx* ctx, const char* tag, const uint64_t* vals_dev, uint32_t nwords);
+
+// ------------------------------------------------------------------ peer exchange
+// All-gather of nv (<= 8) words per GPU through the peer mailboxes (ctl->xchg): publish this GPU's words into slot
+// [seq & 1][rank] of every mailbox, system fence, publish the flag, wait (a bounded number of polls) until this GPU's own
+// mailbox holds every rank's flag for this sequence number, then copy the G x nv words to all[g * 8 + t] (shared memory).
+// A GPU whose device error flag is already set publishes its flag with the poison bit: the GPUs that read it set their own
+// error flag too, so a wait that ran out on one GPU ends the proof with an error status on every GPU instead of leaving the
+// others with sums that no longer match.  Called by all 32 lanes of one warp; mine[] must be visible to the warp.
+// Returns G.
+#define ZKH_XCHG_POISON (1ull << 63)
+static __device__ __noinline__ uint32_t xchg_allgather(ZkhCtl* ctl, const gl_t* mine, int nv, gl_t* all) {
+    ZkhXchg* x = static_cast<ZkhXchg*>(ctl->xchg);
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t G = x->G, me = x->rank;
+    const unsigned long long seq = x->seq + 1;
+    const int slot = (int)(seq & 1);
+    const unsigned int err0 = ctl->err;
+    __syncwarp();
+    if (lane < (uint32_t)nv)
+        for (uint32_t p = 0; p < G; p++)
+            *reinterpret_cast<volatile gl_t*>(&x->mbox[p]->data[slot][me][lane]) = mine[lane];
+    __threadfence_system();
+    __syncwarp();
+    if (lane < G)
+        *reinterpret_cast<volatile unsigned long long*>(&x->mbox[lane]->flag[slot][me]) = seq | (err0 ? ZKH_XCHG_POISON : 0ull);
+    bool ok = true;
+    if (lane < G) {
+        volatile unsigned long long* f = &x->mbox[me]->flag[slot][lane];
+        const uint32_t limit = err0 ? 0u : (1u << 21);   // about a second, then give up with an error flag
+        uint32_t it = 0;
+        unsigned long long v = *f;
+        while ((v & ~ZKH_XCHG_POISON) != seq && it < limit) { __nanosleep(128); it++; v = *f; }
+        ok = (v == seq);                                 // arrived, and the sender had no error
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    __threadfence_system();
+    for (uint32_t i = lane; i < G * (uint32_t)nv; i += 32) {
+        const uint32_t g = i / (uint32_t)nv, t = i % (uint32_t)nv;
+        all[g * 8 + t] = *reinterpret_cast<volatile gl_t*>(&x->mbox[me]->data[slot][g][t]);
+    }
+    if (lane == 0) {
+        x->seq = seq;
+        if (!ok) atomicOr(&ctl->err, 4u);
+    }
+    __syncwarp();
+    return G;
+}
 
 // ------------------------------------------------------------------ round end
 // mode 0: absorb the message under `tag` and draw the challenge on the device.
@@ -66,38 +113,15 @@ __device__ __noinline__ void finish_round(const gl_t (&s)[NT], ZkhCtl* ctl, gl_t
     }
     if (mode == 1) return;
     if (mode == 2) {
-        // sum over the GPUs through the peer mailboxes: publish, fence, flag, bounded wait, add in rank order
-        ZkhXchg* x = static_cast<ZkhXchg*>(ctl->xchg);
-        const uint32_t G = x->G, me = x->rank;
-        const unsigned long long seq = x->seq + 1;
-        const int slot = (int)(seq & 1);
+        // sum over the GPUs through the peer mailboxes, in rank order
+        __shared__ gl_t xall[ZKH_XCHG_MAXG * 8];
         __syncwarp();
-        if (lane < NT)
-            for (uint32_t p = 0; p < G; p++)
-                *reinterpret_cast<volatile gl_t*>(&x->mbox[p]->data[slot][me][lane]) = mvals[lane];
-        __threadfence_system();
-        __syncwarp();
-        if (lane < G) *reinterpret_cast<volatile unsigned long long*>(&x->mbox[lane]->flag[slot][me]) = seq;
-        bool arrived = true;
-        if (lane < G) {
-            volatile unsigned long long* f = &x->mbox[me]->flag[slot][lane];
-            const uint32_t limit = ctl->err ? 0u : (1u << 21);   // about a second, then give up with an error flag
-            uint32_t it = 0;
-            while (*f != seq && it < limit) { __nanosleep(128); it++; }
-            arrived = (*f == seq);
-        }
-        arrived = __all_sync(0xffffffffu, arrived);
-        __threadfence_system();
+        const uint32_t G = xchg_allgather(ctl, mvals, NT, xall);
         if (lane < NT) {
             gl_t a = 0;
-            for (uint32_t g = 0; g < G; g++)
-                a = gl_add(a, *reinterpret_cast<volatile gl_t*>(&x->mbox[me]->data[slot][g][lane]));
+            for (uint32_t g = 0; g < G; g++) a = gl_add(a, xall[g * 8 + lane]);
             mvals[lane] = a;
             msg_out[lane] = a;
-        }
-        if (lane == 0) {
-            x->seq = seq;
-            if (!arrived) atomicOr(&ctl->err, 4u);
         }
         __syncwarp();
     }

@@ -613,6 +613,9 @@ class Prover:
     def shard_local_fused(self, fin):
         self._ck(self._L.zkh_shard_local_fused(self._h, _ptr(fin)))
 
+    def shard_prove_fused(self):
+        self._ck(self._L.zkh_shard_prove_fused(self._h))
+
     def shard_round_local(self, r, sums):
         self._ck(self._L.zkh_shard_round_local(self._h, r, _ptr(sums)))
 
@@ -748,14 +751,22 @@ class Prover:
         return chals, msgs, fin
 
 
-def sc_prove_sharded(engine, tr, tag, dcols, functor, nt, dist=None, par=(), group=None):
+def sc_prove_sharded(engine, tr, tag, dcols, functor, nt, dist=None, par=(), group=None, rendezvous=True):
     """p3sg::sc_prove_gpu over several GPUs of one node: the hypercube is split on its top
     log2(G) variables, rank g holding slice g of every column (``dcols``: this rank's slices).
-    Per round the ranks all-gather their nt partial sums (nt*8 bytes each); every rank adds
-    them mod p, runs the same transcript step and binds its own slice.  After the local
-    rounds the G per-rank values of each column are all-gathered and every rank finishes the
+    Per round the ranks exchange their nt partial sums (nt*8 bytes each); every rank adds
+    them mod p in rank order, runs the same transcript step and binds its own slice.  After the local
+    rounds the G per-rank values of each column are exchanged and every rank finishes the
     last log2(G) rounds.  Returns (r, msgs, finals) exactly as sc_prove_gpu would on the
     concatenated columns; ``tr`` advances identically on every rank.
+
+    With the peer exchange connected (Prover.p2p_connect) the whole proof is device code: one kernel per
+    round with the sums crossing NVLink as peer stores, the last kernel also exchanging the bound values
+    and running the residual rounds; no collective call is made.  The device waits are bounded to about
+    a second, so ``rendezvous`` (default) first completes this rank's stream and meets the other ranks at
+    a host barrier; a caller that issues proofs back to back passes rendezvous=False for all but the
+    first of the series (only kernel skew separates the ranks then).
+    Without the peer exchange every round is all-gathered with ``dist``.
 
     ``engine``: a Prover (CUDA) -- or, in the CPU tests of this host logic, an object with the
     same shard_* methods.  ``dist``: torch.distributed (initialised) or None for one rank."""
@@ -774,23 +785,23 @@ def sc_prove_sharded(engine, tr, tag, dcols, functor, nt, dist=None, par=(), gro
         else:
             dist.all_gather_into_tensor(out, inp, group=group)
 
-    engine.shard_begin(functor, nt, dcols, logn, par, tag, tr.state)
-    fin, gfin = engine.new_buffer(nc), engine.new_buffer(G * nc)
     if G > 1 and getattr(engine, "p2p_ready", False):
-        # the waits inside the fused rounds are bounded (about a second): meet on the host first, inputs complete, so that they
-        # only have to cover kernel skew and not whatever each rank did before (staging copies, page pinning, allocation)
-        engine.sync()
-        dist.barrier(group=group)
-        engine.shard_local_fused(fin)              # one kernel per round, sums cross NVLink as peer stores
+        if rendezvous:
+            engine.sync()
+            dist.barrier(group=group)
+        engine.shard_begin(functor, nt, dcols, logn, par, tag, tr.state)
+        engine.shard_prove_fused()
     else:
+        engine.shard_begin(functor, nt, dcols, logn, par, tag, tr.state)
+        fin, gfin = engine.new_buffer(nc), engine.new_buffer(G * nc)
         sums, gathered = engine.new_buffer(nt), engine.new_buffer(G * nt)
         for r in range(logn):
             engine.shard_round_local(r, sums)
             all_gather(gathered, sums)
             engine.shard_round_combine(r, gathered, G)
         engine.shard_finals(fin)
-    all_gather(gfin, fin)
-    engine.shard_residual(gfin, G)
+        all_gather(gfin, fin)
+        engine.shard_residual(gfin, G)
     state, msgs, chals, finals = engine.shard_end(logn + k)
     tr.state = state
     return chals, msgs, finals
