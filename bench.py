@@ -697,7 +697,7 @@ def run_suite_layer(args):
                 x0, Wt = ig.random_layer_inputs(c, 42 + tries, 0.9 * (0.7 ** (tries // 2)))
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
-                w = ig_dev.itf_build_witness(c, x0, Wt, T) if on_dev else ig.itf_build_witness(c, x0, Wt, T)
+                w = ig_dev.itf_build_witness(c, x0, Wt, T, engine=prover) if on_dev else ig.itf_build_witness(c, x0, Wt, T)
                 torch.cuda.synchronize()
                 t_wit = time.perf_counter() - t0
                 break
@@ -708,7 +708,7 @@ def run_suite_layer(args):
         if on_dev:                                  # second run: kernels and allocator warm
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            w = ig_dev.itf_build_witness(c, x0, Wt, T)
+            w = ig_dev.itf_build_witness(c, x0, Wt, T, engine=prover)
             torch.cuda.synchronize()
             t_wit = time.perf_counter() - t0
         wcol = (lambda a: a) if on_dev else col
@@ -1103,7 +1103,8 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
     ident = lambda a: a
     out = {"metric": "prove s/layer (TinyLlama-1.1B-shaped integer decoder layer, seq 512, R=2, Q=24)",
            "layers": nlayers, "n_gpus": world, "placement": "layer l on GPU l mod N; no collective on the data path",
-           "timed": "witness chain + commitments + proof of every layer (CUDA events per rank, max over ranks)",
+           "timed": "upload of the layer's weights and input from pinned host memory + witness chain + commitments + proof "
+                    "of every layer (CUDA events per rank, max over ranks)",
            "dims": dict(zip(("seq", "d", "nh", "dh", "dff", "batch"), dims)),
            "shape_note": "hidden 2048, 32 heads of 64 (each KV head replicated 8x), MLP 5632 padded to 8192"}
     err = None
@@ -1111,12 +1112,13 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
         cfg = ig.Config(*dims)
         tabs = ig.build_tables(zk.load_library(), cfg.d, cfg.btop)
         lx0, lW = ig.random_layer_inputs(cfg, 42, 0.9)
+        px0, pW = ig_dev.pin_inputs(lx0, lW)       # signed int32 in pinned host memory, as a weight loader would hold them
     except Exception as e:
         err = repr(e)
 
     def one_layer(layer, hiding, acc):
         t = [time.perf_counter()]
-        lw = ig_dev.itf_build_witness(cfg, lx0, lW, tabs, dvc)
+        lw = ig_dev.itf_build_witness(cfg, px0, pW, tabs, dvc, prover)   # uploads the inputs, then all device code
         torch.cuda.synchronize()
         t.append(time.perf_counter())
         if hiding:
@@ -1213,13 +1215,14 @@ def reference_layer_figure(args, zk, prover):
         cfg = ig.Config(*dims)
         tabs = ig.build_tables(zk.load_library(), cfg.d, cfg.btop)
         x0, Wt = ig.random_layer_inputs(cfg, 42, 0.9)
+        px0, pW = ig_dev.pin_inputs(x0, Wt)
         best = None
         prover.keep_trees = not hiding
         for rep in range(2):
             prover.release_kept()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            w = ig_dev.itf_build_witness(cfg, x0, Wt, tabs)
+            w = ig_dev.itf_build_witness(cfg, px0, pW, tabs, "cuda:0", prover)
             torch.cuda.synchronize()
             t1 = time.perf_counter()
             if hiding:

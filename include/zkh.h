@@ -361,6 +361,17 @@ ZKH_API int zkh_gl_matvec(zkh_ctx* ctx, const uint64_t* M_dev, uint64_t rows, ui
  * Stream-ordered. */
 ZKH_API int zkh_gl_matmul(zkh_ctx* ctx, const uint64_t* A_dev, const uint64_t* B_dev, uint64_t I, uint64_t J, uint64_t K,
                           uint64_t* C_dev);
+/* Exact integer matrix products of the integer decoder layer's witness chain: p3itf::build_witness computes the seven
+ * weight matmuls and the per-head score / attention-output products on the host (zkllm-src/p3_int_layer.cuh:182-318 over
+ * p3imm::matmul_i64, p3_int_gadgets.cuh:493-508).  For every batch entry (b0, b1), b0 < nb0, b1 < nb1:
+ *     C[b0][b1][i][k] = sum_j A[b0][b1][i][j] * B[b0][b1][j][k],   i < I, j < J, k < K,
+ * where X[b0][b1][r][c] is the element at X_dev + b0*s[0] + b1*s[1] + r*s[2] + c*s[3] (element strides), so the per-head
+ * slices of the (batch, position, head, lane) activations are addressed in place.  Operands and results are field
+ * elements standing for signed integers (v, or p - |v|); operands must lie in (-2^24, 2^24) (ZKH_ERR_DOMAIN otherwise)
+ * and J <= 2^15, so every sum is exact in 64 bits.  Synchronises the stream (it reports the range check). */
+ZKH_API int zkh_ig_matmul(zkh_ctx* ctx, const uint64_t* A_dev, const int64_t a_strides[4], const uint64_t* B_dev,
+                          const int64_t b_strides[4], uint64_t* C_dev, const int64_t c_strides[4], uint32_t nb0,
+                          uint32_t nb1, uint32_t I, uint32_t J, uint32_t K);
 /* out[i] = a[i]*b[i]: the helper column hT = cnt * 1/(Tc+beta) of the standalone lookup
  * (zkllm-src/p3_logup.cuh:984).  Stream-ordered. */
 ZKH_API int zkh_gl_mul(zkh_ctx* ctx, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev);

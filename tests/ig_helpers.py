@@ -109,3 +109,19 @@ def ref_itf_prove(ref, st, c, x0, Wt, R, Q):
     f.restype = C.c_size_t
     n = f(s, dims, vp(x0c), wp, vp(g1), vp(g2), vp(ct), vp(sn), C.c_uint32(R), C.c_uint32(Q), out, C.c_size_t(cap), vp(grid), ms)
     return bytes(out[:n]), bytes(s), grid, list(ms)
+
+
+class StridedMatmulEngine:
+    """CPU stand-in for Prover.ig_matmul (the strided exact integer products of the device witness chain): the views are
+    rebuilt with numpy strides over the signed values, multiplied in int64 and written back lifted."""
+
+    def ig_matmul(self, A, a_str, B, b_str, Cc, c_str, nb0, nb1, I, J, K):
+        def signed(t):
+            a = t.numpy().view(np.uint64)
+            return np.where(a >> np.uint64(63), a + np.uint64(0xFFFFFFFF), a).view(np.int64)
+
+        def view(a, st, rows, cols):
+            return np.lib.stride_tricks.as_strided(a, shape=(nb0, nb1, rows, cols), strides=[8 * int(x) for x in st])
+        y = np.einsum("abij,abjk->abik", view(signed(A), a_str, I, J), view(signed(B), b_str, J, K))
+        out = Cc.numpy()
+        view(out, c_str, I, K)[...] = np.where(y < 0, y.view(np.uint64) - np.uint64(0xFFFFFFFF), y.view(np.uint64)).view(np.int64)

@@ -157,3 +157,32 @@ def test_ismx(orc, ref_or_none, zk, prover, tables):
         n = f(s, z.ctypes.data_as(C.c_void_p), roots["r"][0], roots["r"][1], C.c_uint32(la), C.c_uint32(lseq), C.c_uint32(R),
               C.c_uint32(Q), out, C.c_size_t(32 << 20), None)
         assert bytes(out)[:n] == pf and bytes(s) == st
+
+
+@pytest.mark.parametrize("nb0,nb1,I,J,K", [(1, 1, 16, 32, 16), (1, 1, 130, 70, 67), (2, 4, 64, 16, 64), (1, 3, 256, 512, 64), (1, 1, 512, 2048, 128)])
+def test_integer_matmul_kernel_equals_int64_products(zk, prover, nb0, nb1, I, J, K):
+    """zkh_ig_matmul (the witness chain's exact integer products, p3imm::matmul_i64 in the reference) against int64 numpy products:
+    plain row-major operands, transposed B (the score product's view), and head-sliced (batch, position, head, lane) views."""
+    import torch
+    from ig_helpers import StridedMatmulEngine
+    rng = np.random.default_rng(I * 131 + J)
+    P = 0xFFFFFFFF00000001
+    lift = lambda a: np.where(a < 0, a.astype(np.int64).view(np.uint64) - np.uint64(0xFFFFFFFF), a.astype(np.int64).view(np.uint64))
+    chk = StridedMatmulEngine()
+    nb = nb0 * nb1
+    layouts = [((nb1 * I * J, I * J, J, 1), (nb1 * J * K, J * K, K, 1), (nb1 * I * K, I * K, K, 1)),           # row-major, batched
+               ((nb1 * I * J, I * J, J, 1), (nb1 * J * K, J * K, 1, J), (nb1 * I * K, I * K, K, 1)),           # B stored transposed
+               ((I * nb1 * J, J, nb1 * J, 1), (J * nb1 * K, K, nb1 * K, 1), (I * nb1 * K, K, nb1 * K, 1))]     # (b0, row, b1, col)
+    for sa, sb, sc in layouts:
+        A = lift(rng.integers(-(1 << 19) + 1, 1 << 19, nb * I * J))
+        B = lift(rng.integers(-(1 << 19) + 1, 1 << 19, nb * J * K))
+        want = torch.zeros(nb * I * K, dtype=torch.int64)
+        chk.ig_matmul(torch.from_numpy(A.view(np.int64)), sa, torch.from_numpy(B.view(np.int64)), sb, want, sc, nb0, nb1, I, J, K)
+        got = torch.zeros(nb * I * K, dtype=torch.int64, device="cuda")
+        prover.ig_matmul(zk.p3.to_device(A), sa, zk.p3.to_device(B), sb, got, sc, nb0, nb1, I, J, K)
+        assert (got.cpu() == want).all()
+        assert bool(((zk.p3.to_host(got) < P)).all())
+    big = A.copy()
+    big[3] = 1 << 30                                     # an operand outside the range is refused, not wrapped
+    with pytest.raises(zk.ZkhError):
+        prover.ig_matmul(zk.p3.to_device(big), sa, zk.p3.to_device(B), sb, got, sc, nb0, nb1, I, J, K)

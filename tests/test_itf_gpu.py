@@ -77,7 +77,11 @@ def test_device_witness_chain_equals_host_chain(zk, prover, dims):
     T = ig.build_tables(zk.load_library(), c.d, c.btop)
     x0, Wt = layer_inputs(ig, c, 9)
     w = ig.itf_build_witness(c, x0, Wt, T)
-    wd = ig_dev.itf_build_witness(c, x0, Wt, T)
+    wd = ig_dev.itf_build_witness(c, x0, Wt, T, engine=prover)
+    px0, pW = ig_dev.pin_inputs(x0, Wt)          # the same chain from signed int32 inputs in pinned memory
+    wp = ig_dev.itf_build_witness(c, px0, pW, T, engine=prover)
+    for k, v in w.items():
+        assert _same(v, wp[k]), k
     for k, v in w.items():
         assert _same(v, wd[k]), k
     ident = lambda a: a

@@ -4,7 +4,7 @@ accepted by the reference's own host-only layer verifier on the same transcript.
 import numpy as np
 import pytest
 
-from ig_helpers import OracleGadgetEngine, arr, layer_inputs, ref_itf_verify
+from ig_helpers import OracleGadgetEngine, StridedMatmulEngine, arr, layer_inputs, ref_itf_verify
 
 
 @pytest.mark.parametrize("dims", [(4, 8, 2, 4, 16, 1), (4, 8, 2, 4, 8, 2)])
@@ -58,7 +58,7 @@ def test_tensor_witness_chain_equals_numpy_chain(zk, dims):
     T = ig.build_tables(zk.load_library(), c.d, c.btop)
     x0, Wt = layer_inputs(ig, c, 9)
     w = ig.itf_build_witness(c, x0, Wt, T)
-    wd = ig_dev.itf_build_witness(c, x0, Wt, T, device="cpu")
+    wd = ig_dev.itf_build_witness(c, x0, Wt, T, device="cpu", engine=StridedMatmulEngine())
     for k, v in w.items():
         a, b = _flat(v), _flat(wd[k])
         assert len(a) == len(b), k

@@ -52,6 +52,17 @@ def test_histogram(orc, zk, prover, M, n):
         assert ei.value.code == -4
 
 
+@pytest.mark.parametrize("M", [1 << 16, 1 << 18])
+def test_histogram_hot_bin_and_uniform(orc, zk, prover, M):
+    """Every index on one row (the padding members of a merged lookup) and uniformly spread indices: the two extremes of
+    contention for the bins held in shared memory."""
+    import torch
+    n = (1 << 21) + 5
+    for idx in (np.full(n, M - 7, dtype=np.uint32), np.random.default_rng(M).integers(0, M, n).astype(np.uint32)):
+        cnt = zk.p3.to_host(prover.histogram(torch.from_numpy(idx.view(np.int32)).cuda(), M))
+        assert (cnt == orc.histogram(idx, M)).all() and int(cnt.sum()) == n
+
+
 def test_gkr_golden(golden, orc, ref_or_none, zk, prover):
     for g in golden["gkr"]:
         L, cl = g["L"], g["combine_last"]

@@ -3,17 +3,19 @@
 //   histogram    zkllm-src/p3_logup.cuh:149-172 (p3lu_cntg/cnts_kernel), host loop :1412-1475
 //   inversion    zkllm-src/p3_logup.cuh:636-660 (inv_all_add, host OpenMP Montgomery trick)
 //   combine      zkllm-src/p3_logup.cuh:663-672 (combine), :93-107 (device Am build)
+#include <cooperative_groups.h>
 #include "common.cuh"
 
 namespace zkh {
 
 // Counting is order-free integer accumulation, so the bins equal the host loop's exactly.
 // Tables of up to 2^15 rows are counted in shared memory (32-bit sub-histograms flushed with
-// 64-bit atomics).  Tables of up to 2^18 rows are cut into windows of 2^15 bins: blockIdx.y picks the
-// window, every CTA scans its slice of the indices and counts only those inside its window, so the
-// indices are read once per window but every increment is a shared-memory atomic (skewed lookups
-// such as range checks of Gaussian activations serialise in L2 otherwise).  Larger tables go
-// straight to 64-bit global atomics.
+// 64-bit atomics).  Tables of up to 2^18 rows are counted by thread-block clusters: the 2, 4 or 8 CTAs of a
+// cluster each hold 2^15 bins in their shared memory (128 KB), the cluster scans its slice of the indices ONCE
+// and every increment is a shared-memory atomic, on the CTA's own bins or on a neighbour's through distributed
+// shared memory (skewed lookups such as range checks of Gaussian activations serialise in L2 otherwise).
+// Where a cluster cannot be launched the same tables are cut into windows of 2^15 bins, blockIdx.y picking the
+// window (the indices are then read once per window).  Larger tables go straight to 64-bit global atomics.
 __global__ void __launch_bounds__(512)
 hist_shared_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsigned long long* bins,
                    unsigned int* oob) {
@@ -59,6 +61,47 @@ hist_window_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsig
     if (bad && blockIdx.y == 0) atomicAdd(oob, bad);
     __syncthreads();
     for (uint32_t t = threadIdx.x; t < W && base + t < M; t += blockDim.x)
+        if (shc[t]) atomicAdd(&bins[base + t], (unsigned long long)shc[t]);
+}
+// One cluster = ceil(M / 2^15) CTAs (a power of two, at most 8); CTA `rank` owns bins [rank * 2^15, (rank + 1) * 2^15).
+// 1024 threads per CTA and four independent 16-byte loads in flight per thread cover the DRAM latency.
+constexpr uint32_t HC_BINS = 1u << 15;
+__global__ void __launch_bounds__(1024)
+hist_cluster_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsigned long long* bins, unsigned int* oob) {
+    namespace cg = cooperative_groups;
+    extern __shared__ uint32_t shc[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank(), csize = cluster.num_blocks();
+    for (uint32_t t = threadIdx.x; t < HC_BINS; t += blockDim.x) shc[t] = 0;
+    cluster.sync();                                     // every member's bins are zero before anyone increments them
+    const size_t nclusters = gridDim.x / csize, cid = blockIdx.x / csize;
+    const size_t lane = (cid * csize + rank) * blockDim.x + threadIdx.x, stride = nclusters * csize * blockDim.x;
+    const size_t n4 = n / 4;
+    const uint4* idx4 = reinterpret_cast<const uint4*>(idx);
+    unsigned bad = 0;
+    auto count = [&](uint32_t r) {
+        if (r >= M) { bad++; return; }
+        uint32_t* dst = cluster.map_shared_rank(shc, r >> 15);
+        atomicAdd(dst + (r & (HC_BINS - 1)), 1u);
+    };
+    for (size_t i = lane; i < n4; i += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const size_t k = i + (size_t)u * stride;
+            v[u] = k < n4 ? __ldg(idx4 + k) : make_uint4(~0u, ~0u, ~0u, ~0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (i + (size_t)u * stride >= n4) break;
+            count(v[u].x); count(v[u].y); count(v[u].z); count(v[u].w);
+        }
+    }
+    for (size_t i = 4 * n4 + lane; i < n; i += stride) count(idx[i]);
+    if (bad) atomicAdd(oob, bad);
+    cluster.sync();                                     // all increments, the neighbours' too, have landed
+    const uint32_t base = rank * HC_BINS;
+    for (uint32_t t = threadIdx.x; t < HC_BINS && base + t < M; t += blockDim.x)
         if (shc[t]) atomicAdd(&bins[base + t], (unsigned long long)shc[t]);
 }
 __global__ void __launch_bounds__(256)
@@ -135,14 +178,40 @@ extern "C" int zkh_histogram(zkh_ctx* c, const uint32_t* idx_dev, uint64_t n, ui
                 idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
         } else if (M <= (1u << 18) && ((uintptr_t)idx_dev & 15) == 0) {
             static std::atomic<uint64_t> attr{0};
-            if (zkh_first_on_device(attr, c->device))
+            if (zkh_first_on_device(attr, c->device)) {
                 cudaFuncSetAttribute(hist_window_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+                cudaFuncSetAttribute(hist_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+            }
             const unsigned windows = (M + (1u << 15) - 1) >> 15;
-            size_t blocks = (n + 512 * 64 - 1) / (512 * 64), cap = (size_t)c->sm_count / windows;
-            if (cap < 1) cap = 1;
-            if (blocks < 1) blocks = 1;
-            hist_window_kernel<<<dim3((unsigned)(blocks < cap ? blocks : cap), windows), 512, 128 * 1024, c->stream>>>(
-                idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
+            unsigned csize = 1;
+            while (csize < windows) csize <<= 1;
+            // clusters: one pass over the indices
+            size_t ncl = (size_t)c->sm_count / csize, want = (n / 4 + (size_t)1024 * 4 * csize - 1) / ((size_t)1024 * 4 * csize);
+            if (ncl < 1) ncl = 1;
+            if (want < 1) want = 1;
+            if (want < ncl) ncl = want;
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof cfg);
+            cfg.gridDim = dim3((unsigned)(ncl * csize));
+            cfg.blockDim = dim3(1024);
+            cfg.dynamicSmemBytes = 128 * 1024;
+            cfg.stream = c->stream;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = csize;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            cudaError_t le = cudaLaunchKernelEx(&cfg, hist_cluster_kernel, idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
+            if (le != cudaSuccess) {        // no room for such a cluster on this device: windows, one read of the indices each
+                cudaGetLastError();
+                size_t blocks = (n + 512 * 64 - 1) / (512 * 64), cap = (size_t)c->sm_count / windows;
+                if (cap < 1) cap = 1;
+                if (blocks < 1) blocks = 1;
+                hist_window_kernel<<<dim3((unsigned)(blocks < cap ? blocks : cap), windows), 512, 128 * 1024, c->stream>>>(
+                    idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
+            }
         } else {
             size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 8;
             hist_global_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(

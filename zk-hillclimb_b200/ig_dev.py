@@ -1,9 +1,10 @@
 """Witness chain of the integer decoder layer on the GPU (torch int64 tensors carrying the field's uint64 bit
 patterns): the same integer replays as ig.py's numpy functions (p3itf::build_witness and the gadgets'
 gen_witness, zkllm-src/p3_int_layer.cuh:182-318, p3_int_gadgets.cuh), so that no witness column crosses PCIe and
-the host does no O(N) work.  Matrix products run in float64 on the device (exact: |x|, |w| < 2^19 and at most 2^13
-terms keep every partial sum below 2^53).  Every function returns the same dictionary / tuple layout as its
-numpy twin with device tensors in place of arrays; index arrays are int32 tensors holding uint32 values.
+the host does no O(N) work.  Matrix products (the seven weight matmuls and the per-head score and attention-output
+products) run in the library's exact integer kernel (zkh_ig_matmul, strided views: no gathers, no index arrays);
+the element-wise replays are integer tensor arithmetic.  Every function returns the same dictionary / tuple layout
+as its numpy twin with device tensors in place of arrays; index arrays are int32 tensors holding uint32 values.
 """
 import numpy as np
 import torch
@@ -29,11 +30,28 @@ def _u32(x):
 
 
 def dev(a, device):
-    """numpy (uint64 field elements or integer tables) -> device tensor with the same bits."""
+    """numpy (uint64 field elements or integer tables) -> device tensor with the same bits.  A torch int32 tensor (the
+    signed values, see pin_inputs) is copied as it is and lifted on the device: half the bytes over PCIe, and from
+    pinned memory the copy needs no staging."""
+    if isinstance(a, torch.Tensor):
+        t = a.to(device, non_blocking=True)
+        return lift(t.to(torch.int64)) if t.dtype == torch.int32 else t
     a = np.ascontiguousarray(a)
     if a.dtype == np.uint64:
         return torch.from_numpy(a.view(np.int64)).to(device)
     return torch.from_numpy(a).to(device)
+
+
+def pin_inputs(x0, Wt):
+    """The layer's inputs (field-lifted numpy columns as ig.random_layer_inputs returns them) as signed int32 tensors in
+    pinned host memory, the form a weight loader would keep them in: (x0, weights) for itf_build_witness."""
+    def pin(a):
+        a = np.ascontiguousarray(a)
+        if a.dtype == np.uint64:
+            a = np.where(a >> np.uint64(63), a + np.uint64(0xFFFFFFFF), a).view(np.int64)
+        t = torch.from_numpy(a.astype(np.int32))
+        return t.pin_memory() if torch.cuda.is_available() else t
+    return pin(x0), {"w": [pin(x) for x in Wt["w"]], "g1": pin(Wt["g1"]), "g2": pin(Wt["g2"]), "ct": Wt["ct"], "st": Wt["st"]}
 
 
 def irs_witness(acc, sf, rng):
@@ -169,24 +187,31 @@ def rs20_idx(v):
     return _u32(s + ABND)
 
 
-def itf_build_witness(c, x0, Wt, T, device="cuda:0"):
-    """p3itf::build_witness on the device.  x0, Wt as for ig.itf_build_witness (host arrays); returns the same
-    dictionary with device tensors, plus "dev_W" = the weights / gains as device columns (for itf_commit_all)."""
+def itf_build_witness(c, x0, Wt, T, device="cuda:0", engine=None):
+    """p3itf::build_witness on the device.  x0, Wt as for ig.itf_build_witness (host arrays, or the pinned int32 tensors of
+    pin_inputs); returns the same dictionary with device tensors, plus "dev_W" = the weights / gains as device columns
+    (for itf_commit_all).  engine: the Prover whose ig_matmul runs the matrix products (one is created for the device
+    when none is given)."""
     ld, lT, ldff, lseq, ldh, la = c.ld, c.lT, c.ldff, c.lseq, c.ldh, c.la
     le, lef, lez = ld + lT, ldff + lT, la + 2 * lseq
+    if engine is None:
+        from .p3 import Prover
+        dv = torch.device(device)
+        engine = Prover(dv.index or 0, torch.cuda.current_stream(dv).cuda_stream)
     d = lambda a: dev(a, device)
     x0 = d(x0)
     Wd = {"w": [d(x) for x in Wt["w"]], "g1": d(Wt["g1"]), "g2": d(Wt["g2"]), "ct": d(Wt["ct"]), "st": d(Wt["st"])}
     silu, isq, expt = (sig(d(T[n]["cols"][1])) for n in ("SILU", "ISQ", "EXPT"))
     w = {"x0": x0, "dev_W": Wd, "idxW": [rs20_idx(x) for x in Wd["w"]], "idxG1": rs20_idx(Wd["g1"]), "idxG2": rs20_idx(Wd["g2"]),
          "idxX0": rs20_idx(x0)}
+    seq, nh, dh, dm, nb = c.seq, c.nh, c.dh, c.d, c.batch
 
     def mat(X, Wm, K, N):
-        y = sig(X).reshape(-1, K).to(torch.float64) @ sig(Wm).reshape(K, N).to(torch.float64)
-        return lift(torch.round(y).to(torch.int64).reshape(-1))
-
-    def vidx(view, nf, ns, first, second):
-        return torch.from_numpy(ig._view_idx(view, nf, ns, first, second)).to(device)
+        """(rows x K) . (K x N), both row-major columns of field-lifted integers."""
+        rows = X.numel() // K
+        out = torch.empty(rows * N, dtype=torch.int64, device=X.device)
+        engine.ig_matmul(X, (0, 0, K, 1), Wm, (0, 0, N, 1), out, (0, 0, N, 1), 1, 1, rows, K, N)
+        return out
 
     w["rms1"] = irms_witness(x0, Wd["g1"], isq, lT, ld)
     w["h1"] = w["rms1"]["y"]
@@ -198,28 +223,21 @@ def itf_build_witness(c, x0, Wt, T, device="cuda:0"):
     w["rpq"] = irope_witness(w["yq"], Wd["ct"], Wd["st"], lseq, ldh, lT, ld)
     w["rpk"] = irope_witness(w["yk"], Wd["ct"], Wd["st"], lseq, ldh, lT, ld)
     w["rq"], w["rk"] = w["rpq"][0], w["rpk"][0]
-    sc = torch.zeros(1 << lez, dtype=torch.int64, device=device)
-    rq, rk = sig(w["rq"]).to(torch.float64), sig(w["rk"]).to(torch.float64)
-    for b in range(c.batch):
-        for h in range(c.nh):
-            xv, wv, yv = ig.views_qk(c, h, b)
-            Xd = rq[vidx(xv, ldh, lseq, ig.S_J, ig.S_A)]
-            Wdd = rk[vidx(wv, ldh, lseq, ig.S_J, ig.S_A)]
-            sc[vidx(yv, lseq, lseq, ig.S_A, ig.S_I)] = torch.round(Xd @ Wdd.T).to(torch.int64)
-    w["sc"] = lift(sc)
+    # scores of head h, batch b (xview_qk / wview_qk / yview_qk, p3_int_layer.cuh:96-122): sc[a][i][k] = sum_j RQ[b][i][h][j] *
+    # RK[b][k][h][j], a = b * nh + h; the activations are laid out (batch, position, head, lane)
+    sc = torch.empty(1 << lez, dtype=torch.int64, device=device)
+    engine.ig_matmul(w["rq"], (seq * dm, dh, dm, 1), w["rk"], (seq * dm, dh, 1, dm), sc, (nh * seq * seq, seq * seq, seq, 1),
+                     nb, nh, seq, dh, seq)
+    w["sc"] = sc
     w["rsz"] = irs_witness(w["sc"], c.sfz, 2)
     w["z"] = w["rsz"][0]
     w["smx"] = ismx_witness(w["z"], expt, la, lseq)
     w["p"] = w["smx"]["p"]
-    pva = torch.zeros(1 << le, dtype=torch.int64, device=device)
-    pp, yv_ = sig(w["p"]).to(torch.float64), sig(w["yv"]).to(torch.float64)
-    for b in range(c.batch):
-        for h in range(c.nh):
-            xv, wv, yv = ig.views_pv(c, h, b)
-            Xd = pp[vidx(xv, lseq, lseq, ig.S_J, ig.S_A)]
-            Wdd = yv_[vidx(wv, lseq, ldh, ig.S_J, ig.S_A)]
-            pva[vidx(yv, ldh, lseq, ig.S_A, ig.S_I)] = torch.round(Xd @ Wdd.T).to(torch.int64)
-    w["pva"] = lift(pva)
+    # attention output (xview_pv / wview_pv / yview_pv, p3_int_layer.cuh:124-148): PVA[b][i][h][k] = sum_j P[a][i][j] * YV[b][j][h][k]
+    pva = torch.empty(1 << le, dtype=torch.int64, device=device)
+    engine.ig_matmul(w["p"], (nh * seq * seq, seq * seq, seq, 1), w["yv"], (seq * dm, dh, dm, 1), pva, (seq * dm, dh, dm, 1),
+                     nb, nh, seq, seq, dh)
+    w["pva"] = pva
     w["rsat"] = irs_witness(w["pva"], 16, 1)
     w["at"] = w["rsat"][0]
     w["acc"][ig.W_O] = mat(w["at"], Wd["w"][ig.W_O], c.d, c.d)

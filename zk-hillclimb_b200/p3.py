@@ -387,6 +387,13 @@ class Prover:
         self._ck(self._L.zkh_gl_matmul(self._h, _ptr(A_dev), _ptr(B_dev), I, J, K, _ptr(out)))
         return out
 
+    def ig_matmul(self, A, a_str, B, b_str, Cc, c_str, nb0, nb1, I, J, K):
+        """Exact integer matrix products of the layer's witness chain (zkh_ig_matmul): C[b0][b1] = A[b0][b1] . B[b0][b1] with
+        A: I x J, B: J x K, all three read / written through element strides (outer batch, inner batch, row, column) over
+        columns of field-lifted signed integers."""
+        sa, sb, sc = ((C.c_int64 * 4)(*[int(x) for x in st]) for st in (a_str, b_str, c_str))
+        self._ck(self._L.zkh_ig_matmul(self._h, _ptr(A), sa, _ptr(B), sb, _ptr(Cc), sc, nb0, nb1, I, J, K))
+
     def scale(self, col_dev, s):
         import torch
         out = torch.empty_like(col_dev)
