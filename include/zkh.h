@@ -8,6 +8,12 @@
  * Pointers named *_dev are device addresses on the context's GPU, everything
  * else is host memory.  Field elements are canonical uint64 values in [0, p),
  * p = 2^64 - 2^32 + 1, exactly as the reference stores them.
+ * Device columns of two or more elements must start on a 16-byte boundary
+ * (the kernels read adjacent pairs with 128-bit loads): the sumcheck, fold,
+ * evaluation and batched-opening entry points return ZKH_ERR_ARG for a column
+ * that does not, before anything is launched.  Whole allocations and slices at
+ * even element offsets qualify.  Function attributes and kernel set-up are kept
+ * per device, so one process may hold contexts on several GPUs.
  *
  * Each entry point names the reference interface it stands in for
  * (file:line relative to the reference project root).  Results are

@@ -59,3 +59,17 @@ def test_missing_library_fails_loudly(zk, monkeypatch, tmp_path):
         assert "no CPU fallback" in str(e)
     else:
         raise AssertionError("a missing library must raise")
+
+
+def test_misaligned_columns_are_refused_before_any_launch():
+    """Columns are read with 128-bit loads: a device address that is not 16-byte aligned is refused with ZKH_ERR_ARG
+    (argument check only: the pointers are never dereferenced, no kernel is launched, no GPU is needed)."""
+    import ctypes as C
+    import zkh_import
+    zk = zkh_import.load()
+    L = zk.load_library()
+    err = C.create_string_buffer(256)
+    z = (C.c_uint64 * 2)(1, 2)
+    y = C.c_uint64(0)
+    rc = L.zkh_gl_mle_eval_static(C.c_void_p(0), C.c_void_p(0x10008), z, 2, C.c_void_p(0x20000), err, len(err))
+    assert rc == -1 and b"16-byte" in err.value

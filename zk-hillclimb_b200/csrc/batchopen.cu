@@ -9,11 +9,17 @@
 //   at the sorted-unique query positions with a pruned node stream).
 //
 // The reference runs the reduction with one message kernel + three device-to-host copies +
-// a bind launch per round, and builds every helper array with host round trips.  Here the T
-// stacked point arrays are treated as ONE sumcheck column of length T*2^v (adjacent pairs never
-// straddle two points), so the reduction is the fused degree-2 engine with the transcript on the
-// device; the host synchronises three times per class (after the reduction, after "final", after
-// the query gather).
+// a bind launch per round, and builds every helper array (the T point arrays G_t, the T eq tables) with host
+// round trips.  Here the T stacked point arrays are treated as ONE sumcheck column of length T*2^v (adjacent
+// pairs never straddle two points) and neither G nor the eq tables are materialised at full size:
+//   * round 0 reads the claims' columns directly and forms G_t(b) = sum_e mu^e col_e[b] in registers;
+//     round 1 reads them once more, binds with the first challenge and stores the halved G (T * 2^(v-1));
+//     later rounds run on that array, halving it each time;
+//   * eq(z_t, b) is the product of two entries of small per-point factor tables (low and high variables),
+//     which are bound with each round's challenge by a tiny kernel instead of being expanded to 2^v entries.
+// Workspace of the reduction: 0.75 * T * 2^v elements (3.5 * T * 2^v before).  One kernel per round with the
+// transcript on the device; the host synchronises three times per class (after the reduction, after "final",
+// after the query gather).
 #include <algorithm>
 #include <vector>
 #include "merkle.cuh"
@@ -49,15 +55,95 @@ __global__ void bo_eq_small_kernel(const gl_t* zs, uint32_t T, uint32_t v, uint3
     for (uint32_t i = 0; i < nv; i++) p = gl_mul(p, ((b >> i) & 1) ? z[i] : gl_sub(1, z[i]));
     out[j] = p;
 }
+// out[x] = in[2x] + a * (in[2x+1] - in[2x]): one more variable of the eq factor tables bound (tables of 2^k entries per
+// point, k >= 1, stacked: pairs never straddle two points)
+__global__ void bo_tab_bind_kernel(const gl_t* in, gl_t* out, uint32_t count, const gl_t* chal) {
+    const uint32_t x = blockIdx.x * blockDim.x + threadIdx.x;
+    if (x < count) out[x] = gl_lerp(in[2 * x], in[2 * x + 1], *chal);
+}
+
+// One round of the reduction sumcheck  sum_t sum_b G_t(b) eq_t(b)  over the stacked arrays.
+//   logL: log2 of the per-point length L of the arrays whose adjacent pairs form this round's message.
+//   FIRST: those arrays are the round's input (round 0).  Otherwise the input has per-point length 2L and is bound with
+//          *chal_prev first; the bound array (T * L) is stored to Gout.
+//   FROM_COLS: the input G is not stored: G_t[b] = sum_{e in [estart[t], estart[t+1])} ew[e] * ecol[e][b]  (rounds 0 and 1).
+//   eq_t(b) at this round's level = lo[(t << lw) | (b & (2^lw - 1))] * hi[(t << hw) | (b >> lw)].
+struct BoRed {
+    const gl_t* const* ecol;
+    const gl_t* ew;
+    const uint32_t* estart;
+    const gl_t* G;
+    gl_t* Gout;
+    const gl_t* lo;
+    const gl_t* hi;
+    uint32_t lw, hw, T, logL;
+};
+template <bool FROM_COLS, bool FIRST>
 __global__ void __launch_bounds__(256)
-bo_eq_expand_kernel(const gl_t* __restrict__ lo, const gl_t* __restrict__ hi, uint32_t vl, uint32_t vh, gl_t* Es,
-                    uint32_t T, size_t N) {
-    const size_t tot = (size_t)T * N, stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < tot; j += stride) {
-        uint32_t t = (uint32_t)(j / N);
-        size_t b = j - (size_t)t * N;
-        Es[j] = gl_mul(lo[((size_t)t << vl) + (b & (((size_t)1 << vl) - 1))], hi[((size_t)t << vh) + (b >> vl)]);
+bo_reduce_kernel(BoRed P, ZkhCtl* ctl, gl_t* partials, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, ZkhTag tag) {
+    __shared__ gl_t sh[3 * 32];
+    Acc192 acc[3];
+#pragma unroll
+    for (int t = 0; t < 3; t++) acc[t].clear();
+    const uint32_t lp = P.logL - 1;                       // pairs per point = 2^lp
+    const size_t items = (size_t)P.T << lp, stride = (size_t)gridDim.x * blockDim.x;
+    const gl_t a = FIRST ? 0 : *chal_prev;
+    const uint32_t lmask = (1u << P.lw) - 1;
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < items; j += stride) {
+        const uint32_t t = (uint32_t)(j >> lp);
+        const size_t i = j & (((size_t)1 << lp) - 1);
+        gl_t g0, g1;
+        if (FIRST) {
+            if (FROM_COLS) {
+                Acc192 s0, s1;
+                s0.clear(); s1.clear();
+                for (uint32_t e = P.estart[t]; e < P.estart[t + 1]; e++) {
+                    const gl_t w = P.ew[e];
+                    const ulonglong2 v = ld2(P.ecol[e] + 2 * i);
+                    s0.add_prod(w, v.x); s1.add_prod(w, v.y);
+                }
+                g0 = s0.reduce(); g1 = s1.reduce();
+            } else {
+                const ulonglong2 v = ld2(P.G + ((size_t)t << P.logL) + 2 * i);
+                g0 = v.x; g1 = v.y;
+            }
+        } else {
+            gl_t q[4];
+            if (FROM_COLS) {
+                Acc192 s4[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) s4[u].clear();
+                for (uint32_t e = P.estart[t]; e < P.estart[t + 1]; e++) {
+                    const gl_t w = P.ew[e];
+                    const ulonglong2 v0 = ld2(P.ecol[e] + 4 * i), v1 = ld2(P.ecol[e] + 4 * i + 2);
+                    s4[0].add_prod(w, v0.x); s4[1].add_prod(w, v0.y); s4[2].add_prod(w, v1.x); s4[3].add_prod(w, v1.y);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) q[u] = s4[u].reduce();
+            } else {
+                const gl_t* src = P.G + ((size_t)t << (P.logL + 1)) + 4 * i;
+                const ulonglong2 v0 = ld2(src), v1 = ld2(src + 2);
+                q[0] = v0.x; q[1] = v0.y; q[2] = v1.x; q[3] = v1.y;
+            }
+            g0 = gl_lerp(q[0], q[1], a);
+            g1 = gl_lerp(q[2], q[3], a);
+            st2(P.Gout + ((size_t)t << P.logL) + 2 * i, g0, g1);
+        }
+        const size_t b0 = 2 * i, b1 = 2 * i + 1;
+        const gl_t* lo = P.lo + ((size_t)t << P.lw);
+        const gl_t* hi = P.hi + ((size_t)t << P.hw);
+        const gl_t e0 = gl_mul(lo[b0 & lmask], hi[b0 >> P.lw]);
+        const gl_t e1 = gl_mul(lo[b1 & lmask], hi[b1 >> P.lw]);
+        acc[0].add_prod(g0, e0);
+        acc[1].add_prod(g1, e1);
+        acc[2].add_prod(gl_sub(g1, g0), gl_sub(e1, e0));
     }
+    gl_t sm[3];
+#pragma unroll
+    for (int t = 0; t < 3; t++) sm[t] = acc[t].reduce();
+    // evaluations at 0, 1, 2 from g(0), g(1) and the leading coefficient: g(2) = 2 g(1) - g(0) + 2 c2
+    sm[2] = gl_add(gl_sub(gl_dbl(sm[1]), sm[0]), gl_dbl(sm[2]));
+    grid_finish<3>(sm, sh, ctl, partials, msg_out, chal_out, tag, 0);
 }
 // ystar[c] = sum_i col_c[i] * w[i]: one CTA per (column, slice), then a per-column sum
 __global__ void __launch_bounds__(256)
@@ -151,7 +237,8 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
     if (v > 64) return zkh_fail(c, ZKH_ERR_LIMIT, "batchopen: too many rounds");
     if (T < 1 || k < 1 || Q < 1 || Q > 4096) return zkh_fail(c, ZKH_ERR_ARG, "batchopen: empty ledger or bad Q");
     for (uint32_t j = 0; j < k; j++)
-        if (zid[j] >= T || !cols_dev[j]) return zkh_fail(c, ZKH_ERR_ARG, "batchopen: entry with bad point index or column");
+        if (zid[j] >= T || !cols_dev[j] || ((uintptr_t)cols_dev[j] & 15))
+            return zkh_fail(c, ZKH_ERR_ARG, "batchopen: entry with bad point index, or a column that is null or not 16-byte aligned");
     ZKH_CUDA(c, cudaSetDevice(c->device));
     const size_t N = (size_t)1 << v;
     const uint32_t logM0 = v + R;
@@ -168,7 +255,7 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
     }
     const uint32_t nc = (uint32_t)first.size();
     if (cap < bo_bound(v, R, Q, nc) + (sseeds ? (size_t)nc * 2 * Q * 32 : 0)) return zkh_fail(c, ZKH_ERR_ARG, "batchopen: output buffer smaller than zkh_batchopen_proof_bound");
-    if ((size_t)T * N > ((size_t)1 << 33)) return zkh_fail(c, ZKH_ERR_LIMIT, "batchopen: T*2^v beyond 2^33");
+    if ((size_t)T * N > ((size_t)1 << 36)) return zkh_fail(c, ZKH_ERR_LIMIT, "batchopen: T*2^v beyond 2^36");
 
     // ---- main transcript: mu and its powers (host; nothing on the device precedes it) ----
     gl_t mu = zkh_tr_chal(state);
@@ -195,10 +282,10 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
     const size_t q0_per_col = (size_t)2 * Q * 8 + (size_t)2 * Q * logM0 * 32;
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += zkh_align(bytes); return o; };
-    const size_t o_G = take((size_t)T * N * 8), o_E = take((size_t)T * N * 8);
-    const size_t o_pa = take(((size_t)T * N + 2) * 8), o_pb = take(((size_t)T * N / 2 + 2) * 8);
+    const size_t o_pa = take(((size_t)T * N / 2 + 2) * 8), o_pb = take(((size_t)T * N / 4 + 2) * 8);
     const size_t o_ecol = take((size_t)(k + nc) * 8), o_ew = take((size_t)(k + nc) * 8), o_es = take((size_t)(T + 3) * 4);
     const size_t o_zs = take((size_t)T * v * 8), o_tlo = take(((size_t)T << vl) * 8), o_thi = take(((size_t)T << vh) * 8);
+    const size_t o_tlo2 = take(((size_t)T << vl) * 8), o_thi2 = take(((size_t)T << vh) * 8);
     const size_t o_eqr = take(N * 8), o_U = take(N * 8), o_ys = take((size_t)nc * 8), o_dp = take((size_t)nc * nb * 8);
     const size_t o_cw0 = take(M0 * 8), o_cwr = take(M0 * 8), o_trees = take((size_t)2 * M0 * 32);
     const size_t o_oa = take((N + 2) * 8), o_ob = take((N / 2 + 2) * 8);
@@ -208,11 +295,12 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
     const size_t o_misc = take(std::max(eq_scratch_bytes(v), ntt_scratch_bytes(logM0)));
     ZKH_TRY(zkh_ws_reserve(c, off));
     char* ws = (char*)c->ws;
-    gl_t *Gs = (gl_t*)(ws + o_G), *Es = (gl_t*)(ws + o_E), *pa = (gl_t*)(ws + o_pa), *pb = (gl_t*)(ws + o_pb);
+    gl_t *pa = (gl_t*)(ws + o_pa), *pb = (gl_t*)(ws + o_pb);
     const gl_t** d_ecol = (const gl_t**)(ws + o_ecol);
     gl_t* d_ew = (gl_t*)(ws + o_ew);
     uint32_t* d_es = (uint32_t*)(ws + o_es);
     gl_t *d_zs = (gl_t*)(ws + o_zs), *tlo_e = (gl_t*)(ws + o_tlo), *thi_e = (gl_t*)(ws + o_thi);
+    gl_t *tlo_2 = (gl_t*)(ws + o_tlo2), *thi_2 = (gl_t*)(ws + o_thi2);
     gl_t *eqr = (gl_t*)(ws + o_eqr), *U = (gl_t*)(ws + o_U), *d_ys = (gl_t*)(ws + o_ys), *d_dp = (gl_t*)(ws + o_dp);
     gl_t *cw0 = (gl_t*)(ws + o_cw0), *cwr = (gl_t*)(ws + o_cwr);
     uint8_t* trees = (uint8_t*)(ws + o_trees);
@@ -241,10 +329,8 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
         size_t b = (items + 255) / 256, capb = (size_t)c->sm_count * 8;
         return (unsigned)(b < capb ? (b ? b : 1) : capb);
     };
-    bo_gbuild_kernel<<<grid_of((size_t)T * N), 256, 0, s>>>(d_ecol, d_ew, d_es, Gs, T, N);
     bo_eq_small_kernel<<<((T << vl) + 255) / 256, 256, 0, s>>>(d_zs, T, v, 0, vl, tlo_e);
     bo_eq_small_kernel<<<((T << vh) + 255) / 256, 256, 0, s>>>(d_zs, T, v, vl, vh, thi_e);
-    bo_eq_expand_kernel<<<grid_of((size_t)T * N), 256, 0, s>>>(tlo_e, thi_e, vl, vh, Es, T, N);
     ZKH_CUDA(c, cudaGetLastError());
 
     // ---- reduction sumcheck on the stacked arrays ----
@@ -252,21 +338,50 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
     gl_t* msgs = c->d_ctl->msgs;
     gl_t* chals = c->d_ctl->chals;
     {
-        const gl_t* cur[2] = {Gs, Es};
+        BoRed P;
+        memset(&P, 0, sizeof P);
+        P.ecol = d_ecol; P.ew = d_ew; P.estart = d_es; P.T = T;
+        const gl_t *lo_cur = tlo_e, *hi_cur = thi_e;
+        gl_t *lo_nxt = tlo_2, *hi_nxt = thi_2;
+        uint32_t lw = vl, hw = vh;
+        const gl_t* g_cur = nullptr;
         gl_t* dst = pa;
+        auto red_grid = [&](size_t items) {
+            size_t b = (items + 255) / 256, capb = (size_t)c->sm_count * 4;
+            if (capb > c->partials_cap / 5) capb = c->partials_cap / 5;
+            return (unsigned)(b < capb ? (b ? b : 1) : capb);
+        };
         for (uint32_t rd = 0; rd < v; rd++) {
-            const size_t L = N >> rd;  // per-point length entering the message of this round
+            if (rd > 0) {   // the eq factor tables take the previous challenge: low variables first, then the high ones
+                if (lw > 0) {
+                    const uint32_t cnt = T << (lw - 1);
+                    bo_tab_bind_kernel<<<(cnt + 255) / 256, 256, 0, s>>>(lo_cur, lo_nxt, cnt, chals + (rd - 1));
+                    const gl_t* tswap = lo_cur; lo_cur = lo_nxt; lo_nxt = (gl_t*)tswap;
+                    lw--;
+                } else {
+                    const uint32_t cnt = T << (hw - 1);
+                    bo_tab_bind_kernel<<<(cnt + 255) / 256, 256, 0, s>>>(hi_cur, hi_nxt, cnt, chals + (rd - 1));
+                    const gl_t* tswap = hi_cur; hi_cur = hi_nxt; hi_nxt = (gl_t*)tswap;
+                    hw--;
+                }
+            }
+            P.lo = lo_cur; P.hi = hi_cur; P.lw = lw; P.hw = hw;
+            P.logL = v - rd;
+            const size_t items = (size_t)T << (v - rd - 1);
             if (rd == 0) {
-                ZKH_TRY(sc_enqueue_round(c, ZKH_F_PROD2, 3, true, cur, nullptr, (size_t)T * L, nullptr, msgs, chals, tag_rm));
+                bo_reduce_kernel<true, true><<<red_grid(items), 256, 0, s>>>(P, c->d_ctl, c->d_partials, nullptr, msgs, chals, tag_rm);
             } else {
-                gl_t* outp[2] = {dst, dst + (size_t)T * L};
-                ZKH_TRY(sc_enqueue_round(c, ZKH_F_PROD2, 3, false, cur, outp, (size_t)T * L * 2, chals + (rd - 1),
-                                         msgs + (size_t)rd * 3, chals + rd, tag_rm));
-                cur[0] = outp[0];
-                cur[1] = outp[1];
+                P.G = g_cur; P.Gout = dst;
+                if (rd == 1)
+                    bo_reduce_kernel<true, false><<<red_grid(items), 256, 0, s>>>(P, c->d_ctl, c->d_partials, chals, msgs + 3, chals + 1, tag_rm);
+                else
+                    bo_reduce_kernel<false, false><<<red_grid(items), 256, 0, s>>>(P, c->d_ctl, c->d_partials, chals + (rd - 1),
+                                                                                  msgs + (size_t)rd * 3, chals + rd, tag_rm);
+                g_cur = dst;
                 dst = (dst == pa) ? pb : pa;
             }
         }
+        ZKH_CUDA(c, cudaGetLastError());
     }
     // ---- y*_c = col_c(r*) ----
     ZKH_TRY(eq_enqueue(c, chals, v, eqr, ws + o_misc, /*z_on_device=*/true));

@@ -308,6 +308,7 @@ extern "C" int zkh_gl_mle_eval(zkh_ctx* c, const uint64_t* c_dev, const uint64_t
     ZKH_CUDA(c, cudaSetDevice(c->device));
     if (v == 0) return zkh_download(c, y, c_dev, 8);
     if (v > 40) return zkh_fail(c, ZKH_ERR_LIMIT, "mle_eval: more than 40 variables");
+    if ((uintptr_t)c_dev & 15) return zkh_fail(c, ZKH_ERR_ARG, "mle_eval: the column must be 16-byte aligned (it is read with 128-bit loads)");
     gl_t *lo, *hi;
     uint32_t vl;
     ZKH_TRY(zkh_ws_reserve(c, eq_scratch_bytes(v)));
@@ -343,6 +344,8 @@ extern "C" int zkh_gl_bind(zkh_ctx* c, const uint64_t* in_dev, uint64_t* out_dev
     if (!c || !in_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "bind: null pointer");
     if (n < 2 || (n & (n - 1))) return zkh_fail(c, ZKH_ERR_ARG, "bind: n must be a power of two >= 2");
     if (a >= GL_P) return zkh_fail(c, ZKH_ERR_ARG, "bind: challenge not canonical");
+    if (n >= 4 && (((uintptr_t)in_dev | (uintptr_t)out_dev) & 15))
+        return zkh_fail(c, ZKH_ERR_ARG, "bind: columns must be 16-byte aligned (128-bit loads and stores)");
     ZKH_CUDA(c, cudaSetDevice(c->device));
     if (n < 4) {
         bind_small_kernel<<<1, 32, 0, c->stream>>>(in_dev, out_dev, n / 2, a);

@@ -104,6 +104,8 @@ extern "C" int zkh_gl_mle_eval_static(void* stream, const uint64_t* c_dev, const
                     "use zkh_gl_mle_eval for larger inputs");
     for (uint32_t i = 0; i < v; i++)
         if (z[i] >= GL_P) return fail(errbuf, errbuf_len, ZKH_ERR_ARG, "mle_eval_static: point not canonical");
+    if (v && ((uintptr_t)c_dev & 15))
+        return fail(errbuf, errbuf_len, ZKH_ERR_ARG, "mle_eval_static: the column must be 16-byte aligned (128-bit loads)");
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(errbuf, errbuf_len, ZKH_ERR_CUDA, "cudaGetDevice: ", cudaGetErrorString(e));

@@ -617,6 +617,9 @@ extern "C" int zkh_sumcheck(zkh_ctx* ctx, int functor, int nt, const uint64_t* c
                             uint32_t logn, const uint64_t* par, int npar, const char* tag,
                             uint8_t state[32], uint64_t* msgs, uint64_t* chals, uint64_t* finals) {
     ZKH_TRY(sumcheck_check(ctx, functor, nt, cols_dev, nc, logn, par, npar, tag, state, msgs, chals));
+    for (int k = 0; k < nc; k++)
+        if (!cols_dev[k] || ((uintptr_t)cols_dev[k] & 15))
+            return zkh_fail(ctx, ZKH_ERR_ARG, "sumcheck: columns must be non-null and 16-byte aligned (128-bit loads)");
     ZKH_CUDA(ctx, cudaSetDevice(ctx->device));
     ZKH_TRY(zkh_ws_reserve(ctx, sc_workspace_bytes(nc, logn)));
     return sumcheck_common(ctx, functor, nt, cols_dev, nc, logn, par, npar, tag, state, msgs, chals,
@@ -652,6 +655,9 @@ extern "C" int zkh_shard_begin(zkh_ctx* c, int functor, int nt, const uint64_t* 
                                const uint8_t state[32]) {
     static const uint64_t dummy = 0;
     ZKH_TRY(sumcheck_check(c, functor, nt, cols_dev, nc, logn_local, par, npar, tag, state, &dummy, &dummy));
+    for (int k = 0; k < nc; k++)
+        if (!cols_dev[k] || ((uintptr_t)cols_dev[k] & 15))
+            return zkh_fail(c, ZKH_ERR_ARG, "shard_begin: columns must be non-null and 16-byte aligned (128-bit loads)");
     ZKH_CUDA(c, cudaSetDevice(c->device));
     const size_t n = (size_t)1 << logn_local;
     const size_t a = zkh_align((size_t)nc * (n / 2 + 1) * 8), b = zkh_align((size_t)nc * (n / 4 + 1) * 8);
