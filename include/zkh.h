@@ -93,6 +93,11 @@ ZKH_API void zkh_tr_absorb(uint8_t state[32], const char* label, const void* dat
 ZKH_API void zkh_tr_challenge_bytes(uint8_t state[32], uint8_t out[32]);
 ZKH_API uint64_t zkh_tr_chal(uint8_t state[32]);
 ZKH_API uint64_t zkh_tr_idx(uint8_t state[32], uint64_t mod);
+/* Merkle hashes of the commitment trees, on the host (p3fri::leaf_hash / node_hash, zkllm-src/p3_fri.cuh:33-39): a leaf is
+ * SHA-256 of the 8-byte little-endian value; a node is ONE compression of left | right from the standard initial state,
+ * without a padding block (p3_sha256_compress64, zkllm-src/p3_merkle.cuh:69-109).  What a verifier needs to check paths. */
+ZKH_API void zkh_merkle_leaf_hash(uint64_t value, uint8_t out[32]);
+ZKH_API void zkh_merkle_node_hash(const uint8_t left[32], const uint8_t right[32], uint8_t out[32]);
 
 /* ---- multilinear vector kernels ---- */
 /* out_dev[b] = eq(b, z), b < 2^v.          zkllm-src/p3_basefold.cuh:247-252 (p3bf_eq_kernel) */

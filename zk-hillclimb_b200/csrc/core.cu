@@ -201,6 +201,19 @@ extern "C" uint64_t zkh_tr_idx(uint8_t state[32], uint64_t mod) {
     return a;
 }
 
+extern "C" void zkh_merkle_leaf_hash(uint64_t value, uint8_t out[32]) {
+    uint32_t h[8];
+    sha256_leaf(value, h);
+    digest_to_bytes(h, out);
+}
+extern "C" void zkh_merkle_node_hash(const uint8_t left[32], const uint8_t right[32], uint8_t out[32]) {
+    uint32_t l[8], r[8], h[8];
+    digest_from_bytes(left, l);
+    digest_from_bytes(right, r);
+    sha256_node(l, r, h);
+    digest_to_bytes(h, out);
+}
+
 // ---------------------------------------------------------------- eq table
 // eq(b,z) = prod_i (b_i ? z_i : 1-z_i) factors over a split of the variables:
 // eq(b) = lo[b & (2^vl-1)] * hi[b >> vl].  The two small tables cost O(sqrt N * v);
