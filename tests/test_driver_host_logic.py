@@ -198,3 +198,115 @@ def test_driven_by_the_reference_orchestrator_helpers(case, tmp_path):
         assert ok
     finally:
         pool.close()
+
+
+def _walk_run(orc, zk, tmp_path):
+    """A two-obligation chain (the second takes the first's rescaled output) laid out as a run directory, proofs from
+    the host logic over the oracle engine."""
+    import json
+    p3 = zk.p3
+    eng = OracleGadgetEngine(orc)
+    run = tmp_path / "run"
+    (run / "registration").mkdir(parents=True)
+    obs = [{"prefix": "layer0.mlp.up_proj", "B": 4, "IN": 8, "OUT": 16, "sf": 8, "weight": "registration/w0.i32",
+            "weight_root": "registration/w0.root", "input_from": None},
+           {"prefix": "layer0.mlp.down_proj", "B": 4, "IN": 16, "OUT": 8, "sf": 8, "weight": "registration/w1.i32",
+            "weight_root": "registration/w1.root", "input_from": "layer0.mlp.up_proj"}]
+    pub = {"R": R, "Q": Q, "input": "registration/input.i32", "input_root": "registration/input.root", "obligations": obs}
+    raw = json.dumps(pub, indent=1).encode()
+    (run / "public.json").write_bytes(raw)
+    import hashlib
+    run_seed = hashlib.sha256(raw).hexdigest()
+    g = np.random.default_rng(21)
+    x = g.integers(-127, 128, (4, 8))
+    com = lambda a: (lambda c: (c, eng.commit_gpu_rootonly(c, R)))(_Arr(lift(np.asarray(a).reshape(-1))))
+    prevYo = None
+    for k, o in enumerate(obs):
+        w = g.integers(-127, 128, (o["IN"], o["OUT"]))
+        li, lj, lk = (max(n - 1, 0).bit_length() for n in (o["B"], o["IN"], o["OUT"]))
+        X = prevYo if prevYo is not None else com(x)
+        if k == 0:
+            (run / "registration" / "input.root").write_bytes(X[1])
+        W, Y = com(w), com(x @ w)
+        (run / "registration" / ("w%d.root" % k)).write_bytes(W[1])
+        tr = zk.Transcript("%s:%s" % (run_seed, o["prefix"]))
+        ledger, luq = p3.Ledger(), []
+        p1 = p3.imm_prove(eng, tr, X, W, Y, lj, lk, li, R, Q, ledger)
+        yo, L, iL, iY = eng.irs_witness(Y[0], o["sf"], 1)
+        Yo = (yo, eng.commit_gpu_rootonly(yo, R))
+        p2 = p3.irs_prove(eng, tr, irs_tables(zk, o["sf"]), Y, Yo, (L, iL, iY), li + lk, o["sf"], 1, R, Q, ledger, luq)
+        lug = p3.lu_flush(eng, tr, luq, ledger, R)
+        bo = p3.tail_prove(eng, tr, ledger, R, Q, "fc-bo")
+        proof = blob(p1) + blob(p2) + len(lug).to_bytes(4, "little") + b"".join(blob(b) for b in lug) \
+            + len(bo).to_bytes(4, "little") + b"".join(blob(b) for b in bo)
+        ob = run / "proofs" / o["prefix"]
+        ob.mkdir(parents=True)
+        (ob / "roots.bin").write_bytes(X[1] + Y[1] + Yo[1])
+        (ob / "proof.bin").write_bytes(proof)
+        sy = yo.a.astype(np.int64)
+        sy = np.where(yo.a > np.uint64(0x7FFFFFFF80000000), (yo.a - np.uint64(0xFFFFFFFF00000001)).astype(np.int64), sy)
+        x = sy.reshape(x.shape[0], -1)
+        prevYo = Yo
+    return run, obs
+
+
+def test_verify_walk_transcript_and_harness_coverage(orc, zk, tmp_path):
+    """The walk over a chained two-obligation run: ACCEPT with a transcript that the reference's check_transcript.py finds
+    complete against the manifest ids of its linear_obligations(); a swapped proof, a broken chain edge and a wrong
+    registered root each turn the verdict to REJECT (exit code 1 from verify.sh)."""
+    import json
+    import zkh_import
+    zkh_import.load()
+    from zk_hillclimb_b200 import p3walk
+    run, obs = _walk_run(orc, zk, tmp_path)
+    quiet = lambda *a, **k: None
+    out = tmp_path / "transcript.json"
+    tr = p3walk.verify_walk(str(run), None, str(out), log=quiet)
+    assert tr["verdict"] == "ACCEPT" and tr["checked"] == p3walk.manifest_ids(json.loads((run / "public.json").read_text()))
+    assert tr["edges"] == ["registered input -> layer0.mlp.up_proj", "layer0.mlp.up_proj -> layer0.mlp.down_proj"]
+    # the shell entry point of the harness contract
+    sh = os.path.join(ROOT, "zk-hillclimb_b200", "host", "verify.sh")
+    r = subprocess.run(["bash", sh, str(run), str(run / "public.json"), str(out)], capture_output=True, text=True)
+    assert r.returncode == 0 and json.loads(out.read_text())["verdict"] == "ACCEPT", r.stdout + r.stderr
+    # coverage against a manifest, with the reference's checker where its tree is present
+    manifest = {"obligations": [{"id": i, "waived": None} for i in tr["checked"]] + [{"id": "embedding.lookup", "waived": "not a linear layer"}]}
+    (tmp_path / "manifest.json").write_text(json.dumps(manifest))
+    root = os.environ.get("ZKH_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+    chk = os.path.join(root, "harness", "check_transcript.py")
+    if os.path.exists(chk):
+        r = subprocess.run([sys.executable, chk, str(tmp_path / "manifest.json"), str(out)], capture_output=True, text=True)
+        assert r.returncode == 0 and "missing: 0  unknown: 0" in r.stdout, r.stdout
+        # with the reference's own DriverPool as the transport
+        C = _reference_common()
+        C.GPU_LOCK = str(tmp_path / "gpu.lock")
+        pool = C.DriverPool(str(run), log=quiet)
+        try:
+            assert p3walk.verify_walk(str(run), None, None, run=pool.run, log=quiet)["verdict"] == "ACCEPT"
+        finally:
+            pool.close()
+    # forgeries
+    a, b = (run / "proofs" / o["prefix"] / "proof.bin" for o in obs)
+    pa, pb = a.read_bytes(), b.read_bytes()
+    a.write_bytes(pb)
+    tr = p3walk.verify_walk(str(run), None, str(out), log=quiet)
+    assert tr["verdict"] == "REJECT" and "layer0.mlp.up_proj.matmul" not in tr["checked"] and "layer0.mlp.down_proj.matmul" in tr["checked"]
+    r = subprocess.run(["bash", sh, str(run), str(run / "public.json"), str(out)], capture_output=True, text=True)
+    assert r.returncode == 1
+    a.write_bytes(pa)
+    rb = run / "proofs" / obs[1]["prefix"] / "roots.bin"
+    good = rb.read_bytes()
+    rb.write_bytes(bytes([good[0] ^ 1]) + good[1:])
+    tr = p3walk.verify_walk(str(run), None, None, log=quiet)
+    assert tr["verdict"] == "REJECT" and any("edge" in f for f in tr["failed"])
+    rb.write_bytes(good)
+    wr = run / "registration" / "w1.root"
+    goodw = wr.read_bytes()
+    wr.write_bytes(goodw[::-1])
+    assert p3walk.verify_walk(str(run), None, None, log=quiet)["verdict"] == "REJECT"
+    wr.write_bytes(goodw)
+    assert p3walk.verify_walk(str(run), None, None, log=quiet)["verdict"] == "ACCEPT"
+    # a statement that changes (another Q) changes the run seed: every proof is rejected
+    pub = json.loads((run / "public.json").read_text())
+    pub["Q"] = Q + 1
+    (run / "public.json").write_text(json.dumps(pub, indent=1))
+    assert p3walk.verify_walk(str(run), None, None, log=quiet)["verdict"] == "REJECT"

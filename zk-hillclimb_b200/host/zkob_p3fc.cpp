@@ -8,7 +8,7 @@
 //   stdin line through the same entry as the one-shot command line and answers "ZKW-RC <rc>" (zkllm-src/zkob_serve.cuh:26-52);
 //   the obligation directory is created by the caller, never here; the transcript seed is "<run_seed>:<obligation id>".
 //
-//   zkob_p3fc commit   <W.i32> <IN> <OUT> <R> <root_out.bin>
+//   zkob_p3fc commit   <M.i32> <rows> <cols> <R> <root_out.bin>        (a weight IN x OUT, or the input activations B x IN)
 //   zkob_p3fc prove    <obdir> <seed> <X.i32> <W.i32> <B> <IN> <OUT> <sf> <R> <Q> [Yr-out.i32] [--claims <accdir> <obid>]
 //   zkob_p3fc verify   <obdir> <seed> <B> <IN> <OUT> <sf> <R> <Q> <root_W.bin> [--claims <vaccdir> <obid>]
 //   zkob_p3fc selftest
@@ -96,13 +96,13 @@ static Prover& gpu() {
 }
 
 static int do_commit(int argc, char** argv) {
-    if (argc != 7) throw std::runtime_error("usage: commit <W.i32> <IN> <OUT> <R> <root_out.bin>");
+    if (argc != 7) throw std::runtime_error("usage: commit <M.i32> <rows> <cols> <R> <root_out.bin>");
     const uint32_t IN = (uint32_t)atoi(argv[3]), OUT = (uint32_t)atoi(argv[4]), R = (uint32_t)atoi(argv[5]);
     Prover& P = gpu();
     DevCol dW(P, load_matrix(argv[2], IN, OUT, clog2(IN), clog2(OUT)));
     Hash r = P.commit_gpu_rootonly(dW, R);
     write_file(argv[6], r.data(), 32);
-    printf("committed W %ux%u (R=%u) -> %s\n", IN, OUT, R, argv[6]);
+    printf("committed %ux%u (R=%u) -> %s\n", IN, OUT, R, argv[6]);
     return 0;
 }
 
