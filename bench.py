@@ -594,6 +594,13 @@ def run_profile_case(args):
     elif name == "hist":
         idx = torch.from_numpy(np.clip(np.rint(rng.normal(32768, 1024, 1 << 25)), 0, 65535).astype(np.int32)).cuda()
         fn = lambda: prover.histogram(idx, 1 << 16)
+    elif name == "igmm":
+        # the witness chain's exact integer product at the TinyLlama attention-projection shape: 512 x 2048 . 2048 x 2048
+        lift = lambda a: np.where(a < 0, a.astype(np.int64).view(np.uint64) - np.uint64(0xFFFFFFFF), a.astype(np.int64).view(np.uint64))
+        A = zk.p3.to_device(lift(rng.integers(-(1 << 18), 1 << 18, 512 * 2048)))
+        B = zk.p3.to_device(lift(rng.integers(-(1 << 10), 1 << 10, 2048 * 2048)))
+        Cc = torch.empty(512 * 2048, dtype=torch.int64, device="cuda")
+        fn = lambda: prover.ig_matmul(A, (0, 0, 2048, 1), B, (0, 0, 2048, 1), Cc, (0, 0, 2048, 1), 1, 1, 512, 2048, 2048)
     elif name == "inv":
         a = gl_rand(1 << 24)
         fn = lambda: prover.inv_all_add(a, 12345)
@@ -1116,60 +1123,97 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
     except Exception as e:
         err = repr(e)
 
-    def one_layer(layer, hiding, acc):
+    nthr = max(1, args.layer_streams)
+    out["concurrent_proofs_per_gpu"] = nthr
+    out["concurrency_note"] = ("each GPU runs %d layer proofs at a time, each on its own stream and library context, so the "
+                               "latency-bound rounds of one proof overlap the hashing and encoding of another" % nthr)
+    streams = [torch.cuda.Stream(device=dvc) for _ in range(nthr)] if nthr > 1 else [torch.cuda.current_stream()]
+    provers = [zk.Prover(local, st.cuda_stream) for st in streams] if nthr > 1 else [prover]
+    keep_zk = (80 << 30) if nthr == 1 else (100 << 30) // nthr
+
+    def one_layer(pr, stream, layer, hiding, acc):
         t = [time.perf_counter()]
-        lw = ig_dev.itf_build_witness(cfg, px0, pW, tabs, dvc, prover)   # uploads the inputs, then all device code
-        torch.cuda.synchronize()
+        lw = ig_dev.itf_build_witness(cfg, px0, pW, tabs, dvc, pr)   # uploads the inputs, then all device code
+        stream.synchronize()
         t.append(time.perf_counter())
         if hiding:
-            zc = zkm.ZkCtx(seed=zseed + layer, Q=Q, keep_bytes=80 << 30)
-            lo = zkm.itf_commit_all(prover, zc, cfg, lw, lw["dev_W"], R, ident)
+            zc = zkm.ZkCtx(seed=zseed + layer, Q=Q, keep_bytes=keep_zk)
+            lo = zkm.itf_commit_all(pr, zc, cfg, lw, lw["dev_W"], R, ident)
         else:
-            lo = ig.itf_commit_all(prover, lw, lw["dev_W"], R, ident)
-        torch.cuda.synchronize()
+            lo = ig.itf_commit_all(pr, lw, lw["dev_W"], R, ident)
+        stream.synchronize()
         t.append(time.perf_counter())
         tr = zk.Transcript("itf-layer-%d" % layer)
         if hiding:
-            pf = zkm.itf_prove(prover, zc, tr, cfg, lw, lo, lW, tabs, R, Q, ident, {})
+            pf = zkm.itf_prove(pr, zc, tr, cfg, lw, lo, lW, tabs, R, Q, ident, {})
         else:
-            pf = ig.itf_prove(prover, tr, cfg, lw, lo, lW, tabs, R, Q, ident)
-        torch.cuda.synchronize()
+            pf = ig.itf_prove(pr, tr, cfg, lw, lo, lW, tabs, R, Q, ident)
+        stream.synchronize()
         t.append(time.perf_counter())
-        prover.release_kept()
+        pr.release_kept()
         del lo, lw
-        if hiding:
-            torch.cuda.empty_cache()
         for k, name in enumerate(("witness_s", "commit_s", "prove_s")):
             acc[name] = acc.get(name, 0.0) + t[k + 1] - t[k]
         acc["n"] = acc.get("n", 0) + 1
         return len(pf)
 
+    def run_layers(layers, hiding, accs):
+        """layers[i] goes to worker i mod nthr; returns (proof bytes of the last layer, first error or None)."""
+        res = {"n": 0, "err": None}
+
+        def worker(tid):
+            try:
+                with torch.cuda.stream(streams[tid]):
+                    for layer in layers[tid::nthr]:
+                        res["n"] = one_layer(provers[tid], streams[tid], layer, hiding, accs[tid])
+                    streams[tid].synchronize()
+            except Exception as e:           # noqa: BLE001 -- reported in the JSON line, the other ranks must not hang
+                res["err"] = repr(e)
+        if nthr == 1:
+            worker(0)
+        else:
+            ths = [threading.Thread(target=worker, args=(i,)) for i in range(nthr)]
+            for th in ths:
+                th.start()
+            for th in ths:
+                th.join()
+        return res["n"], res["err"]
+
     for mode in (("plain",) if args.no_zk_layer else ("plain", "zk")):
         hiding = mode == "zk"
-        res = {}
-        ms, nbytes, acc = 0.0, 0, {}
+        ms, nbytes = 0.0, 0
+        accs = [{} for _ in range(nthr)]
         if err is None:
-            try:
-                prover.keep_trees = not hiding          # plain mode: codewords and trees stay in HBM for the openings
-                nbytes = one_layer(rank, hiding, {})     # warm-up (table uploads, workspace growth)
-            except Exception as e:
-                err = "%s pass, warm-up: %r" % (mode, e)
+            for pr in provers:
+                pr.keep_trees = not hiding              # plain mode: codewords and trees stay in HBM for the openings
+            # warm-up: one layer per worker, one after the other (table uploads, workspace growth, kernel set-up)
+            for tid in range(nthr):
+                if err is None:
+                    try:
+                        with torch.cuda.stream(streams[tid]):
+                            nbytes = one_layer(provers[tid], streams[tid], rank, hiding, {})
+                    except Exception as e:      # noqa: BLE001
+                        err = "%s pass, warm-up: %r" % (mode, e)
+            if hiding:
+                torch.cuda.empty_cache()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         if err is None:
-            try:
-                for layer in range(rank, nlayers, world):
-                    nbytes = one_layer(layer, hiding, acc)
-            except Exception as e:
-                err = "%s pass: %r" % (mode, e)
+            nbytes, werr = run_layers(list(range(rank, nlayers, world)), hiding, accs)
+            if werr:
+                err = "%s pass: %s" % (mode, werr)
+        torch.cuda.synchronize()
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
-        prover.keep_trees = False
-        prover.release_kept()
+        for pr in provers:
+            pr.keep_trees = False
+            pr.release_kept()
+        if hiding:
+            torch.cuda.empty_cache()
         bad = 1.0 if err is not None else 0.0
         if world > 1:
             t = torch.tensor([ms, bad], device="cuda")
@@ -1178,9 +1222,11 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
         if bad:
             out[mode] = {"error": err or "another rank failed"}
             break
-        n = max(acc.get("n", 1), 1)
+        n = max(sum(a.get("n", 0) for a in accs), 1)
         out[mode] = {"total_s": ms / 1e3, "s_per_layer": ms / 1e3 / nlayers, "layers_per_s": nlayers / (ms / 1e3),
-                     "rank0_mean_per_layer": {k: acc.get(k, 0.0) / n for k in ("witness_s", "commit_s", "prove_s")},
+                     "rank0_mean_per_layer": {k: sum(a.get(k, 0.0) for a in accs) / n for k in ("witness_s", "commit_s", "prove_s")},
+                     "rank0_mean_note": "wall time of each phase inside its own worker; with concurrent proofs the phases of "
+                                        "different layers overlap, so their sum exceeds s_per_layer",
                      "proof_MB": nbytes / 1048576.0}
     if "plain" in out and "s_per_layer" in out["plain"]:
         out["s_per_layer"] = out["plain"]["s_per_layer"]
@@ -1271,6 +1317,7 @@ def main():
     ap.add_argument("--ref-budget-s", type=float, default=150.0, help="time budget of the CPU reference arm's calls")
     ap.add_argument("--parity-logn", type=int, default=18, help="N>1: per-rank size of the sharded proof checked against the CPU checker")
     ap.add_argument("--no-zk-layer", action="store_true", help="skip the hiding-mode pass of the 22-layer figure")
+    ap.add_argument("--layer-streams", type=int, default=2, help="layer proofs in flight per GPU (threads, one stream and context each)")
     ap.add_argument("--no-ref-layer", action="store_true", help="skip timing the reference's own layer prover at N=1")
     ap.add_argument("--cpu-logn", type=int, default=26, help="sample size of the cpu_baseline leg")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's CUDA prover")
