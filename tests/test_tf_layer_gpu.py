@@ -119,3 +119,33 @@ def test_layer_proof_same_bytes_as_cpu_engine_and_verifies(orc, ref, zk, prover,
         oh = tfg.tf_commit_all(eng, wh, R, host_col)
         trh = zk.Transcript("tf-layer")
         assert tfg.tf_prove(eng, trh, wh, oh, T, art, R, Q, host_col) == pf and trh.state == tr.state
+
+
+def test_two_layer_model_on_device_accepted_by_reference_verifier(orc, ref, zk, prover):
+    """p3mdl on the GPU engine: embedding gather, two chained layers, final RMSNorm, LM head, public logits; the proof is the
+    one the CPU stand-in engine gives for the same model and the reference's model verifier accepts it."""
+    from test_tf_layer_host_logic import ref_mdl_verify, small_model
+    R, Q = 1, 24
+    tfg = zk.tfg
+    c = tfg.TfConfig(2, 16, 2, 8, 16, 1)
+    nlayers, vocab = 2, 8
+    art = load_art(ref, zk, c.ld)
+    T = tfg.tf_tables(art)
+    MW, ids = small_model(zk, c, nlayers, vocab, 21)
+    w = tfg.mdl_build_witness(c, ids, MW, art, device="cuda:%d" % prover.device, engine=prover)
+    o = tfg.mdl_commit(prover, w, MW, R, ident)
+    roots = tfg.mdl_roots(prover, c, MW, R, ident)
+    tr = zk.Transcript("mdl")
+    pf = tfg.mdl_prove(prover, tr, w, o, T, art, R, Q, ident)
+    st0 = zk.Transcript("mdl").state
+    logits = np.asarray(w["logits"].cpu() if hasattr(w["logits"], "cpu") else w["logits"])
+    ok, st = ref_mdl_verify(ref, st0, c, nlayers, vocab, ids, roots, MW["layers"][0], logits, R, Q, pf)
+    assert ok and st == tr.state
+    bad = logits.copy()
+    bad[1] ^= 1
+    assert not ref_mdl_verify(ref, st0, c, nlayers, vocab, ids, roots, MW["layers"][0], bad, R, Q, pf)[0]
+    wh = tfg.mdl_build_witness(c, ids, MW, art)
+    eng = OracleHwlEngine(orc, ref)
+    oh = tfg.mdl_commit(eng, wh, MW, R, host_col)
+    trh = zk.Transcript("mdl")
+    assert tfg.mdl_prove(eng, trh, wh, oh, T, art, R, Q, host_col) == pf and trh.state == tr.state
