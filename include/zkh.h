@@ -383,6 +383,35 @@ ZKH_API int zkh_gl_matmul(zkh_ctx* ctx, const uint64_t* A_dev, const uint64_t* B
 ZKH_API int zkh_ig_matmul(zkh_ctx* ctx, const uint64_t* A_dev, const int64_t a_strides[4], const uint64_t* B_dev,
                           const int64_t b_strides[4], uint64_t* C_dev, const int64_t c_strides[4], uint32_t nb0,
                           uint32_t nb1, uint32_t I, uint32_t J, uint32_t K);
+/* Witness replays of the integer layer's gadgets on the device (the host loops of p3iadd / p3iswg / p3irope / p3irms /
+ * p3ismx ::gen_witness, zkllm-src/p3_int_gadgets.cuh:690-710, :1738-1788, :1228-1273, :830-916, :1416-1512, and the RS20 row
+ * index of p3itf::build_witness).  Columns are field-lifted signed integers; index arrays are uint32 lookup rows.  A value
+ * outside a gadget's window returns ZKH_ERR_DOMAIN (the reference throws).  Each call synchronises the stream.
+ *   add:      out = a + b, idx = out + 2^19
+ *   rs20:     idx = v + 2^19
+ *   swiglu:   sil = SILU[g + 2^19] (silu_col: the table's value column, 2^20 rows), m = sil * u, mo = round(m / 2^16),
+ *             rem = m + 2^15 - mo * 2^16; idxG = g + 2^19, idxRem = rem, idxMo = mo + 2^19
+ *   rope:     q over (2^lT positions x 2^ld lanes), heads of 2^ldh lanes, cos / sin: int32 tables [2^lseq][2^(ldh-1)] at scale
+ *             2^14; y = round((q C + q' S2) / 2^14), q' = the partner lane of the rotate-half, C / S2 the signed public columns
+ *   rms:      per row M = 2^14 + sum x^2 ... the 18 per-row columns db (order p3irms::B_*), W / remW / remY per element, y, and
+ *             the lookup rows: irow = e, m, m - 2^14, m, L40 L41 L42 D40 D41 D42 L20 D20 LR0, LR1; iel = remW, W + 2^19, remY, Y + 2^19
+ *   softmax:  rows of 2^lseq keys, 2^(la+lseq) rows, causal; xe = first, dm, E, r1 lo, r1 hi, r2 lo, r2 hi; xb = mx, S per row;
+ *             p; idxDM, idxL[4] per element, idxMX = mx + 2^15 per row (expt_col: the EXPT table's value column, 2^17 rows) */
+ZKH_API int zkh_ig_add_witness(zkh_ctx* ctx, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev,
+                               uint32_t* idx_dev);
+ZKH_API int zkh_ig_rs20_index(zkh_ctx* ctx, const uint64_t* v_dev, uint64_t n, uint32_t* idx_dev);
+ZKH_API int zkh_ig_swiglu_witness(zkh_ctx* ctx, const uint64_t* g_dev, const uint64_t* u_dev, const uint64_t* silu_col_dev, uint64_t n,
+                                  uint64_t* sil_dev, uint64_t* rem_dev, uint64_t* mo_dev, uint32_t* idxG_dev, uint32_t* idxRem_dev,
+                                  uint32_t* idxMo_dev);
+ZKH_API int zkh_ig_rope_witness(zkh_ctx* ctx, const uint64_t* q_dev, const int32_t* cos_dev, const int32_t* sin_dev, uint32_t lseq,
+                                uint32_t ldh, uint32_t lT, uint32_t ld, uint64_t* y_dev, uint64_t* rem_dev, uint32_t* idxRem_dev,
+                                uint32_t* idxY_dev, int64_t* c_dev, int64_t* s2_dev);
+ZKH_API int zkh_ig_rms_witness(zkh_ctx* ctx, const uint64_t* x_dev, const uint64_t* g_dev, const uint64_t* isq_col_dev, uint32_t lT,
+                               uint32_t ld, uint64_t* const db_dev[18], uint64_t* const de_dev[3], uint64_t* y_dev,
+                               uint32_t* const irow_dev[14], uint32_t* const iel_dev[4]);
+ZKH_API int zkh_ig_softmax_witness(zkh_ctx* ctx, const uint64_t* z_dev, const uint64_t* expt_col_dev, uint32_t la, uint32_t lseq,
+                                   uint64_t* const xe_dev[7], uint64_t* const xb_dev[2], uint64_t* p_dev, uint32_t* idxDM_dev,
+                                   uint32_t* const idxL_dev[4], uint32_t* idxMX_dev);
 /* out[i] = a[i]*b[i]: the helper column hT = cnt * 1/(Tc+beta) of the standalone lookup
  * (zkllm-src/p3_logup.cuh:984).  Stream-ordered. */
 ZKH_API int zkh_gl_mul(zkh_ctx* ctx, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev);

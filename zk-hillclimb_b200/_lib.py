@@ -74,6 +74,12 @@ def load_library():
         "zkh_fr_dot": (i, [vp, vp, vp, u64, vp]),
         "zkh_fr_lookup_sumcheck": (i, [vp, vp, vp, vp, vp, vp, u32, u32, vp, vp, vp, vp, vp, vp, vp, vp]),
         "zkh_fr_sumcheck": (i, [vp, vp, i, u32, vp, vp, vp, vp, vp]),
+        "zkh_ig_add_witness": (i, [vp, vp, vp, u64, vp, vp]),
+        "zkh_ig_rs20_index": (i, [vp, vp, u64, vp]),
+        "zkh_ig_swiglu_witness": (i, [vp, vp, vp, vp, u64, vp, vp, vp, vp, vp, vp]),
+        "zkh_ig_rope_witness": (i, [vp, vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]),
+        "zkh_ig_rms_witness": (i, [vp, vp, vp, vp, u32, u32, vp, vp, vp, vp, vp]),
+        "zkh_ig_softmax_witness": (i, [vp, vp, vp, u32, u32, vp, vp, vp, vp, vp, vp]),
         "zkh_ig_matmul": (i, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32]),
         "zkh_shard_begin": (i, [vp, i, i, vp, i, u32, vp, i, C.c_char_p, vp]),
         "zkh_shard_round_local": (i, [vp, u32, vp]),

@@ -65,7 +65,11 @@ hist_window_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsig
 }
 // One cluster = ceil(M / 2^15) CTAs (a power of two, at most 8); CTA `rank` owns bins [rank * 2^15, (rank + 1) * 2^15).
 // 1024 threads per CTA and four independent 16-byte loads in flight per thread cover the DRAM latency.
+// REMOTE: the CTAs split the cluster's slice of the indices and increment whichever member owns the bin (half of the
+// increments of a pair cross to the neighbour's shared memory).  Otherwise every member scans the whole slice and counts
+// only its own bins: the slice is read once from DRAM and once more from L2, and every increment is local.
 constexpr uint32_t HC_BINS = 1u << 15;
+template <bool REMOTE>
 __global__ void __launch_bounds__(1024)
 hist_cluster_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsigned long long* bins, unsigned int* oob) {
     namespace cg = cooperative_groups;
@@ -75,14 +79,21 @@ hist_cluster_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsi
     for (uint32_t t = threadIdx.x; t < HC_BINS; t += blockDim.x) shc[t] = 0;
     cluster.sync();                                     // every member's bins are zero before anyone increments them
     const size_t nclusters = gridDim.x / csize, cid = blockIdx.x / csize;
-    const size_t lane = (cid * csize + rank) * blockDim.x + threadIdx.x, stride = nclusters * csize * blockDim.x;
+    const size_t lane = REMOTE ? (cid * csize + rank) * blockDim.x + threadIdx.x : cid * blockDim.x + threadIdx.x;
+    const size_t stride = REMOTE ? nclusters * csize * blockDim.x : nclusters * blockDim.x;
     const size_t n4 = n / 4;
     const uint4* idx4 = reinterpret_cast<const uint4*>(idx);
+    const uint32_t base = rank * HC_BINS;
     unsigned bad = 0;
     auto count = [&](uint32_t r) {
         if (r >= M) { bad++; return; }
-        uint32_t* dst = cluster.map_shared_rank(shc, r >> 15);
-        atomicAdd(dst + (r & (HC_BINS - 1)), 1u);
+        if (REMOTE) {
+            uint32_t* dst = cluster.map_shared_rank(shc, r >> 15);
+            atomicAdd(dst + (r & (HC_BINS - 1)), 1u);
+        } else {
+            const uint32_t d = r - base;
+            if (d < HC_BINS) atomicAdd(&shc[d], 1u);
+        }
     };
     for (size_t i = lane; i < n4; i += 4 * stride) {
         uint4 v[4];
@@ -98,9 +109,8 @@ hist_cluster_kernel(const uint32_t* __restrict__ idx, size_t n, uint32_t M, unsi
         }
     }
     for (size_t i = 4 * n4 + lane; i < n; i += stride) count(idx[i]);
-    if (bad) atomicAdd(oob, bad);
+    if (bad && (REMOTE || rank == 0)) atomicAdd(oob, bad);
     cluster.sync();                                     // all increments, the neighbours' too, have landed
-    const uint32_t base = rank * HC_BINS;
     for (uint32_t t = threadIdx.x; t < HC_BINS && base + t < M; t += blockDim.x)
         if (shc[t]) atomicAdd(&bins[base + t], (unsigned long long)shc[t]);
 }
@@ -180,7 +190,8 @@ extern "C" int zkh_histogram(zkh_ctx* c, const uint32_t* idx_dev, uint64_t n, ui
             static std::atomic<uint64_t> attr{0};
             if (zkh_first_on_device(attr, c->device)) {
                 cudaFuncSetAttribute(hist_window_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
-                cudaFuncSetAttribute(hist_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+                cudaFuncSetAttribute(hist_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+                cudaFuncSetAttribute(hist_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
             }
             const unsigned windows = (M + (1u << 15) - 1) >> 15;
             unsigned csize = 1;
@@ -203,7 +214,13 @@ extern "C" int zkh_histogram(zkh_ctx* c, const uint32_t* idx_dev, uint64_t n, ui
             at[0].val.clusterDim.z = 1;
             cfg.attrs = at;
             cfg.numAttrs = 1;
-            cudaError_t le = cudaLaunchKernelEx(&cfg, hist_cluster_kernel, idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
+            // pairs: every member scans the pair's slice (second read from L2) and all increments are local; larger clusters
+            // split the slice and increment across the cluster.  ZKH_HIST_REMOTE=0/1 overrides (measurement hook).
+            bool remote = csize > 2;
+            if (const char* e = getenv("ZKH_HIST_REMOTE")) remote = atoi(e) != 0;
+            cudaError_t le = remote
+                ? cudaLaunchKernelEx(&cfg, hist_cluster_kernel<true>, idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob)
+                : cudaLaunchKernelEx(&cfg, hist_cluster_kernel<false>, idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
             if (le != cudaSuccess) {        // no room for such a cluster on this device: windows, one read of the indices each
                 cudaGetLastError();
                 size_t blocks = (n + 512 * 64 - 1) / (512 * 64), cap = (size_t)c->sm_count / windows;

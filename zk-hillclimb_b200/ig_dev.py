@@ -202,8 +202,7 @@ def itf_build_witness(c, x0, Wt, T, device="cuda:0", engine=None):
     x0 = d(x0)
     Wd = {"w": [d(x) for x in Wt["w"]], "g1": d(Wt["g1"]), "g2": d(Wt["g2"]), "ct": d(Wt["ct"]), "st": d(Wt["st"])}
     silu, isq, expt = (sig(d(T[n]["cols"][1])) for n in ("SILU", "ISQ", "EXPT"))
-    w = {"x0": x0, "dev_W": Wd, "idxW": [rs20_idx(x) for x in Wd["w"]], "idxG1": rs20_idx(Wd["g1"]), "idxG2": rs20_idx(Wd["g2"]),
-         "idxX0": rs20_idx(x0)}
+    w = {"x0": x0, "dev_W": Wd}
     seq, nh, dh, dm, nb = c.seq, c.nh, c.dh, c.d, c.batch
 
     def mat(X, Wm, K, N):
@@ -213,15 +212,51 @@ def itf_build_witness(c, x0, Wt, T, device="cuda:0", engine=None):
         engine.ig_matmul(X, (0, 0, K, 1), Wm, (0, 0, N, 1), out, (0, 0, N, 1), 1, 1, rows, K, N)
         return out
 
-    w["rms1"] = irms_witness(x0, Wd["g1"], isq, lT, ld)
+    # the library's witness kernels (one per gadget) where the engine has them; the tensor-arithmetic functions of this
+    # module otherwise (the CPU check of this chain's layouts runs those)
+    irs_w, irms_w, irope_w, ismx_w, iswg_w, iadd_w, rs20 = (irs_witness, irms_witness, irope_witness, ismx_witness, iswg_witness,
+                                                              iadd_witness, rs20_idx)
+    if hasattr(engine, "ig_rms_witness"):
+        from ._lib import ZkhError
+        tab = {n: d(T[n]["cols"][1]) for n in ("SILU", "ISQ", "EXPT")}      # value columns, field-lifted
+
+        def guarded(fn):
+            def run(*a):
+                try:
+                    return fn(*a)
+                except ZkhError as e:
+                    if e.code == -4:
+                        raise ValueError("itf: a witness value lies outside its gadget's range (data too large)")
+                    raise
+            return run
+
+        def irms_k(x, g, _isq, lT_, ld_):
+            db, de, y, irow, iel = engine.ig_rms_witness(x, g, tab["ISQ"], lT_, ld_)
+            return {"db": db, "de": de, "y": y, "idxE4": irow[0], "idxM16": irow[1], "idxMS": irow[2], "idxISQ": irow[3],
+                    "idxL": irow[4:13], "idxLR1": irow[13], "idxRW": iel[0], "idxW": iel[1], "idxRY": iel[2], "idxY": iel[3]}
+
+        def ismx_k(z, _expt, la_, lseq_):
+            xe, xb, p, idm, il, imx = engine.ig_softmax_witness(z, tab["EXPT"], la_, lseq_)
+            return {"xe": xe, "xb": xb, "p": p, "idxDM": idm, "idxL": il, "idxMX": imx}
+        irs_w = guarded(engine.irs_witness)
+        irms_w, ismx_w = guarded(irms_k), guarded(ismx_k)
+        irope_w = guarded(lambda q, ct, st, lseq_, ldh_, lT_, ld_: engine.ig_rope_witness(
+            q, ct.reshape(-1).to(torch.int32).contiguous(), st.reshape(-1).to(torch.int32).contiguous(), lseq_, ldh_, lT_, ld_))
+        iswg_w = guarded(lambda g, u, _silu: engine.ig_swiglu_witness(g, u, tab["SILU"]))
+        iadd_w = guarded(engine.ig_add_witness)
+        rs20 = guarded(engine.ig_rs20_index)
+    w["idxW"] = [rs20(x) for x in Wd["w"]]
+    w["idxG1"], w["idxG2"], w["idxX0"] = rs20(Wd["g1"]), rs20(Wd["g2"]), rs20(x0)
+
+    w["rms1"] = irms_w(x0, Wd["g1"], isq, lT, ld)
     w["h1"] = w["rms1"]["y"]
     w["acc"] = [None] * 7
     for i in (ig.W_Q, ig.W_K, ig.W_V):
         w["acc"][i] = mat(w["h1"], Wd["w"][i], c.d, c.d)
-    w["rsq"], w["rsk"], w["rsv"] = (irs_witness(w["acc"][i], 16, 1) for i in (ig.W_Q, ig.W_K, ig.W_V))
+    w["rsq"], w["rsk"], w["rsv"] = (irs_w(w["acc"][i], 16, 1) for i in (ig.W_Q, ig.W_K, ig.W_V))
     w["yq"], w["yk"], w["yv"] = w["rsq"][0], w["rsk"][0], w["rsv"][0]
-    w["rpq"] = irope_witness(w["yq"], Wd["ct"], Wd["st"], lseq, ldh, lT, ld)
-    w["rpk"] = irope_witness(w["yk"], Wd["ct"], Wd["st"], lseq, ldh, lT, ld)
+    w["rpq"] = irope_w(w["yq"], Wd["ct"], Wd["st"], lseq, ldh, lT, ld)
+    w["rpk"] = irope_w(w["yk"], Wd["ct"], Wd["st"], lseq, ldh, lT, ld)
     w["rq"], w["rk"] = w["rpq"][0], w["rpk"][0]
     # scores of head h, batch b (xview_qk / wview_qk / yview_qk, p3_int_layer.cuh:96-122): sc[a][i][k] = sum_j RQ[b][i][h][j] *
     # RK[b][k][h][j], a = b * nh + h; the activations are laid out (batch, position, head, lane)
@@ -229,31 +264,31 @@ def itf_build_witness(c, x0, Wt, T, device="cuda:0", engine=None):
     engine.ig_matmul(w["rq"], (seq * dm, dh, dm, 1), w["rk"], (seq * dm, dh, 1, dm), sc, (nh * seq * seq, seq * seq, seq, 1),
                      nb, nh, seq, dh, seq)
     w["sc"] = sc
-    w["rsz"] = irs_witness(w["sc"], c.sfz, 2)
+    w["rsz"] = irs_w(w["sc"], c.sfz, 2)
     w["z"] = w["rsz"][0]
-    w["smx"] = ismx_witness(w["z"], expt, la, lseq)
+    w["smx"] = ismx_w(w["z"], expt, la, lseq)
     w["p"] = w["smx"]["p"]
     # attention output (xview_pv / wview_pv / yview_pv, p3_int_layer.cuh:124-148): PVA[b][i][h][k] = sum_j P[a][i][j] * YV[b][j][h][k]
     pva = torch.empty(1 << le, dtype=torch.int64, device=device)
     engine.ig_matmul(w["p"], (nh * seq * seq, seq * seq, seq, 1), w["yv"], (seq * dm, dh, dm, 1), pva, (seq * dm, dh, dm, 1),
                      nb, nh, seq, seq, dh)
     w["pva"] = pva
-    w["rsat"] = irs_witness(w["pva"], 16, 1)
+    w["rsat"] = irs_w(w["pva"], 16, 1)
     w["at"] = w["rsat"][0]
     w["acc"][ig.W_O] = mat(w["at"], Wd["w"][ig.W_O], c.d, c.d)
-    w["rso"] = irs_witness(w["acc"][ig.W_O], 16, 1)
+    w["rso"] = irs_w(w["acc"][ig.W_O], 16, 1)
     w["yo"] = w["rso"][0]
-    w["res1"], w["idxRes1"] = iadd_witness(x0, w["yo"])
-    w["rms2"] = irms_witness(w["res1"], Wd["g2"], isq, lT, ld)
+    w["res1"], w["idxRes1"] = iadd_w(x0, w["yo"])
+    w["rms2"] = irms_w(w["res1"], Wd["g2"], isq, lT, ld)
     w["h2"] = w["rms2"]["y"]
     for i in (ig.W_G, ig.W_U):
         w["acc"][i] = mat(w["h2"], Wd["w"][i], c.d, c.dff)
-    w["rsg"], w["rsu"] = irs_witness(w["acc"][ig.W_G], 16, 1), irs_witness(w["acc"][ig.W_U], 16, 1)
+    w["rsg"], w["rsu"] = irs_w(w["acc"][ig.W_G], 16, 1), irs_w(w["acc"][ig.W_U], 16, 1)
     w["gg"], w["uu"] = w["rsg"][0], w["rsu"][0]
-    w["swg"] = iswg_witness(w["gg"], w["uu"], silu)
+    w["swg"] = iswg_w(w["gg"], w["uu"], silu)
     w["mo"] = w["swg"][2]
     w["acc"][ig.W_D] = mat(w["mo"], Wd["w"][ig.W_D], c.dff, c.d)
-    w["rsd"] = irs_witness(w["acc"][ig.W_D], 16, 1)
+    w["rsd"] = irs_w(w["acc"][ig.W_D], 16, 1)
     w["yd"] = w["rsd"][0]
-    w["out"], w["idxOut"] = iadd_witness(w["res1"], w["yd"])
+    w["out"], w["idxOut"] = iadd_w(w["res1"], w["yd"])
     return w

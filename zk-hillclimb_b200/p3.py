@@ -394,6 +394,62 @@ class Prover:
         sa, sb, sc = ((C.c_int64 * 4)(*[int(x) for x in st]) for st in (a_str, b_str, c_str))
         self._ck(self._L.zkh_ig_matmul(self._h, _ptr(A), sa, _ptr(B), sb, _ptr(Cc), sc, nb0, nb1, I, J, K))
 
+    # ---- witness replays of the integer layer's gadgets (one kernel each; see zkh.h) ----
+    def _new(self, n, like, i32=False):
+        import torch
+        return torch.empty(n, dtype=torch.int32 if i32 else torch.int64, device=like.device)
+
+    def ig_add_witness(self, a, b):
+        n = a.numel()
+        out, idx = self._new(n, a), self._new(n, a, True)
+        self._ck(self._L.zkh_ig_add_witness(self._h, _ptr(a), _ptr(b), n, _ptr(out), _ptr(idx)))
+        return out, idx
+
+    def ig_rs20_index(self, v):
+        idx = self._new(v.numel(), v, True)
+        self._ck(self._L.zkh_ig_rs20_index(self._h, _ptr(v), v.numel(), _ptr(idx)))
+        return idx
+
+    def ig_swiglu_witness(self, g, u, silu_col):
+        n = g.numel()
+        sil, rem, mo = (self._new(n, g) for _ in range(3))
+        iG, iR, iM = (self._new(n, g, True) for _ in range(3))
+        self._ck(self._L.zkh_ig_swiglu_witness(self._h, _ptr(g), _ptr(u), _ptr(silu_col), n, _ptr(sil), _ptr(rem), _ptr(mo),
+                                               _ptr(iG), _ptr(iR), _ptr(iM)))
+        return sil, rem, mo, iG, iR, iM
+
+    def ig_rope_witness(self, q, ct, st, lseq, ldh, lT, ld):
+        n = q.numel()
+        y, rem, Cc, S2 = (self._new(n, q) for _ in range(4))
+        iR, iY = self._new(n, q, True), self._new(n, q, True)
+        self._ck(self._L.zkh_ig_rope_witness(self._h, _ptr(q), _ptr(ct), _ptr(st), lseq, ldh, lT, ld, _ptr(y), _ptr(rem), _ptr(iR),
+                                             _ptr(iY), _ptr(Cc), _ptr(S2)))
+        return y, rem, iR, iY, Cc, S2
+
+    def ig_rms_witness(self, x, g, isq_col, lT, ld):
+        B, n = 1 << lT, 1 << (lT + ld)
+        db = [self._new(B, x) for _ in range(18)]
+        de = [self._new(n, x) for _ in range(3)]
+        y = self._new(n, x)
+        irow = [self._new(B, x, True) for _ in range(14)]
+        iel = [self._new(n, x, True) for _ in range(4)]
+        arr = lambda ts: (C.c_uint64 * len(ts))(*[_ptr(t) for t in ts])
+        self._ck(self._L.zkh_ig_rms_witness(self._h, _ptr(x), _ptr(g), _ptr(isq_col), lT, ld, arr(db), arr(de), _ptr(y), arr(irow), arr(iel)))
+        return db, de, y, irow, iel
+
+    def ig_softmax_witness(self, z, expt_col, la, lseq):
+        NR, n = 1 << (la + lseq), 1 << (la + 2 * lseq)
+        xe = [self._new(n, z) for _ in range(7)]
+        xb = [self._new(NR, z) for _ in range(2)]
+        p = self._new(n, z)
+        idm = self._new(n, z, True)
+        il = [self._new(n, z, True) for _ in range(4)]
+        imx = self._new(NR, z, True)
+        arr = lambda ts: (C.c_uint64 * len(ts))(*[_ptr(t) for t in ts])
+        self._ck(self._L.zkh_ig_softmax_witness(self._h, _ptr(z), _ptr(expt_col), la, lseq, arr(xe), arr(xb), _ptr(p), _ptr(idm), arr(il),
+                                                _ptr(imx)))
+        return xe, xb, p, idm, il, imx
+
     def scale(self, col_dev, s):
         import torch
         out = torch.empty_like(col_dev)
