@@ -2,6 +2,7 @@
 host logic and the reference's own provers (witness replay on the host, commitments / lookups / openings on the
 GPU) on the same inputs."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -186,3 +187,44 @@ def test_integer_matmul_kernel_equals_int64_products(zk, prover, nb0, nb1, I, J,
     big[3] = 1 << 30                                     # an operand outside the range is refused, not wrapped
     with pytest.raises(zk.ZkhError):
         prover.ig_matmul(zk.p3.to_device(big), sa, zk.p3.to_device(B), sb, got, sc, nb0, nb1, I, J, K)
+
+
+def test_integer_matmul_tensor_core_and_integer_pipe_paths_agree(zk, tmp_path):
+    """The same products through the tensor-core kernel (three 7-bit limbs, int32 accumulators in tensor memory) and through
+    the integer-pipe kernel, forced with ZKH_IG_MATMUL in fresh processes, against int64 numpy products: full-size tiles,
+    several k-tiles (the shared-memory stages are reused), transposed B, head-sliced views, operands at the limb boundaries."""
+    import subprocess
+    import sys
+    import textwrap
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prog = textwrap.dedent('''
+        import sys, numpy as np, torch
+        sys.path.insert(0, %r); sys.path.insert(0, %r); sys.path.insert(0, %r)
+        import zkh_import
+        from ig_helpers import StridedMatmulEngine
+        zk = zkh_import.load()
+        prover = zk.Prover(0, torch.cuda.current_stream().cuda_stream)
+        lift = lambda a: np.where(a < 0, a.astype(np.int64).view(np.uint64) - np.uint64(0xFFFFFFFF), a.astype(np.int64).view(np.uint64))
+        rng = np.random.default_rng(5)
+        chk = StridedMatmulEngine()
+        for nb0, nb1, I, J, K in [(1, 1, 128, 64, 64), (1, 1, 256, 512, 128), (1, 2, 128, 192, 64), (2, 2, 128, 128, 192), (1, 1, 512, 2048, 256)]:
+            nb = nb0 * nb1
+            for sa, sb, sc in [((nb1 * I * J, I * J, J, 1), (nb1 * J * K, J * K, K, 1), (nb1 * I * K, I * K, K, 1)),
+                               ((nb1 * I * J, I * J, J, 1), (nb1 * J * K, J * K, 1, J), (nb1 * I * K, I * K, K, 1)),
+                               ((I * nb1 * J, J, nb1 * J, 1), (J * nb1 * K, K, nb1 * K, 1), (I * nb1 * K, K, nb1 * K, 1))]:
+                a = rng.integers(-(1 << 20) + 1, 1 << 20, nb * I * J)
+                b = rng.integers(-(1 << 20) + 1, 1 << 20, nb * J * K)
+                a[:8] = [(1 << 20) - 1, -(1 << 20) + 1, 127, 128, -128, -129, 16383, -16384]
+                b[:4] = [-(1 << 20) + 1, (1 << 20) - 1, 16384, -1]
+                A, B = lift(a), lift(b)
+                want = torch.zeros(nb * I * K, dtype=torch.int64)
+                chk.ig_matmul(torch.from_numpy(A.view(np.int64)), sa, torch.from_numpy(B.view(np.int64)), sb, want, sc, nb0, nb1, I, J, K)
+                got = torch.zeros(nb * I * K, dtype=torch.int64, device="cuda")
+                prover.ig_matmul(zk.p3.to_device(A), sa, zk.p3.to_device(B), sb, got, sc, nb0, nb1, I, J, K)
+                assert (got.cpu() == want).all(), (nb0, nb1, I, J, K, sa)
+        print("OK")
+    ''') % (root, os.path.join(root, "oracle"), os.path.join(root, "tests"))
+    for path in ("tc", "imad"):
+        env = dict(os.environ, ZKH_IG_MATMUL=path)
+        r = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=env, timeout=600)
+        assert r.returncode == 0 and "OK" in r.stdout, (path, r.stdout[-2000:], r.stderr[-2000:])

@@ -6,6 +6,8 @@
 // integers (v or p - |v|), read through strided views so that the per-head slices of the (batch, position, head, lane)
 // activations need no gather, multiplied exactly in 64-bit integers and written back lifted.
 //
+// Two kernels: the tensor-core one (ig_matmul_tc.cu) for full-size shapes, and this integer-pipe one for everything else
+// (small or ragged shapes, operands beyond 2^20).
 // Tiling: a CTA of 256 threads owns a 128 x 64 tile of C; operands are converted to int32 while they are staged in
 // shared memory (k-major), every thread accumulates an 8 x 4 block in 64-bit registers with one 32 x 32 + 64 multiply-add
 // per product.  The next k-slab is fetched into registers while the current one is multiplied.
@@ -114,6 +116,9 @@ __global__ void __launch_bounds__(IGM_T) ig_matmul_kernel(const gl_t* __restrict
     if (bad) atomicOr(err, 16u);
 }
 
+int ig_matmul_tc(zkh_ctx* c, const gl_t* A, const long long sa[4], const gl_t* B, const long long sb[4], gl_t* Cc, const long long sc[4],
+                 uint32_t nb0, uint32_t nb1, uint32_t I, uint32_t J, uint32_t K);
+
 }  // namespace zkh
 
 using namespace zkh;
@@ -127,6 +132,15 @@ extern "C" int zkh_ig_matmul(zkh_ctx* c, const uint64_t* A_dev, const int64_t a_
     if (J > (1u << 15)) return zkh_fail(c, ZKH_ERR_LIMIT, "ig_matmul: more than 2^15 terms per output");
     if ((uint64_t)nb0 * nb1 > 65535) return zkh_fail(c, ZKH_ERR_LIMIT, "ig_matmul: more than 65535 batch entries");
     ZKH_CUDA(c, cudaSetDevice(c->device));
+    // full-size shapes run on the tensor cores (three 7-bit limbs per operand, exact); ZKH_IG_MATMUL=imad / tc forces a path
+    const char* force = getenv("ZKH_IG_MATMUL");
+    if (!force || strcmp(force, "imad")) {
+        const long long sa[4] = {a_strides[0], a_strides[1], a_strides[2], a_strides[3]}, sb[4] = {b_strides[0], b_strides[1], b_strides[2], b_strides[3]},
+                        sc[4] = {c_strides[0], c_strides[1], c_strides[2], c_strides[3]};
+        const int rc = ig_matmul_tc(c, A_dev, sa, B_dev, sb, C_dev, sc, nb0, nb1, I, J, K);
+        if (rc != 1) return rc;
+        if (force && !strcmp(force, "tc")) return zkh_fail(c, ZKH_ERR_ARG, "ig_matmul: shape or operand range outside the tensor-core path");
+    }
     MatView va{a_strides[0], a_strides[1], a_strides[2], a_strides[3]};
     MatView vb{b_strides[0], b_strides[1], b_strides[2], b_strides[3]};
     MatView vc{c_strides[0], c_strides[1], c_strides[2], c_strides[3]};
