@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 METRIC = "sumcheck fold GB/s (degree-2, 2^28 Goldilocks MLEs)"
 UNIT = "GB/s"
 SEED = 0xBEEF1234
-DRAM_PER_ALG_BYTE = {"sc_fused_kernel": 0.953}
+DRAM_PER_ALG_BYTE = {"sc_fused_kernel": 0.933}   # dram read + write per algorithmic byte, current kernel, 2^24 capture
 
 
 def alg_bytes(nc, logn):
@@ -1123,13 +1123,16 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
     except Exception as e:
         err = repr(e)
 
-    nthr = max(1, args.layer_streams)
-    out["concurrent_proofs_per_gpu"] = nthr
-    out["concurrency_note"] = ("each GPU runs %d layer proofs at a time, each on its own stream and library context, so the "
-                               "latency-bound rounds of one proof overlap the hashing and encoding of another" % nthr)
-    streams = [torch.cuda.Stream(device=dvc) for _ in range(nthr)] if nthr > 1 else [torch.cuda.current_stream()]
-    provers = [zk.Prover(local, st.cuda_stream) for st in streams] if nthr > 1 else [prover]
-    keep_zk = (80 << 30) if nthr == 1 else (100 << 30) // nthr
+    nmax = max(1, args.layer_streams)
+    out["concurrent_proofs_per_gpu"] = {"plain": nmax, "zk": 1}
+    out["concurrency_note"] = ("plain mode: each GPU runs %d layer proofs at a time, each on its own stream and library context, so "
+                               "the latency-bound rounds of one proof overlap the hashing and encoding of another; hiding mode: one "
+                               "at a time (the openings of its 2^27-entry mask streams need about 80 GB of scratch)" % nmax)
+    prover.release_workspace()                 # the sumcheck steps' scratch is not needed any more
+    streams = [torch.cuda.Stream(device=dvc) for _ in range(nmax)] if nmax > 1 else [torch.cuda.current_stream()]
+    provers = [zk.Prover(local, st.cuda_stream) for st in streams] if nmax > 1 else [prover]
+    keep_zk = 80 << 30
+    nthr = nmax
 
     def one_layer(pr, stream, layer, hiding, acc):
         t = [time.perf_counter()]
@@ -1182,6 +1185,7 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
     for mode in (("plain",) if args.no_zk_layer else ("plain", "zk")):
         hiding = mode == "zk"
         ms, nbytes = 0.0, 0
+        nthr = 1 if hiding else nmax
         accs = [{} for _ in range(nthr)]
         if err is None:
             for pr in provers:
@@ -1212,8 +1216,8 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
         for pr in provers:
             pr.keep_trees = False
             pr.release_kept()
-        if hiding:
-            torch.cuda.empty_cache()
+            pr.release_workspace()
+        torch.cuda.empty_cache()
         bad = 1.0 if err is not None else 0.0
         if world > 1:
             t = torch.tensor([ms, bad], device="cuda")

@@ -69,6 +69,9 @@ ZKH_API int zkh_ctx_create(int device, void* stream, zkh_ctx** out);
 ZKH_API void zkh_ctx_destroy(zkh_ctx* ctx);
 ZKH_API int zkh_ctx_set_stream(zkh_ctx* ctx, void* stream);
 ZKH_API int zkh_ctx_sync(zkh_ctx* ctx);
+/* Frees the context's scratch workspace (it grows to the largest call made so far and is otherwise kept until the
+ * context is destroyed); the next call that needs scratch allocates again.  Synchronises the stream first. */
+ZKH_API int zkh_ctx_release_workspace(zkh_ctx* ctx);
 ZKH_API const char* zkh_last_error(const zkh_ctx* ctx);
 ZKH_API const char* zkh_version(void);
 

@@ -74,6 +74,7 @@ def load_library():
         "zkh_fr_dot": (i, [vp, vp, vp, u64, vp]),
         "zkh_fr_lookup_sumcheck": (i, [vp, vp, vp, vp, vp, vp, u32, u32, vp, vp, vp, vp, vp, vp, vp, vp]),
         "zkh_fr_sumcheck": (i, [vp, vp, i, u32, vp, vp, vp, vp, vp]),
+        "zkh_ctx_release_workspace": (i, [vp]),
         "zkh_ig_add_witness": (i, [vp, vp, vp, u64, vp, vp]),
         "zkh_ig_rs20_index": (i, [vp, vp, u64, vp]),
         "zkh_ig_swiglu_witness": (i, [vp, vp, vp, vp, u64, vp, vp, vp, vp, vp, vp]),

@@ -22,6 +22,16 @@ int zkh_ws_reserve(zkh_ctx* c, size_t bytes) {
     return ZKH_OK;
 }
 
+extern "C" int zkh_ctx_release_workspace(zkh_ctx* c) {
+    if (!c) return ZKH_ERR_ARG;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (c->ws) cudaFree(c->ws);
+    c->ws = nullptr;
+    c->ws_bytes = 0;
+    return ZKH_OK;
+}
+
 extern "C" const char* zkh_version(void) { return "zkh 0.1 (sm_100a)"; }
 
 extern "C" int zkh_ctx_create(int device, void* stream, zkh_ctx** out) {

@@ -156,6 +156,10 @@ class Prover:
     def sync(self):
         self._ck(self._L.zkh_ctx_sync(self._h))
 
+    def release_workspace(self):
+        """Give the context's scratch workspace back to the device (it is re-allocated on demand)."""
+        self._ck(self._L.zkh_ctx_release_workspace(self._h))
+
     def profile_last(self):
         """(kernel name, milliseconds, algorithmic bytes) of the dominant launch of the last call."""
         ms, nb, nm = C.c_float(0), C.c_uint64(0), C.c_char_p()
