@@ -1161,13 +1161,20 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
         return len(pf)
 
     def run_layers(layers, hiding, accs):
-        """layers[i] goes to worker i mod nthr; returns (proof bytes of the last layer, first error or None)."""
+        """The rank's layers, each worker taking the next one when it is free; returns (proof bytes of the last layer,
+        first error or None)."""
         res = {"n": 0, "err": None}
+        todo = list(layers)
+        lock = threading.Lock()
 
         def worker(tid):
             try:
                 with torch.cuda.stream(streams[tid]):
-                    for layer in layers[tid::nthr]:
+                    while res["err"] is None:
+                        with lock:
+                            if not todo:
+                                break
+                            layer = todo.pop(0)
                         res["n"] = one_layer(provers[tid], streams[tid], layer, hiding, accs[tid])
                     streams[tid].synchronize()
             except Exception as e:           # noqa: BLE001 -- reported in the JSON line, the other ranks must not hang

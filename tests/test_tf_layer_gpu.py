@@ -132,11 +132,13 @@ def test_two_layer_model_on_device_accepted_by_reference_verifier(orc, ref, zk, 
     art = load_art(ref, zk, c.ld)
     T = tfg.tf_tables(art)
     MW, ids = small_model(zk, c, nlayers, vocab, 21)
-    w = tfg.mdl_build_witness(c, ids, MW, art, device="cuda:%d" % prover.device, engine=prover)
-    o = tfg.mdl_commit(prover, w, MW, R, ident)
-    roots = tfg.mdl_roots(prover, c, MW, R, ident)
+    dev = "cuda:%d" % prover.device
+    to_dev = lambda t: t if t.is_cuda else t.to(dev)          # the model's host-side columns (embedding, head) are uploaded here
+    w = tfg.mdl_build_witness(c, ids, MW, art, device=dev, engine=prover)
+    o = tfg.mdl_commit(prover, w, MW, R, to_dev)
+    roots = tfg.mdl_roots(prover, c, MW, R, to_dev)
     tr = zk.Transcript("mdl")
-    pf = tfg.mdl_prove(prover, tr, w, o, T, art, R, Q, ident)
+    pf = tfg.mdl_prove(prover, tr, w, o, T, art, R, Q, to_dev)
     st0 = zk.Transcript("mdl").state
     logits = np.asarray(w["logits"].cpu() if hasattr(w["logits"], "cpu") else w["logits"])
     ok, st = ref_mdl_verify(ref, st0, c, nlayers, vocab, ids, roots, MW["layers"][0], logits, R, Q, pf)
