@@ -301,11 +301,15 @@ ZKH_API int zkh_batchopen_prove_class(zkh_ctx* ctx, uint32_t v, const uint64_t* 
                                       const uint64_t* const* cols_dev, const uint8_t* roots, const uint32_t* zid,
                                       uint32_t k, uint32_t R, uint32_t Q, const char* label, uint8_t state[32],
                                       uint8_t* out, size_t cap, size_t* written);
-/* Commitment that keeps its codeword (2^(v+R) elements) and Merkle tree (zkh_merkle_tree_bytes(2^(v+R)) bytes) in
- * caller-owned device buffers, and the batched opening that reads them: with 180 GB of HBM a prover can keep the
- * trees of a whole layer resident, so prove_class no longer re-encodes and re-hashes every opened column as the
+/* Commitment that keeps its codeword (2^(v+R) elements) and its CAPPED Merkle tree (zkh_basefold_kept_tree_bytes(v+R)
+ * bytes) in caller-owned device buffers, and the batched opening that reads them: with 180 GB of HBM a prover can keep
+ * the trees of a whole layer resident, so prove_class no longer re-encodes and re-hashes every opened column as the
  * reference does (zkllm-src/p3_batchopen.cuh:393-445 resolves and rebuilds them).  Proof bytes are unchanged.
+ * A capped tree holds the levels from 64 leaves per node upwards in the layout of zkh_merkle_build (for fewer than 256
+ * leaves: the whole tree): 9 bytes per codeword element together with the codeword instead of 72; the lowest six
+ * siblings of an opened path are recomputed from 64 codeword elements (191 compressions per opened leaf).
  * kept_cw[j] / kept_tree[j]: buffers of entry j's column, or NULL to recompute that column. */
+ZKH_API size_t zkh_basefold_kept_tree_bytes(uint32_t logM);
 ZKH_API int zkh_basefold_commit_keep(zkh_ctx* ctx, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t* cw_dev,
                              uint8_t* tree_dev, uint8_t root[32]);
 ZKH_API int zkh_batchopen_prove_class_kept(zkh_ctx* ctx, uint32_t v, const uint64_t* pts, uint32_t T,
@@ -334,7 +338,7 @@ ZKH_API int zkh_basefold_commit_many(zkh_ctx* ctx, const uint64_t* const* cols_d
 /* Hiding commitment: salted Merkle leaves (zkllm-src/p3_zkc.cuh:230-292 salt_of / salted_leaf / p3zkc_salted_leaf_kernel,
  * :320-397 salted_commit_root, salted_commit_root_dev).  Leaf i = SHA-256(value_le8 | SHA-256(sseed_le8 | i_le8)); internal
  * nodes as in the plain tree, so authentication paths verify unchanged.  cw_dev (2^(v+R) elements) and tree_dev
- * (zkh_merkle_tree_bytes(2^(v+R)) bytes) are optional; a kept tree needs the kept codeword. */
+ * (capped: zkh_basefold_kept_tree_bytes(v+R) bytes) are optional; a kept tree needs the kept codeword. */
 ZKH_API int zkh_basefold_commit_salted(zkh_ctx* ctx, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t sseed,
                                uint64_t* cw_dev, uint8_t* tree_dev, uint8_t root[32]);
 

@@ -122,6 +122,7 @@ def load_library():
         "zkh_ntt": (i, [vp, vp, vp, u32, i]),
         "zkh_rs_encode": (i, [vp, vp, u32, u32, vp]),
         "zkh_merkle_tree_bytes": (sz, [u64]),
+        "zkh_basefold_kept_tree_bytes": (sz, [u32]),
         "zkh_merkle_build": (i, [vp, vp, u64, vp, vp]),
         "zkh_merkle_paths": (i, [vp, vp, u64, vp, u32, vp]),
         "zkh_gl_fold_codeword": (i, [vp, vp, vp, u64, u64]),

@@ -132,8 +132,12 @@ extern "C" int zkh_basefold_commit(zkh_ctx* c, const uint64_t* c_dev, uint32_t v
     return ZKH_OK;
 }
 
-// Commit and KEEP: the codeword and the whole Merkle tree stay in caller-owned device buffers, so that later
+// Commit and KEEP: the codeword and the capped Merkle tree (levels from 64 leaves per node upwards; the lowest six
+// levels of an opened path are rebuilt from 64 codeword elements) stay in caller-owned device buffers, so that later
 // openings of this column read authentication paths instead of encoding and hashing the column again.
+extern "C" size_t zkh_basefold_kept_tree_bytes(uint32_t logM) {
+    return logM >= 1 && logM <= 32 ? merkle_capped_bytes((size_t)1 << logM) : 0;
+}
 extern "C" int zkh_basefold_commit_keep(zkh_ctx* c, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t* cw_dev,
                                         uint8_t* tree_dev, uint8_t root[32]) {
     if (!c || !c_dev || !root || !cw_dev || !tree_dev) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_keep: null pointer");
@@ -141,10 +145,11 @@ extern "C" int zkh_basefold_commit_keep(zkh_ctx* c, const uint64_t* c_dev, uint3
     ZKH_CUDA(c, cudaSetDevice(c->device));
     const uint32_t logM = v + R;
     const size_t M = (size_t)1 << logM;
-    ZKH_TRY(zkh_ws_reserve(c, ntt_scratch_bytes(logM)));
+    const size_t nttb = ntt_scratch_bytes(logM);
+    ZKH_TRY(zkh_ws_reserve(c, nttb + merkle_scratch_bytes(M)));
     ZKH_TRY(ntt_enqueue(c, c_dev, (uint64_t)1 << v, cw_dev, logM, false, c->ws));
     uint8_t* root_dev = (uint8_t*)c->d_ctl->aux;
-    ZKH_TRY(merkle_enqueue(c, cw_dev, M, tree_dev, nullptr, root_dev));
+    ZKH_TRY(merkle_enqueue(c, cw_dev, M, tree_dev, (char*)c->ws + nttb, root_dev, nullptr, merkle_cut(M)));
     ZKH_CUDA(c, cudaMemcpyAsync(c->h_ctl->aux, root_dev, 32, cudaMemcpyDeviceToHost, c->stream));
     ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
     memcpy(root, c->h_ctl->aux, 32);
@@ -184,7 +189,7 @@ extern "C" int zkh_basefold_commit_many(zkh_ctx* c, const uint64_t* const* cols_
 }
 
 // Hiding commitment (zkllm-src/p3_zkc.cuh:320-397 salted_commit_root / salted_commit_root_dev): the same codeword, leaves
-// salted with SHA-256(seed | leaf index).  cw_dev / tree_dev optional (both or none keep codeword and tree resident).
+// salted with SHA-256(seed | leaf index).  cw_dev / tree_dev optional (both or none keep codeword and capped tree resident).
 extern "C" int zkh_basefold_commit_salted(zkh_ctx* c, const uint64_t* c_dev, uint32_t v, uint32_t R, uint64_t sseed,
                                           uint64_t* cw_dev, uint8_t* tree_dev, uint8_t root[32]) {
     if (!c || !c_dev || !root) return zkh_fail(c, ZKH_ERR_ARG, "basefold_commit_salted: null pointer");
@@ -193,12 +198,12 @@ extern "C" int zkh_basefold_commit_salted(zkh_ctx* c, const uint64_t* c_dev, uin
     ZKH_CUDA(c, cudaSetDevice(c->device));
     const uint32_t logM = v + R;
     const size_t M = (size_t)1 << logM;
-    const size_t cwb = cw_dev ? 0 : zkh_align(M * 8), nttb = ntt_scratch_bytes(logM), mkb = tree_dev ? 0 : merkle_scratch_bytes(M);
+    const size_t cwb = cw_dev ? 0 : zkh_align(M * 8), nttb = ntt_scratch_bytes(logM), mkb = merkle_scratch_bytes(M);
     ZKH_TRY(zkh_ws_reserve(c, cwb + nttb + mkb));
     gl_t* cw = cw_dev ? cw_dev : (gl_t*)c->ws;
     ZKH_TRY(ntt_enqueue(c, c_dev, (uint64_t)1 << v, cw, logM, false, (char*)c->ws + cwb));
     uint8_t* root_dev = (uint8_t*)c->d_ctl->aux;
-    ZKH_TRY(merkle_enqueue(c, cw, M, tree_dev, tree_dev ? nullptr : (char*)c->ws + cwb + nttb, root_dev, &sseed));
+    ZKH_TRY(merkle_enqueue(c, cw, M, tree_dev, (char*)c->ws + cwb + nttb, root_dev, &sseed, tree_dev ? merkle_cut(M) : 0));
     ZKH_CUDA(c, cudaMemcpyAsync(c->h_ctl->aux, root_dev, 32, cudaMemcpyDeviceToHost, c->stream));
     ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
     memcpy(root, c->h_ctl->aux, 32);

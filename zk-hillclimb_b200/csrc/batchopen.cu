@@ -166,16 +166,20 @@ __global__ void bo_dots_sum_kernel(const gl_t* partials, uint32_t nb, gl_t* out)
     block_sum<1>(s, sh);
     if (threadIdx.x == 0) out[blockIdx.x] = s[0];
 }
-// openings of rounds 1..v-1 straight into the proof's query section
-__global__ void bo_query_kernel(const gl_t* cw_rest, const uint8_t* trees, uint32_t logM0, uint32_t v, uint32_t Q,
+// where the capped tree of every fold round starts inside the tree region, and how many low levels it leaves out
+struct BoTrees { size_t off[32]; uint32_t cut[32]; };
+// openings of rounds 1..v-1 straight into the proof's query section: values and the path siblings from the capped trees
+// (levels below a round's cut come from merkle_low_paths_enqueue)
+__global__ void bo_query_kernel(const gl_t* cw_rest, const uint8_t* trees, BoTrees bt, uint32_t logM0, uint32_t v, uint32_t Q,
                                 const uint32_t* pos /* [Q][v] */, uint8_t* out, size_t per_query) {
     uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= Q * (v - 1) * 2) return;
     const uint32_t side = t & 1, e = t >> 1, q = e / (v - 1), r = 1 + e % (v - 1);
     const size_t M0 = (size_t)1 << logM0, Mr = M0 >> r, h = Mr / 2;
-    const uint32_t plen = logM0 - r;
+    const uint32_t plen = logM0 - r, cut = bt.cut[r];
     const gl_t* cw = cw_rest + (M0 - 2 * Mr);
-    const uint8_t* tree = trees + (2 * (M0 - 2 * Mr) - (r - 1)) * 32;
+    const uint8_t* tree = trees + bt.off[r];
+    const size_t Mt = Mr >> cut;
     const size_t idx = (size_t)pos[q * v + r] + (side ? h : 0);
     // offset of round r within a query: sum_{i=1}^{r-1} (16 + 64*(logM0-i))
     const size_t rr = r - 1;
@@ -183,29 +187,31 @@ __global__ void bo_query_kernel(const gl_t* cw_rest, const uint8_t* trees, uint3
     uint8_t* o = out + off;
     *reinterpret_cast<gl_t*>(o + 8 * side) = cw[idx];
     uint4* po = reinterpret_cast<uint4*>(o + 16 + (size_t)side * plen * 32);
-    size_t id = idx;
-    for (uint32_t l = 0; l < plen; l++) {
-        size_t cnt = Mr >> l;
-        const uint4* src = reinterpret_cast<const uint4*>(tree + (2 * Mr - 2 * cnt + (id ^ 1)) * 32);
+    size_t id = idx >> cut;
+    for (uint32_t l = cut; l < plen; l++) {
+        size_t cnt = Mt >> (l - cut);
+        const uint4* src = reinterpret_cast<const uint4*>(tree + (2 * Mt - 2 * cnt + (id ^ 1)) * 32);
         po[2 * l] = src[0];
         po[2 * l + 1] = src[1];
         id >>= 1;
     }
 }
-// round-0 opening of one column: values and full authentication paths at the nu positions
+// round-0 opening of one column: values and the authentication-path siblings of levels cut..logM0-1 at the nu positions,
+// read from a capped tree (the lowest `cut` siblings come from merkle_low_paths_enqueue)
 // out: [nu] values (8 bytes each) then [nu][logM0] digests
-__global__ void bo_q0_kernel(const gl_t* cw, const uint8_t* tree, uint32_t logM0, const uint32_t* upos, uint32_t nu,
+__global__ void bo_q0_kernel(const gl_t* cw, const uint8_t* tree, uint32_t logM0, uint32_t cut, const uint32_t* upos, uint32_t nu,
                              uint8_t* out) {
     uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= nu * (logM0 + 1)) return;
     const uint32_t i = t / (logM0 + 1), l = t % (logM0 + 1);
-    const size_t M0 = (size_t)1 << logM0;
     if (l == logM0) {
         reinterpret_cast<gl_t*>(out)[i] = cw[upos[i]];
         return;
     }
-    size_t cnt = M0 >> l, sib = ((size_t)upos[i] >> l) ^ 1;
-    const uint4* src = reinterpret_cast<const uint4*>(tree + (2 * M0 - 2 * cnt + sib) * 32);
+    if (l < cut) return;
+    const size_t Mt = (size_t)1 << (logM0 - cut);
+    size_t cnt = Mt >> (l - cut), sib = ((size_t)upos[i] >> l) ^ 1;
+    const uint4* src = reinterpret_cast<const uint4*>(tree + (2 * Mt - 2 * cnt + sib) * 32);
     uint4* dst = reinterpret_cast<uint4*>(out + (size_t)nu * 8 + ((size_t)i * logM0 + l) * 32);
     dst[0] = src[0];
     dst[1] = src[1];
@@ -287,11 +293,20 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
     const size_t o_zs = take((size_t)T * v * 8), o_tlo = take(((size_t)T << vl) * 8), o_thi = take(((size_t)T << vh) * 8);
     const size_t o_tlo2 = take(((size_t)T << vl) * 8), o_thi2 = take(((size_t)T << vh) * 8);
     const size_t o_eqr = take(N * 8), o_U = take(N * 8), o_ys = take((size_t)nc * 8), o_dp = take((size_t)nc * nb * 8);
-    const size_t o_cw0 = take(M0 * 8), o_cwr = take(M0 * 8), o_trees = take((size_t)2 * M0 * 32);
+    BoTrees bt;
+    memset(&bt, 0, sizeof bt);
+    size_t tree_bytes = 0;
+    for (uint32_t r = 1; r < v; r++) {
+        bt.off[r] = tree_bytes;
+        bt.cut[r] = merkle_cut(M0 >> r);
+        tree_bytes += merkle_capped_bytes(M0 >> r);
+    }
+    const size_t o_cw0 = take(M0 * 8), o_cwr = take(M0 * 8), o_trees = take(tree_bytes + 32);
     const size_t o_oa = take((N + 2) * 8), o_ob = take((N / 2 + 2) * 8);
     const size_t o_roots = take((size_t)v * 32), o_pos = take((size_t)Q * v * 4 + (size_t)2 * Q * 4);
     const size_t o_q = take((size_t)Q * per_query + 16);
-    const size_t o_cwc = take(M0 * 8), o_treec = take(merkle_tree_bytes(M0)), o_q0 = take((size_t)nc * q0_per_col);
+    const uint32_t cut0 = merkle_cut(M0);
+    const size_t o_cwc = take(M0 * 8), o_treec = take(merkle_capped_bytes(M0)), o_mks = take(merkle_scratch_bytes(M0)), o_q0 = take((size_t)nc * q0_per_col);
     const size_t o_misc = take(std::max(eq_scratch_bytes(v), ntt_scratch_bytes(logM0)));
     ZKH_TRY(zkh_ws_reserve(c, off));
     char* ws = (char*)c->ws;
@@ -439,8 +454,7 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
         for (uint32_t r = 0; r < v; r++) {
             const size_t Mr = M0 >> r, n = N >> r;
             if (r > 0) {
-                uint8_t* tree = trees + (2 * (M0 - 2 * Mr) - (r - 1)) * 32;
-                ZKH_TRY(merkle_enqueue(c, cw_cur, Mr, tree, nullptr, d_roots + (size_t)(r - 1) * 32));
+                ZKH_TRY(merkle_enqueue(c, cw_cur, Mr, trees + bt.off[r], ws + o_mks, d_roots + (size_t)(r - 1) * 32, nullptr, bt.cut[r]));
                 ZKH_TRY(tr_absorb_enqueue(c, "root", (const uint64_t*)(d_roots + (size_t)(r - 1) * 32), 4));
             }
             if (r == 0) {
@@ -486,8 +500,16 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
     ZKH_CUDA(c, cudaMemcpyAsync(d_upos, upos.data(), (size_t)nu * 4, cudaMemcpyHostToDevice, s));
     if (v > 1) {
         const uint32_t nth = Q * (v - 1) * 2;
-        bo_query_kernel<<<(nth + 127) / 128, 128, 0, s>>>(cwr, trees, logM0, v, Q, d_pos, d_q, per_query);
+        bo_query_kernel<<<(nth + 127) / 128, 128, 0, s>>>(cwr, trees, bt, logM0, v, Q, d_pos, d_q, per_query);
         ZKH_CUDA(c, cudaGetLastError());
+        for (uint32_t r = 1; r < v; r++) {                     // the lowest levels of both openings of every query, rebuilt from the codeword
+            const size_t Mr = M0 >> r, rr = r - 1;
+            const size_t roff = rr * 16 + 64 * (rr * logM0 - rr * (rr + 1) / 2);
+            for (uint32_t side = 0; side < 2 && bt.cut[r]; side++)
+                ZKH_TRY(merkle_low_paths_enqueue(c, cwr + (M0 - 2 * Mr), bt.cut[r], d_pos + r, Q, nullptr,
+                                                 d_q + roff + 16 + (size_t)side * (logM0 - r) * 32, per_query, v,
+                                                 side ? (uint32_t)(Mr / 2) : 0));
+        }
         ZKH_CUDA(c, cudaMemcpyAsync(p_q, d_q, (size_t)Q * per_query, cudaMemcpyDeviceToHost, s));
     }
     // round-0 openings: re-encode each distinct column, hash its tree, gather values and paths
@@ -496,14 +518,17 @@ static int batchopen_prove_class(zkh_ctx* c, uint32_t v, const uint64_t* pts, ui
         const gl_t* cw_use = cwc;
         const uint8_t* tree_use = treec;
         if (kept_cw && kept_tree && kept_cw[first[cc]] && kept_tree[first[cc]]) {
-            cw_use = kept_cw[first[cc]];          // committed with zkh_basefold_commit_keep: nothing to recompute
+            cw_use = kept_cw[first[cc]];          // committed with zkh_basefold_commit_keep (capped tree): nothing to recompute
             tree_use = kept_tree[first[cc]];
         } else {
             ZKH_TRY(ntt_enqueue(c, cols_dev[first[cc]], N, cwc, logM0, false, ws + o_misc));
-            ZKH_TRY(merkle_enqueue(c, cwc, M0, treec, nullptr, nullptr, sseeds ? sseeds + first[cc] : nullptr));
+            ZKH_TRY(merkle_enqueue(c, cwc, M0, treec, ws + o_mks, nullptr, sseeds ? sseeds + first[cc] : nullptr, cut0));
         }
         const uint32_t nth = nu * (logM0 + 1);
-        bo_q0_kernel<<<(nth + 127) / 128, 128, 0, s>>>(cw_use, tree_use, logM0, d_upos, nu, d_q0 + (size_t)cc * q0_per_col);
+        uint8_t* q0c = d_q0 + (size_t)cc * q0_per_col;
+        bo_q0_kernel<<<(nth + 127) / 128, 128, 0, s>>>(cw_use, tree_use, logM0, cut0, d_upos, nu, q0c);
+        ZKH_TRY(merkle_low_paths_enqueue(c, cw_use, cut0, d_upos, nu, sseeds ? sseeds + first[cc] : nullptr, q0c + (size_t)nu * 8,
+                                         (size_t)logM0 * 32));
     }
     ZKH_CUDA(c, cudaGetLastError());
     std::vector<uint8_t> hq0((size_t)nc * q0_per_col);

@@ -10,24 +10,6 @@
 
 namespace zkh {
 
-__device__ __forceinline__ void store_digest(uint32_t* dst, const uint32_t h[8]) {
-    uint4 a = make_uint4(bswap32(h[0]), bswap32(h[1]), bswap32(h[2]), bswap32(h[3]));
-    uint4 b = make_uint4(bswap32(h[4]), bswap32(h[5]), bswap32(h[6]), bswap32(h[7]));
-    reinterpret_cast<uint4*>(dst)[0] = a;
-    reinterpret_cast<uint4*>(dst)[1] = b;
-}
-__device__ __forceinline__ void load_digest(const uint32_t* src, uint32_t h[8]) {
-    uint4 a = __ldg(reinterpret_cast<const uint4*>(src)), b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
-    h[0] = bswap32(a.x); h[1] = bswap32(a.y); h[2] = bswap32(a.z); h[3] = bswap32(a.w);
-    h[4] = bswap32(b.x); h[5] = bswap32(b.y); h[6] = bswap32(b.z); h[7] = bswap32(b.w);
-}
-
-// leaf digest: plain, or salted with (seed, leaf index) for hiding commitments (zkllm-src/p3_zkc.cuh:272-279)
-template <bool SALT>
-__device__ __forceinline__ void leaf_digest(gl_t v, uint64_t sseed, size_t idx, uint32_t h[8]) {
-    if (SALT) sha256_salted_leaf(v, sseed, (uint64_t)idx, h);
-    else sha256_leaf(v, h);
-}
 // thread i: leaves 4i..4i+3 -> level-1 nodes 2i, 2i+1 -> level-2 node i
 template <bool SALT>
 __global__ void __launch_bounds__(256)
@@ -39,13 +21,13 @@ merkle_leaf4_kernel(const gl_t* __restrict__ cw, uint32_t* lv0, uint32_t* lv1, u
     leaf_digest<SALT>(a.x, sseed, 4 * i, h0);
     leaf_digest<SALT>(a.y, sseed, 4 * i + 1, h1);
     if (lv0) { store_digest(lv0 + (4 * i) * 8, h0); store_digest(lv0 + (4 * i + 1) * 8, h1); }
-    sha256_node(h0, h1, n0);
+    sha256_node<true>(h0, h1, n0);
     leaf_digest<SALT>(b.x, sseed, 4 * i + 2, h0);
     leaf_digest<SALT>(b.y, sseed, 4 * i + 3, h1);
     if (lv0) { store_digest(lv0 + (4 * i + 2) * 8, h0); store_digest(lv0 + (4 * i + 3) * 8, h1); }
-    sha256_node(h0, h1, n1);
+    sha256_node<true>(h0, h1, n1);
     if (lv1) { store_digest(lv1 + (2 * i) * 8, n0); store_digest(lv1 + (2 * i + 1) * 8, n1); }
-    sha256_node(n0, n1, top);
+    sha256_node<true>(n0, n1, top);
     store_digest(lv2 + i * 8, top);
 }
 // thread i: digests 4i..4i+3 of one level -> two parents -> one grandparent
@@ -56,12 +38,12 @@ merkle_node4_kernel(const uint32_t* __restrict__ in, uint32_t* up1, uint32_t* up
     uint32_t a[8], b[8], n0[8], n1[8], top[8];
     load_digest(in + (4 * i) * 8, a);
     load_digest(in + (4 * i + 1) * 8, b);
-    sha256_node(a, b, n0);
+    sha256_node<true>(a, b, n0);
     load_digest(in + (4 * i + 2) * 8, a);
     load_digest(in + (4 * i + 3) * 8, b);
-    sha256_node(a, b, n1);
+    sha256_node<true>(a, b, n1);
     if (up1) { store_digest(up1 + (2 * i) * 8, n0); store_digest(up1 + (2 * i + 1) * 8, n1); }
-    sha256_node(n0, n1, top);
+    sha256_node<true>(n0, n1, top);
     store_digest(up2 + i * 8, top);
 }
 // single level (used for the odd level at the top and for 2-leaf trees)
@@ -71,7 +53,7 @@ __global__ void merkle_node2_kernel(const uint32_t* __restrict__ in, uint32_t* u
     uint32_t a[8], b[8], n[8];
     load_digest(in + (2 * i) * 8, a);
     load_digest(in + (2 * i + 1) * 8, b);
-    sha256_node(a, b, n);
+    sha256_node<true>(a, b, n);
     store_digest(up + i * 8, n);
 }
 template <bool SALT>
@@ -86,48 +68,94 @@ __global__ void copy32_kernel(const uint32_t* src, uint32_t* dst) {
     if (threadIdx.x < 8) dst[threadIdx.x] = src[threadIdx.x];
 }
 
-int merkle_enqueue(zkh_ctx* c, const gl_t* cw, size_t M, uint8_t* tree, void* scratch, uint8_t* root_dev, const uint64_t* sseed) {
+// One CTA of 2^cut threads per opened position: thread t hashes leaf t of the aligned 2^cut-leaf block around the position,
+// the block is reduced level by level in shared memory, and at every level the sibling of the position's ancestor is written out.
+template <bool SALT>
+__global__ void merkle_low_paths_kernel(const gl_t* __restrict__ cw, uint32_t cut, const uint32_t* __restrict__ pos, uint32_t pstride,
+                                        uint32_t padd, uint64_t sseed, uint8_t* out, size_t stride) {
+    __shared__ uint32_t dg[1 << MERKLE_CUT][8];
+    const uint32_t t = threadIdx.x, W = 1u << cut;
+    const size_t p = (size_t)pos[(size_t)blockIdx.x * pstride] + padd, base = p & ~(size_t)(W - 1);
+    {
+        uint32_t h[8];
+        leaf_digest<SALT>(cw[base + t], sseed, base + t, h);
+#pragma unroll
+        for (int k = 0; k < 8; k++) dg[t][k] = h[k];
+    }
+    __syncthreads();
+    uint32_t rel = (uint32_t)(p & (W - 1));
+    for (uint32_t l = 0; l < cut; l++) {
+        const uint32_t half = W >> (l + 1);
+        if (t < 8) reinterpret_cast<uint32_t*>(out + (size_t)blockIdx.x * stride + (size_t)l * 32)[t] = bswap32(dg[rel ^ 1][t]);
+        uint32_t n[8];
+        if (t < half) sha256_node<true>(dg[2 * t], dg[2 * t + 1], n);
+        __syncthreads();
+        if (t < half) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) dg[t][k] = n[k];
+        }
+        __syncthreads();
+        rel >>= 1;
+    }
+}
+
+int merkle_low_paths_enqueue(zkh_ctx* c, const gl_t* cw, uint32_t cut, const uint32_t* pos_dev, uint32_t n, const uint64_t* sseed,
+                             uint8_t* out_dev, size_t stride, uint32_t pstride, uint32_t padd) {
+    if (!cut || !n) return ZKH_OK;
+    if (cut > MERKLE_CUT) return zkh_fail(c, ZKH_ERR_ARG, "merkle: cut beyond the supported subtree size");
+    if (sseed) merkle_low_paths_kernel<true><<<n, 1u << cut, 0, c->stream>>>(cw, cut, pos_dev, pstride, padd, *sseed, out_dev, stride);
+    else merkle_low_paths_kernel<false><<<n, 1u << cut, 0, c->stream>>>(cw, cut, pos_dev, pstride, padd, 0, out_dev, stride);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+
+int merkle_enqueue(zkh_ctx* c, const gl_t* cw, size_t M, uint8_t* tree, void* scratch, uint8_t* root_dev, const uint64_t* sseed,
+                   uint32_t cut) {
     if (M < 2 || (M & (M - 1))) return zkh_fail(c, ZKH_ERR_ARG, "merkle: leaf count must be a power of two >= 2");
+    if ((cut & 1) || (cut && (M >> cut) < 4)) return zkh_fail(c, ZKH_ERR_ARG, "merkle: cut must be even and leave at least 4 nodes");
+    if ((!tree || cut) && !scratch) return zkh_fail(c, ZKH_ERR_ARG, "merkle: scratch needed for the levels that are not stored");
     cudaStream_t s = c->stream;
-    auto level_ptr = [&](size_t cnt_at_level) -> uint32_t* {  // start of the level that has cnt nodes
-        // levels are stored M, M/2, ...: offset = 2M - 2*cnt nodes
-        return (uint32_t*)(tree + (2 * M - 2 * cnt_at_level) * 32);
+    const size_t Mt = M >> cut;                                 // nodes of the lowest stored level
+    auto stored = [&](size_t cnt_at_level) -> uint32_t* {       // start of the level that has cnt nodes, or null when it is not kept
+        // levels are stored Mt, Mt/2, ...: offset = 2 Mt - 2 cnt nodes
+        return (tree && cnt_at_level <= Mt) ? (uint32_t*)(tree + (2 * Mt - 2 * cnt_at_level) * 32) : nullptr;
     };
     uint32_t* sA = (uint32_t*)scratch;
     uint32_t* sB = scratch ? (uint32_t*)((char*)scratch + merkle_scratch_a(M)) : nullptr;
+    bool flip = false;                                          // next scratch target for a level that is not stored
+    auto target = [&](size_t cnt_at_level) -> uint32_t* {       // where a level that the next kernel reads goes
+        uint32_t* t = stored(cnt_at_level);
+        if (!t) { t = flip ? sB : sA; flip = !flip; }
+        return t;
+    };
     const uint32_t* cur;  // current top level
     size_t cnt;
     if (M >= 4) {
-        uint32_t* l2 = tree ? level_ptr(M / 4) : sA;
-        uint32_t* l0 = tree ? level_ptr(M) : nullptr;
-        uint32_t* l1 = tree ? level_ptr(M / 2) : nullptr;
+        uint32_t* l2 = target(M / 4);
         const unsigned grid = (unsigned)((M / 4 + 255) / 256);
-        if (sseed) merkle_leaf4_kernel<true><<<grid, 256, 0, s>>>(cw, l0, l1, l2, M / 4, *sseed);
-        else merkle_leaf4_kernel<false><<<grid, 256, 0, s>>>(cw, l0, l1, l2, M / 4, 0);
+        if (sseed) merkle_leaf4_kernel<true><<<grid, 256, 0, s>>>(cw, stored(M), stored(M / 2), l2, M / 4, *sseed);
+        else merkle_leaf4_kernel<false><<<grid, 256, 0, s>>>(cw, stored(M), stored(M / 2), l2, M / 4, 0);
         cur = l2;
         cnt = M / 4;
     } else {
-        uint32_t* l0 = tree ? level_ptr(M) : sA;
+        uint32_t* l0 = target(M);
         if (sseed) merkle_leaf1_kernel<true><<<1, 32, 0, s>>>(cw, l0, M, *sseed);
         else merkle_leaf1_kernel<false><<<1, 32, 0, s>>>(cw, l0, M, 0);
         cur = l0;
         cnt = M;
     }
-    bool flip = true;  // next scratch target when no tree is kept
     while (cnt > 1) {
         if (cnt >= 4) {
-            uint32_t* up2 = tree ? level_ptr(cnt / 4) : (flip ? sB : sA);
-            merkle_node4_kernel<<<(unsigned)((cnt / 4 + 255) / 256), 256, 0, s>>>(
-                cur, tree ? level_ptr(cnt / 2) : nullptr, up2, cnt / 4);
+            uint32_t* up2 = target(cnt / 4);
+            merkle_node4_kernel<<<(unsigned)((cnt / 4 + 255) / 256), 256, 0, s>>>(cur, stored(cnt / 2), up2, cnt / 4);
             cur = up2;
             cnt /= 4;
         } else {
-            uint32_t* up = tree ? level_ptr(cnt / 2) : (flip ? sB : sA);
+            uint32_t* up = target(cnt / 2);
             merkle_node2_kernel<<<1, 32, 0, s>>>(cur, up, cnt / 2);
             cur = up;
             cnt /= 2;
         }
-        flip = !flip;
     }
     if (root_dev) copy32_kernel<<<1, 32, 0, s>>>(cur, (uint32_t*)root_dev);
     ZKH_CUDA(c, cudaGetLastError());

@@ -254,7 +254,7 @@ class Prover:
             v = c.numel().bit_length() - 1
             M = 1 << (v + R)
             cw = torch.empty(M, dtype=torch.int64, device=c.device)
-            tree = torch.empty(self._L.zkh_merkle_tree_bytes(M), dtype=torch.uint8, device=c.device)
+            tree = torch.empty(self._L.zkh_basefold_kept_tree_bytes(v + R), dtype=torch.uint8, device=c.device)
             self._ck(self._L.zkh_basefold_commit_keep(self._h, _ptr(c), v, R, _ptr(cw), _ptr(tree), root))
             self.__dict__.setdefault("_kept", {})[(c.data_ptr(), R)] = (c, cw, tree)
         else:
@@ -284,7 +284,7 @@ class Prover:
         if keep:
             M = 1 << (v + R)
             cw = torch.empty(M, dtype=torch.int64, device=c.device)
-            tree = torch.empty(self._L.zkh_merkle_tree_bytes(M), dtype=torch.uint8, device=c.device)
+            tree = torch.empty(self._L.zkh_basefold_kept_tree_bytes(v + R), dtype=torch.uint8, device=c.device)
         self._ck(self._L.zkh_basefold_commit_salted(self._h, _ptr(c), v, R, sseed, _ptr(cw) if keep else 0, _ptr(tree) if keep else 0, root))
         return (bytes(root), cw, tree) if keep else bytes(root)
 

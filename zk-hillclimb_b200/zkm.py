@@ -45,8 +45,9 @@ class ZkCtx:
         self.keep_bytes = keep_bytes          # HBM the prover may spend on codewords and salted trees kept for the openings
 
     def take(self, v, R):
-        """Reserve room for the codeword and the tree of a column of 2^v entries; False when the budget is spent."""
-        need = (8 + 64) << (v + R)
+        """Reserve room for the codeword and the capped tree (levels from 64 leaves per node upwards: one byte per codeword
+        element) of a column of 2^v entries; False when the budget is spent."""
+        need = (8 + (1 if v + R >= 8 else 64)) << (v + R)
         if need > self.keep_bytes:
             return False
         self.keep_bytes -= need
