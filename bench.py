@@ -1124,14 +1124,15 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
         err = repr(e)
 
     nmax = max(1, args.layer_streams)
-    out["concurrent_proofs_per_gpu"] = {"plain": nmax, "zk": 1}
-    out["concurrency_note"] = ("plain mode: each GPU runs %d layer proofs at a time, each on its own stream and library context, so "
-                               "the latency-bound rounds of one proof overlap the hashing and encoding of another; hiding mode: one "
-                               "at a time (the openings of its 2^27-entry mask streams need about 80 GB of scratch)" % nmax)
+    nzk = max(1, min(nmax, args.zk_layer_streams))
+    out["concurrent_proofs_per_gpu"] = {"plain": nmax, "zk": nzk}
+    out["concurrency_note"] = ("each GPU runs that many layer proofs at a time, each on its own stream and library context, so the "
+                               "latency-bound rounds of one proof overlap the hashing and encoding of another; a hiding-mode proof "
+                               "holds about 75 GB (columns, masks, codewords and capped trees of all its commitments), so two fit")
     prover.release_workspace()                 # the sumcheck steps' scratch is not needed any more
     streams = [torch.cuda.Stream(device=dvc) for _ in range(nmax)] if nmax > 1 else [torch.cuda.current_stream()]
     provers = [zk.Prover(local, st.cuda_stream) for st in streams] if nmax > 1 else [prover]
-    keep_zk = 80 << 30
+    keep_zk = (80 << 30) if nzk == 1 else (48 << 30)
     nthr = nmax
 
     def one_layer(pr, stream, layer, hiding, acc):
@@ -1189,22 +1190,21 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
                 th.join()
         return res["n"], res["err"]
 
-    for mode in (("plain",) if args.no_zk_layer else ("plain", "zk")):
-        hiding = mode == "zk"
-        ms, nbytes = 0.0, 0
-        nthr = 1 if hiding else nmax
+    def run_mode(hiding):
+        """One timed pass over the rank's layers with nthr workers; returns (ms, proof bytes, per-worker phase sums, error)."""
+        err_m, nbytes = err, 0
         accs = [{} for _ in range(nthr)]
-        if err is None:
+        if err_m is None:
             for pr in provers:
                 pr.keep_trees = not hiding              # plain mode: codewords and trees stay in HBM for the openings
             # warm-up: one layer per worker, one after the other (table uploads, workspace growth, kernel set-up)
             for tid in range(nthr):
-                if err is None:
+                if err_m is None:
                     try:
                         with torch.cuda.stream(streams[tid]):
                             nbytes = one_layer(provers[tid], streams[tid], rank, hiding, {})
                     except Exception as e:      # noqa: BLE001
-                        err = "%s pass, warm-up: %r" % (mode, e)
+                        err_m = "warm-up: %r" % (e,)
             if hiding:
                 torch.cuda.empty_cache()
         if world > 1:
@@ -1212,10 +1212,10 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        if err is None:
+        if err_m is None:
             nbytes, werr = run_layers(list(range(rank, nlayers, world)), hiding, accs)
             if werr:
-                err = "%s pass: %s" % (mode, werr)
+                err_m = werr
         torch.cuda.synchronize()
         e1.record()
         torch.cuda.synchronize()
@@ -1225,13 +1225,27 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
             pr.release_kept()
             pr.release_workspace()
         torch.cuda.empty_cache()
-        bad = 1.0 if err is not None else 0.0
+        bad = 1.0 if err_m is not None else 0.0
         if world > 1:
             t = torch.tensor([ms, bad], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms, bad = float(t[0].item()), float(t[1].item())
-        if bad:
-            out[mode] = {"error": err or "another rank failed"}
+        if bad and err_m is None:
+            err_m = "another rank failed"
+        return ms, nbytes, accs, err_m
+
+    for mode in (("plain",) if args.no_zk_layer else ("plain", "zk")):
+        hiding = mode == "zk"
+        nthr = nzk if hiding else nmax
+        ms, nbytes, accs, merr = run_mode(hiding)
+        if merr is not None and hiding and nthr > 1 and err is None:
+            # two hiding-mode proofs did not fit beside each other on this GPU: one at a time, with the whole keep budget
+            out["concurrent_proofs_per_gpu"]["zk"] = 1
+            out["zk_two_in_flight_error"] = merr[:300]
+            nthr, keep_zk = 1, 80 << 30
+            ms, nbytes, accs, merr = run_mode(hiding)
+        if merr is not None:
+            out[mode] = {"error": "%s pass: %s" % (mode, merr)}
             break
         n = max(sum(a.get("n", 0) for a in accs), 1)
         out[mode] = {"total_s": ms / 1e3, "s_per_layer": ms / 1e3 / nlayers, "layers_per_s": nlayers / (ms / 1e3),
@@ -1329,6 +1343,7 @@ def main():
     ap.add_argument("--parity-logn", type=int, default=18, help="N>1: per-rank size of the sharded proof checked against the CPU checker")
     ap.add_argument("--no-zk-layer", action="store_true", help="skip the hiding-mode pass of the 22-layer figure")
     ap.add_argument("--layer-streams", type=int, default=2, help="layer proofs in flight per GPU (threads, one stream and context each)")
+    ap.add_argument("--zk-layer-streams", type=int, default=2, help="the same for the hiding-mode pass (about 75 GB of HBM per proof in flight)")
     ap.add_argument("--no-ref-layer", action="store_true", help="skip timing the reference's own layer prover at N=1")
     ap.add_argument("--cpu-logn", type=int, default=26, help="sample size of the cpu_baseline leg")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's CUDA prover")

@@ -424,6 +424,15 @@ ZKH_API int zkh_ig_softmax_witness(zkh_ctx* ctx, const uint64_t* z_dev, const ui
 ZKH_API int zkh_gl_mul(zkh_ctx* ctx, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev);
 /* out[i] = s*in[i].  Stream-ordered. */
 ZKH_API int zkh_gl_scale(zkh_ctx* ctx, const uint64_t* in_dev, uint64_t n, uint64_t s, uint64_t* out_dev);
+/* Operand views as maps on index bits (p3imm::op_off / y_off, zkllm-src/p3_int_gadgets.cuh:448-470, and the broadcast
+ * columns of the hiding mode): idx(u) = konst | OR over the set bits b < nbits of u of masks[b]  (nbits <= 32, n <= 2^nbits).
+ * gather: out[u] = col[idx(u)] for u < n (every idx must lie below col_len, else ZKH_ERR_DOMAIN and nothing runs);
+ * scatter: out[idx(u)] = vals[u] (idx below out_len; the map must be injective, other entries of out keep their value).
+ * Stream-ordered. */
+ZKH_API int zkh_gl_gather_bits(zkh_ctx* ctx, const uint64_t* col_dev, uint64_t col_len, uint64_t n, uint64_t konst,
+                               const uint64_t* masks, uint32_t nbits, uint64_t* out_dev);
+ZKH_API int zkh_gl_scatter_bits(zkh_ctx* ctx, const uint64_t* vals_dev, uint64_t n, uint64_t konst, const uint64_t* masks,
+                                uint32_t nbits, uint64_t* out_dev, uint64_t out_len);
 /* Rescale witness (zkllm-src/p3_int_gadgets.cuh:230-275 p3irs::gen_witness): for each signed acc value
  * y = floor((acc + 2^(sf-1)) / 2^sf), remainder limbs L0 (16 bits), L1 (sf > 16 only), and the lookup row
  * indices of the limbs and of y in its window (rng 1: [-2^19,2^19), rng 2: [-2^15,2^15), rng 0: none).

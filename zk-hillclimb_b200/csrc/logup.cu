@@ -386,6 +386,52 @@ extern "C" int zkh_gl_scale(zkh_ctx* c, const uint64_t* in_dev, uint64_t n, uint
     return ZKH_OK;
 }
 
+// ---------------------------------------------------------------- operand views as bit maps
+// The operand views of the per-head matmuls (p3imm::op_off / y_off, zkllm-src/p3_int_gadgets.cuh:448-470) and the broadcast
+// columns of the hiding mode address a committed grid through a map on index BITS: element index = c | OR over the set
+// bits b of u of m[b].  One kernel gathers (out[u] = col[idx(u)]) or scatters (out[idx(u)] = vals[u]) through such a map.
+struct BitMap { uint64_t c; uint64_t m[32]; uint32_t nb; };
+template <bool SCATTER>
+__global__ void bitmap_move_kernel(const gl_t* __restrict__ src, size_t n, BitMap bm, gl_t* __restrict__ dst) {
+    for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < n; u += (size_t)gridDim.x * blockDim.x) {
+        uint64_t idx = bm.c;
+        for (uint32_t b = 0; b < bm.nb; b++)
+            if ((u >> b) & 1) idx |= bm.m[b];
+        if (SCATTER) dst[idx] = src[u];
+        else dst[u] = src[idx];
+    }
+}
+static int bitmap_move(zkh_ctx* c, bool scatter, const uint64_t* src, uint64_t n, uint64_t konst, const uint64_t* masks, uint32_t nbits,
+                       uint64_t other_len, uint64_t* dst, const char* what) {
+    if (!c || !src || !dst || (nbits && !masks)) return zkh_fail(c, ZKH_ERR_ARG, what);
+    if (nbits > 32 || (nbits < 64 && n > ((uint64_t)1 << nbits))) return zkh_fail(c, ZKH_ERR_ARG, "bit map: n beyond 2^nbits, or more than 32 index bits");
+    BitMap bm;
+    bm.c = konst;
+    bm.nb = nbits;
+    uint64_t top = konst;
+    for (uint32_t b = 0; b < 32; b++) {
+        bm.m[b] = b < nbits ? masks[b] : 0;
+        top |= bm.m[b];
+    }
+    if (top >= other_len) return zkh_fail(c, ZKH_ERR_DOMAIN, "bit map: an index reaches beyond the addressed column");
+    if (!n) return ZKH_OK;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 16;
+    const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+    if (scatter) bitmap_move_kernel<true><<<grid, 256, 0, c->stream>>>(src, (size_t)n, bm, dst);
+    else bitmap_move_kernel<false><<<grid, 256, 0, c->stream>>>(src, (size_t)n, bm, dst);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+extern "C" int zkh_gl_gather_bits(zkh_ctx* c, const uint64_t* col_dev, uint64_t col_len, uint64_t n, uint64_t konst, const uint64_t* masks,
+                                  uint32_t nbits, uint64_t* out_dev) {
+    return bitmap_move(c, false, col_dev, n, konst, masks, nbits, col_len, out_dev, "gather_bits: null pointer");
+}
+extern "C" int zkh_gl_scatter_bits(zkh_ctx* c, const uint64_t* vals_dev, uint64_t n, uint64_t konst, const uint64_t* masks, uint32_t nbits,
+                                   uint64_t* out_dev, uint64_t out_len) {
+    return bitmap_move(c, true, vals_dev, n, konst, masks, nbits, out_len, out_dev, "scatter_bits: null pointer");
+}
+
 // ---------------------------------------------------------------- rescale witness
 // y = floor((acc + 2^(sf-1)) / 2^sf) on the signed value of acc, rem = acc + 2^(sf-1) - y*2^sf split into
 // 16-bit limbs, plus the lookup row indices of the limbs and of y in its signed window

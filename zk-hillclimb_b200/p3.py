@@ -510,10 +510,37 @@ class Prover:
         import torch
         return col[torch.from_numpy(np.ascontiguousarray(idx, dtype=np.int64)).to(col.device)].contiguous()
 
+    @staticmethod
+    def _bit_map(fn, n):
+        """(konst, masks) when the index map fn is a map on index bits -- fn(u) = konst | OR over the set bits b of u of
+        masks[b], which every operand view and broadcast pattern is -- else None.  One evaluation of fn on a small host
+        array: zero, the powers of two, and 192 seeded samples that check the model."""
+        nb = max(1, (int(n) - 1).bit_length())
+        if nb > 32:
+            return None
+        rng = np.random.default_rng(nb)
+        samples = rng.integers(0, n, 192, dtype=np.int64)
+        probe = np.concatenate([np.zeros(1, dtype=np.int64), np.int64(1) << np.arange(nb, dtype=np.int64), samples])
+        r = np.asarray(fn(probe), dtype=np.int64) + np.zeros_like(probe)
+        konst = int(r[0])
+        masks = np.ascontiguousarray(r[1:1 + nb], dtype=np.int64)
+        model = np.full(192, konst, dtype=np.int64)
+        for b in range(nb):
+            model |= np.where((samples >> b) & 1, masks[b], 0)
+        if (r[1:1 + nb] & konst != konst).any() or not (model == r[1 + nb:]).all():
+            return None
+        return konst, masks.view(np.uint64), nb
+
     def gather_fn(self, col, n, fn):
-        """out[u] = col[fn(u)] for u < n, the index map written with integer operators (&, |, <<, >>) and evaluated on the
-        device: broadcast columns of the hiding mode's product domains."""
+        """out[u] = col[fn(u)] for u < n, the index map written with integer operators (&, |, <<, >>): broadcast columns and
+        operand views of the hiding mode's product domains.  Maps on index bits run as one kernel (zkh_gl_gather_bits);
+        anything else is evaluated with tensor operations on the device."""
         import torch
+        bm = self._bit_map(fn, n)
+        if bm is not None:
+            out = torch.empty(n, dtype=torch.int64, device=col.device)
+            self._ck(self._L.zkh_gl_gather_bits(self._h, _ptr(col), col.numel(), n, bm[0], bm[1].ctypes.data, bm[2], _ptr(out)))
+            return out
         u = torch.arange(n, dtype=torch.int64, device=col.device)
         return col[fn(u)].contiguous()
 
@@ -521,8 +548,12 @@ class Prover:
         return col[lo:lo + n]
 
     def scatter_fn(self, col, n, fn, vals):
-        """col[fn(u)] = vals[u] for u < n (distinct targets), the index map evaluated on the device; returns col."""
+        """col[fn(u)] = vals[u] for u < n (distinct targets); returns col.  Maps on index bits run as one kernel."""
         import torch
+        bm = self._bit_map(fn, n)
+        if bm is not None and vals.numel() == n:
+            self._ck(self._L.zkh_gl_scatter_bits(self._h, _ptr(vals), n, bm[0], bm[1].ctypes.data, bm[2], _ptr(col), col.numel()))
+            return col
         u = torch.arange(n, dtype=torch.int64, device=col.device)
         col[fn(u)] = vals
         return col
