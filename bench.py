@@ -1197,16 +1197,15 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
         if err_m is None:
             for pr in provers:
                 pr.keep_trees = not hiding              # plain mode: codewords and trees stay in HBM for the openings
-            # warm-up: one layer per worker, one after the other (table uploads, workspace growth, kernel set-up)
-            for tid in range(nthr):
-                if err_m is None:
-                    try:
-                        with torch.cuda.stream(streams[tid]):
-                            nbytes = one_layer(provers[tid], streams[tid], rank, hiding, {})
-                    except Exception as e:      # noqa: BLE001
-                        err_m = "warm-up: %r" % (e,)
-            if hiding:
-                torch.cuda.empty_cache()
+            # warm-up: one layer per worker, all workers at once as in the timed pass, so that table uploads, workspace growth
+            # and the allocator's pool for BOTH working sets happen here (with peer access enabled at N > 1 a cudaMalloc maps
+            # into every peer and costs milliseconds; a timed pass that had to allocate ran 2.7x longer at N = 8)
+            try:
+                nbytes, werr = run_layers([rank] * nthr, hiding, [{} for _ in range(nthr)])
+                if werr:
+                    err_m = "warm-up: %s" % werr
+            except Exception as e:      # noqa: BLE001
+                err_m = "warm-up: %r" % (e,)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -1226,24 +1225,27 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
             pr.release_workspace()
         torch.cuda.empty_cache()
         bad = 1.0 if err_m is not None else 0.0
+        per_rank = [ms / 1e3]
         if world > 1:
             t = torch.tensor([ms, bad], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms, bad = float(t[0].item()), float(t[1].item())
+            got = [torch.zeros_like(t) for _ in range(world)]
+            dist.all_gather(got, t)
+            per_rank = [float(g[0].item()) / 1e3 for g in got]
+            ms, bad = max(per_rank) * 1e3, max(float(g[1].item()) for g in got)
         if bad and err_m is None:
             err_m = "another rank failed"
-        return ms, nbytes, accs, err_m
+        return ms, nbytes, accs, err_m, per_rank
 
     for mode in (("plain",) if args.no_zk_layer else ("plain", "zk")):
         hiding = mode == "zk"
         nthr = nzk if hiding else nmax
-        ms, nbytes, accs, merr = run_mode(hiding)
+        ms, nbytes, accs, merr, per_rank = run_mode(hiding)
         if merr is not None and hiding and nthr > 1 and err is None:
             # two hiding-mode proofs did not fit beside each other on this GPU: one at a time, with the whole keep budget
             out["concurrent_proofs_per_gpu"]["zk"] = 1
             out["zk_two_in_flight_error"] = merr[:300]
             nthr, keep_zk = 1, 80 << 30
-            ms, nbytes, accs, merr = run_mode(hiding)
+            ms, nbytes, accs, merr, per_rank = run_mode(hiding)
         if merr is not None:
             out[mode] = {"error": "%s pass: %s" % (mode, merr)}
             break
@@ -1252,7 +1254,7 @@ def layer_figure(args, zk, prover, world, rank, local, dist):
                      "rank0_mean_per_layer": {k: sum(a.get(k, 0.0) for a in accs) / n for k in ("witness_s", "commit_s", "prove_s")},
                      "rank0_mean_note": "wall time of each phase inside its own worker; with concurrent proofs the phases of "
                                         "different layers overlap, so their sum exceeds s_per_layer",
-                     "proof_MB": nbytes / 1048576.0}
+                     "proof_MB": nbytes / 1048576.0, "per_rank_s": per_rank}
     if "plain" in out and "s_per_layer" in out["plain"]:
         out["s_per_layer"] = out["plain"]["s_per_layer"]
         out["layers_per_s"] = out["plain"]["layers_per_s"]

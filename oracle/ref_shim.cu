@@ -1610,6 +1610,15 @@ int ref_irs_witness(const uint64_t* acc, uint32_t le, uint32_t sf, int rng, uint
 // =====================================================================
 // GPU entry points: the reference's own CUDA paths (need a GPU).
 // =====================================================================
+// how many sumchecks the reference's gadget code sent through libzkh (only in the build that force-includes
+// include/p3_scgpu_zkh.cuh; -1 in the plain build)
+long long ref_zkh_sumcheck_calls() {
+#ifdef sc_prove_gpu
+    return (long long)p3sg::zkh_shim_calls().load();
+#else
+    return -1;
+#endif
+}
 int ref_gpu_available() {
     int n = 0;
     return cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
