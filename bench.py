@@ -1344,7 +1344,7 @@ def main():
     ap.add_argument("--ref-budget-s", type=float, default=150.0, help="time budget of the CPU reference arm's calls")
     ap.add_argument("--parity-logn", type=int, default=18, help="N>1: per-rank size of the sharded proof checked against the CPU checker")
     ap.add_argument("--no-zk-layer", action="store_true", help="skip the hiding-mode pass of the 22-layer figure")
-    ap.add_argument("--layer-streams", type=int, default=2, help="layer proofs in flight per GPU (threads, one stream and context each)")
+    ap.add_argument("--layer-streams", type=int, default=4, help="layer proofs in flight per GPU (threads, one stream and context each)")
     ap.add_argument("--zk-layer-streams", type=int, default=2, help="the same for the hiding-mode pass (about 75 GB of HBM per proof in flight)")
     ap.add_argument("--no-ref-layer", action="store_true", help="skip timing the reference's own layer prover at N=1")
     ap.add_argument("--cpu-logn", type=int, default=26, help="sample size of the cpu_baseline leg")

@@ -30,6 +30,22 @@ def test_static_entry_point_matches_regular_one(orc, zk, prover):
         del c_dev
 
 
+def test_static_entry_point_takes_no_device_memory(orc, zk):
+    """After its first call on the device, a call leaves the driver's free-memory figure where it was."""
+    import torch
+    y_dev = torch.zeros(1, dtype=torch.int64, device="cuda:0")
+    z, s = orc.lcg(16, 77)
+    c_dev = zk.p3.to_device(orc.lcg(1 << 16, s)[0])
+    stream = torch.cuda.current_stream().cuda_stream
+    zk.p3.eval_h_static(c_dev, z, y_dev, stream)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        zk.p3.eval_h_static(c_dev, z, y_dev, stream)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+
+
 def test_static_entry_point_rejects_oversize(zk):
     import torch
     y_dev = torch.zeros(1, dtype=torch.int64, device="cuda:0")

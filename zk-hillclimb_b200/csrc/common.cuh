@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 #include <atomic>
+#include <mutex>
 #include <string>
 #include "gl.cuh"
 #include "sha256.cuh"
@@ -106,10 +107,22 @@ static inline int zkh_fail(zkh_ctx* c, int code, const std::string& msg) {
     } while (0)
 
 // Function attributes (the dynamic shared-memory limit) belong to a device, not to the process: one bit per device
-// ordinal records where a kernel's one-time set-up has run.  True exactly once per (guard, device).
-static inline bool zkh_first_on_device(std::atomic<uint64_t>& done, int device) {
+// ordinal records where a kernel's one-time set-up has run.  The set-up runs exactly once per (guard, device), and a
+// thread that arrives while another is still inside it waits: several library contexts of one process (one per host
+// thread) may make their first launch of a kernel at the same moment, and a launch that overtook the attribute
+// call was refused as "invalid argument".
+struct ZkhOncePerDevice {
+    std::mutex m;
+    uint64_t done = 0;
+};
+template <class F>
+static inline void zkh_once_on_device(ZkhOncePerDevice& g, int device, F&& setup) {
+    std::lock_guard<std::mutex> lk(g.m);
     const uint64_t bit = 1ull << (device & 63);
-    return !(done.fetch_or(bit) & bit);
+    if (!(g.done & bit)) {
+        setup();
+        g.done |= bit;
+    }
 }
 
 // make the workspace at least `bytes` large (contents are not preserved)

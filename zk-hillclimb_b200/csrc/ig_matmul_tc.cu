@@ -259,9 +259,8 @@ int ig_matmul_tc(zkh_ctx* c, const gl_t* A, const long long sa[4], const gl_t* B
     ZKH_CUDA(c, cudaMemcpyAsync(&c->h_ctl->err, flags, 4, cudaMemcpyDeviceToHost, s));
     ZKH_CUDA(c, cudaStreamSynchronize(s));
     if (c->h_ctl->err & 1u) return 1;             // an operand outside (-2^20, 2^20): three 7-bit limbs do not hold it
-    static std::atomic<uint64_t> attr{0};
-    if (zkh_first_on_device(attr, c->device))
-        cudaFuncSetAttribute(ig_matmul_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+    static ZkhOncePerDevice attr;
+    zkh_once_on_device(attr, c->device, [] { cudaFuncSetAttribute(ig_matmul_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES); });
     static_assert(TC_STAGES * TC_STAGE_BYTES <= TC_SMEM_BYTES && 2 * TC_SMEM_BYTES > 227 * 1024, "one CTA per SM");
     ig_matmul_tc_kernel<<<dim3(K / TC_BN, I / TC_BM, (unsigned)nb), 128, TC_SMEM_BYTES, s>>>(
         Al, Bl, planeA, planeB, Cc, vc, nb1, I, J, K, flags);

@@ -179,20 +179,19 @@ extern "C" int zkh_histogram(zkh_ctx* c, const uint32_t* idx_dev, uint64_t n, ui
     ZKH_CUDA(c, cudaMemsetAsync(oob, 0, 4, c->stream));
     if (n) {
         if (M <= (1u << 15)) {
-            static std::atomic<uint64_t> attr{0};
-            if (zkh_first_on_device(attr, c->device))
-                cudaFuncSetAttribute(hist_shared_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+            static ZkhOncePerDevice attr;
+            zkh_once_on_device(attr, c->device, [] { cudaFuncSetAttribute(hist_shared_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024); });
             size_t blocks = (n + 512 * 64 - 1) / (512 * 64), cap = (size_t)c->sm_count;
             if (blocks < 1) blocks = 1;
             hist_shared_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 512, (size_t)M * 4, c->stream>>>(
                 idx_dev, (size_t)n, M, (unsigned long long*)cnt_dev, oob);
         } else if (M <= (1u << 18) && ((uintptr_t)idx_dev & 15) == 0) {
-            static std::atomic<uint64_t> attr{0};
-            if (zkh_first_on_device(attr, c->device)) {
+            static ZkhOncePerDevice attr;
+            zkh_once_on_device(attr, c->device, [] {
                 cudaFuncSetAttribute(hist_window_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
                 cudaFuncSetAttribute(hist_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
                 cudaFuncSetAttribute(hist_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
-            }
+            });
             const unsigned windows = (M + (1u << 15) - 1) >> 15;
             unsigned csize = 1;
             while (csize < windows) csize <<= 1;

@@ -312,13 +312,13 @@ int ntt_enqueue(zkh_ctx* c, const gl_t* in, uint64_t nin, gl_t* out, uint32_t lo
     if (p.np > 4) return zkh_fail(c, ZKH_ERR_LIMIT, "ntt: more than four digits");
     for (uint32_t i = 0; i < p.np; i++) p.ws[i] = logM / p.np + (i < logM % p.np ? 1 : 0);
     ZKH_TRY(ntt_tables(c, logM, inverse, &p.tw_lo, &p.tw_hi, &p.tw_lb));
-    static std::atomic<uint64_t> attr_set{0};
-    if (zkh_first_on_device(attr_set, c->device)) {
+    static ZkhOncePerDevice attr_set;
+    zkh_once_on_device(attr_set, c->device, [] {
         cudaFuncSetAttribute(ntt_pass_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
         cudaFuncSetAttribute(ntt_pass_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
         cudaFuncSetAttribute(ntt_pass_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
         cudaFuncSetAttribute(ntt_pass_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
-    }
+    });
     gl_t* tmp = (gl_t*)scratch;
     uint32_t pos_hi = logM;
     const gl_t* src = in;

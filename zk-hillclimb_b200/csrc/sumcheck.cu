@@ -349,23 +349,23 @@ static int sc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, cons
     memset(&P, 0, sizeof P);
     for (int k = 0; k < nsrc; k++) P.in[k] = in[k];
 
-    static int occ_first = 0, occ_fused = 0, occ_fused_plain = 0;
-    if (!occ_first) {
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_first, sc_first_kernel<F, NT, LD>, 256, 0);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_fused, sc_fused_kernel<F, NT, LD>, 256, 0);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_fused_plain,
-                                                      sc_fused_kernel<F, NT, LD_PLAIN>, 256, 0);
-        if (occ_first < 1) occ_first = 1;
-        if (occ_fused < 1) occ_fused = 1;
-        if (occ_fused_plain < 1) occ_fused_plain = 1;
-    }
-    static std::atomic<uint64_t> attr_set{0};
-    if (zkh_first_on_device(attr_set, ctx->device)) {   // per device: the limit is a property of the device's function
-        cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             NC * (1 << SC_TAIL_LOG) * 8);
-        cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, NC * (1 << SC_TAIL_LOG) * 8);
-    }
+    struct Occ { int first, fused, fused_plain; };
+    static const Occ occ = [] {                          // initialised once, by one thread (others wait)
+        Occ o{0, 0, 0};
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o.first, sc_first_kernel<F, NT, LD>, 256, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o.fused, sc_fused_kernel<F, NT, LD>, 256, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o.fused_plain, sc_fused_kernel<F, NT, LD_PLAIN>, 256, 0);
+        if (o.first < 1) o.first = 1;
+        if (o.fused < 1) o.fused = 1;
+        if (o.fused_plain < 1) o.fused_plain = 1;
+        return o;
+    }();
+    const int occ_first = occ.first, occ_fused = occ.fused, occ_fused_plain = occ.fused_plain;
+    static ZkhOncePerDevice attr_set;                    // per device: the limit is a property of the device's function
+    zkh_once_on_device(attr_set, ctx->device, [] {
+        cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD>, cudaFuncAttributeMaxDynamicSharedMemorySize, NC * (1 << SC_TAIL_LOG) * 8);
+        cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, NC * (1 << SC_TAIL_LOG) * 8);
+    });
     auto grid_for = [&](size_t items, int occ) {
         size_t want = (items + 255) / 256, cap = (size_t)ctx->sm_count * occ;
         if (cap > ctx->partials_cap / 5) cap = ctx->partials_cap / 5;
@@ -477,8 +477,10 @@ static int sc_tail_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t n, int nround
     ScPtrs P;
     memset(&P, 0, sizeof P);
     for (int k = 0; k < NC; k++) P.in[k] = in[k];
-    cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         NC * (1 << SC_TAIL_LOG) * 8);
+    static ZkhOncePerDevice attr;
+    zkh_once_on_device(attr, ctx->device, [] {
+        cudaFuncSetAttribute(sc_tail_kernel<F, NT, LD_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, NC * (1 << SC_TAIL_LOG) * 8);
+    });
     size_t held = pending ? n / 2 : n;
     if (resid > 0 && held < ((size_t)1 << resid)) held = (size_t)1 << resid;   // room for the G-element residual columns
     sc_tail_kernel<F, NT, LD_PLAIN><<<1, 1024, (size_t)NC * held * 8, ctx->stream>>>(P, n, pending, ctx->d_ctl, chal_prev,

@@ -100,11 +100,11 @@ static int scw_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, con
     cudaStream_t s = ctx->stream;
     ZkhCtl* ctl = ctx->d_ctl;
     const size_t n = (size_t)1 << logn;
-    static int occ = 0;
-    if (!occ) {
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, scw_round_kernel<F>, SCW_THREADS, 0);
-        if (occ < 1) occ = 1;
-    }
+    static const int occ = [] {
+        int o = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, scw_round_kernel<F>, SCW_THREADS, 0);
+        return o < 1 ? 1 : o;
+    }();
     auto grid_for = [&](size_t items) {
         size_t want = (items + SCW_THREADS - 1) / SCW_THREADS, cap = (size_t)ctx->sm_count * occ;
         if (cap > ctx->partials_cap / SCW_NT) cap = ctx->partials_cap / SCW_NT;
@@ -216,11 +216,11 @@ static int zc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t lo
     cudaStream_t s = ctx->stream;
     ZkhCtl* ctl = ctx->d_ctl;
     const size_t n = (size_t)1 << logn;
-    static int occ = 0;
-    if (!occ) {
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, zc_round_kernel<NCMAX>, SCW_THREADS, 0);
-        if (occ < 1) occ = 1;
-    }
+    static const int occ = [] {
+        int o = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, zc_round_kernel<NCMAX>, SCW_THREADS, 0);
+        return o < 1 ? 1 : o;
+    }();
     auto grid_for = [&](size_t items) {
         size_t want = (items + SCW_THREADS - 1) / SCW_THREADS, cap = (size_t)ctx->sm_count * occ;
         if (cap > ctx->partials_cap / SCW_NT) cap = ctx->partials_cap / SCW_NT;
@@ -253,68 +253,81 @@ static int zc_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t lo
 
 // Large programs (more than 32 columns or 120 terms: the bf16 gadgets of the fp8 transformer layer, whose constraint
 // systems span 60..200 columns and several hundred monomials; the reference runs them through its host loop sc5_prove,
-// zkllm-src/p3_bfadd.cuh:214-330 and siblings).  Same summand shape; the program and the current value of every column
-// live in dynamic shared memory ([column][thread], conflict-free), the column pointers of the round in global memory.
-// The kernel is bound by the field multiplications of the monomials, not by memory: what matters is how many warps an SM
-// holds, so a thread keeps one word per column and re-reads the pair behind it (from cache) for each evaluation point.
+// zkllm-src/p3_bfadd.cuh:214-330 and siblings).  Same summand shape.  The kernel is bound by the field multiplications of
+// the monomials, not by memory, so what matters is how many warps an SM holds: a ROW (pair of every column) is shared by
+// L adjacent lanes of a warp.  Each lane loads (and binds, and stores) the columns k = sub, sub + L, ... of its row into the
+// block's shared memory as value and difference, and evaluates the monomials j = sub, sub + L, ...; the summand is linear
+// in the inner sum, so a lane simply adds col0 * (its partial sum) to its own running round sums and the block reduction
+// at the end adds the lanes up.  The rows of a warp are produced and consumed by that warp alone: __syncwarp suffices.
+// Shared memory per block: 2 * nc * (T / L + 1) words, 16..24 KB, so 9 or more blocks of 128 threads share an SM
+// (one block at 204 KB with a column set per thread).
 constexpr int ZCX_MAXTERMS = 2048;
 constexpr int ZCX_MAXC = 224;
 struct ZcxHdr { uint32_t nterms, nc; gl_t konst; };
 
 __global__ void zcx_round_kernel(const uint8_t* prog_g, const gl_t* const* in, gl_t* const* out, size_t items, int first,
-                                 ZkhCtl* ctl, gl_t* partials, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out, ZkhTag tag) {
+                                 uint32_t L, ZkhCtl* ctl, gl_t* partials, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out,
+                                 ZkhTag tag) {
     extern __shared__ __align__(16) uint8_t smem[];
     const ZcxHdr hdr = *reinterpret_cast<const ZcxHdr*>(prog_g);
     const uint32_t nc = hdr.nc, nterms = hdr.nterms, T = blockDim.x, tid = threadIdx.x;
+    const uint32_t R = T / L, RP = R + 1;      // rows per block pass; padded row stride of the value tables
+    const uint32_t r = tid / L, sub = tid % L;
     gl_t* coef = reinterpret_cast<gl_t*>(smem);
-    gl_t* cur = coef + nterms;                 // [nc][T]: the columns' values at the current evaluation point
-    gl_t* sh = cur + (size_t)nc * T;           // SCW_NT * 32
+    gl_t* cur = coef + nterms;                 // [nc][RP]: the columns' values at the current evaluation point
+    gl_t* dif = cur + (size_t)nc * RP;         // [nc][RP]: hi - lo
+    gl_t* sh = dif + (size_t)nc * RP;          // SCW_NT * 32
     uint32_t* packed = reinterpret_cast<uint32_t*>(sh + SCW_NT * 32);
     const gl_t* coef_g = reinterpret_cast<const gl_t*>(prog_g + sizeof(ZcxHdr));
     const uint32_t* packed_g = reinterpret_cast<const uint32_t*>(coef_g + nterms);
     for (uint32_t j = tid; j < nterms; j += T) { coef[j] = coef_g[j]; packed[j] = packed_g[j]; }
     __syncthreads();
     const gl_t a = first ? 0 : *chal_prev;
+    const gl_t konst = sub == 0 ? hdr.konst : 0;
     gl_t s[SCW_NT];
 #pragma unroll
     for (int t = 0; t < SCW_NT; t++) s[t] = 0;
-    const size_t stride = (size_t)gridDim.x * T;
-    for (size_t i = (size_t)blockIdx.x * T + tid; i < items; i += stride) {
-        // Only the current values live in shared memory (one word per column and thread, so that several blocks fit an SM);
-        // the pair (lo, hi) of a column is read again for every evaluation point: from the input in the first round, from
-        // the bound pair this thread has just written otherwise.  The reads hit L1 / L2: DRAM traffic stays one pass.
-        for (uint32_t k = 0; k < nc; k++) {
-            gl_t lo;
-            if (first) {
-                lo = in[k][2 * i];
-            } else {
-                const gl_t* src = in[k];
-                ulonglong2 u = ld2(src + 4 * i), w = ld2(src + 4 * i + 2);
-                lo = gl_lerp(u.x, u.y, a);
-                st2(out[k] + 2 * i, lo, gl_lerp(w.x, w.y, a));
+    const size_t stride = (size_t)gridDim.x * R;
+    for (size_t base = (size_t)blockIdx.x * R; base < items; base += stride) {
+        const size_t i = base + r;
+        const bool live = i < items;
+        for (uint32_t k = sub; k < nc; k += L) {
+            gl_t lo = 0, hi = 0;
+            if (live) {
+                if (first) {
+                    ulonglong2 v = ld2(in[k] + 2 * i);
+                    lo = v.x;
+                    hi = v.y;
+                } else {
+                    const gl_t* src = in[k];
+                    ulonglong2 u = ld2(src + 4 * i), w = ld2(src + 4 * i + 2);
+                    lo = gl_lerp(u.x, u.y, a);
+                    hi = gl_lerp(w.x, w.y, a);
+                    st2(out[k] + 2 * i, lo, hi);
+                }
             }
-            cur[(size_t)k * T + tid] = lo;
+            cur[(size_t)k * RP + r] = lo;
+            dif[(size_t)k * RP + r] = gl_sub(hi, lo);
         }
+        __syncwarp();
 #pragma unroll 1
         for (int t = 0; t < SCW_NT; t++) {
             Acc192 acc, accf;
             acc.clear();
             accf.clear();
-            for (uint32_t j = 0; j < nterms; j++) {
+            for (uint32_t j = sub; j < nterms; j += L) {
                 const uint32_t pk = packed[j];
-                gl_t x = cur[(size_t)((pk >> 8) & 0xff) * T + tid];
-                if ((pk & 0x7f) >= 2) x = gl_mul(x, cur[(size_t)((pk >> 16) & 0xff) * T + tid]);
-                if ((pk & 0x7f) >= 3) x = gl_mul(x, cur[(size_t)((pk >> 24) & 0xff) * T + tid]);
+                gl_t x = cur[(size_t)((pk >> 8) & 0xff) * RP + r];
+                if ((pk & 0x7f) >= 2) x = gl_mul(x, cur[(size_t)((pk >> 16) & 0xff) * RP + r]);
+                if ((pk & 0x7f) >= 3) x = gl_mul(x, cur[(size_t)((pk >> 24) & 0xff) * RP + r]);
                 if (pk & 0x80) accf.add_prod(coef[j], x);
                 else acc.add_prod(coef[j], x);
             }
-            s[t] = gl_add(s[t], gl_add(gl_mul(cur[tid], gl_add(acc.reduce(), hdr.konst)), accf.reduce()));
+            if (live) s[t] = gl_add(s[t], gl_add(gl_mul(cur[r], gl_add(acc.reduce(), konst)), accf.reduce()));
+            __syncwarp();                      // every lane of the row has read the values of this point
             if (t + 1 < SCW_NT)
-                for (uint32_t k = 0; k < nc; k++) {
-                    const gl_t* pr = first ? in[k] : out[k];
-                    ulonglong2 v = ld2(pr + 2 * i);
-                    cur[(size_t)k * T + tid] = gl_add(cur[(size_t)k * T + tid], gl_sub(v.y, v.x));
-                }
+                for (uint32_t k = sub; k < nc; k += L) cur[(size_t)k * RP + r] = gl_add(cur[(size_t)k * RP + r], dif[(size_t)k * RP + r]);
+            __syncwarp();
         }
     }
     grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, ctl->par[6] ? 3 : 0);
@@ -324,8 +337,8 @@ __global__ void zcx_finals_kernel(const gl_t* const* in, int nc, const gl_t* cha
     for (int k = threadIdx.x; k < nc; k += blockDim.x) out[k] = gl_lerp(in[k][0], in[k][1], *chal);
 }
 
-static size_t zcx_smem_bytes(int nc, uint32_t nterms, int T) {
-    return (size_t)nterms * 8 + (size_t)nc * T * 8 + SCW_NT * 32 * 8 + (size_t)nterms * 4 + 16;
+static size_t zcx_smem_bytes(int nc, uint32_t nterms, int T, int L) {
+    return (size_t)nterms * 8 + (size_t)2 * nc * (T / L + 1) * 8 + SCW_NT * 32 * 8 + (size_t)nterms * 4 + 16;
 }
 
 // prog_dev: ZcxHdr | coef | packed (already uploaded); ptr_dev: room for logn * 2 * nc pointers
@@ -334,17 +347,25 @@ static int zcx_enqueue(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t nte
     cudaStream_t s = ctx->stream;
     ZkhCtl* ctl = ctx->d_ctl;
     const size_t n = (size_t)1 << logn;
-    // 128 threads per block; fewer only when one block would not fit.  Several blocks share an SM (occupancy query below).
-    int T = 128;
-    while (T > 32 && zcx_smem_bytes(nc, nterms, T) > 200 * 1024) T >>= 1;
-    const size_t smem = zcx_smem_bytes(nc, nterms, T);
+    // 128 threads per block; L lanes per row, the smallest power of two that brings the value tables of a block to 24 KB
+    const int T = 128;
+    int L = 1;
+    while (L < 32 && (size_t)2 * nc * (T / L + 1) * 8 > 24 * 1024) L <<= 1;
+    if (const char* e = getenv("ZKH_ZCX_LANES")) {            // measurement knob: 1, 2, 4, ... 32
+        const int v = atoi(e);
+        if (v >= 1 && v <= 32 && !(v & (v - 1))) L = v;
+    }
+    const size_t smem = zcx_smem_bytes(nc, nterms, T, L);
     if (smem > 220 * 1024) return zkh_fail(ctx, ZKH_ERR_LIMIT, "zero-check: program does not fit shared memory");
-    if (cudaFuncSetAttribute(zcx_round_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return zkh_fail(ctx, ZKH_ERR_CUDA, "zero-check: shared memory attribute");
+    // the limit is raised once per device to the largest program this entry point accepts: a per-call value would let one
+    // host thread lower it between another thread's call and its launch
+    static ZkhOncePerDevice attr;
+    zkh_once_on_device(attr, ctx->device, [] { cudaFuncSetAttribute(zcx_round_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); });
     int occ = 1;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, zcx_round_kernel, T, smem) != cudaSuccess || occ < 1) occ = 1;
+    const size_t R = (size_t)T / L;
     auto grid_for = [&](size_t items) {
-        size_t want = (items + T - 1) / T, cap = (size_t)ctx->sm_count * occ;
+        size_t want = (items + R - 1) / R, cap = (size_t)ctx->sm_count * occ;
         if (cap > ctx->partials_cap / SCW_NT) cap = ctx->partials_cap / SCW_NT;
         return (unsigned)(want < cap ? want : cap);
     };
@@ -366,12 +387,12 @@ static int zcx_enqueue(zkh_ctx* ctx, const gl_t* const* in, int nc, uint32_t nte
     }
     ZKH_CUDA(ctx, cudaMemcpyAsync(ptr_dev, tab.data(), tab.size() * sizeof(void*), cudaMemcpyHostToDevice, s));
     ZKH_CUDA(ctx, cudaStreamSynchronize(s));      // tab is a host temporary
-    zcx_round_kernel<<<grid_for(n / 2), T, smem, s>>>(prog_dev, ptr_dev, nullptr, n / 2, 1, ctl, ctx->d_partials, nullptr,
+    zcx_round_kernel<<<grid_for(n / 2), T, smem, s>>>(prog_dev, ptr_dev, nullptr, n / 2, 1, (uint32_t)L, ctl, ctx->d_partials, nullptr,
                                                      ctl->msgs, ctl->chals, tag);
     cur_n = n;
     for (uint32_t r = 1; r < logn; r++) {
         zcx_round_kernel<<<grid_for(cur_n / 4), T, smem, s>>>(
-            prog_dev, ptr_dev + ((size_t)2 * r) * nc, (gl_t* const*)(ptr_dev + ((size_t)2 * r + 1) * nc), cur_n / 4, 0, ctl,
+            prog_dev, ptr_dev + ((size_t)2 * r) * nc, (gl_t* const*)(ptr_dev + ((size_t)2 * r + 1) * nc), cur_n / 4, 0, (uint32_t)L, ctl,
             ctx->d_partials, ctl->chals + (r - 1), ctl->msgs + (size_t)r * SCW_NT, ctl->chals + r, tag);
         cur_n /= 2;
     }
