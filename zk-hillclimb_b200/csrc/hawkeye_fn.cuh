@@ -12,15 +12,23 @@
 
 namespace zkh {
 
-// sum_j lam[j] * r_j with one modular reduction at the end
-struct Rlc {
+// sum_j lam[j] * r_j with one modular reduction at the end.  PART / NP: only the constraints j = PART (mod NP) are
+// accumulated (j is a compile-time value in the straight-line constraint lists below, so the others, and the column
+// reads only they need, disappear from the code): the summand is linear in the weighted sum, which lets NP warps share
+// one row, each evaluating its own share of the constraints.
+template <int PART = 0, int NP = 1>
+struct RlcT {
     Acc192 a;
     const gl_t* lam;
     int j;
-    __device__ __forceinline__ explicit Rlc(const gl_t* l) : lam(l), j(0) { a.clear(); }
-    __device__ __forceinline__ void push(gl_t r) { a.add_prod(lam[j++], r); }
+    __device__ __forceinline__ explicit RlcT(const gl_t* l) : lam(l), j(0) { a.clear(); }
+    __device__ __forceinline__ void push(gl_t r) {
+        if (j % NP == PART) a.add_prod(lam[j], r);
+        j++;
+    }
     __device__ __forceinline__ gl_t weighted(gl_t e) { return gl_mul(e, a.reduce()); }
 };
+using Rlc = RlcT<0, 1>;
 __device__ __forceinline__ gl_t hw_bool(gl_t x) { return gl_sub(gl_mul(x, x), x); }          // x^2 - x
 __device__ __forceinline__ gl_t hw_or(gl_t a, gl_t b) { return gl_sub(gl_add(a, b), gl_mul(a, b)); }
 __device__ __forceinline__ gl_t hw_xor(gl_t a, gl_t b) { return gl_sub(gl_add(a, b), gl_mul(gl_dbl(a), b)); }
@@ -50,8 +58,9 @@ template <> struct WFn<ZKH_F_HW_DG> {
     static constexpr int NC = 30, NLAM = 18;
     enum { ASIG = 1, BEXP, ASGN, AZ, AINV, ABASE, ALO, ASH, APW, AQ, AR, MAX, ASEL, CSUM, TSGN, TMAG, TZ, TINV,
            WD, PLO, PHI, PDN, PUP, NR, S14, U1H, U1L, U2H, U2L };
-    static __device__ __forceinline__ gl_t eval(const gl_t* v, const gl_t* lam) {
-        Rlc c(lam);
+    template <int PART = 0, int NP = 1, class V = const gl_t*>
+    static __device__ __forceinline__ gl_t eval(const V& v, const gl_t* lam) {
+        RlcT<PART, NP> c(lam);
         c.push(gl_mul(v[AZ], v[ASIG]));                                                            // 0
         c.push(gl_sub(gl_mul(v[ASIG], v[AINV]), hw_not(v[AZ])));                                   // 1
         c.push(gl_sub(v[ASIG], gl_add(gl_mul(v[ABASE], 1024), v[ALO])));                           // 2
@@ -126,7 +135,8 @@ template <> struct WFn<ZKH_F_HW_DO> {
            C2, RB2, TH2, TL2, RTI2, ZRT2, FH2, FL2, FLH2, L02, RUP2, C22, M2, E2, S2, Z2,
            Q16, Q16H, L03, RB3, RT3, RTI3, ZRT3, RUP3, YB,
            XSS, XSE, XZS, XSMH, XSML, WSS, WSE, WZS, WSMH, WSML };
-    static __device__ __forceinline__ gl_t eval(const gl_t* v, const gl_t* lam) {
+    template <int PART = 0, int NP = 1, class V = const gl_t*>
+    static __device__ __forceinline__ gl_t eval(const V& v, const gl_t* lam) {
         constexpr gl_t B23 = 1ull << 23, B24 = 1ull << 24, B31 = 1ull << 31;
         const gl_t live1 = hw_not(v[Z1]), live2 = hw_not(v[Z2]);
         const gl_t manx = gl_add(B23, gl_add(gl_mul(v[XSMH], 4096), v[XSML]));
@@ -135,7 +145,7 @@ template <> struct WFn<ZKH_F_HW_DO> {
         const gl_t fr1 = gl_add(gl_mul(v[FH1], 4096), v[FL1]);
         const gl_t fr2 = gl_add(gl_mul(v[FH2], 4096), v[FL2]);
         const gl_t t2 = gl_add(gl_mul(v[TH2], 4096), v[TL2]);
-        Rlc c(lam);
+        RlcT<PART, NP> c(lam);
         // accumulator value entering the output stage
         c.push(gl_mul(v[FZ], v[S14F]));                                                             // 0
         c.push(gl_sub(gl_mul(v[S14F], v[FINV]), hw_not(v[FZ])));                                    // 1

@@ -74,6 +74,75 @@ scw_round_kernel(WidePtrs P, size_t items, int first, ZkhCtl* ctl, gl_t* partial
     grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, 0);
 }
 
+// The two widest summands (30 and 57 columns, 18 and 49 constraints) with a row shared by the NP warps of a block: the
+// block stages value and difference of every column for 32 rows in shared memory (warp w loads, binds and stores the
+// columns k = w mod NP; lane = row, so every global access is one 512-byte segment), and warp w evaluates the
+// constraints j = w (mod NP) of those 32 rows, reading only the columns they touch.  A thread of the one-row-per-thread
+// kernel needs 172 (30 columns) or 255 registers with spills (57 columns), which leaves 8 warps per SM.
+template <int F>
+struct SmemRow {
+    const gl_t (*c)[32];
+    uint32_t lane;
+    __device__ __forceinline__ gl_t operator[](int k) const { return c[k][lane]; }
+};
+template <int F, int NP>
+__global__ void __launch_bounds__(32 * NP)
+scw_split_kernel(WidePtrs P, size_t items, int first, ZkhCtl* ctl, gl_t* partials, const gl_t* chal_prev, gl_t* msg_out,
+                 gl_t* chal_out, ZkhTag tag) {
+    constexpr int NC = WFn<F>::NC, NLAM = WFn<F>::NLAM;
+    static_assert(NP == 4, "the part dispatch below is written for four warps");
+    __shared__ gl_t lam[NLAM];
+    __shared__ gl_t sh[SCW_NT * 32];
+    __shared__ gl_t cur[NC][32];
+    __shared__ gl_t dif[NC][32];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int j = threadIdx.x; j < NLAM; j += blockDim.x) lam[j] = ctl->aux[j];
+    const gl_t a = first ? 0 : *chal_prev;
+    gl_t s[SCW_NT];
+#pragma unroll
+    for (int t = 0; t < SCW_NT; t++) s[t] = 0;
+    const SmemRow<F> row{cur, lane};
+    for (size_t base = (size_t)blockIdx.x * 32; base < items; base += (size_t)gridDim.x * 32) {
+        const size_t i = base + lane;
+        const bool live = i < items;
+        __syncthreads();                                 // the previous rows (and lam on the first pass) are done with
+        for (int k = warp; k < NC; k += NP) {
+            gl_t lo = 0, hi = 0;
+            if (live) {
+                if (first) {
+                    ulonglong2 v = ld2(P.in[k] + 2 * i);
+                    lo = v.x;
+                    hi = v.y;
+                } else {
+                    ulonglong2 u = ld2(P.in[k] + 4 * i), w = ld2(P.in[k] + 4 * i + 2);
+                    lo = gl_lerp(u.x, u.y, a);
+                    hi = gl_lerp(w.x, w.y, a);
+                    st2(P.out[k] + 2 * i, lo, hi);
+                }
+            }
+            cur[k][lane] = lo;
+            dif[k][lane] = gl_sub(hi, lo);
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int t = 0; t < SCW_NT; t++) {
+            gl_t val;
+            if (warp == 0) val = WFn<F>::template eval<0, NP>(row, lam);
+            else if (warp == 1) val = WFn<F>::template eval<1, NP>(row, lam);
+            else if (warp == 2) val = WFn<F>::template eval<2, NP>(row, lam);
+            else val = WFn<F>::template eval<3, NP>(row, lam);
+            if (live) s[t] = gl_add(s[t], val);
+            if (t + 1 < SCW_NT) {
+                __syncthreads();                         // every warp has read this point's values
+                for (int k = warp; k < NC; k += NP) cur[k][lane] = gl_add(cur[k][lane], dif[k][lane]);
+                __syncthreads();
+            }
+        }
+    }
+    __syncthreads();
+    grid_finish<SCW_NT>(s, sh, ctl, partials, msg_out, chal_out, tag, 0);
+}
+
 // out[k] = in[k][0] + a*(in[k][1] - in[k][0]) after the last round
 __global__ void scw_finals_kernel(WidePtrs P, int nc, const gl_t* chal, gl_t* out) {
     int k = threadIdx.x;
@@ -97,24 +166,38 @@ static size_t scw_workspace_bytes(int nc, uint32_t logn) {
 template <int F>
 static int scw_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, const ZkhTag& tag, gl_t* finals_dev) {
     constexpr int NC = WFn<F>::NC;
+    constexpr bool SPLIT = NC >= 30;                 // the 30- and 57-column summands: a row shared by four warps
+    constexpr int SPLIT_NP = 4;
     cudaStream_t s = ctx->stream;
     ZkhCtl* ctl = ctx->d_ctl;
     const size_t n = (size_t)1 << logn;
     static const int occ = [] {
         int o = 0;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, scw_round_kernel<F>, SCW_THREADS, 0);
+        if constexpr (SPLIT) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, scw_split_kernel<F, SPLIT_NP>, 32 * SPLIT_NP, 0);
+        else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, scw_round_kernel<F>, SCW_THREADS, 0);
         return o < 1 ? 1 : o;
     }();
+    const bool split = SPLIT && !getenv("ZKH_SCW_NOSPLIT");      // measurement knob: the one-row-per-thread kernel
+    const size_t rows_per_block = split ? 32 : SCW_THREADS;
     auto grid_for = [&](size_t items) {
-        size_t want = (items + SCW_THREADS - 1) / SCW_THREADS, cap = (size_t)ctx->sm_count * occ;
+        size_t want = (items + rows_per_block - 1) / rows_per_block, cap = (size_t)ctx->sm_count * occ;
         if (cap > ctx->partials_cap / SCW_NT) cap = ctx->partials_cap / SCW_NT;
         return (unsigned)(want < cap ? want : cap);
+    };
+    auto launch = [&](const WidePtrs& P, size_t items, int first, const gl_t* chal_prev, gl_t* msg_out, gl_t* chal_out) {
+        if constexpr (SPLIT) {
+            if (split) {
+                scw_split_kernel<F, SPLIT_NP><<<grid_for(items), 32 * SPLIT_NP, 0, s>>>(P, items, first, ctl, ctx->d_partials, chal_prev,
+                                                                                        msg_out, chal_out, tag);
+                return;
+            }
+        }
+        scw_round_kernel<F><<<grid_for(items), SCW_THREADS, 0, s>>>(P, items, first, ctl, ctx->d_partials, chal_prev, msg_out, chal_out, tag);
     };
     WidePtrs P;
     memset(&P, 0, sizeof P);
     for (int k = 0; k < NC; k++) P.in[k] = in[k];
-    scw_round_kernel<F><<<grid_for(n / 2), SCW_THREADS, 0, s>>>(P, n / 2, 1, ctl, ctx->d_partials, nullptr, ctl->msgs,
-                                                               ctl->chals, tag);
+    launch(P, n / 2, 1, nullptr, ctl->msgs, ctl->chals);
     gl_t* bufA = (gl_t*)ctx->ws;
     gl_t* bufB = (gl_t*)((char*)ctx->ws + zkh_align((size_t)NC * (n / 2 + 1) * 8));
     gl_t* dst = bufA;
@@ -122,9 +205,7 @@ static int scw_enqueue_t(zkh_ctx* ctx, const gl_t* const* in, uint32_t logn, con
     for (uint32_t r = 1; r < logn; r++) {
         const size_t out_n = cur_n / 2;
         for (int k = 0; k < NC; k++) P.out[k] = dst + (size_t)k * out_n;
-        scw_round_kernel<F><<<grid_for(cur_n / 4), SCW_THREADS, 0, s>>>(
-            P, cur_n / 4, 0, ctl, ctx->d_partials, ctl->chals + (r - 1), ctl->msgs + (size_t)r * SCW_NT,
-            ctl->chals + r, tag);
+        launch(P, cur_n / 4, 0, ctl->chals + (r - 1), ctl->msgs + (size_t)r * SCW_NT, ctl->chals + r);
         for (int k = 0; k < NC; k++) P.in[k] = P.out[k];
         dst = (dst == bufA) ? bufB : bufA;
         cur_n = out_n;
