@@ -647,6 +647,32 @@ def run_profile_case(args):
         terms, konst = tfg.zc_terms(tfg.ba_constraints(cv, tfg.Poly.var(1), tfg.Poly.var(2), tfg.Poly.var(3)), lam)
         cols = [gl_rand(1 << 19) for _ in range(4 + tfg.NBA)]
         fn = lambda: prover.sc_prove_zc(zk.Transcript("prof"), "bfa-scE", cols, terms, konst)
+    elif name in ("layer", "layer_zk"):
+        # ONE TinyLlama-shaped integer decoder layer (witness chain, commitments, proof), run once: the launch list behind the
+        # driver line's "layer" figure (about 2 x 10^4 launches; one-pass metrics only at this size)
+        from zk_hillclimb_b200 import ig_dev
+        ig, zkm = zk.ig, zk.zkm
+        cfg = ig.Config(*TINYLLAMA_DIMS)
+        tabs = ig.build_tables(zk.load_library(), cfg.d, cfg.btop)
+        x0, Wt = ig.random_layer_inputs(cfg, 42, 0.9)
+        px0, pW = ig_dev.pin_inputs(x0, Wt)
+        ident = lambda a: a
+        prover.keep_trees = name == "layer"
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        lw = ig_dev.itf_build_witness(cfg, px0, pW, tabs, torch.device("cuda:0"), prover)
+        tr = zk.Transcript("itf-layer-0")
+        if name == "layer":
+            lo = ig.itf_commit_all(prover, lw, lw["dev_W"], 2, ident)
+            pf = ig.itf_prove(prover, tr, cfg, lw, lo, Wt, tabs, 2, 24, ident)
+        else:
+            zc = zkm.ZkCtx(seed=0xC0FFEE, Q=24, keep_bytes=80 << 30)
+            lo = zkm.itf_commit_all(prover, zc, cfg, lw, lw["dev_W"], 2, ident)
+            pf = zkm.itf_prove(prover, zc, tr, cfg, lw, lo, Wt, tabs, 2, 24, ident, {})
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case": name, "ms": (time.perf_counter() - t0) * 1e3, "proof_bytes": len(pf),
+                          "note": "one cold pass (no warm-up): workspace growth and table uploads included"}), flush=True)
+        return
     else:
         raise SystemExit("unknown profile case " + name)
     fn()
