@@ -433,6 +433,12 @@ ZKH_API int zkh_gl_gather_bits(zkh_ctx* ctx, const uint64_t* col_dev, uint64_t c
                                const uint64_t* masks, uint32_t nbits, uint64_t* out_dev);
 ZKH_API int zkh_gl_scatter_bits(zkh_ctx* ctx, const uint64_t* vals_dev, uint64_t n, uint64_t konst, const uint64_t* masks,
                                 uint32_t nbits, uint64_t* out_dev, uint64_t out_len);
+/* out[u] = col[u ^ xor_mask] for u < n (n a power of two, xor_mask < n): the rotate-half partner column of the RoPE gadget
+ * (zkllm-src/p3_int_gadgets.cuh:1297-1298).  Stream-ordered. */
+ZKH_API int zkh_gl_gather_xor(zkh_ctx* ctx, const uint64_t* col_dev, uint64_t n, uint64_t xor_mask, uint64_t* out_dev);
+/* p3ismx::mask_col (zkllm-src/p3_int_gadgets.cuh:1490-1498): out[u] = 1 where key index j <= query index i over
+ * u = j | i << lseq | a << 2*lseq, 2^(la + 2*lseq) elements.  Stream-ordered. */
+ZKH_API int zkh_ig_causal_mask(zkh_ctx* ctx, uint32_t la, uint32_t lseq, uint64_t* out_dev);
 /* Rescale witness (zkllm-src/p3_int_gadgets.cuh:230-275 p3irs::gen_witness): for each signed acc value
  * y = floor((acc + 2^(sf-1)) / 2^sf), remainder limbs L0 (16 bits), L1 (sf > 16 only), and the lookup row
  * indices of the limbs and of y in its window (rng 1: [-2^19,2^19), rng 2: [-2^15,2^15), rng 0: none).

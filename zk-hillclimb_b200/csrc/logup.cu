@@ -426,6 +426,35 @@ extern "C" int zkh_gl_gather_bits(zkh_ctx* c, const uint64_t* col_dev, uint64_t 
                                   uint32_t nbits, uint64_t* out_dev) {
     return bitmap_move(c, false, col_dev, n, konst, masks, nbits, col_len, out_dev, "gather_bits: null pointer");
 }
+// out[u] = col[u ^ x]: the rotate-half partner column of RoPE (zkllm-src/p3_int_gadgets.cuh:1297-1298)
+__global__ void gather_xor_kernel(const gl_t* __restrict__ col, size_t n, uint64_t x, gl_t* __restrict__ out) {
+    for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < n; u += (size_t)gridDim.x * blockDim.x) out[u] = col[u ^ x];
+}
+extern "C" int zkh_gl_gather_xor(zkh_ctx* c, const uint64_t* col_dev, uint64_t n, uint64_t xor_mask, uint64_t* out_dev) {
+    if (!c || !col_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "gather_xor: null pointer");
+    if (!n || (n & (n - 1)) || xor_mask >= n) return zkh_fail(c, ZKH_ERR_ARG, "gather_xor: n must be a power of two above the mask");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 16;
+    gather_xor_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(col_dev, (size_t)n, xor_mask, out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+// p3ismx::mask_col (zkllm-src/p3_int_gadgets.cuh:1490-1498): 1 where key j <= query i over u = j | i << lseq | a << 2 lseq
+__global__ void causal_mask_kernel(uint32_t lseq, size_t n, gl_t* __restrict__ out) {
+    const uint64_t m = ((uint64_t)1 << lseq) - 1;
+    for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < n; u += (size_t)gridDim.x * blockDim.x)
+        out[u] = (u & m) <= ((u >> lseq) & m) ? 1 : 0;
+}
+extern "C" int zkh_ig_causal_mask(zkh_ctx* c, uint32_t la, uint32_t lseq, uint64_t* out_dev) {
+    if (!c || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "causal_mask: null pointer");
+    if (la + 2 * lseq > 34) return zkh_fail(c, ZKH_ERR_LIMIT, "causal_mask: more than 2^34 elements");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    const size_t n = (size_t)1 << (la + 2 * lseq);
+    size_t blocks = (n + 255) / 256, cap = (size_t)c->sm_count * 16;
+    causal_mask_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, c->stream>>>(lseq, n, out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
 extern "C" int zkh_gl_scatter_bits(zkh_ctx* c, const uint64_t* vals_dev, uint64_t n, uint64_t konst, const uint64_t* masks, uint32_t nbits,
                                    uint64_t* out_dev, uint64_t out_len) {
     return bitmap_move(c, true, vals_dev, n, konst, masks, nbits, out_len, out_dev, "scatter_bits: null pointer");
