@@ -404,6 +404,11 @@ ZKH_API int zkh_ig_matmul(zkh_ctx* ctx, const uint64_t* A_dev, const int64_t a_s
  *             the lookup rows: irow = e, m, m - 2^14, m, L40 L41 L42 D40 D41 D42 L20 D20 LR0, LR1; iel = remW, W + 2^19, remY, Y + 2^19
  *   softmax:  rows of 2^lseq keys, 2^(la+lseq) rows, causal; xe = first, dm, E, r1 lo, r1 hi, r2 lo, r2 hi; xb = mx, S per row;
  *             p; idxDM, idxL[4] per element, idxMX = mx + 2^15 per row (expt_col: the EXPT table's value column, 2^17 rows) */
+/* Signed integers (|v| < 2^63 for the 64-bit form) -> field elements v or p - |v| (p3ig::gsig, zkllm-src/p3_int_gadgets.cuh:57):
+ * weights and activations as a loader keeps them, and the int64 public columns the RoPE replay returns.  in == out is allowed for
+ * the 64-bit form.  Stream-ordered. */
+ZKH_API int zkh_gl_lift_i32(zkh_ctx* ctx, const int32_t* in_dev, uint64_t n, uint64_t* out_dev);
+ZKH_API int zkh_gl_lift_i64(zkh_ctx* ctx, const int64_t* in_dev, uint64_t n, uint64_t* out_dev);
 ZKH_API int zkh_ig_add_witness(zkh_ctx* ctx, const uint64_t* a_dev, const uint64_t* b_dev, uint64_t n, uint64_t* out_dev,
                                uint32_t* idx_dev);
 ZKH_API int zkh_ig_rs20_index(zkh_ctx* ctx, const uint64_t* v_dev, uint64_t n, uint32_t* idx_dev);

@@ -4,7 +4,7 @@
 
 Produces zk-hillclimb_b200/libzkh.so from csrc/*.cu with nvcc.  The library has
 no Python or torch dependency; it is what the C ABI in include/zkh.h names.
-Also builds zk-hillclimb_b200/zkh_p3_selftest, zkh_p3_gadgets_selftest and the driver executable zkob_p3fc
+Also builds zk-hillclimb_b200/zkh_p3_selftest, zkh_p3_gadgets_selftest, the layer prover zkh_p3_layer and the driver executable zkob_p3fc
 from host/*.cpp with g++: the C++ host side (include/zkh_p3.hpp, zkh_p3_verify.hpp) linked against the library.
 """
 import glob
@@ -18,6 +18,7 @@ LIB = os.path.join(HERE, "libzkh.so")
 SELFTEST = os.path.join(HERE, "zkh_p3_selftest")
 GADGETS_SELFTEST = os.path.join(HERE, "zkh_p3_gadgets_selftest")
 DRIVER = os.path.join(HERE, "zkob_p3fc")
+LAYER = os.path.join(HERE, "zkh_p3_layer")
 INCLUDE = os.path.abspath(os.path.join(HERE, "..", "include"))
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -40,9 +41,11 @@ def stale():
 
 def build_selftest(force=False):
     """The C++ host programs over the C ABI; linked with an rpath beside the library."""
-    for name, exe in (("p3_selftest.cpp", SELFTEST), ("p3_gadgets_selftest.cpp", GADGETS_SELFTEST), ("zkob_p3fc.cpp", DRIVER)):
+    for name, exe in (("p3_selftest.cpp", SELFTEST), ("p3_gadgets_selftest.cpp", GADGETS_SELFTEST), ("zkob_p3fc.cpp", DRIVER),
+                      ("p3_layer_main.cpp", LAYER)):
         src = os.path.join(HERE, "host", name)
-        deps = [src, os.path.join(INCLUDE, "zkh.h"), os.path.join(INCLUDE, "zkh_p3.hpp"), os.path.join(INCLUDE, "zkh_p3_verify.hpp"), LIB]
+        deps = [src, os.path.join(INCLUDE, "zkh.h"), os.path.join(INCLUDE, "zkh_p3.hpp"), os.path.join(INCLUDE, "zkh_p3_verify.hpp"),
+                os.path.join(INCLUDE, "zkh_p3_layer.hpp"), LIB]
         if not force and os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
             continue
         subprocess.check_call([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", "-I", INCLUDE, src, "-o", exe,

@@ -251,6 +251,33 @@ extern "C" int zkh_ig_add_witness(zkh_ctx* c, const uint64_t* a_dev, const uint6
     ig_add_kernel<<<igw_grid(c, n), 256, 0, c->stream>>>(a_dev, b_dev, (size_t)n, out_dev, idx_dev, &c->d_ctl->err);
     return igw_finish(c, "ig_add_witness");
 }
+// signed integers -> field elements (v, or p - |v|): how weights, activations and the RoPE gadget's public columns enter
+__global__ void ig_lift_i32_kernel(const int32_t* __restrict__ in, size_t n, gl_t* __restrict__ out) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const long long v = in[i];
+        out[i] = v < 0 ? (gl_t)v - 0xFFFFFFFFull : (gl_t)v;        // v + p (mod 2^64)
+    }
+}
+__global__ void ig_lift_i64_kernel(const long long* in, size_t n, gl_t* out) {     // in == out allowed
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const long long v = in[i];
+        out[i] = v < 0 ? (gl_t)v - 0xFFFFFFFFull : (gl_t)v;
+    }
+}
+extern "C" int zkh_gl_lift_i32(zkh_ctx* c, const int32_t* in_dev, uint64_t n, uint64_t* out_dev) {
+    if (!c || !in_dev || !out_dev || !n) return zkh_fail(c, ZKH_ERR_ARG, "lift_i32: null pointer or empty column");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    ig_lift_i32_kernel<<<igw_grid(c, n), 256, 0, c->stream>>>(in_dev, (size_t)n, out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+extern "C" int zkh_gl_lift_i64(zkh_ctx* c, const int64_t* in_dev, uint64_t n, uint64_t* out_dev) {
+    if (!c || !in_dev || !out_dev || !n) return zkh_fail(c, ZKH_ERR_ARG, "lift_i64: null pointer or empty column");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    ig_lift_i64_kernel<<<igw_grid(c, n), 256, 0, c->stream>>>((const long long*)in_dev, (size_t)n, out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
 extern "C" int zkh_ig_rs20_index(zkh_ctx* c, const uint64_t* v_dev, uint64_t n, uint32_t* idx_dev) {
     if (!c || !v_dev || !idx_dev || !n) return zkh_fail(c, ZKH_ERR_ARG, "ig_rs20_index: null pointer or empty column");
     ZKH_CUDA(c, cudaSetDevice(c->device));
