@@ -24,7 +24,7 @@ inline zkh_ctx* zkh_shim_ctx() {
         zkh_ctx* x = nullptr;
         int dev = 0;
         cudaGetDevice(&dev);
-        if (zkh_ctx_create(dev, nullptr, &x) != ZKH_OK) x = nullptr;      // the legacy default stream, like the reference's launches
+        if (zkh_ctx_create(dev, nullptr, &x) != ZKH_OK) x = nullptr;      // a stream of its own; the call below synchronises on both sides
         return x;
     }();
     return c;

@@ -83,8 +83,14 @@ ZKH_API int zkh_profile_last(zkh_ctx* ctx, float* ms, uint64_t* bytes, const cha
 
 /* ---- device memory (stands in for p3bf::dmalloc / cudaMallocAsync use,
  *      zkllm-src/p3_basefold.cuh:50-72) ---- */
+/* Stream-ordered on the context's stream, from the device's default memory pool (freed blocks stay in the pool until
+ * zkh_ctx_release_workspace trims it): a block is usable by work queued on that stream after the call, and after zkh_dev_free
+ * it is reused only by work queued later on that stream. */
 ZKH_API int zkh_dev_alloc(zkh_ctx* ctx, size_t bytes, void** out_dev);
 ZKH_API int zkh_dev_free(zkh_ctx* ctx, void* ptr_dev);
+/* Page-locked host memory (uploads from it need no staging copy). */
+ZKH_API int zkh_host_alloc(zkh_ctx* ctx, size_t bytes, void** out);
+ZKH_API int zkh_host_free(zkh_ctx* ctx, void* ptr);
 ZKH_API int zkh_upload(zkh_ctx* ctx, void* dst_dev, const void* src, size_t bytes);
 ZKH_API int zkh_download(zkh_ctx* ctx, void* dst, const void* src_dev, size_t bytes);
 

@@ -17,6 +17,7 @@
 #include <cstdint>
 #include <cstring>
 #include <deque>
+#include <map>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -71,7 +72,7 @@ class Prover {
     explicit Prover(int device = 0, void* stream = nullptr) {
         if (zkh_ctx_create(device, stream, &ctx_) != ZKH_OK) throw std::runtime_error("zkh: cannot create a context on this device");
     }
-    ~Prover() { if (ctx_) zkh_ctx_destroy(ctx_); }
+    ~Prover() { if (ctx_) { release_kept(); zkh_ctx_destroy(ctx_); } }
     Prover(const Prover&) = delete;
     Prover& operator=(const Prover&) = delete;
     zkh_ctx* ctx() const { return ctx_; }
@@ -130,12 +131,30 @@ class Prover {
         ck(zkh_gl_mle_eval(ctx_, c.data(), z.data(), (uint32_t)z.size(), &y));
         return y;
     }
+    // keep_trees: commitments leave their codeword and capped Merkle tree in HBM (zkh_basefold_commit_keep) and prove_class
+    // reads authentication paths from them instead of encoding and hashing every opened column again.  The kept buffers are
+    // found by the column's device address: call release_kept() before a committed column is freed.
+    bool keep_trees = false;
     Hash commit_gpu_rootonly(const DevCol& c, uint32_t R) {
         uint32_t v = 0;
         while (((size_t)1 << v) < c.size()) v++;
         Hash h;
+        if (keep_trees && c.size() >= 2) {
+            Kept k{R, c.size(), nullptr, nullptr};
+            ck(zkh_dev_alloc(ctx_, (c.size() << R) * sizeof(gl_t), &k.cw));
+            ck(zkh_dev_alloc(ctx_, zkh_basefold_kept_tree_bytes(v + R), &k.tree));
+            ck(zkh_basefold_commit_keep(ctx_, c.data(), v, R, static_cast<uint64_t*>(k.cw), static_cast<uint8_t*>(k.tree), h.data()));
+            auto it = kept_.find(c.data());
+            if (it != kept_.end()) { zkh_dev_free(ctx_, it->second.cw); zkh_dev_free(ctx_, it->second.tree); }
+            kept_[c.data()] = k;
+            return h;
+        }
         ck(zkh_basefold_commit(ctx_, c.data(), v, R, nullptr, h.data()));
         return h;
+    }
+    void release_kept() {
+        for (auto& kv : kept_) { zkh_dev_free(ctx_, kv.second.cw); zkh_dev_free(ctx_, kv.second.tree); }
+        kept_.clear();
     }
     // serialised p3bf::EvalProof (fields in declaration order, see zkh.h)
     std::vector<uint8_t> prove_eval_dev(const DevCol& c, const std::vector<gl_t>& z, gl_t y, uint32_t R, uint32_t Q,
@@ -176,8 +195,23 @@ class Prover {
         }
         std::vector<uint8_t> out(zkh_batchopen_proof_bound(v, R, Q, k));
         size_t wr = 0;
-        ck(zkh_batchopen_prove_class(ctx_, v, flat.data(), T, cols.data(), roots.data(), zid.data(), k, R, Q, label.c_str(), tr.state,
-                                     out.data(), out.size(), &wr));
+        std::vector<const uint64_t*> kcw(k, nullptr);
+        std::vector<const uint8_t*> ktr(k, nullptr);
+        bool any = false;
+        for (uint32_t j = 0; j < k; j++) {
+            auto it = kept_.find(cols[j]);
+            if (it != kept_.end() && it->second.R == R && it->second.n == ents[j].col->size()) {
+                kcw[j] = static_cast<const uint64_t*>(it->second.cw);
+                ktr[j] = static_cast<const uint8_t*>(it->second.tree);
+                any = true;
+            }
+        }
+        if (any)
+            ck(zkh_batchopen_prove_class_kept(ctx_, v, flat.data(), T, cols.data(), roots.data(), zid.data(), k, R, Q, label.c_str(), tr.state,
+                                              out.data(), out.size(), &wr, kcw.data(), ktr.data()));
+        else
+            ck(zkh_batchopen_prove_class(ctx_, v, flat.data(), T, cols.data(), roots.data(), zid.data(), k, R, Q, label.c_str(), tr.state,
+                                         out.data(), out.size(), &wr));
         out.resize(wr);
         return out;
     }
@@ -282,7 +316,9 @@ class Prover {
     }
 
   private:
+    struct Kept { uint32_t R; size_t n; void* cw; void* tree; };
     zkh_ctx* ctx_ = nullptr;
+    std::map<const gl_t*, Kept> kept_;
 };
 
 inline DevCol::DevCol(Prover& p, size_t n) : ctx_(p.ctx()), n_(n) {

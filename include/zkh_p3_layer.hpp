@@ -612,9 +612,43 @@ inline Views views_pv(const ItfConfig& c, uint32_t h, uint32_t b) {
     return v;
 }
 
+// signed 32-bit integers in page-locked host memory (uploads need no staging copy)
+class HostI32 {
+  public:
+    HostI32() = default;
+    HostI32(Prover& P, size_t n) : ctx_(P.ctx()), n_(n) {
+        void* p = nullptr;
+        P.ck(zkh_host_alloc(ctx_, n * 4, &p));
+        ptr_ = static_cast<int32_t*>(p);
+    }
+    HostI32(HostI32&& o) noexcept : ctx_(o.ctx_), ptr_(o.ptr_), n_(o.n_) { o.ptr_ = nullptr; }
+    HostI32& operator=(HostI32&& o) noexcept {
+        if (this != &o) { if (ptr_) zkh_host_free(ctx_, ptr_); ctx_ = o.ctx_; ptr_ = o.ptr_; n_ = o.n_; o.ptr_ = nullptr; }
+        return *this;
+    }
+    HostI32(const HostI32&) = delete;
+    HostI32& operator=(const HostI32&) = delete;
+    ~HostI32() { if (ptr_) zkh_host_free(ctx_, ptr_); }
+    int32_t* data() const { return ptr_; }
+    size_t size() const { return n_; }
+
+  private:
+    zkh_ctx* ctx_ = nullptr;
+    int32_t* ptr_ = nullptr;
+    size_t n_ = 0;
+};
+
 // the layer's inputs as a weight loader keeps them: signed 32-bit integers on the host
 struct ItfInputs {
-    std::vector<int32_t> x0, w[7], g1, g2, ct, st;     // ct, st: RoPE tables [seq][dh / 2] at scale 2^14
+    HostI32 x0, w[7], g1, g2, ct, st;                  // ct, st: RoPE tables [seq][dh / 2] at scale 2^14
+    ItfInputs(Prover& P, const ItfConfig& c) {
+        x0 = HostI32(P, (size_t)c.seq * c.batch * c.d);
+        for (int i = 0; i < 7; i++) w[i] = HostI32(P, c.wrows(i) * c.wcols(i));
+        g1 = HostI32(P, c.d);
+        g2 = HostI32(P, c.d);
+        ct = HostI32(P, (size_t)c.seq * c.dh / 2);
+        st = HostI32(P, (size_t)c.seq * c.dh / 2);
+    }
 };
 
 // everything p3itf::build_witness produces, resident on the device
@@ -630,8 +664,13 @@ struct ItfWit {
     DevIdx idxRes1, idxOut;
 };
 
-inline DevCol upload_lifted(Prover& P, const std::vector<int32_t>& v) {
-    DevIdx raw(P, std::vector<uint32_t>(reinterpret_cast<const uint32_t*>(v.data()), reinterpret_cast<const uint32_t*>(v.data()) + v.size()));
+inline DevIdx upload_i32(Prover& P, const HostI32& v) {
+    DevIdx raw(P, v.size());
+    P.ck(zkh_upload(P.ctx(), raw.data(), v.data(), v.size() * 4));
+    return raw;
+}
+inline DevCol upload_lifted(Prover& P, const HostI32& v) {
+    DevIdx raw = upload_i32(P, v);
     DevCol out(P, v.size());
     P.ck(zkh_gl_lift_i32(P.ctx(), reinterpret_cast<const int32_t*>(raw.data()), v.size(), out.data()));
     return out;
@@ -675,8 +714,8 @@ inline void itf_build_witness(Prover& P, const ItfConfig& c, IgTables& T, const 
     for (int i = 0; i < 7; i++) w.W[i] = upload_lifted(P, in.w[i]);
     w.g1 = upload_lifted(P, in.g1);
     w.g2 = upload_lifted(P, in.g2);
-    w.ct = DevIdx(P, std::vector<uint32_t>(reinterpret_cast<const uint32_t*>(in.ct.data()), reinterpret_cast<const uint32_t*>(in.ct.data()) + in.ct.size()));
-    w.st = DevIdx(P, std::vector<uint32_t>(reinterpret_cast<const uint32_t*>(in.st.data()), reinterpret_cast<const uint32_t*>(in.st.data()) + in.st.size()));
+    w.ct = upload_i32(P, in.ct);
+    w.st = upload_i32(P, in.st);
     for (int i = 0; i < 7; i++) w.idxW[i] = rs20_index(P, w.W[i]);
     w.idxG1 = rs20_index(P, w.g1);
     w.idxG2 = rs20_index(P, w.g2);

@@ -44,6 +44,8 @@ def load_library():
         "zkh_version": (C.c_char_p, []),
         "zkh_profile_last": (i, [vp, C.POINTER(C.c_float), C.POINTER(u64), C.POINTER(C.c_char_p)]),
         "zkh_dev_alloc": (i, [vp, sz, C.POINTER(vp)]),
+        "zkh_host_alloc": (i, [vp, sz, C.POINTER(vp)]),
+        "zkh_host_free": (i, [vp, vp]),
         "zkh_dev_free": (i, [vp, vp]),
         "zkh_upload": (i, [vp, vp, vp, sz]),
         "zkh_download": (i, [vp, vp, vp, sz]),

@@ -48,7 +48,7 @@ def build_selftest(force=False):
                 os.path.join(INCLUDE, "zkh_p3_layer.hpp"), LIB]
         if not force and os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
             continue
-        subprocess.check_call([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", "-I", INCLUDE, src, "-o", exe,
+        subprocess.check_call([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", "-pthread", "-I", INCLUDE, src, "-o", exe,
                                "-L", HERE, "-lzkh", "-Wl,-rpath,$ORIGIN"])
     return SELFTEST
 

@@ -29,6 +29,8 @@ extern "C" int zkh_ctx_release_workspace(zkh_ctx* c) {
     if (c->ws) cudaFree(c->ws);
     c->ws = nullptr;
     c->ws_bytes = 0;
+    cudaMemPool_t pool;                          // blocks that zkh_dev_free returned to the pool go back to the device
+    if (cudaDeviceGetDefaultMemPool(&pool, c->device) == cudaSuccess) cudaMemPoolTrimTo(pool, 0);
     return ZKH_OK;
 }
 
@@ -112,10 +114,22 @@ extern "C" int zkh_profile_last(zkh_ctx* c, float* ms, uint64_t* bytes, const ch
     return ZKH_OK;
 }
 
+// Device memory for host code that has no allocator of its own (the C++ host side): stream-ordered allocations from the
+// device's default memory pool, whose release threshold is raised once per device so that freed blocks stay in the pool
+// and a prover that allocates hundreds of short-lived columns per proof does not pay a cudaMalloc / cudaFree (each a
+// device-wide synchronisation) for every one of them.  zkh_ctx_release_workspace trims the pool.
 extern "C" int zkh_dev_alloc(zkh_ctx* c, size_t bytes, void** out) {
     if (!c || !out) return ZKH_ERR_ARG;
     ZKH_CUDA(c, cudaSetDevice(c->device));
-    cudaError_t e = cudaMalloc(out, bytes ? bytes : 1);
+    static ZkhOncePerDevice pool_set;
+    zkh_once_on_device(pool_set, c->device, [c] {
+        cudaMemPool_t pool;
+        if (cudaDeviceGetDefaultMemPool(&pool, c->device) == cudaSuccess) {
+            uint64_t keep = UINT64_MAX;
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        }
+    });
+    cudaError_t e = cudaMallocAsync(out, bytes ? bytes : 1, c->stream);
     if (e != cudaSuccess) {
         cudaGetLastError();
         *out = nullptr;
@@ -126,8 +140,23 @@ extern "C" int zkh_dev_alloc(zkh_ctx* c, size_t bytes, void** out) {
 extern "C" int zkh_dev_free(zkh_ctx* c, void* p) {
     if (!c) return ZKH_ERR_ARG;
     if (!p) return ZKH_OK;
-    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
-    ZKH_CUDA(c, cudaFree(p));
+    ZKH_CUDA(c, cudaFreeAsync(p, c->stream));      // reusable once the stream has passed this point
+    return ZKH_OK;
+}
+// page-locked host memory for inputs that are uploaded every proof (weights as a loader keeps them)
+extern "C" int zkh_host_alloc(zkh_ctx* c, size_t bytes, void** out) {
+    if (!c || !out) return ZKH_ERR_ARG;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    if (cudaMallocHost(out, bytes ? bytes : 1) != cudaSuccess) {
+        cudaGetLastError();
+        *out = nullptr;
+        return zkh_fail(c, ZKH_ERR_NOMEM, "page-locked host allocation of " + std::to_string(bytes) + " bytes failed");
+    }
+    return ZKH_OK;
+}
+extern "C" int zkh_host_free(zkh_ctx* c, void* p) {
+    if (!c) return ZKH_ERR_ARG;
+    if (p) ZKH_CUDA(c, cudaFreeHost(p));
     return ZKH_OK;
 }
 extern "C" int zkh_upload(zkh_ctx* c, void* dst, const void* src, size_t bytes) {

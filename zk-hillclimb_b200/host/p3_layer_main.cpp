@@ -1,21 +1,28 @@
 // The integer decoder layer proved from C++ (include/zkh_p3_layer.hpp over libzkh.so): reads the layer's inputs as signed 32-bit
 // integers, runs the witness chain, the commitments and p3itf::prove on the GPU, writes the serialised layer proof.
-//   zkh_p3_layer <inputs.i32> <proof.bin> <seq> <d> <nh> <dh> <dff> <batch> <R> <Q> <transcript seed> [repeats]
+//   zkh_p3_layer <inputs.i32> <proof.bin> <seq> <d> <nh> <dh> <dff> <batch> <R> <Q> <transcript seed> [layers] [workers] [warmup]
+// layers > 1 proves the same inputs that many times (a stand-in for independent layers; layer l > 0 runs on the transcript
+// "<seed>-<l>"); workers > 1 keeps that many proofs in flight, each on its own host thread, library context and stream;
+// warmup = 1 lets every worker prove one untimed layer first (table uploads, workspace growth, the allocator's pool) and starts
+// the clock when all are done.  The last line reports the wall time per layer of the timed pass (upload of the inputs from
+// page-locked memory, witness chain, commitments, proof).  The GPU is device $ZKH_DEVICE (default 0).
 // inputs.i32: x0 (seq*batch*d) | the seven weights Wq Wk Wv Wo (d*d each) Wg Wu (d*dff) Wd (dff*d) | g1 g2 (d) | cos, sin tables
 // (seq * dh/2 each), all little-endian int32.  Exit code 0 on success, 2 on a usage or I/O error, 3 on a library error.
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <fstream>
+#include <mutex>
+#include <thread>
 
 #include "zkh_p3_layer.hpp"
 
 using namespace zkh_p3;
 
-static bool read_i32(std::ifstream& f, std::vector<int32_t>& v, size_t n) {
-    v.resize(n);
-    f.read(reinterpret_cast<char*>(v.data()), (std::streamsize)(n * 4));
-    return (size_t)f.gcount() == n * 4;
+static bool read_i32(std::ifstream& f, HostI32& v) {
+    f.read(reinterpret_cast<char*>(v.data()), (std::streamsize)(v.size() * 4));
+    return (size_t)f.gcount() == v.size() * 4;
 }
 
 int main(int argc, char** argv) {
@@ -31,30 +38,68 @@ int main(int argc, char** argv) {
         const int reps = argc > 12 ? atoi(argv[12]) : 1;
         std::ifstream f(argv[1], std::ios::binary);
         if (!f) { fprintf(stderr, "cannot open %s\n", argv[1]); return 2; }
-        ItfInputs in;
-        bool ok = read_i32(f, in.x0, (size_t)c.seq * c.batch * c.d);
-        for (int i = 0; i < 7 && ok; i++) ok = read_i32(f, in.w[i], c.wrows(i) * c.wcols(i));
-        ok = ok && read_i32(f, in.g1, c.d) && read_i32(f, in.g2, c.d) && read_i32(f, in.ct, (size_t)c.seq * c.dh / 2) &&
-             read_i32(f, in.st, (size_t)c.seq * c.dh / 2);
+        const int workers = argc > 13 ? std::max(1, atoi(argv[13])) : 1;
+        const bool warm = argc > 14 && atoi(argv[14]) > 0;
+        const int device = getenv("ZKH_DEVICE") ? atoi(getenv("ZKH_DEVICE")) : 0;
+        Prover P0(device);
+        ItfInputs in(P0, c);
+        bool ok = read_i32(f, in.x0);
+        for (int i = 0; i < 7 && ok; i++) ok = read_i32(f, in.w[i]);
+        ok = ok && read_i32(f, in.g1) && read_i32(f, in.g2) && read_i32(f, in.ct) && read_i32(f, in.st);
         if (!ok) { fprintf(stderr, "%s is shorter than the configuration needs\n", argv[1]); return 2; }
-        Prover P(0);
-        IgTables T(c.d, c.btop);
         std::vector<uint8_t> proof;
-        for (int rep = 0; rep < reps; rep++) {
-            auto t0 = std::chrono::steady_clock::now();
-            ItfWit w;
-            itf_build_witness(P, c, T, in, w);
-            auto t1 = std::chrono::steady_clock::now();
-            ItfCom o = itf_commit_all(P, w, R);
-            auto t2 = std::chrono::steady_clock::now();
-            Transcript tr(seed);
-            proof = itf_prove(P, tr, c, T, w, o, R, Q);
-            auto t3 = std::chrono::steady_clock::now();
-            auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
-            printf("{\"rep\": %d, \"witness_ms\": %.3f, \"commit_ms\": %.3f, \"prove_ms\": %.3f, \"proof_bytes\": %zu}\n", rep, ms(t0, t1),
-                   ms(t1, t2), ms(t2, t3), proof.size());
-            fflush(stdout);
-        }
+        std::mutex mu;
+        std::atomic<int> next{0}, ready{0};
+        std::chrono::steady_clock::time_point w0;
+        std::string failure;
+        std::atomic<bool> failed{false};
+        auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
+        auto worker = [&](int id) {
+            try {
+                Prover P(device);
+                P.keep_trees = getenv("ZKH_LAYER_NO_KEEP") == nullptr;   // codewords and capped trees stay resident for the openings
+                IgTables T(c.d, c.btop);
+                if (warm) {
+                    ItfWit w;
+                    itf_build_witness(P, c, T, in, w);
+                    ItfCom o = itf_commit_all(P, w, R);
+                    Transcript tr(seed + "-warm");
+                    itf_prove(P, tr, c, T, w, o, R, Q);
+                    P.release_kept();
+                }
+                if (++ready == workers) w0 = std::chrono::steady_clock::now();      // the last worker to get here starts the clock
+                while (ready.load() < workers && !failed.load()) std::this_thread::yield();
+                for (int rep = next++; rep < reps; rep = next++) {
+                    auto t0 = std::chrono::steady_clock::now();
+                    ItfWit w;
+                    itf_build_witness(P, c, T, in, w);
+                    auto t1 = std::chrono::steady_clock::now();
+                    ItfCom o = itf_commit_all(P, w, R);
+                    auto t2 = std::chrono::steady_clock::now();
+                    Transcript tr(rep ? seed + "-" + std::to_string(rep) : seed);
+                    std::vector<uint8_t> pf = itf_prove(P, tr, c, T, w, o, R, Q);
+                    auto t3 = std::chrono::steady_clock::now();
+                    P.release_kept();
+                    std::lock_guard<std::mutex> lk(mu);
+                    printf("{\"layer\": %d, \"worker\": %d, \"witness_ms\": %.3f, \"commit_ms\": %.3f, \"prove_ms\": %.3f, \"proof_bytes\": %zu}\n", rep, id,
+                           ms(t0, t1), ms(t1, t2), ms(t2, t3), pf.size());
+                    fflush(stdout);
+                    if (rep == 0) proof.swap(pf);
+                }
+            } catch (const std::exception& e) {
+                std::lock_guard<std::mutex> lk(mu);
+                failure = e.what();
+                failed = true;
+                ready += workers;                 // nobody waits for a worker that failed
+            }
+        };
+        std::vector<std::thread> th;
+        for (int i = 1; i < workers; i++) th.emplace_back(worker, i);
+        worker(0);
+        for (auto& t : th) t.join();
+        const auto w1 = std::chrono::steady_clock::now();
+        if (failed) throw std::runtime_error(failure);
+        printf("{\"layers\": %d, \"workers\": %d, \"wall_ms\": %.3f, \"ms_per_layer\": %.3f}\n", reps, workers, ms(w0, w1), ms(w0, w1) / reps);
         std::ofstream g(argv[2], std::ios::binary);
         g.write(reinterpret_cast<const char*>(proof.data()), (std::streamsize)proof.size());
         if (!g) { fprintf(stderr, "cannot write %s\n", argv[2]); return 2; }
