@@ -297,14 +297,24 @@ matvec_rows_kernel(const gl_t* __restrict__ M, const gl_t* __restrict__ w, size_
     block_sum<1>(s, sh);
     if (threadIdx.x == 0) out[blockIdx.x] = s[0];
 }
+// blockIdx.y selects a chunk of rows: out[chunk * C + c] = sum over the chunk's rows of w[r] * M[r][c].  A matrix with few
+// columns (2048 columns fill 8 blocks) still covers the GPU; matvec_cols_sum_kernel adds the chunks.
 __global__ void __launch_bounds__(256)
-matvec_cols_kernel(const gl_t* __restrict__ M, const gl_t* __restrict__ w, size_t R, size_t C, gl_t* out) {
+matvec_cols_kernel(const gl_t* __restrict__ M, const gl_t* __restrict__ w, size_t R, size_t C, size_t rows_per_chunk, gl_t* out) {
     size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
+    const size_t r0 = (size_t)blockIdx.y * rows_per_chunk, r1 = r0 + rows_per_chunk < R ? r0 + rows_per_chunk : R;
     Acc192 acc;
     acc.clear();
-    for (size_t r = 0; r < R; r++) acc.add_prod(w[r], M[r * C + c]);
-    out[c] = acc.reduce();
+    for (size_t r = r0; r < r1; r++) acc.add_prod(w[r], M[r * C + c]);
+    out[(size_t)blockIdx.y * C + c] = acc.reduce();
+}
+__global__ void __launch_bounds__(256) matvec_cols_sum_kernel(const gl_t* __restrict__ part, size_t chunks, size_t C, gl_t* out) {
+    size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    gl_t s = 0;
+    for (size_t k = 0; k < chunks; k++) s = gl_add(s, part[k * C + c]);
+    out[c] = s;
 }
 __global__ void __launch_bounds__(256) scale_vec_kernel(const gl_t* __restrict__ in, gl_t s, size_t n, gl_t* out) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -320,9 +330,22 @@ extern "C" int zkh_gl_matvec(zkh_ctx* c, const uint64_t* M_dev, uint64_t rows, u
     ZKH_CUDA(c, cudaSetDevice(c->device));
     if (along_rows)
         matvec_rows_kernel<<<(unsigned)rows, cols >= 256 ? 256 : 32, 0, c->stream>>>(M_dev, w_dev, (size_t)cols, out_dev);
-    else
-        matvec_cols_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, c->stream>>>(M_dev, w_dev, (size_t)rows, (size_t)cols,
-                                                                                 out_dev);
+    else {
+        const size_t col_blocks = (cols + 255) / 256, want = (size_t)c->sm_count * 4;
+        size_t chunks = col_blocks >= want ? 1 : (want + col_blocks - 1) / col_blocks;
+        if (chunks > rows) chunks = rows;
+        if (chunks > 65535) chunks = 65535;
+        const size_t rpc = (rows + chunks - 1) / chunks;
+        chunks = (rows + rpc - 1) / rpc;
+        if (chunks == 1) {
+            matvec_cols_kernel<<<dim3((unsigned)col_blocks, 1), 256, 0, c->stream>>>(M_dev, w_dev, (size_t)rows, (size_t)cols, rpc, out_dev);
+        } else {
+            ZKH_TRY(zkh_ws_reserve(c, chunks * cols * 8));
+            gl_t* part = (gl_t*)c->ws;
+            matvec_cols_kernel<<<dim3((unsigned)col_blocks, (unsigned)chunks), 256, 0, c->stream>>>(M_dev, w_dev, (size_t)rows, (size_t)cols, rpc, part);
+            matvec_cols_sum_kernel<<<(unsigned)col_blocks, 256, 0, c->stream>>>(part, chunks, (size_t)cols, out_dev);
+        }
+    }
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }
