@@ -779,7 +779,7 @@ inline ItfCom itf_commit_all(Prover& P, ItfWit& w, uint32_t R) {
 }
 
 // p3itf::prove, non-zk: all sub-proofs in fixed order on one transcript with one ledger and one lookup queue, one merged-lookup
-// flush, the public input / output bindings, one batched opening per size class.  Serialised TfProof: 6 x u32 dims | 26 + 2A
+// flush, the public input / output bindings, one batched opening per size class.  Serialised TfProof: 6 x u32 dims | 24 + 2A
 // length-prefixed sub-proofs in proving order | 27 roots | u32 groups (len, GroupProof)* | ioin ioout | u32 batches (len, BatchProof)*
 inline std::vector<uint8_t> itf_prove(Prover& P, Transcript& tr, const ItfConfig& c, IgTables& T, ItfWit& w, const ItfCom& o, uint32_t R,
                                       uint32_t Q) {

@@ -42,6 +42,31 @@ def test_cxx_layer_prover_same_bytes(tmp_path, ref_or_none, zk, prover, dims):
     r = subprocess.run([EXE, inp, outp] + [str(d) for d in dims] + [str(R), str(Q), "itf-layer"], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr
     got = open(outp, "rb").read()
+    # the C++ host verifier (no GPU work, no reference): accepts the proof, rejects a flipped byte and a wrong output grid
+    vargs = [EXE, "verify", inp, outp] + [str(d) for d in dims] + [str(R), str(Q), "itf-layer"]
+    v = subprocess.run(vargs, capture_output=True, text=True, timeout=600)
+    assert v.returncode == 0 and "ACCEPT" in v.stdout, v.stdout + v.stderr
+    if dims[1] <= 32:
+        for pos in (40, len(got) // 3, len(got) - 50):
+            bad = bytearray(got)
+            bad[pos] ^= 1
+            open(outp, "wb").write(bytes(bad))
+            v = subprocess.run(vargs, capture_output=True, text=True, timeout=600)
+            assert v.returncode == 1 and "REJECT" in v.stdout, (pos, v.stdout, v.stderr)
+        open(outp, "wb").write(got)
+        pubp = outp + ".pub"
+        pb = bytearray(open(pubp, "rb").read())
+        keep = bytes(pb)
+        pb[320] ^= 1                                  # first element of the public output grid
+        open(pubp, "wb").write(bytes(pb))
+        v = subprocess.run(vargs, capture_output=True, text=True, timeout=600)
+        assert v.returncode == 1 and "REJECT" in v.stdout
+        open(pubp, "wb").write(keep)
+        gold = os.environ.get("ZKH_WRITE_LAYER_GOLDEN")
+        if gold and dims[0] == 4:                     # fixture for the CPU test of the verifier (tests/golden/make_itf_layer_golden.py)
+            os.makedirs(gold, exist_ok=True)
+            for src, name in ((inp, "in.i32"), (outp, "proof.bin"), (pubp, "proof.bin.pub")):
+                open(os.path.join(gold, name), "wb").write(open(src, "rb").read())
     # the Python host over the same library
     w = ig_dev.itf_build_witness(c, x0, Wt, T, engine=prover)
     ident = lambda a: a

@@ -1,5 +1,5 @@
 """One decoder layer (p3itf::prove, non-zk) through the host logic in zk_hillclimb_b200.ig on CPU: witness chain,
-commitments, 26 + 2A sub-proofs, merged lookups, public I/O bindings and batched openings; the proof must be
+commitments, 24 + 2A sub-proofs, merged lookups, public I/O bindings and batched openings; the proof must be
 accepted by the reference's own host-only layer verifier on the same transcript."""
 import numpy as np
 import pytest
@@ -8,7 +8,7 @@ from ig_helpers import OracleGadgetEngine, StridedMatmulEngine, arr, layer_input
 
 
 @pytest.mark.parametrize("dims", [(4, 8, 2, 4, 16, 1), (4, 8, 2, 4, 8, 2)])
-def test_layer_accepted_by_reference_verifier(orc, ref, zk, dims):
+def test_layer_accepted_by_reference_verifier(tmp_path, orc, ref, zk, dims):
     R, Q = 1, 24
     ig = zk.ig
     c = ig.Config(*dims)
@@ -33,6 +33,40 @@ def test_layer_accepted_by_reference_verifier(orc, ref, zk, dims):
         bad = bytearray(pf)
         bad[off] ^= 1
         assert not ref_itf_verify(ref, st0, c, x0, o["x0"][1], wroots, Wt, w["out"], R, Q, bytes(bad))[0]
+    native_layer_verifier_agrees(tmp_path, dims, x0, Wt, o, w, pf, R, Q)
+
+
+def native_layer_verifier_agrees(tmp_path, dims, x0, Wt, o, w, pf, R, Q):
+    """The C++ host verifier (include/zkh_p3_layer_verify.hpp through the program zkh_p3_layer; no GPU, no reference) gives the
+    reference verifier's answers on the same proof: accept, and reject for a wrong output, a wrong weight root, a flipped byte."""
+    import os
+    import subprocess
+    from test_cxx_layer_gpu import EXE, write_inputs
+    if not os.path.exists(EXE):
+        pytest.skip("zkh_p3_layer not built")
+    inp, outp = str(tmp_path / "in.i32"), str(tmp_path / "proof.bin")
+    write_inputs(inp, x0, Wt)
+    roots = [o["x0"][1]] + [x[1] for x in o["w"]] + [o["g1"][1], o["g2"][1]]
+    pub = b"".join(roots) + np.ascontiguousarray(w["out"], dtype=np.uint64).tobytes()
+    args = [EXE, "verify", inp, outp] + [str(d) for d in dims] + [str(R), str(Q), "itf-layer"]
+
+    def run(proof, pubdata):
+        open(outp, "wb").write(proof)
+        open(outp + ".pub", "wb").write(pubdata)
+        r = subprocess.run(args, capture_output=True, text=True, timeout=600)
+        assert r.returncode in (0, 1), r.stderr
+        return r.returncode == 0, r.stdout.strip()
+    ok, why = run(pf, pub)
+    assert ok, why
+    bad_pub = bytearray(pub)
+    bad_pub[320 + 3 * 8] ^= 1                       # public output entry 3
+    assert not run(pf, bytes(bad_pub))[0]
+    swapped = b"".join([roots[0]] + roots[2:8] + roots[1:2] + roots[8:]) + pub[320:]
+    assert not run(pf, swapped)[0]
+    for off in (30, len(pf) // 2, len(pf) - 9):
+        bad = bytearray(pf)
+        bad[off] ^= 1
+        assert not run(bytes(bad), pub)[0]
 
 
 def _flat(v):

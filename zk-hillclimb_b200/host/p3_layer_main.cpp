@@ -5,7 +5,12 @@
 // "<seed>-<l>"); workers > 1 keeps that many proofs in flight, each on its own host thread, library context and stream;
 // warmup = 1 lets every worker prove one untimed layer first (table uploads, workspace growth, the allocator's pool) and starts
 // the clock when all are done.  The last line reports the wall time per layer of the timed pass (upload of the inputs from
-// page-locked memory, witness chain, commitments, proof).  The GPU is device $ZKH_DEVICE (default 0).
+// page-locked memory, witness chain, commitments, proof).  The GPU is device $ZKH_DEVICE (default 0).  Beside the proof it writes
+// <proof.bin>.pub: the commitment roots of the input, the seven weights and the two gains (10 x 32 bytes), then the output grid
+// (field elements), i.e. what a verifier holds besides the public input and the RoPE tables.
+//   zkh_p3_layer verify <inputs.i32> <proof.bin> <seq> <d> <nh> <dh> <dff> <batch> <R> <Q> <transcript seed>
+// checks the proof on the host (no GPU work) against x0 and the RoPE tables of inputs.i32 and <proof.bin>.pub; prints ACCEPT or
+// REJECT <reason>; exit code 0 / 1.
 // inputs.i32: x0 (seq*batch*d) | the seven weights Wq Wk Wv Wo (d*d each) Wg Wu (d*dff) Wd (dff*d) | g1 g2 (d) | cos, sin tables
 // (seq * dh/2 each), all little-endian int32.  Exit code 0 on success, 2 on a usage or I/O error, 3 on a library error.
 #include <chrono>
@@ -13,10 +18,11 @@
 #include <cstdlib>
 #include <atomic>
 #include <fstream>
+#include <iterator>
 #include <mutex>
 #include <thread>
 
-#include "zkh_p3_layer.hpp"
+#include "zkh_p3_layer_verify.hpp"
 
 using namespace zkh_p3;
 
@@ -25,7 +31,56 @@ static bool read_i32(std::ifstream& f, HostI32& v) {
     return (size_t)f.gcount() == v.size() * 4;
 }
 
+static int verify_main(int argc, char** argv) {
+    if (argc < 13) { fprintf(stderr, "usage: %s verify <inputs.i32> <proof.bin> <seq> <d> <nh> <dh> <dff> <batch> <R> <Q> <seed>\n", argv[0]); return 2; }
+    const ItfConfig c((uint32_t)atoi(argv[4]), (uint32_t)atoi(argv[5]), (uint32_t)atoi(argv[6]), (uint32_t)atoi(argv[7]), (uint32_t)atoi(argv[8]),
+                      (uint32_t)atoi(argv[9]));
+    const uint32_t R = (uint32_t)atoi(argv[10]), Q = (uint32_t)atoi(argv[11]);
+    auto slurp = [](const std::string& path, std::vector<uint8_t>& b) {
+        std::ifstream f(path, std::ios::binary);
+        if (!f) return false;
+        b.assign(std::istreambuf_iterator<char>(f), std::istreambuf_iterator<char>());
+        return true;
+    };
+    std::vector<uint8_t> in, proof, pubb;
+    if (!slurp(argv[2], in) || !slurp(argv[3], proof) || !slurp(std::string(argv[3]) + ".pub", pubb)) { fprintf(stderr, "cannot read the inputs\n"); return 2; }
+    const size_t ne = (size_t)c.seq * c.batch * c.d, nt = (size_t)c.seq * c.dh / 2;
+    size_t wsum = 0;
+    for (int i = 0; i < 7; i++) wsum += c.wrows(i) * c.wcols(i);
+    if (in.size() < (ne + wsum + 2 * c.d + 2 * nt) * 4 || pubb.size() != 320 + ne * 8) { fprintf(stderr, "input files do not match the configuration\n"); return 2; }
+    const int32_t* iv = reinterpret_cast<const int32_t*>(in.data());
+    zkh_p3v::ItfPublic pub;
+    pub.x0.resize(ne);
+    for (size_t k = 0; k < ne; k++) pub.x0[k] = zkh_p3v::lift(iv[k]);
+    const int32_t* tabs = iv + ne + wsum + 2 * c.d;
+    pub.ct.assign(tabs, tabs + nt);
+    pub.st.assign(tabs + nt, tabs + 2 * nt);
+    const uint8_t* q = pubb.data();
+    memcpy(pub.rX0.data(), q, 32);
+    for (int i = 0; i < 7; i++) memcpy(pub.rW[i].data(), q + 32 * (1 + i), 32);
+    memcpy(pub.rG1.data(), q + 256, 32);
+    memcpy(pub.rG2.data(), q + 288, 32);
+    pub.out.resize(ne);
+    memcpy(pub.out.data(), q + 320, ne * 8);
+    for (gl_t v : pub.out)
+        if (v >= GL_P) { printf("REJECT output grid not canonical\n"); return 1; }
+    IgTables T(c.d, c.btop);
+    Transcript tr(argv[12]);
+    const zkh_p3v::Verdict vd = zkh_p3v::guarded([&] { return zkh_p3v::itf_verify(tr, zkh_p3v::Reader(proof), c, T, pub, R, Q); });
+    if (vd) { printf("ACCEPT\n"); return 0; }
+    printf("REJECT %s\n", vd.why.c_str());
+    return 1;
+}
+
 int main(int argc, char** argv) {
+    if (argc > 1 && std::string(argv[1]) == "verify") {
+        try {
+            return verify_main(argc, argv);
+        } catch (const std::exception& e) {
+            fprintf(stderr, "zkh_p3_layer verify: %s\n", e.what());
+            return 3;
+        }
+    }
     if (argc < 12) {
         fprintf(stderr, "usage: %s <inputs.i32> <proof.bin> <seq> <d> <nh> <dh> <dff> <batch> <R> <Q> <seed> [repeats]\n", argv[0]);
         return 2;
@@ -47,7 +102,7 @@ int main(int argc, char** argv) {
         for (int i = 0; i < 7 && ok; i++) ok = read_i32(f, in.w[i]);
         ok = ok && read_i32(f, in.g1) && read_i32(f, in.g2) && read_i32(f, in.ct) && read_i32(f, in.st);
         if (!ok) { fprintf(stderr, "%s is shorter than the configuration needs\n", argv[1]); return 2; }
-        std::vector<uint8_t> proof;
+        std::vector<uint8_t> proof, pubdata;
         std::mutex mu;
         std::atomic<int> next{0}, ready{0};
         std::chrono::steady_clock::time_point w0;
@@ -84,7 +139,15 @@ int main(int argc, char** argv) {
                     printf("{\"layer\": %d, \"worker\": %d, \"witness_ms\": %.3f, \"commit_ms\": %.3f, \"prove_ms\": %.3f, \"proof_bytes\": %zu}\n", rep, id,
                            ms(t0, t1), ms(t1, t2), ms(t2, t3), pf.size());
                     fflush(stdout);
-                    if (rep == 0) proof.swap(pf);
+                    if (rep == 0) {
+                        proof.swap(pf);
+                        const CCol* rr[10] = {&o.x0, &o.w[0], &o.w[1], &o.w[2], &o.w[3], &o.w[4], &o.w[5], &o.w[6], &o.g1, &o.g2};
+                        pubdata.clear();
+                        for (const CCol* r : rr) pubdata.insert(pubdata.end(), r->root.begin(), r->root.end());
+                        const std::vector<gl_t> og = w.out.to_host();
+                        const uint8_t* ob = reinterpret_cast<const uint8_t*>(og.data());
+                        pubdata.insert(pubdata.end(), ob, ob + og.size() * 8);
+                    }
                 }
             } catch (const std::exception& e) {
                 std::lock_guard<std::mutex> lk(mu);
@@ -103,6 +166,9 @@ int main(int argc, char** argv) {
         std::ofstream g(argv[2], std::ios::binary);
         g.write(reinterpret_cast<const char*>(proof.data()), (std::streamsize)proof.size());
         if (!g) { fprintf(stderr, "cannot write %s\n", argv[2]); return 2; }
+        std::ofstream gp(std::string(argv[2]) + ".pub", std::ios::binary);
+        gp.write(reinterpret_cast<const char*>(pubdata.data()), (std::streamsize)pubdata.size());
+        if (!gp) { fprintf(stderr, "cannot write %s.pub\n", argv[2]); return 2; }
         return 0;
     } catch (const std::exception& e) {
         fprintf(stderr, "zkh_p3_layer: %s\n", e.what());

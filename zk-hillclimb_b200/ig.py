@@ -650,7 +650,7 @@ def itf_commit_all(engine, w, Wt, R, col):
 def itf_prove(engine, tr, c, w, o, Wt, T, R, Q, col):
     """p3itf::prove (p3_int_layer.cuh:452-581), non-zk: all sub-proofs in fixed order on one transcript with one
     ledger and one lookup queue, one merged-lookup flush, the public input/output bindings, one batched opening per
-    size class.  Returns the serialised TfProof: 6 x u32 dims | 26 + 2A length-prefixed sub-proofs in proving order |
+    size class.  Returns the serialised TfProof: 6 x u32 dims | 24 + 2A length-prefixed sub-proofs in proving order |
     28 roots | u32 groups (len, GroupProof)* | ioin ioout | u32 batches (len, BatchProof)*."""
     ld, lT, ldff, lseq, ldh, la = c.ld, c.lT, c.ldff, c.lseq, c.ldh, c.la
     le, lef, lez = ld + lT, ldff + lT, la + 2 * lseq

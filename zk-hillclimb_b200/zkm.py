@@ -938,7 +938,7 @@ def itf_commit_all(engine, zc, c, w, Wt, R, col):
 
 
 def itf_prove(engine, zc, tr, c, w, o, Wt, T, R, Q, col, stages=None):
-    """p3itf::prove with the zk switch on (zkllm-src/p3_int_layer.cuh:452-581): the decoder layer's 26 + 2A sub-proofs in fixed
+    """p3itf::prove with the zk switch on (zkllm-src/p3_int_layer.cuh:452-581): the decoder layer's 24 + 2A sub-proofs in fixed
     order on one transcript with one ledger and one lookup queue, one merged-lookup flush, the public input / output
     bindings at zero-extended points, one blinded batched opening per size class.  Same serialised layout as the plain
     layer proof, every part in its hiding form."""
