@@ -539,6 +539,15 @@ ZKH_API int zkh_fr_mul_throughput(zkh_ctx* ctx, uint32_t iters, double* gmul_per
 ZKH_API int zkh_fr_sumcheck(zkh_ctx* ctx, const void* const* cols_dev, int nc, uint32_t logn,
                     const char* const* labels, uint8_t state[32], void* evals, void* chals, void* finals);
 
+/* ---- BLS12-381 G1: Pedersen row commitments of the first proof stack (zkllm-src/commitment.cu:41-103,
+ *      Commitment::commit -> commit_pippenger) ----
+ * out[r] = sum_i scalars[r][i] * gens[i] for m rows of n scalars.  gens, out: the reference's G1Jacobian_t (144 bytes: X, Y, Z,
+ * each twelve 32-bit limbs in Montgomery form); scalars: the reference's Fr_t (32 bytes), whose RAW limbs are the multiplier,
+ * as in the reference.  The sums are formed in the reference's order (4-bit windows, buckets filled in generator order,
+ * running sum from bucket 15, Horner from the top window), so the Jacobian triples equal the reference's byte for byte.
+ * All buffers on the device, 16-byte aligned.  Stream-ordered. */
+ZKH_API int zkh_g1_pedersen_commit(zkh_ctx* ctx, const void* gens_dev, const void* scalars_dev, uint32_t m, uint32_t n, void* out_dev);
+
 #ifdef __cplusplus
 }
 #endif

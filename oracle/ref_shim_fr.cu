@@ -199,4 +199,18 @@ int refA_lookup(uint8_t st[32], const uint32_t* S, const uint32_t* T, const uint
     } catch (...) { return -1; }
 }
 
+// Pedersen row commitments of the reference (Commitment::random / Commitment::commit, zkllm-src/commitment.cu:3-8, :41-103):
+// generators and commitments as the reference's 144-byte Jacobian triples
+int refA_commit_random(uint32_t n, uint8_t* gens_out) {
+    Commitment g = Commitment::random(n);
+    cudaMemcpy(gens_out, g.gpu_data, (size_t)n * sizeof(G1Jacobian_t), cudaMemcpyDeviceToHost);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int refA_pedersen_commit(const uint8_t* gens, uint32_t n, const uint32_t* scalars, uint32_t m, uint8_t* out) {
+    Commitment g(n, (const G1Jacobian_t*)gens);
+    FrTensor t(m * n, (const Fr_t*)scalars);
+    G1TensorJacobian c = g.commit(t);
+    cudaMemcpy(out, c.gpu_data, (size_t)m * sizeof(G1Jacobian_t), cudaMemcpyDeviceToHost);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
 }  // extern "C"

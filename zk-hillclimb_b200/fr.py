@@ -161,3 +161,12 @@ def mul_throughput(prover, iters=4096):
     out = C.c_double(0)
     prover._ck(prover._L.zkh_fr_mul_throughput(prover._h, iters, C.byref(out)))
     return out.value
+
+
+def g1_pedersen_commit(prover, gens, scalars, m, n):
+    """Commitment::commit (zkllm-src/commitment.cu:41-103): m row commitments over n generators.  gens: uint8 device tensor of
+    n * 144 bytes (Jacobian triples), scalars: packed Fr tensor of m * n elements (pack / to_device); returns m * 144 bytes."""
+    import torch
+    out = torch.empty(m * 144, dtype=torch.uint8, device=gens.device)
+    prover._ck(prover._L.zkh_g1_pedersen_commit(prover._h, gens.data_ptr(), scalars.data_ptr(), m, n, out.data_ptr()))
+    return out
