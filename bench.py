@@ -555,6 +555,34 @@ def run_suite_fr(args):
                      "same_transcript": bool(st == hold["st"] and ev == hold["sc"][0] and fin == hold["sc"][2])})
     print(json.dumps(line), flush=True)
 
+    # Pedersen row commitments of the weight matrix (Commitment::commit): 1024 rows over 1024 generators
+    import ctypes as C
+    m_, n_ = 1024, 1024
+    sc = rng.integers(0, 1 << 32, (m_ * n_, 8), dtype=np.uint64).astype(np.uint32)
+    sc[:, 7] %= 0x73EDA753
+    if refA is not None and hasattr(refA.lib, "refA_pedersen_commit"):
+        gens = (C.c_uint8 * (n_ * 144))()
+        refA.lib.refA_commit_random(C.c_uint32(n_), gens)
+        gens_b = bytes(gens)
+    else:
+        import g1_oracle as g1
+        gens_b = b"".join(g1.to_bytes(g1.scalar_mul(g1.GEN, 3 + 2 * k)) for k in range(n_))
+    gd = torch.from_numpy(np.frombuffer(gens_b, dtype=np.uint8).copy()).cuda()
+    sd = torch.from_numpy(sc.reshape(-1).view(np.int32)).cuda()
+    hold = {}
+
+    def ped():
+        hold["out"] = fr.g1_pedersen_commit(prover, gd, sd, m_, n_)
+    ms = wall(ped)
+    line = {"suite": "Pedersen row commitments over BLS12-381 G1: 1024 rows x 1024 generators (the reference's bucket method and addition order)", "ms": ms}
+    if refA is not None and hasattr(refA.lib, "refA_pedersen_commit"):
+        want = (C.c_uint8 * (m_ * 144))()
+        rms = C.c_double(0)
+        refA.lib.refA_pedersen_commit(gens, C.c_uint32(n_), sc.ctypes.data_as(C.c_void_p), C.c_uint32(m_), want, C.byref(rms))
+        line.update({"reference_cuda_ms": rms.value, "speedup_vs_reference_cuda": rms.value / ms,
+                     "same_bytes": bool(hold["out"].cpu().numpy().tobytes() == bytes(want))})
+    print(json.dumps(line), flush=True)
+
 
 def run_profile_case(args):
     """--profile-case NAME: one small, self-terminating invocation of one kernel family (a few hundred MB on

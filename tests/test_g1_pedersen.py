@@ -69,7 +69,7 @@ def test_kernels_match_reference_kernels(zk, prover, m, n):
     rnd = random.Random(5)
     sc = _pack_scalars(_scalars(rnd, m, n))
     want = (C.c_uint8 * (m * 144))()
-    assert lib.refA_pedersen_commit(gens, C.c_uint32(n), sc.ctypes.data_as(C.c_void_p), C.c_uint32(m), want) == 0
+    assert lib.refA_pedersen_commit(gens, C.c_uint32(n), sc.ctypes.data_as(C.c_void_p), C.c_uint32(m), want, None) == 0
     gd = torch.from_numpy(np.frombuffer(bytes(gens), dtype=np.uint8).copy()).cuda()
     sd = torch.from_numpy(sc.view(np.int32)).cuda()
     out = zk.fr.g1_pedersen_commit(prover, gd, sd, m, n)

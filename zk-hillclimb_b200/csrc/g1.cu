@@ -4,11 +4,8 @@
 // The reference's bucket method fixes the Jacobian representative of every commitment: 4-bit windows of the scalar's raw limbs,
 // per (row, window) sixteen buckets filled in generator order, the running-sum reduction from bucket 15 down to 1, windows
 // combined by Horner from the top.  The files the orchestrator compares byte by byte hold those triples, so the same sums are
-// formed in the same order here; what changes is who does them.  The reference gives one thread a whole (row, window) with its
-// sixteen buckets in local memory (m * 64 threads).  Buckets of one window never interact before the running sum, so here one
-// thread owns ONE bucket of one (row, window): m * 64 * 15 threads, each scanning the row's digits and adding the generators
-// that fall into its bucket (in generator order, as the reference does), then m * 64 threads do the running sums and m threads
-// the Horner step.  Integer-pipe bound (a Jacobian addition is sixteen 384-bit Montgomery products).
+// formed in the same order here: one thread per (row, window) with its sixteen buckets in local memory (m * 64 threads), then
+// one thread per row for the Horner step.  Integer-pipe bound (a Jacobian addition is sixteen 384-bit Montgomery products).
 #include "common.cuh"
 #include "g1.cuh"
 
@@ -36,28 +33,25 @@ __device__ __forceinline__ G1 g1_load(const G1* p) {
     fp_load(r.z, q + 6);
     return r;
 }
-// thread = (row, window, bucket b in 1..15): bucket[b] = sum in generator order of the generators whose digit is b
-__global__ void __launch_bounds__(128) pedersen_bucket_kernel(const G1* __restrict__ gen, const uint32_t* __restrict__ scalars,
-                                                              G1* __restrict__ buckets, uint32_t m, uint32_t n) {
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (tid >= (size_t)m * PIP_W * (PIP_NB - 1)) return;
-    const uint32_t b = 1 + (uint32_t)(tid % (PIP_NB - 1));
-    const size_t rw = tid / (PIP_NB - 1);
+// thread = (row, window), as in the reference: sixteen buckets in local memory filled in generator order, then
+// sum_b b * bucket[b] by the running-sum trick from bucket 15 down.  (A thread per BUCKET gives fifteen times the threads but at
+// every generator only one of a window's fifteen bucket threads has work: two active lanes per warp, measured 13x slower.)
+__global__ void __launch_bounds__(64, 7) pedersen_bucket_kernel(const G1* __restrict__ gen, const uint32_t* __restrict__ scalars,
+                                                             G1* __restrict__ partials, uint32_t m, uint32_t n) {
+    const size_t rw = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (rw >= (size_t)m * PIP_W) return;
     const uint32_t w = (uint32_t)(rw % PIP_W);
     const size_t row = rw / PIP_W;
     const uint32_t* srow = scalars + row * (size_t)n * 8;
-    G1 acc = g1_zero();
-    for (uint32_t i = 0; i < n; i++)
-        if (pip_digit(srow + (size_t)i * 8, w) == b) acc = g1_add(acc, g1_load(gen + i));
-    buckets[rw * PIP_NB + b] = acc;
-}
-// thread = (row, window): sum_b b * bucket[b] by the running-sum trick, bucket 15 first
-__global__ void __launch_bounds__(128) pedersen_window_kernel(const G1* __restrict__ buckets, G1* __restrict__ partials, size_t nrw) {
-    const size_t rw = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (rw >= nrw) return;
+    G1 bucket[PIP_NB];
+    for (uint32_t b = 0; b < PIP_NB; b++) bucket[b] = g1_zero();
+    for (uint32_t i = 0; i < n; i++) {
+        const uint32_t d = pip_digit(srow + (size_t)i * 8, w);
+        if (d) bucket[d] = g1_add(bucket[d], g1_load(gen + i));
+    }
     G1 acc = g1_zero(), run = g1_zero();
     for (int b = (int)PIP_NB - 1; b >= 1; b--) {
-        acc = g1_add(acc, g1_load(buckets + rw * PIP_NB + b));
+        acc = g1_add(acc, bucket[b]);
         run = g1_add(run, acc);
     }
     partials[rw] = run;
@@ -85,13 +79,9 @@ extern "C" int zkh_g1_pedersen_commit(zkh_ctx* c, const void* gens_dev, const vo
         return zkh_fail(c, ZKH_ERR_ARG, "g1_pedersen_commit: buffers must be 16-byte aligned");
     ZKH_CUDA(c, cudaSetDevice(c->device));
     const size_t nrw = (size_t)m * PIP_W;
-    const size_t bk = zkh_align(nrw * PIP_NB * sizeof(G1)), pt = zkh_align(nrw * sizeof(G1));
-    ZKH_TRY(zkh_ws_reserve(c, bk + pt));
-    G1* buckets = (G1*)c->ws;
-    G1* partials = (G1*)((char*)c->ws + bk);
-    const size_t nthr = nrw * (PIP_NB - 1);
-    pedersen_bucket_kernel<<<(unsigned)((nthr + 127) / 128), 128, 0, c->stream>>>((const G1*)gens_dev, (const uint32_t*)scalars_dev, buckets, m, n);
-    pedersen_window_kernel<<<(unsigned)((nrw + 127) / 128), 128, 0, c->stream>>>(buckets, partials, nrw);
+    ZKH_TRY(zkh_ws_reserve(c, zkh_align(nrw * sizeof(G1))));
+    G1* partials = (G1*)c->ws;
+    pedersen_bucket_kernel<<<(unsigned)((nrw + 63) / 64), 64, 0, c->stream>>>((const G1*)gens_dev, (const uint32_t*)scalars_dev, partials, m, n);
     pedersen_combine_kernel<<<(m + 63) / 64, 64, 0, c->stream>>>(partials, (G1*)out_dev, m);
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;

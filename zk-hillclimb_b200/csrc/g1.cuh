@@ -84,42 +84,91 @@ __device__ __forceinline__ Fp fp_sub(const Fp& a, const Fp& b) {
     }
     return r;
 }
-// Montgomery product a * b / 2^384 mod p, operand scanning with the reduction interleaved (CIOS)
+// t[0..13] += x[0..11] * y.  Two carry chains: the products of the even limbs occupy limb pairs (0,1) .. (10,11), those of the odd
+// limbs (1,2) .. (11,12); inside a chain every low half is followed by the high half of the same product.
+__device__ __forceinline__ void fp_row_mad(uint32_t (&t)[14], const uint32_t (&x)[12], uint32_t y) {
+    asm(
+        "mad.lo.cc.u32 %0, %14, %26, %0;\n\t"
+        "madc.hi.cc.u32 %1, %14, %26, %1;\n\t"
+        "madc.lo.cc.u32 %2, %16, %26, %2;\n\t"
+        "madc.hi.cc.u32 %3, %16, %26, %3;\n\t"
+        "madc.lo.cc.u32 %4, %18, %26, %4;\n\t"
+        "madc.hi.cc.u32 %5, %18, %26, %5;\n\t"
+        "madc.lo.cc.u32 %6, %20, %26, %6;\n\t"
+        "madc.hi.cc.u32 %7, %20, %26, %7;\n\t"
+        "madc.lo.cc.u32 %8, %22, %26, %8;\n\t"
+        "madc.hi.cc.u32 %9, %22, %26, %9;\n\t"
+        "madc.lo.cc.u32 %10, %24, %26, %10;\n\t"
+        "madc.hi.cc.u32 %11, %24, %26, %11;\n\t"
+        "addc.cc.u32 %12, %12, 0;\n\t"
+        "addc.u32 %13, %13, 0;\n\t"
+        "mad.lo.cc.u32 %1, %15, %26, %1;\n\t"
+        "madc.hi.cc.u32 %2, %15, %26, %2;\n\t"
+        "madc.lo.cc.u32 %3, %17, %26, %3;\n\t"
+        "madc.hi.cc.u32 %4, %17, %26, %4;\n\t"
+        "madc.lo.cc.u32 %5, %19, %26, %5;\n\t"
+        "madc.hi.cc.u32 %6, %19, %26, %6;\n\t"
+        "madc.lo.cc.u32 %7, %21, %26, %7;\n\t"
+        "madc.hi.cc.u32 %8, %21, %26, %8;\n\t"
+        "madc.lo.cc.u32 %9, %23, %26, %9;\n\t"
+        "madc.hi.cc.u32 %10, %23, %26, %10;\n\t"
+        "madc.lo.cc.u32 %11, %25, %26, %11;\n\t"
+        "madc.hi.cc.u32 %12, %25, %26, %12;\n\t"
+        "addc.u32 %13, %13, 0;"
+        : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]), "+r"(t[4]), "+r"(t[5]), "+r"(t[6]), "+r"(t[7]), "+r"(t[8]), "+r"(t[9]), "+r"(t[10]), "+r"(t[11]), "+r"(t[12]), "+r"(t[13])
+        : "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(x[4]), "r"(x[5]), "r"(x[6]), "r"(x[7]), "r"(x[8]), "r"(x[9]), "r"(x[10]), "r"(x[11]), "r"(y));
+}
+// Montgomery product a * b / 2^384 mod p, operand scanning with the reduction interleaved
 __device__ __noinline__ Fp fp_mul(const Fp& a, const Fp& b) {
     uint32_t t[14];
 #pragma unroll
     for (int i = 0; i < 14; i++) t[i] = 0;
+    uint32_t pl[12], av[12];
+#pragma unroll
+    for (int i = 0; i < 12; i++) { pl[i] = FP_P.v[i]; av[i] = a.v[i]; }
 #pragma unroll
     for (int i = 0; i < 12; i++) {
-        uint64_t c = 0;
-#pragma unroll
-        for (int j = 0; j < 12; j++) {
-            c += (uint64_t)a.v[j] * b.v[i] + t[j];
-            t[j] = (uint32_t)c;
-            c >>= 32;
-        }
-        c += t[12];
-        t[12] = (uint32_t)c;
-        t[13] = (uint32_t)(c >> 32);
+        fp_row_mad(t, av, b.v[i]);
         const uint32_t m = t[0] * ZKH_FP_INV;
-        c = (uint64_t)m * FP_P.v[0] + t[0];
-        c >>= 32;
+        fp_row_mad(t, pl, m);              // now t[0] == 0
 #pragma unroll
-        for (int j = 1; j < 12; j++) {
-            c += (uint64_t)m * FP_P.v[j] + t[j];
-            t[j - 1] = (uint32_t)c;
-            c >>= 32;
-        }
-        c += t[12];
-        t[11] = (uint32_t)c;
-        t[12] = t[13] + (uint32_t)(c >> 32);
+        for (int j = 0; j < 13; j++) t[j] = t[j + 1];
+        t[13] = 0;
     }
     Fp r;
 #pragma unroll
     for (int i = 0; i < 12; i++) r.v[i] = t[i];
-    return fp_gte_p(r) ? fp_sub_p(r) : r;
+    return fp_gte_p(r) ? fp_sub_p(r) : r;  // t < 2p < 2^383: t[12] == 0 here
 }
 __device__ __forceinline__ Fp fp_sqr(const Fp& a) { return fp_mul(a, a); }
+// two independent products in one pass: r0 = a0 * b0, r1 = a1 * b1.  A Montgomery product is one long dependent chain of
+// multiply-adds (each waits for the carry of the one before); two of them side by side give the scheduler a second chain
+// to issue from while the first waits.
+__device__ __noinline__ void fp_mul2(Fp& r0, Fp& r1, const Fp& a0, const Fp& b0, const Fp& a1, const Fp& b1) {
+    uint32_t t[14], u[14];
+#pragma unroll
+    for (int i = 0; i < 14; i++) { t[i] = 0; u[i] = 0; }
+    uint32_t pl[12], av[12], cv[12];
+#pragma unroll
+    for (int i = 0; i < 12; i++) { pl[i] = FP_P.v[i]; av[i] = a0.v[i]; cv[i] = a1.v[i]; }
+#pragma unroll
+    for (int i = 0; i < 12; i++) {
+        fp_row_mad(t, av, b0.v[i]);
+        fp_row_mad(u, cv, b1.v[i]);
+        const uint32_t m = t[0] * ZKH_FP_INV, k = u[0] * ZKH_FP_INV;
+        fp_row_mad(t, pl, m);
+        fp_row_mad(u, pl, k);
+#pragma unroll
+        for (int j = 0; j < 13; j++) { t[j] = t[j + 1]; u[j] = u[j + 1]; }
+        t[13] = 0;
+        u[13] = 0;
+    }
+    Fp x, y;
+#pragma unroll
+    for (int i = 0; i < 12; i++) { x.v[i] = t[i]; y.v[i] = u[i]; }
+    r0 = fp_gte_p(x) ? fp_sub_p(x) : x;
+    r1 = fp_gte_p(y) ? fp_sub_p(y) : y;
+}
 
 __device__ __forceinline__ G1 g1_zero() {
     G1 r;
@@ -135,15 +184,18 @@ __device__ __noinline__ G1 g1_double(const G1& p) {
         r = p;
         return r;
     }
-    const Fp a = fp_sqr(p.x), b = fp_sqr(p.y);
-    Fp c = fp_sqr(b);
-    Fp d = fp_sqr(fp_add(p.x, b));
-    d = fp_double(fp_sub(fp_sub(d, a), c));
-    const Fp e = fp_add(fp_double(a), a), f = fp_sqr(e);
-    r.z = fp_double(fp_mul(p.y, p.z));
+    Fp a, b, c, d, f, yz, t;
+    fp_mul2(a, b, p.x, p.x, p.y, p.y);                 // A = X1^2, B = Y1^2
+    const Fp xb = fp_add(p.x, b);
+    fp_mul2(c, d, b, b, xb, xb);                       // C = B^2, (X1 + B)^2
+    d = fp_double(fp_sub(fp_sub(d, a), c));            // D = 2 ((X1 + B)^2 - A - C)
+    const Fp e = fp_add(fp_double(a), a);              // E = 3 A
+    fp_mul2(f, yz, e, e, p.y, p.z);                    // F = E^2, Y1 Z1
+    r.z = fp_double(yz);
     r.x = fp_sub(fp_sub(f, d), d);
     c = fp_double(fp_double(fp_double(c)));
-    r.y = fp_sub(fp_mul(fp_sub(d, r.x), e), c);
+    t = fp_mul(fp_sub(d, r.x), e);
+    r.y = fp_sub(t, c);
     return r;
 }
 // add-2007-bl with the reference's early returns (zkllm-src/bls12-381.cu:1429-1464)
@@ -157,22 +209,21 @@ __device__ __noinline__ G1 g1_add(const G1& a, const G1& b) {
         r = a;
         return r;
     }
-    const Fp z1z1 = fp_sqr(a.z), z2z2 = fp_sqr(b.z);
-    const Fp u1 = fp_mul(a.x, z2z2), u2 = fp_mul(b.x, z1z1);
-    Fp s1 = fp_mul(fp_mul(a.y, b.z), z2z2);
-    const Fp s2 = fp_mul(fp_mul(b.y, a.z), z1z1);
+    Fp z1z1, z2z2, u1, u2, s1, s2, ii, zz, jj, v, r2, sj, t1, t2;
+    fp_mul2(z1z1, z2z2, a.z, a.z, b.z, b.z);
+    fp_mul2(u1, u2, a.x, z2z2, b.x, z1z1);             // U1 = X1 Z2Z2, U2 = X2 Z1Z1
+    fp_mul2(t1, t2, a.y, b.z, b.y, a.z);
+    fp_mul2(s1, s2, t1, z2z2, t2, z1z1);               // S1 = Y1 Z2 Z2Z2, S2 = Y2 Z1 Z1Z1
     if (fp_eq(u1, u2) && fp_eq(s1, s2)) return g1_double(a);
-    const Fp h = fp_sub(u2, u1);
-    const Fp i = fp_sqr(fp_double(h));
-    const Fp j = fp_mul(h, i);
-    const Fp rr = fp_double(fp_sub(s2, s1));
-    const Fp v = fp_mul(u1, i);
-    r.x = fp_sub(fp_sub(fp_sub(fp_sqr(rr), j), v), v);
-    r.y = fp_mul(fp_sub(v, r.x), rr);
-    s1 = fp_double(fp_mul(s1, j));
-    r.y = fp_sub(r.y, s1);
-    r.z = fp_sqr(fp_add(a.z, b.z));
-    r.z = fp_mul(fp_sub(fp_sub(r.z, z1z1), z2z2), h);
+    const Fp h = fp_sub(u2, u1), h2 = fp_double(h), zs = fp_add(a.z, b.z);
+    fp_mul2(ii, zz, h2, h2, zs, zs);                   // I = (2H)^2, (Z1 + Z2)^2
+    fp_mul2(jj, v, h, ii, u1, ii);                     // J = H I, V = U1 I
+    const Fp rr = fp_double(fp_sub(s2, s1));           // r = 2 (S2 - S1)
+    fp_mul2(r2, sj, rr, rr, s1, jj);
+    r.x = fp_sub(fp_sub(fp_sub(r2, jj), v), v);        // X3 = r^2 - J - 2 V
+    fp_mul2(t1, t2, fp_sub(v, r.x), rr, fp_sub(fp_sub(zz, z1z1), z2z2), h);
+    r.y = fp_sub(t1, fp_double(sj));                   // Y3 = r (V - X3) - 2 S1 J
+    r.z = t2;                                          // Z3 = ((Z1 + Z2)^2 - Z1Z1 - Z2Z2) H
     return r;
 }
 #endif  // __CUDACC__
