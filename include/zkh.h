@@ -548,6 +548,33 @@ ZKH_API int zkh_fr_sumcheck(zkh_ctx* ctx, const void* const* cols_dev, int nc, u
  * All buffers on the device, 16-byte aligned.  Stream-ordered. */
 ZKH_API int zkh_g1_pedersen_commit(zkh_ctx* ctx, const void* gens_dev, const void* scalars_dev, uint32_t m, uint32_t n, void* out_dev);
 
+/* ---- BLS12-381 G1: openings of the first proof stack (zkllm-src/vrf_common.cuh) ----
+ * Points are the reference's G1Jacobian_t (144 bytes), scalars its Fr_t (32 bytes, plain integers below the modulus).  The
+ * proof files hold Jacobian triples, so every point below is produced by the reference's own sequence of additions and
+ * doublings (G1Jacobian_mul from the lowest bit up, zkllm-src/g1-tensor.cu:445-453; dev_msm's halving sums) and equals the
+ * reference's byte for byte.  Device buffers 16-byte aligned; results are returned to host memory and the calls synchronise
+ * the stream before they return.
+ *
+ * zkh_g1_msm: <g, a> over n points, n a power of two: dev_msm (vrf_common.cuh:165-184).
+ * zkh_g1_fold_chain: fold_chain (vrf_common.cuh:144-163): nu pair folds of `size` points with the challenges us (host, nu
+ *   scalars); orientation 0 = c[2i] + u (c[2i+1] - c[2i]) (k_com_me, :52-58), 1 = c[2i+1] + u (c[2i] - c[2i+1]) (k_gen_fold,
+ *   :59-65); odd levels are padded with a record of zero bytes as the reference pads them.  out144 = element 0 after the folds.
+ * zkh_g1_ipa_prove: ipa_prove (vrf_common.cuh:302-336), the Fiat-Shamir inner-product argument for P = <g, a> + <a, b> Q:
+ *   log2(n) rounds of L, R under the labels "L", "R", challenge by the reference's limb mapping, folds of a, b, g.  a_dev,
+ *   b_dev: n scalars; g_dev: n points; Q144: host.  state: the caller's transcript state, advanced in place.  L_out, R_out: host,
+ *   log2(n) points each; a_final32: host.  The whole argument runs on the device (transcript included): no host round trip per
+ *   round.
+ * zkh_g1_ipa_verify: ipa_verify (vrf_common.cuh:340-371): replays the transcript, folds P0 with x^2 L + P + x^-2 R, the public
+ *   weights me_weights(u_b) (log2(n) scalars, host) and the generators (through the s-vector product), and sets *accept to 1 iff
+ *   P == a_f g_f + (a_f b_f) Q as group elements.  A rejected proof is ZKH_OK with *accept = 0. */
+ZKH_API int zkh_g1_msm(zkh_ctx* ctx, const void* g_dev, const void* a_dev, uint32_t n, void* out144);
+ZKH_API int zkh_g1_fold_chain(zkh_ctx* ctx, const void* src_dev, uint32_t size, const void* us, uint32_t nu, int orientation,
+                              void* out144);
+ZKH_API int zkh_g1_ipa_prove(zkh_ctx* ctx, const void* a_dev, const void* b_dev, const void* g_dev, const void* Q144, uint32_t n,
+                             uint8_t state[32], void* L_out, void* R_out, void* a_final32);
+ZKH_API int zkh_g1_ipa_verify(zkh_ctx* ctx, const void* g_dev, uint32_t n, const void* Q144, const void* P0_144, const void* u_b,
+                              const void* L, const void* R, const void* a_final32, uint8_t state[32], int* accept);
+
 #ifdef __cplusplus
 }
 #endif

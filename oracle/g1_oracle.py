@@ -115,3 +115,115 @@ def pedersen_commit(gens, scalars):
             acc = add(acc, partial[w])
         out.append(acc)
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Openings of the first proof stack: scalar multiples in the reference's order, its multi-scalar product, the pair-fold
+# chains and the Fiat-Shamir inner-product argument (zkllm-src/vrf_common.cuh).  Scalars are plain integers below the
+# scalar field's modulus; `tr` is oracle/fr_oracle.py's Transcript.
+FR_P = 0x73eda753299d7d483339d80809a1d80553bda402fffe5bfeffffffff00000001
+ZERO_BYTES = (0, 0, 0)          # a record of zero bytes (the reference pads odd fold levels with cudaMemset)
+
+
+def neg(p):
+    """G1Jacobian_minus (zkllm-src/g1-tensor.cu:11-21): (X, 0 - Y, Z)."""
+    return (p[0], (-p[1]) % P, p[2])
+
+
+def jac_mul(p, k):
+    """G1Jacobian_mul (zkllm-src/g1-tensor.cu:445-453): from the lowest bit up, out += a on a set bit, a doubles."""
+    out, a = ZERO, p
+    for i in range(256):
+        if (k >> i) & 1:
+            out = add(out, a)
+        a = double(a)
+    return out
+
+
+def msm_tree(g, a):
+    """dev_msm (vrf_common.cuh:165-184): x[i] = a[i] g[i], then x[i] += x[i + half] while halving; n a power of two."""
+    x = [jac_mul(gi, ai) for gi, ai in zip(g, a)]
+    sz = len(x)
+    while sz > 1:
+        half = sz // 2
+        x = [add(x[i], x[i + half]) for i in range(half)]
+        sz = half
+    return x[0]
+
+
+def fold_chain(c, us, orientation):
+    """fold_chain (vrf_common.cuh:144-163) over k_com_me (orientation 0: c0 + u (c1 - c0)) or k_gen_fold
+    (orientation 1: g1 + u (g0 - g1)), :52-66; odd levels are padded with a record of zero bytes."""
+    c = list(c)
+    for u in us:
+        if len(c) % 2:
+            c.append(ZERO_BYTES)
+        if orientation == 0:
+            c = [add(c[2 * i], jac_mul(add(c[2 * i + 1], neg(c[2 * i])), u)) for i in range(len(c) // 2)]
+        else:
+            c = [add(c[2 * i + 1], jac_mul(add(c[2 * i], neg(c[2 * i + 1])), u)) for i in range(len(c) // 2)]
+    return c[0]
+
+
+def ipa_prove(a, b, g, Q, tr):
+    """ipa_prove (vrf_common.cuh:302-336).  Returns (L, R, a_final); tr is advanced as the reference advances it."""
+    a, b, g = list(a), list(b), list(g)
+    Ls, Rs = [], []
+    while len(a) > 1:
+        h = len(a) // 2
+        ip = lambda x, y: sum(p * q for p, q in zip(x, y)) % FR_P
+        Lp = add(msm_tree(g[h:], a[:h]), jac_mul(Q, ip(a[:h], b[h:])))
+        Rp = add(msm_tree(g[:h], a[h:]), jac_mul(Q, ip(a[h:], b[:h])))
+        tr.absorb("L", to_bytes(Lp))
+        tr.absorb("R", to_bytes(Rp))
+        x = tr.challenge_fr()
+        xi = pow(x, FR_P - 2, FR_P)
+        a = [(x * a[i] + xi * a[i + h]) % FR_P for i in range(h)]
+        b = [(xi * b[i] + x * b[i + h]) % FR_P for i in range(h)]
+        g = [add(jac_mul(g[i], xi), jac_mul(g[i + h], x)) for i in range(h)]
+        Ls.append(Lp)
+        Rs.append(Rp)
+    return Ls, Rs, a[0]
+
+
+def me_weights(u):
+    """me_weights (vrf_common.cuh:205-216): b_k = prod_i (bit i of k ? u[i] : 1 - u[i])."""
+    out = []
+    for k in range(1 << len(u)):
+        w = 1
+        for i, ui in enumerate(u):
+            w = w * (ui if (k >> i) & 1 else (1 - ui)) % FR_P
+        out.append(w)
+    return out
+
+
+def same_point(p, q):
+    """g1_eq (vrf_common.cuh:115-122): p - q is the point at infinity."""
+    return add(p, neg(q))[2] == 0
+
+
+def ipa_verify(g, Q, P0, u_b, Ls, Rs, a_final, tr):
+    """ipa_verify (vrf_common.cuh:340-371): witness-free check of an argument against P0 = <g, a> + <a, b> Q."""
+    rounds = len(Ls)
+    if rounds != len(Rs) or len(g) != 1 << rounds or len(u_b) != rounds:
+        return False
+    b = me_weights(u_b)
+    Pt, xs, xis = P0, [], []
+    for r in range(rounds):
+        tr.absorb("L", to_bytes(Ls[r]))
+        tr.absorb("R", to_bytes(Rs[r]))
+        x = tr.challenge_fr()
+        xi = pow(x, FR_P - 2, FR_P)
+        xs.append(x)
+        xis.append(xi)
+        Pt = add(add(jac_mul(Ls[r], x * x % FR_P), Pt), jac_mul(Rs[r], xi * xi % FR_P))
+        h = len(b) // 2
+        b = [(xi * b[k] + x * b[k + h]) % FR_P for k in range(h)]
+    s = []
+    for i in range(len(g)):
+        w = 1
+        for r in range(rounds):
+            w = w * (xs[r] if (i >> (rounds - 1 - r)) & 1 else xis[r]) % FR_P
+        s.append(w)
+    g_f = msm_tree(g, s)
+    return same_point(Pt, add(jac_mul(g_f, a_final), jac_mul(Q, a_final * b[0] % FR_P)))

@@ -216,4 +216,82 @@ int refA_pedersen_commit(const uint8_t* gens, uint32_t n, const uint32_t* scalar
     cudaMemcpy(out, c.gpu_data, (size_t)m * sizeof(G1Jacobian_t), cudaMemcpyDeviceToHost);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+
+// Openings of the reference (zkllm-src/vrf_common.cuh): dev_msm, fold_chain, ipa_prove and ipa_verify as they stand.
+// Points: 144-byte Jacobian triples; scalars: 32-byte Fr_t; st: the transcript state, advanced in place.
+int refA_msm(const uint8_t* gens, const uint32_t* scalars, uint32_t n, uint8_t* out, double* ms) {
+    Commitment g(n, (const G1Jacobian_t*)gens);
+    FrTensor a(n, (const Fr_t*)scalars);
+    cudaDeviceSynchronize();
+    const double t0 = now_ms();
+    G1Jacobian_t r = dev_msm(g.gpu_data, a.gpu_data, n);
+    if (ms) *ms = now_ms() - t0;
+    memcpy(out, &r, sizeof r);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int refA_fold_chain(const uint8_t* pts, uint32_t size, const uint32_t* us, uint32_t nu, int orientation, uint8_t* out, double* ms) {
+    Commitment c(size, (const G1Jacobian_t*)pts);
+    std::vector<Fr_t> u = vec_from(us, nu);
+    cudaDeviceSynchronize();
+    const double t0 = now_ms();
+    G1Jacobian_t r = fold_chain(c.gpu_data, size, u, orientation);
+    if (ms) *ms = now_ms() - t0;
+    memcpy(out, &r, sizeof r);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int refA_ipa_prove(const uint32_t* a, const uint32_t* b, const uint8_t* gens, const uint8_t* Q, uint32_t n, uint8_t st[32],
+                   uint8_t* L, uint8_t* R, uint32_t* a_final, double* ms) {
+    try {
+        Commitment g(n, (const G1Jacobian_t*)gens);
+        FrTensor av(n, (const Fr_t*)a);
+        std::vector<Fr_t> bv = vec_from(b, n);
+        G1Jacobian_t q; memcpy(&q, Q, sizeof q);
+        fs::Transcript tr = tr_from(st);
+        cudaDeviceSynchronize();
+        const double t0 = now_ms();
+        IpaProof pf = ipa_prove(av.gpu_data, bv, g.gpu_data, q, n, tr);
+        if (ms) *ms = now_ms() - t0;
+        if (!pf.L.empty()) {
+            memcpy(L, pf.L.data(), pf.L.size() * sizeof(G1Jacobian_t));
+            memcpy(R, pf.R.data(), pf.R.size() * sizeof(G1Jacobian_t));
+        }
+        memcpy(a_final, &pf.a_final, 32);
+        memcpy(st, tr.state, 32);
+        return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    } catch (...) { return -1; }
+}
+// single group operations of the reference's host helpers (h_add / subtraction through k_g1_addsub, h_mul)
+int refA_g1_addsub(const uint8_t* a, const uint8_t* b, int sub, uint8_t* out) {
+    G1Jacobian_t x, y, *d, h; memcpy(&x, a, sizeof x); memcpy(&y, b, sizeof y);
+    cudaMalloc(&d, sizeof(G1Jacobian_t));
+    k_g1_addsub<<<1, 1>>>(x, y, sub, d);
+    cudaMemcpy(&h, d, sizeof h, cudaMemcpyDeviceToHost); cudaFree(d);
+    memcpy(out, &h, sizeof h);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int refA_g1_mul(const uint8_t* g, const uint32_t* c, uint8_t* out) {
+    G1Jacobian_t x; Fr_t k; memcpy(&x, g, sizeof x); memcpy(&k, c, 32);
+    G1Jacobian_t h = h_mul(x, k);
+    memcpy(out, &h, sizeof h);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+// returns 1 = accepted, 0 = rejected, -1 = error
+int refA_ipa_verify(const uint8_t* gens, uint32_t n, const uint8_t* Q, const uint8_t* P0, const uint32_t* u_b, uint32_t nu,
+                    const uint8_t* L, const uint8_t* R, uint32_t rounds, const uint32_t* a_final, uint8_t st[32], double* ms) {
+    try {
+        Commitment g(n, (const G1Jacobian_t*)gens);
+        G1Jacobian_t q, p0; memcpy(&q, Q, sizeof q); memcpy(&p0, P0, sizeof p0);
+        IpaProof pf;
+        pf.L.resize(rounds); pf.R.resize(rounds);
+        if (rounds) { memcpy(pf.L.data(), L, rounds * sizeof(G1Jacobian_t)); memcpy(pf.R.data(), R, rounds * sizeof(G1Jacobian_t)); }
+        memcpy(&pf.a_final, a_final, 32);
+        fs::Transcript tr = tr_from(st);
+        cudaDeviceSynchronize();
+        const double t0 = now_ms();
+        const bool ok = ipa_verify(g.gpu_data, n, q, p0, vec_from(u_b, nu), pf, tr);
+        if (ms) *ms = now_ms() - t0;
+        memcpy(st, tr.state, 32);
+        return ok ? 1 : 0;
+    } catch (...) { return -1; }
+}
 }  // extern "C"

@@ -115,6 +115,10 @@ def load_library():
         "zkh_gl_scatter_bits": (i, [vp, vp, u64, u64, vp, u32, vp, u64]),
         "zkh_gl_gather_xor": (i, [vp, vp, u64, u64, vp]),
         "zkh_g1_pedersen_commit": (i, [vp, vp, vp, u32, u32, vp]),
+        "zkh_g1_msm": (i, [vp, vp, vp, u32, vp]),
+        "zkh_g1_fold_chain": (i, [vp, vp, u32, vp, u32, i, vp]),
+        "zkh_g1_ipa_prove": (i, [vp, vp, vp, vp, vp, u32, vp, vp, vp, vp]),
+        "zkh_g1_ipa_verify": (i, [vp, vp, u32, vp, vp, vp, vp, vp, vp, vp, vp]),
         "zkh_gl_lift_i32": (i, [vp, vp, u64, vp]),
         "zkh_gl_lift_i64": (i, [vp, vp, u64, vp]),
         "zkh_ig_causal_mask": (i, [vp, u32, u32, vp]),

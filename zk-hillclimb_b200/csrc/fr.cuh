@@ -198,6 +198,18 @@ __device__ __forceinline__ bool fr_is_zero(const Fr& x) {
     for (int i = 0; i < 8; i++) o |= x.v[i];
     return o == 0;
 }
+// Montgomery-form inverse by Fermat: x^(p-2)
+static __device__ __noinline__ Fr fr_inv_mont(const Fr& x) {
+    // p - 2, little-endian limbs
+    const uint32_t e[8] = {0xffffffffu, 0xfffffffeu, 0xfffe5bfeu, 0x53bda402u, 0x09a1d805u, 0x3339d808u, 0x299d7d48u, 0x73eda753u};
+    Fr r = FR_RPOW[0];   // 1 in Montgomery form
+    for (int limb = 7; limb >= 0; limb--)
+        for (int b = 31; b >= 0; b--) {
+            r = fr_mmul(r, r);
+            if ((e[limb] >> b) & 1u) r = fr_mmul(r, x);
+        }
+    return r;
+}
 #endif  // __CUDACC__
 
 }  // namespace zkh

@@ -207,18 +207,6 @@ __global__ void fr_lu_finals_kernel(LuPtrs P, uint32_t pend, const Fr* chal, Fr*
     if (a < 5) out[a] = (pend & (1u << a)) ? fr_lerp(P.in[a][0], P.in[a][1], fr_to_mont(*chal)) : P.in[a][0];
 }
 
-// Montgomery-form inverse by Fermat: x^(p-2)
-__device__ Fr fr_inv_mont(const Fr& x) {
-    // p - 2, little-endian limbs
-    const uint32_t e[8] = {0xffffffffu, 0xfffffffeu, 0xfffe5bfeu, 0x53bda402u, 0x09a1d805u, 0x3339d808u, 0x299d7d48u, 0x73eda753u};
-    Fr r = FR_RPOW[0];   // 1 in Montgomery form
-    for (int limb = 7; limb >= 0; limb--)
-        for (int b = 31; b >= 0; b--) {
-            r = fr_mmul(r, r);
-            if ((e[limb] >> b) & 1u) r = fr_mmul(r, x);
-        }
-    return r;
-}
 // out[i] = 1/(in[i] + beta), 0 where the denominator is 0 (as the reference's inverse of 0); plain values.
 // Eight strided elements per thread share one Fermat inversion (prefix products, peel back).
 #define FR_INV_K 8

@@ -18,21 +18,6 @@ __device__ __forceinline__ uint32_t pip_digit(const uint32_t* s, uint32_t w) {
     const uint32_t bit = w * PIP_C;
     return (s[bit >> 5] >> (bit & 31)) & (PIP_NB - 1);
 }
-__device__ __forceinline__ void fp_load(Fp& c, const uint4* q) {
-#pragma unroll
-    for (int j = 0; j < 3; j++) {
-        const uint4 t = __ldg(q + j);
-        c.v[4 * j] = t.x; c.v[4 * j + 1] = t.y; c.v[4 * j + 2] = t.z; c.v[4 * j + 3] = t.w;
-    }
-}
-__device__ __forceinline__ G1 g1_load(const G1* p) {
-    G1 r;
-    const uint4* q = reinterpret_cast<const uint4*>(p);
-    fp_load(r.x, q);
-    fp_load(r.y, q + 3);
-    fp_load(r.z, q + 6);
-    return r;
-}
 // thread = (row, window), as in the reference: sixteen buckets in local memory filled in generator order, then
 // sum_b b * bucket[b] by the running-sum trick from bucket 15 down.  (A thread per BUCKET gives fifteen times the threads but at
 // every generator only one of a window's fifteen bucket threads has work: two active lanes per warp, measured 13x slower.)

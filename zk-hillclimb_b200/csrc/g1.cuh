@@ -119,7 +119,7 @@ __device__ __forceinline__ void fp_row_mad(uint32_t (&t)[14], const uint32_t (&x
         : "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(x[4]), "r"(x[5]), "r"(x[6]), "r"(x[7]), "r"(x[8]), "r"(x[9]), "r"(x[10]), "r"(x[11]), "r"(y));
 }
 // Montgomery product a * b / 2^384 mod p, operand scanning with the reduction interleaved
-__device__ __noinline__ Fp fp_mul(const Fp& a, const Fp& b) {
+static __device__ __noinline__ Fp fp_mul(const Fp& a, const Fp& b) {
     uint32_t t[14];
 #pragma unroll
     for (int i = 0; i < 14; i++) t[i] = 0;
@@ -144,7 +144,7 @@ __device__ __forceinline__ Fp fp_sqr(const Fp& a) { return fp_mul(a, a); }
 // two independent products in one pass: r0 = a0 * b0, r1 = a1 * b1.  A Montgomery product is one long dependent chain of
 // multiply-adds (each waits for the carry of the one before); two of them side by side give the scheduler a second chain
 // to issue from while the first waits.
-__device__ __noinline__ void fp_mul2(Fp& r0, Fp& r1, const Fp& a0, const Fp& b0, const Fp& a1, const Fp& b1) {
+static __device__ __noinline__ void fp_mul2(Fp& r0, Fp& r1, const Fp& a0, const Fp& b0, const Fp& a1, const Fp& b1) {
     uint32_t t[14], u[14];
 #pragma unroll
     for (int i = 0; i < 14; i++) { t[i] = 0; u[i] = 0; }
@@ -178,7 +178,7 @@ __device__ __forceinline__ G1 g1_zero() {
     return r;
 }
 // dbl-2009-l (zkllm-src/bls12-381.cu:1361-1386).  Operands by reference, the result built in a local of its own.
-__device__ __noinline__ G1 g1_double(const G1& p) {
+static __device__ __noinline__ G1 g1_double(const G1& p) {
     G1 r;
     if (fp_is_zero(p.z)) {
         r = p;
@@ -199,7 +199,7 @@ __device__ __noinline__ G1 g1_double(const G1& p) {
     return r;
 }
 // add-2007-bl with the reference's early returns (zkllm-src/bls12-381.cu:1429-1464)
-__device__ __noinline__ G1 g1_add(const G1& a, const G1& b) {
+static __device__ __noinline__ G1 g1_add(const G1& a, const G1& b) {
     G1 r;
     if (fp_is_zero(a.z)) {
         r = b;
@@ -224,6 +224,36 @@ __device__ __noinline__ G1 g1_add(const G1& a, const G1& b) {
     fp_mul2(t1, t2, fp_sub(v, r.x), rr, fp_sub(fp_sub(zz, z1z1), z2z2), h);
     r.y = fp_sub(t1, fp_double(sj));                   // Y3 = r (V - X3) - 2 S1 J
     r.z = t2;                                          // Z3 = ((Z1 + Z2)^2 - Z1Z1 - Z2Z2) H
+    return r;
+}
+__device__ __forceinline__ void fp_load(Fp& c, const uint4* q) {
+#pragma unroll
+    for (int j = 0; j < 3; j++) {
+        const uint4 t = __ldg(q + j);
+        c.v[4 * j] = t.x; c.v[4 * j + 1] = t.y; c.v[4 * j + 2] = t.z; c.v[4 * j + 3] = t.w;
+    }
+}
+__device__ __forceinline__ G1 g1_load(const G1* p) {
+    G1 r;
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+    fp_load(r.x, q);
+    fp_load(r.y, q + 3);
+    fp_load(r.z, q + 6);
+    return r;
+}
+__device__ __forceinline__ void g1_store(G1* p, const G1& v) {
+    uint4* q = reinterpret_cast<uint4*>(p);
+    const uint32_t* w = v.x.v;                  // x, y, z are contiguous: 36 limbs
+#pragma unroll
+    for (int j = 0; j < 9; j++) q[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+// -P: (X, 0 - Y, Z), the reference's G1Jacobian_minus (zkllm-src/g1-tensor.cu:11-21)
+__device__ __forceinline__ G1 g1_neg(const G1& p) {
+    G1 r = p;
+    Fp z;
+#pragma unroll
+    for (int i = 0; i < 12; i++) z.v[i] = 0;
+    r.y = fp_sub(z, p.y);
     return r;
 }
 #endif  // __CUDACC__

@@ -170,3 +170,54 @@ def g1_pedersen_commit(prover, gens, scalars, m, n):
     out = torch.empty(m * 144, dtype=torch.uint8, device=gens.device)
     prover._ck(prover._L.zkh_g1_pedersen_commit(prover._h, gens.data_ptr(), scalars.data_ptr(), m, n, out.data_ptr()))
     return out
+
+
+# ------------------------------------------------------------------------------------------------------------------------
+# G1 openings (zkllm-src/vrf_common.cuh).  Points are 144-byte Jacobian triples: `bytes` on the host, uint8 tensors of
+# n * 144 bytes on the device.
+def g1_msm(prover, gens, scalars, n):
+    """dev_msm (vrf_common.cuh:165-184): <g, a> over n points (n a power of two), the reference's triple."""
+    out = (C.c_uint8 * 144)()
+    prover._ck(prover._L.zkh_g1_msm(prover._h, gens.data_ptr(), scalars.data_ptr(), n, out))
+    return bytes(out)
+
+
+def g1_fold_chain(prover, src, size, us, orientation):
+    """fold_chain (vrf_common.cuh:144-163): orientation 0 folds commitments (k_com_me), 1 generators (k_gen_fold)."""
+    out = (C.c_uint8 * 144)()
+    a = _pt(us)
+    prover._ck(prover._L.zkh_g1_fold_chain(prover._h, src.data_ptr(), size, a.ctypes.data, len(us), orientation, out))
+    return bytes(out)
+
+
+def ipa_prove(prover, a, b, gens, Q, n, state):
+    """ipa_prove (vrf_common.cuh:302-336).  a, b: packed Fr device tensors of n scalars; gens: n points on the device;
+    Q: 144 bytes; state: the transcript state (32 bytes).  Returns (L, R, a_final, new_state): lists of 144-byte points."""
+    rounds = n.bit_length() - 1
+    L = (C.c_uint8 * (144 * max(rounds, 1)))()
+    R = (C.c_uint8 * (144 * max(rounds, 1)))()
+    af = (C.c_uint8 * 32)()
+    st = (C.c_uint8 * 32).from_buffer_copy(state)
+    q = (C.c_uint8 * 144).from_buffer_copy(Q)
+    prover._ck(prover._L.zkh_g1_ipa_prove(prover._h, a.data_ptr(), b.data_ptr(), gens.data_ptr(), q, n, st, L, R, af))
+    Lb, Rb = bytes(L), bytes(R)
+    return ([Lb[144 * r:144 * r + 144] for r in range(rounds)], [Rb[144 * r:144 * r + 144] for r in range(rounds)],
+            int.from_bytes(bytes(af), "little"), bytes(st))
+
+
+def ipa_verify(prover, gens, n, Q, P0, u_b, L, R, a_final, state):
+    """ipa_verify (vrf_common.cuh:340-371).  Returns (accepted, new_state).  The shape checks of the reference (round
+    counts, n = 2^rounds = 2^len(u_b)) reject before any device work."""
+    rounds = len(L)
+    if rounds != len(R) or n != (1 << rounds) or len(u_b) != rounds or not 0 <= a_final < P:
+        return False, bytes(state)
+    st = (C.c_uint8 * 32).from_buffer_copy(state)
+    q = (C.c_uint8 * 144).from_buffer_copy(Q)
+    p0 = (C.c_uint8 * 144).from_buffer_copy(P0)
+    Lb = (C.c_uint8 * (144 * max(rounds, 1))).from_buffer_copy(b"".join(L).ljust(144, b"\0"))
+    Rb = (C.c_uint8 * (144 * max(rounds, 1))).from_buffer_copy(b"".join(R).ljust(144, b"\0"))
+    af = (C.c_uint8 * 32).from_buffer_copy(int(a_final).to_bytes(32, "little"))
+    ub = _pt(u_b)
+    acc = C.c_int(0)
+    prover._ck(prover._L.zkh_g1_ipa_verify(prover._h, gens.data_ptr(), n, q, p0, ub.ctypes.data, Lb, Rb, af, st, C.byref(acc)))
+    return bool(acc.value), bytes(st)
