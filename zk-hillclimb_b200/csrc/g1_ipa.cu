@@ -12,8 +12,9 @@
 // (for L and R) and then by the challenge and its inverse (for the fold), three products from one table where the
 // reference doubles three times.  A round is a fixed sequence of launches on the context's stream with the transcript on
 // the device; the host reads L, R, the final scalar and the transcript state once at the end.  Every kernel here is bound by
-// the latency of one thread's dependent additions (16 products of 384 bits each), so blocks are single warps spread over
-// all SMs.
+// the latency of one chain of dependent group operations with most of the GPU idle, so each point operation is spread over
+// four lanes (g1q_add / g1q_double: the independent 384-bit products of a formula run one per lane) and blocks are single
+// warps of eight points spread over all SMs.
 #include "common.cuh"
 #include "fr_dev.cuh"
 #include "g1.cuh"
@@ -23,23 +24,44 @@ namespace zkh {
 
 constexpr uint32_t G1_BITS = 256;               // table depth: bit k of the scalar's eight raw limbs selects 2^k P
 constexpr int G1_WARP = 32;
+constexpr int G1_QPB = G1_WARP / 4;             // points per block: each point operation runs on four lanes (g1q_add / g1q_double)
+
+// index of this thread's quad in the grid
+__device__ __forceinline__ uint32_t quad_index() { return blockIdx.x * G1_QPB + (threadIdx.x >> 2); }
+// the four lanes of a quad hold the same point and store a quarter each
+__device__ __forceinline__ void g1q_store(G1* p, const G1& v) {
+    uint4* q = reinterpret_cast<uint4*>(p);
+    const uint32_t* w = v.x.v;                  // x, y, z are contiguous: 36 limbs, nine 16-byte pieces
+    const int ql = threadIdx.x & 3;
+#pragma unroll
+    for (int j = 0; j < 9; j++)
+        if ((j & 3) == ql) q[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
 
 // tab[k * n + i] = 2^k g[i]
 __global__ void __launch_bounds__(G1_WARP) g1_table_kernel(const G1* __restrict__ g, uint32_t n, G1* __restrict__ tab) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t i = quad_index();
     if (i >= n) return;
+    const uint32_t qm = g1q_mask();
     G1 a = g1_load(g + i);
     for (uint32_t k = 0; k < G1_BITS; k++) {
-        g1_store(tab + (size_t)k * n + i, a);
-        if (k + 1 < G1_BITS) a = g1_double(a);
+        g1q_store(tab + (size_t)k * n + i, a);
+        if (k + 1 < G1_BITS) a = g1q_double(a, qm);
     }
 }
 // sum over the set bits of s, lowest first, of 2^k P: the accumulator of G1Jacobian_mul, which starts at infinity and
-// therefore takes the first selected entry unchanged
-__device__ __forceinline__ G1 g1_chain(const G1* __restrict__ tab, size_t n, size_t i, const Fr& s) {
+// therefore takes the first selected entry unchanged.  The loop visits set bits only, so that the quads of a warp, whose
+// scalars differ, all add in every iteration.
+__device__ __forceinline__ G1 g1q_chain(const G1* __restrict__ tab, size_t n, size_t i, const Fr& s, uint32_t qm) {
     G1 out = g1_zero();
-    for (uint32_t k = 0; k < G1_BITS; k++)
-        if ((s.v[k >> 5] >> (k & 31)) & 1u) out = g1_add(out, g1_load(tab + (size_t)k * n + i));
+    uint32_t w = 0, cur = s.v[0];
+    for (;;) {
+        while (cur == 0 && w < 7) cur = s.v[++w];
+        if (cur == 0) break;
+        const uint32_t k = 32 * w + (uint32_t)__ffs((int)cur) - 1;
+        cur &= cur - 1;
+        out = g1q_add(out, g1_load(tab + (size_t)k * n + i), qm);
+    }
     return out;
 }
 // One batch of scalar multiples: out[idx] = s(idx) * point((idx ^ pxor) & pmask) for idx < count.
@@ -51,20 +73,20 @@ struct ChainSeg {
     uint32_t n, count, pxor, pmask, mode;
 };
 __global__ void __launch_bounds__(G1_WARP) g1_chain_kernel(ChainSeg A, ChainSeg B) {
-    uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    uint32_t idx = quad_index();
     const bool second = idx >= A.count;
     if (second) idx -= A.count;
     const ChainSeg& S = second ? B : A;
     if (idx >= S.count) return;
     const Fr s = fr_load(S.sc + (S.mode == 0 ? idx : S.mode == 1 ? 0u : (idx < S.count / 2 ? 1u : 0u)));
-    g1_store(S.out + idx, g1_chain(S.tab, S.n, (idx ^ S.pxor) & S.pmask, s));
+    g1q_store(S.out + idx, g1q_chain(S.tab, S.n, (idx ^ S.pxor) & S.pmask, s, g1q_mask()));
 }
 // one level of the pairwise sums of dev_msm: p[i] += p[i + half], for each of gridDim.y arrays `stride` apart
 __global__ void __launch_bounds__(G1_WARP) g1_tree_kernel(G1* T, uint32_t stride, uint32_t half) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t i = quad_index();
     if (i >= half) return;
     G1* p = T + (size_t)blockIdx.y * stride;
-    g1_store(p + i, g1_add(g1_load(p + i), g1_load(p + i + half)));
+    g1q_store(p + i, g1q_add(g1_load(p + i), g1_load(p + i + half), g1q_mask()));
 }
 
 // ------------------------------------------------------------------ the argument's rounds
@@ -83,11 +105,11 @@ __global__ void __launch_bounds__(G1_WARP) ipa_round_end_kernel(const G1* T, uin
                                                               Fr* sc, ZkhTag tagL, ZkhTag tagR) {
     __shared__ __align__(16) G1 lr[2];
     __shared__ __align__(16) uint32_t trbuf[ZKH_TRBUF_WORDS];
-    const uint32_t lane = threadIdx.x;
-    if (lane < 2) {
-        const G1 v = g1_add(g1_load(T + (size_t)lane * h), g1_load(QT + lane));
-        lr[lane] = v;
-        g1_store(lane ? Rout : Lout, v);
+    const uint32_t lane = threadIdx.x, q = lane >> 2;
+    if (q < 2) {                                              // quad 0: L, quad 1: R
+        const G1 v = g1q_add(g1_load(T + (size_t)q * h), g1_load(QT + q), g1q_mask());
+        if ((lane & 3) == 0) lr[q] = v;
+        g1q_store(q ? Rout : Lout, v);
     }
     __syncwarp();
     uint32_t st[8];
@@ -114,17 +136,22 @@ __global__ void __launch_bounds__(G1_WARP) ipa_round_end_kernel(const G1* T, uin
 // doubling table of g' for the next round
 __global__ void __launch_bounds__(G1_WARP) ipa_fold_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, const G1* __restrict__ W,
                                                          const Fr* __restrict__ sc, uint32_t h, Fr* a2, Fr* b2, G1* g2, G1* tab) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t i = quad_index();
     if (i >= h) return;
-    const Fr xm = fr_to_mont(fr_load(sc + 2)), xim = fr_to_mont(fr_load(sc + 3));
-    fr_store(a2 + i, fr_add(fr_mmul(xm, fr_load(a + i)), fr_mmul(xim, fr_load(a + i + h))));
-    fr_store(b2 + i, fr_add(fr_mmul(xim, fr_load(b + i)), fr_mmul(xm, fr_load(b + i + h))));
-    G1 p = g1_add(g1_load(W + i), g1_load(W + i + h));
-    g1_store(g2 + i, p);
+    const uint32_t qm = g1q_mask();
+    const int ql = threadIdx.x & 3;
+    if (ql < 2) {                                             // lane 0 folds a, lane 1 folds b
+        const Fr xm = fr_to_mont(fr_load(sc + 2)), xim = fr_to_mont(fr_load(sc + 3));
+        const Fr* v = ql ? b : a;
+        fr_store((ql ? b2 : a2) + i, fr_add(fr_mmul(ql ? xim : xm, fr_load(v + i)), fr_mmul(ql ? xm : xim, fr_load(v + i + h))));
+    }
+    __syncwarp(qm);
+    G1 p = g1q_add(g1_load(W + i), g1_load(W + i + h), qm);
+    g1q_store(g2 + i, p);
     if (h < 2) return;
     for (uint32_t k = 0; k < G1_BITS; k++) {
-        g1_store(tab + (size_t)k * h + i, p);
-        if (k + 1 < G1_BITS) p = g1_double(p);
+        g1q_store(tab + (size_t)k * h + i, p);
+        if (k + 1 < G1_BITS) p = g1q_double(p, qm);
     }
 }
 
@@ -138,19 +165,20 @@ __device__ __forceinline__ G1 g1_zero_bytes() {
     return r;
 }
 __global__ void __launch_bounds__(G1_WARP) g1_pair_diff_kernel(const G1* __restrict__ c, uint32_t sz, uint32_t nsz, int orientation, G1* d) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t i = quad_index();
     if (i >= nsz) return;
+    const uint32_t qm = g1q_mask();
     const G1 lo = g1_load(c + 2 * i), hi = (2 * i + 1 < sz) ? g1_load(c + 2 * i + 1) : g1_zero_bytes();
-    g1_store(d + i, orientation == 0 ? g1_add(hi, g1_neg(lo)) : g1_add(lo, g1_neg(hi)));
+    g1q_store(d + i, orientation == 0 ? g1q_add(hi, g1_neg(lo), qm) : g1q_add(lo, g1_neg(hi), qm));
 }
 // out[i] = c[2i] + u d[i] (orientation 0) or c[2i+1] + u d[i] (orientation 1); M = u d
 __global__ void __launch_bounds__(G1_WARP) g1_pair_join_kernel(const G1* __restrict__ c, uint32_t sz, uint32_t nsz, int orientation,
                                                              const G1* __restrict__ M, G1* out) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t i = quad_index();
     if (i >= nsz) return;
     const uint32_t j = orientation == 0 ? 2 * i : 2 * i + 1;
     const G1 base = j < sz ? g1_load(c + j) : g1_zero_bytes();
-    g1_store(out + i, g1_add(base, g1_load(M + i)));
+    g1q_store(out + i, g1q_add(base, g1_load(M + i), g1q_mask()));
 }
 
 // ------------------------------------------------------------------ the argument's verifier
@@ -228,24 +256,25 @@ __global__ void __launch_bounds__(FR_THREADS) ipa_svec_kernel(const Fr* __restri
         w = fr_mmul(w, fr_to_mont(fr_load(((i >> (rounds - 1 - r)) & 1u) ? xs + r : xis + r)));
     fr_store(s + i, fr_from_mont(w));
 }
-// One thread: P = P0, then P = (x_r^2 L_r + P) + x_r^-2 R_r per round; accept iff P == a_f g_f + (a_f b_f) Q as group elements.
+// One quad: P = P0, then P = (x_r^2 L_r + P) + x_r^-2 R_r per round; accept iff P == a_f g_f + (a_f b_f) Q as group elements.
 // M: the 2 rounds + 1 scaled points (L, R interleaved, then (a_f b_f) Q); gf = <g, s>.
-__global__ void ipa_verify_final_kernel(const G1* M, uint32_t rounds, const G1* P0, const G1* gf, const Fr* a_f, int* accept) {
-    if (blockIdx.x || threadIdx.x) return;
+__global__ void __launch_bounds__(4) ipa_verify_final_kernel(const G1* M, uint32_t rounds, const G1* P0, const G1* gf, const Fr* a_f,
+                                                           int* accept) {
+    const uint32_t qm = g1q_mask();
     G1 Pt = g1_load(P0);
-    for (uint32_t r = 0; r < rounds; r++) Pt = g1_add(g1_add(g1_load(M + 2 * r), Pt), g1_load(M + 2 * r + 1));
+    for (uint32_t r = 0; r < rounds; r++) Pt = g1q_add(g1q_add(g1_load(M + 2 * r), Pt, qm), g1_load(M + 2 * r + 1), qm);
     const Fr af = fr_load(a_f);
     G1 out = g1_zero(), a = g1_load(gf);
     for (uint32_t k = 0; k < G1_BITS; k++) {
-        if ((af.v[k >> 5] >> (k & 31)) & 1u) out = g1_add(out, a);
-        a = g1_double(a);
+        if ((af.v[k >> 5] >> (k & 31)) & 1u) out = g1q_add(out, a, qm);
+        a = g1q_double(a, qm);
     }
-    const G1 rhs = g1_add(out, g1_load(M + 2 * rounds));
-    const G1 d = g1_add(Pt, g1_neg(rhs));
-    *accept = fp_is_zero(d.z) ? 1 : 0;
+    const G1 rhs = g1q_add(out, g1_load(M + 2 * rounds), qm);
+    const G1 d = g1q_add(Pt, g1_neg(rhs), qm);
+    if (threadIdx.x == 0) *accept = fp_is_zero(d.z) ? 1 : 0;
 }
 
-static inline unsigned warp_blocks(size_t items) { return (unsigned)((items + G1_WARP - 1) / G1_WARP); }
+static inline unsigned warp_blocks(size_t items) { return (unsigned)((items + G1_QPB - 1) / G1_QPB); }   // a quad per item
 
 // tab = tables of the n points at g, then out[i] = s(i) g[i]; stream-ordered
 static int g1_mul_enqueue(zkh_ctx* c, const G1* g, uint32_t n, const Fr* sc, uint32_t mode, G1* tab, G1* out) {
@@ -444,9 +473,9 @@ extern "C" int zkh_g1_ipa_verify(zkh_ctx* c, const void* g_dev, uint32_t n, cons
     g1_table_kernel<<<warp_blocks(nm), G1_WARP, 0, c->stream>>>(pts, nm, tabM);
     g1_table_kernel<<<warp_blocks(n), G1_WARP, 0, c->stream>>>((const G1*)g_dev, n, tab);
     ChainSeg A = {tab, s, T, n, n, 0u, 0xffffffffu, 0u}, B = {tabM, sq, M, nm, nm, 0u, 0xffffffffu, 0u};
-    g1_chain_kernel<<<warp_blocks((size_t)n + nm + G1_WARP), G1_WARP, 0, c->stream>>>(A, B);
+    g1_chain_kernel<<<warp_blocks((size_t)n + nm), G1_WARP, 0, c->stream>>>(A, B);
     ZKH_TRY(g1_tree_enqueue(c, T, 0, n, 1));
-    ipa_verify_final_kernel<<<1, 1, 0, c->stream>>>(M, rounds, pts + nm, T, afd, acc_dev);
+    ipa_verify_final_kernel<<<1, 4, 0, c->stream>>>(M, rounds, pts + nm, T, afd, acc_dev);
     ZKH_CUDA(c, cudaGetLastError());
     int acc = 0;
     ZKH_CUDA(c, cudaMemcpyAsync(hc, c->d_ctl, offsetof(ZkhCtl, local), cudaMemcpyDeviceToHost, c->stream));
