@@ -583,6 +583,50 @@ def run_suite_fr(args):
                      "same_bytes": bool(hold["out"].cpu().numpy().tobytes() == bytes(want))})
     print(json.dumps(line), flush=True)
 
+    # G1 openings of the fully connected layer's drivers (ipa_prove of the 1024-wide generator set, vrf_common.cuh:302-336;
+    # the same inputs through the reference's code, which steps every round from the host)
+    n_ = 1024
+    rounds = 10
+    a_h, b_h = rand_fr(n_), rand_fr(n_)
+    a_d, b_d = fr.to_device(a_h), fr.to_device(b_h)
+    gq = gens_b[:n_ * 144]
+    Q = gens_b[5 * 144:6 * 144]
+    st0 = zk.Transcript("ipa-bench").state
+    hold = {}
+
+    def ipa():
+        hold["pf"] = fr.ipa_prove(prover, a_d, b_d, gd, Q, n_, st0)
+    ipa()
+    ms = wall(ipa)
+    line = {"suite": "inner-product argument over BLS12-381 G1: 1024 generators, 10 rounds (ipa_prove)", "ms": ms}
+    if refA is not None and hasattr(refA.lib, "refA_ipa_prove"):
+        vp = C.c_void_p
+        st = (C.c_uint8 * 32).from_buffer_copy(st0)
+        L = (C.c_uint8 * (rounds * 144))()
+        R = (C.c_uint8 * (rounds * 144))()
+        af = (C.c_uint32 * 8)()
+        rms = C.c_double(0)
+        refA.lib.refA_ipa_prove(a_h.ctypes.data_as(vp), b_h.ctypes.data_as(vp), gq, Q, C.c_uint32(n_), st, L, R, af, C.byref(rms))
+        gL, gR, gaf, gst = hold["pf"]
+        line.update({"reference_cuda_ms": rms.value, "speedup_vs_reference_cuda": rms.value / ms,
+                     "same_bytes": bool(b"".join(gL) == bytes(L) and b"".join(gR) == bytes(R) and gst == bytes(st)
+                                        and gaf == int.from_bytes(bytes(af), "little"))})
+    print(json.dumps(line), flush=True)
+
+    def msm():
+        hold["m"] = fr.g1_msm(prover, gd, a_d, n_)
+    msm()
+    ms = wall(msm)
+    line = {"suite": "multi-scalar product over 1024 points in the reference's summation order (dev_msm)", "ms": ms}
+    if refA is not None and hasattr(refA.lib, "refA_msm"):
+        want = (C.c_uint8 * 144)()
+        rms = C.c_double(0)
+        for _ in range(2):
+            refA.lib.refA_msm(gq, a_h.ctypes.data_as(C.c_void_p), C.c_uint32(n_), want, C.byref(rms))
+        line.update({"reference_cuda_ms": rms.value, "speedup_vs_reference_cuda": rms.value / ms,
+                     "same_bytes": bool(hold["m"] == bytes(want))})
+    print(json.dumps(line), flush=True)
+
 
 def run_profile_case(args):
     """--profile-case NAME: one small, self-terminating invocation of one kernel family (a few hundred MB on
@@ -657,6 +701,21 @@ def run_profile_case(args):
             nc = 3 if name == "fr_hp3" else 2
             cols = [rand_fr(1 << 21) for _ in range(nc)]
             fn = lambda: zk.fr.product_sumcheck(prover, zk.Transcript("prof"), cols, ["l%d" % t for t in range(nc + 1)])
+    elif name == "g1_ipa":
+        # inner-product argument over 256 generators (8 rounds): about 80 launches, all latency-bound chains of group operations
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import g1_oracle as g1
+        n_ = 256
+        pts, acc = [], g1.GEN
+        for _ in range(n_ + 1):                      # distinct points: G, 2G + G, ... (cheap to make on the host)
+            pts.append(acc)
+            acc = g1.add(g1.double(acc), g1.GEN)
+        gd = torch.from_numpy(np.frombuffer(b"".join(g1.to_bytes(q) for q in pts[:n_]), dtype=np.uint8).copy()).cuda()
+        fa = rng.integers(0, 1 << 32, (2 * n_, 8), dtype=np.uint64).astype(np.uint32)
+        fa[:, 7] %= 0x73EDA753
+        a_d, b_d = zk.fr.to_device(fa[:n_]), zk.fr.to_device(fa[n_:])
+        Q, st0 = g1.to_bytes(pts[n_]), zk.Transcript("prof").state
+        fn = lambda: zk.fr.ipa_prove(prover, a_d, b_d, gd, Q, n_, st0)
     elif name == "hwl_witness":
         # fp8 witness replay, 64 x 512 . 512 x 256: 2^24 padded products, 1.9 GB of columns written
         dims = (64, 512, 256)
