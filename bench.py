@@ -627,6 +627,50 @@ def run_suite_fr(args):
                      "same_bytes": bool(hold["m"] == bytes(want))})
     print(json.dumps(line), flush=True)
 
+    # the fully connected obligation of BASELINE configs[0] end to end through the driver programs (process start, CUDA
+    # initialisation, file input and output included): commit of W, then prove, 128 x 768 . 768 x 768
+    import subprocess
+    import tempfile
+    exe = os.path.join(ROOT, "zk-hillclimb_b200", "zkob_fc")
+    ref_exe = os.path.join(ROOT, "oracle", "_ref", "zkob_fc_ref")
+    if refA is not None and os.path.exists(exe):
+        B_, IN_, OUT_ = 128, 768, 768
+        with tempfile.TemporaryDirectory() as td:
+            for name, n in (("gi", 1024), ("go", 1024), ("q", 1)):
+                buf = (C.c_uint8 * (n * 144))()
+                refA.lib.refA_commit_random(C.c_uint32(n), buf)
+                open(os.path.join(td, name), "wb").write(bytes(buf))
+            open(os.path.join(td, "X"), "wb").write(rng.integers(-(1 << 15), 1 << 15, B_ * IN_, dtype=np.int32).tobytes())
+            open(os.path.join(td, "W"), "wb").write(rng.integers(-(1 << 15), 1 << 15, IN_ * OUT_, dtype=np.int32).tobytes())
+            res = {}
+            for tag, prog in (("ours", exe), ("reference", ref_exe)):
+                if not os.path.exists(prog):
+                    continue
+                d = os.path.join(td, tag)
+                os.mkdir(d)
+                best = 1e30
+                for _ in range(2):
+                    t0 = time.perf_counter()
+                    subprocess.check_call([prog, "prove", d, "bench-seed", os.path.join(td, "X"), os.path.join(td, "W"), str(B_), str(IN_),
+                                           str(OUT_), os.path.join(td, "gi"), os.path.join(td, "go"), os.path.join(td, "q")],
+                                          stdout=subprocess.DEVNULL)
+                    best = min(best, time.perf_counter() - t0)
+                res[tag] = best
+            line = {"suite": "zkob_fc prove as a program, 128 x 768 . 768 x 768 (three commitments, 10-round sumcheck, three inner-product arguments, files)",
+                    "s": res["ours"]}
+            if "reference" in res:
+                same = all(open(os.path.join(td, "ours", f), "rb").read() == open(os.path.join(td, "reference", f), "rb").read()
+                           for f in ("com_X.bin", "com_Y.bin", "sumcheck.bin", "ipa_W.bin", "ipa_X.bin", "ipa_Y.bin", "dims.bin"))
+                line.update({"reference_program_s": res["reference"], "speedup_vs_reference_program": res["reference"] / res["ours"],
+                             "same_files": bool(same)})
+            t0 = time.perf_counter()
+            rc = subprocess.call([exe, "commit", os.path.join(td, "W"), str(IN_), str(OUT_), os.path.join(td, "go"), os.path.join(td, "cw")],
+                                 stdout=subprocess.DEVNULL)
+            rc = rc or subprocess.call([exe, "verify", os.path.join(td, "ours"), "bench-seed", str(B_), str(IN_), str(OUT_), os.path.join(td, "cw"),
+                                        os.path.join(td, "gi"), os.path.join(td, "go"), os.path.join(td, "q")], stdout=subprocess.DEVNULL)
+            line.update({"commit_and_verify_s": time.perf_counter() - t0, "verify_accepts": rc == 0})
+            print(json.dumps(line), flush=True)
+
 
 def run_profile_case(args):
     """--profile-case NAME: one small, self-terminating invocation of one kernel family (a few hundred MB on
