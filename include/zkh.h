@@ -567,6 +567,10 @@ ZKH_API int zkh_g1_pedersen_commit(zkh_ctx* ctx, const void* gens_dev, const voi
  * zkh_g1_ipa_verify: ipa_verify (vrf_common.cuh:340-371): replays the transcript, folds P0 with x^2 L + P + x^-2 R, the public
  *   weights me_weights(u_b) (log2(n) scalars, host) and the generators (through the s-vector product), and sets *accept to 1 iff
  *   P == a_f g_f + (a_f b_f) Q as group elements.  A rejected proof is ZKH_OK with *accept = 0. */
+/* *n_bad = the number of rows j < rows with lhs[j] != s a[j] + b[j] as group elements: the homomorphic affine link of the
+ * rescaling obligation (zkllm-src/zkob_rescale.cu:226-241, com_X[j] == sf com_Xr[j] + com_rem[j]).  s32: one scalar, host. */
+ZKH_API int zkh_g1_rows_check(zkh_ctx* ctx, const void* lhs_dev, const void* a_dev, const void* s32, const void* b_dev, uint32_t rows,
+                              uint32_t* n_bad);
 ZKH_API int zkh_g1_msm(zkh_ctx* ctx, const void* g_dev, const void* a_dev, uint32_t n, void* out144);
 ZKH_API int zkh_g1_fold_chain(zkh_ctx* ctx, const void* src_dev, uint32_t size, const void* us, uint32_t nu, int orientation,
                               void* out144);

@@ -20,6 +20,7 @@ GADGETS_SELFTEST = os.path.join(HERE, "zkh_p3_gadgets_selftest")
 DRIVER = os.path.join(HERE, "zkob_p3fc")
 LAYER = os.path.join(HERE, "zkh_p3_layer")
 FC_DRIVER = os.path.join(HERE, "zkob_fc")
+RESCALE_DRIVER = os.path.join(HERE, "zkob_rescale")
 INCLUDE = os.path.abspath(os.path.join(HERE, "..", "include"))
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -43,10 +44,10 @@ def stale():
 def build_selftest(force=False):
     """The C++ host programs over the C ABI; linked with an rpath beside the library."""
     for name, exe in (("p3_selftest.cpp", SELFTEST), ("p3_gadgets_selftest.cpp", GADGETS_SELFTEST), ("zkob_p3fc.cpp", DRIVER),
-                      ("p3_layer_main.cpp", LAYER), ("zkob_fc.cpp", FC_DRIVER)):
+                      ("p3_layer_main.cpp", LAYER), ("zkob_fc.cpp", FC_DRIVER), ("zkob_rescale.cpp", RESCALE_DRIVER)):
         src = os.path.join(HERE, "host", name)
         deps = [src, os.path.join(INCLUDE, "zkh.h"), os.path.join(INCLUDE, "zkh_p3.hpp"), os.path.join(INCLUDE, "zkh_p3_verify.hpp"),
-                os.path.join(INCLUDE, "zkh_p3_layer.hpp"), LIB]
+                os.path.join(INCLUDE, "zkh_p3_layer.hpp"), os.path.join(HERE, "host", "zkob_common.hpp"), LIB]
         if not force and os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
             continue
         subprocess.check_call([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", "-pthread", "-I", INCLUDE, src, "-o", exe,

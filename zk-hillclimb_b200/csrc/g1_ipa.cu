@@ -274,6 +274,26 @@ __global__ void __launch_bounds__(4) ipa_verify_final_kernel(const G1* M, uint32
     if (threadIdx.x == 0) *accept = fp_is_zero(d.z) ? 1 : 0;
 }
 
+// ------------------------------------------------------------------ row-wise linear relation of commitments
+// bad += 1 for every row j with lhs[j] != s a[j] + b[j] as group elements (the affine link of the rescaling obligation,
+// zkllm-src/zkob_rescale.cu:226-241: com_X[j] == sf com_Xr[j] + com_rem[j]); one quad per row
+__global__ void __launch_bounds__(G1_WARP) g1_rows_check_kernel(const G1* __restrict__ lhs, const G1* __restrict__ a, const G1* __restrict__ b, Fr s,
+                                                              uint32_t rows, unsigned int* bad) {
+    const uint32_t j = quad_index();
+    if (j >= rows) return;
+    const uint32_t qm = g1q_mask();
+    G1 acc = g1_zero(), p = g1_load(a + j);
+    int top = 255;
+    while (top >= 0 && !((s.v[top >> 5] >> (top & 31)) & 1u)) top--;
+    for (int k = 0; k <= top; k++) {
+        if ((s.v[k >> 5] >> (k & 31)) & 1u) acc = g1q_add(acc, p, qm);
+        if (k < top) p = g1q_double(p, qm);
+    }
+    const G1 rhs = g1q_add(acc, g1_load(b + j), qm);
+    const G1 d = g1q_add(g1_load(lhs + j), g1_neg(rhs), qm);
+    if ((threadIdx.x & 3) == 0 && !fp_is_zero(d.z)) atomicAdd(bad, 1u);
+}
+
 static inline unsigned warp_blocks(size_t items) { return (unsigned)((items + G1_QPB - 1) / G1_QPB); }   // a quad per item
 
 // tab = tables of the n points at g, then out[i] = s(i) g[i]; stream-ordered
@@ -484,5 +504,24 @@ extern "C" int zkh_g1_ipa_verify(zkh_ctx* c, const void* g_dev, uint32_t n, cons
     if (hc->err) return zkh_fail(c, ZKH_ERR_DEVICE, "g1_ipa_verify: device error flag set");
     digest_to_bytes(hc->st, state);
     *accept = acc;
+    return ZKH_OK;
+}
+
+extern "C" int zkh_g1_rows_check(zkh_ctx* c, const void* lhs_dev, const void* a_dev, const void* s32, const void* b_dev, uint32_t rows,
+                                 uint32_t* n_bad) {
+    if (!c || !lhs_dev || !a_dev || !s32 || !b_dev || !n_bad) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_check: null pointer");
+    if (!rows) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_check: no rows");
+    if (((uintptr_t)lhs_dev | (uintptr_t)a_dev | (uintptr_t)b_dev) & 15) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_check: buffers must be 16-byte aligned");
+    if (!fr_canonical((const uint32_t*)s32)) return zkh_fail(c, ZKH_ERR_DOMAIN, "g1_rows_check: scalar not below p");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    ZKH_TRY(zkh_ws_reserve(c, 256));
+    unsigned int* bad = (unsigned int*)c->ws;
+    Fr s;
+    memcpy(s.v, s32, 32);
+    ZKH_CUDA(c, cudaMemsetAsync(bad, 0, sizeof(unsigned int), c->stream));
+    g1_rows_check_kernel<<<warp_blocks(rows), G1_WARP, 0, c->stream>>>((const G1*)lhs_dev, (const G1*)a_dev, (const G1*)b_dev, s, rows, bad);
+    ZKH_CUDA(c, cudaGetLastError());
+    ZKH_CUDA(c, cudaMemcpyAsync(n_bad, bad, sizeof(unsigned int), cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
     return ZKH_OK;
 }

@@ -1,0 +1,268 @@
+// Host-side glue shared by the driver programs of the first proof stack (zkob_fc, zkob_rescale): a handful of scalars over the
+// BLS12-381 scalar field on the host, file helpers, the library context, the reference's transcript helpers
+// (zkllm-src/vrf_common.cuh:219-250), and the row-committed openings open_prove / open_verify (zkllm-src/zkob_lookup.cuh:112-138)
+// over the C ABI.
+#pragma once
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <exception>
+#include <iostream>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "zkh.h"
+
+namespace zkob {
+
+constexpr size_t G1B = 144, FRB = 32;
+
+// ------------------------------------------------------------------ scalars on the host (a handful per proof)
+struct Fr { uint32_t v[8]; };
+const Fr FR_MOD = {{0x00000001u, 0xffffffffu, 0xfffe5bfeu, 0x53bda402u, 0x09a1d805u, 0x3339d808u, 0x299d7d48u, 0x73eda753u}};
+Fr fr_u32(uint32_t x) { Fr r{}; r.v[0] = x; return r; }
+bool fr_is_zero(const Fr& a) { uint32_t o = 0; for (int i = 0; i < 8; i++) o |= a.v[i]; return o == 0; }
+bool fr_eq(const Fr& a, const Fr& b) { return memcmp(a.v, b.v, FRB) == 0; }
+bool fr_lt(const Fr& a, const Fr& b) {
+    for (int i = 7; i >= 0; i--) if (a.v[i] != b.v[i]) return a.v[i] < b.v[i];
+    return false;
+}
+Fr raw_sub(const Fr& a, const Fr& b) {
+    Fr r; int64_t br = 0;
+    for (int i = 0; i < 8; i++) { int64_t d = (int64_t)a.v[i] - b.v[i] - br; r.v[i] = (uint32_t)d; br = d < 0; }
+    return r;
+}
+Fr fr_add(const Fr& a, const Fr& b) {
+    Fr r; uint64_t c = 0;
+    for (int i = 0; i < 8; i++) { c += (uint64_t)a.v[i] + b.v[i]; r.v[i] = (uint32_t)c; c >>= 32; }
+    return (c || !fr_lt(r, FR_MOD)) ? raw_sub(r, FR_MOD) : r;      // 2p < 2^256: no carry out for reduced operands
+}
+Fr fr_sub(const Fr& a, const Fr& b) { return fr_lt(a, b) ? raw_sub(FR_MOD, raw_sub(b, a)) : raw_sub(a, b); }
+Fr fr_mul(const Fr& a, const Fr& b) {                               // double-and-add: a few hundred calls per proof
+    Fr r{};
+    for (int i = 255; i >= 0; i--) {
+        r = fr_add(r, r);
+        if ((b.v[i >> 5] >> (i & 31)) & 1u) r = fr_add(r, a);
+    }
+    return r;
+}
+Fr fr_from_i64(int64_t x) {
+    Fr r{};
+    const uint64_t m = x < 0 ? (uint64_t)(-(x + 1)) + 1 : (uint64_t)x;
+    r.v[0] = (uint32_t)m; r.v[1] = (uint32_t)(m >> 32);
+    return x < 0 ? raw_sub(FR_MOD, r) : r;
+}
+// p(u) from p(0), p(1), p(2) (lagrange3, zkllm-src/vrf_common.cuh:130-140)
+Fr lagrange3(const Fr& p0, const Fr& p1, const Fr& p2, const Fr& u) {
+    const Fr one = fr_u32(1), two = fr_u32(2);
+    const Fr inv2 = {{2147483649u, 2147483647u, 2147429887u, 2849952257u, 80800770u, 429714436u, 2496577188u, 972477353u}};
+    const Fr um1 = fr_sub(u, one), um2 = fr_sub(u, two);
+    const Fr l0 = fr_mul(fr_mul(um1, um2), inv2), l1 = fr_mul(u, fr_sub(two, u)), l2 = fr_mul(fr_mul(u, um1), inv2);
+    return fr_add(fr_add(fr_mul(p0, l0), fr_mul(p1, l1)), fr_mul(p2, l2));
+}
+
+// ------------------------------------------------------------------ files
+std::vector<uint8_t> read_file(const std::string& path) {
+    FILE* f = fopen(path.c_str(), "rb");
+    if (!f) throw std::runtime_error("cannot open " + path);
+    std::vector<uint8_t> b;
+    uint8_t buf[1 << 16];
+    size_t n;
+    while ((n = fread(buf, 1, sizeof buf, f)) > 0) b.insert(b.end(), buf, buf + n);
+    fclose(f);
+    return b;
+}
+void write_file(const std::string& path, const std::vector<uint8_t>& b) {
+    FILE* f = fopen(path.c_str(), "wb");
+    if (!f) throw std::runtime_error("cannot write " + path);
+    if (!b.empty() && fwrite(b.data(), 1, b.size(), f) != b.size()) { fclose(f); throw std::runtime_error("short write to " + path); }
+    fclose(f);
+}
+void put(std::vector<uint8_t>& b, const void* p, size_t n) { const uint8_t* q = (const uint8_t*)p; b.insert(b.end(), q, q + n); }
+uint32_t clog2(uint32_t n) { uint32_t l = 0; while ((1u << l) < n) l++; return l; }
+
+std::vector<int32_t> load_ints(const std::string& path, size_t expect) {
+    std::vector<uint8_t> raw = read_file(path);
+    if (raw.size() < expect * 4) throw std::runtime_error("short read / wrong dims: " + path);
+    std::vector<int32_t> v(expect);
+    memcpy(v.data(), raw.data(), expect * 4);
+    return v;
+}
+
+// ------------------------------------------------------------------ the library
+struct Ctx {
+    zkh_ctx* c = nullptr;
+    Ctx() {
+        const char* d = getenv("ZKH_DEVICE");
+        if (zkh_ctx_create(d ? atoi(d) : 0, nullptr, &c) != ZKH_OK) throw std::runtime_error("no CUDA device for libzkh");
+    }
+    ~Ctx() { if (c) zkh_ctx_destroy(c); }
+    void ck(int rc, const char* what) const {
+        if (rc != ZKH_OK) throw std::runtime_error(std::string(what) + ": " + zkh_last_error(c));
+    }
+};
+struct Dev {                                                        // device buffer
+    Ctx& x; void* p = nullptr; size_t bytes = 0;
+    Dev(Ctx& x_, size_t n) : x(x_), bytes(n) { x.ck(zkh_dev_alloc(x.c, n ? n : 16, &p), "device allocation"); }
+    Dev(Ctx& x_, const void* host, size_t n) : Dev(x_, n) { x.ck(zkh_upload(x.c, p, host, n), "upload"); }
+    Dev(const Dev&) = delete;
+    ~Dev() { if (p) zkh_dev_free(x.c, p); }
+    std::vector<uint8_t> host() const {
+        std::vector<uint8_t> h(bytes);
+        x.ck(zkh_download(x.c, h.data(), p, bytes), "download");
+        return h;
+    }
+};
+
+// rows x cols integers, zero-padded to rows_pad x cols_pad scalars (FrTensor(int*) then pad, zkllm-src/fr-tensor.cu:727-736, :809-828)
+std::vector<Fr> pad_matrix(const int64_t* v, uint32_t rows, uint32_t cols, uint32_t rp, uint32_t cp) {
+    std::vector<Fr> out((size_t)rp * cp, Fr{});
+    for (uint32_t r = 0; r < rows; r++)
+        for (uint32_t c = 0; c < cols; c++) out[(size_t)r * cp + c] = fr_from_i64(v[(size_t)r * cols + c]);
+    return out;
+}
+std::vector<int64_t> widen(const std::vector<int32_t>& v) { return std::vector<int64_t>(v.begin(), v.end()); }
+
+// Pedersen commitments of the rows of a rows x n scalar matrix
+std::vector<uint8_t> commit_rows(Ctx& x, const Dev& gens, const Dev& mat, uint32_t rows, uint32_t n) {
+    Dev out(x, (size_t)rows * G1B);
+    x.ck(zkh_g1_pedersen_commit(x.c, gens.p, mat.p, rows, n, out.p), "commitment");
+    return out.host();
+}
+
+// fs::Transcript over the library's host functions, with the reference's helpers (zkllm-src/vrf_common.cuh:219-250)
+struct Transcript {
+    uint8_t st[32];
+    explicit Transcript(const std::string& seed) { zkh_tr_init(st, seed.data(), seed.size()); }
+    void absorb(const char* label, const void* p, size_t n) { zkh_tr_absorb(st, label, p, n); }
+    void absorb_u32(const char* label, uint32_t v) { absorb(label, &v, 4); }
+    void absorb_fr(const char* label, const Fr& v) { absorb(label, v.v, FRB); }
+    Fr challenge_fr() {
+        for (;;) {
+            uint8_t b[32];
+            zkh_tr_challenge_bytes(st, b);
+            Fr r;
+            for (int i = 0; i < 8; i++) r.v[i] = (uint32_t)b[4 * i] | ((uint32_t)b[4 * i + 1] << 8) | ((uint32_t)b[4 * i + 2] << 16) | ((uint32_t)b[4 * i + 3] << 24);
+            r.v[7] %= 1944954707u;
+            if (!fr_is_zero(r)) return r;
+        }
+    }
+    std::vector<Fr> challenge_vec(uint32_t n) { std::vector<Fr> o(n); for (auto& e : o) e = challenge_fr(); return o; }
+};
+
+void refuse_flags(int argc, char** argv) {
+    for (int i = 1; i < argc; i++)
+        if (!strncmp(argv[i], "--", 2)) throw std::invalid_argument(std::string("flag not built in this driver: ") + argv[i]);
+}
+
+// partial evaluation of a device tensor viewed as [other][2^logd][window] at u (FrTensor::partial_me)
+void partial_me(Ctx& x, const Dev& t, uint64_t other, uint32_t logd, uint64_t window, const std::vector<Fr>& u, Dev& out) {
+    if (logd == 0) {                                                // a dimension of one: nothing to fold
+        const std::vector<uint8_t> h = t.host();
+        x.ck(zkh_upload(x.c, out.p, h.data(), (size_t)other * window * FRB), "copy");
+        return;
+    }
+    x.ck(zkh_fr_partial_me(x.c, t.p, other, logd, window, u.data(), out.p), "partial_me");
+}
+// the multilinear extension of a 2^la x 2^lb matrix at (ua for the rows, ub for the columns) (FrTensor::multi_dim_me)
+Fr eval2(Ctx& x, const Dev& t, uint32_t la, uint32_t lb, const std::vector<Fr>& ua, const std::vector<Fr>& ub) {
+    Dev rows(x, ((size_t)1 << la) * FRB);
+    partial_me(x, t, (uint64_t)1 << la, lb, 1, ub, rows);
+    Fr r;
+    if (la == 0) x.ck(zkh_download(x.c, r.v, rows.p, FRB), "download");
+    else x.ck(zkh_fr_mle_eval(x.c, rows.p, ua.data(), la, r.v), "mle_eval");
+    return r;
+}
+// one inner-product argument into a file (ipa_prove + write_ipa, zkllm-src/vrf_common.cuh:286-292, :302-336)
+void ipa_to_file(Ctx& x, const std::string& path, const Dev& a, const std::vector<Fr>& u_b, const Dev& gens, const uint8_t* Q, uint32_t n,
+                 Transcript& tr) {
+    const uint32_t rounds = clog2(n);
+    Dev b(x, (size_t)n * FRB);
+    const Fr one = fr_u32(1);
+    if (rounds == 0) x.ck(zkh_upload(x.c, b.p, one.v, FRB), "upload");
+    else x.ck(zkh_fr_eq_build(x.c, u_b.data(), rounds, b.p), "eq_build");                       // me_weights(u_b)
+    std::vector<uint8_t> L((size_t)rounds * G1B + 1), R((size_t)rounds * G1B + 1);
+    Fr af;
+    x.ck(zkh_g1_ipa_prove(x.c, a.p, b.p, gens.p, Q, n, tr.st, L.data(), R.data(), af.v), "ipa_prove");
+    std::vector<uint8_t> f;
+    put(f, &rounds, 4); put(f, L.data(), (size_t)rounds * G1B);
+    put(f, &rounds, 4); put(f, R.data(), (size_t)rounds * G1B);
+    put(f, af.v, FRB);
+    write_file(path, f);
+}
+
+struct Ipa { uint32_t rounds = 0; std::vector<uint8_t> L, R; Fr af; };
+Ipa read_ipa(const std::string& path) {
+    const std::vector<uint8_t> f = read_file(path);
+    Ipa p;
+    size_t o = 0;
+    auto need = [&](size_t n) { if (o + n > f.size()) throw std::runtime_error("read_ipa: truncated " + path); };
+    uint32_t nl, nr;
+    need(4); memcpy(&nl, &f[o], 4); o += 4;
+    if (nl > 32) throw std::runtime_error("read_ipa: round count");
+    need((size_t)nl * G1B); p.L.assign(f.begin() + o, f.begin() + o + (size_t)nl * G1B); o += (size_t)nl * G1B;
+    need(4); memcpy(&nr, &f[o], 4); o += 4;
+    if (nr > 32) throw std::runtime_error("read_ipa: round count");
+    need((size_t)nr * G1B); p.R.assign(f.begin() + o, f.begin() + o + (size_t)nr * G1B); o += (size_t)nr * G1B;
+    need(FRB); memcpy(p.af.v, &f[o], FRB);
+    p.rounds = nl == nr ? nl : 0xffffffffu;
+    return p;
+}
+// one opening of the verifier: fold the row commitments, P0 = C0 + eval Q, then the argument's verifier
+bool open_verify(Ctx& x, const std::vector<uint8_t>& com, uint32_t rows, const std::vector<Fr>& u_rows, const Fr& eval, const Dev& gens,
+                 uint32_t n, const uint8_t* Q, const std::vector<Fr>& u_b, const Ipa& pf, Transcript& tr) {
+    if (pf.rounds != clog2(n) || u_b.size() != pf.rounds) return false;
+    if (!fr_lt(pf.af, FR_MOD)) return false;
+    Dev cd(x, com.data(), com.size());
+    uint8_t pair[2 * G1B];
+    Fr none{};
+    x.ck(zkh_g1_fold_chain(x.c, cd.p, rows, u_rows.empty() ? &none : u_rows.data(), (uint32_t)u_rows.size(), 0, pair), "fold_chain");
+    memcpy(pair + G1B, Q, G1B);
+    // C0 + eval Q as the halving sum of (1 C0, eval Q): the reference's h_add(C0, h_mul(Q, eval))
+    const Fr sc[2] = {fr_u32(1), eval};
+    Dev pd(x, pair, sizeof pair), sd(x, sc, sizeof sc);
+    uint8_t P0[G1B];
+    x.ck(zkh_g1_msm(x.c, pd.p, sd.p, 2, P0), "statement point");
+    int ok = 0;
+    x.ck(zkh_g1_ipa_verify(x.c, gens.p, n, Q, P0, u_b.empty() ? &none : u_b.data(), pf.L.data(), pf.R.data(), pf.af.v, tr.st, &ok), "ipa_verify");
+    return ok == 1;
+}
+
+// one request per stdin line through the same entry as the one-shot command line, "ZKW-RC <rc>" after each
+inline int serve_loop(char* argv0, int (*run1)(int, char**)) {
+    std::cout << "ZKW-READY" << std::endl;
+    std::string line;
+    while (std::getline(std::cin, line)) {
+        std::istringstream iss(line);
+        std::vector<std::string> toks;
+        for (std::string t; iss >> t;) toks.push_back(t);
+        if (toks.empty()) continue;
+        std::vector<char*> av{argv0};
+        for (auto& t : toks) av.push_back(const_cast<char*>(t.c_str()));
+        int rc;
+        try {
+            rc = run1((int)av.size(), av.data());
+        } catch (const std::exception& e) {
+            std::cout << "serve: request failed: " << e.what() << std::endl;
+            rc = 3;
+        }
+        fflush(stdout);
+        std::cout << "ZKW-RC " << rc << std::endl;
+    }
+    return 0;
+}
+
+// x^-1 by Fermat (a few per proof)
+inline Fr fr_inv(const Fr& a) {
+    const Fr e = raw_sub(FR_MOD, fr_u32(2));
+    Fr r = fr_u32(1);
+    for (int i = 255; i >= 0; i--) {
+        r = fr_mul(r, r);
+        if ((e.v[i >> 5] >> (i & 31)) & 1u) r = fr_mul(r, a);
+    }
+    return r;
+}
+
+}  // namespace zkob
