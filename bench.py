@@ -671,6 +671,37 @@ def run_suite_fr(args):
             line.update({"commit_and_verify_s": time.perf_counter() - t0, "verify_accepts": rc == 0})
             print(json.dumps(line), flush=True)
 
+            # the rescaling obligation that follows it: 128 x 768 pre-rescale products, sf = 2^16 (2^17 lookups into 2^16 rows)
+            exe_r = os.path.join(ROOT, "zk-hillclimb_b200", "zkob_rescale")
+            ref_r = os.path.join(ROOT, "oracle", "_ref", "zkob_rescale_ref")
+            open(os.path.join(td, "Y"), "wb").write(rng.integers(-(1 << 40), 1 << 40, B_ * OUT_, dtype=np.int64).tobytes())
+            res = {}
+            for tag, prog in (("ours", exe_r), ("reference", ref_r)):
+                if not os.path.exists(prog):
+                    continue
+                d = os.path.join(td, "r_" + tag)
+                os.mkdir(d)
+                best = 1e30
+                for _ in range(2):
+                    t0 = time.perf_counter()
+                    subprocess.check_call([prog, "prove", d, "bench-seed", os.path.join(td, "Y"), str(B_), str(OUT_), "16", os.path.join(td, "go"),
+                                           os.path.join(td, "q")], stdout=subprocess.DEVNULL)
+                    best = min(best, time.perf_counter() - t0)
+                res[tag] = best
+            if "ours" in res:
+                line = {"suite": "zkob_rescale prove as a program, 128 x 768 values, sf 2^16 (five commitments, 17-round lookup sumcheck, three inner-product arguments, files)",
+                        "s": res["ours"]}
+                if "reference" in res:
+                    names = ("com_X.bin", "com_Xr.bin", "com_rem.bin", "com_m.bin", "com_A.bin", "lookup.bin", "ipa_A.bin", "ipa_rem.bin", "ipa_m.bin", "dims.bin")
+                    same = all(open(os.path.join(td, "r_ours", f), "rb").read() == open(os.path.join(td, "r_reference", f), "rb").read() for f in names)
+                    line.update({"reference_program_s": res["reference"], "speedup_vs_reference_program": res["reference"] / res["ours"],
+                                 "same_files": bool(same)})
+                t0 = time.perf_counter()
+                rc = subprocess.call([exe_r, "verify", os.path.join(td, "r_ours"), "bench-seed", str(B_), str(OUT_), "16", os.path.join(td, "go"),
+                                      os.path.join(td, "q")], stdout=subprocess.DEVNULL)
+                line.update({"verify_s": time.perf_counter() - t0, "verify_accepts": rc == 0})
+                print(json.dumps(line), flush=True)
+
 
 def run_profile_case(args):
     """--profile-case NAME: one small, self-terminating invocation of one kernel family (a few hundred MB on
