@@ -109,6 +109,21 @@ def test_fold_chain_matches_oracle(zk, prover, size, orientation):
     assert got == g1.to_bytes(g1.fold_chain(gens, us, orientation))
 
 
+@pytest.mark.gpu
+def test_rows_check_counts_broken_relations(zk, prover):
+    rnd = random.Random(9)
+    rows, s = 11, 65536
+    a = [g1.jac_mul(g1.GEN, rnd.randrange(1, g1.FR_P)) for _ in range(rows)]
+    b = [g1.jac_mul(g1.GEN, rnd.randrange(1, g1.FR_P)) for _ in range(rows)]
+    b[3] = g1.ZERO                                                    # a row whose addend is the point at infinity
+    lhs = [g1.add(g1.jac_mul(p, s), q) for p, q in zip(a, b)]
+    lhs = [g1.add(g1.double(x), g1.neg(x)) for x in lhs]              # another representative of the same points
+    assert zk.fr.g1_rows_check(prover, _pts_dev(lhs), _pts_dev(a), s, _pts_dev(b), rows) == 0
+    lhs[2], lhs[7] = g1.double(lhs[2]), g1.add(lhs[7], g1.GEN)
+    assert zk.fr.g1_rows_check(prover, _pts_dev(lhs), _pts_dev(a), s, _pts_dev(b), rows) == 2
+    assert zk.fr.g1_rows_check(prover, _pts_dev(lhs), _pts_dev(a), s + 1, _pts_dev(b), rows) == rows
+
+
 def _ref():
     if not fo.ReferenceFr.available():
         pytest.skip("oracle/_ref/libfrref.so not built")

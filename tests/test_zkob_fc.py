@@ -24,8 +24,9 @@ def run(exe, *args, timeout=900):
 def test_usage_and_refused_flags(tmp_path):
     assert os.path.exists(EXE), "build() makes the driver"
     assert run(EXE).returncode == 2 and run(EXE, "prove", "x").returncode == 2
-    r = run(EXE, "prove", tmp_path, "seed", "X", "W", 4, 6, 3, "gi", "go", "q", "--claims", "acc", "id", "comW")
+    r = run(EXE, "prove", tmp_path, "seed", "X", "W", 4, 6, 3, "gi", "go", "q", "--claims", "acc", "id", "comW", "--wpriv", "wacc", "blinds")
     assert r.returncode == 2 and "not built" in r.stderr
+    assert run(EXE, "prove", tmp_path, "seed", "X", "W", 4, 6, 3, "gi", "go", "q", "--claims", "acc", "id").returncode == 2   # no registered com_W
     import torch
     if not torch.cuda.is_available():
         (tmp_path / "W.i32").write_bytes(np.zeros(18, dtype=np.int32).tobytes())
@@ -109,3 +110,34 @@ def test_serve_loop_and_changed_opening(tmp_path):
     (ob / "ipa_W.bin").write_bytes(bytes(ipa))
     r = run(EXE, "verify", ob, "seed-a", B, IN, OUT, ob / "com_W.bin", gi, go, q)
     assert r.returncode == 1 and "claim_W" in r.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,IN,OUT", [(4, 6, 3), (16, 12, 5)])
+def test_claim_mode_files_equal_the_reference_programs(tmp_path, B, IN, OUT):
+    """--claims: claims.bin, drvstates.bin, witrefs.txt and the witness tensors of prove, and the verifier's recomputed claims, against
+    the reference's program run at the same paths (the claim records carry the commitment paths)."""
+    if not os.path.exists(REF_EXE):
+        pytest.skip("oracle/_ref/zkob_fc_ref not built")
+    X, W, gi, go, q = _inputs(tmp_path, B, IN, OUT, 3 * B + OUT)
+    comW = tmp_path / "registered_com_W.bin"
+    assert run(EXE, "commit", W, IN, OUT, go, comW).returncode == 0
+    kept = {}
+    for tag, exe in (("ref", REF_EXE), ("ours", EXE)):
+        ob, acc, vacc = tmp_path / "ob", tmp_path / "acc", tmp_path / "vacc"
+        for d in (ob, acc, vacc):
+            d.mkdir()
+        r = run(exe, "prove", ob, "run-seed:l0.fc", X, W, B, IN, OUT, gi, go, q, "--claims", acc, "l0.fc", comW)
+        assert r.returncode == 0 and "claim mode" in r.stdout, r.stdout + r.stderr
+        assert not (ob / "ipa_W.bin").exists()
+        r = run(exe, "verify", ob, "run-seed:l0.fc", B, IN, OUT, comW, gi, go, q, "--claims", vacc, "l0.fc")
+        assert r.returncode == 0 and "ACCEPT-conditional" in r.stdout, r.stdout + r.stderr
+        kept[tag] = {p.relative_to(tmp_path).as_posix(): p.read_bytes() for d in (ob, acc, vacc) for p in sorted(d.iterdir())}
+        for d in (ob, acc, vacc):
+            for p in d.iterdir():
+                p.unlink()
+            d.rmdir()
+    assert kept["ours"].keys() == kept["ref"].keys()
+    for name in kept["ref"]:
+        assert kept["ours"][name] == kept["ref"][name], name
+    assert kept["ours"]["acc/claims.bin"] == kept["ours"]["vacc/claims.bin"]          # what the orchestrator compares

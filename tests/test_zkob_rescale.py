@@ -24,8 +24,9 @@ def run(exe, *args, timeout=900):
 def test_usage_and_refused_flag(tmp_path):
     assert os.path.exists(EXE), "build() makes the driver"
     assert run(EXE).returncode == 2 and run(EXE, "verify", "x").returncode == 2
-    r = run(EXE, "prove", tmp_path, "seed", "X", 8, 4, 4, "gen", "q", "--claims", "acc", "id")
+    r = run(EXE, "prove", tmp_path, "seed", "X", 8, 4, 4, "gen", "q", "--wpriv", "acc", "id")
     assert r.returncode == 2 and "not built" in r.stderr
+    assert run(EXE, "prove", tmp_path, "seed", "X", 8, 4, 4, "gen", "q", "--claims", "acc").returncode == 2
     import torch
     if not torch.cuda.is_available():
         (tmp_path / "X.i64").write_bytes(np.zeros(32, dtype=np.int64).tobytes())
@@ -92,3 +93,29 @@ def test_files_equal_the_reference_programs(tmp_path, B, Cc, log_sf):
         raw[off] ^= 1
         (ours / name).write_bytes(bytes(raw))
     assert run(EXE, "verify", ours, "run-seed:layer0.rescale", B, Cc, log_sf, gen, q).returncode == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Cc,log_sf", [(8, 4, 4), (8, 6, 6)])
+def test_claim_mode_files_equal_the_reference_programs(tmp_path, B, Cc, log_sf):
+    if not os.path.exists(REF_EXE):
+        pytest.skip("oracle/_ref/zkob_rescale_ref not built")
+    X, gen, q = _inputs(tmp_path, B, Cc, log_sf, 7 * B + Cc)
+    kept = {}
+    for tag, exe in (("ref", REF_EXE), ("ours", EXE)):
+        ob, acc, vacc = tmp_path / "ob", tmp_path / "acc", tmp_path / "vacc"
+        for d in (ob, acc, vacc):
+            d.mkdir()
+        r = run(exe, "prove", ob, "run-seed:l0.rs", X, B, Cc, log_sf, gen, q, "--claims", acc, "l0.rs")
+        assert r.returncode == 0 and "claim mode" in r.stdout, r.stdout + r.stderr
+        r = run(EXE, "verify", ob, "run-seed:l0.rs", B, Cc, log_sf, gen, q, "--claims", vacc, "l0.rs")
+        assert r.returncode == 0 and "ACCEPT-conditional" in r.stdout, r.stdout + r.stderr
+        kept[tag] = {p.relative_to(tmp_path).as_posix(): p.read_bytes() for d in (ob, acc, vacc) for p in sorted(d.iterdir())}
+        for d in (ob, acc, vacc):
+            for p in d.iterdir():
+                p.unlink()
+            d.rmdir()
+    assert kept["ours"].keys() == kept["ref"].keys()
+    for name in kept["ref"]:
+        assert kept["ours"][name] == kept["ref"][name], name
+    assert kept["ours"]["acc/claims.bin"] == kept["ours"]["vacc/claims.bin"]

@@ -221,3 +221,12 @@ def ipa_verify(prover, gens, n, Q, P0, u_b, L, R, a_final, state):
     acc = C.c_int(0)
     prover._ck(prover._L.zkh_g1_ipa_verify(prover._h, gens.data_ptr(), n, q, p0, ub.ctypes.data, Lb, Rb, af, st, C.byref(acc)))
     return bool(acc.value), bytes(st)
+
+
+def g1_rows_check(prover, lhs, a, s, b, rows):
+    """The affine link of the rescaling verifier (zkllm-src/zkob_rescale.cu:226-241): the number of rows j with
+    lhs[j] != s * a[j] + b[j] as group elements.  lhs, a, b: device tensors of rows * 144 bytes; s: an integer below P."""
+    sv = _pt([s])
+    bad = C.c_uint32(0)
+    prover._ck(prover._L.zkh_g1_rows_check(prover._h, lhs.data_ptr(), a.data_ptr(), sv.ctypes.data, b.data_ptr(), rows, C.byref(bad)))
+    return bad.value

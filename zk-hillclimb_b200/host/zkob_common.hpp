@@ -3,6 +3,7 @@
 // (zkllm-src/vrf_common.cuh:219-250), and the row-committed openings open_prove / open_verify (zkllm-src/zkob_lookup.cuh:112-138)
 // over the C ABI.
 #pragma once
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -16,6 +17,21 @@
 #include "zkh.h"
 
 namespace zkob {
+
+// stage timer: with ZKOB_TIMING set, lap() prints the milliseconds since the previous lap to stderr
+struct Laps {
+    const char* who;
+    bool on;
+    std::chrono::steady_clock::time_point t;
+    explicit Laps(const char* w) : who(w), on(getenv("ZKOB_TIMING") != nullptr), t(std::chrono::steady_clock::now()) {}
+    void lap(const char* what) {
+        if (!on) return;
+        const auto n = std::chrono::steady_clock::now();
+        fprintf(stderr, "[%s] %-18s %8.2f ms\n", who, what, std::chrono::duration<double, std::milli>(n - t).count());
+        t = n;
+    }
+};
+
 
 constexpr size_t G1B = 144, FRB = 32;
 
@@ -152,9 +168,107 @@ struct Transcript {
     std::vector<Fr> challenge_vec(uint32_t n) { std::vector<Fr> o(n); for (auto& e : o) e = challenge_fr(); return o; }
 };
 
-void refuse_flags(int argc, char** argv) {
-    for (int i = 1; i < argc; i++)
-        if (!strncmp(argv[i], "--", 2)) throw std::invalid_argument(std::string("flag not built in this driver: ") + argv[i]);
+// The optional claim-mode block at the end of a command line: --claims <accdir> <obid> [<registered commitment>]
+// (zkllm-src/zkob_fc.cu:1213-1236, zkob_rescale.cu:525-534).  Every other flag is refused.
+struct ClaimFlags {
+    int base_argc;
+    std::string accdir, obid, comref;
+    bool on() const { return !accdir.empty(); }
+};
+inline ClaimFlags claim_flags(int argc, char** argv) {
+    ClaimFlags f;
+    f.base_argc = argc;
+    for (int i = 2; i < argc; i++) {
+        if (strncmp(argv[i], "--", 2)) continue;
+        if (std::string(argv[i]) != "--claims") throw std::invalid_argument(std::string("flag not built in this driver: ") + argv[i]);
+        f.base_argc = i;
+        if (i + 1 < argc) f.accdir = argv[i + 1];
+        if (i + 2 < argc) f.obid = argv[i + 2];
+        if (i + 3 < argc) f.comref = argv[i + 3];
+        for (int j = i + 1; j < argc; j++)
+            if (!strncmp(argv[j], "--", 2)) throw std::invalid_argument(std::string("flag not built in this driver: ") + argv[j]);
+        if (f.accdir.empty() || f.obid.empty()) throw std::invalid_argument("--claims needs <accdir> <obid>");
+        break;
+    }
+    return f;
+}
+
+// ------------------------------------------------------------------ the claim accumulator's files (zkllm-src/zkob_claims.cuh:76-270)
+// An opening claim: the tensor committed row-wise in the file `comref` (n_rows rows over `domain` generators) evaluates to
+// `eval` at `point` (column bits first).  claims.bin = "ZKCL", version 1, count, then per claim: id, comref (length-prefixed),
+// domain, n_rows, point (count-prefixed), tag 0, eval.  The claim-mode drivers append to it instead of opening inline; a
+// separate batch program discharges the list.
+struct Claim {
+    std::string id, comref;
+    uint32_t domain = 0, n_rows = 0;
+    std::vector<Fr> point;
+    Fr eval{};
+};
+inline void put_u32(std::vector<uint8_t>& b, uint32_t v) { for (int i = 0; i < 4; i++) b.push_back((uint8_t)(v >> (8 * i))); }
+inline bool file_exists(const std::string& path) { FILE* f = fopen(path.c_str(), "rb"); if (f) fclose(f); return f != nullptr; }
+// append one record to a file of the form magic, version 1, count, records
+inline void append_record(const std::string& path, const char magic[4], const std::vector<uint8_t>& rec) {
+    std::vector<uint8_t> b;
+    if (file_exists(path)) {
+        b = read_file(path);
+        if (b.size() < 12 || memcmp(b.data(), magic, 4)) throw std::runtime_error(path + ": bad magic");
+        uint32_t ver, n;
+        memcpy(&ver, &b[4], 4); memcpy(&n, &b[8], 4);
+        if (ver != 1) throw std::runtime_error(path + ": bad version");
+        n++;
+        memcpy(&b[8], &n, 4);
+    } else {
+        put(b, magic, 4); put_u32(b, 1); put_u32(b, 1);
+    }
+    put(b, rec.data(), rec.size());
+    write_file(path, b);
+}
+inline void claim_emit(const std::string& accdir, const Claim& c) {
+    std::vector<uint8_t> r;
+    put_u32(r, (uint32_t)c.id.size()); put(r, c.id.data(), c.id.size());
+    put_u32(r, (uint32_t)c.comref.size()); put(r, c.comref.data(), c.comref.size());
+    put_u32(r, c.domain); put_u32(r, c.n_rows);
+    put_u32(r, (uint32_t)c.point.size()); put(r, c.point.data(), c.point.size() * FRB);
+    r.push_back(0);                                                 // the evaluation is given in the clear
+    put(r, c.eval.v, FRB);
+    append_record(accdir + "/claims.bin", "ZKCL", r);
+}
+// the prover's pointer from a commitment file to the witness tensor behind it: one line per distinct tensor
+inline void witref_emit(const std::string& accdir, const std::string& comref, const std::string& witpath) {
+    const std::string path = accdir + "/witrefs.txt";
+    if (file_exists(path)) {
+        const std::vector<uint8_t> b = read_file(path);
+        const std::string all((const char*)b.data(), b.size());
+        if (all.find(comref + "\t") != std::string::npos) return;
+    }
+    FILE* f = fopen(path.c_str(), "ab");
+    if (!f) throw std::runtime_error("cannot write " + path);
+    fprintf(f, "%s\t%s\n", comref.c_str(), witpath.c_str());
+    fclose(f);
+}
+// the driver's final transcript state, which the batch absorbs
+inline void drvstate_emit(const std::string& accdir, const std::string& obid, const uint8_t state[32]) {
+    std::vector<uint8_t> r;
+    put_u32(r, (uint32_t)obid.size()); put(r, obid.data(), obid.size());
+    put(r, state, 32);
+    append_record(accdir + "/drvstates.bin", "ZKDS", r);
+}
+inline Claim make_claim(const std::string& obid, const char* tensor, const std::string& comref, uint32_t domain, uint32_t n_rows,
+                        const std::vector<Fr>& u_col, const std::vector<Fr>& u_row, const Fr& eval) {
+    Claim c;
+    c.id = obid + ":" + tensor;
+    c.comref = comref;
+    c.domain = domain; c.n_rows = n_rows;
+    c.point = u_col;
+    c.point.insert(c.point.end(), u_row.begin(), u_row.end());
+    c.eval = eval;
+    return c;
+}
+// a padded witness tensor as the raw scalars the batch program reads (FrTensor::save)
+inline void save_scalars(const std::string& path, const std::vector<Fr>& t) {
+    std::vector<uint8_t> b(t.size() * FRB);
+    memcpy(b.data(), t.data(), b.size());
+    write_file(path, b);
 }
 
 // partial evaluation of a device tensor viewed as [other][2^logd][window] at u (FrTensor::partial_me)
@@ -215,18 +329,22 @@ bool open_verify(Ctx& x, const std::vector<uint8_t>& com, uint32_t rows, const s
                  uint32_t n, const uint8_t* Q, const std::vector<Fr>& u_b, const Ipa& pf, Transcript& tr) {
     if (pf.rounds != clog2(n) || u_b.size() != pf.rounds) return false;
     if (!fr_lt(pf.af, FR_MOD)) return false;
+    Laps laps("open_verify");
     Dev cd(x, com.data(), com.size());
     uint8_t pair[2 * G1B];
     Fr none{};
     x.ck(zkh_g1_fold_chain(x.c, cd.p, rows, u_rows.empty() ? &none : u_rows.data(), (uint32_t)u_rows.size(), 0, pair), "fold_chain");
+    laps.lap("fold_chain");
     memcpy(pair + G1B, Q, G1B);
     // C0 + eval Q as the halving sum of (1 C0, eval Q): the reference's h_add(C0, h_mul(Q, eval))
     const Fr sc[2] = {fr_u32(1), eval};
     Dev pd(x, pair, sizeof pair), sd(x, sc, sizeof sc);
     uint8_t P0[G1B];
     x.ck(zkh_g1_msm(x.c, pd.p, sd.p, 2, P0), "statement point");
+    laps.lap("statement");
     int ok = 0;
     x.ck(zkh_g1_ipa_verify(x.c, gens.p, n, Q, P0, u_b.empty() ? &none : u_b.data(), pf.L.data(), pf.R.data(), pf.af.v, tr.st, &ok), "ipa_verify");
+    laps.lap("ipa_verify");
     return ok == 1;
 }
 

@@ -12,8 +12,10 @@
 // Files in <obdir> (byte for byte the reference's): dims.bin, com_X.bin, com_Y.bin, sumcheck.bin, ipa_W.bin, ipa_X.bin,
 // ipa_Y.bin.  Exit 0 = success / ACCEPT, 1 = REJECT, anything else = failure; `serve` prints ZKW-READY and answers
 // "ZKW-RC <rc>" per request line (zkllm-src/zkob_serve.cuh:26-52).  The obligation directory is the caller's.
-// The claim-accumulator and weight-privacy variants of the reference (--claims, --wpriv, --apriv, --hiding) are not built:
-// those flags are refused with exit code 2.
+// With --claims <accdir> <obid> [<registered com_W>] (zkob_fc.cu:41-57) prove appends its three terminal claims, the witness
+// tensors and its final transcript state to the accumulator directory instead of opening inline, and verify recomputes the
+// claims into the verifier's accumulator and answers "ACCEPT-conditional".  The weight-privacy variants of the reference
+// (--wpriv, --apriv, --hiding) are not built: those flags are refused with exit code 2.
 //
 // Everything heavy runs through the C ABI of libzkh (commitments, partial evaluations, the sumcheck with its transcript on
 // the device, the arguments, fold chains); the host keeps the transcript between those calls and a few scalars.
@@ -33,7 +35,7 @@ Dims dims_of(const char* b, const char* in, const char* out) {
     return d;
 }
 int do_commit(int argc, char** argv) {
-    refuse_flags(argc, argv);
+    if (claim_flags(argc, argv).on()) throw std::invalid_argument("commit takes no --claims block");
     if (argc != 7) throw std::invalid_argument("commit <W-int.bin> <IN> <OUT> <gen_out.bin> <com_out.bin>");
     const Dims d = dims_of("1", argv[3], argv[4]);
     const std::vector<int32_t> W = load_ints(argv[2], (size_t)d.IN * d.OUT);
@@ -48,7 +50,9 @@ int do_commit(int argc, char** argv) {
 }
 
 int do_prove(int argc, char** argv) {
-    refuse_flags(argc, argv);
+    const ClaimFlags cf = claim_flags(argc, argv);
+    if (cf.on() && cf.comref.empty()) throw std::invalid_argument("prove --claims needs <accdir> <obid> <registered-com_W>");
+    argc = cf.base_argc;
     if (argc != 12 && argc != 13) throw std::invalid_argument("prove <obdir> <seed> <X> <W> <B> <IN> <OUT> <gen_in> <gen_out> <q> [Y-out]");
     const std::string obdir = argv[2], seed = argv[3];
     const Dims d = dims_of(argv[6], argv[7], argv[8]);
@@ -118,6 +122,22 @@ int do_prove(int argc, char** argv) {
         put(f, claim.v, FRB); put(f, claim_X.v, FRB); put(f, claim_W.v, FRB);
         write_file(obdir + "/sumcheck.bin", f);
     }
+    if (cf.on()) {
+        // claim mode: the three terminal claims go to the accumulator at the program points of the inline openings (order W, X,
+        // Y) with the witness tensors the batch program reads, then this transcript's final state (zkob_fc.cu:442-470)
+        const std::string witW = cf.accdir + "/wit_" + cf.obid + "_W.fr", witX = cf.accdir + "/wit_" + cf.obid + "_X.fr",
+                          witY = cf.accdir + "/wit_" + cf.obid + "_Y.fr";
+        save_scalars(witW, Wp); save_scalars(witX, Xp); save_scalars(witY, Yp);
+        claim_emit(cf.accdir, make_claim(cf.obid, "W", cf.comref, d.OUTp, d.INp, u_output, u_input, claim_W));
+        witref_emit(cf.accdir, cf.comref, witW);
+        claim_emit(cf.accdir, make_claim(cf.obid, "X", obdir + "/com_X.bin", d.INp, d.Bp, u_input, u_batch, claim_X));
+        witref_emit(cf.accdir, obdir + "/com_X.bin", witX);
+        claim_emit(cf.accdir, make_claim(cf.obid, "Y", obdir + "/com_Y.bin", d.OUTp, d.Bp, u_output, u_batch, claim));
+        witref_emit(cf.accdir, obdir + "/com_Y.bin", witY);
+        drvstate_emit(cf.accdir, cf.obid, tr.st);
+        std::cout << "PROVED matmul obligation (claim mode, 3 claims emitted) -> " << obdir << std::endl;
+        return 0;
+    }
     // openings on the same transcript, in the order W, X, Y
     {
         Dev aW(x, (size_t)d.OUTp * FRB);
@@ -135,7 +155,7 @@ int do_prove(int argc, char** argv) {
 }
 
 bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Dims& d, const std::string& comW_path, const std::vector<uint8_t>& gi,
-            const std::vector<uint8_t>& go, const std::vector<uint8_t>& q) {
+            const std::vector<uint8_t>& go, const std::vector<uint8_t>& q, const ClaimFlags& cf) {
     if (gi.size() != (size_t)d.INp * G1B || go.size() != (size_t)d.OUTp * G1B) { std::cout << "REJECT: generator sizes don't match dims" << std::endl; return false; }
     {
         const std::vector<uint8_t> f = read_file(obdir + "/dims.bin");
@@ -187,6 +207,15 @@ bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Dim
     if (!fr_eq(cur, fr_mul(claim_X, claim_W))) { std::cout << "REJECT: terminal claim != claim_X * claim_W" << std::endl; return false; }
     tr.absorb_fr("claim_X", claim_X); tr.absorb_fr("claim_W", claim_W);
 
+    if (cf.on()) {
+        // claim mode: the claims recomputed from this replay go to the verifier's accumulator; the verdict is conditional on the batch
+        claim_emit(cf.accdir, make_claim(cf.obid, "W", comW_path, d.OUTp, d.INp, u_output, u_input, claim_W));
+        claim_emit(cf.accdir, make_claim(cf.obid, "X", obdir + "/com_X.bin", d.INp, d.Bp, u_input, u_batch, claim_X));
+        claim_emit(cf.accdir, make_claim(cf.obid, "Y", obdir + "/com_Y.bin", d.OUTp, d.Bp, u_output, u_batch, claim));
+        drvstate_emit(cf.accdir, cf.obid, tr.st);
+        std::cout << "ACCEPT-conditional (3 claims emitted; final verdict gated on opening_batch)" << std::endl;
+        return true;
+    }
     Dev gid(x, gi.data(), gi.size()), god(x, go.data(), go.size());
     if (!open_verify(x, comW, d.INp, u_input, claim_W, god, d.OUTp, q.data(), u_output, read_ipa(obdir + "/ipa_W.bin"), tr)) {
         std::cout << "REJECT: IPA opening of claim_W vs registered weight commitment" << std::endl; return false;
@@ -202,13 +231,14 @@ bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Dim
 }
 
 int do_verify(int argc, char** argv) {
-    refuse_flags(argc, argv);
+    const ClaimFlags cf = claim_flags(argc, argv);
+    argc = cf.base_argc;
     if (argc != 11) throw std::invalid_argument("verify <obdir> <seed> <B> <IN> <OUT> <com_W.bin> <gen_in> <gen_out> <q>");
     const Dims d = dims_of(argv[4], argv[5], argv[6]);
     const std::vector<uint8_t> gi = read_file(argv[8]), go = read_file(argv[9]), q = read_file(argv[10]);
     if (q.size() < G1B) throw std::runtime_error("q.bin holds no point");
     Ctx x;
-    return verify(x, argv[2], argv[3], d, argv[7], gi, go, q) ? 0 : 1;
+    return verify(x, argv[2], argv[3], d, argv[7], gi, go, q, cf) ? 0 : 1;
 }
 
 int run1(int argc, char** argv);

@@ -9,8 +9,9 @@
 //
 // Files in <obdir> (byte for byte the reference's): dims.bin, com_X.bin, com_Xr.bin, com_rem.bin, com_m.bin, com_A.bin,
 // lookup.bin, ipa_A.bin, ipa_rem.bin, ipa_m.bin.  Exit 0 = success / ACCEPT, 1 = REJECT, anything else = failure; `serve`
-// prints ZKW-READY and answers "ZKW-RC <rc>" per request line.  The claim-accumulator mode (--claims) is not built: the
-// flag is refused with exit code 2.
+// prints ZKW-READY and answers "ZKW-RC <rc>" per request line.  With --claims <accdir> <obid> (zkob_rescale.cu:47-57) prove
+// appends its three lookup-terminal claims, the witness tensors and its final transcript state to the accumulator directory
+// instead of opening inline, and verify recomputes the claims into the verifier's accumulator and answers "ACCEPT-conditional".
 //
 // Transcript schedule (zkob_rescale.cu:19-28): B, C, LOG_SF, com_X, com_Xr, com_rem, com_m -> beta; A = 1 / (rem + beta),
 // com_A -> alpha, u; per round p(0..3) -> w_r; A_f, S_f, m_f; the three openings at the reversed round challenges.
@@ -78,7 +79,8 @@ bool open_check(Ctx& x, const std::vector<uint8_t>& com, uint32_t G, const Dev& 
 }
 
 int do_prove(int argc, char** argv) {
-    refuse_flags(argc, argv);
+    const ClaimFlags cf = claim_flags(argc, argv);
+    argc = cf.base_argc;
     if (argc != 10 && argc != 11) throw std::invalid_argument("prove <obdir> <seed> <X-int64.bin> <B> <C> <LOG_SF> <gen.bin> <q.bin> [Xr-out]");
     const std::string obdir = argv[2], seed = argv[3];
     const Lay y = lay_of(argv[5], argv[6], argv[7]);
@@ -111,7 +113,9 @@ int do_prove(int argc, char** argv) {
     for (size_t i = 0; i < rem.size(); i++) cnt[(size_t)(rem[i] + hsf)]++;
     cnt[(size_t)hsf] += (int64_t)y.D - (int64_t)rem.size();
 
+    Laps laps("rescale_prove");
     Ctx x;
+    laps.lap("context");
     const std::vector<Fr> Xp = pad_matrix(X.data(), y.B, y.C, y.Bp, y.Cp), Xrp = pad_matrix(Xr.data(), y.B, y.C, y.Bp, y.Cp),
                           Rp = pad_matrix(rem.data(), y.B, y.C, y.Bp, y.Cp), Mp = pad_matrix(cnt.data(), y.N / y.Cp, y.Cp, y.N / y.Cp, y.Cp),
                           Tp = range_table(y);
@@ -120,6 +124,7 @@ int do_prove(int argc, char** argv) {
         td(x, Tp.data(), Tp.size() * FRB);
     const std::vector<uint8_t> comX = commit_rows(x, gd, xd, y.Bp, y.Cp), comXr = commit_rows(x, gd, xrd, y.Bp, y.Cp),
                                comR = commit_rows(x, gd, rd, y.Bp, y.Cp), comM = commit_rows(x, gd, md, y.N / y.Cp, y.Cp);
+    laps.lap("commitments");
     write_file(obdir + "/com_X.bin", comX);
     write_file(obdir + "/com_Xr.bin", comXr);
     write_file(obdir + "/com_rem.bin", comR);
@@ -156,15 +161,35 @@ int do_prove(int argc, char** argv) {
         write_file(obdir + "/lookup.bin", f);
     }
     tr.absorb_fr("A_f", term[0]); tr.absorb_fr("S_f", term[1]); tr.absorb_fr("m_f", term[4]);
+    laps.lap("lookup");
     const std::vector<Fr> u_pt(ws.rbegin(), ws.rend()), u_m(ws.rbegin(), ws.rend() - y.n1);
+    if (cf.on()) {
+        // claim mode (zkob_rescale.cu:179-203): the three lookup terminals as claims (order A, rem, m), witnesses, final state
+        const std::string witA = cf.accdir + "/wit_" + cf.obid + "_A.fr", witR = cf.accdir + "/wit_" + cf.obid + "_rem.fr",
+                          witM = cf.accdir + "/wit_" + cf.obid + "_m.fr";
+        write_file(witA, ad.host());
+        save_scalars(witR, Rp); save_scalars(witM, Mp);
+        const std::vector<Fr> none;
+        claim_emit(cf.accdir, make_claim(cf.obid, "A", obdir + "/com_A.bin", y.Cp, y.Bp, u_pt, none, term[0]));
+        witref_emit(cf.accdir, obdir + "/com_A.bin", witA);
+        claim_emit(cf.accdir, make_claim(cf.obid, "rem", obdir + "/com_rem.bin", y.Cp, y.Bp, u_pt, none, term[1]));
+        witref_emit(cf.accdir, obdir + "/com_rem.bin", witR);
+        claim_emit(cf.accdir, make_claim(cf.obid, "m", obdir + "/com_m.bin", y.Cp, y.N / y.Cp, u_m, none, term[4]));
+        witref_emit(cf.accdir, obdir + "/com_m.bin", witM);
+        drvstate_emit(cf.accdir, cf.obid, tr.st);
+        std::cout << "PROVED rescaling obligation (claim mode, 3 claims emitted) -> " << obdir << std::endl;
+        return 0;
+    }
     open_prove(x, ad, y.Bp, y.Cp, gd, q.data(), u_pt, obdir + "/ipa_A.bin", tr);
     open_prove(x, rd, y.Bp, y.Cp, gd, q.data(), u_pt, obdir + "/ipa_rem.bin", tr);
     open_prove(x, md, y.N / y.Cp, y.Cp, gd, q.data(), u_m, obdir + "/ipa_m.bin", tr);
+    laps.lap("openings");
     std::cout << "PROVED rescaling obligation -> " << obdir << std::endl;
     return 0;
 }
 
-bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay& y, const std::vector<uint8_t>& g, const std::vector<uint8_t>& q) {
+bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay& y, const std::vector<uint8_t>& g, const std::vector<uint8_t>& q,
+            const ClaimFlags& cf) {
     if (g.size() != (size_t)y.Cp * G1B || !layout_ok(y)) { std::cout << "REJECT: bad layout params" << std::endl; return false; }
     {
         const std::vector<uint8_t> f = read_file(obdir + "/dims.bin");
@@ -179,6 +204,7 @@ bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay
     if (comX.size() != rowsB || comXr.size() != rowsB || comR.size() != rowsB || comA.size() != rowsB || comM.size() != (size_t)(y.N / y.Cp) * G1B) {
         std::cout << "REJECT: commitment row counts" << std::endl; return false;
     }
+    Laps laps("rescale_verify");
     // (1) the homomorphic affine link, all rows at once
     {
         Dev dx(x, comX.data(), comX.size()), dxr(x, comXr.data(), comXr.size()), dr(x, comR.data(), comR.size());
@@ -187,6 +213,7 @@ bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay
         x.ck(zkh_g1_rows_check(x.c, dx.p, dxr.p, s.v, dr.p, y.Bp, &bad), "affine link");
         if (bad) { std::cout << "REJECT: affine link com_X != sf*com_Xr + com_rem (" << bad << " rows)" << std::endl; return false; }
     }
+    laps.lap("affine_link");
     std::vector<Fr> ev((size_t)4 * y.logD);
     Fr A_f, S_f, m_f;
     {
@@ -229,6 +256,7 @@ bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay
         alpha_acc = fr_mul(alpha_acc, eqv);
         if (k >= y.n1) alphasq_acc = fr_mul(alphasq_acc, eqv);
     }
+    laps.lap("rounds");
     // (3) B_f, T_f from the public table, folded with the phase-2 challenges in round order (each binds the current top bit)
     Fr B_f, T_f;
     {
@@ -244,6 +272,7 @@ bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay
         x.ck(zkh_download(x.c, B_f.v, bc, FRB), "download");
         x.ck(zkh_download(x.c, T_f.v, tc, FRB), "download");
     }
+    laps.lap("table_fold");
     // (4) the terminal identity
     const Fr inv_ratio = fr_mul(fr_u32(y.N), fr_inv(fr_u32(y.D)));
     const Fr t1 = fr_mul(alpha_acc, fr_mul(A_f, fr_add(S_f, beta)));
@@ -252,24 +281,36 @@ bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay
     if (!fr_eq(cur, fr_sub(fr_add(fr_add(t1, t2), A_f), t4))) { std::cout << "REJECT: lookup terminal identity" << std::endl; return false; }
     tr.absorb_fr("A_f", A_f); tr.absorb_fr("S_f", S_f); tr.absorb_fr("m_f", m_f);
 
+    laps.lap("terminal");
     // (5) the openings bind the terminals to the commitments
     const std::vector<Fr> u_pt(ws.rbegin(), ws.rend()), u_m(ws.rbegin(), ws.rend() - y.n1);
+    if (cf.on()) {
+        const std::vector<Fr> none;
+        claim_emit(cf.accdir, make_claim(cf.obid, "A", obdir + "/com_A.bin", y.Cp, y.Bp, u_pt, none, A_f));
+        claim_emit(cf.accdir, make_claim(cf.obid, "rem", obdir + "/com_rem.bin", y.Cp, y.Bp, u_pt, none, S_f));
+        claim_emit(cf.accdir, make_claim(cf.obid, "m", obdir + "/com_m.bin", y.Cp, y.N / y.Cp, u_m, none, m_f));
+        drvstate_emit(cf.accdir, cf.obid, tr.st);
+        std::cout << "ACCEPT-conditional (3 claims emitted; final verdict gated on opening_batch)" << std::endl;
+        return true;
+    }
     Dev gd(x, g.data(), g.size());
     if (!open_check(x, comA, y.Cp, gd, q.data(), u_pt, A_f, obdir + "/ipa_A.bin", tr)) { std::cout << "REJECT: IPA opening of A_f vs com_A" << std::endl; return false; }
     if (!open_check(x, comR, y.Cp, gd, q.data(), u_pt, S_f, obdir + "/ipa_rem.bin", tr)) { std::cout << "REJECT: IPA opening of S_f vs com_rem" << std::endl; return false; }
     if (!open_check(x, comM, y.Cp, gd, q.data(), u_m, m_f, obdir + "/ipa_m.bin", tr)) { std::cout << "REJECT: IPA opening of m_f vs com_m" << std::endl; return false; }
+    laps.lap("openings");
     std::cout << "ACCEPT" << std::endl;
     return true;
 }
 
 int do_verify(int argc, char** argv) {
-    refuse_flags(argc, argv);
+    const ClaimFlags cf = claim_flags(argc, argv);
+    argc = cf.base_argc;
     if (argc != 9) throw std::invalid_argument("verify <obdir> <seed> <B> <C> <LOG_SF> <gen.bin> <q.bin>");
     const Lay y = lay_of(argv[4], argv[5], argv[6]);
     const std::vector<uint8_t> g = read_file(argv[7]), q = read_file(argv[8]);
     if (q.size() < G1B) throw std::runtime_error("q.bin holds no point");
     Ctx x;
-    return verify(x, argv[2], argv[3], y, g, q) ? 0 : 1;
+    return verify(x, argv[2], argv[3], y, g, q, cf) ? 0 : 1;
 }
 
 int run1(int argc, char** argv);
