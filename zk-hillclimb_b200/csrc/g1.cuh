@@ -144,6 +144,14 @@ __device__ __forceinline__ Fp fp_sqr(const Fp& a) { return fp_mul(a, a); }
 // two independent products in one pass: r0 = a0 * b0, r1 = a1 * b1.  A Montgomery product is one long dependent chain of
 // multiply-adds (each waits for the carry of the one before); two of them side by side give the scheduler a second chain
 // to issue from while the first waits.
+#ifdef ZKH_FP_PAIR_AS_SINGLE
+// (a translation unit whose kernels run at high occupancy does better with two plain products: fewer live registers)
+__device__ __forceinline__ void fp_mul2(Fp& r0, Fp& r1, const Fp& a0, const Fp& b0, const Fp& a1, const Fp& b1) {
+    const Fp x = fp_mul(a0, b0), y = fp_mul(a1, b1);
+    r0 = x;
+    r1 = y;
+}
+#else
 static __device__ __noinline__ void fp_mul2(Fp& r0, Fp& r1, const Fp& a0, const Fp& b0, const Fp& a1, const Fp& b1) {
     uint32_t t[14], u[14];
 #pragma unroll
@@ -169,6 +177,7 @@ static __device__ __noinline__ void fp_mul2(Fp& r0, Fp& r1, const Fp& a0, const 
     r0 = fp_gte_p(x) ? fp_sub_p(x) : x;
     r1 = fp_gte_p(y) ? fp_sub_p(y) : y;
 }
+#endif
 
 __device__ __forceinline__ G1 g1_zero() {
     G1 r;
