@@ -499,7 +499,8 @@ ZKH_API int zkh_ig_table(int kind, uint32_t d, uint64_t* col0, uint64_t* col1);
 /* E[b] = prod_i (bit_i(b) ? u[i] : 1 - u[i]), 2^v entries: build_eq_tensor / k_eq_expand
  * (zkllm-src/zkob_lookup.cuh:202-212, :247-268). */
 ZKH_API int zkh_fr_eq_build(zkh_ctx* ctx, const void* u, uint32_t v, void* out_dev);
-/* out[i] = in[i] + w*(in[i+h] - in[i]), i < h: k_fr_fold (zkllm-src/zkob_lookup.cuh:285-293 call sites). */
+/* out[i] = in[i] + w*(in[i+h] - in[i]), i < h: k_fr_fold (zkllm-src/zkob_lookup.cuh:285-293 call sites).  out_dev may equal
+ * in_dev (every element is read by the thread that overwrites it, before it does). */
 ZKH_API int zkh_fr_fold(zkh_ctx* ctx, const void* in_dev, uint64_t h, const void* w, void* out_dev);
 /* FrTensor::partial_me (zkllm-src/fr-tensor.cu:542-561, :601-632) for a power-of-two dimension:
  * t viewed as [other][2^logd][window]; out[o][w] = sum_d eq(u, d) * t[o][d][w], u[0] bound first.
@@ -518,6 +519,13 @@ ZKH_API int zkh_fr_mle_eval(zkh_ctx* ctx, const void* t_dev, const void* u, uint
  * fs_challenge_fr does (zkllm-src/vrf_common.cuh:233-244).  The columns are left untouched.
  *   state   transcript in/out;  evals: logn*nt*32 bytes out;  chals: logn*32 bytes out (round order);
  *   finals  nc*32 bytes out: every column bound at all challenges (may be NULL). */
+/* out[i] += c * in[i] over n elements: k_bo_axpy of the batch opening (zkllm-src/zkob_claims.cuh:386-391).  c32: one scalar, host.
+ * Stream-ordered. */
+ZKH_API int zkh_fr_axpy(zkh_ctx* ctx, void* out_dev, const void* in_dev, const void* c32, uint64_t n);
+/* The three round evaluations (t = 0, 1, 2) of sum_x a(x) b(x) with the top variable free: sum over i < h of
+ * (a[i] + t (a[i+h] - a[i])) (b[i] + t (b[i+h] - b[i])): k_bo_hp2 plus its three sums (zkllm-src/zkob_claims.cuh:365-384, :930-937).
+ * out96: three scalars, host; the call synchronises the stream. */
+ZKH_API int zkh_fr_round_sums(zkh_ctx* ctx, const void* a_dev, const void* b_dev, uint64_t h, void* out96);
 /* sum_i a[i]*b[i]: (B * m).sum() of the lookup set-up (zkllm-src/zkob_rescale.cu:137).  out32: 32 bytes, host. */
 ZKH_API int zkh_fr_dot(zkh_ctx* ctx, const void* a_dev, const void* b_dev, uint64_t n, void* out32);
 /* out[i] = 1/(in[i] + beta), 0 where in[i] + beta = 0: tlookup_inv_kernel (zkllm-src/tlookup.cu:50-62), with one

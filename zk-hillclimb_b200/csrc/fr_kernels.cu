@@ -242,6 +242,44 @@ int fr_eq_enqueue(zkh_ctx* c, const Fr* u_dev, const Fr* u_host, uint32_t v, Fr*
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(c, ZKH_ERR_CUDA, "fr eq launch");
 }
 
+// out[i] += c * in[i] (k_bo_axpy, zkllm-src/zkob_claims.cuh:386-391); c plain
+__global__ void __launch_bounds__(FR_THREADS) fr_axpy_plain_kernel(Fr* out, const Fr* __restrict__ in, Fr cplain, size_t n) {
+    const Fr cm = fr_to_mont(cplain);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        fr_store(out + i, fr_add(fr_load(out + i), fr_mmul(cm, fr_load(in + i))));
+}
+// partials[b][t] = sum over this CTA of (a_i + t da_i)(b_i + t db_i) / R for t = 0, 1, 2, pairs (i, i + h): the round
+// evaluations of sum_x M(x) P(x) with the top variable free (k_bo_hp2, zkllm-src/zkob_claims.cuh:365-384)
+__global__ void __launch_bounds__(FR_THREADS) fr_round_sums_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, size_t h, Fr* partials) {
+    __shared__ __align__(16) Fr sh[3 * 32];
+    Fr acc[3] = {fr_zero(), fr_zero(), fr_zero()};
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < h; i += (size_t)gridDim.x * blockDim.x) {
+        Fr m = fr_load(a + i), p = fr_load(b + i);
+        const Fr dm = fr_sub(fr_load(a + i + h), m), dp = fr_sub(fr_load(b + i + h), p);
+#pragma unroll
+        for (int t = 0; t < 3; t++) {
+            acc[t] = fr_add(acc[t], fr_mmul(m, p));
+            m = fr_add(m, dm);
+            p = fr_add(p, dp);
+        }
+    }
+    fr_block_sum<3>(acc, sh);
+    if (threadIdx.x == 0)
+#pragma unroll
+        for (int t = 0; t < 3; t++) partials[(size_t)blockIdx.x * 3 + t] = acc[t];
+}
+__global__ void __launch_bounds__(FR_THREADS) fr_sum3_fix_kernel(const Fr* partials, unsigned n, Fr* out) {
+    __shared__ __align__(16) Fr sh[3 * 32];
+    Fr acc[3] = {fr_zero(), fr_zero(), fr_zero()};
+    for (unsigned i = threadIdx.x; i < n; i += blockDim.x)
+#pragma unroll
+        for (int t = 0; t < 3; t++) acc[t] = fr_add(acc[t], partials[(size_t)i * 3 + t]);
+    fr_block_sum<3>(acc, sh);
+    if (threadIdx.x == 0)
+#pragma unroll
+        for (int t = 0; t < 3; t++) out[t] = fr_mmul(acc[t], FR_RPOW[1]);
+}
+
 }  // namespace zkh
 
 using namespace zkh;
@@ -435,5 +473,31 @@ extern "C" int zkh_fr_mul_throughput(zkh_ctx* c, uint32_t iters, double* gmul_pe
     cudaEventDestroy(e1);
     if (err != cudaSuccess) return zkh_fail(c, ZKH_ERR_CUDA, "fr_mul_throughput: launch failed");
     *gmul_per_s = 4.0 * iters * grid * 256 / (ms * 1e6);
+    return ZKH_OK;
+}
+
+extern "C" int zkh_fr_axpy(zkh_ctx* c, void* out_dev, const void* in_dev, const void* c32, uint64_t n) {
+    if (!c) return ZKH_ERR_ARG;
+    if (!out_dev || !in_dev || !c32 || !n) return zkh_fail(c, ZKH_ERR_ARG, "fr_axpy: bad arguments");
+    if (!fr_canonical((const uint32_t*)c32)) return zkh_fail(c, ZKH_ERR_DOMAIN, "fr_axpy: scalar not below p");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    Fr cv;
+    memcpy(cv.v, c32, 32);
+    fr_axpy_plain_kernel<<<fr_grid(c, n, 8), FR_THREADS, 0, c->stream>>>((Fr*)out_dev, (const Fr*)in_dev, cv, (size_t)n);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(c, ZKH_ERR_CUDA, "fr_axpy launch");
+}
+
+extern "C" int zkh_fr_round_sums(zkh_ctx* c, const void* a_dev, const void* b_dev, uint64_t h, void* out96) {
+    if (!c) return ZKH_ERR_ARG;
+    if (!a_dev || !b_dev || !out96 || !h) return zkh_fail(c, ZKH_ERR_ARG, "fr_round_sums: bad arguments");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    const unsigned g = fr_grid(c, h, 8);
+    ZKH_TRY(zkh_ws_reserve(c, (size_t)g * 96 + 96));
+    Fr* part = (Fr*)c->ws;
+    Fr* res = part + (size_t)g * 3;
+    fr_round_sums_kernel<<<g, FR_THREADS, 0, c->stream>>>((const Fr*)a_dev, (const Fr*)b_dev, (size_t)h, part);
+    fr_sum3_fix_kernel<<<1, FR_THREADS, 0, c->stream>>>(part, g, res);
+    ZKH_CUDA(c, cudaMemcpyAsync(out96, res, 96, cudaMemcpyDeviceToHost, c->stream));
+    ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
     return ZKH_OK;
 }

@@ -223,7 +223,8 @@ inline void append_record(const std::string& path, const char magic[4], const st
     put(b, rec.data(), rec.size());
     write_file(path, b);
 }
-inline void claim_emit(const std::string& accdir, const Claim& c) {
+// the canonical bytes of one claim: the record of claims.bin and what the batch transcript absorbs (claim_blob)
+inline std::vector<uint8_t> claim_blob(const Claim& c) {
     std::vector<uint8_t> r;
     put_u32(r, (uint32_t)c.id.size()); put(r, c.id.data(), c.id.size());
     put_u32(r, (uint32_t)c.comref.size()); put(r, c.comref.data(), c.comref.size());
@@ -231,7 +232,75 @@ inline void claim_emit(const std::string& accdir, const Claim& c) {
     put_u32(r, (uint32_t)c.point.size()); put(r, c.point.data(), c.point.size() * FRB);
     r.push_back(0);                                                 // the evaluation is given in the clear
     put(r, c.eval.v, FRB);
-    append_record(accdir + "/claims.bin", "ZKCL", r);
+    return r;
+}
+inline void claim_emit(const std::string& accdir, const Claim& c) { append_record(accdir + "/claims.bin", "ZKCL", claim_blob(c)); }
+// bounds-checked reader of the accumulator's files
+struct Reader {
+    const std::vector<uint8_t>& b;
+    size_t off = 0;
+    explicit Reader(const std::vector<uint8_t>& bb) : b(bb) {}
+    void bytes(void* p, size_t n) {
+        if (off + n > b.size()) throw std::runtime_error("accumulator file truncated");
+        memcpy(p, b.data() + off, n);
+        off += n;
+    }
+    uint32_t u32() { uint32_t v; bytes(&v, 4); return v; }
+    std::string str(uint32_t n) {
+        if (off + n > b.size()) throw std::runtime_error("accumulator file truncated");
+        std::string s((const char*)b.data() + off, n);
+        off += n;
+        return s;
+    }
+};
+// claims.bin -> claims (claims_parse, zkllm-src/zkob_claims.cuh:165-192); committed evaluations are not accepted here
+inline std::vector<Claim> claims_load(const std::string& path) {
+    const std::vector<uint8_t> bytes = read_file(path);
+    Reader r(bytes);
+    char magic[4];
+    r.bytes(magic, 4);
+    if (memcmp(magic, "ZKCL", 4)) throw std::runtime_error("claims: bad magic");
+    if (r.u32() != 1) throw std::runtime_error("claims: bad version");
+    std::vector<Claim> cs(r.u32());
+    for (Claim& c : cs) {
+        c.id = r.str(r.u32());
+        c.comref = r.str(r.u32());
+        c.domain = r.u32();
+        c.n_rows = r.u32();
+        const uint32_t np = r.u32();
+        if (np > 64) throw std::runtime_error("claims: point too long");
+        c.point.resize(np);
+        r.bytes(c.point.data(), (size_t)np * FRB);
+        uint8_t tag;
+        r.bytes(&tag, 1);
+        if (tag != 0) throw std::invalid_argument("claims: committed evaluations are not built in this program (claim " + c.id + ")");
+        r.bytes(c.eval.v, FRB);
+    }
+    if (r.off != bytes.size()) throw std::runtime_error("claims: trailing bytes");
+    return cs;
+}
+inline std::vector<uint8_t> claims_serialize(const std::vector<Claim>& cs) {
+    std::vector<uint8_t> b;
+    put(b, "ZKCL", 4); put_u32(b, 1); put_u32(b, (uint32_t)cs.size());
+    for (const Claim& c : cs) { const std::vector<uint8_t> r = claim_blob(c); put(b, r.data(), r.size()); }
+    return b;
+}
+struct DrvState { std::string id; uint8_t state[32]; };
+inline std::vector<DrvState> drvstates_load(const std::string& path) {
+    const std::vector<uint8_t> bytes = read_file(path);
+    Reader r(bytes);
+    char magic[4];
+    r.bytes(magic, 4);
+    if (memcmp(magic, "ZKDS", 4)) throw std::runtime_error("drvstates: bad magic");
+    if (r.u32() != 1) throw std::runtime_error("drvstates: bad version");
+    std::vector<DrvState> ds(r.u32());
+    for (DrvState& d : ds) { d.id = r.str(r.u32()); r.bytes(d.state, 32); }
+    return ds;
+}
+// 1 + 2uv - u - v: the equality polynomial on one variable (my_eq / bo_eq1)
+inline Fr eq1(const Fr& u, const Fr& v) {
+    const Fr uv = fr_mul(u, v);
+    return fr_add(fr_sub(fr_add(uv, uv), fr_add(u, v)), fr_u32(1));
 }
 // the prover's pointer from a commitment file to the witness tensor behind it: one line per distinct tensor
 inline void witref_emit(const std::string& accdir, const std::string& comref, const std::string& witpath) {

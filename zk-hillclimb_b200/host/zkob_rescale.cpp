@@ -43,11 +43,6 @@ std::vector<Fr> range_table(const Lay& y) {
     for (uint32_t i = 0; i < y.N; i++) t[i] = fr_from_i64((int64_t)i - (int64_t)(y.sf >> 1));
     return t;
 }
-// 1 + 2uv - u - v (my_eq, zkllm-src/zkob_lookup.cuh:56-60)
-Fr eq1(const Fr& u, const Fr& v) {
-    const Fr uv = fr_mul(u, v);
-    return fr_add(fr_sub(fr_add(uv, uv), fr_add(u, v)), fr_u32(1));
-}
 // p(v) from p(0..3) (lagrange4, zkllm-src/zkob_lookup.cuh:62-73)
 Fr lagrange4(const std::array<Fr, 4>& p, const Fr& v, const Fr& inv6, const Fr& inv2) {
     const Fr zero{}, vm1 = fr_sub(v, fr_u32(1)), vm2 = fr_sub(v, fr_u32(2)), vm3 = fr_sub(v, fr_u32(3));
