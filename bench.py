@@ -702,6 +702,47 @@ def run_suite_fr(args):
                 line.update({"verify_s": time.perf_counter() - t0, "verify_accepts": rc == 0})
                 print(json.dumps(line), flush=True)
 
+            # the same two obligations as a claim-mode walk: both drivers emit their claims into one accumulator, the batch
+            # program discharges the six claims (one generator domain of 1024, tensors of 2^17 and 2^20 scalars)
+            exe_b = os.path.join(ROOT, "zk-hillclimb_b200", "zkob_batchopen")
+            ref_b = os.path.join(ROOT, "oracle", "_ref", "zkob_batchopen_ref")
+            walk, kept, secs = os.path.join(td, "walk"), {}, {}
+            gfile, qfile = os.path.join(td, "go"), os.path.join(td, "q")
+            subprocess.check_call([exe, "commit", os.path.join(td, "W"), str(IN_), str(OUT_), gfile, os.path.join(td, "cw1024")], stdout=subprocess.DEVNULL)
+            for rep, tag, progs in [(r_, t_, p_) for r_ in range(2) for t_, p_ in (("ours", (exe, exe_r, exe_b)), ("reference", (ref_exe, ref_r, ref_b)))]:
+                if not all(os.path.exists(p) for p in progs):
+                    continue
+                for d in ("", "/obfc", "/obrs", "/acc"):
+                    os.mkdir(walk + d)
+                t0 = time.perf_counter()
+                subprocess.check_call([progs[0], "prove", walk + "/obfc", "walk:fc", os.path.join(td, "X"), os.path.join(td, "W"), str(B_), str(IN_), str(OUT_),
+                                       gfile, gfile, qfile, "--claims", walk + "/acc", "l0.fc", os.path.join(td, "cw1024")], stdout=subprocess.DEVNULL)
+                subprocess.check_call([progs[1], "prove", walk + "/obrs", "walk:rs", os.path.join(td, "Y"), str(B_), str(OUT_), "16", gfile, qfile,
+                                       "--claims", walk + "/acc", "l0.rs"], stdout=subprocess.DEVNULL)
+                t1 = time.perf_counter()
+                subprocess.check_call([progs[2], "prove", walk + "/acc", "walk", qfile, "1024=" + gfile], stdout=subprocess.DEVNULL)
+                now = (t1 - t0, time.perf_counter() - t1)
+                secs[tag] = now if tag not in secs or sum(now) < sum(secs[tag]) else secs[tag]        # the better of two walks
+                kept[tag] = {f: open(os.path.join(walk, "acc", f), "rb").read() for f in ("claims.bin", "batch_sumcheck.bin", "batch_vfin.bin", "ipa_batch_1024.bin")}
+                if tag == "ours" and rep == 0:
+                    os.mkdir(walk + "/vacc")
+                    subprocess.check_call([exe, "verify", walk + "/obfc", "walk:fc", str(B_), str(IN_), str(OUT_), os.path.join(td, "cw1024"), gfile, gfile, qfile,
+                                           "--claims", walk + "/vacc", "l0.fc"], stdout=subprocess.DEVNULL)
+                    subprocess.check_call([exe_r, "verify", walk + "/obrs", "walk:rs", str(B_), str(OUT_), "16", gfile, qfile, "--claims", walk + "/vacc", "l0.rs"],
+                                          stdout=subprocess.DEVNULL)
+                    t0 = time.perf_counter()
+                    rc = subprocess.call([exe_b, "verify", walk + "/acc", walk + "/vacc", "walk", qfile, "1024=" + gfile], stdout=subprocess.DEVNULL)
+                    vsec = time.perf_counter() - t0
+                os.rename(walk, walk + "_%s%d" % (tag, rep))
+            if "ours" in secs:
+                line = {"suite": "claim-mode walk as programs: zkob_fc + zkob_rescale prove with --claims, then zkob_batchopen prove (6 claims, domain 1024)",
+                        "drivers_s": secs["ours"][0], "batch_prove_s": secs["ours"][1], "batch_verify_s": vsec, "batch_verify_accepts": rc == 0}
+                if "reference" in secs:
+                    line.update({"reference_drivers_s": secs["reference"][0], "reference_batch_prove_s": secs["reference"][1],
+                                 "speedup_batch_prove": secs["reference"][1] / secs["ours"][1],
+                                 "speedup_walk": sum(secs["reference"]) / sum(secs["ours"]), "same_files": bool(kept["ours"] == kept["reference"])})
+                print(json.dumps(line), flush=True)
+
 
 def run_profile_case(args):
     """--profile-case NAME: one small, self-terminating invocation of one kernel family (a few hundred MB on
