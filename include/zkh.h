@@ -579,6 +579,9 @@ ZKH_API int zkh_g1_pedersen_commit(zkh_ctx* ctx, const void* gens_dev, const voi
  * rescaling obligation (zkllm-src/zkob_rescale.cu:226-241, com_X[j] == sf com_Xr[j] + com_rem[j]).  s32: one scalar, host. */
 ZKH_API int zkh_g1_rows_check(zkh_ctx* ctx, const void* lhs_dev, const void* a_dev, const void* s32, const void* b_dev, uint32_t rows,
                               uint32_t* n_bad);
+/* out[j] = a[j] + b[j] for j < rows: the homomorphic sum of two commitment vectors (hom_add, zkllm-src/zkob_skip.cu:39-48), each
+ * sum the reference's Jacobian triple.  Stream-ordered; out_dev may not overlap the inputs. */
+ZKH_API int zkh_g1_rows_add(zkh_ctx* ctx, const void* a_dev, const void* b_dev, uint32_t rows, void* out_dev);
 ZKH_API int zkh_g1_msm(zkh_ctx* ctx, const void* g_dev, const void* a_dev, uint32_t n, void* out144);
 ZKH_API int zkh_g1_fold_chain(zkh_ctx* ctx, const void* src_dev, uint32_t size, const void* us, uint32_t nu, int orientation,
                               void* out144);

@@ -294,6 +294,14 @@ __global__ void __launch_bounds__(G1_WARP) g1_rows_check_kernel(const G1* __rest
     if ((threadIdx.x & 3) == 0 && !fp_is_zero(d.z)) atomicAdd(bad, 1u);
 }
 
+// out[j] = a[j] + b[j]: the homomorphic sum of two commitment vectors (hom_add of the skip-connection obligation,
+// zkllm-src/zkob_skip.cu:39-48); one quad per row
+__global__ void __launch_bounds__(G1_WARP) g1_rows_add_kernel(const G1* __restrict__ a, const G1* __restrict__ b, uint32_t rows, G1* __restrict__ out) {
+    const uint32_t j = quad_index();
+    if (j >= rows) return;
+    g1q_store(out + j, g1q_add(g1_load(a + j), g1_load(b + j), g1q_mask()));
+}
+
 static inline unsigned warp_blocks(size_t items) { return (unsigned)((items + G1_QPB - 1) / G1_QPB); }   // a quad per item
 
 // tab = tables of the n points at g, then out[i] = s(i) g[i]; stream-ordered
@@ -523,5 +531,15 @@ extern "C" int zkh_g1_rows_check(zkh_ctx* c, const void* lhs_dev, const void* a_
     ZKH_CUDA(c, cudaGetLastError());
     ZKH_CUDA(c, cudaMemcpyAsync(n_bad, bad, sizeof(unsigned int), cudaMemcpyDeviceToHost, c->stream));
     ZKH_CUDA(c, cudaStreamSynchronize(c->stream));
+    return ZKH_OK;
+}
+
+extern "C" int zkh_g1_rows_add(zkh_ctx* c, const void* a_dev, const void* b_dev, uint32_t rows, void* out_dev) {
+    if (!c || !a_dev || !b_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_add: null pointer");
+    if (!rows) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_add: no rows");
+    if (((uintptr_t)a_dev | (uintptr_t)b_dev | (uintptr_t)out_dev) & 15) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_add: buffers must be 16-byte aligned");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    g1_rows_add_kernel<<<warp_blocks(rows), G1_WARP, 0, c->stream>>>((const G1*)a_dev, (const G1*)b_dev, rows, (G1*)out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }
