@@ -582,6 +582,10 @@ ZKH_API int zkh_g1_rows_check(zkh_ctx* ctx, const void* lhs_dev, const void* a_d
 /* out[j] = a[j] + b[j] for j < rows: the homomorphic sum of two commitment vectors (hom_add, zkllm-src/zkob_skip.cu:39-48), each
  * sum the reference's Jacobian triple.  Stream-ordered; out_dev may not overlap the inputs. */
 ZKH_API int zkh_g1_rows_add(zkh_ctx* ctx, const void* a_dev, const void* b_dev, uint32_t rows, void* out_dev);
+/* out[j] = s a[j] + b[j] for j < rows, each the reference's Jacobian triple: hb_addmul (zkllm-src/zkob_fastg1.cuh:56-92), the
+ * combined commitment com_G + r com_S of the mapping-lookup drivers; mul_first selects the operand order of the addition
+ * (1: (s a) + b, 0: b + (s a)).  s32: one scalar, host.  Stream-ordered; out_dev may not overlap the inputs. */
+ZKH_API int zkh_g1_rows_lincomb(zkh_ctx* ctx, const void* a_dev, const void* s32, const void* b_dev, uint32_t rows, int mul_first, void* out_dev);
 ZKH_API int zkh_g1_msm(zkh_ctx* ctx, const void* g_dev, const void* a_dev, uint32_t n, void* out144);
 ZKH_API int zkh_g1_fold_chain(zkh_ctx* ctx, const void* src_dev, uint32_t size, const void* us, uint32_t nu, int orientation,
                               void* out144);

@@ -116,6 +116,7 @@ def load_library():
         "zkh_gl_gather_xor": (i, [vp, vp, u64, u64, vp]),
         "zkh_g1_pedersen_commit": (i, [vp, vp, vp, u32, u32, vp]),
         "zkh_g1_msm": (i, [vp, vp, vp, u32, vp]),
+        "zkh_g1_rows_lincomb": (i, [vp, vp, vp, vp, u32, i, vp]),
         "zkh_g1_rows_add": (i, [vp, vp, vp, u32, vp]),
         "zkh_fr_axpy": (i, [vp, vp, vp, vp, u64]),
         "zkh_fr_round_sums": (i, [vp, vp, vp, u64, vp]),

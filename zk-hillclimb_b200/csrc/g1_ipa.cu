@@ -302,6 +302,24 @@ __global__ void __launch_bounds__(G1_WARP) g1_rows_add_kernel(const G1* __restri
     g1q_store(out + j, g1q_add(g1_load(a + j), g1_load(b + j), g1q_mask()));
 }
 
+// out[j] = s a[j] + b[j] with the operand order of the reference's host helpers (hb_addmul, zkllm-src/zkob_fastg1.cuh:56-92):
+// mul_first ? add(mul(a, s), b) : add(b, mul(a, s)); mul in the order of G1Jacobian_mul; one quad per row
+__global__ void __launch_bounds__(G1_WARP) g1_rows_lincomb_kernel(const G1* __restrict__ a, Fr s, const G1* __restrict__ b, uint32_t rows, int mul_first,
+                                                                G1* __restrict__ out) {
+    const uint32_t j = quad_index();
+    if (j >= rows) return;
+    const uint32_t qm = g1q_mask();
+    G1 acc = g1_zero(), p = g1_load(a + j);
+    int top = 255;
+    while (top >= 0 && !((s.v[top >> 5] >> (top & 31)) & 1u)) top--;
+    for (int k = 0; k <= top; k++) {
+        if ((s.v[k >> 5] >> (k & 31)) & 1u) acc = g1q_add(acc, p, qm);
+        if (k < top) p = g1q_double(p, qm);
+    }
+    const G1 bj = g1_load(b + j);
+    g1q_store(out + j, mul_first ? g1q_add(acc, bj, qm) : g1q_add(bj, acc, qm));
+}
+
 static inline unsigned warp_blocks(size_t items) { return (unsigned)((items + G1_QPB - 1) / G1_QPB); }   // a quad per item
 
 // tab = tables of the n points at g, then out[i] = s(i) g[i]; stream-ordered
@@ -540,6 +558,19 @@ extern "C" int zkh_g1_rows_add(zkh_ctx* c, const void* a_dev, const void* b_dev,
     if (((uintptr_t)a_dev | (uintptr_t)b_dev | (uintptr_t)out_dev) & 15) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_add: buffers must be 16-byte aligned");
     ZKH_CUDA(c, cudaSetDevice(c->device));
     g1_rows_add_kernel<<<warp_blocks(rows), G1_WARP, 0, c->stream>>>((const G1*)a_dev, (const G1*)b_dev, rows, (G1*)out_dev);
+    ZKH_CUDA(c, cudaGetLastError());
+    return ZKH_OK;
+}
+
+extern "C" int zkh_g1_rows_lincomb(zkh_ctx* c, const void* a_dev, const void* s32, const void* b_dev, uint32_t rows, int mul_first, void* out_dev) {
+    if (!c || !a_dev || !s32 || !b_dev || !out_dev) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_lincomb: null pointer");
+    if (!rows) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_lincomb: no rows");
+    if (((uintptr_t)a_dev | (uintptr_t)b_dev | (uintptr_t)out_dev) & 15) return zkh_fail(c, ZKH_ERR_ARG, "g1_rows_lincomb: buffers must be 16-byte aligned");
+    if (!fr_canonical((const uint32_t*)s32)) return zkh_fail(c, ZKH_ERR_DOMAIN, "g1_rows_lincomb: scalar not below p");
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    Fr s;
+    memcpy(s.v, s32, 32);
+    g1_rows_lincomb_kernel<<<warp_blocks(rows), G1_WARP, 0, c->stream>>>((const G1*)a_dev, s, (const G1*)b_dev, rows, mul_first, (G1*)out_dev);
     ZKH_CUDA(c, cudaGetLastError());
     return ZKH_OK;
 }

@@ -3,6 +3,7 @@
 // (zkllm-src/vrf_common.cuh:219-250), and the row-committed openings open_prove / open_verify (zkllm-src/zkob_lookup.cuh:112-138)
 // over the C ABI.
 #pragma once
+#include <array>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -459,6 +460,78 @@ inline Fr fr_inv(const Fr& a) {
         if ((e.v[i >> 5] >> (i & 31)) & 1u) r = fr_mul(r, a);
     }
     return r;
+}
+
+// p(v) from p(0..3) (lagrange4, zkllm-src/zkob_lookup.cuh:62-73)
+Fr lagrange4(const std::array<Fr, 4>& p, const Fr& v, const Fr& inv6, const Fr& inv2) {
+    const Fr zero{}, vm1 = fr_sub(v, fr_u32(1)), vm2 = fr_sub(v, fr_u32(2)), vm3 = fr_sub(v, fr_u32(3));
+    const Fr l0 = fr_sub(zero, fr_mul(fr_mul(fr_mul(vm1, vm2), vm3), inv6));
+    const Fr l1 = fr_mul(fr_mul(fr_mul(v, vm2), vm3), inv2);
+    const Fr l2 = fr_sub(zero, fr_mul(fr_mul(fr_mul(v, vm1), vm3), inv2));
+    const Fr l3 = fr_mul(fr_mul(fr_mul(v, vm1), vm2), inv6);
+    return fr_add(fr_add(fr_add(fr_mul(p[0], l0), fr_mul(p[1], l1)), fr_mul(p[2], l2)), fr_mul(p[3], l3));
+}
+
+// a flat tensor of rows x G scalars committed row-wise, opened at u_pt = (column bits, then row bits) (open_prove)
+void open_prove(Ctx& x, const Dev& t, uint32_t rows, uint32_t G, const Dev& gens, const uint8_t* Q, const std::vector<Fr>& u_pt, const std::string& path,
+                Transcript& tr) {
+    const uint32_t logG = clog2(G);
+    const std::vector<Fr> u_col(u_pt.begin(), u_pt.begin() + logG), u_row(u_pt.begin() + logG, u_pt.end());
+    if ((1u << u_row.size()) != rows) throw std::runtime_error("open_prove: point does not match the tensor");
+    Dev a(x, (size_t)G * FRB);
+    partial_me(x, t, 1, (uint32_t)u_row.size(), G, u_row, a);
+    ipa_to_file(x, path, a, u_col, gens, Q, G, tr);
+}
+bool open_check(Ctx& x, const std::vector<uint8_t>& com, uint32_t G, const Dev& gens, const uint8_t* Q, const std::vector<Fr>& u_pt, const Fr& eval,
+                const std::string& path, Transcript& tr) {
+    const uint32_t logG = clog2(G);
+    if (u_pt.size() < logG) return false;
+    const uint32_t rows = (uint32_t)(com.size() / G1B);
+    if (rows != (1u << (u_pt.size() - logG))) return false;
+    const std::vector<Fr> u_col(u_pt.begin(), u_pt.begin() + logG), u_row(u_pt.begin() + logG, u_pt.end());
+    return open_verify(x, com, rows, u_row, eval, gens, G, Q, u_col, read_ipa(path), tr);
+}
+
+// The verifier's side of the logUp lookup sumcheck (zkllm-src/zkob_rescale.cu:256-313, zkob_glu.cu:341-394): the round checks with
+// the anchor alpha + alpha^2 recomputed, B_f and T_f from the PUBLIC table (T_dev, 2^logN scalars, consumed) folded with the
+// phase-2 challenges in round order, and the terminal identity.  Prints the reference's REJECT lines.  ws: the round challenges.
+inline bool lookup_verify(Ctx& x, Transcript& tr, const std::vector<Fr>& ev, const Fr& A_f, const Fr& S_f, const Fr& m_f, const Fr& alpha,
+                          const Fr& beta, const std::vector<Fr>& u, Dev& T_dev, uint32_t logD, uint32_t logN, std::vector<Fr>& ws, Laps& laps) {
+    const uint32_t n1 = logD - logN, N = 1u << logN;
+    const Fr inv2 = fr_inv(fr_u32(2)), inv6 = fr_inv(fr_u32(6));
+    Fr alpha_acc = alpha, alphasq_acc = fr_mul(alpha, alpha), cur = fr_add(alpha, alphasq_acc);
+    ws.clear();
+    for (uint32_t k = 0; k < logD; k++) {
+        const std::array<Fr, 4> e = {ev[4 * k], ev[4 * k + 1], ev[4 * k + 2], ev[4 * k + 3]};
+        if (!fr_eq(cur, fr_add(e[0], e[1]))) { std::cout << "REJECT: lookup round " << k << " p(0)+p(1) != claim" << std::endl; return false; }
+        tr.absorb_fr("p0", e[0]); tr.absorb_fr("p1", e[1]); tr.absorb_fr("p2", e[2]); tr.absorb_fr("p3", e[3]);
+        const Fr w = tr.challenge_fr();
+        ws.push_back(w);
+        cur = lagrange4(e, w, inv6, inv2);
+        const Fr eqv = eq1(u[logD - 1 - k], w);
+        alpha_acc = fr_mul(alpha_acc, eqv);
+        if (k >= n1) alphasq_acc = fr_mul(alphasq_acc, eqv);
+    }
+    laps.lap("rounds");
+    Fr B_f, T_f;
+    {
+        Dev bd(x, (size_t)N * FRB);
+        x.ck(zkh_fr_inv_add(x.c, T_dev.p, N, beta.v, bd.p), "B = 1 / (T + beta)");
+        for (uint32_t k = 0, sz = N; k < logN; k++, sz >>= 1) {         // each fold binds the current top bit, in place
+            x.ck(zkh_fr_fold(x.c, bd.p, sz / 2, ws[n1 + k].v, bd.p), "fold B");
+            x.ck(zkh_fr_fold(x.c, T_dev.p, sz / 2, ws[n1 + k].v, T_dev.p), "fold T");
+        }
+        x.ck(zkh_download(x.c, B_f.v, bd.p, FRB), "download");
+        x.ck(zkh_download(x.c, T_f.v, T_dev.p, FRB), "download");
+    }
+    laps.lap("table_fold");
+    const Fr inv_ratio = fr_mul(fr_u32(N), fr_inv(fr_u32(1u << logD)));
+    const Fr t1 = fr_mul(alpha_acc, fr_mul(A_f, fr_add(S_f, beta)));
+    const Fr t2 = fr_mul(inv_ratio, fr_mul(alphasq_acc, fr_mul(B_f, fr_add(T_f, beta))));
+    const Fr t4 = fr_mul(inv_ratio, fr_mul(m_f, B_f));
+    if (!fr_eq(cur, fr_sub(fr_add(fr_add(t1, t2), A_f), t4))) { std::cout << "REJECT: lookup terminal identity" << std::endl; return false; }
+    laps.lap("terminal");
+    return true;
 }
 
 }  // namespace zkob

@@ -17,8 +17,6 @@
 // com_A -> alpha, u; per round p(0..3) -> w_r; A_f, S_f, m_f; the three openings at the reversed round challenges.
 #include "zkob_common.hpp"
 
-#include <array>
-
 using namespace zkob;
 
 namespace {
@@ -43,36 +41,6 @@ std::vector<Fr> range_table(const Lay& y) {
     for (uint32_t i = 0; i < y.N; i++) t[i] = fr_from_i64((int64_t)i - (int64_t)(y.sf >> 1));
     return t;
 }
-// p(v) from p(0..3) (lagrange4, zkllm-src/zkob_lookup.cuh:62-73)
-Fr lagrange4(const std::array<Fr, 4>& p, const Fr& v, const Fr& inv6, const Fr& inv2) {
-    const Fr zero{}, vm1 = fr_sub(v, fr_u32(1)), vm2 = fr_sub(v, fr_u32(2)), vm3 = fr_sub(v, fr_u32(3));
-    const Fr l0 = fr_sub(zero, fr_mul(fr_mul(fr_mul(vm1, vm2), vm3), inv6));
-    const Fr l1 = fr_mul(fr_mul(fr_mul(v, vm2), vm3), inv2);
-    const Fr l2 = fr_sub(zero, fr_mul(fr_mul(fr_mul(v, vm1), vm3), inv2));
-    const Fr l3 = fr_mul(fr_mul(fr_mul(v, vm1), vm2), inv6);
-    return fr_add(fr_add(fr_add(fr_mul(p[0], l0), fr_mul(p[1], l1)), fr_mul(p[2], l2)), fr_mul(p[3], l3));
-}
-
-// a flat tensor of rows x G scalars committed row-wise, opened at u_pt = (column bits, then row bits) (open_prove)
-void open_prove(Ctx& x, const Dev& t, uint32_t rows, uint32_t G, const Dev& gens, const uint8_t* Q, const std::vector<Fr>& u_pt, const std::string& path,
-                Transcript& tr) {
-    const uint32_t logG = clog2(G);
-    const std::vector<Fr> u_col(u_pt.begin(), u_pt.begin() + logG), u_row(u_pt.begin() + logG, u_pt.end());
-    if ((1u << u_row.size()) != rows) throw std::runtime_error("open_prove: point does not match the tensor");
-    Dev a(x, (size_t)G * FRB);
-    partial_me(x, t, 1, (uint32_t)u_row.size(), G, u_row, a);
-    ipa_to_file(x, path, a, u_col, gens, Q, G, tr);
-}
-bool open_check(Ctx& x, const std::vector<uint8_t>& com, uint32_t G, const Dev& gens, const uint8_t* Q, const std::vector<Fr>& u_pt, const Fr& eval,
-                const std::string& path, Transcript& tr) {
-    const uint32_t logG = clog2(G);
-    if (u_pt.size() < logG) return false;
-    const uint32_t rows = (uint32_t)(com.size() / G1B);
-    if (rows != (1u << (u_pt.size() - logG))) return false;
-    const std::vector<Fr> u_col(u_pt.begin(), u_pt.begin() + logG), u_row(u_pt.begin() + logG, u_pt.end());
-    return open_verify(x, com, rows, u_row, eval, gens, G, Q, u_col, read_ipa(path), tr);
-}
-
 int do_prove(int argc, char** argv) {
     const ClaimFlags cf = claim_flags(argc, argv);
     argc = cf.base_argc;
@@ -236,47 +204,15 @@ bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay
     const Fr alpha = tr.challenge_fr();
     const std::vector<Fr> u = tr.challenge_vec(y.logD);
 
-    // (2) the lookup rounds: anchor recomputed, then the Lagrange chain
-    const Fr inv2 = fr_inv(fr_u32(2)), inv6 = fr_inv(fr_u32(6));
-    Fr alpha_acc = alpha, alphasq_acc = fr_mul(alpha, alpha), cur = fr_add(alpha, alphasq_acc);
+    // (2) the lookup rounds, (3) B_f and T_f from the public table, (4) the terminal identity
     std::vector<Fr> ws;
-    for (uint32_t k = 0; k < y.logD; k++) {
-        const std::array<Fr, 4> e = {ev[4 * k], ev[4 * k + 1], ev[4 * k + 2], ev[4 * k + 3]};
-        if (!fr_eq(cur, fr_add(e[0], e[1]))) { std::cout << "REJECT: lookup round " << k << " p(0)+p(1) != claim" << std::endl; return false; }
-        tr.absorb_fr("p0", e[0]); tr.absorb_fr("p1", e[1]); tr.absorb_fr("p2", e[2]); tr.absorb_fr("p3", e[3]);
-        const Fr w = tr.challenge_fr();
-        ws.push_back(w);
-        cur = lagrange4(e, w, inv6, inv2);
-        const Fr eqv = eq1(u[y.logD - 1 - k], w);
-        alpha_acc = fr_mul(alpha_acc, eqv);
-        if (k >= y.n1) alphasq_acc = fr_mul(alphasq_acc, eqv);
-    }
-    laps.lap("rounds");
-    // (3) B_f, T_f from the public table, folded with the phase-2 challenges in round order (each binds the current top bit)
-    Fr B_f, T_f;
     {
         const std::vector<Fr> Tp = range_table(y);
-        Dev td(x, Tp.data(), Tp.size() * FRB), bd(x, (size_t)y.N * FRB), t2(x, (size_t)y.N * FRB / 2 + FRB), b2(x, (size_t)y.N * FRB / 2 + FRB);
-        x.ck(zkh_fr_inv_add(x.c, td.p, y.N, beta.v, bd.p), "B = 1 / (T + beta)");
-        void *tc = td.p, *tn = t2.p, *bc = bd.p, *bn = b2.p;
-        for (uint32_t k = 0, sz = y.N; k < y.logN; k++, sz >>= 1) {
-            x.ck(zkh_fr_fold(x.c, bc, sz / 2, ws[y.n1 + k].v, bn), "fold B");
-            x.ck(zkh_fr_fold(x.c, tc, sz / 2, ws[y.n1 + k].v, tn), "fold T");
-            std::swap(bc, bn); std::swap(tc, tn);
-        }
-        x.ck(zkh_download(x.c, B_f.v, bc, FRB), "download");
-        x.ck(zkh_download(x.c, T_f.v, tc, FRB), "download");
+        Dev td(x, Tp.data(), Tp.size() * FRB);
+        if (!lookup_verify(x, tr, ev, A_f, S_f, m_f, alpha, beta, u, td, y.logD, y.logN, ws, laps)) return false;
     }
-    laps.lap("table_fold");
-    // (4) the terminal identity
-    const Fr inv_ratio = fr_mul(fr_u32(y.N), fr_inv(fr_u32(y.D)));
-    const Fr t1 = fr_mul(alpha_acc, fr_mul(A_f, fr_add(S_f, beta)));
-    const Fr t2 = fr_mul(inv_ratio, fr_mul(alphasq_acc, fr_mul(B_f, fr_add(T_f, beta))));
-    const Fr t4 = fr_mul(inv_ratio, fr_mul(m_f, B_f));
-    if (!fr_eq(cur, fr_sub(fr_add(fr_add(t1, t2), A_f), t4))) { std::cout << "REJECT: lookup terminal identity" << std::endl; return false; }
     tr.absorb_fr("A_f", A_f); tr.absorb_fr("S_f", S_f); tr.absorb_fr("m_f", m_f);
 
-    laps.lap("terminal");
     // (5) the openings bind the terminals to the commitments
     const std::vector<Fr> u_pt(ws.rbegin(), ws.rend()), u_m(ws.rbegin(), ws.rend() - y.n1);
     if (cf.on()) {
