@@ -10,6 +10,7 @@
 #include <cstring>
 #include <exception>
 #include <iostream>
+#include <memory>
 #include <sstream>
 #include <stdexcept>
 #include <string>
