@@ -522,6 +522,9 @@ ZKH_API int zkh_fr_mle_eval(zkh_ctx* ctx, const void* t_dev, const void* u, uint
 /* out[i] += c * in[i] over n elements: k_bo_axpy of the batch opening (zkllm-src/zkob_claims.cuh:386-391).  c32: one scalar, host.
  * Stream-ordered. */
 ZKH_API int zkh_fr_axpy(zkh_ctx* ctx, void* out_dev, const void* in_dev, const void* c32, uint64_t n);
+/* out[i] = a[i] * b[i] over n elements, out may alias an input: FrTensor::operator* (zkllm-src/fr-tensor.cu:141-147, :343-350).
+ * Stream-ordered. */
+ZKH_API int zkh_fr_mul(zkh_ctx* ctx, void* out_dev, const void* a_dev, const void* b_dev, uint64_t n);
 /* The three round evaluations (t = 0, 1, 2) of sum_x a(x) b(x) with the top variable free: sum over i < h of
  * (a[i] + t (a[i+h] - a[i])) (b[i] + t (b[i+h] - b[i])): k_bo_hp2 plus its three sums (zkllm-src/zkob_claims.cuh:365-384, :930-937).
  * out96: three scalars, host; the call synchronises the stream. */

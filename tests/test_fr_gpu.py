@@ -149,6 +149,19 @@ def test_inv_add(zk, prover, n):
     assert got == fo.inv_add(vals, beta)
 
 
+@pytest.mark.parametrize("n", [1, 5, 1000, 40000])
+def test_elementwise_product(zk, prover, n):
+    rng = random.Random(n)
+    fr = zk.fr
+    a, b = rnd(rng, n), rnd(rng, n)
+    a[0], b[n - 1] = fo.P - 1, 0
+    da, db = fr.to_device(a), fr.to_device(b)
+    want = [x * y % fo.P for x, y in zip(a, b)]
+    assert fr.to_host(fr.mul(prover, da, db)) == want
+    prover._ck(prover._L.zkh_fr_mul(prover._h, da.data_ptr(), da.data_ptr(), db.data_ptr(), n))     # in place
+    assert fr.to_host(da) == want
+
+
 @pytest.mark.parametrize("logD,logN", [(1, 1), (3, 3), (5, 2), (9, 6), (12, 12), (13, 8)])
 def test_lookup_sumcheck(zk, prover, logD, logN):
     rng = random.Random(logD * 31 + logN)

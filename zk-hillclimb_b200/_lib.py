@@ -120,6 +120,7 @@ def load_library():
         "zkh_g1_rows_add": (i, [vp, vp, vp, u32, vp]),
         "zkh_fr_axpy": (i, [vp, vp, vp, vp, u64]),
         "zkh_fr_round_sums": (i, [vp, vp, vp, u64, vp]),
+        "zkh_fr_mul": (i, [vp, vp, vp, vp, u64]),
         "zkh_g1_rows_check": (i, [vp, vp, vp, vp, vp, u32, vp]),
         "zkh_g1_fold_chain": (i, [vp, vp, u32, vp, u32, i, vp]),
         "zkh_g1_ipa_prove": (i, [vp, vp, vp, vp, vp, u32, vp, vp, vp, vp]),

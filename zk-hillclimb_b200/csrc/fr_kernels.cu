@@ -248,6 +248,11 @@ __global__ void __launch_bounds__(FR_THREADS) fr_axpy_plain_kernel(Fr* out, cons
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         fr_store(out + i, fr_add(fr_load(out + i), fr_mmul(cm, fr_load(in + i))));
 }
+// out[i] = a[i] * b[i], all plain (Fr_elementwise_mul, zkllm-src/fr-tensor.cu:141-147); out may alias a or b
+__global__ void __launch_bounds__(FR_THREADS) fr_mul_plain_kernel(Fr* out, const Fr* a, const Fr* b, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        fr_store(out + i, fr_mmul(fr_to_mont(fr_load(a + i)), fr_load(b + i)));
+}
 // partials[b][t] = sum over this CTA of (a_i + t da_i)(b_i + t db_i) / R for t = 0, 1, 2, pairs (i, i + h): the round
 // evaluations of sum_x M(x) P(x) with the top variable free (k_bo_hp2, zkllm-src/zkob_claims.cuh:365-384)
 __global__ void __launch_bounds__(FR_THREADS) fr_round_sums_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, size_t h, Fr* partials) {
@@ -485,6 +490,15 @@ extern "C" int zkh_fr_axpy(zkh_ctx* c, void* out_dev, const void* in_dev, const 
     memcpy(cv.v, c32, 32);
     fr_axpy_plain_kernel<<<fr_grid(c, n, 8), FR_THREADS, 0, c->stream>>>((Fr*)out_dev, (const Fr*)in_dev, cv, (size_t)n);
     return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(c, ZKH_ERR_CUDA, "fr_axpy launch");
+}
+
+extern "C" int zkh_fr_mul(zkh_ctx* c, void* out_dev, const void* a_dev, const void* b_dev, uint64_t n) {
+    if (!c) return ZKH_ERR_ARG;
+    if (!out_dev || !a_dev || !b_dev) return zkh_fail(c, ZKH_ERR_ARG, "fr_mul: bad arguments");
+    if (!n) return ZKH_OK;
+    ZKH_CUDA(c, cudaSetDevice(c->device));
+    fr_mul_plain_kernel<<<fr_grid(c, n, 8), FR_THREADS, 0, c->stream>>>((Fr*)out_dev, (const Fr*)a_dev, (const Fr*)b_dev, (size_t)n);
+    return cudaGetLastError() == cudaSuccess ? ZKH_OK : zkh_fail(c, ZKH_ERR_CUDA, "fr_mul launch");
 }
 
 extern "C" int zkh_fr_round_sums(zkh_ctx* c, const void* a_dev, const void* b_dev, uint64_t h, void* out96) {

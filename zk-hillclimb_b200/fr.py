@@ -127,6 +127,13 @@ def inv_add(prover, t, beta):
     return out
 
 
+def mul(prover, a, b):
+    """Element-wise product a * b (FrTensor::operator*, zkllm-src/fr-tensor.cu:343-350)."""
+    out = _new(prover, a.shape[0])
+    prover._ck(prover._L.zkh_fr_mul(prover._h, out.data_ptr(), a.data_ptr(), b.data_ptr(), a.shape[0]))
+    return out
+
+
 def dot(prover, a, b):
     """(a * b).sum() over Fr."""
     out = (C.c_uint8 * 32)()
