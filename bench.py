@@ -743,6 +743,64 @@ def run_suite_fr(args):
                                  "speedup_walk": sum(secs["reference"]) / sum(secs["ours"]), "same_files": bool(kept["ours"] == kept["reference"])})
                 print(json.dumps(line), flush=True)
 
+            # the attention-side structural obligations of the same layer as programs: rotary embedding of a 128 x 768 tensor, the
+            # per-head slicing of Q, K, V and the merge of the 12 head outputs (head width 64)
+            HD_ = 64
+            buf = (C.c_uint8 * (HD_ * 144))()
+            refA.lib.refA_commit_random(C.c_uint32(HD_), buf)
+            open(os.path.join(td, "g64"), "wb").write(bytes(buf))
+            f_ = lambda k: os.path.join(td, k)
+            open(f_("T"), "wb").write(rng.integers(-(1 << 15), 1 << 15, B_ * OUT_, dtype=np.int32).tobytes())
+            for k in ("Q", "K", "V"):                                   # the slicing driver commits the transposed key slices with a set of B generators: B = 64
+                open(f_(k), "wb").write(rng.integers(-(1 << 15), 1 << 15, 64 * OUT_, dtype=np.int32).tobytes())
+            ang = rng.uniform(0, 2 * np.pi, (B_, HD_))
+            open(f_("cos"), "wb").write(np.rint(np.cos(ang) * 65536).astype(np.int32).tobytes())
+            open(f_("sin"), "wb").write(np.rint(np.sin(ang) * 65536).astype(np.int32).tobytes())
+            for h in range(OUT_ // HD_):
+                open(f_("O%02d.i32.bin" % h), "wb").write(rng.integers(-(1 << 15), 1 << 15, B_ * HD_, dtype=np.int32).tobytes())
+            cases = (
+                ("zkob_rope", "rotary embedding, 128 x 768, head width 64 (two commitments, two 17-round Hadamard sumchecks, three inner-product arguments, files)",
+                 lambda d: [f_("T"), B_, OUT_, HD_, f_("cos"), f_("sin"), f_("go"), f_("q")],
+                 lambda d: [B_, OUT_, HD_, f_("cos"), f_("sin"), f_("go"), f_("q")]),
+                ("zkob_headmerge", "merge of 12 head outputs into 128 x 768 through the transpose-and-reshape permutation (13 commitments, twelve 13-round Hadamard sumchecks, 13 inner-product arguments, files)",
+                 lambda d: [f_("O"), B_, OUT_, HD_, "pi157", f_("go"), f_("g64"), f_("q")],
+                 lambda d: [B_, OUT_, HD_, "pi157", f_("go"), f_("g64"), f_("q")]),
+                ("zkob_headslice", "per-head slicing of Q, K, V, 64 x 768 into 12 heads (39 commitments, 72 inner-product arguments, files)",
+                 lambda d: [f_("Q"), f_("K"), f_("V"), 64, OUT_, HD_, f_("go"), f_("g64"), f_("q")],
+                 lambda d: [64, OUT_, HD_, f_("go"), f_("g64"), f_("q")]),
+            )
+            for prog, what, pargs, vargs in cases:
+                mine, theirs = os.path.join(ROOT, "zk-hillclimb_b200", prog), os.path.join(ROOT, "oracle", "_ref", prog + "_ref")
+                if not os.path.exists(mine):
+                    continue
+                res = {}
+                for tag, exe_ in (("ours", mine), ("reference", theirs)):
+                    if not os.path.exists(exe_):
+                        continue
+                    d = os.path.join(td, prog + "_" + tag)
+                    best = 1e30
+                    for _ in range(2):
+                        if os.path.isdir(d):
+                            for fn in os.listdir(d):
+                                os.unlink(os.path.join(d, fn))
+                        else:
+                            os.mkdir(d)
+                        t0 = time.perf_counter()
+                        subprocess.check_call([exe_, "prove", d, "bench-seed"] + [str(a) for a in pargs(d)], stdout=subprocess.DEVNULL)
+                        best = min(best, time.perf_counter() - t0)
+                    res[tag] = best
+                line = {"suite": prog + " prove as a program: " + what, "s": res["ours"]}
+                if "reference" in res:
+                    d0, d1 = os.path.join(td, prog + "_ours"), os.path.join(td, prog + "_reference")
+                    same = sorted(os.listdir(d0)) == sorted(os.listdir(d1)) and all(
+                        open(os.path.join(d0, fn), "rb").read() == open(os.path.join(d1, fn), "rb").read() for fn in os.listdir(d1))
+                    line.update({"reference_program_s": res["reference"], "speedup_vs_reference_program": res["reference"] / res["ours"],
+                                 "files": len(os.listdir(d1)), "same_files": bool(same)})
+                t0 = time.perf_counter()
+                rc = subprocess.call([mine, "verify", os.path.join(td, prog + "_ours"), "bench-seed"] + [str(a) for a in vargs(None)], stdout=subprocess.DEVNULL)
+                line.update({"verify_s": time.perf_counter() - t0, "verify_accepts": rc == 0})
+                print(json.dumps(line), flush=True)
+
 
 def run_profile_case(args):
     """--profile-case NAME: one small, self-terminating invocation of one kernel family (a few hundred MB on

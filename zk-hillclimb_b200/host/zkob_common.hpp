@@ -495,16 +495,18 @@ bool open_check(Ctx& x, const std::vector<uint8_t>& com, uint32_t G, const Dev& 
 
 // The verifier's side of the logUp lookup sumcheck (zkllm-src/zkob_rescale.cu:256-313, zkob_glu.cu:341-394): the round checks with
 // the anchor alpha + alpha^2 recomputed, B_f and T_f from the PUBLIC table (T_dev, 2^logN scalars, consumed) folded with the
-// phase-2 challenges in round order, and the terminal identity.  Prints the reference's REJECT lines.  ws: the round challenges.
+// phase-2 challenges in round order, and the terminal identity.  Prints the reference's REJECT lines (tag names the lookup in them).
+// ws: the round challenges.
 inline bool lookup_verify(Ctx& x, Transcript& tr, const std::vector<Fr>& ev, const Fr& A_f, const Fr& S_f, const Fr& m_f, const Fr& alpha,
-                          const Fr& beta, const std::vector<Fr>& u, Dev& T_dev, uint32_t logD, uint32_t logN, std::vector<Fr>& ws, Laps& laps) {
+                          const Fr& beta, const std::vector<Fr>& u, Dev& T_dev, uint32_t logD, uint32_t logN, std::vector<Fr>& ws, Laps& laps,
+                          const char* tag = "lookup") {
     const uint32_t n1 = logD - logN, N = 1u << logN;
     const Fr inv2 = fr_inv(fr_u32(2)), inv6 = fr_inv(fr_u32(6));
     Fr alpha_acc = alpha, alphasq_acc = fr_mul(alpha, alpha), cur = fr_add(alpha, alphasq_acc);
     ws.clear();
     for (uint32_t k = 0; k < logD; k++) {
         const std::array<Fr, 4> e = {ev[4 * k], ev[4 * k + 1], ev[4 * k + 2], ev[4 * k + 3]};
-        if (!fr_eq(cur, fr_add(e[0], e[1]))) { std::cout << "REJECT: lookup round " << k << " p(0)+p(1) != claim" << std::endl; return false; }
+        if (!fr_eq(cur, fr_add(e[0], e[1]))) { std::cout << "REJECT: " << tag << " round " << k << " p(0)+p(1) != claim" << std::endl; return false; }
         tr.absorb_fr("p0", e[0]); tr.absorb_fr("p1", e[1]); tr.absorb_fr("p2", e[2]); tr.absorb_fr("p3", e[3]);
         const Fr w = tr.challenge_fr();
         ws.push_back(w);
@@ -530,7 +532,7 @@ inline bool lookup_verify(Ctx& x, Transcript& tr, const std::vector<Fr>& ev, con
     const Fr t1 = fr_mul(alpha_acc, fr_mul(A_f, fr_add(S_f, beta)));
     const Fr t2 = fr_mul(inv_ratio, fr_mul(alphasq_acc, fr_mul(B_f, fr_add(T_f, beta))));
     const Fr t4 = fr_mul(inv_ratio, fr_mul(m_f, B_f));
-    if (!fr_eq(cur, fr_sub(fr_add(fr_add(t1, t2), A_f), t4))) { std::cout << "REJECT: lookup terminal identity" << std::endl; return false; }
+    if (!fr_eq(cur, fr_sub(fr_add(fr_add(t1, t2), A_f), t4))) { std::cout << "REJECT: " << tag << " terminal identity" << std::endl; return false; }
     laps.lap("terminal");
     return true;
 }
