@@ -758,7 +758,16 @@ def run_suite_fr(args):
             open(f_("sin"), "wb").write(np.rint(np.sin(ang) * 65536).astype(np.int32).tobytes())
             for h in range(OUT_ // HD_):
                 open(f_("O%02d.i32.bin" % h), "wb").write(rng.integers(-(1 << 15), 1 << 15, B_ * HD_, dtype=np.int32).tobytes())
+            SB_, SLE_, SLR_ = 256, 1024, 8192                      # one head's 256 x 256 score grid, exp table of 1024 rows at scale 2^16, 13-bit limbs
+            buf = (C.c_uint8 * (SB_ * 144))()
+            refA.lib.refA_commit_random(C.c_uint32(SB_), buf)
+            open(f_("g256"), "wb").write(bytes(buf))
+            open(f_("z"), "wb").write(rng.integers(1 - SLE_, 1, SB_ * SB_, dtype=np.int32).tobytes())
+            open(f_("expmap"), "wb").write(np.maximum(1, np.rint(65536 * np.exp(np.arange(1 - SLE_, 1) * (8.0 / SLE_)))).astype(np.int32).tobytes())
             cases = (
+                ("zkob_softmax", "causal softmax of a 256 x 256 score grid (9 commitments, a 16-round and an 18-round lookup sumcheck, three 16-round Hadamard sumchecks, 16 inner-product arguments, files)",
+                 lambda d: [f_("z"), SB_, SB_, 1 - SLE_, SLE_, f_("expmap"), SLR_, f_("g256"), f_("q")],
+                 lambda d: [SB_, SB_, 1 - SLE_, SLE_, f_("expmap"), SLR_, f_("g256"), f_("q")]),
                 ("zkob_rope", "rotary embedding, 128 x 768, head width 64 (two commitments, two 17-round Hadamard sumchecks, three inner-product arguments, files)",
                  lambda d: [f_("T"), B_, OUT_, HD_, f_("cos"), f_("sin"), f_("go"), f_("q")],
                  lambda d: [B_, OUT_, HD_, f_("cos"), f_("sin"), f_("go"), f_("q")]),
