@@ -29,6 +29,8 @@ HEADMERGE_DRIVER = os.path.join(HERE, "zkob_headmerge")
 ROPE_DRIVER = os.path.join(HERE, "zkob_rope")
 SOFTMAX_DRIVER = os.path.join(HERE, "zkob_softmax")
 RMSNORM_DRIVER = os.path.join(HERE, "zkob_rmsnorm")
+SOFTMAX8_DRIVER = os.path.join(HERE, "zkob_softmax8")
+ROWMAX_DRIVER = os.path.join(HERE, "zkob_rowmax")
 INCLUDE = os.path.abspath(os.path.join(HERE, "..", "include"))
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -54,7 +56,8 @@ def build_selftest(force=False):
     for name, exe in (("p3_selftest.cpp", SELFTEST), ("p3_gadgets_selftest.cpp", GADGETS_SELFTEST), ("zkob_p3fc.cpp", DRIVER),
                       ("p3_layer_main.cpp", LAYER), ("zkob_fc.cpp", FC_DRIVER), ("zkob_rescale.cpp", RESCALE_DRIVER), ("zkob_batchopen.cpp", BATCH_DRIVER), ("zkob_skip.cpp", SKIP_DRIVER), ("zkob_glu.cpp", GLU_DRIVER), ("zkob_headslice.cpp", HEADSLICE_DRIVER),
                       ("zkob_headmerge.cpp", HEADMERGE_DRIVER), ("zkob_rope.cpp", ROPE_DRIVER), ("zkob_softmax.cpp", SOFTMAX_DRIVER),
-                      ("zkob_rmsnorm.cpp", RMSNORM_DRIVER)):
+                      ("zkob_rmsnorm.cpp", RMSNORM_DRIVER), ("zkob_softmax8.cpp", SOFTMAX8_DRIVER),
+                      ("zkob_rowmax.cpp", ROWMAX_DRIVER)):
         src = os.path.join(HERE, "host", name)
         deps = [src, os.path.join(INCLUDE, "zkh.h"), os.path.join(INCLUDE, "zkh_p3.hpp"), os.path.join(INCLUDE, "zkh_p3_verify.hpp"),
                 os.path.join(INCLUDE, "zkh_p3_layer.hpp"), os.path.join(HERE, "host", "zkob_common.hpp"), LIB]
