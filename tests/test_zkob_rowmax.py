@@ -145,7 +145,7 @@ def test_claim_mode_files_equal_the_reference_and_the_batch_accepts(tmp_path, ca
             d.mkdir()
         r = run(exe, "prove", ob, "rs:l0.rowmax.h00", zp, B, NCOL, mode, V, LEN_R, NPL, g, gmx, q, "-", *extra, "--claims", acc, "l0.rowmax.h00")
         assert r.returncode == 0 and "claim mode" in r.stdout, r.stdout + r.stderr
-        r = run(exe, "verify", ob, "rs:l0.rowmax.h00", B, NCOL, mode, V, LEN_R, NPL, g, gmx, q, *extra, "--claims", vacc, "l0.rowmax.h00")
+        r = run(EXE, "verify", ob, "rs:l0.rowmax.h00", B, NCOL, mode, V, LEN_R, NPL, g, gmx, q, *extra, "--claims", vacc, "l0.rowmax.h00")
         assert r.returncode == 0 and "ACCEPT-conditional" in r.stdout, r.stdout + r.stderr
         kept[tag] = {p.relative_to(tmp_path).as_posix(): p.read_bytes() for d in (ob, acc, vacc) for p in sorted(d.iterdir())}
         if tag == "ours":
