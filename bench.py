@@ -764,7 +764,24 @@ def run_suite_fr(args):
             open(f_("g256"), "wb").write(bytes(buf))
             open(f_("z"), "wb").write(rng.integers(1 - SLE_, 1, SB_ * SB_, dtype=np.int32).tobytes())
             open(f_("expmap"), "wb").write(np.maximum(1, np.rint(65536 * np.exp(np.arange(1 - SLE_, 1) * (8.0 / SLE_)))).astype(np.int32).tobytes())
+            import math
+            buf = (C.c_uint8 * (B_ * 144))()
+            refA.lib.refA_commit_random(C.c_uint32(B_), buf)
+            open(f_("g128"), "wb").write(bytes(buf))
+            Xn = rng.integers(-(1 << 15), 1 << 15, (B_, OUT_), dtype=np.int32)
+            ceps = round(1e-5 * (1 << 32)) * OUT_
+            Rn = []
+            for srow in range(B_):                                      # the exact inverse-RMS advice of every row, in Python integers
+                Mrow = int((Xn[srow].astype(np.int64) ** 2).sum()) + ceps
+                rr = math.isqrt((OUT_ << 64) // Mrow)
+                Rn.append(rr)
+            open(f_("Xn"), "wb").write(Xn.tobytes())
+            open(f_("Rn"), "wb").write(np.array(Rn, dtype=np.int32).tobytes())
+            open(f_("gn"), "wb").write(rng.integers(1 << 15, 1 << 17, OUT_, dtype=np.int32).tobytes())
             cases = (
+                ("zkob_rmsnorm", "RMS norm of 128 x 768 (12 commitments, a 16-round limb lookup, two 17-round Hadamard and two 7-round degree-4 sumchecks, 17 inner-product arguments, files)",
+                 lambda d: [f_("Xn"), f_("Rn"), f_("gn"), B_, OUT_, ceps, f_("go"), f_("g128"), f_("q")],
+                 lambda d: [B_, OUT_, ceps, os.path.join(d, "com_g.bin"), f_("go"), f_("g128"), f_("q")]),
                 ("zkob_softmax", "causal softmax of a 256 x 256 score grid (9 commitments, a 16-round and an 18-round lookup sumcheck, three 16-round Hadamard sumchecks, 16 inner-product arguments, files)",
                  lambda d: [f_("z"), SB_, SB_, 1 - SLE_, SLE_, f_("expmap"), SLR_, f_("g256"), f_("q")],
                  lambda d: [SB_, SB_, 1 - SLE_, SLE_, f_("expmap"), SLR_, f_("g256"), f_("q")]),
@@ -806,7 +823,7 @@ def run_suite_fr(args):
                     line.update({"reference_program_s": res["reference"], "speedup_vs_reference_program": res["reference"] / res["ours"],
                                  "files": len(os.listdir(d1)), "same_files": bool(same)})
                 t0 = time.perf_counter()
-                rc = subprocess.call([mine, "verify", os.path.join(td, prog + "_ours"), "bench-seed"] + [str(a) for a in vargs(None)], stdout=subprocess.DEVNULL)
+                rc = subprocess.call([mine, "verify", os.path.join(td, prog + "_ours"), "bench-seed"] + [str(a) for a in vargs(os.path.join(td, prog + "_ours"))], stdout=subprocess.DEVNULL)
                 line.update({"verify_s": time.perf_counter() - t0, "verify_accepts": rc == 0})
                 print(json.dumps(line), flush=True)
 
