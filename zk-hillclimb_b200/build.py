@@ -31,6 +31,7 @@ SOFTMAX_DRIVER = os.path.join(HERE, "zkob_softmax")
 RMSNORM_DRIVER = os.path.join(HERE, "zkob_rmsnorm")
 SOFTMAX8_DRIVER = os.path.join(HERE, "zkob_softmax8")
 ROWMAX_DRIVER = os.path.join(HERE, "zkob_rowmax")
+HOSTMATH = os.path.join(HERE, "zkob_hostmath")
 INCLUDE = os.path.abspath(os.path.join(HERE, "..", "include"))
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -57,7 +58,7 @@ def build_selftest(force=False):
                       ("p3_layer_main.cpp", LAYER), ("zkob_fc.cpp", FC_DRIVER), ("zkob_rescale.cpp", RESCALE_DRIVER), ("zkob_batchopen.cpp", BATCH_DRIVER), ("zkob_skip.cpp", SKIP_DRIVER), ("zkob_glu.cpp", GLU_DRIVER), ("zkob_headslice.cpp", HEADSLICE_DRIVER),
                       ("zkob_headmerge.cpp", HEADMERGE_DRIVER), ("zkob_rope.cpp", ROPE_DRIVER), ("zkob_softmax.cpp", SOFTMAX_DRIVER),
                       ("zkob_rmsnorm.cpp", RMSNORM_DRIVER), ("zkob_softmax8.cpp", SOFTMAX8_DRIVER),
-                      ("zkob_rowmax.cpp", ROWMAX_DRIVER)):
+                      ("zkob_rowmax.cpp", ROWMAX_DRIVER), ("zkob_hostmath.cpp", HOSTMATH)):
         src = os.path.join(HERE, "host", name)
         deps = [src, os.path.join(INCLUDE, "zkh.h"), os.path.join(INCLUDE, "zkh_p3.hpp"), os.path.join(INCLUDE, "zkh_p3_verify.hpp"),
                 os.path.join(INCLUDE, "zkh_p3_layer.hpp"), os.path.join(HERE, "host", "zkob_common.hpp"), LIB]

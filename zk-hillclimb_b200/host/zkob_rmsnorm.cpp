@@ -366,16 +366,6 @@ bool read_pf(const std::string& path, uint32_t want, int nterm, Pf& p) {
     for (const Fr& e : p.ev) if (!fr_lt(e, FR_MOD)) return false;
     return fr_lt(p.claim, FR_MOD);
 }
-// p(v) from p(0..4) (lagrange5, zkllm-src/zkob_lookup.cuh:356-375)
-Fr lagrange5(const std::array<Fr, 5>& p, const Fr& v, const Fr& inv24, const Fr& inv6, const Fr& inv4) {
-    const Fr m1 = fr_sub(v, fr_u32(1)), m2 = fr_sub(v, fr_u32(2)), m3 = fr_sub(v, fr_u32(3)), m4 = fr_sub(v, fr_u32(4)), zero = fr_u32(0);
-    auto mul4 = [](const Fr& a, const Fr& b, const Fr& c, const Fr& d) { return fr_mul(fr_mul(a, b), fr_mul(c, d)); };
-    const Fr l0 = fr_mul(mul4(m1, m2, m3, m4), inv24), l1 = fr_sub(zero, fr_mul(mul4(v, m2, m3, m4), inv6)), l2 = fr_mul(mul4(v, m1, m3, m4), inv4),
-             l3 = fr_sub(zero, fr_mul(mul4(v, m1, m2, m4), inv6)), l4 = fr_mul(mul4(v, m1, m2, m3), inv24);
-    Fr acc = fr_mul(p[0], l0);
-    acc = fr_add(acc, fr_mul(p[1], l1)); acc = fr_add(acc, fr_mul(p[2], l2)); acc = fr_add(acc, fr_mul(p[3], l3)); acc = fr_add(acc, fr_mul(p[4], l4));
-    return acc;
-}
 // sum_{i<5} 2^(16 i) com_L[first + i] compared with the one-row commitment `com` as group elements
 bool affine_link(Ctx& x, const std::vector<uint8_t>& comL, uint32_t first, const std::vector<uint8_t>& com) {
     std::vector<Fr> sc(8, fr_u32(0));
