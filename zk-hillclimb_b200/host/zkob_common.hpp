@@ -484,6 +484,46 @@ Fr lagrange5(const std::array<Fr, 5>& p, const Fr& v, const Fr& inv24, const Fr&
     return acc;
 }
 
+// ------------------------------------------------------------------ helpers shared by the structural drivers
+// the verifier's verdict line
+bool rj(const std::string& msg) { std::cout << "REJECT: " << msg << std::endl; return false; }
+// signed integers as field elements (the FrTensor integer constructors)
+std::vector<Fr> lift(const std::vector<int64_t>& v) {
+    std::vector<Fr> o(v.size());
+    for (size_t i = 0; i < v.size(); i++) o[i] = fr_from_i64(v[i]);
+    return o;
+}
+// a Hadamard proof file: claim, count, 4 evaluations per round, the two terminals (write_hp / read_hp, zkllm-src/zkob_lookup.cuh:262-289)
+void write_hp(const std::string& path, const Fr& claim, const std::vector<Fr>& hev, const Fr& S_f2, const Fr& U_f2) {
+    std::vector<uint8_t> f;
+    const uint32_t n = (uint32_t)hev.size();
+    put(f, claim.v, FRB); put(f, &n, 4); put(f, hev.data(), hev.size() * FRB); put(f, S_f2.v, FRB); put(f, U_f2.v, FRB);
+    write_file(path, f);
+}
+struct Hp { Fr claim, S_f2, U_f2; std::vector<Fr> ev; };
+// false on a wrong size, a wrong count or a non-canonical scalar
+bool read_hp(const std::string& path, uint32_t want, Hp& p) {
+    const std::vector<uint8_t> f = read_file(path);
+    if (f.size() != FRB + 4 + (size_t)want * FRB + 2 * FRB) return false;
+    uint32_t n;
+    memcpy(p.claim.v, &f[0], FRB);
+    memcpy(&n, &f[FRB], 4);
+    if (n != want) return false;
+    p.ev.resize(n);
+    memcpy(p.ev.data(), &f[FRB + 4], (size_t)n * FRB);
+    memcpy(p.S_f2.v, &f[FRB + 4 + (size_t)n * FRB], FRB);
+    memcpy(p.U_f2.v, &f[FRB + 4 + (size_t)(n + 1) * FRB], FRB);
+    for (const Fr& e : p.ev) if (!fr_lt(e, FR_MOD)) return false;
+    return fr_lt(p.claim, FR_MOD) && fr_lt(p.S_f2, FR_MOD) && fr_lt(p.U_f2, FR_MOD);
+}
+// a public weight tensor folded over the round challenges, in place (fold_public of the drivers)
+Fr fold_public(Ctx& x, Dev& w, uint64_t n, const std::vector<Fr>& ws) {
+    for (const Fr& c : ws) { x.ck(zkh_fr_fold(x.c, w.p, n / 2, c.v, w.p), "fold weights"); n /= 2; }
+    Fr out;
+    x.ck(zkh_download(x.c, out.v, w.p, FRB), "download");
+    return out;
+}
+
 // a flat tensor of rows x G scalars committed row-wise, opened at u_pt = (column bits, then row bits) (open_prove)
 void open_prove(Ctx& x, const Dev& t, uint32_t rows, uint32_t G, const Dev& gens, const uint8_t* Q, const std::vector<Fr>& u_pt, const std::string& path,
                 Transcript& tr) {

@@ -43,11 +43,6 @@ std::vector<int32_t> load_mapped(const std::string& path, const Lay& y) {
 }
 // table + r * mapped on the device (T_comb); the same shape serves comb = G + r S
 void combine(Ctx& x, Dev& acc, const Dev& add, const Fr& r, uint64_t n) { x.ck(zkh_fr_axpy(x.c, acc.p, add.p, r.v, n), "combination"); }
-std::vector<Fr> lift(const std::vector<int64_t>& v) {
-    std::vector<Fr> o(v.size());
-    for (size_t i = 0; i < v.size(); i++) o[i] = fr_from_i64(v[i]);
-    return o;
-}
 void absorb_head(Transcript& tr, const Lay& y) {
     tr.absorb_u32("B", y.B); tr.absorb_u32("C", y.C); tr.absorb_u32("LOW", (uint32_t)y.low); tr.absorb_u32("LEN", y.len);
 }

@@ -184,24 +184,6 @@ int do_prove(int argc, char** argv) {
     return 0;
 }
 
-bool rj(const std::string& msg) { std::cout << "REJECT: " << msg << std::endl; return false; }
-
-struct Hp { Fr claim, S_f2, U_f2; std::vector<Fr> ev; };
-bool read_hp(const std::string& path, uint32_t want, Hp& p) {
-    const std::vector<uint8_t> f = read_file(path);
-    if (f.size() != FRB + 4 + (size_t)want * FRB + 2 * FRB) return false;
-    uint32_t n;
-    memcpy(p.claim.v, &f[0], FRB);
-    memcpy(&n, &f[FRB], 4);
-    if (n != want) return false;
-    p.ev.resize(n);
-    memcpy(p.ev.data(), &f[FRB + 4], (size_t)n * FRB);
-    memcpy(p.S_f2.v, &f[FRB + 4 + (size_t)n * FRB], FRB);
-    memcpy(p.U_f2.v, &f[FRB + 4 + (size_t)(n + 1) * FRB], FRB);
-    for (const Fr& e : p.ev) if (!fr_lt(e, FR_MOD)) return false;
-    return fr_lt(p.claim, FR_MOD) && fr_lt(p.S_f2, FR_MOD) && fr_lt(p.U_f2, FR_MOD);
-}
-
 bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay& y, const std::vector<uint8_t>& gb, const std::vector<uint8_t>& gs,
             const std::vector<uint8_t>& q, const ClaimFlags& cf) {
     if (!layout_error(y, gb.size(), gs.size()).empty()) return rj("bad layout params");

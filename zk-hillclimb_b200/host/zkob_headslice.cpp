@@ -179,8 +179,6 @@ int do_prove(int argc, char** argv) {
     return 0;
 }
 
-bool rj(const std::string& msg) { std::cout << "REJECT: " << msg << std::endl; return false; }
-
 bool verify(const std::string& obdir, const std::string& seed, const Lay& y, const std::vector<uint8_t>& gb, const std::vector<uint8_t>& gs,
             const std::vector<uint8_t>& q, const ClaimFlags& cf) {
     if (!layout_error(y, gb.size(), gs.size()).empty()) return rj("bad layout params");

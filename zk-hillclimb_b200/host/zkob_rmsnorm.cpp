@@ -55,15 +55,10 @@ Fr fr_from_u128(u128 v) {
     return r;
 }
 Fr fr_from_u64(uint64_t v) { return fr_from_u128(v); }
-std::vector<Fr> lift(const std::vector<int64_t>& v) {
-    std::vector<Fr> o(v.size());
-    for (size_t i = 0; i < v.size(); i++) o[i] = fr_from_i64(v[i]);
-    return o;
-}
 void absorb_head(Transcript& tr, const Lay& y) {
     tr.absorb_u32("B", y.B); tr.absorb_u32("C", y.C); tr.absorb_u32("C_eps_lo", (uint32_t)y.C_eps); tr.absorb_u32("C_eps_hi", (uint32_t)(y.C_eps >> 32));
 }
-void write_hp(const std::string& path, const Fr& claim, const std::vector<Fr>& hev, const Fr& a, const Fr& b, const Fr* c = nullptr) {
+void write_pf(const std::string& path, const Fr& claim, const std::vector<Fr>& hev, const Fr& a, const Fr& b, const Fr* c = nullptr) {
     std::vector<uint8_t> f;
     const uint32_t n = (uint32_t)hev.size();
     put(f, claim.v, FRB); put(f, &n, 4); put(f, hev.data(), hev.size() * FRB); put(f, a.v, FRB); put(f, b.v, FRB);
@@ -245,7 +240,7 @@ int do_prove(int argc, char** argv) {
         bcast_eq(x, u_b, y, dE);
         const Sum s = sumcheck(x, tr, ev_M, {dE.p, dX.p, dX.p}, y.logD, nullptr);
         tr.absorb_fr("S_f2", s.fin[1]); tr.absorb_fr("U_f2", s.fin[2]);
-        write_hp(obdir + "/hpss.bin", ev_M, s.ev, s.fin[1], s.fin[2]);
+        write_pf(obdir + "/hpss.bin", ev_M, s.ev, s.fin[1], s.fin[2]);
         const std::vector<Fr> u_ss(s.ws.rbegin(), s.ws.rend());
         if (cf.on()) {
             claim("X_ss", obdir + "/com_X.bin", Cp, B, u_ss, s.fin[1]);
@@ -270,8 +265,8 @@ int do_prove(int argc, char** argv) {
         const Sum q2 = sumcheck(x, tr, ev_P2, {dE2.p, dT2.p, dT2.p, dM.p}, y.logB, "q2");
         tr.absorb_fr("q1A_f", q1.fin[1]); tr.absorb_fr("q1B_f", q1.fin[2]); tr.absorb_fr("q1C_f", q1.fin[3]);
         tr.absorb_fr("q2A_f", q2.fin[1]); tr.absorb_fr("q2B_f", q2.fin[2]); tr.absorb_fr("q2C_f", q2.fin[3]);
-        write_hp(obdir + "/qp1.bin", ev_P1, q1.ev, q1.fin[1], q1.fin[2], &q1.fin[3]);
-        write_hp(obdir + "/qp2.bin", ev_P2, q2.ev, q2.fin[1], q2.fin[2], &q2.fin[3]);
+        write_pf(obdir + "/qp1.bin", ev_P1, q1.ev, q1.fin[1], q1.fin[2], &q1.fin[3]);
+        write_pf(obdir + "/qp2.bin", ev_P2, q2.ev, q2.fin[1], q2.fin[2], &q2.fin[3]);
         const std::vector<Fr> pt1(q1.ws.rbegin(), q1.ws.rend()), pt2(q2.ws.rbegin(), q2.ws.rend());
         const Fr one = fr_u32(1), R1 = fr_add(q1.fin[1], one), R2 = fr_sub(q2.fin[1], one);
         if (cf.on()) {
@@ -327,7 +322,7 @@ int do_prove(int argc, char** argv) {
     x.ck(zkh_fr_eq_build(x.c, u_h.data(), y.logD, dEh.p), "eq table");
     const Sum h = sumcheck(x, tr, claim_Y, {dEh.p, dWr.p, dX.p}, y.logD, nullptr);
     tr.absorb_fr("S_f2h", h.fin[1]); tr.absorb_fr("U_f2h", h.fin[2]);
-    write_hp(obdir + "/hp.bin", claim_Y, h.ev, h.fin[1], h.fin[2]);
+    write_pf(obdir + "/hp.bin", claim_Y, h.ev, h.fin[1], h.fin[2]);
     const std::vector<Fr> u_pth(h.ws.rbegin(), h.ws.rend());
     if (cf.on()) {
         claim("Y", obdir + "/com_Y.bin", Cp, B, u_h, claim_Y);
@@ -345,8 +340,6 @@ int do_prove(int argc, char** argv) {
     std::cout << "PROVED rmsnorm obligation -> " << obdir << std::endl;
     return 0;
 }
-
-bool rj(const std::string& msg) { std::cout << "REJECT: " << msg << std::endl; return false; }
 
 // claim, count, evaluations, then `nterm` terminals (read_hp / read_qp); false on a wrong size, count or a non-canonical scalar
 struct Pf { Fr claim, fin[3]; std::vector<Fr> ev; };

@@ -59,19 +59,8 @@ void build_weights(std::vector<int64_t>& W1, std::vector<int64_t>& W2, const std
             W2[g] = ((e & flipv) ? 1 : -1) * (int64_t)sinT[(size_t)t * y.HD + (e % y.HD)];
         }
 }
-std::vector<Fr> lift(const std::vector<int64_t>& v) {
-    std::vector<Fr> o(v.size());
-    for (size_t i = 0; i < v.size(); i++) o[i] = fr_from_i64(v[i]);
-    return o;
-}
 void absorb_head(Transcript& tr, const Lay& y) {
     tr.absorb_u32("B", y.B); tr.absorb_u32("C", y.C); tr.absorb_u32("HD", y.HD); tr.absorb_u32("SCALE_R", SCALE_R);
-}
-void write_hp(const std::string& path, const Fr& claim, const std::vector<Fr>& hev, const Fr& S_f2, const Fr& U_f2) {
-    std::vector<uint8_t> f;
-    const uint32_t n = (uint32_t)hev.size();
-    put(f, claim.v, FRB); put(f, &n, 4); put(f, hev.data(), hev.size() * FRB); put(f, S_f2.v, FRB); put(f, U_f2.v, FRB);
-    write_file(path, f);
 }
 
 struct Had { Fr claim, S_f2, U_f2; std::vector<Fr> ws; };
@@ -190,24 +179,6 @@ int do_prove(int argc, char** argv) {
     open_prove(x, dY, B, Cp, gd, q.data(), u, obdir + "/ipa_Y.bin", tr);
     std::cout << "PROVED rope obligation -> " << obdir << std::endl;
     return 0;
-}
-
-bool rj(const std::string& msg) { std::cout << "REJECT: " << msg << std::endl; return false; }
-
-struct Hp { Fr claim, S_f2, U_f2; std::vector<Fr> ev; };
-bool read_hp(const std::string& path, uint32_t want, Hp& p) {
-    const std::vector<uint8_t> f = read_file(path);
-    if (f.size() != FRB + 4 + (size_t)want * FRB + 2 * FRB) return false;
-    uint32_t n;
-    memcpy(p.claim.v, &f[0], FRB);
-    memcpy(&n, &f[FRB], 4);
-    if (n != want) return false;
-    p.ev.resize(n);
-    memcpy(p.ev.data(), &f[FRB + 4], (size_t)n * FRB);
-    memcpy(p.S_f2.v, &f[FRB + 4 + (size_t)n * FRB], FRB);
-    memcpy(p.U_f2.v, &f[FRB + 4 + (size_t)(n + 1) * FRB], FRB);
-    for (const Fr& e : p.ev) if (!fr_lt(e, FR_MOD)) return false;
-    return fr_lt(p.claim, FR_MOD) && fr_lt(p.S_f2, FR_MOD) && fr_lt(p.U_f2, FR_MOD);
 }
 
 // one Hadamard leg of the verifier: round checks, U_f2 == 1, the verifier's own folded weights; the round challenges in ws

@@ -69,21 +69,10 @@ std::string tstar_error(const Lay& y, const std::vector<int32_t>* t) {
     return "";
 }
 bool allowed(const Lay& y, uint32_t i, uint32_t j) { return y.MODE == 0 ? j <= i : j < y.V; }
-std::vector<Fr> lift(const std::vector<int64_t>& v) {
-    std::vector<Fr> o(v.size());
-    for (size_t i = 0; i < v.size(); i++) o[i] = fr_from_i64(v[i]);
-    return o;
-}
 void absorb_head(Transcript& tr, const Lay& y, const std::vector<int32_t>* tstar) {
     tr.absorb_u32("B", y.B); tr.absorb_u32("NCOL", y.NCOL); tr.absorb_u32("MODE", y.MODE); tr.absorb_u32("V", y.V);
     tr.absorb_u32("LEN_R", y.LEN_R); tr.absorb_u32("NPL", y.NPL);
     if (y.MODE == 1 && tstar) tr.absorb("TSTAR", tstar->data(), (size_t)y.B * 4);
-}
-void write_hp(const std::string& path, const Fr& claim, const std::vector<Fr>& hev, const Fr& S_f2, const Fr& U_f2) {
-    std::vector<uint8_t> f;
-    const uint32_t n = (uint32_t)hev.size();
-    put(f, claim.v, FRB); put(f, &n, 4); put(f, hev.data(), hev.size() * FRB); put(f, S_f2.v, FRB); put(f, U_f2.v, FRB);
-    write_file(path, f);
 }
 // bcast_rows(eq(u)) restricted to the allowed set (sel = 1), to its complement (sel = 0), or unrestricted (sel = 2)
 void row_weights(Ctx& x, const std::vector<Fr>& u, const Lay& y, int sel, Dev& out) {
@@ -362,23 +351,6 @@ int do_prove(int argc, char** argv) {
     return 0;
 }
 
-bool rj(const std::string& msg) { std::cout << "REJECT: " << msg << std::endl; return false; }
-
-struct Hp { Fr claim, S_f2, U_f2; std::vector<Fr> ev; };
-bool read_hp(const std::string& path, uint32_t want, Hp& p) {
-    const std::vector<uint8_t> f = read_file(path);
-    if (f.size() != FRB + 4 + (size_t)want * FRB + 2 * FRB) return false;
-    uint32_t n;
-    memcpy(p.claim.v, &f[0], FRB);
-    memcpy(&n, &f[FRB], 4);
-    if (n != want) return false;
-    p.ev.resize(n);
-    memcpy(p.ev.data(), &f[FRB + 4], (size_t)n * FRB);
-    memcpy(p.S_f2.v, &f[FRB + 4 + (size_t)n * FRB], FRB);
-    memcpy(p.U_f2.v, &f[FRB + 4 + (size_t)(n + 1) * FRB], FRB);
-    for (const Fr& e : p.ev) if (!fr_lt(e, FR_MOD)) return false;
-    return fr_lt(p.claim, FR_MOD) && fr_lt(p.S_f2, FR_MOD) && fr_lt(p.U_f2, FR_MOD);
-}
 // the round checks of one Hadamard sumcheck from the claim `cur`; ws the challenges; eq_acc the product of eq(u[nu - 1 - k], w_k) over
 // the first nu rounds when u is given
 bool hadamard_rounds(Transcript& tr, const Hp& hp, uint32_t logn, const char* tag, const Fr& inv2, const Fr& inv6, std::vector<Fr>& ws, Fr& cur,
@@ -393,12 +365,6 @@ bool hadamard_rounds(Transcript& tr, const Hp& hp, uint32_t logn, const char* ta
         if (u && k < u->size()) *eq_acc = fr_mul(*eq_acc, eq1((*u)[u->size() - 1 - k], w));
     }
     return true;
-}
-Fr fold_public(Ctx& x, Dev& w, uint64_t n, const std::vector<Fr>& ws) {
-    for (const Fr& c : ws) { x.ck(zkh_fr_fold(x.c, w.p, n / 2, c.v, w.p), "fold weights"); n /= 2; }
-    Fr out;
-    x.ck(zkh_download(x.c, out.v, w.p, FRB), "download");
-    return out;
 }
 
 bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay& y, const std::vector<uint8_t>& gen, const std::vector<uint8_t>& genmx,

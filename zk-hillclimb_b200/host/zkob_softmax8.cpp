@@ -58,20 +58,9 @@ std::vector<int32_t> load_expmap(const std::string& path, uint32_t len) {
     memcpy(v.data(), raw.data(), (size_t)len * 4);
     return v;
 }
-std::vector<Fr> lift(const std::vector<int64_t>& v) {
-    std::vector<Fr> o(v.size());
-    for (size_t i = 0; i < v.size(); i++) o[i] = fr_from_i64(v[i]);
-    return o;
-}
 void absorb_head(Transcript& tr, const Lay& y) {
     tr.absorb_u32("B", y.B); tr.absorb_u32("NCOL", y.NCOL); tr.absorb_u32("LOW8", (uint32_t)y.LOW_E); tr.absorb_u32("LEN8", y.LEN_E);
     tr.absorb_u32("LEN_R8", y.LEN_R); tr.absorb_u32("LOG_OUT", LOG_OUT); tr.absorb_u32("SENT", (uint32_t)(int32_t)((int64_t)y.LOW_E + y.LEN_E - 1));
-}
-void write_hp(const std::string& path, const Fr& claim, const std::vector<Fr>& hev, const Fr& S_f2, const Fr& U_f2) {
-    std::vector<uint8_t> f;
-    const uint32_t n = (uint32_t)hev.size();
-    put(f, claim.v, FRB); put(f, &n, 4); put(f, hev.data(), hev.size() * FRB); put(f, S_f2.v, FRB); put(f, U_f2.v, FRB);
-    write_file(path, f);
 }
 void write_lookup(const std::string& path, const std::vector<Fr>& ev, const Fr* term) {
     std::vector<uint8_t> f;
@@ -423,23 +412,6 @@ int do_prove(int argc, char** argv) {
     return 0;
 }
 
-bool rj(const std::string& msg) { std::cout << "REJECT: " << msg << std::endl; return false; }
-
-struct Hp { Fr claim, S_f2, U_f2; std::vector<Fr> ev; };
-bool read_hp(const std::string& path, uint32_t want, Hp& p) {
-    const std::vector<uint8_t> f = read_file(path);
-    if (f.size() != FRB + 4 + (size_t)want * FRB + 2 * FRB) return false;
-    uint32_t n;
-    memcpy(p.claim.v, &f[0], FRB);
-    memcpy(&n, &f[FRB], 4);
-    if (n != want) return false;
-    p.ev.resize(n);
-    memcpy(p.ev.data(), &f[FRB + 4], (size_t)n * FRB);
-    memcpy(p.S_f2.v, &f[FRB + 4 + (size_t)n * FRB], FRB);
-    memcpy(p.U_f2.v, &f[FRB + 4 + (size_t)(n + 1) * FRB], FRB);
-    for (const Fr& e : p.ev) if (!fr_lt(e, FR_MOD)) return false;
-    return fr_lt(p.claim, FR_MOD) && fr_lt(p.S_f2, FR_MOD) && fr_lt(p.U_f2, FR_MOD);
-}
 struct Lk { Fr A_f, S_f, m_f; std::vector<Fr> ev; };
 bool read_lookup(const std::string& path, uint32_t want, Lk& p) {
     const std::vector<uint8_t> f = read_file(path);
@@ -471,13 +443,6 @@ bool hadamard_rounds(Transcript& tr, const Hp& hp, uint32_t logn, const char* ta
         if (u) *eq_acc = fr_mul(*eq_acc, eq1((*u)[logn - 1 - k], w));
     }
     return true;
-}
-// a public weight tensor folded over the round challenges, in place (fold_public)
-Fr fold_public(Ctx& x, Dev& w, uint64_t n, const std::vector<Fr>& ws) {
-    for (const Fr& c : ws) { x.ck(zkh_fr_fold(x.c, w.p, n / 2, c.v, w.p), "fold weights"); n /= 2; }
-    Fr out;
-    x.ck(zkh_download(x.c, out.v, w.p, FRB), "download");
-    return out;
 }
 
 bool verify(Ctx& x, const std::string& obdir, const std::string& seed, const Lay& y, const std::vector<int32_t>& maph, const std::vector<uint8_t>& gen,
