@@ -82,3 +82,121 @@ def test_batch_verifier_refuses_malformed_accumulators_before_any_device_work(tm
     (v / "claims.bin").write_bytes(_claims(good)[:-1] + b"\x01" + b"\x00")       # trailing byte
     r = subprocess.run([bo, "verify", p, v, "seed", q, "4=%s" % gen], capture_output=True, text=True, timeout=60)
     assert r.returncode not in (0, 1) and "trailing" in r.stderr
+
+
+def _batch_sumcheck_oracle(run_seed, items, wits, comfiles):
+    """The sumcheck half of the batch opening in Python integers (zkllm-src/zkob_claims.cuh:832-960: the first absorbs, the powers of
+    rho, M_j = sum_i rho^i eq(point_i), the rounds from the top variable down with the smaller tensors carried by (1 - x)^2 factors,
+    the terminal values): the round evaluations and the terminals a prover writes to batch_sumcheck.bin and batch_vfin.bin."""
+    import hashlib
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import fr_oracle as fo
+    P = fo.P
+    tensors, key = [], {}
+    for i, (cid, comref, domain, n_rows, point, ev) in enumerate(items):
+        k = str(comref)
+        if k not in key:
+            key[k] = len(tensors)
+            tensors.append({"comref": k, "vars": len(point), "idx": []})
+        tensors[key[k]]["idx"].append(i)
+    tr = fo.Transcript(run_seed + ":opening_batch")
+    tr.absorb("n_claims", len(items).to_bytes(4, "little"))
+    for it in items:
+        tr.absorb("claim", _claims([it])[12:])                       # the claim's record without the file header
+    for t in tensors:
+        tr.absorb("comref", len(t["comref"]).to_bytes(4, "little") + t["comref"].encode() + hashlib.sha256(comfiles[t["comref"]]).digest())
+    rho = tr.challenge_fr()
+    rp = [pow(rho, i, P) for i in range(len(items))]
+    m_max = max(t["vars"] for t in tensors)
+    M, Pw, S, c2 = [], [], [], []
+    for t in tensors:
+        n = 1 << t["vars"]
+        m = [0] * n
+        for i in t["idx"]:
+            e = fo.eq_build(items[i][4])
+            m = [(a + rp[i] * b) % P for a, b in zip(m, e)]
+        M.append(m)
+        Pw.append(list(wits[t["comref"]]))
+        S.append(sum(a * b for a, b in zip(m, Pw[-1])) % P)
+        c2.append(1)
+    cur = sum(rp[i] * items[i][5] for i in range(len(items))) % P
+    evs, r = [], [0] * m_max
+    for rnd in range(m_max):
+        v = m_max - 1 - rnd
+        p = [0, 0, 0]
+        for j, t in enumerate(tensors):
+            if t["vars"] <= v:
+                p[0] = (p[0] + c2[j] * S[j]) % P
+                p[2] = (p[2] + c2[j] * S[j]) % P
+            else:
+                h = len(M[j]) // 2
+                for T in range(3):
+                    p[T] = (p[T] + c2[j] * sum((M[j][i] + T * (M[j][i + h] - M[j][i])) * (Pw[j][i] + T * (Pw[j][i + h] - Pw[j][i])) for i in range(h))) % P
+        assert cur == (p[0] + p[1]) % P
+        for lab, val in zip(("bp0", "bp1", "bp2"), p):
+            tr.absorb_fr(lab, val)
+        x = tr.challenge_fr()
+        r[v] = x
+        evs += p
+        cur = fo.lagrange(p, x)
+        for j, t in enumerate(tensors):
+            if t["vars"] <= v:
+                c2[j] = c2[j] * (1 - x) * (1 - x) % P
+            else:
+                h = len(M[j]) // 2
+                M[j] = [(M[j][i] + x * (M[j][i + h] - M[j][i])) % P for i in range(h)]
+                Pw[j] = [(Pw[j][i] + x * (Pw[j][i + h] - Pw[j][i])) % P for i in range(h)]
+    return evs, [pw[0] for pw in Pw], m_max, len(tensors)
+
+
+def test_batch_verifier_replays_a_python_provers_sumcheck(tmp_path):
+    """Two tensors of different sizes, three claims (two on one tensor): the round evaluations and terminals of a Python-integer
+    prover pass every host-side check of the batch verifier (which then stops only at the group arithmetic, where it needs the GPU or
+    the missing argument file); changed rounds, terminals and evaluations are refused at the reference's loci."""
+    import random
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import fr_oracle as fo
+    P = fo.P
+    rng = random.Random(21)
+    bo = os.path.join(PKG, "zkob_batchopen")
+    p, v = tmp_path / "p", tmp_path / "v"
+    p.mkdir()
+    v.mkdir()
+    gen, q = tmp_path / "g4", tmp_path / "q"
+    gen.write_bytes(bytes(4 * 144))
+    q.write_bytes(bytes(144))
+    comA, comB = tmp_path / "comA.bin", tmp_path / "comB.bin"
+    comA.write_bytes(bytes(range(144)) * 4)                          # 4 rows of 4: 4 variables
+    comB.write_bytes(bytes(range(1, 145)))                           # 1 row of 4: 2 variables
+    wA, wB = [rng.randrange(P) for _ in range(16)], [rng.randrange(P) for _ in range(4)]
+    pts = [[rng.randrange(P) for _ in range(4)], [rng.randrange(P) for _ in range(2)], [rng.randrange(P) for _ in range(4)]]
+    items = [("a:T", comA, 4, 4, pts[0], fo.mle_eval(wA, pts[0])), ("b:S", comB, 4, 1, pts[1], fo.mle_eval(wB, pts[1])),
+             ("c:T2", comA, 4, 4, pts[2], fo.mle_eval(wA, pts[2]))]
+    wits = {str(comA): wA, str(comB): wB}
+    comfiles = {str(comA): comA.read_bytes(), str(comB): comB.read_bytes()}
+    evs, vfin, m_max, nT = _batch_sumcheck_oracle("seed", items, wits, comfiles)
+
+    def verdict(evs_, vfin_, items_=items):
+        (v / "claims.bin").write_bytes(_claims(items_))
+        (p / "claims.bin").write_bytes(_claims(items_))
+        (p / "batch_sumcheck.bin").write_bytes(b"ZKBS" + len(items_).to_bytes(4, "little") + m_max.to_bytes(4, "little") + len(evs_).to_bytes(4, "little")
+                                               + b"".join(e.to_bytes(32, "little") for e in evs_))
+        (p / "batch_vfin.bin").write_bytes(b"ZKBV" + nT.to_bytes(4, "little") + b"".join(e.to_bytes(32, "little") for e in vfin_))
+        return subprocess.run([bo, "verify", p, v, "seed", q, "4=%s" % gen], capture_output=True, text=True, timeout=120)
+
+    r = verdict(evs, vfin)
+    host_rejects = ("claims_match", "shape", "xcheck", "round", "vfin_count", "terminal")
+    assert not any("REJECT[opening_batch." + k in r.stdout for k in host_rejects), r.stdout
+    assert r.returncode != 0                                         # no argument file (and on this machine no GPU): never an ACCEPT
+    assert "no CUDA device" in r.stderr or "REJECT[opening_batch.group_missing]" in r.stdout, r.stdout + r.stderr
+    bad = list(evs)
+    bad[4] = (bad[4] + 1) % P
+    assert "REJECT[opening_batch.round1]" in verdict(bad, vfin).stdout
+    bad = list(evs)
+    bad[2] = (bad[2] + 1) % P                                        # p(2) of round 0 moves the next running claim
+    assert "REJECT[opening_batch.round1]" in verdict(bad, vfin).stdout
+    assert "REJECT[opening_batch.terminal]" in verdict(evs, [vfin[0], (vfin[1] + 1) % P]).stdout
+    wrong = [items[0], (items[1][0], items[1][1], 4, 1, pts[1], (items[1][5] + 1) % P), items[2]]
+    assert "REJECT[opening_batch.round0]" in verdict(evs, vfin, wrong).stdout
