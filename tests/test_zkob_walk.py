@@ -229,3 +229,62 @@ def test_an_attention_block_and_a_gate_through_all_twelve_programs(tmp_path):
     (vacc / "claims.bin").write_bytes((acc / "claims.bin").read_bytes()[:-1] + b"\x01")
     r = subprocess.run([os.path.join(PKG, "zkob_batchopen"), "verify", acc, vacc, "w", q, "16=%s" % g16, "8=%s" % g8], capture_output=True, text=True, timeout=600)
     assert r.returncode == 1 and "REJECT" in r.stdout
+
+
+def test_every_chain_file_without_a_gpu(tmp_path):
+    """Every program writes its chain file (the integer tensor the next program reads) before it touches the device: each program of
+    the walk is started on the numpy chain's inputs and its chain file compared with the numpy statement.  Without a GPU the run then
+    stops at the device context; with one it goes on to prove."""
+    d = tmp_path
+    t = chain(3)
+    for name, k in (("g16", 16), ("g8", 8), ("q", 1)):
+        (d / name).write_bytes(bytes(k * 144))                       # sizes only: the layout rules are checked, the points are not read
+    g16, g8, q = d / "g16", d / "g8", d / "q"
+
+    def put(name, a, dtype):
+        (d / name).write_bytes(np.asarray(a).astype(dtype).tobytes())
+        return d / name
+
+    def start(prog, *args):
+        (d / "ob").mkdir(exist_ok=True)
+        r = subprocess.run([os.path.join(PKG, prog), "prove", d / "ob", "s"] + [str(a) for a in args], capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0 or "no CUDA device" in r.stderr, (prog, r.stdout[-300:], r.stderr[-300:])
+
+    def same(path, want, dtype):
+        assert np.array_equal(np.frombuffer((d / path).read_bytes(), dtype=dtype), np.asarray(want).astype(dtype).ravel()), path
+
+    start("zkob_rmsnorm", put("X", t["X"], np.int32), put("R", t["R"], np.int32), put("gain", t["gain"], np.int32), B, CC, t["c_eps"], g16, g8, q, d / "W.i64", d / "Y.i64")
+    same("Y.i64", t["normY"], np.int64)
+    same("W.i64", t["R"].astype(np.int64)[:, None] * t["gain"].astype(np.int64)[None, :], np.int64)
+    start("zkob_rescale", put("normY", t["normY"], np.int64), B, CC, 7, g16, q, d / "n1.i32")
+    same("n1.i32", t["n1"], np.int32)
+    start("zkob_fc", put("Xn", t["Xn"], np.int32), put("Wq", t["Wq"], np.int32), B, CC, CC, g16, g16, q, d / "Yq.i64")
+    same("Yq.i64", t["Yq"], np.int64)
+    start("zkob_rope", put("q0", t["q0"], np.int32), B, CC, HD, put("cos", t["cos"], np.int32), put("sin", t["sin"], np.int32), g16, q, d / "rope.i64")
+    same("rope.i64", t["ropeq"], np.int64)
+    (d / "sl").mkdir()
+    start("zkob_headslice", put("qr", t["qr"], np.int32), put("kr", t["kr"], np.int32), put("v0", t["v0"], np.int32), B, CC, HD, g16, g8, q, d / "sl")
+    for h in range(NH):
+        sl = slice(h * HD, (h + 1) * HD)
+        same("sl/Qh%02d.i32.bin" % h, t["qr"][:, sl], np.int32)
+        same("sl/KhT%02d.i32.bin" % h, t["kr"][:, sl].T, np.int32)
+        same("sl/Vh%02d.i32.bin" % h, t["v0"][:, sl], np.int32)
+    start("zkob_rowmax", put("z0", t["z0"], np.int32), B, B, "causal", 0, 64, 1, g8, g8, q, d / "mx.i32")
+    same("mx.i32", t["mx0"], np.int32)
+    start("zkob_softmax8", d / "z0", put("mx0", t["mx0"], np.int32), B, B, -62, 64, put("map8", t["map8"], np.int32), 256, g8, q, d / "P0.i32")
+    same("P0.i32", t["P0"], np.int32)
+    start("zkob_softmax", put("z1", t["z1"], np.int32), B, B, -32, 64, put("map", t["map"], np.int32), 256, g8, q, d / "P1.i32")
+    same("P1.i32", t["P1"], np.int32)
+    for h in range(NH):
+        put("out%02d.i32.bin" % h, t["o%d" % h], np.int32)
+    start("zkob_headmerge", d / "out", B, CC, HD, "concat", g16, g8, q, d / "O2.i32")
+    same("O2.i32", t["O2"], np.int32)
+    start("zkob_headmerge", d / "out", B, CC, HD, "pi157", g16, g8, q, d / "O2p.i32")
+    m = np.arange(B * CC)
+    same("O2p.i32", t["O2"][m % B, m // B], np.int32)
+    start("zkob_glu", put("attn", t["attn"], np.int32), d / "Xn", B, CC, -64, 128, put("mapg", t["mapg"], np.int32), g16, q, d / "H.i64")
+    same("H.i64", t["H"], np.int64)
+    # a vocabulary-padded row maximum: 11 real columns of 16, two limb planes
+    zv = np.random.default_rng(4).integers(-500, 500, (B, 11)).astype(np.int32)
+    start("zkob_rowmax", put("zv", zv, np.int32), B, 16, "vpad", 11, 32, 2, g16, g8, q, d / "mxv.i32")
+    same("mxv.i32", zv.max(axis=1), np.int32)
