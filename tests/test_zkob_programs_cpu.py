@@ -200,3 +200,52 @@ def test_batch_verifier_replays_a_python_provers_sumcheck(tmp_path):
     assert "REJECT[opening_batch.terminal]" in verdict(evs, [vfin[0], (vfin[1] + 1) % P]).stdout
     wrong = [items[0], (items[1][0], items[1][1], 4, 1, pts[1], (items[1][5] + 1) % P), items[2]]
     assert "REJECT[opening_batch.round0]" in verdict(evs, vfin, wrong).stdout
+
+
+def test_honest_prover_guards_stop_before_the_device(tmp_path):
+    """The range and layout guards of the provers (the reference's honest-prover throws) fire on the host: exit code 3 with the
+    reference's message, no device needed."""
+    import numpy as np
+    t = tmp_path
+
+    def f(name, a, dtype=np.int32):
+        (t / name).write_bytes(np.asarray(a).astype(dtype).tobytes())
+        return t / name
+
+    for name, k in (("g16", 16), ("g8", 8), ("q", 1)):
+        (t / name).write_bytes(bytes(k * 144))
+    g16, g8, q = t / "g16", t / "g8", t / "q"
+
+    def stopped(prog, message, *args):
+        r = subprocess.run([os.path.join(PKG, prog), "prove", t, "s"] + [str(a) for a in args], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 3 and message in r.stderr, (prog, message, r.returncode, r.stderr[-300:])
+
+    z = np.zeros((8, 8), dtype=np.int32)
+    z[5, 2] = -40                                                    # row maximum 0, difference 40
+    stopped("zkob_rowmax", "allowed Df >= LEN_R^NPL", f("z", z), 8, 8, "causal", 0, 32, 1, g8, g8, q)
+    stopped("zkob_rowmax", "vpad |z| >= 2^25", f("zb", np.full((8, 5), 1 << 25)), 8, 8, "vpad", 5, 32, 1, g8, g8, q)
+    emap8 = np.ones(16, dtype=np.int32)
+    emap8[-1] = 0
+    z2 = np.zeros((8, 8), dtype=np.int32)
+    z2[3, 1] = -20                                                   # below LOW8 = -14
+    stopped("zkob_softmax8", "allowed diff below LOW8", f("z2", z2), f("mx", np.zeros(8)), 8, 8, -14, 16, f("m8", emap8), 32, g8, q)
+    z3 = np.zeros((8, 8), dtype=np.int32)
+    z3[0, 0] = 1 << 19
+    stopped("zkob_softmax8", "z_ outside the +-2^19 envelope", f("z3", z3), t / "mx", 8, 8, -14, 16, t / "m8", 32, g8, q)
+    stopped("zkob_softmax", "bracket residual >= LEN_R^2", f("z0", np.zeros((8, 8))), 8, 8, -8, 16, f("mbig", np.full(16, 1 << 20)), 32, g8, q)
+    stopped("zkob_softmax", "S[i] < 1", t / "z0", 8, 8, -8, 16, f("mzero", np.zeros(16)), 32, g8, q)
+    big = np.full((8, 16), (1 << 31) - 1, dtype=np.int32)
+    stopped("zkob_rope", "|Y64| >= 2^47", f("T", big), 8, 16, 8, f("cos", np.full((8, 8), 1 << 16)), f("sin", np.full((8, 8), 1 << 16)), g16, q)
+    stopped("zkob_rope", "NH = C/HD must be >= 2", t / "T", 8, 16, 16, f("cos16", np.zeros((8, 16))), t / "cos16", g16, q)
+    G = np.zeros((8, 16), dtype=np.int32)
+    G[2, 3] = 64                                                     # the table covers [-64, 64)
+    stopped("zkob_glu", "outside the table", f("G", G), f("U", np.ones((8, 16))), 8, 16, -64, 128, f("mg", np.zeros(128)), g16, q)
+    stopped("zkob_glu", "mapped(0) == 0", t / "G", t / "U", 8, 16, -64, 128, f("mg1", np.ones(128)), g16, q)
+    f("o00.i32.bin", np.zeros((8, 8)))
+    f("o01.i32.bin", np.zeros((8, 7)))
+    stopped("zkob_headmerge", "file size != expected int32 count", t / "o", 8, 16, 8, "concat", g16, g8, q)
+    stopped("zkob_headslice", "HD must divide C", f("Q", np.zeros((8, 12))), t / "Q", t / "Q", 8, 12, 8, g16, g8, q)
+    stopped("zkob_rescale", "layout needs C_pad <= N <= D", f("X64", np.zeros((8, 16)), np.int64), 8, 16, 16, g16, q)
+    X = np.full((8, 16), 100, dtype=np.int32)
+    stopped("zkob_rmsnorm", "bracket violated", f("X", X), f("R", np.full(8, 5)), f("gain", np.ones(16)), 8, 16, 7, g16, g8, q)
+    stopped("zkob_rmsnorm", "gen_C size != C_pad", t / "X", t / "R", t / "gain", 8, 16, 7, g8, g8, q)
